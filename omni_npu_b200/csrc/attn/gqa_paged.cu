@@ -1,0 +1,715 @@
+// Paged grouped-query attention: variable-length causal prefill (with cached
+// context, so chunked prefill and prefix reuse work) and split-KV decode.
+//
+// K/V are read straight out of the paged cache
+//   k_cache [num_blocks, kv_heads, block_size, DQK],  v_cache [.., DV]
+// with 16-byte cp.async copies into swizzled shared-memory tiles, double /
+// triple buffered.  The matrix products run on mma.sync m16n8k16 (bf16 in,
+// fp32 accumulate); softmax is the usual online form in base 2.
+//
+// Prefill: one CTA = 128 query rows of one (sequence, q head); 8 warps x 16 rows.
+// Decode:  one CTA = one (sequence, kv head, kv split); the q heads of the group
+//          (times the query length for multi-token decode) form the 16 MMA rows;
+//          4 warps take 16 keys each of every 64-key tile and merge at the end.
+//          With more than one split the partial outputs and log-sum-exps go to
+//          fp32 scratch and a small kernel merges them.
+//
+// Replaces npu_fused_infer_attention_score in its TND paged form
+// (omni_npu/attention/backends/attention.py:216-281).
+
+#include "attn_common.cuh"
+
+namespace b200 {
+
+static constexpr float kLog2e = 1.4426950408889634f;
+
+// ------------------------------------------------------------------ prefill
+template <int DQK, int DV>
+struct PrefillCfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = 64;
+  static constexpr int THREADS = 256;
+  static constexpr int Q_BYTES = BM * DQK * 2;
+  static constexpr int K_BYTES = BN * DQK * 2;
+  static constexpr int V_BYTES = BN * DV * 2;
+  static constexpr int SMEM = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES;
+};
+
+struct AttnParams {
+  const __nv_bfloat16* q;     // [T, Hq, DQK]
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  __nv_bfloat16* out;         // [T, Hq, DV]
+  float* lse;                 // [T, Hq] or null (natural log)
+  const int* block_tables;    // [B, max_blocks]
+  const int* cu_q;            // [B+1] query start offsets (prefill) / null
+  const int* seq_lens;        // [B] total kv length including this step's tokens
+  int max_blocks;
+  int block_size;
+  int Hq, Hk;
+  long long q_stride;         // elements between tokens in q
+  long long out_stride;       // elements between tokens in out
+  float scale_log2;           // softmax scale * log2(e)
+  int causal;
+  int window;                 // sliding window (keys older than pos - window + 1 masked), 0 = off
+  // decode only
+  int q_len;                  // tokens per sequence in this step (>=1)
+  int splits;
+  float* o_part;              // [B, splits, 16, DV] fp32
+  float* lse_part;            // [B, splits, 16]   (per kv head: index includes head)
+};
+
+template <int ROW_ELEMS, int ROWS, int THREADS>
+__device__ __forceinline__ void load_kv_tile(uint8_t* smem_tile, const __nv_bfloat16* cache,
+                                             const int* block_table, int n0, int kv_len, int kvh,
+                                             int Hk, int block_size, int tid) {
+  constexpr int CHUNKS = ROW_ELEMS / 8;
+  constexpr int TOTAL = ROWS * CHUNKS;
+  constexpr int PER_THREAD = TOTAL / THREADS;
+  static_assert(TOTAL % THREADS == 0, "tile must divide evenly");
+  constexpr int THREADS_PER_ROW = CHUNKS / PER_THREAD;
+  static_assert(CHUNKS % PER_THREAD == 0, "row must divide evenly");
+  const int row = tid / THREADS_PER_ROW;
+  const int c0 = (tid % THREADS_PER_ROW) * PER_THREAD;
+  const int key = n0 + row;
+  const bool valid = key < kv_len;
+  const __nv_bfloat16* src = cache;
+  if (valid) {
+    const int blk = block_table[key / block_size];
+    const int off = key % block_size;
+    src = cache + ((static_cast<long long>(blk) * Hk + kvh) * block_size + off) * ROW_ELEMS;
+  }
+  const uint32_t base = smem_u32(smem_tile);
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = c0 + i;
+    const uint32_t dst = base + tile_offset<ROW_ELEMS>(row, c);
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src + c * 8),
+                 "r"(sz)
+                 : "memory");
+  }
+}
+
+template <int DQK, int DV>
+__global__ void __launch_bounds__(256, 1) gqa_prefill_kernel(const AttnParams p) {
+  using Cfg = PrefillCfg<DQK, DV>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + Cfg::Q_BYTES;
+  uint8_t* sV = sK + 2 * Cfg::K_BYTES;
+
+  const int b = blockIdx.z;
+  const int h = blockIdx.y;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int m0 = blockIdx.x * Cfg::BM;
+  if (m0 >= q_len) return;
+  const int kv_len = p.seq_lens[b];
+  const int ctx = kv_len - q_len;  // tokens already cached before this step's queries
+  const int kvh = h / (p.Hq / p.Hk);
+  const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- Q tile -> shared (rows beyond q_len are zero filled)
+  {
+    constexpr int CHUNKS = DQK / 8;
+    for (int idx = tid; idx < Cfg::BM * CHUNKS; idx += Cfg::THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      const bool valid = (m0 + row) < q_len;
+      const __nv_bfloat16* src =
+          p.q + (valid ? (static_cast<long long>(q_begin + m0 + row) * p.q_stride +
+                          static_cast<long long>(h) * DQK + c * 8)
+                       : 0);
+      const uint32_t dst = smem_u32(sQ) + tile_offset<DQK>(row, c);
+      const int sz = valid ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz)
+                   : "memory");
+    }
+  }
+  // Last key any row of this tile may see.
+  const int last_row = min(q_len, m0 + Cfg::BM) - 1;
+  const int kv_end = p.causal ? min(kv_len, ctx + last_row + 1) : kv_len;
+  int kv_start = 0;
+  if (p.window > 0) kv_start = max(0, ctx + m0 - p.window + 1) / Cfg::BN * Cfg::BN;
+  const int n_tiles = (kv_end - kv_start + Cfg::BN - 1) / Cfg::BN;
+
+  load_kv_tile<DQK, Cfg::BN, Cfg::THREADS>(sK, p.k_cache, bt, kv_start, kv_end, kvh, p.Hk,
+                                            p.block_size, tid);
+  load_kv_tile<DV, Cfg::BN, Cfg::THREADS>(sV, p.v_cache, bt, kv_start, kv_end, kvh, p.Hk,
+                                           p.block_size, tid);
+  cp_async_commit();
+
+  float o_acc[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY};
+  float row_sum[2] = {0.f, 0.f};
+  uint32_t q_frag[DQK / 16][4];
+
+  const int row_a = warp * 16 + (lane >> 2);  // tile-local rows of this thread: row_a, row_a + 8
+  const int pos_a = ctx + m0 + row_a;         // absolute position of row_a
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) {
+      const int n_next = kv_start + (it + 1) * Cfg::BN;
+      load_kv_tile<DQK, Cfg::BN, Cfg::THREADS>(sK + (stage ^ 1) * Cfg::K_BYTES, p.k_cache, bt,
+                                                n_next, kv_end, kvh, p.Hk, p.block_size, tid);
+      load_kv_tile<DV, Cfg::BN, Cfg::THREADS>(sV + (stage ^ 1) * Cfg::V_BYTES, p.v_cache, bt,
+                                               n_next, kv_end, kvh, p.Hk, p.block_size, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int ks = 0; ks < DQK / 16; ++ks) {
+        const uint32_t addr =
+            smem_u32(sQ) + tile_offset<DQK>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4));
+        ldmatrix_x4(q_frag[ks], addr);
+      }
+    }
+    const uint8_t* kt = sK + stage * Cfg::K_BYTES;
+    const uint8_t* vt = sV + stage * Cfg::V_BYTES;
+    const int n0 = kv_start + it * Cfg::BN;
+
+    // S = Q K^T : 16 rows x 64 keys per warp
+    float s[Cfg::BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < Cfg::BN / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < DQK / 16; ++ks) {
+#pragma unroll
+      for (int nt = 0; nt < Cfg::BN / 16; ++nt) {
+        uint32_t kf[4];
+        const int krow = nt * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int kchunk = ks * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(kf, smem_u32(kt) + tile_offset<DQK>(krow, kchunk));
+        mma_bf16_16816(s[2 * nt], q_frag[ks], kf[0], kf[1]);
+        mma_bf16_16816(s[2 * nt + 1], q_frag[ks], kf[2], kf[3]);
+      }
+    }
+    // mask + online softmax
+    const bool need_mask = (n0 + Cfg::BN > kv_end) ||
+                           (p.causal && (n0 + Cfg::BN - 1 > ctx + m0 + warp * 16)) ||
+                           (p.window > 0);
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < Cfg::BN / 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = s[i][j] * p.scale_log2;
+        if (need_mask) {
+          const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
+          const int pos = pos_a + ((j >> 1) << 3);
+          bool ok = key < kv_end;
+          if (p.causal) ok = ok && key <= pos;
+          if (p.window > 0) ok = ok && key > pos - p.window;
+          if (!ok) v = -INFINITY;
+        }
+        s[i][j] = v;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float tm = quad_max(tile_max[r]);
+      const float new_max = fmaxf(row_max[r], tm);
+      corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+      row_max[r] = new_max;
+      row_sum[r] *= corr[r];
+    }
+    const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
+                            row_max[1] == -INFINITY ? 0.f : row_max[1]};
+#pragma unroll
+    for (int i = 0; i < Cfg::BN / 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2f(s[i][j] - m_use[j >> 1]);
+        s[i][j] = e;
+        row_sum[j >> 1] += e;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) {
+      o_acc[i][0] *= corr[0];
+      o_acc[i][1] *= corr[0];
+      o_acc[i][2] *= corr[1];
+      o_acc[i][3] *= corr[1];
+    }
+    // O += P V
+#pragma unroll
+    for (int ks = 0; ks < Cfg::BN / 16; ++ks) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16x2(s[2 * ks][0], s[2 * ks][1]);
+      pa[1] = pack_bf16x2(s[2 * ks][2], s[2 * ks][3]);
+      pa[2] = pack_bf16x2(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      pa[3] = pack_bf16x2(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int dt = 0; dt < DV / 16; ++dt) {
+        uint32_t vf[4];
+        const int vrow = ks * 16 + (lane & 15);
+        const int vchunk = dt * 2 + (lane >> 4);
+        ldmatrix_x4_trans(vf, smem_u32(vt) + tile_offset<DV>(vrow, vchunk));
+        mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
+        mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
+      }
+    }
+    __syncthreads();
+  }
+
+  cp_async_wait<0>();
+  __syncthreads();
+  // ---- finalise: O / l, stage through the Q tile, 16-byte stores
+  float inv[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] = quad_sum(row_sum[r]);
+    inv[r] = row_sum[r] > 0.f ? 1.f / row_sum[r] : 0.f;
+  }
+  static_assert(DV <= DQK, "output staging reuses the Q tile");
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) {
+    const int col = i * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = warp * 16 + (lane >> 2) + r * 8;
+      const uint32_t v = pack_bf16x2(o_acc[i][2 * r] * inv[r], o_acc[i][2 * r + 1] * inv[r]);
+      uint8_t* dst = sQ + tile_offset<DQK>(row, col >> 3) + (col & 7) * 2;
+      *reinterpret_cast<uint32_t*>(dst) = v;
+    }
+  }
+  if (p.lse && (lane & 3) == 0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = m0 + warp * 16 + (lane >> 2) + r * 8;
+      if (row < q_len) {
+        const float l = row_sum[r] > 0.f ? (row_max[r] + log2f(row_sum[r])) / kLog2e : -INFINITY;
+        p.lse[static_cast<long long>(q_begin + row) * p.Hq + h] = l;
+      }
+    }
+  }
+  __syncwarp();
+  {
+    constexpr int CHUNKS = DV / 8;
+    // Each warp stores the 16 rows it owns.
+    for (int idx = lane; idx < 16 * CHUNKS; idx += 32) {
+      const int r = idx / CHUNKS, c = idx % CHUNKS;
+      const int row = warp * 16 + r;
+      if (m0 + row < q_len) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sQ + tile_offset<DQK>(row, c));
+        *reinterpret_cast<uint4*>(p.out + static_cast<long long>(q_begin + m0 + row) * p.out_stride +
+                                  static_cast<long long>(h) * DV + c * 8) = v;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------- decode
+template <int D>
+struct DecodeCfg {
+  static constexpr int BN = 64;
+  static constexpr int STAGES = 3;
+  static constexpr int THREADS = 128;
+  static constexpr int Q_BYTES = 16 * D * 2;
+  static constexpr int KV_BYTES = BN * D * 2;
+  static constexpr int SMEM = Q_BYTES + 2 * STAGES * KV_BYTES;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128) gqa_decode_kernel(const AttnParams p) {
+  using Cfg = DecodeCfg<D>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + Cfg::Q_BYTES;
+  uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
+
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int split = blockIdx.z;
+  const int G = p.Hq / p.Hk;
+  const int rows = G * p.q_len;  // <= 16
+  const int kv_len = p.seq_lens[b];
+  const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  const int n_tiles_all = (kv_len + Cfg::BN - 1) / Cfg::BN;
+  const int per = (n_tiles_all + p.splits - 1) / p.splits;
+  const int t_begin = split * per;
+  const int t_end = min(n_tiles_all, t_begin + per);
+  const int n_tiles = max(0, t_end - t_begin);
+
+  // Row r of the MMA tile = (query token r / G, q head kvh*G + r % G).
+  {
+    constexpr int CHUNKS = D / 8;
+    for (int idx = tid; idx < 16 * CHUNKS; idx += Cfg::THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      const bool valid = row < rows;
+      const int qi = row / G, hh = kvh * G + row % G;
+      const __nv_bfloat16* src =
+          p.q + (valid ? (static_cast<long long>(b * p.q_len + qi) * p.q_stride +
+                          static_cast<long long>(hh) * D + c * 8)
+                       : 0);
+      const uint32_t dst = smem_u32(sQ) + tile_offset<D>(row, c);
+      const int sz = valid ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz)
+                   : "memory");
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < Cfg::STAGES - 1; ++s) {
+    if (s < n_tiles) {
+      const int n0 = (t_begin + s) * Cfg::BN;
+      load_kv_tile<D, Cfg::BN, Cfg::THREADS>(sK + s * Cfg::KV_BYTES, p.k_cache, bt, n0, kv_len, kvh,
+                                              p.Hk, p.block_size, tid);
+      load_kv_tile<D, Cfg::BN, Cfg::THREADS>(sV + s * Cfg::KV_BYTES, p.v_cache, bt, n0, kv_len, kvh,
+                                              p.Hk, p.block_size, tid);
+    }
+    cp_async_commit();
+  }
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY};
+  float row_sum[2] = {0.f, 0.f};
+  uint32_t q_frag[D / 16][4];
+
+  const int r_a = lane >> 2;  // rows r_a and r_a + 8
+  int pos_r[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r_a + 8 * r;
+    pos_r[r] = kv_len - p.q_len + row / G;  // causal limit for this row's query token
+  }
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it % Cfg::STAGES;
+    {
+      const int nxt = it + Cfg::STAGES - 1;
+      if (nxt < n_tiles) {
+        const int ns = nxt % Cfg::STAGES;
+        const int n0 = (t_begin + nxt) * Cfg::BN;
+        load_kv_tile<D, Cfg::BN, Cfg::THREADS>(sK + ns * Cfg::KV_BYTES, p.k_cache, bt, n0, kv_len,
+                                                kvh, p.Hk, p.block_size, tid);
+        load_kv_tile<D, Cfg::BN, Cfg::THREADS>(sV + ns * Cfg::KV_BYTES, p.v_cache, bt, n0, kv_len,
+                                                kvh, p.Hk, p.block_size, tid);
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<Cfg::STAGES - 1>();
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(q_frag[ks], smem_u32(sQ) + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+    }
+    const uint8_t* kt = sK + stage * Cfg::KV_BYTES;
+    const uint8_t* vt = sV + stage * Cfg::KV_BYTES;
+    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;  // this warp's 16 keys
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kf[4];
+      const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int kchunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(kf, smem_u32(kt) + tile_offset<D>(krow, kchunk));
+      mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
+      mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
+        const int pos = pos_r[j >> 1];
+        bool ok = key <= pos && key < kv_len;
+        if (p.window > 0) ok = ok && key > pos - p.window;
+        const float v = ok ? s[i][j] * p.scale_log2 : -INFINITY;
+        s[i][j] = v;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float tm = quad_max(tile_max[r]);
+      const float new_max = fmaxf(row_max[r], tm);
+      corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+      row_max[r] = new_max;
+      row_sum[r] *= corr[r];
+    }
+    const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
+                            row_max[1] == -INFINITY ? 0.f : row_max[1]};
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2f(s[i][j] - m_use[j >> 1]);
+        s[i][j] = e;
+        row_sum[j >> 1] += e;
+      }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o_acc[i][0] *= corr[0];
+      o_acc[i][1] *= corr[0];
+      o_acc[i][2] *= corr[1];
+      o_acc[i][3] *= corr[1];
+    }
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(s[0][0], s[0][1]);
+    pa[1] = pack_bf16x2(s[0][2], s[0][3]);
+    pa[2] = pack_bf16x2(s[1][0], s[1][1]);
+    pa[3] = pack_bf16x2(s[1][2], s[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+      uint32_t vf[4];
+      const int vrow = warp * 16 + (lane & 15);
+      const int vchunk = dt * 2 + (lane >> 4);
+      ldmatrix_x4_trans(vf, smem_u32(vt) + tile_offset<D>(vrow, vchunk));
+      mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
+      mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps' partial results through shared memory
+  float* m_buf = reinterpret_cast<float*>(sK);          // [4][16]
+  float* l_buf = m_buf + 64;                            // [4][16]
+  float* o_buf = l_buf + 64;                            // [4][16][D]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] = quad_sum(row_sum[r]);
+    if ((lane & 3) == 0) {
+      m_buf[warp * 16 + r_a + 8 * r] = row_max[r];
+      l_buf[warp * 16 + r_a + 8 * r] = row_sum[r];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int col = i * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float* dst = o_buf + (static_cast<size_t>(warp) * 16 + r_a + 8 * r) * D + col;
+      dst[0] = o_acc[i][2 * r];
+      dst[1] = o_acc[i][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * (D / 4); idx += Cfg::THREADS) {
+    const int row = idx / (D / 4);
+    const int c4 = (idx % (D / 4)) * 4;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, m_buf[w * 16 + row]);
+    float l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = m_buf[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      l += l_buf[w * 16 + row] * f;
+      const float4 x = *reinterpret_cast<const float4*>(o_buf + (static_cast<size_t>(w) * 16 + row) * D + c4);
+      acc.x += x.x * f;
+      acc.y += x.y * f;
+      acc.z += x.z * f;
+      acc.w += x.w * f;
+    }
+    const int qi = row / G, hh = kvh * G + row % G;
+    if (p.splits == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint2 pk;
+      pk.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+      pk.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                                static_cast<long long>(hh) * D + c4) = pk;
+      if (p.lse && c4 == 0)
+        p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+            l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+    } else {
+      // partial: unnormalised numerator, base-2 max and sum
+      const size_t pr = ((static_cast<size_t>(b) * p.Hk + kvh) * p.splits + split) * 16 + row;
+      *reinterpret_cast<float4*>(p.o_part + pr * D + c4) = acc;
+      if (c4 == 0) {
+        p.lse_part[pr * 2] = m;
+        p.lse_part[pr * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// Merge of split-KV partials: one warp per (sequence, kv head, row).
+template <int D>
+__global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnParams p, int B) {
+  const int G = p.Hq / p.Hk;
+  const int rows = G * p.q_len;
+  const long long gw = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const long long total = static_cast<long long>(B) * p.Hk * rows;
+  if (gw >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int row = static_cast<int>(gw % rows);
+  const int kvh = static_cast<int>((gw / rows) % p.Hk);
+  const int b = static_cast<int>(gw / (static_cast<long long>(rows) * p.Hk));
+  const size_t base = (static_cast<size_t>(b) * p.Hk + kvh) * p.splits;
+  float m = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) m = fmaxf(m, p.lse_part[((base + s) * 16 + row) * 2]);
+  float l = 0.f;
+  float acc[D / 32];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < p.splits; ++s) {
+    const size_t pr = (base + s) * 16 + row;
+    const float ms = p.lse_part[pr * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    l += p.lse_part[pr * 2 + 1] * f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] += p.o_part[pr * D + i * 32 + lane] * f;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const int qi = row / G, hh = kvh * G + row % G;
+  __nv_bfloat16* dst = p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                       static_cast<long long>(hh) * D;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) dst[i * 32 + lane] = __float2bfloat16(acc[i] * inv);
+  if (p.lse && lane == 0)
+    p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+        l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+}
+
+template <int DQK, int DV>
+static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t stream) {
+  using Cfg = PrefillCfg<DQK, DV>;
+  auto kern = gqa_prefill_kernel<DQK, DV>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+        cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  dim3 grid((max_q_len + Cfg::BM - 1) / Cfg::BM, p.Hq, B);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+template <int D>
+static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
+  using Cfg = DecodeCfg<D>;
+  auto kern = gqa_decode_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+        cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  dim3 grid(B, p.Hk, p.splits);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (p.splits > 1) {
+    const long long warps = static_cast<long long>(B) * p.Hk * (p.Hq / p.Hk) * p.q_len;
+    gqa_decode_merge_kernel<D><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(p, B);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                float* lse, const int* block_tables, const int* cu_q,
+                                const int* seq_lens, int B, int max_q_len, int max_blocks,
+                                int block_size, int Hq, int Hk, int Dqk, int Dv, long long q_stride,
+                                long long out_stride, float scale, int causal, int window,
+                                cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (Hq % Hk != 0) return -1;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.block_tables = block_tables;
+  p.cu_q = cu_q;
+  p.seq_lens = seq_lens;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.Hq = Hq;
+  p.Hk = Hk;
+  p.q_stride = q_stride;
+  p.out_stride = out_stride;
+  p.scale_log2 = scale * kLog2e;
+  p.causal = causal;
+  p.window = window;
+  p.q_len = 0;
+  p.splits = 1;
+  if (Dqk == 128 && Dv == 128) return launch_prefill<128, 128>(p, B, max_q_len, stream);
+  if (Dqk == 64 && Dv == 64) return launch_prefill<64, 64>(p, B, max_q_len, stream);
+  if (Dqk == 192 && Dv == 128) return launch_prefill<192, 128>(p, B, max_q_len, stream);
+  return -2;
+}
+
+// Scratch needed by the decode kernel for a given split count (bytes).
+extern "C" size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits) {
+  if (splits <= 1) return 0;
+  return static_cast<size_t>(B) * Hk * splits * 16 * (static_cast<size_t>(D) + 2) * sizeof(float);
+}
+
+extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                               float* lse, const int* block_tables, const int* seq_lens, int B,
+                               int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
+                               long long q_stride, long long out_stride, float scale, int window,
+                               int splits, void* scratch, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (Hq % Hk != 0 || (Hq / Hk) * q_len > 16 || q_len < 1) return -1;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && scratch == nullptr) return -3;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.block_tables = block_tables;
+  p.cu_q = nullptr;
+  p.seq_lens = seq_lens;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.Hq = Hq;
+  p.Hk = Hk;
+  p.q_stride = q_stride;
+  p.out_stride = out_stride;
+  p.scale_log2 = scale * kLog2e;
+  p.causal = 1;
+  p.window = window;
+  p.q_len = q_len;
+  p.splits = splits;
+  if (splits > 1) {
+    p.o_part = static_cast<float*>(scratch);
+    p.lse_part = p.o_part + static_cast<size_t>(B) * Hk * splits * 16 * D;
+  }
+  if (D == 128) return launch_decode<128>(p, B, stream);
+  if (D == 64) return launch_decode<64>(p, B, stream);
+  return -2;
+}

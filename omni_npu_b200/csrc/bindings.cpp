@@ -1,0 +1,417 @@
+// torch.ops.omni_b200.* : tensor-level entry points of the sm_100a kernels.
+// The kernels themselves live in .cu files with plain C launchers (raw
+// pointers + stream); this file only validates tensors and forwards.
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include <tuple>
+
+extern "C" {
+void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, int force_bn, int force_splits,
+                    int* out_bn, int* out_splits, size_t* out_ws_bytes, int* out_counters);
+int b200_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
+              int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu,
+              int BN, int splits, void* workspace, int* counters, int* status, int max_ctas,
+              cudaStream_t stream);
+int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_offsets,
+                      int num_experts, int total_rows, int N, int K, int lda, int ldc,
+                      int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
+                      cudaStream_t stream);
+int b200_rmsnorm(void* out, const void* x, void* residual, const void* w, float eps, long long rows,
+                 int H, long long x_stride, long long out_stride, long long res_stride,
+                 cudaStream_t stream);
+int b200_silu_mul(void* out, const void* x, long long rows, int I, long long x_stride,
+                  long long out_stride, cudaStream_t stream);
+int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, int H,
+                         long long x_stride, int ue8m0, cudaStream_t stream);
+int b200_rope_qk(void* q, void* k, const int* positions, const float* cos_sin, int T, int Hq,
+                 int Hk, int D, int rot_dim, int neox, long long q_stride, long long k_stride,
+                 int sec_t, int sec_h, int interleaved_mrope, cudaStream_t stream);
+int b200_rope_cache_gqa(void* q, const void* k, const void* v, void* k_cache, void* v_cache,
+                        const int* positions, const int* slot_mapping, const float* cos_sin, int T,
+                        int Hq, int Hk, int D, int rot_dim, int neox, long long q_stride,
+                        long long k_stride, long long v_stride, int block_size,
+                        cudaStream_t stream);
+int b200_mla_kv_rmsnorm_rope_cache(const void* kv_c, const void* k_pe, const void* w, void* cache,
+                                   void* kv_c_out, void* k_pe_out, const int* positions,
+                                   const int* slot_mapping, const float* cos_sin, float eps, int T,
+                                   int L, int R, int neox, long long kvc_stride,
+                                   long long kpe_stride, long long cache_row_stride,
+                                   cudaStream_t stream);
+int b200_paged_scatter_rows(void* dst, const void* src, const int* slot_mapping, int T,
+                            int row_elems, long long src_stride, long long dst_row_stride,
+                            cudaStream_t stream);
+int b200_gqa_cache_write(const void* k, const void* v, void* k_cache, void* v_cache,
+                         const int* slot_mapping, int T, int Hk, int D, int Dv, long long k_stride,
+                         long long v_stride, int block_size, cudaStream_t stream);
+int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
+                     const int* block_tables, const int* cu_q, const int* seq_lens, int B,
+                     int max_q_len, int max_blocks, int block_size, int Hq, int Hk, int Dqk, int Dv,
+                     long long q_stride, long long out_stride, float scale, int causal, int window,
+                     cudaStream_t stream);
+size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits);
+int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
+                    const int* block_tables, const int* seq_lens, int B, int q_len, int max_blocks,
+                    int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
+                    float scale, int window, int splits, void* scratch, cudaStream_t stream);
+int b200_argmax(const void* logits, int* out, int B, int V, long long stride, int is_fp32,
+                cudaStream_t stream);
+int b200_sample(const void* logits, int* out, const float* temperature, const int* top_k,
+                const float* top_p, const long long* seeds, const long long* step_offset, int B,
+                int V, long long stride, int is_fp32, cudaStream_t stream);
+}
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "omni_b200::", what, " failed with code ", rc);
+}
+
+#define CHECK_CUDA_BF16(t) \
+  TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16, #t " must be a CUDA bf16 tensor")
+#define CHECK_I32(t) \
+  TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kInt && (t).is_contiguous(), #t " must be a contiguous CUDA int32 tensor")
+
+// (BN, splits, workspace bytes, counters) for a problem.
+std::tuple<int64_t, int64_t, int64_t, int64_t> gemm_plan(int64_t M, int64_t N, int64_t K,
+                                                         int64_t elem_bytes, bool swiglu,
+                                                         int64_t force_bn, int64_t force_splits) {
+  int bn, sp, cnt;
+  size_t ws;
+  b200_gemm_plan((int)M, (int)N, (int)K, (int)elem_bytes, swiglu ? 1 : 0, (int)force_bn,
+                 (int)force_splits, &bn, &sp, &ws, &cnt);
+  return {bn, sp, (int64_t)ws, cnt};
+}
+
+// C = A @ W^T (+bias) (+residual).  A [M,K], W [N,K]; bf16 or float8_e4m3fn.
+Tensor gemm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& bias,
+            const c10::optional<Tensor>& residual, bool out_fp32, bool swiglu, int64_t bn,
+            int64_t splits, const c10::optional<Tensor>& workspace,
+            const c10::optional<Tensor>& counters, const Tensor& status, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm: 2-D CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == w.scalar_type(), "gemm: dtype mismatch");
+  const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK(fp8 || a.scalar_type() == at::kBFloat16, "gemm: bf16 or float8_e4m3fn inputs");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1, "gemm: K must be contiguous");
+  const int M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "gemm: K mismatch");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int n_out = swiglu ? N / 2 : N;
+  Tensor c = torch::empty({M, n_out}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  const void* bias_p = nullptr;
+  const void* res_p = nullptr;
+  if (bias.has_value()) {
+    CHECK_CUDA_BF16(*bias);
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "gemm: bias [N]");
+    bias_p = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    CHECK_CUDA_BF16(*residual);
+    TORCH_CHECK(residual->is_contiguous() && residual->size(0) == M && residual->size(1) == n_out,
+                "gemm: residual [M,N] contiguous");
+    res_p = residual->data_ptr();
+  }
+  void* ws_p = nullptr;
+  int* cnt_p = nullptr;
+  if (splits > 1) {
+    TORCH_CHECK(workspace.has_value() && counters.has_value(), "gemm: split-K needs workspace");
+    ws_p = workspace->data_ptr();
+    cnt_p = counters->data_ptr<int>();
+  }
+  check(b200_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), bias_p, res_p, M, N, K,
+                  (int)a.stride(0), (int)w.stride(0), n_out, fp8 ? 1 : 0, out_fp32 ? 1 : 0,
+                  swiglu ? 1 : 0, (int)bn, (int)splits, ws_p, cnt_p, status.data_ptr<int>(),
+                  (int)max_ctas, cur_stream()),
+        "gemm");
+  return c;
+}
+
+Tensor grouped_gemm(const Tensor& a, const Tensor& w, const Tensor& expert_offsets, bool swiglu,
+                    int64_t bn, const Tensor& status, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 3, "grouped_gemm: shapes");
+  TORCH_CHECK(a.scalar_type() == w.scalar_type(), "grouped_gemm: dtype mismatch");
+  const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK(fp8 || a.scalar_type() == at::kBFloat16, "grouped_gemm: bf16 or fp8 inputs");
+  TORCH_CHECK(a.stride(1) == 1 && w.is_contiguous(), "grouped_gemm: contiguity");
+  CHECK_I32(expert_offsets);
+  const int E = w.size(0), N = w.size(1), K = w.size(2), rows = a.size(0);
+  TORCH_CHECK(a.size(1) == K && expert_offsets.numel() == E + 1, "grouped_gemm: size mismatch");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int n_out = swiglu ? N / 2 : N;
+  Tensor c = torch::empty({rows, n_out}, a.options().dtype(at::kBFloat16));
+  check(b200_grouped_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), expert_offsets.data_ptr<int>(),
+                          E, rows, N, K, (int)a.stride(0), n_out, fp8 ? 1 : 0, swiglu ? 1 : 0,
+                          (int)bn, status.data_ptr<int>(), (int)max_ctas, cur_stream()),
+        "grouped_gemm");
+  return c;
+}
+
+Tensor rms_norm(const Tensor& x, const Tensor& w, double eps) {
+  CHECK_CUDA_BF16(x);
+  CHECK_CUDA_BF16(w);
+  TORCH_CHECK(x.stride(-1) == 1, "rms_norm: last dim contiguous");
+  const int H = x.size(-1);
+  Tensor x2 = x.dim() == 2 ? x : x.reshape({-1, H});
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x2.size(0), H}, x.options());
+  check(b200_rmsnorm(out.data_ptr(), x2.data_ptr(), nullptr, w.data_ptr(), (float)eps, x2.size(0),
+                     H, x2.stride(0), H, 0, cur_stream()),
+        "rms_norm");
+  return out.view(x.sizes());
+}
+
+// residual <- x + residual ; returns norm(residual) * w
+Tensor fused_add_rms_norm(const Tensor& x, Tensor residual, const Tensor& w, double eps) {
+  CHECK_CUDA_BF16(x);
+  CHECK_CUDA_BF16(residual);
+  CHECK_CUDA_BF16(w);
+  TORCH_CHECK(x.dim() == 2 && residual.dim() == 2 && x.stride(1) == 1 && residual.stride(1) == 1,
+              "fused_add_rms_norm: 2-D, last dim contiguous");
+  const int H = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), H}, x.options());
+  check(b200_rmsnorm(out.data_ptr(), x.data_ptr(), residual.data_ptr(), w.data_ptr(), (float)eps,
+                     x.size(0), H, x.stride(0), H, residual.stride(0), cur_stream()),
+        "fused_add_rms_norm");
+  return out;
+}
+
+Tensor silu_and_mul(const Tensor& x) {
+  CHECK_CUDA_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "silu_and_mul: 2-D, last dim contiguous");
+  const int I = x.size(1) / 2;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), I}, x.options());
+  check(b200_silu_mul(out.data_ptr(), x.data_ptr(), x.size(0), I, x.stride(0), I, cur_stream()),
+        "silu_and_mul");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> quant_fp8_1x128(const Tensor& x, bool ue8m0) {
+  CHECK_CUDA_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "quant_fp8_1x128: 2-D, last dim contiguous");
+  const int H = x.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = torch::empty({x.size(0), H}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor s = torch::empty({x.size(0), H / 128}, x.options().dtype(at::kFloat));
+  check(b200_quant_fp8_1x128(q.data_ptr(), s.data_ptr(), x.data_ptr(), x.size(0), H, x.stride(0),
+                             ue8m0 ? 1 : 0, cur_stream()),
+        "quant_fp8_1x128");
+  return {q, s};
+}
+
+void rope_qk(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin, int64_t head_dim,
+             int64_t rot_dim, bool neox, int64_t sec_t, int64_t sec_h, bool interleaved) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(k);
+  CHECK_I32(positions);
+  TORCH_CHECK(cos_sin.is_cuda() && cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous(),
+              "rope: cos_sin must be contiguous fp32");
+  TORCH_CHECK(q.dim() == 2 && k.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1, "rope: [T, H*D]");
+  const int T = q.size(0);
+  c10::cuda::CUDAGuard guard(q.device());
+  check(b200_rope_qk(q.data_ptr(), k.data_ptr(), positions.data_ptr<int>(),
+                     cos_sin.data_ptr<float>(), T, (int)(q.size(1) / head_dim),
+                     (int)(k.size(1) / head_dim), (int)head_dim, (int)rot_dim, neox ? 1 : 0,
+                     q.stride(0), k.stride(0), (int)sec_t, (int)sec_h, interleaved ? 1 : 0,
+                     cur_stream()),
+        "rope_qk");
+}
+
+void rope_cache_gqa(Tensor q, const Tensor& k, const Tensor& v, Tensor k_cache, Tensor v_cache,
+                    const Tensor& positions, const Tensor& slot_mapping, const Tensor& cos_sin,
+                    int64_t head_dim, int64_t rot_dim, bool neox) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(k);
+  CHECK_CUDA_BF16(v);
+  CHECK_CUDA_BF16(k_cache);
+  CHECK_CUDA_BF16(v_cache);
+  CHECK_I32(positions);
+  CHECK_I32(slot_mapping);
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(),
+              "cache: [blocks, kv_heads, block_size, D] contiguous");
+  TORCH_CHECK(q.dim() == 2 && k.dim() == 2 && v.dim() == 2, "rope_cache: [T, H*D] views");
+  const int T = q.size(0);
+  const int Hk = k_cache.size(1), bs = k_cache.size(2);
+  c10::cuda::CUDAGuard guard(q.device());
+  check(b200_rope_cache_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), k_cache.data_ptr(),
+                            v_cache.data_ptr(), positions.data_ptr<int>(),
+                            slot_mapping.data_ptr<int>(), cos_sin.data_ptr<float>(), T,
+                            (int)(q.size(1) / head_dim), Hk, (int)head_dim, (int)rot_dim,
+                            neox ? 1 : 0, q.stride(0), k.stride(0), v.stride(0), bs, cur_stream()),
+        "rope_cache_gqa");
+}
+
+void mla_kv_rmsnorm_rope_cache(const Tensor& kv_c, const Tensor& k_pe, const Tensor& w, Tensor cache,
+                               const c10::optional<Tensor>& kv_c_out,
+                               const c10::optional<Tensor>& k_pe_out, const Tensor& positions,
+                               const Tensor& slot_mapping, const Tensor& cos_sin, double eps,
+                               bool neox) {
+  CHECK_CUDA_BF16(kv_c);
+  CHECK_CUDA_BF16(k_pe);
+  CHECK_CUDA_BF16(cache);
+  CHECK_I32(positions);
+  CHECK_I32(slot_mapping);
+  const int T = kv_c.size(0), L = kv_c.size(1), R = k_pe.size(1);
+  TORCH_CHECK(cache.is_contiguous() && cache.size(-1) >= L + R, "mla cache row too small");
+  c10::cuda::CUDAGuard guard(kv_c.device());
+  check(b200_mla_kv_rmsnorm_rope_cache(
+            kv_c.data_ptr(), k_pe.data_ptr(), w.data_ptr(), cache.data_ptr(),
+            kv_c_out.has_value() ? kv_c_out->data_ptr() : nullptr,
+            k_pe_out.has_value() ? k_pe_out->data_ptr() : nullptr, positions.data_ptr<int>(),
+            slot_mapping.data_ptr<int>(), cos_sin.data_ptr<float>(), (float)eps, T, L, R,
+            neox ? 1 : 0, kv_c.stride(0), k_pe.stride(0), cache.size(-1), cur_stream()),
+        "mla_kv_rmsnorm_rope_cache");
+}
+
+void paged_scatter_rows(Tensor dst, const Tensor& src, const Tensor& slot_mapping) {
+  CHECK_CUDA_BF16(dst);
+  CHECK_CUDA_BF16(src);
+  CHECK_I32(slot_mapping);
+  TORCH_CHECK(dst.is_contiguous() && src.dim() == 2 && src.stride(1) == 1, "paged_scatter_rows");
+  c10::cuda::CUDAGuard guard(src.device());
+  check(b200_paged_scatter_rows(dst.data_ptr(), src.data_ptr(), slot_mapping.data_ptr<int>(),
+                                (int)src.size(0), (int)src.size(1), src.stride(0), dst.size(-1),
+                                cur_stream()),
+        "paged_scatter_rows");
+}
+
+void gqa_cache_write(const Tensor& k, const Tensor& v, Tensor k_cache, Tensor v_cache,
+                     const Tensor& slot_mapping) {
+  CHECK_CUDA_BF16(k);
+  CHECK_CUDA_BF16(v);
+  CHECK_I32(slot_mapping);
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "cache layout");
+  const int Hk = k_cache.size(1), bs = k_cache.size(2), D = k_cache.size(3), Dv = v_cache.size(3);
+  c10::cuda::CUDAGuard guard(k.device());
+  check(b200_gqa_cache_write(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                             slot_mapping.data_ptr<int>(), (int)k.size(0), Hk, D, Dv, k.stride(0),
+                             v.stride(0), bs, cur_stream()),
+        "gqa_cache_write");
+}
+
+std::tuple<Tensor, Tensor> gqa_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                                       const Tensor& block_tables, const Tensor& cu_q,
+                                       const Tensor& seq_lens, int64_t num_seqs, int64_t max_q_len,
+                                       int64_t num_q_heads, double scale, bool causal,
+                                       int64_t window, bool return_lse) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(k_cache);
+  CHECK_CUDA_BF16(v_cache);
+  CHECK_I32(block_tables);
+  CHECK_I32(cu_q);
+  CHECK_I32(seq_lens);
+  TORCH_CHECK(q.dim() == 2 && q.stride(1) == 1, "gqa_prefill: q [T, Hq*D]");
+  const int T = q.size(0);
+  const int Hk = k_cache.size(1), bs = k_cache.size(2), Dqk = k_cache.size(3), Dv = v_cache.size(3);
+  const int Hq = num_q_heads;
+  TORCH_CHECK(q.size(1) == (int64_t)Hq * Dqk, "gqa_prefill: q width");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({T, (int64_t)Hq * Dv}, q.options());
+  Tensor lse = return_lse ? torch::empty({T, Hq}, q.options().dtype(at::kFloat)) : Tensor();
+  check(b200_gqa_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                         return_lse ? lse.data_ptr<float>() : nullptr, block_tables.data_ptr<int>(),
+                         cu_q.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)num_seqs,
+                         (int)max_q_len, (int)block_tables.size(1), bs, Hq, Hk, Dqk, Dv,
+                         q.stride(0), out.stride(0), (float)scale, causal ? 1 : 0, (int)window,
+                         cur_stream()),
+        "gqa_prefill");
+  return {out, lse};
+}
+
+int64_t gqa_decode_scratch_bytes(int64_t B, int64_t Hk, int64_t D, int64_t splits) {
+  return (int64_t)b200_gqa_decode_scratch_bytes((int)B, (int)Hk, (int)D, (int)splits);
+}
+
+Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
+                  const Tensor& block_tables, const Tensor& seq_lens, int64_t num_seqs,
+                  int64_t q_len, int64_t num_q_heads, double scale, int64_t window, int64_t splits,
+                  const c10::optional<Tensor>& scratch) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(k_cache);
+  CHECK_CUDA_BF16(v_cache);
+  CHECK_I32(block_tables);
+  CHECK_I32(seq_lens);
+  const int Hk = k_cache.size(1), bs = k_cache.size(2), D = k_cache.size(3);
+  const int Hq = num_q_heads;
+  TORCH_CHECK(q.dim() == 2 && q.stride(1) == 1 && q.size(1) == (int64_t)Hq * D, "gqa_decode: q");
+  TORCH_CHECK(q.size(0) >= num_seqs * q_len, "gqa_decode: q rows");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({q.size(0), (int64_t)Hq * D}, q.options());
+  void* sp = nullptr;
+  if (splits > 1) {
+    TORCH_CHECK(scratch.has_value(), "gqa_decode: scratch required for splits > 1");
+    TORCH_CHECK((int64_t)scratch->nbytes() >=
+                    (int64_t)b200_gqa_decode_scratch_bytes((int)num_seqs, Hk, D, (int)splits),
+                "gqa_decode: scratch too small");
+    sp = scratch->data_ptr();
+  }
+  check(b200_gqa_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                        nullptr, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
+                        (int)num_seqs, (int)q_len, (int)block_tables.size(1), bs, Hq, Hk, D,
+                        q.stride(0), out.stride(0), (float)scale, (int)window, (int)splits, sp,
+                        cur_stream()),
+        "gqa_decode");
+  return out;
+}
+
+Tensor argmax(const Tensor& logits) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "argmax: [B,V]");
+  const bool f32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || logits.scalar_type() == at::kBFloat16, "argmax: fp32 or bf16");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty({logits.size(0)}, logits.options().dtype(at::kInt));
+  check(b200_argmax(logits.data_ptr(), out.data_ptr<int>(), (int)logits.size(0),
+                    (int)logits.size(1), logits.stride(0), f32 ? 1 : 0, cur_stream()),
+        "argmax");
+  return out;
+}
+
+Tensor sample(const Tensor& logits, const c10::optional<Tensor>& temperature,
+              const c10::optional<Tensor>& top_k, const c10::optional<Tensor>& top_p,
+              const c10::optional<Tensor>& seeds, const c10::optional<Tensor>& step_offset) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "sample: [B,V]");
+  const bool f32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || logits.scalar_type() == at::kBFloat16, "sample: fp32 or bf16");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty({logits.size(0)}, logits.options().dtype(at::kInt));
+  check(b200_sample(logits.data_ptr(), out.data_ptr<int>(),
+                    temperature.has_value() ? temperature->data_ptr<float>() : nullptr,
+                    top_k.has_value() ? top_k->data_ptr<int>() : nullptr,
+                    top_p.has_value() ? top_p->data_ptr<float>() : nullptr,
+                    seeds.has_value() ? (const long long*)seeds->data_ptr<int64_t>() : nullptr,
+                    step_offset.has_value() ? (const long long*)step_offset->data_ptr<int64_t>() : nullptr,
+                    (int)logits.size(0), (int)logits.size(1), logits.stride(0), f32 ? 1 : 0,
+                    cur_stream()),
+        "sample");
+  return out;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(omni_b200, m) {
+  m.def("gemm_plan", &gemm_plan);
+  m.def("gemm", &gemm);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("rms_norm", &rms_norm);
+  m.def("fused_add_rms_norm", &fused_add_rms_norm);
+  m.def("silu_and_mul", &silu_and_mul);
+  m.def("quant_fp8_1x128", &quant_fp8_1x128);
+  m.def("rope_qk", &rope_qk);
+  m.def("rope_cache_gqa", &rope_cache_gqa);
+  m.def("mla_kv_rmsnorm_rope_cache", &mla_kv_rmsnorm_rope_cache);
+  m.def("paged_scatter_rows", &paged_scatter_rows);
+  m.def("gqa_cache_write", &gqa_cache_write);
+  m.def("gqa_prefill", &gqa_prefill);
+  m.def("gqa_decode_scratch_bytes", &gqa_decode_scratch_bytes);
+  m.def("gqa_decode", &gqa_decode);
+  m.def("argmax", &argmax);
+  m.def("sample", &sample);
+}

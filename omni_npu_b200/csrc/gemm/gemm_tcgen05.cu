@@ -1,0 +1,715 @@
+// Dense and grouped (per-expert) GEMM for sm_100a on the 5th-generation
+// tensor cores:   C[M,N] = A[M,K] * W[N,K]^T   (bf16 or fp8-e4m3 in, fp32 accumulate).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A tile (128 x 64
+//               elements... 128 bytes per row) and the W tile (BN rows) into a
+//               ring of 128B-swizzled shared-memory stages.  Plain per-CTA loads
+//               only; no cluster multicast anywhere.
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN,
+//               K=16 for bf16 / 32 for fp8) with the accumulator in TMEM.  Two
+//               accumulator buffers let the epilogue of tile i overlap the
+//               main loop of tile i+1.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, apply bias / residual /
+//               SwiGLU, convert and store.  With split-K the partial sums go to
+//               an fp32 workspace and the last CTA to finish a tile reduces them.
+//
+// BN is a run-time value (multiple of 16, 16..256) so the host can pick a tile
+// width that fills the 148 SMs in a whole number of waves.
+//
+// Every barrier wait is bounded; on a timeout the kernel records a status code,
+// drains what it has in flight, frees its TMEM columns and returns.
+//
+// Replaces the reference's torch.matmul / npu_quant_matmul / npu_grouped_matmul
+// call sites (omni_npu/v1/layers/linear.py:124-130,
+// omni_npu/layers/fused_moe/npu_moe_permute_unpermute.py:108-149).
+
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+
+namespace b200 {
+
+static constexpr int kBM = 128;          // rows of A per tile (UMMA M)
+static constexpr int kRowBytes = 128;    // bytes of K per stage row (one swizzle span)
+static constexpr int kThreads = 192;
+static constexpr int kMaxExperts = 512;
+
+struct GemmParams {
+  int M, N, K;            // problem (grouped: M = total packed rows)
+  int BN;                 // tile width
+  int stages;             // shared-memory ring depth
+  int k_iters;            // ceil(K_bytes / 128)
+  int splits;             // split-K factor (>=1)
+  int num_m_blocks;       // dense only
+  int num_n_blocks;
+  int elem_bytes;         // 2 (bf16) or 1 (fp8)
+  int tmem_cols;          // power of two >= 2*acc stride
+  int acc_stride;         // TMEM column distance between the two accumulators
+  int ldc;                // row pitch of C in elements
+  int out_fp32;           // 1: C is fp32, 0: bf16
+  int swiglu;             // 1: C[:, n/2] = silu(acc[gate]) * acc[up], gate/up interleaved per 16 cols
+  int num_experts;        // grouped: number of local experts (0 = dense)
+  void* C;
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* residual;   // [M, ldc] or null
+  float* workspace;                // split-K partials [splits][M_pad][N_pad]
+  int* tile_counters;              // split-K arrival counters, one per (m,n) tile, zero at rest
+  const int* expert_offsets;       // grouped: [E+1] row offsets into A / C (device)
+  const float* a_scales;           // fp8: [M, ceil(K/128)] per-row-per-128 scales or null
+  const float* w_scales;           // fp8: [E][ceil(N/128)][ceil(K/128)] block scales or null
+  int* status;                     // error word (0 = ok)
+};
+
+struct TileCoord {
+  int m0;        // first row in A / C
+  int m_end;     // one past the last valid row
+  int n0;        // first column
+  int expert;    // weight slab
+  int k_begin;   // first k iteration
+  int k_end;     // one past last k iteration
+  int split;     // split index
+  int mn_index;  // index of the (m,n) tile for split-K bookkeeping
+};
+
+template <bool GROUPED>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const int* s_tile_prefix,
+                                            int total_mn_tiles, long long t, int& cursor,
+                                            TileCoord& tc) {
+  const long long total = static_cast<long long>(total_mn_tiles) * p.splits;
+  if (t >= total) return false;
+  const int split = static_cast<int>(t % p.splits);
+  const int mn = static_cast<int>(t / p.splits);
+  tc.split = split;
+  tc.mn_index = mn;
+  const int per = (p.k_iters + p.splits - 1) / p.splits;
+  tc.k_begin = split * per;
+  tc.k_end = min(p.k_iters, tc.k_begin + per);
+  if constexpr (!GROUPED) {
+    const int mb = mn % p.num_m_blocks;
+    const int nb = mn / p.num_m_blocks;
+    tc.m0 = mb * kBM;
+    tc.m_end = min(p.M, tc.m0 + kBM);
+    tc.n0 = nb * p.BN;
+    tc.expert = 0;
+  } else {
+    // s_tile_prefix[e] = number of m-blocks of experts < e.  n is fastest so the
+    // CTAs that run together share one expert's A rows and sweep its weights.
+    const int mblk_global = mn / p.num_n_blocks;
+    const int nb = mn % p.num_n_blocks;
+    while (cursor + 1 < p.num_experts && s_tile_prefix[cursor + 1] <= mblk_global) ++cursor;
+    const int e = cursor;
+    const int mb = mblk_global - s_tile_prefix[e];
+    const int row0 = p.expert_offsets[e];
+    const int row1 = p.expert_offsets[e + 1];
+    tc.m0 = row0 + mb * kBM;
+    tc.m_end = min(row1, tc.m0 + kBM);
+    tc.n0 = nb * p.BN;
+    tc.expert = e;
+  }
+  return true;
+}
+
+template <bool GROUPED, bool FP8>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the 128B swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int a_stage_bytes = kBM * kRowBytes;
+  const int w_stage_bytes = p.BN * kRowBytes;
+  uint8_t* smem_a = smem;
+  uint8_t* smem_w = smem + p.stages * a_stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes);
+  uint64_t* full_bar = bars;                    // [stages]
+  uint64_t* empty_bar = bars + p.stages;        // [stages]
+  uint64_t* tmem_full = bars + 2 * p.stages;    // [2]
+  uint64_t* tmem_empty = tmem_full + 2;         // [2]
+  uint64_t* drain_bar = tmem_empty + 2;         // [1]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  int* s_flags = reinterpret_cast<int*>(tmem_base_slot + 1);  // [0]=abort, [1]=is_last
+  int* s_tile_prefix = s_flags + 2;                           // [num_experts + 1] (grouped)
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], 4);
+    mbar_init(&tmem_empty[1], 4);
+    mbar_init(drain_bar, 1);
+    s_flags[0] = 0;
+    s_flags[1] = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
+  }
+  int total_mn_tiles;
+  if constexpr (GROUPED) {
+    if (threadIdx.x == 32) {
+      int acc = 0;
+      for (int e = 0; e < p.num_experts; ++e) {
+        s_tile_prefix[e] = acc;
+        const int rows = p.expert_offsets[e + 1] - p.expert_offsets[e];
+        acc += (rows + kBM - 1) / kBM;
+      }
+      s_tile_prefix[p.num_experts] = acc;
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, static_cast<uint32_t>(p.tmem_cols));
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+  if constexpr (GROUPED) {
+    total_mn_tiles = s_tile_prefix[p.num_experts] * p.num_n_blocks;
+  } else {
+    total_mn_tiles = p.num_m_blocks * p.num_n_blocks;
+  }
+
+  volatile int* abort_flag = s_flags;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int cursor = 0;
+      long long issued = 0;
+      bool ok = true;
+      TileCoord tc;
+      for (long long t = blockIdx.x; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
+                                                                cursor, tc);
+           t += gridDim.x) {
+        for (int k = tc.k_begin; k < tc.k_end; ++k) {
+          if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage],
+                                static_cast<uint32_t>(a_stage_bytes + w_stage_bytes));
+          const int kcoord = k * (kRowBytes / p.elem_bytes);
+          tma_load_2d(smem_a + stage * a_stage_bytes, &tmap_a, &full_bar[stage], kcoord, tc.m0);
+          if constexpr (GROUPED) {
+            tma_load_3d(smem_w + stage * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0,
+                        tc.expert);
+          } else {
+            tma_load_2d(smem_w + stage * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0);
+          }
+          ++issued;
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Abort path: wait (bounded) until the loads already issued have landed
+        // so that no bulk copy writes into shared memory after the CTA retires.
+        const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) {
+            s = p.stages - 1;
+            ph ^= 1;
+          }
+          mbar_wait(&full_bar[s], ph);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = FP8 ? make_idesc(0, 0, kBM, p.BN) : make_idesc(1, 1, kBM, p.BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      int cursor = 0;
+      bool ok = true;
+      TileCoord tc;
+      for (long long t = blockIdx.x; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
+                                                                cursor, tc);
+           t += gridDim.x) {
+        if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutTmemEmpty);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
+        for (int k = tc.k_begin; k < tc.k_end; ++k) {
+          if (*abort_flag || !mbar_wait(&full_bar[stage], phase)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes));
+          const uint64_t w_desc = make_smem_desc_sw128(smem_u32(smem_w + stage * w_stage_bytes));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            // 32 bytes of K per instruction: advance the start-address field by 2.
+            const uint32_t accum = (k > tc.k_begin || kk > 0) ? 1u : 0u;
+            if constexpr (FP8) {
+              umma_f8(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
+            } else {
+              umma_f16(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
+            }
+          }
+          tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs retire
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int cursor = 0;
+    TileCoord tc;
+    for (long long t = blockIdx.x;
+         decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cursor, tc); t += gridDim.x) {
+      bool ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
+      {
+        // The four epilogue warps take the decision together (barrier + AND
+        // reduction) so that none of them is left alone at a later barrier.
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(all_ok)
+            : "r"(ok ? 1u : 0u)
+            : "memory");
+        ok = all_ok != 0;
+      }
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutTmemFull);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tc.m0 + quarter * 32 + lane;
+      const bool row_ok = row < tc.m_end;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * p.acc_stride);
+      const bool partial = p.splits > 1;
+      float* ws_row = nullptr;
+      if (partial) {
+        // workspace layout: [split][mn_tile][128 rows][BN cols]
+        ws_row = p.workspace +
+                 ((static_cast<size_t>(tc.split) * total_mn_tiles + tc.mn_index) * kBM +
+                  (quarter * 32 + lane)) *
+                     p.BN;
+      }
+      for (int c = 0; c < p.BN; c += 16) {
+        uint32_t r[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+              "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(t_row + static_cast<uint32_t>(c))
+            : "memory");
+        tmem_ld_wait();
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+        const int col = tc.n0 + c;
+        if (partial) {
+          float4* dst = reinterpret_cast<float4*>(ws_row + c);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          continue;
+        }
+        if (!row_ok || col >= p.N) continue;
+        if (p.swiglu) {
+          // Columns [c, c+8) hold gate values, [c+8, c+16) the matching up values.
+          const int ocol = col >> 1;
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float g = v[i];
+            o[i] = (g / (1.f + __expf(-g))) * v[8 + i];
+          }
+          __nv_bfloat16* dst =
+              reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + ocol;
+          uint4 pk;
+          pk.x = pack_bf16x2(o[0], o[1]);
+          pk.y = pack_bf16x2(o[2], o[3]);
+          pk.z = pack_bf16x2(o[4], o[5]);
+          pk.w = pack_bf16x2(o[6], o[7]);
+          *reinterpret_cast<uint4*>(dst) = pk;
+          continue;
+        }
+        const int ncols = min(16, p.N - col);
+        if (p.bias) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (i < ncols) v[i] += __bfloat162float(p.bias[col + i]);
+        }
+        if (p.residual) {
+          const __nv_bfloat16* rsd = p.residual + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (i < ncols) v[i] += __bfloat162float(rsd[i]);
+        }
+        if (p.out_fp32) {
+          float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+          if (ncols == 16 && (p.ldc & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<float4*>(dst)[i] =
+                  make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            for (int i = 0; i < ncols; ++i) dst[i] = v[i];
+          }
+        } else {
+          __nv_bfloat16* dst =
+              reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+          if (ncols == 16 && (p.ldc & 7) == 0) {
+            uint4 pk0, pk1;
+            pk0.x = pack_bf16x2(v[0], v[1]);
+            pk0.y = pack_bf16x2(v[2], v[3]);
+            pk0.z = pack_bf16x2(v[4], v[5]);
+            pk0.w = pack_bf16x2(v[6], v[7]);
+            pk1.x = pack_bf16x2(v[8], v[9]);
+            pk1.y = pack_bf16x2(v[10], v[11]);
+            pk1.z = pack_bf16x2(v[12], v[13]);
+            pk1.w = pack_bf16x2(v[14], v[15]);
+            reinterpret_cast<uint4*>(dst)[0] = pk0;
+            reinterpret_cast<uint4*>(dst)[1] = pk1;
+          } else {
+            for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
+          }
+        }
+      }
+      // Accumulator buffer is free for the MMA warp again.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+
+      if (partial) {
+        // Split-K fix-up: the last CTA to arrive at this (m,n) tile sums the
+        // partials in split order (deterministic) and writes the result.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int old = atomicAdd(&p.tile_counters[tc.mn_index], 1);
+          const int last = (old == p.splits - 1) ? 1 : 0;
+          if (last) p.tile_counters[tc.mn_index] = 0;  // leave the counter at rest
+          s_flags[1] = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool is_last = s_flags[1] != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (is_last) {
+          __threadfence();
+          if (row_ok) {
+            const size_t split_stride = static_cast<size_t>(total_mn_tiles) * kBM * p.BN;
+            const float* base =
+                p.workspace +
+                (static_cast<size_t>(tc.mn_index) * kBM + (quarter * 32 + lane)) * p.BN;
+            for (int c = 0; c < p.BN; c += 4) {
+              const int col = tc.n0 + c;
+              if (col >= p.N) break;
+              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int sp = 0; sp < p.splits; ++sp) {
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(base + sp * split_stride + c));
+                s.x += x.x;
+                s.y += x.y;
+                s.z += x.z;
+                s.w += x.w;
+              }
+              float v[4] = {s.x, s.y, s.z, s.w};
+              const int ncols = min(4, p.N - col);
+              for (int i = 0; i < ncols; ++i) {
+                if (p.bias) v[i] += __bfloat162float(p.bias[col + i]);
+                if (p.residual)
+                  v[i] += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ldc + col + i]);
+              }
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+                for (int i = 0; i < ncols; ++i) dst[i] = v[i];
+              } else {
+                __nv_bfloat16* dst =
+                    reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+                if (ncols == 4 && (p.ldc & 3) == 0) {
+                  uint2 pk;
+                  pk.x = pack_bf16x2(v[0], v[1]);
+                  pk.y = pack_bf16x2(v[2], v[3]);
+                  *reinterpret_cast<uint2*>(dst) = pk;
+                } else {
+                  for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag && lane == 0) {
+      // Give MMAs still in flight a bounded time to retire before TMEM goes away.
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0);
+    }
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct GemmPlan {
+  int BN;
+  int splits;
+  int stages;
+};
+
+static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Cost model used to choose the tile width and split-K factor.  All rates are
+// per SM; the model only has to rank candidates, not predict time.
+static GemmPlan plan_gemm(int M, int N, int K, int elem_bytes, int sms, bool allow_split,
+                          bool swiglu) {
+  const int k_iters = (K * elem_bytes + kRowBytes - 1) / kRowBytes;
+  const int m_blocks = (M + kBM - 1) / kBM;
+  const double sm_ingest = 90e9;                              // bytes/s one SM can pull from L2
+  const double sm_flops = (elem_bytes == 1 ? 2.8e15 : 1.4e15) / 148.0;
+  const double hbm = 6.5e12;
+  double best = 1e30;
+  GemmPlan bestp{128, 1, 4};
+  for (int bn = 256; bn >= 32; bn -= 16) {
+    if (swiglu && (bn % 32) != 0) continue;
+    if (bn > round_up(N, 16) && bn != 32) continue;
+    const int n_blocks = (N + bn - 1) / bn;
+    const long long tiles = static_cast<long long>(m_blocks) * n_blocks;
+    const int max_split = allow_split ? 8 : 1;
+    for (int sp = 1; sp <= max_split; ++sp) {
+      const int per = (k_iters + sp - 1) / sp;
+      if (sp > 1 && (per < 8 || (sp - 1) * per >= k_iters)) continue;
+      const long long ctas = tiles * sp;
+      const double rows_a = M < kBM ? M : kBM;
+      const double bytes_cta = (rows_a + bn) * per * static_cast<double>(kRowBytes);
+      const double flops_cta = 2.0 * kBM * bn * per * (kRowBytes / elem_bytes);
+      double t_cta = bytes_cta / sm_ingest;
+      const double t_f = flops_cta / sm_flops;
+      if (t_f > t_cta) t_cta = t_f;
+      t_cta += 1.5e-6 + (sp > 1 ? 1.0e-6 : 0.0);
+      const double waves = static_cast<double>((ctas + sms - 1) / sms);
+      double t = waves * t_cta;
+      double unique = (static_cast<double>(M) * K + static_cast<double>(N) * K) * elem_bytes +
+                      static_cast<double>(M) * N * 2;
+      if (sp > 1) unique += 2.0 * sp * static_cast<double>(m_blocks) * kBM * n_blocks * bn * 4;
+      const double t_hbm = unique / hbm;
+      if (t_hbm > t) t = t_hbm;
+      if (sp > 1) t += 2.0 * sp * static_cast<double>(m_blocks) * kBM * n_blocks * bn * 4 / hbm * 0.5;
+      if (t < best * 0.999) {
+        best = t;
+        bestp.BN = bn;
+        bestp.splits = sp;
+      }
+    }
+  }
+  const int stage_bytes = kBM * kRowBytes + bestp.BN * kRowBytes;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  bestp.stages = stages;
+  return bestp;
+}
+
+static size_t smem_bytes_for(int BN, int stages, int num_experts) {
+  return 1024 + static_cast<size_t>(stages) * (kBM * kRowBytes + BN * kRowBytes) +
+         (2 * stages + 5) * 8 + 16 + (num_experts + 2) * 4 + 64;
+}
+
+static int next_pow2_cols(int x) {
+  int c = 32;
+  while (c < x) c <<= 1;
+  return c;
+}
+
+template <bool GROUPED, bool FP8>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
+                  size_t smem, cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<GROUPED, FP8>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return -20;
+    configured = true;
+  }
+  kern<<<grid, kThreads, smem, stream>>>(ta, tw, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Workspace the caller must provide for a given problem: bytes of fp32
+// partials (zero when the plan does not split K) and number of int counters.
+extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, int force_bn,
+                               int force_splits, int* out_bn, int* out_splits,
+                               size_t* out_ws_bytes, int* out_counters) {
+  GemmPlan pl = plan_gemm(M, N, K, elem_bytes, sm_count(), true, swiglu != 0);
+  if (force_bn > 0) pl.BN = force_bn;
+  if (force_splits > 0) pl.splits = force_splits;
+  const int m_blocks = (M + kBM - 1) / kBM;
+  const int n_blocks = (N + pl.BN - 1) / pl.BN;
+  *out_bn = pl.BN;
+  *out_splits = pl.splits;
+  *out_counters = m_blocks * n_blocks;
+  *out_ws_bytes = pl.splits > 1
+                      ? static_cast<size_t>(pl.splits) * m_blocks * n_blocks * kBM * pl.BN * 4
+                      : 0;
+}
+
+// Dense GEMM.  A [M,K] (pitch lda), W [N,K] (pitch ldw), C [M,N or N/2 with
+// swiglu] (pitch ldc).  dtype_fp8 = 0: bf16 inputs; 1: e4m3 inputs (no scale
+// handling here; callers fold scales, see the block-scaled wrapper).
+// workspace / counters may be null when splits == 1.  Returns 0 on success.
+extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
+                         const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
+                         int dtype_fp8, int out_fp32, int swiglu, int BN, int splits,
+                         void* workspace, int* counters, int* status, int max_ctas,
+                         cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int eb = dtype_fp8 ? 1 : 2;
+  if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
+  if (swiglu && ((BN % 32) != 0 || (N % 16) != 0 || splits != 1)) return -11;
+  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return -12;
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.BN = BN;
+  p.elem_bytes = eb;
+  p.k_iters = (K * eb + kRowBytes - 1) / kRowBytes;
+  p.splits = splits;
+  p.num_m_blocks = (M + kBM - 1) / kBM;
+  p.num_n_blocks = (N + BN - 1) / BN;
+  const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  p.tmem_cols = next_pow2_cols(2 * p.acc_stride);
+  p.ldc = ldc;
+  p.out_fp32 = out_fp32;
+  p.swiglu = swiglu;
+  p.num_experts = 0;
+  p.C = C;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.workspace = static_cast<float*>(workspace);
+  p.tile_counters = counters;
+  p.expert_offsets = nullptr;
+  p.status = status;
+  CUtensorMap ta, tw;
+  const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int box_k = kRowBytes / eb;
+  int r = make_tensormap_2d(&ta, dt, eb, A, M, K, lda, kBM, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+  r = make_tensormap_2d(&tw, dt, eb, W, N, K, ldw, BN, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 1000;
+  long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks * splits;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  const size_t smem = smem_bytes_for(BN, stages, 0);
+  if (dtype_fp8) return launch<false, true>(ta, tw, p, grid, smem, stream);
+  return launch<false, false>(ta, tw, p, grid, smem, stream);
+}
+
+// Grouped GEMM over E experts.  A [total_rows, K] holds each expert's rows
+// contiguously, expert e owning rows expert_offsets[e] .. expert_offsets[e+1]
+// (device array, so no host synchronisation is needed to learn the counts).
+// W [E, N, K].  C [total_rows, N (or N/2 with swiglu)].
+extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_offsets,
+                                 int num_experts, int total_rows, int N, int K, int lda, int ldc,
+                                 int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
+                                 cudaStream_t stream) {
+  if (total_rows <= 0 || num_experts <= 0) return 0;
+  if (num_experts > kMaxExperts) return -13;
+  const int eb = dtype_fp8 ? 1 : 2;
+  if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
+  if (swiglu && ((BN % 32) != 0 || (N % 16) != 0)) return -11;
+  GemmParams p{};
+  p.M = total_rows;
+  p.N = N;
+  p.K = K;
+  p.BN = BN;
+  p.elem_bytes = eb;
+  p.k_iters = (K * eb + kRowBytes - 1) / kRowBytes;
+  p.splits = 1;
+  p.num_m_blocks = 0;
+  p.num_n_blocks = (N + BN - 1) / BN;
+  const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  p.tmem_cols = next_pow2_cols(2 * p.acc_stride);
+  p.ldc = ldc;
+  p.out_fp32 = 0;
+  p.swiglu = swiglu;
+  p.num_experts = num_experts;
+  p.C = C;
+  p.expert_offsets = expert_offsets;
+  p.status = status;
+  CUtensorMap ta, tw;
+  const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int box_k = kRowBytes / eb;
+  int r = make_tensormap_2d(&ta, dt, eb, A, total_rows, K, lda, kBM, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+  r = make_tensormap_3d(&tw, dt, eb, W, num_experts, N, K, static_cast<uint64_t>(N) * K, K, BN,
+                        box_k, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 1000;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  const size_t smem = smem_bytes_for(BN, stages, num_experts);
+  if (dtype_fp8) return launch<true, true>(ta, tw, p, grid, smem, stream);
+  return launch<true, false>(ta, tw, p, grid, smem, stream);
+}

@@ -1,0 +1,169 @@
+"""Engine and offline ``LLM`` front end.
+
+``LLMEngine`` ties scheduler and worker together: ``add_request`` / ``step``.
+``LLM.generate`` is the offline batch API.  With more than one rank the engine
+runs SPMD: every rank executes the same deterministic scheduler over the same
+requests, so no per-step control broadcast is needed (ranks only meet inside
+the model's collectives); rank 0's outputs are the result.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Dict, Iterable, List, Optional, Sequence, Union
+
+import torch
+
+from .. import ops
+from ..config import EngineConfig, ModelConfig, PRESETS
+from ..logger import logger
+from ..worker.worker import Worker
+from .request import Request, RequestOutput, SamplingParams
+from .scheduler import Scheduler, SchedulerOutput
+
+
+class LLMEngine:
+    def __init__(self, config: EngineConfig, local_rank: Optional[int] = None,
+                 rank: Optional[int] = None) -> None:
+        import os
+        self.config = config
+        local_rank = int(os.environ.get("LOCAL_RANK", "0")) if local_rank is None else local_rank
+        rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+        self.rank = rank
+        self.worker = Worker(config, local_rank=local_rank, rank=rank)
+        self.worker.init_device()
+        self.worker.load_model()
+        num_blocks = self.worker.determine_num_blocks()
+        self.worker.initialize_from_config(num_blocks)
+        self.worker.compile_or_warm_up_model()
+        connector = None
+        if config.kv_transfer is not None and config.kv_transfer.kv_connector:
+            from ..kv_transfer.connector import create_connector
+            connector = create_connector(config, role="scheduler")
+        reserved = getattr(self.worker.get_model(), "num_reserved_kv_blocks", 0)
+        self.scheduler = Scheduler(config.scheduler, config.cache, num_blocks, reserved, connector)
+        self._ids = itertools.count()
+        self.stats = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "h2d_bytes": 0,
+                      "d2h_bytes": 0, "output_tokens": 0}
+
+    @property
+    def device(self) -> torch.device:
+        return self.worker.device
+
+    def add_request(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, kv_transfer_params=None,
+                    arrival_time: Optional[float] = None) -> str:
+        rid = request_id or f"req-{next(self._ids)}"
+        req = Request(rid, prompt_token_ids, sampling_params, self.config.model.eos_token_id,
+                      arrival_time, kv_transfer_params)
+        self.scheduler.add_request(req)
+        return rid
+
+    def abort_request(self, request_id: str) -> None:
+        self.scheduler.abort_request(request_id)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def step(self) -> List[RequestOutput]:
+        out = self.scheduler.schedule()
+        if out.kind == "idle":
+            if out.finished_req_ids:
+                self.worker.model_runner.execute_model(out)
+            return []
+        tokens = self.worker.execute_model(out)
+        finished = self.scheduler.update_from_output(out, tokens)
+        st = self.stats
+        st["steps"] += 1
+        st[out.kind + "_steps"] += 1
+        st["h2d_bytes"] += self.worker.model_runner.input_batch.h2d_bytes_last
+        st["d2h_bytes"] += self.worker.model_runner.d2h_bytes_last
+        st["output_tokens"] += sum(1 for s in out.seqs if s.samples)
+        for r in finished:
+            self.worker.model_runner.input_batch.remove_request(r.request_id)
+        return [RequestOutput.from_request(r) for r in finished]
+
+    def shutdown(self) -> None:
+        self.worker.shutdown()
+
+
+class LLM:
+    """Offline inference front end.
+
+    >>> llm = LLM(model="llama-3-8b")                # preset name, HF directory or ModelConfig
+    >>> outs = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=8))
+    """
+
+    def __init__(self, model: Union[str, ModelConfig, EngineConfig] = "llama-3-8b", **kw) -> None:
+        if isinstance(model, EngineConfig):
+            config = model
+        else:
+            import os
+            path = None
+            if isinstance(model, ModelConfig):
+                mc = model
+            elif model in PRESETS:
+                mc = PRESETS[model]()
+            elif os.path.isdir(model):
+                mc, path = ModelConfig.from_pretrained(model, kw.pop("dtype", None)), model
+            else:
+                raise ValueError(f"unknown model {model!r}: give a preset {sorted(PRESETS)}, a directory or a config")
+            config = build_engine_config(mc, model_path=path, **kw)
+        self.config = config
+        self.engine = LLMEngine(config)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 ) -> List[RequestOutput]:
+        sps = sampling_params if isinstance(sampling_params, (list, tuple)) else [sampling_params] * len(prompts)
+        order: Dict[str, int] = {}
+        now = time.monotonic()
+        for i, (p, sp) in enumerate(zip(prompts, sps)):
+            order[self.engine.add_request(p, sp, arrival_time=now)] = i
+        results: List[Optional[RequestOutput]] = [None] * len(prompts)
+        while self.engine.has_unfinished_requests():
+            for o in self.engine.step():
+                results[order[o.request_id]] = o
+        if self.engine.device.type == "cuda":
+            ops.check_status(self.engine.device)
+        return results  # type: ignore[return-value]
+
+
+def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **kw) -> EngineConfig:
+    """Keyword-style construction mirroring the usual serving flags
+    (tensor_parallel_size, max_num_seqs, block_size, ...)."""
+    from ..config import (CacheConfig, CompilationConfig, KVTransferConfig, ParallelConfig,
+                          SchedulerConfig, SpeculativeConfig)
+    cache = CacheConfig(block_size=kw.pop("block_size", 16),
+                        gpu_memory_utilization=kw.pop("gpu_memory_utilization", 0.9),
+                        num_gpu_blocks=kw.pop("num_gpu_blocks", None))
+    par = ParallelConfig(tensor_parallel_size=kw.pop("tensor_parallel_size", 1),
+                         pipeline_parallel_size=kw.pop("pipeline_parallel_size", 1),
+                         data_parallel_size=kw.pop("data_parallel_size", 1),
+                         enable_expert_parallel=kw.pop("enable_expert_parallel", False),
+                         layer_parallel_config=kw.pop("layer_parallel_config", {}) or {})
+    sched = SchedulerConfig(max_num_seqs=kw.pop("max_num_seqs", 128),
+                            max_num_batched_tokens=kw.pop("max_num_batched_tokens", 8192),
+                            max_model_len=kw.pop("max_model_len", min(8192, model.max_position_embeddings)),
+                            enable_chunked_prefill=kw.pop("enable_chunked_prefill", True))
+    comp = kw.pop("compilation_config", None)
+    if isinstance(comp, dict):
+        comp = CompilationConfig(cudagraph_mode=comp.get("cudagraph_mode", "FULL_DECODE_ONLY"),
+                                 cudagraph_capture_sizes=comp.get("cudagraph_capture_sizes"))
+    kvt = kw.pop("kv_transfer_config", None)
+    if isinstance(kvt, dict):
+        kvt = KVTransferConfig(**kvt)
+    spec = kw.pop("speculative_config", None)
+    if isinstance(spec, dict):
+        spec = SpeculativeConfig(method=spec.get("method"),
+                                 num_speculative_tokens=spec.get("num_speculative_tokens", 0))
+    cfg = EngineConfig(model=model, cache=cache, parallel=par, scheduler=sched,
+                       compilation=comp or CompilationConfig(), kv_transfer=kvt,
+                       speculative=spec or SpeculativeConfig(), model_path=model_path,
+                       load_format=kw.pop("load_format", "auto"), seed=kw.pop("seed", 0),
+                       device=kw.pop("device", "auto"), enforce_eager=kw.pop("enforce_eager", False),
+                       enable_sleep_mode=kw.pop("enable_sleep_mode", False),
+                       additional_config=kw.pop("additional_config", {}) or {})
+    if kw:
+        raise TypeError(f"unknown engine arguments: {sorted(kw)}")
+    return cfg

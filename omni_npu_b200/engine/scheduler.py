@@ -1,0 +1,240 @@
+"""Continuous-batching scheduler with chunked prefill and recompute preemption.
+
+A step is either a *prefill* step (one or more prompt chunks, run eagerly) or
+a *decode* step (one new token for every running sequence, run from a CUDA
+graph).  Prefill has priority while there is room for more running sequences.
+KV-connector hooks mirror the life cycle the reference drives through vLLM's
+scheduler (omni_npu/connector/llmdatadist_connector_v1.py:233-291,457-576):
+a consumer request first waits for its remote KV, a producer request parks its
+blocks after finishing so they can still be pulled.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Any, Deque, Dict, List, Optional, Tuple
+
+from ..config import CacheConfig, SchedulerConfig
+from .block_manager import BlockPool
+from .request import Request, RequestStatus
+
+
+@dataclass
+class ScheduledSeq:
+    request: Request
+    start: int             # tokens already in the KV cache before this step
+    num_new_tokens: int    # tokens computed in this step
+    samples: bool          # whether this step yields an output token for the request
+
+
+@dataclass
+class SchedulerOutput:
+    kind: str = "idle"                      # "prefill" | "decode" | "idle"
+    seqs: List[ScheduledSeq] = field(default_factory=list)
+    num_tokens: int = 0
+    preempted: List[str] = field(default_factory=list)
+    finished_req_ids: List[str] = field(default_factory=list)
+    kv_connector_metadata: Any = None
+    step_index: int = 0
+
+    @property
+    def total_num_scheduled_tokens(self) -> int:
+        return self.num_tokens
+
+
+class Scheduler:
+    def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
+                 num_reserved_blocks: int = 0, kv_connector=None) -> None:
+        self.cfg = sched_cfg
+        self.block_size = cache_cfg.block_size
+        self.pool = BlockPool(num_blocks, cache_cfg.block_size, num_reserved_blocks)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.requests: Dict[str, Request] = {}
+        self.kv_connector = kv_connector
+        self._finished_since_last: List[str] = []
+        self._step = 0
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, req: Request) -> None:
+        if req.num_prompt_tokens >= self.cfg.max_model_len:
+            raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len "
+                             f"{self.cfg.max_model_len}")
+        self.requests[req.request_id] = req
+        self.waiting.append(req)
+
+    def abort_request(self, request_id: str) -> None:
+        req = self.requests.get(request_id)
+        if req is None or req.is_finished:
+            return
+        req.status = RequestStatus.FINISHED_ABORTED
+        req.finish_time = time.monotonic()
+        if req in self.running:
+            self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        self._release(req)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    @property
+    def num_unfinished(self) -> int:
+        return len(self.waiting) + len(self.running)
+
+    # ---------------------------------------------------------------- blocks
+    def _ensure_blocks(self, req: Request, total_tokens: int) -> bool:
+        need = self.pool.blocks_needed(total_tokens, len(req.block_ids))
+        if need == 0:
+            return True
+        if not self.pool.can_allocate(need):
+            return False
+        req.block_ids.extend(self.pool.allocate(need))
+        return True
+
+    def _release(self, req: Request) -> None:
+        delay = None
+        if self.kv_connector is not None and req.status != RequestStatus.FINISHED_ABORTED:
+            delay, params = self.kv_connector.request_finished(req, req.block_ids)
+            if params is not None:
+                req.kv_transfer_params = params
+        if delay:
+            self.pool.park(req.request_id, req.block_ids, delay)
+        else:
+            self.pool.free(req.block_ids)
+        req.block_ids = []
+        self._finished_since_last.append(req.request_id)
+
+    def _preempt_one(self, protect: Request) -> Optional[Request]:
+        """Evict the most recently admitted running request (recompute later)."""
+        for victim in reversed(self.running):
+            if victim is protect:
+                continue
+            self.running.remove(victim)
+            self.pool.free(victim.block_ids)
+            victim.block_ids = []
+            victim.num_computed_tokens = 0
+            victim.status = RequestStatus.PREEMPTED
+            victim.num_preemptions += 1
+            self.waiting.appendleft(victim)
+            return victim
+        return None
+
+    # -------------------------------------------------------------- schedule
+    def schedule(self) -> SchedulerOutput:
+        self._step += 1
+        out = SchedulerOutput(step_index=self._step)
+        self.pool.expire_parked()
+        if self.kv_connector is not None:
+            for rid in self.kv_connector.take_released_requests():
+                self.pool.release_parked(rid)
+
+        budget = self.cfg.max_num_batched_tokens
+        # 1) unfinished prompt chunks of running requests, then new admissions
+        prefill: List[ScheduledSeq] = []
+        for req in self.running:
+            remaining = req.num_tokens - req.num_computed_tokens
+            if remaining > 1 or (remaining == 1 and not req.output_token_ids):
+                n = min(remaining, budget)
+                if n <= 0:
+                    break
+                if not self.cfg.enable_chunked_prefill and n < remaining:
+                    break
+                if not self._ensure_blocks(req, req.num_computed_tokens + n):
+                    break
+                prefill.append(ScheduledSeq(req, req.num_computed_tokens, n, n == remaining))
+                budget -= n
+        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+            req = self.waiting[0]
+            if req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
+                if self.kv_connector is not None and self.kv_connector.is_load_finished(req):
+                    req.status = RequestStatus.WAITING
+                else:
+                    # keep order simple: look at the next request instead
+                    self.waiting.rotate(-1)
+                    if all(r.status == RequestStatus.WAITING_FOR_REMOTE_KVS for r in self.waiting):
+                        break
+                    continue
+            if (self.kv_connector is not None and req.num_computed_tokens == 0
+                    and req.num_external_tokens == 0 and req.kv_transfer_params):
+                ext, is_async = self.kv_connector.get_num_new_matched_tokens(req, 0)
+                if ext > 0:
+                    if not self._ensure_blocks(req, ext):
+                        break
+                    req.num_external_tokens = ext
+                    self.kv_connector.update_state_after_alloc(req, req.block_ids, ext)
+                    if is_async:
+                        req.status = RequestStatus.WAITING_FOR_REMOTE_KVS
+                        continue
+            if req.num_external_tokens and req.num_computed_tokens == 0:
+                # remote KV covers the prompt except (at least) its last token
+                req.num_computed_tokens = min(req.num_external_tokens, req.num_tokens - 1)
+            remaining = req.num_tokens - req.num_computed_tokens
+            n = min(remaining, budget)
+            if n < remaining and not self.cfg.enable_chunked_prefill:
+                break
+            if not self._ensure_blocks(req, req.num_computed_tokens + n):
+                break
+            self.waiting.popleft()
+            req.status = RequestStatus.RUNNING
+            self.running.append(req)
+            prefill.append(ScheduledSeq(req, req.num_computed_tokens, n, n == remaining))
+            budget -= n
+        if prefill:
+            out.kind = "prefill"
+            out.seqs = prefill
+            out.num_tokens = sum(s.num_new_tokens for s in prefill)
+            self._finish_output(out)
+            return out
+
+        # 2) decode: one token for every running request
+        decode: List[ScheduledSeq] = []
+        i = 0
+        while i < len(self.running):
+            req = self.running[i]
+            while not self._ensure_blocks(req, req.num_tokens):
+                victim = self._preempt_one(protect=req)
+                if victim is None:
+                    raise RuntimeError("KV cache too small for a single sequence")
+                out.preempted.append(victim.request_id)
+                decode = [s for s in decode if s.request is not victim]
+            if req in self.running:
+                decode.append(ScheduledSeq(req, req.num_computed_tokens, 1, True))
+            i = self.running.index(req) + 1
+        if decode:
+            out.kind = "decode"
+            out.seqs = decode
+            out.num_tokens = len(decode)
+        self._finish_output(out)
+        return out
+
+    def _finish_output(self, out: SchedulerOutput) -> None:
+        out.finished_req_ids, self._finished_since_last = self._finished_since_last, []
+        if self.kv_connector is not None:
+            out.kv_connector_metadata = self.kv_connector.build_connector_meta(out)
+
+    # ---------------------------------------------------------------- update
+    def update_from_output(self, out: SchedulerOutput, sampled: List[int],
+                           now: Optional[float] = None) -> List[Request]:
+        """Apply one step's results.  ``sampled[i]`` belongs to ``out.seqs[i]``.
+        Returns requests that finished in this step."""
+        finished: List[Request] = []
+        now = time.monotonic() if now is None else now
+        for seq, tok in zip(out.seqs, sampled):
+            req = seq.request
+            if req.is_finished:
+                continue
+            req.num_computed_tokens = seq.start + seq.num_new_tokens
+            if not seq.samples:
+                continue
+            req.append_output(tok, now)
+            if req.check_stop() or req.num_tokens >= self.cfg.max_model_len:
+                if not req.is_finished:
+                    req.status = RequestStatus.FINISHED_LENGTH_CAPPED
+                    req.finish_time = now
+                finished.append(req)
+        for req in finished:
+            self.running.remove(req)
+            self._release(req)
+        return finished

@@ -1,0 +1,53 @@
+"""RMSNorm (optionally fused with the residual add) and LayerNorm.
+
+Counterpart of ``NPURMSNorm`` (omni_npu/layers/npu_rms_norm.py:12-33): calling
+with a residual performs ``residual += x`` and normalises the sum in one
+kernel; ``y_transform="AG"`` all-gathers the normalised rows over the tensor
+parallel group (sequence-parallel residual stream).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple, Union
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..parallel import state as pstate
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16,
+                 device=None) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device),
+                                   requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                y_transform: Optional[str] = None
+                ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+        if residual is None:
+            y = ops.rms_norm(x, self.weight, self.eps)
+            if y_transform == "AG":
+                y = pstate.get_tp_group().all_gather(y, dim=0)
+            return y
+        y = ops.fused_add_rms_norm(x, residual, self.weight, self.eps)
+        if y_transform == "AG":
+            y = pstate.get_tp_group().all_gather(y, dim=0)
+        return y, residual
+
+
+class LayerNorm(nn.Module):
+    """Plain LayerNorm in fp32 (used by the sparse-attention indexer key path)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, dtype=torch.float32, device=None) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device), requires_grad=False)
+        self.eps = eps
+        self.dim = dim
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.layer_norm(x.float(), (self.dim,), self.weight.float(),
+                                              self.bias.float(), self.eps).to(x.dtype)

@@ -1,0 +1,131 @@
+"""Dense decoder-only transformer (Llama / Qwen2 / Qwen3 family).
+
+One implementation covers the three: Qwen2 adds QKV bias, Qwen3 adds per-head
+RMSNorm on q and k (reference: omni_npu/v1/models/qwen/qwen3.py:60-173).
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..attention.gqa import GQAAttention
+from ..config import EngineConfig, ModelConfig
+from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from ..layers.linear import QKVParallelLinear, RowParallelLinear
+from ..layers.mlp import FusedMLP
+from ..layers.norm import RMSNorm
+from ..layers.rope import get_rope
+from ..parallel import state as pstate
+from .utils import load_stacked_weights
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        self.head_dim = cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_heads,
+                                          cfg.num_kv_heads, bias=cfg.attention_bias, dtype=cfg.dtype,
+                                          device=device, prefix=f"{prefix}.qkv_proj")
+        self.o_proj = RowParallelLinear(cfg.num_heads * cfg.head_dim, cfg.hidden_size, dtype=cfg.dtype,
+                                        device=device, prefix=f"{prefix}.o_proj")
+        self.qk_norm = cfg.qk_norm
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.dtype, device)
+            self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, cfg.dtype, device)
+        self.rotary = get_rope(cfg.head_dim, cfg.rotary_dim, cfg.max_position_embeddings,
+                               cfg.rope_theta, cfg.rope_neox, cfg.rope_scaling, device)
+        self.attn = GQAAttention(layer_idx, self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads,
+                                 cfg.head_dim, cfg.head_dim ** -0.5 * self.rotary.mscale ** 2
+                                 if self.rotary.mscale != 1.0 else cfg.head_dim ** -0.5,
+                                 cfg.rotary_dim, cfg.rope_neox, cfg.sliding_window)
+
+    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        q, k, v = self.qkv_proj(hidden)
+        if self.qk_norm:
+            t = q.shape[0]
+            q = self.q_norm(q.reshape(-1, self.head_dim)).view(t, -1)
+            k = self.k_norm(k.reshape(-1, self.head_dim)).view(t, -1)
+        o = self.attn(q, k, v, self.rotary.cos_sin_cache)
+        return self.o_proj(o)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        self.self_attn = LlamaAttention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        self.mlp = FusedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.dtype, device,
+                            prefix=f"{prefix}.mlp")
+
+    def forward(self, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        if residual is None:
+            residual = hidden
+            hidden = self.input_layernorm(hidden)
+        else:
+            hidden, residual = self.input_layernorm(hidden, residual)
+        hidden = self.self_attn(hidden)
+        hidden, residual = self.post_attention_layernorm(hidden, residual)
+        hidden = self.mlp(hidden)
+        return hidden, residual
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:
+        super().__init__()
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+        self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, i, device, f"{prefix}.layers.{i}")
+                                     for i in range(cfg.num_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+
+    def forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
+                inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+        hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        residual = None
+        for layer in self.layers:
+            hidden, residual = layer(hidden, residual)
+        hidden, _ = self.norm(hidden, residual)
+        return hidden
+
+
+class LlamaForCausalLM(nn.Module):
+    stacked_params_mapping = [
+        # (fused parameter, checkpoint name, shard id)
+        (".qkv_proj", ".q_proj", "q"), (".qkv_proj", ".k_proj", "k"), (".qkv_proj", ".v_proj", "v"),
+        (".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1),
+    ]
+
+    def __init__(self, engine_config: EngineConfig, device=None) -> None:
+        super().__init__()
+        cfg = engine_config.model
+        self.config = cfg
+        self.model = LlamaModel(cfg, device)
+        if cfg.tie_word_embeddings:
+            self.lm_head = self.model.embed_tokens
+            self.lm_head.__class__ = ParallelLMHead
+        else:
+            self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+
+    def forward(self, input_ids, positions, inputs_embeds=None) -> torch.Tensor:
+        return self.model(input_ids, positions, inputs_embeds)
+
+    def embed_input_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.model.embed_tokens(input_ids)
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.compute_logits(hidden)
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        skip = ("rotary_emb.inv_freq",)
+        if self.config.tie_word_embeddings:
+            skip = skip + ("lm_head.weight",)
+        return load_stacked_weights(self, weights, self.stacked_params_mapping, skip_substrings=skip)
+
+
+# Qwen2 / Qwen3 dense share the implementation; differences come from ModelConfig.
+Qwen2ForCausalLM = LlamaForCausalLM
+Qwen3ForCausalLM = LlamaForCausalLM
+MistralForCausalLM = LlamaForCausalLM

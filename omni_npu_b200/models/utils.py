@@ -1,0 +1,114 @@
+"""Weight-loading helpers shared by the model classes."""
+from __future__ import annotations
+
+import glob
+import json
+import os
+from typing import Dict, Iterable, Iterator, List, Optional, Sequence, Set, Tuple
+
+import torch
+from torch import nn
+
+
+def default_weight_loader(param: nn.Parameter, loaded: torch.Tensor) -> None:
+    if param.shape != loaded.shape:
+        raise ValueError(f"shape mismatch: parameter {tuple(param.shape)} vs checkpoint {tuple(loaded.shape)}")
+    param.data.copy_(loaded if param.dtype == torch.float8_e4m3fn else loaded.to(param.dtype))
+
+
+def _owner_loader(model: nn.Module, name: str):
+    """The ``weight_loader`` of the module that owns parameter ``name``, if any."""
+    mod_name = name.rsplit(".", 1)[0] if "." in name else ""
+    try:
+        mod = model.get_submodule(mod_name)
+    except AttributeError:
+        return None
+    return getattr(mod, "weight_loader", None)
+
+
+def load_stacked_weights(model: nn.Module, weights: Iterable[Tuple[str, torch.Tensor]],
+                         stacked: Sequence[Tuple[str, str, object]],
+                         skip_substrings: Sequence[str] = (),
+                         rename=None) -> Set[str]:
+    """Generic loader: checkpoint tensors whose name contains a ``stacked`` source
+    pattern go into the fused parameter with the given shard id; everything else
+    is loaded by name through the owning module's ``weight_loader``."""
+    params: Dict[str, nn.Parameter] = dict(model.named_parameters())
+    loaded: Set[str] = set()
+    for name, tensor in weights:
+        if any(s in name for s in skip_substrings):
+            continue
+        if rename is not None:
+            name = rename(name)
+            if name is None:
+                continue
+        done = False
+        for fused, src, shard in stacked:
+            if src not in name:
+                continue
+            target = name.replace(src, fused)
+            if target not in params:
+                continue
+            loader = _owner_loader(model, target)
+            loader(params[target], tensor, shard)
+            loaded.add(target)
+            done = True
+            break
+        if done:
+            continue
+        if name not in params:
+            continue
+        loader = _owner_loader(model, name)
+        if loader is not None:
+            loader(params[name], tensor)
+        else:
+            default_weight_loader(params[name], tensor)
+        loaded.add(name)
+    return loaded
+
+
+def iter_safetensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Yield (name, tensor) from every ``*.safetensors`` shard of an HF directory
+    (index file order when present)."""
+    from safetensors import safe_open
+    index = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(index):
+        with open(index) as f:
+            files = sorted(set(json.load(f)["weight_map"].values()))
+        files = [os.path.join(path, x) for x in files]
+    else:
+        files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if not files:
+        raise FileNotFoundError(f"no safetensors files under {path}")
+    for fn in files:
+        with safe_open(fn, framework="pt", device="cpu") as f:
+            for k in f.keys():
+                yield k, f.get_tensor(k)
+
+
+@torch.no_grad()
+def random_init_(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
+    """Deterministic random initialisation (normal, std 0.02; norm weights 1).
+    Values are generated on the CPU per parameter so that a tensor-parallel
+    shard equals the matching slice of the unsharded tensor only when the
+    caller seeds per full tensor; for benchmarking each rank simply gets its
+    own stream."""
+    g = torch.Generator(device="cpu")
+    for i, (name, p) in enumerate(sorted(model.named_parameters(), key=lambda kv: kv[0])):
+        g.manual_seed(seed * 1000003 + i)
+        if "norm" in name and p.dim() == 1 and "bias" not in name:
+            p.data.fill_(1.0)
+        elif name.endswith("weight_scale_inv"):
+            p.data.fill_(1.0)
+        elif name.endswith(".bias") or "e_score_correction_bias" in name:
+            p.data.zero_()
+        elif p.device.type == "cuda" and p.numel() >= (1 << 22):
+            gg = torch.Generator(device=p.device)
+            gg.manual_seed(seed * 1000003 + i)
+            tmp = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device).normal_(0.0, std, generator=gg)
+            p.data.copy_(tmp if p.dtype != torch.float8_e4m3fn else (tmp.float() * (448 * 0.25 / (3 * std))).to(p.dtype))
+            del tmp
+        else:
+            tmp = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g)
+            p.data.copy_(tmp.to(p.dtype) if p.dtype != torch.float8_e4m3fn
+                         else (tmp * (448 * 0.25 / (3 * std))).to(p.dtype))

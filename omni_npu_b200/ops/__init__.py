@@ -1,0 +1,364 @@
+"""Device ops of the framework.
+
+Every function takes torch tensors.  CUDA tensors run the hand-written sm_100a
+kernels from ``_C.so`` (``torch.ops.omni_b200.*``); a missing extension on a
+CUDA tensor is an error, never a silent fallback.  CPU tensors run the fp32
+PyTorch references in :mod:`omni_npu_b200.ops.ref`, which is what the gloo /
+no-GPU plumbing tests exercise.
+
+``launch_count()`` returns how many of this library's kernels have been
+launched (graph replays add the number of kernels captured in the graph).
+"""
+from __future__ import annotations
+
+import os
+import threading
+from pathlib import Path
+from typing import Optional, Tuple
+
+import torch
+
+from . import ref
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB = _PKG / "_C.so"
+_loaded = False
+_load_error: Optional[str] = None
+_lock = threading.Lock()
+
+
+def load_extension(required: bool = False) -> bool:
+    """Load ``_C.so`` (idempotent).  Returns whether the ops are available."""
+    global _loaded, _load_error
+    if _loaded:
+        return True
+    with _lock:
+        if _loaded:
+            return True
+        if not _LIB.exists():
+            _load_error = f"{_LIB} not built (run `python -m omni_npu_b200._build`)"
+        else:
+            try:
+                torch.ops.load_library(str(_LIB))
+                _loaded = True
+            except Exception as e:  # pragma: no cover - depends on the box
+                _load_error = f"loading {_LIB} failed: {e}"
+    if required and not _loaded:
+        raise RuntimeError("omni_npu_b200 CUDA extension unavailable: " + str(_load_error))
+    return _loaded
+
+
+def _C():
+    load_extension(required=True)
+    return torch.ops.omni_b200
+
+
+# --------------------------------------------------------------- launch count
+class _Counter:
+    __slots__ = ("n", "capturing", "captured")
+
+    def __init__(self) -> None:
+        self.n = 0
+        self.capturing = False
+        self.captured = 0
+
+
+_counter = _Counter()
+
+
+def _count(k: int = 1) -> None:
+    if _counter.capturing:
+        _counter.captured += k
+    else:
+        _counter.n += k
+
+
+def launch_count() -> int:
+    return _counter.n
+
+
+def add_launches(k: int) -> None:
+    _counter.n += k
+
+
+class count_capture:
+    """Context manager used around CUDA-graph capture: kernels launched inside are
+    tallied separately so each replay can add them to the global count."""
+
+    def __enter__(self):
+        self._saved = (_counter.capturing, _counter.captured)
+        _counter.capturing, _counter.captured = True, 0
+        return self
+
+    def __exit__(self, *exc):
+        self.kernels = _counter.captured
+        _counter.capturing, _counter.captured = self._saved
+        return False
+
+
+# ------------------------------------------------------------------ workspaces
+class _DeviceState:
+    """Per-device persistent scratch for split-K GEMM and split-KV decode plus
+    the kernel status word.  Allocated once, before any graph capture."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.gemm_ws_bytes = int(os.environ.get("OMNI_B200_GEMM_WS_MB", "64")) << 20
+        self.gemm_ws = {}
+        self.counters = {}
+        self.attn_scratch = {}
+        self.plans = {}
+
+    def gemm_workspace(self, stream_id: int, nbytes: int, ncounters: int):
+        ws = self.gemm_ws.get(stream_id)
+        if ws is None or ws.numel() < nbytes:
+            ws = torch.empty(max(nbytes, self.gemm_ws_bytes), dtype=torch.uint8, device=self.device)
+            self.gemm_ws[stream_id] = ws
+        cnt = self.counters.get(stream_id)
+        if cnt is None or cnt.numel() < ncounters:
+            cnt = torch.zeros(max(ncounters, 65536), dtype=torch.int32, device=self.device)
+            self.counters[stream_id] = cnt
+        return ws, cnt
+
+    def decode_scratch(self, stream_id: int, nbytes: int):
+        sc = self.attn_scratch.get(stream_id)
+        if sc is None or sc.numel() < nbytes:
+            sc = torch.empty(max(nbytes, 32 << 20), dtype=torch.uint8, device=self.device)
+            self.attn_scratch[stream_id] = sc
+        return sc
+
+
+_states = {}
+
+
+def device_state(device: torch.device) -> _DeviceState:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _states.get(idx)
+    if st is None:
+        st = _DeviceState(torch.device("cuda", idx))
+        _states[idx] = st
+    return st
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Raise if any kernel recorded a bounded-wait timeout since the last check
+    (synchronises the device)."""
+    for st in _states.values():
+        if device is not None and st.device != device:
+            continue
+        code = int(st.status.item())
+        if code != 0:
+            st.status.zero_()
+            raise RuntimeError(f"omni_npu_b200 kernel reported status {code} (bounded wait expired)")
+
+
+# ------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         swiglu: bool = False, bn: int = 0, splits: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``a[M,K] @ w[N,K].T`` (+bias, +residual).  bf16 or float8_e4m3fn inputs,
+    fp32 accumulation, bf16 (default) or fp32 output.  ``swiglu`` fuses
+    silu(gate)*up for weights laid out by :func:`ref.interleave_gate_up`."""
+    if not a.is_cuda:
+        return ref.gemm(a, w, bias, residual, out_dtype, swiglu)
+    C = _C()
+    st = device_state(a.device)
+    m, k = a.shape
+    n = w.shape[0]
+    key = (m, n, k, a.dtype.itemsize, swiglu, bn, splits)
+    plan = st.plans.get(key)
+    if plan is None:
+        plan = C.gemm_plan(m, n, k, a.dtype.itemsize, swiglu, bn, 1 if swiglu else splits)
+        st.plans[key] = plan
+    pbn, psplits, ws_bytes, ncnt = plan
+    ws = cnt = None
+    if psplits > 1:
+        ws, cnt = st.gemm_workspace(torch.cuda.current_stream(a.device).cuda_stream, ws_bytes, ncnt)
+    _count(1)
+    return C.gemm(a, w, bias, residual, out_dtype == torch.float32, swiglu, pbn, psplits, ws, cnt,
+                  st.status, max_ctas)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
+                 swiglu: bool = False, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """Per-expert GEMM: rows expert_offsets[e]:expert_offsets[e+1] of ``a`` times ``w[e].T``."""
+    if not a.is_cuda:
+        return ref.grouped_gemm(a, w, expert_offsets, swiglu)
+    if bn <= 0:
+        n = w.shape[1]
+        bn = 256 if n % 256 == 0 else (128 if n % 128 == 0 else (64 if n % 64 == 0 else 32))
+    st = device_state(a.device)
+    _count(1)
+    return _C().grouped_gemm(a, w, expert_offsets, swiglu, bn, st.status, max_ctas)
+
+
+# ------------------------------------------------------------- norm/activation
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    if not x.is_cuda:
+        return ref.rms_norm(x, w, eps)
+    _count(1)
+    return _C().rms_norm(x, w, eps)
+
+
+def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor,
+                       eps: float) -> torch.Tensor:
+    """residual <- x + residual (in place); returns RMSNorm(residual) * w."""
+    if not x.is_cuda:
+        return ref.fused_add_rms_norm(x, residual, w, eps)
+    _count(1)
+    return _C().fused_add_rms_norm(x, residual, w, eps)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    if not x.is_cuda:
+        return ref.silu_and_mul(x)
+    _count(1)
+    return _C().silu_and_mul(x)
+
+
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    if not x.is_cuda:
+        return ref.quant_fp8_1x128(x, ue8m0)
+    _count(1)
+    return _C().quant_fp8_1x128(x, ue8m0)
+
+
+# ------------------------------------------------------------------ rope/cache
+def rope_qk_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+             head_dim: int, rot_dim: int, neox: bool = True,
+             mrope_section: Optional[Tuple[int, int, int]] = None,
+             mrope_interleaved: bool = False) -> None:
+    """In-place rotary embedding of q [T,Hq*D] and k [T,Hk*D]."""
+    if not q.is_cuda:
+        qo, ko = ref.rope_qk(q, k, positions, cos_sin, head_dim, rot_dim, neox, mrope_section,
+                             mrope_interleaved)
+        q.copy_(qo)
+        k.copy_(ko)
+        return
+    sec_t, sec_h = (-1, -1) if mrope_section is None else (mrope_section[0], mrope_section[1])
+    _count(1)
+    _C().rope_qk(q, k, positions, cos_sin, head_dim, rot_dim, neox, sec_t, sec_h, mrope_interleaved)
+
+
+def rope_cache_gqa_(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor,
+                    v_cache: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor,
+                    cos_sin: torch.Tensor, head_dim: int, rot_dim: int, neox: bool = True) -> None:
+    """RoPE on q (in place) and k, then k / v stored into the paged cache."""
+    if not q.is_cuda:
+        qo, ko = ref.rope_qk(q, k, positions, cos_sin, head_dim, rot_dim, neox)
+        q.copy_(qo)
+        ref.gqa_cache_write(ko, v, k_cache, v_cache, slot_mapping)
+        return
+    _count(1)
+    _C().rope_cache_gqa(q, k, v, k_cache, v_cache, positions, slot_mapping, cos_sin, head_dim,
+                        rot_dim, neox)
+
+
+def gqa_cache_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    slot_mapping: torch.Tensor) -> None:
+    if not k.is_cuda:
+        return ref.gqa_cache_write(k, v, k_cache, v_cache, slot_mapping)
+    _count(1)
+    _C().gqa_cache_write(k, v, k_cache, v_cache, slot_mapping)
+
+
+def paged_scatter_rows(dst: torch.Tensor, src: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    if not src.is_cuda:
+        return ref.paged_scatter_rows(dst, src, slot_mapping)
+    _count(1)
+    _C().paged_scatter_rows(dst, src, slot_mapping)
+
+
+def mla_kv_rmsnorm_rope_cache(kv_c: torch.Tensor, k_pe: torch.Tensor, w: torch.Tensor,
+                              cache: torch.Tensor, positions: torch.Tensor,
+                              slot_mapping: torch.Tensor, cos_sin: torch.Tensor, eps: float,
+                              neox: bool = False, want_outputs: bool = False):
+    """RMSNorm(kv_c) and RoPE(k_pe) written into the paged latent cache row
+    [norm(kv_c) | rope(k_pe)]; optionally also returned in token order."""
+    t, l = kv_c.shape
+    r = k_pe.shape[1]
+    if not kv_c.is_cuda:
+        kn = ref.rms_norm(kv_c, w, eps)
+        half = r // 2
+        cs = cos_sin[positions.long()]
+        pe = ref._rope_one(k_pe.view(t, 1, r), cs[:, :half], cs[:, half:], r, neox).view(t, r)
+        ref.paged_scatter_rows(cache, torch.cat([kn, pe], dim=-1), slot_mapping)
+        return (kn, pe) if want_outputs else None
+    kv_out = torch.empty_like(kv_c, memory_format=torch.contiguous_format) if want_outputs else None
+    pe_out = torch.empty((t, r), dtype=k_pe.dtype, device=k_pe.device) if want_outputs else None
+    _count(1)
+    _C().mla_kv_rmsnorm_rope_cache(kv_c, k_pe, w, cache, kv_out, pe_out, positions, slot_mapping,
+                                   cos_sin, eps, neox)
+    return (kv_out, pe_out) if want_outputs else None
+
+
+# ------------------------------------------------------------------- attention
+def gqa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
+                num_seqs: int, max_q_len: int, num_q_heads: int, scale: float, causal: bool = True,
+                window: int = 0, return_lse: bool = False):
+    """Variable-length attention of this step's queries over the paged cache
+    (which already holds this step's keys/values)."""
+    if not q.is_cuda:
+        return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu_q[: num_seqs + 1],
+                                   seq_lens[:num_seqs], num_q_heads, scale, causal, window, return_lse)
+    _count(1)
+    out, lse = _C().gqa_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, num_seqs,
+                                max_q_len, num_q_heads, scale, causal, window, return_lse)
+    return (out, lse) if return_lse else out
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, max_seq_len: int, sms: int = 148) -> int:
+    """Split-KV factor: enough CTAs for two waves, at least 256 keys per split."""
+    base = max(1, num_seqs * num_kv_heads)
+    want = (2 * sms + base - 1) // base
+    cap = max(1, max_seq_len // 256)
+    return max(1, min(want, cap, 16))
+
+
+def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+               block_tables: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, num_q_heads: int,
+               scale: float, q_len: int = 1, window: int = 0, splits: int = 0,
+               max_seq_len: int = 0) -> torch.Tensor:
+    """Decode attention: q_len (usually 1) new tokens per sequence, sequences laid
+    out back to back in q."""
+    if not q.is_cuda:
+        cu = torch.arange(0, (num_seqs + 1) * q_len, q_len, dtype=torch.int32, device=q.device)
+        return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu,
+                                   seq_lens[:num_seqs], num_q_heads, scale, True, window)
+    C = _C()
+    hk, d = k_cache.shape[1], k_cache.shape[3]
+    if splits <= 0:
+        bound = max_seq_len if max_seq_len > 0 else block_tables.shape[1] * k_cache.shape[2]
+        splits = decode_splits(num_seqs, hk, bound)
+    scratch = None
+    if splits > 1:
+        st = device_state(q.device)
+        nbytes = C.gqa_decode_scratch_bytes(num_seqs, hk, d, splits)
+        scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
+    _count(2 if splits > 1 else 1)
+    return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
+                        scale, window, splits, scratch)
+
+
+merge_attn_states = ref.merge_attn_states
+
+
+# -------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    if not logits.is_cuda:
+        return ref.argmax(logits)
+    _count(1)
+    return _C().argmax(logits)
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           seeds: Optional[torch.Tensor] = None, step_offset: Optional[torch.Tensor] = None,
+           generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """Temperature / top-k / top-p sampling; rows with temperature < 1e-5 are greedy."""
+    if not logits.is_cuda:
+        return ref.sample(logits, temperature, top_k, top_p, generator)
+    _count(1)
+    return _C().sample(logits, temperature, top_k, top_p, seeds, step_offset)

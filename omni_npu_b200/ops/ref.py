@@ -1,0 +1,273 @@
+"""Plain PyTorch reference implementations (fp32 math) of every device op.
+
+They serve two purposes: the CPU execution path (gloo / no-GPU plumbing runs)
+and the oracle the CUDA kernels are tested against.  Shapes and semantics are
+identical to the CUDA entry points in ``omni_npu_b200.ops``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         swiglu: bool = False) -> torch.Tensor:
+    """``a @ w.T`` with fp32 accumulation.  With ``swiglu`` the N columns are
+    interpreted as interleaved groups of 8 gate / 8 up columns."""
+    out = a.float() @ w.float().t()
+    if swiglu:
+        n = out.shape[-1]
+        g = out.view(*out.shape[:-1], n // 16, 2, 8)
+        out = (F.silu(g[..., 0, :]) * g[..., 1, :]).reshape(*out.shape[:-1], n // 2)
+    if bias is not None:
+        out = out + bias.float()
+    if residual is not None:
+        out = out + residual.float()
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if a.dtype.itemsize == 1 else a.dtype
+    return out.to(out_dtype)
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Row layout the fused SwiGLU epilogue expects: 8 gate rows, the 8 matching
+    up rows, 8 gate rows, ...  ([I,K],[I,K]) -> [2I,K]."""
+    i, k = w_gate.shape[-2:]
+    lead = w_gate.shape[:-2]
+    g = w_gate.reshape(*lead, i // 8, 1, 8, k)
+    u = w_up.reshape(*lead, i // 8, 1, 8, k)
+    return torch.cat([g, u], dim=-3).reshape(*lead, 2 * i, k)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
+                 swiglu: bool = False) -> torch.Tensor:
+    e = w.shape[0]
+    offs = expert_offsets.tolist()
+    n_out = w.shape[1] // 2 if swiglu else w.shape[1]
+    out = torch.zeros(a.shape[0], n_out, dtype=torch.bfloat16 if a.dtype.itemsize == 1 else a.dtype,
+                      device=a.device)
+    for i in range(e):
+        lo, hi = offs[i], offs[i + 1]
+        if hi > lo:
+            out[lo:hi] = gemm(a[lo:hi], w[i], swiglu=swiglu, out_dtype=out.dtype)
+    return out
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * w.float()).to(x.dtype)
+
+
+def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor,
+                       eps: float) -> torch.Tensor:
+    """residual <- x + residual (in place, rounded to its dtype); returns norm(residual)*w."""
+    residual.copy_((x.float() + residual.float()).to(residual.dtype))
+    return rms_norm(residual, w, eps)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    i = x.shape[-1] // 2
+    return (F.silu(x[..., :i].float()) * x[..., i:].float()).to(x.dtype)
+
+
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    t, h = x.shape
+    xf = x.float().view(t, h // 128, 128)
+    amax = xf.abs().amax(-1).clamp_min(1e-10)
+    scale = amax / 448.0
+    if ue8m0:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
+    q = (xf / scale.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.view(t, h), scale
+
+
+def dequant_fp8_block(wq: torch.Tensor, scale: torch.Tensor, block: Tuple[int, int] = (128, 128)) -> torch.Tensor:
+    """Weights [.., N, K] in e4m3 with one fp32 scale per (128 x 128) block."""
+    n, k = wq.shape[-2:]
+    bn, bk = block
+    s = scale.repeat_interleave(bn, dim=-2)[..., :n, :].repeat_interleave(bk, dim=-1)[..., :k]
+    return wq.float() * s
+
+
+def build_cos_sin_cache(rot_dim: int, max_pos: int, base: float = 10000.0,
+                        inv_freq: Optional[torch.Tensor] = None, mscale: float = 1.0,
+                        device=None) -> torch.Tensor:
+    """[max_pos, rot_dim] fp32: cos in the first half, sin in the second."""
+    if inv_freq is None:
+        inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    t = torch.arange(max_pos, dtype=torch.float32)
+    freqs = torch.outer(t, inv_freq.float().cpu())
+    cache = torch.cat([freqs.cos() * mscale, freqs.sin() * mscale], dim=-1)
+    return cache.to(device) if device is not None else cache
+
+
+def mrope_axis_of_freq(i: torch.Tensor, half: int, sec_t: int, sec_h: int,
+                       interleaved: bool) -> torch.Tensor:
+    """Which of the (t, h, w) position rows frequency index ``i`` reads."""
+    if not interleaved:
+        return torch.where(i < sec_t, 0, torch.where(i < sec_t + sec_h, 1, 2))
+    sec_w = half - sec_t - sec_h
+    m = i % 3
+    axis = torch.zeros_like(i)
+    axis = torch.where((m == 1) & (i < 3 * sec_h), torch.ones_like(i), axis)
+    axis = torch.where((m == 2) & (i < 3 * sec_w), torch.full_like(i, 2), axis)
+    return axis
+
+
+def _rope_one(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dim: int,
+              neox: bool) -> torch.Tensor:
+    """x [T, H, D]; cos/sin [T, rot/2]."""
+    xf = x.float()
+    rot, rest = xf[..., :rot_dim], xf[..., rot_dim:]
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    if neox:
+        x0, x1 = rot[..., : rot_dim // 2], rot[..., rot_dim // 2:]
+        y = torch.cat([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1)
+    else:
+        x0, x1 = rot[..., 0::2], rot[..., 1::2]
+        y = torch.stack([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1).flatten(-2)
+    return torch.cat([y, rest], dim=-1).to(x.dtype)
+
+
+def rope_qk(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+            head_dim: int, rot_dim: int, neox: bool = True,
+            mrope_section: Optional[Tuple[int, int, int]] = None,
+            mrope_interleaved: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [T, Hq*D], k [T, Hk*D]; returns rotated copies."""
+    half = rot_dim // 2
+    if mrope_section is None:
+        cs = cos_sin[positions.long()]
+        cos, sin = cs[:, :half], cs[:, half:]
+    else:
+        idx = torch.arange(half, device=q.device)
+        axis = mrope_axis_of_freq(idx, half, mrope_section[0], mrope_section[1], mrope_interleaved)
+        pos = positions.long()[axis, :]            # [half, T] -> pick per frequency
+        pos = pos.t()                              # [T, half]
+        cos = cos_sin[:, :half][pos, idx]
+        sin = cos_sin[:, half:][pos, idx]
+    t = q.shape[0]
+    qo = _rope_one(q.view(t, -1, head_dim), cos, sin, rot_dim, neox).reshape(q.shape)
+    ko = _rope_one(k.view(t, -1, head_dim), cos, sin, rot_dim, neox).reshape(k.shape)
+    return qo, ko
+
+
+def gqa_cache_write(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    slot_mapping: torch.Tensor) -> None:
+    """k [T, Hk*D] -> k_cache [blocks, Hk, bs, D] at slot (block*bs + off); negative slots skipped."""
+    nb, hk, bs, d = k_cache.shape
+    dv = v_cache.shape[-1]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    blk, off = slots // bs, slots % bs
+    k_cache[blk, :, off, :] = k[valid].view(-1, hk, d).to(k_cache.dtype)
+    v_cache[blk, :, off, :] = v[valid].view(-1, hk, dv).to(v_cache.dtype)
+
+
+def paged_scatter_rows(dst: torch.Tensor, src: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    valid = slot_mapping >= 0
+    dst.view(-1, dst.shape[-1])[slot_mapping[valid].long(), : src.shape[1]] = src[valid].to(dst.dtype)
+
+
+def _gather_kv(cache: torch.Tensor, block_table: torch.Tensor, n: int) -> torch.Tensor:
+    """cache [blocks, Hk, bs, D] -> [n, Hk, D] for one sequence."""
+    bs = cache.shape[2]
+    nblk = (n + bs - 1) // bs
+    x = cache[block_table[:nblk].long()]          # [nblk, Hk, bs, D]
+    return x.permute(0, 2, 1, 3).reshape(nblk * bs, cache.shape[1], cache.shape[3])[:n]
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
+                    num_q_heads: int, scale: float, causal: bool = True, window: int = 0,
+                    return_lse: bool = False):
+    """Variable-length attention over the paged cache.  q [T, Hq*Dqk]; the queries of
+    sequence b are rows cu_q[b]:cu_q[b+1] and sit at the END of its seq_lens[b] cached tokens."""
+    hk, dqk, dv = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
+    hq = num_q_heads
+    g = hq // hk
+    t = q.shape[0]
+    out = torch.zeros(t, hq * dv, dtype=q.dtype, device=q.device)
+    lse = torch.full((t, hq), float("-inf"), dtype=torch.float32, device=q.device)
+    cu = cu_q.tolist()
+    sl = seq_lens.tolist()
+    for b in range(len(sl)):
+        qs, qe = cu[b], cu[b + 1]
+        ql, n = qe - qs, sl[b]
+        if ql == 0:
+            continue
+        kk = _gather_kv(k_cache, block_tables[b], n).float().repeat_interleave(g, dim=1)  # [n,Hq,D]
+        vv = _gather_kv(v_cache, block_tables[b], n).float().repeat_interleave(g, dim=1)
+        qq = q[qs:qe].view(ql, hq, dqk).float()
+        s = torch.einsum("qhd,khd->hqk", qq, kk) * scale
+        pos_q = torch.arange(n - ql, n, device=q.device).view(1, ql, 1)
+        pos_k = torch.arange(n, device=q.device).view(1, 1, n)
+        mask = torch.ones(1, ql, n, dtype=torch.bool, device=q.device)
+        if causal:
+            mask &= pos_k <= pos_q
+        if window > 0:
+            mask &= pos_k > pos_q - window
+        s = s.masked_fill(~mask, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l.unsqueeze(-1))
+        p = torch.nan_to_num(p, nan=0.0)
+        o = torch.einsum("hqk,khd->qhd", p, vv)
+        out[qs:qe] = o.reshape(ql, hq * dv).to(q.dtype)
+        lse[qs:qe] = l.t()
+    return (out, lse) if return_lse else out
+
+
+def merge_attn_states(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor,
+                      lse2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """LSE-weighted merge of two partial attention results.  o [T,H,D], lse [T,H]."""
+    m = torch.maximum(lse1, lse2)
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w1, w2 = torch.exp(lse1 - m), torch.exp(lse2 - m)
+    den = (w1 + w2).clamp_min(1e-30)
+    o = (o1.float() * (w1 / den).unsqueeze(-1) + o2.float() * (w2 / den).unsqueeze(-1)).to(o1.dtype)
+    return o, m + torch.log(den)
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    return logits.float().argmax(dim=-1).to(torch.int32)
+
+
+def apply_top_k_top_p(logits: torch.Tensor, top_k: Optional[torch.Tensor],
+                      top_p: Optional[torch.Tensor]) -> torch.Tensor:
+    """Mask (to -inf) everything outside the top-k / nucleus set; ties at the
+    k-th value are kept.  logits [B,V] fp32."""
+    logits = logits.float().clone()
+    b, v = logits.shape
+    if top_k is not None:
+        k = top_k.clamp(min=1, max=v).long()
+        k = torch.where(top_k.long() <= 0, torch.full_like(k, v), k)
+        srt = logits.sort(dim=-1, descending=True).values
+        kth = srt.gather(1, (k - 1).unsqueeze(1))
+        logits = logits.masked_fill(logits < kth, float("-inf"))
+    if top_p is not None:
+        probs = logits.softmax(dim=-1)
+        srt, idx = probs.sort(dim=-1, descending=True)
+        csum = srt.cumsum(dim=-1)
+        # keep the smallest prefix whose mass reaches p (always at least one token)
+        drop = (csum - srt) >= top_p.unsqueeze(1)
+        drop[:, 0] = False
+        thr = torch.where(drop, torch.full_like(srt, 2.0), srt).amin(dim=-1, keepdim=True)
+        logits = logits.masked_fill(probs < thr, float("-inf"))
+    return logits
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    logits = logits.float()
+    greedy = argmax(logits)
+    if temperature is None:
+        temperature = torch.ones(logits.shape[0], device=logits.device)
+    t = temperature.clamp_min(1e-5).unsqueeze(1)
+    masked = apply_top_k_top_p(logits / t, top_k, top_p)
+    probs = masked.softmax(dim=-1)
+    e = torch.empty_like(probs).exponential_(1.0, generator=generator)
+    tok = (probs / e).argmax(dim=-1).to(torch.int32)
+    return torch.where(temperature < 1e-5, greedy, tok)

@@ -1,0 +1,195 @@
+"""Device communicator: the collective surface every parallel layer uses.
+
+``B200Communicator`` exposes the same primitives as the reference's
+``NPUCommunicator`` (omni_npu/distributed/communicator.py:17-278): all_reduce,
+all_gather / all_gatherv, reduce_scatter / reduce_scatterv, gather,
+all_to_all (list based, with scatter/gather sizes), send / recv, and the
+expert-parallel ``dispatch`` / ``combine`` pair, which here are real device
+operations rather than no-ops.
+
+Transport: ``torch.distributed`` (NCCL over NVLink/NVSwitch on GPUs, gloo on
+CPU) for bootstrap, point-to-point and as the general path; when a
+``SymmetricMemory`` pool is attached (see :mod:`.symm_mem`) the latency-bound
+collectives run as this library's own peer-memory kernels.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+import torch
+import torch.distributed as dist
+
+
+class B200Communicator:
+    def __init__(self, cpu_group=None, device: Optional[torch.device] = None, device_group=None,
+                 unique_name: str = "") -> None:
+        self.cpu_group = cpu_group
+        self.device_group = device_group if device_group is not None else cpu_group
+        self.device = device or torch.device("cpu")
+        self.unique_name = unique_name
+        if self.device_group is not None and dist.is_initialized():
+            self.world_size = dist.get_world_size(self.device_group)
+            self.rank_in_group = dist.get_rank(self.device_group)
+            self.ranks = dist.get_process_group_ranks(self.device_group)
+        else:
+            self.world_size, self.rank_in_group, self.ranks = 1, 0, [0]
+        self.symm = None            # SymmetricMemory pool (attached lazily on CUDA)
+        self.ep_buffers = None      # expert-parallel dispatch/combine state
+
+    # ------------------------------------------------------------ basic ops
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        if self.symm is not None and self.symm.can_all_reduce(x):
+            return self.symm.all_reduce(x)
+        dist.all_reduce(x, group=self.device_group)
+        return x
+
+    def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        if dim < 0:
+            dim += x.dim()
+        xc = x.contiguous()
+        out = torch.empty((self.world_size,) + tuple(xc.shape), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, xc, group=self.device_group)
+        if dim == 0:
+            return out.reshape((self.world_size * x.shape[0],) + tuple(x.shape[1:]))
+        out = out.movedim(0, dim)
+        shape = list(x.shape)
+        shape[dim] *= self.world_size
+        return out.reshape(shape)
+
+    def reduce_scatter(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        if dim < 0:
+            dim += x.dim()
+        xm = x.movedim(dim, 0).contiguous()
+        assert xm.shape[0] % self.world_size == 0
+        chunk = xm.shape[0] // self.world_size
+        out = torch.empty((chunk,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, xm, group=self.device_group)
+        return out.movedim(0, dim)
+
+    def all_gatherv(self, x: Union[torch.Tensor, List[torch.Tensor]], dim: int = 0,
+                    sizes: Optional[Sequence[int]] = None):
+        """All-gather of tensors whose size along ``dim`` differs per rank."""
+        if isinstance(x, (list, tuple)):
+            return [self.all_gatherv(t, dim, sizes) for t in x]
+        if self.world_size == 1:
+            return x
+        if sizes is None:
+            return self.all_gather(x, dim)
+        assert dim == 0, "ragged all-gather is along the leading dimension"
+        assert x.shape[0] == sizes[self.rank_in_group]
+        outs = [torch.empty((s,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device) for s in sizes]
+        dist.all_gather(outs, x.contiguous(), group=self.device_group)
+        return torch.cat(outs, dim=0)
+
+    def reduce_scatterv(self, x: torch.Tensor, dim: int = 0,
+                        sizes: Optional[Sequence[int]] = None) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        if sizes is None:
+            return self.reduce_scatter(x, dim)
+        assert dim == 0
+        chunks = list(torch.split(x.contiguous(), list(sizes), dim=0))
+        out = torch.empty_like(chunks[self.rank_in_group])
+        dist.reduce_scatter(out, chunks, group=self.device_group)
+        return out
+
+    def gather(self, x: torch.Tensor, dst: int = 0, dim: int = -1) -> Optional[torch.Tensor]:
+        if self.world_size == 1:
+            return x
+        if dim < 0:
+            dim += x.dim()
+        outs = None
+        if self.rank_in_group == dst:
+            outs = [torch.empty_like(x) for _ in range(self.world_size)]
+        dist.gather(x.contiguous(), outs, dst=self.ranks[dst], group=self.device_group)
+        return torch.cat(outs, dim=dim) if outs is not None else None
+
+    def broadcast(self, x: torch.Tensor, src: int = 0) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        dist.broadcast(x, src=self.ranks[src], group=self.device_group)
+        return x
+
+    def all_to_all(self, x: torch.Tensor, scatter_dim: int = 0, gather_dim: int = -1,
+                   scatter_sizes: Optional[Sequence[int]] = None,
+                   gather_sizes: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Split ``x`` along scatter_dim (evenly or by scatter_sizes), exchange,
+        concatenate what arrives along gather_dim."""
+        if self.world_size == 1:
+            return x
+        if scatter_dim < 0:
+            scatter_dim += x.dim()
+        if gather_dim < 0:
+            gather_dim += x.dim()
+        if scatter_sizes is not None:
+            ins = [t.contiguous() for t in torch.split(x, list(scatter_sizes), dim=scatter_dim)]
+        else:
+            ins = [t.contiguous() for t in torch.tensor_split(x, self.world_size, dim=scatter_dim)]
+        outs = []
+        for r in range(self.world_size):
+            shape = list(ins[self.rank_in_group].shape)
+            if gather_sizes is not None:
+                shape[gather_dim] = gather_sizes[r]
+            elif scatter_sizes is not None and scatter_dim == gather_dim:
+                raise ValueError("gather_sizes required for ragged exchange along one dim")
+            outs.append(torch.empty(shape, dtype=x.dtype, device=x.device))
+        dist.all_to_all(outs, ins, group=self.device_group)
+        return torch.cat(outs, dim=gather_dim)
+
+    def all_to_all_single(self, x: torch.Tensor, output_split_sizes=None,
+                          input_split_sizes=None) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        n_out = sum(output_split_sizes) if output_split_sizes is not None else x.shape[0]
+        out = torch.empty((n_out,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes, input_split_sizes,
+                               group=self.device_group)
+        return out
+
+    def send(self, x: torch.Tensor, dst: Optional[int] = None) -> None:
+        """Point-to-point send inside the group; default destination is the next rank (ring)."""
+        if dst is None:
+            dst = (self.rank_in_group + 1) % self.world_size
+        dist.send(x, self.ranks[dst], group=self.device_group)
+
+    def recv(self, size, dtype: torch.dtype, src: Optional[int] = None) -> torch.Tensor:
+        if src is None:
+            src = (self.rank_in_group - 1) % self.world_size
+        out = torch.empty(size, dtype=dtype, device=self.device)
+        dist.recv(out, self.ranks[src], group=self.device_group)
+        return out
+
+    def barrier(self) -> None:
+        if self.world_size > 1:
+            dist.barrier(group=self.cpu_group if self.cpu_group is not None else self.device_group)
+
+    # ------------------------------------------------- expert-parallel pair
+    def prepare_communication_buffer_for_model(self, model: torch.nn.Module) -> None:
+        """Give every MoE layer of ``model`` its dispatch/combine buffers
+        (counterpart of maybe_init_modular_kernel in the reference,
+        omni_npu/distributed/communicator.py:41-50)."""
+        for m in model.modules():
+            hook = getattr(m, "init_ep_buffers", None)
+            if callable(hook):
+                hook(self)
+
+    def dispatch(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                 num_experts: int, **kw):
+        from ..layers.moe_dispatch import ep_dispatch
+        return ep_dispatch(self, hidden, topk_ids, topk_weights, num_experts, **kw)
+
+    def combine(self, expert_out: torch.Tensor, handle, **kw) -> torch.Tensor:
+        from ..layers.moe_dispatch import ep_combine
+        return ep_combine(self, expert_out, handle, **kw)
+
+    def destroy(self) -> None:
+        if self.symm is not None:
+            self.symm.close()
+            self.symm = None
+        self.ep_buffers = None

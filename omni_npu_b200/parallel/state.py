@@ -1,0 +1,256 @@
+"""Process-group state: world, tensor / pipeline / data / expert parallel groups,
+a node-local group, and named per-layer groups.
+
+Rank layout (outermost to innermost): DP x PP x TP, the same order vLLM uses,
+so rank = dp * (pp * tp) + pp_rank * tp + tp_rank.  The expert-parallel group
+spans DP x TP of one pipeline stage.  Every group owns a device process group
+(NCCL on GPUs, gloo on CPU), a gloo CPU group for host-side barriers and object
+exchange, and a :class:`B200Communicator`.
+
+Per-layer groups (the reference's "layer parallel" JSON,
+omni_npu/v1/distributed/parallel_state_ext.py:123-193,380-545) let single
+linears run with a TP degree or rank list different from the model-wide one.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+import torch.distributed as dist
+
+from .communicator import B200Communicator
+
+
+class GroupCoordinator:
+    def __init__(self, ranks: Sequence[int], device: torch.device, backend: str, name: str,
+                 all_rank_lists: Optional[Sequence[Sequence[int]]] = None) -> None:
+        self.name = name
+        self.ranks = list(ranks)
+        self.world_size = len(self.ranks)
+        self.device = device
+        my = dist.get_rank() if dist.is_initialized() else 0
+        self.rank_in_group = self.ranks.index(my) if my in self.ranks else 0
+        self.device_group = None
+        self.cpu_group = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # new_group is collective over the default group: every rank must
+            # create every subgroup, in the same order.
+            for rl in (all_rank_lists or [self.ranks]):
+                dg = dist.new_group(list(rl), backend=backend)
+                cg = dg if backend == "gloo" else dist.new_group(list(rl), backend="gloo")
+                if my in rl:
+                    self.device_group, self.cpu_group = dg, cg
+        self.comm = B200Communicator(self.cpu_group, device, self.device_group, unique_name=name)
+
+    @property
+    def is_first_rank(self) -> bool:
+        return self.rank_in_group == 0
+
+    @property
+    def is_last_rank(self) -> bool:
+        return self.rank_in_group == self.world_size - 1
+
+    # thin forwards so call sites read like the usual group API
+    def all_reduce(self, x):
+        return self.comm.all_reduce(x)
+
+    def all_gather(self, x, dim=-1):
+        return self.comm.all_gather(x, dim)
+
+    def reduce_scatter(self, x, dim=-1):
+        return self.comm.reduce_scatter(x, dim)
+
+    def all_gatherv(self, x, dim=0, sizes=None):
+        return self.comm.all_gatherv(x, dim, sizes)
+
+    def reduce_scatterv(self, x, dim=0, sizes=None):
+        return self.comm.reduce_scatterv(x, dim, sizes)
+
+    def all_to_all_single(self, x, output_split_sizes=None, input_split_sizes=None):
+        return self.comm.all_to_all_single(x, output_split_sizes, input_split_sizes)
+
+    def broadcast(self, x, src=0):
+        return self.comm.broadcast(x, src)
+
+    def broadcast_object(self, obj, src: int = 0):
+        if self.world_size == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.ranks[src], group=self.cpu_group)
+        return box[0]
+
+    def all_gather_object(self, obj) -> list:
+        if self.world_size == 1:
+            return [obj]
+        out = [None] * self.world_size
+        dist.all_gather_object(out, obj, group=self.cpu_group)
+        return out
+
+    def barrier(self):
+        self.comm.barrier()
+
+    def send(self, x, dst=None):
+        self.comm.send(x, dst)
+
+    def recv(self, size, dtype, src=None):
+        return self.comm.recv(size, dtype, src)
+
+    def destroy(self):
+        self.comm.destroy()
+
+
+@dataclass
+class _State:
+    world: Optional[GroupCoordinator] = None
+    tp: Optional[GroupCoordinator] = None
+    pp: Optional[GroupCoordinator] = None
+    dp: Optional[GroupCoordinator] = None
+    ep: Optional[GroupCoordinator] = None
+    local: Optional[GroupCoordinator] = None
+    layer_groups: Optional[Dict[str, GroupCoordinator]] = None
+    backend: str = "gloo"
+    device: Optional[torch.device] = None
+    initialized: bool = False
+
+
+_S = _State()
+
+
+def init_distributed(device: torch.device, backend: Optional[str] = None,
+                     init_method: Optional[str] = None, world_size: Optional[int] = None,
+                     rank: Optional[int] = None, timeout_s: float = 600.0) -> None:
+    """Join the default process group (env:// by default).  A single process
+    without RANK/WORLD_SIZE in the environment stays un-initialised: every
+    group then has world size 1 and every collective is the identity."""
+    import datetime
+    world_size = int(os.environ.get("WORLD_SIZE", "1")) if world_size is None else world_size
+    rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+    backend = backend or ("nccl" if device.type == "cuda" else "gloo")
+    _S.backend, _S.device = backend, device
+    if world_size > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        kw = {}
+        if device.type == "cuda":
+            kw["device_id"] = device
+        dist.init_process_group(backend=backend, init_method=init_method or "env://",
+                                world_size=world_size, rank=rank,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+
+
+def init_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, device: Optional[torch.device] = None,
+                        backend: Optional[str] = None) -> None:
+    device = device or _S.device or torch.device("cpu")
+    backend = backend or _S.backend or ("nccl" if device.type == "cuda" else "gloo")
+    _S.device, _S.backend = device, backend
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world != tp * pp * dp:
+        raise ValueError(f"world size {world} != tp {tp} * pp {pp} * dp {dp}")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    grid = torch.arange(world).view(dp, pp, tp)
+
+    def make(name: str, lists: List[List[int]]) -> GroupCoordinator:
+        mine = next(l for l in lists if rank in l)
+        return GroupCoordinator(mine, device, backend, name, all_rank_lists=lists)
+
+    _S.world = make("world", [list(range(world))])
+    _S.tp = make("tp", grid.reshape(-1, tp).tolist())
+    _S.pp = make("pp", grid.permute(0, 2, 1).reshape(-1, pp).tolist())
+    _S.dp = make("dp", grid.permute(1, 2, 0).reshape(-1, dp).tolist())
+    _S.ep = make("ep", grid.permute(1, 0, 2).reshape(pp, dp * tp).tolist())
+    _S.local = _S.world
+    _S.layer_groups = {}
+    _S.initialized = True
+
+
+def model_parallel_is_initialized() -> bool:
+    return _S.initialized
+
+
+def ensure_initialized(device: Optional[torch.device] = None) -> None:
+    if not _S.initialized:
+        init_model_parallel(1, 1, 1, device or torch.device("cpu"))
+
+
+def _get(name: str) -> GroupCoordinator:
+    ensure_initialized()
+    return getattr(_S, name)
+
+
+def get_world_group() -> GroupCoordinator:
+    return _get("world")
+
+
+def get_tp_group() -> GroupCoordinator:
+    return _get("tp")
+
+
+def get_pp_group() -> GroupCoordinator:
+    return _get("pp")
+
+
+def get_dp_group() -> GroupCoordinator:
+    return _get("dp")
+
+
+def get_ep_group() -> GroupCoordinator:
+    return _get("ep")
+
+
+def get_local_world_group() -> GroupCoordinator:
+    return _get("local")
+
+
+def tp_world_size() -> int:
+    return get_tp_group().world_size
+
+
+def tp_rank() -> int:
+    return get_tp_group().rank_in_group
+
+
+# ------------------------------------------------------------ per-layer groups
+def register_layer_group(key: str, tp_size_or_ranks: Union[int, Sequence[Sequence[int]]]) -> GroupCoordinator:
+    """Create (collectively) a named group.  An int n partitions the world into
+    consecutive groups of n ranks; a list of rank lists is used as given."""
+    ensure_initialized()
+    world = _S.world.world_size
+    if isinstance(tp_size_or_ranks, int):
+        n = tp_size_or_ranks
+        if world % n != 0:
+            raise ValueError(f"layer group size {n} does not divide world size {world}")
+        lists = [list(range(i, i + n)) for i in range(0, world, n)]
+    else:
+        lists = [list(l) for l in tp_size_or_ranks]
+        flat = sorted(r for l in lists for r in l)
+        if flat != list(range(world)):
+            raise ValueError("layer group rank lists must partition the world")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    mine = next(l for l in lists if rank in l)
+    g = GroupCoordinator(mine, _S.device, _S.backend, f"layer:{key}", all_rank_lists=lists)
+    _S.layer_groups[key] = g
+    return g
+
+
+def get_layer_group(key: str) -> Optional[GroupCoordinator]:
+    ensure_initialized()
+    return _S.layer_groups.get(key)
+
+
+def destroy_model_parallel() -> None:
+    for g in (_S.tp, _S.pp, _S.dp, _S.ep, _S.world):
+        if g is not None:
+            g.destroy()
+    for g in (_S.layer_groups or {}).values():
+        g.destroy()
+    _S.world = _S.tp = _S.pp = _S.dp = _S.ep = _S.local = None
+    _S.layer_groups = None
+    _S.initialized = False
+
+
+def destroy_distributed() -> None:
+    destroy_model_parallel()
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -1,0 +1,227 @@
+"""Persistent per-request rows and per-step input staging.
+
+Each running request owns a row of host-side numpy arrays (block table, number
+of computed tokens, sampling parameters).  A step's device inputs are built with
+vectorised numpy operations into ONE pinned int32 staging buffer laid out as
+
+    [ input_ids | positions | slot_mapping | seq_lens | cu_q | temperature(f32 bits)
+      | top_k | top_p(f32 bits) | block_table rows ]
+
+and shipped with a single host-to-device copy.  For every CUDA-graph batch size
+the section offsets are fixed, so the captured graph reads the same device
+addresses at every replay.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..engine.request import Request
+
+
+@dataclass
+class StepLayout:
+    """Offsets (in int32 elements) of each section for a given (tokens, seqs) capacity."""
+    T: int
+    S: int
+    max_blocks: int
+    ids: int = 0
+    pos: int = 0
+    slot: int = 0
+    seq_lens: int = 0
+    cu_q: int = 0
+    temp: int = 0
+    top_k: int = 0
+    top_p: int = 0
+    seeds: int = 0
+    logits_idx: int = 0
+    bt: int = 0
+    total: int = 0
+
+    @classmethod
+    def make(cls, T: int, S: int, max_blocks: int) -> "StepLayout":
+        lay = cls(T, S, max_blocks)
+        off = 0
+        for name, n in (("ids", T), ("pos", T), ("slot", T), ("seq_lens", S), ("cu_q", S + 1),
+                        ("temp", S), ("top_k", S), ("top_p", S), ("seeds", 2 * S),
+                        ("logits_idx", S), ("bt", S * max_blocks)):
+            off = (off + 3) // 4 * 4           # 16-byte aligned sections
+            setattr(lay, name, off)
+            off += n
+        lay.total = (off + 3) // 4 * 4
+        return lay
+
+
+class InputBatch:
+    def __init__(self, max_num_seqs: int, max_model_len: int, block_size: int,
+                 max_num_batched_tokens: int, device: torch.device) -> None:
+        self.max_num_seqs = max_num_seqs
+        self.block_size = block_size
+        self.max_blocks = (max_model_len + block_size - 1) // block_size
+        self.device = device
+        self.num_rows = 0
+        self.rows: List[Optional[Request]] = [None] * max_num_seqs
+        self.row_of: Dict[str, int] = {}
+        self.block_table = np.zeros((max_num_seqs, self.max_blocks), dtype=np.int32)
+        self.num_blocks = np.zeros(max_num_seqs, dtype=np.int32)
+        self.temperature = np.zeros(max_num_seqs, dtype=np.float32)
+        self.top_k = np.zeros(max_num_seqs, dtype=np.int32)
+        self.top_p = np.ones(max_num_seqs, dtype=np.float32)
+        self.seeds = np.zeros(max_num_seqs, dtype=np.int64)
+        cap_T = max(max_num_batched_tokens, max_num_seqs)
+        self.capacity = StepLayout.make(cap_T, max_num_seqs, self.max_blocks)
+        pin = device.type == "cuda"
+        self.host = torch.zeros(self.capacity.total, dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.capacity.total, dtype=torch.int32, device=device)
+        self.h2d_bytes_last = 0
+
+    # ------------------------------------------------------------------ rows
+    def add_request(self, req: Request) -> int:
+        row = self.row_of.get(req.request_id)
+        if row is None:
+            row = self.num_rows
+            if row >= self.max_num_seqs:
+                raise RuntimeError("input batch is full")
+            self.num_rows += 1
+            self.rows[row] = req
+            self.row_of[req.request_id] = row
+            self.num_blocks[row] = 0
+            sp = req.sampling_params
+            self.temperature[row] = sp.temperature
+            self.top_k[row] = sp.top_k if sp.top_k and sp.top_k > 0 else 0
+            self.top_p[row] = sp.top_p
+            seed = sp.seed if sp.seed is not None else hash(req.request_id) & 0x7FFFFFFFFFFFFFFF
+            self.seeds[row] = seed
+        self.sync_blocks(row, req)
+        return row
+
+    def sync_blocks(self, row: int, req: Request) -> None:
+        have, want = int(self.num_blocks[row]), len(req.block_ids)
+        if want > have:
+            self.block_table[row, have:want] = req.block_ids[have:want]
+            self.num_blocks[row] = want
+        elif want < have:                        # request was preempted and re-admitted
+            self.block_table[row, :want] = req.block_ids
+            self.num_blocks[row] = want
+
+    def remove_request(self, request_id: str) -> None:
+        row = self.row_of.pop(request_id, None)
+        if row is None:
+            return
+        last = self.num_rows - 1
+        if row != last:
+            moved = self.rows[last]
+            self.rows[row] = moved
+            self.row_of[moved.request_id] = row
+            self.block_table[row] = self.block_table[last]
+            for arr in (self.num_blocks, self.temperature, self.top_k, self.top_p, self.seeds):
+                arr[row] = arr[last]
+        self.rows[last] = None
+        self.num_rows = last
+
+    # ----------------------------------------------------------------- staging
+    def layout_for(self, T: int, S: int) -> StepLayout:
+        return StepLayout.make(T, S, self.max_blocks)
+
+    def views(self, lay: StepLayout, buf: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """Typed views into ``buf`` (host or device) for a layout."""
+        T, S, mb = lay.T, lay.S, lay.max_blocks
+        return {
+            "ids": buf[lay.ids: lay.ids + T],
+            "pos": buf[lay.pos: lay.pos + T],
+            "slot": buf[lay.slot: lay.slot + T],
+            "seq_lens": buf[lay.seq_lens: lay.seq_lens + S],
+            "cu_q": buf[lay.cu_q: lay.cu_q + S + 1],
+            "temp": buf[lay.temp: lay.temp + S].view(torch.float32),
+            "top_k": buf[lay.top_k: lay.top_k + S],
+            "top_p": buf[lay.top_p: lay.top_p + S].view(torch.float32),
+            "seeds": buf[lay.seeds: lay.seeds + 2 * S].view(torch.int64),
+            "logits_idx": buf[lay.logits_idx: lay.logits_idx + S],
+            "bt": buf[lay.bt: lay.bt + S * mb].view(S, mb),
+        }
+
+    def upload(self, lay: StepLayout) -> None:
+        """One H2D copy of the staged step (pinned host -> device)."""
+        self.dev[: lay.total].copy_(self.host[: lay.total], non_blocking=True)
+        self.h2d_bytes_last = lay.total * 4
+
+    def _fill_sampling(self, lay: StepLayout, rows: np.ndarray, n: int) -> None:
+        h = self.host_np
+        h[lay.temp: lay.temp + n] = self.temperature[rows].view(np.int32)
+        h[lay.top_k: lay.top_k + n] = self.top_k[rows]
+        h[lay.top_p: lay.top_p + n] = self.top_p[rows].view(np.int32)
+        h[lay.seeds: lay.seeds + 2 * n] = self.seeds[rows].view(np.int32)
+        if lay.S > n:
+            h[lay.temp + n: lay.temp + lay.S] = 0
+            h[lay.top_k + n: lay.top_k + lay.S] = 0
+            h[lay.top_p + n: lay.top_p + lay.S] = np.float32(1.0).view(np.int32)
+
+    def stage_decode(self, lay: StepLayout, reqs: Sequence[Request], q_len: int = 1) -> np.ndarray:
+        """Stage a decode step for ``reqs`` (one new token each) padded to lay.S
+        sequences.  Returns the row indices used."""
+        n = len(reqs)
+        bs = self.block_size
+        h = self.host_np
+        rows = np.fromiter((self.row_of[r.request_id] for r in reqs), dtype=np.int64, count=n)
+        for r, row in zip(reqs, rows):
+            if len(r.block_ids) != self.num_blocks[row]:
+                self.sync_blocks(int(row), r)
+        pos = np.fromiter((r.num_tokens - 1 for r in reqs), dtype=np.int32, count=n)
+        ids = np.fromiter((r.output_token_ids[-1] if r.output_token_ids else r.prompt_token_ids[-1]
+                           for r in reqs), dtype=np.int32, count=n)
+        h[lay.ids: lay.ids + n] = ids
+        h[lay.pos: lay.pos + n] = pos
+        blk = self.block_table[rows, pos // bs]
+        h[lay.slot: lay.slot + n] = blk * bs + pos % bs
+        h[lay.seq_lens: lay.seq_lens + n] = pos + 1
+        if lay.S > n:
+            # padded sequences: length 1 over block 0, results discarded
+            h[lay.ids + n: lay.ids + lay.T] = 0
+            h[lay.pos + n: lay.pos + lay.T] = 0
+            h[lay.slot + n: lay.slot + lay.T] = -1
+            h[lay.seq_lens + n: lay.seq_lens + lay.S] = 1
+        h[lay.cu_q: lay.cu_q + lay.S + 1] = np.arange(lay.S + 1, dtype=np.int32) * q_len
+        h[lay.logits_idx: lay.logits_idx + lay.S] = np.arange(lay.S, dtype=np.int32)
+        self._fill_sampling(lay, rows, n)
+        bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
+        bt[:n] = self.block_table[rows]
+        if lay.S > n:
+            bt[n:] = 0
+        return rows
+
+    def stage_prefill(self, lay: StepLayout, seqs) -> Tuple[np.ndarray, int]:
+        """Stage a prefill step.  ``seqs`` are ScheduledSeq (request, start,
+        num_new_tokens).  Returns (rows, max_q_len)."""
+        h = self.host_np
+        bs = self.block_size
+        n = len(seqs)
+        rows = np.empty(n, dtype=np.int64)
+        off = 0
+        max_q = 0
+        cu = h[lay.cu_q: lay.cu_q + n + 1]
+        cu[0] = 0
+        for i, s in enumerate(seqs):
+            req = s.request
+            row = self.add_request(req)
+            rows[i] = row
+            q = s.num_new_tokens
+            max_q = max(max_q, q)
+            toks = req.prompt_token_ids[s.start: s.start + q]
+            if len(toks) < q:                     # recomputation after preemption reaches into outputs
+                toks = req.all_token_ids[s.start: s.start + q]
+            h[lay.ids + off: lay.ids + off + q] = toks
+            p = np.arange(s.start, s.start + q, dtype=np.int32)
+            h[lay.pos + off: lay.pos + off + q] = p
+            h[lay.slot + off: lay.slot + off + q] = self.block_table[row, p // bs] * bs + p % bs
+            h[lay.seq_lens + i] = s.start + q
+            off += q
+            cu[i + 1] = off
+            h[lay.logits_idx + i] = off - 1
+        self._fill_sampling(lay, rows, n)
+        bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
+        bt[:n] = self.block_table[rows]
+        return rows, max_q

@@ -1,0 +1,321 @@
+"""Standalone model runner: owns the model, the paged KV cache, the persistent
+input batch and the CUDA-graph cache, and turns a scheduler output into
+sampled token ids.
+
+It is self-contained (it does not derive from vLLM's GPU model runner, which
+the reference does: omni_npu/worker/npu_model_runner.py:68).  Responsibilities
+matching the reference's runner: ``load_model`` (+ graph wrapping, :237-272),
+``get_kv_cache_spec`` / ``initialize_kv_cache`` (:125-187), ``capture_model``
+(:274-281), ``execute_model`` / ``sample_tokens`` (:283-297) and
+``_dummy_run`` (:306-583).
+
+Decode steps replay a CUDA graph that contains the whole step: embedding,
+all layers (attention reads lengths and block tables from device buffers),
+LM head and sampling.  Prefill steps run eagerly.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..attention.gqa import GQABackend
+from ..attention.metadata import AttentionMetadata, set_forward_context
+from ..compilation.cuda_graph import CUDAGraphRunner
+from ..config import EngineConfig
+from ..engine.scheduler import SchedulerOutput
+from ..logger import logger
+from ..models.registry import resolve_model_cls
+from ..models.utils import iter_safetensors, random_init_
+from ..parallel import state as pstate
+from ..sample.sampler import Sampler
+from .input_batch import InputBatch, StepLayout
+
+
+@dataclass
+class KVCacheSpec:
+    kind: str                  # "gqa" | "mla" | "dsa"
+    num_layers: int
+    block_size: int
+    bytes_per_block: int       # all layers of this rank
+    shapes: Dict[str, Tuple[int, ...]]
+
+
+class ModelRunner:
+    def __init__(self, config: EngineConfig, device: torch.device) -> None:
+        self.config = config
+        self.device = device
+        self.model_config = config.model
+        self.model: Optional[torch.nn.Module] = None
+        self.kv_caches: List = []
+        self.num_blocks = 0
+        sc = config.scheduler
+        self.input_batch = InputBatch(sc.max_num_seqs, sc.max_model_len, config.cache.block_size,
+                                      sc.max_num_batched_tokens, device)
+        self.sampler = Sampler(config, device)
+        self.graphs: Dict[int, CUDAGraphRunner] = {}
+        self.capture_sizes: List[int] = []
+        pin = device.type == "cuda"
+        self.sampled_host = torch.zeros(max(sc.max_num_seqs, 1), dtype=torch.int32, pin_memory=pin)
+        self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
+        self.d2h_bytes_last = 0
+        self.kv_connector = None
+        self.timings: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ model
+    def load_model(self) -> None:
+        cfg = self.config
+        t0 = time.time()
+        cls = resolve_model_cls(cfg.model.architecture)
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(cfg.model.dtype)
+        try:
+            self.model = cls(cfg, device=self.device)
+        finally:
+            torch.set_default_dtype(prev)
+        if cfg.model_path and cfg.load_format != "dummy":
+            loaded = self.model.load_weights(iter_safetensors(cfg.model_path))
+            logger.info("loaded %d tensors from %s", len(loaded), cfg.model_path)
+        else:
+            random_init_(self.model, seed=cfg.seed)
+        for m in self.model.modules():
+            hook = getattr(m, "process_weights_after_loading", None)
+            if callable(hook):
+                hook()
+        post = getattr(self.model, "post_load", None)
+        if callable(post):
+            post()
+        self.model.eval()
+        tp = pstate.get_tp_group()
+        ep = pstate.get_ep_group()
+        tp.comm.prepare_communication_buffer_for_model(self.model)
+        if ep is not tp:
+            ep.comm.prepare_communication_buffer_for_model(self.model)
+        self.timings["load_model_s"] = time.time() - t0
+
+    def get_model(self) -> torch.nn.Module:
+        return self.model
+
+    # --------------------------------------------------------------- KV cache
+    def get_kv_cache_spec(self) -> KVCacheSpec:
+        mc = self.model_config
+        bs = self.config.cache.block_size
+        tp = pstate.tp_world_size()
+        spec_fn = getattr(self.model, "get_kv_cache_spec", None)
+        if callable(spec_fn):
+            return spec_fn(bs)
+        hk = max(1, mc.num_kv_heads // tp)
+        per_layer = GQABackend.bytes_per_block(bs, hk, mc.head_dim, mc.dtype)
+        k_shape, v_shape = GQABackend.get_kv_cache_shape(1, bs, hk, mc.head_dim)
+        return KVCacheSpec("gqa", mc.num_layers, bs, per_layer * mc.num_layers,
+                           {"k": k_shape[1:], "v": v_shape[1:]})
+
+    @torch.inference_mode()
+    def profile_run(self) -> int:
+        """One eager prefill-shaped forward with the largest token count to find
+        the activation peak.  Returns peak bytes allocated during the run."""
+        if self.device.type != "cuda":
+            return 0
+        torch.cuda.synchronize(self.device)
+        torch.cuda.reset_peak_memory_stats(self.device)
+        before = torch.cuda.memory_allocated(self.device)
+        sc = self.config.scheduler
+        self._init_kv_cache_tensors(num_blocks=max(8, sc.max_num_batched_tokens // self.config.cache.block_size + 8))
+        self._dummy_run(num_tokens=sc.max_num_batched_tokens, prefill=True)
+        torch.cuda.synchronize(self.device)
+        peak = torch.cuda.max_memory_allocated(self.device) - before
+        self.kv_caches = []
+        torch.cuda.empty_cache()
+        return peak
+
+    def determine_num_blocks(self) -> int:
+        cc = self.config.cache
+        if cc.num_gpu_blocks:
+            return cc.num_gpu_blocks
+        spec = self.get_kv_cache_spec()
+        if self.device.type != "cuda":
+            return max(64, 4 * self.config.scheduler.max_num_seqs)
+        peak = self.profile_run()
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * cc.gpu_memory_utilization) - (total - free) - peak
+        n = budget // spec.bytes_per_block
+        sc = self.config.scheduler
+        # never take more than every sequence at full length could use
+        cap = sc.max_num_seqs * ((sc.max_model_len + cc.block_size - 1) // cc.block_size) + 64
+        n = int(min(n, cap))
+        if n < 16:
+            raise RuntimeError(f"not enough memory for the KV cache (budget {budget} bytes)")
+        logger.info("KV cache: %d blocks of %d tokens (%.2f GiB), activation peak %.2f GiB", n,
+                    cc.block_size, n * spec.bytes_per_block / 2**30, peak / 2**30)
+        return n
+
+    def _init_kv_cache_tensors(self, num_blocks: int) -> None:
+        alloc = getattr(self.model, "allocate_kv_cache", None)
+        if callable(alloc):
+            self.kv_caches = alloc(num_blocks, self.config.cache.block_size, self.device)
+        else:
+            mc = self.model_config
+            hk = max(1, mc.num_kv_heads // pstate.tp_world_size())
+            self.kv_caches = [GQABackend.allocate_kv_cache(num_blocks, self.config.cache.block_size,
+                                                           hk, mc.head_dim, mc.dtype, self.device)
+                              for _ in range(mc.num_layers)]
+        self.num_blocks = num_blocks
+
+    def initialize_kv_cache(self, num_blocks: int) -> None:
+        self._init_kv_cache_tensors(num_blocks)
+        if self.kv_connector is not None:
+            self.kv_connector.register_kv_caches(self.kv_caches)
+
+    # ------------------------------------------------------------- execution
+    def _metadata(self, lay: StepLayout, views, is_prefill: bool, num_seqs: int, num_tokens: int,
+                  max_q_len: int, max_seq_len: int, q_len: int, actual_tokens: int,
+                  actual_seqs: int) -> AttentionMetadata:
+        return AttentionMetadata(is_prefill=is_prefill, num_seqs=num_seqs, num_tokens=num_tokens,
+                                 max_q_len=max_q_len, max_seq_len=max_seq_len, q_len=q_len,
+                                 positions=views["pos"], slot_mapping=views["slot"],
+                                 block_tables=views["bt"], seq_lens=views["seq_lens"],
+                                 cu_q=views["cu_q"], num_actual_tokens=actual_tokens,
+                                 num_actual_seqs=actual_seqs)
+
+    def _forward_and_sample(self, views, md: AttentionMetadata, num_samples: int) -> torch.Tensor:
+        """Model forward + LM head + sampling for the staged step (device side only)."""
+        with set_forward_context(md, self.kv_caches, self.config):
+            hidden = self.model(views["ids"], views["pos"])
+            if md.is_prefill:
+                hidden = hidden.index_select(0, views["logits_idx"][:num_samples].long())
+            else:
+                hidden = hidden[:num_samples]
+            logits = self.model.compute_logits(hidden)
+        return self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
+                            views["top_p"][:num_samples], views["seeds"][:num_samples],
+                            self.step_counter)
+
+    def _pad_decode_size(self, n: int) -> Optional[int]:
+        for s in self.capture_sizes:
+            if s >= n:
+                return s
+        return None
+
+    @torch.inference_mode()
+    def execute_model(self, out: SchedulerOutput) -> List[int]:
+        """Run one scheduled step; returns one sampled token per scheduled sequence
+        (meaningless for sequences whose chunk does not end their prompt)."""
+        if out.kind == "idle" or not out.seqs:
+            return []
+        ib = self.input_batch
+        for rid in out.finished_req_ids:
+            ib.remove_request(rid)
+        for rid in out.preempted:
+            ib.remove_request(rid)
+        if self.kv_connector is not None and out.kv_connector_metadata is not None:
+            self.kv_connector.start_load_kv(out.kv_connector_metadata)
+        n = len(out.seqs)
+        if out.kind == "decode":
+            reqs = [s.request for s in out.seqs]
+            padded = self._pad_decode_size(n) if self.graphs else None
+            S = padded or n
+            lay = ib.layout_for(S, S)
+            ib.stage_decode(lay, reqs)
+            ib.upload(lay)
+            if padded is not None:
+                sampled = self.graphs[padded].replay()
+            else:
+                views = ib.views(lay, ib.dev)
+                md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len,
+                                    1, n, n)
+                sampled = self._forward_and_sample(views, md, S)
+        else:
+            T = out.num_tokens
+            lay = ib.layout_for(T, n)
+            _, max_q = ib.stage_prefill(lay, out.seqs)
+            ib.upload(lay)
+            views = ib.views(lay, ib.dev)
+            max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
+            md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
+            sampled = self._forward_and_sample(views, md, n)
+        self.step_counter += 1
+        # D2H of the step's result (pinned), then the host learns the tokens
+        host = self.sampled_host[:n]
+        host.copy_(sampled[:n], non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        self.d2h_bytes_last = n * 4
+        tokens = host.tolist()
+        if self.kv_connector is not None:
+            self.kv_connector.wait_for_save()
+        return tokens
+
+    # ------------------------------------------------------------ dummy / graphs
+    @torch.inference_mode()
+    def _dummy_run(self, num_tokens: int, prefill: bool = False) -> None:
+        """Forward over synthetic inputs that touch only KV block 0."""
+        ib = self.input_batch
+        bs = self.config.cache.block_size
+        if prefill:
+            T = num_tokens
+            max_len = min(self.config.scheduler.max_model_len - 1, T,
+                          (self.num_blocks - 1) * bs if self.num_blocks else T)
+            n_seq = max(1, (T + max_len - 1) // max_len)
+            n_seq = min(n_seq, self.config.scheduler.max_num_seqs)
+            per = T // n_seq
+            T = per * n_seq
+            lay = ib.layout_for(T, n_seq)
+            h = ib.host_np
+            h[lay.ids: lay.ids + T] = 0
+            pos = np.tile(np.arange(per, dtype=np.int32), n_seq)
+            h[lay.pos: lay.pos + T] = pos
+            h[lay.slot: lay.slot + T] = -1
+            h[lay.seq_lens: lay.seq_lens + n_seq] = per
+            h[lay.cu_q: lay.cu_q + n_seq + 1] = np.arange(n_seq + 1, dtype=np.int32) * per
+            h[lay.logits_idx: lay.logits_idx + n_seq] = np.arange(1, n_seq + 1, dtype=np.int32) * per - 1
+            h[lay.temp: lay.temp + n_seq] = 0
+            h[lay.top_k: lay.top_k + n_seq] = 0
+            h[lay.top_p: lay.top_p + n_seq] = np.float32(1.0).view(np.int32)
+            bt = h[lay.bt: lay.bt + n_seq * lay.max_blocks].reshape(n_seq, lay.max_blocks)
+            nb = (per + bs - 1) // bs
+            bt[:, :nb] = np.arange(nb, dtype=np.int32) % max(1, self.num_blocks)
+            ib.upload(lay)
+            views = ib.views(lay, ib.dev)
+            md = self._metadata(lay, views, True, n_seq, T, per, per, 0, T, n_seq)
+            self._forward_and_sample(views, md, n_seq)
+        else:
+            S = num_tokens
+            lay = ib.layout_for(S, S)
+            ib.stage_decode(lay, [])
+            ib.upload(lay)
+            views = ib.views(lay, ib.dev)
+            md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len, 1, 0, 0)
+            self._forward_and_sample(views, md, S)
+
+    def execute_dummy_batch(self) -> None:
+        """Keeps collectives in lock-step on data-parallel ranks with no work."""
+        self._dummy_run(1, prefill=False)
+
+    @torch.inference_mode()
+    def capture_model(self) -> None:
+        """Capture one full-step decode graph per batch size."""
+        cc = self.config.compilation
+        if self.device.type != "cuda" or cc.cudagraph_mode == "NONE":
+            return
+        t0 = time.time()
+        self.capture_sizes = cc.capture_sizes(self.config.scheduler.max_num_seqs)
+        ib = self.input_batch
+        pool = None
+        for S in sorted(self.capture_sizes, reverse=True):
+            lay = ib.layout_for(S, S)
+            ib.stage_decode(lay, [])
+            ib.upload(lay)
+            views = ib.views(lay, ib.dev)
+            md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len, 1, 0, 0)
+            runner = CUDAGraphRunner(lambda v=views, m=md, s=S: self._forward_and_sample(v, m, s),
+                                     self.device, pool)
+            runner.capture(warmup=2)
+            pool = runner.pool
+            self.graphs[S] = runner
+        torch.cuda.synchronize(self.device)
+        self.timings["capture_s"] = time.time() - t0
+        logger.info("captured %d decode graphs in %.1f s", len(self.graphs), time.time() - t0)

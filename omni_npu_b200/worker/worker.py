@@ -1,0 +1,150 @@
+"""Per-device worker: device and process-group set-up, model loading, memory
+profiling, KV-cache creation, graph capture and step execution.
+
+Counterpart of ``NPUWorker`` (omni_npu/worker/npu_worker.py:38-291):
+``init_device`` (:77-120), ``determine_available_memory`` (:123-159),
+``initialize_from_config`` (:164-179), ``compile_or_warm_up_model`` (:199-202),
+``execute_model`` with token-threshold profiling (:229-246) and the profiler
+set-up (:248-284).
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..config import EngineConfig
+from ..engine.scheduler import SchedulerOutput
+from ..logger import logger
+from ..parallel import state as pstate
+from .model_runner import ModelRunner
+
+
+class Worker:
+    def __init__(self, config: EngineConfig, local_rank: int = 0, rank: int = 0,
+                 distributed_init_method: Optional[str] = None, is_driver_worker: bool = True) -> None:
+        self.config = config
+        self.local_rank = local_rank
+        self.rank = rank
+        self.distributed_init_method = distributed_init_method
+        self.is_driver_worker = is_driver_worker
+        self.device: Optional[torch.device] = None
+        self.model_runner: Optional[ModelRunner] = None
+        self.profiler = None
+        self._profile_steps_left = 0
+        self._profile_threshold = int(os.environ.get("PROFILER_TOKEN_THRESHOLD", "0"))
+        self._profile_stop_step = int(os.environ.get("PROFILER_STOP_STEP", "5"))
+
+    # -------------------------------------------------------------- set-up
+    def init_device(self) -> None:
+        want_cuda = self.config.device in ("auto", "cuda") and torch.cuda.is_available()
+        if self.config.device == "cuda" and not want_cuda:
+            raise RuntimeError("device='cuda' requested but CUDA is not available")
+        if want_cuda:
+            torch.cuda.set_device(self.local_rank)
+            self.device = torch.device("cuda", self.local_rank)
+            ops.load_extension(required=True)
+            self._init_free, self._init_total = torch.cuda.mem_get_info(self.device)
+        else:
+            self.device = torch.device("cpu")
+        pc = self.config.parallel
+        if not pstate.model_parallel_is_initialized():
+            pstate.init_distributed(self.device, init_method=self.distributed_init_method)
+            pstate.init_model_parallel(pc.tensor_parallel_size, pc.pipeline_parallel_size,
+                                       pc.data_parallel_size, self.device)
+            for key, spec in (pc.layer_parallel_config or {}).items():
+                if isinstance(spec, dict) and "tp_size_or_ranks" in spec:
+                    pstate.register_layer_group(key, spec["tp_size_or_ranks"])
+        if self.device.type == "cuda" and pc.tensor_parallel_size > 1 and self.config.fused_collectives:
+            from ..parallel.symm_mem import attach_symmetric_memory
+            attach_symmetric_memory(pstate.get_tp_group(), self.device)
+        torch.manual_seed(self.config.seed)
+        self.model_runner = ModelRunner(self.config, self.device)
+        self._init_profiler()
+
+    def load_model(self) -> None:
+        self.model_runner.load_model()
+
+    def get_model(self):
+        return self.model_runner.get_model()
+
+    def determine_num_blocks(self) -> int:
+        n = self.model_runner.determine_num_blocks()
+        # every rank of the world must agree on the number of blocks
+        world = pstate.get_world_group()
+        if world.world_size > 1:
+            n = min(world.all_gather_object(n))
+        return n
+
+    def get_kv_cache_spec(self):
+        return self.model_runner.get_kv_cache_spec()
+
+    def initialize_from_config(self, num_blocks: int) -> None:
+        if self.config.kv_transfer is not None and self.config.kv_transfer.kv_connector:
+            from ..kv_transfer.connector import create_connector
+            self.model_runner.kv_connector = create_connector(self.config, role="worker",
+                                                              device=self.device)
+        if self.config.enable_sleep_mode and self.device.type == "cuda":
+            from .mem_pool import CudaMemAllocator
+            with CudaMemAllocator.get_instance().use_memory_pool(tag="kv_cache"):
+                self.model_runner.initialize_kv_cache(num_blocks)
+        else:
+            self.model_runner.initialize_kv_cache(num_blocks)
+
+    def compile_or_warm_up_model(self) -> None:
+        if self.device.type == "cuda":
+            # touch every kernel once outside of capture, then capture
+            self.model_runner._dummy_run(min(256, self.config.scheduler.max_num_batched_tokens), prefill=True)
+            self.model_runner._dummy_run(1, prefill=False)
+            torch.cuda.synchronize(self.device)
+            ops.check_status(self.device)
+        self.model_runner.capture_model()
+
+    # ------------------------------------------------------------- running
+    def execute_model(self, out: SchedulerOutput) -> List[int]:
+        if self._profile_threshold and self.profiler is not None:
+            if self._profile_steps_left == 0 and out.total_num_scheduled_tokens == self._profile_threshold:
+                self.profiler.start()
+                self._profile_steps_left = self._profile_stop_step
+        tokens = self.model_runner.execute_model(out)
+        if self._profile_steps_left > 0:
+            self._profile_steps_left -= 1
+            if self._profile_steps_left == 0:
+                self.profiler.stop()
+        return tokens
+
+    def execute_dummy_batch(self) -> None:
+        self.model_runner.execute_dummy_batch()
+
+    def profile(self, is_start: bool = True) -> None:
+        if self.profiler is None:
+            raise RuntimeError("profiler not enabled: set VLLM_TORCH_PROFILER_DIR")
+        self.profiler.start() if is_start else self.profiler.stop()
+
+    def _init_profiler(self) -> None:
+        trace_dir = os.environ.get("VLLM_TORCH_PROFILER_DIR")
+        if not trace_dir:
+            return
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if self.device.type == "cuda":
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self.profiler = torch.profiler.profile(
+            activities=acts,
+            record_shapes=bool(int(os.environ.get("VLLM_TORCH_PROFILER_RECORD_SHAPES", "0"))),
+            profile_memory=bool(int(os.environ.get("VLLM_TORCH_PROFILER_WITH_PROFILE_MEMORY", "0"))),
+            with_stack=bool(int(os.environ.get("VLLM_TORCH_PROFILER_WITH_STACK", "0"))),
+            on_trace_ready=torch.profiler.tensorboard_trace_handler(trace_dir, use_gzip=True))
+
+    def sleep(self, level: int = 1) -> None:
+        from .mem_pool import CudaMemAllocator
+        CudaMemAllocator.get_instance().sleep(offload_tags=("weights",) if level == 1 else ())
+
+    def wake_up(self, tags=None) -> None:
+        from .mem_pool import CudaMemAllocator
+        CudaMemAllocator.get_instance().wake_up(tags)
+
+    def shutdown(self) -> None:
+        if self.model_runner is not None and self.model_runner.kv_connector is not None:
+            self.model_runner.kv_connector.close()
