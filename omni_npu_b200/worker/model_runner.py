@@ -65,6 +65,9 @@ class ModelRunner:
         self.d2h_bytes_last = 0
         self.kv_connector = None
         self.timings: Dict[str, float] = {}
+        # optional device-side timing of every step (CUDA events around the kernels)
+        self.enable_step_events = False
+        self._step_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
 
     # ------------------------------------------------------------------ model
     def load_model(self) -> None:
@@ -214,6 +217,7 @@ class ModelRunner:
         if self.kv_connector is not None and out.kv_connector_metadata is not None:
             self.kv_connector.start_load_kv(out.kv_connector_metadata)
         n = len(out.seqs)
+        ev = None
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
             padded = self._pad_decode_size(n) if self.graphs else None
@@ -221,6 +225,7 @@ class ModelRunner:
             lay = ib.layout_for(S, S)
             ib.stage_decode(lay, reqs)
             ib.upload(lay)
+            ev = self._event_start()
             if padded is not None:
                 sampled = self.graphs[padded].replay()
             else:
@@ -233,11 +238,13 @@ class ModelRunner:
             lay = ib.layout_for(T, n)
             _, max_q = ib.stage_prefill(lay, out.seqs)
             ib.upload(lay)
+            ev = self._event_start()
             views = ib.views(lay, ib.dev)
             max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
             sampled = self._forward_and_sample(views, md, n)
         self.step_counter += 1
+        self._event_stop(ev)
         # D2H of the step's result (pinned), then the host learns the tokens
         host = self.sampled_host[:n]
         host.copy_(sampled[:n], non_blocking=True)
@@ -248,6 +255,28 @@ class ModelRunner:
         if self.kv_connector is not None:
             self.kv_connector.wait_for_save()
         return tokens
+
+    def _event_start(self):
+        if not self.enable_step_events or self.device.type != "cuda":
+            return None
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        return (e0, e1)
+
+    def _event_stop(self, ev) -> None:
+        if ev is not None:
+            ev[1].record()
+            self._step_events.append(ev)
+
+    def drain_step_events(self) -> float:
+        """Sum (ms) of the device time of the steps recorded since the last call."""
+        if not self._step_events:
+            return 0.0
+        torch.cuda.synchronize(self.device)
+        total = sum(a.elapsed_time(b) for a, b in self._step_events)
+        self._step_events = []
+        return total
 
     # ------------------------------------------------------------ dummy / graphs
     @torch.inference_mode()

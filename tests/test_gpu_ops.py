@@ -1,0 +1,295 @@
+"""Numerics of every CUDA kernel against the fp32 PyTorch references."""
+import math
+
+import pytest
+import torch
+
+from omni_npu_b200 import ops
+from omni_npu_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol):
+    torch.testing.assert_close(a.float().cpu(), b.float().cpu(), atol=atol, rtol=rtol)
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    ops.check_status()
+
+
+# ------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 128), (256, 512, 4096), (77, 200, 136),
+                                   (1, 4096, 4096), (128, 6144, 4096), (1000, 1024, 2048),
+                                   (8192, 4096, 4096)])
+def test_gemm_bf16(m, n, k):
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    out = ops.gemm(a, w)
+    want = ref.gemm(a.cpu(), w.cpu())
+    _close(out, want, atol=2e-2 * math.sqrt(k / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("bn,splits", [(32, 1), (64, 2), (112, 4), (128, 3), (208, 1), (256, 1), (256, 8)])
+def test_gemm_tile_widths_and_split_k(bn, splits):
+    torch.manual_seed(1)
+    m, n, k = 200, 1000, 4096
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    out = ops.gemm(a, w, bn=bn, splits=splits)
+    _close(out, ref.gemm(a.cpu(), w.cpu()), atol=0.15, rtol=2e-2)
+    # split-K leaves its counters at rest: a second call must agree
+    out2 = ops.gemm(a, w, bn=bn, splits=splits)
+    assert torch.equal(out, out2)
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(2)
+    m, n, k = 300, 768, 1024
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    _close(ops.gemm(a, w, bias, res), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
+    _close(ops.gemm(a, w, bias, res, splits=2), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
+    o32 = ops.gemm(a, w, out_dtype=torch.float32)
+    assert o32.dtype == torch.float32
+    _close(o32, ref.gemm(a.cpu(), w.cpu(), out_dtype=torch.float32), 2e-2, 1e-2)
+    # fused SwiGLU with interleaved gate/up rows
+    i = n // 2
+    wi = ref.interleave_gate_up(w[:i], w[i:])
+    fused = ops.gemm(a, wi, swiglu=True)
+    want = ref.silu_and_mul(ref.gemm(a.cpu(), w.cpu(), out_dtype=torch.float32))
+    _close(fused, want, 0.06, 3e-2)
+
+
+def test_grouped_gemm():
+    torch.manual_seed(3)
+    e, n, k = 8, 512, 1024
+    counts = [0, 5, 128, 129, 300, 1, 0, 77]
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    rows = int(offs[-1])
+    a = torch.randn(rows, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(e, n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    out = ops.grouped_gemm(a, w, offs.to(DEV))
+    _close(out, ref.grouped_gemm(a.cpu(), w.cpu(), offs), 0.08, 2e-2)
+    wi = ref.interleave_gate_up(w[:, : n // 2], w[:, n // 2:])
+    out = ops.grouped_gemm(a, wi, offs.to(DEV), swiglu=True)
+    want = ref.silu_and_mul(ref.grouped_gemm(a.cpu().float(), w.cpu().float(), offs))
+    _close(out, want, 0.06, 3e-2)
+
+
+def test_gemm_fp8_plain():
+    torch.manual_seed(4)
+    m, n, k = 256, 512, 1024
+    a = (torch.randn(m, k, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    w = (torch.randn(n, k, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    out = ops.gemm(a, w)
+    _close(out, ref.gemm(a.cpu(), w.cpu()), 0.25, 2e-2)
+
+
+# --------------------------------------------------------------- row kernels
+@pytest.mark.parametrize("t,h", [(1, 4096), (37, 4096), (128, 2048), (5, 7168), (16, 128), (33, 16384)])
+def test_rms_norm(t, h):
+    torch.manual_seed(0)
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(h, device=DEV, dtype=torch.bfloat16)
+    _close(ops.rms_norm(x, w, 1e-6), ref.rms_norm(x.cpu(), w.cpu(), 1e-6), 2e-2, 2e-2)
+    r = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    r_ref = r.cpu().clone()
+    y = ops.fused_add_rms_norm(x, r, w, 1e-6)
+    y_ref = ref.fused_add_rms_norm(x.cpu(), r_ref, w.cpu(), 1e-6)
+    _close(r, r_ref, 1e-2, 1e-2)
+    _close(y, y_ref, 3e-2, 2e-2)
+
+
+def test_rms_norm_strided_heads():
+    x = torch.randn(9, 3 * 128 * 4, device=DEV, dtype=torch.bfloat16)
+    q = x[:, : 128 * 4]
+    w = torch.randn(128, device=DEV, dtype=torch.bfloat16)
+    got = ops.rms_norm(q.reshape(-1, 128), w, 1e-6)
+    _close(got, ref.rms_norm(q.cpu().reshape(-1, 128), w.cpu(), 1e-6), 2e-2, 2e-2)
+
+
+def test_silu_and_mul_and_quant():
+    x = torch.randn(50, 2 * 1408, device=DEV, dtype=torch.bfloat16)
+    _close(ops.silu_and_mul(x), ref.silu_and_mul(x.cpu()), 2e-2, 2e-2)
+    y = torch.randn(19, 1024, device=DEV, dtype=torch.bfloat16) * 3
+    q, s = ops.quant_fp8_1x128(y)
+    qr, sr = ref.quant_fp8_1x128(y.cpu())
+    _close(s, sr, 1e-6, 1e-5)
+    deq = q.float().view(19, 8, 128) * s.unsqueeze(-1)
+    _close(deq.view(19, 1024), y, 0.25, 0.07)
+
+
+@pytest.mark.parametrize("neox", [True, False])
+@pytest.mark.parametrize("rot", [128, 64])
+def test_rope_qk(neox, rot):
+    t, hq, hk, d = 23, 8, 2, 128
+    q = torch.randn(t, hq * d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(t, hk * d, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 4000, (t,), device=DEV, dtype=torch.int32)
+    cs = ref.build_cos_sin_cache(rot, 4096, 10000.0).to(DEV)
+    qr, kr = ref.rope_qk(q.cpu(), k.cpu(), pos.cpu(), cs.cpu(), d, rot, neox)
+    ops.rope_qk_(q, k, pos, cs, d, rot, neox)
+    _close(q, qr, 2e-2, 2e-2)
+    _close(k, kr, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_mrope(interleaved):
+    t, hq, hk, d = 11, 4, 2, 128
+    q = torch.randn(t, hq * d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(t, hk * d, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (3, t), device=DEV, dtype=torch.int32)
+    cs = ref.build_cos_sin_cache(d, 512, 10000.0).to(DEV)
+    sec = (24, 20, 20)
+    qr, kr = ref.rope_qk(q.cpu(), k.cpu(), pos.cpu(), cs.cpu(), d, d, True, sec, interleaved)
+    ops.rope_qk_(q, k, pos, cs, d, d, True, sec, interleaved)
+    _close(q, qr, 2e-2, 2e-2)
+    _close(k, kr, 2e-2, 2e-2)
+
+
+def _paged_setup(seq_lens, q_lens, hq, hk, d, bs, dv=None, seed=0):
+    torch.manual_seed(seed)
+    dv = dv or d
+    b = len(seq_lens)
+    max_blocks = max((s + bs - 1) // bs for s in seq_lens) + 1
+    nblocks = b * max_blocks + 3
+    perm = torch.randperm(nblocks)[: b * max_blocks].view(b, max_blocks).to(torch.int32)
+    k_cache = torch.randn(nblocks, hk, bs, d, dtype=torch.bfloat16)
+    v_cache = torch.randn(nblocks, hk, bs, dv, dtype=torch.bfloat16)
+    t = sum(q_lens)
+    q = torch.randn(t, hq * d, dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    return q, k_cache, v_cache, perm, cu, sl
+
+
+@pytest.mark.parametrize("d,bs", [(128, 16), (64, 16), (128, 128)])
+def test_gqa_prefill(d, bs):
+    seq_lens, q_lens = [130, 64, 517, 9], [130, 33, 200, 9]
+    hq, hk = 8, 2
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, q_lens, hq, hk, d, bs)
+    want, lse_want = ref.paged_attention(q, kc, vc, bt, cu, sl, hq, d ** -0.5, True, 0, True)
+    got, lse = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV),
+                               len(seq_lens), max(q_lens), hq, d ** -0.5, True, 0, True)
+    _close(got, want, 2e-2, 2e-2)
+    _close(lse, lse_want, 2e-2, 1e-2)
+
+
+def test_gqa_prefill_window_and_mla_dims():
+    seq_lens, q_lens = [300, 77], [300, 40]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, q_lens, 4, 4, 128, 16, seed=5)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 4, 0.1, True, 64)
+    got = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV), 2, 300,
+                          4, 0.1, True, 64)
+    _close(got, want, 2e-2, 2e-2)
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, q_lens, 4, 4, 192, 16, dv=128, seed=6)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 4, 192 ** -0.5, True, 0)
+    got = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV), 2, 300,
+                          4, 192 ** -0.5, True, 0)
+    _close(got, want, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (4, 2, 64), (16, 1, 128)])
+def test_gqa_decode(splits, hq, hk, d):
+    seq_lens = [1, 17, 64, 65, 1000, 333]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 6, hq, hk, d, 16, seed=7)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, hq, d ** -0.5, True, 0)
+    got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 6, hq, d ** -0.5,
+                         splits=splits)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_gqa_decode_multi_token():
+    seq_lens = [40, 130, 7]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [3] * 3, 8, 2, 128, 16, seed=8)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.09, True, 0)
+    got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 3, 8, 0.09, q_len=3,
+                         splits=2)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_rope_cache_gqa_and_cache_write():
+    t, hq, hk, d, bs = 29, 8, 2, 128, 16
+    qkv = torch.randn(t, (hq + 2 * hk) * d, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, : hq * d], qkv[:, hq * d: (hq + hk) * d], qkv[:, (hq + hk) * d:]
+    pos = torch.randint(0, 1000, (t,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(10 * bs)[:t].to(torch.int32)
+    slots[3] = -1
+    cs = ref.build_cos_sin_cache(d, 1024, 500000.0).to(DEV)
+    kc = torch.zeros(10, hk, bs, d, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc_ref, vc_ref = kc.cpu().clone(), vc.cpu().clone()
+    qr, kr = ref.rope_qk(q.cpu(), k.cpu(), pos.cpu(), cs.cpu(), d, d, True)
+    ref.gqa_cache_write(kr, v.cpu(), kc_ref, vc_ref, slots)
+    ops.rope_cache_gqa_(q, k, v, kc, vc, pos, slots.to(DEV), cs, d, d, True)
+    _close(q, qr, 2e-2, 2e-2)
+    _close(kc, kc_ref, 2e-2, 2e-2)
+    _close(vc, vc_ref, 0, 0)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops.gqa_cache_write(k, v, kc2, vc2, slots.to(DEV))
+    kc3, vc3 = torch.zeros_like(kc_ref), torch.zeros_like(vc_ref)
+    ref.gqa_cache_write(k.cpu(), v.cpu(), kc3, vc3, slots)
+    _close(kc2, kc3, 0, 0)
+    _close(vc2, vc3, 0, 0)
+
+
+def test_mla_kv_rmsnorm_rope_cache():
+    t, l, r, bs = 21, 512, 64, 16
+    kv = torch.randn(t, l + r, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(l, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 900, (t,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(4 * bs)[:t].to(torch.int32)
+    cs = ref.build_cos_sin_cache(r, 1024, 10000.0).to(DEV)
+    cache = torch.zeros(4, bs, l + r, device=DEV, dtype=torch.bfloat16)
+    cache_ref = cache.cpu().clone()
+    a = ops.mla_kv_rmsnorm_rope_cache(kv[:, :l], kv[:, l:], w, cache, pos, slots.to(DEV), cs, 1e-6, False, True)
+    b = ops.mla_kv_rmsnorm_rope_cache(kv[:, :l].cpu(), kv[:, l:].cpu(), w.cpu(), cache_ref, pos.cpu(), slots,
+                                      cs.cpu(), 1e-6, False, True)
+    _close(cache, cache_ref, 3e-2, 2e-2)
+    _close(a[0], b[0], 3e-2, 2e-2)
+    _close(a[1], b[1], 3e-2, 2e-2)
+
+
+# ------------------------------------------------------------------ sampling
+def test_argmax_and_greedy_sample():
+    torch.manual_seed(0)
+    logits = torch.randn(33, 128256, device=DEV, dtype=torch.float32)
+    want = logits.argmax(-1).to(torch.int32)
+    assert torch.equal(ops.argmax(logits), want)
+    assert torch.equal(ops.argmax(logits.bfloat16()), logits.bfloat16().float().argmax(-1).to(torch.int32))
+    t = torch.zeros(33, device=DEV)
+    got = ops.sample(logits, t, torch.zeros(33, dtype=torch.int32, device=DEV), torch.ones(33, device=DEV),
+                     torch.arange(33, device=DEV), torch.zeros(1, dtype=torch.int64, device=DEV))
+    assert torch.equal(got, want)
+
+
+def test_sample_respects_top_k_top_p_and_distribution():
+    torch.manual_seed(1)
+    v, n = 1000, 4096
+    base = torch.randn(v, device=DEV) * 2
+    logits = base.unsqueeze(0).repeat(n, 1).contiguous()
+    temp = torch.full((n,), 0.8, device=DEV)
+    topk = torch.full((n,), 20, dtype=torch.int32, device=DEV)
+    topp = torch.full((n,), 0.9, device=DEV)
+    seeds = torch.arange(n, device=DEV, dtype=torch.int64) * 7919 + 13
+    step = torch.zeros(1, dtype=torch.int64, device=DEV)
+    got = ops.sample(logits, temp, topk, topp, seeds, step).long().cpu()
+    masked = ref.apply_top_k_top_p((base / 0.8).unsqueeze(0).cpu(), torch.tensor([20]), torch.tensor([0.9]))[0]
+    allowed = torch.isfinite(masked)
+    assert allowed[got].all(), "sampled a token outside the top-k/top-p set"
+    probs = masked.softmax(-1)
+    freq = torch.bincount(got, minlength=v).float() / n
+    assert (freq - probs).abs().max() < 0.04
+    # a different step offset gives different draws; the same offset repeats them
+    again = ops.sample(logits, temp, topk, topp, seeds, step).long().cpu()
+    assert torch.equal(again, got)
+    other = ops.sample(logits, temp, topk, topp, seeds, step + 1).long().cpu()
+    assert (other != got).float().mean() > 0.3
