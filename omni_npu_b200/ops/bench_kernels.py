@@ -1,0 +1,178 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m omni_npu_b200.ops.bench_kernels gemm            # GEMM shapes of the serving configs
+    python -m omni_npu_b200.ops.bench_kernels gemm --m 128 --n 4096 --k 4096 --bn 128 --splits 4
+    python -m omni_npu_b200.ops.bench_kernels attn | norm | sample | all
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed
+(a 256 MB buffer is rewritten) before every timed launch, median of the timed
+launches.  Fractions are of the measured peaks in MEASURED_PEAKS.json at the
+repository root when present (copy bandwidth and cuBLAS bf16 throughput), else
+of 6.65 TB/s / 1.59 PFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+from omni_npu_b200 import ops
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    except Exception:
+        return 6.65e12, 1.59e15, "fallback"
+
+
+_flush = None
+
+
+def time_fn(fn, iters=10, warmup=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        if flush:
+            _flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+SERVING_GEMMS = [
+    # (label, M, N, K)
+    ("llama8b qkv prefill", 8192, 6144, 4096), ("llama8b o prefill", 8192, 4096, 4096),
+    ("llama8b gate_up prefill", 8192, 28672, 4096), ("llama8b down prefill", 8192, 4096, 14336),
+    ("llama8b qkv decode", 128, 6144, 4096), ("llama8b o decode", 128, 4096, 4096),
+    ("llama8b gate_up decode", 128, 28672, 4096), ("llama8b down decode", 128, 4096, 14336),
+    ("llama8b lm_head decode", 128, 128256, 4096),
+    ("square 8192", 8192, 8192, 8192),
+]
+
+
+def bench_gemm(args):
+    hbm, flops_peak, src = peaks()
+    shapes = SERVING_GEMMS if args.m is None else [("custom", args.m, args.n, args.k)]
+    print(f"# GEMM bf16, fractions of {src} peaks: {hbm/1e12:.2f} TB/s, {flops_peak/1e12:.0f} TFLOP/s")
+    print(f"{'shape':28s} {'M':>6s} {'N':>7s} {'K':>6s} {'bn':>4s} {'sp':>3s} {'ours_us':>9s} {'cublas_us':>9s} "
+          f"{'TFLOP/s':>8s} {'GB/s':>7s} {'frac':>5s} {'vs_cublas':>9s}")
+    for label, m, n, k in shapes:
+        a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+        bn, sp = args.bn, args.splits
+        plan = torch.ops.omni_b200.gemm_plan(m, n, k, 2, False, bn, sp)
+        t = time_fn(lambda: ops.gemm(a, w, bn=bn, splits=sp), iters=args.iters)
+        tc = time_fn(lambda: torch.matmul(a, w.t()), iters=args.iters)
+        fl = 2.0 * m * n * k
+        by = 2.0 * (m * k + n * k + m * n)
+        tf, gb = fl / t / 1e9, by / t / 1e6
+        frac = max(fl / flops_peak, by / hbm) / (t / 1e3)
+        print(f"{label:28s} {m:6d} {n:7d} {k:6d} {plan[0]:4d} {plan[1]:3d} {t*1e3:9.1f} {tc*1e3:9.1f} "
+              f"{tf:8.1f} {gb:7.0f} {frac:5.2f} {tc/t:9.2f}")
+    ops.check_status()
+
+
+def bench_attn(args):
+    hbm, flops_peak, src = peaks()
+    print(f"# paged GQA attention, fractions of {src} peaks")
+    hq, hk, d, bs = 32, 8, 128, 16
+    for b, ctx in ((128, 1152), (128, 4096), (16, 8192), (1, 32768)):
+        nblk = b * ((ctx + bs - 1) // bs) + 1
+        kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        q = torch.randn(b, hq * d, device="cuda", dtype=torch.bfloat16)
+        bt = torch.arange(1, nblk, device="cuda", dtype=torch.int32).view(b, -1)
+        sl = torch.full((b,), ctx, device="cuda", dtype=torch.int32)
+        for splits in ((0,) if args.splits == 0 else (args.splits,)):
+            t = time_fn(lambda: ops.gqa_decode(q, kc, vc, bt, sl, b, hq, d ** -0.5, splits=splits,
+                                               max_seq_len=ctx), iters=args.iters)
+            by = 2.0 * b * ctx * hk * d * 2
+            print(f"decode  B={b:4d} ctx={ctx:6d} splits={splits}: {t*1e3:8.1f} us  {by/t/1e6:7.0f} GB/s "
+                  f"frac {by/hbm/(t/1e3):.2f}")
+    for b, s in ((8, 1024), (2, 4096), (1, 8192)):
+        nblk = b * (s // bs) + 1
+        kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        q = torch.randn(b * s, hq * d, device="cuda", dtype=torch.bfloat16)
+        bt = torch.arange(1, nblk, device="cuda", dtype=torch.int32).view(b, -1)
+        sl = torch.full((b,), s, device="cuda", dtype=torch.int32)
+        cu = torch.arange(0, (b + 1) * s, s, device="cuda", dtype=torch.int32)
+        t = time_fn(lambda: ops.gqa_prefill(q, kc, vc, bt, cu, sl, b, s, hq, d ** -0.5), iters=args.iters)
+        fl = 4.0 * b * hq * s * s * d / 2
+        print(f"prefill B={b:3d} S={s:6d}: {t*1e3:9.1f} us  {fl/t/1e9:7.1f} TFLOP/s  frac {fl/flops_peak/(t/1e3):.2f}")
+    ops.check_status()
+
+
+def bench_norm(args):
+    hbm, _, src = peaks()
+    print(f"# row kernels, fractions of {src} copy bandwidth")
+    for t_, h in ((8192, 4096), (128, 4096), (8192, 7168), (65536, 4096)):
+        x = torch.randn(t_, h, device="cuda", dtype=torch.bfloat16)
+        r = torch.randn_like(x)
+        w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+        t = time_fn(lambda: ops.rms_norm(x, w, 1e-6), iters=args.iters)
+        by = 2.0 * t_ * h * 2
+        print(f"rms_norm      [{t_},{h}]: {t*1e3:8.1f} us {by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
+        t = time_fn(lambda: ops.fused_add_rms_norm(x, r, w, 1e-6), iters=args.iters)
+        by = 2.0 * t_ * h * 4
+        print(f"add_rms_norm  [{t_},{h}]: {t*1e3:8.1f} us {by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
+    x = torch.randn(8192, 2 * 14336, device="cuda", dtype=torch.bfloat16)
+    t = time_fn(lambda: ops.silu_and_mul(x), iters=args.iters)
+    by = 2.0 * 8192 * 14336 * 3
+    print(f"silu_and_mul  [8192,28672]: {t*1e3:8.1f} us {by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
+
+
+def bench_sample(args):
+    hbm, _, src = peaks()
+    for b, v in ((128, 128256), (1, 128256), (128, 151936)):
+        logits = torch.randn(b, v, device="cuda", dtype=torch.float32)
+        temp = torch.full((b,), 0.8, device="cuda")
+        tk = torch.full((b,), 50, dtype=torch.int32, device="cuda")
+        tp = torch.full((b,), 0.9, device="cuda")
+        seeds = torch.arange(b, device="cuda")
+        step = torch.zeros(1, dtype=torch.int64, device="cuda")
+        t0 = time_fn(lambda: ops.argmax(logits), iters=args.iters)
+        t1 = time_fn(lambda: ops.sample(logits, temp, tk, tp, seeds, step), iters=args.iters)
+        print(f"B={b:4d} V={v}: argmax {t0*1e3:7.1f} us ({4.0*b*v/t0/1e6:6.0f} GB/s), "
+              f"top-k/top-p sample {t1*1e3:7.1f} us")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "all"])
+    ap.add_argument("--m", type=int)
+    ap.add_argument("--n", type=int)
+    ap.add_argument("--k", type=int)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    ops.load_extension(required=True)
+    if args.what in ("gemm", "all"):
+        bench_gemm(args)
+    if args.what in ("attn", "all"):
+        bench_attn(args)
+    if args.what in ("norm", "all"):
+        bench_norm(args)
+    if args.what in ("sample", "all"):
+        bench_sample(args)
+
+
+if __name__ == "__main__":
+    main()
