@@ -92,7 +92,12 @@ def bench_attn(args):
     hbm, flops_peak, src = peaks()
     print(f"# paged GQA attention, fractions of {src} peaks")
     hq, hk, d, bs = 32, 8, 128, 16
-    for b, ctx in ((128, 1152), (128, 4096), (16, 8192), (1, 32768)):
+    decode_cases = ((128, 1152), (128, 4096), (16, 8192), (1, 32768))
+    prefill_cases = ((8, 1024), (2, 4096), (1, 8192))
+    if args.b is not None:
+        decode_cases = ((args.b, args.ctx),) if args.phase != "prefill" else ()
+        prefill_cases = ((args.b, args.ctx),) if args.phase != "decode" else ()
+    for b, ctx in decode_cases:
         nblk = b * ((ctx + bs - 1) // bs) + 1
         kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -105,7 +110,7 @@ def bench_attn(args):
             by = 2.0 * b * ctx * hk * d * 2
             print(f"decode  B={b:4d} ctx={ctx:6d} splits={splits}: {t*1e3:8.1f} us  {by/t/1e6:7.0f} GB/s "
                   f"frac {by/hbm/(t/1e3):.2f}")
-    for b, s in ((8, 1024), (2, 4096), (1, 8192)):
+    for b, s in prefill_cases:
         nblk = b * (s // bs) + 1
         kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -162,6 +167,9 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--b", type=int, help="attn: batch size of a single case")
+    ap.add_argument("--ctx", type=int, default=1024, help="attn: context length of a single case")
+    ap.add_argument("--phase", default="both", choices=["both", "decode", "prefill"])
     args = ap.parse_args()
     ops.load_extension(required=True)
     if args.what in ("gemm", "all"):
