@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--no-fused-collectives", action="store_true")
+    ap.add_argument("--profile", default=None,
+                    help="write a per-kernel time table (torch profiler, one extra untimed pass) to this file")
     return ap.parse_args()
 
 
@@ -179,6 +181,19 @@ def run_ours(args) -> None:
         return sum(len(o.output_token_ids) for o in outs)
 
     for _ in range(args.warmup):
+        one_pass()
+        runner.drain_step_events()
+
+    if args.profile and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            one_pass()
+            torch.cuda.synchronize()
+        runner.drain_step_events()
+        with open(args.profile, "w") as f:
+            f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40,
+                                              max_name_column_width=90))
+    elif args.profile:
         one_pass()
         runner.drain_step_events()
 

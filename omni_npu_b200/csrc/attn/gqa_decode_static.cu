@@ -40,7 +40,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
                                float* lse, const int* block_tables, const int* seq_lens, int B,
                                int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
                                long long q_stride, long long out_stride, float scale, int window,
-                               int splits, void* scratch, cudaStream_t stream);
+                               int splits, void* scratch, int num_cache_blocks, int* status,
+                               cudaStream_t stream);
 
 namespace {
 
@@ -112,5 +113,6 @@ extern "C" int b200_gqa_decode_static(const void* q, const void* k_cache, const 
   }
   return b200_gqa_decode(q, k_cache, v_cache, out, nullptr, block_tables, seq_lens, num_seqs, q_len,
                          max_blocks, block_size, num_q_heads, num_kv_heads, head_dim, q_stride,
-                         out_stride, scale, window, splits, scratch, stream);
+                         out_stride, scale, window, splits, scratch, /*num_cache_blocks=*/0,
+                         /*status=*/nullptr, stream);
 }

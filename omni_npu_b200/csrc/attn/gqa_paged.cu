@@ -18,6 +18,7 @@
 // (omni_npu/attention/backends/attention.py:216-281).
 
 #include "attn_common.cuh"
+#include "../common/tensormap.h"
 
 namespace b200 {
 
@@ -57,6 +58,8 @@ struct AttnParams {
   int splits;
   float* o_part;              // [B, splits, 16, DV] fp32
   float* lse_part;            // [B, splits, 16]   (per kv head: index includes head)
+  int* status;                // error word for bounded waits (may be null)
+  int num_cache_blocks;       // blocks in the cache tensors (bounds the TMA view)
 };
 
 template <int ROW_ELEMS, int ROWS, int THREADS>
@@ -556,6 +559,329 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const AttnParams p) {
   }
 }
 
+
+// ------------------------------------------------------- decode, TMA-fed
+// Same computation as gqa_decode_kernel, but the K/V tiles are brought in by
+// the TMA engine (cp.async.bulk.tensor, 128B swizzle) instead of per-thread
+// cp.async: a handful of bulk copies per tile keep far more bytes in flight
+// per SM than the load/store unit allows, which is what a bandwidth-bound
+// decode needs.  The cache is addressed as a 2-D tensor
+// [num_blocks * kv_heads * block_size rows, D columns]; a box is
+// (box_rows = min(block_size, 64)) rows x 64 columns (128 bytes).
+template <int D>
+struct DecodeTmaCfg {
+  static constexpr int BN = 64;
+  static constexpr int STAGES = 3;
+  static constexpr int COMPUTE_THREADS = 128;
+  static constexpr int THREADS = 160;          // 4 compute warps + 1 producer warp
+  static constexpr int HALVES = D / 64;
+  static constexpr int HALF_BYTES = BN * 128;
+  static constexpr int KV_BYTES = HALVES * HALF_BYTES;
+  static constexpr int Q_BYTES = 16 * D * 2;
+  static constexpr int BT_ENTRIES = 1024;      // block-table slice cached in shared memory
+  static constexpr int SMEM = 1024 + 2 * STAGES * KV_BYTES + Q_BYTES + BT_ENTRIES * 4 + 128;
+};
+
+template <int D>
+__device__ __forceinline__ uint32_t kv_swz(int key, int chunk) {
+  return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
+}
+
+template <int D>
+__global__ void __launch_bounds__(160)
+gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p,
+                      const int box_rows) {
+  using Cfg = DecodeTmaCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
+  uint8_t* sQ = sV + Cfg::STAGES * Cfg::KV_BYTES;
+  int* s_bt = reinterpret_cast<int*>(sQ + Cfg::Q_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_bt + Cfg::BT_ENTRIES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  int* s_abort = reinterpret_cast<int*>(empty_bar + Cfg::STAGES);
+
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int split = blockIdx.z;
+  const int G = p.Hq / p.Hk;
+  const int rows = G * p.q_len;
+  const int kv_len = p.seq_lens[b];
+  const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  const int n_tiles_all = (kv_len + Cfg::BN - 1) / Cfg::BN;
+  const int per = (n_tiles_all + p.splits - 1) / p.splits;
+  const int t_begin = split * per;
+  const int t_end = min(n_tiles_all, t_begin + per);
+  const int n_tiles = max(0, t_end - t_begin);
+  // Block-table entries this CTA needs: blocks [bt_first, bt_last).
+  const int bt_first = (t_begin * Cfg::BN) / p.block_size;
+  const int bt_last = min(p.max_blocks, (min(kv_len, t_end * Cfg::BN) + p.block_size - 1) / p.block_size);
+  const bool bt_cached = (bt_last - bt_first) <= Cfg::BT_ENTRIES;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    *s_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (bt_cached)
+    for (int i = bt_first + tid; i < bt_last; i += Cfg::THREADS) s_bt[i - bt_first] = bt[i];
+  // Zero the stages once: rows of a partly filled tile that no copy writes must
+  // hold finite values (they are multiplied by zero probabilities).
+  {
+    uint4* z = reinterpret_cast<uint4*>(sK);
+    const int n16 = 2 * Cfg::STAGES * Cfg::KV_BYTES / 16;
+    for (int i = tid; i < n16; i += Cfg::THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  fence_proxy_async();
+  __syncthreads();
+  volatile int* abort_flag = s_abort;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % Cfg::STAGES;
+        if (it >= Cfg::STAGES) {
+          const uint32_t parity = static_cast<uint32_t>(((it / Cfg::STAGES) - 1) & 1);
+          if (*abort_flag || !mbar_wait(&empty_bar[stage], parity)) {
+            if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+            *abort_flag = 1;
+            break;
+          }
+        }
+        const int n0 = (t_begin + it) * Cfg::BN;
+        const int nvalid = min(Cfg::BN, kv_len - n0);
+        const int nboxes = (nvalid + box_rows - 1) / box_rows;
+        mbar_arrive_expect_tx(&full_bar[stage],
+                              static_cast<uint32_t>(nboxes * box_rows * 128 * Cfg::HALVES * 2));
+        for (int j = 0; j < nboxes; ++j) {
+          const int key = n0 + j * box_rows;
+          const int bi = key / p.block_size;
+          const int blk = bt_cached ? s_bt[bi - bt_first] : bt[bi];
+          const int row = (blk * p.Hk + kvh) * p.block_size + key % p.block_size;
+#pragma unroll
+          for (int h = 0; h < Cfg::HALVES; ++h) {
+            const int dst = stage * Cfg::KV_BYTES + h * Cfg::HALF_BYTES + j * box_rows * 128;
+            tma_load_2d(sK + dst, &tm_k, &full_bar[stage], h * 64, row);
+            tma_load_2d(sV + dst, &tm_v, &full_bar[stage], h * 64, row);
+          }
+        }
+        ++issued;
+      }
+      if (*abort_flag) {
+        // Bounded wait for the copies still in flight before the CTA retires.
+        const int first = issued > Cfg::STAGES ? issued - Cfg::STAGES : 0;
+        for (int i = first; i < issued; ++i)
+          mbar_wait(&full_bar[i % Cfg::STAGES], static_cast<uint32_t>((i / Cfg::STAGES) & 1));
+      }
+    }
+    __syncthreads();   // pairs with the barrier before the merge
+    __syncthreads();   // pairs with the barrier inside the merge
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  {
+    constexpr int CHUNKS = D / 8;
+    // Each compute warp only needs the Q rows; every warp loads the whole (small) tile part.
+    for (int idx = tid; idx < 16 * CHUNKS; idx += Cfg::COMPUTE_THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < rows) {
+        const int qi = row / G, hh = kvh * G + row % G;
+        v = *reinterpret_cast<const uint4*>(p.q + static_cast<long long>(b * p.q_len + qi) * p.q_stride +
+                                            static_cast<long long>(hh) * D + c * 8);
+      }
+      *reinterpret_cast<uint4*>(sQ + tile_offset<D>(row, c)) = v;
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY};
+  float row_sum[2] = {0.f, 0.f};
+  uint32_t q_frag[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks)
+    ldmatrix_x4(q_frag[ks], smem_u32(sQ) + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+
+  const int r_a = lane >> 2;
+  int pos_r[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it % Cfg::STAGES;
+    bool ok = !*abort_flag &&
+              mbar_wait(&full_bar[stage], static_cast<uint32_t>((it / Cfg::STAGES) & 1));
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+      if (lane == 0) {
+        if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+        *abort_flag = 1;
+      }
+      break;
+    }
+    const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
+    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
+    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kf[4];
+      const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int kchunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
+      mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
+      mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
+        const int pos = pos_r[j >> 1];
+        bool keep = key <= pos && key < kv_len;
+        if (p.window > 0) keep = keep && key > pos - p.window;
+        const float v = keep ? s[i][j] * p.scale_log2 : -INFINITY;
+        s[i][j] = v;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float tm = quad_max(tile_max[r]);
+      const float new_max = fmaxf(row_max[r], tm);
+      corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+      row_max[r] = new_max;
+      row_sum[r] *= corr[r];
+    }
+    const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
+                            row_max[1] == -INFINITY ? 0.f : row_max[1]};
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2f(s[i][j] - m_use[j >> 1]);
+        s[i][j] = e;
+        row_sum[j >> 1] += e;
+      }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o_acc[i][0] *= corr[0];
+      o_acc[i][1] *= corr[0];
+      o_acc[i][2] *= corr[1];
+      o_acc[i][3] *= corr[1];
+    }
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(s[0][0], s[0][1]);
+    pa[1] = pack_bf16x2(s[0][2], s[0][3]);
+    pa[2] = pack_bf16x2(s[1][0], s[1][1]);
+    pa[3] = pack_bf16x2(s[1][2], s[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+      uint32_t vf[4];
+      const int vrow = warp * 16 + (lane & 15);
+      const int vchunk = dt * 2 + (lane >> 4);
+      ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
+      mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
+      mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
+    }
+    // This warp is done reading the stage.
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);
+  }
+  __syncthreads();   // every warp (and the producer) is past the main loop
+  if (*abort_flag) {
+    __syncthreads();
+    return;
+  }
+
+  // ---- merge the four warps' partial results through shared memory
+  float* m_buf = reinterpret_cast<float*>(sK);
+  float* l_buf = m_buf + 64;
+  float* o_buf = l_buf + 64;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] = quad_sum(row_sum[r]);
+    if ((lane & 3) == 0) {
+      m_buf[warp * 16 + r_a + 8 * r] = row_max[r];
+      l_buf[warp * 16 + r_a + 8 * r] = row_sum[r];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int col = i * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float* dst = o_buf + (static_cast<size_t>(warp) * 16 + r_a + 8 * r) * (D + 4) + col;
+      *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * (D / 4); idx += Cfg::COMPUTE_THREADS) {
+    const int row = idx / (D / 4);
+    const int c4 = (idx % (D / 4)) * 4;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, m_buf[w * 16 + row]);
+    float l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = m_buf[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      l += l_buf[w * 16 + row] * f;
+      const float4 x =
+          *reinterpret_cast<const float4*>(o_buf + (static_cast<size_t>(w) * 16 + row) * (D + 4) + c4);
+      acc.x += x.x * f;
+      acc.y += x.y * f;
+      acc.z += x.z * f;
+      acc.w += x.w * f;
+    }
+    const int qi = row / G, hh = kvh * G + row % G;
+    if (p.splits == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint2 pk;
+      pk.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+      pk.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                                static_cast<long long>(hh) * D + c4) = pk;
+      if (p.lse && c4 == 0)
+        p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+            l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+    } else {
+      const size_t pr = ((static_cast<size_t>(b) * p.Hk + kvh) * p.splits + split) * 16 + row;
+      *reinterpret_cast<float4*>(p.o_part + pr * D + c4) = acc;
+      if (c4 == 0) {
+        p.lse_part[pr * 2] = m;
+        p.lse_part[pr * 2 + 1] = l;
+      }
+    }
+  }
+}
+
 // Merge of split-KV partials: one warp per (sequence, kv head, row).
 template <int D>
 __global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnParams p, int B) {
@@ -612,17 +938,48 @@ static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_
 
 template <int D>
 static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
-  using Cfg = DecodeCfg<D>;
-  auto kern = gqa_decode_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
-        cudaSuccess)
-      return -20;
-    configured = true;
-  }
+  const bool use_tma = (p.block_size % 8) == 0 && (p.block_size <= 64 ? (64 % p.block_size) == 0
+                                                                       : (p.block_size % 64) == 0) &&
+                       (reinterpret_cast<uintptr_t>(p.k_cache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(p.v_cache) & 15) == 0;
   dim3 grid(B, p.Hk, p.splits);
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
+  if (use_tma) {
+    using Cfg = DecodeTmaCfg<D>;
+    auto kern = gqa_decode_tma_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+          cudaSuccess)
+        return -20;
+      cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+      configured = true;
+    }
+    const int box_rows = p.block_size < 64 ? p.block_size : 64;
+    CUtensorMap tk, tv;
+    // Unknown cache size (callers on the raw C ABI): describe a view large enough for
+    // any block index; only the boxes named by the block table are ever touched.
+    const uint64_t rows = p.num_cache_blocks > 0
+                              ? static_cast<uint64_t>(p.num_cache_blocks) * p.Hk * p.block_size
+                              : (1ull << 31);
+    int r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.k_cache, rows, D, D,
+                              box_rows, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r - 2000;
+    r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.v_cache, rows, D, D, box_rows,
+                          64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r - 3000;
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tk, tv, p, box_rows);
+  } else {
+    using Cfg = DecodeCfg<D>;
+    auto kern = gqa_decode_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+          cudaSuccess)
+        return -20;
+      configured = true;
+    }
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
+  }
   if (cudaGetLastError() != cudaSuccess) return -21;
   if (p.splits > 1) {
     const long long warps = static_cast<long long>(B) * p.Hk * (p.Hq / p.Hk) * p.q_len;
@@ -680,7 +1037,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
                                float* lse, const int* block_tables, const int* seq_lens, int B,
                                int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
                                long long q_stride, long long out_stride, float scale, int window,
-                               int splits, void* scratch, cudaStream_t stream) {
+                               int splits, void* scratch, int num_cache_blocks, int* status,
+                               cudaStream_t stream) {
   if (B <= 0) return 0;
   if (Hq % Hk != 0 || (Hq / Hk) * q_len > 16 || q_len < 1) return -1;
   if (splits < 1) splits = 1;
@@ -705,6 +1063,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.window = window;
   p.q_len = q_len;
   p.splits = splits;
+  p.status = status;
+  p.num_cache_blocks = num_cache_blocks;
   if (splits > 1) {
     p.o_part = static_cast<float*>(scratch);
     p.lse_part = p.o_part + static_cast<size_t>(B) * Hk * splits * 16 * D;

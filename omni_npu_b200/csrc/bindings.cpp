@@ -56,7 +56,8 @@ size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits);
 int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                     const int* block_tables, const int* seq_lens, int B, int q_len, int max_blocks,
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
-                    float scale, int window, int splits, void* scratch, cudaStream_t stream);
+                    float scale, int window, int splits, void* scratch, int num_cache_blocks,
+                    int* status, cudaStream_t stream);
 int b200_argmax(const void* logits, int* out, int B, int V, long long stride, int is_fp32,
                 cudaStream_t stream);
 int b200_sample(const void* logits, int* out, const float* temperature, const int* top_k,
@@ -333,7 +334,7 @@ int64_t gqa_decode_scratch_bytes(int64_t B, int64_t Hk, int64_t D, int64_t split
 Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& block_tables, const Tensor& seq_lens, int64_t num_seqs,
                   int64_t q_len, int64_t num_q_heads, double scale, int64_t window, int64_t splits,
-                  const c10::optional<Tensor>& scratch) {
+                  const c10::optional<Tensor>& scratch, const Tensor& status) {
   CHECK_CUDA_BF16(q);
   CHECK_CUDA_BF16(k_cache);
   CHECK_CUDA_BF16(v_cache);
@@ -357,7 +358,7 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                         nullptr, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
                         (int)num_seqs, (int)q_len, (int)block_tables.size(1), bs, Hq, Hk, D,
                         q.stride(0), out.stride(0), (float)scale, (int)window, (int)splits, sp,
-                        cur_stream()),
+                        (int)k_cache.size(0), status.data_ptr<int>(), cur_stream()),
         "gqa_decode");
   return out;
 }

@@ -321,13 +321,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * p.acc_stride);
       const bool partial = p.splits > 1;
-      float* ws_row = nullptr;
+      float* ws_col = nullptr;
       if (partial) {
-        // workspace layout: [split][mn_tile][128 rows][BN cols]
-        ws_row = p.workspace +
-                 ((static_cast<size_t>(tc.split) * total_mn_tiles + tc.mn_index) * kBM +
-                  (quarter * 32 + lane)) *
-                     p.BN;
+        // workspace layout: [split][mn_tile][BN cols][128 rows]: for one column the 32
+        // lanes of a warp (32 consecutive rows) touch 128 contiguous bytes.
+        ws_col = p.workspace +
+                 (static_cast<size_t>(tc.split) * total_mn_tiles + tc.mn_index) * kBM * p.BN +
+                 (quarter * 32 + lane);
       }
       for (int c = 0; c < p.BN; c += 16) {
         uint32_t r[16];
@@ -345,10 +345,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
         const int col = tc.n0 + c;
         if (partial) {
-          float4* dst = reinterpret_cast<float4*>(ws_row + c);
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int i = 0; i < 16; ++i) ws_col[static_cast<size_t>(c + i) * kBM] = v[i];
           continue;
         }
         if (!row_ok || col >= p.N) continue;
@@ -438,43 +436,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (is_last) {
           __threadfence();
-          if (row_ok) {
-            const size_t split_stride = static_cast<size_t>(total_mn_tiles) * kBM * p.BN;
-            const float* base =
-                p.workspace +
-                (static_cast<size_t>(tc.mn_index) * kBM + (quarter * 32 + lane)) * p.BN;
-            for (int c = 0; c < p.BN; c += 4) {
-              const int col = tc.n0 + c;
-              if (col >= p.N) break;
-              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int sp = 0; sp < p.splits; ++sp) {
-                const float4 x = __ldcg(reinterpret_cast<const float4*>(base + sp * split_stride + c));
-                s.x += x.x;
-                s.y += x.y;
-                s.z += x.z;
-                s.w += x.w;
-              }
-              float v[4] = {s.x, s.y, s.z, s.w};
-              const int ncols = min(4, p.N - col);
-              for (int i = 0; i < ncols; ++i) {
+          const size_t split_stride = static_cast<size_t>(total_mn_tiles) * kBM * p.BN;
+          const float* base =
+              p.workspace + static_cast<size_t>(tc.mn_index) * kBM * p.BN + (quarter * 32 + lane);
+          for (int c = 0; c < p.BN; c += 8) {
+            const int col = tc.n0 + c;
+            if (col >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            for (int sp = 0; sp < p.splits; ++sp) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                v[i] += __ldcg(base + sp * split_stride + static_cast<size_t>(c + i) * kBM);
+            }
+            if (!row_ok) continue;
+            const int ncols = min(8, p.N - col);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (i < ncols) {
                 if (p.bias) v[i] += __bfloat162float(p.bias[col + i]);
                 if (p.residual)
                   v[i] += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ldc + col + i]);
               }
-              if (p.out_fp32) {
-                float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-                for (int i = 0; i < ncols; ++i) dst[i] = v[i];
+            }
+            if (p.out_fp32) {
+              float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+              for (int i = 0; i < ncols; ++i) dst[i] = v[i];
+            } else {
+              __nv_bfloat16* dst =
+                  reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+              if (ncols == 8 && (p.ldc & 7) == 0) {
+                uint4 pk;
+                pk.x = pack_bf16x2(v[0], v[1]);
+                pk.y = pack_bf16x2(v[2], v[3]);
+                pk.z = pack_bf16x2(v[4], v[5]);
+                pk.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(dst) = pk;
               } else {
-                __nv_bfloat16* dst =
-                    reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col;
-                if (ncols == 4 && (p.ldc & 3) == 0) {
-                  uint2 pk;
-                  pk.x = pack_bf16x2(v[0], v[1]);
-                  pk.y = pack_bf16x2(v[2], v[3]);
-                  *reinterpret_cast<uint2*>(dst) = pk;
-                } else {
-                  for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
-                }
+                for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
               }
             }
           }

@@ -333,13 +333,13 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         bound = max_seq_len if max_seq_len > 0 else block_tables.shape[1] * k_cache.shape[2]
         splits = decode_splits(num_seqs, hk, bound)
     scratch = None
+    st = device_state(q.device)
     if splits > 1:
-        st = device_state(q.device)
         nbytes = C.gqa_decode_scratch_bytes(num_seqs, hk, d, splits)
         scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
     _count(2 if splits > 1 else 1)
     return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
-                        scale, window, splits, scratch)
+                        scale, window, splits, scratch, st.status)
 
 
 merge_attn_states = ref.merge_attn_states

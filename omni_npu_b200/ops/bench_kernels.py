@@ -66,7 +66,58 @@ SERVING_GEMMS = [
 ]
 
 
+def time_graph(make_fns, iters=5):
+    """Capture the given launches (each reading different buffers, together larger
+    than L2) in one CUDA graph and return the mean device time per launch in ms.
+    This is how launch-bound decode kernels run in production: back to back from a
+    graph, with cold operands but no host gaps."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for f in make_fns:
+            f()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in make_fns:
+            f()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times) / len(make_fns)
+
+
+def bench_gemm_graph(args):
+    hbm, flops_peak, src = peaks()
+    shapes = [s for s in SERVING_GEMMS if s[1] <= 512] if args.m is None else [("custom", args.m, args.n, args.k)]
+    print(f"# GEMM bf16 inside a CUDA graph over rotating weights (> L2 in total); fractions of {src} peaks")
+    print(f"{'shape':28s} {'M':>6s} {'N':>7s} {'K':>6s} {'bn':>4s} {'sp':>3s} {'ours_us':>9s} {'cublas_us':>9s} "
+          f"{'GB/s':>7s} {'frac':>5s} {'vs_cublas':>9s}")
+    for label, m, n, k in shapes:
+        nbuf = max(4, min(64, (300 << 20) // (n * k * 2) + 1))
+        a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        ws = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05 for _ in range(nbuf)]
+        bn, sp = args.bn, args.splits
+        plan = torch.ops.omni_b200.gemm_plan(m, n, k, 2, False, bn, sp)
+        t = time_graph([(lambda w=w: ops.gemm(a, w, bn=bn, splits=sp)) for w in ws])
+        tc = time_graph([(lambda w=w: torch.matmul(a, w.t())) for w in ws])
+        by = 2.0 * (m * k + n * k + m * n)
+        fl = 2.0 * m * n * k
+        frac = max(fl / flops_peak, by / hbm) / (t / 1e3)
+        print(f"{label:28s} {m:6d} {n:7d} {k:6d} {plan[0]:4d} {plan[1]:3d} {t*1e3:9.1f} {tc*1e3:9.1f} "
+              f"{by/t/1e6:7.0f} {frac:5.2f} {tc/t:9.2f}")
+    ops.check_status()
+
+
 def bench_gemm(args):
+    if args.graph:
+        return bench_gemm_graph(args)
     hbm, flops_peak, src = peaks()
     shapes = SERVING_GEMMS if args.m is None else [("custom", args.m, args.n, args.k)]
     print(f"# GEMM bf16, fractions of {src} peaks: {hbm/1e12:.2f} TB/s, {flops_peak/1e12:.0f} TFLOP/s")
@@ -167,6 +218,8 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--graph", action="store_true",
+                    help="gemm: time decode-shaped GEMMs back to back inside a CUDA graph")
     ap.add_argument("--b", type=int, help="attn: batch size of a single case")
     ap.add_argument("--ctx", type=int, default=1024, help="attn: context length of a single case")
     ap.add_argument("--phase", default="both", choices=["both", "decode", "prefill"])
