@@ -11,11 +11,12 @@
 
 extern "C" {
 void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, int force_bn, int force_splits,
-                    int* out_bn, int* out_splits, size_t* out_ws_bytes, int* out_counters);
+                    int* out_bn, int* out_splits, size_t* out_ws_bytes, int* out_counters,
+                    int* out_cluster);
 int b200_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
               int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu,
-              int BN, int splits, void* workspace, int* counters, int* status, int max_ctas,
-              cudaStream_t stream);
+              int BN, int splits, int cluster_split, void* workspace, int* counters, int* status,
+              int max_ctas, cudaStream_t stream);
 int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_offsets,
                       int num_experts, int total_rows, int N, int K, int lda, int ldc,
                       int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
@@ -80,21 +81,22 @@ inline void check(int rc, const char* what) {
 #define CHECK_I32(t) \
   TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kInt && (t).is_contiguous(), #t " must be a contiguous CUDA int32 tensor")
 
-// (BN, splits, workspace bytes, counters) for a problem.
-std::tuple<int64_t, int64_t, int64_t, int64_t> gemm_plan(int64_t M, int64_t N, int64_t K,
-                                                         int64_t elem_bytes, bool swiglu,
-                                                         int64_t force_bn, int64_t force_splits) {
-  int bn, sp, cnt;
+// (BN, splits, workspace bytes, counters, cluster flag) for a problem.
+std::tuple<int64_t, int64_t, int64_t, int64_t, int64_t> gemm_plan(int64_t M, int64_t N, int64_t K,
+                                                                  int64_t elem_bytes, bool swiglu,
+                                                                  int64_t force_bn,
+                                                                  int64_t force_splits) {
+  int bn, sp, cnt, cl;
   size_t ws;
   b200_gemm_plan((int)M, (int)N, (int)K, (int)elem_bytes, swiglu ? 1 : 0, (int)force_bn,
-                 (int)force_splits, &bn, &sp, &ws, &cnt);
-  return {bn, sp, (int64_t)ws, cnt};
+                 (int)force_splits, &bn, &sp, &ws, &cnt, &cl);
+  return {bn, sp, (int64_t)ws, cnt, cl};
 }
 
 // C = A @ W^T (+bias) (+residual).  A [M,K], W [N,K]; bf16 or float8_e4m3fn.
 Tensor gemm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& bias,
             const c10::optional<Tensor>& residual, bool out_fp32, bool swiglu, int64_t bn,
-            int64_t splits, const c10::optional<Tensor>& workspace,
+            int64_t splits, bool cluster_split, const c10::optional<Tensor>& workspace,
             const c10::optional<Tensor>& counters, const Tensor& status, int64_t max_ctas) {
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm: 2-D CUDA tensors");
   TORCH_CHECK(a.scalar_type() == w.scalar_type(), "gemm: dtype mismatch");
@@ -121,14 +123,15 @@ Tensor gemm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& bias,
   }
   void* ws_p = nullptr;
   int* cnt_p = nullptr;
-  if (splits > 1) {
+  if (splits > 1 && !cluster_split) {
     TORCH_CHECK(workspace.has_value() && counters.has_value(), "gemm: split-K needs workspace");
     ws_p = workspace->data_ptr();
     cnt_p = counters->data_ptr<int>();
   }
   check(b200_gemm(a.data_ptr(), w.data_ptr(), c.data_ptr(), bias_p, res_p, M, N, K,
                   (int)a.stride(0), (int)w.stride(0), n_out, fp8 ? 1 : 0, out_fp32 ? 1 : 0,
-                  swiglu ? 1 : 0, (int)bn, (int)splits, ws_p, cnt_p, status.data_ptr<int>(),
+                  swiglu ? 1 : 0, (int)bn, (int)splits, cluster_split ? 1 : 0, ws_p, cnt_p,
+                  status.data_ptr<int>(),
                   (int)max_ctas, cur_stream()),
         "gemm");
   return c;

@@ -1,0 +1,473 @@
+// Collectives over peer-mapped ("symmetric") device memory: every rank of a group
+// owns one data buffer and one signal pad, all ranks have all of them mapped
+// (CUDA IPC), and the kernels below move data with plain loads / stores over
+// NVLink + NVSwitch.  One process per GPU; every rank launches the same kernel.
+//
+//  * all_reduce, one shot   (small messages): stage own data, flag barrier,
+//        every rank reads all ranks' data and sums in rank order.
+//  * all_reduce, two shot   (large messages): stage, barrier, each rank reduces
+//        its slice from all peers (reduce-scatter), barrier, each rank gathers
+//        the reduced slices from all peers (all-gather).
+//  * both optionally fuse  "+ residual, RMSNorm"  into the final pass, which is
+//        what follows the o_proj / down_proj all-reduce in a decoder layer.
+//  * all_gather / reduce_scatter for the sequence-parallel residual stream.
+//
+// Synchronisation: a monotonically increasing epoch kept in device memory (so
+// CUDA-graph replays need no host update) and per-(rank, block) flags in every
+// rank's signal pad.  Data buffers are split in two halves used alternately
+// (epoch parity): the barrier that opens call n+1 proves every rank has left
+// call n, so half (n & 1) is free again when call n+2 stages into it.
+// Every flag wait is bounded; on expiry the kernel records a status code and
+// returns without touching peer memory again.
+//
+// Replaces HCCL all_reduce / all_gather / reduce_scatter call sites of the
+// reference (omni_npu/distributed/communicator.py:52-83) on the latency-bound
+// paths; NCCL remains the transport for everything else.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+namespace b200 {
+
+static constexpr int kMaxRanks = 8;
+static constexpr int kMaxCommBlocks = 64;
+static constexpr uint32_t kMaxFlagPolls = 1u << 24;   // ~ a second of polling
+
+struct SymmGroup {
+  void* data[kMaxRanks];        // peer-mapped data buffers (this rank's own at index rank)
+  uint32_t* signal[kMaxRanks];  // peer-mapped signal pads: [kMaxRanks][kMaxCommBlocks] flags, then epoch
+  int world;
+  int rank;
+  size_t half_bytes;            // bytes of one half of a data buffer
+};
+
+// Layout of a signal pad (uint32 words):
+//   [0, kMaxRanks*kMaxCommBlocks)        flags[src_rank][block]
+//   [kMaxRanks*kMaxCommBlocks]           epoch counter (local use only)
+static constexpr int kEpochWord = kMaxRanks * kMaxCommBlocks;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Barrier between block `blockIdx.x` of every rank.  Thread t < world signals
+// peer t and waits for peer t.  Returns false if a peer did not show up in time.
+__device__ __forceinline__ bool block_barrier(const SymmGroup& g, uint32_t epoch, int* status) {
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x < g.world) {
+    __threadfence_system();
+    const int peer = threadIdx.x;
+    st_release_sys(g.signal[peer] + g.rank * kMaxCommBlocks + blockIdx.x, epoch);
+    const uint32_t* mine = g.signal[g.rank] + peer * kMaxCommBlocks + blockIdx.x;
+    uint32_t i = 0;
+    // flags only grow; a peer that is already one call ahead has a larger value
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (++i > kMaxFlagPolls) {
+        ok = false;
+        break;
+      }
+    }
+    if (!ok && status) atomicCAS(status, 0, 5);
+  }
+  return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
+union Pack8 {
+  uint4 u;
+  __nv_bfloat16 h[8];
+};
+
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
+  Pack8 p;
+  p.u = v;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(p.h[i]);
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
+  Pack8 p;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) p.h[i] = __float2bfloat16(acc[i]);
+  return p.u;
+}
+
+// Each call advances the epoch by `steps` barriers.  The value is read by every
+// block before block 0 bumps it at the very end of the kernel.
+__device__ __forceinline__ uint32_t read_epoch(const SymmGroup& g) {
+  return *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord);
+}
+
+// ---------------------------------------------------------------- one shot
+// in/out: [n_vec] vectors of 8 bf16.  Rows are `row_vecs` vectors long when the
+// fused norm is requested (residual / norm_w non-null): out = RMSNorm(residual +=
+// sum) * norm_w, with the updated residual written back.
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ out,
+                         long long n_vec, uint4* __restrict__ residual,
+                         const uint4* __restrict__ norm_w, int row_vecs, float eps,
+                         uint32_t* done_counter, int* status) {
+  const uint32_t epoch0 = read_epoch(g);
+  const uint32_t epoch = epoch0 + 1;
+  const int half = epoch & 1;
+  uint4* stage = reinterpret_cast<uint4*>(static_cast<char*>(g.data[g.rank]) + half * g.half_bytes);
+  const bool fused = norm_w != nullptr;
+  // Work split: contiguous chunk per block (whole rows when fused).
+  long long begin, end;
+  if (fused) {
+    const long long rows = n_vec / row_vecs;
+    const long long per = (rows + gridDim.x - 1) / gridDim.x;
+    begin = min(rows, per * blockIdx.x) * row_vecs;
+    end = min(rows, per * (blockIdx.x + 1)) * row_vecs;
+  } else {
+    const long long per = (n_vec + gridDim.x - 1) / gridDim.x;
+    begin = min(n_vec, per * blockIdx.x);
+    end = min(n_vec, per * (blockIdx.x + 1));
+  }
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) stage[i] = in[i];
+  const bool ok = block_barrier(g, epoch, status);
+  if (ok) {
+    const uint4* src[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      src[r] = r < g.world ? reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                            half * g.half_bytes)
+                           : nullptr;
+    if (!fused) {
+      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < g.world) add8(acc, __ldcv(src[r] + i));
+        out[i] = pack8(acc);
+      }
+    } else {
+      __shared__ float red[32];
+      // one row at a time per block; a thread owns up to 4 vectors of the row
+      for (long long row0 = begin; row0 < end; row0 += row_vecs) {
+        float vals[4][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int v = threadIdx.x + k * blockDim.x;
+          if (v < row_vecs) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < g.world) add8(acc, __ldcv(src[r] + row0 + v));
+            // the reduced value is rounded to bf16 before the residual add, exactly
+            // as an unfused all-reduce followed by add+norm would do
+            Pack8 y;
+            y.u = pack8(acc);
+            Pack8 rs;
+            rs.u = residual[row0 + v];
+            Pack8 nr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              nr.h[j] = __float2bfloat16(__bfloat162float(y.h[j]) + __bfloat162float(rs.h[j]));
+              vals[k][j] = __bfloat162float(nr.h[j]);
+              ss += vals[k][j] * vals[k][j];
+            }
+            residual[row0 + v] = nr.u;
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+        __syncthreads();
+        const float inv = rsqrtf(tot / static_cast<float>(row_vecs * 8) + eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int v = threadIdx.x + k * blockDim.x;
+          if (v < row_vecs) {
+            Pack8 w8, o8;
+            w8.u = norm_w[v];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o8.h[j] = __float2bfloat16(vals[k][j] * inv * __bfloat162float(w8.h[j]));
+            out[row0 + v] = o8.u;
+          }
+        }
+      }
+    }
+  }
+  // The last block to finish advances the epoch for the next call.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = epoch;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- two shot
+// Stage -> barrier -> reduce my slice (into my "reduced" area) -> barrier ->
+// gather all slices.  The slice of rank r covers vectors [r*slice, (r+1)*slice).
+// Every pass splits each slice across the blocks in the same way, so block b only
+// ever consumes data produced by block b of a peer and the per-block barrier is
+// all the ordering that is needed.
+__device__ __forceinline__ void slice_part(long long n_vec, long long slice_vecs, int r,
+                                           long long* s_begin, long long* b, long long* e) {
+  *s_begin = slice_vecs * r;
+  const long long s_end = min(n_vec, *s_begin + slice_vecs);
+  const long long n_r = max(0LL, s_end - *s_begin);
+  const long long per = (n_r + gridDim.x - 1) / gridDim.x;
+  *b = min(n_r, per * blockIdx.x);
+  *e = min(n_r, per * (blockIdx.x + 1));
+}
+
+__global__ void __launch_bounds__(512)
+allreduce_twoshot_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ out,
+                         long long n_vec, long long slice_vecs, uint32_t* done_counter,
+                         int* status) {
+  const uint32_t epoch0 = read_epoch(g);
+  // two barriers; the call consumes three epoch values so that the next call
+  // lands on the other half of the buffers
+  const uint32_t e1 = epoch0 + 1, e2 = epoch0 + 2, e_end = epoch0 + 3;
+  const int half = e1 & 1;
+  char* my_base = static_cast<char*>(g.data[g.rank]) + half * g.half_bytes;
+  uint4* stage = reinterpret_cast<uint4*>(my_base);
+  const size_t red_off = static_cast<size_t>(n_vec) * sizeof(uint4);
+  for (int r = 0; r < g.world; ++r) {
+    long long sb, b, e;
+    slice_part(n_vec, slice_vecs, r, &sb, &b, &e);
+    for (long long i = b + threadIdx.x; i < e; i += blockDim.x) stage[sb + i] = in[sb + i];
+  }
+  bool ok = block_barrier(g, e1, status);
+  if (ok) {
+    long long sb, b, e;
+    slice_part(n_vec, slice_vecs, g.rank, &sb, &b, &e);
+    uint4* red = reinterpret_cast<uint4*>(my_base + red_off);
+    for (long long i = b + threadIdx.x; i < e; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < g.world) {
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                            half * g.half_bytes);
+          add8(acc, __ldcv(src + sb + i));
+        }
+      }
+      red[i] = pack8(acc);
+    }
+    ok = block_barrier(g, e2, status);
+  }
+  if (ok) {
+    for (int r = 0; r < g.world; ++r) {
+      long long sb, b, e;
+      slice_part(n_vec, slice_vecs, r, &sb, &b, &e);
+      const uint4* red = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                        half * g.half_bytes + red_off);
+      for (long long i = b + threadIdx.x; i < e; i += blockDim.x) out[sb + i] = __ldcv(red + i);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = e_end;
+    }
+  }
+}
+
+// ------------------------------------------------------------- all-gather
+// out [world * n_vec] = concatenation of every rank's in [n_vec].
+__global__ void __launch_bounds__(512)
+allgather_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ out, long long n_vec,
+                 uint32_t* done_counter, int* status) {
+  const uint32_t epoch = read_epoch(g) + 1;
+  const int half = epoch & 1;
+  uint4* stage = reinterpret_cast<uint4*>(static_cast<char*>(g.data[g.rank]) + half * g.half_bytes);
+  const long long per = (n_vec + gridDim.x - 1) / gridDim.x;
+  const long long begin = min(n_vec, per * blockIdx.x), end = min(n_vec, per * (blockIdx.x + 1));
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) stage[i] = in[i];
+  if (block_barrier(g, epoch, status)) {
+    for (int r = 0; r < g.world; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                        half * g.half_bytes);
+      uint4* dst = out + static_cast<long long>(r) * n_vec;
+      if (r == g.rank) {
+        for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) dst[i] = in[i];
+      } else {
+        for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) dst[i] = __ldcv(src + i);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = epoch;
+    }
+  }
+}
+
+// ---------------------------------------------------------- reduce-scatter
+// in [world * n_vec]; out [n_vec] = sum over ranks of their chunk `rank`.
+__global__ void __launch_bounds__(512)
+reducescatter_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ out,
+                     long long n_vec, uint32_t* done_counter, int* status) {
+  const uint32_t epoch = read_epoch(g) + 1;
+  const int half = epoch & 1;
+  uint4* stage = reinterpret_cast<uint4*>(static_cast<char*>(g.data[g.rank]) + half * g.half_bytes);
+  const long long per = (n_vec + gridDim.x - 1) / gridDim.x;
+  const long long begin = min(n_vec, per * blockIdx.x), end = min(n_vec, per * (blockIdx.x + 1));
+  // stage every chunk (block b stages part b of every chunk, which is what block b of the
+  // owning rank will read)
+  for (int r = 0; r < g.world; ++r)
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x)
+      stage[static_cast<long long>(r) * n_vec + i] = in[static_cast<long long>(r) * n_vec + i];
+  if (block_barrier(g, epoch, status)) {
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < g.world) {
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                            half * g.half_bytes);
+          add8(acc, __ldcv(src + static_cast<long long>(g.rank) * n_vec + i));
+        }
+      }
+      out[i] = pack8(acc);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = epoch;
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// ---- IPC plumbing (host).  The buffers are plain cudaMalloc allocations so that
+// cudaIpcGetMemHandle applies to the whole allocation.
+extern "C" int b200_symm_alloc(size_t bytes, void** ptr, void* handle_out_64) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return -1;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess) return -2;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return -3;
+  memcpy(handle_out_64, &h, sizeof(h));
+  *ptr = p;
+  return 0;
+}
+
+extern "C" int b200_symm_open(const void* handle_64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return -1;
+  *ptr = p;
+  return 0;
+}
+
+extern "C" int b200_symm_close(void* ptr) {
+  return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int b200_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+
+extern "C" int b200_symm_signal_words() { return kEpochWord + 4; }
+
+static SymmGroup make_group(void* const* data, void* const* signal, int world, int rank,
+                            size_t half_bytes) {
+  SymmGroup g{};
+  for (int r = 0; r < kMaxRanks; ++r) {
+    g.data[r] = r < world ? data[r] : nullptr;
+    g.signal[r] = r < world ? static_cast<uint32_t*>(signal[r]) : nullptr;
+  }
+  g.world = world;
+  g.rank = rank;
+  g.half_bytes = half_bytes;
+  return g;
+}
+
+static int pick_blocks(long long n_vec, int max_blocks) {
+  long long b = (n_vec + 2047) / 2048;   // >= 4 vectors per thread at 512 threads
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return static_cast<int>(b);
+}
+
+// mode: 0 auto, 1 one shot, 2 two shot.  n_elems bf16 elements (multiple of 8).
+// Fused add+norm (residual, norm_w non-null, row_elems = hidden size) is available in
+// one-shot mode.  done_counter: a zero-initialised device word owned by the caller.
+extern "C" int b200_symm_all_reduce(void* const* data, void* const* signal, int world, int rank,
+                                    size_t half_bytes, const void* in, void* out, long long n_elems,
+                                    void* residual, const void* norm_w, int row_elems, float eps,
+                                    int mode, void* done_counter, int* status,
+                                    cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks) return -1;
+  if ((n_elems & 7) != 0) return -2;
+  const long long n_vec = n_elems >> 3;
+  const size_t bytes = static_cast<size_t>(n_elems) * 2;
+  const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
+  const bool fused = norm_w != nullptr;
+  if (fused && ((row_elems & 7) != 0 || row_elems > 512 * 4 * 8 || n_elems % row_elems != 0)) return -3;
+  if (mode == 0) mode = (fused || bytes <= (world <= 2 ? (8u << 20) : (world <= 4 ? (1u << 20) : (512u << 10)))) ? 1 : 2;
+  if (fused) mode = 1;
+  if (mode == 1) {
+    if (bytes > half_bytes) return -4;
+    const int blocks = fused ? static_cast<int>((n_elems / row_elems) < kMaxCommBlocks ? (n_elems / row_elems) : kMaxCommBlocks)
+                             : pick_blocks(n_vec, kMaxCommBlocks);
+    allreduce_oneshot_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, stream>>>(
+        g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
+        static_cast<uint4*>(residual), static_cast<const uint4*>(norm_w), row_elems >> 3, eps,
+        static_cast<uint32_t*>(done_counter), status);
+  } else {
+    const long long slice = (n_vec + world - 1) / world;
+    if (bytes + static_cast<size_t>(slice) * 16 > half_bytes) return -4;
+    const int blocks = pick_blocks(n_vec, kMaxCommBlocks);
+    allreduce_twoshot_kernel<<<blocks, 512, 0, stream>>>(
+        g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec, slice,
+        static_cast<uint32_t*>(done_counter), status);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int b200_symm_all_gather(void* const* data, void* const* signal, int world, int rank,
+                                    size_t half_bytes, const void* in, void* out, long long n_elems,
+                                    void* done_counter, int* status, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || (n_elems & 7) != 0) return -1;
+  if (static_cast<size_t>(n_elems) * 2 > half_bytes) return -4;
+  const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
+  const long long n_vec = n_elems >> 3;
+  allgather_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
+      g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
+      static_cast<uint32_t*>(done_counter), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int b200_symm_reduce_scatter(void* const* data, void* const* signal, int world, int rank,
+                                        size_t half_bytes, const void* in, void* out,
+                                        long long n_elems_out, void* done_counter, int* status,
+                                        cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || (n_elems_out & 7) != 0) return -1;
+  if (static_cast<size_t>(n_elems_out) * 2 * world > half_bytes) return -4;
+  const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
+  const long long n_vec = n_elems_out >> 3;
+  reducescatter_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
+      g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
+      static_cast<uint32_t*>(done_counter), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -49,6 +49,7 @@ struct GemmParams {
   int out_fp32;           // 1: C is fp32, 0: bf16
   int swiglu;             // 1: C[:, n/2] = silu(acc[gate]) * acc[up], gate/up interleaved per 16 cols
   int num_experts;        // grouped: number of local experts (0 = dense)
+  int cluster_split;      // 1: the `splits` CTAs of a cluster share one tile and reduce over DSMEM
   void* C;
   const __nv_bfloat16* bias;       // [N] or null
   const __nv_bfloat16* residual;   // [M, ldc] or null
@@ -73,12 +74,20 @@ struct TileCoord {
 
 template <bool GROUPED>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const int* s_tile_prefix,
-                                            int total_mn_tiles, long long t, int& cursor,
-                                            TileCoord& tc) {
-  const long long total = static_cast<long long>(total_mn_tiles) * p.splits;
-  if (t >= total) return false;
-  const int split = static_cast<int>(t % p.splits);
-  const int mn = static_cast<int>(t / p.splits);
+                                            int total_mn_tiles, long long t, int cta_rank,
+                                            int& cursor, TileCoord& tc) {
+  int split, mn;
+  if (p.cluster_split) {
+    // every CTA of a cluster walks the same (m,n) tiles; its rank picks the K slice
+    if (t >= total_mn_tiles) return false;
+    split = cta_rank;
+    mn = static_cast<int>(t);
+  } else {
+    const long long total = static_cast<long long>(total_mn_tiles) * p.splits;
+    if (t >= total) return false;
+    split = static_cast<int>(t % p.splits);
+    mn = static_cast<int>(t / p.splits);
+  }
   tc.split = split;
   tc.mn_index = mn;
   const int per = (p.k_iters + p.splits - 1) / p.splits;
@@ -121,13 +130,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int w_stage_bytes = p.BN * kRowBytes;
   uint8_t* smem_a = smem;
   uint8_t* smem_w = smem + p.stages * a_stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes);
+  // staging for the cluster reduction: [128 rows][BN + 4] fp32
+  float* red_buf = reinterpret_cast<float*>(smem_w + p.stages * w_stage_bytes);
+  const int red_stride = p.BN + 4;
+  const int red_bytes = p.cluster_split ? kBM * red_stride * 4 : 0;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes + red_bytes);
   uint64_t* full_bar = bars;                    // [stages]
   uint64_t* empty_bar = bars + p.stages;        // [stages]
   uint64_t* tmem_full = bars + 2 * p.stages;    // [2]
   uint64_t* tmem_empty = tmem_full + 2;         // [2]
   uint64_t* drain_bar = tmem_empty + 2;         // [1]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* red_ready = drain_bar + 1;          // [1] all K slices staged (cluster split-K)
+  uint64_t* red_done = red_ready + 1;           // [1] all peers finished reading my staging
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(red_done + 1);
   int* s_flags = reinterpret_cast<int*>(tmem_base_slot + 1);  // [0]=abort, [1]=is_last
   int* s_tile_prefix = s_flags + 2;                           // [num_experts + 1] (grouped)
 
@@ -144,6 +159,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(&tmem_empty[0], 4);
     mbar_init(&tmem_empty[1], 4);
     mbar_init(drain_bar, 1);
+    mbar_init(red_ready, static_cast<uint32_t>(p.splits));
+    mbar_init(red_done, static_cast<uint32_t>(p.splits));
     s_flags[0] = 0;
     s_flags[1] = 0;
     fence_barrier_init();
@@ -169,6 +186,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  int cta_rank = 0;
+  long long t_first = blockIdx.x, t_stride = gridDim.x;
+  if (p.cluster_split) {
+    cta_rank = static_cast<int>(cluster_ctarank());
+    t_first = blockIdx.x / p.splits;
+    t_stride = gridDim.x / p.splits;
+    cluster_sync_all();  // peers' barriers are initialised before anyone signals them
+  }
   const uint32_t tmem_base = *tmem_base_slot;
   if constexpr (GROUPED) {
     total_mn_tiles = s_tile_prefix[p.num_experts] * p.num_n_blocks;
@@ -187,9 +212,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       long long issued = 0;
       bool ok = true;
       TileCoord tc;
-      for (long long t = blockIdx.x; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
-                                                                cursor, tc);
-           t += gridDim.x) {
+      for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
+                                                                cta_rank, cursor, tc);
+           t += t_stride) {
         for (int k = tc.k_begin; k < tc.k_end; ++k) {
           if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
             if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
@@ -240,9 +265,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int cursor = 0;
       bool ok = true;
       TileCoord tc;
-      for (long long t = blockIdx.x; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
-                                                                cursor, tc);
-           t += gridDim.x) {
+      for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
+                                                                cta_rank, cursor, tc);
+           t += t_stride) {
         if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutTmemEmpty);
           *abort_flag = 1;
@@ -290,9 +315,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     int cursor = 0;
+    int tile_iter = 0;
     TileCoord tc;
-    for (long long t = blockIdx.x;
-         decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cursor, tc); t += gridDim.x) {
+    for (long long t = t_first;
+         decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cta_rank, cursor, tc); t += t_stride) {
       bool ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
       {
         // The four epilogue warps take the decision together (barrier + AND
@@ -320,6 +346,115 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = row < tc.m_end;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * p.acc_stride);
+      if (p.cluster_split) {
+        // ---- split-K inside a cluster: stage my K slice's partial tile in shared
+        // memory, then every CTA sums a band of rows over all peers (DSMEM reads).
+        bool okc = true;
+        if (tile_iter > 0) okc = mbar_wait_cluster(red_done, static_cast<uint32_t>((tile_iter - 1) & 1));
+        float* my_row = red_buf + static_cast<size_t>(quarter * 32 + lane) * red_stride;
+        if (okc) {
+          for (int c = 0; c < p.BN; c += 16) {
+            uint32_t r[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                  "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                  "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(t_row + static_cast<uint32_t>(c))
+                : "memory");
+            tmem_ld_wait();
+            uint4* dst = reinterpret_cast<uint4*>(my_row + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const uint32_t a = smem_u32(red_ready);
+          for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
+        }
+        okc = okc && mbar_wait_cluster(red_ready, static_cast<uint32_t>(tile_iter & 1));
+        {
+          uint32_t all_ok;
+          asm volatile(
+              "{\n\t"
+              ".reg .pred p, q;\n\t"
+              "setp.ne.u32 q, %1, 0;\n\t"
+              "bar.red.and.pred p, 1, 128, q;\n\t"
+              "selp.u32 %0, 1, 0, p;\n\t"
+              "}"
+              : "=r"(all_ok)
+              : "r"(okc ? 1u : 0u)
+              : "memory");
+          okc = all_ok != 0;
+        }
+        if (!okc) {
+          if (lane == 0 && !*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+          *abort_flag = 1;
+          break;
+        }
+        {
+          const int rows_per = (kBM + p.splits - 1) / p.splits;
+          const int r_begin = cta_rank * rows_per;
+          const int r_count = max(0, min(kBM, r_begin + rows_per) - r_begin);
+          const int c4n = p.BN >> 2;
+          const int et = threadIdx.x - 64;
+          const uint32_t red_base = smem_u32(red_buf);
+          for (int idx = et; idx < r_count * c4n; idx += 128) {
+            const int rl = r_begin + idx / c4n;
+            const int c = (idx % c4n) * 4;
+            const uint32_t off = static_cast<uint32_t>((rl * red_stride + c) * 4);
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+              const float4 x = ld_shared_cluster_f4(mapa_shared(red_base + off, s2));
+              sum.x += x.x;
+              sum.y += x.y;
+              sum.z += x.z;
+              sum.w += x.w;
+            }
+            const int orow = tc.m0 + rl;
+            const int col = tc.n0 + c;
+            if (orow >= tc.m_end || col >= p.N) continue;
+            float v[4] = {sum.x, sum.y, sum.z, sum.w};
+            const int ncols = min(4, p.N - col);
+            for (int i = 0; i < ncols; ++i) {
+              if (p.bias) v[i] += __bfloat162float(p.bias[col + i]);
+              if (p.residual)
+                v[i] += __bfloat162float(p.residual[static_cast<size_t>(orow) * p.ldc + col + i]);
+            }
+            if (p.out_fp32) {
+              float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(orow) * p.ldc + col;
+              for (int i = 0; i < ncols; ++i) dst[i] = v[i];
+            } else {
+              __nv_bfloat16* dst =
+                  reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(orow) * p.ldc + col;
+              if (ncols == 4 && (p.ldc & 3) == 0) {
+                uint2 pk;
+                pk.x = pack_bf16x2(v[0], v[1]);
+                pk.y = pack_bf16x2(v[2], v[3]);
+                *reinterpret_cast<uint2*>(dst) = pk;
+              } else {
+                for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const uint32_t a = smem_u32(red_done);
+          for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
+        }
+        ++tile_iter;
+        continue;
+      }
       const bool partial = p.splits > 1;
       float* ws_col = nullptr;
       if (partial) {
@@ -486,6 +621,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  // No CTA of a cluster may retire while a peer can still read its staging
+  // buffer or signal its barriers.
+  if (p.cluster_split) cluster_sync_all();
   if (warp == 1) {
     if (*abort_flag && lane == 0) {
       // Give MMAs still in flight a bounded time to retire before TMEM goes away.
@@ -504,9 +642,27 @@ struct GemmPlan {
   int BN;
   int splits;
   int stages;
+  int cluster;   // 1: split-K inside a thread-block cluster (DSMEM reduction)
 };
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static size_t red_bytes_for(int BN, int cluster_split) {
+  return cluster_split ? static_cast<size_t>(kBM) * (BN + 4) * 4 : 0;
+}
+
+static size_t smem_bytes_for(int BN, int stages, int num_experts, int cluster_split = 0) {
+  return 1024 + static_cast<size_t>(stages) * (kBM * kRowBytes + BN * kRowBytes) +
+         red_bytes_for(BN, cluster_split) + (2 * stages + 7) * 8 + 16 + (num_experts + 2) * 4 + 64;
+}
+
+static int stages_for(int BN, int cluster_split) {
+  const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
+  int stages = static_cast<int>((226 * 1024 - 2048 - red_bytes_for(BN, cluster_split)) / stage_bytes);
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  return stages;
+}
 
 // Cost model used to choose the tile width and split-K factor.  All rates are
 // per SM; the model only has to rank candidates, not predict time.
@@ -518,9 +674,8 @@ static GemmPlan plan_gemm(int M, int N, int K, int elem_bytes, int sms, bool all
   const double sm_flops = (elem_bytes == 1 ? 2.8e15 : 1.4e15) / 148.0;
   const double hbm = 6.5e12;
   double best = 1e30;
-  GemmPlan bestp{128, 1, 4};
+  GemmPlan bestp{128, 1, 4, 0};
   for (int bn = 256; bn >= 32; bn -= 16) {
-    if (swiglu && (bn % 32) != 0) continue;
     if (bn > round_up(N, 16) && bn != 32) continue;
     const int n_blocks = (N + bn - 1) / bn;
     const long long tiles = static_cast<long long>(m_blocks) * n_blocks;
@@ -551,17 +706,8 @@ static GemmPlan plan_gemm(int M, int N, int K, int elem_bytes, int sms, bool all
       }
     }
   }
-  const int stage_bytes = kBM * kRowBytes + bestp.BN * kRowBytes;
-  int stages = (200 * 1024) / stage_bytes;
-  if (stages > 8) stages = 8;
-  if (stages < 2) stages = 2;
-  bestp.stages = stages;
+  bestp.stages = stages_for(bestp.BN, 0);
   return bestp;
-}
-
-static size_t smem_bytes_for(int BN, int stages, int num_experts) {
-  return 1024 + static_cast<size_t>(stages) * (kBM * kRowBytes + BN * kRowBytes) +
-         (2 * stages + 5) * 8 + 16 + (num_experts + 2) * 4 + 64;
 }
 
 static int next_pow2_cols(int x) {
@@ -580,28 +726,125 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams
     if (e != cudaSuccess) return -20;
     configured = true;
   }
+  if (p.cluster_split) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tw, p) == cudaSuccess ? 0 : -22;
+  }
   kern<<<grid, kThreads, smem, stream>>>(ta, tw, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// How many clusters of `size` CTAs of this kernel can be resident at once.
+static int max_active_clusters(int size, size_t smem) {
+  static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (size < 1 || size > 8) return 0;
+  if (cache[size] > 0) return cache[size];
+  auto kern = gemm_tcgen05_kernel<false, false>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(size * 148, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = sm_count() / size - (size > 2 ? 2 : 0);
+  }
+  cache[size] = n;
+  return n;
 }
 
 }  // namespace b200
 
 using namespace b200;
 
-// Workspace the caller must provide for a given problem: bytes of fp32
-// partials (zero when the plan does not split K) and number of int counters.
+// Small-M (weight-streaming) problems: split K across the CTAs of a cluster so
+// that every SM streams a slab of the weights, and reduce on chip.
+static bool plan_small_m(int M, int N, int K, int elem_bytes, bool allow_split, GemmPlan* out) {
+  const int k_iters = (K * elem_bytes + kRowBytes - 1) / kRowBytes;
+  const int m_blocks = (M + kBM - 1) / kBM;
+  const double sm_ingest = 110e9, hbm = 6.5e12;
+  double best = 1e30;
+  bool found = false;
+  for (int bn = 256; bn >= 64; bn -= 16) {
+    if (bn > ((N + 15) / 16) * 16) continue;
+    const int n_blocks = (N + bn - 1) / bn;
+    const int clusters = m_blocks * n_blocks;
+    const int max_sp = (allow_split && bn <= 128) ? 8 : 1;
+    for (int sp = 1; sp <= max_sp; ++sp) {
+      const int per = (k_iters + sp - 1) / sp;
+      if (sp > 1 && (per < 4 || (sp - 1) * per >= k_iters)) continue;
+      const int stages = stages_for(bn, sp > 1);
+      const int cap = sp > 1 ? max_active_clusters(sp, smem_bytes_for(bn, stages, 0, 1)) : sm_count();
+      if (cap <= 0) continue;
+      const int waves = (clusters + cap - 1) / cap;
+      const double rows_a = M < kBM ? M : kBM;
+      double t_cta = (rows_a + bn) * per * static_cast<double>(kRowBytes) / sm_ingest + 2.5e-6;
+      if (sp > 1) t_cta += 1.5e-6;
+      double t = waves * t_cta;
+      const double t_hbm = (static_cast<double>(N) * K * elem_bytes) / hbm;
+      if (t_hbm > t) t = t_hbm;
+      t += 0.1 * waves * t_cta;  // among HBM-bound candidates prefer the best SM fill
+      if (t < best * 0.999) {
+        best = t;
+        out->BN = bn;
+        out->splits = sp;
+        out->cluster = sp > 1 ? 1 : 0;
+        out->stages = stages;
+        found = true;
+      }
+    }
+  }
+  return found;
+}
+
+// Chooses tile width / split-K for a problem.  out_cluster = 1 means the splits run
+// as one thread-block cluster (no workspace needed); otherwise split-K uses the
+// caller's fp32 workspace (bytes) and per-tile counters.
 extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, int force_bn,
                                int force_splits, int* out_bn, int* out_splits,
-                               size_t* out_ws_bytes, int* out_counters) {
-  GemmPlan pl = plan_gemm(M, N, K, elem_bytes, sm_count(), true, swiglu != 0);
+                               size_t* out_ws_bytes, int* out_counters, int* out_cluster) {
+  GemmPlan pl = plan_gemm(M, N, K, elem_bytes, sm_count(), false, swiglu != 0);
+  pl.cluster = 0;
+  if (M <= 256 && force_bn <= 0 && force_splits <= 0) {
+    GemmPlan small = pl;
+    if (plan_small_m(M, N, K, elem_bytes, !swiglu, &small)) pl = small;
+  }
   if (force_bn > 0) pl.BN = force_bn;
-  if (force_splits > 0) pl.splits = force_splits;
+  if (force_splits > 0) {
+    pl.splits = force_splits;
+    // a forced split count runs as a cluster when it can
+    pl.cluster = (force_splits > 1 && force_splits <= 8 && pl.BN <= 128 && !swiglu) ? 1 : 0;
+  }
+  if (force_splits < 0) {  // negative: force the workspace (non-cluster) split-K with |splits|
+    pl.splits = -force_splits;
+    pl.cluster = 0;
+  }
   const int m_blocks = (M + kBM - 1) / kBM;
   const int n_blocks = (N + pl.BN - 1) / pl.BN;
   *out_bn = pl.BN;
   *out_splits = pl.splits;
+  *out_cluster = pl.cluster;
   *out_counters = m_blocks * n_blocks;
-  *out_ws_bytes = pl.splits > 1
+  *out_ws_bytes = (pl.splits > 1 && !pl.cluster)
                       ? static_cast<size_t>(pl.splits) * m_blocks * n_blocks * kBM * pl.BN * 4
                       : 0;
 }
@@ -609,17 +852,20 @@ extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, 
 // Dense GEMM.  A [M,K] (pitch lda), W [N,K] (pitch ldw), C [M,N or N/2 with
 // swiglu] (pitch ldc).  dtype_fp8 = 0: bf16 inputs; 1: e4m3 inputs (no scale
 // handling here; callers fold scales, see the block-scaled wrapper).
-// workspace / counters may be null when splits == 1.  Returns 0 on success.
+// workspace / counters may be null when splits == 1 or cluster_split == 1.
+// Returns 0 on success.
 extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
                          const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
                          int dtype_fp8, int out_fp32, int swiglu, int BN, int splits,
-                         void* workspace, int* counters, int* status, int max_ctas,
-                         cudaStream_t stream) {
+                         int cluster_split, void* workspace, int* counters, int* status,
+                         int max_ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
-  if (swiglu && ((BN % 32) != 0 || (N % 16) != 0 || splits != 1)) return -11;
-  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return -12;
+  if (swiglu && ((N % 16) != 0 || splits != 1)) return -11;
+  if (splits <= 1) cluster_split = 0;
+  if (cluster_split && (splits > 8 || BN > 128)) return -14;
+  if (splits > 1 && !cluster_split && (workspace == nullptr || counters == nullptr)) return -12;
   GemmParams p{};
   p.M = M;
   p.N = N;
@@ -628,12 +874,10 @@ extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias
   p.elem_bytes = eb;
   p.k_iters = (K * eb + kRowBytes - 1) / kRowBytes;
   p.splits = splits;
+  p.cluster_split = cluster_split;
   p.num_m_blocks = (M + kBM - 1) / kBM;
   p.num_n_blocks = (N + BN - 1) / BN;
-  const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
-  int stages = (200 * 1024) / stage_bytes;
-  if (stages > 8) stages = 8;
-  p.stages = stages;
+  p.stages = stages_for(BN, cluster_split);
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   p.tmem_cols = next_pow2_cols(2 * p.acc_stride);
   p.ldc = ldc;
@@ -654,11 +898,20 @@ extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias
   if (r) return r;
   r = make_tensormap_2d(&tw, dt, eb, W, N, K, ldw, BN, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
-  long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks * splits;
-  int grid = sm_count();
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (tiles < grid) grid = static_cast<int>(tiles);
-  const size_t smem = smem_bytes_for(BN, stages, 0);
+  const size_t smem = smem_bytes_for(BN, p.stages, 0, cluster_split);
+  int grid;
+  if (cluster_split) {
+    const long long clusters = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
+    int cap = max_active_clusters(splits, smem);
+    if (cap <= 0) return -15;
+    if (max_ctas > 0 && max_ctas / splits < cap) cap = max_ctas / splits > 0 ? max_ctas / splits : 1;
+    grid = static_cast<int>(clusters < cap ? clusters : cap) * splits;
+  } else {
+    const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks * splits;
+    grid = sm_count();
+    if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+    if (tiles < grid) grid = static_cast<int>(tiles);
+  }
   if (dtype_fp8) return launch<false, true>(ta, tw, p, grid, smem, stream);
   return launch<false, false>(ta, tw, p, grid, smem, stream);
 }
@@ -675,7 +928,7 @@ extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const in
   if (num_experts > kMaxExperts) return -13;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
-  if (swiglu && ((BN % 32) != 0 || (N % 16) != 0)) return -11;
+  if (swiglu && (N % 16) != 0) return -11;
   GemmParams p{};
   p.M = total_rows;
   p.N = N;
@@ -686,10 +939,9 @@ extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const in
   p.splits = 1;
   p.num_m_blocks = 0;
   p.num_n_blocks = (N + BN - 1) / BN;
-  const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
-  int stages = (200 * 1024) / stage_bytes;
-  if (stages > 8) stages = 8;
+  const int stages = stages_for(BN, 0);
   p.stages = stages;
+  p.cluster_split = 0;
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   p.tmem_cols = next_pow2_cols(2 * p.acc_stride);
   p.ldc = ldc;

@@ -275,14 +275,14 @@ class RowParallelLinear(LinearBase):
             self.y_transform = "AllReduce"
         self._create(self.in_local, out_features, device)
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                reduce: bool = True) -> torch.Tensor:
+        """``reduce=False`` returns this rank's partial sums; the caller then reduces them
+        itself, typically fused with the following residual add + RMSNorm."""
         x = apply_transform(x, self.x_transform, self.group)
         bias = self.bias if self.tp_rank == 0 else None
-        if self.tp_size == 1 or not self.reduce_results:
+        if self.tp_size == 1 or not self.reduce_results or not reduce:
             return self.quant_method.apply(self, x, bias, residual=residual)
-        fused = _try_fused_gemm_reduce(self, x, bias, residual)
-        if fused is not None:
-            return fused
         y = self.quant_method.apply(self, x, bias)
         y = apply_transform(y, self.y_transform, self.group)
         if residual is not None:
@@ -294,16 +294,6 @@ class RowParallelLinear(LinearBase):
             param.data.copy_(loaded.to(param.dtype))
             return
         _copy_sharded(param, loaded, 1, self.tp_rank, self.tp_size)
-
-
-def _try_fused_gemm_reduce(layer: RowParallelLinear, x, bias, residual):
-    """GEMM with the all-reduce done by this library's peer-memory kernels."""
-    symm = layer.group.comm.symm
-    if symm is None or not x.is_cuda or layer.y_transform != "AllReduce":
-        return None
-    if not isinstance(layer.quant_method, UnquantizedLinearMethod):
-        return None
-    return symm.gemm_all_reduce(x, layer.weight, bias, residual)
 
 
 def _copy_sharded(param: nn.Parameter, loaded: torch.Tensor, dim: int, rank: int, world: int) -> None:

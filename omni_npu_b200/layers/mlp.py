@@ -32,9 +32,10 @@ class FusedMLP(nn.Module):
                                            group=group, reduce_results=reduce_results)
         self.act = SiluAndMul()
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                reduce: bool = True) -> torch.Tensor:
         if self.fuse_swiglu:
             h = self.gate_up_proj(x, fuse_swiglu=True)
         else:
             h = self.act(self.gate_up_proj(x))
-        return self.down_proj(h, residual=residual)
+        return self.down_proj(h, residual=residual, reduce=reduce)

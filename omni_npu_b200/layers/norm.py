@@ -38,6 +38,22 @@ class RMSNorm(nn.Module):
         return y, residual
 
 
+def reduce_add_rms_norm(norm: RMSNorm, x_partial: torch.Tensor, residual: torch.Tensor, group):
+    """``residual += all_reduce(x_partial)``; returns (RMSNorm(residual), residual).
+
+    This is the tail of every row-parallel projection (o_proj, down_proj).  With
+    symmetric memory attached to the group it runs as one peer-memory kernel
+    (GEMM -> all-reduce + residual + RMSNorm); otherwise as an all-reduce followed
+    by the fused add+norm kernel."""
+    if group.world_size == 1:
+        return norm(x_partial, residual)
+    symm = group.comm.symm
+    if symm is not None and symm.can_all_reduce(x_partial):
+        y = symm.all_reduce_add_rms_norm(x_partial, residual, norm.weight, norm.eps)
+        return y, residual
+    return norm(group.all_reduce(x_partial), residual)
+
+
 class LayerNorm(nn.Module):
     """Plain LayerNorm in fp32 (used by the sparse-attention indexer key path)."""
 

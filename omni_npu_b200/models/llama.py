@@ -16,7 +16,7 @@ from ..config import EngineConfig, ModelConfig
 from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
 from ..layers.linear import QKVParallelLinear, RowParallelLinear
 from ..layers.mlp import FusedMLP
-from ..layers.norm import RMSNorm
+from ..layers.norm import RMSNorm, reduce_add_rms_norm
 from ..layers.rope import get_rope
 from ..parallel import state as pstate
 from .utils import load_stacked_weights
@@ -42,14 +42,14 @@ class LlamaAttention(nn.Module):
                                  if self.rotary.mscale != 1.0 else cfg.head_dim ** -0.5,
                                  cfg.rotary_dim, cfg.rope_neox, cfg.sliding_window)
 
-    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden: torch.Tensor, reduce: bool = True) -> torch.Tensor:
         q, k, v = self.qkv_proj(hidden)
         if self.qk_norm:
             t = q.shape[0]
             q = self.q_norm(q.reshape(-1, self.head_dim)).view(t, -1)
             k = self.k_norm(k.reshape(-1, self.head_dim)).view(t, -1)
         o = self.attn(q, k, v, self.rotary.cos_sin_cache)
-        return self.o_proj(o)
+        return self.o_proj(o, reduce=reduce)
 
 
 class LlamaDecoderLayer(nn.Module):
@@ -60,16 +60,22 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
         self.mlp = FusedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.dtype, device,
                             prefix=f"{prefix}.mlp")
+        self.tp_group = pstate.get_tp_group()
 
     def forward(self, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        """``hidden`` is the previous layer's MLP output BEFORE its tensor-parallel
+        reduction (or the embeddings for the first layer); the reduction is fused
+        with this layer's residual add + input norm.  The returned ``hidden`` is
+        likewise un-reduced."""
+        tp = self.tp_group
         if residual is None:
             residual = hidden
             hidden = self.input_layernorm(hidden)
         else:
-            hidden, residual = self.input_layernorm(hidden, residual)
-        hidden = self.self_attn(hidden)
-        hidden, residual = self.post_attention_layernorm(hidden, residual)
-        hidden = self.mlp(hidden)
+            hidden, residual = reduce_add_rms_norm(self.input_layernorm, hidden, residual, tp)
+        hidden = self.self_attn(hidden, reduce=False)
+        hidden, residual = reduce_add_rms_norm(self.post_attention_layernorm, hidden, residual, tp)
+        hidden = self.mlp(hidden, reduce=False)
         return hidden, residual
 
 
@@ -87,7 +93,7 @@ class LlamaModel(nn.Module):
         residual = None
         for layer in self.layers:
             hidden, residual = layer(hidden, residual)
-        hidden, _ = self.norm(hidden, residual)
+        hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, pstate.get_tp_group())
         return hidden
 
 

@@ -159,7 +159,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          swiglu: bool = False, bn: int = 0, splits: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """``a[M,K] @ w[N,K].T`` (+bias, +residual).  bf16 or float8_e4m3fn inputs,
     fp32 accumulation, bf16 (default) or fp32 output.  ``swiglu`` fuses
-    silu(gate)*up for weights laid out by :func:`ref.interleave_gate_up`."""
+    silu(gate)*up for weights laid out by :func:`ref.interleave_gate_up`.
+    ``splits`` > 1 forces split-K (as a thread-block cluster when it fits), a
+    negative value forces the workspace variant with |splits| slices."""
     if not a.is_cuda:
         return ref.gemm(a, w, bias, residual, out_dtype, swiglu)
     C = _C()
@@ -171,13 +173,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
     if plan is None:
         plan = C.gemm_plan(m, n, k, a.dtype.itemsize, swiglu, bn, 1 if swiglu else splits)
         st.plans[key] = plan
-    pbn, psplits, ws_bytes, ncnt = plan
+    pbn, psplits, ws_bytes, ncnt, cluster = plan
     ws = cnt = None
-    if psplits > 1:
+    if psplits > 1 and not cluster:
         ws, cnt = st.gemm_workspace(torch.cuda.current_stream(a.device).cuda_stream, ws_bytes, ncnt)
     _count(1)
-    return C.gemm(a, w, bias, residual, out_dtype == torch.float32, swiglu, pbn, psplits, ws, cnt,
-                  st.status, max_ctas)
+    return C.gemm(a, w, bias, residual, out_dtype == torch.float32, swiglu, pbn, psplits,
+                  bool(cluster), ws, cnt, st.status, max_ctas)
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,

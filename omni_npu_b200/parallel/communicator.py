@@ -36,6 +36,12 @@ class B200Communicator:
         self.symm = None            # SymmetricMemory pool (attached lazily on CUDA)
         self.ep_buffers = None      # expert-parallel dispatch/combine state
 
+    def _is_gloo(self) -> bool:
+        try:
+            return dist.get_backend(self.device_group) == "gloo"
+        except Exception:
+            return False
+
     # ------------------------------------------------------------ basic ops
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
@@ -51,11 +57,14 @@ class B200Communicator:
         if dim < 0:
             dim += x.dim()
         xc = x.contiguous()
-        out = torch.empty((self.world_size,) + tuple(xc.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, xc, group=self.device_group)
+        if dim == 0 and self.symm is not None and self.symm._ok(xc) and xc.numel() * 2 <= self.symm.half_bytes:
+            return self.symm.all_gather(xc)
+        flat = torch.empty((self.world_size * xc.shape[0],) + tuple(xc.shape[1:]), dtype=x.dtype,
+                           device=x.device) if xc.dim() > 0 else torch.empty(self.world_size, dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, xc if xc.dim() > 0 else xc.view(1), group=self.device_group)
         if dim == 0:
-            return out.reshape((self.world_size * x.shape[0],) + tuple(x.shape[1:]))
-        out = out.movedim(0, dim)
+            return flat
+        out = flat.view((self.world_size,) + tuple(xc.shape)).movedim(0, dim)
         shape = list(x.shape)
         shape[dim] *= self.world_size
         return out.reshape(shape)
@@ -68,8 +77,15 @@ class B200Communicator:
         xm = x.movedim(dim, 0).contiguous()
         assert xm.shape[0] % self.world_size == 0
         chunk = xm.shape[0] // self.world_size
-        out = torch.empty((chunk,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.reduce_scatter_tensor(out, xm, group=self.device_group)
+        if self.symm is not None and self.symm._ok(xm) and xm.numel() * 2 <= self.symm.half_bytes:
+            return self.symm.reduce_scatter(xm).movedim(0, dim)
+        if self._is_gloo():
+            # gloo has no reduce-scatter: reduce everything, keep this rank's chunk
+            dist.all_reduce(xm, group=self.device_group)
+            out = xm[self.rank_in_group * chunk:(self.rank_in_group + 1) * chunk].clone()
+        else:
+            out = torch.empty((chunk,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, xm, group=self.device_group)
         return out.movedim(0, dim)
 
     def all_gatherv(self, x: Union[torch.Tensor, List[torch.Tensor]], dim: int = 0,
@@ -83,9 +99,15 @@ class B200Communicator:
             return self.all_gather(x, dim)
         assert dim == 0, "ragged all-gather is along the leading dimension"
         assert x.shape[0] == sizes[self.rank_in_group]
-        outs = [torch.empty((s,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device) for s in sizes]
-        dist.all_gather(outs, x.contiguous(), group=self.device_group)
-        return torch.cat(outs, dim=0)
+        # pad every contribution to the largest one, gather once, trim
+        m = max(sizes)
+        padded = x.contiguous()
+        if padded.shape[0] < m:
+            pad = torch.zeros((m - padded.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            padded = torch.cat([padded, pad], dim=0)
+        flat = torch.empty((self.world_size * m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, padded, group=self.device_group)
+        return torch.cat([flat[r * m: r * m + s] for r, s in enumerate(sizes)], dim=0)
 
     def reduce_scatterv(self, x: torch.Tensor, dim: int = 0,
                         sizes: Optional[Sequence[int]] = None) -> torch.Tensor:
@@ -94,7 +116,11 @@ class B200Communicator:
         if sizes is None:
             return self.reduce_scatter(x, dim)
         assert dim == 0
-        chunks = list(torch.split(x.contiguous(), list(sizes), dim=0))
+        xc = x.contiguous()
+        if self._is_gloo():
+            dist.all_reduce(xc, group=self.device_group)
+            return torch.split(xc, list(sizes), dim=0)[self.rank_in_group].clone()
+        chunks = list(torch.split(xc, list(sizes), dim=0))
         out = torch.empty_like(chunks[self.rank_in_group])
         dist.reduce_scatter(out, chunks, group=self.device_group)
         return out
@@ -139,7 +165,19 @@ class B200Communicator:
             elif scatter_sizes is not None and scatter_dim == gather_dim:
                 raise ValueError("gather_sizes required for ragged exchange along one dim")
             outs.append(torch.empty(shape, dtype=x.dtype, device=x.device))
-        dist.all_to_all(outs, ins, group=self.device_group)
+        if self._is_gloo():
+            # gloo has no all_to_all: pairwise exchange
+            reqs = []
+            for r in range(self.world_size):
+                if r == self.rank_in_group:
+                    outs[r].copy_(ins[r])
+                    continue
+                reqs.append(dist.isend(ins[r], self.ranks[r], group=self.device_group))
+                reqs.append(dist.irecv(outs[r], self.ranks[r], group=self.device_group))
+            for q in reqs:
+                q.wait()
+        else:
+            dist.all_to_all(outs, ins, group=self.device_group)
         return torch.cat(outs, dim=gather_dim)
 
     def all_to_all_single(self, x: torch.Tensor, output_split_sizes=None,
@@ -148,6 +186,20 @@ class B200Communicator:
             return x
         n_out = sum(output_split_sizes) if output_split_sizes is not None else x.shape[0]
         out = torch.empty((n_out,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if self._is_gloo():
+            w = self.world_size
+            ins = list(torch.split(x.contiguous(), list(input_split_sizes) if input_split_sizes else x.shape[0] // w))
+            outs = list(torch.split(out, list(output_split_sizes) if output_split_sizes else n_out // w))
+            reqs = []
+            for r in range(w):
+                if r == self.rank_in_group:
+                    outs[r].copy_(ins[r])
+                    continue
+                reqs.append(dist.isend(ins[r].contiguous(), self.ranks[r], group=self.device_group))
+                reqs.append(dist.irecv(outs[r], self.ranks[r], group=self.device_group))
+            for q in reqs:
+                q.wait()
+            return out
         dist.all_to_all_single(out, x.contiguous(), output_split_sizes, input_split_sizes,
                                group=self.device_group)
         return out

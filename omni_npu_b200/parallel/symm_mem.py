@@ -1,0 +1,205 @@
+"""Symmetric (peer-mapped) device memory for a process group and the collectives
+built on it.
+
+Every rank allocates one data buffer and one signal pad with ``cudaMalloc``,
+exports CUDA IPC handles, exchanges them over the group's CPU (gloo) side and
+maps every peer's buffers.  The kernels in ``csrc/comm/symm_collectives.cu``
+then read and write peer memory directly over NVLink / NVSwitch:
+
+* ``all_reduce``  one-shot for small messages, two-shot for large ones, with an
+  optional fused ``residual += x; RMSNorm`` tail (the op that follows every
+  row-parallel projection in a decoder layer);
+* ``all_gather`` / ``reduce_scatter`` along dim 0 for the token-sharded
+  (sequence-parallel) residual stream.
+
+NCCL stays the fallback for anything these kernels do not cover (other dtypes,
+messages larger than the buffer, point-to-point).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..logger import logger
+
+_LIB: Optional[ctypes.CDLL] = None
+
+
+def _lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        ops.load_extension(required=True)
+        lib = ctypes.CDLL(str(Path(__file__).resolve().parent.parent / "_C.so"))
+        vp, ci, sz, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_longlong
+        lib.b200_symm_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
+        lib.b200_symm_alloc.restype = ci
+        lib.b200_symm_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        lib.b200_symm_open.restype = ci
+        lib.b200_symm_close.argtypes = [vp]
+        lib.b200_symm_free.argtypes = [vp]
+        lib.b200_symm_signal_words.restype = ci
+        pp = ctypes.POINTER(vp)
+        lib.b200_symm_all_reduce.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, ci, ctypes.c_float,
+                                             ci, vp, vp, vp]
+        lib.b200_symm_all_reduce.restype = ci
+        lib.b200_symm_all_gather.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, vp]
+        lib.b200_symm_all_gather.restype = ci
+        lib.b200_symm_reduce_scatter.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, vp]
+        lib.b200_symm_reduce_scatter.restype = ci
+        _LIB = lib
+    return _LIB
+
+
+class SymmetricMemory:
+    ONE_SHOT_FUSED_MAX_BYTES = 2 << 20      # above this the fused one-shot tail is not worth it
+
+    def __init__(self, group, device: torch.device, half_bytes: int = 80 << 20) -> None:
+        self.group = group
+        self.device = device
+        self.world = group.world_size
+        self.rank = group.rank_in_group
+        self.half_bytes = int(half_bytes)
+        lib = _lib()
+        torch.cuda.set_device(device)
+        self._own = []
+        self._opened = []
+
+        def alloc(nbytes: int):
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            rc = lib.b200_symm_alloc(nbytes, ctypes.byref(ptr), handle)
+            if rc != 0:
+                raise RuntimeError(f"symmetric memory allocation of {nbytes} bytes failed ({rc})")
+            self._own.append(ptr)
+            return ptr, handle.raw
+
+        data_ptr, data_h = alloc(2 * self.half_bytes)
+        sig_ptr, sig_h = alloc(lib.b200_symm_signal_words() * 4)
+        everyone = group.all_gather_object((data_h, sig_h))
+        vp = ctypes.c_void_p
+        self.data_ptrs = (vp * 8)()
+        self.signal_ptrs = (vp * 8)()
+        for r, (dh, sh) in enumerate(everyone):
+            if r == self.rank:
+                self.data_ptrs[r], self.signal_ptrs[r] = data_ptr.value, sig_ptr.value
+                continue
+            for handle, table in ((dh, self.data_ptrs), (sh, self.signal_ptrs)):
+                p = vp()
+                rc = lib.b200_symm_open(handle, ctypes.byref(p))
+                if rc != 0:
+                    raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r} ({rc}); "
+                                       "peer access between the GPUs is required")
+                table[r] = p.value
+                self._opened.append(p)
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        self.status = ops.device_state(device).status
+        torch.cuda.synchronize(device)
+        group.barrier()
+        logger.info("symmetric memory ready: rank %d/%d, %d MiB per rank", self.rank, self.world,
+                    (2 * self.half_bytes) >> 20)
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _ok(self, x: torch.Tensor) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0
+                and x.numel() > 0)
+
+    def can_all_reduce(self, x: torch.Tensor) -> bool:
+        return self._ok(x) and x.numel() * 2 * (1 + 1.0 / self.world) + 64 <= self.half_bytes
+
+    # --------------------------------------------------------------- collectives
+    def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = 0) -> torch.Tensor:
+        """Sum over the group.  Returns a new tensor (``out`` if given)."""
+        out = torch.empty_like(x) if out is None else out
+        rc = _lib().b200_symm_all_reduce(self.data_ptrs, self.signal_ptrs, self.world, self.rank,
+                                         self.half_bytes, x.data_ptr(), out.data_ptr(), x.numel(), None,
+                                         None, 0, 0.0, mode, self.done.data_ptr(),
+                                         self.status.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"symm all_reduce failed ({rc})")
+        ops._count(1)
+        return out
+
+    def all_reduce_add_rms_norm(self, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                                eps: float) -> torch.Tensor:
+        """residual += all_reduce(x) (in place); returns RMSNorm(residual) * weight.
+        Small messages run as ONE kernel; large ones as two-shot reduce + add/norm."""
+        h = x.shape[-1]
+        if (x.numel() * 2 <= self.ONE_SHOT_FUSED_MAX_BYTES and h <= 16384 and residual.is_contiguous()
+                and weight.is_contiguous()):
+            out = torch.empty_like(x)
+            rc = _lib().b200_symm_all_reduce(self.data_ptrs, self.signal_ptrs, self.world, self.rank,
+                                             self.half_bytes, x.data_ptr(), out.data_ptr(), x.numel(),
+                                             residual.data_ptr(), weight.data_ptr(), h, eps, 1,
+                                             self.done.data_ptr(), self.status.data_ptr(), self._stream())
+            if rc != 0:
+                raise RuntimeError(f"symm fused all_reduce failed ({rc})")
+            ops._count(1)
+            return out
+        y = self.all_reduce(x)
+        return ops.fused_add_rms_norm(y, residual, weight, eps)
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """Concatenate every rank's ``x`` along dim 0."""
+        out = torch.empty((self.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        rc = _lib().b200_symm_all_gather(self.data_ptrs, self.signal_ptrs, self.world, self.rank,
+                                         self.half_bytes, x.data_ptr(), out.data_ptr(), x.numel(),
+                                         self.done.data_ptr(), self.status.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"symm all_gather failed ({rc})")
+        ops._count(1)
+        return out
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over the group, rank r keeps rows [r*n, (r+1)*n) of dim 0."""
+        assert x.shape[0] % self.world == 0
+        n = x.shape[0] // self.world
+        out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        rc = _lib().b200_symm_reduce_scatter(self.data_ptrs, self.signal_ptrs, self.world, self.rank,
+                                             self.half_bytes, x.data_ptr(), out.data_ptr(), out.numel(),
+                                             self.done.data_ptr(), self.status.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"symm reduce_scatter failed ({rc})")
+        ops._count(1)
+        return out
+
+    def gemm_all_reduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual) -> Optional[torch.Tensor]:
+        """Row-parallel projection: local GEMM, then the peer-memory all-reduce."""
+        y = ops.gemm(x, w, bias)
+        if not self.can_all_reduce(y):
+            return None
+        y = self.all_reduce(y)
+        if residual is not None:
+            y = y + residual
+        return y
+
+    def close(self) -> None:
+        lib = _lib()
+        try:
+            torch.cuda.synchronize(self.device)
+        except Exception:
+            pass
+        for p in self._opened:
+            lib.b200_symm_close(p)
+        for p in self._own:
+            lib.b200_symm_free(p)
+        self._opened, self._own = [], []
+
+
+def attach_symmetric_memory(group, device: torch.device, half_bytes: Optional[int] = None):
+    """Create the group's symmetric memory (idempotent) and hook it into its communicator."""
+    if group.world_size <= 1 or group.comm.symm is not None:
+        return group.comm.symm
+    if group.world_size > 8:
+        logger.warning("symmetric-memory collectives support up to 8 ranks; using NCCL")
+        return None
+    hb = half_bytes or int(os.environ.get("OMNI_B200_SYMM_HALF_MB", "80")) << 20
+    group.comm.symm = SymmetricMemory(group, device, hb)
+    return group.comm.symm

@@ -1,0 +1,161 @@
+"""Worker entry for multi-process tests (CPU/gloo and multi-GPU/NCCL).
+
+    python tests/dist_worker.py <task> <rank> <world> <port> <workdir> [device]
+
+Each task writes ``<workdir>/result_<rank>.json``.
+"""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch  # noqa: E402
+
+
+def setup(rank, world, port, device_kind):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from omni_npu_b200.parallel import state
+    if device_kind == "cuda":
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+    else:
+        dev = torch.device("cpu")
+    state.init_distributed(dev, timeout_s=120)
+    return dev, state
+
+
+def task_comm(rank, world, port, workdir, device_kind):
+    """Communicator semantics against closed-form expectations."""
+    dev, state = setup(rank, world, port, device_kind)
+    state.init_model_parallel(tp=world, device=dev)
+    g = state.get_tp_group()
+    res = {}
+    x = torch.full((4, 6), float(rank + 1), device=dev)
+    res["all_reduce"] = g.all_reduce(x.clone()).flatten()[0].item()
+    ag = g.all_gather(torch.full((2, 3), float(rank), device=dev), dim=0)
+    res["all_gather0"] = ag[:, 0].tolist()
+    ag1 = g.all_gather(torch.full((2, 3), float(rank), device=dev), dim=-1)
+    res["all_gather_last_shape"] = list(ag1.shape)
+    res["all_gather_last_row"] = ag1[0].tolist()
+    rs = g.reduce_scatter(torch.arange(world * 2, dtype=torch.float32, device=dev).view(world * 2, 1).repeat(1, 2), dim=0)
+    res["reduce_scatter"] = rs[:, 0].tolist()
+    sizes = [r + 1 for r in range(world)]
+    agv = g.all_gatherv(torch.full((rank + 1, 2), float(rank), device=dev), dim=0, sizes=sizes)
+    res["all_gatherv"] = agv[:, 0].tolist()
+    rsv = g.reduce_scatterv(torch.ones(sum(sizes), 2, device=dev), dim=0, sizes=sizes)
+    res["reduce_scatterv_shape"] = list(rsv.shape)
+    res["reduce_scatterv_val"] = rsv[0, 0].item()
+    a2a = g.comm.all_to_all(torch.arange(world * 2, dtype=torch.float32, device=dev).view(world * 2, 1) + 100 * rank,
+                            scatter_dim=0, gather_dim=0)
+    res["all_to_all"] = a2a[:, 0].tolist()
+    gat = g.comm.gather(torch.full((1, 2), float(rank), device=dev), dst=0, dim=0)
+    res["gather"] = gat[:, 0].tolist() if gat is not None else None
+    if world >= 2:
+        if rank == 0:
+            g.send(torch.tensor([7.0, 8.0], device=dev), dst=1)
+        elif rank == 1:
+            res["recv"] = g.recv((2,), torch.float32, src=0).tolist()
+    res["bcast_obj"] = g.broadcast_object({"k": rank} if rank == 0 else None, src=0)
+    lg = state.register_layer_group("self_attn.o_proj", world)
+    res["layer_group"] = [lg.world_size, lg.rank_in_group]
+    g.barrier()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.destroy_distributed()
+
+
+def task_tp_engine(rank, world, port, workdir, device_kind):
+    """Tiny Llama with tensor parallelism; rank 0 writes the generated tokens."""
+    dev, state = setup(rank, world, port, device_kind)
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.engine.llm import LLM
+    model_dir = os.path.join(workdir, "model")
+    prompts = json.load(open(os.path.join(workdir, "prompts.json")))
+    kw = dict(device=device_kind, tensor_parallel_size=world, max_num_seqs=4, max_num_batched_tokens=64,
+              max_model_len=256, block_size=16, num_gpu_blocks=64)
+    if device_kind == "cpu":
+        kw["dtype"] = "float32"
+    llm = LLM(model=model_dir, **kw)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    json.dump({"tokens": [o.output_token_ids for o in outs]},
+              open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.get_world_group().barrier()
+    state.destroy_distributed()
+
+
+def task_symm(rank, world, port, workdir, device_kind):
+    """Peer-memory collectives against NCCL results."""
+    dev, state = setup(rank, world, port, "cuda")
+    state.init_model_parallel(tp=world, device=dev)
+    import torch.distributed as dist
+    from omni_npu_b200 import ops
+    from omni_npu_b200.parallel.symm_mem import attach_symmetric_memory
+    g = state.get_tp_group()
+    symm = attach_symmetric_memory(g, dev, half_bytes=96 << 20)
+    res = {"max_err": {}}
+    torch.manual_seed(100 + rank)
+    for name, shape, mode in (("small_1shot", (128, 4096), 1), ("small_2shot", (128, 4096), 2),
+                              ("odd", (7, 1032), 0), ("large_auto", (4096, 4096), 0),
+                              ("large_1shot", (2048, 4096), 1)):
+        x = torch.randn(*shape, device=dev, dtype=torch.bfloat16)
+        want = x.float().clone()
+        dist.all_reduce(want, group=g.device_group)
+        for rep in range(3):       # repeated calls exercise the alternating halves
+            got = symm.all_reduce(x, mode=mode)
+        res["max_err"][name] = (got.float() - want).abs().max().item()
+    # fused all-reduce + residual + RMSNorm
+    x = torch.randn(96, 4096, device=dev, dtype=torch.bfloat16)
+    resid = torch.randn(96, 4096, device=dev, dtype=torch.bfloat16)
+    dist.broadcast(resid, src=0, group=g.device_group)
+    w = torch.randn(4096, device=dev, dtype=torch.bfloat16)
+    dist.broadcast(w, src=0, group=g.device_group)
+    red = x.clone()
+    dist.all_reduce(red, group=g.device_group)
+    r_ref = resid.clone()
+    y_ref = ops.fused_add_rms_norm(red, r_ref, w, 1e-6)
+    r_got = resid.clone()
+    y_got = symm.all_reduce_add_rms_norm(x, r_got, w, 1e-6)
+    res["max_err"]["fused_norm_out"] = (y_got.float() - y_ref.float()).abs().max().item()
+    res["max_err"]["fused_norm_res"] = (r_got.float() - r_ref.float()).abs().max().item()
+    # all-gather / reduce-scatter
+    x = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
+    ag_ref = torch.empty(world * 64, 512, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(ag_ref, x, group=g.device_group)
+    res["max_err"]["all_gather"] = (symm.all_gather(x).float() - ag_ref.float()).abs().max().item()
+    xs = torch.randn(world * 32, 512, device=dev, dtype=torch.bfloat16)
+    rs_ref = torch.empty(32, 512, device=dev, dtype=torch.float32)
+    dist.reduce_scatter_tensor(rs_ref, xs.float(), group=g.device_group)
+    res["max_err"]["reduce_scatter"] = (symm.reduce_scatter(xs).float() - rs_ref).abs().max().item()
+    # timing: decode-sized all-reduce, ours vs NCCL
+    x = torch.randn(128, 4096, device=dev, dtype=torch.bfloat16)
+    def timeit(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+    res["us_symm_1MiB"] = timeit(lambda: symm.all_reduce(x))
+    res["us_nccl_1MiB"] = timeit(lambda: dist.all_reduce(x, group=g.device_group))
+    big = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
+    res["us_symm_64MiB"] = timeit(lambda: symm.all_reduce(big), 10)
+    res["us_nccl_64MiB"] = timeit(lambda: dist.all_reduce(big, group=g.device_group), 10)
+    torch.cuda.synchronize()
+    ops.check_status()
+    g.barrier()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.destroy_distributed()
+
+
+TASKS = {"comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
+
+if __name__ == "__main__":
+    task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+    device_kind = sys.argv[6] if len(sys.argv) > 6 else "cpu"
+    TASKS[task](rank, world, port, workdir, device_kind)

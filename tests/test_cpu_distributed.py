@@ -1,0 +1,44 @@
+"""Multi-process tests on CPU (gloo, world size 2): communicator semantics and a
+tensor-parallel engine run compared with the plain PyTorch model."""
+import json
+import os
+import tempfile
+
+import torch
+
+import reference_llama as refm
+from dist_utils import run_ranks
+from omni_npu_b200.config import tiny_llama
+from test_cpu_plumbing import _save
+
+
+def test_communicator_semantics_two_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        r0, r1 = run_ranks("comm", 2, d)
+    assert r0["all_reduce"] == 3.0 and r1["all_reduce"] == 3.0
+    assert r0["all_gather0"] == [0.0, 0.0, 1.0, 1.0]
+    assert r0["all_gather_last_shape"] == [2, 6] and r0["all_gather_last_row"] == [0, 0, 0, 1, 1, 1]
+    assert r0["reduce_scatter"] == [0.0, 2.0] and r1["reduce_scatter"] == [4.0, 6.0]
+    assert r1["all_gatherv"] == [0.0, 1.0, 1.0]
+    assert r0["reduce_scatterv_shape"] == [1, 2] and r1["reduce_scatterv_shape"] == [2, 2]
+    assert r0["reduce_scatterv_val"] == 2.0
+    assert r0["all_to_all"] == [0.0, 1.0, 100.0, 101.0] and r1["all_to_all"] == [2.0, 3.0, 102.0, 103.0]
+    assert r0["gather"] == [0.0, 1.0] and r1["gather"] is None
+    assert r1["recv"] == [7.0, 8.0]
+    assert r1["bcast_obj"] == {"k": 0}
+    assert r0["layer_group"] == [2, 0] and r1["layer_group"] == [2, 1]
+
+
+def test_tensor_parallel_engine_matches_plain_pytorch():
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=3)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 33, 9)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        res = run_ranks("tp_engine", 2, d)
+    for p, toks in zip(prompts, res[0]["tokens"]):
+        assert toks == refm.greedy_generate(weights, cfg, p, 12)
+    assert res[0]["tokens"] == res[1]["tokens"]

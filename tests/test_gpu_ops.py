@@ -34,7 +34,8 @@ def test_gemm_bf16(m, n, k):
     _close(out, want, atol=2e-2 * math.sqrt(k / 64), rtol=2e-2)
 
 
-@pytest.mark.parametrize("bn,splits", [(32, 1), (64, 2), (112, 4), (128, 3), (208, 1), (256, 1), (256, 8)])
+@pytest.mark.parametrize("bn,splits", [(32, 1), (64, 2), (112, 4), (128, 3), (208, 1), (256, 1), (256, 8),
+                                       (64, -2), (112, -4), (128, 8), (96, 5), (16, 7)])
 def test_gemm_tile_widths_and_split_k(bn, splits):
     torch.manual_seed(1)
     m, n, k = 200, 1000, 4096
@@ -47,6 +48,19 @@ def test_gemm_tile_widths_and_split_k(bn, splits):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 4096, 4096), (64, 6144, 4096), (1, 4096, 14336), (100, 1000, 4104)])
+def test_gemm_small_m_default_plan(m, n, k):
+    """Decode-shaped problems take the cluster split-K path by default."""
+    torch.manual_seed(5)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    out = ops.gemm(a, w, bias, res)
+    _close(out, ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.2, 2e-2)
+    assert torch.equal(out, ops.gemm(a, w, bias, res))
+
+
 def test_gemm_epilogues():
     torch.manual_seed(2)
     m, n, k = 300, 768, 1024
@@ -55,7 +69,8 @@ def test_gemm_epilogues():
     bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
     res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
     _close(ops.gemm(a, w, bias, res), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
-    _close(ops.gemm(a, w, bias, res, splits=2), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
+    _close(ops.gemm(a, w, bias, res, splits=2, bn=128), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
+    _close(ops.gemm(a, w, bias, res, splits=-2), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
     o32 = ops.gemm(a, w, out_dtype=torch.float32)
     assert o32.dtype == torch.float32
     _close(o32, ref.gemm(a.cpu(), w.cpu(), out_dtype=torch.float32), 2e-2, 1e-2)
