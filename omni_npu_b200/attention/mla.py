@@ -1,0 +1,202 @@
+"""Multi-head latent attention (DeepSeek V2 / V3 family) over a paged latent cache.
+
+Cache row per token: ``[RMSNorm(c_kv) (kv_lora_rank) | RoPE(k_pe) (qk_rope_head_dim)]``
+written by one fused kernel.  Two compute paths, as in the reference
+(omni_npu/attention/backends/mla.py:452-616 prefill, :695-804 decode;
+omni_npu/v1/layers/attention/npu_mla.py:169-348):
+
+* prefill  (non-absorbed): the latent rows of every sequence (cached context
+  included, so chunked prefill needs no separate merge pass) are up-projected
+  with ``kv_b_proj`` to per-head K (nope|rope, 192) and V (128) and run through
+  the variable-length attention kernel.
+* decode   (absorbed): q_nope is folded through W_UK into the latent space, one
+  MQA pass over the latent cache yields [N, 512] per token, W_UV maps it back.
+
+``MLABackend`` carries the cache-shape bookkeeping the model runner needs.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..layers.linear import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear
+from ..layers.norm import RMSNorm
+from ..layers.rope import get_rope, yarn_get_mscale
+from ..parallel import state as pstate
+from .metadata import AttentionMetadata, get_forward_context
+
+
+class MLABackend:
+    name = "B200_MLA"
+
+    @staticmethod
+    def get_name() -> str:
+        return MLABackend.name
+
+    @staticmethod
+    def get_kv_cache_shape(num_blocks: int, block_size: int, kv_lora_rank: int, rope_dim: int):
+        return (num_blocks, block_size, kv_lora_rank + rope_dim)
+
+    @staticmethod
+    def allocate_kv_cache(num_blocks, block_size, kv_lora_rank, rope_dim, dtype, device):
+        return torch.zeros(MLABackend.get_kv_cache_shape(num_blocks, block_size, kv_lora_rank, rope_dim),
+                           dtype=dtype, device=device)
+
+    @staticmethod
+    def bytes_per_block(block_size, kv_lora_rank, rope_dim, dtype) -> int:
+        return block_size * (kv_lora_rank + rope_dim) * dtype.itemsize
+
+
+def kv_slots_for_sequences(md: AttentionMetadata, block_size: int, total_kv: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """For a prefill step: cache slot of every kv token of every sequence, laid out
+    sequence after sequence, plus (seq id, position) of each.  Device-side only."""
+    dev = md.seq_lens.device
+    lens = md.seq_lens[: md.num_seqs].long()
+    seq_id = torch.repeat_interleave(torch.arange(md.num_seqs, device=dev), lens, output_size=total_kv)
+    starts = torch.cumsum(lens, 0) - lens
+    pos = torch.arange(total_kv, device=dev) - starts[seq_id]
+    blk = md.block_tables[seq_id, pos // block_size].long()
+    return blk * block_size + pos % block_size, seq_id, pos
+
+
+class MLAAttention(nn.Module):
+    """Attention block of a DeepSeek-style layer: projections, cache write, attention, o_proj."""
+
+    def __init__(self, cfg, layer_idx: int, device, prefix: str, quant_factory=None) -> None:
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.hidden = cfg.hidden_size
+        tp = pstate.get_tp_group()
+        self.tp_size = tp.world_size
+        assert cfg.num_heads % self.tp_size == 0
+        self.num_heads = cfg.num_heads // self.tp_size
+        self.q_lora_rank, self.kv_lora_rank = cfg.q_lora_rank, cfg.kv_lora_rank
+        self.nope, self.rope_dim, self.v_dim = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        self.qk_dim = self.nope + self.rope_dim
+        qm = quant_factory or (lambda: None)
+        dt = cfg.dtype
+        if self.q_lora_rank:
+            self.q_a_proj = ReplicatedLinear(self.hidden, self.q_lora_rank, dtype=dt, device=device,
+                                             quant_method=qm(), prefix=f"{prefix}.q_a_proj")
+            self.q_a_layernorm = RMSNorm(self.q_lora_rank, cfg.rms_norm_eps, dt, device)
+            self.q_b_proj = ColumnParallelLinear(self.q_lora_rank, cfg.num_heads * self.qk_dim, dtype=dt,
+                                                 device=device, quant_method=qm(), prefix=f"{prefix}.q_b_proj")
+        else:
+            self.q_proj = ColumnParallelLinear(self.hidden, cfg.num_heads * self.qk_dim, dtype=dt,
+                                               device=device, quant_method=qm(), prefix=f"{prefix}.q_proj")
+        self.kv_a_proj_with_mqa = ReplicatedLinear(self.hidden, self.kv_lora_rank + self.rope_dim, dtype=dt,
+                                                   device=device, quant_method=qm(),
+                                                   prefix=f"{prefix}.kv_a_proj_with_mqa")
+        self.kv_a_layernorm = RMSNorm(self.kv_lora_rank, cfg.rms_norm_eps, dt, device)
+        self.kv_b_proj = ColumnParallelLinear(self.kv_lora_rank, cfg.num_heads * (self.nope + self.v_dim),
+                                              dtype=dt, device=device, prefix=f"{prefix}.kv_b_proj")
+        self.o_proj = RowParallelLinear(cfg.num_heads * self.v_dim, self.hidden, dtype=dt, device=device,
+                                        quant_method=qm(), prefix=f"{prefix}.o_proj")
+        self.rotary = get_rope(self.rope_dim, self.rope_dim, cfg.max_position_embeddings, cfg.rope_theta,
+                               False, cfg.rope_scaling, device)
+        self.scale = self.qk_dim ** -0.5
+        rs = cfg.rope_scaling or {}
+        if rs.get("rope_type", rs.get("type")) in ("yarn", "deepseek_yarn") and rs.get("mscale_all_dim"):
+            m = yarn_get_mscale(rs["factor"], rs["mscale_all_dim"])
+            self.scale *= m * m
+        self.w_uk: Optional[torch.Tensor] = None    # [N, 512, 128]: rows = latent dims  (q_nope @ W_UK)
+        self.w_uv: Optional[torch.Tensor] = None    # [N, 128, 512]: rows = v dims       (o_lat @ W_UV^T)
+
+    def process_weights_after_loading(self) -> None:
+        """Split kv_b_proj into the absorbed-path matrices."""
+        w = self.kv_b_proj.weight.data
+        if w.dtype == torch.float8_e4m3fn:
+            return
+        n, l = self.num_heads, self.kv_lora_rank
+        w = w.view(n, self.nope + self.v_dim, l)
+        # q_lat[n, t, l] = sum_p q_nope[n,t,p] * W[n,p,l]  ->  GEMM weight rows are output dims: [l, p]
+        self.w_uk = w[:, : self.nope, :].transpose(1, 2).contiguous()
+        # v[n, t, d] = sum_l o_lat[n,t,l] * W[n, nope+d, l] ->  weight rows [d, l]
+        self.w_uv = w[:, self.nope:, :].contiguous()
+
+    # ------------------------------------------------------------------ forward
+    def _project_q(self, hidden: torch.Tensor) -> torch.Tensor:
+        if self.q_lora_rank:
+            return self.q_b_proj(self.q_a_layernorm(self.q_a_proj(hidden)))
+        return self.q_proj(hidden)
+
+    def forward(self, hidden: torch.Tensor, reduce: bool = True,
+                topk_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+        ctx = get_forward_context()
+        md: AttentionMetadata = ctx.attn_metadata
+        cache = ctx.kv_caches[self.layer_idx]
+        cache = cache[0] if isinstance(cache, (tuple, list)) else cache
+        t = hidden.shape[0]
+        n = self.num_heads
+        q = self._project_q(hidden).view(t, n, self.qk_dim)
+        kv_a = self.kv_a_proj_with_mqa(hidden)
+        # fused: RMSNorm(c_kv), RoPE(k_pe), write [c_kv | k_pe] into the paged cache
+        ops.mla_kv_rmsnorm_rope_cache(kv_a[:, : self.kv_lora_rank], kv_a[:, self.kv_lora_rank:],
+                                      self.kv_a_layernorm.weight, cache, md.positions, md.slot_mapping,
+                                      self.rotary.cos_sin_cache, self.kv_a_layernorm.eps, False)
+        # RoPE on the rope part of q (k_pe is handled by the cache kernel)
+        q_pe = q[:, :, self.nope:].reshape(t, n * self.rope_dim).contiguous()
+        dummy_k = q_pe.new_empty(t, 0)
+        ops.rope_qk_(q_pe, dummy_k, md.positions, self.rotary.cos_sin_cache, self.rope_dim, self.rope_dim, False)
+        q_pe = q_pe.view(t, n, self.rope_dim)
+        if md.is_prefill and topk_indices is None:
+            o = self._prefill(q, q_pe, cache, md)
+        else:
+            o = self._decode(q, q_pe, cache, md, topk_indices)
+        return self.o_proj(o, reduce=reduce)
+
+    def _prefill(self, q, q_pe, cache, md: AttentionMetadata) -> torch.Tensor:
+        t, n = q.shape[0], self.num_heads
+        bs = cache.shape[1]
+        total_kv = int(md.extra.get("total_kv", 0)) or int(md.seq_lens[: md.num_seqs].sum().item())
+        slots, seq_id, pos = kv_slots_for_sequences(md, bs, total_kv)
+        lat = cache.view(-1, cache.shape[-1]).index_select(0, slots)              # [Tkv, 576]
+        kv = self.kv_b_proj(lat[:, : self.kv_lora_rank].contiguous()).view(total_kv, n, self.nope + self.v_dim)
+        k = torch.cat([kv[:, :, : self.nope],
+                       lat[:, self.kv_lora_rank:].unsqueeze(1).expand(total_kv, n, self.rope_dim)], dim=-1)
+        v = kv[:, :, self.nope:]
+        # temporary paged layout, one run of blocks per sequence
+        lens = md.seq_lens[: md.num_seqs].long()
+        nblk_per = (lens + bs - 1) // bs
+        blk_start = torch.cumsum(nblk_per, 0) - nblk_per
+        max_blocks = (md.max_seq_len + bs - 1) // bs
+        total_blocks = md.num_seqs * max_blocks
+        k_paged = torch.zeros(total_blocks, n, bs, self.qk_dim, dtype=q.dtype, device=q.device)
+        v_paged = torch.zeros(total_blocks, n, bs, self.v_dim, dtype=q.dtype, device=q.device)
+        tblk = seq_id * max_blocks + pos // bs
+        k_paged[tblk, :, pos % bs] = k
+        v_paged[tblk, :, pos % bs] = v
+        bt = (torch.arange(md.num_seqs, device=q.device).unsqueeze(1) * max_blocks +
+              torch.arange(max_blocks, device=q.device).unsqueeze(0)).to(torch.int32)
+        qf = torch.cat([q[:, :, : self.nope], q_pe], dim=-1).reshape(t, n * self.qk_dim)
+        out = ops.gqa_prefill(qf, k_paged, v_paged, bt, md.cu_q, md.seq_lens, md.num_seqs, md.max_q_len, n,
+                              self.scale, True, 0)
+        return out
+
+    def _decode(self, q, q_pe, cache, md: AttentionMetadata, topk_indices) -> torch.Tensor:
+        t, n = q.shape[0], self.num_heads
+        l = self.kv_lora_rank
+        if self.w_uk is None:
+            self.process_weights_after_loading()
+        # absorb: q_lat[h] = q_nope[h] @ W_UK[h]  (heads act as the groups of a grouped GEMM)
+        q_nope = q[:, :, : self.nope].transpose(0, 1).reshape(n * t, self.nope).contiguous()
+        offs = torch.arange(0, (n + 1) * t, t, dtype=torch.int32, device=q.device)
+        q_lat = ops.grouped_gemm(q_nope, self.w_uk, offs).view(n, t, l).transpose(0, 1)
+        qf = torch.cat([q_lat, q_pe], dim=-1).reshape(t, n * (l + self.rope_dim)).contiguous()
+        if md.is_prefill:
+            # sparse prefill: every query token is its own "sequence" row for the kernel
+            seq_of_tok = torch.repeat_interleave(torch.arange(md.num_seqs, device=q.device),
+                                                 (md.cu_q[1: md.num_seqs + 1] - md.cu_q[: md.num_seqs]).long(),
+                                                 output_size=t)
+            bt = md.block_tables[seq_of_tok]
+            sl = md.seq_lens[seq_of_tok]
+            o_lat = ops.mla_decode(qf, cache, bt.contiguous(), sl.contiguous(), t, n, self.scale, 1, topk_indices)
+        else:
+            o_lat = ops.mla_decode(qf, cache, md.block_tables, md.seq_lens, md.num_seqs, n, self.scale, md.q_len,
+                                   topk_indices, max_seq_len=md.max_seq_len)
+        o_lat = o_lat.view(t, n, l).transpose(0, 1).reshape(n * t, l).contiguous()
+        o = ops.grouped_gemm(o_lat, self.w_uv, offs).view(n, t, self.v_dim).transpose(0, 1)
+        return o.reshape(t, n * self.v_dim).contiguous()

@@ -59,6 +59,15 @@ int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, voi
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
                     float scale, int window, int splits, void* scratch, int num_cache_blocks,
                     int* status, cudaStream_t stream);
+size_t b200_mla_decode_scratch_bytes(int total_tokens, int N, int splits);
+int b200_mla_decode(const void* q, const void* cache, void* out, float* lse, const int* block_tables,
+                    const int* seq_lens, const int* topk_indices, int topk, int B, int q_len, int N,
+                    int max_blocks, int block_size, int num_cache_blocks, long long q_stride,
+                    long long out_stride, float scale, int splits, void* scratch, int* status,
+                    cudaStream_t stream);
+int b200_moe_topk(const float* logits, const float* bias, int* topk_ids, float* topk_w, int T, int E,
+                  int k, int scoring, int n_group, int topk_group, int renorm, float scale,
+                  cudaStream_t stream);
 int b200_argmax(const void* logits, int* out, int B, int V, long long stride, int is_fp32,
                 cudaStream_t stream);
 int b200_sample(const void* logits, int* out, const float* temperature, const int* top_k,
@@ -366,6 +375,74 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   return out;
 }
 
+int64_t mla_decode_scratch_bytes(int64_t T, int64_t N, int64_t splits) {
+  return (int64_t)b200_mla_decode_scratch_bytes((int)T, (int)N, (int)splits);
+}
+
+// Absorbed multi-head latent attention over the paged latent cache.
+// q [T, N*576], cache [blocks, block_size, 576] -> out [T, N*512].
+Tensor mla_decode(const Tensor& q, const Tensor& cache, const Tensor& block_tables,
+                  const Tensor& seq_lens, const c10::optional<Tensor>& topk_indices,
+                  int64_t num_seqs, int64_t q_len, int64_t num_heads, double scale, int64_t splits,
+                  const c10::optional<Tensor>& scratch, const Tensor& status) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(cache);
+  CHECK_I32(block_tables);
+  CHECK_I32(seq_lens);
+  TORCH_CHECK(cache.dim() == 3 && cache.size(2) == 576 && cache.is_contiguous(), "mla cache [blocks, bs, 576]");
+  TORCH_CHECK(q.dim() == 2 && q.stride(1) == 1 && q.size(1) == num_heads * 576, "mla_decode: q [T, N*576]");
+  const int T = num_seqs * q_len;
+  TORCH_CHECK(q.size(0) >= T, "mla_decode: q rows");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({q.size(0), num_heads * 512}, q.options());
+  const int* tk = nullptr;
+  int topk = 0;
+  if (topk_indices.has_value()) {
+    CHECK_I32(*topk_indices);
+    TORCH_CHECK(topk_indices->dim() == 2 && topk_indices->size(0) >= T, "topk_indices [T, topk]");
+    tk = topk_indices->data_ptr<int>();
+    topk = topk_indices->size(1);
+  }
+  void* sp = nullptr;
+  if (splits > 1) {
+    TORCH_CHECK(scratch.has_value() &&
+                    (int64_t)scratch->nbytes() >= mla_decode_scratch_bytes(T, num_heads, splits),
+                "mla_decode: scratch too small");
+    sp = scratch->data_ptr();
+  }
+  check(b200_mla_decode(q.data_ptr(), cache.data_ptr(), out.data_ptr(), nullptr,
+                        block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), tk, topk, (int)num_seqs,
+                        (int)q_len, (int)num_heads, (int)block_tables.size(1), (int)cache.size(1),
+                        (int)cache.size(0), q.stride(0), out.stride(0), (float)scale, (int)splits, sp,
+                        status.data_ptr<int>(), cur_stream()),
+        "mla_decode");
+  return out;
+}
+
+// Router: gate logits [T,E] fp32 -> (top-k ids int32 [T,k], weights fp32 [T,k]).
+std::tuple<Tensor, Tensor> moe_topk(const Tensor& logits, const c10::optional<Tensor>& bias,
+                                    int64_t k, bool sigmoid, int64_t n_group, int64_t topk_group,
+                                    bool renorm, double scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous() &&
+                  logits.dim() == 2,
+              "moe_topk: logits [T,E] fp32 contiguous");
+  const int T = logits.size(0), E = logits.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor ids = torch::empty({T, k}, logits.options().dtype(at::kInt));
+  Tensor w = torch::empty({T, k}, logits.options());
+  const float* bp = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->numel() == E && bias->is_contiguous(),
+                "moe_topk: bias [E] fp32");
+    bp = bias->data_ptr<float>();
+  }
+  check(b200_moe_topk(logits.data_ptr<float>(), bp, ids.data_ptr<int>(), w.data_ptr<float>(), T, E,
+                      (int)k, sigmoid ? 1 : 0, (int)n_group, (int)topk_group, renorm ? 1 : 0,
+                      (float)scale, cur_stream()),
+        "moe_topk");
+  return {ids, w};
+}
+
 Tensor argmax(const Tensor& logits) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "argmax: [B,V]");
   const bool f32 = logits.scalar_type() == at::kFloat;
@@ -416,6 +493,9 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gqa_prefill", &gqa_prefill);
   m.def("gqa_decode_scratch_bytes", &gqa_decode_scratch_bytes);
   m.def("gqa_decode", &gqa_decode);
+  m.def("mla_decode_scratch_bytes", &mla_decode_scratch_bytes);
+  m.def("mla_decode", &mla_decode);
+  m.def("moe_topk", &moe_topk);
   m.def("argmax", &argmax);
   m.def("sample", &sample);
 }

@@ -1,0 +1,444 @@
+// Mixture-of-experts routing and expert-parallel dispatch / combine.
+//
+//  moe_topk          gate scores (softmax or sigmoid, optional correction bias,
+//                    optional group-limited routing) -> top-k expert ids + weights.
+//  ep_count          per-expert token counts of this rank, published to every
+//                    rank of the expert-parallel group (peer stores).
+//  ep_layout         from the full count matrix: row offsets of every local expert
+//                    in this rank's receive buffer, and for every global expert the
+//                    first receive row this rank may write on the owning rank.
+//  ep_scatter        copies each routed token row straight into the owning rank's
+//                    receive buffer over NVLink (expert-sorted, no host sync),
+//                    remembers the slot for the way back.
+//  ep_signal/ep_wait flag barrier between the phases (bounded waits).
+//  ep_combine        every token pulls its k expert outputs from the owners'
+//                    output buffers and reduces them with the routing weights
+//                    (+ optional shared-expert output) in fp32.
+//
+// With a group of one rank the same kernels are the local permute / un-permute.
+// All counts live in device memory, so the whole sequence can be captured in a
+// CUDA graph (the reference's prefill path needs a host sync for the counts:
+// omni_npu/v1/layers/fused_moe/fused_moe_prepare_permute_unpermute_finalize.py:100-112).
+//
+// Replaces npu_moe_gating_top_k(_softmax), npu_moe_init_routing_v2,
+// npu_moe_distribute_dispatch_v2 / combine_v2 and npu_moe_finalize_routing
+// (omni_npu/layers/fused_moe/layer.py:254-308,
+// omni_npu/layers/fused_moe/npu_moe_prepare_finalize.py:66-119).
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+static constexpr int kEpMaxRanks = 8;
+static constexpr int kEpMaxExperts = 512;
+static constexpr uint32_t kEpMaxPolls = 1u << 24;
+
+// ------------------------------------------------------------------ top-k
+// One warp per token.  logits [T, E] fp32.  scoring: 0 softmax, 1 sigmoid.
+// Group-limited routing (n_group > 1): group score = sum of its two best
+// (bias-corrected) scores when a bias is given, else its best score; only the
+// best topk_group groups stay eligible.  The returned weight is the unbiased
+// score, optionally renormalised over the selection, times scale.
+__global__ void __launch_bounds__(256)
+moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                int* __restrict__ topk_ids, float* __restrict__ topk_w, int T, int E, int k,
+                int scoring, int n_group, int topk_group, int renorm, float scale) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  constexpr int PER = kEpMaxExperts / 32;
+  float s[PER];      // unbiased scores
+  float c[PER];      // scores used for choosing (bias-corrected)
+  const float* row = logits + static_cast<long long>(t) * E;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    s[i] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, s[i]);
+  }
+  if (scoring == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      s[i] = e < E ? __expf(s[i] - mx) : 0.f;
+      sum += s[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) s[i] *= inv;
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      s[i] = e < E ? 1.f / (1.f + __expf(-s[i])) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    c[i] = e < E ? s[i] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  if (n_group > 1) {
+    // every lane computes the group scores redundantly from warp-wide data
+    const int gsz = E / n_group;
+    float gscore[32];  // n_group <= 32
+    for (int g = 0; g < n_group; ++g) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = i * 32 + lane;
+        if (e < E && e / gsz == g) {
+          if (c[i] > b1) {
+            b2 = b1;
+            b1 = c[i];
+          } else if (c[i] > b2) {
+            b2 = c[i];
+          }
+        }
+      }
+      // merge (best, second) pairs across lanes
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float o1 = __shfl_xor_sync(0xffffffffu, b1, o);
+        const float o2 = __shfl_xor_sync(0xffffffffu, b2, o);
+        const float n1 = fmaxf(b1, o1);
+        const float n2 = fmaxf(fminf(b1, o1), fmaxf(b2, o2));
+        b1 = n1;
+        b2 = n2;
+      }
+      gscore[g] = bias ? (b1 + (b2 == -INFINITY ? 0.f : b2)) : b1;
+    }
+    // keep the topk_group best groups (lower index wins ties)
+    uint32_t keep = 0;
+    for (int r = 0; r < topk_group; ++r) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < n_group; ++g)
+        if (!((keep >> g) & 1u) && gscore[g] > bv) {
+          bv = gscore[g];
+          best = g;
+        }
+      if (best >= 0) keep |= 1u << best;
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && !((keep >> (e / gsz)) & 1u)) c[i] = -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = -1;
+  for (int j = 0; j < k; ++j) {
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && (c[i] > bv || (c[i] == bv && e < be))) {
+        bv = c[i];
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    // the owner lane reports the unbiased score and retires the expert
+    float w = 0.f;
+    if (be != 0x7fffffff && (be & 31) == lane) {
+      w = s[be >> 5];
+      c[be >> 5] = -INFINITY;
+    }
+    w = __shfl_sync(0xffffffffu, w, be == 0x7fffffff ? 0 : (be & 31));
+    wsum += w;
+    if (lane == j) {
+      my_w = w;
+      my_id = be == 0x7fffffff ? 0 : be;
+    }
+  }
+  if (lane < k) {
+    const float denom = renorm ? fmaxf(wsum, 1e-20f) : 1.f;
+    topk_ids[static_cast<long long>(t) * k + lane] = my_id;
+    topk_w[static_cast<long long>(t) * k + lane] = my_w / denom * scale;
+  }
+}
+
+// ------------------------------------------------------------ EP plumbing
+struct EpGroup {
+  void* recv_x[kEpMaxRanks];       // [cap_rows, H] token rows received for my experts (peer-mapped)
+  void* expert_y[kEpMaxRanks];     // [cap_rows, H] expert outputs, same row order (peer-mapped)
+  int* counts[kEpMaxRanks];        // [world][E] count matrix replica on every rank (peer-mapped)
+  uint32_t* flags[kEpMaxRanks];    // [4][world] phase flags + epoch word (peer-mapped)
+  int world;
+  int rank;
+  int num_experts;                 // global
+  int experts_per_rank;
+  int cap_rows;
+};
+
+static constexpr int kEpFlagEpochWord = 4 * kEpMaxRanks;
+
+__device__ __forceinline__ void ep_st_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Phase 0: zero my count row, histogram my routed tokens (ids < 0 = inactive slots),
+// publish the row to every rank, raise phase-0 flags.  Single block.
+__global__ void __launch_bounds__(1024)
+ep_count_kernel(EpGroup g, const int* __restrict__ topk_ids, int n_pairs, int* __restrict__ cursors) {
+  __shared__ int hist[kEpMaxExperts];
+  for (int e = threadIdx.x; e < g.num_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = topk_ids[i];
+    if (e >= 0 && e < g.num_experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(g.flags[g.rank] + kEpFlagEpochWord) + 1;
+  for (int e = threadIdx.x; e < g.num_experts; e += blockDim.x) {
+    cursors[e] = 0;
+    for (int r = 0; r < g.world; ++r) g.counts[r][g.rank * g.num_experts + e] = hist[e];
+  }
+  __syncthreads();
+  if (threadIdx.x < g.world) {
+    __threadfence_system();
+    ep_st_release(g.flags[threadIdx.x] + 0 * kEpMaxRanks + g.rank, epoch);
+  }
+}
+
+// Waits (bounded) until every rank has raised `phase` for the current call.
+// phase 0: counts published, 1: rows scattered, 2: expert outputs ready.
+// advance != 0: this is the last wait of the call, bump the epoch afterwards.
+__global__ void ep_wait_kernel(EpGroup g, int phase, int advance, int* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(g.flags[g.rank] + kEpFlagEpochWord) + 1;
+  bool ok = true;
+  if (threadIdx.x < g.world) {
+    const uint32_t* f = g.flags[g.rank] + phase * kEpMaxRanks + threadIdx.x;
+    uint32_t i = 0;
+    while (static_cast<int32_t>(ep_ld_acquire(f) - epoch) < 0) {
+      if (++i > kEpMaxPolls) {
+        ok = false;
+        break;
+      }
+    }
+    if (!ok && status) atomicCAS(status, 0, 5);
+  }
+  __syncthreads();
+  if (advance && threadIdx.x == 0)
+    *reinterpret_cast<volatile uint32_t*>(g.flags[g.rank] + kEpFlagEpochWord) = epoch;
+}
+
+// Raises `phase` on every rank (after all prior work of this stream is visible system-wide).
+__global__ void ep_signal_kernel(EpGroup g, int phase) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(g.flags[g.rank] + kEpFlagEpochWord) + 1;
+  if (threadIdx.x < g.world) {
+    __threadfence_system();
+    ep_st_release(g.flags[threadIdx.x] + phase * kEpMaxRanks + g.rank, epoch);
+  }
+}
+
+// Phase 1 (after wait 0): layout.  Single block.
+//   expert_offsets[e_local]  rows of my receive buffer per local expert (prefix sums)
+//   send_base[e]             first row on the owner of expert e reserved for my tokens
+//   total_recv[0]            rows I will receive in total
+__global__ void __launch_bounds__(1024)
+ep_layout_kernel(EpGroup g, int* __restrict__ expert_offsets, int* __restrict__ send_base,
+                 int* __restrict__ total_recv, int* status) {
+  __shared__ int per_expert[kEpMaxExperts];   // rows per global expert over all sources
+  __shared__ int before_me[kEpMaxExperts];    // rows for expert e from sources < me
+  const int* C = g.counts[g.rank];
+  for (int e = threadIdx.x; e < g.num_experts; e += blockDim.x) {
+    int tot = 0, bef = 0;
+    for (int s = 0; s < g.world; ++s) {
+      const int c = C[s * g.num_experts + e];
+      if (s < g.rank) bef += c;
+      tot += c;
+    }
+    per_expert[e] = tot;
+    before_me[e] = bef;
+  }
+  __syncthreads();
+  if (threadIdx.x < g.world) {
+    // thread d walks the experts owned by rank d
+    const int d = threadIdx.x;
+    int acc = 0;
+    for (int el = 0; el < g.experts_per_rank; ++el) {
+      const int e = d * g.experts_per_rank + el;
+      send_base[e] = acc + before_me[e];
+      if (d == g.rank) expert_offsets[el] = acc;
+      acc += per_expert[e];
+    }
+    if (d == g.rank) {
+      expert_offsets[g.experts_per_rank] = acc > g.cap_rows ? g.cap_rows : acc;
+      total_recv[0] = acc;
+      if (acc > g.cap_rows && status) atomicCAS(status, 0, 7);  // receive buffer overflow
+    }
+  }
+}
+
+// Phase 1b: scatter rows.  One warp per (token, j) pair.
+__global__ void __launch_bounds__(256)
+ep_scatter_kernel(EpGroup g, const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_ids,
+                  const int* __restrict__ send_base, int* __restrict__ cursors,
+                  int* __restrict__ slots, int n_pairs, int k, int H, long long x_stride) {
+  const int pair = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pair >= n_pairs) return;
+  const int lane = threadIdx.x & 31;
+  const int e = topk_ids[pair];
+  int pos = -1;
+  if (e >= 0 && e < g.num_experts) {
+    if (lane == 0) pos = send_base[e] + atomicAdd(&cursors[e], 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos >= g.cap_rows) pos = -1;   // dropped: receiver overflowed (status raised by layout)
+  }
+  if (lane == 0) slots[pair] = pos;
+  if (pos < 0) return;
+  const int d = e / g.experts_per_rank;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(pair / k) * x_stride);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.recv_x[d]) +
+                                        static_cast<long long>(pos) * H);
+  for (int i = lane; i < (H >> 3); i += 32) dst[i] = src[i];
+}
+
+// Phase 3 (after wait 2): out[t] = sum_j w[t,j] * y_owner[slot[t,j]] (+ shared[t]).
+// One CTA per token, 128 threads x 8 columns per pass.
+__global__ void __launch_bounds__(128)
+ep_combine_kernel(EpGroup g, __nv_bfloat16* __restrict__ out, const int* __restrict__ topk_ids,
+                  const float* __restrict__ topk_w, const int* __restrict__ slots,
+                  const __nv_bfloat16* __restrict__ shared_out, int k, int H, long long out_stride,
+                  long long shared_stride) {
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int pair = t * k + j;
+      const int pos = slots[pair];
+      if (pos < 0) continue;
+      const int d = topk_ids[pair] / g.experts_per_rank;
+      const float w = topk_w[pair];
+      const uint4 raw = __ldcv(reinterpret_cast<const uint4*>(
+                                   static_cast<const __nv_bfloat16*>(g.expert_y[d]) +
+                                   static_cast<long long>(pos) * H) + v);
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += w * __bfloat162float(h[i]);
+    }
+    if (shared_out) {
+      const uint4 raw = reinterpret_cast<const uint4*>(shared_out + t * shared_stride)[v];
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(h[i]);
+    }
+    uint4 o;
+    __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) oh[i] = __float2bfloat16(acc[i]);
+    reinterpret_cast<uint4*>(out + t * out_stride)[v] = o;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_topk(const float* logits, const float* bias, int* topk_ids, float* topk_w,
+                             int T, int E, int k, int scoring, int n_group, int topk_group,
+                             int renorm, float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > kEpMaxExperts || k > 32 || n_group > 32 || (n_group > 1 && E % n_group != 0)) return -1;
+  moe_topk_kernel<<<(T + 7) / 8, 256, 0, stream>>>(logits, bias, topk_ids, topk_w, T, E, k, scoring,
+                                                    n_group, topk_group, renorm, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+struct EpHostArgs {
+  void* recv_x[kEpMaxRanks];
+  void* expert_y[kEpMaxRanks];
+  void* counts[kEpMaxRanks];
+  void* flags[kEpMaxRanks];
+};
+
+static EpGroup make_ep(const EpHostArgs* a, int world, int rank, int num_experts, int cap_rows) {
+  EpGroup g{};
+  for (int r = 0; r < kEpMaxRanks; ++r) {
+    g.recv_x[r] = r < world ? a->recv_x[r] : nullptr;
+    g.expert_y[r] = r < world ? a->expert_y[r] : nullptr;
+    g.counts[r] = r < world ? static_cast<int*>(a->counts[r]) : nullptr;
+    g.flags[r] = r < world ? static_cast<uint32_t*>(a->flags[r]) : nullptr;
+  }
+  g.world = world;
+  g.rank = rank;
+  g.num_experts = num_experts;
+  g.experts_per_rank = num_experts / world;
+  g.cap_rows = cap_rows;
+  return g;
+}
+
+extern "C" int b200_ep_flag_words() { return kEpFlagEpochWord + 4; }
+
+// Routes x [T,H] by topk_ids [T,k] to the owners' receive buffers.
+//   expert_offsets [E_local+1], send_base [E], cursors [E], slots [T*k], total_recv [1]: device ints.
+// On return (stream order) this rank's recv_x holds its experts' rows, grouped by
+// expert as described by expert_offsets.
+extern "C" int b200_ep_dispatch(const EpHostArgs* a, int world, int rank, int num_experts,
+                                int cap_rows, const void* x, const int* topk_ids, int T, int k, int H,
+                                long long x_stride, int* expert_offsets, int* send_base,
+                                int* cursors, int* slots, int* total_recv, int* status,
+                                cudaStream_t stream) {
+  if (world < 1 || world > kEpMaxRanks || num_experts > kEpMaxExperts || num_experts % world != 0)
+    return -1;
+  if ((H & 7) != 0) return -2;
+  const EpGroup g = make_ep(a, world, rank, num_experts, cap_rows);
+  const int n_pairs = T * k;
+  ep_count_kernel<<<1, 1024, 0, stream>>>(g, topk_ids, n_pairs, cursors);
+  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 0, 0, status);
+  ep_layout_kernel<<<1, 1024, 0, stream>>>(g, expert_offsets, send_base, total_recv, status);
+  if (n_pairs > 0)
+    ep_scatter_kernel<<<(n_pairs + 7) / 8, 256, 0, stream>>>(
+        g, static_cast<const __nv_bfloat16*>(x), topk_ids, send_base, cursors, slots, n_pairs, k, H,
+        x_stride);
+  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 1);
+  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 1, 0, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// After the experts have written expert_y (same row order as recv_x): publish,
+// wait for every owner, pull and reduce.
+extern "C" int b200_ep_combine(const EpHostArgs* a, int world, int rank, int num_experts,
+                               int cap_rows, void* out, const int* topk_ids, const float* topk_w,
+                               const int* slots, const void* shared_out, int T, int k, int H,
+                               long long out_stride, long long shared_stride, int* status,
+                               cudaStream_t stream) {
+  if (world < 1 || world > kEpMaxRanks) return -1;
+  if ((H & 7) != 0) return -2;
+  const EpGroup g = make_ep(a, world, rank, num_experts, cap_rows);
+  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 2);
+  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 2, 0, status);
+  if (T > 0)
+    ep_combine_kernel<<<T, 128, 0, stream>>>(g, static_cast<__nv_bfloat16*>(out), topk_ids, topk_w,
+                                             slots, static_cast<const __nv_bfloat16*>(shared_out), k,
+                                             H, out_stride, shared_stride);
+  // everyone has finished pulling before any rank starts the next call's scatter
+  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 3);
+  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 3, 1, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,223 @@
+"""Fused mixture-of-experts layer.
+
+Pipeline (one code path for 1 GPU, tensor-parallel replicas and expert
+parallelism):
+
+    router GEMM (fp32 logits) -> top-k (softmax / sigmoid, bias correction,
+    group-limited) -> dispatch (rows go straight into the owning rank's receive
+    buffer, expert-sorted) -> grouped GEMM gate_up with SwiGLU epilogue ->
+    grouped GEMM down -> combine (each token pulls its k outputs, weighted sum,
+    + shared experts).
+
+Shared experts run on a side stream while the routed experts run, as the
+reference does (omni_npu/v1/layers/quantization/compressed_tensors/npu_compressed_tensors_moe.py:145-158).
+Tokens are de-duplicated across attention-TP ranks before dispatch and
+all-gathered afterwards when the residual stream is replicated
+(omni_npu/v1/layers/fused_moe/layer.py:46-56,89-90).
+
+Expert weights: ``w13`` [E_local, 2I, H] with gate / up rows interleaved in
+groups of eight (SwiGLU epilogue layout), ``w2`` [E_local, H, I].
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional, Tuple
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..ops import ref
+from ..parallel import state as pstate
+from .linear import ReplicatedLinear
+from .mlp import FusedMLP
+from .moe_dispatch import EpBuffers, ep_combine, ep_dispatch
+
+
+def select_experts(router_logits: torch.Tensor, top_k: int, scoring_func: str = "softmax",
+                   e_score_correction_bias: Optional[torch.Tensor] = None, n_group: int = 1,
+                   topk_group: int = 1, renormalize: bool = False,
+                   routed_scaling_factor: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(weights fp32 [T,k], ids int32 [T,k]); counterpart of
+    omni_npu/layers/fused_moe/layer.py:254-308."""
+    ids, w = ops.moe_topk(router_logits.float(), e_score_correction_bias, top_k,
+                          scoring_func == "sigmoid", n_group, topk_group, renormalize,
+                          routed_scaling_factor)
+    return w, ids
+
+
+class FusedMoE(nn.Module):
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 dtype=torch.bfloat16, device=None, scoring_func: str = "softmax",
+                 renormalize: bool = False, routed_scaling_factor: float = 1.0, n_group: int = 1,
+                 topk_group: int = 1, router_bias: bool = False, num_shared_experts: int = 0,
+                 shared_intermediate_size: Optional[int] = None, enable_expert_parallel: bool = True,
+                 prefix: str = "", max_tokens: int = 8192, quant: Optional[str] = None) -> None:
+        super().__init__()
+        self.num_experts, self.top_k = num_experts, top_k
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.scoring_func, self.renormalize = scoring_func, renormalize
+        self.routed_scaling_factor = routed_scaling_factor
+        self.n_group, self.topk_group = n_group, topk_group
+        self.max_tokens = max_tokens
+        self.dtype = dtype
+        self.tp_group = pstate.get_tp_group()
+        self.ep_group = pstate.get_ep_group() if enable_expert_parallel else None
+        self.ep_size = self.ep_group.world_size if self.ep_group is not None else 1
+        self.ep_rank = self.ep_group.rank_in_group if self.ep_group is not None else 0
+        assert num_experts % self.ep_size == 0
+        self.local_experts = num_experts // self.ep_size
+        self.expert_start = self.ep_rank * self.local_experts
+        self.gate = ReplicatedLinear(hidden_size, num_experts, dtype=dtype, device=device,
+                                     prefix=f"{prefix}.gate")
+        if router_bias:
+            self.e_score_correction_bias = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32,
+                                                                    device=device), requires_grad=False)
+        else:
+            self.e_score_correction_bias = None
+        wdt = torch.float8_e4m3fn if quant == "fp8" else dtype
+        self.quant = quant
+        self.w13 = nn.Parameter(torch.empty(self.local_experts, 2 * intermediate_size, hidden_size,
+                                            dtype=wdt, device=device), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(self.local_experts, hidden_size, intermediate_size,
+                                           dtype=wdt, device=device), requires_grad=False)
+        if quant == "fp8":
+            self.w13_scale = nn.Parameter(torch.ones(self.local_experts, (2 * intermediate_size + 127) // 128,
+                                                     (hidden_size + 127) // 128, dtype=torch.float32,
+                                                     device=device), requires_grad=False)
+            self.w2_scale = nn.Parameter(torch.ones(self.local_experts, (hidden_size + 127) // 128,
+                                                    (intermediate_size + 127) // 128, dtype=torch.float32,
+                                                    device=device), requires_grad=False)
+        self.shared_experts = None
+        if num_shared_experts > 0:
+            inter = (shared_intermediate_size or intermediate_size) * num_shared_experts
+            # shared experts are replicated when tokens are de-duplicated across TP ranks
+            self.shared_experts = FusedMLP(hidden_size, inter, dtype, device, prefix=f"{prefix}.shared_experts",
+                                           group=_solo_group() if self.ep_size > 1 else None,
+                                           reduce_results=False)
+        self.buffers: Optional[EpBuffers] = None
+        self._side_stream: Optional[torch.cuda.Stream] = None
+        self.expert_load: Optional[torch.Tensor] = None   # per-expert token counts (EPLB statistics)
+
+    # ----------------------------------------------------------------- set-up
+    def init_ep_buffers(self, comm=None) -> None:
+        """Called once after loading (``prepare_communication_buffer_for_model``)."""
+        dev = self.w13.device
+        if dev.type != "cuda" or self.buffers is not None:
+            return
+        shared = _SHARED_BUFFERS.get((id(self.ep_group), self.num_experts, self.hidden_size, self.top_k))
+        if shared is None:
+            group = self.ep_group if self.ep_group is not None else _solo_group()
+            shared = EpBuffers(group, dev, self.num_experts if self.ep_size > 1 else self.local_experts,
+                               self.hidden_size, self.max_tokens, self.top_k)
+            _SHARED_BUFFERS[(id(self.ep_group), self.num_experts, self.hidden_size, self.top_k)] = shared
+        self.buffers = shared
+        self._side_stream = torch.cuda.Stream(dev)
+
+    def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, expert_id: int, shard: str) -> bool:
+        """Load one expert's gate / up / down tensor.  Returns False when the expert
+        lives on another rank."""
+        local = expert_id - self.expert_start
+        if local < 0 or local >= self.local_experts:
+            return False
+        i = self.intermediate_size
+        if shard in ("gate", "up"):
+            j = torch.arange(i, device=param.device)
+            rows = (j // 8) * 16 + (0 if shard == "gate" else 8) + (j % 8)
+            if param.dim() == 3 and param.shape[1] == 2 * i:
+                param.data[local, rows] = loaded.to(param.device).to(param.dtype) \
+                    if param.dtype != torch.float8_e4m3fn else loaded.to(param.device)
+            else:   # block scales: gate blocks then up blocks are kept in checkpoint order
+                nb = loaded.shape[0]
+                off = 0 if shard == "gate" else nb
+                param.data[local, off:off + nb].copy_(loaded)
+        else:
+            param.data[local].copy_(loaded if param.dtype == torch.float8_e4m3fn else loaded.to(param.dtype))
+        return True
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        """hidden [T,H] (replicated across TP ranks) -> [T,H]."""
+        tp = self.tp_group.world_size
+        t_full = hidden.shape[0]
+        dedup = self.ep_size > 1 and tp > 1
+        if dedup:
+            # each TP rank handles a slice of the tokens; results are gathered afterwards
+            per = (t_full + tp - 1) // tp
+            lo = min(t_full, per * self.tp_group.rank_in_group)
+            x = hidden[lo: min(t_full, lo + per)]
+            if x.shape[0] < per:
+                x = torch.cat([x, hidden.new_zeros(per - x.shape[0], hidden.shape[1])])
+        else:
+            x = hidden
+        logits = self.gate(x, out_dtype=torch.float32)
+        w, ids = select_experts(logits, self.top_k, self.scoring_func, self.e_score_correction_bias,
+                                self.n_group, self.topk_group, self.renormalize,
+                                self.routed_scaling_factor)
+        if dedup and lo + per > t_full:
+            pad_from = max(0, t_full - lo)
+            ids = ids.clone()
+            ids[pad_from:] = -1          # padded rows take part in nothing
+        out = self._routed(x, w, ids)
+        if dedup:
+            out = self.tp_group.all_gather(out, dim=0)[:t_full]
+        elif tp > 1 and self.ep_size == 1:
+            pass  # experts replicated: nothing to reduce
+        return out
+
+    def _routed(self, x: torch.Tensor, w: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        comm = self.ep_group.comm if self.ep_size > 1 else _Solo.comm
+        shared_out = None
+        if x.is_cuda:
+            if self.buffers is None:
+                self.init_ep_buffers()
+            ids_local = ids
+            if self.shared_experts is not None:
+                # shared experts overlap with dispatch + routed experts on a side stream
+                cur = torch.cuda.current_stream(x.device)
+                self._side_stream.wait_stream(cur)
+                with torch.cuda.stream(self._side_stream):
+                    shared_out = self.shared_experts(x)
+            rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_experts, self.buffers)
+            h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
+            y = ops.grouped_gemm(h1, self.w2, offsets)
+            self.buffers.expert_y[: y.shape[0]].copy_(y)
+            if shared_out is not None:
+                torch.cuda.current_stream(x.device).wait_stream(self._side_stream)
+            return ep_combine(comm, self.buffers.expert_y, handle, shared_out, self.buffers)
+        # CPU / reference path
+        if self.shared_experts is not None:
+            shared_out = self.shared_experts(x)
+        rows, offsets, handle = ep_dispatch(comm, x, ids, w, self.num_experts)
+        h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
+        y = ops.grouped_gemm(h1, self.w2, offsets)
+        return ep_combine(comm, y, handle, shared_out)
+
+
+_SHARED_BUFFERS: dict = {}
+
+
+class _Solo:
+    """A one-rank stand-in for a process group."""
+    world_size = 1
+    rank_in_group = 0
+
+    class _Comm:
+        world_size = 1
+        rank_in_group = 0
+        symm = None
+        ep_buffers = None
+
+    comm = _Comm()
+
+    def all_gather_object(self, obj):
+        return [obj]
+
+    def all_reduce(self, x):
+        return x
+
+    def barrier(self):
+        pass
+
+
+def _solo_group():
+    return _Solo()

@@ -1,0 +1,170 @@
+"""DeepSeek V2 / V2-Lite / V3 / V3.2 decoder.
+
+Multi-head latent attention (optionally DeepSeek sparse attention when the
+config carries ``index_topk``), dense FFN in the first ``first_k_dense_replace``
+layers and a shared + routed mixture of experts afterwards.  Mirrors the
+structure of omni_npu/v1/models/deepseek/deepseek_v3.py:64-777: the decoder
+layer picks the sparse attention block when the HF config has ``index_topk``
+(:288-306), weights of gate/up and of the experts are stacked at load time
+(:591-777), MTP layers are skipped by the main model.
+"""
+from __future__ import annotations
+
+import re
+from typing import Iterable, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from ..attention.mla import MLAAttention, MLABackend
+from ..config import EngineConfig, ModelConfig
+from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from ..layers.linear import Fp8BlockLinearMethod
+from ..layers.mlp import FusedMLP
+from ..layers.moe import FusedMoE
+from ..layers.norm import RMSNorm, reduce_add_rms_norm
+from ..parallel import state as pstate
+from .utils import load_stacked_weights
+
+_EXPERT_RE = re.compile(r"(.*)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$")
+
+
+def _quant_factory(cfg: ModelConfig):
+    if cfg.quant_method == "fp8":
+        return lambda: Fp8BlockLinearMethod(cfg.weight_block_size)
+    return lambda: None
+
+
+class DeepseekDecoderLayer(nn.Module):
+    def __init__(self, engine: EngineConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        cfg = engine.model
+        qf = _quant_factory(cfg)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        if cfg.use_sparse:
+            from ..attention.dsa import SparseMLAAttention
+            self.self_attn = SparseMLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf)
+        else:
+            self.self_attn = MLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        self.is_moe = cfg.layer_is_moe(layer_idx)
+        if self.is_moe:
+            self.mlp = FusedMoE(cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size,
+                                cfg.moe_intermediate_size, cfg.dtype, device, cfg.scoring_func,
+                                cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.n_group, cfg.topk_group,
+                                cfg.router_bias, cfg.num_shared_experts,
+                                enable_expert_parallel=engine.parallel.enable_expert_parallel
+                                or engine.parallel.tensor_parallel_size > 1,
+                                prefix=f"{prefix}.mlp", max_tokens=engine.scheduler.max_num_batched_tokens,
+                                quant=None)
+        else:
+            self.mlp = FusedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.dtype, device,
+                                quant_method_factory=qf, prefix=f"{prefix}.mlp",
+                                fuse_swiglu=cfg.quant_method is None)
+        self.tp_group = pstate.get_tp_group()
+
+    def forward(self, hidden, residual, pending_reduce: bool):
+        tp = self.tp_group
+        if residual is None:
+            residual = hidden
+            hidden = self.input_layernorm(hidden)
+        elif pending_reduce:
+            hidden, residual = reduce_add_rms_norm(self.input_layernorm, hidden, residual, tp)
+        else:
+            hidden, residual = self.input_layernorm(hidden, residual)
+        hidden = self.self_attn(hidden, reduce=False)
+        hidden, residual = reduce_add_rms_norm(self.post_attention_layernorm, hidden, residual, tp)
+        if self.is_moe:
+            return self.mlp(hidden), residual, False
+        return self.mlp(hidden, reduce=False), residual, True
+
+
+class DeepseekModel(nn.Module):
+    def __init__(self, engine: EngineConfig, device) -> None:
+        super().__init__()
+        cfg = engine.model
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+        self.layers = nn.ModuleList([DeepseekDecoderLayer(engine, i, device, f"model.layers.{i}")
+                                     for i in range(cfg.num_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+
+    def forward(self, input_ids, positions, inputs_embeds=None, return_prenorm: bool = False):
+        hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        residual, pending = None, False
+        for layer in self.layers:
+            hidden, residual, pending = layer(hidden, residual, pending)
+        if pending:
+            hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, pstate.get_tp_group())
+        else:
+            hidden, _ = self.norm(hidden, residual)
+        return hidden
+
+
+class DeepseekForCausalLM(nn.Module):
+    stacked_params_mapping = [(".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1)]
+
+    def __init__(self, engine_config: EngineConfig, device=None) -> None:
+        super().__init__()
+        self.config = engine_config.model
+        self.engine_config = engine_config
+        self.model = DeepseekModel(engine_config, device)
+        self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device)
+
+    def forward(self, input_ids, positions, inputs_embeds=None):
+        return self.model(input_ids, positions, inputs_embeds)
+
+    def compute_logits(self, hidden):
+        return self.lm_head.compute_logits(hidden)
+
+    # ---- KV cache: one latent cache per layer (+ indexer key cache for sparse attention)
+    def get_kv_cache_spec(self, block_size: int):
+        from ..worker.model_runner import KVCacheSpec
+        c = self.config
+        per = MLABackend.bytes_per_block(block_size, c.kv_lora_rank, c.qk_rope_head_dim, c.dtype)
+        shapes = {"latent": (block_size, c.kv_lora_rank + c.qk_rope_head_dim)}
+        if c.use_sparse:
+            per += block_size * c.index_head_dim * c.dtype.itemsize
+            shapes["index_key"] = (block_size, c.index_head_dim)
+        return KVCacheSpec("dsa" if c.use_sparse else "mla", c.num_layers, block_size, per * c.num_layers, shapes)
+
+    def allocate_kv_cache(self, num_blocks: int, block_size: int, device) -> List:
+        c = self.config
+        caches = []
+        for _ in range(c.num_layers):
+            lat = MLABackend.allocate_kv_cache(num_blocks, block_size, c.kv_lora_rank, c.qk_rope_head_dim,
+                                               c.dtype, device)
+            if c.use_sparse:
+                idx = torch.zeros(num_blocks, block_size, c.index_head_dim, dtype=c.dtype, device=device)
+                caches.append((lat, idx))
+            else:
+                caches.append(lat)
+        return caches
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        loaded, rest = set(), []
+        n_layers = self.config.num_layers
+        for name, tensor in weights:
+            m = re.match(r"model\.layers\.(\d+)\.", name)
+            if m and int(m.group(1)) >= n_layers:
+                continue                                   # multi-token-prediction layers
+            em = _EXPERT_RE.match(name)
+            if em is None:
+                rest.append((name.replace(".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+                             tensor))
+                continue
+            prefix, eid, proj, kind = em.group(1), int(em.group(2)), em.group(3), em.group(4)
+            moe: FusedMoE = self.get_submodule(prefix + ".mlp")
+            pname = ("w13" if proj != "down_proj" else "w2") + ("" if kind == "weight" else "_scale")
+            if not hasattr(moe, pname):
+                continue
+            shard = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down"}[proj]
+            if moe.weight_loader(getattr(moe, pname), tensor, eid, shard):
+                loaded.add(f"{prefix}.mlp.{pname}")
+        loaded |= load_stacked_weights(self, rest, self.stacked_params_mapping,
+                                       skip_substrings=("rotary_emb.inv_freq",))
+        return loaded
+
+
+DeepseekV2ForCausalLM = DeepseekForCausalLM
+DeepseekV3ForCausalLM = DeepseekForCausalLM
+DeepseekV32ForCausalLM = DeepseekForCausalLM

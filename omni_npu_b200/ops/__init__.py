@@ -233,10 +233,12 @@ def rope_qk_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin:
              mrope_interleaved: bool = False) -> None:
     """In-place rotary embedding of q [T,Hq*D] and k [T,Hk*D]."""
     if not q.is_cuda:
-        qo, ko = ref.rope_qk(q, k, positions, cos_sin, head_dim, rot_dim, neox, mrope_section,
+        kk = k if k.numel() else q[:, :head_dim]
+        qo, ko = ref.rope_qk(q, kk, positions, cos_sin, head_dim, rot_dim, neox, mrope_section,
                              mrope_interleaved)
         q.copy_(qo)
-        k.copy_(ko)
+        if k.numel():
+            k.copy_(ko)
         return
     sec_t, sec_h = (-1, -1) if mrope_section is None else (mrope_section[0], mrope_section[1])
     _count(1)
@@ -364,3 +366,41 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
         return ref.sample(logits, temperature, top_k, top_p, generator)
     _count(1)
     return _C().sample(logits, temperature, top_k, top_p, seeds, step_offset)
+
+
+# ------------------------------------------------------------------------- MoE
+def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, sigmoid: bool = False,
+             n_group: int = 1, topk_group: int = 1, renorm: bool = False,
+             scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router top-k (softmax or sigmoid scores, optional bias correction and
+    group-limited selection)."""
+    if not logits.is_cuda:
+        return ref.moe_topk(logits, bias, k, sigmoid, n_group, topk_group, renorm, scale)
+    _count(1)
+    return _C().moe_topk(logits.contiguous(), bias, k, sigmoid, n_group, topk_group, renorm, scale)
+
+
+def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+               num_seqs: int, num_heads: int, scale: float, q_len: int = 1,
+               topk_indices: Optional[torch.Tensor] = None, splits: int = 0,
+               max_seq_len: int = 0) -> torch.Tensor:
+    """Absorbed multi-head latent attention (MQA over the 576-wide latent cache);
+    optionally restricted to ``topk_indices`` (sparse attention)."""
+    if not q.is_cuda:
+        return ref.mla_decode(q, cache, block_tables[:num_seqs], seq_lens[:num_seqs], num_seqs, q_len,
+                              num_heads, scale, topk_indices)
+    C = _C()
+    st = device_state(q.device)
+    t = num_seqs * q_len
+    tiles = (num_heads + 15) // 16
+    if splits <= 0:
+        bound = topk_indices.shape[1] if topk_indices is not None else (
+            max_seq_len if max_seq_len > 0 else block_tables.shape[1] * cache.shape[1])
+        splits = max(1, min((2 * 148 + t * tiles - 1) // max(1, t * tiles), max(1, bound // 256), 16))
+    scratch = None
+    if splits > 1:
+        nbytes = C.mla_decode_scratch_bytes(t, num_heads, splits)
+        scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
+    _count(2 if splits > 1 else 1)
+    return C.mla_decode(q, cache, block_tables, seq_lens, topk_indices, num_seqs, q_len, num_heads, scale,
+                        splits, scratch, st.status)

@@ -271,3 +271,80 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
     e = torch.empty_like(probs).exponential_(1.0, generator=generator)
     tok = (probs / e).argmax(dim=-1).to(torch.int32)
     return torch.where(temperature < 1e-5, greedy, tok)
+
+
+def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, sigmoid: bool = False,
+             n_group: int = 1, topk_group: int = 1, renorm: bool = False,
+             scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router reference.  logits [T,E] -> (ids int32 [T,k], weights fp32 [T,k]).
+    Selection uses the bias-corrected scores, the returned weights the unbiased
+    ones (DeepSeek-V3 "noaux_tc"); with groups, a group's score is the sum of its
+    two best corrected scores when a bias is present, else its best score."""
+    lf = logits.float()
+    scores = torch.sigmoid(lf) if sigmoid else torch.softmax(lf, dim=-1)
+    choice = scores + bias.float() if bias is not None else scores.clone()
+    t, e = scores.shape
+    if n_group > 1:
+        grp = choice.view(t, n_group, e // n_group)
+        gscore = grp.topk(2, dim=-1).values.sum(-1) if bias is not None else grp.max(-1).values
+        gi = _stable_topk(gscore, topk_group)
+        gmask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, gi, True)
+        choice = choice.masked_fill(~gmask.unsqueeze(-1).expand(t, n_group, e // n_group).reshape(t, e),
+                                    float("-inf"))
+    ids = _stable_topk(choice, k)
+    w = scores.gather(1, ids)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+    return ids.to(torch.int32), (w * scale).float()
+
+
+def _stable_topk(x: torch.Tensor, k: int) -> torch.Tensor:
+    """top-k indices, lowest index first among equal values (the CUDA kernel's tie rule)."""
+    order = torch.sort(x, dim=-1, descending=True, stable=True).indices
+    return order[:, :k]
+
+
+def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_ids: torch.Tensor,
+                topk_w: torch.Tensor, swiglu_interleaved: bool = True) -> torch.Tensor:
+    """Dense reference of the routed experts: out[t] = sum_j w[t,j] * MLP_{id[t,j]}(x[t])."""
+    t, h = x.shape
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    for e in topk_ids.unique().tolist():
+        if e < 0:
+            continue
+        rows, js = (topk_ids == e).nonzero(as_tuple=True)
+        xe = x[rows]
+        hmid = gemm(xe, w13[e], swiglu=swiglu_interleaved, out_dtype=x.dtype)
+        if not swiglu_interleaved:
+            hmid = silu_and_mul(hmid)
+        ye = gemm(hmid, w2[e], out_dtype=x.dtype)
+        out.index_add_(0, rows, ye.float() * topk_w[rows, js].unsqueeze(1))
+    return out.to(x.dtype)
+
+
+def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+               num_seqs: int, q_len: int, num_heads: int, scale: float,
+               topk_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Absorbed MLA reference.  q [T, N*576], cache [blocks, bs, 576] -> [T, N*512].
+    Query token i of a sequence sees keys 0 .. seq_len - q_len + i; with
+    ``topk_indices`` [T, topk] only those positions (negative = hole)."""
+    bs = cache.shape[1]
+    out = torch.zeros(q.shape[0], num_heads * 512, dtype=q.dtype, device=q.device)
+    flat = cache.view(-1, 576)
+    for b in range(num_seqs):
+        n = int(seq_lens[b])
+        for i in range(q_len):
+            t = b * q_len + i
+            if topk_indices is not None:
+                pos = topk_indices[t]
+                pos = pos[pos >= 0].long()
+            else:
+                pos = torch.arange(max(0, n - q_len + i + 1), device=q.device)
+            if pos.numel() == 0:
+                continue
+            rows = block_tables[b][pos // bs].long() * bs + pos % bs
+            kv = flat[rows].float()                                   # [L, 576]
+            qq = q[t].view(num_heads, 576).float()
+            p = torch.softmax(qq @ kv.t() * scale, dim=-1)
+            out[t] = (p @ kv[:, :512]).reshape(-1).to(q.dtype)
+    return out

@@ -308,3 +308,79 @@ def test_sample_respects_top_k_top_p_and_distribution():
     assert torch.equal(again, got)
     other = ops.sample(logits, temp, topk, topp, seeds, step + 1).long().cpu()
     assert (other != got).float().mean() > 0.3
+
+
+# --------------------------------------------------------------------- MoE
+@pytest.mark.parametrize("e,k,sigmoid,groups,bias", [(64, 6, False, (1, 1), False), (128, 8, False, (1, 1), False),
+                                                      (256, 8, True, (8, 4), True), (8, 2, True, (4, 2), False)])
+def test_moe_topk(e, k, sigmoid, groups, bias):
+    torch.manual_seed(0)
+    t = 77
+    logits = torch.randn(t, e, device=DEV)
+    b = (torch.randn(e, device=DEV) * 0.1) if bias else None
+    ids, w = ops.moe_topk(logits, b, k, sigmoid, groups[0], groups[1], True, 2.5)
+    ids_r, w_r = ref.moe_topk(logits.cpu(), b.cpu() if bias else None, k, sigmoid, groups[0], groups[1], True, 2.5)
+    # same selected set (order of equal scores may differ) and same weights per expert
+    assert torch.equal(ids.cpu().sort(-1).values, ids_r.sort(-1).values)
+    got = torch.zeros(t, e).scatter_(1, ids.cpu().long(), w.cpu())
+    want = torch.zeros(t, e).scatter_(1, ids_r.long(), w_r)
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-4)
+
+
+def test_fused_moe_layer_single_gpu_matches_cpu_reference():
+    from omni_npu_b200.layers.moe import FusedMoE
+    torch.manual_seed(1)
+    kw = dict(num_experts=16, top_k=4, hidden_size=256, intermediate_size=128, num_shared_experts=1,
+              renormalize=True, max_tokens=512)
+    gpu = FusedMoE(dtype=torch.bfloat16, device=DEV, **kw)
+    for p in gpu.parameters():
+        p.data.normal_(0, 0.05)
+    cpu = FusedMoE(dtype=torch.bfloat16, **kw)
+    cpu.load_state_dict({k_: v.cpu() for k_, v in gpu.state_dict().items()})
+    for t in (1, 37, 300):
+        x = torch.randn(t, 256, device=DEV, dtype=torch.bfloat16)
+        _close(gpu(x), cpu(x.cpu()), 3e-2, 3e-2)
+    # inactive (padded) rows: ids of -1 must contribute nothing and must not fault
+    x = torch.randn(8, 256, device=DEV, dtype=torch.bfloat16)
+    w = torch.full((8, 4), 0.25, device=DEV)
+    ids = torch.randint(0, 16, (8, 4), device=DEV, dtype=torch.int32)
+    ids[5:] = -1
+    out = gpu._routed(x, w, ids)
+    sh = gpu.shared_experts(x)
+    _close(out[5:], sh[5:], 2e-2, 2e-2)
+
+
+# --------------------------------------------------------------------- MLA
+@pytest.mark.parametrize("n_heads,splits,q_len", [(16, 1, 1), (16, 3, 1), (128, 2, 1), (8, 2, 2)])
+def test_mla_decode(n_heads, splits, q_len):
+    torch.manual_seed(3)
+    bs, seq_lens = 16, [5, 64, 200, 1031]
+    b = len(seq_lens)
+    max_blocks = max((s + bs - 1) // bs for s in seq_lens) + 1
+    nblocks = b * max_blocks + 2
+    bt = torch.randperm(nblocks)[: b * max_blocks].view(b, max_blocks).to(torch.int32)
+    cache = torch.randn(nblocks, bs, 576).bfloat16()
+    q = (torch.randn(b * q_len, n_heads * 576) * 0.3).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    want = ref.mla_decode(q, cache, bt, sl, b, q_len, n_heads, 0.07)
+    got = ops.mla_decode(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), b, n_heads, 0.07, q_len, splits=splits)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_mla_decode_sparse_selection():
+    torch.manual_seed(4)
+    bs, n_heads, topk = 16, 16, 128
+    seq_lens = [300, 90]
+    b = len(seq_lens)
+    max_blocks = 20
+    bt = torch.randperm(b * max_blocks)[: b * max_blocks].view(b, max_blocks).to(torch.int32)
+    cache = torch.randn(b * max_blocks, bs, 576).bfloat16()
+    q = (torch.randn(b, n_heads * 576) * 0.3).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    sel = torch.full((b, topk), -1, dtype=torch.int32)
+    sel[0] = torch.randperm(300)[:topk].to(torch.int32)
+    sel[1, :90] = torch.randperm(90).to(torch.int32)
+    sel[1, 7] = -1
+    want = ref.mla_decode(q, cache, bt, sl, b, 1, n_heads, 0.07, sel)
+    got = ops.mla_decode(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), b, n_heads, 0.07, 1, sel.to(DEV), splits=2)
+    _close(got, want, 2e-2, 2e-2)
