@@ -261,10 +261,38 @@ def run_ours(args) -> None:
             "gpu_launches": launches,
             "clocks": clocks,
         }
-        print(json.dumps(out))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        print(json.dumps(out), flush=True)
+    _shutdown(llm, world)
+
+
+def _shutdown(llm, world: int) -> None:
+    """Orderly teardown with a hard deadline: release peer-mapped memory, leave the
+    process groups, and end the process even if a library's finaliser blocks."""
+    import threading
+
+    import torch.distributed as dist
+
+    def _deadline():
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+    timer = threading.Timer(30.0, _deadline)
+    timer.daemon = True
+    timer.start()
+    try:
+        if world > 1:
+            dist.barrier()
+        from omni_npu_b200.parallel import state as pstate
+        llm.engine.shutdown()
+        pstate.destroy_model_parallel()
+        if world > 1 and dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover - best effort
+        print(f"shutdown: {type(e).__name__}: {e}", file=sys.stderr)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def main() -> None:

@@ -32,7 +32,7 @@
 namespace b200 {
 
 static constexpr int kMaxRanks = 8;
-static constexpr int kMaxCommBlocks = 64;
+static constexpr int kMaxCommBlocks = 144;
 static constexpr uint32_t kMaxFlagPolls = 1u << 24;   // ~ a second of polling
 
 struct SymmGroup {
@@ -250,16 +250,36 @@ allreduce_twoshot_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __res
     long long sb, b, e;
     slice_part(n_vec, slice_vecs, g.rank, &sb, &b, &e);
     uint4* red = reinterpret_cast<uint4*>(my_base + red_off);
-    for (long long i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const uint4* srcs[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      srcs[r] = r < g.world ? reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
+                                                             half * g.half_bytes) + sb
+                            : nullptr;
+    // four independent vectors per thread and iteration keep more loads in flight
+    long long i = b + threadIdx.x;
+    for (; i + 3LL * blockDim.x < e; i += 4LL * blockDim.x) {
+      uint4 v[4][kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < g.world) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u][r] = __ldcv(srcs[r] + i + u * blockDim.x);
+        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < g.world) add8(acc, v[u][r]);
+        red[i + u * blockDim.x] = pack8(acc);
+      }
+    }
+    for (; i < e; i += blockDim.x) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r) {
-        if (r < g.world) {
-          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
-                                                            half * g.half_bytes);
-          add8(acc, __ldcv(src + sb + i));
-        }
-      }
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < g.world) add8(acc, __ldcv(srcs[r] + i));
       red[i] = pack8(acc);
     }
     ok = block_barrier(g, e2, status);
@@ -270,7 +290,15 @@ allreduce_twoshot_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __res
       slice_part(n_vec, slice_vecs, r, &sb, &b, &e);
       const uint4* red = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[r]) +
                                                         half * g.half_bytes + red_off);
-      for (long long i = b + threadIdx.x; i < e; i += blockDim.x) out[sb + i] = __ldcv(red + i);
+      long long i = b + threadIdx.x;
+      for (; i + 3LL * blockDim.x < e; i += 4LL * blockDim.x) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcv(red + i + u * blockDim.x);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) out[sb + i + u * blockDim.x] = v[u];
+      }
+      for (; i < e; i += blockDim.x) out[sb + i] = __ldcv(red + i);
     }
   }
   __syncthreads();
@@ -403,7 +431,7 @@ static SymmGroup make_group(void* const* data, void* const* signal, int world, i
 }
 
 static int pick_blocks(long long n_vec, int max_blocks) {
-  long long b = (n_vec + 2047) / 2048;   // >= 4 vectors per thread at 512 threads
+  long long b = (n_vec + 1023) / 1024;   // >= 2 vectors per thread at 512 threads
   if (b < 1) b = 1;
   if (b > max_blocks) b = max_blocks;
   return static_cast<int>(b);

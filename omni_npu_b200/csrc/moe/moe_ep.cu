@@ -409,15 +409,18 @@ extern "C" int b200_ep_dispatch(const EpHostArgs* a, int world, int rank, int nu
   if ((H & 7) != 0) return -2;
   const EpGroup g = make_ep(a, world, rank, num_experts, cap_rows);
   const int n_pairs = T * k;
+  // with a single rank there is nobody to wait for: the flag kernels are skipped
   ep_count_kernel<<<1, 1024, 0, stream>>>(g, topk_ids, n_pairs, cursors);
-  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 0, 0, status);
+  if (world > 1) ep_wait_kernel<<<1, 32, 0, stream>>>(g, 0, 0, status);
   ep_layout_kernel<<<1, 1024, 0, stream>>>(g, expert_offsets, send_base, total_recv, status);
   if (n_pairs > 0)
     ep_scatter_kernel<<<(n_pairs + 7) / 8, 256, 0, stream>>>(
         g, static_cast<const __nv_bfloat16*>(x), topk_ids, send_base, cursors, slots, n_pairs, k, H,
         x_stride);
-  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 1);
-  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 1, 0, status);
+  if (world > 1) {
+    ep_signal_kernel<<<1, 32, 0, stream>>>(g, 1);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(g, 1, 0, status);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -431,14 +434,18 @@ extern "C" int b200_ep_combine(const EpHostArgs* a, int world, int rank, int num
   if (world < 1 || world > kEpMaxRanks) return -1;
   if ((H & 7) != 0) return -2;
   const EpGroup g = make_ep(a, world, rank, num_experts, cap_rows);
-  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 2);
-  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 2, 0, status);
+  if (world > 1) {
+    ep_signal_kernel<<<1, 32, 0, stream>>>(g, 2);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(g, 2, 0, status);
+  }
   if (T > 0)
     ep_combine_kernel<<<T, 128, 0, stream>>>(g, static_cast<__nv_bfloat16*>(out), topk_ids, topk_w,
                                              slots, static_cast<const __nv_bfloat16*>(shared_out), k,
                                              H, out_stride, shared_stride);
   // everyone has finished pulling before any rank starts the next call's scatter
-  ep_signal_kernel<<<1, 32, 0, stream>>>(g, 3);
-  ep_wait_kernel<<<1, 32, 0, stream>>>(g, 3, 1, status);
+  if (world > 1) {
+    ep_signal_kernel<<<1, 32, 0, stream>>>(g, 3);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(g, 3, 1, status);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -79,7 +79,7 @@ class EpBuffers:
         def alloc(nbytes):
             ptr = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
-            rc = lib.b200_symm_alloc(max(nbytes, 256), ctypes.byref(ptr), handle)
+            rc = lib.b200_symm_alloc(max(nbytes, 2 << 20), ctypes.byref(ptr), handle)
             if rc != 0:
                 raise RuntimeError(f"EP buffer allocation of {nbytes} bytes failed ({rc})")
             self._own.append(ptr)
@@ -163,7 +163,7 @@ def ep_dispatch(comm, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights
                                  buf.total_recv.data_ptr(), buf.status.data_ptr(), stream)
     if rc != 0:
         raise RuntimeError(f"ep_dispatch failed ({rc})")
-    ops._count(3 if buf.world == 1 else 6)
+    ops._count(3 if buf.world == 1 else 6)  # count, layout, scatter (+ flag kernels)
     # static upper bound on the rows in use (device-side counts decide the real extent)
     rows = buf.cap_rows if buf.world > 1 else max(t * k, 1)
     handle = DispatchHandle(topk_ids, topk_weights, buf.slots, t, rows, buf.expert_offsets)

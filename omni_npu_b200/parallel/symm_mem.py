@@ -72,7 +72,8 @@ class SymmetricMemory:
         def alloc(nbytes: int):
             ptr = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
-            rc = lib.b200_symm_alloc(nbytes, ctypes.byref(ptr), handle)
+            # at least one 2 MiB page per allocation: the IPC handle then names exactly this buffer
+            rc = lib.b200_symm_alloc(max(nbytes, 2 << 20), ctypes.byref(ptr), handle)
             if rc != 0:
                 raise RuntimeError(f"symmetric memory allocation of {nbytes} bytes failed ({rc})")
             self._own.append(ptr)

@@ -101,6 +101,13 @@ class Worker:
             torch.cuda.synchronize(self.device)
             ops.check_status(self.device)
         self.model_runner.capture_model()
+        # ranks may have drifted by seconds (loading, capture); meet on the host so that the
+        # first device-side wait of the serving loop starts with every peer present
+        world = pstate.get_world_group()
+        if world.world_size > 1:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            world.barrier()
 
     # ------------------------------------------------------------- running
     def execute_model(self, out: SchedulerOutput) -> List[int]:
