@@ -59,6 +59,8 @@ int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, voi
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
                     float scale, int window, int splits, void* scratch, int num_cache_blocks,
                     int* status, cudaStream_t stream);
+int b200_kv_p2p_copy(const void* tensors, int num_tensors, const int* src_blocks, const int* dst_blocks,
+                     int num_pairs, long long max_block_bytes, cudaStream_t stream);
 size_t b200_mla_decode_scratch_bytes(int total_tokens, int N, int splits);
 int b200_mla_decode(const void* q, const void* cache, void* out, float* lse, const int* block_tables,
                     const int* seq_lens, const int* topk_indices, int topk, int B, int q_len, int N,
@@ -375,6 +377,22 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   return out;
 }
 
+// Copies KV blocks between two sets of cache tensors (the source may be another GPU's,
+// mapped through CUDA IPC).  desc: int64 [num_tensors, 3] = (src base, dst base, block bytes).
+void kv_p2p_copy(const Tensor& desc, const Tensor& src_blocks, const Tensor& dst_blocks,
+                 int64_t max_block_bytes) {
+  TORCH_CHECK(desc.is_cuda() && desc.scalar_type() == at::kLong && desc.dim() == 2 && desc.size(1) == 3 &&
+                  desc.is_contiguous(),
+              "kv_p2p_copy: desc int64 [n,3] on the device");
+  CHECK_I32(src_blocks);
+  CHECK_I32(dst_blocks);
+  TORCH_CHECK(src_blocks.numel() == dst_blocks.numel(), "kv_p2p_copy: block list sizes differ");
+  c10::cuda::CUDAGuard guard(desc.device());
+  check(b200_kv_p2p_copy(desc.data_ptr(), (int)desc.size(0), src_blocks.data_ptr<int>(),
+                         dst_blocks.data_ptr<int>(), (int)src_blocks.numel(), max_block_bytes, cur_stream()),
+        "kv_p2p_copy");
+}
+
 int64_t mla_decode_scratch_bytes(int64_t T, int64_t N, int64_t splits) {
   return (int64_t)b200_mla_decode_scratch_bytes((int)T, (int)N, (int)splits);
 }
@@ -493,6 +511,7 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gqa_prefill", &gqa_prefill);
   m.def("gqa_decode_scratch_bytes", &gqa_decode_scratch_bytes);
   m.def("gqa_decode", &gqa_decode);
+  m.def("kv_p2p_copy", &kv_p2p_copy);
   m.def("mla_decode_scratch_bytes", &mla_decode_scratch_bytes);
   m.def("mla_decode", &mla_decode);
   m.def("moe_topk", &moe_topk);
