@@ -68,8 +68,10 @@ class LLMEngine:
     def step(self) -> List[RequestOutput]:
         out = self.scheduler.schedule()
         if out.kind == "idle":
-            if out.finished_req_ids:
-                self.worker.model_runner.execute_model(out)
+            # nothing to compute: still let the runner retire rows and start KV loads
+            self.worker.model_runner.execute_model(out)
+            if self.scheduler.has_unfinished():
+                time.sleep(0.001)        # waiting for remote KV
             return []
         tokens = self.worker.execute_model(out)
         finished = self.scheduler.update_from_output(out, tokens)

@@ -404,3 +404,13 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
     _count(2 if splits > 1 else 1)
     return C.mla_decode(q, cache, block_tables, seq_lens, topk_indices, num_seqs, q_len, num_heads, scale,
                         splits, scratch, st.status)
+
+
+# ------------------------------------------------------------------ KV transfer
+def kv_p2p_copy(desc: torch.Tensor, src_blocks: torch.Tensor, dst_blocks: torch.Tensor,
+                max_block_bytes: int) -> None:
+    """One launch copies blocks ``src_blocks[i] -> dst_blocks[i]`` for every cache
+    tensor described by ``desc`` (int64 [n,3]: source base, destination base, block
+    bytes).  Sources may be another GPU's memory mapped through CUDA IPC."""
+    _count(1)
+    _C().kv_p2p_copy(desc, src_blocks, dst_blocks, int(max_block_bytes))

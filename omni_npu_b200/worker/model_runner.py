@@ -207,8 +207,6 @@ class ModelRunner:
     def execute_model(self, out: SchedulerOutput) -> List[int]:
         """Run one scheduled step; returns one sampled token per scheduled sequence
         (meaningless for sequences whose chunk does not end their prompt)."""
-        if out.kind == "idle" or not out.seqs:
-            return []
         ib = self.input_batch
         for rid in out.finished_req_ids:
             ib.remove_request(rid)
@@ -216,6 +214,8 @@ class ModelRunner:
             ib.remove_request(rid)
         if self.kv_connector is not None and out.kv_connector_metadata is not None:
             self.kv_connector.start_load_kv(out.kv_connector_metadata)
+        if out.kind == "idle" or not out.seqs:
+            return []
         n = len(out.seqs)
         ev = None
         if out.kind == "decode":
