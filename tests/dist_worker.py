@@ -153,7 +153,97 @@ def task_symm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
+def task_ep_moe(rank, world, port, workdir, device_kind):
+    """Expert-parallel MoE layer (dispatch -> grouped GEMMs -> combine over peer memory, or the
+    gloo all-to-all path on CPU) against the dense single-process computation."""
+    dev, state = setup(rank, world, port, device_kind)
+    state.init_model_parallel(tp=world, device=dev)
+    from omni_npu_b200 import ops
+    from omni_npu_b200.layers.moe import FusedMoE, select_experts
+    from omni_npu_b200.ops import ref
+    dt = torch.bfloat16 if device_kind == "cuda" else torch.float32
+    E, K, H, I = 16, 4, 256, 128
+    g = torch.Generator().manual_seed(42)
+    full = dict(gate=torch.randn(E, H, generator=g) * 0.1, w13=torch.randn(E, 2 * I, H, generator=g) * 0.05,
+                w2=torch.randn(E, H, I, generator=g) * 0.05,
+                sh13=torch.randn(2 * I, H, generator=g) * 0.05, sh2=torch.randn(H, I, generator=g) * 0.05)
+    layer = FusedMoE(E, K, H, I, dtype=dt, device=dev, renormalize=True, num_shared_experts=1, max_tokens=512)
+    assert layer.ep_size == world and layer.local_experts == E // world
+    lo = layer.expert_start
+    layer.gate.weight.data.copy_(full["gate"])
+    layer.w13.data.copy_(full["w13"][lo:lo + layer.local_experts])
+    layer.w2.data.copy_(full["w2"][lo:lo + layer.local_experts])
+    layer.shared_experts.gate_up_proj.weight.data.copy_(full["sh13"])
+    layer.shared_experts.down_proj.weight.data.copy_(full["sh2"])
+    errs = {}
+    for t in (1, 37, 200):
+        x = (torch.randn(t, H, generator=g) * 0.5).to(dt)
+        xr = x.to(dt).float() if dt == torch.float32 else x
+        logits = ref.gemm(xr.cpu(), full["gate"].to(dt), out_dtype=torch.float32)
+        w, ids = select_experts(logits, K, renormalize=True)
+        want = ref.moe_experts(xr.cpu(), full["w13"].to(dt), full["w2"].to(dt), ids, w).float()
+        sh = ref.gemm(ref.gemm(xr.cpu(), full["sh13"].to(dt), swiglu=True), full["sh2"].to(dt)).float()
+        want = want + sh
+        for rep in range(2):
+            got = layer(x.to(dev))
+        errs[str(t)] = (got.float().cpu() - want).abs().max().item()
+    if device_kind == "cuda":
+        torch.cuda.synchronize()
+        ops.check_status()
+    state.get_world_group().barrier()
+    json.dump({"max_err": errs}, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if layer.buffers is not None:
+        layer.buffers.close()
+    state.destroy_distributed()
+
+
+def task_kv_pull(rank, world, port, workdir, device_kind):
+    """Rank 0 owns a KV cache, rank 1 maps it through CUDA IPC and pulls blocks with the copy kernel."""
+    dev, state = setup(rank, world, port, "cuda")
+    state.init_model_parallel(tp=1, dp=world, device=dev) if False else state.init_model_parallel(tp=world, device=dev)
+    from omni_npu_b200.kv_transfer.manager import KVLinkManager, make_cluster_id
+    g = state.get_world_group()
+    mgr = KVLinkManager(make_cluster_id("127.0.0.1", 30000 + rank, 1), 0, dev)
+    torch.manual_seed(7)
+    caches = [(torch.randn(64, 2, 16, 128, device=dev, dtype=torch.bfloat16),
+               torch.randn(64, 2, 16, 128, device=dev, dtype=torch.bfloat16)) for _ in range(4)]
+    if rank == 1:
+        for k, v in caches:
+            k.zero_(), v.zero_()
+    export = mgr.register_memory(caches)
+    exports = g.all_gather_object(export)
+    res = {}
+    if rank == 1:
+        src_blocks, dst_blocks = [3, 9, 63, 0, 17], [5, 6, 7, 8, 60]
+        ev = mgr.pull_kv(exports[0].cluster_id, 0, src_blocks, dst_blocks, refresh=lambda: exports[0])
+        ev.synchronize()
+        torch.manual_seed(7)
+        ok = True
+        for k, v in caches:
+            rk = torch.randn(64, 2, 16, 128, device=dev, dtype=torch.bfloat16)
+            rv = torch.randn(64, 2, 16, 128, device=dev, dtype=torch.bfloat16)
+            ok &= torch.equal(k[dst_blocks], rk[src_blocks]) and torch.equal(v[dst_blocks], rv[src_blocks])
+            ok &= bool(k[1].abs().sum() == 0)
+        res["byte_exact"] = bool(ok)
+        # bandwidth on a larger pull
+        n = 60
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(10):
+            ev = mgr.pull_kv(exports[0].cluster_id, 0, list(range(n)), list(range(n)))
+        ev.synchronize()
+        t1.record()
+        torch.cuda.synchronize()
+        res["gbs"] = 10 * n * 8 * (2 * 16 * 128 * 2) / (t0.elapsed_time(t1) * 1e-3) / 1e9
+    g.barrier()
+    mgr.close()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.destroy_distributed()
+
+
+TASKS = {"ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

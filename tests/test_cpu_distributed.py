@@ -42,3 +42,10 @@ def test_tensor_parallel_engine_matches_plain_pytorch():
     for p, toks in zip(prompts, res[0]["tokens"]):
         assert toks == refm.greedy_generate(weights, cfg, p, 12)
     assert res[0]["tokens"] == res[1]["tokens"]
+
+
+def test_expert_parallel_moe_two_ranks_gloo():
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("ep_moe", 2, d)
+    for r in res:
+        assert max(r["max_err"].values()) < 1e-4, r
