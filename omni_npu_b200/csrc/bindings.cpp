@@ -17,6 +17,9 @@ int b200_gemm(const void* A, const void* W, void* C, const void* bias, const voi
               int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu,
               int BN, int splits, int cluster_split, void* workspace, int* counters, int* status,
               int max_ctas, cudaStream_t stream);
+int b200_gemm_pair(const void* A, const void* W, void* C, const void* bias, const void* residual,
+                   int M, int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32,
+                   int swiglu, int BN, int* status, int max_ctas, cudaStream_t stream);
 int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_offsets,
                       int num_experts, int total_rows, int N, int K, int lda, int ldc,
                       int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
@@ -145,6 +148,41 @@ Tensor gemm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& bias,
                   status.data_ptr<int>(),
                   (int)max_ctas, cur_stream()),
         "gemm");
+  return c;
+}
+
+// Same contract as gemm() without split-K, run by CTA pairs: one 256 x BN tile per pair of SMs
+// (tcgen05 cta_group::2), each SM staging half of the weight tile.
+Tensor gemm_pair(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& bias,
+                 const c10::optional<Tensor>& residual, bool out_fp32, bool swiglu, int64_t bn,
+                 const Tensor& status, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_pair: 2-D CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == w.scalar_type(), "gemm_pair: dtype mismatch");
+  const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK(fp8 || a.scalar_type() == at::kBFloat16, "gemm_pair: bf16 or float8_e4m3fn inputs");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1, "gemm_pair: K must be contiguous");
+  const int M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "gemm_pair: K mismatch");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int n_out = swiglu ? N / 2 : N;
+  Tensor c = torch::empty({M, n_out}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  const void* bias_p = nullptr;
+  const void* res_p = nullptr;
+  if (bias.has_value()) {
+    CHECK_CUDA_BF16(*bias);
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "gemm_pair: bias [N]");
+    bias_p = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    CHECK_CUDA_BF16(*residual);
+    TORCH_CHECK(residual->is_contiguous() && residual->size(0) == M && residual->size(1) == n_out,
+                "gemm_pair: residual [M,N] contiguous");
+    res_p = residual->data_ptr();
+  }
+  check(b200_gemm_pair(a.data_ptr(), w.data_ptr(), c.data_ptr(), bias_p, res_p, M, N, K,
+                       (int)a.stride(0), (int)w.stride(0), n_out, fp8 ? 1 : 0, out_fp32 ? 1 : 0,
+                       swiglu ? 1 : 0, (int)bn, status.data_ptr<int>(), (int)max_ctas, cur_stream()),
+        "gemm_pair");
   return c;
 }
 
@@ -498,6 +536,7 @@ Tensor sample(const Tensor& logits, const c10::optional<Tensor>& temperature,
 TORCH_LIBRARY(omni_b200, m) {
   m.def("gemm_plan", &gemm_plan);
   m.def("gemm", &gemm);
+  m.def("gemm_pair", &gemm_pair);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);
   m.def("fused_add_rms_norm", &fused_add_rms_norm);

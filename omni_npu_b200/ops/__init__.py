@@ -154,20 +154,33 @@ def check_status(device: Optional[torch.device] = None) -> None:
 
 
 # ------------------------------------------------------------------------ GEMM
+# smallest M routed to the CTA-pair GEMM (0 = never); prefill-sized problems only
+PAIR_MIN_M = int(os.environ.get("OMNI_B200_GEMM_PAIR_MIN_M", "0"))
+
 def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         swiglu: bool = False, bn: int = 0, splits: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         swiglu: bool = False, bn: int = 0, splits: int = 0, max_ctas: int = 0,
+         pair: Optional[bool] = None) -> torch.Tensor:
     """``a[M,K] @ w[N,K].T`` (+bias, +residual).  bf16 or float8_e4m3fn inputs,
     fp32 accumulation, bf16 (default) or fp32 output.  ``swiglu`` fuses
     silu(gate)*up for weights laid out by :func:`ref.interleave_gate_up`.
     ``splits`` > 1 forces split-K (as a thread-block cluster when it fits), a
-    negative value forces the workspace variant with |splits| slices."""
+    negative value forces the workspace variant with |splits| slices.
+    ``pair`` selects the CTA-pair kernel (256-row tiles over two SMs); by default
+    it runs for M >= PAIR_MIN_M when no split-K was asked for."""
     if not a.is_cuda:
         return ref.gemm(a, w, bias, residual, out_dtype, swiglu)
     C = _C()
     st = device_state(a.device)
     m, k = a.shape
     n = w.shape[0]
+    if pair is None:
+        pair = PAIR_MIN_M > 0 and m >= PAIR_MIN_M and splits == 0 and bn == 0
+    if pair:
+        n_eff = n
+        pbn = bn if bn > 0 else (256 if n_eff >= 256 else max(32, ((n_eff + 31) // 32) * 32))
+        _count(1)
+        return C.gemm_pair(a, w, bias, residual, out_dtype == torch.float32, swiglu, pbn, st.status, max_ctas)
     key = (m, n, k, a.dtype.itemsize, swiglu, bn, splits)
     plan = st.plans.get(key)
     if plan is None:

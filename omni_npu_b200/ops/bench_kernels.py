@@ -128,7 +128,12 @@ def bench_gemm(args):
         w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
         bn, sp = args.bn, args.splits
         plan = torch.ops.omni_b200.gemm_plan(m, n, k, 2, False, bn, sp)
-        t = time_fn(lambda: ops.gemm(a, w, bn=bn, splits=sp), iters=args.iters)
+        if args.pair and m >= 256:
+            t = time_fn(lambda: ops.gemm(a, w, bn=bn, pair=True), iters=args.iters)
+            plan = (bn or 256, 1)
+            label = label + " [pair]"
+        else:
+            t = time_fn(lambda: ops.gemm(a, w, bn=bn, splits=sp), iters=args.iters)
         tc = time_fn(lambda: torch.matmul(a, w.t()), iters=args.iters)
         fl = 2.0 * m * n * k
         by = 2.0 * (m * k + n * k + m * n)
@@ -218,6 +223,7 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--pair", action="store_true", help="gemm: run M >= 256 shapes on the CTA-pair kernel")
     ap.add_argument("--graph", action="store_true",
                     help="gemm: time decode-shaped GEMMs back to back inside a CUDA graph")
     ap.add_argument("--b", type=int, help="attn: batch size of a single case")

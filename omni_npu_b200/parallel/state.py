@@ -254,3 +254,34 @@ def destroy_distributed() -> None:
     destroy_model_parallel()
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def finish_process(engine=None, code: int = 0, deadline_s: float = 30.0) -> None:
+    """End a rank of a multi-process program: barrier, release peer-mapped memory and
+    CUDA graphs (``engine.shutdown()``), leave the process groups, then ``os._exit``.
+
+    A watchdog ends the process after ``deadline_s`` even if a library finaliser
+    blocks: communicator tear-down has been seen to wait for minutes when peers
+    unmap shared buffers in a different order."""
+    import os
+    import sys
+    import threading
+
+    def _now():
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(code)
+
+    timer = threading.Timer(deadline_s, _now)
+    timer.daemon = True
+    timer.start()
+    try:
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            world = getattr(_S, "world", None)
+            world.barrier() if world is not None else dist.barrier()   # host-side (gloo) when set up
+        if engine is not None:
+            engine.shutdown()
+        destroy_distributed()
+    except Exception as e:  # best effort: the process ends either way
+        print(f"finish_process: {type(e).__name__}: {e}", file=sys.stderr)
+    _now()

@@ -81,6 +81,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs]},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if device_kind == "cuda":
+        state.finish_process(llm.engine)
     state.get_world_group().barrier()
     state.destroy_distributed()
 
@@ -194,6 +196,8 @@ def task_ep_moe(rank, world, port, workdir, device_kind):
     json.dump({"max_err": errs}, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if layer.buffers is not None:
         layer.buffers.close()
+    if device_kind == "cuda":
+        state.finish_process()
     state.destroy_distributed()
 
 
@@ -237,10 +241,10 @@ def task_kv_pull(rank, world, port, workdir, device_kind):
         t1.record()
         torch.cuda.synchronize()
         res["gbs"] = 10 * n * 8 * (2 * 16 * 128 * 2) / (t0.elapsed_time(t1) * 1e-3) / 1e9
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     g.barrier()
     mgr.close()
-    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
-    state.destroy_distributed()
+    state.finish_process()
 
 
 TASKS = {"ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}

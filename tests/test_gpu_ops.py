@@ -82,6 +82,43 @@ def test_gemm_epilogues():
     _close(fused, want, 0.06, 3e-2)
 
 
+@pytest.mark.parametrize("m,n,k,bn", [(256, 256, 128, 0), (512, 1024, 4096, 0), (300, 200, 136, 0),
+                                      (1000, 1024, 2048, 128), (8192, 4096, 4096, 0), (257, 96, 64, 96),
+                                      (2048, 6144, 4096, 192), (130, 4096, 512, 32)])
+def test_gemm_cta_pair(m, n, k, bn):
+    """256-row tiles computed by two SMs (tcgen05 cta_group::2)."""
+    torch.manual_seed(6)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    out = ops.gemm(a, w, bn=bn, pair=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(out, ref.gemm(a.cpu(), w.cpu()), atol=2e-2 * math.sqrt(k / 64), rtol=2e-2)
+    assert torch.equal(out, ops.gemm(a, w, bn=bn, pair=True))
+
+
+def test_gemm_cta_pair_epilogues_and_fp8():
+    torch.manual_seed(7)
+    m, n, k = 700, 768, 1024
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    _close(ops.gemm(a, w, bias, res, pair=True), ref.gemm(a.cpu(), w.cpu(), bias.cpu(), res.cpu()), 0.08, 2e-2)
+    o32 = ops.gemm(a, w, out_dtype=torch.float32, pair=True)
+    assert o32.dtype == torch.float32
+    _close(o32, ref.gemm(a.cpu(), w.cpu(), out_dtype=torch.float32), 2e-2, 1e-2)
+    i = n // 2
+    wi = ref.interleave_gate_up(w[:i], w[i:])
+    fused = ops.gemm(a, wi, swiglu=True, pair=True)
+    _close(fused, ref.silu_and_mul(ref.gemm(a.cpu(), w.cpu(), out_dtype=torch.float32)), 0.06, 3e-2)
+    a8 = (torch.randn(512, 1024, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    w8 = (torch.randn(512, 1024, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    _close(ops.gemm(a8, w8, pair=True), ref.gemm(a8.cpu(), w8.cpu()), 0.25, 2e-2)
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
 def test_grouped_gemm():
     torch.manual_seed(3)
     e, n, k = 8, 512, 1024
