@@ -97,8 +97,9 @@ class LinearBase(nn.Module):
         self.group = group or pstate.get_layer_group(_layer_key(prefix)) or pstate.get_tp_group()
         self.tp_size = self.group.world_size
         self.tp_rank = self.group.rank_in_group
-        self.x_transform = x_transform
-        self.y_transform = y_transform
+        planned_x, planned_y = pstate.get_layer_transforms(_layer_key(prefix))
+        self.x_transform = x_transform if x_transform is not None else planned_x
+        self.y_transform = y_transform if y_transform is not None else planned_y
         self.quant_method = quant_method or UnquantizedLinearMethod()
         self.dtype = dtype
         self._has_bias = bias

@@ -110,6 +110,7 @@ class _State:
     ep: Optional[GroupCoordinator] = None
     local: Optional[GroupCoordinator] = None
     layer_groups: Optional[Dict[str, GroupCoordinator]] = None
+    layer_transforms: Optional[Dict[str, tuple]] = None
     backend: str = "gloo"
     device: Optional[torch.device] = None
     initialized: bool = False
@@ -162,6 +163,7 @@ def init_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, device: Optional[
     _S.ep = make("ep", grid.permute(1, 0, 2).reshape(pp, dp * tp).tolist())
     _S.local = _S.world
     _S.layer_groups = {}
+    _S.layer_transforms = {}
     _S.initialized = True
 
 
@@ -239,6 +241,46 @@ def get_layer_group(key: str) -> Optional[GroupCoordinator]:
     return _S.layer_groups.get(key)
 
 
+_TRANSFORM_NAMES = {"none": None, "noop": None, "allreduce": "AllReduce", "allgather": "AllGather",
+                    "reducescatter": "ReduceScatter", "all2all": "ALL2ALL", "alltoall": "ALL2ALL"}
+
+
+def _transform_name(spec) -> Optional[str]:
+    if spec is None:
+        return None
+    kind = spec.get("type") if isinstance(spec, dict) else spec
+    key = str(kind).replace("_", "").lower()
+    if key not in _TRANSFORM_NAMES:
+        raise ValueError(f"unknown transform type {kind!r}")
+    return _TRANSFORM_NAMES[key]
+
+
+def apply_layer_parallel_config(layer_parallel_config: Dict[str, dict]) -> Dict[str, GroupCoordinator]:
+    """Create the per-layer groups and record the input / output transforms a
+    deployment plan asks for.  ``layer_parallel_config`` maps a layer key (the last
+    two components of the module name, e.g. ``"mlp.down_proj"``) to
+    ``{"tp_size_or_ranks": int | [[ranks]...], "x_transform": {"type": ...},
+    "y_transform": {"type": ...}}``.  Every rank must call this with the same
+    dictionary (group creation is collective).  Same role as
+    ``init_layer_parallel_groups`` in omni_npu/v1/distributed/parallel_state_ext.py:380-545."""
+    ensure_initialized()
+    made = {}
+    for key in sorted(layer_parallel_config):
+        spec = layer_parallel_config[key] or {}
+        size = spec.get("tp_size_or_ranks", None)
+        if size is not None:
+            made[key] = register_layer_group(key, size)
+        _S.layer_transforms[key] = (_transform_name(spec.get("x_transform")),
+                                    _transform_name(spec.get("y_transform")))
+    return made
+
+
+def get_layer_transforms(key: str) -> tuple:
+    """(x_transform, y_transform) recorded for a layer key, (None, None) if none."""
+    ensure_initialized()
+    return (_S.layer_transforms or {}).get(key, (None, None))
+
+
 def destroy_model_parallel() -> None:
     for g in (_S.tp, _S.pp, _S.dp, _S.ep, _S.world):
         if g is not None:
@@ -247,6 +289,7 @@ def destroy_model_parallel() -> None:
         g.destroy()
     _S.world = _S.tp = _S.pp = _S.dp = _S.ep = _S.local = None
     _S.layer_groups = None
+    _S.layer_transforms = None
     _S.initialized = False
 
 
