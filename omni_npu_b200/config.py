@@ -307,8 +307,12 @@ class KVTransferConfig:
 
 @dataclass
 class SpeculativeConfig:
-    method: Optional[str] = None              # "deepseek_mtp" | "mtp" | None
-    num_speculative_tokens: int = 0
+    # who proposes draft tokens: "ngram" (prompt lookup, any model), "mtp" / "deepseek_mtp"
+    # (the model's multi-token-prediction head); None = no speculation
+    method: Optional[str] = None
+    num_speculative_tokens: int = 0           # drafts per request and step
+    prompt_lookup_max: int = 4
+    prompt_lookup_min: int = 2
 
 
 @dataclass

@@ -24,6 +24,8 @@ int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_o
                       int num_experts, int total_rows, int N, int K, int lda, int ldc,
                       int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
                       cudaStream_t stream);
+int b200_spec_verify(const int* draft, const int* target, const int* bonus, const int* cu, int* out,
+                     int* num_out, int B, int max_spec, cudaStream_t stream);
 int b200_rmsnorm(void* out, const void* x, void* residual, const void* w, float eps, long long rows,
                  int H, long long x_stride, long long out_stride, long long res_stride,
                  cudaStream_t stream);
@@ -94,6 +96,24 @@ inline void check(int rc, const char* what) {
   TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16, #t " must be a CUDA bf16 tensor")
 #define CHECK_I32(t) \
   TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kInt && (t).is_contiguous(), #t " must be a contiguous CUDA int32 tensor")
+
+// Speculative decoding: accept drafts while they equal the target's tokens.
+// Returns (tokens [B, max_spec+1] padded with -1, count [B]).
+std::tuple<Tensor, Tensor> spec_verify(const Tensor& draft, const Tensor& target, const Tensor& bonus,
+                                       const Tensor& cu, int64_t max_spec) {
+  for (const Tensor* t : {&draft, &target, &bonus, &cu})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "spec_verify: int32 CUDA");
+  const int B = (int)cu.numel() - 1;
+  TORCH_CHECK(bonus.numel() >= B && draft.numel() == target.numel(), "spec_verify: shapes");
+  c10::cuda::CUDAGuard guard(draft.device());
+  Tensor out = torch::empty({B, max_spec + 1}, draft.options());
+  Tensor num = torch::empty({B}, draft.options());
+  check(b200_spec_verify(draft.data_ptr<int>(), target.data_ptr<int>(), bonus.data_ptr<int>(),
+                         cu.data_ptr<int>(), out.data_ptr<int>(), num.data_ptr<int>(), B, (int)max_spec,
+                         cur_stream()),
+        "spec_verify");
+  return {out, num};
+}
 
 // (BN, splits, workspace bytes, counters, cluster flag) for a problem.
 std::tuple<int64_t, int64_t, int64_t, int64_t, int64_t> gemm_plan(int64_t M, int64_t N, int64_t K,
@@ -534,6 +554,7 @@ Tensor sample(const Tensor& logits, const c10::optional<Tensor>& temperature,
 }  // namespace
 
 TORCH_LIBRARY(omni_b200, m) {
+  m.def("spec_verify", &spec_verify);
   m.def("gemm_plan", &gemm_plan);
   m.def("gemm", &gemm);
   m.def("gemm_pair", &gemm_pair);

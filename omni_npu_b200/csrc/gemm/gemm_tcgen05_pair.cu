@@ -14,6 +14,8 @@
 //   tmem_empty[a]  leader's copy only, 8 arrivals (4 epilogue warps of each CTA).
 // TMA loads are plain per-CTA loads (no multicast).  All waits are bounded.
 
+#include <cstdlib>
+
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 
@@ -22,6 +24,12 @@ namespace b200 {
 static constexpr int kPBM = 128;        // rows of A per CTA (256 per pair)
 static constexpr int kPRowBytes = 128;
 static constexpr int kPThreads = 192;
+
+// cycle counters of CTA 0's MMA and producer threads, written only with diagnostics bit 64:
+// [0] cycles waiting for full barriers, [1] issuing MMAs, [2] committing, [3] waiting for a free
+// accumulator, [4] full waits, [5] of which already complete, [6] producer cycles waiting for
+// empty barriers, [7] empty barriers already free, [8] stages issued
+__device__ long long g_pair_prof[16];
 
 struct PairParams {
   int M, N, K;
@@ -33,6 +41,11 @@ struct PairParams {
   int elem_bytes;
   int tmem_cols, acc_stride;
   int ldc, out_fp32, swiglu;
+  // timing diagnostics only (results are wrong), a bit mask: 1 stages are loaded once and then reused,
+  // 2 no MMAs are issued, 4 the MMA thread does not wait for full barriers, 8 no empty-barrier
+  // hand-back (the producer does not wait for it either), 16 one lane per epilogue warp polls,
+  // 64 CTA 0 records cycle counters in g_pair_prof
+  int diag;
   void* C;
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
@@ -100,19 +113,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
+      const bool prof = (p.diag & 64) && blockIdx.x == 0;
+      long long c_empty = 0, n_empty_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
         const int mb = static_cast<int>(t % p.num_m_blocks), nb = static_cast<int>(t / p.num_m_blocks);
         const int m0 = mb * 2 * kPBM + cta_rank * kPBM;
         const int n0 = nb * p.BN + cta_rank * (p.BN / 2);
         for (int k = 0; k < p.k_iters; ++k) {
-          if (*abort_flag || !mbar_wait_cluster(&empty_bar[stage], phase ^ 1)) {
+          const long long tp0 = prof ? clock64() : 0;
+          if (prof && mbar_test(&empty_bar[stage], phase ^ 1)) ++n_empty_ready;
+          if ((p.diag & 4) && issued >= p.stages) {
+            ok = false;   // nobody waits for full barriers: the producer is done after the first fill
+            break;
+          }
+          if (*abort_flag || (!(p.diag & 8) && !mbar_wait_cluster(&empty_bar[stage], phase ^ 1))) {
             if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
             *abort_flag = 1;
             ok = false;
             break;
           }
+          if (prof) c_empty += clock64() - tp0;
           // the leader's barrier collects the bytes of both CTAs
           const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          if ((p.diag & 1) && issued >= p.stages) {
+            // diagnostics: hand the stage back without reloading it
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 0u);
+            ++issued;
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           if (leader)
             mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>(2 * (a_stage_bytes + w_stage_bytes)));
           const int kcoord = k * (kPRowBytes / p.elem_bytes);
@@ -125,7 +157,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
-      (void)issued;
+      if (prof) {
+        g_pair_prof[6] = c_empty;
+        g_pair_prof[7] = n_empty_ready;
+        g_pair_prof[8] = issued;
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
@@ -136,20 +172,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const bool prof = (p.diag & 64) && blockIdx.x == 0;
+      long long c_wait = 0, c_issue = 0, c_commit = 0, c_tmem = 0, n_wait = 0, n_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
+        long long t0 = prof ? clock64() : 0;
         if (*abort_flag || !mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1)) {
           if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutTmemEmpty);
           *abort_flag = 1;
           break;
         }
+        if (prof) c_tmem += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
         for (int k = 0; k < p.k_iters; ++k) {
-          if (*abort_flag || !mbar_wait_cluster(&full_bar[stage], phase)) {
+          if (prof) {
+            t0 = clock64();
+            ++n_wait;
+            if (mbar_test(&full_bar[stage], phase)) ++n_ready;
+          }
+          if (*abort_flag || (!(p.diag & 4) && !mbar_wait_cluster(&full_bar[stage], phase))) {
             if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
             *abort_flag = 1;
             ok = false;
             break;
+          }
+          if (prof) {
+            const long long t1 = clock64();
+            c_wait += t1 - t0;
+            t0 = t1;
           }
           tc_fence_after_sync();
           const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes));
@@ -157,29 +207,40 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t accum = (k > 0 || kk > 0) ? 1u : 0u;
+            if (p.diag & 2) continue;
             if constexpr (FP8) {
               umma_f8_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
             } else {
               umma_f16_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
             }
           }
+          if (prof) {
+            const long long t1 = clock64();
+            c_issue += t1 - t0;
+            t0 = t1;
+          }
           // the stage is free in both CTAs once these MMAs retire
-          const uint32_t e = smem_u32(&empty_bar[stage]);
-          tc_commit_pair(e);
-          tc_commit_pair(mapa_shared(e, 1));
+          if (!(p.diag & 8)) tc_commit_pair_both(smem_u32(&empty_bar[stage]));
+          if (prof) c_commit += clock64() - t0;
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        const uint32_t f = smem_u32(&tmem_full[acc]);
-        tc_commit_pair(f);
-        tc_commit_pair(mapa_shared(f, 1));
+        tc_commit_pair_both(smem_u32(&tmem_full[acc]));
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
         }
+      }
+      if (prof) {
+        g_pair_prof[0] = c_wait;
+        g_pair_prof[1] = c_issue;
+        g_pair_prof[2] = c_commit;
+        g_pair_prof[3] = c_tmem;
+        g_pair_prof[4] = n_wait;
+        g_pair_prof[5] = n_ready;
       }
     }
   } else {
@@ -191,7 +252,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int mb = static_cast<int>(t % p.num_m_blocks), nb = static_cast<int>(t / p.num_m_blocks);
       const int m0 = mb * 2 * kPBM + cta_rank * kPBM;
       const int n0 = nb * p.BN;
-      bool ok = !*abort_flag && mbar_wait_cluster(&tmem_full[acc], acc_phase);
+      bool ok = true;
+      if (!(p.diag & 16) || lane == 0) ok = !*abort_flag && mbar_wait_cluster(&tmem_full[acc], acc_phase);
+      if (p.diag & 16) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       {
         uint32_t all_ok;
         asm volatile(
@@ -369,6 +432,11 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const PairP
 
 using namespace b200;
 
+// Copies the diagnostics counters (see g_pair_prof) to the host.
+extern "C" int b200_gemm_pair_prof(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_pair_prof, sizeof(long long) * 16) == cudaSuccess ? 0 : -1;
+}
+
 // Same contract as b200_gemm (no split-K).  BN: multiple of 32 in [32, 256].
 extern "C" int b200_gemm_pair(const void* A, const void* W, void* C, const void* bias, const void* residual,
                               int M, int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32,
@@ -396,6 +464,13 @@ extern "C" int b200_gemm_pair(const void* A, const void* W, void* C, const void*
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.status = status;
+  {
+    static const int diag = [] {
+      const char* e = getenv("OMNI_B200_GEMM_DIAG");
+      return e ? atoi(e) : 0;
+    }();
+    p.diag = diag;
+  }
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kPRowBytes / eb;

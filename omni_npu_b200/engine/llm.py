@@ -43,8 +43,10 @@ class LLMEngine:
         reserved = getattr(self.worker.get_model(), "num_reserved_kv_blocks", 0)
         self.scheduler = Scheduler(config.scheduler, config.cache, num_blocks, reserved, connector)
         self._ids = itertools.count()
-        self.stats = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "h2d_bytes": 0,
-                      "d2h_bytes": 0, "output_tokens": 0}
+        self.stats = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "spec_decode_steps": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0, "output_tokens": 0}
+        from ..spec_decode import make_proposer
+        self.proposer = make_proposer(config.speculative, self.worker.model_runner)
 
     @property
     def device(self) -> torch.device:
@@ -74,16 +76,35 @@ class LLMEngine:
                 time.sleep(0.001)        # waiting for remote KV
             return []
         tokens = self.worker.execute_model(out)
-        finished = self.scheduler.update_from_output(out, tokens)
+        drafts = None
+        if self.proposer is not None and any(s.samples for s in out.seqs):
+            drafts = self._propose(out, tokens)
+        before = sum(len(s.request.output_token_ids) for s in out.seqs)
+        finished = self.scheduler.update_from_output(out, tokens, drafts=drafts)
         st = self.stats
         st["steps"] += 1
         st[out.kind + "_steps"] += 1
         st["h2d_bytes"] += self.worker.model_runner.input_batch.h2d_bytes_last
         st["d2h_bytes"] += self.worker.model_runner.d2h_bytes_last
-        st["output_tokens"] += sum(1 for s in out.seqs if s.samples)
+        st["output_tokens"] += sum(len(s.request.output_token_ids) for s in out.seqs) - before
         for r in finished:
             self.worker.model_runner.input_batch.remove_request(r.request_id)
         return [RequestOutput.from_request(r) for r in finished]
+
+    def _propose(self, out, tokens) -> List[List[int]]:
+        """Draft tokens for the next step of every sequence that just produced a token.
+        Host-side proposers see the token history including this step's tokens."""
+        prop = self.proposer
+        if getattr(prop, "needs_hidden_states", False):
+            return prop.propose(out, tokens)
+        drafts: List[List[int]] = []
+        for seq, tok in zip(out.seqs, tokens):
+            if not seq.samples:
+                drafts.append([])
+                continue
+            new = list(tok) if isinstance(tok, (list, tuple)) else [tok]
+            drafts.append(prop.propose_one(seq.request.all_token_ids + [int(t) for t in new]))
+        return drafts
 
     def shutdown(self) -> None:
         self.worker.shutdown()
@@ -158,7 +179,9 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
     spec = kw.pop("speculative_config", None)
     if isinstance(spec, dict):
         spec = SpeculativeConfig(method=spec.get("method"),
-                                 num_speculative_tokens=spec.get("num_speculative_tokens", 0))
+                                 num_speculative_tokens=spec.get("num_speculative_tokens", 0),
+                                 prompt_lookup_max=spec.get("prompt_lookup_max", 4),
+                                 prompt_lookup_min=spec.get("prompt_lookup_min", 2))
     cfg = EngineConfig(model=model, cache=cache, parallel=par, scheduler=sched,
                        compilation=comp or CompilationConfig(), kv_transfer=kvt,
                        speculative=spec or SpeculativeConfig(), model_path=model_path,

@@ -26,11 +26,12 @@ class ScheduledSeq:
     start: int             # tokens already in the KV cache before this step
     num_new_tokens: int    # tokens computed in this step
     samples: bool          # whether this step yields an output token for the request
+    spec_token_ids: List[int] = field(default_factory=list)   # draft tokens verified in this step
 
 
 @dataclass
 class SchedulerOutput:
-    kind: str = "idle"                      # "prefill" | "decode" | "idle"
+    kind: str = "idle"                      # "prefill" | "decode" | "spec_decode" | "idle"
     seqs: List[ScheduledSeq] = field(default_factory=list)
     num_tokens: int = 0
     preempted: List[str] = field(default_factory=list)
@@ -55,6 +56,7 @@ class Scheduler:
         self.kv_connector = kv_connector
         self._finished_since_last: List[str] = []
         self._step = 0
+        self.spec_stats = {"drafted": 0, "accepted": 0}
 
     # ------------------------------------------------------------------ intake
     def add_request(self, req: Request) -> None:
@@ -188,24 +190,30 @@ class Scheduler:
             self._finish_output(out)
             return out
 
-        # 2) decode: one token for every running request
+        # 2) decode: one token for every running request, plus its draft tokens to verify
         decode: List[ScheduledSeq] = []
         i = 0
         while i < len(self.running):
             req = self.running[i]
-            while not self._ensure_blocks(req, req.num_tokens):
+            # drafts must leave room for the bonus token inside max_model_len and the budget
+            room = min(self.cfg.max_model_len - req.num_tokens - 1,
+                       req.sampling_params.max_tokens - len(req.output_token_ids) - 1)
+            drafts = req.spec_token_ids[: max(0, room)] if req.spec_token_ids else []
+            while not self._ensure_blocks(req, req.num_tokens + len(drafts)):
                 victim = self._preempt_one(protect=req)
                 if victim is None:
                     raise RuntimeError("KV cache too small for a single sequence")
                 out.preempted.append(victim.request_id)
+                victim.spec_token_ids = []
                 decode = [s for s in decode if s.request is not victim]
             if req in self.running:
-                decode.append(ScheduledSeq(req, req.num_computed_tokens, 1, True))
+                decode.append(ScheduledSeq(req, req.num_computed_tokens, 1 + len(drafts), True, list(drafts)))
             i = self.running.index(req) + 1
         if decode:
-            out.kind = "decode"
+            spec = any(s.spec_token_ids for s in decode)
+            out.kind = "spec_decode" if spec else "decode"
             out.seqs = decode
-            out.num_tokens = len(decode)
+            out.num_tokens = sum(s.num_new_tokens for s in decode)
         self._finish_output(out)
         return out
 
@@ -215,25 +223,43 @@ class Scheduler:
             out.kv_connector_metadata = self.kv_connector.build_connector_meta(out)
 
     # ---------------------------------------------------------------- update
-    def update_from_output(self, out: SchedulerOutput, sampled: List[int],
-                           now: Optional[float] = None) -> List[Request]:
-        """Apply one step's results.  ``sampled[i]`` belongs to ``out.seqs[i]``.
-        Returns requests that finished in this step."""
+    def update_from_output(self, out: SchedulerOutput, sampled: List, now: Optional[float] = None,
+                           drafts: Optional[List[List[int]]] = None) -> List[Request]:
+        """Apply one step's results.  ``sampled[i]`` belongs to ``out.seqs[i]``: one token,
+        or (after a verification step) the list of tokens the step settled.  ``drafts[i]``
+        are the draft tokens proposed for the request's next step.  Returns requests that
+        finished in this step."""
         finished: List[Request] = []
         now = time.monotonic() if now is None else now
-        for seq, tok in zip(out.seqs, sampled):
+        for idx, (seq, tok) in enumerate(zip(out.seqs, sampled)):
             req = seq.request
             if req.is_finished:
                 continue
-            req.num_computed_tokens = seq.start + seq.num_new_tokens
+            toks = list(tok) if isinstance(tok, (list, tuple)) else [tok]
+            if seq.spec_token_ids:
+                # the KV entries of the accepted drafts (and of the token before them) are valid;
+                # the last emitted token has none yet
+                req.num_computed_tokens = seq.start + len(toks)
+                self.spec_stats["drafted"] += len(seq.spec_token_ids)
+                self.spec_stats["accepted"] += len(toks) - 1
+            else:
+                req.num_computed_tokens = seq.start + seq.num_new_tokens
+            req.spec_token_ids = []
             if not seq.samples:
                 continue
-            req.append_output(tok, now)
-            if req.check_stop() or req.num_tokens >= self.cfg.max_model_len:
-                if not req.is_finished:
-                    req.status = RequestStatus.FINISHED_LENGTH_CAPPED
-                    req.finish_time = now
+            done = False
+            for t in toks:
+                req.append_output(t, now)
+                if req.check_stop() or req.num_tokens >= self.cfg.max_model_len:
+                    if not req.is_finished:
+                        req.status = RequestStatus.FINISHED_LENGTH_CAPPED
+                        req.finish_time = now
+                    done = True
+                    break
+            if done:
                 finished.append(req)
+            elif drafts is not None and idx < len(drafts) and drafts[idx]:
+                req.spec_token_ids = [int(t) for t in drafts[idx]]
         for req in finished:
             self.running.remove(req)
             self._release(req)

@@ -381,6 +381,16 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
     return _C().sample(logits, temperature, top_k, top_p, seeds, step_offset)
 
 
+def spec_verify(draft: torch.Tensor, target: torch.Tensor, bonus: torch.Tensor, cu: torch.Tensor,
+                max_spec: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Accept draft tokens while they equal the target's tokens (see ref.spec_verify)."""
+    if not draft.is_cuda:
+        return ref.spec_verify(draft, target, bonus, cu, max_spec)
+    _count(1)
+    return _C().spec_verify(draft.int().contiguous(), target.int().contiguous(), bonus.int().contiguous(),
+                            cu.int().contiguous(), max_spec)
+
+
 # ------------------------------------------------------------------------- MoE
 def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, sigmoid: bool = False,
              n_group: int = 1, topk_group: int = 1, renorm: bool = False,

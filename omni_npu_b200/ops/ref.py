@@ -348,3 +348,28 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
             p = torch.softmax(qq @ kv.t() * scale, dim=-1)
             out[t] = (p @ kv[:, :512]).reshape(-1).to(q.dtype)
     return out
+
+
+def spec_verify(draft: torch.Tensor, target: torch.Tensor, bonus: torch.Tensor, cu: torch.Tensor,
+                max_spec: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """draft/target [T] tokens at the draft positions (request b owns cu[b]:cu[b+1]),
+    bonus [B].  Row b of the result: target tokens up to and including the first
+    mismatch with the draft, plus the bonus token when every draft matched; -1 padded."""
+    b = cu.numel() - 1
+    out = torch.full((b, max_spec + 1), -1, dtype=torch.int32, device=draft.device)
+    num = torch.zeros(b, dtype=torch.int32, device=draft.device)
+    cul = cu.tolist()
+    d, t, bo = draft.tolist(), target.tolist(), bonus.tolist()
+    for r in range(b):
+        emitted, ok = 0, True
+        for i in range(cul[r], min(cul[r + 1], cul[r] + max_spec)):
+            out[r, emitted] = t[i]
+            emitted += 1
+            if t[i] != d[i]:
+                ok = False
+                break
+        if ok:
+            out[r, emitted] = bo[r]
+            emitted += 1
+        num[r] = emitted
+    return out, num

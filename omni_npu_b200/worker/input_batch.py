@@ -193,6 +193,40 @@ class InputBatch:
             bt[n:] = 0
         return rows
 
+    def stage_spec_decode(self, lay: StepLayout, seqs) -> Tuple[np.ndarray, int]:
+        """Stage a verification step: every sequence feeds its last token followed by its
+        draft tokens (ScheduledSeq.spec_token_ids) at positions start .. start + k.
+        Returns (rows, max_q_len)."""
+        h = self.host_np
+        bs = self.block_size
+        n = len(seqs)
+        rows = np.empty(n, dtype=np.int64)
+        off = 0
+        max_q = 0
+        cu = h[lay.cu_q: lay.cu_q + n + 1]
+        cu[0] = 0
+        for i, s in enumerate(seqs):
+            req = s.request
+            row = self.add_request(req)
+            rows[i] = row
+            q = 1 + len(s.spec_token_ids)
+            max_q = max(max_q, q)
+            last = req.output_token_ids[-1] if req.output_token_ids else req.prompt_token_ids[-1]
+            h[lay.ids + off] = last
+            if q > 1:
+                h[lay.ids + off + 1: lay.ids + off + q] = s.spec_token_ids
+            p = np.arange(s.start, s.start + q, dtype=np.int32)
+            h[lay.pos + off: lay.pos + off + q] = p
+            h[lay.slot + off: lay.slot + off + q] = self.block_table[row, p // bs] * bs + p % bs
+            h[lay.seq_lens + i] = s.start + q
+            off += q
+            cu[i + 1] = off
+            h[lay.logits_idx + i] = off - 1
+        self._fill_sampling(lay, rows, n)
+        bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
+        bt[:n] = self.block_table[rows]
+        return rows, max_q
+
     def stage_prefill(self, lay: StepLayout, seqs) -> Tuple[np.ndarray, int]:
         """Stage a prefill step.  ``seqs`` are ScheduledSeq (request, start,
         num_new_tokens).  Returns (rows, max_q_len)."""

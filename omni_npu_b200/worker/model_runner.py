@@ -32,6 +32,7 @@ from ..logger import logger
 from ..models.registry import resolve_model_cls
 from ..models.utils import iter_safetensors, random_init_
 from ..parallel import state as pstate
+from ..sample.rejection_sampler import RejectionSampler, SpecDecodeMetadata
 from ..sample.sampler import Sampler
 from .input_batch import InputBatch, StepLayout
 
@@ -57,6 +58,7 @@ class ModelRunner:
         self.input_batch = InputBatch(sc.max_num_seqs, sc.max_model_len, config.cache.block_size,
                                       sc.max_num_batched_tokens, device)
         self.sampler = Sampler(config, device)
+        self.rejection_sampler = RejectionSampler(self.sampler)
         self.graphs: Dict[int, CUDAGraphRunner] = {}
         self.capture_sizes: List[int] = []
         pin = device.type == "cuda"
@@ -197,6 +199,21 @@ class ModelRunner:
                             views["top_p"][:num_samples], views["seeds"][:num_samples],
                             self.step_counter)
 
+    def _forward_and_verify(self, views, md: AttentionMetadata, seqs) -> torch.Tensor:
+        """Verification step of speculative decoding: logits at every fed position, target
+        tokens sampled there, drafts accepted while they agree.  Returns int32
+        [n, max_k + 2]: the settled tokens (-1 padded) and, in the last column, their count."""
+        n = len(seqs)
+        with set_forward_context(md, self.kv_caches, self.config):
+            hidden = self.model(views["ids"], views["pos"])
+            self._last_hidden = hidden
+            logits = self.model.compute_logits(hidden)
+        smd = SpecDecodeMetadata.make([s.spec_token_ids for s in seqs], self.device)
+        toks, counts = self.rejection_sampler(smd, None, logits, views["temp"][:n], views["top_k"][:n],
+                                              views["top_p"][:n], views["seeds"][:n],
+                                              self.step_counter)
+        return torch.cat([toks, counts.unsqueeze(1)], dim=1)
+
     def _pad_decode_size(self, n: int) -> Optional[int]:
         for s in self.capture_sizes:
             if s >= n:
@@ -218,6 +235,22 @@ class ModelRunner:
             return []
         n = len(out.seqs)
         ev = None
+        if out.kind == "spec_decode":
+            T = out.num_tokens
+            lay = ib.layout_for(T, n)
+            _, max_q = ib.stage_spec_decode(lay, out.seqs)
+            ib.upload(lay)
+            ev = self._event_start()
+            views = ib.views(lay, ib.dev)
+            max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
+            md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
+            packed = self._forward_and_verify(views, md, out.seqs)
+            self.step_counter += max_q
+            self._event_stop(ev)
+            host = packed.cpu() if self.device.type != "cuda" else self._to_host(packed)
+            self.d2h_bytes_last = packed.numel() * 4
+            rows = host.tolist()
+            return [r[: r[-1]] for r in rows]
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
             padded = self._pad_decode_size(n) if self.graphs else None
@@ -255,6 +288,13 @@ class ModelRunner:
         if self.kv_connector is not None:
             self.kv_connector.wait_for_save()
         return tokens
+
+    def _to_host(self, t: torch.Tensor) -> torch.Tensor:
+        """Device -> pinned host copy of a small result, synchronised."""
+        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        host.copy_(t, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return host
 
     def _event_start(self):
         if not self.enable_step_events or self.device.type != "cuda":
