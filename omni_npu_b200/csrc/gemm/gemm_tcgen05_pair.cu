@@ -12,7 +12,9 @@
 //   empty[s]       one per CTA, the leader commits to both after the MMAs of a stage;
 //   tmem_full[a]   one per CTA, the leader commits to both after a tile;
 //   tmem_empty[a]  leader's copy only, 8 arrivals (4 epilogue warps of each CTA).
-// TMA loads are plain per-CTA loads (no multicast).  All waits are bounded.
+// TMA loads are plain per-CTA loads (no multicast).  All waits are bounded, and they use the
+// CTA-scope try_wait: the cluster-scope acquire form costs ~300 cycles per call even on a
+// completed barrier, which made the single producer / MMA threads the bottleneck.
 
 #include <cstdlib>
 
@@ -35,6 +37,7 @@ struct PairParams {
   int M, N, K;
   int BN;              // tile width (multiple of 32, <= 256); each CTA stages BN/2 rows of W
   int stages;
+  int ksub;            // 128-byte K slabs per stage (1 or 2): more MMAs per barrier round trip
   int k_iters;
   int num_m_blocks;    // blocks of 256 rows
   int num_n_blocks;
@@ -59,8 +62,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const int a_stage_bytes = kPBM * kPRowBytes;
-  const int w_stage_bytes = (p.BN / 2) * kPRowBytes;
+  const int a_sub_bytes = kPBM * kPRowBytes;
+  const int w_sub_bytes = (p.BN / 2) * kPRowBytes;
+  const int a_stage_bytes = p.ksub * a_sub_bytes;
+  const int w_stage_bytes = p.ksub * w_sub_bytes;
   uint8_t* smem_a = smem;
   uint8_t* smem_w = smem + p.stages * a_stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes);
@@ -126,8 +131,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = false;   // nobody waits for full barriers: the producer is done after the first fill
             break;
           }
-          if (*abort_flag || (!(p.diag & 8) && !mbar_wait_cluster(&empty_bar[stage], phase ^ 1))) {
-            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+          if (!(p.diag & 8) && !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
             *abort_flag = 1;
             ok = false;
             break;
@@ -147,9 +152,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (leader)
             mbar_arrive_expect_tx(&full_bar[stage], static_cast<uint32_t>(2 * (a_stage_bytes + w_stage_bytes)));
-          const int kcoord = k * (kPRowBytes / p.elem_bytes);
-          tma_load_2d_pair(smem_a + stage * a_stage_bytes, &tmap_a, full_leader, kcoord, m0);
-          tma_load_2d_pair(smem_w + stage * w_stage_bytes, &tmap_w, full_leader, kcoord, n0);
+          const int slab_elems = kPRowBytes / p.elem_bytes;
+          for (int j = 0; j < p.ksub; ++j) {
+            const int kcoord = (k * p.ksub + j) * slab_elems;
+            tma_load_2d_pair(smem_a + stage * a_stage_bytes + j * a_sub_bytes, &tmap_a, full_leader, kcoord, m0);
+            tma_load_2d_pair(smem_w + stage * w_stage_bytes + j * w_sub_bytes, &tmap_w, full_leader, kcoord, n0);
+          }
           ++issued;
           if (++stage == p.stages) {
             stage = 0;
@@ -176,11 +184,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       long long c_wait = 0, c_issue = 0, c_commit = 0, c_tmem = 0, n_wait = 0, n_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
         long long t0 = prof ? clock64() : 0;
-        if (*abort_flag || !mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1)) {
+        if (*abort_flag || !mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutTmemEmpty);
           *abort_flag = 1;
           break;
-        }
+        }   // (once per tile; the per-stage waits below do not read the flag)
         if (prof) c_tmem += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
@@ -190,8 +198,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ++n_wait;
             if (mbar_test(&full_bar[stage], phase)) ++n_ready;
           }
-          if (*abort_flag || (!(p.diag & 4) && !mbar_wait_cluster(&full_bar[stage], phase))) {
-            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+          if (!(p.diag & 4) && !mbar_wait(&full_bar[stage], phase)) {
+            atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
             *abort_flag = 1;
             ok = false;
             break;
@@ -202,16 +210,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             t0 = t1;
           }
           tc_fence_after_sync();
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes));
-          const uint64_t w_desc = make_smem_desc_sw128(smem_u32(smem_w + stage * w_stage_bytes));
+          for (int j = 0; j < p.ksub; ++j) {
+            const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes + j * a_sub_bytes));
+            const uint64_t w_desc = make_smem_desc_sw128(smem_u32(smem_w + stage * w_stage_bytes + j * w_sub_bytes));
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t accum = (k > 0 || kk > 0) ? 1u : 0u;
-            if (p.diag & 2) continue;
-            if constexpr (FP8) {
-              umma_f8_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
-            } else {
-              umma_f16_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t accum = (k > 0 || j > 0 || kk > 0) ? 1u : 0u;
+              if (p.diag & 2) continue;
+              if constexpr (FP8) {
+                umma_f8_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
+              } else {
+                umma_f16_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
+              }
             }
           }
           if (prof) {
@@ -253,7 +263,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m0 = mb * 2 * kPBM + cta_rank * kPBM;
       const int n0 = nb * p.BN;
       bool ok = true;
-      if (!(p.diag & 16) || lane == 0) ok = !*abort_flag && mbar_wait_cluster(&tmem_full[acc], acc_phase);
+      if (!(p.diag & 16) || lane == 0) ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
       if (p.diag & 16) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       {
         uint32_t all_ok;
@@ -379,15 +389,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-static int pair_stages(int BN) {
-  const int stage_bytes = kPBM * kPRowBytes + (BN / 2) * kPRowBytes;
+static int pair_stages(int BN, int ksub) {
+  const int stage_bytes = ksub * (kPBM * kPRowBytes + (BN / 2) * kPRowBytes);
   int st = (222 * 1024) / stage_bytes;
   if (st > 8) st = 8;
   return st < 2 ? 2 : st;
 }
 
-static size_t pair_smem(int BN, int stages) {
-  return 1024 + static_cast<size_t>(stages) * (kPBM * kPRowBytes + (BN / 2) * kPRowBytes) + (2 * stages + 5) * 8 + 64;
+static size_t pair_smem(int BN, int stages, int ksub) {
+  return 1024 + static_cast<size_t>(stages) * ksub * (kPBM * kPRowBytes + (BN / 2) * kPRowBytes) +
+         (2 * stages + 5) * 8 + 64;
 }
 
 template <bool FP8>
@@ -396,7 +407,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const PairP
   auto kern = gemm_pair_kernel<FP8>;
   static bool configured = false;
   static int max_pairs = 0;
-  const size_t smem = pair_smem(p.BN, p.stages);
+  const size_t smem = pair_smem(p.BN, p.stages, p.ksub);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kPThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
@@ -451,10 +462,17 @@ extern "C" int b200_gemm_pair(const void* A, const void* W, void* C, const void*
   p.K = K;
   p.BN = BN;
   p.elem_bytes = eb;
-  p.k_iters = (K * eb + kPRowBytes - 1) / kPRowBytes;
+  {
+    static const int ksub_env = [] {
+      const char* e = getenv("OMNI_B200_GEMM_PAIR_KSUB");
+      return e ? atoi(e) : 0;
+    }();
+    p.ksub = ksub_env == 1 || ksub_env == 2 ? ksub_env : (K * eb > 2 * kPRowBytes ? 2 : 1);
+  }
+  p.k_iters = (K * eb + kPRowBytes * p.ksub - 1) / (kPRowBytes * p.ksub);
   p.num_m_blocks = (M + 2 * kPBM - 1) / (2 * kPBM);
   p.num_n_blocks = (N + BN - 1) / BN;
-  p.stages = pair_stages(BN);
+  p.stages = pair_stages(BN, p.ksub);
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   p.tmem_cols = 2 * p.acc_stride < 32 ? 32 : 2 * p.acc_stride;
   p.ldc = ldc;

@@ -36,6 +36,8 @@ def _quant_factory(cfg: ModelConfig):
 
 
 class DeepseekDecoderLayer(nn.Module):
+    takes_pending = True      # forward(hidden, residual, pending_reduce) -> (hidden, residual, pending)
+
     def __init__(self, engine: EngineConfig, layer_idx: int, device, prefix: str) -> None:
         super().__init__()
         cfg = engine.model
@@ -109,9 +111,24 @@ class DeepseekForCausalLM(nn.Module):
         self.engine_config = engine_config
         self.model = DeepseekModel(engine_config, device)
         self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device)
+        self.mtp = None
+        self.num_kv_layers = self.config.num_layers
+        spec = engine_config.speculative
+        if spec.method in ("mtp", "deepseek_mtp") and spec.num_speculative_tokens > 0:
+            from .mtp import MultiTokenPredictor
+            self.mtp = MultiTokenPredictor(
+                engine_config, device,
+                lambda idx, prefix: DeepseekDecoderLayer(engine_config, idx, device, prefix))
+            self.num_kv_layers += self.mtp.num_mtp_layers
 
     def forward(self, input_ids, positions, inputs_embeds=None):
         return self.model(input_ids, positions, inputs_embeds)
+
+    def mtp_forward(self, next_ids, positions, hidden):
+        return self.mtp(self.model.embed_tokens(next_ids), hidden)
+
+    def mtp_logits(self, hidden):
+        return (self.mtp.own_head or self.lm_head).compute_logits(hidden)
 
     def compute_logits(self, hidden):
         return self.lm_head.compute_logits(hidden)
@@ -125,12 +142,13 @@ class DeepseekForCausalLM(nn.Module):
         if c.use_sparse:
             per += block_size * c.index_head_dim * c.dtype.itemsize
             shapes["index_key"] = (block_size, c.index_head_dim)
-        return KVCacheSpec("dsa" if c.use_sparse else "mla", c.num_layers, block_size, per * c.num_layers, shapes)
+        n = self.num_kv_layers
+        return KVCacheSpec("dsa" if c.use_sparse else "mla", n, block_size, per * n, shapes)
 
     def allocate_kv_cache(self, num_blocks: int, block_size: int, device) -> List:
         c = self.config
         caches = []
-        for _ in range(c.num_layers):
+        for _ in range(self.num_kv_layers):
             lat = MLABackend.allocate_kv_cache(num_blocks, block_size, c.kv_lora_rank, c.qk_rope_head_dim,
                                                c.dtype, device)
             if c.use_sparse:
@@ -146,7 +164,11 @@ class DeepseekForCausalLM(nn.Module):
         for name, tensor in weights:
             m = re.match(r"model\.layers\.(\d+)\.", name)
             if m and int(m.group(1)) >= n_layers:
-                continue                                   # multi-token-prediction layers
+                # multi-token-prediction layers: loaded only when the head is in use
+                new = self.mtp.rewrite_name(name) if self.mtp is not None else None
+                if new is None or new.startswith("__"):
+                    continue
+                name = "mtp." + new
             em = _EXPERT_RE.match(name)
             if em is None:
                 rest.append((name.replace(".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),

@@ -114,9 +114,25 @@ class LlamaForCausalLM(nn.Module):
             self.lm_head.__class__ = ParallelLMHead
         else:
             self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+        self.mtp = None
+        self.num_kv_layers = cfg.num_layers
+        spec = engine_config.speculative
+        if spec.method in ("mtp", "deepseek_mtp") and spec.num_speculative_tokens > 0:
+            from .mtp import MultiTokenPredictor
+            self.mtp = MultiTokenPredictor(engine_config, device,
+                                           lambda idx, prefix: LlamaDecoderLayer(cfg, idx, device, prefix))
+            self.num_kv_layers += self.mtp.num_mtp_layers
 
     def forward(self, input_ids, positions, inputs_embeds=None) -> torch.Tensor:
         return self.model(input_ids, positions, inputs_embeds)
+
+    def mtp_forward(self, next_ids: torch.Tensor, positions: torch.Tensor, hidden: torch.Tensor) -> torch.Tensor:
+        """Hidden states of the MTP head for (embedding of the next token, target hidden state)."""
+        return self.mtp(self.model.embed_tokens(next_ids), hidden)
+
+    def mtp_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        head = self.mtp.own_head or self.lm_head
+        return head.compute_logits(hidden)
 
     def embed_input_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
         return self.model.embed_tokens(input_ids)
@@ -128,6 +144,11 @@ class LlamaForCausalLM(nn.Module):
         skip = ("rotary_emb.inv_freq",)
         if self.config.tie_word_embeddings:
             skip = skip + ("lm_head.weight",)
+        if self.mtp is not None:
+            weights, mtp_weights = self.mtp.split_weights(weights)
+            loaded = load_stacked_weights(self, weights, self.stacked_params_mapping, skip_substrings=skip)
+            return loaded | load_stacked_weights(self, [("mtp." + n, t) for n, t in mtp_weights],
+                                                 self.stacked_params_mapping, skip_substrings=skip)
         return load_stacked_weights(self, weights, self.stacked_params_mapping, skip_substrings=skip)
 
 

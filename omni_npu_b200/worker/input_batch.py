@@ -38,6 +38,7 @@ class StepLayout:
     top_p: int = 0
     seeds: int = 0
     logits_idx: int = 0
+    next_ids: int = 0
     bt: int = 0
     total: int = 0
 
@@ -47,7 +48,7 @@ class StepLayout:
         off = 0
         for name, n in (("ids", T), ("pos", T), ("slot", T), ("seq_lens", S), ("cu_q", S + 1),
                         ("temp", S), ("top_k", S), ("top_p", S), ("seeds", 2 * S),
-                        ("logits_idx", S), ("bt", S * max_blocks)):
+                        ("logits_idx", S), ("next_ids", T), ("bt", S * max_blocks)):
             off = (off + 3) // 4 * 4           # 16-byte aligned sections
             setattr(lay, name, off)
             off += n
@@ -141,6 +142,7 @@ class InputBatch:
             "top_p": buf[lay.top_p: lay.top_p + S].view(torch.float32),
             "seeds": buf[lay.seeds: lay.seeds + 2 * S].view(torch.int64),
             "logits_idx": buf[lay.logits_idx: lay.logits_idx + S],
+            "next_ids": buf[lay.next_ids: lay.next_ids + T],
             "bt": buf[lay.bt: lay.bt + S * mb].view(S, mb),
         }
 
@@ -186,6 +188,7 @@ class InputBatch:
             h[lay.seq_lens + n: lay.seq_lens + lay.S] = 1
         h[lay.cu_q: lay.cu_q + lay.S + 1] = np.arange(lay.S + 1, dtype=np.int32) * q_len
         h[lay.logits_idx: lay.logits_idx + lay.S] = np.arange(lay.S, dtype=np.int32)
+        h[lay.next_ids: lay.next_ids + lay.T] = -1
         self._fill_sampling(lay, rows, n)
         bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
         bt[:n] = self.block_table[rows]
@@ -225,6 +228,13 @@ class InputBatch:
         self._fill_sampling(lay, rows, n)
         bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
         bt[:n] = self.block_table[rows]
+        # successor of fed token j of sequence i = element (i, j) of the [n, max_q] matrix of
+        # verified tokens the step produces (staged as a flat index into that matrix)
+        off = 0
+        for i, s in enumerate(seqs):
+            q = 1 + len(s.spec_token_ids)
+            h[lay.next_ids + off: lay.next_ids + off + q] = i * max_q + np.arange(q, dtype=np.int32)
+            off += q
         return rows, max_q
 
     def stage_prefill(self, lay: StepLayout, seqs) -> Tuple[np.ndarray, int]:
@@ -252,6 +262,10 @@ class InputBatch:
             h[lay.pos + off: lay.pos + off + q] = p
             h[lay.slot + off: lay.slot + off + q] = self.block_table[row, p // bs] * bs + p % bs
             h[lay.seq_lens + i] = s.start + q
+            # successors inside the chunk, then the token after it if the request already has it
+            h[lay.next_ids + off: lay.next_ids + off + q - 1] = toks[1:]
+            nxt = s.start + q
+            h[lay.next_ids + off + q - 1] = req.token_at(nxt) if nxt < req.num_tokens else -1
             off += q
             cu[i + 1] = off
             h[lay.logits_idx + i] = off - 1

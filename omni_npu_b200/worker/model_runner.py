@@ -63,6 +63,9 @@ class ModelRunner:
         self.capture_sizes: List[int] = []
         pin = device.type == "cuda"
         self.sampled_host = torch.zeros(max(sc.max_num_seqs, 1), dtype=torch.int32, pin_memory=pin)
+        self.sampled_host2 = torch.zeros(max(sc.max_num_seqs, 1), 2, dtype=torch.int32, pin_memory=pin)
+        self.mtp = None                       # the model's multi-token-prediction head, if it drafts
+        self.last_drafts: List[List[int]] = []
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
         self.d2h_bytes_last = 0
         self.kv_connector = None
@@ -95,6 +98,10 @@ class ModelRunner:
         if callable(post):
             post()
         self.model.eval()
+        if cfg.speculative.method in ("mtp", "deepseek_mtp") and cfg.speculative.num_speculative_tokens > 0:
+            self.mtp = getattr(self.model, "mtp", None)
+            if self.mtp is None:
+                raise ValueError(f"{type(self.model).__name__} has no multi-token-prediction head")
         tp = pstate.get_tp_group()
         ep = pstate.get_ep_group()
         tp.comm.prepare_communication_buffer_for_model(self.model)
@@ -116,7 +123,8 @@ class ModelRunner:
         hk = max(1, mc.num_kv_heads // tp)
         per_layer = GQABackend.bytes_per_block(bs, hk, mc.head_dim, mc.dtype)
         k_shape, v_shape = GQABackend.get_kv_cache_shape(1, bs, hk, mc.head_dim)
-        return KVCacheSpec("gqa", mc.num_layers, bs, per_layer * mc.num_layers,
+        n_layers = getattr(self.model, "num_kv_layers", mc.num_layers)
+        return KVCacheSpec("gqa", n_layers, bs, per_layer * n_layers,
                            {"k": k_shape[1:], "v": v_shape[1:]})
 
     @torch.inference_mode()
@@ -167,7 +175,7 @@ class ModelRunner:
             hk = max(1, mc.num_kv_heads // pstate.tp_world_size())
             self.kv_caches = [GQABackend.allocate_kv_cache(num_blocks, self.config.cache.block_size,
                                                            hk, mc.head_dim, mc.dtype, self.device)
-                              for _ in range(mc.num_layers)]
+                              for _ in range(getattr(self.model, "num_kv_layers", mc.num_layers))]
         self.num_blocks = num_blocks
 
     def initialize_kv_cache(self, num_blocks: int) -> None:
@@ -187,32 +195,57 @@ class ModelRunner:
                                  num_actual_seqs=actual_seqs)
 
     def _forward_and_sample(self, views, md: AttentionMetadata, num_samples: int) -> torch.Tensor:
-        """Model forward + LM head + sampling for the staged step (device side only)."""
+        """Model forward + LM head + sampling for the staged step (device side only).
+        Returns the sampled tokens [num_samples]; with an MTP head int32 [num_samples, 2]:
+        the sampled token and the draft for the token after it."""
         with set_forward_context(md, self.kv_caches, self.config):
-            hidden = self.model(views["ids"], views["pos"])
-            if md.is_prefill:
-                hidden = hidden.index_select(0, views["logits_idx"][:num_samples].long())
-            else:
-                hidden = hidden[:num_samples]
+            hidden_all = self.model(views["ids"], views["pos"])
+            idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
+            hidden = hidden_all.index_select(0, idx) if idx is not None else hidden_all[:num_samples]
             logits = self.model.compute_logits(hidden)
-        return self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
-                            views["top_p"][:num_samples], views["seeds"][:num_samples],
-                            self.step_counter)
+            sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
+                                   views["top_p"][:num_samples], views["seeds"][:num_samples],
+                                   self.step_counter)
+            if self.mtp is None:
+                return sampled
+            # successor of every fed token: known for prompt tokens, the fresh sample otherwise
+            tok = sampled.to(torch.int32)
+            if idx is not None:
+                nxt = views["next_ids"].clone()
+                cur = nxt.index_select(0, idx)
+                nxt.index_copy_(0, idx, torch.where(cur < 0, tok, cur))
+            else:
+                nxt = views["next_ids"].clone()
+                nxt[:num_samples] = tok
+                nxt.clamp_(min=0)
+            h = self.model.mtp_forward(nxt, views["pos"], hidden_all)
+            h = h.index_select(0, idx) if idx is not None else h[:num_samples]
+            draft = ops.argmax(self.model.mtp_logits(h))
+        return torch.stack([tok, draft.to(torch.int32)], dim=1)
 
     def _forward_and_verify(self, views, md: AttentionMetadata, seqs) -> torch.Tensor:
         """Verification step of speculative decoding: logits at every fed position, target
         tokens sampled there, drafts accepted while they agree.  Returns int32
-        [n, max_k + 2]: the settled tokens (-1 padded) and, in the last column, their count."""
+        [n, max_k + 2 (+1)]: the settled tokens (-1 padded), their count and, with an MTP
+        head, the draft for the next step."""
         n = len(seqs)
         with set_forward_context(md, self.kv_caches, self.config):
             hidden = self.model(views["ids"], views["pos"])
-            self._last_hidden = hidden
             logits = self.model.compute_logits(hidden)
-        smd = SpecDecodeMetadata.make([s.spec_token_ids for s in seqs], self.device)
-        toks, counts = self.rejection_sampler(smd, None, logits, views["temp"][:n], views["top_k"][:n],
-                                              views["top_p"][:n], views["seeds"][:n],
-                                              self.step_counter)
-        return torch.cat([toks, counts.unsqueeze(1)], dim=1)
+            smd = SpecDecodeMetadata.make([s.spec_token_ids for s in seqs], self.device)
+            toks, counts = self.rejection_sampler(smd, None, logits, views["temp"][:n], views["top_k"][:n],
+                                                  views["top_p"][:n], views["seeds"][:n],
+                                                  self.step_counter)
+            cols = [toks, counts.unsqueeze(1)]
+            if self.mtp is not None:
+                # fed token j of sequence i is followed by verified token (i, j); the draft for
+                # the next step comes from the last verified position
+                nxt = toks.reshape(-1).index_select(0, views["next_ids"].long()).clamp_min(0)
+                h = self.model.mtp_forward(nxt, views["pos"], hidden)
+                rows = (views["cu_q"][:n] + counts - 1).long()
+                draft = ops.argmax(self.model.mtp_logits(h.index_select(0, rows)))
+                cols.append(draft.to(torch.int32).unsqueeze(1))
+        return torch.cat(cols, dim=1)
 
     def _pad_decode_size(self, n: int) -> Optional[int]:
         for s in self.capture_sizes:
@@ -250,6 +283,9 @@ class ModelRunner:
             host = packed.cpu() if self.device.type != "cuda" else self._to_host(packed)
             self.d2h_bytes_last = packed.numel() * 4
             rows = host.tolist()
+            if self.mtp is not None:
+                self.last_drafts = [[r[-1]] for r in rows]
+                return [r[: r[-2]] for r in rows]
             return [r[: r[-1]] for r in rows]
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
@@ -279,12 +315,22 @@ class ModelRunner:
         self.step_counter += 1
         self._event_stop(ev)
         # D2H of the step's result (pinned), then the host learns the tokens
-        host = self.sampled_host[:n]
-        host.copy_(sampled[:n], non_blocking=True)
-        if self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()
-        self.d2h_bytes_last = n * 4
-        tokens = host.tolist()
+        if self.mtp is not None:
+            host = self.sampled_host2[:n]
+            host.copy_(sampled[:n], non_blocking=True)
+            if self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).synchronize()
+            self.d2h_bytes_last = n * 8
+            pairs = host.tolist()
+            tokens = [p[0] for p in pairs]
+            self.last_drafts = [[p[1]] if s.samples else [] for p, s in zip(pairs, out.seqs)]
+        else:
+            host = self.sampled_host[:n]
+            host.copy_(sampled[:n], non_blocking=True)
+            if self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).synchronize()
+            self.d2h_bytes_last = n * 4
+            tokens = host.tolist()
         if self.kv_connector is not None:
             self.kv_connector.wait_for_save()
         return tokens
@@ -338,6 +384,7 @@ class ModelRunner:
             pos = np.tile(np.arange(per, dtype=np.int32), n_seq)
             h[lay.pos: lay.pos + T] = pos
             h[lay.slot: lay.slot + T] = -1
+            h[lay.next_ids: lay.next_ids + T] = 0
             h[lay.seq_lens: lay.seq_lens + n_seq] = per
             h[lay.cu_q: lay.cu_q + n_seq + 1] = np.arange(n_seq + 1, dtype=np.int32) * per
             h[lay.logits_idx: lay.logits_idx + n_seq] = np.arange(1, n_seq + 1, dtype=np.int32) * per - 1

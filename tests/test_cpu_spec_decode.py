@@ -81,3 +81,41 @@ def test_engine_with_ngram_speculation_matches_plain_greedy():
     # fewer model steps than tokens when drafts are accepted
     if st["accepted"]:
         assert spec.engine.stats["steps"] < plain.engine.stats["steps"]
+
+
+def test_engine_with_mtp_head_matches_plain_greedy():
+    """A randomly initialised MTP head drafts mostly wrong tokens; verification must keep the
+    output identical to plain greedy decoding, and the head's own KV-cache layer must exist."""
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (9, 30, 17)]
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=24, max_model_len=128,
+              block_size=8, num_gpu_blocks=96, seed=3)
+    plain = LLM(model=_tiny(), **kw)
+    want = [o.output_token_ids for o in plain.generate(prompts, sp)]
+    spec = LLM(model=_tiny(), speculative_config={"method": "mtp", "num_speculative_tokens": 1}, **kw)
+    runner = spec.engine.worker.model_runner
+    assert runner.mtp is not None and len(runner.kv_caches) == 3        # 2 layers + 1 MTP layer
+    got = [o.output_token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    st = spec.engine.scheduler.spec_stats
+    assert st["drafted"] > 0 and spec.engine.stats["spec_decode_steps"] > 0
+
+
+def test_mtp_checkpoint_names():
+    from omni_npu_b200.config import EngineConfig, SpeculativeConfig
+    from omni_npu_b200.models.llama import LlamaForCausalLM
+    from omni_npu_b200.parallel import state
+    state.ensure_initialized(torch.device("cpu"))
+    cfg = EngineConfig(model=_tiny(), speculative=SpeculativeConfig("mtp", 1), device="cpu")
+    m = LlamaForCausalLM(cfg, device="cpu")
+    r = m.mtp.rewrite_name
+    assert r("model.layers.1.mlp.down_proj.weight") is None                 # target layer
+    assert r("model.layers.2.enorm.weight") == "layers.0.enorm.weight"
+    assert r("model.layers.2.shared_head.norm.weight") == "layers.0.shared_head_norm.weight"
+    assert r("model.layers.2.self_attn.o_proj.weight") == "layers.0.mtp_block.self_attn.o_proj.weight"
+    assert r("model.layers.2.embed_tokens.weight") == "__shared_embedding__"
+    assert r("model.layers.3.enorm.weight") is None                         # beyond the MTP layers
+    w = torch.full((64,), 2.0)
+    loaded = m.load_weights([("model.layers.2.hnorm.weight", w), ("model.norm.weight", w)])
+    assert "mtp.layers.0.hnorm.weight" in loaded and torch.equal(m.mtp.layers[0].hnorm.weight.data, w)
