@@ -332,6 +332,87 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, u
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Lean issue path for the main loop: the descriptors' high words are loop constants, only
+// the low words (start address >> 4) change between K steps, and the accumulate flag of all
+// but the first MMA of a tile is the constant 1.
+constexpr uint32_t kSmemDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+template <bool FP8>
+__device__ __forceinline__ void umma_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  if constexpr (FP8) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .pred p;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHiSw128), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .pred p;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHiSw128), "r"(idesc)
+        : "memory");
+  }
+}
+template <bool FP8>
+__device__ __forceinline__ void umma_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  const uint64_t da = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | a_lo;
+  const uint64_t db = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | b_lo;
+  if constexpr (FP8) umma_f8(d_tmem, da, db, idesc, accumulate);
+  else umma_f16(d_tmem, da, db, idesc, accumulate);
+}
+template <bool FP8>
+__device__ __forceinline__ void umma_pair_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  if constexpr (FP8) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .pred p;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHiSw128), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .pred p;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHiSw128), "r"(idesc)
+        : "memory");
+  }
+}
+template <bool FP8>
+__device__ __forceinline__ void umma_pair_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+  const uint64_t da = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | a_lo;
+  const uint64_t db = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | b_lo;
+  if constexpr (FP8) umma_f8_pair(d_tmem, da, db, idesc, accumulate);
+  else umma_f16_pair(d_tmem, da, db, idesc, accumulate);
+}
+
 // TMA load into this CTA's shared memory whose completion is signalled on an mbarrier
 // given by a shared::cluster address (the leader CTA's barrier for both CTAs of a pair).
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m,

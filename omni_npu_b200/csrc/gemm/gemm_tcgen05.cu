@@ -24,6 +24,8 @@
 // call sites (omni_npu/v1/layers/linear.py:124-130,
 // omni_npu/layers/fused_moe/npu_moe_permute_unpermute.py:108-149).
 
+#include <cstdlib>
+
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 
@@ -37,7 +39,8 @@ static constexpr int kMaxExperts = 512;
 struct GemmParams {
   int M, N, K;            // problem (grouped: M = total packed rows)
   int BN;                 // tile width
-  int stages;             // shared-memory ring depth
+  int stages;             // shared-memory ring depth (128-byte K slabs)
+  int ksub;               // slabs per barrier round trip (1 or 2); stages is a multiple of it
   int k_iters;            // ceil(K_bytes / 128)
   int splits;             // split-K factor (>=1)
   int num_m_blocks;       // dense only
@@ -202,6 +205,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   volatile int* abort_flag = s_flags;
+  const int groups = p.stages / p.ksub;   // barrier pairs in use
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -215,25 +219,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
                                                                 cta_rank, cursor, tc);
            t += t_stride) {
-        for (int k = tc.k_begin; k < tc.k_end; ++k) {
-          if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+        for (int k = tc.k_begin; k < tc.k_end; k += p.ksub) {
+          // one barrier round trip covers up to ksub slabs (`stage` counts groups of slabs)
+          const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
             *abort_flag = 1;
             ok = false;
             break;
           }
           mbar_arrive_expect_tx(&full_bar[stage],
-                                static_cast<uint32_t>(a_stage_bytes + w_stage_bytes));
-          const int kcoord = k * (kRowBytes / p.elem_bytes);
-          tma_load_2d(smem_a + stage * a_stage_bytes, &tmap_a, &full_bar[stage], kcoord, tc.m0);
-          if constexpr (GROUPED) {
-            tma_load_3d(smem_w + stage * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0,
-                        tc.expert);
-          } else {
-            tma_load_2d(smem_w + stage * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0);
+                                static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
+          for (int j = 0; j < ns; ++j) {
+            const int slab = stage * p.ksub + j;
+            const int kcoord = (k + j) * (kRowBytes / p.elem_bytes);
+            tma_load_2d(smem_a + slab * a_stage_bytes, &tmap_a, &full_bar[stage], kcoord, tc.m0);
+            if constexpr (GROUPED) {
+              tma_load_3d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0,
+                          tc.expert);
+            } else {
+              tma_load_2d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0);
+            }
           }
           ++issued;
-          if (++stage == p.stages) {
+          if (++stage == groups) {
             stage = 0;
             phase ^= 1;
           }
@@ -242,12 +251,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) {
         // Abort path: wait (bounded) until the loads already issued have landed
         // so that no bulk copy writes into shared memory after the CTA retires.
-        const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
+        const int pending = issued < groups ? static_cast<int>(issued) : groups;
         int s = stage;
         uint32_t ph = phase;
         for (int i = 0; i < pending; ++i) {
           if (--s < 0) {
-            s = p.stages - 1;
+            s = groups - 1;
             ph ^= 1;
           }
           mbar_wait(&full_bar[s], ph);
@@ -258,6 +267,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = FP8 ? make_idesc(0, 0, kBM, p.BN) : make_idesc(1, 1, kBM, p.BN);
+      // low words of the shared-memory descriptors (start address >> 4) and the slab pitch
+      const uint32_t a_lo0 = (smem_u32(smem_a) & 0x3FFFF) >> 4, w_lo0 = (smem_u32(smem_w) & 0x3FFFF) >> 4;
+      const uint32_t a_slab_lo = static_cast<uint32_t>(a_stage_bytes) >> 4, w_slab_lo = static_cast<uint32_t>(w_stage_bytes) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -275,28 +287,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
-        for (int k = tc.k_begin; k < tc.k_end; ++k) {
-          if (*abort_flag || !mbar_wait(&full_bar[stage], phase)) {
-            if (!*abort_flag) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+        for (int k = tc.k_begin; k < tc.k_end; k += p.ksub) {
+          const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
+          // (the abort flag is not read here: shared-memory reads by this thread queue behind
+          // the tensor core's operand traffic and cost ~100 cycles each)
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes));
-          const uint64_t w_desc = make_smem_desc_sw128(smem_u32(smem_w + stage * w_stage_bytes));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // 32 bytes of K per instruction: advance the start-address field by 2.
-            const uint32_t accum = (k > tc.k_begin || kk > 0) ? 1u : 0u;
-            if constexpr (FP8) {
-              umma_f8(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
-            } else {
-              umma_f16(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
-            }
+          uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage * p.ksub) * a_slab_lo;
+          uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * p.ksub) * w_slab_lo;
+          for (int j = 0; j < ns; ++j) {
+            // 32 bytes of K per instruction: the start-address field advances by 2
+            umma_first<FP8>(d_tmem, a_lo, w_lo, idesc, (k > tc.k_begin || j > 0) ? 1u : 0u);
+            umma_acc<FP8>(d_tmem, a_lo + 2, w_lo + 2, idesc);
+            umma_acc<FP8>(d_tmem, a_lo + 4, w_lo + 4, idesc);
+            umma_acc<FP8>(d_tmem, a_lo + 6, w_lo + 6, idesc);
+            a_lo += a_slab_lo;
+            w_lo += w_slab_lo;
           }
-          tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs retire
-          if (++stage == p.stages) {
+          tc_commit(&empty_bar[stage]);  // slabs reusable once these MMAs retire
+          if (++stage == groups) {
             stage = 0;
             phase ^= 1;
           }
@@ -656,6 +670,19 @@ static size_t smem_bytes_for(int BN, int stages, int num_experts, int cluster_sp
          red_bytes_for(BN, cluster_split) + (2 * stages + 7) * 8 + 16 + (num_experts + 2) * 4 + 64;
 }
 
+// Slabs per barrier round trip: two when that still leaves three groups in flight.  The
+// producer and MMA threads each spend several hundred cycles per round trip (their
+// shared-memory accesses queue behind the tensor core's), so fewer, larger rounds keep
+// them off the critical path.
+static int ksub_for(int stages) {
+  static const int forced = [] {
+    const char* e = getenv("OMNI_B200_GEMM_KSUB");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || (forced == 2 && stages >= 4)) return forced;
+  return stages >= 6 ? 2 : 1;
+}
+
 static int stages_for(int BN, int cluster_split) {
   const int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
   int stages = static_cast<int>((226 * 1024 - 2048 - red_bytes_for(BN, cluster_split)) / stage_bytes);
@@ -878,6 +905,8 @@ extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias
   p.num_m_blocks = (M + kBM - 1) / kBM;
   p.num_n_blocks = (N + BN - 1) / BN;
   p.stages = stages_for(BN, cluster_split);
+  p.ksub = ksub_for(p.stages);
+  p.stages -= p.stages % p.ksub;
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   p.tmem_cols = next_pow2_cols(2 * p.acc_stride);
   p.ldc = ldc;
@@ -940,7 +969,8 @@ extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const in
   p.num_m_blocks = 0;
   p.num_n_blocks = (N + BN - 1) / BN;
   const int stages = stages_for(BN, 0);
-  p.stages = stages;
+  p.ksub = ksub_for(stages);
+  p.stages = stages - stages % p.ksub;
   p.cluster_split = 0;
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   p.tmem_cols = next_pow2_cols(2 * p.acc_stride);

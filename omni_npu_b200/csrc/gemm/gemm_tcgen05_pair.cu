@@ -180,6 +180,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const bool no_mma = (p.diag & 2) != 0;
+      // low words of the shared-memory descriptors (start address >> 4) and their strides
+      const uint32_t a_lo0 = (smem_u32(smem_a) & 0x3FFFF) >> 4, w_lo0 = (smem_u32(smem_w) & 0x3FFFF) >> 4;
+      const uint32_t a_sub_lo = static_cast<uint32_t>(a_sub_bytes) >> 4, w_sub_lo = static_cast<uint32_t>(w_sub_bytes) >> 4;
+      const uint32_t a_stage_lo = static_cast<uint32_t>(a_stage_bytes) >> 4, w_stage_lo = static_cast<uint32_t>(w_stage_bytes) >> 4;
       const bool prof = (p.diag & 64) && blockIdx.x == 0;
       long long c_wait = 0, c_issue = 0, c_commit = 0, c_tmem = 0, n_wait = 0, n_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
@@ -210,18 +215,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             t0 = t1;
           }
           tc_fence_after_sync();
-          for (int j = 0; j < p.ksub; ++j) {
-            const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * a_stage_bytes + j * a_sub_bytes));
-            const uint64_t w_desc = make_smem_desc_sw128(smem_u32(smem_w + stage * w_stage_bytes + j * w_sub_bytes));
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint32_t accum = (k > 0 || j > 0 || kk > 0) ? 1u : 0u;
-              if (p.diag & 2) continue;
-              if constexpr (FP8) {
-                umma_f8_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
-              } else {
-                umma_f16_pair(d_tmem, a_desc + 2 * kk, w_desc + 2 * kk, idesc, accum);
-              }
+          if (!no_mma) {
+            uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * a_stage_lo;
+            uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage) * w_stage_lo;
+            for (int j = 0; j < p.ksub; ++j) {
+              // 32 bytes of K per MMA: the start-address field advances by 2
+              umma_pair_first<FP8>(d_tmem, a_lo, w_lo, idesc, (k > 0 || j > 0) ? 1u : 0u);
+              umma_pair_acc<FP8>(d_tmem, a_lo + 2, w_lo + 2, idesc);
+              umma_pair_acc<FP8>(d_tmem, a_lo + 4, w_lo + 4, idesc);
+              umma_pair_acc<FP8>(d_tmem, a_lo + 6, w_lo + 6, idesc);
+              a_lo += a_sub_lo;
+              w_lo += w_sub_lo;
             }
           }
           if (prof) {

@@ -113,9 +113,14 @@ class FusedMoE(nn.Module):
         self.buffers = shared
         self._side_stream = torch.cuda.Stream(dev)
 
-    def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, expert_id: int, shard: str) -> bool:
+    def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, expert_id: Optional[int] = None,
+                      shard: Optional[str] = None) -> bool:
         """Load one expert's gate / up / down tensor.  Returns False when the expert
-        lives on another rank."""
+        lives on another rank.  Without an expert id the tensor is a plain parameter of
+        the layer (router bias) and is copied as is."""
+        if expert_id is None:
+            param.data.copy_(loaded.to(param.dtype))
+            return True
         local = expert_id - self.expert_start
         if local < 0 or local >= self.local_experts:
             return False

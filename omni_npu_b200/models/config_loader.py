@@ -92,7 +92,7 @@ class KernelPlan:
     prefill_enable_mla_alltoall: bool = False
     prefill_enable_mla_alltoall_local: bool = False
     # GEMM / scheduling
-    cta_pair_gemm_min_m: int = 256
+    cta_pair_gemm_min_m: int = 1024
     enable_prefill_micro_batch: bool = False
     enable_mlp_seq_split: bool = False
     control_accept_rate: float = -1.0         # outside [0, 1] = off; forces the MTP acceptance rate (testing only)

@@ -82,11 +82,12 @@ class DeepseekDecoderLayer(nn.Module):
 
 
 class DeepseekModel(nn.Module):
-    def __init__(self, engine: EngineConfig, device) -> None:
+    def __init__(self, engine: EngineConfig, device, layer_cls=None) -> None:
         super().__init__()
         cfg = engine.model
+        layer_cls = layer_cls or DeepseekDecoderLayer
         self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
-        self.layers = nn.ModuleList([DeepseekDecoderLayer(engine, i, device, f"model.layers.{i}")
+        self.layers = nn.ModuleList([layer_cls(engine, i, device, f"model.layers.{i}")
                                      for i in range(cfg.num_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
 
@@ -104,12 +105,14 @@ class DeepseekModel(nn.Module):
 
 class DeepseekForCausalLM(nn.Module):
     stacked_params_mapping = [(".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1)]
+    decoder_layer_cls = None          # subclasses may swap the decoder layer
 
     def __init__(self, engine_config: EngineConfig, device=None) -> None:
         super().__init__()
         self.config = engine_config.model
         self.engine_config = engine_config
-        self.model = DeepseekModel(engine_config, device)
+        layer_cls = type(self).decoder_layer_cls or DeepseekDecoderLayer
+        self.model = DeepseekModel(engine_config, device, layer_cls)
         self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device)
         self.mtp = None
         self.num_kv_layers = self.config.num_layers
@@ -118,7 +121,7 @@ class DeepseekForCausalLM(nn.Module):
             from .mtp import MultiTokenPredictor
             self.mtp = MultiTokenPredictor(
                 engine_config, device,
-                lambda idx, prefix: DeepseekDecoderLayer(engine_config, idx, device, prefix))
+                lambda idx, prefix: layer_cls(engine_config, idx, device, prefix))
             self.num_kv_layers += self.mtp.num_mtp_layers
 
     def forward(self, input_ids, positions, inputs_embeds=None):

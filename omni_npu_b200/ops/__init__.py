@@ -155,7 +155,7 @@ def check_status(device: Optional[torch.device] = None) -> None:
 
 # ------------------------------------------------------------------------ GEMM
 # smallest M routed to the CTA-pair GEMM (0 = never); prefill-sized problems only
-PAIR_MIN_M = int(os.environ.get("OMNI_B200_GEMM_PAIR_MIN_M", "0"))
+PAIR_MIN_M = int(os.environ.get("OMNI_B200_GEMM_PAIR_MIN_M", "1024"))
 
 def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
