@@ -76,6 +76,8 @@ class LLMEngine:
                 time.sleep(0.001)        # waiting for remote KV
             return []
         tokens = self.worker.execute_model(out)
+        if isinstance(tokens, dict):
+            return self._after_recovered_step(out, tokens)
         drafts = None
         if self.proposer is not None and any(s.samples for s in out.seqs):
             drafts = self._propose(out, tokens)
@@ -90,6 +92,27 @@ class LLMEngine:
         for r in finished:
             self.worker.model_runner.input_batch.remove_request(r.request_id)
         return [RequestOutput.from_request(r) for r in finished]
+
+    def _after_recovered_step(self, out, verdict: dict) -> List[RequestOutput]:
+        """The step failed and the workers recovered (token recovery).  ``recompute``: nothing
+        of the step is kept, every scheduled request is recomputed from scratch (its KV may be
+        half-written); ``abort``: requests that own a damaged KV block are aborted, the rest
+        recomputed."""
+        self.stats["recovered_steps"] = self.stats.get("recovered_steps", 0) + 1
+        bad = set(verdict.get("bad_blocks") or [])
+        finished: List[RequestOutput] = []
+        for seq in list(out.seqs):
+            req = seq.request
+            if req.is_finished:
+                continue
+            if verdict.get("opt") == "abort" and bad & set(req.block_ids):
+                self.scheduler.abort_request(req.request_id)
+                self.worker.model_runner.input_batch.remove_request(req.request_id)
+                finished.append(RequestOutput.from_request(req))
+            else:
+                self.scheduler.preempt_for_recompute(req)
+                self.worker.model_runner.input_batch.remove_request(req.request_id)
+        return finished
 
     def _propose(self, out, tokens) -> List[List[int]]:
         """Draft tokens for the next step of every sequence that just produced a token.

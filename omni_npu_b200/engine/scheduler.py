@@ -123,6 +123,20 @@ class Scheduler:
             return victim
         return None
 
+    def preempt_for_recompute(self, req: Request) -> None:
+        """Send a running request back to the head of the waiting queue; its KV is dropped
+        and recomputed from its tokens (prompt + outputs so far)."""
+        if req in self.running:
+            self.running.remove(req)
+        self.pool.free(req.block_ids)
+        req.block_ids = []
+        req.num_computed_tokens = 0
+        req.spec_token_ids = []
+        req.status = RequestStatus.PREEMPTED
+        req.num_preemptions += 1
+        if req not in self.waiting:
+            self.waiting.appendleft(req)
+
     # -------------------------------------------------------------- schedule
     def schedule(self) -> SchedulerOutput:
         self._step += 1

@@ -20,6 +20,8 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 import torch.distributed as dist
 
+from ..logger import logger
+
 from .communicator import B200Communicator
 
 
@@ -297,6 +299,53 @@ def destroy_distributed() -> None:
     destroy_model_parallel()
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def _all_groups() -> List[GroupCoordinator]:
+    gs = [g for g in (_S.world, _S.tp, _S.pp, _S.dp, _S.ep, _S.local) if g is not None]
+    gs += list((_S.layer_groups or {}).values())
+    seen, out = set(), []
+    for g in gs:
+        if id(g) not in seen:
+            seen.add(id(g))
+            out.append(g)
+    return out
+
+
+def abort_communicators() -> int:
+    """Abort the device communicators of every group so that collectives blocked on a
+    failed peer return (used by token recovery).  Returns how many were aborted."""
+    n = 0
+    for g in _all_groups():
+        pg = getattr(g, "device_group", None)
+        if pg is None:
+            continue
+        try:
+            backend = pg._get_backend(torch.device("cuda")) if _S.backend == "nccl" else None
+            abort = getattr(backend, "abort", None) or getattr(backend, "_abort", None)
+            if abort is not None:
+                abort()
+                n += 1
+        except Exception as e:        # best effort: a communicator that never started has nothing to abort
+            logger.debug("abort of %s: %s", getattr(g, "name", "?"), e)
+    return n
+
+
+def reinit_communicators() -> None:
+    """Bring the groups' communicators back after ``abort_communicators`` and drop
+    peer-mapped buffers whose signal state may be mid-flight (they are rebuilt lazily)."""
+    for g in _all_groups():
+        comm = getattr(g, "comm", None)
+        symm = getattr(comm, "symm", None)
+        if symm is not None:
+            try:
+                symm.close()
+            except Exception:
+                pass
+            comm.symm = None
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        world = getattr(_S, "world", None)
+        (world.barrier if world is not None else dist.barrier)()     # host-side rendezvous of the survivors
 
 
 def finish_process(engine=None, code: int = 0, deadline_s: float = 30.0) -> None:

@@ -17,6 +17,7 @@ import torch
 from .. import ops
 from ..config import EngineConfig
 from ..engine.scheduler import SchedulerOutput
+from ..ha.monitor import token_recover_wrapper
 from ..logger import logger
 from ..parallel import state as pstate
 from .model_runner import ModelRunner
@@ -28,6 +29,7 @@ class Worker:
         self.config = config
         self.local_rank = local_rank
         self.rank = rank
+        self.ha_agent = None            # token recovery (ha/monitor.py), off unless enabled
         self.distributed_init_method = distributed_init_method
         self.is_driver_worker = is_driver_worker
         self.device: Optional[torch.device] = None
@@ -110,6 +112,7 @@ class Worker:
             world.barrier()
 
     # ------------------------------------------------------------- running
+    @token_recover_wrapper
     def execute_model(self, out: SchedulerOutput) -> List[int]:
         if self._profile_threshold and self.profiler is not None:
             if self._profile_steps_left == 0 and out.total_num_scheduled_tokens == self._profile_threshold:
@@ -121,6 +124,35 @@ class Worker:
             if self._profile_steps_left == 0:
                 self.profiler.stop()
         return tokens
+
+    # ------------------------------------------------ token recovery hooks
+    def enable_token_recovery(self, env=None) -> None:
+        """Start this worker's command endpoint and register it with the coordinator
+        (``USE_HA=1``, ``HA_SERVER_IP``, ``HA_PORT``)."""
+        from ..ha.common import HAEnv
+        from ..ha.monitor import HAWorkerAgent
+        env = env or HAEnv.from_environ()
+        if env.use_ha and self.ha_agent is None:
+            self.ha_agent = HAWorkerAgent(env, self.rank, self.local_rank).start()
+
+    def stop_device(self) -> None:
+        """Leave whatever the device is doing: wait (bounded by the communicators' own
+        timeouts) for queued work and abort the communicators so peers' collectives end."""
+        if self.device.type == "cuda":
+            try:
+                torch.cuda.synchronize(self.device)
+            except Exception as e:
+                logger.warning("synchronize during stop_device: %s", e)
+        pstate.abort_communicators()
+
+    def restart_device(self) -> None:
+        """Drop state that may be inconsistent after a failed step (captured graphs stay
+        valid: they hold no communicator handles of torch.distributed)."""
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def reinit_process_group(self) -> None:
+        pstate.reinit_communicators()
 
     def execute_dummy_batch(self) -> None:
         self.model_runner.execute_dummy_batch()
