@@ -248,6 +248,9 @@ class ParallelConfig:
     data_parallel_size: int = 1
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
+    # keep the residual stream sharded by tokens inside the tensor-parallel group
+    # (reduce-scatter / all-gather around every block instead of all-reduce)
+    sequence_parallel_residual: bool = False
     # per-layer overrides: {"layer name suffix": {"tp_size_or_ranks": ..., "x_transform": ..., ...}}
     layer_parallel_config: Dict[str, Any] = field(default_factory=dict)
 

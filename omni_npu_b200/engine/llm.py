@@ -187,6 +187,7 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                          pipeline_parallel_size=kw.pop("pipeline_parallel_size", 1),
                          data_parallel_size=kw.pop("data_parallel_size", 1),
                          enable_expert_parallel=kw.pop("enable_expert_parallel", False),
+                         sequence_parallel_residual=kw.pop("sequence_parallel_residual", False),
                          layer_parallel_config=kw.pop("layer_parallel_config", {}) or {})
     sched = SchedulerConfig(max_num_seqs=kw.pop("max_num_seqs", 128),
                             max_num_batched_tokens=kw.pop("max_num_batched_tokens", 8192),

@@ -78,8 +78,17 @@ class LlamaDecoderLayer(nn.Module):
         hidden = self.mlp(hidden, reduce=False)
         return hidden, residual
 
+    def forward_sequence_parallel(self, sp, hidden: Optional[torch.Tensor], residual: torch.Tensor):
+        """The same layer on a token-sharded residual stream (layers/flashcomm.py)."""
+        hidden, residual = sp.block(self.input_layernorm, hidden, residual,
+                                    lambda full: self.self_attn(full, reduce=False))
+        return sp.block(self.post_attention_layernorm, hidden, residual,
+                        lambda full: self.mlp(full, reduce=False))
+
 
 class LlamaModel(nn.Module):
+    sequence_parallel = False       # set by the owning model from ParallelConfig
+
     def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:
         super().__init__()
         self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
@@ -90,10 +99,19 @@ class LlamaModel(nn.Module):
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
                 inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        tp = pstate.get_tp_group()
+        if self.sequence_parallel and tp.world_size > 1:
+            from ..layers.flashcomm import SequenceParallelStream
+            sp = SequenceParallelStream(tp)
+            residual, hidden = sp.scatter(hidden), None
+            for layer in self.layers:
+                hidden, residual = layer.forward_sequence_parallel(sp, hidden, residual)
+            hidden, _ = self.norm(hidden, residual)
+            return sp.gather(hidden, trim=True)
         residual = None
         for layer in self.layers:
             hidden, residual = layer(hidden, residual)
-        hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, pstate.get_tp_group())
+        hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, tp)
         return hidden
 
 
@@ -109,6 +127,7 @@ class LlamaForCausalLM(nn.Module):
         cfg = engine_config.model
         self.config = cfg
         self.model = LlamaModel(cfg, device)
+        self.model.sequence_parallel = bool(engine_config.parallel.sequence_parallel_residual)
         if cfg.tie_word_embeddings:
             self.lm_head = self.model.embed_tokens
             self.lm_head.__class__ = ParallelLMHead

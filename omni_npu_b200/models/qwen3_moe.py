@@ -67,11 +67,25 @@ class Qwen3MoeDecoderLayer(nn.Module):
             return self.mlp(hidden), residual, False
         return self.mlp(hidden, reduce=False), residual, True
 
+    def forward_sequence_parallel(self, sp, hidden: Optional[torch.Tensor], residual: torch.Tensor):
+        """Token-sharded residual stream (layers/flashcomm.py): attention between an
+        all-gather and a reduce-scatter; the MoE block consumes the gathered rows and its
+        (already complete) output is sliced back to this rank's tokens."""
+        hidden, residual = sp.block(self.input_layernorm, hidden, residual,
+                                    lambda full: self.self_attn(full, reduce=False))
+        if not self.is_moe:
+            return sp.block(self.post_attention_layernorm, hidden, residual,
+                            lambda full: self.mlp(full, reduce=False))
+        normed, residual = self.post_attention_layernorm(hidden, residual)
+        full = sp.gather(normed)[: sp.num_tokens]
+        return sp.scatter(self.mlp(full)), residual
+
 
 class Qwen3MoeModel(nn.Module):
     def __init__(self, engine: EngineConfig, device) -> None:
         super().__init__()
         cfg = engine.model
+        self.sequence_parallel = bool(engine.parallel.sequence_parallel_residual)
         self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
         self.layers = nn.ModuleList([Qwen3MoeDecoderLayer(cfg, i, device, f"model.layers.{i}", engine)
                                      for i in range(cfg.num_layers)])
@@ -79,6 +93,15 @@ class Qwen3MoeModel(nn.Module):
 
     def forward(self, input_ids, positions, inputs_embeds=None) -> torch.Tensor:
         hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        tp = pstate.get_tp_group()
+        if self.sequence_parallel and tp.world_size > 1:
+            from ..layers.flashcomm import SequenceParallelStream
+            sp = SequenceParallelStream(tp)
+            residual, hidden = sp.scatter(hidden), None
+            for layer in self.layers:
+                hidden, residual = layer.forward_sequence_parallel(sp, hidden, residual)
+            hidden, _ = self.norm(hidden, residual)
+            return sp.gather(hidden, trim=True)
         residual, pending = None, False
         for layer in self.layers:
             hidden, residual, pending = layer(hidden, residual, pending)

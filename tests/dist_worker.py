@@ -77,6 +77,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
               max_model_len=256, block_size=16, num_gpu_blocks=64)
     if device_kind == "cpu":
         kw["dtype"] = "float32"
+    if os.path.exists(os.path.join(workdir, "sequence_parallel")):
+        kw["sequence_parallel_residual"] = True
     llm = LLM(model=model_dir, **kw)
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs]},

@@ -44,6 +44,24 @@ def test_tensor_parallel_engine_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
+def test_sequence_parallel_residual_stream_matches_plain_pytorch():
+    """Token-sharded residual stream (reduce-scatter / all-gather around every block); prompt
+    lengths that do not divide by the group size exercise the padding."""
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=5)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (21, 34, 7)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "sequence_parallel"), "w").close()
+        res = run_ranks("tp_engine", 2, d)
+    for p, toks in zip(prompts, res[0]["tokens"]):
+        assert toks == refm.greedy_generate(weights, cfg, p, 12)
+    assert res[0]["tokens"] == res[1]["tokens"]
+
+
 def test_expert_parallel_moe_two_ranks_gloo():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("ep_moe", 2, d)
