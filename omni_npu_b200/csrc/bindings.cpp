@@ -33,6 +33,11 @@ int b200_silu_mul(void* out, const void* x, long long rows, int I, long long x_s
                   long long out_stride, cudaStream_t stream);
 int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, int H,
                          long long x_stride, int ue8m0, cudaStream_t stream);
+int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long rows, int H,
+                              long long x_stride, cudaStream_t stream);
+int b200_gemm_scaled(const void* A, const void* W, void* C, const float* a_scales, const float* w_scales,
+                     const void* bias, const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
+                     int kind, int out_fp32, int BN, int* status, int max_ctas, cudaStream_t stream);
 int b200_rope_qk(void* q, void* k, const int* positions, const float* cos_sin, int T, int Hq,
                  int Hk, int D, int rot_dim, int neox, long long q_stride, long long k_stride,
                  int sec_t, int sec_h, int interleaved_mrope, cudaStream_t stream);
@@ -278,6 +283,57 @@ std::tuple<Tensor, Tensor> quant_fp8_1x128(const Tensor& x, bool ue8m0) {
                              ue8m0 ? 1 : 0, cur_stream()),
         "quant_fp8_1x128");
   return {q, s};
+}
+
+std::tuple<Tensor, Tensor> quant_int8_per_token(const Tensor& x) {
+  CHECK_CUDA_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "quant_int8_per_token: 2-D, last dim contiguous");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = torch::empty({x.size(0), x.size(1)}, x.options().dtype(at::kChar));
+  Tensor s = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  check(b200_quant_int8_per_token(q.data_ptr(), s.data_ptr(), x.data_ptr(), x.size(0), (int)x.size(1),
+                                  x.stride(0), cur_stream()),
+        "quant_int8_per_token");
+  return {q, s};
+}
+
+// Quantised GEMM: (a_q @ w_q^T) * a_scale[:, None] * w_scale[None, :] (+bias, +residual).
+// int8 x int8 (s32 accumulate) or e4m3 x e4m3 (fp32 accumulate).
+Tensor gemm_scaled(const Tensor& a, const Tensor& w, const Tensor& a_scale, const Tensor& w_scale,
+                   const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual, bool out_fp32,
+                   int64_t bn, const Tensor& status, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_scaled: 2-D CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == w.scalar_type(), "gemm_scaled: dtype mismatch");
+  const bool i8 = a.scalar_type() == at::kChar;
+  TORCH_CHECK(i8 || a.scalar_type() == at::kFloat8_e4m3fn, "gemm_scaled: int8 or float8_e4m3fn inputs");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1, "gemm_scaled: K must be contiguous");
+  const int M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && K % 16 == 0, "gemm_scaled: K mismatch / K must be a multiple of 16");
+  TORCH_CHECK(a_scale.is_cuda() && a_scale.scalar_type() == at::kFloat && a_scale.numel() == M &&
+                  a_scale.is_contiguous(), "gemm_scaled: a_scale fp32 [M]");
+  TORCH_CHECK(w_scale.is_cuda() && w_scale.scalar_type() == at::kFloat && w_scale.numel() == N &&
+                  w_scale.is_contiguous(), "gemm_scaled: w_scale fp32 [N]");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor c = torch::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  const void* bias_p = nullptr;
+  const void* res_p = nullptr;
+  if (bias.has_value()) {
+    CHECK_CUDA_BF16(*bias);
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "gemm_scaled: bias [N]");
+    bias_p = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    CHECK_CUDA_BF16(*residual);
+    TORCH_CHECK(residual->is_contiguous() && residual->size(0) == M && residual->size(1) == N,
+                "gemm_scaled: residual [M,N] contiguous");
+    res_p = residual->data_ptr();
+  }
+  check(b200_gemm_scaled(a.data_ptr(), w.data_ptr(), c.data_ptr(), a_scale.data_ptr<float>(),
+                         w_scale.data_ptr<float>(), bias_p, res_p, M, N, K, (int)a.stride(0), (int)w.stride(0),
+                         N, i8 ? 2 : 1, out_fp32 ? 1 : 0, (int)bn, status.data_ptr<int>(), (int)max_ctas,
+                         cur_stream()),
+        "gemm_scaled");
+  return c;
 }
 
 void rope_qk(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin, int64_t head_dim,
@@ -558,6 +614,8 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gemm_plan", &gemm_plan);
   m.def("gemm", &gemm);
   m.def("gemm_pair", &gemm_pair);
+  m.def("gemm_scaled", &gemm_scaled);
+  m.def("quant_int8_per_token", &quant_int8_per_token);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);
   m.def("fused_add_rms_norm", &fused_add_rms_norm);

@@ -336,9 +336,38 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, u
 // the low words (start address >> 4) change between K steps, and the accumulate flag of all
 // but the first MMA of a tile is the constant 1.
 constexpr uint32_t kSmemDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
-template <bool FP8>
+// Operand kinds of the GEMM kernels: bf16, fp8 (e4m3) and int8 (s8 x s8 -> s32).
+constexpr int kKindBF16 = 0, kKindFP8 = 1, kKindI8 = 2;
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int KIND>
 __device__ __forceinline__ void umma_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
-  if constexpr (FP8) {
+  if constexpr (KIND == kKindI8) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .pred p;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kSmemDescHiSw128), "r"(idesc)
+        : "memory");
+  } else if constexpr (KIND == kKindFP8) {
     asm volatile(
         "{\n\t"
         ".reg .b64 da, db;\n\t"
@@ -366,12 +395,13 @@ __device__ __forceinline__ void umma_acc(uint32_t d_tmem, uint32_t a_lo, uint32_
         : "memory");
   }
 }
-template <bool FP8>
+template <int KIND>
 __device__ __forceinline__ void umma_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
                                            uint32_t accumulate) {
   const uint64_t da = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | a_lo;
   const uint64_t db = (static_cast<uint64_t>(kSmemDescHiSw128) << 32) | b_lo;
-  if constexpr (FP8) umma_f8(d_tmem, da, db, idesc, accumulate);
+  if constexpr (KIND == kKindI8) umma_i8(d_tmem, da, db, idesc, accumulate);
+  else if constexpr (KIND == kKindFP8) umma_f8(d_tmem, da, db, idesc, accumulate);
   else umma_f16(d_tmem, da, db, idesc, accumulate);
 }
 template <bool FP8>
@@ -429,6 +459,11 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
 // Instruction descriptor for kind::f16 / kind::f8f6f4, fp32 accumulate,
 // both operands K-major.  fmt: f16 0 / bf16 1 for kind::f16; e4m3 0 / e5m2 1
 // for kind::f8f6f4.
+// kind::i8: signed 8-bit operands (format 1), 32-bit integer accumulator (format 2).
+__host__ __device__ constexpr uint32_t make_idesc_i8(uint32_t m, uint32_t n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m,
                                                   uint32_t n) {
   return (1u << 4)            // accumulator format: fp32

@@ -59,8 +59,8 @@ struct GemmParams {
   float* workspace;                // split-K partials [splits][M_pad][N_pad]
   int* tile_counters;              // split-K arrival counters, one per (m,n) tile, zero at rest
   const int* expert_offsets;       // grouped: [E+1] row offsets into A / C (device)
-  const float* a_scales;           // fp8: [M, ceil(K/128)] per-row-per-128 scales or null
-  const float* w_scales;           // fp8: [E][ceil(N/128)][ceil(K/128)] block scales or null
+  const float* a_scales;           // quantised inputs: [M] per-row scales or null (direct epilogue only)
+  const float* w_scales;           // quantised inputs: [N] per-column scales (with a_scales)
   int* status;                     // error word (0 = ok)
 };
 
@@ -121,7 +121,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const int* s_ti
   return true;
 }
 
-template <bool GROUPED, bool FP8>
+template <bool GROUPED, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
@@ -266,7 +266,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = FP8 ? make_idesc(0, 0, kBM, p.BN) : make_idesc(1, 1, kBM, p.BN);
+      const uint32_t idesc = KIND == kKindI8 ? make_idesc_i8(kBM, p.BN)
+                             : (KIND == kKindFP8 ? make_idesc(0, 0, kBM, p.BN) : make_idesc(1, 1, kBM, p.BN));
       // low words of the shared-memory descriptors (start address >> 4) and the slab pitch
       const uint32_t a_lo0 = (smem_u32(smem_a) & 0x3FFFF) >> 4, w_lo0 = (smem_u32(smem_w) & 0x3FFFF) >> 4;
       const uint32_t a_slab_lo = static_cast<uint32_t>(a_stage_bytes) >> 4, w_slab_lo = static_cast<uint32_t>(w_stage_bytes) >> 4;
@@ -302,10 +303,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * p.ksub) * w_slab_lo;
           for (int j = 0; j < ns; ++j) {
             // 32 bytes of K per instruction: the start-address field advances by 2
-            umma_first<FP8>(d_tmem, a_lo, w_lo, idesc, (k > tc.k_begin || j > 0) ? 1u : 0u);
-            umma_acc<FP8>(d_tmem, a_lo + 2, w_lo + 2, idesc);
-            umma_acc<FP8>(d_tmem, a_lo + 4, w_lo + 4, idesc);
-            umma_acc<FP8>(d_tmem, a_lo + 6, w_lo + 6, idesc);
+            umma_first<KIND>(d_tmem, a_lo, w_lo, idesc, (k > tc.k_begin || j > 0) ? 1u : 0u);
+            umma_acc<KIND>(d_tmem, a_lo + 2, w_lo + 2, idesc);
+            umma_acc<KIND>(d_tmem, a_lo + 4, w_lo + 4, idesc);
+            umma_acc<KIND>(d_tmem, a_lo + 6, w_lo + 6, idesc);
             a_lo += a_slab_lo;
             w_lo += w_slab_lo;
           }
@@ -491,8 +492,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_wait();
         float v[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 16; ++i) {
+          if constexpr (KIND == kKindI8) v[i] = static_cast<float>(static_cast<int>(r[i]));
+          else v[i] = __uint_as_float(r[i]);
+        }
         const int col = tc.n0 + c;
+        if (p.a_scales != nullptr && row_ok && !partial) {
+          // per-row (token) times per-column (output channel) scales of a quantised product
+          const float sa = p.a_scales[row];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (col + i < p.N) v[i] *= sa * p.w_scales[col + i];
+        }
         if (partial) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) ws_col[static_cast<size_t>(c + i) * kBM] = v[i];
@@ -743,10 +754,10 @@ static int next_pow2_cols(int x) {
   return c;
 }
 
-template <bool GROUPED, bool FP8>
+template <bool GROUPED, int KIND>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
                   size_t smem, cudaStream_t stream) {
-  auto kern = gemm_tcgen05_kernel<GROUPED, FP8>;
+  auto kern = gemm_tcgen05_kernel<GROUPED, KIND>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -881,11 +892,36 @@ extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, 
 // handling here; callers fold scales, see the block-scaled wrapper).
 // workspace / counters may be null when splits == 1 or cluster_split == 1.
 // Returns 0 on success.
+static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
+                     int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
+                     int splits, int cluster_split, void* workspace, int* counters, int* status,
+                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales);
+
 extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
                          const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
                          int dtype_fp8, int out_fp32, int swiglu, int BN, int splits,
                          int cluster_split, void* workspace, int* counters, int* status,
                          int max_ctas, cudaStream_t stream) {
+  return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, dtype_fp8, out_fp32, swiglu, BN, splits,
+                   cluster_split, workspace, counters, status, max_ctas, stream, nullptr, nullptr);
+}
+
+// Quantised product with per-row (a_scales[M]) and per-column (w_scales[N]) scales applied to
+// the accumulator: kind 1 = e4m3 operands, 2 = int8 operands (s32 accumulate).  No split-K.
+extern "C" int b200_gemm_scaled(const void* A, const void* W, void* C, const float* a_scales,
+                                const float* w_scales, const void* bias, const void* residual, int M, int N,
+                                int K, int lda, int ldw, int ldc, int kind, int out_fp32, int BN, int* status,
+                                int max_ctas, cudaStream_t stream) {
+  if (kind != 1 && kind != 2) return -15;
+  if (a_scales == nullptr || w_scales == nullptr) return -16;
+  return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, kind, out_fp32, 0, BN, 1, 0, nullptr,
+                   nullptr, status, max_ctas, stream, a_scales, w_scales);
+}
+
+static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
+                     int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
+                     int splits, int cluster_split, void* workspace, int* counters, int* status,
+                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
@@ -920,6 +956,8 @@ extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias
   p.tile_counters = counters;
   p.expert_offsets = nullptr;
   p.status = status;
+  p.a_scales = a_scales;
+  p.w_scales = w_scales;
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kRowBytes / eb;
@@ -941,8 +979,9 @@ extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (tiles < grid) grid = static_cast<int>(tiles);
   }
-  if (dtype_fp8) return launch<false, true>(ta, tw, p, grid, smem, stream);
-  return launch<false, false>(ta, tw, p, grid, smem, stream);
+  if (dtype_fp8 == 2) return launch<false, kKindI8>(ta, tw, p, grid, smem, stream);
+  if (dtype_fp8) return launch<false, kKindFP8>(ta, tw, p, grid, smem, stream);
+  return launch<false, kKindBF16>(ta, tw, p, grid, smem, stream);
 }
 
 // Grouped GEMM over E experts.  A [total_rows, K] holds each expert's rows
@@ -992,6 +1031,6 @@ extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const in
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const size_t smem = smem_bytes_for(BN, stages, num_experts);
-  if (dtype_fp8) return launch<true, true>(ta, tw, p, grid, smem, stream);
-  return launch<true, false>(ta, tw, p, grid, smem, stream);
+  if (dtype_fp8) return launch<true, kKindFP8>(ta, tw, p, grid, smem, stream);
+  return launch<true, kKindBF16>(ta, tw, p, grid, smem, stream);
 }

@@ -239,6 +239,41 @@ extern "C" int b200_silu_mul(void* out, const void* x, long long rows, int I, lo
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// ---------------------------------------------------------------- int8 per token
+// Dynamic symmetric quantisation of activations: one scale per row,
+// q = round(x / scale), scale = max|x| / 127.  One CTA per row.
+__global__ void __launch_bounds__(256)
+quant_int8_per_token_kernel(int8_t* __restrict__ q, float* __restrict__ scales,
+                            const __nv_bfloat16* __restrict__ x, int H, long long x_stride) {
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * x_stride;
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(xr[i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+  const float scale = fmaxf(amax, 1e-10f) / 127.f;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) scales[row] = scale;
+  int8_t* qr = q + row * static_cast<long long>(H);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = rintf(__bfloat162float(xr[i]) * inv);
+    qr[i] = static_cast<int8_t>(fminf(fmaxf(v, -127.f), 127.f));
+  }
+}
+
+extern "C" int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long rows, int H,
+                                         long long x_stride, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  quant_int8_per_token_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
+      static_cast<int8_t*>(q), static_cast<float*>(scales), static_cast<const __nv_bfloat16*>(x), H, x_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 extern "C" int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, int H,
                                     long long x_stride, int ue8m0, cudaStream_t stream) {
   if (rows <= 0) return 0;

@@ -72,6 +72,60 @@ class KVExport:
 class _Link:
     tensors: List[torch.Tensor]
     created: float = field(default_factory=time.monotonic)
+    mappings: List[Any] = field(default_factory=list)     # IPC mappings this link opened (CUDA)
+
+
+class _RemoteView:
+    """A tensor-like handle on memory of another GPU mapped into this process: just what the
+    copy kernel and the layout checks need (address, shape, dtype)."""
+
+    def __init__(self, ptr: int, shape, dtype: torch.dtype) -> None:
+        self._ptr, self.shape, self.dtype = ptr, torch.Size(shape), dtype
+
+    def data_ptr(self) -> int:
+        return self._ptr
+
+    def element_size(self) -> int:
+        return self.dtype.itemsize
+
+
+def _open_ipc_exports(ipc, shapes, dtype: torch.dtype):
+    """Map a producer's cache tensors on THIS rank's current device.  The handles come from
+    torch's storage sharing (handle of the allocation + byte offset of the storage in it); they
+    are opened with cudaIpcOpenMemHandle + lazy peer access in the current context, so kernels
+    of this GPU may dereference the addresses (a mapping made in the producer device's context
+    is not accessible from another GPU without peer access enabled).  One allocation is opened
+    once even when several tensors live in it."""
+    import ctypes
+
+    from ..parallel.symm_mem import _lib
+    lib = _lib()
+    opened: Dict[bytes, int] = {}
+    mappings: List[Any] = []
+    views: List[_RemoteView] = []
+    try:
+        for (info, offset_elems, stride), shape in zip(ipc, shapes):
+            handle, storage_off = bytes(info[1]), int(info[3])
+            want = tuple(int(x) for x in stride)
+            dense = tuple(torch.empty(shape, device="meta").stride())
+            if want != dense:
+                raise ValueError(f"remote cache tensor is not contiguous (strides {want})")
+            base = opened.get(handle)
+            if base is None:
+                p = ctypes.c_void_p()
+                rc = lib.b200_symm_open(handle, ctypes.byref(p))
+                if rc != 0:
+                    raise ConnectionError(f"cudaIpcOpenMemHandle failed ({rc}); peer access between the "
+                                          "two GPUs is required")
+                base = p.value
+                opened[handle] = base
+                mappings.append(p)
+            views.append(_RemoteView(base + storage_off + int(offset_elems) * dtype.itemsize, shape, dtype))
+    except Exception:
+        for p in mappings:
+            lib.b200_symm_close(p)
+        raise
+    return views, mappings
 
 
 class KVLinkManager:
@@ -112,22 +166,19 @@ class KVLinkManager:
             if len(export.shapes) != len(self.local):
                 raise ValueError(f"remote instance has {len(export.shapes)} cache tensors, local has "
                                  f"{len(self.local)}: layouts do not match")
+            mappings: List[Any] = []
             if export.device_type == "cpu":
                 tensors = _LOCAL_EXPORTS.get(key)
                 if tensors is None:
                     raise ConnectionError(f"no export registered for {key}")
             else:
                 dtype = getattr(torch, export.dtype.replace("torch.", ""))
-                tensors = []
-                for (info, offset, stride), shape in zip(export.ipc, export.shapes):
-                    storage = torch.UntypedStorage._new_shared_cuda(*info)
-                    t = torch.empty(0, dtype=dtype, device=storage.device).set_(storage, offset, shape, stride)
-                    tensors.append(t)
+                tensors, mappings = _open_ipc_exports(export.ipc, export.shapes, dtype)
             for mine, theirs in zip(self.local, tensors):
                 if mine.shape[1:] != theirs.shape[1:] or mine.dtype != theirs.dtype:
                     raise ValueError("KV block layout differs between the two instances: "
                                      f"{tuple(mine.shape[1:])} vs {tuple(theirs.shape[1:])}")
-            self.links[key] = _Link(tensors)
+            self.links[key] = _Link(tensors, mappings=mappings)
             self._desc_cache.pop(key, None)
             logger.info("KV link up: %s -> %s", f"{self.cluster_id}/{self.rank}", key)
 
@@ -135,8 +186,14 @@ class KVLinkManager:
         with self._lock:
             for key in [k for k in self.links if k.split("/")[0] == cluster_id and
                         (rank is None or k.endswith(f"/{rank}"))]:
-                del self.links[key]
+                link = self.links.pop(key)
                 self._desc_cache.pop(key, None)
+                if link.mappings:
+                    if self._stream is not None:
+                        self._stream.synchronize()           # no copy may still read the mapping
+                    from ..parallel.symm_mem import _lib
+                    for p in link.mappings:
+                        _lib().b200_symm_close(p)
                 logger.info("KV link closed: %s", key)
 
     def force_unlink(self, cluster_id: str) -> None:

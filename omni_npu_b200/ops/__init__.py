@@ -195,6 +195,30 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   bool(cluster), ws, cnt, st.status, max_ctas)
 
 
+def quant_int8_per_token(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dynamic symmetric int8 quantisation, one scale per row: (q int8 [T,H], scale fp32 [T])."""
+    if not x.is_cuda:
+        return ref.quant_int8_per_token(x)
+    _count(1)
+    return _C().quant_int8_per_token(x)
+
+
+def gemm_scaled(a_q: torch.Tensor, w_q: torch.Tensor, a_scale: torch.Tensor, w_scale: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``(a_q @ w_q.T) * a_scale[:, None] * w_scale[None, :]`` (+bias, +residual) for int8 or
+    e4m3 operands; integer products accumulate exactly in 32 bits on the tensor cores."""
+    if not a_q.is_cuda:
+        return ref.gemm_scaled(a_q, w_q, a_scale, w_scale, bias, residual, out_dtype)
+    st = device_state(a_q.device)
+    if bn <= 0:
+        n = w_q.shape[0]
+        bn = 256 if n >= 2048 else (128 if n >= 128 else max(16, (n + 15) // 16 * 16))
+    _count(1)
+    return _C().gemm_scaled(a_q, w_q, a_scale.contiguous(), w_scale.reshape(-1).contiguous(), bias, residual,
+                            out_dtype == torch.float32, bn, st.status, max_ctas)
+
+
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
                  swiglu: bool = False, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """Per-expert GEMM: rows expert_offsets[e]:expert_offsets[e+1] of ``a`` times ``w[e].T``."""

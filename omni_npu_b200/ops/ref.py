@@ -373,3 +373,22 @@ def spec_verify(draft: torch.Tensor, target: torch.Tensor, bonus: torch.Tensor, 
             emitted += 1
         num[r] = emitted
     return out, num
+
+
+def quant_int8_per_token(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    xf = x.float()
+    scale = xf.abs().amax(dim=-1).clamp_min(1e-10) / 127.0
+    q = torch.round(xf / scale.unsqueeze(-1)).clamp_(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def gemm_scaled(a_q: torch.Tensor, w_q: torch.Tensor, a_scale: torch.Tensor, w_scale: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    acc = a_q.double() @ w_q.double().t()          # exact for int8 products
+    out = acc.float() * a_scale.float().reshape(-1, 1) * w_scale.float().reshape(1, -1)
+    if bias is not None:
+        out = out + bias.float()
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(out_dtype or torch.bfloat16)

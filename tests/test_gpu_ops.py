@@ -119,6 +119,40 @@ def test_gemm_cta_pair_epilogues_and_fp8():
     ops.check_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (200, 1000, 4096), (1, 4096, 4096), (777, 6144, 1024)])
+def test_gemm_int8_scaled(m, n, k):
+    """int8 x int8 with s32 accumulation on the tensor cores; per-token x per-channel scales."""
+    torch.manual_seed(8)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV) * 0.05
+    xq, xs = ops.quant_int8_per_token(x)
+    rq, rs = ref.quant_int8_per_token(x.cpu())
+    assert (xq.cpu().int() - rq.int()).abs().max() <= 1 and torch.allclose(xs.cpu(), rs, rtol=1e-3)
+    ws = w.abs().amax(dim=1) / 127.0
+    wq = torch.round(w / ws[:, None]).clamp(-127, 127).to(torch.int8)
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    out = ops.gemm_scaled(xq, wq, xs, ws, bias, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ref.gemm_scaled(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu(), bias.cpu(), out_dtype=torch.float32)
+    _close(out, want, atol=2e-3 * math.sqrt(k / 64), rtol=1e-3)     # integer accumulation is exact
+    # against the unquantised product: quantisation error only
+    full = x.float().cpu() @ w.cpu().t() + bias.float().cpu()
+    assert (out.cpu() - full).abs().max() < 0.05 * full.abs().max() + 0.05
+
+
+def test_gemm_fp8_scaled():
+    torch.manual_seed(9)
+    m, n, k = 300, 512, 1024
+    a = (torch.randn(m, k, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    w = (torch.randn(n, k, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    sa = torch.rand(m, device=DEV) + 0.5
+    sw = torch.rand(n, device=DEV) + 0.5
+    out = ops.gemm_scaled(a, w, sa, sw, out_dtype=torch.float32)
+    want = (a.float().cpu() @ w.float().cpu().t()) * sa.cpu()[:, None] * sw.cpu()[None, :]
+    _close(out, want, atol=0.05, rtol=1e-2)
+
+
 def test_grouped_gemm():
     torch.manual_seed(3)
     e, n, k = 8, 512, 1024
