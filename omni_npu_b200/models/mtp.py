@@ -119,3 +119,58 @@ class MultiTokenPredictor(nn.Module):
 
 def select_rows(hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return hidden.index_select(0, rows.long())
+
+
+class _StandaloneMTP(nn.Module):
+    """A draft model made of the MTP layers of a checkpoint alone, for deployments that load
+    the draft as its own model (architectures ``DeepSeekMTPModel`` / ``OpenPanguMTPModel``).
+    It owns an embedding and an LM head (the checkpoint usually repeats both under the MTP
+    layer's prefix).  ``forward`` needs the target model's hidden states."""
+    layer_cls_path = ("omni_npu_b200.models.deepseek", "DeepseekDecoderLayer")
+
+    def __init__(self, engine_config: EngineConfig, device=None) -> None:
+        super().__init__()
+        import importlib
+
+        from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
+        cfg = engine_config.model
+        self.config = cfg
+        mod, name = self.layer_cls_path
+        layer_cls = getattr(importlib.import_module(mod), name)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+        self.mtp = MultiTokenPredictor(engine_config, device,
+                                       lambda idx, prefix: layer_cls(engine_config, idx, device, prefix))
+        self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
+        self.num_kv_layers = cfg.num_layers + self.mtp.num_mtp_layers      # cache indices follow the target's
+
+    def forward(self, input_ids, positions, previous_hidden, spec_step: int = 0):
+        return self.mtp(self.embed_tokens(input_ids), previous_hidden, spec_step)
+
+    def compute_logits(self, hidden):
+        return self.lm_head.compute_logits(hidden)
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]]) -> set:
+        from .utils import load_stacked_weights
+        renamed: List[Tuple[str, torch.Tensor]] = []
+        for name, t in weights:
+            new = self.mtp.rewrite_name(name)
+            if new is None:
+                if name in ("model.embed_tokens.weight", "lm_head.weight"):
+                    renamed.append((name.replace("model.", ""), t))
+                continue
+            if new == "__shared_embedding__":
+                renamed.append(("embed_tokens.weight", t))
+            elif new == "__shared_head__":
+                renamed.append(("lm_head.weight", t))
+            else:
+                renamed.append(("mtp." + new, t))
+        stacked = [(".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1)]
+        return load_stacked_weights(self, renamed, stacked, skip_substrings=("rotary_emb.inv_freq",))
+
+
+class DeepSeekMTP(_StandaloneMTP):
+    layer_cls_path = ("omni_npu_b200.models.deepseek", "DeepseekDecoderLayer")
+
+
+class OpenPanguMTP(_StandaloneMTP):
+    layer_cls_path = ("omni_npu_b200.models.pangu", "PanguUltraDecoderLayer")
