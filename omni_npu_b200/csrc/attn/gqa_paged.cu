@@ -53,6 +53,7 @@ struct AttnParams {
   float scale_log2;           // softmax scale * log2(e)
   int causal;
   int window;                 // sliding window (keys older than pos - window + 1 masked), 0 = off
+  int sink;                   // leading keys [0, sink) stay visible whatever the window (0 = none)
   // decode only
   int q_len;                  // tokens per sequence in this step (>=1)
   int splits;
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(256, 1) gqa_prefill_kernel(const AttnParams p)
   const int last_row = min(q_len, m0 + Cfg::BM) - 1;
   const int kv_end = p.causal ? min(kv_len, ctx + last_row + 1) : kv_len;
   int kv_start = 0;
-  if (p.window > 0) kv_start = max(0, ctx + m0 - p.window + 1) / Cfg::BN * Cfg::BN;
+  // (with sink tokens the leading tiles must stay: no skipping then)
+  if (p.window > 0 && p.sink == 0) kv_start = max(0, ctx + m0 - p.window + 1) / Cfg::BN * Cfg::BN;
   const int n_tiles = (kv_end - kv_start + Cfg::BN - 1) / Cfg::BN;
 
   load_kv_tile<DQK, Cfg::BN, Cfg::THREADS>(sK, p.k_cache, bt, kv_start, kv_end, kvh, p.Hk,
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(256, 1) gqa_prefill_kernel(const AttnParams p)
           const int pos = pos_a + ((j >> 1) << 3);
           bool ok = key < kv_end;
           if (p.causal) ok = ok && key <= pos;
-          if (p.window > 0) ok = ok && key > pos - p.window;
+          if (p.window > 0) ok = ok && (key > pos - p.window || key < p.sink);
           if (!ok) v = -INFINITY;
         }
         s[i][j] = v;
@@ -443,7 +445,7 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const AttnParams p) {
         const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
         const int pos = pos_r[j >> 1];
         bool ok = key <= pos && key < kv_len;
-        if (p.window > 0) ok = ok && key > pos - p.window;
+        if (p.window > 0) ok = ok && (key > pos - p.window || key < p.sink);
         const float v = ok ? s[i][j] * p.scale_log2 : -INFINITY;
         s[i][j] = v;
         tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
@@ -762,7 +764,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
         const int pos = pos_r[j >> 1];
         bool keep = key <= pos && key < kv_len;
-        if (p.window > 0) keep = keep && key > pos - p.window;
+        if (p.window > 0) keep = keep && (key > pos - p.window || key < p.sink);
         const float v = keep ? s[i][j] * p.scale_log2 : -INFINITY;
         s[i][j] = v;
         tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
@@ -1018,7 +1020,8 @@ extern "C" int b200_gqa_prefill(const void* q, const void* k_cache, const void* 
   p.out_stride = out_stride;
   p.scale_log2 = scale * kLog2e;
   p.causal = causal;
-  p.window = window;
+  p.window = window & 0xFFFFF;   // low 20 bits: sliding window; upper bits: leading sink tokens
+  p.sink = window >> 20;
   p.q_len = 0;
   p.splits = 1;
   if (Dqk == 128 && Dv == 128) return launch_prefill<128, 128>(p, B, max_q_len, stream);
@@ -1060,7 +1063,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.out_stride = out_stride;
   p.scale_log2 = scale * kLog2e;
   p.causal = 1;
-  p.window = window;
+  p.window = window & 0xFFFFF;   // low 20 bits: sliding window; upper bits: leading sink tokens
+  p.sink = window >> 20;
   p.q_len = q_len;
   p.splits = splits;
   p.status = status;

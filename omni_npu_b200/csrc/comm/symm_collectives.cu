@@ -383,6 +383,197 @@ reducescatter_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restric
   }
 }
 
+
+// ------------------------------------------------------- push all-reduce ("LL")
+// Latency-optimised all-reduce for small messages: no barrier at all.  Every rank
+// PUSHES its vectors into a slot of every peer's receive buffer; the payload itself
+// tells the receiver when it has arrived: slots are pre-filled with a sentinel bit
+// pattern (the bf16 pair -0.0/-0.0 in every 32-bit word, which senders never emit: they
+// turn such a word into +0.0/+0.0), and the receiver polls its OWN memory until the
+// four words of a 16-byte vector differ from the sentinel.  One NVLink one-way trip is
+// the whole synchronisation cost.
+//
+// Receive buffer of a rank: [3 slots][world source ranks][slot_vecs vectors].  Call e
+// uses slot e % 3 and, at its very end, re-arms slot (e + 2) % 3 (the one call e - 1
+// used): a peer can only be writing into that slot again in call e + 2, which it
+// enters after receiving this rank's data of call e + 1, i.e. after this kernel (and
+// its re-arming stores) completed.  The epoch lives in device memory and is advanced by
+// the last block, so CUDA-graph replays need no host update.
+static constexpr uint32_t kLLSentinel = 0x80008000u;
+
+struct LLGroup {
+  uint4* recv[kMaxRanks];     // peer-mapped receive buffers (own at index rank)
+  uint32_t* epoch;            // this rank's [epoch, vectors written in slot 0, 1, 2] (device memory)
+  int world;
+  int rank;
+  long long slot_vecs;        // capacity of one (slot, source) region in 16-byte vectors
+};
+
+__device__ __forceinline__ uint4 ll_sanitize(uint4 v) {
+  if (v.x == kLLSentinel) v.x = 0u;
+  if (v.y == kLLSentinel) v.y = 0u;
+  if (v.z == kLLSentinel) v.z = 0u;
+  if (v.w == kLLSentinel) v.w = 0u;
+  return v;
+}
+
+__device__ __forceinline__ void ll_store(uint4* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ uint4 ll_load(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Poll until the vector has arrived (bounded).  Returns false on expiry.
+__device__ __forceinline__ bool ll_wait(const uint4* p, uint4& v) {
+  for (uint32_t i = 0; i < kMaxFlagPolls; ++i) {
+    v = ll_load(p);
+    if (v.x != kLLSentinel && v.y != kLLSentinel && v.z != kLLSentinel && v.w != kLLSentinel) return true;
+  }
+  return false;
+}
+
+// in/out [n_vec] vectors of 8 bf16; rows of row_vecs vectors when fused with
+// "residual += sum; out = RMSNorm(residual) * w".  One block per row (fused) or per
+// contiguous chunk; a thread owns up to 4 vectors of its block's range at a time.
+__global__ void __launch_bounds__(512)
+allreduce_ll_kernel(LLGroup g, const uint4* __restrict__ in, uint4* __restrict__ out, long long n_vec,
+                    uint4* __restrict__ residual, const uint4* __restrict__ norm_w, int row_vecs, float eps,
+                    uint32_t* done_counter, int* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(g.epoch) + 1;
+  const long long slot_stride = static_cast<long long>(g.world) * g.slot_vecs;
+  const long long slot_off = static_cast<long long>(epoch % 3) * slot_stride;
+  const long long rearm_off = static_cast<long long>((epoch + 2) % 3) * slot_stride;
+  const bool fused = norm_w != nullptr;
+  long long begin, end;
+  if (fused) {
+    const long long rows = n_vec / row_vecs;
+    const long long per = (rows + gridDim.x - 1) / gridDim.x;
+    begin = min(rows, per * blockIdx.x) * row_vecs;
+    end = min(rows, per * (blockIdx.x + 1)) * row_vecs;
+  } else {
+    const long long per = (n_vec + gridDim.x - 1) / gridDim.x;
+    begin = min(n_vec, per * blockIdx.x);
+    end = min(n_vec, per * (blockIdx.x + 1));
+  }
+  // 1) push my vectors into every rank's slot (my own included: uniform receive code)
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const uint4 v = ll_sanitize(in[i]);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < g.world) ll_store(g.recv[r] + slot_off + static_cast<long long>(g.rank) * g.slot_vecs + i, v);
+  }
+  // 2) receive + reduce (rank order, so every rank computes bit-identical sums)
+  const uint4* mine = g.recv[g.rank] + slot_off;
+  bool ok = true;
+  if (!fused) {
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < g.world) {
+          uint4 v;
+          ok = ll_wait(mine + static_cast<long long>(r) * g.slot_vecs + i, v) && ok;
+          add8(acc, v);
+        }
+      }
+      out[i] = pack8(acc);
+    }
+  } else {
+    __shared__ float red[32];
+    for (long long row0 = begin; row0 < end; row0 += row_vecs) {
+      float vals[4][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < row_vecs) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < g.world) {
+              uint4 x;
+              ok = ll_wait(mine + static_cast<long long>(r) * g.slot_vecs + row0 + v, x) && ok;
+              add8(acc, x);
+            }
+          }
+          Pack8 y;
+          y.u = pack8(acc);          // the sum is rounded to bf16 before the residual add
+          Pack8 rs;
+          rs.u = residual[row0 + v];
+          Pack8 nr;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            nr.h[j] = __float2bfloat16(__bfloat162float(y.h[j]) + __bfloat162float(rs.h[j]));
+            vals[k][j] = __bfloat162float(nr.h[j]);
+            ss += vals[k][j] * vals[k][j];
+          }
+          residual[row0 + v] = nr.u;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+      __syncthreads();
+      const float inv = rsqrtf(tot / static_cast<float>(row_vecs * 8) + eps);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < row_vecs) {
+          Pack8 w8, o8;
+          w8.u = norm_w[v];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o8.h[j] = __float2bfloat16(vals[k][j] * inv * __bfloat162float(w8.h[j]));
+          out[row0 + v] = o8.u;
+        }
+      }
+    }
+  }
+  if (!ok && status) atomicCAS(status, 0, 5);
+  // 3) re-arm the slot of the previous call for its next use (two calls from now).  How many
+  //    vectors that call wrote per source rank is recorded in device memory (epoch[1 + slot]),
+  //    so calls of different sizes and CUDA-graph replays in any order stay consistent.
+  {
+    const uint32_t prev_vecs = reinterpret_cast<volatile uint32_t*>(g.epoch)[1 + (epoch + 2) % 3];
+    const uint4 s4 = make_uint4(kLLSentinel, kLLSentinel, kLLSentinel, kLLSentinel);
+    uint4* rearm = g.recv[g.rank] + rearm_off;
+    const long long total = static_cast<long long>(prev_vecs) * g.world;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long r = idx / prev_vecs, i = idx % prev_vecs;
+      rearm[r * g.slot_vecs + i] = s4;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      volatile uint32_t* meta = reinterpret_cast<volatile uint32_t*>(g.epoch);
+      meta[1 + epoch % 3] = static_cast<uint32_t>(n_vec);
+      meta[0] = epoch;
+    }
+  }
+}
+
+__global__ void ll_fill_kernel(uint4* p, long long n) {
+  const uint4 s4 = make_uint4(kLLSentinel, kLLSentinel, kLLSentinel, kLLSentinel);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    p[i] = s4;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -497,5 +688,48 @@ extern "C" int b200_symm_reduce_scatter(void* const* data, void* const* signal, 
   reducescatter_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
       g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
       static_cast<uint32_t*>(done_counter), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+
+// ---- push ("LL") all-reduce: host side
+// Arms a receive buffer (3 * world * slot_vecs vectors) with the sentinel pattern.
+extern "C" int b200_symm_ll_arm(void* recv, long long total_vecs, cudaStream_t stream) {
+  ll_fill_kernel<<<256, 256, 0, stream>>>(static_cast<uint4*>(recv), total_vecs);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// recv: the group's peer-mapped receive buffers; epoch: four zero-initialised device words of
+// this rank (epoch and the per-slot fill counts).  The message (n_elems bf16, a multiple of 8) must fit one slot region: n_elems / 8 <=
+// slot_vecs.  Calls of different sizes may follow one another freely.
+extern "C" int b200_symm_all_reduce_ll(void* const* recv, int world, int rank, long long slot_vecs,
+                                       void* epoch, const void* in, void* out, long long n_elems,
+                                       void* residual, const void* norm_w, int row_elems, float eps,
+                                       void* done_counter, int* status, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks) return -1;
+  if ((n_elems & 7) != 0) return -2;
+  const long long n_vec = n_elems >> 3;
+  if (n_vec > slot_vecs) return -4;
+  const bool fused = norm_w != nullptr;
+  if (fused && ((row_elems & 7) != 0 || row_elems > 512 * 4 * 8 || n_elems % row_elems != 0)) return -3;
+  LLGroup g{};
+  for (int r = 0; r < kMaxRanks; ++r) g.recv[r] = r < world ? static_cast<uint4*>(recv[r]) : nullptr;
+  g.epoch = static_cast<uint32_t*>(epoch);
+  g.world = world;
+  g.rank = rank;
+  g.slot_vecs = slot_vecs;
+  int blocks;
+  if (fused) {
+    const long long rows = n_elems / row_elems;
+    blocks = static_cast<int>(rows < kMaxCommBlocks ? rows : kMaxCommBlocks);
+  } else {
+    blocks = static_cast<int>((n_vec + 511) / 512);
+    if (blocks > kMaxCommBlocks) blocks = kMaxCommBlocks;
+  }
+  if (blocks < 1) blocks = 1;
+  allreduce_ll_kernel<<<blocks, 512, 0, stream>>>(g, static_cast<const uint4*>(in), static_cast<uint4*>(out),
+                                                  n_vec, static_cast<uint4*>(residual),
+                                                  static_cast<const uint4*>(norm_w), row_elems >> 3, eps,
+                                                  static_cast<uint32_t*>(done_counter), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -89,6 +89,21 @@ class _RemoteView:
         return self.dtype.itemsize
 
 
+def _raw_ipc_handle(blob: bytes) -> bytes:
+    """The 64-byte cudaIpcMemHandle_t inside torch's shareable handle.  Newer torch versions
+    prefix it with a format version and a type tag ('c' = plain cudaMalloc allocation,
+    'e' = expandable segment, which cannot be opened with cudaIpcOpenMemHandle)."""
+    if len(blob) == 64:
+        return blob
+    if len(blob) > 64:
+        tag = blob[len(blob) - 65: len(blob) - 64]
+        if tag == b"e":
+            raise ConnectionError("the producer's KV cache lives in an expandable allocator segment; "
+                                  "disable expandable_segments for the KV cache to share it")
+        return blob[-64:]
+    raise ConnectionError(f"unexpected IPC handle of {len(blob)} bytes")
+
+
 def _open_ipc_exports(ipc, shapes, dtype: torch.dtype):
     """Map a producer's cache tensors on THIS rank's current device.  The handles come from
     torch's storage sharing (handle of the allocation + byte offset of the storage in it); they
@@ -105,7 +120,7 @@ def _open_ipc_exports(ipc, shapes, dtype: torch.dtype):
     views: List[_RemoteView] = []
     try:
         for (info, offset_elems, stride), shape in zip(ipc, shapes):
-            handle, storage_off = bytes(info[1]), int(info[3])
+            handle, storage_off = _raw_ipc_handle(bytes(info[1])), int(info[3])
             want = tuple(int(x) for x in stride)
             dense = tuple(torch.empty(shape, device="meta").stride())
             if want != dense:

@@ -335,18 +335,27 @@ def mla_kv_rmsnorm_rope_cache(kv_c: torch.Tensor, k_pe: torch.Tensor, w: torch.T
 
 
 # ------------------------------------------------------------------- attention
+def _pack_window(window: int, sink: int) -> int:
+    """The kernels take the sliding window in the low 20 bits of one integer and the
+    number of leading sink tokens above them."""
+    if window >= (1 << 20) or sink >= (1 << 11) or window < 0 or sink < 0:
+        raise ValueError(f"window {window} / sink {sink} out of range")
+    return window | (sink << 20)
+
+
 def gqa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                 num_seqs: int, max_q_len: int, num_q_heads: int, scale: float, causal: bool = True,
-                window: int = 0, return_lse: bool = False):
+                window: int = 0, return_lse: bool = False, sink: int = 0):
     """Variable-length attention of this step's queries over the paged cache
-    (which already holds this step's keys/values)."""
+    (which already holds this step's keys/values).  ``sink``: the first ``sink`` cached
+    tokens of every sequence are attention sinks, visible through any sliding window."""
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu_q[: num_seqs + 1],
-                                   seq_lens[:num_seqs], num_q_heads, scale, causal, window, return_lse)
+                                   seq_lens[:num_seqs], num_q_heads, scale, causal, window, return_lse, sink)
     _count(1)
     out, lse = _C().gqa_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, num_seqs,
-                                max_q_len, num_q_heads, scale, causal, window, return_lse)
+                                max_q_len, num_q_heads, scale, causal, _pack_window(window, sink), return_lse)
     return (out, lse) if return_lse else out
 
 
@@ -361,13 +370,13 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_seq_len: int, sms: int =
 def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                block_tables: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, num_q_heads: int,
                scale: float, q_len: int = 1, window: int = 0, splits: int = 0,
-               max_seq_len: int = 0) -> torch.Tensor:
+               max_seq_len: int = 0, sink: int = 0) -> torch.Tensor:
     """Decode attention: q_len (usually 1) new tokens per sequence, sequences laid
     out back to back in q."""
     if not q.is_cuda:
         cu = torch.arange(0, (num_seqs + 1) * q_len, q_len, dtype=torch.int32, device=q.device)
         return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu,
-                                   seq_lens[:num_seqs], num_q_heads, scale, True, window)
+                                   seq_lens[:num_seqs], num_q_heads, scale, True, window, False, sink)
     C = _C()
     hk, d = k_cache.shape[1], k_cache.shape[3]
     if splits <= 0:
@@ -380,7 +389,7 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
     _count(2 if splits > 1 else 1)
     return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
-                        scale, window, splits, scratch, st.status)
+                        scale, _pack_window(window, sink), splits, scratch, st.status)
 
 
 merge_attn_states = ref.merge_attn_states

@@ -183,9 +183,10 @@ def _gather_kv(cache: torch.Tensor, block_table: torch.Tensor, n: int) -> torch.
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_tables: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                     num_q_heads: int, scale: float, causal: bool = True, window: int = 0,
-                    return_lse: bool = False):
+                    return_lse: bool = False, sink: int = 0):
     """Variable-length attention over the paged cache.  q [T, Hq*Dqk]; the queries of
-    sequence b are rows cu_q[b]:cu_q[b+1] and sit at the END of its seq_lens[b] cached tokens."""
+    sequence b are rows cu_q[b]:cu_q[b+1] and sit at the END of its seq_lens[b] cached tokens.
+    ``sink`` leading keys stay visible to every query whatever the sliding window."""
     hk, dqk, dv = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
     hq = num_q_heads
     g = hq // hk
@@ -209,7 +210,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if causal:
             mask &= pos_k <= pos_q
         if window > 0:
-            mask &= pos_k > pos_q - window
+            mask &= (pos_k > pos_q - window) | (pos_k < sink)
         s = s.masked_fill(~mask, float("-inf"))
         l = torch.logsumexp(s, dim=-1)
         p = torch.exp(s - l.unsqueeze(-1))

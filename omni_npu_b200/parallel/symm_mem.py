@@ -51,12 +51,18 @@ def _lib() -> ctypes.CDLL:
         lib.b200_symm_all_gather.restype = ci
         lib.b200_symm_reduce_scatter.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, vp]
         lib.b200_symm_reduce_scatter.restype = ci
+        lib.b200_symm_ll_arm.argtypes = [vp, ll, vp]
+        lib.b200_symm_ll_arm.restype = ci
+        lib.b200_symm_all_reduce_ll.argtypes = [pp, ci, ci, ll, vp, vp, vp, ll, vp, vp, ci, ctypes.c_float, vp, vp, vp]
+        lib.b200_symm_all_reduce_ll.restype = ci
         _LIB = lib
     return _LIB
 
 
 class SymmetricMemory:
     ONE_SHOT_FUSED_MAX_BYTES = 2 << 20      # above this the fused one-shot tail is not worth it
+
+    LL_SLOT_BYTES = 2 << 20                 # largest message of the push ("LL") all-reduce
 
     def __init__(self, group, device: torch.device, half_bytes: int = 80 << 20) -> None:
         self.group = group
@@ -81,15 +87,20 @@ class SymmetricMemory:
 
         data_ptr, data_h = alloc(2 * self.half_bytes)
         sig_ptr, sig_h = alloc(lib.b200_symm_signal_words() * 4)
-        everyone = group.all_gather_object((data_h, sig_h))
+        # receive buffer of the push all-reduce: [3 slots][world sources][LL_SLOT_BYTES]
+        self.ll_slot_vecs = self.LL_SLOT_BYTES // 16
+        ll_total_vecs = 3 * self.world * self.ll_slot_vecs
+        ll_ptr, ll_h = alloc(ll_total_vecs * 16)
+        everyone = group.all_gather_object((data_h, sig_h, ll_h))
         vp = ctypes.c_void_p
         self.data_ptrs = (vp * 8)()
         self.signal_ptrs = (vp * 8)()
-        for r, (dh, sh) in enumerate(everyone):
+        self.ll_ptrs = (vp * 8)()
+        for r, (dh, sh, lh) in enumerate(everyone):
             if r == self.rank:
-                self.data_ptrs[r], self.signal_ptrs[r] = data_ptr.value, sig_ptr.value
+                self.data_ptrs[r], self.signal_ptrs[r], self.ll_ptrs[r] = data_ptr.value, sig_ptr.value, ll_ptr.value
                 continue
-            for handle, table in ((dh, self.data_ptrs), (sh, self.signal_ptrs)):
+            for handle, table in ((dh, self.data_ptrs), (sh, self.signal_ptrs), (lh, self.ll_ptrs)):
                 p = vp()
                 rc = lib.b200_symm_open(handle, ctypes.byref(p))
                 if rc != 0:
@@ -98,7 +109,12 @@ class SymmetricMemory:
                 table[r] = p.value
                 self._opened.append(p)
         self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ll_meta = torch.zeros(4, dtype=torch.int32, device=device)      # epoch + per-slot fill counts
+        self.ll_done = torch.zeros(4, dtype=torch.int32, device=device)
+        self.use_ll = os.environ.get("OMNI_B200_SYMM_LL", "1") != "0"
         self.status = ops.device_state(device).status
+        if lib.b200_symm_ll_arm(ll_ptr, ll_total_vecs, self._stream()) != 0:
+            raise RuntimeError("arming the push all-reduce buffer failed")
         torch.cuda.synchronize(device)
         group.barrier()
         logger.info("symmetric memory ready: rank %d/%d, %d MiB per rank", self.rank, self.world,
@@ -116,9 +132,23 @@ class SymmetricMemory:
         return self._ok(x) and x.numel() * 2 * (1 + 1.0 / self.world) + 64 <= self.half_bytes
 
     # --------------------------------------------------------------- collectives
+    def _ll(self, x: torch.Tensor, out: torch.Tensor, residual, weight, h: int, eps: float) -> None:
+        rc = _lib().b200_symm_all_reduce_ll(self.ll_ptrs, self.world, self.rank, self.ll_slot_vecs,
+                                            self.ll_meta.data_ptr(), x.data_ptr(), out.data_ptr(), x.numel(),
+                                            residual.data_ptr() if residual is not None else None,
+                                            weight.data_ptr() if weight is not None else None, h, eps,
+                                            self.ll_done.data_ptr(), self.status.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"symm push all_reduce failed ({rc})")
+        ops._count(1)
+
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = 0) -> torch.Tensor:
-        """Sum over the group.  Returns a new tensor (``out`` if given)."""
+        """Sum over the group.  Returns a new tensor (``out`` if given).  ``mode``: 0 auto,
+        1 one shot (pull), 2 two shot, 3 push (data-carried flags, no barrier)."""
         out = torch.empty_like(x) if out is None else out
+        if mode == 3 or (mode == 0 and self.use_ll and x.numel() * 2 <= self.LL_SLOT_BYTES):
+            self._ll(x, out, None, None, 0, 0.0)
+            return out
         rc = _lib().b200_symm_all_reduce(self.data_ptrs, self.signal_ptrs, self.world, self.rank,
                                          self.half_bytes, x.data_ptr(), out.data_ptr(), x.numel(), None,
                                          None, 0, 0.0, mode, self.done.data_ptr(),
@@ -133,6 +163,11 @@ class SymmetricMemory:
         """residual += all_reduce(x) (in place); returns RMSNorm(residual) * weight.
         Small messages run as ONE kernel; large ones as two-shot reduce + add/norm."""
         h = x.shape[-1]
+        if (self.use_ll and x.numel() * 2 <= self.LL_SLOT_BYTES and h <= 16384 and residual.is_contiguous()
+                and weight.is_contiguous()):
+            out = torch.empty_like(x)
+            self._ll(x, out, residual, weight, h, eps)
+            return out
         if (x.numel() * 2 <= self.ONE_SHOT_FUSED_MAX_BYTES and h <= 16384 and residual.is_contiguous()
                 and weight.is_contiguous()):
             out = torch.empty_like(x)

@@ -100,7 +100,9 @@ def task_symm(rank, world, port, workdir, device_kind):
     symm = attach_symmetric_memory(g, dev, half_bytes=96 << 20)
     res = {"max_err": {}}
     torch.manual_seed(100 + rank)
-    for name, shape, mode in (("small_1shot", (128, 4096), 1), ("small_2shot", (128, 4096), 2),
+    for name, shape, mode in (("push_tiny", (1, 4096), 3), ("push", (128, 4096), 3), ("push_odd", (7, 1032), 3),
+                              ("push_small_after_big", (3, 512), 3), ("push_again", (128, 4096), 3),
+                              ("small_1shot", (128, 4096), 1), ("small_2shot", (128, 4096), 2),
                               ("odd", (7, 1032), 0), ("large_auto", (4096, 4096), 0),
                               ("large_1shot", (2048, 4096), 1)):
         x = torch.randn(*shape, device=dev, dtype=torch.bfloat16)
@@ -122,6 +124,13 @@ def task_symm(rank, world, port, workdir, device_kind):
     r_got = resid.clone()
     y_got = symm.all_reduce_add_rms_norm(x, r_got, w, 1e-6)
     res["max_err"]["fused_norm_out"] = (y_got.float() - y_ref.float()).abs().max().item()
+    # the same through the barrier-based (pull) kernel
+    symm.use_ll = False
+    r_pull = resid.clone()
+    y_pull = symm.all_reduce_add_rms_norm(x, r_pull, w, 1e-6)
+    symm.use_ll = True
+    res["max_err"]["fused_norm_out_pull"] = (y_pull.float() - y_ref.float()).abs().max().item()
+    res["max_err"]["fused_norm_res_pull"] = (r_pull.float() - r_ref.float()).abs().max().item()
     res["max_err"]["fused_norm_res"] = (r_got.float() - r_ref.float()).abs().max().item()
     # all-gather / reduce-scatter
     x = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
@@ -147,6 +156,35 @@ def task_symm(rank, world, port, workdir, device_kind):
         return e0.elapsed_time(e1) / n * 1e3
     res["us_symm_1MiB"] = timeit(lambda: symm.all_reduce(x))
     res["us_nccl_1MiB"] = timeit(lambda: dist.all_reduce(x, group=g.device_group))
+    # the same inside a CUDA graph (no launch gaps): plain and fused with residual + RMSNorm
+    def graph_time(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(reps):
+                fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * reps) * 1e3
+    wn = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+    for rows in (1, 16, 128):
+        xs = torch.randn(rows, 4096, device=dev, dtype=torch.bfloat16)
+        rr = torch.zeros(rows, 4096, device=dev, dtype=torch.bfloat16)
+        res[f"us_graph_symm_{rows}"] = graph_time(lambda: symm.all_reduce(xs, mode=1))
+        res[f"us_graph_push_{rows}"] = graph_time(lambda: symm.all_reduce(xs, mode=3))
+        res[f"us_graph_fused_{rows}"] = graph_time(lambda: symm.all_reduce_add_rms_norm(xs, rr, wn, 1e-6))
+        res[f"us_graph_local_norm_{rows}"] = graph_time(lambda: ops.fused_add_rms_norm(xs, rr, wn, 1e-6))
     big = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
     res["us_symm_64MiB"] = timeit(lambda: symm.all_reduce(big), 10)
     res["us_nccl_64MiB"] = timeit(lambda: dist.all_reduce(big, group=g.device_group), 10)

@@ -302,6 +302,29 @@ def test_gqa_decode_multi_token():
     _close(got, want, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("window,sink", [(64, 32), (16, 16), (200, 48)])
+def test_gqa_window_with_sink_tokens(window, sink):
+    """Sliding-window attention where the first `sink` cached tokens stay visible."""
+    seq_lens, q_lens = [300, 77, 40], [300, 40, 1]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, q_lens, 8, 2, 128, 16, seed=12)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.1, True, window, False, sink)
+    got = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV), 3, 300,
+                          8, 0.1, True, window, sink=sink)
+    _close(got, want, 2e-2, 2e-2)
+    # without the sink the result differs (the mask matters) ...
+    nosink = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV), 3, 300,
+                             8, 0.1, True, window)
+    assert (nosink.float().cpu() - want.float()).abs().max() > 1e-2
+    # ... and decode agrees too
+    seq_lens = [1, 17, 64, 65, 1000, 333]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 6, 8, 2, 128, 16, seed=13)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.1, True, window, False, sink)
+    for splits in (1, 3):
+        got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 6, 8, 0.1,
+                             window=window, splits=splits, sink=sink)
+        _close(got, want, 2e-2, 2e-2)
+
+
 def test_rope_cache_gqa_and_cache_write():
     t, hq, hk, d, bs = 29, 8, 2, 128, 16
     qkv = torch.randn(t, (hq + 2 * hk) * d, device=DEV, dtype=torch.bfloat16)

@@ -19,6 +19,7 @@ def test_symmetric_memory_collectives_match_nccl():
         for name, err in r["max_err"].items():
             tol = 0.13 if name.startswith(("small", "odd", "large")) else 0.07
             assert err <= tol, (name, err)
+    print("graph-timed all-reduce us:", {k: round(v, 1) for k, v in res[0].items() if k.startswith("us_graph")})
     print("all-reduce us (symm vs nccl):", res[0]["us_symm_1MiB"], res[0]["us_nccl_1MiB"],
           res[0]["us_symm_64MiB"], res[0]["us_nccl_64MiB"])
 
