@@ -1,0 +1,86 @@
+"""Small components: group-scoped comm helpers, graph-mode config / decorators, tracing."""
+import pytest
+import torch
+
+from omni_npu_b200.attention.metadata import AttentionMetadata, set_forward_context
+from omni_npu_b200.compilation.config import B200CompilationConfig
+from omni_npu_b200.compilation.decorators import step_is_capturable, support_graph_replay
+from omni_npu_b200.parallel import comm_ops, state
+from omni_npu_b200.utils import trace
+
+
+def test_comm_ops_are_identity_on_one_rank():
+    state.ensure_initialized(torch.device("cpu"))
+    x = torch.arange(12.0).view(4, 3)
+    for fn in (comm_ops.all_reduce, comm_ops.all_reduce_two_stage):
+        assert fn(x) is x
+    assert comm_ops.all_gather(x, 0) is x and comm_ops.reduce_scatter(x, 0) is x
+    assert comm_ops.all_gather_pipeline(x) is x and comm_ops.all_gather_local(x) is x
+    assert comm_ops.all_to_all(x) is x and comm_ops.sequence_parallel_chunk(x) is x
+    assert comm_ops.get_world_size() == 1 and comm_ops.get_rank("mlp.down_proj") == 0
+
+
+def test_compilation_config_gears():
+    cfg = B200CompilationConfig.from_additional_config({"decode_gear_list": [8, 2, 32]}, max_num_seqs=48)
+    assert cfg.decode_gear_list == [2, 8, 32, 48]            # the largest gear covers a full batch
+    gears = cfg.gears(48)
+    assert cfg.pad_to_gear(1, gears) == 2 and cfg.pad_to_gear(9, gears) == 32 and cfg.pad_to_gear(49, gears) is None
+    auto = B200CompilationConfig().gears(128)
+    assert auto[:5] == [1, 2, 4, 8, 16] and auto[-1] == 128
+    assert B200CompilationConfig(cudagraph_mode="NONE").gears(128) == []
+    with pytest.raises(ValueError):
+        B200CompilationConfig.from_additional_config({"cudagraph_mode": "PIECEWISE"})
+    with pytest.raises(ValueError):
+        B200CompilationConfig.from_additional_config({"decode_gear_list": list(range(1, 80))})
+
+
+def _md(prefill):
+    z = torch.zeros(1, dtype=torch.int32)
+    return AttentionMetadata(prefill, 1, 1, 1, 1, 1, z, z, z.view(1, 1), z, torch.zeros(2, dtype=torch.int32), 1, 1)
+
+
+def test_prefill_bypasses_the_graph_path():
+    calls = []
+
+    @support_graph_replay
+    class M:
+        device = torch.device("cpu")
+        cudagraph_mode = "NONE"
+
+        def forward(self, x):
+            calls.append("forward")
+            return x + 1
+
+        def __call__(self, x):
+            calls.append("call")
+            return self.forward(x)
+
+    m = M()
+    assert M._graph_bypass_installed
+    with set_forward_context(_md(True), []):
+        assert m(torch.ones(1)).item() == 2
+    with set_forward_context(_md(False), []):
+        assert m(torch.ones(1)).item() == 2                  # mode NONE: eager as well
+    assert calls == ["forward", "forward"]
+    assert not step_is_capturable(_md(True), "FULL_DECODE_ONLY") and step_is_capturable(_md(False), "FULL_DECODE_ONLY")
+
+
+def test_trace_timers_and_request_lines():
+    trace.enable(True)
+    try:
+        @trace.timer("unit.work")
+        def work(n):
+            return sum(range(n))
+
+        work(10), work(20)
+        rep = trace.timer_report(reset=True)
+        assert rep["unit.work"]["calls"] == 2 and rep["unit.work"]["total_s"] >= 0
+        lines = []
+        t = trace.RequestTracer(role="prefill", sink=lines.append)
+        line = t.trace("first_token", "req-1", ttft_ms=12.5)
+        assert lines == [line] and "event=first_token" in line and "role=prefill" in line and "ttft_ms=12.5" in line
+        with trace.nvtx_range("block"):
+            pass
+    finally:
+        trace.enable(False)
+    assert trace.RequestTracer(sink=lambda l: (_ for _ in ()).throw(AssertionError)).trace("x", "r")
