@@ -1,0 +1,285 @@
+"""OpenAI-compatible HTTP front end of the standalone engine.
+
+    python -m omni_npu_b200.serving.api_server --model llama-3-8b --port 8000 \
+        --max-num-seqs 128 --tensor-parallel-size 1 [--kv-transfer-config '{...}'] \
+        [--reasoning-parser pangu] [--tool-call-parser pangu] [--reasoning-config '{...}']
+
+Endpoints: ``POST /v1/completions`` (token ids or text when a tokenizer directory is
+given), ``POST /v1/chat/completions``, ``GET /v1/models``, ``GET /health``,
+``GET /metrics`` (Prometheus text).  One engine thread runs ``LLMEngine.step`` in a loop;
+request handlers enqueue requests and wait for their outputs (streaming sends one
+server-sent event per engine step that produced tokens for the request).
+
+The reference serves through ``vllm serve`` with its platform plugin
+(examples/serve-single-instance.sh:100-187); this module is the same surface for the
+standalone engine, including the request field ``thinking_token_budget``
+(omni_npu/vllm_patches/patches/common/patch_think_limit.py) and ``kv_transfer_params`` for
+prefill/decode disaggregation.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import threading
+import time
+import uuid
+from typing import Any, Dict, List, Optional
+
+from ..engine.request import SamplingParams
+from ..logger import logger
+
+
+class EngineLoop:
+    """Owns the engine; a background thread steps it while there is work."""
+
+    def __init__(self, llm) -> None:
+        self.llm = llm
+        self.engine = llm.engine
+        self.lock = threading.Lock()
+        self.wake = threading.Event()
+        self.waiters: Dict[str, Dict[str, Any]] = {}
+        self.running = True
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        self.counters = {"requests": 0, "finished": 0, "output_tokens": 0, "steps": 0}
+
+    def submit(self, prompt_ids: List[int], sp: SamplingParams, kv_transfer_params=None) -> str:
+        rid = f"cmpl-{uuid.uuid4().hex}"
+        slot = {"event": threading.Event(), "output": None, "seen": 0, "queue": [], "request": None}
+        with self.lock:
+            self.waiters[rid] = slot
+            self.engine.add_request(prompt_ids, sp, request_id=rid, kv_transfer_params=kv_transfer_params)
+            slot["request"] = self.engine.scheduler.requests[rid]
+            self.counters["requests"] += 1
+        self.wake.set()
+        return rid
+
+    def abort(self, rid: str) -> None:
+        with self.lock:
+            self.engine.abort_request(rid)
+            self.waiters.pop(rid, None)
+
+    def _run(self) -> None:
+        while self.running:
+            if not self.engine.has_unfinished_requests():
+                self.wake.wait(0.05)
+                self.wake.clear()
+                continue
+            with self.lock:
+                outs = self.engine.step()
+                self.counters["steps"] += 1
+                # streaming: hand over tokens produced since the last look
+                for rid, slot in self.waiters.items():
+                    req = slot["request"]
+                    if req is not None and len(req.output_token_ids) > slot["seen"]:
+                        slot["queue"].extend(req.output_token_ids[slot["seen"]:])
+                        slot["seen"] = len(req.output_token_ids)
+                for o in outs:
+                    slot = self.waiters.get(o.request_id)
+                    if slot is not None:
+                        slot["output"] = o
+                        slot["event"].set()
+                    self.counters["finished"] += 1
+                    self.counters["output_tokens"] += len(o.output_token_ids)
+
+    def wait(self, rid: str, timeout: Optional[float] = None):
+        slot = self.waiters[rid]
+        slot["event"].wait(timeout)
+        out = slot["output"]
+        if out is not None:
+            self.waiters.pop(rid, None)
+        return out
+
+    def shutdown(self) -> None:
+        self.running = False
+        self.wake.set()
+        self.thread.join(timeout=5)
+
+
+def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
+    stop_ids = body.get("stop_token_ids") or ()
+    return SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+                          temperature=float(body.get("temperature", 1.0 if body.get("top_p") else 0.0) or 0.0),
+                          top_k=int(body.get("top_k") or 0), top_p=float(body.get("top_p") or 1.0),
+                          seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
+                          stop_token_ids=tuple(stop_ids),
+                          presence_penalty=float(body.get("presence_penalty") or 0.0),
+                          frequency_penalty=float(body.get("frequency_penalty") or 0.0),
+                          repetition_penalty=float(body.get("repetition_penalty") or 1.0),
+                          thinking_token_budget=body.get("thinking_token_budget"))
+
+
+def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    app = FastAPI()
+    loop = EngineLoop(llm)
+    app.state.engine_loop = loop
+
+    def encode(prompt) -> List[int]:
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return prompt
+        if tokenizer is None:
+            raise HTTPException(400, "this server has no tokenizer: send 'prompt' as a list of token ids")
+        return tokenizer.encode(prompt)
+
+    def decode(ids: List[int]) -> str:
+        return tokenizer.decode(ids) if tokenizer is not None else ""
+
+    @app.get("/health")
+    def health():
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    @app.get("/metrics")
+    def metrics():
+        c, e = loop.counters, llm.engine.stats
+        lines = [f"omni_b200_requests_total {c['requests']}", f"omni_b200_requests_finished_total {c['finished']}",
+                 f"omni_b200_output_tokens_total {c['output_tokens']}", f"omni_b200_engine_steps_total {e['steps']}",
+                 f"omni_b200_running_requests {len(llm.engine.scheduler.running)}",
+                 f"omni_b200_waiting_requests {len(llm.engine.scheduler.waiting)}"]
+        return PlainTextResponse("\n".join(lines) + "\n")
+
+    async def _finish(rid: str):
+        while True:
+            out = await asyncio.to_thread(loop.wait, rid, 0.5)
+            if out is not None:
+                return out
+
+    async def _stream(rid: str, make_chunk):
+        slot = loop.waiters[rid]
+        while True:
+            await asyncio.sleep(0.005)
+            with loop.lock:
+                toks, slot["queue"] = slot["queue"], []
+            if toks:
+                yield "data: " + json.dumps(make_chunk(toks, None)) + "\n\n"
+            if slot["event"].is_set():
+                out = loop.wait(rid, 0)
+                with loop.lock:
+                    rest = slot["queue"]
+                if rest:
+                    yield "data: " + json.dumps(make_chunk(rest, None)) + "\n\n"
+                yield "data: " + json.dumps(make_chunk([], out.finish_reason or "stop")) + "\n\n"
+                yield "data: [DONE]\n\n"
+                return
+
+    @app.post("/v1/completions")
+    async def completions(body: Dict[str, Any]):
+        ids = encode(body.get("prompt"))
+        rid = loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+        created = int(time.time())
+        if body.get("stream"):
+            def chunk(toks, finish):
+                return {"id": rid, "object": "text_completion", "created": created, "model": model_name,
+                        "choices": [{"index": 0, "text": decode(toks), "token_ids": toks, "finish_reason": finish}]}
+            return StreamingResponse(_stream(rid, chunk), media_type="text/event-stream")
+        out = await _finish(rid)
+        return JSONResponse({
+            "id": rid, "object": "text_completion", "created": created, "model": model_name,
+            "choices": [{"index": 0, "text": decode(out.output_token_ids), "token_ids": out.output_token_ids,
+                         "finish_reason": out.finish_reason or "stop"}],
+            "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
+                      "total_tokens": len(ids) + len(out.output_token_ids)},
+            "kv_transfer_params": out.kv_transfer_params})
+
+    @app.post("/v1/chat/completions")
+    async def chat(body: Dict[str, Any]):
+        msgs = body.get("messages") or []
+        if tokenizer is not None and hasattr(tokenizer, "apply_chat_template"):
+            ids = tokenizer.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True)
+        elif msgs and isinstance(msgs[-1].get("content"), list) and all(isinstance(t, int) for t in msgs[-1]["content"]):
+            ids = msgs[-1]["content"]                      # token ids in the last message (no tokenizer)
+        else:
+            raise HTTPException(400, "chat needs a tokenizer with a chat template")
+        rid = loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+        out = await _finish(rid)
+        text = decode(out.output_token_ids)
+        message: Dict[str, Any] = {"role": "assistant", "content": text}
+        if reasoning_parser is not None:
+            reasoning, content = reasoning_parser.extract_reasoning(text)
+            message["reasoning_content"], message["content"] = reasoning, content
+        if tool_parser is not None and body.get("tools"):
+            info = tool_parser.extract_tool_calls(message["content"] or "")
+            if getattr(info, "tools_called", False):
+                import dataclasses
+                message["tool_calls"] = [dataclasses.asdict(tc) if dataclasses.is_dataclass(tc) else tc
+                                         for tc in info.tool_calls]
+                message["content"] = info.content
+        return JSONResponse({
+            "id": rid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
+            "choices": [{"index": 0, "message": message, "finish_reason": out.finish_reason or "stop"}],
+            "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
+                      "total_tokens": len(ids) + len(out.output_token_ids)}})
+
+    return app
+
+
+def make_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser("omni_npu_b200.serving.api_server")
+    ap.add_argument("--model", default="llama-3-8b", help="preset name or HF directory")
+    ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--tokenizer", default=None, help="HF tokenizer directory (default: the model directory)")
+    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--data-parallel-size", type=int, default=1)
+    ap.add_argument("--enable-expert-parallel", action="store_true")
+    ap.add_argument("--max-num-seqs", type=int, default=128)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--max-model-len", type=int, default=8192)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
+    ap.add_argument("--compilation-config", type=json.loads, default=None)
+    ap.add_argument("--kv-transfer-config", type=json.loads, default=None)
+    ap.add_argument("--speculative-config", type=json.loads, default=None)
+    ap.add_argument("--additional-config", type=json.loads, default=None)
+    ap.add_argument("--reasoning-parser", default=None)
+    ap.add_argument("--tool-call-parser", default=None)
+    ap.add_argument("--reasoning-config", type=json.loads, default=None)
+    ap.add_argument("--enable-kv-rmsnorm-rope-cache", action="store_true", default=True)
+    ap.add_argument("--load-format", default="auto")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap
+
+
+def main(argv=None) -> None:
+    import os
+
+    import uvicorn
+
+    from ..engine.llm import LLM
+    from .parsers import get_reasoning_parser, get_tool_parser
+    args = make_parser().parse_args(argv)
+    kw = dict(tensor_parallel_size=args.tensor_parallel_size, data_parallel_size=args.data_parallel_size,
+              enable_expert_parallel=args.enable_expert_parallel, max_num_seqs=args.max_num_seqs,
+              max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
+              block_size=args.block_size, gpu_memory_utilization=args.gpu_memory_utilization,
+              enforce_eager=args.enforce_eager, enable_chunked_prefill=args.enable_chunked_prefill,
+              compilation_config=args.compilation_config, kv_transfer_config=args.kv_transfer_config,
+              speculative_config=args.speculative_config, additional_config=args.additional_config,
+              load_format=args.load_format, seed=args.seed)
+    llm = LLM(model=args.model, **kw)
+    tokenizer = None
+    tok_dir = args.tokenizer or (args.model if os.path.isdir(args.model) else None)
+    if tok_dir:
+        try:
+            from transformers import AutoTokenizer
+            tokenizer = AutoTokenizer.from_pretrained(tok_dir)
+        except Exception as e:
+            logger.warning("no tokenizer loaded from %s (%s): token-id requests only", tok_dir, e)
+    rp = get_reasoning_parser(args.reasoning_parser)(tokenizer) if args.reasoning_parser and tokenizer else None
+    tp = get_tool_parser(args.tool_call_parser)(tokenizer) if args.tool_call_parser and tokenizer else None
+    app = build_app(llm, tokenizer, args.served_model_name or os.path.basename(str(args.model)), rp, tp)
+    uvicorn.run(app, host=args.host, port=args.port, log_level="info")
+
+
+if __name__ == "__main__":
+    main()

@@ -11,6 +11,24 @@ from .pangu_tool_parser import PanguToolParser  # noqa: F401
 
 PARSER_NAME = "pangu"
 
+_REASONING = {PARSER_NAME: PanguReasoningParser}
+_TOOLS = {PARSER_NAME: PanguToolParser}
+
+
+def get_reasoning_parser(name: str):
+    """Parser class for ``--reasoning-parser <name>`` of this package's own server."""
+    try:
+        return _REASONING[name]
+    except KeyError:
+        raise ValueError(f"unknown reasoning parser {name!r}; known: {sorted(_REASONING)}") from None
+
+
+def get_tool_parser(name: str):
+    try:
+        return _TOOLS[name]
+    except KeyError:
+        raise ValueError(f"unknown tool-call parser {name!r}; known: {sorted(_TOOLS)}") from None
+
 
 def register_lazy_parsers() -> bool:
     from ... import compat
