@@ -29,11 +29,11 @@
 #include <stdint.h>
 #include <string.h>
 
+#include "ll_protocol.cuh"
+
 namespace b200 {
 
-static constexpr int kMaxRanks = 8;
 static constexpr int kMaxCommBlocks = 144;
-static constexpr uint32_t kMaxFlagPolls = 1u << 24;   // ~ a second of polling
 
 struct SymmGroup {
   void* data[kMaxRanks];        // peer-mapped data buffers (this rank's own at index rank)
@@ -78,25 +78,6 @@ __device__ __forceinline__ bool block_barrier(const SymmGroup& g, uint32_t epoch
     if (!ok && status) atomicCAS(status, 0, 5);
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
-}
-
-union Pack8 {
-  uint4 u;
-  __nv_bfloat16 h[8];
-};
-
-__device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
-  Pack8 p;
-  p.u = v;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(p.h[i]);
-}
-
-__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
-  Pack8 p;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) p.h[i] = __float2bfloat16(acc[i]);
-  return p.u;
 }
 
 // Each call advances the epoch by `steps` barriers.  The value is read by every
@@ -399,48 +380,6 @@ reducescatter_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restric
 // enters after receiving this rank's data of call e + 1, i.e. after this kernel (and
 // its re-arming stores) completed.  The epoch lives in device memory and is advanced by
 // the last block, so CUDA-graph replays need no host update.
-static constexpr uint32_t kLLSentinel = 0x80008000u;
-
-struct LLGroup {
-  uint4* recv[kMaxRanks];     // peer-mapped receive buffers (own at index rank)
-  uint32_t* epoch;            // this rank's [epoch, vectors written in slot 0, 1, 2] (device memory)
-  int world;
-  int rank;
-  long long slot_vecs;        // capacity of one (slot, source) region in 16-byte vectors
-};
-
-__device__ __forceinline__ uint4 ll_sanitize(uint4 v) {
-  if (v.x == kLLSentinel) v.x = 0u;
-  if (v.y == kLLSentinel) v.y = 0u;
-  if (v.z == kLLSentinel) v.z = 0u;
-  if (v.w == kLLSentinel) v.w = 0u;
-  return v;
-}
-
-__device__ __forceinline__ void ll_store(uint4* p, const uint4& v) {
-  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-
-__device__ __forceinline__ uint4 ll_load(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
-// Poll until the vector has arrived (bounded).  Returns false on expiry.
-__device__ __forceinline__ bool ll_wait(const uint4* p, uint4& v) {
-  for (uint32_t i = 0; i < kMaxFlagPolls; ++i) {
-    v = ll_load(p);
-    if (v.x != kLLSentinel && v.y != kLLSentinel && v.z != kLLSentinel && v.w != kLLSentinel) return true;
-  }
-  return false;
-}
-
 // in/out [n_vec] vectors of 8 bf16; rows of row_vecs vectors when fused with
 // "residual += sum; out = RMSNorm(residual) * w".  One block per row (fused) or per
 // contiguous chunk; a thread owns up to 4 vectors of its block's range at a time.

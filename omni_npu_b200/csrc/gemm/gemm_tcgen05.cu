@@ -28,6 +28,7 @@
 
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "../comm/ll_protocol.cuh"
 
 namespace b200 {
 
@@ -62,6 +63,15 @@ struct GemmParams {
   const float* a_scales;           // quantised inputs: [M] per-row scales or null (direct epilogue only)
   const float* w_scales;           // quantised inputs: [N] per-column scales (with a_scales)
   int* status;                     // error word (0 = ok)
+  // ---- fused tensor-parallel tail (ar_world > 1): the epilogue pushes the bf16 tile to every
+  // rank's receive buffer (ll_protocol.cuh) instead of writing C; once a CTA has finished its
+  // tiles it reduces whole rows that have arrived from all ranks, adds the residual and applies
+  // RMSNorm.  C then receives the normed rows, `residual` is updated in place.
+  LLGroup ar;                      // peer receive buffers, epoch words, world, rank
+  int ar_world;                    // 0 / 1 = off
+  const __nv_bfloat16* ar_norm_w;  // [N] RMSNorm weight, or null: C = all-reduced sum (+residual)
+  float ar_eps;
+  uint32_t* ar_done;               // zero-initialised device counter
 };
 
 struct TileCoord {
@@ -206,6 +216,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   volatile int* abort_flag = s_flags;
   const int groups = p.stages / p.ksub;   // barrier pairs in use
+  uint32_t ar_epoch = 0;
+  long long ar_slot_off = 0;
+  if (p.ar_world > 1) {
+    ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1;
+    ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -510,6 +526,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           continue;
         }
         if (!row_ok || col >= p.N) continue;
+        if (p.ar_world > 1) {
+          // push 16 columns (two 16-byte vectors) of this row to every rank; rank 0 adds the bias
+          if (p.bias && p.ar.rank == 0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col + i < p.N) v[i] += __bfloat162float(p.bias[col + i]);
+          }
+          uint4 pk0, pk1;
+          pk0.x = pack_bf16x2(v[0], v[1]);
+          pk0.y = pack_bf16x2(v[2], v[3]);
+          pk0.z = pack_bf16x2(v[4], v[5]);
+          pk0.w = pack_bf16x2(v[6], v[7]);
+          pk1.x = pack_bf16x2(v[8], v[9]);
+          pk1.y = pack_bf16x2(v[10], v[11]);
+          pk1.z = pack_bf16x2(v[12], v[13]);
+          pk1.w = pack_bf16x2(v[14], v[15]);
+          pk0 = ll_sanitize(pk0);
+          pk1 = ll_sanitize(pk1);
+          const long long vec = (static_cast<long long>(row) * p.N + col) >> 3;
+          const bool second = col + 8 < p.N;
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.ar_world) {
+              uint4* dst = p.ar.recv[r] + ar_slot_off + static_cast<long long>(p.ar.rank) * p.ar.slot_vecs + vec;
+              ll_store(dst, pk0);
+              if (second) ll_store(dst + 1, pk1);
+            }
+          }
+          continue;
+        }
         if (p.swiglu) {
           // Columns [c, c+8) hold gate values, [c+8, c+16) the matching up values.
           const int ocol = col >> 1;
@@ -646,6 +692,97 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (p.ar_world > 1) {
+    // ---- fused tail: reduce rows that have arrived from every rank (data-carried flags: no
+    // barrier between the ranks), + residual, RMSNorm.  Row r belongs to CTA r % gridDim.
+    __shared__ float ar_red[8];
+    const int nvec_row = p.N >> 3;
+    const uint4* mine = p.ar.recv[p.ar.rank] + ar_slot_off;
+    bool ar_ok = *abort_flag == 0;
+    for (int row = blockIdx.x; ar_ok && row < p.M; row += gridDim.x) {
+      // a thread owns vectors tid, tid + 192, ...; values are kept for the second pass
+      float ss = 0.f;
+      for (int vb = 0; vb < nvec_row; vb += kThreads) {
+        const int vi = vb + threadIdx.x;
+        if (vi < nvec_row) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.ar_world) {
+              uint4 x;
+              ar_ok = ll_wait(mine + static_cast<long long>(r) * p.ar.slot_vecs +
+                                  static_cast<long long>(row) * nvec_row + vi, x) && ar_ok;
+              add8(acc, x);
+            }
+          }
+          Pack8 y;
+          y.u = pack8(acc);            // the sum is rounded to bf16 before the residual add
+          Pack8 nr = y;
+          if (p.residual) {
+            uint4* rp = reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(p.residual)) +
+                        static_cast<long long>(row) * nvec_row + vi;
+            Pack8 rs;
+            rs.u = *rp;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              nr.h[j] = __float2bfloat16(__bfloat162float(y.h[j]) + __bfloat162float(rs.h[j]));
+            if (p.ar_norm_w) *rp = nr.u;      // the residual stream carries the pre-norm sum
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float f = __bfloat162float(nr.h[j]);
+            ss += f * f;
+          }
+          // first pass result parked in C (bf16); rewritten below when a norm follows
+          reinterpret_cast<uint4*>(p.C)[static_cast<long long>(row) * (p.ldc >> 3) + vi] = nr.u;
+        }
+      }
+      if (p.ar_norm_w) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) ar_red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) tot += ar_red[w];
+        const float inv = rsqrtf(tot / static_cast<float>(p.N) + p.ar_eps);
+        for (int vb = 0; vb < nvec_row; vb += kThreads) {
+          const int vi = vb + threadIdx.x;
+          if (vi < nvec_row) {
+            uint4* cp = reinterpret_cast<uint4*>(p.C) + static_cast<long long>(row) * (p.ldc >> 3) + vi;
+            Pack8 x, w8, o8;
+            x.u = *cp;                       // written by this same thread above
+            w8.u = reinterpret_cast<const uint4*>(p.ar_norm_w)[vi];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o8.h[j] = __float2bfloat16(__bfloat162float(x.h[j]) * inv * __bfloat162float(w8.h[j]));
+            *cp = o8.u;
+          }
+        }
+        __syncthreads();
+      }
+    }
+    if (!ar_ok) atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+    // re-arm the slot of the previous call, then the last CTA advances the epoch
+    {
+      volatile uint32_t* meta = reinterpret_cast<volatile uint32_t*>(p.ar.epoch);
+      const uint32_t prev_vecs = meta[1 + (ar_epoch + 2) % 3];
+      const uint4 s4 = make_uint4(kLLSentinel, kLLSentinel, kLLSentinel, kLLSentinel);
+      uint4* rearm = p.ar.recv[p.ar.rank] + static_cast<long long>((ar_epoch + 2) % 3) * p.ar_world * p.ar.slot_vecs;
+      const long long total = static_cast<long long>(prev_vecs) * p.ar_world;
+      for (long long idx = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; idx < total;
+           idx += static_cast<long long>(gridDim.x) * kThreads)
+        rearm[(idx / prev_vecs) * p.ar.slot_vecs + idx % prev_vecs] = s4;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.ar_done, 1u) == gridDim.x - 1) {
+          *p.ar_done = 0;
+          meta[1 + ar_epoch % 3] = static_cast<uint32_t>((static_cast<long long>(p.M) * p.N) >> 3);
+          meta[0] = ar_epoch;
+        }
+      }
+    }
+  }
   // No CTA of a cluster may retire while a peer can still read its staging
   // buffer or signal its barriers.
   if (p.cluster_split) cluster_sync_all();
@@ -892,10 +1029,12 @@ extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, 
 // handling here; callers fold scales, see the block-scaled wrapper).
 // workspace / counters may be null when splits == 1 or cluster_split == 1.
 // Returns 0 on success.
+struct ArArgs;
 static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
-                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales);
+                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
+                     const ArArgs* ar = nullptr);
 
 extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
                          const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
@@ -918,10 +1057,51 @@ extern "C" int b200_gemm_scaled(const void* A, const void* W, void* C, const flo
                    nullptr, status, max_ctas, stream, a_scales, w_scales);
 }
 
+struct ArArgs {
+  void* const* recv = nullptr;
+  int world = 0, rank = 0;
+  long long slot_vecs = 0;
+  void* epoch = nullptr;
+  const void* norm_w = nullptr;
+  float eps = 0.f;
+  void* done = nullptr;
+};
+
 static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
-                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales) {
+                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
+                     const ArArgs* ar);
+
+// Row-parallel projection of a tensor-parallel layer in ONE kernel: C = RMSNorm(residual +=
+// sum over ranks of (A @ W^T)) * norm_w  (norm_w null: C = sum (+ residual), residual untouched).
+// Output tiles are pushed to every rank's receive buffer (data-carried flags, no barrier);
+// the CTAs then reduce the rows as they arrive.  bf16, M * N * 2 bytes <= slot size, N % 8 == 0.
+extern "C" int b200_gemm_all_reduce(const void* A, const void* W, void* C, const void* bias, void* residual,
+                                    const void* norm_w, float eps, int M, int N, int K, int lda, int ldw,
+                                    int BN, void* const* recv, int world, int rank, long long slot_vecs,
+                                    void* epoch, void* done_counter, int* status, int max_ctas,
+                                    cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks) return -30;
+  if ((N & 7) != 0 || (static_cast<long long>(M) * N >> 3) > slot_vecs) return -31;
+  ArArgs ar;
+  ar.recv = recv;
+  ar.world = world;
+  ar.rank = rank;
+  ar.slot_vecs = slot_vecs;
+  ar.epoch = epoch;
+  ar.norm_w = norm_w;
+  ar.eps = eps;
+  ar.done = done_counter;
+  return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, N, 0, 0, 0, BN, 1, 0, nullptr, nullptr, status,
+                   max_ctas, stream, nullptr, nullptr, &ar);
+}
+
+static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
+                     int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
+                     int splits, int cluster_split, void* workspace, int* counters, int* status,
+                     int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
+                     const ArArgs* ar) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
@@ -958,6 +1138,17 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   p.status = status;
   p.a_scales = a_scales;
   p.w_scales = w_scales;
+  if (ar != nullptr && ar->world > 1) {
+    for (int r = 0; r < kMaxRanks; ++r) p.ar.recv[r] = r < ar->world ? static_cast<uint4*>(ar->recv[r]) : nullptr;
+    p.ar.epoch = static_cast<uint32_t*>(ar->epoch);
+    p.ar.world = ar->world;
+    p.ar.rank = ar->rank;
+    p.ar.slot_vecs = ar->slot_vecs;
+    p.ar_world = ar->world;
+    p.ar_norm_w = static_cast<const __nv_bfloat16*>(ar->norm_w);
+    p.ar_eps = ar->eps;
+    p.ar_done = static_cast<uint32_t*>(ar->done);
+  }
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kRowBytes / eb;

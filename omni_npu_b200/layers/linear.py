@@ -297,6 +297,23 @@ class RowParallelLinear(LinearBase):
         _copy_sharded(param, loaded, 1, self.tp_rank, self.tp_size)
 
 
+def row_parallel_add_rms_norm(linear: "RowParallelLinear", x: torch.Tensor, norm, residual: torch.Tensor):
+    """``residual += all_reduce(linear(x))``; returns (RMSNorm(residual), residual).
+
+    With the group's peer-mapped memory and a decode-sized problem this is ONE kernel (GEMM,
+    push all-reduce, residual add and norm: ``SymmetricMemory.gemm_all_reduce``); otherwise the
+    projection runs unreduced and the reduction is fused with the add + norm."""
+    from .norm import reduce_add_rms_norm
+    group = linear.group
+    symm = getattr(group.comm, "symm", None) if group.world_size > 1 else None
+    if (symm is not None and linear.x_transform is None and isinstance(linear.quant_method, UnquantizedLinearMethod)
+            and residual is not None and residual.is_contiguous() and symm.can_fuse_gemm(x, linear.weight)):
+        bias = linear.bias if (linear.bias is not None) else None
+        out = symm.gemm_all_reduce(x, linear.weight, bias, residual, norm.weight, norm.eps)
+        return out, residual
+    return reduce_add_rms_norm(norm, linear(x, reduce=False), residual, group)
+
+
 def _copy_sharded(param: nn.Parameter, loaded: torch.Tensor, dim: int, rank: int, world: int) -> None:
     if param.dim() == 2 and param.dtype == torch.float32 and loaded.dtype == torch.float32 \
             and loaded.shape != param.shape and world > 1 and loaded.shape[dim] % world != 0:

@@ -13,7 +13,7 @@ import torch
 from torch import nn
 
 from .activation import SiluAndMul
-from .linear import MergedColumnParallelLinear, RowParallelLinear
+from .linear import MergedColumnParallelLinear, RowParallelLinear, row_parallel_add_rms_norm
 
 
 class FusedMLP(nn.Module):
@@ -39,3 +39,13 @@ class FusedMLP(nn.Module):
         else:
             h = self.act(self.gate_up_proj(x))
         return self.down_proj(h, residual=residual, reduce=reduce)
+
+    def forward_add_rms_norm(self, x: torch.Tensor, norm, residual: torch.Tensor):
+        """MLP whose down projection, tensor-parallel reduction, residual add and the FOLLOWING
+        RMSNorm run as one kernel when the group has peer-mapped memory.  Returns
+        (norm(residual + mlp(x)), residual)."""
+        if self.fuse_swiglu:
+            h = self.gate_up_proj(x, fuse_swiglu=True)
+        else:
+            h = self.act(self.gate_up_proj(x))
+        return row_parallel_add_rms_norm(self.down_proj, h, norm, residual)

@@ -14,6 +14,7 @@ from .. import ops
 from ..attention.gqa import GQAAttention
 from ..config import EngineConfig, ModelConfig
 from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from ..layers.linear import row_parallel_add_rms_norm
 from ..layers.linear import QKVParallelLinear, RowParallelLinear
 from ..layers.mlp import FusedMLP
 from ..layers.norm import RMSNorm, reduce_add_rms_norm
@@ -42,13 +43,16 @@ class LlamaAttention(nn.Module):
                                  if self.rotary.mscale != 1.0 else cfg.head_dim ** -0.5,
                                  cfg.rotary_dim, cfg.rope_neox, cfg.sliding_window)
 
-    def forward(self, hidden: torch.Tensor, reduce: bool = True) -> torch.Tensor:
+    def forward(self, hidden: torch.Tensor, reduce: bool = True, fuse_norm=None):
         q, k, v = self.qkv_proj(hidden)
         if self.qk_norm:
             t = q.shape[0]
             q = self.q_norm(q.reshape(-1, self.head_dim)).view(t, -1)
             k = self.k_norm(k.reshape(-1, self.head_dim)).view(t, -1)
         o = self.attn(q, k, v, self.rotary.cos_sin_cache)
+        if fuse_norm is not None:
+            # o_proj + tensor-parallel reduction + residual add + the following RMSNorm
+            return row_parallel_add_rms_norm(self.o_proj, o, fuse_norm[0], fuse_norm[1])
         return self.o_proj(o, reduce=reduce)
 
 
@@ -78,6 +82,14 @@ class LlamaDecoderLayer(nn.Module):
         hidden = self.mlp(hidden, reduce=False)
         return hidden, residual
 
+    def forward_fused(self, hidden: torch.Tensor, residual: torch.Tensor, next_norm):
+        """``hidden`` is this layer's input AFTER its input norm, ``residual`` the stream.  Both
+        row-parallel projections run fused with their reduction, the residual add and the norm
+        that follows them (this layer's post-attention norm; ``next_norm`` = the next layer's
+        input norm or the model's final norm).  Returns (next layer's normed input, residual)."""
+        hidden, residual = self.self_attn(hidden, fuse_norm=(self.post_attention_layernorm, residual))
+        return self.mlp.forward_add_rms_norm(hidden, next_norm, residual)
+
     def forward_sequence_parallel(self, sp, hidden: Optional[torch.Tensor], residual: torch.Tensor):
         """The same layer on a token-sharded residual stream (layers/flashcomm.py)."""
         hidden, residual = sp.block(self.input_layernorm, hidden, residual,
@@ -88,6 +100,7 @@ class LlamaDecoderLayer(nn.Module):
 
 class LlamaModel(nn.Module):
     sequence_parallel = False       # set by the owning model from ParallelConfig
+    fused_tail = True               # GEMM + all-reduce + add + norm in one kernel where possible
 
     def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:
         super().__init__()
@@ -108,6 +121,15 @@ class LlamaModel(nn.Module):
                 hidden, residual = layer.forward_sequence_parallel(sp, hidden, residual)
             hidden, _ = self.norm(hidden, residual)
             return sp.gather(hidden, trim=True)
+        if tp.world_size > 1 and getattr(tp.comm, "symm", None) is not None and self.fused_tail:
+            # every row-parallel projection carries its reduction, residual add and next norm
+            residual = hidden
+            hidden = self.layers[0].input_layernorm(hidden)
+            n = len(self.layers)
+            for i, layer in enumerate(self.layers):
+                nxt = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
+                hidden, residual = layer.forward_fused(hidden, residual, nxt)
+            return hidden
         residual = None
         for layer in self.layers:
             hidden, residual = layer(hidden, residual)

@@ -50,7 +50,10 @@ def register_models() -> None:
     except Exception:
         return
     from .vllm_adapters import ADAPTERS
+    known = set(ModelRegistry.get_supported_archs()) if hasattr(ModelRegistry, "get_supported_archs") else set()
     for arch, path in ADAPTERS.items():
+        if arch in known:
+            continue            # vLLM's own class already runs on this platform with our kernels underneath
         try:
             ModelRegistry.register_model(arch, path)
         except Exception:

@@ -55,6 +55,9 @@ def _lib() -> ctypes.CDLL:
         lib.b200_symm_ll_arm.restype = ci
         lib.b200_symm_all_reduce_ll.argtypes = [pp, ci, ci, ll, vp, vp, vp, ll, vp, vp, ci, ctypes.c_float, vp, vp, vp]
         lib.b200_symm_all_reduce_ll.restype = ci
+        lib.b200_gemm_all_reduce.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_float, ci, ci, ci, ci, ci, ci, pp, ci, ci,
+                                             ll, vp, vp, vp, ci, vp]
+        lib.b200_gemm_all_reduce.restype = ci
         _LIB = lib
     return _LIB
 
@@ -112,6 +115,7 @@ class SymmetricMemory:
         self.ll_meta = torch.zeros(4, dtype=torch.int32, device=device)      # epoch + per-slot fill counts
         self.ll_done = torch.zeros(4, dtype=torch.int32, device=device)
         self.use_ll = os.environ.get("OMNI_B200_SYMM_LL", "1") != "0"
+        self.fuse_gemm = os.environ.get("OMNI_B200_FUSE_GEMM_AR", "1") != "0"
         self.status = ops.device_state(device).status
         if lib.b200_symm_ll_arm(ll_ptr, ll_total_vecs, self._stream()) != 0:
             raise RuntimeError("arming the push all-reduce buffer failed")
@@ -206,15 +210,38 @@ class SymmetricMemory:
         ops._count(1)
         return out
 
-    def gemm_all_reduce(self, x: torch.Tensor, w: torch.Tensor, bias, residual) -> Optional[torch.Tensor]:
-        """Row-parallel projection: local GEMM, then the peer-memory all-reduce."""
-        y = ops.gemm(x, w, bias)
-        if not self.can_all_reduce(y):
-            return None
-        y = self.all_reduce(y)
-        if residual is not None:
-            y = y + residual
-        return y
+    def can_fuse_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """The one-kernel GEMM + all-reduce handles bf16 problems whose output fits one slot of the
+        push buffer and whose K is short enough to need no split-K (decode-sized M)."""
+        m, n = x.shape[0], w.shape[0]
+        return (self.use_ll and self.fuse_gemm and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.dim() == 2 and x.stride(1) == 1 and w.is_contiguous() and n % 8 == 0 and m <= 256
+                and m * n * 2 <= self.LL_SLOT_BYTES and x.shape[1] <= 8192)
+
+    def gemm_all_reduce(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                        residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                        eps: float = 0.0, bn: int = 0) -> torch.Tensor:
+        """Row-parallel projection of a tensor-parallel layer as ONE kernel: every rank computes
+        its partial ``x @ w.T``, the GEMM epilogue pushes the tiles into all ranks' receive
+        buffers, and the same kernel reduces the rows as they arrive.  With ``norm_weight``:
+        ``residual += sum`` (in place) and the result is ``RMSNorm(residual) * norm_weight``;
+        without: the result is ``sum (+ residual)``."""
+        m, k = x.shape
+        n = w.shape[0]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        if bn <= 0:
+            # one row of tiles (M <= 128) or two: pick the tile width that spreads them over the SMs
+            bn = 32 if n <= 4608 else (64 if n <= 9216 else 128)
+        rc = _lib().b200_gemm_all_reduce(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+            residual.data_ptr() if residual is not None else None,
+            norm_weight.data_ptr() if norm_weight is not None else None, eps, m, n, k, x.stride(0), w.stride(0), bn,
+            self.ll_ptrs, self.world, self.rank, self.ll_slot_vecs, self.ll_meta.data_ptr(), self.ll_done.data_ptr(),
+            self.status.data_ptr(), 0, self._stream())
+        if rc != 0:
+            raise RuntimeError(f"fused gemm + all_reduce failed ({rc})")
+        ops._count(1)
+        return out
 
     def close(self) -> None:
         lib = _lib()

@@ -132,6 +132,28 @@ def task_symm(rank, world, port, workdir, device_kind):
     res["max_err"]["fused_norm_out_pull"] = (y_pull.float() - y_ref.float()).abs().max().item()
     res["max_err"]["fused_norm_res_pull"] = (r_pull.float() - r_ref.float()).abs().max().item()
     res["max_err"]["fused_norm_res"] = (r_got.float() - r_ref.float()).abs().max().item()
+    # GEMM + all-reduce (+ residual + RMSNorm) as one kernel, against the unfused sequence
+    for name, (m, n, k), with_norm in (("gemm_ar_norm", (128, 4096, 2048), True), ("gemm_ar_norm_odd", (7, 1032, 520), True),
+                                       ("gemm_ar_plain", (33, 4096, 512), False), ("gemm_ar_norm_again", (128, 4096, 2048), True)):
+        xa = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        wa = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+        ba = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        ra = torch.randn(m, n, device=dev, dtype=torch.bfloat16)
+        wn = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        for t in (ba, ra, wn):
+            dist.broadcast(t, src=0, group=g.device_group)
+        part = ops.gemm(xa, wa, ba if rank == 0 else None)
+        dist.all_reduce(part, group=g.device_group)
+        if with_norm:
+            r_ref = ra.clone()
+            y_ref = ops.fused_add_rms_norm(part, r_ref, wn, 1e-6)
+            r_got = ra.clone()
+            y_got = symm.gemm_all_reduce(xa, wa, ba, r_got, wn, 1e-6)
+            res["max_err"][name + "_res"] = (r_got.float() - r_ref.float()).abs().max().item()
+        else:
+            y_ref = part + ra
+            y_got = symm.gemm_all_reduce(xa, wa, ba, ra, None, 0.0)
+        res["max_err"][name] = (y_got.float() - y_ref.float()).abs().max().item() / max(1.0, y_ref.float().abs().max().item())
     # all-gather / reduce-scatter
     x = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
     ag_ref = torch.empty(world * 64, 512, device=dev, dtype=torch.bfloat16)
@@ -185,6 +207,12 @@ def task_symm(rank, world, port, workdir, device_kind):
         res[f"us_graph_push_{rows}"] = graph_time(lambda: symm.all_reduce(xs, mode=3))
         res[f"us_graph_fused_{rows}"] = graph_time(lambda: symm.all_reduce_add_rms_norm(xs, rr, wn, 1e-6))
         res[f"us_graph_local_norm_{rows}"] = graph_time(lambda: ops.fused_add_rms_norm(xs, rr, wn, 1e-6))
+    # decode-sized row-parallel projection: one kernel vs GEMM followed by the fused all-reduce
+    xa = torch.randn(128, 2048, device=dev, dtype=torch.bfloat16)
+    wa = torch.randn(4096, 2048, device=dev, dtype=torch.bfloat16) * 0.05
+    rr = torch.zeros(128, 4096, device=dev, dtype=torch.bfloat16)
+    res["us_graph_gemm_then_ar_norm"] = graph_time(lambda: symm.all_reduce_add_rms_norm(ops.gemm(xa, wa), rr, wn, 1e-6))
+    res["us_graph_gemm_ar_norm_fused"] = graph_time(lambda: symm.gemm_all_reduce(xa, wa, None, rr, wn, 1e-6))
     big = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
     res["us_symm_64MiB"] = timeit(lambda: symm.all_reduce(big), 10)
     res["us_nccl_64MiB"] = timeit(lambda: dist.all_reduce(big, group=g.device_group), 10)
