@@ -695,7 +695,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (p.ar_world > 1) {
     // ---- fused tail: reduce rows that have arrived from every rank (data-carried flags: no
     // barrier between the ranks), + residual, RMSNorm.  Row r belongs to CTA r % gridDim.
-    __shared__ float ar_red[8];
+    // (the operand stages are idle by now: every load has landed and every MMA has retired)
+    float* ar_red = reinterpret_cast<float*>(smem_a);
     const int nvec_row = p.N >> 3;
     const uint4* mine = p.ar.recv[p.ar.rank] + ar_slot_off;
     bool ar_ok = *abort_flag == 0;
