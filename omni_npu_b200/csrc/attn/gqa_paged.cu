@@ -17,6 +17,8 @@
 // Replaces npu_fused_infer_attention_score in its TND paged form
 // (omni_npu/attention/backends/attention.py:216-281).
 
+#include <cstdlib>
+
 #include "attn_common.cuh"
 #include "../common/tensormap.h"
 
@@ -570,10 +572,10 @@ __global__ void __launch_bounds__(128) gqa_decode_kernel(const AttnParams p) {
 // decode needs.  The cache is addressed as a 2-D tensor
 // [num_blocks * kv_heads * block_size rows, D columns]; a box is
 // (box_rows = min(block_size, 64)) rows x 64 columns (128 bytes).
-template <int D>
+template <int D, int NSTAGES = 3>
 struct DecodeTmaCfg {
   static constexpr int BN = 64;
-  static constexpr int STAGES = 3;
+  static constexpr int STAGES = NSTAGES;
   static constexpr int COMPUTE_THREADS = 128;
   static constexpr int THREADS = 160;          // 4 compute warps + 1 producer warp
   static constexpr int HALVES = D / 64;
@@ -589,12 +591,14 @@ __device__ __forceinline__ uint32_t kv_swz(int key, int chunk) {
   return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
 }
 
-template <int D>
-__global__ void __launch_bounds__(160)
+// NSTAGES / MINB: three stages and two CTAs per SM, or two stages and three CTAs per SM (more
+// warps to hide the latency of the dependent ldmatrix -> mma -> softmax chains).
+template <int D, int NSTAGES, int MINB>
+__global__ void __launch_bounds__(160, MINB)
 gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p,
                       const int box_rows) {
-  using Cfg = DecodeTmaCfg<D>;
+  using Cfg = DecodeTmaCfg<D, NSTAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -938,6 +942,40 @@ static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
+template <int D, int NSTAGES, int MINB>
+static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  using Cfg = DecodeTmaCfg<D, NSTAGES>;
+  auto kern = gqa_decode_tma_kernel<D, NSTAGES, MINB>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+      return -20;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    configured = true;
+  }
+  const int box_rows = p.block_size < 64 ? p.block_size : 64;
+  CUtensorMap tk, tv;
+  // Unknown cache size (callers on the raw C ABI): describe a view large enough for
+  // any block index; only the boxes named by the block table are ever touched.
+  const uint64_t rows = p.num_cache_blocks > 0
+                            ? static_cast<uint64_t>(p.num_cache_blocks) * p.Hk * p.block_size
+                            : (1ull << 31);
+  int r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.k_cache, rows, D, D, box_rows, 64,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 2000;
+  r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.v_cache, rows, D, D, box_rows, 64,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 3000;
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tk, tv, p, box_rows);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (p.splits > 1) {
+    const long long warps = static_cast<long long>(grid.x) * p.Hk * (p.Hq / p.Hk) * p.q_len;
+    gqa_decode_merge_kernel<D><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(p, static_cast<int>(grid.x));
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
 template <int D>
 static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
   const bool use_tma = (p.block_size % 8) == 0 && (p.block_size <= 64 ? (64 % p.block_size) == 0
@@ -946,30 +984,12 @@ static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
                        (reinterpret_cast<uintptr_t>(p.v_cache) & 15) == 0;
   dim3 grid(B, p.Hk, p.splits);
   if (use_tma) {
-    using Cfg = DecodeTmaCfg<D>;
-    auto kern = gqa_decode_tma_kernel<D>;
-    static bool configured = false;
-    if (!configured) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
-          cudaSuccess)
-        return -20;
-      cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-      configured = true;
-    }
-    const int box_rows = p.block_size < 64 ? p.block_size : 64;
-    CUtensorMap tk, tv;
-    // Unknown cache size (callers on the raw C ABI): describe a view large enough for
-    // any block index; only the boxes named by the block table are ever touched.
-    const uint64_t rows = p.num_cache_blocks > 0
-                              ? static_cast<uint64_t>(p.num_cache_blocks) * p.Hk * p.block_size
-                              : (1ull << 31);
-    int r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.k_cache, rows, D, D,
-                              box_rows, 64, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r) return r - 2000;
-    r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.v_cache, rows, D, D, box_rows,
-                          64, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r) return r - 3000;
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tk, tv, p, box_rows);
+    static const int occ3 = [] {
+      const char* e = getenv("OMNI_B200_DECODE_OCC3");
+      return e ? atoi(e) : 0;
+    }();
+    if (occ3) return launch_decode_tma<D, 2, 3>(p, grid, stream);
+    return launch_decode_tma<D, 3, 2>(p, grid, stream);
   } else {
     using Cfg = DecodeCfg<D>;
     auto kern = gqa_decode_kernel<D>;

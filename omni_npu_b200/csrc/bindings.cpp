@@ -24,6 +24,10 @@ int b200_grouped_gemm(const void* A, const void* W, void* C, const int* expert_o
                       int num_experts, int total_rows, int N, int K, int lda, int ldc,
                       int dtype_fp8, int swiglu, int BN, int* status, int max_ctas,
                       cudaStream_t stream);
+int b200_lse_merge(void* out, float* lse_out, const void* outs, const float* lses, int N, long long T, int H, int D,
+                   long long stride_n_out, long long stride_n_lse, cudaStream_t stream);
+int b200_gather_cache(void* dst, const void* cache, const int* block_tables, const int* cu_seq, int B,
+                      int max_blocks, int block_size, int row_bytes, int max_seq_len, cudaStream_t stream);
 int b200_spec_verify(const int* draft, const int* target, const int* bonus, const int* cu, int* out,
                      int* num_out, int B, int max_spec, cudaStream_t stream);
 int b200_rmsnorm(void* out, const void* x, void* residual, const void* w, float eps, long long rows,
@@ -101,6 +105,44 @@ inline void check(int rc, const char* what) {
   TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16, #t " must be a CUDA bf16 tensor")
 #define CHECK_I32(t) \
   TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kInt && (t).is_contiguous(), #t " must be a contiguous CUDA int32 tensor")
+
+// Merge N partial attention results over disjoint key sets by their log-sum-exp.
+// outs [N, T, H, D] bf16, lses [N, T, H] fp32 -> (out [T, H, D], lse [T, H]).
+std::tuple<Tensor, Tensor> lse_merge(const Tensor& outs, const Tensor& lses) {
+  CHECK_CUDA_BF16(outs);
+  TORCH_CHECK(outs.dim() == 4 && outs.is_contiguous() && lses.is_cuda() && lses.scalar_type() == at::kFloat &&
+                  lses.dim() == 3 && lses.is_contiguous(), "lse_merge: outs [N,T,H,D] bf16, lses [N,T,H] fp32");
+  const int N = outs.size(0), H = outs.size(2), D = outs.size(3);
+  const long long T = outs.size(1);
+  TORCH_CHECK(lses.size(0) == N && lses.size(1) == T && lses.size(2) == H, "lse_merge: shapes");
+  c10::cuda::CUDAGuard guard(outs.device());
+  Tensor out = torch::empty({T, H, D}, outs.options());
+  Tensor lse = torch::empty({T, H}, lses.options());
+  check(b200_lse_merge(out.data_ptr(), lse.data_ptr<float>(), outs.data_ptr(), lses.data_ptr<float>(), N, T, H, D,
+                       T * H * D, T * H, cur_stream()),
+        "lse_merge");
+  return {out, lse};
+}
+
+// Contiguous copy of the cached rows of B sequences: cache [blocks, block_size, ...],
+// cu_seq [B+1] int32 -> [cu_seq[B], ...].
+Tensor gather_cache(const Tensor& cache, const Tensor& block_tables, const Tensor& cu_seq, int64_t total_tokens,
+                    int64_t max_seq_len) {
+  TORCH_CHECK(cache.is_cuda() && cache.is_contiguous() && cache.dim() >= 3, "gather_cache: cache [blocks, bs, ...]");
+  CHECK_I32(block_tables);
+  CHECK_I32(cu_seq);
+  const int bs = cache.size(1);
+  const int64_t width = cache.numel() / (cache.size(0) * bs);
+  c10::cuda::CUDAGuard guard(cache.device());
+  std::vector<int64_t> shape{total_tokens};
+  for (int i = 2; i < cache.dim(); ++i) shape.push_back(cache.size(i));
+  Tensor dst = torch::empty(shape, cache.options());
+  check(b200_gather_cache(dst.data_ptr(), cache.data_ptr(), block_tables.data_ptr<int>(), cu_seq.data_ptr<int>(),
+                          (int)cu_seq.numel() - 1, (int)block_tables.size(1), bs,
+                          (int)(width * cache.element_size()), (int)max_seq_len, cur_stream()),
+        "gather_cache");
+  return dst;
+}
 
 // Speculative decoding: accept drafts while they equal the target's tokens.
 // Returns (tokens [B, max_spec+1] padded with -1, count [B]).
@@ -611,6 +653,8 @@ Tensor sample(const Tensor& logits, const c10::optional<Tensor>& temperature,
 
 TORCH_LIBRARY(omni_b200, m) {
   m.def("spec_verify", &spec_verify);
+  m.def("lse_merge", &lse_merge);
+  m.def("gather_cache", &gather_cache);
   m.def("gemm_plan", &gemm_plan);
   m.def("gemm", &gemm);
   m.def("gemm_pair", &gemm_pair);

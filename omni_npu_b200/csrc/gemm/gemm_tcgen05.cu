@@ -456,6 +456,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (orow >= tc.m_end || col >= p.N) continue;
             float v[4] = {sum.x, sum.y, sum.z, sum.w};
             const int ncols = min(4, p.N - col);
+            if (p.ar_world > 1) {
+              // fused tensor-parallel tail: push 4 columns (half a 16-byte vector) to every rank;
+              // N is a multiple of 8 here, so the 4 columns are all valid
+              if (p.bias && p.ar.rank == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] += __bfloat162float(p.bias[col + i]);
+              }
+              uint32_t w0 = pack_bf16x2(v[0], v[1]), w1 = pack_bf16x2(v[2], v[3]);
+              if (w0 == kLLSentinel) w0 = 0u;
+              if (w1 == kLLSentinel) w1 = 0u;
+              const long long word = (static_cast<long long>(orow) * p.N + col) >> 1;     // 32-bit words
+#pragma unroll
+              for (int r = 0; r < kMaxRanks; ++r) {
+                if (r < p.ar_world) {
+                  uint32_t* dst = reinterpret_cast<uint32_t*>(p.ar.recv[r] + ar_slot_off +
+                                                              static_cast<long long>(p.ar.rank) * p.ar.slot_vecs) + word;
+                  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(w0), "r"(w1) : "memory");
+                }
+              }
+              continue;
+            }
             for (int i = 0; i < ncols; ++i) {
               if (p.bias) v[i] += __bfloat162float(p.bias[col + i]);
               if (p.residual)
@@ -1094,8 +1115,18 @@ extern "C" int b200_gemm_all_reduce(const void* A, const void* W, void* C, const
   ar.norm_w = norm_w;
   ar.eps = eps;
   ar.done = done_counter;
-  return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, N, 0, 0, 0, BN, 1, 0, nullptr, nullptr, status,
-                   max_ctas, stream, nullptr, nullptr, &ar);
+  int splits = 1, cluster = 0;
+  if (BN <= 0) {
+    // same plan as the stand-alone decode GEMM: K split over the CTAs of a cluster when that
+    // spreads the weight stream over more SMs (the cluster's reduced tile is what gets pushed)
+    GemmPlan pl{128, 1, 4, 0};
+    if (!plan_small_m(M, N, K, 2, true, &pl)) pl = GemmPlan{128, 1, 4, 0};
+    BN = pl.BN;
+    splits = pl.splits;
+    cluster = pl.cluster;
+  }
+  return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, N, 0, 0, 0, BN, splits, cluster, nullptr, nullptr,
+                   status, max_ctas, stream, nullptr, nullptr, &ar);
 }
 
 static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,

@@ -359,6 +359,29 @@ def gqa_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return (out, lse) if return_lse else out
 
 
+def merge_attn_states(outs: torch.Tensor, lses: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Combine N partial attention results over disjoint key sets.  ``outs`` [N, T, H, D],
+    ``lses`` [N, T, H] (natural log-sum-exp of the scaled scores, -inf where a partial saw no
+    key) -> (out [T, H, D], lse [T, H])."""
+    if not outs.is_cuda:
+        return ref.merge_attn_states(outs, lses)
+    _count(1)
+    return _C().lse_merge(outs.contiguous(), lses.float().contiguous())
+
+
+def gather_cache(cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor) -> torch.Tensor:
+    """Contiguous copy of the cached rows of each sequence, one sequence after another:
+    cache [blocks, block_size, ...] -> [sum(seq_lens), ...]."""
+    lens = seq_lens.tolist()
+    total, longest = sum(lens), max(lens) if lens else 0
+    if not cache.is_cuda:
+        return ref.gather_cache(cache, block_tables, seq_lens)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=cache.device)
+    cu[1:] = seq_lens.to(cache.device).cumsum(0)
+    _count(1)
+    return _C().gather_cache(cache, block_tables.contiguous(), cu, total, longest)
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int, max_seq_len: int, sms: int = 148) -> int:
     """Split-KV factor: enough CTAs for two waves, at least 256 keys per split."""
     base = max(1, num_seqs * num_kv_heads)

@@ -393,3 +393,25 @@ def gemm_scaled(a_q: torch.Tensor, w_q: torch.Tensor, a_scale: torch.Tensor, w_s
     if residual is not None:
         out = out + residual.float()
     return out.to(out_dtype or torch.bfloat16)
+
+
+def merge_attn_states(outs: torch.Tensor, lses: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """outs [N,T,H,D], lses [N,T,H] -> (out [T,H,D], lse [T,H]); -inf partials are ignored."""
+    l = lses.float()
+    m = l.max(dim=0).values
+    w = torch.exp(l - torch.where(torch.isinf(m), torch.zeros_like(m), m))
+    w = torch.where(torch.isinf(l), torch.zeros_like(w), w)
+    denom = w.sum(0)
+    out = (outs.float() * (w / denom.clamp_min(1e-38)).unsqueeze(-1)).sum(0)
+    lse = torch.where(denom > 0, m + torch.log(denom.clamp_min(1e-38)), torch.full_like(m, float("-inf")))
+    return out.to(outs.dtype), lse
+
+
+def gather_cache(cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor) -> torch.Tensor:
+    bs = cache.shape[1]
+    parts = []
+    for b, n in enumerate(seq_lens.tolist()):
+        pos = torch.arange(n, device=cache.device)
+        rows = block_tables[b][pos // bs].long() * bs + pos % bs
+        parts.append(cache.reshape(-1, *cache.shape[2:])[rows])
+    return torch.cat(parts) if parts else cache.new_zeros(0, *cache.shape[2:])

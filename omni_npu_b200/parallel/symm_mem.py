@@ -229,9 +229,7 @@ class SymmetricMemory:
         m, k = x.shape
         n = w.shape[0]
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-        if bn <= 0:
-            # one row of tiles (M <= 128) or two: pick the tile width that spreads them over the SMs
-            bn = 32 if n <= 4608 else (64 if n <= 9216 else 128)
+        # bn = 0: the kernel plans tile width / cluster split-K like the stand-alone decode GEMM
         rc = _lib().b200_gemm_all_reduce(
             x.data_ptr(), w.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
             residual.data_ptr() if residual is not None else None,

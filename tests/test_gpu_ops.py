@@ -325,6 +325,37 @@ def test_gqa_window_with_sink_tokens(window, sink):
         _close(got, want, 2e-2, 2e-2)
 
 
+def test_lse_merge_and_gather_cache():
+    torch.manual_seed(14)
+    n, t, h, d = 3, 37, 8, 128
+    outs = torch.randn(n, t, h, d, device=DEV, dtype=torch.bfloat16)
+    lses = torch.randn(n, t, h, device=DEV) * 3
+    lses[1, 5] = float("-inf")                      # a partial that saw no key
+    lses[:, 9, 2] = float("-inf")                   # nobody saw a key
+    got, lse = ops.merge_attn_states(outs, lses)
+    want, lse_want = ref.merge_attn_states(outs.cpu(), lses.cpu())
+    _close(got, want, 2e-2, 2e-2)
+    assert torch.isinf(lse[9, 2]) and float(got[9, 2].abs().sum()) == 0
+    fin = ~torch.isinf(lse_want)
+    _close(lse.cpu()[fin], lse_want[fin], 1e-3, 1e-3)
+    # merging the two halves of a key set reproduces attention over the whole set
+    q = torch.randn(4, 64)
+    k, v = torch.randn(50, 64), torch.randn(50, 64)
+    def part(ks, vs):
+        s_ = q @ ks.t()
+        l_ = torch.logsumexp(s_, -1)
+        return torch.softmax(s_, -1) @ vs, l_
+    (o1, l1), (o2, l2) = part(k[:20], v[:20]), part(k[20:], v[20:])
+    whole, _ = part(k, v)
+    m_out, _ = ops.merge_attn_states(torch.stack([o1, o2]).unsqueeze(2).to(DEV, torch.bfloat16),
+                                     torch.stack([l1, l2]).unsqueeze(2).to(DEV))
+    _close(m_out[:, 0], whole, 3e-2, 3e-2)
+    cache = torch.randn(12, 16, 576, device=DEV, dtype=torch.bfloat16)
+    bt = torch.tensor([[3, 7, 1, 0], [11, 2, 0, 0]], dtype=torch.int32, device=DEV)
+    sl = torch.tensor([40, 17], dtype=torch.int32)
+    assert torch.equal(ops.gather_cache(cache, bt, sl).cpu(), ref.gather_cache(cache.cpu(), bt.cpu(), sl))
+
+
 def test_rope_cache_gqa_and_cache_write():
     t, hq, hk, d, bs = 29, 8, 2, 128, 16
     qkv = torch.randn(t, (hq + 2 * hk) * d, device=DEV, dtype=torch.bfloat16)
