@@ -555,10 +555,10 @@ int64_t mla_decode_scratch_bytes(int64_t T, int64_t N, int64_t splits) {
 
 // Absorbed multi-head latent attention over the paged latent cache.
 // q [T, N*576], cache [blocks, block_size, 576] -> out [T, N*512].
-Tensor mla_decode(const Tensor& q, const Tensor& cache, const Tensor& block_tables,
+std::tuple<Tensor, Tensor> mla_decode(const Tensor& q, const Tensor& cache, const Tensor& block_tables,
                   const Tensor& seq_lens, const c10::optional<Tensor>& topk_indices,
                   int64_t num_seqs, int64_t q_len, int64_t num_heads, double scale, int64_t splits,
-                  const c10::optional<Tensor>& scratch, const Tensor& status) {
+                  const c10::optional<Tensor>& scratch, const Tensor& status, bool return_lse) {
   CHECK_CUDA_BF16(q);
   CHECK_CUDA_BF16(cache);
   CHECK_I32(block_tables);
@@ -584,13 +584,14 @@ Tensor mla_decode(const Tensor& q, const Tensor& cache, const Tensor& block_tabl
                 "mla_decode: scratch too small");
     sp = scratch->data_ptr();
   }
-  check(b200_mla_decode(q.data_ptr(), cache.data_ptr(), out.data_ptr(), nullptr,
+  Tensor lse = return_lse ? torch::empty({q.size(0), num_heads}, q.options().dtype(at::kFloat)) : Tensor();
+  check(b200_mla_decode(q.data_ptr(), cache.data_ptr(), out.data_ptr(), return_lse ? lse.data_ptr<float>() : nullptr,
                         block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), tk, topk, (int)num_seqs,
                         (int)q_len, (int)num_heads, (int)block_tables.size(1), (int)cache.size(1),
                         (int)cache.size(0), q.stride(0), out.stride(0), (float)scale, (int)splits, sp,
                         status.data_ptr<int>(), cur_stream()),
         "mla_decode");
-  return out;
+  return {out, lse};
 }
 
 // Router: gate logits [T,E] fp32 -> (top-k ids int32 [T,k], weights fp32 [T,k]).

@@ -462,12 +462,13 @@ def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, sigmoid
 def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                num_seqs: int, num_heads: int, scale: float, q_len: int = 1,
                topk_indices: Optional[torch.Tensor] = None, splits: int = 0,
-               max_seq_len: int = 0) -> torch.Tensor:
+               max_seq_len: int = 0, return_lse: bool = False):
     """Absorbed multi-head latent attention (MQA over the 576-wide latent cache);
-    optionally restricted to ``topk_indices`` (sparse attention)."""
+    optionally restricted to ``topk_indices`` (sparse attention).  ``return_lse`` also returns
+    the natural log-sum-exp of the scaled scores [T, N] (for merging partial results)."""
     if not q.is_cuda:
         return ref.mla_decode(q, cache, block_tables[:num_seqs], seq_lens[:num_seqs], num_seqs, q_len,
-                              num_heads, scale, topk_indices)
+                              num_heads, scale, topk_indices, return_lse)
     C = _C()
     st = device_state(q.device)
     t = num_seqs * q_len
@@ -481,8 +482,9 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
         nbytes = C.mla_decode_scratch_bytes(t, num_heads, splits)
         scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
     _count(2 if splits > 1 else 1)
-    return C.mla_decode(q, cache, block_tables, seq_lens, topk_indices, num_seqs, q_len, num_heads, scale,
-                        splits, scratch, st.status)
+    out, lse = C.mla_decode(q, cache, block_tables, seq_lens, topk_indices, num_seqs, q_len, num_heads, scale,
+                            splits, scratch, st.status, return_lse)
+    return (out, lse) if return_lse else out
 
 
 # ------------------------------------------------------------------ KV transfer

@@ -325,12 +325,13 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_ids: 
 
 def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
                num_seqs: int, q_len: int, num_heads: int, scale: float,
-               topk_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+               topk_indices: Optional[torch.Tensor] = None, return_lse: bool = False):
     """Absorbed MLA reference.  q [T, N*576], cache [blocks, bs, 576] -> [T, N*512].
     Query token i of a sequence sees keys 0 .. seq_len - q_len + i; with
     ``topk_indices`` [T, topk] only those positions (negative = hole)."""
     bs = cache.shape[1]
     out = torch.zeros(q.shape[0], num_heads * 512, dtype=q.dtype, device=q.device)
+    lse = torch.full((q.shape[0], num_heads), float("-inf"), dtype=torch.float32, device=q.device)
     flat = cache.view(-1, 576)
     for b in range(num_seqs):
         n = int(seq_lens[b])
@@ -346,9 +347,11 @@ def mla_decode(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
             rows = block_tables[b][pos // bs].long() * bs + pos % bs
             kv = flat[rows].float()                                   # [L, 576]
             qq = q[t].view(num_heads, 576).float()
-            p = torch.softmax(qq @ kv.t() * scale, dim=-1)
+            sc = qq @ kv.t() * scale
+            p = torch.softmax(sc, dim=-1)
+            lse[t] = torch.logsumexp(sc, dim=-1)
             out[t] = (p @ kv[:, :512]).reshape(-1).to(q.dtype)
-    return out
+    return (out, lse) if return_lse else out
 
 
 def spec_verify(draft: torch.Tensor, target: torch.Tensor, bonus: torch.Tensor, cu: torch.Tensor,

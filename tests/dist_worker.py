@@ -315,7 +315,46 @@ def task_kv_pull(rank, world, port, workdir, device_kind):
     state.finish_process()
 
 
-TASKS = {"ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
+def task_dcp_mla(rank, world, port, workdir, device_kind):
+    """Decode context parallelism: the latent cache is sharded by tokens (token p on rank p % world);
+    the merged result must equal attention over the whole cache."""
+    dev, state = setup(rank, world, port, device_kind)
+    state.init_model_parallel(tp=world, device=dev)
+    from omni_npu_b200 import ops
+    from omni_npu_b200.attention.dcp import dcp_mla_decode, local_seq_lens
+    g = state.get_tp_group()
+    dt = torch.bfloat16 if device_kind == "cuda" else torch.float32
+    torch.manual_seed(3)
+    bs, heads, b = 16, 4 * world, 3
+    seq_lens = torch.tensor([37, 5, 64], dtype=torch.int32)
+    nblk = 16
+    full = (torch.randn(nblk, bs, 576) * 0.3).to(dt)                      # every rank builds the same global cache
+    bt = torch.tensor([[1, 2, 3, 4, 5], [6, 0, 0, 0, 0], [7, 8, 9, 10, 11]], dtype=torch.int32)
+    q = (torch.randn(b, heads, 576) * 0.3).to(dt)
+    want = ops.mla_decode(q.reshape(b, -1), full, bt, seq_lens, b, heads, 0.1)
+    # local shard: token p of sequence s sits at local position p // world of the same block-table row
+    local = torch.zeros_like(full)
+    flat_full, flat_local = full.view(-1, 576), local.view(-1, 576)
+    for s in range(b):
+        for p in range(int(seq_lens[s])):
+            if p % world != rank:
+                continue
+            lp = p // world
+            flat_local[int(bt[s, lp // bs]) * bs + lp % bs] = flat_full[int(bt[s, p // bs]) * bs + p % bs]
+    hl = heads // world
+    q_local = q[:, rank * hl: (rank + 1) * hl].reshape(b, -1).contiguous()
+    got = dcp_mla_decode(q_local.to(dev), local.to(dev), bt.to(dev), seq_lens.to(dev), b, hl, 0.1, g)
+    ref_local = want.view(b, heads, 512)[:, rank * hl: (rank + 1) * hl].reshape(b, -1)
+    err = (got.float().cpu() - ref_local.float()).abs().max().item()
+    assert local_seq_lens(seq_lens, world, rank).tolist() == [(int(n) - rank + world - 1) // world for n in seq_lens]
+    g.barrier()
+    json.dump({"max_err": err}, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if device_kind == "cuda":
+        state.finish_process()
+    state.destroy_distributed()
+
+
+TASKS = {"dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

@@ -62,6 +62,13 @@ def test_sequence_parallel_residual_stream_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
+def test_decode_context_parallel_mla_two_ranks_gloo():
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("dcp_mla", 2, d)
+    for r in res:
+        assert r["max_err"] < 1e-4, r
+
+
 def test_expert_parallel_moe_two_ranks_gloo():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("ep_moe", 2, d)
