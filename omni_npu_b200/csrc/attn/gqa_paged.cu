@@ -20,6 +20,7 @@
 #include <cstdlib>
 
 #include "attn_common.cuh"
+#include "../common/pdl.cuh"
 #include "../common/tensormap.h"
 
 namespace b200 {
@@ -610,6 +611,8 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
   int* s_abort = reinterpret_cast<int*>(empty_bar + Cfg::STAGES);
 
+  pdl_trigger();
+  pdl_wait();   // sequence lengths, block tables, q and the cache rows of this step come from earlier kernels
   const int b = blockIdx.x;
   const int kvh = blockIdx.y;
   const int split = blockIdx.z;
@@ -966,8 +969,8 @@ static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream
   r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.v_cache, rows, D, D, box_rows, 64,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 3000;
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tk, tv, p, box_rows);
-  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (launch_pdl(kern, grid, dim3(Cfg::THREADS), Cfg::SMEM, stream, 1, tk, tv, p, box_rows) != cudaSuccess)
+    return -21;
   if (p.splits > 1) {
     const long long warps = static_cast<long long>(grid.x) * p.Hk * (p.Hq / p.Hk) * p.q_len;
     gqa_decode_merge_kernel<D><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(p, static_cast<int>(grid.x));

@@ -39,6 +39,11 @@ int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, i
                          long long x_stride, int ue8m0, cudaStream_t stream);
 int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long rows, int H,
                               long long x_stride, cudaStream_t stream);
+int b200_rmsnorm_quant(void* q, void* scales, void* out, const void* x, void* residual, const void* w, float eps,
+                       long long rows, int H, long long x_stride, long long out_stride, long long res_stride,
+                       int kind, cudaStream_t stream);
+int b200_silu_mul_quant(void* q, void* scales, const void* x, long long rows, int I, long long x_stride, int kind,
+                        cudaStream_t stream);
 int b200_gemm_scaled(const void* A, const void* W, void* C, const float* a_scales, const float* w_scales,
                      const void* bias, const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
                      int kind, int out_fp32, int BN, int* status, int max_ctas, cudaStream_t stream);
@@ -336,6 +341,48 @@ std::tuple<Tensor, Tensor> quant_int8_per_token(const Tensor& x) {
   check(b200_quant_int8_per_token(q.data_ptr(), s.data_ptr(), x.data_ptr(), x.size(0), (int)x.size(1),
                                   x.stride(0), cur_stream()),
         "quant_int8_per_token");
+  return {q, s};
+}
+
+// RMSNorm (+ residual add, in place on `residual`) fused with per-token quantisation.
+// kind 1: e4m3, 2: int8.  Returns (q [T,H], scale [T], normalised bf16 row or empty).
+std::tuple<Tensor, Tensor, Tensor> rms_norm_quant(const Tensor& x, const c10::optional<Tensor>& residual,
+                                                  const Tensor& w, double eps, int64_t kind, bool want_bf16) {
+  CHECK_CUDA_BF16(x);
+  CHECK_CUDA_BF16(w);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "rms_norm_quant: 2-D, last dim contiguous");
+  TORCH_CHECK(kind == 1 || kind == 2, "rms_norm_quant: kind 1 (e4m3) or 2 (int8)");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.size(0), H = x.size(1);
+  Tensor q = torch::empty({T, H}, x.options().dtype(kind == 1 ? at::kFloat8_e4m3fn : at::kChar));
+  Tensor s = torch::empty({T}, x.options().dtype(at::kFloat));
+  Tensor out = want_bf16 ? torch::empty({T, H}, x.options()) : Tensor();
+  void* res_p = nullptr;
+  long long res_stride = 0;
+  if (residual.has_value()) {
+    CHECK_CUDA_BF16((*residual));
+    TORCH_CHECK(residual->dim() == 2 && residual->stride(1) == 1 && residual->size(0) == T && residual->size(1) == H,
+                "rms_norm_quant: residual shape");
+    res_p = residual->data_ptr();
+    res_stride = residual->stride(0);
+  }
+  check(b200_rmsnorm_quant(q.data_ptr(), s.data_ptr(), want_bf16 ? out.data_ptr() : nullptr, x.data_ptr(), res_p,
+                           w.data_ptr(), (float)eps, T, (int)H, x.stride(0), H, res_stride, (int)kind, cur_stream()),
+        "rms_norm_quant");
+  return {q, s, out};
+}
+
+// silu(x[:, :I]) * x[:, I:] fused with per-token quantisation (kind 1: e4m3, 2: int8).
+std::tuple<Tensor, Tensor> silu_and_mul_quant(const Tensor& x, int64_t kind) {
+  CHECK_CUDA_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 16 == 0, "silu_and_mul_quant: [T, 2I], I % 8 == 0");
+  TORCH_CHECK(kind == 1 || kind == 2, "silu_and_mul_quant: kind 1 (e4m3) or 2 (int8)");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.size(0), I = x.size(1) / 2;
+  Tensor q = torch::empty({T, I}, x.options().dtype(kind == 1 ? at::kFloat8_e4m3fn : at::kChar));
+  Tensor s = torch::empty({T}, x.options().dtype(at::kFloat));
+  check(b200_silu_mul_quant(q.data_ptr(), s.data_ptr(), x.data_ptr(), T, (int)I, x.stride(0), (int)kind, cur_stream()),
+        "silu_and_mul_quant");
   return {q, s};
 }
 
@@ -661,6 +708,8 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gemm_pair", &gemm_pair);
   m.def("gemm_scaled", &gemm_scaled);
   m.def("quant_int8_per_token", &quant_int8_per_token);
+  m.def("rms_norm_quant", &rms_norm_quant);
+  m.def("silu_and_mul_quant", &silu_and_mul_quant);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);
   m.def("fused_add_rms_norm", &fused_add_rms_norm);

@@ -26,6 +26,7 @@
 
 #include <cstdlib>
 
+#include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "../comm/ll_protocol.cuh"
@@ -182,6 +183,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   int total_mn_tiles;
   if constexpr (GROUPED) {
+    pdl_wait();      // the expert offsets are written by the routing kernel ahead of this one
     if (threadIdx.x == 32) {
       int acc = 0;
       for (int e = 0; e < p.num_experts; ++e) {
@@ -216,11 +218,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   volatile int* abort_flag = s_flags;
   const int groups = p.stages / p.ksub;   // barrier pairs in use
+  // Dependent launch: the next kernel of the stream may start its own prologue now.  This
+  // kernel's weights are written by no earlier kernel, so the producer thread of a dense
+  // problem streams the first ring of weight slabs before it waits for the kernels ahead;
+  // every other thread waits here, before it reads anything those kernels produced.
+  pdl_trigger();
+  const bool w_preload = !GROUPED && threadIdx.x == 0;
   uint32_t ar_epoch = 0;
   long long ar_slot_off = 0;
-  if (p.ar_world > 1) {
-    ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1;
-    ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
+  if (!w_preload) {
+    pdl_wait();
+    if (p.ar_world > 1) {
+      ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1;
+      ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
+    }
   }
 
   if (warp == 0) {
@@ -230,22 +241,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       int cursor = 0;
       long long issued = 0;
+      long long preloaded = 0;     // leading barrier groups whose weight slabs are already in flight
       bool ok = true;
       TileCoord tc;
+      if constexpr (!GROUPED) {
+        int c0 = 0;
+        if (decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t_first, cta_rank, c0, tc)) {
+          int g = 0;
+          for (int k = tc.k_begin; k < tc.k_end && g < groups; k += p.ksub, ++g) {
+            const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
+            mbar_arrive_expect_tx(&full_bar[g], static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
+            for (int j = 0; j < ns; ++j)
+              tma_load_2d(smem_w + (g * p.ksub + j) * w_stage_bytes, &tmap_w, &full_bar[g],
+                          (k + j) * (kRowBytes / p.elem_bytes), tc.n0);
+          }
+          preloaded = g;
+        }
+        pdl_wait();
+        if (p.ar_world > 1) {
+          ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1;
+          ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
+        }
+      }
       for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
                                                                 cta_rank, cursor, tc);
            t += t_stride) {
         for (int k = tc.k_begin; k < tc.k_end; k += p.ksub) {
           // one barrier round trip covers up to ksub slabs (`stage` counts groups of slabs)
           const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
-            *abort_flag = 1;
-            ok = false;
-            break;
+          const bool w_in_flight = issued < preloaded;     // first ring of the first tile: only A is missing
+          if (!w_in_flight) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+              atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&full_bar[stage],
+                                  static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
           }
-          mbar_arrive_expect_tx(&full_bar[stage],
-                                static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
           for (int j = 0; j < ns; ++j) {
             const int slab = stage * p.ksub + j;
             const int kcoord = (k + j) * (kRowBytes / p.elem_bytes);
@@ -254,7 +288,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tma_load_3d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0,
                           tc.expert);
             } else {
-              tma_load_2d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0);
+              if (!w_in_flight)
+                tma_load_2d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0);
             }
           }
           ++issued;
@@ -923,23 +958,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams
     if (e != cudaSuccess) return -20;
     configured = true;
   }
-  if (p.cluster_split) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = p.splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tw, p) == cudaSuccess ? 0 : -22;
-  }
-  kern<<<grid, kThreads, smem, stream>>>(ta, tw, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  const int cluster_x = p.cluster_split ? p.splits : 1;
+  return launch_pdl(kern, dim3(grid, 1, 1), dim3(kThreads, 1, 1), smem, stream, cluster_x, ta, tw, p) == cudaSuccess
+             ? 0
+             : (p.cluster_split ? -22 : -21);
 }
 
 // How many clusters of `size` CTAs of this kernel can be resident at once.

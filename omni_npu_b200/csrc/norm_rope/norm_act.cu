@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../common/pdl.cuh"
+
 namespace b200 {
 
 static constexpr int kNormThreads = 256;
@@ -47,6 +49,8 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict_
                __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, float eps,
                int H, long long x_stride, long long out_stride, long long res_stride) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * x_stride;
   __nv_bfloat16* rr = ADD ? residual + row * res_stride : nullptr;
@@ -191,6 +195,155 @@ quant_fp8_1x128_kernel(uint8_t* __restrict__ q, float* __restrict__ scales,
   if (lane == 0) scales[row * groups + g] = scale;
 }
 
+// ------------------------------------------------- norm / activation fused with quantisation
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();                       // red may still be read by the reduction before this one
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+  return m;
+}
+
+// KIND 1: e4m3, scale = amax / 448;  KIND 2: int8, scale = amax / 127 (round to nearest even).
+template <int KIND>
+__device__ __forceinline__ uint8_t quant_one(float v, float inv) {
+  if constexpr (KIND == 1) {
+    const __nv_fp8_e4m3 f(v * inv);
+    return f.__x;
+  } else {
+    const float r = fminf(fmaxf(rintf(v * inv), -127.f), 127.f);
+    return static_cast<uint8_t>(static_cast<int8_t>(r));
+  }
+}
+
+// (x [+ residual]) -> RMSNorm -> per-token dynamic quantisation, one pass over the row: the row
+// lives in registers between the two block reductions (sum of squares, then max |y|).  The
+// normalised row is rounded to bf16 before it is quantised, as the unfused sequence would do.
+// One CTA per row; optional bf16 copy of the normalised row (for consumers that are not quantised).
+template <bool ADD, int KIND>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, __nv_bfloat16* __restrict__ out,
+                     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                     const __nv_bfloat16* __restrict__ w, float eps, int H, long long x_stride,
+                     long long out_stride, long long res_stride) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * x_stride;
+  __nv_bfloat16* rr = ADD ? residual + row * res_stride : nullptr;
+  const int nvec = H >> 3;
+  float vals[kMaxVecPerThread][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerThread; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      Vec8 a;
+      a.u = reinterpret_cast<const uint4*>(xr)[v];
+      if (ADD) {
+        Vec8 b, s;
+        b.u = reinterpret_cast<const uint4*>(rr)[v];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s.h[j] = __float2bfloat16(__bfloat162float(a.h[j]) + __bfloat162float(b.h[j]));
+          vals[i][j] = __bfloat162float(s.h[j]);
+        }
+        reinterpret_cast<uint4*>(rr)[v] = s.u;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = __bfloat162float(a.h[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float inv_rms = rsqrtf(tot / static_cast<float>(H) + eps);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerThread; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      Vec8 g, o;
+      g.u = reinterpret_cast<const uint4*>(w)[v];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o.h[j] = __float2bfloat16(vals[i][j] * inv_rms * __bfloat162float(g.h[j]));
+        vals[i][j] = __bfloat162float(o.h[j]);
+        amax = fmaxf(amax, fabsf(vals[i][j]));
+      }
+      if (out) reinterpret_cast<uint4*>(out + row * out_stride)[v] = o.u;
+    }
+  }
+  amax = block_max(amax, red);
+  const float scale = fmaxf(amax, 1e-10f) / (KIND == 1 ? 448.f : 127.f);
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) scales[row] = scale;
+  uint8_t* qr = q + row * static_cast<long long>(H);
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerThread; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= static_cast<uint32_t>(quant_one<KIND>(vals[i][j], inv)) << (8 * j);
+        hi |= static_cast<uint32_t>(quant_one<KIND>(vals[i][4 + j], inv)) << (8 * j);
+      }
+      reinterpret_cast<uint2*>(qr)[v] = make_uint2(lo, hi);
+    }
+  }
+}
+
+// silu(x[:, :I]) * x[:, I:] -> per-token dynamic quantisation.  One CTA per row, two sweeps over
+// the row (the second one hits L1/L2): max |y| first, then quantise.  y is rounded to bf16 first.
+template <int KIND>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(uint8_t* __restrict__ q, float* __restrict__ scales, const __nv_bfloat16* __restrict__ x,
+                      int I, long long x_stride) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const long long row = blockIdx.x;
+  const uint4* g4 = reinterpret_cast<const uint4*>(x + row * x_stride);
+  const uint4* u4 = reinterpret_cast<const uint4*>(x + row * x_stride + I);
+  const int nvec = I >> 3;
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    Vec8 g, u;
+    g.u = g4[v];
+    u.u = u4[v];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = __bfloat162float(g.h[j]);
+      const float y = __bfloat162float(__float2bfloat16((a / (1.f + __expf(-a))) * __bfloat162float(u.h[j])));
+      amax = fmaxf(amax, fabsf(y));
+    }
+  }
+  amax = block_max(amax, red);
+  const float scale = fmaxf(amax, 1e-10f) / (KIND == 1 ? 448.f : 127.f);
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) scales[row] = scale;
+  uint2* qr = reinterpret_cast<uint2*>(q + row * static_cast<long long>(I));
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    Vec8 g, u;
+    g.u = g4[v];
+    u.u = u4[v];
+    uint32_t w2[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = __bfloat162float(g.h[j]);
+      const float y = __bfloat162float(__float2bfloat16((a / (1.f + __expf(-a))) * __bfloat162float(u.h[j])));
+      w2[j >> 2] |= static_cast<uint32_t>(quant_one<KIND>(y, inv)) << (8 * (j & 3));
+    }
+    qr[v] = make_uint2(w2[0], w2[1]);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -209,14 +362,15 @@ extern "C" int b200_rmsnorm(void* out, const void* x, void* residual, const void
   }
   if (H > kNormThreads * kMaxVecPerThread * 8) return -2;
   if (residual) {
-    rmsnorm_kernel<true><<<static_cast<unsigned>(rows), kNormThreads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x),
-        static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(w), eps, H,
-        x_stride, out_stride, res_stride);
+    launch_pdl(rmsnorm_kernel<true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, 1,
+               static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x),
+               static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(w), eps, H,
+               x_stride, out_stride, res_stride);
   } else {
-    rmsnorm_kernel<false><<<static_cast<unsigned>(rows), kNormThreads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x), nullptr,
-        static_cast<const __nv_bfloat16*>(w), eps, H, x_stride, out_stride, 0);
+    launch_pdl(rmsnorm_kernel<false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, 1,
+               static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x),
+               static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(w), eps, H, x_stride,
+               out_stride, 0LL);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -285,4 +439,47 @@ extern "C" int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long l
                                                      static_cast<const __nv_bfloat16*>(x), rows, H,
                                                      x_stride, ue8m0);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// RMSNorm (optionally with residual add, written back to `residual`) fused with per-token
+// quantisation.  kind 1: e4m3 (scale = amax/448), 2: int8 (scale = amax/127).  out may be null.
+extern "C" int b200_rmsnorm_quant(void* q, void* scales, void* out, const void* x, void* residual, const void* w,
+                                  float eps, long long rows, int H, long long x_stride, long long out_stride,
+                                  long long res_stride, int kind, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) != 0 || (kind != 1 && kind != 2)) return -1;
+  if (H > kNormThreads * kMaxVecPerThread * 8) return -2;
+  const dim3 grid(static_cast<unsigned>(rows)), block(kNormThreads);
+  auto* qq = static_cast<uint8_t*>(q);
+  auto* sc = static_cast<float*>(scales);
+  auto* o = static_cast<__nv_bfloat16*>(out);
+  auto* xx = static_cast<const __nv_bfloat16*>(x);
+  auto* rr = static_cast<__nv_bfloat16*>(residual);
+  auto* ww = static_cast<const __nv_bfloat16*>(w);
+  cudaError_t e;
+  if (residual) {
+    e = kind == 1 ? launch_pdl(rmsnorm_quant_kernel<true, 1>, grid, block, 0, stream, 1, qq, sc, o, xx, rr, ww, eps, H,
+                               x_stride, out_stride, res_stride)
+                  : launch_pdl(rmsnorm_quant_kernel<true, 2>, grid, block, 0, stream, 1, qq, sc, o, xx, rr, ww, eps, H,
+                               x_stride, out_stride, res_stride);
+  } else {
+    e = kind == 1 ? launch_pdl(rmsnorm_quant_kernel<false, 1>, grid, block, 0, stream, 1, qq, sc, o, xx, rr, ww, eps,
+                               H, x_stride, out_stride, res_stride)
+                  : launch_pdl(rmsnorm_quant_kernel<false, 2>, grid, block, 0, stream, 1, qq, sc, o, xx, rr, ww, eps,
+                               H, x_stride, out_stride, res_stride);
+  }
+  return e == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_silu_mul_quant(void* q, void* scales, const void* x, long long rows, int I, long long x_stride,
+                                   int kind, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((I & 7) != 0 || (kind != 1 && kind != 2)) return -1;
+  const dim3 grid(static_cast<unsigned>(rows)), block(256);
+  auto* qq = static_cast<uint8_t*>(q);
+  auto* sc = static_cast<float*>(scales);
+  auto* xx = static_cast<const __nv_bfloat16*>(x);
+  const cudaError_t e = kind == 1 ? launch_pdl(silu_mul_quant_kernel<1>, grid, block, 0, stream, 1, qq, sc, xx, I, x_stride)
+                                  : launch_pdl(silu_mul_quant_kernel<2>, grid, block, 0, stream, 1, qq, sc, xx, I, x_stride);
+  return e == cudaSuccess ? 0 : -3;
 }

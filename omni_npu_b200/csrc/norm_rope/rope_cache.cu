@@ -21,6 +21,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../common/pdl.cuh"
+
 namespace b200 {
 
 __device__ __forceinline__ void rotate_pair(__nv_bfloat16* base, int i0, int i1, float c, float s) {
@@ -78,6 +80,8 @@ rope_cache_gqa_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
                       const int* __restrict__ slot_mapping, const float* __restrict__ cos_sin,
                       int Hq, int Hk, int D, int rot_dim, int neox, long long q_stride,
                       long long k_stride, long long v_stride, int block_size) {
+  b200::pdl_trigger();
+  b200::pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = slot_mapping[t];
@@ -265,11 +269,11 @@ extern "C" int b200_rope_cache_gqa(void* q, const void* k, const void* v, void* 
                                    long long v_stride, int block_size, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((D & 7) != 0 || (rot_dim & 1) != 0 || rot_dim > D) return -1;
-  rope_cache_gqa_kernel<<<T, 256, 0, stream>>>(
-      static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
-      static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(k_cache),
-      static_cast<__nv_bfloat16*>(v_cache), positions, slot_mapping, cos_sin, Hq, Hk, D, rot_dim,
-      neox, q_stride, k_stride, v_stride, block_size);
+  b200::launch_pdl(rope_cache_gqa_kernel, dim3(T), dim3(256), 0, stream, 1,
+                   static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                   static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(k_cache),
+                   static_cast<__nv_bfloat16*>(v_cache), positions, slot_mapping, cos_sin, Hq, Hk, D, rot_dim,
+                   neox, q_stride, k_stride, v_stride, block_size);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

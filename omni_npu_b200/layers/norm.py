@@ -37,6 +37,15 @@ class RMSNorm(nn.Module):
             y = pstate.get_tp_group().all_gather(y, dim=0)
         return y, residual
 
+    def forward_quant(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, kind: str = "int8",
+                      want_bf16: bool = False):
+        """Norm fused with the per-token activation quantisation of the W8A8 linear that follows:
+        returns ``((q, scale), residual, bf16 row or None)``; the pair is accepted by the quantised
+        linear methods in place of a bf16 activation (the reference fuses the same pair of ops,
+        omni_npu/v1/layers/layernorm.py and npu_compressed_tensors_linear.py:149-231)."""
+        q, s, y = ops.rms_norm_quant(x, self.weight, self.eps, residual, kind, want_bf16)
+        return (q, s), residual, y
+
 
 def reduce_add_rms_norm(norm: RMSNorm, x_partial: torch.Tensor, residual: torch.Tensor, group):
     """``residual += all_reduce(x_partial)``; returns (RMSNorm(residual), residual).

@@ -44,6 +44,10 @@ def quantize_weight_per_channel(w: torch.Tensor):
 
 def int8_linear(x: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    if isinstance(x, tuple):
+        # already quantised by the producing kernel (norm + quant, SwiGLU + quant): (q [T,K], scale [T])
+        xq, xs = x
+        return ops.gemm_scaled(xq, w_q, xs, w_scale, bias, residual, out_dtype or torch.bfloat16)
     shape = x.shape
     x2 = x.reshape(-1, shape[-1])
     xq, xs = ops.quant_int8_per_token(x2)

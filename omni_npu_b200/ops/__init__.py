@@ -203,6 +203,26 @@ def quant_int8_per_token(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return _C().quant_int8_per_token(x)
 
 
+def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
+                   kind: str = "int8", want_bf16: bool = False):
+    """RMSNorm of ``x`` (or of ``x + residual``, which is written back to ``residual``) fused with
+    per-token dynamic quantisation to int8 (scale = amax/127) or e4m3 (scale = amax/448).
+    Returns (q [T,H], scale fp32 [T], normalised bf16 [T,H] or None)."""
+    if not x.is_cuda:
+        return ref.rms_norm_quant(x, weight, eps, residual, kind, want_bf16)
+    _count(1)
+    q, s, out = _C().rms_norm_quant(x, residual, weight, eps, 1 if kind == "fp8" else 2, want_bf16)
+    return q, s, (out if want_bf16 else None)
+
+
+def silu_and_mul_quant(x: torch.Tensor, kind: str = "int8") -> Tuple[torch.Tensor, torch.Tensor]:
+    """``silu(x[:, :I]) * x[:, I:]`` fused with per-token dynamic quantisation: (q [T,I], scale [T])."""
+    if not x.is_cuda:
+        return ref.silu_and_mul_quant(x, kind)
+    _count(1)
+    return _C().silu_and_mul_quant(x, 1 if kind == "fp8" else 2)
+
+
 def gemm_scaled(a_q: torch.Tensor, w_q: torch.Tensor, a_scale: torch.Tensor, w_scale: torch.Tensor,
                 bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:

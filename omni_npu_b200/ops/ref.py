@@ -418,3 +418,33 @@ def gather_cache(cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torc
         rows = block_tables[b][pos // bs].long() * bs + pos % bs
         parts.append(cache.reshape(-1, *cache.shape[2:])[rows])
     return torch.cat(parts) if parts else cache.new_zeros(0, *cache.shape[2:])
+
+
+def quant_per_token(y: torch.Tensor, kind: str):
+    """Per-row symmetric dynamic quantisation: int8 (amax/127, round to nearest even) or e4m3 (amax/448)."""
+    yf = y.float()
+    amax = yf.abs().amax(dim=-1).clamp_min(1e-10)
+    if kind == "fp8":
+        scale = amax / 448.0
+        q = (yf / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    else:
+        scale = amax / 127.0
+        q = torch.round(yf * (1.0 / scale).unsqueeze(-1)).clamp_(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def rms_norm_quant(x, weight, eps, residual=None, kind="int8", want_bf16=False):
+    if residual is not None:
+        s = (x.float() + residual.float()).to(x.dtype)
+        residual.copy_(s)
+        x = s
+    xf = x.float()
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+    q, scale = quant_per_token(y, kind)
+    return q, scale, (y if want_bf16 else None)
+
+
+def silu_and_mul_quant(x, kind="int8"):
+    i = x.shape[-1] // 2
+    y = (torch.nn.functional.silu(x[..., :i].float()) * x[..., i:].float()).to(x.dtype)
+    return quant_per_token(y, kind)

@@ -5,6 +5,7 @@ import torch
 from omni_npu_b200.layers.linear import ColumnParallelLinear
 from omni_npu_b200.layers.quant_int8 import (CompressedTensorsConfig, QUANT_NAME, W8A8Int8LinearMethod,
                                              int8_linear, quantize_weight_per_channel)
+from omni_npu_b200 import ops
 from omni_npu_b200.ops import ref
 from omni_npu_b200.parallel import state
 
@@ -65,3 +66,23 @@ def test_linear_layer_with_int8_method():
     y = lin(x).float()
     want = x @ w.t() + lin.bias
     assert (y - want).abs().max() < 0.05 * want.abs().max()
+
+
+def test_norm_quant_pair_feeds_int8_linear():
+    """RMSNorm fused with activation quantisation hands (q, scale) straight to the W8A8 product;
+    the result equals norm -> quantise -> product done separately."""
+    from omni_npu_b200.layers.norm import RMSNorm
+    from omni_npu_b200.layers.quant_int8 import int8_linear, quantize_weight_per_channel
+    torch.manual_seed(0)
+    x, res = torch.randn(6, 64), torch.randn(6, 64)
+    norm = RMSNorm(64, 1e-6, torch.float32)
+    norm.weight.data = torch.rand(64) + 0.5
+    wq, ws = quantize_weight_per_channel(torch.randn(32, 64))
+    res2 = res.clone()
+    pair, r_out, y = norm.forward_quant(x, res, "int8", want_bf16=True)
+    y_ref, r_ref = norm(x, res2)
+    assert torch.allclose(r_out, r_ref) and torch.allclose(y, y_ref, atol=1e-6)
+    assert torch.allclose(int8_linear(pair, wq, ws, out_dtype=torch.float32),
+                          int8_linear(y_ref, wq, ws, out_dtype=torch.float32), atol=1e-5)
+    q, s = ops.silu_and_mul_quant(torch.randn(4, 32), "int8")
+    assert q.dtype == torch.int8 and q.shape == (4, 16) and s.shape == (4,)

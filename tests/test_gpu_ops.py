@@ -487,9 +487,11 @@ def test_mla_decode(n_heads, splits, q_len):
     cache = torch.randn(nblocks, bs, 576).bfloat16()
     q = (torch.randn(b * q_len, n_heads * 576) * 0.3).bfloat16()
     sl = torch.tensor(seq_lens, dtype=torch.int32)
-    want = ref.mla_decode(q, cache, bt, sl, b, q_len, n_heads, 0.07)
-    got = ops.mla_decode(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), b, n_heads, 0.07, q_len, splits=splits)
+    want, want_lse = ref.mla_decode(q, cache, bt, sl, b, q_len, n_heads, 0.07, None, True)
+    got, lse = ops.mla_decode(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), b, n_heads, 0.07, q_len,
+                              splits=splits, return_lse=True)
     _close(got, want, 2e-2, 2e-2)
+    _close(lse, want_lse, 2e-2, 2e-2)
 
 
 def test_mla_decode_sparse_selection():
@@ -509,3 +511,38 @@ def test_mla_decode_sparse_selection():
     want = ref.mla_decode(q, cache, bt, sl, b, 1, n_heads, 0.07, sel)
     got = ops.mla_decode(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), b, n_heads, 0.07, 1, sel.to(DEV), splits=2)
     _close(got, want, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("kind", ["int8", "fp8"])
+@pytest.mark.parametrize("add", [False, True])
+def test_rms_norm_quant_fused(kind, add):
+    torch.manual_seed(11)
+    t, h = 37, 4096
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w = (torch.rand(h, device=DEV) + 0.5).bfloat16()
+    res = torch.randn(t, h, device=DEV, dtype=torch.bfloat16) if add else None
+    res_ref = res.cpu().clone() if add else None
+    q, s, y = ops.rms_norm_quant(x, w, 1e-6, res, kind, want_bf16=True)
+    q0, s0, y0 = ref.rms_norm_quant(x.cpu(), w.cpu(), 1e-6, res_ref, kind, True)
+    if add:
+        _close(res, res_ref, 1e-2, 1e-2)
+    _close(y, y0, 2e-2, 2e-2)
+    _close(s, s0, 1e-6, 2e-2)
+    # the quantised row must reproduce the normalised row to within one quantisation step
+    deq = q.float().cpu() * s.cpu().unsqueeze(-1)
+    step = s.cpu().unsqueeze(-1) * (1.0 if kind == "int8" else 32.0)
+    assert ((deq - y.float().cpu()).abs() <= step + 1e-3).all()
+
+
+@pytest.mark.parametrize("kind", ["int8", "fp8"])
+def test_silu_and_mul_quant_fused(kind):
+    torch.manual_seed(12)
+    t, i = 19, 14336
+    x = torch.randn(t, 2 * i, device=DEV, dtype=torch.bfloat16)
+    q, s = ops.silu_and_mul_quant(x, kind)
+    q0, s0 = ref.silu_and_mul_quant(x.cpu(), kind)
+    _close(s, s0, 1e-6, 2e-2)
+    y = ops.silu_and_mul(x).float().cpu()
+    deq = q.float().cpu() * s.cpu().unsqueeze(-1)
+    step = s.cpu().unsqueeze(-1) * (1.0 if kind == "int8" else 32.0)
+    assert ((deq - y).abs() <= step + 1e-3).all()
