@@ -92,36 +92,21 @@ class Indexer(nn.Module):
         return self._topk(q, w, md, index_cache)
 
     def _topk(self, q, w, md: AttentionMetadata, index_cache) -> torch.Tensor:
+        """Scores on the tensor cores and a radix select per query token (one score kernel and one
+        select kernel for the whole batch, no host synchronisation, so the step stays graph
+        capturable).  Index shapes the kernel does not cover (head dim != 128, heads not a
+        multiple of 16, pages that do not tile 128 keys) take the dense torch path."""
         bs = index_cache.shape[1]
-        t = q.shape[0]
-        out = torch.full((t, self.topk), -1, dtype=torch.int32, device=q.device)
-        flat = index_cache.view(-1, index_cache.shape[-1])
+        kernel_ok = (not q.is_cuda) or (self.head_dim == 128 and self.n_heads % 16 == 0 and self.n_heads <= 256 and
+                                        bs % 8 == 0 and (bs % 128 == 0 if bs >= 128 else 128 % bs == 0))
+        fn = ops.dsa_indexer_topk if kernel_ok else (
+            lambda *a, max_ctx=0, max_q=0, **k: ops.ref.dsa_indexer_topk(*a, **k))
         if md.is_prefill:
-            cu = md.cu_q[: md.num_seqs + 1].tolist()
-            lens = md.seq_lens[: md.num_seqs].tolist()
-        else:
-            cu = [i * md.q_len for i in range(md.num_seqs + 1)]
-            lens = None
-        for b in range(md.num_seqs):
-            qs, qe = cu[b], cu[b + 1]
-            if qe <= qs:
-                continue
-            if lens is not None:
-                n = lens[b]
-                pos = torch.arange(n, device=q.device)
-                rows = md.block_tables[b][pos // bs].long() * bs + pos % bs
-                keys = flat[rows]
-                q_pos = md.positions[qs:qe].long()
-            else:
-                # decode under a CUDA graph: fixed-size window over the whole block table,
-                # keys beyond the sequence are masked by position
-                n = md.block_tables.shape[1] * bs
-                pos = torch.arange(n, device=q.device)
-                rows = md.block_tables[b][pos // bs].long() * bs + pos % bs
-                keys = flat[rows]
-                q_pos = md.positions[qs:qe].long()
-            out[qs:qe] = indexer_topk_reference(q[qs:qe], w[qs:qe], keys, q_pos, self.topk)
-        return out
+            return fn(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk, cu_q=md.cu_q,
+                      max_ctx=int(md.max_seq_len or 0), max_q=int(md.max_q_len or 0))
+        q_len = max(1, md.q_len)
+        return fn(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk, q_len=q_len,
+                  max_ctx=int(md.max_seq_len or 0), max_q=q_len)
 
 
 class SparseMLAAttention(MLAAttention):

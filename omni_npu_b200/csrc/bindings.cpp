@@ -39,6 +39,10 @@ int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, i
                          long long x_stride, int ue8m0, cudaStream_t stream);
 int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long rows, int H,
                               long long x_stride, cudaStream_t stream);
+int b200_dsa_indexer(const void* q, const float* w, const void* cache, const int* block_tables, const int* cu_q,
+                     const int* positions, float* scores, int* topk_out, int T, int B, int H, int q_len,
+                     long long num_blocks, int block_size, int max_blocks, long long ld, int max_ctx, int max_q,
+                     int topk, int* status, cudaStream_t stream);
 int b200_rmsnorm_quant(void* q, void* scales, void* out, const void* x, void* residual, const void* w, float eps,
                        long long rows, int H, long long x_stride, long long out_stride, long long res_stride,
                        int kind, cudaStream_t stream);
@@ -342,6 +346,45 @@ std::tuple<Tensor, Tensor> quant_int8_per_token(const Tensor& x) {
                                   x.stride(0), cur_stream()),
         "quant_int8_per_token");
   return {q, s};
+}
+
+// Sparse-attention indexer: scores on the tensor cores + radix select of the topk best key
+// positions per query token.  q [T,H,128] bf16, w [T,H] fp32, cache [blocks, block_size, 128]
+// bf16, cu_q [B+1] int32 or none (then q_len tokens per sequence), positions [T] int32.
+// Returns (topk indices int32 [T, topk], scores fp32 [T, ld]); entries of `scores` beyond a
+// token's position are not defined.
+std::tuple<Tensor, Tensor> dsa_indexer(const Tensor& q, const Tensor& w, const Tensor& cache,
+                                       const Tensor& block_tables, const c10::optional<Tensor>& cu_q,
+                                       const Tensor& positions, int64_t num_seqs, int64_t q_len, int64_t max_ctx,
+                                       int64_t max_q, int64_t topk, const Tensor& status) {
+  CHECK_CUDA_BF16(q);
+  CHECK_CUDA_BF16(cache);
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous(), "dsa_indexer: q [T, H, 128] contiguous");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.is_contiguous() && w.dim() == 2 &&
+                  w.size(0) == q.size(0) && w.size(1) == q.size(1), "dsa_indexer: w fp32 [T, H]");
+  TORCH_CHECK(cache.dim() == 3 && cache.size(2) == 128 && cache.is_contiguous(), "dsa_indexer: cache [blocks, bs, 128]");
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous(),
+              "dsa_indexer: block_tables int32 [B, max_blocks]");
+  TORCH_CHECK(positions.scalar_type() == at::kInt && positions.is_contiguous() && positions.numel() >= q.size(0),
+              "dsa_indexer: positions int32 [T]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t T = q.size(0), H = q.size(1);
+  const int64_t ld = ((std::max<int64_t>(max_ctx, 1) + 127) / 128) * 128;
+  Tensor scores = torch::empty({T, ld}, q.options().dtype(at::kFloat));
+  Tensor sel = torch::empty({T, topk}, q.options().dtype(at::kInt));
+  const int* cu = nullptr;
+  if (cu_q.has_value()) {
+    TORCH_CHECK(cu_q->scalar_type() == at::kInt && cu_q->is_contiguous() && cu_q->numel() >= num_seqs + 1,
+                "dsa_indexer: cu_q int32 [B + 1]");
+    cu = cu_q->data_ptr<int>();
+  }
+  check(b200_dsa_indexer(q.data_ptr(), w.data_ptr<float>(), cache.data_ptr(), block_tables.data_ptr<int>(), cu,
+                         positions.data_ptr<int>(), scores.data_ptr<float>(), sel.data_ptr<int>(), (int)T,
+                         (int)num_seqs, (int)H, (int)q_len, cache.size(0), (int)cache.size(1),
+                         (int)block_tables.size(1), ld, (int)max_ctx, (int)max_q, (int)topk, status.data_ptr<int>(),
+                         cur_stream()),
+        "dsa_indexer");
+  return {sel, scores};
 }
 
 // RMSNorm (+ residual add, in place on `residual`) fused with per-token quantisation.
@@ -709,6 +752,7 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gemm_scaled", &gemm_scaled);
   m.def("quant_int8_per_token", &quant_int8_per_token);
   m.def("rms_norm_quant", &rms_norm_quant);
+  m.def("dsa_indexer", &dsa_indexer);
   m.def("silu_and_mul_quant", &silu_and_mul_quant);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);

@@ -46,7 +46,9 @@ struct SymmGroup {
 // Layout of a signal pad (uint32 words):
 //   [0, kMaxRanks*kMaxCommBlocks)        flags[src_rank][block]
 //   [kMaxRanks*kMaxCommBlocks]           epoch counter (local use only)
+//   [kAgFlagWord, kAgFlagWord + kMaxRanks)  "rank r has staged its block" flags of the fused all-gather GEMM
 static constexpr int kEpochWord = kMaxRanks * kMaxCommBlocks;
+static constexpr int kAgFlagWord = kEpochWord + 4;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -325,6 +327,29 @@ allgather_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ 
   }
 }
 
+// ------------------------------------------- staging for the fused all-gather GEMM
+// Copies this rank's block into its staging half of the next epoch; the last block to finish
+// tells every rank (flag word kAgFlagWord + rank of their signal pads) and advances the epoch.
+// No waiting here: the GEMM that follows waits per source block, right before it first needs it.
+__global__ void __launch_bounds__(512)
+ag_stage_kernel(SymmGroup g, const uint4* __restrict__ in, long long n_vec, uint32_t* done_counter) {
+  const uint32_t epoch = read_epoch(g) + 1;
+  uint4* stage = reinterpret_cast<uint4*>(static_cast<char*>(g.data[g.rank]) + (epoch & 1) * g.half_bytes);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    stage[i] = in[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < g.world; ++r) st_release_sys(g.signal[r] + kAgFlagWord + g.rank, epoch);
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = epoch;
+    }
+  }
+}
+
 // ---------------------------------------------------------- reduce-scatter
 // in [world * n_vec]; out [n_vec] = sum over ranks of their chunk `rank`.
 __global__ void __launch_bounds__(512)
@@ -545,7 +570,9 @@ extern "C" int b200_symm_close(void* ptr) {
 
 extern "C" int b200_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
 
-extern "C" int b200_symm_signal_words() { return kEpochWord + 4; }
+extern "C" int b200_symm_signal_words() { return kAgFlagWord + kMaxRanks + 4; }
+extern "C" int b200_symm_epoch_word() { return kEpochWord; }
+extern "C" int b200_symm_ag_flag_word() { return kAgFlagWord; }
 
 static SymmGroup make_group(void* const* data, void* const* signal, int world, int rank,
                             size_t half_bytes) {
@@ -613,6 +640,17 @@ extern "C" int b200_symm_all_gather(void* const* data, void* const* signal, int 
   allgather_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
       g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
       static_cast<uint32_t*>(done_counter), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int b200_symm_ag_stage(void* const* data, void* const* signal, int world, int rank, size_t half_bytes,
+                                  const void* in, long long n_elems, void* done_counter, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || (n_elems & 7) != 0) return -1;
+  if (static_cast<size_t>(n_elems) * 2 > half_bytes) return -4;
+  const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
+  const long long n_vec = n_elems >> 3;
+  ag_stage_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(g, static_cast<const uint4*>(in), n_vec,
+                                                                          static_cast<uint32_t*>(done_counter));
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -73,6 +73,15 @@ struct GemmParams {
   const __nv_bfloat16* ar_norm_w;  // [N] RMSNorm weight, or null: C = all-reduced sum (+residual)
   float ar_eps;
   uint32_t* ar_done;               // zero-initialised device counter
+  // ---- fused all-gather of A (ag_world > 1): A is the row-wise concatenation of every rank's
+  // staged block of ag_rows rows.  The producer reads each block straight from its owner's
+  // memory with (plain, non-multicast) TMA, own block first, and waits (bounded) for the
+  // owner's "staged" flag before the first tile of a foreign block.
+  const CUtensorMap* ag_maps;      // [2 halves][ag_world] tensor maps over the staging buffers (global memory)
+  const uint32_t* ag_signal;       // this rank's signal pad: word ag_epoch_word = epoch, ag_flag_word + r = rank r staged
+  int ag_world, ag_rank;
+  int ag_rows;                     // rows per rank, a multiple of 128
+  int ag_epoch_word, ag_flag_word;
 };
 
 struct TileCoord {
@@ -84,6 +93,8 @@ struct TileCoord {
   int k_end;     // one past last k iteration
   int split;     // split index
   int mn_index;  // index of the (m,n) tile for split-K bookkeeping
+  int a_src;     // fused all-gather: rank whose staging buffer holds the A rows (-1: plain A)
+  int a_row0;    // fused all-gather: first row inside that buffer
 };
 
 template <bool GROUPED>
@@ -107,9 +118,24 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const int* s_ti
   const int per = (p.k_iters + p.splits - 1) / p.splits;
   tc.k_begin = split * per;
   tc.k_end = min(p.k_iters, tc.k_begin + per);
+  tc.a_src = -1;
+  tc.a_row0 = 0;
   if constexpr (!GROUPED) {
-    const int mb = mn % p.num_m_blocks;
-    const int nb = mn / p.num_m_blocks;
+    int mb = mn % p.num_m_blocks;
+    int nb = mn / p.num_m_blocks;
+    if (p.ag_world > 1) {
+      // walk the row blocks rank by rank, own rows first: all (m, n) tiles of one rank's block
+      // before the next rank's, so remote rows are first needed 1/world of the way in
+      const int chunk = p.ag_rows / kBM;
+      const int per_chunk = chunk * p.num_n_blocks;
+      const int c = mn / per_chunk, rem = mn - c * per_chunk;
+      const int src = (p.ag_rank + c) % p.ag_world;
+      nb = rem / chunk;
+      const int mb_in = rem - nb * chunk;
+      mb = src * chunk + mb_in;
+      tc.a_src = src;
+      tc.a_row0 = mb_in * kBM;
+    }
     tc.m0 = mb * kBM;
     tc.m_end = min(p.M, tc.m0 + kBM);
     tc.n0 = nb * p.BN;
@@ -263,9 +289,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
         }
       }
+      uint32_t ag_epoch = 0, ag_ready = 0;
+      const CUtensorMap* ag_maps = nullptr;
+      if (p.ag_world > 1) {
+        ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_signal + p.ag_epoch_word);
+        ag_maps = p.ag_maps + (ag_epoch & 1u) * p.ag_world;
+        ag_ready = 1u << p.ag_rank;
+      }
       for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
                                                                 cta_rank, cursor, tc);
            t += t_stride) {
+        const CUtensorMap* map_a = &tmap_a;
+        int a_row = tc.m0;
+        if (tc.a_src >= 0) {
+          if (!((ag_ready >> tc.a_src) & 1u)) {
+            // first tile of a foreign block: its owner must have finished staging (flags only grow)
+            const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + tc.a_src;
+            uint32_t polls = 0;
+            while (static_cast<int32_t>(*flag - ag_epoch) < 0) {
+              if (++polls > (1u << 24)) {
+                ok = false;
+                break;
+              }
+              __nanosleep(64);
+            }
+            if (!ok) {
+              atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+              *abort_flag = 1;
+              break;
+            }
+            __threadfence_system();
+            fence_proxy_async();
+            ag_ready |= 1u << tc.a_src;
+          }
+          map_a = ag_maps + tc.a_src;
+          a_row = tc.a_row0;
+        }
         for (int k = tc.k_begin; k < tc.k_end; k += p.ksub) {
           // one barrier round trip covers up to ksub slabs (`stage` counts groups of slabs)
           const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
@@ -283,7 +342,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < ns; ++j) {
             const int slab = stage * p.ksub + j;
             const int kcoord = (k + j) * (kRowBytes / p.elem_bytes);
-            tma_load_2d(smem_a + slab * a_stage_bytes, &tmap_a, &full_bar[stage], kcoord, tc.m0);
+            tma_load_2d(smem_a + slab * a_stage_bytes, map_a, &full_bar[stage], kcoord, a_row);
             if constexpr (GROUPED) {
               tma_load_3d(smem_w + slab * w_stage_bytes, &tmap_w, &full_bar[stage], kcoord, tc.n0,
                           tc.expert);
@@ -302,6 +361,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) {
         // Abort path: wait (bounded) until the loads already issued have landed
         // so that no bulk copy writes into shared memory after the CTA retires.
+        if (issued < preloaded)      // weight slabs in flight whose barrier will never complete: let them land
+          for (int i = 0; i < 1000; ++i) __nanosleep(1000);
         const int pending = issued < groups ? static_cast<int>(issued) : groups;
         int s = stage;
         uint32_t ph = phase;
@@ -1078,7 +1139,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar = nullptr);
+                     const ArArgs* ar = nullptr, const struct AgArgs* ag = nullptr);
 
 extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
                          const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
@@ -1101,6 +1162,13 @@ extern "C" int b200_gemm_scaled(const void* A, const void* W, void* C, const flo
                    nullptr, status, max_ctas, stream, a_scales, w_scales);
 }
 
+struct AgArgs {
+  const void* maps = nullptr;       // device: [2][world] CUtensorMap over the staging halves
+  const void* signal = nullptr;     // this rank's signal pad
+  int world = 0, rank = 0, rows = 0;
+  int epoch_word = 0, flag_word = 0;
+};
+
 struct ArArgs {
   void* const* recv = nullptr;
   int world = 0, rank = 0;
@@ -1115,7 +1183,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar);
+                     const ArArgs* ar, const struct AgArgs* ag);
 
 // Row-parallel projection of a tensor-parallel layer in ONE kernel: C = RMSNorm(residual +=
 // sum over ranks of (A @ W^T)) * norm_w  (norm_w null: C = sum (+ residual), residual untouched).
@@ -1148,14 +1216,57 @@ extern "C" int b200_gemm_all_reduce(const void* A, const void* W, void* C, const
     cluster = pl.cluster;
   }
   return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, N, 0, 0, 0, BN, splits, cluster, nullptr, nullptr,
-                   status, max_ctas, stream, nullptr, nullptr, &ar);
+                   status, max_ctas, stream, nullptr, nullptr, &ar, nullptr);
+}
+
+// Encodes the tensor maps of the fused all-gather GEMM into `out_host` (2 * world maps of 128
+// bytes: half 0 of every rank, then half 1).  data[r]: rank r's peer-mapped staging buffer of
+// 2 * half_bytes; rows_cap rows of K bf16 elements fit one half.
+extern "C" int b200_gemm_ag_encode_maps(void* out_host, void* const* data, int world, size_t half_bytes, int K) {
+  if (world < 2 || world > kMaxRanks || K <= 0 || (K % 8) != 0) return -1;
+  const uint64_t rows_cap = half_bytes / (static_cast<size_t>(K) * 2);
+  if (rows_cap < kBM) return -2;
+  CUtensorMap* out = static_cast<CUtensorMap*>(out_host);
+  for (int h = 0; h < 2; ++h)
+    for (int r = 0; r < world; ++r) {
+      const int rc = make_tensormap_2d(&out[h * world + r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                       static_cast<const char*>(data[r]) + h * half_bytes, rows_cap, K, K, kBM,
+                                       kRowBytes / 2, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc - 100;
+    }
+  return 0;
+}
+
+// Column-parallel projection of a sequence-sharded activation in ONE kernel:
+// C [world * rows, N] = concat_r(A_r) @ W^T, where A_r (rows x K, bf16) is the block rank r
+// staged in its symmetric buffer.  The producer warp reads every block from its owner with
+// TMA (own rows first), so the gather overlaps the tensor-core work tile by tile and the
+// gathered activation is never materialised.  swiglu: C [.., N/2] = silu(gate) * up with the
+// interleaved weight layout of the dense kernel.
+extern "C" int b200_gemm_all_gather(const void* maps_dev, const void* signal_local, const void* a_local,
+                                    const void* W, void* C, const void* bias, int rows, int N, int K, int ldw,
+                                    int ldc, int swiglu, int world, int rank, int epoch_word, int flag_word,
+                                    int* status, int max_ctas, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks) return -30;
+  AgArgs ag;
+  ag.maps = maps_dev;
+  ag.signal = signal_local;
+  ag.world = world;
+  ag.rank = rank;
+  ag.rows = rows;
+  ag.epoch_word = epoch_word;
+  ag.flag_word = flag_word;
+  const int M = rows * world;
+  GemmPlan pl = plan_gemm(M, N, K, 2, sm_count(), false, swiglu != 0);
+  return gemm_impl(a_local, W, C, bias, nullptr, M, N, K, K, ldw, ldc, 0, 0, swiglu, pl.BN, 1, 0, nullptr, nullptr,
+                   status, max_ctas, stream, nullptr, nullptr, nullptr, &ag);
 }
 
 static int gemm_impl(const void* A, const void* W, void* C, const void* bias, const void* residual, int M,
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar) {
+                     const ArArgs* ar, const AgArgs* ag) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
@@ -1203,10 +1314,22 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
     p.ar_eps = ar->eps;
     p.ar_done = static_cast<uint32_t*>(ar->done);
   }
+  if (ag != nullptr && ag->world > 1) {
+    if (splits != 1 || ag->rows <= 0 || (ag->rows % kBM) != 0 || ag->rows * ag->world != M) return -17;
+    p.ag_maps = static_cast<const CUtensorMap*>(ag->maps);
+    p.ag_signal = static_cast<const uint32_t*>(ag->signal);
+    p.ag_world = ag->world;
+    p.ag_rank = ag->rank;
+    p.ag_rows = ag->rows;
+    p.ag_epoch_word = ag->epoch_word;
+    p.ag_flag_word = ag->flag_word;
+  }
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kRowBytes / eb;
-  int r = make_tensormap_2d(&ta, dt, eb, A, M, K, lda, kBM, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
+  // with a gathered A the kernel addresses the per-rank maps; `ta` then only has to be valid
+  int r = make_tensormap_2d(&ta, dt, eb, A, p.ag_world > 1 ? p.ag_rows : M, K, lda, kBM, box_k,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   r = make_tensormap_2d(&tw, dt, eb, W, N, K, ldw, BN, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;

@@ -25,6 +25,30 @@ from typing import Optional, Tuple
 import torch
 
 
+class ShardedRows:
+    """A token-sharded activation on its way into a column-parallel projection.  The projection
+    either consumes the shard directly (all-gather fused into its GEMM over peer memory) or
+    asks for the gathered rows."""
+
+    def __init__(self, shard: torch.Tensor, stream: "SequenceParallelStream") -> None:
+        self.shard = shard
+        self.stream = stream
+        self._full: Optional[torch.Tensor] = None
+
+    @property
+    def num_tokens(self) -> int:
+        return self.stream.num_tokens
+
+    @property
+    def shape(self):
+        return (self.stream.num_tokens,) + tuple(self.shard.shape[1:])
+
+    def full(self) -> torch.Tensor:
+        if self._full is None:
+            self._full = self.stream.gather(self.shard)[: self.stream.num_tokens]
+        return self._full
+
+
 class SequenceParallelStream:
     def __init__(self, group) -> None:
         self.group = group
@@ -32,6 +56,7 @@ class SequenceParallelStream:
         self.rank = group.rank_in_group
         self.num_tokens = 0
         self.padded = 0
+        self.fused_gather = False     # True: blocks get ShardedRows; their first projection fuses the gather
 
     @property
     def enabled(self) -> bool:
@@ -79,5 +104,9 @@ class SequenceParallelStream:
             normed = norm(shard_residual)
         else:
             normed, shard_residual = norm(shard_hidden, shard_residual)
+        symm = getattr(self.group.comm, "symm", None)
+        if self.fused_gather and symm is not None and normed.is_cuda and normed.shape[0] % 128 == 0:
+            # the block's first projection reads the shards from their owners inside its GEMM
+            return self.reduce_scatter(fn(ShardedRows(normed, self))), shard_residual
         full = self.gather(normed)[: self.num_tokens]
         return self.reduce_scatter(fn(full)), shard_residual

@@ -44,6 +44,27 @@ def apply_transform(x: torch.Tensor, kind: Optional[str], group: GroupCoordinato
     raise ValueError(f"unknown transform {kind}")
 
 
+def _sharded_input(layer: "LinearBase", x, swiglu: bool = False, out_dtype=None):
+    """Input handed over as token shards (``layers.flashcomm.ShardedRows``): returns
+    (y, None) when the gather was fused into the GEMM, else (None, gathered rows)."""
+    y = gathered_gemm(layer, x.shard, swiglu, out_dtype)
+    if y is not None:
+        return y[: x.num_tokens], None
+    return None, x.full()
+
+
+def gathered_gemm(layer: "LinearBase", x: torch.Tensor, swiglu: bool = False,
+                  out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``all_gather(x) @ W^T`` as one kernel over peer memory when the layer is an unquantised bf16
+    projection and the group has symmetric memory (the all-gather feeding a column-parallel
+    projection of a sequence-sharded residual stream); None when the fused path does not apply."""
+    symm = getattr(layer.group.comm, "symm", None)
+    if (symm is None or not isinstance(layer.quant_method, UnquantizedLinearMethod) or x.dim() != 2
+            or out_dtype not in (None, torch.bfloat16) or not symm.can_all_gather_gemm(x, layer.weight)):
+        return None
+    return symm.all_gather_gemm(x, layer.weight, layer.bias, swiglu)
+
+
 # ------------------------------------------------------------------ methods
 class UnquantizedLinearMethod:
     def create_weights(self, layer: "LinearBase", in_features: int, out_features: int,
@@ -149,8 +170,14 @@ class ColumnParallelLinear(LinearBase):
         self._create(in_features, self.out_local, device)
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        x = apply_transform(x, self.x_transform, self.group)
-        y = self.quant_method.apply(self, x, self.bias, out_dtype=out_dtype)
+        y = None
+        if not isinstance(x, torch.Tensor):
+            y, x = _sharded_input(self, x, out_dtype=out_dtype)
+        elif self.x_transform == "AllGather" and self.tp_size > 1:
+            y = gathered_gemm(self, x, out_dtype=out_dtype)
+        if y is None:
+            x = apply_transform(x, self.x_transform, self.group)
+            y = self.quant_method.apply(self, x, self.bias, out_dtype=out_dtype)
         if self.gather_output and self.tp_size > 1:
             y = self.group.all_gather(y, dim=-1)
         return apply_transform(y, self.y_transform, self.group)
@@ -178,8 +205,17 @@ class MergedColumnParallelLinear(LinearBase):
         self._create(in_features, sum(self.local_sizes), device)
 
     def forward(self, x: torch.Tensor, fuse_swiglu: bool = False) -> torch.Tensor:
+        swiglu = fuse_swiglu and self.swiglu_interleave
+        if not isinstance(x, torch.Tensor):
+            y, x = _sharded_input(self, x, swiglu=swiglu)
+            if y is not None:
+                return y
+        elif self.x_transform == "AllGather" and self.tp_size > 1:
+            y = gathered_gemm(self, x, swiglu=swiglu)
+            if y is not None:
+                return y
         x = apply_transform(x, self.x_transform, self.group)
-        return self.quant_method.apply(self, x, self.bias, swiglu=fuse_swiglu and self.swiglu_interleave)
+        return self.quant_method.apply(self, x, self.bias, swiglu=swiglu)
 
     def _rows_of(self, shard_id: int) -> torch.Tensor:
         """Row indices (in the local weight) that hold shard ``shard_id``."""
@@ -244,8 +280,14 @@ class QKVParallelLinear(LinearBase):
         self._create(hidden_size, self.q_size + self.k_size + self.v_size, device)
 
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        x = apply_transform(x, self.x_transform, self.group)
-        qkv = self.quant_method.apply(self, x, self.bias)
+        qkv = None
+        if not isinstance(x, torch.Tensor):
+            qkv, x = _sharded_input(self, x)
+        elif self.x_transform == "AllGather" and self.tp_size > 1:
+            qkv = gathered_gemm(self, x)
+        if qkv is None:
+            x = apply_transform(x, self.x_transform, self.group)
+            qkv = self.quant_method.apply(self, x, self.bias)
         return (qkv[:, : self.q_size], qkv[:, self.q_size: self.q_size + self.k_size],
                 qkv[:, self.q_size + self.k_size:])
 

@@ -51,7 +51,8 @@ class FusedMoE(nn.Module):
                  renormalize: bool = False, routed_scaling_factor: float = 1.0, n_group: int = 1,
                  topk_group: int = 1, router_bias: bool = False, num_shared_experts: int = 0,
                  shared_intermediate_size: Optional[int] = None, enable_expert_parallel: bool = True,
-                 prefix: str = "", max_tokens: int = 8192, quant: Optional[str] = None) -> None:
+                 prefix: str = "", max_tokens: int = 8192, quant: Optional[str] = None,
+                 num_redundant_experts: int = 0) -> None:
         super().__init__()
         self.num_experts, self.top_k = num_experts, top_k
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -64,9 +65,15 @@ class FusedMoE(nn.Module):
         self.ep_group = pstate.get_ep_group() if enable_expert_parallel else None
         self.ep_size = self.ep_group.world_size if self.ep_group is not None else 1
         self.ep_rank = self.ep_group.rank_in_group if self.ep_group is not None else 0
-        assert num_experts % self.ep_size == 0
-        self.local_experts = num_experts // self.ep_size
+        # physical expert slots = logical experts + redundant copies of the hot ones (parallel/eplb.py)
+        self.num_physical = num_experts + num_redundant_experts
+        assert self.num_physical % self.ep_size == 0
+        self.local_experts = self.num_physical // self.ep_size
         self.expert_start = self.ep_rank * self.local_experts
+        self.eplb = None
+        if num_redundant_experts > 0:
+            from ..parallel.eplb import EplbState
+            self.eplb = EplbState(num_experts, num_redundant_experts, self.ep_size, device)
         self.gate = ReplicatedLinear(hidden_size, num_experts, dtype=dtype, device=device,
                                      prefix=f"{prefix}.gate")
         if router_bias:
@@ -104,12 +111,12 @@ class FusedMoE(nn.Module):
         dev = self.w13.device
         if dev.type != "cuda" or self.buffers is not None:
             return
-        shared = _SHARED_BUFFERS.get((id(self.ep_group), self.num_experts, self.hidden_size, self.top_k))
+        shared = _SHARED_BUFFERS.get((id(self.ep_group), self.num_physical, self.hidden_size, self.top_k))
         if shared is None:
             group = self.ep_group if self.ep_group is not None else _solo_group()
-            shared = EpBuffers(group, dev, self.num_experts if self.ep_size > 1 else self.local_experts,
+            shared = EpBuffers(group, dev, self.num_physical if self.ep_size > 1 else self.local_experts,
                                self.hidden_size, self.max_tokens, self.top_k)
-            _SHARED_BUFFERS[(id(self.ep_group), self.num_experts, self.hidden_size, self.top_k)] = shared
+            _SHARED_BUFFERS[(id(self.ep_group), self.num_physical, self.hidden_size, self.top_k)] = shared
         self.buffers = shared
         self._side_stream = torch.cuda.Stream(dev)
 
@@ -121,9 +128,19 @@ class FusedMoE(nn.Module):
         if expert_id is None:
             param.data.copy_(loaded.to(param.dtype))
             return True
+        if self.eplb is not None:
+            # every local slot that holds (a copy of) this expert receives the tensor
+            mine = [j for j, e in enumerate(self.eplb.local_logical_ids(self.ep_rank)) if e == expert_id]
+            for j in mine:
+                self._load_slot(param, loaded, j, shard)
+            return bool(mine)
         local = expert_id - self.expert_start
         if local < 0 or local >= self.local_experts:
             return False
+        self._load_slot(param, loaded, local, shard)
+        return True
+
+    def _load_slot(self, param: nn.Parameter, loaded: torch.Tensor, local: int, shard: Optional[str]) -> None:
         i = self.intermediate_size
         if shard in ("gate", "up"):
             j = torch.arange(i, device=param.device)
@@ -137,7 +154,22 @@ class FusedMoE(nn.Module):
                 param.data[local, off:off + nb].copy_(loaded)
         else:
             param.data[local].copy_(loaded if param.dtype == torch.float8_e4m3fn else loaded.to(param.dtype))
-        return True
+
+    def rebalance(self, decay: float = 0.0) -> int:
+        """Re-plan the expert placement from the load seen since the last call and move the
+        expert weights accordingly (collective over the expert-parallel group; call between
+        steps).  Returns the number of physical slots whose expert changed."""
+        if self.eplb is None:
+            return 0
+        from ..parallel.eplb import rearrange_expert_weights
+        group = self.ep_group if self.ep_size > 1 else None
+        old, new = self.eplb.replan(group, decay)
+        tensors = [self.w13.data, self.w2.data]
+        if self.quant == "fp8":
+            tensors += [self.w13_scale.data, self.w2_scale.data]
+        moved = rearrange_expert_weights(tensors, old, new, group)
+        self.eplb.set_placement(new)
+        return moved
 
     # ----------------------------------------------------------------- forward
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -162,6 +194,9 @@ class FusedMoE(nn.Module):
             pad_from = max(0, t_full - lo)
             ids = ids.clone()
             ids[pad_from:] = -1          # padded rows take part in nothing
+        if self.eplb is not None:
+            self.eplb.record(ids)
+            ids = self.eplb.remap(ids)
         out = self._routed(x, w, ids)
         if dedup:
             out = self.tp_group.all_gather(out, dim=0)[:t_full]
@@ -182,7 +217,7 @@ class FusedMoE(nn.Module):
                 self._side_stream.wait_stream(cur)
                 with torch.cuda.stream(self._side_stream):
                     shared_out = self.shared_experts(x)
-            rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_experts, self.buffers)
+            rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_physical, self.buffers)
             h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
             y = ops.grouped_gemm(h1, self.w2, offsets)
             self.buffers.expert_y[: y.shape[0]].copy_(y)
@@ -192,7 +227,7 @@ class FusedMoE(nn.Module):
         # CPU / reference path
         if self.shared_experts is not None:
             shared_out = self.shared_experts(x)
-        rows, offsets, handle = ep_dispatch(comm, x, ids, w, self.num_experts)
+        rows, offsets, handle = ep_dispatch(comm, x, ids, w, self.num_physical)
         h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
         y = ops.grouped_gemm(h1, self.w2, offsets)
         return ep_combine(comm, y, handle, shared_out)

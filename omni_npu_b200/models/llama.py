@@ -116,6 +116,7 @@ class LlamaModel(nn.Module):
         if self.sequence_parallel and tp.world_size > 1:
             from ..layers.flashcomm import SequenceParallelStream
             sp = SequenceParallelStream(tp)
+            sp.fused_gather = True      # qkv_proj / gate_up_proj read the token shards inside their GEMM
             residual, hidden = sp.scatter(hidden), None
             for layer in self.layers:
                 hidden, residual = layer.forward_sequence_parallel(sp, hidden, residual)

@@ -203,6 +203,34 @@ def quant_int8_per_token(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return _C().quant_int8_per_token(x)
 
 
+def dsa_indexer_topk(q: torch.Tensor, w: torch.Tensor, index_cache: torch.Tensor, block_tables: torch.Tensor,
+                     positions: torch.Tensor, num_seqs: int, topk: int, cu_q: Optional[torch.Tensor] = None,
+                     q_len: int = 1, max_ctx: int = 0, max_q: int = 0, return_scores: bool = False):
+    """Sparse-attention indexer: ``score[t, j] = sum_h w[t, h] * relu(q[t, h] . k[j])`` over the cached
+    keys ``j <= positions[t]`` of the token's sequence, then the ``topk`` best positions per token
+    (int32 [T, topk], unordered, -1 padded).  ``cu_q`` [B + 1] gives the first query token of each
+    sequence; without it every sequence has ``q_len`` tokens.  ``max_ctx`` / ``max_q`` bound the longest
+    context / query run (both default to the largest possible value)."""
+    t, h = q.shape[0], q.shape[1]
+    bs = index_cache.shape[1]
+    if max_ctx <= 0:
+        max_ctx = block_tables.shape[1] * bs
+    if max_q <= 0:
+        max_q = q_len if cu_q is None else t
+    if not q.is_cuda:
+        return ref.dsa_indexer_topk(q, w, index_cache, block_tables, positions, num_seqs, topk, cu_q, q_len,
+                                    return_scores)
+    supported = (q.shape[2] == 128 and h % 16 == 0 and h <= 256 and bs % 8 == 0 and
+                 (bs % 128 == 0 if bs >= 128 else 128 % bs == 0))
+    if not supported:
+        raise RuntimeError(f"dsa_indexer_topk: unsupported shape (heads {h}, dim {q.shape[2]}, page {bs})")
+    st = device_state(q.device)
+    _count(2)
+    sel, scores = _C().dsa_indexer(q.contiguous(), w.float().contiguous(), index_cache, block_tables, cu_q,
+                                   positions, num_seqs, q_len, max_ctx, max_q, topk, st.status)
+    return (sel, scores) if return_scores else sel
+
+
 def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
                    kind: str = "int8", want_bf16: bool = False):
     """RMSNorm of ``x`` (or of ``x + residual``, which is written back to ``residual``) fused with

@@ -2,7 +2,7 @@
 
     python -m omni_npu_b200.ops.bench_kernels gemm            # GEMM shapes of the serving configs
     python -m omni_npu_b200.ops.bench_kernels gemm --m 128 --n 4096 --k 4096 --bn 128 --splits 4
-    python -m omni_npu_b200.ops.bench_kernels attn | norm | sample | all
+    python -m omni_npu_b200.ops.bench_kernels attn | norm | sample | indexer | all
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed
 (a 256 MB buffer is rewritten) before every timed launch, median of the timed
@@ -214,9 +214,36 @@ def bench_sample(args):
               f"top-k/top-p sample {t1*1e3:7.1f} us")
 
 
+def bench_indexer(args):
+    """Sparse-attention indexer (64 heads x 128 dims, page 16, top-2048): decode batches and one
+    prefill chunk.  Bytes = the index keys read once; FLOPs = 2 * heads * 128 per (token, key)."""
+    hbm, flops, src = peaks()
+    print(f"# dsa indexer: scores (tcgen05) + radix select, fractions of {src} peaks")
+    h, bs, topk = 64, 16, 2048
+    cases = [("decode", 128, 1, 4096), ("decode", 128, 1, 16384), ("decode", 32, 2, 32768), ("prefill", 2, 4096, 4096)]
+    if args.b:
+        cases = [(args.phase if args.phase != "both" else "decode", args.b, 1, args.ctx)]
+    for mode, b, ql, ctx in cases:
+        max_blocks = (ctx + bs - 1) // bs
+        cache = torch.randn(b * max_blocks, bs, 128, device="cuda", dtype=torch.bfloat16)
+        bt = torch.arange(b * max_blocks, device="cuda", dtype=torch.int32).view(b, max_blocks)
+        t = b * ql
+        q = torch.randn(t, h, 128, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(t, h, device="cuda") * 0.1
+        pos = (torch.arange(ctx - ql, ctx, dtype=torch.int32).repeat(b)).cuda()
+        cu = torch.arange(0, t + 1, ql, dtype=torch.int32, device="cuda")
+        kw = dict(cu_q=cu if mode == "prefill" else None, q_len=ql, max_ctx=ctx, max_q=ql)
+        ms = time_fn(lambda: ops.dsa_indexer_topk(q, w, cache, bt, pos, b, topk, **kw), iters=args.iters)
+        pairs = b * (ql * (ctx - ql) + ql * (ql + 1) / 2)
+        fl = 2.0 * h * 128 * pairs
+        by = b * ctx * 256.0
+        print(f"{mode:8s} B={b:4d} q={ql:5d} ctx={ctx:6d}: {ms*1e3:8.1f} us  {fl/ms/1e9:7.1f} TFLOP/s "
+              f"(frac {fl/flops/(ms/1e3):.2f})  keys {by/ms/1e6:6.0f} GB/s (frac {by/hbm/(ms/1e3):.2f})")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "all"])
+    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "indexer", "all"])
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
@@ -239,6 +266,8 @@ def main():
         bench_norm(args)
     if args.what in ("sample", "all"):
         bench_sample(args)
+    if args.what in ("indexer", "all"):
+        bench_indexer(args)
 
 
 if __name__ == "__main__":

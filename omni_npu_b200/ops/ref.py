@@ -448,3 +448,33 @@ def silu_and_mul_quant(x, kind="int8"):
     i = x.shape[-1] // 2
     y = (torch.nn.functional.silu(x[..., :i].float()) * x[..., i:].float()).to(x.dtype)
     return quant_per_token(y, kind)
+
+
+def dsa_indexer_topk(q, w, index_cache, block_tables, positions, num_seqs, topk, cu_q=None, q_len=1,
+                     return_scores=False):
+    """Dense reference of the sparse-attention indexer (see ``ops.dsa_indexer_topk``)."""
+    t, h, d = q.shape
+    bs = index_cache.shape[1]
+    flat = index_cache.reshape(-1, d).float()
+    out = torch.full((t, topk), -1, dtype=torch.int32, device=q.device)
+    ld = (block_tables.shape[1] * bs + 127) // 128 * 128
+    scores = torch.full((t, ld), float("-inf"), dtype=torch.float32, device=q.device)
+    cu = cu_q.tolist() if cu_q is not None else [i * q_len for i in range(num_seqs + 1)]
+    for b in range(num_seqs):
+        qs, qe = cu[b], cu[b + 1]
+        if qe <= qs or int(positions[qs]) < 0:
+            continue
+        n = int(positions[qe - 1]) + 1
+        pos = torch.arange(n, device=q.device)
+        rows = block_tables[b][pos // bs].long() * bs + pos % bs
+        keys = flat[rows]
+        logits = torch.einsum("thd,ld->thl", q[qs:qe].float(), keys).relu_()
+        sc = (logits * w[qs:qe].float().unsqueeze(-1)).sum(1)
+        mask = pos.unsqueeze(0) > positions[qs:qe].long().unsqueeze(1)
+        sc = sc.masked_fill(mask, float("-inf"))
+        scores[qs:qe, :n] = sc
+        k = min(topk, n)
+        vals, idx = sc.topk(k, dim=-1)
+        idx = torch.where(torch.isinf(vals), torch.full_like(idx, -1), idx)
+        out[qs:qe, :k] = idx.to(torch.int32)
+    return (out, scores) if return_scores else out

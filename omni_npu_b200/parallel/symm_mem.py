@@ -58,6 +58,14 @@ def _lib() -> ctypes.CDLL:
         lib.b200_gemm_all_reduce.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_float, ci, ci, ci, ci, ci, ci, pp, ci, ci,
                                              ll, vp, vp, vp, ci, vp]
         lib.b200_gemm_all_reduce.restype = ci
+        lib.b200_symm_epoch_word.restype = ci
+        lib.b200_symm_ag_flag_word.restype = ci
+        lib.b200_symm_ag_stage.argtypes = [pp, pp, ci, ci, sz, vp, ll, vp, vp]
+        lib.b200_symm_ag_stage.restype = ci
+        lib.b200_gemm_ag_encode_maps.argtypes = [vp, pp, ci, sz, ci]
+        lib.b200_gemm_ag_encode_maps.restype = ci
+        lib.b200_gemm_all_gather.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp, ci, vp]
+        lib.b200_gemm_all_gather.restype = ci
         _LIB = lib
     return _LIB
 
@@ -116,6 +124,8 @@ class SymmetricMemory:
         self.ll_done = torch.zeros(4, dtype=torch.int32, device=device)
         self.use_ll = os.environ.get("OMNI_B200_SYMM_LL", "1") != "0"
         self.fuse_gemm = os.environ.get("OMNI_B200_FUSE_GEMM_AR", "1") != "0"
+        self.fuse_ag_gemm = os.environ.get("OMNI_B200_FUSE_AG_GEMM", "1") != "0"
+        self._ag_maps = {}                      # K -> device tensor holding the 2 * world tensor maps
         self.status = ops.device_state(device).status
         if lib.b200_symm_ll_arm(ll_ptr, ll_total_vecs, self._stream()) != 0:
             raise RuntimeError("arming the push all-reduce buffer failed")
@@ -239,6 +249,51 @@ class SymmetricMemory:
         if rc != 0:
             raise RuntimeError(f"fused gemm + all_reduce failed ({rc})")
         ops._count(1)
+        return out
+
+    # ------------------------------------------------- fused all-gather -> GEMM
+    def can_all_gather_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """bf16, whole 128-row tiles per rank, the block fits one staging half."""
+        return (self.fuse_ag_gemm and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.dim() == 2 and x.is_contiguous() and w.dim() == 2 and w.stride(1) == 1
+                and x.shape[0] > 0 and x.shape[0] % 128 == 0 and x.shape[1] % 64 == 0
+                and x.numel() * 2 <= self.half_bytes)
+
+    def _ag_maps_for(self, k: int) -> torch.Tensor:
+        maps = self._ag_maps.get(k)
+        if maps is None:
+            host = ctypes.create_string_buffer(2 * self.world * 128)
+            rc = _lib().b200_gemm_ag_encode_maps(host, self.data_ptrs, self.world, self.half_bytes, k)
+            if rc != 0:
+                raise RuntimeError(f"encoding the all-gather tensor maps failed ({rc})")
+            maps = torch.frombuffer(bytearray(host.raw), dtype=torch.uint8).to(self.device)
+            torch.cuda.synchronize(self.device)
+            self._ag_maps[k] = maps
+        return maps
+
+    def all_gather_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                        swiglu: bool = False) -> torch.Tensor:
+        """``all_gather(x, dim=0) @ w.T`` (+bias, optional fused SwiGLU) without materialising the
+        gathered activation: every rank stages its rows in its symmetric buffer, and the GEMM's
+        TMA producer reads the row blocks from their owners (own rows first) while the tensor
+        cores work on the tiles that are already there."""
+        lib = _lib()
+        rows, k = x.shape
+        n = w.shape[0]
+        maps = self._ag_maps_for(k)
+        rc = lib.b200_symm_ag_stage(self.data_ptrs, self.signal_ptrs, self.world, self.rank, self.half_bytes,
+                                    x.data_ptr(), x.numel(), self.done.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"all-gather staging failed ({rc})")
+        out = torch.empty((rows * self.world, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
+        rc = lib.b200_gemm_all_gather(maps.data_ptr(), self.signal_ptrs[self.rank], x.data_ptr(), w.data_ptr(),
+                                      out.data_ptr(), bias.data_ptr() if bias is not None else None, rows, n, k,
+                                      w.stride(0), out.stride(0), 1 if swiglu else 0, self.world, self.rank,
+                                      lib.b200_symm_epoch_word(), lib.b200_symm_ag_flag_word(),
+                                      self.status.data_ptr(), 0, self._stream())
+        if rc != 0:
+            raise RuntimeError(f"fused all_gather + gemm failed ({rc})")
+        ops._count(2)
         return out
 
     def close(self) -> None:

@@ -546,3 +546,42 @@ def test_silu_and_mul_quant_fused(kind):
     deq = q.float().cpu() * s.cpu().unsqueeze(-1)
     step = s.cpu().unsqueeze(-1) * (1.0 if kind == "int8" else 32.0)
     assert ((deq - y).abs() <= step + 1e-3).all()
+
+
+@pytest.mark.parametrize("mode", ["decode", "decode_mtp", "prefill"])
+def test_dsa_indexer_scores_and_topk(mode):
+    """Indexer on tcgen05 + radix select against the dense fp32 reference: same scores, and the
+    selected set is a valid top-k (every selected score >= every unselected one)."""
+    torch.manual_seed(21)
+    bs, h, topk = 16, 64, 256
+    if mode == "prefill":
+        ctx, q_lens = [700, 130, 1500], [700, 100, 333]
+    elif mode == "decode":
+        ctx, q_lens = [5, 257, 900, 2049], [1, 1, 1, 1]
+    else:
+        ctx, q_lens = [300, 1025, 64], [2, 2, 2]
+    b = len(ctx)
+    max_blocks = max((c + bs - 1) // bs for c in ctx) + 2
+    nblocks = b * max_blocks + 3
+    bt = torch.randperm(nblocks)[: b * max_blocks].view(b, max_blocks).to(torch.int32)
+    cache = (torch.randn(nblocks, bs, 128) * 0.5).bfloat16()
+    t = sum(q_lens)
+    q = (torch.randn(t, h, 128) * 0.5).bfloat16()
+    w = torch.randn(t, h) * 0.1
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    pos = torch.cat([torch.arange(c - n, c) for c, n in zip(ctx, q_lens)]).to(torch.int32)
+    uniform = mode != "prefill"
+    want_sel, want_sc = ref.dsa_indexer_topk(q, w, cache, bt, pos, b, topk, None if uniform else cu, q_lens[0], True)
+    sel, sc = ops.dsa_indexer_topk(q.to(DEV), w.to(DEV), cache.to(DEV), bt.to(DEV), pos.to(DEV), b, topk,
+                                   None if uniform else cu.to(DEV), q_lens[0], max_ctx=max(ctx),
+                                   max_q=max(q_lens), return_scores=True)
+    sel, sc = sel.cpu(), sc.cpu()
+    for i in range(t):
+        n = int(pos[i]) + 1
+        assert torch.allclose(sc[i, :n], want_sc[i, :n], rtol=2e-2, atol=2e-2), (mode, i)
+        got = sel[i][sel[i] >= 0].long()
+        assert got.numel() == min(topk, n) and got.unique().numel() == got.numel() and int(got.max()) < n
+        if n > topk:
+            chosen = torch.zeros(n, dtype=torch.bool)
+            chosen[got] = True
+            assert sc[i, :n][chosen].min() >= sc[i, :n][~chosen].max()
