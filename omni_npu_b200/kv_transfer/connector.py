@@ -266,6 +266,8 @@ class P2PKVConnector:
 
 
 _INSTANCES: Dict[Tuple[int, int], P2PKVConnector] = {}
+# connector names that select the host-memory pool data path (kv_transfer/host_pool.py)
+HOST_POOL_NAMES = ("HostPoolKVConnector", "OmniCacheConnector")
 
 
 def create_connector(config: EngineConfig, role: str, device: Optional[torch.device] = None) -> P2PKVConnector:
@@ -273,7 +275,12 @@ def create_connector(config: EngineConfig, role: str, device: Optional[torch.dev
     key = (os.getpid(), id(config))
     inst = _INSTANCES.get(key)
     if inst is None:
-        inst = P2PKVConnector(config, device)
+        name = config.kv_transfer.kv_connector if config.kv_transfer is not None else None
+        if name in HOST_POOL_NAMES:
+            from .host_pool import HostPoolKVConnector
+            inst = HostPoolKVConnector(config, device)
+        else:
+            inst = P2PKVConnector(config, device)
         _INSTANCES[key] = inst
     elif device is not None and inst.device.type == "cpu" and device.type == "cuda":
         inst.device = device

@@ -1,12 +1,13 @@
 """Registration of the KV connector with vLLM's connector factory
 (counterpart of omni_npu/connector/register.py:37-51).  The connector is
-reachable as ``P2PKVConnector`` and, for drop-in compatibility with launch
-scripts written for the reference, as ``LLMDataDistConnector``."""
+reachable as ``P2PKVConnector`` (GPU-to-GPU pulls) and ``HostPoolKVConnector`` (blocks
+travel through a pinned host pool) and, for drop-in compatibility with launch scripts
+written for the reference, as ``LLMDataDistConnector`` / ``OmniCacheConnector``."""
 from __future__ import annotations
 
 from .. import compat
 
-CONNECTOR_NAMES = ("P2PKVConnector", "LLMDataDistConnector")
+CONNECTOR_NAMES = ("P2PKVConnector", "LLMDataDistConnector", "HostPoolKVConnector", "OmniCacheConnector")
 MODULE = "omni_npu_b200.kv_transfer.vllm_connector"
 
 

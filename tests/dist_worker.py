@@ -354,7 +354,69 @@ def task_dcp_mla(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
+def task_ag_gemm(rank, world, port, workdir, device_kind):
+    """Column-parallel projection of a token-sharded activation as one kernel (the GEMM's TMA
+    producer reads every rank's rows from its owner) against all-gather followed by a GEMM."""
+    dev, state = setup(rank, world, port, "cuda")
+    state.init_model_parallel(tp=world, device=dev)
+    import torch.distributed as dist
+    from omni_npu_b200 import ops
+    from omni_npu_b200.parallel.symm_mem import attach_symmetric_memory
+    g = state.get_tp_group()
+    symm = attach_symmetric_memory(g, dev, half_bytes=96 << 20)
+    res = {"max_err": {}}
+    torch.manual_seed(7 + rank)
+
+    def gathered(x):
+        full = torch.empty(world * x.shape[0], x.shape[1], device=dev, dtype=x.dtype)
+        dist.all_gather_into_tensor(full, x, group=g.device_group)
+        return full
+
+    for name, rows, n, k, swiglu, bias in (("plain", 256, 1024, 512, False, False), ("bias", 128, 768, 1024, False, True),
+                                           ("swiglu", 384, 2048, 512, True, False),
+                                           ("prefill", 4096 // world, 6144, 4096, False, False)):
+        x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+        b = torch.randn(n, device=dev, dtype=torch.bfloat16) if bias else None
+        want = ops.gemm(gathered(x), w, b, None, None, swiglu).float()
+        for rep in range(3):           # alternating staging halves; a plain collective in between
+            got = symm.all_gather_gemm(x, w, b, swiglu)
+            if rep == 1:
+                symm.all_reduce(torch.ones(8, 64, device=dev, dtype=torch.bfloat16))
+        torch.cuda.synchronize()
+        res["max_err"][name] = (got.float() - want).abs().max().item()
+    # timing at a prefill shape: one kernel pair (stage + GEMM) vs all-gather then GEMM
+    rows, n, k = 8192 // world, 6144, 4096
+    x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+
+    def timeit(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+    res["us_fused"] = timeit(lambda: symm.all_gather_gemm(x, w))
+    res["us_symm_ag_then_gemm"] = timeit(lambda: ops.gemm(symm.all_gather(x), w))
+    res["us_nccl_ag_then_gemm"] = timeit(lambda: ops.gemm(gathered(x), w))
+    full = gathered(x)
+    res["us_gemm_alone"] = timeit(lambda: ops.gemm(full, w))
+    res["tflops_fused"] = 2.0 * rows * world * n * k / res["us_fused"] / 1e6
+    torch.cuda.synchronize()
+    ops.check_status()
+    g.barrier()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.finish_process()
+    state.destroy_distributed()
+
+
+TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

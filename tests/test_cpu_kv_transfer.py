@@ -133,3 +133,67 @@ def test_disaggregated_prefill_then_decode_matches_single_engine():
     finally:
         prefill.engine.shutdown()
         decode.engine.shutdown()
+
+
+def test_host_pool_slots_allocate_and_recycle(tmp_path, monkeypatch):
+    from omni_npu_b200.kv_transfer import host_pool
+    monkeypatch.setattr(host_pool, "POOL_DIR", str(tmp_path))
+    pool = host_pool.HostKVPool("p0", 4, [64, 32], create=True)
+    other = host_pool.HostKVPool("p0", 4, [64, 32], create=False)
+    try:
+        a = pool.alloc(3)
+        assert sorted(a) == [0, 1, 2] and pool.alloc(2) is None
+        pool.slots_view(1)[a[0]] = torch.arange(32, dtype=torch.uint8)
+        assert torch.equal(other.slots_view(1)[a[0]], torch.arange(32, dtype=torch.uint8))    # same memory
+        assert pool.slot_bytes == 96 and pool.slots_view(0).shape == (4, 64)
+        pool.free(a)
+        assert pool.num_free == 4
+    finally:
+        other.close()
+        pool.close()
+    assert not (tmp_path / "p0").exists()
+
+
+def test_disaggregated_serving_through_the_host_pool(tmp_path, monkeypatch):
+    """Prefill instance stores the prompt KV in the host pool and frees its GPU blocks at once;
+    the decode instance loads the slots, generates the same tokens, and its ack recycles the slots."""
+    from omni_npu_b200.kv_transfer import host_pool
+    monkeypatch.setattr(host_pool, "POOL_DIR", str(tmp_path))
+    cfg = tiny_llama()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (35, 16, 50)]
+    common = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=32, seed=1, additional_config={"async_pull_kv": False})
+    mono = LLM(model=cfg, **common)
+    want = [o.output_token_ids for o in mono.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    prefill = LLM(model=cfg, kv_transfer_config=dict(
+        kv_connector="HostPoolKVConnector", kv_role="kv_producer",
+        kv_connector_extra_config={"kv_port": 24511, "kv_pool_slots": 16, "kv_pool_name": "pool_t"}), **common)
+    decode = LLM(model=cfg, kv_transfer_config=dict(kv_connector="OmniCacheConnector", kv_role="kv_consumer",
+                                                     kv_connector_extra_config={"kv_port": 24611}), **common)
+    decode.engine.worker.get_model().load_state_dict(prefill.engine.worker.get_model().state_dict())
+    try:
+        p_out = prefill.generate(prompts, SamplingParams(max_tokens=1, ignore_eos=True))
+        conn = prefill.engine.worker.model_runner.kv_connector
+        nblk = sum((len(p) + 15) // 16 for p in prompts)
+        assert prefill.engine.scheduler.pool.num_parked == 0 and prefill.engine.scheduler.pool.num_free == 32
+        assert conn.pool.num_free == 16 - nblk
+        order = {}
+        for i, (p, o) in enumerate(zip(prompts, p_out)):
+            assert o.kv_transfer_params["kv_pool"]["pool"] == "pool_t"
+            rid = decode.engine.add_request(p, SamplingParams(max_tokens=6, ignore_eos=True),
+                                            kv_transfer_params=o.kv_transfer_params)
+            order[rid] = i
+        got = [None] * 3
+        while decode.engine.has_unfinished_requests():
+            for o in decode.engine.step():
+                got[order[o.request_id]] = o.output_token_ids
+        assert got == want
+        deadline = time.time() + 5
+        while conn.pool.num_free < 16 and time.time() < deadline:
+            prefill.engine.scheduler.schedule()
+            time.sleep(0.05)
+        assert conn.pool.num_free == 16
+    finally:
+        prefill.engine.shutdown()
+        decode.engine.shutdown()

@@ -24,6 +24,15 @@ def test_symmetric_memory_collectives_match_nccl():
           res[0]["us_symm_64MiB"], res[0]["us_nccl_64MiB"])
 
 
+def test_fused_all_gather_gemm_matches_gather_then_gemm():
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("ag_gemm", 2, d, device="cuda", timeout=300)
+    for r in res:
+        for name, err in r["max_err"].items():
+            assert err <= 0.05, (name, err)
+    print("all-gather + GEMM us:", {k: round(v, 1) for k, v in res[0].items() if k.startswith(("us_", "tflops"))})
+
+
 def test_expert_parallel_moe_dispatch_combine_over_peer_memory():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("ep_moe", 2, d, device="cuda", timeout=300)
