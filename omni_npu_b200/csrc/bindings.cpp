@@ -39,6 +39,9 @@ int b200_quant_fp8_1x128(void* q, void* scales, const void* x, long long rows, i
                          long long x_stride, int ue8m0, cudaStream_t stream);
 int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long rows, int H,
                               long long x_stride, cudaStream_t stream);
+int b200_gemm_fp8_block(const void* A, const float* a_scales, const void* W, const float* w_scales, void* C,
+                        const void* bias, const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
+                        int out_fp32, int* status, int max_ctas, cudaStream_t stream);
 int b200_dsa_indexer(const void* q, const float* w, const void* cache, const int* block_tables, const int* cu_q,
                      const int* positions, float* scores, int* topk_out, int T, int B, int H, int q_len,
                      long long num_blocks, int block_size, int max_blocks, long long ld, int max_ctx, int max_q,
@@ -346,6 +349,44 @@ std::tuple<Tensor, Tensor> quant_int8_per_token(const Tensor& x) {
                                   x.stride(0), cur_stream()),
         "quant_int8_per_token");
   return {q, s};
+}
+
+// Block-scaled e4m3 GEMM: a [M,K] e4m3 with a_scale [M, K/128]; w [N,K] e4m3 with w_scale
+// [ceil(N/128), K/128]; every 128-wide K block's product is scaled before it is accumulated.
+Tensor gemm_fp8_block(const Tensor& a, const Tensor& a_scale, const Tensor& w, const Tensor& w_scale,
+                      const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual, bool out_fp32,
+                      const Tensor& status, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_fp8_block: 2-D CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == at::kFloat8_e4m3fn && w.scalar_type() == at::kFloat8_e4m3fn,
+              "gemm_fp8_block: float8_e4m3fn operands");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1, "gemm_fp8_block: K must be contiguous");
+  const int64_t M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && K % 128 == 0, "gemm_fp8_block: K mismatch / K must be a multiple of 128");
+  const int64_t kb = K / 128, nbk = (N + 127) / 128;
+  TORCH_CHECK(a_scale.is_cuda() && a_scale.scalar_type() == at::kFloat && a_scale.is_contiguous() &&
+                  a_scale.numel() == M * kb, "gemm_fp8_block: a_scale fp32 [M, K/128]");
+  TORCH_CHECK(w_scale.is_cuda() && w_scale.scalar_type() == at::kFloat && w_scale.is_contiguous() &&
+                  w_scale.numel() == nbk * kb, "gemm_fp8_block: w_scale fp32 [ceil(N/128), K/128]");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor c = torch::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  const void* bias_p = nullptr;
+  const void* res_p = nullptr;
+  if (bias.has_value()) {
+    CHECK_CUDA_BF16((*bias));
+    TORCH_CHECK(bias->numel() == N, "gemm_fp8_block: bias [N]");
+    bias_p = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    CHECK_CUDA_BF16((*residual));
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == M && residual->size(1) == N && residual->is_contiguous(),
+                "gemm_fp8_block: residual [M, N] contiguous");
+    res_p = residual->data_ptr();
+  }
+  check(b200_gemm_fp8_block(a.data_ptr(), a_scale.data_ptr<float>(), w.data_ptr(), w_scale.data_ptr<float>(),
+                            c.data_ptr(), bias_p, res_p, (int)M, (int)N, (int)K, (int)a.stride(0), (int)w.stride(0),
+                            (int)N, out_fp32 ? 1 : 0, status.data_ptr<int>(), (int)max_ctas, cur_stream()),
+        "gemm_fp8_block");
+  return c;
 }
 
 // Sparse-attention indexer: scores on the tensor cores + radix select of the topk best key
@@ -753,6 +794,7 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("quant_int8_per_token", &quant_int8_per_token);
   m.def("rms_norm_quant", &rms_norm_quant);
   m.def("dsa_indexer", &dsa_indexer);
+  m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("silu_and_mul_quant", &silu_and_mul_quant);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);

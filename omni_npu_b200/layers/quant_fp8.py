@@ -35,8 +35,10 @@ def fp8_block_gemm(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor,
                    block: Tuple[int, int] = (128, 128), swiglu: bool = False,
                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M,K] bf16 times block-scaled e4m3 weights [N,K]."""
-    if x.is_cuda and x.shape[1] % 128 == 0 and hasattr(ops, "gemm_fp8_block"):
-        xq, xs = ops.quant_fp8_1x128(x)
-        return ops.gemm_fp8_block(xq, xs, wq, w_scale, bias, residual, swiglu=swiglu, out_dtype=out_dtype)
+    if x.is_cuda and x.dim() == 2 and x.shape[1] % 128 == 0 and tuple(block) == (128, 128) and not swiglu \
+            and x.dtype == torch.bfloat16 and wq.dim() == 2:
+        # native path: per-token-per-128 activation quantisation, then the block-scaled tcgen05 kernel
+        xq, xs = ops.quant_fp8_1x128(x.contiguous())
+        return ops.gemm_fp8_block(xq, xs, wq, w_scale, bias, residual, out_dtype)
     w = ref.dequant_fp8_block(wq, w_scale, block).to(x.dtype if x.dtype.itemsize > 1 else torch.bfloat16)
     return ops.gemm(x, w, bias, residual, out_dtype, swiglu)

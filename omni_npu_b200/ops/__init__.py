@@ -203,6 +203,19 @@ def quant_int8_per_token(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return _C().quant_int8_per_token(x)
 
 
+def gemm_fp8_block(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                   out_dtype: Optional[torch.dtype] = None, max_ctas: int = 0) -> torch.Tensor:
+    """Block-scaled e4m3 product: ``a_q`` [M,K] with one scale per (row, 128 columns), ``w_q`` [N,K]
+    with one scale per 128 x 128 block; each 128-wide K block is scaled before accumulation."""
+    if not a_q.is_cuda:
+        return ref.gemm_fp8_block(a_q, a_scale, w_q, w_scale, bias, residual, out_dtype)
+    st = device_state(a_q.device)
+    _count(1)
+    return _C().gemm_fp8_block(a_q, a_scale.contiguous(), w_q, w_scale.contiguous(), bias, residual,
+                               out_dtype == torch.float32, st.status, max_ctas)
+
+
 def dsa_indexer_topk(q: torch.Tensor, w: torch.Tensor, index_cache: torch.Tensor, block_tables: torch.Tensor,
                      positions: torch.Tensor, num_seqs: int, topk: int, cu_q: Optional[torch.Tensor] = None,
                      q_len: int = 1, max_ctx: int = 0, max_q: int = 0, return_scores: bool = False):

@@ -478,3 +478,16 @@ def dsa_indexer_topk(q, w, index_cache, block_tables, positions, num_seqs, topk,
         idx = torch.where(torch.isinf(vals), torch.full_like(idx, -1), idx)
         out[qs:qe, :k] = idx.to(torch.int32)
     return (out, scores) if return_scores else out
+
+
+def gemm_fp8_block(a_q, a_scale, w_q, w_scale, bias=None, residual=None, out_dtype=None):
+    """fp32 reference of the block-scaled e4m3 product (scales: a [M, K/128], w [N/128, K/128])."""
+    m, k = a_q.shape
+    a = a_q.float() * a_scale.float().repeat_interleave(128, dim=1)[:, :k]
+    w = dequant_fp8_block(w_q, w_scale)
+    y = a @ w.t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype or torch.bfloat16)

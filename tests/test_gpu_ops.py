@@ -585,3 +585,24 @@ def test_dsa_indexer_scores_and_topk(mode):
             chosen = torch.zeros(n, dtype=torch.bool)
             chosen[got] = True
             assert sc[i, :n][chosen].min() >= sc[i, :n][~chosen].max()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 1000, 1024), (8, 4096, 7168)])
+def test_gemm_fp8_block_scaled(m, n, k):
+    """128 x 128 block-scaled weights, per-token-per-128 activations (DeepSeek-V3 checkpoint format)."""
+    from omni_npu_b200.layers.quant_fp8 import fp8_block_gemm, quantize_weight_block
+    torch.manual_seed(31)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.float32) * 0.05
+    # per-block magnitudes differ by orders of magnitude, so a missing or misplaced scale shows
+    w = w * torch.logspace(-2, 2, (k // 128)).to(DEV).repeat_interleave(128)[None, :]
+    wq, ws = quantize_weight_block(w)
+    xq, xs = ops.quant_fp8_1x128(x)
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    want = ref.gemm_fp8_block(xq.cpu(), xs.cpu(), wq.cpu(), ws.cpu(), bias.cpu(), res.cpu(), torch.float32)
+    got = ops.gemm_fp8_block(xq, xs, wq, ws, bias, res, torch.float32)
+    _close(got, want, 2e-3 * float(want.abs().max()), 2e-3)
+    got16 = fp8_block_gemm(x, wq, ws, bias, res)
+    assert got16.dtype == torch.bfloat16
+    _close(got16, want, 2e-2 * float(want.abs().max()), 2e-2)
