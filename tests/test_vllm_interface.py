@@ -72,7 +72,8 @@ def test_connector_and_custom_ops_match_vllm_interface():
         assert hasattr(KVConnectorBase_V1, name), f"vLLM dropped KVConnectorBase_V1.{name}"
         assert name in B200KVConnector.__dict__, name
     from omni_npu_b200.kv_transfer import register
-    assert register.CONNECTOR_NAMES == ("P2PKVConnector", "LLMDataDistConnector")
+    assert register.CONNECTOR_NAMES[:2] == ("P2PKVConnector", "LLMDataDistConnector")
+    assert "HostPoolKVConnector" in register.CONNECTOR_NAMES
     from omni_npu_b200.layers import vllm_custom_ops
     assert {"SiluAndMul", "RMSNorm"} <= set(vllm_custom_ops.REGISTERED)
     from vllm.model_executor.custom_op import CustomOp
