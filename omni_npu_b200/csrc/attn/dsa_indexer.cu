@@ -56,6 +56,7 @@ struct IndexerParams {
   int H;
   int ntok;                // query tokens per MMA: N = ntok * H
   int tiles_per_cta;
+  int q_split;             // grid.z: the token groups of a sequence are divided over this many CTAs
   int tmem_cols;
   int* status;
 };
@@ -95,8 +96,13 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
   const int kt_begin = blockIdx.x * p.tiles_per_cta;
   const int kt_end = min(n_key_tiles, kt_begin + p.tiles_per_cta);
   if (pos0 < 0 || kt_begin >= kt_end) return;               // uniform over the CTA: nothing allocated yet
-  const int groups = (nq + p.ntok - 1) / p.ntok;
-  const bool single_q = groups == 1;                        // the one query group stays resident
+  const int groups_all = (nq + p.ntok - 1) / p.ntok;
+  // this CTA's share of the token groups: [gz0, groups)
+  const int per_z = (groups_all + p.q_split - 1) / p.q_split;
+  const int gz0 = blockIdx.z * per_z;
+  const int groups = min(groups_all, gz0 + per_z);
+  if (gz0 >= groups) return;
+  const bool single_q = groups - gz0 == 1;                  // the one query group stays resident
   const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,6 +141,8 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
       uint32_t last_par = 0;
       for (int kt = kt_begin; ok && kt < kt_end; ++kt) {
         const int k0 = kt * kIdxBK;
+        const int g_begin = max(max(0, k0 - pos0) / p.ntok, gz0);
+        if (g_begin >= groups) continue;           // none of this CTA's tokens sees the tile
         if (!mbar_wait(&key_empty[ks], kph ^ 1)) {
           ok = false;
           break;
@@ -151,7 +159,6 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
         }
         last_bar = &key_full[ks];
         last_par = kph;
-        const int g_begin = max(0, k0 - pos0) / p.ntok;
         for (int g = g_begin; ok && g < groups; ++g) {
           if (single_q && q_loaded) break;
           if (!mbar_wait(&q_empty[qst], qph ^ 1)) {
@@ -188,12 +195,13 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
       bool q_seen = false, ok = true;
       for (int kt = kt_begin; ok && kt < kt_end; ++kt) {
         const int k0 = kt * kIdxBK;
+        const int g_begin = max(max(0, k0 - pos0) / p.ntok, gz0);
+        if (g_begin >= groups) continue;
         if (*abort_flag || !mbar_wait(&key_full[ks], kph)) {
           ok = false;
           break;
         }
         const uint32_t a_lo0 = (smem_u32(s_keys + ks * kIdxKeyBytes) & 0x3FFFF) >> 4;
-        const int g_begin = max(0, k0 - pos0) / p.ntok;
         for (int g = g_begin; g < groups; ++g) {
           if (!(single_q && q_seen)) {
             if (*abort_flag || !mbar_wait(&q_full[qst], qph)) {
@@ -255,7 +263,7 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     for (int kt = kt_begin; ok && kt < kt_end; ++kt) {
       const int k0 = kt * kIdxBK;
       const int key = k0 + r;
-      const int g_begin = max(0, k0 - pos0) / p.ntok;
+      const int g_begin = max(max(0, k0 - pos0) / p.ntok, gz0);
       for (int g = g_begin; g < groups; ++g) {
         const int t0 = g * p.ntok;                   // first token of the group, relative to qs
         float* wbuf = s_w + acc * N;
@@ -288,20 +296,35 @@ dsa_indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                                static_cast<uint32_t>(acc * acc_stride);
         for (int j = 0; j < p.ntok; ++j) {
           float sum = 0.f;
-          for (int c = 0; c < p.H; c += 16) {
-            uint32_t v[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-                  "=r"(v[15])
-                : "r"(t_row + static_cast<uint32_t>(j * p.H + c))
-                : "memory");
-            tmem_ld_wait();
-            const float* wj = wbuf + j * p.H + c;
+          if ((p.H & 63) == 0) {
+            // 64 columns in flight per wait: the load latency is paid once per 64 heads
+            for (int c = 0; c < p.H; c += 64) {
+              uint32_t v0[32], v1[32];
+              tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(j * p.H + c), v0);
+              tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(j * p.H + c + 32), v1);
+              tmem_ld_wait();
+              const float* wj = wbuf + j * p.H + c;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sum += wj[i] * fmaxf(__uint_as_float(v[i]), 0.f);
+              for (int i = 0; i < 32; ++i) sum += wj[i] * fmaxf(__uint_as_float(v0[i]), 0.f);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) sum += wj[32 + i] * fmaxf(__uint_as_float(v1[i]), 0.f);
+            }
+          } else {
+            for (int c = 0; c < p.H; c += 16) {
+              uint32_t v[16];
+              asm volatile(
+                  "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                    "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                    "=r"(v[15])
+                  : "r"(t_row + static_cast<uint32_t>(j * p.H + c))
+                  : "memory");
+              tmem_ld_wait();
+              const float* wj = wbuf + j * p.H + c;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sum += wj[i] * fmaxf(__uint_as_float(v[i]), 0.f);
+            }
           }
           const int tok = t0 + j;
           if (tok < nq && key < p.ld)
@@ -449,6 +472,13 @@ extern "C" int b200_dsa_indexer(const void* q, const float* w, const void* cache
   if (chunks < 1) chunks = 1;
   p.tiles_per_cta = (key_tiles + chunks - 1) / chunks;
   chunks = (key_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+  // long query runs (prefill): also divide the token groups, so that a few sequences fill the GPU
+  const int groups_max = (max_q + ntok - 1) / ntok;
+  int q_split = (2 * 148 + chunks * B - 1) / (chunks * B);
+  if (q_split > groups_max / 8) q_split = groups_max / 8;      // keep >= 8 groups per CTA per key tile
+  if (q_split < 1) q_split = 1;
+  if (q_split > 64) q_split = 64;
+  p.q_split = q_split;
   const size_t smem = 1024 + 2 * kIdxKeyBytes + 2 * (2 * static_cast<size_t>(N) * 128) + 2 * N * 4 + 12 * 8 + 16;
   static size_t configured = 0;
   if (smem > configured) {
@@ -465,7 +495,7 @@ extern "C" int b200_dsa_indexer(const void* q, const float* w, const void* cache
   r = make_tensormap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, static_cast<uint64_t>(T) * H, kIdxD, kIdxD, N, 64,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 3000;
-  if (launch_pdl(dsa_indexer_scores_kernel, dim3(chunks, B), dim3(kIdxThreads), smem, stream, 1, tk, tq, p) !=
+  if (launch_pdl(dsa_indexer_scores_kernel, dim3(chunks, B, q_split), dim3(kIdxThreads), smem, stream, 1, tk, tq, p) !=
       cudaSuccess)
     return -21;
   if (topk_out && topk > 0) {

@@ -155,6 +155,31 @@ class FusedMoE(nn.Module):
         else:
             param.data[local].copy_(loaded if param.dtype == torch.float8_e4m3fn else loaded.to(param.dtype))
 
+    def process_weights_after_loading(self) -> None:
+        """Block-scaled e4m3 expert weights are expanded to the compute dtype once, after loading
+        (the grouped kernel has no per-block scale path): ``w * scale`` per 128 x 128 block.  The
+        gate / up rows of ``w13`` are interleaved in groups of 8, their scale blocks are not, so
+        every stored row looks up the block of the checkpoint row it came from."""
+        if self.quant != "fp8" or self.w13.dtype != torch.float8_e4m3fn:
+            return
+        i, h = self.intermediate_size, self.hidden_size
+        dev = self.w13.device
+        r = torch.arange(2 * i, device=dev)
+        is_up = (r // 8) % 2
+        src = (r // 16) * 8 + r % 8                      # row inside the gate (or up) matrix
+        nb = (i + 127) // 128
+        blk = src // 128 + is_up * nb
+        w13 = torch.empty(self.w13.shape, dtype=self.dtype, device=dev)
+        w2 = torch.empty(self.w2.shape, dtype=self.dtype, device=dev)
+        for e in range(self.local_experts):              # expert by expert: bounded temporary memory
+            s13 = self.w13_scale[e][blk].repeat_interleave(128, dim=1)[:, :h]
+            w13[e] = (self.w13[e].float() * s13).to(self.dtype)
+            s2 = self.w2_scale[e].repeat_interleave(128, dim=0)[:h].repeat_interleave(128, dim=1)[:, :i]
+            w2[e] = (self.w2[e].float() * s2).to(self.dtype)
+        self.w13 = nn.Parameter(w13, requires_grad=False)
+        self.w2 = nn.Parameter(w2, requires_grad=False)
+        self.quant = "fp8-expanded"
+
     def rebalance(self, decay: float = 0.0) -> int:
         """Re-plan the expert placement from the load seen since the last call and move the
         expert weights accordingly (collective over the expert-parallel group; call between

@@ -82,3 +82,31 @@ def test_rearrange_single_rank_moves_within_rank():
     old, new = [0, 1, 2, 0], [0, 1, 2, 2]
     assert rearrange_expert_weights([w], old, new, None) == 1
     assert w.flatten().tolist() == [0.0, 1.0, 2.0, 2.0]
+
+
+def test_fp8_block_scaled_experts_expand_to_the_same_layer():
+    """An MoE layer loaded from block-scaled e4m3 expert tensors computes what the layer with the
+    de-quantised weights computes (gate/up rows are interleaved, their scale blocks are not)."""
+    from omni_npu_b200.layers.moe import FusedMoE
+    from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
+    from omni_npu_b200.ops import ref
+    state.ensure_initialized(torch.device("cpu"))
+    torch.manual_seed(1)
+    e, k, h, inter = 2, 1, 256, 256
+    q = FusedMoE(e, k, h, inter, dtype=torch.float32, enable_expert_parallel=False, quant="fp8")
+    plain = FusedMoE(e, k, h, inter, dtype=torch.float32, enable_expert_parallel=False)
+    gate_w = torch.randn(e, h)
+    q.gate.weight.data.copy_(gate_w)
+    plain.gate.weight.data.copy_(gate_w)
+    for i in range(e):
+        for shard, shape, param, sparam in (("gate", (inter, h), "w13", "w13_scale"), ("up", (inter, h), "w13", "w13_scale"),
+                                            ("down", (h, inter), "w2", "w2_scale")):
+            w = torch.randn(*shape) * torch.logspace(-1, 1, shape[0]).unsqueeze(1)     # block scales differ a lot
+            wq, ws = quantize_weight_block(w)
+            q.weight_loader(getattr(q, param), wq, i, shard)
+            q.weight_loader(getattr(q, sparam), ws, i, shard)
+            plain.weight_loader(getattr(plain, param), ref.dequant_fp8_block(wq, ws), i, shard)
+    q.process_weights_after_loading()
+    assert q.w13.dtype == torch.float32 and q.quant == "fp8-expanded"
+    x = torch.randn(5, h)
+    assert torch.allclose(q(x), plain(x), rtol=1e-4, atol=1e-4)
