@@ -49,6 +49,8 @@ struct SymmGroup {
 //   [kAgFlagWord, kAgFlagWord + kMaxRanks)  "rank r has staged its block" flags of the fused all-gather GEMM
 static constexpr int kEpochWord = kMaxRanks * kMaxCommBlocks;
 static constexpr int kAgFlagWord = kEpochWord + 4;
+//   [kRsFlagWord, kRsFlagWord + kMaxRanks)  "rank r has pushed all its partial rows" flags of the fused GEMM + reduce-scatter
+static constexpr int kRsFlagWord = kAgFlagWord + kMaxRanks;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -350,6 +352,102 @@ ag_stage_kernel(SymmGroup g, const uint4* __restrict__ in, long long n_vec, uint
   }
 }
 
+// --------------------------- second half of the fused GEMM + reduce-scatter
+// The GEMM before this kernel stored every rank's partial rows into the owners' staging halves:
+// stage[src][rows][row_vecs] on the owner.  Block 0 tells every rank that this rank's stores are
+// done (they are: the GEMM has completed), then every block waits (bounded) for all sources and
+// sums its share of the rows in rank order; optional "+ residual" and RMSNorm as in the
+// all-reduce kernels.  The last block advances the epoch.
+__global__ void __launch_bounds__(512)
+rs_reduce_kernel(SymmGroup g, uint4* __restrict__ out, long long rows, int row_vecs, uint4* __restrict__ residual,
+                 const uint4* __restrict__ norm_w, float eps, uint32_t* done_counter, int* status) {
+  const uint32_t epoch = read_epoch(g) + 1;
+  const uint4* stage = reinterpret_cast<const uint4*>(static_cast<const char*>(g.data[g.rank]) +
+                                                      (epoch & 1) * g.half_bytes);
+  if (blockIdx.x == 0 && threadIdx.x < g.world) {
+    __threadfence_system();
+    st_release_sys(g.signal[threadIdx.x] + kRsFlagWord + g.rank, epoch);
+  }
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < g.world) {
+    const uint32_t* mine = g.signal[g.rank] + kRsFlagWord + threadIdx.x;
+    uint32_t i = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (++i > kMaxFlagPolls) {
+        s_ok = 0;
+        if (status) atomicCAS(status, 0, 5);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    __shared__ float red[32];
+    const long long slot = rows * row_vecs;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+      float vals[4][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < row_vecs) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < g.world) add8(acc, __ldcv(stage + r * slot + row * row_vecs + v));
+          Pack8 y;
+          y.u = pack8(acc);
+          if (residual) {
+            Pack8 rs;
+            rs.u = residual[row * row_vecs + v];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              y.h[j] = __float2bfloat16(__bfloat162float(y.h[j]) + __bfloat162float(rs.h[j]));
+            if (norm_w) residual[row * row_vecs + v] = y.u;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            vals[k][j] = __bfloat162float(y.h[j]);
+            ss += vals[k][j] * vals[k][j];
+          }
+          if (!norm_w) out[row * row_vecs + v] = y.u;
+        }
+      }
+      if (norm_w) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+        const float inv = rsqrtf(tot / static_cast<float>(row_vecs * 8) + eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int v = threadIdx.x + k * blockDim.x;
+          if (v < row_vecs) {
+            Pack8 w8, o8;
+            w8.u = norm_w[v];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o8.h[j] = __float2bfloat16(vals[k][j] * inv * __bfloat162float(w8.h[j]));
+            out[row * row_vecs + v] = o8.u;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1u) == gridDim.x - 1) {
+      *done_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(g.signal[g.rank] + kEpochWord) = epoch;
+    }
+  }
+}
+
 // ---------------------------------------------------------- reduce-scatter
 // in [world * n_vec]; out [n_vec] = sum over ranks of their chunk `rank`.
 __global__ void __launch_bounds__(512)
@@ -570,7 +668,7 @@ extern "C" int b200_symm_close(void* ptr) {
 
 extern "C" int b200_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
 
-extern "C" int b200_symm_signal_words() { return kAgFlagWord + kMaxRanks + 4; }
+extern "C" int b200_symm_signal_words() { return kRsFlagWord + kMaxRanks + 4; }
 extern "C" int b200_symm_epoch_word() { return kEpochWord; }
 extern "C" int b200_symm_ag_flag_word() { return kAgFlagWord; }
 
@@ -640,6 +738,22 @@ extern "C" int b200_symm_all_gather(void* const* data, void* const* signal, int 
   allgather_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
       g, static_cast<const uint4*>(in), static_cast<uint4*>(out), n_vec,
       static_cast<uint32_t*>(done_counter), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// rows x row_elems bf16 per rank (row_elems % 8 == 0, <= 16384); out [rows, row_elems].
+// residual / norm_w optional: out = RMSNorm(residual += sum) * norm_w, or out = sum (+ residual).
+extern "C" int b200_symm_rs_reduce(void* const* data, void* const* signal, int world, int rank, size_t half_bytes,
+                                   void* out, long long rows, int row_elems, void* residual, const void* norm_w,
+                                   float eps, void* done_counter, int* status, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || (row_elems & 7) != 0 || row_elems > 512 * 4 * 8) return -1;
+  if (static_cast<size_t>(rows) * row_elems * 2 * world > half_bytes) return -4;
+  const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
+  long long blocks = rows < kMaxCommBlocks ? rows : kMaxCommBlocks;
+  if (blocks < 1) blocks = 1;
+  rs_reduce_kernel<<<static_cast<unsigned>(blocks), 512, 0, stream>>>(
+      g, static_cast<uint4*>(out), rows, row_elems >> 3, static_cast<uint4*>(residual),
+      static_cast<const uint4*>(norm_w), eps, static_cast<uint32_t*>(done_counter), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

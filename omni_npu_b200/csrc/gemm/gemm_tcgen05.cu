@@ -82,6 +82,16 @@ struct GemmParams {
   int ag_world, ag_rank;
   int ag_rows;                     // rows per rank, a multiple of 128
   int ag_epoch_word, ag_flag_word;
+  // ---- fused reduce-scatter of C (rs_world > 1): every rank computes a partial [M, N]; rank r
+  // owns rows [r * rs_rows, (r + 1) * rs_rows).  The epilogue stores each bf16 tile row straight
+  // into its owner's staging buffer (slot of this rank: [rs_rank][rs_rows][N]) with plain peer
+  // stores, so the transfer overlaps the tensor-core work; a small kernel then signals, waits for
+  // all sources and sums the slots (rs_reduce_kernel in the collectives file).
+  void* rs_data[kMaxRanks];        // peer-mapped staging buffers (both halves)
+  const uint32_t* rs_signal;       // this rank's signal pad (epoch word)
+  long long rs_half_bytes;
+  int rs_world, rs_rank, rs_rows;
+  int rs_epoch_word;
 };
 
 struct TileCoord {
@@ -443,6 +453,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     int cursor = 0;
     int tile_iter = 0;
+    long long rs_half_off = 0;     // fused reduce-scatter: staging half of the epoch this call opens
+    if (p.rs_world > 1) {
+      const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(p.rs_signal + p.rs_epoch_word) + 1u;
+      rs_half_off = static_cast<long long>(e & 1u) * p.rs_half_bytes;
+    }
     TileCoord tc;
     for (long long t = t_first;
          decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cta_rank, cursor, tc); t += t_stride) {
@@ -693,6 +708,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           continue;
         }
         const int ncols = min(16, p.N - col);
+        if (p.rs_world > 1) {
+          // partial tile row -> slot [this rank] of the row owner's staging half (N % 16 == 0 here)
+          const int owner = row / p.rs_rows;
+          const int row_local = row - owner * p.rs_rows;
+          if (p.bias && p.rs_rank == 0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += __bfloat162float(p.bias[col + i]);
+          }
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(p.rs_data[owner]) + rs_half_off) +
+                               (static_cast<long long>(p.rs_rank) * p.rs_rows + row_local) * p.N + col;
+          uint4 pk0, pk1;
+          pk0.x = pack_bf16x2(v[0], v[1]);
+          pk0.y = pack_bf16x2(v[2], v[3]);
+          pk0.z = pack_bf16x2(v[4], v[5]);
+          pk0.w = pack_bf16x2(v[6], v[7]);
+          pk1.x = pack_bf16x2(v[8], v[9]);
+          pk1.y = pack_bf16x2(v[10], v[11]);
+          pk1.z = pack_bf16x2(v[12], v[13]);
+          pk1.w = pack_bf16x2(v[14], v[15]);
+          reinterpret_cast<uint4*>(dst)[0] = pk0;
+          reinterpret_cast<uint4*>(dst)[1] = pk1;
+          continue;
+        }
         if (p.bias) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
@@ -1139,7 +1177,8 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar = nullptr, const struct AgArgs* ag = nullptr);
+                     const ArArgs* ar = nullptr, const struct AgArgs* ag = nullptr,
+                     const struct RsArgs* rs = nullptr);
 
 extern "C" int b200_gemm(const void* A, const void* W, void* C, const void* bias,
                          const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
@@ -1162,6 +1201,14 @@ extern "C" int b200_gemm_scaled(const void* A, const void* W, void* C, const flo
                    nullptr, status, max_ctas, stream, a_scales, w_scales);
 }
 
+struct RsArgs {
+  void* const* data = nullptr;      // peer-mapped staging buffers
+  const void* signal = nullptr;     // this rank's signal pad
+  long long half_bytes = 0;
+  int world = 0, rank = 0, rows = 0;
+  int epoch_word = 0;
+};
+
 struct AgArgs {
   const void* maps = nullptr;       // device: [2][world] CUtensorMap over the staging halves
   const void* signal = nullptr;     // this rank's signal pad
@@ -1183,7 +1230,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar, const struct AgArgs* ag);
+                     const ArArgs* ar, const struct AgArgs* ag, const struct RsArgs* rs);
 
 // Row-parallel projection of a tensor-parallel layer in ONE kernel: C = RMSNorm(residual +=
 // sum over ranks of (A @ W^T)) * norm_w  (norm_w null: C = sum (+ residual), residual untouched).
@@ -1217,6 +1264,30 @@ extern "C" int b200_gemm_all_reduce(const void* A, const void* W, void* C, const
   }
   return gemm_impl(A, W, C, bias, residual, M, N, K, lda, ldw, N, 0, 0, 0, BN, splits, cluster, nullptr, nullptr,
                    status, max_ctas, stream, nullptr, nullptr, &ar, nullptr);
+}
+
+// Row-parallel projection whose result is reduce-scattered, first half of the pair: the partial
+// product A @ W^T (M = world * rows) is stored tile by tile into the row owners' staging buffers
+// (slot of this rank) while the GEMM runs.  b200_symm_rs_reduce (collectives file) must follow on
+// the same stream: it signals the peers, waits for all sources and sums the slots.
+extern "C" int b200_gemm_reduce_scatter_push(const void* A, const void* W, const void* bias, int M, int N, int K,
+                                             int lda, int ldw, void* const* data, const void* signal_local,
+                                             long long half_bytes, int world, int rank, int epoch_word,
+                                             int* status, int max_ctas, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || M % world != 0) return -30;
+  if (static_cast<long long>(M) * N * 2 > half_bytes) return -31;
+  RsArgs rs;
+  rs.data = data;
+  rs.signal = signal_local;
+  rs.half_bytes = half_bytes;
+  rs.world = world;
+  rs.rank = rank;
+  rs.rows = M / world;
+  rs.epoch_word = epoch_word;
+  GemmPlan pl = plan_gemm(M, N, K, 2, sm_count(), false, false);
+  // C is never written in this mode; pass the local staging buffer as a valid placeholder
+  return gemm_impl(A, W, data[rank], bias, nullptr, M, N, K, lda, ldw, N, 0, 0, 0, pl.BN, 1, 0, nullptr, nullptr,
+                   status, max_ctas, stream, nullptr, nullptr, nullptr, nullptr, &rs);
 }
 
 // Encodes the tensor maps of the fused all-gather GEMM into `out_host` (2 * world maps of 128
@@ -1266,7 +1337,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
                      int N, int K, int lda, int ldw, int ldc, int dtype_fp8, int out_fp32, int swiglu, int BN,
                      int splits, int cluster_split, void* workspace, int* counters, int* status,
                      int max_ctas, cudaStream_t stream, const float* a_scales, const float* w_scales,
-                     const ArArgs* ar, const AgArgs* ag) {
+                     const ArArgs* ar, const AgArgs* ag, const RsArgs* rs) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = dtype_fp8 ? 1 : 2;
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
@@ -1323,6 +1394,17 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
     p.ag_rows = ag->rows;
     p.ag_epoch_word = ag->epoch_word;
     p.ag_flag_word = ag->flag_word;
+  }
+  if (rs != nullptr && rs->world > 1) {
+    if (splits != 1 || swiglu || out_fp32 || dtype_fp8 || rs->rows <= 0 || rs->rows * rs->world != M || (N % 16) != 0)
+      return -18;
+    for (int r = 0; r < kMaxRanks; ++r) p.rs_data[r] = r < rs->world ? rs->data[r] : nullptr;
+    p.rs_signal = static_cast<const uint32_t*>(rs->signal);
+    p.rs_half_bytes = rs->half_bytes;
+    p.rs_world = rs->world;
+    p.rs_rank = rs->rank;
+    p.rs_rows = rs->rows;
+    p.rs_epoch_word = rs->epoch_word;
   }
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;

@@ -107,6 +107,18 @@ class SequenceParallelStream:
         symm = getattr(self.group.comm, "symm", None)
         if self.fused_gather and symm is not None and normed.is_cuda and normed.shape[0] % 128 == 0:
             # the block's first projection reads the shards from their owners inside its GEMM
-            return self.reduce_scatter(fn(ShardedRows(normed, self))), shard_residual
+            return self._reduced(fn(ShardedRows(normed, self))), shard_residual
         full = self.gather(normed)[: self.num_tokens]
-        return self.reduce_scatter(fn(full)), shard_residual
+        return self._reduced(fn(full)), shard_residual
+
+    def _reduced(self, out) -> torch.Tensor:
+        """Block output -> reduced shard: already reduced inside the block's last GEMM
+        (``layers.linear.ReducedShard``) or a partial sum that still needs the reduce-scatter."""
+        if isinstance(out, torch.Tensor):
+            return self.reduce_scatter(out)
+        return out.tensor
+
+    @property
+    def scatter_mode(self):
+        """What a block passes as ``reduce=`` to its row-parallel projection."""
+        return "scatter" if (self.fused_gather and self.padded == self.num_tokens) else False

@@ -44,6 +44,14 @@ def apply_transform(x: torch.Tensor, kind: Optional[str], group: GroupCoordinato
     raise ValueError(f"unknown transform {kind}")
 
 
+class ReducedShard:
+    """Result of a row-parallel projection that was already reduce-scattered inside its GEMM:
+    ``tensor`` holds this rank's rows of the sum."""
+
+    def __init__(self, tensor: torch.Tensor) -> None:
+        self.tensor = tensor
+
+
 def _sharded_input(layer: "LinearBase", x, swiglu: bool = False, out_dtype=None):
     """Input handed over as token shards (``layers.flashcomm.ShardedRows``): returns
     (y, None) when the gather was fused into the GEMM, else (None, gathered rows)."""
@@ -319,11 +327,22 @@ class RowParallelLinear(LinearBase):
         self._create(self.in_local, out_features, device)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                reduce: bool = True) -> torch.Tensor:
+                reduce=True):
         """``reduce=False`` returns this rank's partial sums; the caller then reduces them
-        itself, typically fused with the following residual add + RMSNorm."""
+        itself, typically fused with the following residual add + RMSNorm.  ``reduce="scatter"``:
+        see below."""
         x = apply_transform(x, self.x_transform, self.group)
         bias = self.bias if self.tp_rank == 0 else None
+        if reduce == "scatter":
+            # token-sharded residual stream: the caller wants this rank's rows of the reduced
+            # product.  With peer memory the GEMM epilogue pushes its tiles to the row owners
+            # and a small kernel sums them (ReducedShard); otherwise the partial goes back and
+            # the caller reduce-scatters it.
+            symm = getattr(self.group.comm, "symm", None) if self.tp_size > 1 else None
+            if (symm is not None and isinstance(self.quant_method, UnquantizedLinearMethod) and residual is None
+                    and symm.can_gemm_reduce_scatter(x, self.weight)):
+                return ReducedShard(symm.gemm_reduce_scatter(x, self.weight, self.bias))
+            return self.quant_method.apply(self, x, bias)
         if self.tp_size == 1 or not self.reduce_results or not reduce:
             return self.quant_method.apply(self, x, bias, residual=residual)
         y = self.quant_method.apply(self, x, bias)

@@ -5,6 +5,8 @@ RMSNorm on q and k (reference: omni_npu/v1/models/qwen/qwen3.py:60-173).
 """
 from __future__ import annotations
 
+import os
+
 from typing import Iterable, Optional, Tuple
 
 import torch
@@ -19,6 +21,7 @@ from ..layers.linear import QKVParallelLinear, RowParallelLinear
 from ..layers.mlp import FusedMLP
 from ..layers.norm import RMSNorm, reduce_add_rms_norm
 from ..layers.rope import get_rope
+from ..attention.metadata import get_forward_context
 from ..parallel import state as pstate
 from .utils import load_stacked_weights
 
@@ -92,14 +95,17 @@ class LlamaDecoderLayer(nn.Module):
 
     def forward_sequence_parallel(self, sp, hidden: Optional[torch.Tensor], residual: torch.Tensor):
         """The same layer on a token-sharded residual stream (layers/flashcomm.py)."""
+        mode = sp.scatter_mode      # "scatter": o_proj / down_proj push their tiles to the row owners
         hidden, residual = sp.block(self.input_layernorm, hidden, residual,
-                                    lambda full: self.self_attn(full, reduce=False))
+                                    lambda full: self.self_attn(full, reduce=mode))
         return sp.block(self.post_attention_layernorm, hidden, residual,
-                        lambda full: self.mlp(full, reduce=False))
+                        lambda full: self.mlp(full, reduce=mode))
 
 
 class LlamaModel(nn.Module):
     sequence_parallel = False       # set by the owning model from ParallelConfig
+    # OMNI_B200_AUTO_SP=0 keeps large prefill steps on the replicated stream (all-reduce after the GEMMs)
+    auto_sequence_parallel = os.environ.get("OMNI_B200_AUTO_SP", "1") != "0"
     fused_tail = True               # GEMM + all-reduce + add + norm in one kernel where possible
 
     def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:
@@ -113,7 +119,17 @@ class LlamaModel(nn.Module):
                 inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
         tp = pstate.get_tp_group()
-        if self.sequence_parallel and tp.world_size > 1:
+        use_sp = self.sequence_parallel
+        if not use_sp and self.auto_sequence_parallel and tp.world_size > 1 and hidden.is_cuda:
+            # prefill steps whose rows split into whole 128-row tiles per rank run on the token-sharded
+            # stream: the all-gathers and reduce-scatters then live inside the projections' GEMMs
+            try:
+                md = get_forward_context().attn_metadata
+            except RuntimeError:          # called outside an engine step
+                md = None
+            use_sp = (md is not None and md.is_prefill and getattr(tp.comm, "symm", None) is not None
+                      and hidden.shape[0] % (128 * tp.world_size) == 0)
+        if use_sp and tp.world_size > 1:
             from ..layers.flashcomm import SequenceParallelStream
             sp = SequenceParallelStream(tp)
             sp.fused_gather = True      # qkv_proj / gate_up_proj read the token shards inside their GEMM

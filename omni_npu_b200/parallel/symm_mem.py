@@ -66,6 +66,10 @@ def _lib() -> ctypes.CDLL:
         lib.b200_gemm_ag_encode_maps.restype = ci
         lib.b200_gemm_all_gather.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp, ci, vp]
         lib.b200_gemm_all_gather.restype = ci
+        lib.b200_gemm_reduce_scatter_push.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, pp, vp, ll, ci, ci, ci, vp, ci, vp]
+        lib.b200_gemm_reduce_scatter_push.restype = ci
+        lib.b200_symm_rs_reduce.argtypes = [pp, pp, ci, ci, sz, vp, ll, ci, vp, vp, ctypes.c_float, vp, vp, vp]
+        lib.b200_symm_rs_reduce.restype = ci
         _LIB = lib
     return _LIB
 
@@ -293,6 +297,42 @@ class SymmetricMemory:
                                       self.status.data_ptr(), 0, self._stream())
         if rc != 0:
             raise RuntimeError(f"fused all_gather + gemm failed ({rc})")
+        ops._count(2)
+        return out
+
+    # ------------------------------------------------ fused GEMM -> reduce-scatter
+    def can_gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        m, n = x.shape[0], w.shape[0]
+        return (self.fuse_ag_gemm and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.dim() == 2 and x.stride(1) == 1 and w.dim() == 2 and w.stride(1) == 1
+                and m >= 128 * self.world and m % self.world == 0 and n % 16 == 0 and n <= 16384
+                and m * n * 2 <= self.half_bytes)
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                            residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                            eps: float = 0.0) -> torch.Tensor:
+        """``reduce_scatter(x @ w.T, dim=0)`` (+bias on one rank) with the transfer inside the GEMM:
+        the epilogue stores every tile row into its owner's staging buffer over NVLink while
+        later tiles are still being computed; a small second kernel signals, waits for all
+        sources and sums this rank's rows (optionally ``+ residual`` and RMSNorm)."""
+        lib = _lib()
+        m, k = x.shape
+        n = w.shape[0]
+        rows = m // self.world
+        rc = lib.b200_gemm_reduce_scatter_push(x.data_ptr(), w.data_ptr(),
+                                               bias.data_ptr() if bias is not None else None, m, n, k, x.stride(0),
+                                               w.stride(0), self.data_ptrs, self.signal_ptrs[self.rank],
+                                               self.half_bytes, self.world, self.rank, lib.b200_symm_epoch_word(),
+                                               self.status.data_ptr(), 0, self._stream())
+        if rc != 0:
+            raise RuntimeError(f"fused gemm + reduce_scatter (push) failed ({rc})")
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+        rc = lib.b200_symm_rs_reduce(self.data_ptrs, self.signal_ptrs, self.world, self.rank, self.half_bytes,
+                                     out.data_ptr(), rows, n, residual.data_ptr() if residual is not None else None,
+                                     norm_weight.data_ptr() if norm_weight is not None else None, eps,
+                                     self.done.data_ptr(), self.status.data_ptr(), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"fused gemm + reduce_scatter (reduce) failed ({rc})")
         ops._count(2)
         return out
 

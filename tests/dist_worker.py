@@ -79,6 +79,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         kw["dtype"] = "float32"
     if os.path.exists(os.path.join(workdir, "sequence_parallel")):
         kw["sequence_parallel_residual"] = True
+    if os.path.exists(os.path.join(workdir, "long_prompts")):
+        kw.update(max_num_batched_tokens=256, max_model_len=512)
     llm = LLM(model=model_dir, **kw)
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs]},
@@ -385,6 +387,40 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
                 symm.all_reduce(torch.ones(8, 64, device=dev, dtype=torch.bfloat16))
         torch.cuda.synchronize()
         res["max_err"][name] = (got.float() - want).abs().max().item()
+    # row-parallel projection + reduce-scatter with the pushes inside the GEMM epilogue
+    for name, m, n, k, bias in (("rs_plain", 256 * world, 1024, 512, False), ("rs_bias", 128 * world, 4096, 1024, True),
+                                ("rs_prefill", 4096, 4096, 2048, False)):
+        x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+        b = torch.randn(n, device=dev, dtype=torch.bfloat16) if bias else None
+        if b is not None:
+            dist.broadcast(b, src=0, group=g.device_group)
+        part = ops.gemm(x, w, b if rank == 0 else None).float()
+        want = torch.empty(m // world, n, device=dev, dtype=torch.float32)
+        dist.reduce_scatter_tensor(want, part, group=g.device_group)
+        for rep in range(3):
+            got = symm.gemm_reduce_scatter(x, w, b)
+            if rep == 1:
+                symm.all_gather_gemm(x[: 128], w)       # a different fused collective in between
+        torch.cuda.synchronize()
+        res["max_err"][name] = (got.float() - want).abs().max().item() / max(1.0, want.abs().max().item())
+    # fused tail: + residual and RMSNorm on the reduced rows
+    m, n, k = 256 * world, 1024, 512
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+    resid = torch.randn(m // world, n, device=dev, dtype=torch.bfloat16)
+    wn = (torch.rand(n, device=dev) + 0.5).bfloat16()
+    dist.broadcast(wn, src=0, group=g.device_group)
+    part = ops.gemm(x, w).float()
+    red = torch.empty(m // world, n, device=dev, dtype=torch.float32)
+    dist.reduce_scatter_tensor(red, part, group=g.device_group)
+    r_ref = resid.clone()
+    y_ref = ops.fused_add_rms_norm(red.bfloat16(), r_ref, wn, 1e-6)
+    r_got = resid.clone()
+    y_got = symm.gemm_reduce_scatter(x, w, None, r_got, wn, 1e-6)
+    torch.cuda.synchronize()
+    res["max_err"]["rs_norm"] = (y_got.float() - y_ref.float()).abs().max().item()
+    res["max_err"]["rs_norm_residual"] = (r_got.float() - r_ref.float()).abs().max().item()
     # timing at a prefill shape: one kernel pair (stage + GEMM) vs all-gather then GEMM
     rows, n, k = 8192 // world, 6144, 4096
     x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
@@ -408,6 +444,14 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     full = gathered(x)
     res["us_gemm_alone"] = timeit(lambda: ops.gemm(full, w))
     res["tflops_fused"] = 2.0 * rows * world * n * k / res["us_fused"] / 1e6
+    # o_proj-shaped row-parallel GEMM (K sharded) + reduce-scatter
+    xo = torch.randn(8192, 4096 // world, device=dev, dtype=torch.bfloat16)
+    wo = torch.randn(4096, 4096 // world, device=dev, dtype=torch.bfloat16) * 0.05
+    outp = torch.empty(8192 // world, 4096, device=dev, dtype=torch.bfloat16)
+    res["us_rs_fused"] = timeit(lambda: symm.gemm_reduce_scatter(xo, wo))
+    res["us_rs_symm_after_gemm"] = timeit(lambda: symm.reduce_scatter(ops.gemm(xo, wo)))
+    res["us_rs_nccl_after_gemm"] = timeit(lambda: dist.reduce_scatter_tensor(outp, ops.gemm(xo, wo), group=g.device_group))
+    res["us_rs_gemm_alone"] = timeit(lambda: ops.gemm(xo, wo))
     torch.cuda.synchronize()
     ops.check_status()
     g.barrier()

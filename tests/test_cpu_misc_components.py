@@ -84,3 +84,24 @@ def test_trace_timers_and_request_lines():
     finally:
         trace.enable(False)
     assert trace.RequestTracer(sink=lambda l: (_ for _ in ()).throw(AssertionError)).trace("x", "r")
+
+
+def test_sharded_rows_fall_back_to_gather_without_peer_memory():
+    """A column-parallel projection handed token shards either fuses the gather into its GEMM
+    (peer memory, GPU) or asks the stream for the gathered rows; on CPU it must be the latter."""
+    import torch
+    from omni_npu_b200.layers.flashcomm import SequenceParallelStream, ShardedRows
+    from omni_npu_b200.layers.linear import ColumnParallelLinear, MergedColumnParallelLinear
+    from omni_npu_b200.parallel import state
+    state.ensure_initialized(torch.device("cpu"))
+    sp = SequenceParallelStream(state.get_tp_group())
+    x = torch.randn(6, 16)
+    shard = sp.scatter(x)
+    lin = ColumnParallelLinear(16, 8, dtype=torch.float32)
+    lin.weight.data.normal_()
+    rows = ShardedRows(shard, sp)
+    assert rows.shape == (6, 16)
+    assert torch.allclose(lin(rows), x @ lin.weight.t(), atol=1e-5)
+    merged = MergedColumnParallelLinear(16, [8, 8], dtype=torch.float32)
+    merged.weight.data.normal_()
+    assert torch.allclose(merged(ShardedRows(shard, sp)), x @ merged.weight.t(), atol=1e-5)

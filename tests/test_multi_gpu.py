@@ -24,13 +24,13 @@ def test_symmetric_memory_collectives_match_nccl():
           res[0]["us_symm_64MiB"], res[0]["us_nccl_64MiB"])
 
 
-def test_fused_all_gather_gemm_matches_gather_then_gemm():
+def test_fused_all_gather_gemm_and_gemm_reduce_scatter():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("ag_gemm", 2, d, device="cuda", timeout=300)
     for r in res:
         for name, err in r["max_err"].items():
-            assert err <= 0.05, (name, err)
-    print("all-gather + GEMM us:", {k: round(v, 1) for k, v in res[0].items() if k.startswith(("us_", "tflops"))})
+            assert err <= (0.13 if name.startswith("rs_norm") else 0.05), (name, err)
+    print("all-gather + GEMM / GEMM + reduce-scatter us:", {k: round(v, 1) for k, v in res[0].items() if k.startswith(("us_", "tflops"))})
 
 
 def test_expert_parallel_moe_dispatch_combine_over_peer_memory():
@@ -73,3 +73,33 @@ def test_tensor_parallel_engine_two_gpus_matches_one_gpu():
     # bf16 partial sums differ in rounding between 1 and 2 GPUs: require the first tokens to agree
     agree = sum(a[:2] == b[:2] for a, b in zip(res[0]["tokens"], want))
     assert agree >= 2
+
+
+def test_tensor_parallel_prefill_on_token_sharded_stream_matches_one_gpu():
+    """A prefill step of 256 tokens on 2 GPUs splits into whole tiles per rank, so the layers run on the
+    token-sharded stream with the all-gather / reduce-scatter inside the GEMMs; tokens must match 1 GPU."""
+    import reference_llama as refm
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    from test_cpu_plumbing import _save
+    cfg = ModelConfig(hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=64,
+                      intermediate_size=1024, vocab_size=1024, rope_theta=10000.0, max_position_embeddings=2048)
+    weights = refm.make_weights(cfg, seed=5, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (128,), generator=g).tolist() for _ in range(2)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        cfgj = json.load(open(os.path.join(d, "model", "config.json")))
+        cfgj["torch_dtype"] = "bfloat16"
+        json.dump(cfgj, open(os.path.join(d, "model", "config.json"), "w"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "long_prompts"), "w").close()
+        res = run_ranks("tp_engine", 2, d, device="cuda", timeout=300)
+        one = LLM(model=os.path.join(d, "model"), device="cuda", max_num_seqs=4, max_num_batched_tokens=256,
+                  max_model_len=512, block_size=16, num_gpu_blocks=64)
+        want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+    assert res[0]["tokens"] == res[1]["tokens"]
+    agree = sum(a[:2] == b[:2] for a, b in zip(res[0]["tokens"], want))
+    assert agree >= 1, (res[0]["tokens"], want)

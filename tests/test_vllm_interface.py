@@ -92,3 +92,32 @@ def test_worker_and_model_adapters():
         assert issubclass(getattr(importlib.import_module(mod), name), StandaloneModelAdapter)
     sig = inspect.signature(StandaloneModelAdapter.__init__)
     assert "vllm_config" in sig.parameters and sig.parameters["vllm_config"].kind is inspect.Parameter.KEYWORD_ONLY
+
+
+def test_thinking_budget_processor_follows_vllm_batch_updates():
+    """Rows added / moved / removed through vLLM's BatchUpdate keep their budget state; a row past its
+    budget is forced to the end marker."""
+    import torch
+    from vllm import SamplingParams
+    from vllm.v1.sample.logits_processor import BatchUpdate, LogitsProcessor, MoveDirectionality
+    from omni_npu_b200.sample.vllm_logits_processor import ThinkingBudgetLogitsProcessor
+    from omni_npu_b200.serving.reasoning_config import ReasoningConfig
+    assert issubclass(ThinkingBudgetLogitsProcessor, LogitsProcessor)
+    cfg = ReasoningConfig(think_start_token_ids=[5], think_end_token_ids=[6])
+    proc = ThinkingBudgetLogitsProcessor(None, torch.device("cpu"), False, reasoning_config=cfg)
+    out0, out1 = [], []
+    sp = SamplingParams(max_tokens=8, extra_args={"thinking_token_budget": 2})
+    ThinkingBudgetLogitsProcessor.validate_params(sp)
+    proc.update_state(BatchUpdate(batch_size=2, removed=[], moved=[],
+                                  added=[(0, sp, [1, 5], out0), (1, SamplingParams(max_tokens=8), [1, 5], out1)]))
+    logits = torch.zeros(2, 10)
+    assert torch.isfinite(proc.apply(logits.clone())).all()           # budget not used up yet
+    out0.extend([7, 8])                                               # two thinking tokens generated
+    got = proc.apply(logits.clone())
+    assert got[0].argmax() == 6 and torch.isinf(got[0, 7]) and torch.isfinite(got[1]).all()
+    # the budgeted row moves to slot 1 (swap), then is removed
+    proc.update_state(BatchUpdate(batch_size=2, removed=[], added=[], moved=[(0, 1, MoveDirectionality.SWAP)]))
+    got = proc.apply(logits.clone())
+    assert got[1].argmax() == 6 and torch.isfinite(got[0]).all()
+    proc.update_state(BatchUpdate(batch_size=1, removed=[1], added=[], moved=[]))
+    assert torch.isfinite(proc.apply(logits.clone())).all() and not proc.inner.state
