@@ -158,6 +158,13 @@ class LLM:
         self.config = config
         self.engine = LLMEngine(config)
 
+    def start_profile(self) -> None:
+        """Start the worker's torch profiler (needs ``VLLM_TORCH_PROFILER_DIR`` at start-up)."""
+        self.engine.worker.profile(True)
+
+    def stop_profile(self) -> None:
+        self.engine.worker.profile(False)
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  ) -> List[RequestOutput]:

@@ -73,6 +73,17 @@ class GroupCoordinator:
     def all_to_all_single(self, x, output_split_sizes=None, input_split_sizes=None):
         return self.comm.all_to_all_single(x, output_split_sizes, input_split_sizes)
 
+    def swap(self, x):
+        """Exchange ``x`` with the other rank of a two-rank group (each side receives the peer's
+        tensor of the same shape); the 2-rank shortcut the reference's v0 coordinator offers
+        for DP<->TP hand-overs (omni_npu/v0/distributed/parallel_state.py:52-208)."""
+        if self.world_size == 1:
+            return x
+        if self.world_size != 2:
+            raise ValueError("swap() is defined for groups of exactly two ranks")
+        both = self.all_gather(x.unsqueeze(0), dim=0)
+        return both[1 - self.rank_in_group].contiguous()
+
     def broadcast(self, x, src=0):
         return self.comm.broadcast(x, src)
 

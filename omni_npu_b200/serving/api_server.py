@@ -132,6 +132,16 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
     def health():
         return {"status": "ok"}
 
+    @app.post("/start_profile")
+    async def start_profile():
+        llm.start_profile()
+        return {"status": "profiling"}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        llm.stop_profile()
+        return {"status": "stopped"}
+
     @app.get("/v1/models")
     def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model"}]}

@@ -53,6 +53,8 @@ def task_comm(rank, world, port, workdir, device_kind):
     res["all_to_all"] = a2a[:, 0].tolist()
     gat = g.comm.gather(torch.full((1, 2), float(rank), device=dev), dst=0, dim=0)
     res["gather"] = gat[:, 0].tolist() if gat is not None else None
+    if world == 2:
+        res["swap"] = g.swap(torch.full((3,), float(rank + 10), device=dev)).tolist()
     if world >= 2:
         if rank == 0:
             g.send(torch.tensor([7.0, 8.0], device=dev), dst=1)

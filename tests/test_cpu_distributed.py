@@ -25,6 +25,7 @@ def test_communicator_semantics_two_ranks():
     assert r0["all_to_all"] == [0.0, 1.0, 100.0, 101.0] and r1["all_to_all"] == [2.0, 3.0, 102.0, 103.0]
     assert r0["gather"] == [0.0, 1.0] and r1["gather"] is None
     assert r1["recv"] == [7.0, 8.0]
+    assert r0["swap"] == [11.0] * 3 and r1["swap"] == [10.0] * 3
     assert r1["bcast_obj"] == {"k": 0}
     assert r0["layer_group"] == [2, 0] and r1["layer_group"] == [2, 1]
 

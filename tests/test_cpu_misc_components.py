@@ -105,3 +105,17 @@ def test_sharded_rows_fall_back_to_gather_without_peer_memory():
     merged = MergedColumnParallelLinear(16, [8, 8], dtype=torch.float32)
     merged.weight.data.normal_()
     assert torch.allclose(merged(ShardedRows(shard, sp)), x @ merged.weight.t(), atol=1e-5)
+
+
+def test_stop_buffer_is_not_applied_inside_the_reasoning_span():
+    from omni_npu_b200.patches.common.think_stream import hold_back, reasoning_finished
+    assert not reasoning_finished([1, 2, 3])
+    assert not reasoning_finished([5, 151668])                   # end marker just emitted, no newline yet
+    assert reasoning_finished([5, 151668, 271, 9])               # Qwen3: </think> then a blank line
+    assert reasoning_finished([128799, 201])                     # DeepSeek-R1
+    assert not reasoning_finished([151668, 7])
+    assert reasoning_finished([9, 8, 7], {8: (7,)})              # ids from a reasoning config
+    assert hold_back(5, finished=False, done_reasoning=False, new_text="abc") == 0
+    assert hold_back(5, finished=False, done_reasoning=True, new_text="x</think>\n") == 0
+    assert hold_back(5, finished=False, done_reasoning=True, new_text="answer") == 5
+    assert hold_back(5, finished=True, done_reasoning=True, new_text="answer") == 0
