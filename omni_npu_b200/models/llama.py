@@ -104,8 +104,9 @@ class LlamaDecoderLayer(nn.Module):
 
 class LlamaModel(nn.Module):
     sequence_parallel = False       # set by the owning model from ParallelConfig
-    # OMNI_B200_AUTO_SP=0 keeps large prefill steps on the replicated stream (all-reduce after the GEMMs)
-    auto_sequence_parallel = os.environ.get("OMNI_B200_AUTO_SP", "1") != "0"
+    # OMNI_B200_AUTO_SP=1: large prefill steps under tensor parallelism run on the token-sharded stream
+    # (all-gather / reduce-scatter inside the GEMMs); default: replicated stream, all-reduce after the GEMMs
+    auto_sequence_parallel = os.environ.get("OMNI_B200_AUTO_SP", "0") == "1"
     fused_tail = True               # GEMM + all-reduce + add + norm in one kernel where possible
 
     def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:

@@ -83,6 +83,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         kw["sequence_parallel_residual"] = True
     if os.path.exists(os.path.join(workdir, "long_prompts")):
         kw.update(max_num_batched_tokens=256, max_model_len=512)
+        from omni_npu_b200.models.llama import LlamaModel
+        LlamaModel.auto_sequence_parallel = True
     llm = LLM(model=model_dir, **kw)
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs]},
