@@ -42,6 +42,10 @@ int b200_quant_int8_per_token(void* q, void* scales, const void* x, long long ro
 int b200_gemm_fp8_block(const void* A, const float* a_scales, const void* W, const float* w_scales, void* C,
                         const void* bias, const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
                         int out_fp32, int* status, int max_ctas, cudaStream_t stream);
+int b200_grouped_gemm_fp8_block(const void* A, const float* a_scales, const void* W, const float* w_scales, void* C,
+                                const int* expert_offsets, int num_experts, int total_rows, int N, int K, int lda,
+                                int ldc, int scale_rows, int swiglu, int up_scale_row0, int* status, int max_ctas,
+                                cudaStream_t stream);
 int b200_dsa_indexer(const void* q, const float* w, const void* cache, const int* block_tables, const int* cu_q,
                      const int* positions, float* scores, int* topk_out, int T, int B, int H, int q_len,
                      long long num_blocks, int block_size, int max_blocks, long long ld, int max_ctx, int max_q,
@@ -386,6 +390,38 @@ Tensor gemm_fp8_block(const Tensor& a, const Tensor& a_scale, const Tensor& w, c
                             c.data_ptr(), bias_p, res_p, (int)M, (int)N, (int)K, (int)a.stride(0), (int)w.stride(0),
                             (int)N, out_fp32 ? 1 : 0, status.data_ptr<int>(), (int)max_ctas, cur_stream()),
         "gemm_fp8_block");
+  return c;
+}
+
+// Grouped block-scaled e4m3 GEMM (MoE experts): a [rows, K] e4m3 + a_scale [rows, K/128]; w [E, N, K] e4m3 +
+// w_scale [E, R, K/128]; expert e owns rows expert_offsets[e] .. [e + 1].  swiglu: gate / up rows of w are
+// interleaved in groups of 8, their scale rows are gate blocks then up blocks (from row up_scale_row0).
+Tensor grouped_gemm_fp8_block(const Tensor& a, const Tensor& a_scale, const Tensor& w, const Tensor& w_scale,
+                              const Tensor& expert_offsets, bool swiglu, int64_t up_scale_row0, const Tensor& status,
+                              int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 3, "grouped_gemm_fp8_block: shapes");
+  TORCH_CHECK(a.scalar_type() == at::kFloat8_e4m3fn && w.scalar_type() == at::kFloat8_e4m3fn,
+              "grouped_gemm_fp8_block: float8_e4m3fn operands");
+  TORCH_CHECK(a.stride(1) == 1 && w.is_contiguous(), "grouped_gemm_fp8_block: contiguity");
+  CHECK_I32(expert_offsets);
+  const int64_t E = w.size(0), N = w.size(1), K = w.size(2), rows = a.size(0);
+  TORCH_CHECK(a.size(1) == K && K % 128 == 0 && expert_offsets.numel() == E + 1, "grouped_gemm_fp8_block: sizes");
+  TORCH_CHECK(a_scale.is_cuda() && a_scale.scalar_type() == at::kFloat && a_scale.is_contiguous() &&
+                  a_scale.numel() == rows * (K / 128), "grouped_gemm_fp8_block: a_scale fp32 [rows, K/128]");
+  TORCH_CHECK(w_scale.is_cuda() && w_scale.scalar_type() == at::kFloat && w_scale.is_contiguous() &&
+                  w_scale.dim() == 3 && w_scale.size(0) == E && w_scale.size(2) == K / 128,
+              "grouped_gemm_fp8_block: w_scale fp32 [E, R, K/128]");
+  const int64_t R = w_scale.size(1);
+  TORCH_CHECK(swiglu ? (N % 256 == 0 && up_scale_row0 + (N / 2 + 127) / 128 <= R) : (N + 127) / 128 <= R,
+              "grouped_gemm_fp8_block: scale rows do not cover the weight rows");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t n_out = swiglu ? N / 2 : N;
+  Tensor c = torch::empty({rows, n_out}, a.options().dtype(at::kBFloat16));
+  check(b200_grouped_gemm_fp8_block(a.data_ptr(), a_scale.data_ptr<float>(), w.data_ptr(), w_scale.data_ptr<float>(),
+                                    c.data_ptr(), expert_offsets.data_ptr<int>(), (int)E, (int)rows, (int)N, (int)K,
+                                    (int)a.stride(0), (int)n_out, (int)R, swiglu ? 1 : 0, (int)up_scale_row0,
+                                    status.data_ptr<int>(), (int)max_ctas, cur_stream()),
+        "grouped_gemm_fp8_block");
   return c;
 }
 
@@ -795,6 +831,7 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("rms_norm_quant", &rms_norm_quant);
   m.def("dsa_indexer", &dsa_indexer);
   m.def("gemm_fp8_block", &gemm_fp8_block);
+  m.def("grouped_gemm_fp8_block", &grouped_gemm_fp8_block);
   m.def("silu_and_mul_quant", &silu_and_mul_quant);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("rms_norm", &rms_norm);

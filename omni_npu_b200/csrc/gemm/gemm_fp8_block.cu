@@ -33,7 +33,7 @@ constexpr int kFbBM = 128, kFbBN = 128, kFbSlab = 128;   // tile and K slab (byt
 constexpr int kFbStages = 6;
 constexpr int kFbStageBytes = (kFbBM + kFbBN) * kFbSlab;  // 32 KB
 constexpr int kFbThreads = 192;
-constexpr size_t kFbSmem = 1024 + static_cast<size_t>(kFbStages) * kFbStageBytes + (2 * kFbStages + 4) * 8 + 32;
+constexpr size_t kFbSmemBase = 1024 + static_cast<size_t>(kFbStages) * kFbStageBytes + (2 * kFbStages + 4) * 8 + 32;
 
 struct Fp8BlockParams {
   int M, N, K;
@@ -47,7 +47,44 @@ struct Fp8BlockParams {
   const __nv_bfloat16* bias;       // [N] or null
   const __nv_bfloat16* residual;   // [M, ldc] or null
   int* status;
+  // grouped (mixture-of-experts) mode, num_experts > 0: A holds every expert's rows back to back,
+  // expert e owns rows expert_offsets[e] .. expert_offsets[e + 1] (device array); W [E, N, K];
+  // w_scales [E, scale_rows, k_iters].
+  const int* expert_offsets;
+  int num_experts;
+  int scale_rows;           // rows of one expert's scale matrix
+  // swiglu: W rows hold gate / up interleaved in groups of 8 (rows 16g .. 16g+7 gate, +8 .. +15 up);
+  // their scale blocks are not interleaved: gate block b at scale row b, up block b at up_scale_row0 + b.
+  // C [.., N / 2] = silu(gate) * up.
+  int swiglu;
+  int up_scale_row0;
 };
+
+constexpr int kFbMaxExperts = 512;
+
+struct FbTile {
+  int m0, m_end, n0, nb, expert;
+};
+
+// Tile t of this problem; grouped: n is the fast index so that concurrently running CTAs share
+// an expert's rows.  s_prefix[e] = number of 128-row blocks of the experts before e.
+__device__ __forceinline__ void fb_decode(const Fp8BlockParams& p, const int* s_prefix, long long t, int& cursor,
+                                          FbTile& tc) {
+  if (p.num_experts == 0) {
+    tc.m0 = static_cast<int>(t % p.num_m_blocks) * kFbBM;
+    tc.m_end = p.M;
+    tc.nb = static_cast<int>(t / p.num_m_blocks);
+    tc.expert = 0;
+  } else {
+    const int mblk = static_cast<int>(t / p.num_n_blocks);
+    tc.nb = static_cast<int>(t % p.num_n_blocks);
+    while (cursor + 1 < p.num_experts && s_prefix[cursor + 1] <= mblk) ++cursor;
+    tc.expert = cursor;
+    tc.m0 = p.expert_offsets[cursor] + (mblk - s_prefix[cursor]) * kFbBM;
+    tc.m_end = p.expert_offsets[cursor + 1];
+  }
+  tc.n0 = tc.nb * kFbBN;
+}
 
 __global__ void __launch_bounds__(kFbThreads)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -64,8 +101,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   uint64_t* part_empty = part_full + 2;      // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + 2);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+  int* s_prefix = s_abort + 1;               // [num_experts + 1] (grouped)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (p.num_experts > 0) pdl_wait();         // the expert offsets come from the routing kernels ahead
   if (threadIdx.x == 0) {
     for (int s = 0; s < kFbStages; ++s) {
       mbar_init(&full[s], 1);
@@ -80,6 +119,14 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_w);
   }
+  if (p.num_experts > 0 && threadIdx.x == 64) {
+    int acc = 0;
+    for (int e = 0; e < p.num_experts; ++e) {
+      s_prefix[e] = acc;
+      acc += (p.expert_offsets[e + 1] - p.expert_offsets[e] + kFbBM - 1) / kFbBM;
+    }
+    s_prefix[p.num_experts] = acc;
+  }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
@@ -91,7 +138,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   volatile int* abort_flag = s_abort;
   pdl_trigger();
   pdl_wait();
-  const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
+  const long long tiles = p.num_experts > 0 ? static_cast<long long>(s_prefix[p.num_experts]) * p.num_n_blocks
+                                            : static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -100,9 +148,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
+      int cursor = 0;
+      FbTile tc;
       for (long long t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
-        const int m0 = static_cast<int>(t % p.num_m_blocks) * kFbBM;
-        const int n0 = static_cast<int>(t / p.num_m_blocks) * kFbBN;
+        fb_decode(p, s_prefix, t, cursor, tc);
+        const int m0 = tc.m0, n0 = tc.n0;
         for (int kb = 0; kb < p.k_iters; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
@@ -112,7 +162,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           }
           mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(kFbStageBytes));
           tma_load_2d(s_a + stage * kFbBM * kFbSlab, &tm_a, &full[stage], kb * kFbSlab, m0);
-          tma_load_2d(s_w + stage * kFbBN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0);
+          if (p.num_experts > 0)
+            tma_load_3d(s_w + stage * kFbBN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0, tc.expert);
+          else
+            tma_load_2d(s_w + stage * kFbBN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0);
           ++issued;
           if (++stage == kFbStages) {
             stage = 0;
@@ -177,21 +230,31 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     int pb = 0;
     uint32_t pph = 0;
     bool ok = true;
+    int cursor = 0;
+    FbTile tc;
     for (long long t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
-      const int m0 = static_cast<int>(t % p.num_m_blocks) * kFbBM;
-      const int nb = static_cast<int>(t / p.num_m_blocks);
-      const int n0 = nb * kFbBN;
-      const int row = m0 + r;
-      const bool row_ok = row < p.M;
+      fb_decode(p, s_prefix, t, cursor, tc);
+      const int n0 = tc.n0;
+      const int row = tc.m0 + r;
+      const bool row_ok = row < tc.m_end;
       const float* a_s = p.a_scales + static_cast<long long>(row_ok ? row : 0) * p.k_iters;
-      const float* w_s = p.w_scales + static_cast<long long>(nb) * p.k_iters;
+      const float* w_base = p.w_scales + static_cast<long long>(tc.expert) * p.scale_rows * p.k_iters;
+      // scale row of the tile's columns; with SwiGLU the gate and the up columns have one each
+      const float* w_s = w_base + static_cast<long long>(p.swiglu ? (n0 >> 1) / 128 : tc.nb) * p.k_iters;
+      const float* w_s2 = p.swiglu ? w_base + static_cast<long long>(p.up_scale_row0 + (n0 >> 1) / 128) * p.k_iters
+                                   : w_s;
       float acc[kFbBN];
 #pragma unroll
       for (int c = 0; c < kFbBN; ++c) acc[c] = 0.f;
-      float s_next = (row_ok ? a_s[0] : 0.f) * w_s[0];
+      const float a0 = row_ok ? a_s[0] : 0.f;
+      float s_next = a0 * w_s[0], s2_next = a0 * w_s2[0];
       for (int kb = 0; kb < p.k_iters; ++kb) {
-        const float s = s_next;
-        if (kb + 1 < p.k_iters) s_next = (row_ok ? a_s[kb + 1] : 0.f) * w_s[kb + 1];   // off the critical path
+        const float s = s_next, s2 = s2_next;
+        if (kb + 1 < p.k_iters) {                     // off the critical path
+          const float a1 = row_ok ? a_s[kb + 1] : 0.f;
+          s_next = a1 * w_s[kb + 1];
+          s2_next = a1 * w_s2[kb + 1];
+        }
         // every warp of the group decides alike: they all wait on the same barrier phase
         const bool mine = !*abort_flag && mbar_wait(&part_full[pb], pph);
         if (!__all_sync(0xffffffffu, mine)) {
@@ -207,7 +270,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(s, __uint_as_float(v[i]), acc[c0 + i]);
+          for (int i = 0; i < 32; ++i)      // columns 8..15 of every 16 are "up" columns under SwiGLU
+            acc[c0 + i] = fmaf(((i >> 3) & 1) ? s2 : s, __uint_as_float(v[i]), acc[c0 + i]);
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -218,7 +282,28 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
       }
       if (!ok) break;
-      if (row_ok) {
+      if (row_ok && p.swiglu) {
+        // 64 outputs per row: silu(gate) * up, gate / up interleaved in groups of 8 columns (N % 16 == 0)
+        __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + (n0 >> 1);
+        const int nout = min(kFbBN, p.N - n0) >> 1;
+#pragma unroll
+        for (int g = 0; g < kFbBN / 16; ++g) {
+          if (g * 8 < nout) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float gt = acc[g * 16 + i];
+              o[i] = (gt / (1.f + __expf(-gt))) * acc[g * 16 + 8 + i];
+            }
+            uint4 pk;
+            pk.x = pack_bf16x2(o[0], o[1]);
+            pk.y = pack_bf16x2(o[2], o[3]);
+            pk.z = pack_bf16x2(o[4], o[5]);
+            pk.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(crow + g * 8) = pk;
+          }
+        }
+      } else if (row_ok) {
         const int ncols = min(kFbBN, p.N - n0);
         if (p.out_fp32) {
           float* crow = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + n0;
@@ -279,6 +364,28 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 
 using namespace b200;
 
+static int fb_launch(const CUtensorMap& ta, const CUtensorMap& tw, const Fp8BlockParams& p, long long tiles,
+                     int max_ctas, cudaStream_t stream) {
+  const size_t smem = kFbSmemBase + (static_cast<size_t>(p.num_experts) + 2) * 4;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return -20;
+    configured = smem;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = sms;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  if (grid < 1) grid = 1;
+  return launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(kFbThreads), smem, stream, 1, ta, tw, p) == cudaSuccess
+             ? 0
+             : -21;
+}
+
 // A [M, K] e4m3 (pitch lda bytes), a_scales [M, K/128]; W [N, K] e4m3 (pitch ldw), w_scales
 // [ceil(N/128), K/128]; C [M, N] bf16 or fp32 (pitch ldc elements).  K must be a multiple of 128.
 extern "C" int b200_gemm_fp8_block(const void* A, const float* a_scales, const void* W, const float* w_scales,
@@ -302,6 +409,7 @@ extern "C" int b200_gemm_fp8_block(const void* A, const float* a_scales, const v
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.status = status;
+  p.scale_rows = p.num_n_blocks;
   CUtensorMap ta, tw;
   int r = make_tensormap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, lda, kFbBM, kFbSlab,
                             CU_TENSOR_MAP_SWIZZLE_128B);
@@ -309,21 +417,48 @@ extern "C" int b200_gemm_fp8_block(const void* A, const float* a_scales, const v
   r = make_tensormap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K, ldw, kFbBN, kFbSlab,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kFbSmem)) != cudaSuccess)
-      return -20;
-    configured = true;
-  }
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
-  int grid = sms;
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (tiles < grid) grid = static_cast<int>(tiles);
-  return launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(kFbThreads), kFbSmem, stream, 1, ta, tw, p) == cudaSuccess
-             ? 0
-             : -21;
+  return fb_launch(ta, tw, p, tiles, max_ctas, stream);
+}
+
+// Grouped (mixture-of-experts) variant.  A [total_rows, K] e4m3 holds every expert's rows back to
+// back (expert_offsets [E + 1] on the device), a_scales [total_rows, K/128]; W [E, N, K] e4m3,
+// w_scales [E, scale_rows, K/128].  swiglu = 1: W's gate / up rows are interleaved in groups of 8
+// and C [total_rows, N/2] = silu(gate) * up; the scale rows are gate blocks 0.., then up blocks
+// from row up_scale_row0.  C is bf16.
+extern "C" int b200_grouped_gemm_fp8_block(const void* A, const float* a_scales, const void* W, const float* w_scales,
+                                           void* C, const int* expert_offsets, int num_experts, int total_rows,
+                                           int N, int K, int lda, int ldc, int scale_rows, int swiglu,
+                                           int up_scale_row0, int* status, int max_ctas, cudaStream_t stream) {
+  if (total_rows <= 0 || num_experts <= 0) return 0;
+  if (num_experts > kFbMaxExperts) return -13;
+  if ((K % kFbSlab) != 0) return -10;
+  if (swiglu && (N % 16) != 0) return -11;
+  Fp8BlockParams p{};
+  p.M = total_rows;
+  p.N = N;
+  p.K = K;
+  p.k_iters = K / kFbSlab;
+  p.num_m_blocks = 0;
+  p.num_n_blocks = (N + kFbBN - 1) / kFbBN;
+  p.a_scales = a_scales;
+  p.w_scales = w_scales;
+  p.C = C;
+  p.ldc = ldc;
+  p.status = status;
+  p.expert_offsets = expert_offsets;
+  p.num_experts = num_experts;
+  p.scale_rows = scale_rows;
+  p.swiglu = swiglu;
+  p.up_scale_row0 = up_scale_row0;
+  CUtensorMap ta, tw;
+  int r = make_tensormap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, total_rows, K, lda, kFbBM, kFbSlab,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+  r = make_tensormap_3d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, num_experts, N, K,
+                        static_cast<uint64_t>(N) * K, K, kFbBN, kFbSlab, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 1000;
+  // upper bound on the tiles (the kernel computes the exact count from the offsets)
+  const long long tiles = (static_cast<long long>(total_rows) / kFbBM + num_experts) * p.num_n_blocks;
+  return fb_launch(ta, tw, p, tiles, max_ctas, stream);
 }

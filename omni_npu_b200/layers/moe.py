@@ -163,6 +163,8 @@ class FusedMoE(nn.Module):
         if self.quant != "fp8" or self.w13.dtype != torch.float8_e4m3fn:
             return
         i, h = self.intermediate_size, self.hidden_size
+        if self.w13.is_cuda and h % 128 == 0 and i % 128 == 0:
+            return        # stays e4m3: the grouped block-scaled kernel consumes weights and scales as loaded
         dev = self.w13.device
         r = torch.arange(2 * i, device=dev)
         is_up = (r // 8) % 2
@@ -243,8 +245,17 @@ class FusedMoE(nn.Module):
                 with torch.cuda.stream(self._side_stream):
                     shared_out = self.shared_experts(x)
             rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_physical, self.buffers)
-            h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
-            y = ops.grouped_gemm(h1, self.w2, offsets)
+            if self.quant == "fp8":
+                # block-scaled e4m3 experts: quantise the dispatched rows per token per 128 columns,
+                # SwiGLU fused into the first product's epilogue, requantise, second product
+                rq, rs = ops.quant_fp8_1x128(rows)
+                h1 = ops.grouped_gemm_fp8_block(rq, rs, self.w13, self.w13_scale, offsets, swiglu=True,
+                                                up_scale_row0=(self.intermediate_size + 127) // 128)
+                hq, hs = ops.quant_fp8_1x128(h1)
+                y = ops.grouped_gemm_fp8_block(hq, hs, self.w2, self.w2_scale, offsets)
+            else:
+                h1 = ops.grouped_gemm(rows, self.w13, offsets, swiglu=True)
+                y = ops.grouped_gemm(h1, self.w2, offsets)
             self.buffers.expert_y[: y.shape[0]].copy_(y)
             if shared_out is not None:
                 torch.cuda.current_stream(x.device).wait_stream(self._side_stream)

@@ -216,6 +216,21 @@ def gemm_fp8_block(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.Tensor, 
                                out_dtype == torch.float32, st.status, max_ctas)
 
 
+def grouped_gemm_fp8_block(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor,
+                           expert_offsets: torch.Tensor, swiglu: bool = False, up_scale_row0: int = 0,
+                           max_ctas: int = 0) -> torch.Tensor:
+    """Per-expert block-scaled e4m3 GEMM: rows ``expert_offsets[e]:expert_offsets[e+1]`` of ``a_q`` times
+    ``w_q[e].T`` with ``w_scale[e]`` (one scale per 128 x 128 block).  ``swiglu``: gate / up rows of
+    ``w_q`` are interleaved in groups of 8 and the result is ``silu(gate) * up``; the scale rows are the
+    gate blocks followed, from row ``up_scale_row0``, by the up blocks."""
+    if not a_q.is_cuda:
+        return ref.grouped_gemm_fp8_block(a_q, a_scale, w_q, w_scale, expert_offsets, swiglu, up_scale_row0)
+    st = device_state(a_q.device)
+    _count(1)
+    return _C().grouped_gemm_fp8_block(a_q, a_scale.contiguous(), w_q, w_scale.contiguous(), expert_offsets, swiglu,
+                                       up_scale_row0, st.status, max_ctas)
+
+
 def dsa_indexer_topk(q: torch.Tensor, w: torch.Tensor, index_cache: torch.Tensor, block_tables: torch.Tensor,
                      positions: torch.Tensor, num_seqs: int, topk: int, cu_q: Optional[torch.Tensor] = None,
                      q_len: int = 1, max_ctx: int = 0, max_q: int = 0, return_scores: bool = False):

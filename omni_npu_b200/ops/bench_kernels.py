@@ -2,7 +2,7 @@
 
     python -m omni_npu_b200.ops.bench_kernels gemm            # GEMM shapes of the serving configs
     python -m omni_npu_b200.ops.bench_kernels gemm --m 128 --n 4096 --k 4096 --bn 128 --splits 4
-    python -m omni_npu_b200.ops.bench_kernels attn | norm | sample | indexer | all
+    python -m omni_npu_b200.ops.bench_kernels attn | norm | sample | indexer | quant | all
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed
 (a 256 MB buffer is rewritten) before every timed launch, median of the timed
@@ -214,6 +214,35 @@ def bench_sample(args):
               f"top-k/top-p sample {t1*1e3:7.1f} us")
 
 
+def bench_quant(args):
+    """Quantised GEMMs at a prefill and a decode shape: per-token x per-channel scaled e4m3 / int8
+    (one accumulation, scales in the epilogue) and 128 x 128 block-scaled e4m3 (per-slab promotion)."""
+    from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
+    _, flops, src = peaks()
+    print(f"# quantised GEMMs, TFLOP/s and fraction of the {src} bf16 peak (fp8 / int8 nominal peak is 2x bf16)")
+    for m, n, k in ((8192, 4096, 4096), (8192, 7168, 2048), (128, 4096, 7168)):
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.float32) * 0.05
+        fl = 2.0 * m * n * k
+        t = time_fn(lambda: ops.gemm(x, w.bfloat16()), iters=args.iters)
+        print(f"bf16            [{m},{n},{k}]: {t*1e3:8.1f} us {fl/t/1e9:7.1f} TFLOP/s frac {fl/flops/(t/1e3):.2f}")
+        wq, ws = quantize_weight_block(w)
+        xq, xs = ops.quant_fp8_1x128(x)
+        t = time_fn(lambda: ops.gemm_fp8_block(xq, xs, wq, ws), iters=args.iters)
+        print(f"e4m3 128x128    [{m},{n},{k}]: {t*1e3:8.1f} us {fl/t/1e9:7.1f} TFLOP/s frac {fl/flops/(t/1e3):.2f}")
+        wr = (w / w.abs().amax(1, keepdim=True) * 448).to(torch.float8_e4m3fn)
+        wsr = (w.abs().amax(1) / 448).float()
+        xr = (x.float() / x.float().abs().amax(1, keepdim=True) * 448).to(torch.float8_e4m3fn)
+        xsr = (x.float().abs().amax(1) / 448).float()
+        t = time_fn(lambda: ops.gemm_scaled(xr, wr, xsr, wsr), iters=args.iters)
+        print(f"e4m3 row x col  [{m},{n},{k}]: {t*1e3:8.1f} us {fl/t/1e9:7.1f} TFLOP/s frac {fl/flops/(t/1e3):.2f}")
+        xi, xsi = ops.quant_int8_per_token(x)
+        wi = torch.round(w / w.abs().amax(1, keepdim=True) * 127).to(torch.int8)
+        wsi = (w.abs().amax(1) / 127).float()
+        t = time_fn(lambda: ops.gemm_scaled(xi, wi, xsi, wsi), iters=args.iters)
+        print(f"int8 row x col  [{m},{n},{k}]: {t*1e3:8.1f} us {fl/t/1e9:7.1f} TFLOP/s frac {fl/flops/(t/1e3):.2f}")
+
+
 def bench_indexer(args):
     """Sparse-attention indexer (64 heads x 128 dims, page 16, top-2048): decode batches and one
     prefill chunk.  Bytes = the index keys read once; FLOPs = 2 * heads * 128 per (token, key)."""
@@ -243,7 +272,7 @@ def bench_indexer(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "indexer", "all"])
+    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "indexer", "quant", "all"])
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
@@ -268,6 +297,8 @@ def main():
         bench_sample(args)
     if args.what in ("indexer", "all"):
         bench_indexer(args)
+    if args.what in ("quant", "all"):
+        bench_quant(args)
 
 
 if __name__ == "__main__":

@@ -491,3 +491,27 @@ def gemm_fp8_block(a_q, a_scale, w_q, w_scale, bias=None, residual=None, out_dty
     if residual is not None:
         y = y + residual.float()
     return y.to(out_dtype or torch.bfloat16)
+
+
+def grouped_gemm_fp8_block(a_q, a_scale, w_q, w_scale, expert_offsets, swiglu=False, up_scale_row0=0):
+    """fp32 reference of the grouped block-scaled product (see ``ops.grouped_gemm_fp8_block``)."""
+    e, n, k = w_q.shape
+    a = a_q.float() * a_scale.float().repeat_interleave(128, dim=1)[:, :k]
+    out = torch.zeros(a.shape[0], n // 2 if swiglu else n, dtype=torch.float32, device=a.device)
+    offs = expert_offsets.tolist()
+    r = torch.arange(n, device=a.device)
+    for i in range(e):
+        if swiglu:
+            half = n // 2
+            src = (r // 16) * 8 + r % 8
+            blk = src // 128 + ((r // 8) % 2) * up_scale_row0
+        else:
+            blk = r // 128
+        s = w_scale[i][blk].float().repeat_interleave(128, dim=1)[:, :k]
+        w = w_q[i].float() * s
+        y = a[offs[i]: offs[i + 1]] @ w.t()
+        if swiglu:
+            y = y.view(-1, n // 16, 2, 8)
+            y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(-1, half)
+        out[offs[i]: offs[i + 1]] = y
+    return out.to(torch.bfloat16)

@@ -606,3 +606,66 @@ def test_gemm_fp8_block_scaled(m, n, k):
     got16 = fp8_block_gemm(x, wq, ws, bias, res)
     assert got16.dtype == torch.bfloat16
     _close(got16, want, 2e-2 * float(want.abs().max()), 2e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_gemm_fp8_block_scaled(swiglu):
+    """Expert GEMM on block-scaled e4m3 weights; with SwiGLU the gate / up rows are interleaved in groups
+    of 8 while their scale blocks stay in checkpoint order (gate blocks, then up blocks)."""
+    from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
+    torch.manual_seed(41)
+    e, k, inter = 4, 512, 256
+    n = 2 * inter if swiglu else 384
+    counts = [130, 0, 7, 300]
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    rows = int(offs[-1])
+    x = torch.randn(rows + 50, k, device=DEV, dtype=torch.bfloat16)          # rows past the last expert are unused
+    xq, xs = ops.quant_fp8_1x128(x)
+    wq = torch.empty(e, n, k, dtype=torch.float8_e4m3fn, device=DEV)
+    up0 = (inter + 127) // 128
+    ws = torch.empty(e, (2 * up0) if swiglu else (n + 127) // 128, k // 128, device=DEV)
+    for i in range(e):
+        w = torch.randn(n, k, device=DEV) * 0.05 * torch.logspace(-1, 1, k // 128, device=DEV).repeat_interleave(128)
+        if swiglu:
+            qg, sg = quantize_weight_block(w[:inter])
+            qu, su = quantize_weight_block(w[inter:])
+            j = torch.arange(inter, device=DEV)
+            wq[i, (j // 8) * 16 + j % 8] = qg
+            wq[i, (j // 8) * 16 + 8 + j % 8] = qu
+            ws[i, :up0], ws[i, up0:] = sg, su
+        else:
+            wq[i], ws[i] = quantize_weight_block(w)
+    want = ref.grouped_gemm_fp8_block(xq.cpu(), xs.cpu(), wq.cpu(), ws.cpu(), offs, swiglu, up0 if swiglu else 0)
+    got = ops.grouped_gemm_fp8_block(xq, xs, wq, ws, offs.to(DEV), swiglu, up0 if swiglu else 0)
+    scale = float(want[:rows].float().abs().max())
+    _close(got[:rows], want[:rows], 2e-2 * scale, 2e-2)
+
+
+def test_fused_moe_layer_with_block_scaled_fp8_experts():
+    """MoE layer whose experts stay in block-scaled e4m3 on the GPU (grouped block-scaled kernel with the
+    SwiGLU epilogue) against the same layer with the weights expanded to fp32 on the CPU."""
+    from omni_npu_b200.layers.moe import FusedMoE
+    from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
+    torch.manual_seed(2)
+    e, k, h, inter = 8, 2, 256, 256
+    kw = dict(num_experts=e, top_k=k, hidden_size=h, intermediate_size=inter, renormalize=True, max_tokens=512,
+              quant="fp8")
+    gpu = FusedMoE(dtype=torch.bfloat16, device=DEV, **kw)
+    cpu = FusedMoE(dtype=torch.float32, **kw)
+    gate_w = torch.randn(e, h) * 0.3
+    gpu.gate.weight.data.copy_(gate_w.to(DEV))
+    cpu.gate.weight.data.copy_(gate_w)
+    for i in range(e):
+        for shard, shape, pname, sname in (("gate", (inter, h), "w13", "w13_scale"), ("up", (inter, h), "w13", "w13_scale"),
+                                           ("down", (h, inter), "w2", "w2_scale")):
+            wq, ws = quantize_weight_block(torch.randn(*shape) * 0.05 * torch.logspace(-0.5, 0.5, shape[0]).unsqueeze(1))
+            for layer in (gpu, cpu):
+                layer.weight_loader(getattr(layer, pname), wq, i, shard)
+                layer.weight_loader(getattr(layer, sname), ws, i, shard)
+    gpu.process_weights_after_loading()
+    cpu.process_weights_after_loading()
+    assert gpu.w13.dtype == torch.float8_e4m3fn and cpu.w13.dtype == torch.float32
+    for t in (3, 200):
+        x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+        want = cpu(x.cpu().float())
+        _close(gpu(x), want, 5e-2 * float(want.abs().max()), 5e-2)
