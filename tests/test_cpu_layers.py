@@ -1,0 +1,128 @@
+"""Layer-level unit tests on CPU: rotary-embedding family, norms, activation, embedding sharding."""
+import math
+
+import pytest
+import torch
+
+from omni_npu_b200.layers.rope import get_rope, yarn_get_mscale
+
+
+def _rot_ref(x, pos, inv, mscale, neox=True):
+    """Explicit complex rotation of [T, D] with frequencies inv [D/2]."""
+    ang = pos.float().unsqueeze(1) * inv.unsqueeze(0)
+    cos, sin = ang.cos() * mscale, ang.sin() * mscale
+    if neox:
+        a, b = x[:, : x.shape[1] // 2], x[:, x.shape[1] // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=1)
+    a, b = x[:, 0::2], x[:, 1::2]
+    out = torch.empty_like(x)
+    out[:, 0::2], out[:, 1::2] = a * cos - b * sin, b * cos + a * sin
+    return out
+
+
+@pytest.mark.parametrize("neox", [True, False])
+def test_default_rope_rotates_like_the_closed_form(neox):
+    d = 16
+    rope = get_rope(d, d, 128, 10000.0, neox)
+    q, k = torch.randn(5, 2 * d), torch.randn(5, d)
+    pos = torch.tensor([0, 1, 7, 100, 127], dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))
+    want_q = torch.cat([_rot_ref(q[:, :d], pos, inv, 1.0, neox), _rot_ref(q[:, d:], pos, inv, 1.0, neox)], 1)
+    want_k = _rot_ref(k, pos, inv, 1.0, neox)
+    gq, gk = rope(pos, q.clone(), k.clone())
+    assert torch.allclose(gq, want_q, atol=1e-5) and torch.allclose(gk, want_k, atol=1e-5)
+    cos, sin = rope.get_cos_sin(pos)
+    assert cos.shape == (5, d // 2) and torch.allclose(cos[0], torch.ones(d // 2)) and torch.allclose(sin[0], torch.zeros(d // 2))
+
+
+def test_partial_rotary_leaves_the_tail_dims_alone():
+    rope = get_rope(16, 8, 64, 10000.0, True)
+    q, k = torch.randn(3, 16), torch.randn(3, 16)
+    gq, _ = rope(torch.tensor([1, 2, 3], dtype=torch.int32), q.clone(), k.clone())
+    assert torch.equal(gq[:, 8:], q[:, 8:]) and not torch.allclose(gq[:, :8], q[:, :8])
+
+
+def test_scaled_variants_frequencies_and_amplitudes():
+    d, base = 32, 10000.0
+    inv0 = 1.0 / (base ** (torch.arange(0, d, 2).float() / d))
+
+    def table(rope):
+        # angle of position 1 = inv_freq (while < pi), amplitude = mscale
+        cs = rope.cos_sin_cache[1]
+        return torch.atan2(cs[d // 2:], cs[: d // 2]), torch.sqrt(cs[: d // 2] ** 2 + cs[d // 2:] ** 2)
+
+    lin = get_rope(d, d, 64, base, True, {"rope_type": "linear", "factor": 4.0})
+    ang, amp = table(lin)
+    assert torch.allclose(ang, inv0 / 4.0, atol=1e-6) and torch.allclose(amp, torch.ones_like(amp), atol=1e-6)
+    assert lin.cos_sin_cache.shape[0] == 256                                # table extended by the factor
+
+    l3 = get_rope(d, d, 64, base, True, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                         "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
+    ang, _ = table(l3)
+    assert torch.allclose(ang[0], inv0[0], atol=1e-6)                       # short wavelengths untouched
+    assert torch.allclose(ang[-1], inv0[-1] / 8.0, atol=1e-7)               # long wavelengths divided by the factor
+    assert ((ang <= inv0 + 1e-7) & (ang >= inv0 / 8.0 - 1e-7)).all()
+
+    yarn = get_rope(d, d, 64, base, True, {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64})
+    ang, amp = table(yarn)
+    assert torch.allclose(amp, torch.full_like(amp, yarn_get_mscale(4.0)), atol=1e-5)
+    assert torch.allclose(ang[0], inv0[0], atol=1e-6) and torch.allclose(ang[-1], inv0[-1] / 4.0, atol=1e-7)
+    assert yarn.cos_sin_cache.shape[0] == 256
+
+    ds = get_rope(d, d, 64, base, True, {"rope_type": "deepseek_yarn", "factor": 40.0, "mscale": 1.0,
+                                         "mscale_all_dim": 1.0, "original_max_position_embeddings": 64})
+    _, amp = table(ds)
+    assert torch.allclose(amp, torch.ones_like(amp), atol=1e-5)             # mscale / mscale_all_dim cancel
+
+    ntk = get_rope(d, d, 256, base, True, {"rope_type": "ntk", "factor": 2.0, "original_max_position_embeddings": 64})
+    ang, _ = table(ntk)
+    new_base = base * ((2.0 * 256 / 64) - 1.0) ** (d / (d - 2))
+    assert torch.allclose(ang, 1.0 / (new_base ** (torch.arange(0, d, 2).float() / d)), atol=1e-6)
+
+    lr = get_rope(d, d, 256, base, True, {"rope_type": "longrope", "original_max_position_embeddings": 64,
+                                          "long_factor": [2.0] * (d // 2), "short_factor": [1.0] * (d // 2)})
+    ang, amp = table(lr)
+    assert torch.allclose(ang, inv0 / 2.0, atol=1e-6)
+    assert torch.allclose(amp, torch.full_like(amp, math.sqrt(1 + math.log(4.0) / math.log(64))), atol=1e-5)
+    with pytest.raises(ValueError):
+        get_rope(d, d, 64, base, True, {"rope_type": "nope"})
+
+
+def test_rope_instances_are_cached_per_configuration():
+    a = get_rope(16, 16, 64, 10000.0, True, {"rope_type": "linear", "factor": 2.0})
+    assert get_rope(16, 16, 64, 10000.0, True, {"rope_type": "linear", "factor": 2.0}) is a
+    assert get_rope(16, 16, 64, 10000.0, True, {"rope_type": "linear", "factor": 3.0}) is not a
+
+
+def test_mrope_sections_take_their_axis_positions():
+    """M-RoPE: frequency index i takes the position of the axis its section names (t, h, w)."""
+    d = 16
+    rope = get_rope(d, d, 64, 10000.0, True, {"rope_type": "mrope", "mrope_section": [4, 2, 2]})
+    pos = torch.tensor([[3, 5], [10, 1], [20, 2]], dtype=torch.int32)       # [3 axes, T]
+    q, k = torch.randn(2, d), torch.randn(2, d)
+    gq, _ = rope(pos, q.clone(), k.clone())
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))
+    axis = torch.tensor([0] * 4 + [1] * 2 + [2] * 2)
+    per_freq_pos = pos.float()[axis, :].t()                                 # [T, d/2]
+    ang = per_freq_pos * inv
+    a, b = q[:, : d // 2], q[:, d // 2:]
+    want = torch.cat([a * ang.cos() - b * ang.sin(), b * ang.cos() + a * ang.sin()], 1)
+    assert torch.allclose(gq, want, atol=1e-5)
+
+
+def test_norm_and_activation_layers_match_formulas():
+    from omni_npu_b200.layers.activation import SiluAndMul
+    from omni_npu_b200.layers.norm import LayerNorm, RMSNorm
+    x, r = torch.randn(4, 32), torch.randn(4, 32)
+    n = RMSNorm(32, 1e-5, torch.float32)
+    n.weight.data = torch.rand(32) + 0.5
+    want = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * n.weight
+    assert torch.allclose(n(x), want, atol=1e-5)
+    r0 = r.clone()
+    y, res = n(x, r)
+    s = x + r0
+    assert torch.allclose(res, s) and torch.allclose(y, s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * n.weight, atol=1e-5)
+    ln = LayerNorm(32, 1e-6, torch.float32, None)
+    assert torch.allclose(ln(x), torch.nn.functional.layer_norm(x, (32,), ln.weight, ln.bias, 1e-6), atol=1e-5)
+    g = torch.randn(3, 16)
+    assert torch.allclose(SiluAndMul()(g), torch.nn.functional.silu(g[:, :8]) * g[:, 8:], atol=1e-6)
