@@ -251,6 +251,10 @@ class ParallelConfig:
     # keep the residual stream sharded by tokens inside the tensor-parallel group
     # (reduce-scatter / all-gather around every block instead of all-reduce)
     sequence_parallel_residual: bool = False
+    # expert-parallel load balancing: spare expert slots that hold copies of the hottest experts, and
+    # how often (engine steps, 0 = never) the placement is re-planned from the measured load
+    num_redundant_experts: int = 0
+    eplb_step_interval: int = 0
     # per-layer overrides: {"layer name suffix": {"tp_size_or_ranks": ..., "x_transform": ..., ...}}
     layer_parallel_config: Dict[str, Any] = field(default_factory=dict)
 

@@ -91,7 +91,21 @@ class LLMEngine:
         st["output_tokens"] += sum(len(s.request.output_token_ids) for s in out.seqs) - before
         for r in finished:
             self.worker.model_runner.input_batch.remove_request(r.request_id)
+        interval = self.config.parallel.eplb_step_interval
+        if interval > 0 and st["steps"] % interval == 0:
+            self.rebalance_experts()
         return [RequestOutput.from_request(r) for r in finished]
+
+    def rebalance_experts(self) -> int:
+        """Re-plan the expert placement of every MoE layer from the load measured since the last
+        call and move the weights (between steps; every rank reaches this at the same step count,
+        so the collectives inside line up).  Returns the number of physical slots that changed."""
+        moved = 0
+        for m in self.worker.get_model().modules():
+            if getattr(m, "eplb", None) is not None and hasattr(m, "rebalance"):
+                moved += m.rebalance()
+        self.stats["eplb_moves"] = self.stats.get("eplb_moves", 0) + moved
+        return moved
 
     def _after_recovered_step(self, out, verdict: dict) -> List[RequestOutput]:
         """The step failed and the workers recovered (token recovery).  ``recompute``: nothing
@@ -195,6 +209,8 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                          data_parallel_size=kw.pop("data_parallel_size", 1),
                          enable_expert_parallel=kw.pop("enable_expert_parallel", False),
                          sequence_parallel_residual=kw.pop("sequence_parallel_residual", False),
+                         num_redundant_experts=kw.pop("num_redundant_experts", 0),
+                         eplb_step_interval=kw.pop("eplb_step_interval", 0),
                          layer_parallel_config=kw.pop("layer_parallel_config", {}) or {})
     sched = SchedulerConfig(max_num_seqs=kw.pop("max_num_seqs", 128),
                             max_num_batched_tokens=kw.pop("max_num_batched_tokens", 8192),

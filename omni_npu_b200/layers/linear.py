@@ -237,10 +237,12 @@ class MergedColumnParallelLinear(LinearBase):
     def weight_loader(self, param: nn.Parameter, loaded: torch.Tensor, shard_id=None) -> None:
         if shard_id is None:
             # already-fused checkpoint tensor: split it into its parts
+            blocks = param.dim() == 2 and param.shape[0] != sum(self.local_sizes) and param.dtype == torch.float32
             off = 0
             for i, s in enumerate(self.output_sizes):
-                self.weight_loader(param, loaded.narrow(0, off, s), i)
-                off += s
+                n = (s + 127) // 128 if blocks else s      # block-scale tensors count rows in blocks of 128
+                self.weight_loader(param, loaded.narrow(0, off, n), i)
+                off += n
             return
         n = self.local_sizes[shard_id]
         scale_like = param.dim() == 2 and param.shape[0] != sum(self.local_sizes) and param.dtype == torch.float32

@@ -52,7 +52,7 @@ class FusedMoE(nn.Module):
                  topk_group: int = 1, router_bias: bool = False, num_shared_experts: int = 0,
                  shared_intermediate_size: Optional[int] = None, enable_expert_parallel: bool = True,
                  prefix: str = "", max_tokens: int = 8192, quant: Optional[str] = None,
-                 num_redundant_experts: int = 0) -> None:
+                 num_redundant_experts: int = 0, shared_quant_factory=None) -> None:
         super().__init__()
         self.num_experts, self.top_k = num_experts, top_k
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -98,9 +98,11 @@ class FusedMoE(nn.Module):
         if num_shared_experts > 0:
             inter = (shared_intermediate_size or intermediate_size) * num_shared_experts
             # shared experts are replicated when tokens are de-duplicated across TP ranks
+            # quantised checkpoints quantise the shared experts like every other linear
             self.shared_experts = FusedMLP(hidden_size, inter, dtype, device, prefix=f"{prefix}.shared_experts",
+                                           quant_method_factory=shared_quant_factory,
                                            group=_solo_group() if self.ep_size > 1 else None,
-                                           reduce_results=False)
+                                           reduce_results=False, fuse_swiglu=shared_quant_factory is None)
         self.buffers: Optional[EpBuffers] = None
         self._side_stream: Optional[torch.cuda.Stream] = None
         self.expert_load: Optional[torch.Tensor] = None   # per-expert token counts (EPLB statistics)

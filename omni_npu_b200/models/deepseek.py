@@ -58,7 +58,9 @@ class DeepseekDecoderLayer(nn.Module):
                                 enable_expert_parallel=engine.parallel.enable_expert_parallel
                                 or engine.parallel.tensor_parallel_size > 1,
                                 prefix=f"{prefix}.mlp", max_tokens=engine.scheduler.max_num_batched_tokens,
-                                quant=None)
+                                quant="fp8" if cfg.quant_method == "fp8" else None,
+                                shared_quant_factory=qf if cfg.quant_method == "fp8" else None,
+                                num_redundant_experts=engine.parallel.num_redundant_experts)
         else:
             self.mlp = FusedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.dtype, device,
                                 quant_method_factory=qf, prefix=f"{prefix}.mlp",

@@ -44,7 +44,8 @@ class Qwen3MoeDecoderLayer(nn.Module):
                                 enable_expert_parallel=engine.parallel.enable_expert_parallel
                                 or engine.parallel.tensor_parallel_size > 1,
                                 prefix=f"{prefix}.mlp",
-                                max_tokens=engine.scheduler.max_num_batched_tokens)
+                                max_tokens=engine.scheduler.max_num_batched_tokens,
+                                num_redundant_experts=engine.parallel.num_redundant_experts)
         else:
             self.mlp = FusedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.dtype, device,
                                 prefix=f"{prefix}.mlp")
