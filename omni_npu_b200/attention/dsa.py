@@ -95,18 +95,42 @@ class Indexer(nn.Module):
         """Scores on the tensor cores and a radix select per query token (one score kernel and one
         select kernel for the whole batch, no host synchronisation, so the step stays graph
         capturable).  Index shapes the kernel does not cover (head dim != 128, heads not a
-        multiple of 16, pages that do not tile 128 keys) take the dense torch path."""
+        multiple of 16, pages that do not tile 128 keys) take the dense torch path below."""
         bs = index_cache.shape[1]
         kernel_ok = (not q.is_cuda) or (self.head_dim == 128 and self.n_heads % 16 == 0 and self.n_heads <= 256 and
                                         bs % 8 == 0 and (bs % 128 == 0 if bs >= 128 else 128 % bs == 0))
-        fn = ops.dsa_indexer_topk if kernel_ok else (
-            lambda *a, max_ctx=0, max_q=0, **k: ops.ref.dsa_indexer_topk(*a, **k))
+        if not kernel_ok:
+            return self._topk_dense(q, w, md, index_cache)
         if md.is_prefill:
-            return fn(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk, cu_q=md.cu_q,
-                      max_ctx=int(md.max_seq_len or 0), max_q=int(md.max_q_len or 0))
+            return ops.dsa_indexer_topk(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk,
+                                        cu_q=md.cu_q, max_ctx=int(md.max_seq_len or 0), max_q=int(md.max_q_len or 0))
         q_len = max(1, md.q_len)
-        return fn(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk, q_len=q_len,
-                  max_ctx=int(md.max_seq_len or 0), max_q=q_len)
+        return ops.dsa_indexer_topk(q, w, index_cache, md.block_tables, md.positions, md.num_seqs, self.topk,
+                                    q_len=q_len, max_ctx=int(md.max_seq_len or 0), max_q=q_len)
+
+    def _topk_dense(self, q, w, md: AttentionMetadata, index_cache) -> torch.Tensor:
+        """Per-sequence dense scores + ``torch.topk``.  Decode steps touch no host value (a fixed
+        window over the whole block table, keys beyond a token's position masked), so they can
+        be captured in a CUDA graph; prefill steps read the lengths on the host."""
+        bs = index_cache.shape[1]
+        t = q.shape[0]
+        out = torch.full((t, self.topk), -1, dtype=torch.int32, device=q.device)
+        flat = index_cache.view(-1, index_cache.shape[-1])
+        if md.is_prefill:
+            cu = md.cu_q[: md.num_seqs + 1].tolist()
+            lens = md.seq_lens[: md.num_seqs].tolist()
+        else:
+            cu = [i * md.q_len for i in range(md.num_seqs + 1)]
+            lens = None
+        for b in range(md.num_seqs):
+            qs, qe = cu[b], cu[b + 1]
+            if qe <= qs:
+                continue
+            n = lens[b] if lens is not None else md.block_tables.shape[1] * bs
+            pos = torch.arange(n, device=q.device)
+            rows = md.block_tables[b][pos // bs].long() * bs + pos % bs
+            out[qs:qe] = indexer_topk_reference(q[qs:qe], w[qs:qe], flat[rows], md.positions[qs:qe].long(), self.topk)
+        return out
 
 
 class SparseMLAAttention(MLAAttention):

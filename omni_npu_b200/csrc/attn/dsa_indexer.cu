@@ -360,6 +360,26 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 
 constexpr int kSelThreads = 512;
 
+// Adds 1 to hist[bin] for every active lane; lanes that hit the same bin are combined into one
+// shared-memory atomic (scores of one row share their leading bytes, so without this the first
+// passes serialise thousands of atomics on two or three addresses).
+__device__ __forceinline__ void hist_add(uint32_t* hist, uint32_t bin, bool active) {
+  const uint32_t peers = __match_any_sync(0xffffffffu, active ? bin : 0xffffffffu);
+  if (active && (__ffs(peers) - 1) == static_cast<int>(threadIdx.x & 31)) atomicAdd(&hist[bin], __popc(peers));
+}
+
+// Slot reservation for the lanes with `take` set: one atomic per warp, lanes get consecutive slots.
+__device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, bool take) {
+  const uint32_t mask = __ballot_sync(0xffffffffu, take);
+  uint32_t base = 0;
+  if (mask != 0u) {
+    const int leader = __ffs(mask) - 1;
+    if (static_cast<int>(threadIdx.x & 31) == leader) base = atomicAdd(counter, __popc(mask));
+    base = __shfl_sync(0xffffffffu, base, leader);
+  }
+  return base + __popc(mask & ((1u << (threadIdx.x & 31)) - 1u));
+}
+
 __global__ void __launch_bounds__(kSelThreads)
 dsa_indexer_select_kernel(int* __restrict__ out, const float* __restrict__ scores, long long ld,
                           const int* __restrict__ positions, int topk) {
@@ -383,40 +403,57 @@ dsa_indexer_select_kernel(int* __restrict__ out, const float* __restrict__ score
     s_cnt = 0u;
     s_eq = 0u;
   }
+  const int n_round = (n + kSelThreads - 1) / kSelThreads * kSelThreads;   // whole warps take part in every step
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     for (int i = threadIdx.x; i < 256; i += kSelThreads) hist[i] = 0u;
     __syncthreads();
     const uint32_t prefix = s_prefix, mask = s_mask;
-    for (int i = threadIdx.x; i < n; i += kSelThreads) {
-      const uint32_t u = order_key(row[i]);
-      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255u], 1u);
+    for (int i = threadIdx.x; i < n_round; i += kSelThreads) {
+      const uint32_t u = i < n ? order_key(row[i]) : 0u;
+      hist_add(hist, (u >> shift) & 255u, i < n && (u & mask) == prefix);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t cum = 0u;
+    if (threadIdx.x < 32) {
+      // warp 0 scans the 256 bins from the top: lane l owns bins 255 - 8l .. 248 - 8l
+      uint32_t mine[8], sum = 0u;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        mine[b] = hist[255 - (threadIdx.x * 8 + b)];
+        sum += mine[b];
+      }
+      uint32_t before = sum;                       // exclusive prefix over the lanes
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, before, d);
+        if (static_cast<int>(threadIdx.x) >= d) before += v;
+      }
+      before -= sum;
       const uint32_t k = s_krem;
-      for (int bin = 255; bin >= 0; --bin) {
-        const uint32_t h = hist[bin];
-        if (cum + h >= k) {
-          s_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
-          s_mask = mask | (255u << shift);
-          s_krem = k - cum;
-          break;
+      if (before < k && before + sum >= k) {       // the k-th best value falls into one of my bins
+        uint32_t cum = before;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          if (cum < k && cum + mine[b] >= k) {
+            s_prefix = prefix | (static_cast<uint32_t>(255 - (threadIdx.x * 8 + b)) << shift);
+            s_mask = mask | (255u << shift);
+            s_krem = k - cum;
+          }
+          cum += mine[b];
         }
-        cum += h;
       }
     }
     __syncthreads();
   }
   const uint32_t thr = s_prefix, krem = s_krem;
-  for (int i = threadIdx.x; i < n; i += kSelThreads) {
-    const uint32_t u = order_key(row[i]);
-    if (u > thr) {
-      o[atomicAdd(&s_cnt, 1u)] = i;
-    } else if (u == thr) {
-      if (atomicAdd(&s_eq, 1u) < krem) o[atomicAdd(&s_cnt, 1u)] = i;
-    }
+  for (int i = threadIdx.x; i < n_round; i += kSelThreads) {
+    const uint32_t u = i < n ? order_key(row[i]) : 0u;
+    const bool above = i < n && u > thr;
+    const bool equal = i < n && u == thr;
+    const uint32_t e = warp_reserve(&s_eq, equal);
+    const bool take = above || (equal && e < krem);
+    const uint32_t slot = warp_reserve(&s_cnt, take);
+    if (take) o[slot] = i;
   }
 }
 

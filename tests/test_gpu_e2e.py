@@ -60,11 +60,13 @@ def _tiny_deepseek(sparse: bool):
               qk_rope_head_dim=64, v_head_dim=128, scoring_func="sigmoid", norm_topk_prob=True,
               n_group=4, topk_group=2, router_bias=True, routed_scaling_factor=2.5)
     if sparse:
-        kw.update(architecture="DeepseekV32ForCausalLM", index_topk=64, index_n_heads=8, index_head_dim=128)
+        # 8 index heads: dense torch indexer (the kernel wants a multiple of 16); 16 heads: tcgen05 indexer
+        kw.update(architecture="DeepseekV32ForCausalLM", index_topk=64, index_n_heads=16 if sparse == "kernel" else 8,
+                  index_head_dim=128)
     return ModelConfig(**kw)
 
 
-@pytest.mark.parametrize("sparse", [False, True])
+@pytest.mark.parametrize("sparse", [False, True, "kernel"])
 def test_deepseek_mla_moe_engine_runs_and_paths_agree(sparse):
     """MLA + MoE model on the GPU: graph decode and eager decode give the same tokens."""
     cfg = _tiny_deepseek(sparse)
