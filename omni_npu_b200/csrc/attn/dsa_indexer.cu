@@ -409,9 +409,18 @@ dsa_indexer_select_kernel(int* __restrict__ out, const float* __restrict__ score
     for (int i = threadIdx.x; i < 256; i += kSelThreads) hist[i] = 0u;
     __syncthreads();
     const uint32_t prefix = s_prefix, mask = s_mask;
-    for (int i = threadIdx.x; i < n_round; i += kSelThreads) {
-      const uint32_t u = i < n ? order_key(row[i]) : 0u;
-      hist_add(hist, (u >> shift) & 255u, i < n && (u & mask) == prefix);
+    if (pass < 2) {
+      // leading bytes (sign, exponent, top of the mantissa) are shared by most of the row: combine per warp
+      for (int i = threadIdx.x; i < n_round; i += kSelThreads) {
+        const uint32_t u = i < n ? order_key(row[i]) : 0u;
+        hist_add(hist, (u >> shift) & 255u, i < n && (u & mask) == prefix);
+      }
+    } else {
+      // trailing bytes are spread over the bins and few elements still match the prefix: plain atomics
+      for (int i = threadIdx.x; i < n; i += kSelThreads) {
+        const uint32_t u = order_key(row[i]);
+        if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255u], 1u);
+      }
     }
     __syncthreads();
     if (threadIdx.x < 32) {
