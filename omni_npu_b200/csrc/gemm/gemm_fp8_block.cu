@@ -23,6 +23,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
@@ -30,10 +32,17 @@
 namespace b200 {
 
 constexpr int kFbBM = 128, kFbBN = 128, kFbSlab = 128;   // tile and K slab (bytes = elements for e4m3)
-constexpr int kFbStages = 6;
-constexpr int kFbStageBytes = (kFbBM + kFbBN) * kFbSlab;  // 32 KB
-constexpr int kFbThreads = 192;
-constexpr size_t kFbSmemBase = 1024 + static_cast<size_t>(kFbStages) * kFbStageBytes + (2 * kFbStages + 4) * 8 + 32;
+// WG = number of epilogue warp groups = tile width / 128.  One group: 128 x 128 tiles, six stages.
+// Two groups: 128 x 256 tiles (each group promotes its own 128 columns, so the promotion time per MMA
+// cycle halves), four stages, all 512 TMEM columns for the two partial accumulators.
+template <int WG> struct FbCfg {
+  static constexpr int TN = kFbBN * WG;
+  static constexpr int STAGES = WG == 1 ? 6 : 4;
+  static constexpr int STAGE_BYTES = (kFbBM + TN) * kFbSlab;
+  static constexpr int THREADS = 64 + 128 * WG;
+  static constexpr int TMEM_COLS = 2 * TN;
+  static constexpr size_t SMEM_BASE = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 4) * 8 + 32;
+};
 
 struct Fp8BlockParams {
   int M, N, K;
@@ -69,7 +78,7 @@ struct FbTile {
 // Tile t of this problem; grouped: n is the fast index so that concurrently running CTAs share
 // an expert's rows.  s_prefix[e] = number of 128-row blocks of the experts before e.
 __device__ __forceinline__ void fb_decode(const Fp8BlockParams& p, const int* s_prefix, long long t, int& cursor,
-                                          FbTile& tc) {
+                                          FbTile& tc, int tile_n) {
   if (p.num_experts == 0) {
     tc.m0 = static_cast<int>(t % p.num_m_blocks) * kFbBM;
     tc.m_end = p.M;
@@ -83,12 +92,17 @@ __device__ __forceinline__ void fb_decode(const Fp8BlockParams& p, const int* s_
     tc.m0 = p.expert_offsets[cursor] + (mblk - s_prefix[cursor]) * kFbBM;
     tc.m_end = p.expert_offsets[cursor + 1];
   }
-  tc.n0 = tc.nb * kFbBN;
+  tc.n0 = tc.nb * tile_n;
 }
 
-__global__ void __launch_bounds__(kFbThreads)
+template <int WG>
+__global__ void __launch_bounds__(FbCfg<WG>::THREADS)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                       const Fp8BlockParams p) {
+  using Cfg = FbCfg<WG>;
+  constexpr int kFbStages = Cfg::STAGES;
+  constexpr int kFbStageBytes = Cfg::STAGE_BYTES;
+  constexpr int TN = Cfg::TN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -112,7 +126,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&part_full[i], 1);
-      mbar_init(&part_empty[i], 4);
+      mbar_init(&part_empty[i], 4 * WG);
     }
     *s_abort = 0;
     fence_barrier_init();
@@ -128,7 +142,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     s_prefix[p.num_experts] = acc;
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -151,7 +165,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       int cursor = 0;
       FbTile tc;
       for (long long t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
-        fb_decode(p, s_prefix, t, cursor, tc);
+        fb_decode(p, s_prefix, t, cursor, tc, TN);
         const int m0 = tc.m0, n0 = tc.n0;
         for (int kb = 0; kb < p.k_iters; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
@@ -163,9 +177,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(kFbStageBytes));
           tma_load_2d(s_a + stage * kFbBM * kFbSlab, &tm_a, &full[stage], kb * kFbSlab, m0);
           if (p.num_experts > 0)
-            tma_load_3d(s_w + stage * kFbBN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0, tc.expert);
+            tma_load_3d(s_w + stage * TN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0, tc.expert);
           else
-            tma_load_2d(s_w + stage * kFbBN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0);
+            tma_load_2d(s_w + stage * TN * kFbSlab, &tm_w, &full[stage], kb * kFbSlab, n0);
           ++issued;
           if (++stage == kFbStages) {
             stage = 0;
@@ -190,7 +204,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(0, 0, kFbBM, kFbBN);       // e4m3 x e4m3 -> fp32
+      const uint32_t idesc = make_idesc(0, 0, kFbBM, TN);          // e4m3 x e4m3 -> fp32
       const uint32_t a_lo0 = (smem_u32(s_a) & 0x3FFFF) >> 4, w_lo0 = (smem_u32(s_w) & 0x3FFFF) >> 4;
       int stage = 0, pb = 0;
       uint32_t phase = 0, pph = 0;
@@ -204,9 +218,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             break;
           }
           tc_fence_after_sync();
-          const uint32_t d = tmem_base + static_cast<uint32_t>(pb * kFbBN);
+          const uint32_t d = tmem_base + static_cast<uint32_t>(pb * TN);
           const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage * (kFbBM * kFbSlab >> 4));
-          const uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * (kFbBN * kFbSlab >> 4));
+          const uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * (TN * kFbSlab >> 4));
           umma_first<kKindFP8>(d, a_lo, w_lo, idesc, 0u);
 #pragma unroll
           for (int kk = 1; kk < 4; ++kk) umma_acc<kKindFP8>(d, a_lo + kk * 2, w_lo + kk * 2, idesc);
@@ -227,21 +241,23 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     // ------------------------------------------------------ promotion + epilogue
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
+    const int cb = ((warp - 2) >> 2) * kFbBN;     // this warp group's 128 columns inside the tile
     int pb = 0;
     uint32_t pph = 0;
     bool ok = true;
     int cursor = 0;
     FbTile tc;
     for (long long t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
-      fb_decode(p, s_prefix, t, cursor, tc);
-      const int n0 = tc.n0;
+      fb_decode(p, s_prefix, t, cursor, tc, TN);
+      const int n0 = tc.n0 + cb;                   // first column of this thread's block (may lie beyond N)
+      const int n0s = min(n0, p.N - 1);            // for scale lookups only
       const int row = tc.m0 + r;
       const bool row_ok = row < tc.m_end;
       const float* a_s = p.a_scales + static_cast<long long>(row_ok ? row : 0) * p.k_iters;
       const float* w_base = p.w_scales + static_cast<long long>(tc.expert) * p.scale_rows * p.k_iters;
-      // scale row of the tile's columns; with SwiGLU the gate and the up columns have one each
-      const float* w_s = w_base + static_cast<long long>(p.swiglu ? (n0 >> 1) / 128 : tc.nb) * p.k_iters;
-      const float* w_s2 = p.swiglu ? w_base + static_cast<long long>(p.up_scale_row0 + (n0 >> 1) / 128) * p.k_iters
+      // scale row of the block's columns; with SwiGLU the gate and the up columns have one each
+      const float* w_s = w_base + static_cast<long long>(p.swiglu ? (n0s >> 1) / 128 : n0s / 128) * p.k_iters;
+      const float* w_s2 = p.swiglu ? w_base + static_cast<long long>(p.up_scale_row0 + (n0s >> 1) / 128) * p.k_iters
                                    : w_s;
       float acc[kFbBN];
 #pragma unroll
@@ -263,7 +279,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
         tc_fence_after_sync();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                               static_cast<uint32_t>(pb * kFbBN);
+                               static_cast<uint32_t>(pb * TN + cb);
 #pragma unroll
         for (int c0 = 0; c0 < kFbBN; c0 += 32) {
           uint32_t v[32];
@@ -356,7 +372,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -364,12 +380,14 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 
 using namespace b200;
 
-static int fb_launch(const CUtensorMap& ta, const CUtensorMap& tw, const Fp8BlockParams& p, long long tiles,
-                     int max_ctas, cudaStream_t stream) {
-  const size_t smem = kFbSmemBase + (static_cast<size_t>(p.num_experts) + 2) * 4;
+template <int WG>
+static int fb_launch_wg(const CUtensorMap& ta, const CUtensorMap& tw, const Fp8BlockParams& p, long long tiles,
+                        int max_ctas, cudaStream_t stream) {
+  using Cfg = FbCfg<WG>;
+  const size_t smem = Cfg::SMEM_BASE + (static_cast<size_t>(p.num_experts) + 2) * 4;
   static size_t configured = 0;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_fp8_block_kernel<WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return -20;
     configured = smem;
@@ -381,9 +399,22 @@ static int fb_launch(const CUtensorMap& ta, const CUtensorMap& tw, const Fp8Bloc
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
   if (grid < 1) grid = 1;
-  return launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(kFbThreads), smem, stream, 1, ta, tw, p) == cudaSuccess
+  return launch_pdl(gemm_fp8_block_kernel<WG>, dim3(grid), dim3(Cfg::THREADS), smem, stream, 1, ta, tw, p) ==
+                 cudaSuccess
              ? 0
              : -21;
+}
+
+// 256-wide tiles pay off once there are enough of them to fill the GPU; small problems keep the
+// narrow tile (more CTAs).  OMNI_B200_FP8_BLOCK_WG=1|2 forces a variant.
+static int fb_pick_wg(long long rows, int N) {
+  static const int forced = [] {
+    const char* e = getenv("OMNI_B200_FP8_BLOCK_WG");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2) return N >= 256 || forced == 1 ? forced : 1;
+  const long long wide_tiles = ((rows + kFbBM - 1) / kFbBM) * ((N + 255) / 256);
+  return (N >= 256 && wide_tiles >= 148) ? 2 : 1;
 }
 
 // A [M, K] e4m3 (pitch lda bytes), a_scales [M, K/128]; W [N, K] e4m3 (pitch ldw), w_scales
@@ -399,8 +430,10 @@ extern "C" int b200_gemm_fp8_block(const void* A, const float* a_scales, const v
   p.N = N;
   p.K = K;
   p.k_iters = K / kFbSlab;
+  const int wg = fb_pick_wg(M, N);
+  const int tn = kFbBN * wg;
   p.num_m_blocks = (M + kFbBM - 1) / kFbBM;
-  p.num_n_blocks = (N + kFbBN - 1) / kFbBN;
+  p.num_n_blocks = (N + tn - 1) / tn;
   p.a_scales = a_scales;
   p.w_scales = w_scales;
   p.C = C;
@@ -409,16 +442,16 @@ extern "C" int b200_gemm_fp8_block(const void* A, const float* a_scales, const v
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.status = status;
-  p.scale_rows = p.num_n_blocks;
+  p.scale_rows = (N + kFbBN - 1) / kFbBN;
   CUtensorMap ta, tw;
   int r = make_tensormap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, lda, kFbBM, kFbSlab,
                             CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
-  r = make_tensormap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K, ldw, kFbBN, kFbSlab,
+  r = make_tensormap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K, ldw, tn, kFbSlab,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
   const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
-  return fb_launch(ta, tw, p, tiles, max_ctas, stream);
+  return wg == 2 ? fb_launch_wg<2>(ta, tw, p, tiles, max_ctas, stream) : fb_launch_wg<1>(ta, tw, p, tiles, max_ctas, stream);
 }
 
 // Grouped (mixture-of-experts) variant.  A [total_rows, K] e4m3 holds every expert's rows back to
@@ -439,8 +472,10 @@ extern "C" int b200_grouped_gemm_fp8_block(const void* A, const float* a_scales,
   p.N = N;
   p.K = K;
   p.k_iters = K / kFbSlab;
+  const int wg = fb_pick_wg(total_rows, N);
+  const int tn = kFbBN * wg;
   p.num_m_blocks = 0;
-  p.num_n_blocks = (N + kFbBN - 1) / kFbBN;
+  p.num_n_blocks = (N + tn - 1) / tn;
   p.a_scales = a_scales;
   p.w_scales = w_scales;
   p.C = C;
@@ -456,9 +491,9 @@ extern "C" int b200_grouped_gemm_fp8_block(const void* A, const float* a_scales,
                             CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   r = make_tensormap_3d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, num_experts, N, K,
-                        static_cast<uint64_t>(N) * K, K, kFbBN, kFbSlab, CU_TENSOR_MAP_SWIZZLE_128B);
+                        static_cast<uint64_t>(N) * K, K, tn, kFbSlab, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
   // upper bound on the tiles (the kernel computes the exact count from the offsets)
   const long long tiles = (static_cast<long long>(total_rows) / kFbBM + num_experts) * p.num_n_blocks;
-  return fb_launch(ta, tw, p, tiles, max_ctas, stream);
+  return wg == 2 ? fb_launch_wg<2>(ta, tw, p, tiles, max_ctas, stream) : fb_launch_wg<1>(ta, tw, p, tiles, max_ctas, stream);
 }

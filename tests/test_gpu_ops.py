@@ -587,7 +587,7 @@ def test_dsa_indexer_scores_and_topk(mode):
             assert sc[i, :n][chosen].min() >= sc[i, :n][~chosen].max()
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 1000, 1024), (8, 4096, 7168)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 1000, 1024), (8, 4096, 7168), (2048, 2500, 512)])
 def test_gemm_fp8_block_scaled(m, n, k):
     """128 x 128 block-scaled weights, per-token-per-128 activations (DeepSeek-V3 checkpoint format)."""
     from omni_npu_b200.layers.quant_fp8 import fp8_block_gemm, quantize_weight_block
@@ -608,8 +608,9 @@ def test_gemm_fp8_block_scaled(m, n, k):
     _close(got16, want, 2e-2 * float(want.abs().max()), 2e-2)
 
 
+@pytest.mark.parametrize("large", [False, True])
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_grouped_gemm_fp8_block_scaled(swiglu):
+def test_grouped_gemm_fp8_block_scaled(swiglu, large):
     """Expert GEMM on block-scaled e4m3 weights; with SwiGLU the gate / up rows are interleaved in groups
     of 8 while their scale blocks stay in checkpoint order (gate blocks, then up blocks)."""
     from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
@@ -617,6 +618,10 @@ def test_grouped_gemm_fp8_block_scaled(swiglu):
     e, k, inter = 4, 512, 256
     n = 2 * inter if swiglu else 384
     counts = [130, 0, 7, 300]
+    if large:                       # enough 128 x 256 tiles for the two-warp-group variant
+        inter = 512
+        n = 2 * inter if swiglu else 1000
+        counts = [1300, 0, 700, 3000]
     offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
     rows = int(offs[-1])
     x = torch.randn(rows + 50, k, device=DEV, dtype=torch.bfloat16)          # rows past the last expert are unused
