@@ -330,16 +330,23 @@ allgather_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ 
 }
 
 // ------------------------------------------- staging for the fused all-gather GEMM
-// Copies this rank's block into its staging half of the next epoch; the last block to finish
-// tells every rank (flag word kAgFlagWord + rank of their signal pads) and advances the epoch.
-// No waiting here: the GEMM that follows waits per source block, right before it first needs it.
+// Copies this rank's block into its staging half of the next epoch (where the peers' GEMM kernels
+// fetch it) and into its place in the local gathered buffer; clears the per-source arrival
+// counters of the GEMM; the last block to finish tells every rank (flag word kAgFlagWord + rank of
+// their signal pads) and advances the epoch.  No waiting here: the GEMM that follows waits per
+// source block, right before it needs it.
 __global__ void __launch_bounds__(512)
-ag_stage_kernel(SymmGroup g, const uint4* __restrict__ in, long long n_vec, uint32_t* done_counter) {
+ag_stage_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ local_out, long long n_vec,
+                uint32_t* ready, uint32_t* done_counter) {
   const uint32_t epoch = read_epoch(g) + 1;
   uint4* stage = reinterpret_cast<uint4*>(static_cast<char*>(g.data[g.rank]) + (epoch & 1) * g.half_bytes);
+  if (blockIdx.x == 0 && threadIdx.x < g.world) ready[threadIdx.x] = 0u;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
-    stage[i] = in[i];
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 v = in[i];
+    stage[i] = v;
+    local_out[i] = v;
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -757,14 +764,17 @@ extern "C" int b200_symm_rs_reduce(void* const* data, void* const* signal, int w
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+// in: this rank's block (n_elems bf16); gathered: local [world * n_elems] buffer; ready: [world] counters.
 extern "C" int b200_symm_ag_stage(void* const* data, void* const* signal, int world, int rank, size_t half_bytes,
-                                  const void* in, long long n_elems, void* done_counter, cudaStream_t stream) {
+                                  const void* in, void* gathered, long long n_elems, void* ready,
+                                  void* done_counter, cudaStream_t stream) {
   if (world < 2 || world > kMaxRanks || (n_elems & 7) != 0) return -1;
   if (static_cast<size_t>(n_elems) * 2 > half_bytes) return -4;
   const SymmGroup g = make_group(data, signal, world, rank, half_bytes);
   const long long n_vec = n_elems >> 3;
-  ag_stage_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(g, static_cast<const uint4*>(in), n_vec,
-                                                                          static_cast<uint32_t*>(done_counter));
+  ag_stage_kernel<<<pick_blocks(n_vec, kMaxCommBlocks), 512, 0, stream>>>(
+      g, static_cast<const uint4*>(in), static_cast<uint4*>(gathered) + static_cast<long long>(rank) * n_vec, n_vec,
+      static_cast<uint32_t*>(ready), static_cast<uint32_t*>(done_counter));
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -37,6 +37,8 @@ static constexpr int kBM = 128;          // rows of A per tile (UMMA M)
 static constexpr int kRowBytes = 128;    // bytes of K per stage row (one swizzle span)
 static constexpr int kThreads = 192;
 static constexpr int kMaxExperts = 512;
+static constexpr int kRsPitch = 144;                 // bytes per staged row (64 bf16 columns + padding)
+static constexpr int kRsWarpBytes = 32 * kRsPitch;   // staging of one epilogue warp
 
 struct GemmParams {
   int M, N, K;            // problem (grouped: M = total packed rows)
@@ -73,12 +75,17 @@ struct GemmParams {
   const __nv_bfloat16* ar_norm_w;  // [N] RMSNorm weight, or null: C = all-reduced sum (+residual)
   float ar_eps;
   uint32_t* ar_done;               // zero-initialised device counter
-  // ---- fused all-gather of A (ag_world > 1): A is the row-wise concatenation of every rank's
-  // staged block of ag_rows rows.  The producer reads each block straight from its owner's
-  // memory with (plain, non-multicast) TMA, own block first, and waits (bounded) for the
-  // owner's "staged" flag before the first tile of a foreign block.
-  const CUtensorMap* ag_maps;      // [2 halves][ag_world] tensor maps over the staging buffers (global memory)
+  // ---- fused all-gather of A (ag_world > 1): A [M = ag_world * ag_rows, K] is a LOCAL buffer whose
+  // own block was filled by the staging kernel.  The epilogue warps of every CTA, idle until the
+  // first accumulator is ready, pull this CTA's share of every foreign block from the owner's
+  // staging buffer over NVLink (once: a tile re-read per N block would cross the link every time)
+  // and bump a per-source counter; the producer walks the row blocks own-first and waits (bounded)
+  // until a foreign block's counter shows that all CTAs delivered their share.
+  void* ag_data[kMaxRanks];        // peer-mapped staging buffers (both halves)
+  long long ag_half_bytes;
   const uint32_t* ag_signal;       // this rank's signal pad: word ag_epoch_word = epoch, ag_flag_word + r = rank r staged
+  uint32_t* ag_ready;              // [ag_world] local counters, zeroed by the staging kernel
+  const void* ag_local;            // the local gathered A buffer (same memory tmap_a describes)
   int ag_world, ag_rank;
   int ag_rows;                     // rows per rank, a multiple of 128
   int ag_epoch_word, ag_flag_word;
@@ -183,7 +190,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // staging for the cluster reduction: [128 rows][BN + 4] fp32
   float* red_buf = reinterpret_cast<float*>(smem_w + p.stages * w_stage_bytes);
   const int red_stride = p.BN + 4;
-  const int red_bytes = p.cluster_split ? kBM * red_stride * 4 : 0;
+  const int red_bytes = p.cluster_split ? kBM * red_stride * 4 : (p.rs_world > 1 ? 4 * kRsWarpBytes : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes + red_bytes);
   uint64_t* full_bar = bars;                    // [stages]
   uint64_t* empty_bar = bars + p.stages;        // [stages]
@@ -299,41 +306,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ar_slot_off = static_cast<long long>(ar_epoch % 3) * p.ar_world * p.ar.slot_vecs;
         }
       }
-      uint32_t ag_epoch = 0, ag_ready = 0;
-      const CUtensorMap* ag_maps = nullptr;
-      if (p.ag_world > 1) {
-        ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_signal + p.ag_epoch_word);
-        ag_maps = p.ag_maps + (ag_epoch & 1u) * p.ag_world;
-        ag_ready = 1u << p.ag_rank;
-      }
+      uint32_t ag_have = p.ag_world > 1 ? (1u << p.ag_rank) : 0u;
       for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
                                                                 cta_rank, cursor, tc);
            t += t_stride) {
         const CUtensorMap* map_a = &tmap_a;
-        int a_row = tc.m0;
-        if (tc.a_src >= 0) {
-          if (!((ag_ready >> tc.a_src) & 1u)) {
-            // first tile of a foreign block: its owner must have finished staging (flags only grow)
-            const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + tc.a_src;
-            uint32_t polls = 0;
-            while (static_cast<int32_t>(*flag - ag_epoch) < 0) {
-              if (++polls > (1u << 24)) {
-                ok = false;
-                break;
-              }
-              __nanosleep(64);
-            }
-            if (!ok) {
-              atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
-              *abort_flag = 1;
+        const int a_row = tc.m0;
+        if (tc.a_src >= 0 && !((ag_have >> tc.a_src) & 1u)) {
+          // first tile of a foreign block: every CTA must have delivered its share of it
+          const volatile uint32_t* cnt = p.ag_ready + tc.a_src;
+          uint32_t polls = 0;
+          while (*cnt < gridDim.x) {
+            if (*abort_flag || ++polls > (1u << 24)) {
+              ok = false;
               break;
             }
-            __threadfence_system();
-            fence_proxy_async();
-            ag_ready |= 1u << tc.a_src;
+            __nanosleep(64);
           }
-          map_a = ag_maps + tc.a_src;
-          a_row = tc.a_row0;
+          if (!ok) {
+            atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+            *abort_flag = 1;
+            break;
+          }
+          __threadfence();
+          fence_proxy_async();
+          ag_have |= 1u << tc.a_src;
         }
         for (int k = tc.k_begin; k < tc.k_end; k += p.ksub) {
           // one barrier round trip covers up to ksub slabs (`stage` counts groups of slabs)
@@ -453,6 +450,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     int cursor = 0;
     int tile_iter = 0;
+    if (p.ag_world > 1) {
+      // ---- all-gather pull: this CTA's slice of every foreign block, nearest rank first
+      const int et = threadIdx.x - 64;
+      const uint32_t ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_signal + p.ag_epoch_word);
+      const long long half_off = static_cast<long long>(ag_epoch & 1u) * p.ag_half_bytes;
+      const long long nvec = (static_cast<long long>(p.ag_rows) * p.K * p.elem_bytes) >> 4;
+      const long long per = (nvec + gridDim.x - 1) / gridDim.x;
+      const long long begin = min(nvec, per * blockIdx.x), end = min(nvec, per * (blockIdx.x + 1));
+      for (int c = 1; c < p.ag_world; ++c) {
+        const int src = (p.ag_rank + c) % p.ag_world;
+        uint32_t staged = 1u;
+        if (et == 0) {
+          const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + src;
+          uint32_t polls = 0;
+          while (static_cast<int32_t>(*flag - ag_epoch) < 0) {     // flags only grow
+            if (++polls > (1u << 24)) {
+              staged = 0u;
+              break;
+            }
+            __nanosleep(64);
+          }
+          __threadfence_system();
+          s_flags[1] = static_cast<int>(staged);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        staged = static_cast<uint32_t>(s_flags[1]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!staged) {
+          if (et == 0) {
+            atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+            *abort_flag = 1;
+          }
+          break;
+        }
+        const uint4* from = reinterpret_cast<const uint4*>(static_cast<const char*>(p.ag_data[src]) + half_off);
+        uint4* to = reinterpret_cast<uint4*>(const_cast<void*>(p.ag_local)) + static_cast<long long>(src) * nvec;
+        long long i = begin + et;
+        for (; i + 3 * 128 < end; i += 4 * 128) {                  // four loads in flight per thread
+          const uint4 v0 = __ldcv(from + i), v1 = __ldcv(from + i + 128), v2 = __ldcv(from + i + 256),
+                      v3 = __ldcv(from + i + 384);
+          to[i] = v0;
+          to[i + 128] = v1;
+          to[i + 256] = v2;
+          to[i + 384] = v3;
+        }
+        for (; i < end; i += 128) to[i] = __ldcv(from + i);
+        __threadfence();
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) atomicAdd(p.ag_ready + src, 1u);
+      }
+    }
     long long rs_half_off = 0;     // fused reduce-scatter: staging half of the epoch this call opens
     if (p.rs_world > 1) {
       const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(p.rs_signal + p.rs_epoch_word) + 1u;
@@ -657,6 +706,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int i = 0; i < 16; ++i) ws_col[static_cast<size_t>(c + i) * kBM] = v[i];
           continue;
         }
+        if (p.rs_world > 1) {
+          // ---- reduce-scatter push.  Rows of the tile belong to different owners and a thread holds
+          // one row, so direct stores would be 32-byte pieces at a row pitch apart.  Instead the warp
+          // parks 64 columns of its 32 rows in shared memory and writes them out as 128-byte row
+          // segments (8 lanes per row, 4 rows per store instruction) into the owners' staging slots.
+          if (p.bias && p.rs_rank == 0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col + i < p.N) v[i] += __bfloat162float(p.bias[col + i]);
+          }
+          uint8_t* rs_stage = reinterpret_cast<uint8_t*>(red_buf) + quarter * kRsWarpBytes;
+          uint4* mine = reinterpret_cast<uint4*>(rs_stage + lane * kRsPitch + (c & 63) * 2);
+          uint4 pk0, pk1;
+          pk0.x = pack_bf16x2(v[0], v[1]);
+          pk0.y = pack_bf16x2(v[2], v[3]);
+          pk0.z = pack_bf16x2(v[4], v[5]);
+          pk0.w = pack_bf16x2(v[6], v[7]);
+          pk1.x = pack_bf16x2(v[8], v[9]);
+          pk1.y = pack_bf16x2(v[10], v[11]);
+          pk1.z = pack_bf16x2(v[12], v[13]);
+          pk1.w = pack_bf16x2(v[14], v[15]);
+          mine[0] = pk0;
+          mine[1] = pk1;
+          if ((c & 63) == 48 || c + 16 >= p.BN) {
+            __syncwarp();
+            const int c64 = c & ~63;
+            const int segs = (min(64, p.BN - c64)) >> 3;          // 16-byte segments per row in this group
+            for (int idx = lane; idx < 32 * segs; idx += 32) {
+              const int rowi = idx / segs, seg = idx - rowi * segs;
+              const int grow = tc.m0 + quarter * 32 + rowi;
+              const int gcol = tc.n0 + c64 + seg * 8;
+              if (grow < tc.m_end && gcol < p.N) {
+                const int owner = grow / p.rs_rows;
+                const int row_local = grow - owner * p.rs_rows;
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(p.rs_data[owner]) + rs_half_off) +
+                                     (static_cast<long long>(p.rs_rank) * p.rs_rows + row_local) * p.N + gcol;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(rs_stage + rowi * kRsPitch + seg * 16);
+              }
+            }
+            __syncwarp();
+          }
+          continue;
+        }
         if (!row_ok || col >= p.N) continue;
         if (p.ar_world > 1) {
           // push 16 columns (two 16-byte vectors) of this row to every rank; rank 0 adds the bias
@@ -708,29 +800,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           continue;
         }
         const int ncols = min(16, p.N - col);
-        if (p.rs_world > 1) {
-          // partial tile row -> slot [this rank] of the row owner's staging half (N % 16 == 0 here)
-          const int owner = row / p.rs_rows;
-          const int row_local = row - owner * p.rs_rows;
-          if (p.bias && p.rs_rank == 0) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] += __bfloat162float(p.bias[col + i]);
-          }
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(p.rs_data[owner]) + rs_half_off) +
-                               (static_cast<long long>(p.rs_rank) * p.rs_rows + row_local) * p.N + col;
-          uint4 pk0, pk1;
-          pk0.x = pack_bf16x2(v[0], v[1]);
-          pk0.y = pack_bf16x2(v[2], v[3]);
-          pk0.z = pack_bf16x2(v[4], v[5]);
-          pk0.w = pack_bf16x2(v[6], v[7]);
-          pk1.x = pack_bf16x2(v[8], v[9]);
-          pk1.y = pack_bf16x2(v[10], v[11]);
-          pk1.z = pack_bf16x2(v[12], v[13]);
-          pk1.w = pack_bf16x2(v[14], v[15]);
-          reinterpret_cast<uint4*>(dst)[0] = pk0;
-          reinterpret_cast<uint4*>(dst)[1] = pk1;
-          continue;
-        }
         if (p.bias) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
@@ -965,7 +1034,12 @@ struct GemmPlan {
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// Bytes of the staging region that follows the pipeline stages.  mode 1: cluster split-K partial
+// tile (fp32); mode 2: reduce-scatter push, per epilogue warp 32 rows x 64 bf16 columns at a
+// 144-byte pitch.
+static constexpr int kRsStageBytes = 4 * kRsWarpBytes;
 static size_t red_bytes_for(int BN, int cluster_split) {
+  if (cluster_split == 2) return kRsStageBytes;
   return cluster_split ? static_cast<size_t>(kBM) * (BN + 4) * 4 : 0;
 }
 
@@ -1210,8 +1284,10 @@ struct RsArgs {
 };
 
 struct AgArgs {
-  const void* maps = nullptr;       // device: [2][world] CUtensorMap over the staging halves
+  void* const* data = nullptr;      // peer-mapped staging buffers
+  long long half_bytes = 0;
   const void* signal = nullptr;     // this rank's signal pad
+  void* ready = nullptr;            // [world] local counters
   int world = 0, rank = 0, rows = 0;
   int epoch_word = 0, flag_word = 0;
 };
@@ -1290,38 +1366,24 @@ extern "C" int b200_gemm_reduce_scatter_push(const void* A, const void* W, const
                    status, max_ctas, stream, nullptr, nullptr, nullptr, nullptr, &rs);
 }
 
-// Encodes the tensor maps of the fused all-gather GEMM into `out_host` (2 * world maps of 128
-// bytes: half 0 of every rank, then half 1).  data[r]: rank r's peer-mapped staging buffer of
-// 2 * half_bytes; rows_cap rows of K bf16 elements fit one half.
-extern "C" int b200_gemm_ag_encode_maps(void* out_host, void* const* data, int world, size_t half_bytes, int K) {
-  if (world < 2 || world > kMaxRanks || K <= 0 || (K % 8) != 0) return -1;
-  const uint64_t rows_cap = half_bytes / (static_cast<size_t>(K) * 2);
-  if (rows_cap < kBM) return -2;
-  CUtensorMap* out = static_cast<CUtensorMap*>(out_host);
-  for (int h = 0; h < 2; ++h)
-    for (int r = 0; r < world; ++r) {
-      const int rc = make_tensormap_2d(&out[h * world + r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                                       static_cast<const char*>(data[r]) + h * half_bytes, rows_cap, K, K, kBM,
-                                       kRowBytes / 2, CU_TENSOR_MAP_SWIZZLE_128B);
-      if (rc) return rc - 100;
-    }
-  return 0;
-}
-
-// Column-parallel projection of a sequence-sharded activation in ONE kernel:
-// C [world * rows, N] = concat_r(A_r) @ W^T, where A_r (rows x K, bf16) is the block rank r
-// staged in its symmetric buffer.  The producer warp reads every block from its owner with
-// TMA (own rows first), so the gather overlaps the tensor-core work tile by tile and the
-// gathered activation is never materialised.  swiglu: C [.., N/2] = silu(gate) * up with the
-// interleaved weight layout of the dense kernel.
-extern "C" int b200_gemm_all_gather(const void* maps_dev, const void* signal_local, const void* a_local,
-                                    const void* W, void* C, const void* bias, int rows, int N, int K, int ldw,
-                                    int ldc, int swiglu, int world, int rank, int epoch_word, int flag_word,
-                                    int* status, int max_ctas, cudaStream_t stream) {
+// Column-parallel projection of a sequence-sharded activation in ONE GEMM kernel:
+// C [world * rows, N] = concat_r(A_r) @ W^T.  `gathered` [world * rows, K] bf16 is local memory
+// whose own block (and every rank's staging buffer) the staging kernel has filled.  While the
+// tensor cores work on the own rows, the epilogue warps of all CTAs pull the foreign blocks from
+// their owners' staging buffers over NVLink, each byte once; tiles of a foreign block start when
+// its counter shows it complete.  swiglu: C [.., N/2] = silu(gate) * up (interleaved weight layout).
+extern "C" int b200_gemm_all_gather(void* gathered, void* const* data, long long half_bytes,
+                                    const void* signal_local, void* ready, const void* W, void* C,
+                                    const void* bias, int rows, int N, int K, int ldw, int ldc, int swiglu,
+                                    int world, int rank, int epoch_word, int flag_word, int* status,
+                                    int max_ctas, cudaStream_t stream) {
   if (world < 2 || world > kMaxRanks) return -30;
+  if ((static_cast<long long>(rows) * K * 2) % 16 != 0) return -31;
   AgArgs ag;
-  ag.maps = maps_dev;
+  ag.data = data;
+  ag.half_bytes = half_bytes;
   ag.signal = signal_local;
+  ag.ready = ready;
   ag.world = world;
   ag.rank = rank;
   ag.rows = rows;
@@ -1329,7 +1391,7 @@ extern "C" int b200_gemm_all_gather(const void* maps_dev, const void* signal_loc
   ag.flag_word = flag_word;
   const int M = rows * world;
   GemmPlan pl = plan_gemm(M, N, K, 2, sm_count(), false, swiglu != 0);
-  return gemm_impl(a_local, W, C, bias, nullptr, M, N, K, K, ldw, ldc, 0, 0, swiglu, pl.BN, 1, 0, nullptr, nullptr,
+  return gemm_impl(gathered, W, C, bias, nullptr, M, N, K, K, ldw, ldc, 0, 0, swiglu, pl.BN, 1, 0, nullptr, nullptr,
                    status, max_ctas, stream, nullptr, nullptr, nullptr, &ag);
 }
 
@@ -1356,7 +1418,8 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   p.cluster_split = cluster_split;
   p.num_m_blocks = (M + kBM - 1) / kBM;
   p.num_n_blocks = (N + BN - 1) / BN;
-  p.stages = stages_for(BN, cluster_split);
+  const int smem_mode = cluster_split ? 1 : ((rs != nullptr && rs->world > 1) ? 2 : 0);
+  p.stages = stages_for(BN, smem_mode);
   p.ksub = ksub_for(p.stages);
   p.stages -= p.stages % p.ksub;
   p.acc_stride = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
@@ -1387,7 +1450,10 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   }
   if (ag != nullptr && ag->world > 1) {
     if (splits != 1 || ag->rows <= 0 || (ag->rows % kBM) != 0 || ag->rows * ag->world != M) return -17;
-    p.ag_maps = static_cast<const CUtensorMap*>(ag->maps);
+    for (int r = 0; r < kMaxRanks; ++r) p.ag_data[r] = r < ag->world ? ag->data[r] : nullptr;
+    p.ag_half_bytes = ag->half_bytes;
+    p.ag_ready = static_cast<uint32_t*>(ag->ready);
+    p.ag_local = A;
     p.ag_signal = static_cast<const uint32_t*>(ag->signal);
     p.ag_world = ag->world;
     p.ag_rank = ag->rank;
@@ -1409,13 +1475,11 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kRowBytes / eb;
-  // with a gathered A the kernel addresses the per-rank maps; `ta` then only has to be valid
-  int r = make_tensormap_2d(&ta, dt, eb, A, p.ag_world > 1 ? p.ag_rows : M, K, lda, kBM, box_k,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
+  int r = make_tensormap_2d(&ta, dt, eb, A, M, K, lda, kBM, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   r = make_tensormap_2d(&tw, dt, eb, W, N, K, ldw, BN, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
-  const size_t smem = smem_bytes_for(BN, p.stages, 0, cluster_split);
+  const size_t smem = smem_bytes_for(BN, p.stages, 0, smem_mode);
   int grid;
   if (cluster_split) {
     const long long clusters = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;

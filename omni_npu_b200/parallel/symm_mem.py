@@ -60,11 +60,10 @@ def _lib() -> ctypes.CDLL:
         lib.b200_gemm_all_reduce.restype = ci
         lib.b200_symm_epoch_word.restype = ci
         lib.b200_symm_ag_flag_word.restype = ci
-        lib.b200_symm_ag_stage.argtypes = [pp, pp, ci, ci, sz, vp, ll, vp, vp]
+        lib.b200_symm_ag_stage.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, vp]
         lib.b200_symm_ag_stage.restype = ci
-        lib.b200_gemm_ag_encode_maps.argtypes = [vp, pp, ci, sz, ci]
-        lib.b200_gemm_ag_encode_maps.restype = ci
-        lib.b200_gemm_all_gather.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp, ci, vp]
+        lib.b200_gemm_all_gather.argtypes = [vp, pp, ll, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp,
+                                             ci, vp]
         lib.b200_gemm_all_gather.restype = ci
         lib.b200_gemm_reduce_scatter_push.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, pp, vp, ll, ci, ci, ci, vp, ci, vp]
         lib.b200_gemm_reduce_scatter_push.restype = ci
@@ -129,7 +128,7 @@ class SymmetricMemory:
         self.use_ll = os.environ.get("OMNI_B200_SYMM_LL", "1") != "0"
         self.fuse_gemm = os.environ.get("OMNI_B200_FUSE_GEMM_AR", "1") != "0"
         self.fuse_ag_gemm = os.environ.get("OMNI_B200_FUSE_AG_GEMM", "1") != "0"
-        self._ag_maps = {}                      # K -> device tensor holding the 2 * world tensor maps
+        self.ag_ready = torch.zeros(8, dtype=torch.int32, device=device)    # per-source arrival counters
         self.status = ops.device_state(device).status
         if lib.b200_symm_ll_arm(ll_ptr, ll_total_vecs, self._stream()) != 0:
             raise RuntimeError("arming the push all-reduce buffer failed")
@@ -263,34 +262,25 @@ class SymmetricMemory:
                 and x.shape[0] > 0 and x.shape[0] % 128 == 0 and x.shape[1] % 64 == 0
                 and x.numel() * 2 <= self.half_bytes)
 
-    def _ag_maps_for(self, k: int) -> torch.Tensor:
-        maps = self._ag_maps.get(k)
-        if maps is None:
-            host = ctypes.create_string_buffer(2 * self.world * 128)
-            rc = _lib().b200_gemm_ag_encode_maps(host, self.data_ptrs, self.world, self.half_bytes, k)
-            if rc != 0:
-                raise RuntimeError(f"encoding the all-gather tensor maps failed ({rc})")
-            maps = torch.frombuffer(bytearray(host.raw), dtype=torch.uint8).to(self.device)
-            torch.cuda.synchronize(self.device)
-            self._ag_maps[k] = maps
-        return maps
-
     def all_gather_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                        swiglu: bool = False) -> torch.Tensor:
-        """``all_gather(x, dim=0) @ w.T`` (+bias, optional fused SwiGLU) without materialising the
-        gathered activation: every rank stages its rows in its symmetric buffer, and the GEMM's
-        TMA producer reads the row blocks from their owners (own rows first) while the tensor
-        cores work on the tiles that are already there."""
+                        swiglu: bool = False, return_gathered: bool = False):
+        """``all_gather(x, dim=0) @ w.T`` (+bias, optional fused SwiGLU) with the gather inside the
+        GEMM kernel: every rank stages its rows in its symmetric buffer; while the tensor cores
+        work on the own rows, the GEMM's epilogue warps pull the other ranks' rows over NVLink
+        into a local buffer (each byte crosses the link once) and the tiles of a foreign block
+        start as soon as it is complete."""
         lib = _lib()
         rows, k = x.shape
         n = w.shape[0]
-        maps = self._ag_maps_for(k)
+        gathered = torch.empty((rows * self.world, k), dtype=torch.bfloat16, device=x.device)
         rc = lib.b200_symm_ag_stage(self.data_ptrs, self.signal_ptrs, self.world, self.rank, self.half_bytes,
-                                    x.data_ptr(), x.numel(), self.done.data_ptr(), self._stream())
+                                    x.data_ptr(), gathered.data_ptr(), x.numel(), self.ag_ready.data_ptr(),
+                                    self.done.data_ptr(), self._stream())
         if rc != 0:
             raise RuntimeError(f"all-gather staging failed ({rc})")
         out = torch.empty((rows * self.world, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
-        rc = lib.b200_gemm_all_gather(maps.data_ptr(), self.signal_ptrs[self.rank], x.data_ptr(), w.data_ptr(),
+        rc = lib.b200_gemm_all_gather(gathered.data_ptr(), self.data_ptrs, self.half_bytes,
+                                      self.signal_ptrs[self.rank], self.ag_ready.data_ptr(), w.data_ptr(),
                                       out.data_ptr(), bias.data_ptr() if bias is not None else None, rows, n, k,
                                       w.stride(0), out.stride(0), 1 if swiglu else 0, self.world, self.rank,
                                       lib.b200_symm_epoch_word(), lib.b200_symm_ag_flag_word(),
@@ -298,7 +288,7 @@ class SymmetricMemory:
         if rc != 0:
             raise RuntimeError(f"fused all_gather + gemm failed ({rc})")
         ops._count(2)
-        return out
+        return (out, gathered) if return_gathered else out
 
     # ------------------------------------------------ fused GEMM -> reduce-scatter
     def can_gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> bool:
