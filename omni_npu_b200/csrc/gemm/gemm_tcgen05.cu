@@ -450,58 +450,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     int cursor = 0;
     int tile_iter = 0;
+    // ---- all-gather pull: this CTA's slice of every foreign block, nearest rank first.  One block
+    // is pulled before the first tile's epilogue and one more before every later tile, which is
+    // the order and roughly the pace at which the producer needs them; what is left is pulled
+    // after the last tile (other CTAs wait for this CTA's share of every block).
+    int ag_next = 1;
+    uint32_t ag_epoch = 0;
+    long long ag_begin = 0, ag_end = 0, ag_nvec = 0, ag_half_off = 0;
     if (p.ag_world > 1) {
-      // ---- all-gather pull: this CTA's slice of every foreign block, nearest rank first
-      const int et = threadIdx.x - 64;
-      const uint32_t ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_signal + p.ag_epoch_word);
-      const long long half_off = static_cast<long long>(ag_epoch & 1u) * p.ag_half_bytes;
-      const long long nvec = (static_cast<long long>(p.ag_rows) * p.K * p.elem_bytes) >> 4;
-      const long long per = (nvec + gridDim.x - 1) / gridDim.x;
-      const long long begin = min(nvec, per * blockIdx.x), end = min(nvec, per * (blockIdx.x + 1));
-      for (int c = 1; c < p.ag_world; ++c) {
-        const int src = (p.ag_rank + c) % p.ag_world;
-        uint32_t staged = 1u;
-        if (et == 0) {
-          const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + src;
-          uint32_t polls = 0;
-          while (static_cast<int32_t>(*flag - ag_epoch) < 0) {     // flags only grow
-            if (++polls > (1u << 24)) {
-              staged = 0u;
-              break;
-            }
-            __nanosleep(64);
-          }
-          __threadfence_system();
-          s_flags[1] = static_cast<int>(staged);
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        staged = static_cast<uint32_t>(s_flags[1]);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (!staged) {
-          if (et == 0) {
-            atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
-            *abort_flag = 1;
-          }
-          break;
-        }
-        const uint4* from = reinterpret_cast<const uint4*>(static_cast<const char*>(p.ag_data[src]) + half_off);
-        uint4* to = reinterpret_cast<uint4*>(const_cast<void*>(p.ag_local)) + static_cast<long long>(src) * nvec;
-        long long i = begin + et;
-        for (; i + 3 * 128 < end; i += 4 * 128) {                  // four loads in flight per thread
-          const uint4 v0 = __ldcv(from + i), v1 = __ldcv(from + i + 128), v2 = __ldcv(from + i + 256),
-                      v3 = __ldcv(from + i + 384);
-          to[i] = v0;
-          to[i + 128] = v1;
-          to[i + 256] = v2;
-          to[i + 384] = v3;
-        }
-        for (; i < end; i += 128) to[i] = __ldcv(from + i);
-        __threadfence();
-        fence_proxy_async();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) atomicAdd(p.ag_ready + src, 1u);
-      }
+      ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag_signal + p.ag_epoch_word);
+      ag_half_off = static_cast<long long>(ag_epoch & 1u) * p.ag_half_bytes;
+      ag_nvec = (static_cast<long long>(p.ag_rows) * p.K * p.elem_bytes) >> 4;
+      const long long per = (ag_nvec + gridDim.x - 1) / gridDim.x;
+      ag_begin = min(ag_nvec, per * blockIdx.x);
+      ag_end = min(ag_nvec, per * (blockIdx.x + 1));
     }
+    auto ag_pull = [&](int c) {
+      const int et = threadIdx.x - 64;
+      const int src = (p.ag_rank + c) % p.ag_world;
+      if (et == 0) {
+        uint32_t staged = *abort_flag ? 0u : 1u;
+        const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + src;
+        uint32_t polls = 0;
+        while (staged && static_cast<int32_t>(*flag - ag_epoch) < 0) {     // flags only grow
+          if (++polls > (1u << 24)) staged = 0u;
+          else __nanosleep(64);
+        }
+        __threadfence_system();
+        if (!staged && !*abort_flag) {
+          atomicCAS(p.status, 0, kStatusTimeoutPeerFlag);
+          *abort_flag = 1;
+        }
+        s_flags[1] = static_cast<int>(staged);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool staged = s_flags[1] != 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!staged) return;
+      const uint4* from = reinterpret_cast<const uint4*>(static_cast<const char*>(p.ag_data[src]) + ag_half_off);
+      uint4* to = reinterpret_cast<uint4*>(const_cast<void*>(p.ag_local)) + static_cast<long long>(src) * ag_nvec;
+      long long i = ag_begin + et;
+      for (; i + 3 * 128 < ag_end; i += 4 * 128) {                  // four loads in flight per thread
+        const uint4 v0 = __ldcv(from + i), v1 = __ldcv(from + i + 128), v2 = __ldcv(from + i + 256),
+                    v3 = __ldcv(from + i + 384);
+        to[i] = v0;
+        to[i + 128] = v1;
+        to[i + 256] = v2;
+        to[i + 384] = v3;
+      }
+      for (; i < ag_end; i += 128) to[i] = __ldcv(from + i);
+      __threadfence();
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) atomicAdd(p.ag_ready + src, 1u);
+    };
     long long rs_half_off = 0;     // fused reduce-scatter: staging half of the epoch this call opens
     if (p.rs_world > 1) {
       const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(p.rs_signal + p.rs_epoch_word) + 1u;
@@ -510,6 +512,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     TileCoord tc;
     for (long long t = t_first;
          decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cta_rank, cursor, tc); t += t_stride) {
+      if (ag_next < p.ag_world) ag_pull(ag_next++);
       bool ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
       {
         // The four epilogue warps take the decision together (barrier + AND
@@ -911,6 +914,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    // foreign blocks this CTA has not delivered its share of yet (fewer tiles than sources, or an abort)
+    while (ag_next < p.ag_world) ag_pull(ag_next++);
   }
 
   // ------------------------------------------------------------- teardown
