@@ -454,7 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // is pulled before the first tile's epilogue and one more before every later tile, which is
     // the order and roughly the pace at which the producer needs them; what is left is pulled
     // after the last tile (other CTAs wait for this CTA's share of every block).
-    int ag_next = 1;
+    int ag_next = 1, ag_part = 0, ag_parts = 1;
     uint32_t ag_epoch = 0;
     long long ag_begin = 0, ag_end = 0, ag_nvec = 0, ag_half_off = 0;
     if (p.ag_world > 1) {
@@ -464,11 +464,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long per = (ag_nvec + gridDim.x - 1) / gridDim.x;
       ag_begin = min(ag_nvec, per * blockIdx.x);
       ag_end = min(ag_nvec, per * (blockIdx.x + 1));
+      // a block is pulled in as many pieces as this CTA has own-row tiles to hide them behind (minus one)
+      const long long own_tiles = static_cast<long long>(p.ag_rows / kBM) * p.num_n_blocks;
+      ag_parts = static_cast<int>(own_tiles / gridDim.x) - 1;
+      if (ag_parts < 1) ag_parts = 1;
+      if (ag_parts > 8) ag_parts = 8;
     }
-    auto ag_pull = [&](int c) {
+    // one piece of foreign block c; returns true when the block is finished (or given up)
+    auto ag_pull = [&](int c, int part) -> bool {
+      const long long ag_begin_all = ag_begin, this_end = ag_end;
       const int et = threadIdx.x - 64;
       const int src = (p.ag_rank + c) % p.ag_world;
-      if (et == 0) {
+      if (part == 0) {
+       if (et == 0) {
         uint32_t staged = *abort_flag ? 0u : 1u;
         const volatile uint32_t* flag = p.ag_signal + p.ag_flag_word + src;
         uint32_t polls = 0;
@@ -482,27 +490,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           *abort_flag = 1;
         }
         s_flags[1] = static_cast<int>(staged);
+       }
+       asm volatile("bar.sync 1, 128;" ::: "memory");
+       const bool staged = s_flags[1] != 0;
+       asm volatile("bar.sync 1, 128;" ::: "memory");
+       if (!staged) return true;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const bool staged = s_flags[1] != 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!staged) return;
       const uint4* from = reinterpret_cast<const uint4*>(static_cast<const char*>(p.ag_data[src]) + ag_half_off);
       uint4* to = reinterpret_cast<uint4*>(const_cast<void*>(p.ag_local)) + static_cast<long long>(src) * ag_nvec;
-      long long i = ag_begin + et;
-      for (; i + 3 * 128 < ag_end; i += 4 * 128) {                  // four loads in flight per thread
-        const uint4 v0 = __ldcv(from + i), v1 = __ldcv(from + i + 128), v2 = __ldcv(from + i + 256),
-                    v3 = __ldcv(from + i + 384);
-        to[i] = v0;
-        to[i + 128] = v1;
-        to[i + 256] = v2;
-        to[i + 384] = v3;
+      const long long piece = (this_end - ag_begin_all + ag_parts - 1) / ag_parts;
+      const long long stop = min(this_end, ag_begin_all + piece * (part + 1));
+      long long i = ag_begin_all + piece * part + et;
+      // eight 16-byte loads in flight per thread: 16 KB per CTA, which at ~3 us of NVLink round trip
+      // is what it takes for 148 CTAs together to keep the link busy (four gave half the rate)
+      for (; i + 7 * 128 < stop; i += 8 * 128) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldcv(from + i + u * 128);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) to[i + u * 128] = v[u];
       }
-      for (; i < ag_end; i += 128) to[i] = __ldcv(from + i);
+      for (; i < stop; i += 128) to[i] = __ldcv(from + i);
+      if (part + 1 < ag_parts) return false;
       __threadfence();
       fence_proxy_async();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (et == 0) atomicAdd(p.ag_ready + src, 1u);
+      return true;
+    };
+    // advance the pull by one piece
+    auto ag_step = [&]() {
+      if (ag_pull(ag_next, ag_part)) {
+        ++ag_next;
+        ag_part = 0;
+      } else {
+        ++ag_part;
+      }
     };
     long long rs_half_off = 0;     // fused reduce-scatter: staging half of the epoch this call opens
     if (p.rs_world > 1) {
@@ -512,7 +535,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     TileCoord tc;
     for (long long t = t_first;
          decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t, cta_rank, cursor, tc); t += t_stride) {
-      if (ag_next < p.ag_world) ag_pull(ag_next++);
+      if (ag_next < p.ag_world) ag_step();
       bool ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
       {
         // The four epilogue warps take the decision together (barrier + AND
@@ -915,7 +938,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     // foreign blocks this CTA has not delivered its share of yet (fewer tiles than sources, or an abort)
-    while (ag_next < p.ag_world) ag_pull(ag_next++);
+    while (ag_next < p.ag_world) ag_step();
   }
 
   // ------------------------------------------------------------- teardown
