@@ -220,7 +220,10 @@ def bench_quant(args):
     from omni_npu_b200.layers.quant_fp8 import quantize_weight_block
     _, flops, src = peaks()
     print(f"# quantised GEMMs, TFLOP/s and fraction of the {src} bf16 peak (fp8 / int8 nominal peak is 2x bf16)")
-    for m, n, k in ((8192, 4096, 4096), (8192, 7168, 2048), (128, 4096, 7168)):
+    shapes = ((8192, 4096, 4096), (8192, 7168, 2048), (128, 4096, 7168))
+    if args.m and args.n and args.k:
+        shapes = ((args.m, args.n, args.k),)
+    for m, n, k in shapes:
         x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
         w = torch.randn(n, k, device="cuda", dtype=torch.float32) * 0.05
         fl = 2.0 * m * n * k
