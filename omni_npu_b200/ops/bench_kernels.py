@@ -147,7 +147,7 @@ def bench_gemm(args):
 def bench_attn(args):
     hbm, flops_peak, src = peaks()
     print(f"# paged GQA attention, fractions of {src} peaks")
-    hq, hk, d, bs = 32, 8, 128, 16
+    hq, hk, d, bs = args.hq, args.hk, 128, 16       # 32 / 8: Llama-3-8B on one GPU; 16 / 4, 8 / 2, 4 / 1: TP 2, 4, 8
     decode_cases = ((128, 1152), (128, 4096), (16, 8192), (1, 32768))
     prefill_cases = ((8, 1024), (2, 4096), (1, 8192))
     if args.b is not None:
@@ -285,6 +285,8 @@ def main():
     ap.add_argument("--pair", action="store_true", help="gemm: run M >= 256 shapes on the CTA-pair kernel")
     ap.add_argument("--graph", action="store_true",
                     help="gemm: time decode-shaped GEMMs back to back inside a CUDA graph")
+    ap.add_argument("--hq", type=int, default=32, help="attn: query heads")
+    ap.add_argument("--hk", type=int, default=8, help="attn: KV heads")
     ap.add_argument("--b", type=int, help="attn: batch size of a single case")
     ap.add_argument("--ctx", type=int, default=1024, help="attn: context length of a single case")
     ap.add_argument("--phase", default="both", choices=["both", "decode", "prefill"])
