@@ -991,11 +991,19 @@ static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
       const char* e = getenv("OMNI_B200_DECODE_OCC3");
       return e ? atoi(e) : -1;
     }();
-    // Three CTAs per SM with a two-stage ring hide more of the consumer's latency once the grid spans
-    // several waves (measured +3..6 % at 1024 CTAs); a grid that fits in one wave of two CTAs per SM is
-    // faster with the deeper three-stage ring (measured -15 % at 256 CTAs with the shallow ring).
+    // Two variants: three CTAs per SM with a two-stage ring, or two per SM with a three-stage ring.
+    // A wave of the first costs about 1.3x a wave of the second (the SM's bandwidth is shared by more
+    // CTAs), so it wins exactly when it saves whole waves.  Measured (B = 128, ctx 1152, us, 3/SM vs
+    // 2/SM): 1024 CTAs 127 / 131, 512 CTAs 86 / 72, 384 CTAs 32 / 38, 256 CTAs 56 / 48.
     const long ctas = (long)B * p.Hk * p.splits;
-    const bool shallow = occ3 < 0 ? ctas > 3L * 148 : occ3 != 0;
+    static const int sms = [] {
+      int dev = 0, n = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+      return n;
+    }();
+    const long waves2 = (ctas + 2L * sms - 1) / (2L * sms), waves3 = (ctas + 3L * sms - 1) / (3L * sms);
+    const bool shallow = occ3 < 0 ? (13 * waves3 < 10 * waves2) : occ3 != 0;
     if (shallow) return launch_decode_tma<D, 2, 3>(p, grid, stream);
     return launch_decode_tma<D, 3, 2>(p, grid, stream);
   } else {
