@@ -105,3 +105,72 @@ class RequestTracer:
         if _ENABLED:
             self.sink(line)
         return line
+
+
+# ------------------------------------------------------------ dynamic wrapping by name list
+_WRAPPERS = ("timer", "nvtx", "marker")
+
+
+def _wrap(fn: Callable, kind: str, label: str) -> Callable:
+    if kind == "timer":
+        return timer(label)(fn)
+    if kind == "nvtx":
+        @functools.wraps(fn)
+        def ranged(*a, **k):
+            with nvtx_range(label):
+                return fn(*a, **k)
+        return ranged
+    if kind == "marker":
+        @functools.wraps(fn)
+        def marked(*a, **k):
+            marker(f"enter {label}")
+            try:
+                return fn(*a, **k)
+            finally:
+                marker(f"exit {label}")
+        return marked
+    raise ValueError(f"unknown trace wrapper {kind!r} (one of {_WRAPPERS})")
+
+
+def apply_namelist(path: Optional[str] = None) -> int:
+    """Wrap the functions named in a YAML list with a tracing wrapper, without touching their
+    source.  The file (``PROFILING_NAMELIST`` when ``path`` is not given) looks like
+
+        type: timer                  # default wrapper: timer | nvtx | marker
+        targets:
+          - module: omni_npu_b200.engine.scheduler:Scheduler     # module[:Class]
+            function_name: schedule
+          - module: omni_npu_b200.ops
+            function_name: [gemm, gqa_decode]
+            type: nvtx
+
+    Returns the number of functions wrapped.  Same mechanism as the reference's name-list driven
+    tracing (omni_npu/vllm_patches/patches/common/patch_trace.py:26-163)."""
+    import importlib
+
+    import yaml
+    path = path or os.environ.get("PROFILING_NAMELIST")
+    if not path:
+        return 0
+    with open(path) as f:
+        spec = yaml.safe_load(f) or {}
+    default = spec.get("type", "timer")
+    count = 0
+    for target in spec.get("targets", []):
+        mod_name, _, cls_name = str(target["module"]).partition(":")
+        owner = importlib.import_module(mod_name)
+        if cls_name:
+            owner = getattr(owner, cls_name)
+        names = target["function_name"]
+        for fn_name in names if isinstance(names, (list, tuple)) else [names]:
+            fn = getattr(owner, fn_name)
+            if getattr(fn, "_omni_traced", False):
+                continue
+            label = f"{mod_name}{':' + cls_name if cls_name else ''}.{fn_name}"
+            wrapped = _wrap(fn, target.get("type", default), label)
+            wrapped._omni_traced = True
+            setattr(owner, fn_name, wrapped)
+            count += 1
+    if count:
+        logger.info("tracing: wrapped %d functions from %s", count, path)
+    return count

@@ -41,6 +41,9 @@ class Worker:
 
     # -------------------------------------------------------------- set-up
     def init_device(self) -> None:
+        if os.environ.get("PROFILING_NAMELIST"):
+            from ..utils.trace import apply_namelist
+            apply_namelist()        # wrap the functions the name list asks for before anything runs
         want_cuda = self.config.device in ("auto", "cuda") and torch.cuda.is_available()
         if self.config.device == "cuda" and not want_cuda:
             raise RuntimeError("device='cuda' requested but CUDA is not available")

@@ -119,3 +119,26 @@ def test_stop_buffer_is_not_applied_inside_the_reasoning_span():
     assert hold_back(5, finished=False, done_reasoning=True, new_text="x</think>\n") == 0
     assert hold_back(5, finished=False, done_reasoning=True, new_text="answer") == 5
     assert hold_back(5, finished=True, done_reasoning=True, new_text="answer") == 0
+
+
+def test_trace_namelist_wraps_functions_by_name(tmp_path):
+    from omni_npu_b200.engine.block_manager import BlockPool
+    from omni_npu_b200.utils import trace
+    spec = tmp_path / "names.yaml"
+    spec.write_text("type: timer\ntargets:\n  - module: omni_npu_b200.engine.block_manager:BlockPool\n"
+                    "    function_name: [allocate, free]\n")
+    original = BlockPool.allocate
+    try:
+        assert trace.apply_namelist(str(spec)) == 2
+        assert trace.apply_namelist(str(spec)) == 0              # already wrapped: not wrapped twice
+        trace.enable(True)
+        trace.timer_report(reset=True)
+        pool = BlockPool(8, 4)
+        pool.free(pool.allocate(3))
+        rep = trace.timer_report()
+        key = "omni_npu_b200.engine.block_manager:BlockPool.allocate"
+        assert rep[key]["calls"] == 1 and pool.num_free == 8
+    finally:
+        trace.enable(False)
+        BlockPool.allocate = original
+        BlockPool.free = BlockPool.free.__wrapped__
