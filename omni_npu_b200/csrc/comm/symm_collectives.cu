@@ -329,6 +329,33 @@ allgather_kernel(SymmGroup g, const uint4* __restrict__ in, uint4* __restrict__ 
   }
 }
 
+// ------------------------------------------------------- bounded-wait self test
+// Waits on a flag with the same acquire-poll loop and give-up path the collectives use, with a
+// caller-chosen poll limit.  A flag that nothing sets makes the wait run out: the kernel records
+// status 5 and returns, the context stays usable.  This is how the failure path is exercised
+// without a failing peer.
+__global__ void flag_wait_probe_kernel(const uint32_t* flag, uint32_t want, uint32_t max_polls, int* status,
+                                       uint32_t* polls_out) {
+  uint32_t i = 0;
+  bool ok = true;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - want) < 0) {
+    if (++i > max_polls) {
+      ok = false;
+      break;
+    }
+  }
+  if (!ok && status) atomicCAS(status, 0, 5);
+  if (polls_out) *polls_out = i;
+}
+
+extern "C" int b200_symm_wait_probe(const void* flag, unsigned want, unsigned max_polls, int* status, void* polls_out,
+                                    cudaStream_t stream) {
+  if (max_polls > kMaxFlagPolls) max_polls = kMaxFlagPolls;
+  flag_wait_probe_kernel<<<1, 1, 0, stream>>>(static_cast<const uint32_t*>(flag), want, max_polls, status,
+                                              static_cast<uint32_t*>(polls_out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
 // ------------------------------------------- staging for the fused all-gather GEMM
 // Copies this rank's block into its staging half of the next epoch (where the peers' GEMM kernels
 // fetch it) and into its place in the local gathered buffer; clears the per-source arrival

@@ -58,6 +58,8 @@ def _lib() -> ctypes.CDLL:
         lib.b200_gemm_all_reduce.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_float, ci, ci, ci, ci, ci, ci, pp, ci, ci,
                                              ll, vp, vp, vp, ci, vp]
         lib.b200_gemm_all_reduce.restype = ci
+        lib.b200_symm_wait_probe.argtypes = [vp, ctypes.c_uint, ctypes.c_uint, vp, vp, vp]
+        lib.b200_symm_wait_probe.restype = ci
         lib.b200_symm_epoch_word.restype = ci
         lib.b200_symm_ag_flag_word.restype = ci
         lib.b200_symm_ag_stage.argtypes = [pp, pp, ci, ci, sz, vp, vp, ll, vp, vp, vp]
@@ -337,6 +339,20 @@ class SymmetricMemory:
         for p in self._own:
             lib.b200_symm_free(p)
         self._opened, self._own = [], []
+
+
+def wait_probe(flag: torch.Tensor, want: int, max_polls: int) -> int:
+    """Run the collectives' bounded flag wait on ``flag`` (uint32/int32 [1] on the GPU) with a poll
+    limit; returns the number of polls made.  When the flag never reaches ``want`` the kernel gives
+    up, records status 5 (``ops.check_status`` raises) and returns: the failure path of the
+    peer-memory kernels, reachable without a failing peer."""
+    polls = torch.zeros(1, dtype=torch.int32, device=flag.device)
+    st = ops.device_state(flag.device)
+    rc = _lib().b200_symm_wait_probe(flag.data_ptr(), want, max_polls, st.status.data_ptr(), polls.data_ptr(),
+                                     torch.cuda.current_stream(flag.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"wait probe launch failed ({rc})")
+    return int(polls.item())
 
 
 def attach_symmetric_memory(group, device: torch.device, half_bytes: Optional[int] = None):

@@ -674,3 +674,21 @@ def test_fused_moe_layer_with_block_scaled_fp8_experts():
         x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
         want = cpu(x.cpu().float())
         _close(gpu(x), want, 5e-2 * float(want.abs().max()), 5e-2)
+
+
+def test_bounded_wait_gives_up_and_leaves_the_context_usable():
+    """A flag that nothing sets: the wait runs out after its poll limit, the kernel reports status 5
+    and returns; the next kernels run normally.  A flag that is already set returns at once."""
+    from omni_npu_b200.parallel.symm_mem import wait_probe
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    polls = wait_probe(flag, want=1, max_polls=20000)
+    assert polls == 20001
+    with pytest.raises(RuntimeError, match="status 5"):
+        ops.check_status()
+    ops.check_status()                                   # the status word was cleared by the report
+    flag.fill_(3)
+    assert wait_probe(flag, want=2, max_polls=20000) == 0
+    ops.check_status()
+    a = torch.randn(64, 128, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(32, 128, device=DEV, dtype=torch.bfloat16)
+    _close(ops.gemm(a, w), a.float().cpu() @ w.float().cpu().t(), 2e-1, 2e-2)
