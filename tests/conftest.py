@@ -36,3 +36,18 @@ def _fresh_parallel_state():
             state.destroy_model_parallel()
     except Exception:
         pass
+
+
+@pytest.fixture(autouse=True)
+def _no_kernel_gave_up(request):
+    """Every GPU test ends with the device status word at rest: a kernel whose bounded wait
+    expired (or that rejected its arguments) fails the test that launched it, not a later one."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from omni_npu_b200 import ops
+    if getattr(ops, "_states", None):
+        ops.check_status()
