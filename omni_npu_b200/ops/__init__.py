@@ -103,7 +103,10 @@ class _DeviceState:
 
     def __init__(self, device: torch.device) -> None:
         self.device = device
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # a plain (not inference-mode) tensor: the first kernel often runs under inference_mode, and an
+        # inference tensor could not be cleared later by a caller outside that mode
+        with torch.inference_mode(False):
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.gemm_ws_bytes = int(os.environ.get("OMNI_B200_GEMM_WS_MB", "64")) << 20
         self.gemm_ws = {}
         self.counters = {}

@@ -142,3 +142,20 @@ def test_trace_namelist_wraps_functions_by_name(tmp_path):
         trace.enable(False)
         BlockPool.allocate = original
         BlockPool.free = BlockPool.free.__wrapped__
+
+
+def test_status_word_created_under_inference_mode_can_be_cleared_outside(monkeypatch):
+    """The first kernel of a process usually runs under inference_mode; the status word it creates
+    must still be clearable by a caller outside that mode (``check_status`` after a timeout)."""
+    import torch
+    from omni_npu_b200 import ops
+    monkeypatch.setattr(ops, "_states", {})
+    with torch.inference_mode():
+        st = ops._DeviceState(torch.device("cpu"))
+    assert not st.status.is_inference()
+    st.status.fill_(5)
+    ops._states[0] = st
+    import pytest
+    with pytest.raises(RuntimeError, match="status 5"):
+        ops.check_status()
+    ops.check_status()
