@@ -47,6 +47,12 @@ class LLMEngine:
                       "h2d_bytes": 0, "d2h_bytes": 0, "output_tokens": 0}
         from ..spec_decode import make_proposer
         self.proposer = make_proposer(config.speculative, self.worker.model_runner)
+        # launch decode step n + 1 before reading the tokens of step n (host scheduling and staging then
+        # overlap the GPU); OMNI_B200_ASYNC_SCHED=1 or additional_config["async_scheduling"]
+        import os as _os
+        self.async_scheduling = bool(config.additional_config.get(
+            "async_scheduling", _os.environ.get("OMNI_B200_ASYNC_SCHED", "0") == "1"))
+        self._inflight = None
 
     @property
     def device(self) -> torch.device:
@@ -65,10 +71,54 @@ class LLMEngine:
         self.scheduler.abort_request(request_id)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
+
+    # ---------------------------------------------------- asynchronous decode scheduling
+    def _async_ok(self) -> bool:
+        """Decode steps may be launched before the previous step's tokens are read when nothing on the
+        host needs the token values between steps: no draft proposer, no KV connector, no draft head."""
+        return (self.async_scheduling and self.proposer is None and self.scheduler.kv_connector is None
+                and self.worker.model_runner.mtp is None and getattr(self.worker, "ha_agent", None) is None)
+
+    def _settle(self) -> List[RequestOutput]:
+        """Read back the step in flight and fill its tokens in."""
+        if self._inflight is None:
+            return []
+        out, handle = self._inflight
+        self._inflight = None
+        runner = self.worker.model_runner
+        finished = self.scheduler.resolve_pending(out, runner.collect_decode(handle))
+        self.stats["d2h_bytes"] += handle["n"] * 4
+        self.stats["output_tokens"] += handle["n"]
+        for r in finished:
+            runner.input_batch.remove_request(r.request_id)
+        return [RequestOutput.from_request(r) for r in finished]
+
+    def _step_async(self) -> List[RequestOutput]:
+        out = self.scheduler.schedule()
+        if out.kind == "decode":
+            runner = self.worker.model_runner
+            handle = runner.launch_decode(out, self._inflight[1] if self._inflight is not None else None)
+            self.scheduler.advance_pending(out)
+            done = self._settle()                       # the previous step, while this one runs
+            self._inflight = (out, handle)
+            st = self.stats
+            st["steps"] += 1
+            st["decode_steps"] += 1
+            st["h2d_bytes"] += runner.input_batch.h2d_bytes_last
+            return done
+        # anything but a plain decode step needs the token values on the host first
+        done = self._settle()
+        return done + self._run_scheduled(out)
 
     def step(self) -> List[RequestOutput]:
-        out = self.scheduler.schedule()
+        if self._async_ok():
+            return self._step_async()
+        if self._inflight is not None:                  # the switch was turned off mid-flight
+            return self._settle()
+        return self._run_scheduled(self.scheduler.schedule())
+
+    def _run_scheduled(self, out: SchedulerOutput) -> List[RequestOutput]:
         if out.kind == "idle":
             # nothing to compute: still let the runner retire rows and start KV loads
             self.worker.model_runner.execute_model(out)

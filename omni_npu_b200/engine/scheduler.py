@@ -38,6 +38,7 @@ class SchedulerOutput:
     finished_req_ids: List[str] = field(default_factory=list)
     kv_connector_metadata: Any = None
     step_index: int = 0
+    pending_pos: List[int] = field(default_factory=list)   # asynchronous scheduling: output index of each placeholder
 
     @property
     def total_num_scheduled_tokens(self) -> int:
@@ -230,6 +231,64 @@ class Scheduler:
             out.num_tokens = sum(s.num_new_tokens for s in decode)
         self._finish_output(out)
         return out
+
+    # ------------------------------------------------ decode steps settled one step late
+    # With asynchronous scheduling the host launches decode step n + 1 before it has read the tokens
+    # of step n: the token VALUES are fed forward on the device, the host only needs the COUNTS to
+    # build the next step.  ``advance_pending`` does the bookkeeping of a launched step with
+    # placeholder tokens; ``resolve_pending`` fills the values in when they arrive.
+    PENDING_TOKEN = -1
+
+    def advance_pending(self, out: SchedulerOutput, now: Optional[float] = None) -> None:
+        now = time.monotonic() if now is None else now
+        out.pending_pos = []
+        done: List[Request] = []
+        for seq in out.seqs:
+            req = seq.request
+            req.num_computed_tokens = seq.start + seq.num_new_tokens
+            req.spec_token_ids = []
+            req.append_output(self.PENDING_TOKEN, now)
+            out.pending_pos.append(len(req.output_token_ids) - 1)
+            if len(req.output_token_ids) >= req.sampling_params.max_tokens or req.num_tokens >= self.cfg.max_model_len:
+                # ends by length whatever the token turns out to be
+                req.status = RequestStatus.FINISHED_LENGTH_CAPPED
+                req.finish_time = now
+                done.append(req)
+        for req in done:
+            self.running.remove(req)
+            self._release(req)
+
+    def resolve_pending(self, out: SchedulerOutput, tokens: List[int], now: Optional[float] = None) -> List[Request]:
+        """Tokens of a step accounted by ``advance_pending``.  A request whose token ends it (EOS,
+        stop token) finishes now; the placeholder a later launched step already appended for it is
+        dropped and that step's token for it is ignored.  Returns the requests this step finished."""
+        now = time.monotonic() if now is None else now
+        finished: List[Request] = []
+        for seq, tok, pos in zip(out.seqs, tokens, out.pending_pos):
+            req = seq.request
+            if pos >= len(req.output_token_ids):
+                continue                      # the request ended at an earlier token: surplus step
+            if req.status == RequestStatus.FINISHED_ABORTED:
+                continue
+            req.output_token_ids[pos] = int(tok)
+            sp = req.sampling_params
+            stop = ((not sp.ignore_eos and req.eos_token_id is not None and int(tok) == req.eos_token_id)
+                    or int(tok) in sp.stop_token_ids)
+            if stop:
+                del req.output_token_ids[pos + 1:]
+                was_running = not req.is_finished
+                req.status = RequestStatus.FINISHED_STOPPED
+                req.finish_time = now
+                if was_running:
+                    if req in self.running:
+                        self.running.remove(req)
+                    elif req in self.waiting:          # preempted in the meantime
+                        self.waiting.remove(req)
+                    self._release(req)
+                finished.append(req)
+            elif req.is_finished and pos == len(req.output_token_ids) - 1:
+                finished.append(req)          # ended by length in advance_pending; this was its last token
+        return finished
 
     def _finish_output(self, out: SchedulerOutput) -> None:
         out.finished_req_ids, self._finished_since_last = self._finished_since_last, []

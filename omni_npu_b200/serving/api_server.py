@@ -72,9 +72,15 @@ class EngineLoop:
                 # streaming: hand over tokens produced since the last look
                 for rid, slot in self.waiters.items():
                     req = slot["request"]
-                    if req is not None and len(req.output_token_ids) > slot["seen"]:
-                        slot["queue"].extend(req.output_token_ids[slot["seen"]:])
-                        slot["seen"] = len(req.output_token_ids)
+                    if req is None:
+                        continue
+                    ids = req.output_token_ids
+                    ready = len(ids)
+                    while ready > 0 and ids[ready - 1] < 0:     # tokens of a step still in flight
+                        ready -= 1
+                    if ready > slot["seen"]:
+                        slot["queue"].extend(ids[slot["seen"]:ready])
+                        slot["seen"] = ready
                 for o in outs:
                     slot = self.waiters.get(o.request_id)
                     if slot is not None:

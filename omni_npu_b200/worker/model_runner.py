@@ -335,6 +335,66 @@ class ModelRunner:
             self.kv_connector.wait_for_save()
         return tokens
 
+    # ------------------------------------------- decode steps launched ahead of their results
+    @torch.inference_mode()
+    def launch_decode(self, out: SchedulerOutput, prev: Optional[dict] = None) -> dict:
+        """Enqueue a plain decode step and return without waiting for it.  Requests whose newest
+        token is still a placeholder (their previous step, ``prev``, has not been read back yet) get
+        it on the device from that step's output.  ``collect_decode`` returns the tokens."""
+        ib = self.input_batch
+        for rid in out.finished_req_ids:
+            ib.remove_request(rid)
+        for rid in out.preempted:
+            ib.remove_request(rid)
+        n = len(out.seqs)
+        reqs = [s.request for s in out.seqs]
+        padded = self._pad_decode_size(n) if self.graphs else None
+        S = padded or n
+        cuda = self.device.type == "cuda"
+        if cuda and getattr(self, "_upload_event", None) is not None:
+            self._upload_event.synchronize()          # the staging buffer is still being read by the last H2D copy
+        lay = ib.layout_for(S, S)
+        ib.stage_decode(lay, reqs)
+        ib.upload(lay)
+        if cuda:
+            self._upload_event = torch.cuda.Event()
+            self._upload_event.record()
+        views = ib.views(lay, ib.dev)
+        if prev is not None:
+            where = {id(r): i for i, r in enumerate(prev["reqs"])}
+            fb = [where.get(id(r), -1) if (r.output_token_ids and r.output_token_ids[-1] < 0) else -1 for r in reqs]
+            if any(i >= 0 for i in fb):
+                fb_host = torch.tensor(fb, dtype=torch.int64, pin_memory=cuda)
+                fb_dev = fb_host.to(self.device, non_blocking=True)
+                src = prev["sampled"].reshape(-1).to(torch.int32)
+                ids = views["ids"][:n]
+                ids.copy_(torch.where(fb_dev >= 0, src.index_select(0, fb_dev.clamp_min(0)), ids))
+        ev = self._event_start()
+        if padded is not None:
+            sampled = self.graphs[padded].replay()
+        else:
+            md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len, 1, n, n)
+            sampled = self._forward_and_sample(views, md, S)
+        self.step_counter += 1
+        self._event_stop(ev)
+        parity = getattr(self, "_launch_parity", 0)
+        self._launch_parity = parity ^ 1
+        if not hasattr(self, "_sampled_hosts"):
+            self._sampled_hosts = [torch.zeros_like(self.sampled_host, pin_memory=cuda) for _ in range(2)]
+        host = self._sampled_hosts[parity][:n]
+        host.copy_(sampled[:n], non_blocking=True)
+        done = None
+        if cuda:
+            done = torch.cuda.Event()
+            done.record()
+        self.d2h_bytes_last = n * 4
+        return {"reqs": reqs, "sampled": sampled, "host": host, "event": done, "n": n}
+
+    def collect_decode(self, handle: dict) -> List[int]:
+        if handle["event"] is not None:
+            handle["event"].synchronize()
+        return handle["host"].tolist()
+
     def _to_host(self, t: torch.Tensor) -> torch.Tensor:
         """Device -> pinned host copy of a small result, synchronised."""
         host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)

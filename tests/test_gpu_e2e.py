@@ -93,3 +93,28 @@ def test_qwen3_moe_engine_runs():
     outs = llm.generate([[5, 6, 7] * 20, [9] * 7], SamplingParams(max_tokens=8, ignore_eos=True))
     assert all(len(o.output_token_ids) == 8 for o in outs)
     ops.check_status()
+
+
+@pytest.mark.parametrize("eager", [False, True])
+def test_asynchronous_decode_scheduling_gives_the_same_tokens(eager):
+    """Decode step n + 1 is launched before the tokens of step n are read (values fed forward on the device);
+    tokens must equal the synchronous engine's, with CUDA graphs and without, including EOS stops."""
+    cfg = _small_cfg()
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (48, 5, 130, 64, 17, 33, 90, 12, 7, 21)]
+    sps = [SamplingParams(max_tokens=m, ignore_eos=False) for m in (24, 3, 17, 1, 30, 9, 12, 24, 2, 11)]
+    base = LLM(model=cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=256, max_model_len=512,
+               num_gpu_blocks=256, enforce_eager=eager, seed=3)
+    free = [o.output_token_ids for o in base.generate(prompts, [SamplingParams(max_tokens=30, ignore_eos=True)] * 10)]
+    del base
+    cfg.eos_token_id = free[4][10]                      # request 4 stops on this token at step 11 at the latest
+    outs = {}
+    for mode in (False, True):
+        llm = LLM(model=cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=256, max_model_len=512,
+                  num_gpu_blocks=256, enforce_eager=eager, seed=3, additional_config={"async_scheduling": mode})
+        outs[mode] = [(o.output_token_ids, o.finish_reason) for o in llm.generate(prompts, sps)]
+        ops.check_status()
+        assert llm.engine.scheduler.pool.num_free == 256
+        del llm
+    assert outs[True] == outs[False]
+    assert outs[True][4][1] == "stop" and len(outs[True][4][0]) <= 11
