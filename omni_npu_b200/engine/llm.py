@@ -48,10 +48,11 @@ class LLMEngine:
         from ..spec_decode import make_proposer
         self.proposer = make_proposer(config.speculative, self.worker.model_runner)
         # launch decode step n + 1 before reading the tokens of step n (host scheduling and staging then
-        # overlap the GPU); OMNI_B200_ASYNC_SCHED=1 or additional_config["async_scheduling"]
+        # overlap the GPU); on by default, OMNI_B200_ASYNC_SCHED=0 or additional_config["async_scheduling"]
+        # = False restores the strictly alternating loop
         import os as _os
         self.async_scheduling = bool(config.additional_config.get(
-            "async_scheduling", _os.environ.get("OMNI_B200_ASYNC_SCHED", "0") == "1"))
+            "async_scheduling", _os.environ.get("OMNI_B200_ASYNC_SCHED", "1") != "0"))
         self._inflight = None
 
     @property
