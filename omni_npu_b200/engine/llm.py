@@ -107,6 +107,9 @@ class LLMEngine:
             st["steps"] += 1
             st["decode_steps"] += 1
             st["h2d_bytes"] += runner.input_batch.h2d_bytes_last
+            interval = self.config.parallel.eplb_step_interval
+            if interval > 0 and st["steps"] % interval == 0:
+                self.rebalance_experts()                 # weight moves queue behind the step in flight
             return done
         # anything but a plain decode step needs the token values on the host first
         done = self._settle()
