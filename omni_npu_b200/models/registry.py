@@ -23,6 +23,7 @@ _REGISTRY: Dict[str, Tuple[str, str]] = {
     "OpenPanguMTPModel": ("omni_npu_b200.models.mtp", "OpenPanguMTP"),
     "PanguProMoEV2ForCausalLM": ("omni_npu_b200.models.pangu", "PanguProMoEV2ForCausalLM"),
     "Qwen3VLForConditionalGeneration": ("omni_npu_b200.models.qwen3_vl", "Qwen3VLForConditionalGeneration"),
+    "OpenPanguVLForConditionalGeneration": ("omni_npu_b200.models.openpangu_vl", "OpenPanguVLForConditionalGeneration"),
     "MockModel": ("omni_npu_b200.models.mock", "MockModelForCausalLM"),
 }
 

@@ -347,7 +347,11 @@ def rope_qk_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin:
              head_dim: int, rot_dim: int, neox: bool = True,
              mrope_section: Optional[Tuple[int, int, int]] = None,
              mrope_interleaved: bool = False) -> None:
-    """In-place rotary embedding of q [T,Hq*D] and k [T,Hk*D]."""
+    """In-place rotary embedding of q [T,Hq*D] and k [T,Hk*D].  With ``mrope_section`` the positions
+    are [3, T] (temporal, row, column); plain [T] positions (text-only steps of a multimodal model)
+    rotate every frequency with the one position, which is what three equal axes would give."""
+    if mrope_section is not None and positions.dim() == 1:
+        mrope_section = None
     if not q.is_cuda:
         kk = k if k.numel() else q[:, :head_dim]
         qo, ko = ref.rope_qk(q, kk, positions, cos_sin, head_dim, rot_dim, neox, mrope_section,
