@@ -57,3 +57,27 @@ def test_preemption_while_a_step_is_in_flight():
     async_llm, got = _run(True, prompts, sps, **kw)
     assert got == want
     assert sum(r.num_preemptions for r in async_llm.engine.scheduler.requests.values()) > 0
+
+
+def test_abort_while_a_step_is_in_flight_leaves_the_other_request_intact():
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(1, 97, (n,), generator=g).tolist() for n in (9, 13)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    _, want = _run(False, prompts, [sp, sp])
+    cfg = _cfg()
+    llm = LLM(model=cfg, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=4,
+              num_gpu_blocks=64, seed=3, additional_config={"async_scheduling": True})
+    eng = llm.engine
+    a = eng.add_request(prompts[0], sp)
+    b = eng.add_request(prompts[1], sp)
+    outs = []
+    for _ in range(4):                                   # prefill, then a few decode steps: one is in flight now
+        outs += eng.step()
+    assert eng._inflight is not None
+    eng.abort_request(a)
+    while eng.has_unfinished_requests():
+        outs += eng.step()
+    done = {o.request_id: o for o in outs}
+    assert done[b].output_token_ids == want[1][0] and done[b].finish_reason == "length"
+    assert a not in done or done[a].finish_reason == "abort"
+    assert eng.scheduler.pool.num_free == 64 and eng._inflight is None
