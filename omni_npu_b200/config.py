@@ -350,6 +350,13 @@ class EngineConfig:
             self.scheduler.max_model_len = self.model.max_position_embeddings
         if self.enforce_eager:
             self.compilation.cudagraph_mode = "NONE"
+        if self.parallel.pipeline_parallel_size > 1:
+            # stages exchange (hidden, residual) with point-to-point sends; the draft paths would
+            # need the last stage's hidden states on every stage
+            if self.speculative.method and self.speculative.num_speculative_tokens > 0:
+                raise ValueError("speculative decoding is not supported with pipeline_parallel_size > 1")
+            if self.kv_transfer is not None:
+                raise ValueError("KV transfer connectors are not supported with pipeline_parallel_size > 1")
 
     def resolved_device(self) -> torch.device:
         if self.device == "cpu":

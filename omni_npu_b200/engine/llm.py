@@ -79,7 +79,8 @@ class LLMEngine:
         """Decode steps may be launched before the previous step's tokens are read when nothing on the
         host needs the token values between steps: no draft proposer, no KV connector, no draft head."""
         return (self.async_scheduling and self.proposer is None and self.scheduler.kv_connector is None
-                and self.worker.model_runner.mtp is None and getattr(self.worker, "ha_agent", None) is None)
+                and self.worker.model_runner.mtp is None and getattr(self.worker, "ha_agent", None) is None
+                and self.worker.model_runner.pp_group is None)
 
     def _settle(self) -> List[RequestOutput]:
         """Read back the step in flight and fill its tokens in."""

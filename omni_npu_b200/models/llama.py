@@ -23,7 +23,7 @@ from ..layers.norm import RMSNorm, reduce_add_rms_norm
 from ..layers.rope import get_rope
 from ..attention.metadata import get_forward_context
 from ..parallel import state as pstate
-from .utils import load_stacked_weights
+from .utils import IntermediateTensors, PPMissingLayer, load_stacked_weights, pp_layer_range
 
 
 class LlamaAttention(nn.Module):
@@ -111,13 +111,28 @@ class LlamaModel(nn.Module):
 
     def __init__(self, cfg: ModelConfig, device, prefix: str = "model") -> None:
         super().__init__()
-        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
-        self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, i, device, f"{prefix}.layers.{i}")
-                                     for i in range(cfg.num_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        # pipeline stage: this rank owns layers [start, end); the first stage embeds, the last one
+        # applies the final norm.  KV caches are indexed by the layer's position within the stage.
+        pp = pstate.get_pp_group() if pstate.model_parallel_is_initialized() else None
+        self.pp_group = pp if pp is not None and pp.world_size > 1 else None
+        first = self.pp_group is None or self.pp_group.is_first_rank
+        last = self.pp_group is None or self.pp_group.is_last_rank
+        self.start_layer, self.end_layer = (0, cfg.num_layers) if self.pp_group is None else \
+            pp_layer_range(cfg.num_layers, pp.rank_in_group, pp.world_size)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device) \
+            if first or (last and cfg.tie_word_embeddings) else PPMissingLayer()
+        self.layers = nn.ModuleList([
+            LlamaDecoderLayer(cfg, i - self.start_layer, device, f"{prefix}.layers.{i}")
+            if self.start_layer <= i < self.end_layer else PPMissingLayer()
+            for i in range(cfg.num_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device) if last else PPMissingLayer()
+        self.hidden_size = cfg.hidden_size
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor,
-                inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+                inputs_embeds: Optional[torch.Tensor] = None,
+                intermediate_tensors: Optional[IntermediateTensors] = None):
+        if self.pp_group is not None:
+            return self._forward_stage(input_ids, inputs_embeds, intermediate_tensors)
         hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
         tp = pstate.get_tp_group()
         use_sp = self.sequence_parallel
@@ -154,6 +169,32 @@ class LlamaModel(nn.Module):
         hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, tp)
         return hidden
 
+    def _forward_stage(self, input_ids, inputs_embeds, intermediate_tensors):
+        """One pipeline stage.  ``hidden`` crosses the stage boundary BEFORE its tensor-parallel
+        reduction, together with the residual stream: pipeline neighbours have the same
+        tensor-parallel rank, so each rank forwards its own partial sum and the first layer of
+        the next stage folds the reduction into its input norm as usual.  Returns the normed
+        hidden states on the last stage and ``IntermediateTensors`` elsewhere."""
+        pp, tp = self.pp_group, pstate.get_tp_group()
+        if pp.is_first_rank:
+            hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+            residual = None
+        else:
+            hidden, residual = intermediate_tensors["hidden_states"], intermediate_tensors["residual"]
+        for layer in self.layers[self.start_layer:self.end_layer]:
+            hidden, residual = layer(hidden, residual)
+        if not pp.is_last_rank:
+            if residual is None:        # a stage without layers passes the embeddings on
+                residual = torch.zeros_like(hidden)
+            return IntermediateTensors({"hidden_states": hidden, "residual": residual})
+        hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, tp)
+        return hidden
+
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype: torch.dtype, device) -> IntermediateTensors:
+        h = self.hidden_size
+        return IntermediateTensors({"hidden_states": torch.empty(num_tokens, h, dtype=dtype, device=device),
+                                    "residual": torch.empty(num_tokens, h, dtype=dtype, device=device)})
+
 
 class LlamaForCausalLM(nn.Module):
     stacked_params_mapping = [
@@ -168,13 +209,16 @@ class LlamaForCausalLM(nn.Module):
         self.config = cfg
         self.model = LlamaModel(cfg, device)
         self.model.sequence_parallel = bool(engine_config.parallel.sequence_parallel_residual)
-        if cfg.tie_word_embeddings:
+        pp = self.model.pp_group
+        if pp is not None and not pp.is_last_rank:
+            self.lm_head = PPMissingLayer()          # logits and sampling happen on the last stage
+        elif cfg.tie_word_embeddings:
             self.lm_head = self.model.embed_tokens
             self.lm_head.__class__ = ParallelLMHead
         else:
             self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
         self.mtp = None
-        self.num_kv_layers = cfg.num_layers
+        self.num_kv_layers = self.model.end_layer - self.model.start_layer
         spec = engine_config.speculative
         if spec.method in ("mtp", "deepseek_mtp") and spec.num_speculative_tokens > 0:
             from .mtp import MultiTokenPredictor
@@ -182,8 +226,11 @@ class LlamaForCausalLM(nn.Module):
                                            lambda idx, prefix: LlamaDecoderLayer(cfg, idx, device, prefix))
             self.num_kv_layers += self.mtp.num_mtp_layers
 
-    def forward(self, input_ids, positions, inputs_embeds=None) -> torch.Tensor:
-        return self.model(input_ids, positions, inputs_embeds)
+    def forward(self, input_ids, positions, inputs_embeds=None, intermediate_tensors=None):
+        return self.model(input_ids, positions, inputs_embeds, intermediate_tensors)
+
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype: torch.dtype, device):
+        return self.model.make_empty_intermediate_tensors(num_tokens, dtype, device)
 
     def mtp_forward(self, next_ids: torch.Tensor, positions: torch.Tensor, hidden: torch.Tensor) -> torch.Tensor:
         """Hidden states of the MTP head for (embedding of the next token, target hidden state)."""

@@ -112,3 +112,56 @@ def random_init_(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
             tmp = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g)
             p.data.copy_(tmp.to(p.dtype) if p.dtype != torch.float8_e4m3fn
                          else (tmp * (448 * 0.25 / (3 * std))).to(p.dtype))
+
+
+# ------------------------------------------------------------------ pipeline parallelism
+class PPMissingLayer(nn.Module):
+    """Placeholder for a module that lives on another pipeline stage: no
+    parameters, returns its first input unchanged.  Keeping the placeholder in
+    the ``ModuleList`` leaves the checkpoint's layer numbering intact, so weight
+    names need no translation per stage.
+    (reference: ``PPMissingLayer`` use in omni_npu/v1/models/deepseek/deepseek_v3.py:370-393)"""
+
+    def forward(self, *args, **kwargs):
+        return args[0] if args else next(iter(kwargs.values()))
+
+
+class IntermediateTensors:
+    """Named activations handed from one pipeline stage to the next
+    (``hidden_states`` and, for pre-norm decoders that carry it, ``residual``).
+    (reference: ``IntermediateTensors`` in omni_npu/v1/models/deepseek/deepseek_v3.py:436-456 and
+    the runner's buffer allocation in omni_npu/worker/npu_model_runner.py:494-508)"""
+
+    def __init__(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.tensors = tensors
+
+    def __getitem__(self, key: str) -> torch.Tensor:
+        return self.tensors[key]
+
+    def __contains__(self, key: str) -> bool:
+        return key in self.tensors
+
+    def items(self):
+        return self.tensors.items()
+
+
+def pp_layer_range(num_layers: int, pp_rank: int, pp_size: int) -> Tuple[int, int]:
+    """[start, end) of the decoder layers owned by stage ``pp_rank``.  Layers are
+    split evenly; a remainder goes to the middle stages first and the last stage
+    last, because the first stage also holds the embedding and the last the LM
+    head and sampler.  ``OMNI_B200_PP_LAYER_PARTITION`` (comma-separated counts)
+    overrides the split."""
+    override = os.environ.get("OMNI_B200_PP_LAYER_PARTITION")
+    if override:
+        counts = [int(x) for x in override.split(",")]
+        if len(counts) != pp_size or sum(counts) != num_layers or min(counts) < 0:
+            raise ValueError(f"OMNI_B200_PP_LAYER_PARTITION={override!r} does not split {num_layers} "
+                             f"layers over {pp_size} stages")
+    else:
+        base, rem = divmod(num_layers, pp_size)
+        counts = [base] * pp_size
+        order = list(range(1, pp_size - 1)) + [0, pp_size - 1]
+        for i in range(rem):
+            counts[order[i % pp_size]] += 1
+    start = sum(counts[:pp_rank])
+    return start, start + counts[pp_rank]

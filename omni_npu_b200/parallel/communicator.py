@@ -210,10 +210,13 @@ class B200Communicator:
             dst = (self.rank_in_group + 1) % self.world_size
         dist.send(x, self.ranks[dst], group=self.device_group)
 
-    def recv(self, size, dtype: torch.dtype, src: Optional[int] = None) -> torch.Tensor:
+    def recv(self, size, dtype: torch.dtype, src: Optional[int] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Receive from ``src`` (default: the previous rank of the ring) into ``out`` or a new tensor."""
         if src is None:
             src = (self.rank_in_group - 1) % self.world_size
-        out = torch.empty(size, dtype=dtype, device=self.device)
+        if out is None:
+            out = torch.empty(size, dtype=dtype, device=self.device)
         dist.recv(out, self.ranks[src], group=self.device_group)
         return out
 

@@ -69,6 +69,8 @@ class ModelRunner:
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
         self.d2h_bytes_last = 0
         self.kv_connector = None
+        pp = pstate.get_pp_group()
+        self.pp_group = pp if pp.world_size > 1 else None     # set: this rank runs one pipeline stage
         self.timings: Dict[str, float] = {}
         # optional device-side timing of every step (CUDA events around the kernels)
         self.enable_step_events = False
@@ -85,6 +87,9 @@ class ModelRunner:
             self.model = cls(cfg, device=self.device)
         finally:
             torch.set_default_dtype(prev)
+        if self.pp_group is not None and not callable(getattr(self.model, "make_empty_intermediate_tensors", None)):
+            raise ValueError(f"{type(self.model).__name__} does not implement pipeline stages "
+                             "(pipeline_parallel_size > 1 needs make_empty_intermediate_tensors)")
         if cfg.model_path and cfg.load_format != "dummy":
             loaded = self.model.load_weights(iter_safetensors(cfg.model_path))
             logger.info("loaded %d tensors from %s", len(loaded), cfg.model_path)
@@ -198,6 +203,8 @@ class ModelRunner:
         """Model forward + LM head + sampling for the staged step (device side only).
         Returns the sampled tokens [num_samples]; with an MTP head int32 [num_samples, 2]:
         the sampled token and the draft for the token after it."""
+        if self.pp_group is not None:
+            return self._forward_and_sample_pipeline(views, md, num_samples)
         with set_forward_context(md, self.kv_caches, self.config):
             hidden_all = self.model(views["ids"], views["pos"])
             idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
@@ -222,6 +229,35 @@ class ModelRunner:
             h = h.index_select(0, idx) if idx is not None else h[:num_samples]
             draft = ops.argmax(self.model.mtp_logits(h))
         return torch.stack([tok, draft.to(torch.int32)], dim=1)
+
+    def _forward_and_sample_pipeline(self, views, md: AttentionMetadata, num_samples: int) -> torch.Tensor:
+        """One step of this rank's pipeline stage.  Activations travel stage to stage with
+        point-to-point sends inside the pipeline group; the last stage computes logits and
+        samples, then broadcasts the tokens so that every rank's scheduler (all ranks run the
+        same deterministic scheduler) books the same result.
+        (reference: intermediate-tensor buffers in omni_npu/worker/npu_model_runner.py:494-508,
+        ``send``/``recv`` in omni_npu/distributed/communicator.py:247-257)"""
+        pp = self.pp_group
+        T = views["ids"].shape[0]
+        it = None
+        if not pp.is_first_rank:
+            it = self.model.make_empty_intermediate_tensors(T, self.model_config.dtype, self.device)
+            for _, t in sorted(it.items()):
+                pp.comm.recv(t.shape, t.dtype, src=pp.rank_in_group - 1, out=t)
+        with set_forward_context(md, self.kv_caches, self.config):
+            out = self.model(views["ids"], views["pos"], intermediate_tensors=it)
+            if pp.is_last_rank:
+                idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
+                hidden = out.index_select(0, idx) if idx is not None else out[:num_samples]
+                logits = self.model.compute_logits(hidden)
+                sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
+                                       views["top_p"][:num_samples], views["seeds"][:num_samples],
+                                       self.step_counter).to(torch.int64)
+            else:
+                for _, t in sorted(out.items()):
+                    pp.comm.send(t.contiguous(), dst=pp.rank_in_group + 1)
+                sampled = torch.empty(num_samples, dtype=torch.int64, device=self.device)
+        return pp.comm.broadcast(sampled, src=pp.world_size - 1)
 
     def _forward_and_verify(self, views, md: AttentionMetadata, seqs) -> torch.Tensor:
         """Verification step of speculative decoding: logits at every fed position, target
@@ -476,6 +512,9 @@ class ModelRunner:
         """Capture one full-step decode graph per batch size."""
         cc = self.config.compilation
         if self.device.type != "cuda" or cc.cudagraph_mode == "NONE":
+            return
+        if self.pp_group is not None:
+            logger.info("pipeline parallelism: decode steps run eagerly (stage-to-stage sends are not captured)")
             return
         t0 = time.time()
         self.capture_sizes = cc.capture_sizes(self.config.scheduler.max_num_seqs)

@@ -81,6 +81,9 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         kw["dtype"] = "float32"
     if os.path.exists(os.path.join(workdir, "sequence_parallel")):
         kw["sequence_parallel_residual"] = True
+    if os.path.exists(os.path.join(workdir, "pipeline_parallel")):
+        pp = int(open(os.path.join(workdir, "pipeline_parallel")).read())
+        kw.update(pipeline_parallel_size=pp, tensor_parallel_size=world // pp)
     if os.path.exists(os.path.join(workdir, "long_prompts")):
         kw.update(max_num_batched_tokens=256, max_model_len=512)
         from omni_npu_b200.models.llama import LlamaModel

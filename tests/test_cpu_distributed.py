@@ -63,6 +63,45 @@ def test_sequence_parallel_residual_stream_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
+def _pipeline_case(world: int, pp: int, seed: int, partition=None):
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=seed)
+    g = torch.Generator().manual_seed(seed)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 33, 9, 70)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "pipeline_parallel"), "w").write(str(pp))
+        old = os.environ.pop("OMNI_B200_PP_LAYER_PARTITION", None)
+        if partition:
+            os.environ["OMNI_B200_PP_LAYER_PARTITION"] = partition
+        try:
+            res = run_ranks("tp_engine", world, d)
+        finally:
+            os.environ.pop("OMNI_B200_PP_LAYER_PARTITION", None)
+            if old is not None:
+                os.environ["OMNI_B200_PP_LAYER_PARTITION"] = old
+    for p, toks in zip(prompts, res[0]["tokens"]):
+        assert toks == refm.greedy_generate(weights, cfg, p, 12)
+    for r in res[1:]:
+        assert r["tokens"] == res[0]["tokens"]
+
+
+def test_pipeline_parallel_two_stages_matches_plain_pytorch():
+    """Two pipeline stages (gloo): hidden state and residual cross the boundary, the last stage
+    samples and every rank books the same tokens (the 70-token prompt is chunked at 64)."""
+    _pipeline_case(world=2, pp=2, seed=7)
+
+
+def test_pipeline_times_tensor_parallel_with_uneven_stages():
+    """pp 2 x tp 2 with an uneven layer split: the un-reduced partial sums travel between equal
+    tensor-parallel ranks of neighbouring stages."""
+    cfg = tiny_llama()
+    part = f"1,{cfg.num_layers - 1}"
+    _pipeline_case(world=4, pp=2, seed=8, partition=part)
+
+
 def test_decode_context_parallel_mla_two_ranks_gloo():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("dcp_mla", 2, d)

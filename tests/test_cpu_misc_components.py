@@ -159,3 +159,22 @@ def test_status_word_created_under_inference_mode_can_be_cleared_outside(monkeyp
     with pytest.raises(RuntimeError, match="status 5"):
         ops.check_status()
     ops.check_status()
+
+
+def test_pp_layer_range_splits_evenly_and_honours_override(monkeypatch):
+    from omni_npu_b200.models.utils import PPMissingLayer, pp_layer_range
+    monkeypatch.delenv("OMNI_B200_PP_LAYER_PARTITION", raising=False)
+    assert [pp_layer_range(8, r, 2) for r in range(2)] == [(0, 4), (4, 8)]
+    spans = [pp_layer_range(10, r, 4) for r in range(4)]
+    assert spans[0][0] == 0 and spans[-1][1] == 10
+    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    sizes = [e - s for s, e in spans]
+    assert sorted(sizes) == [2, 2, 3, 3] and sizes[1] == 3 and sizes[2] == 3   # middle stages take the remainder
+    monkeypatch.setenv("OMNI_B200_PP_LAYER_PARTITION", "1,5,2")
+    assert [pp_layer_range(8, r, 3) for r in range(3)] == [(0, 1), (1, 6), (6, 8)]
+    monkeypatch.setenv("OMNI_B200_PP_LAYER_PARTITION", "4,5")
+    import pytest as _pt
+    with _pt.raises(ValueError):
+        pp_layer_range(8, 0, 2)
+    x = torch.ones(2)
+    assert PPMissingLayer()(x) is x and not list(PPMissingLayer().parameters())
