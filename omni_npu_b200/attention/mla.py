@@ -176,27 +176,123 @@ class MLAAttention(nn.Module):
                               self.scale, True, 0)
         return out
 
-    def _decode(self, q, q_pe, cache, md: AttentionMetadata, topk_indices) -> torch.Tensor:
-        t, n = q.shape[0], self.num_heads
-        l = self.kv_lora_rank
+    def _absorb_q(self, q, q_pe):
+        """q_lat[h] = q_nope[h] @ W_UK[h] (heads act as the groups of a grouped GEMM); returns the
+        [t, n * 576] query of the latent-space kernel and the group offsets."""
+        t, n, l = q.shape[0], self.num_heads, self.kv_lora_rank
         if self.w_uk is None:
             self.process_weights_after_loading()
-        # absorb: q_lat[h] = q_nope[h] @ W_UK[h]  (heads act as the groups of a grouped GEMM)
         q_nope = q[:, :, : self.nope].transpose(0, 1).reshape(n * t, self.nope).contiguous()
         offs = torch.arange(0, (n + 1) * t, t, dtype=torch.int32, device=q.device)
         q_lat = ops.grouped_gemm(q_nope, self.w_uk, offs).view(n, t, l).transpose(0, 1)
         qf = torch.cat([q_lat, q_pe], dim=-1).reshape(t, n * (l + self.rope_dim)).contiguous()
+        return qf, offs
+
+    def _unabsorb_o(self, o_lat, offs):
+        """v[h] = o_lat[h] @ W_UV[h]^T -> [t, n * v_dim]."""
+        t, n, l = o_lat.shape[0], self.num_heads, self.kv_lora_rank
+        o_lat = o_lat.view(t, n, l).transpose(0, 1).reshape(n * t, l).contiguous()
+        o = ops.grouped_gemm(o_lat, self.w_uv, offs).view(n, t, self.v_dim).transpose(0, 1)
+        return o.reshape(t, n * self.v_dim).contiguous()
+
+    @staticmethod
+    def _rows_per_token(md: AttentionMetadata, t: int, device):
+        """Block table and causal length for every query token taken as a one-token sequence
+        (prefill steps through the latent-space kernel, per-token key selections)."""
         if md.is_prefill:
-            # sparse prefill: every query token is its own "sequence" row for the kernel
-            seq_of_tok = torch.repeat_interleave(torch.arange(md.num_seqs, device=q.device),
+            seq_of_tok = torch.repeat_interleave(torch.arange(md.num_seqs, device=device),
                                                  (md.cu_q[1: md.num_seqs + 1] - md.cu_q[: md.num_seqs]).long(),
                                                  output_size=t)
+        else:
+            seq_of_tok = torch.arange(md.num_seqs, device=device).repeat_interleave(md.q_len)
+        return seq_of_tok
+
+    def _decode(self, q, q_pe, cache, md: AttentionMetadata, topk_indices) -> torch.Tensor:
+        t, n = q.shape[0], self.num_heads
+        qf, offs = self._absorb_q(q, q_pe)
+        if md.is_prefill:
+            # sparse prefill: every query token is its own "sequence" row for the kernel
+            seq_of_tok = self._rows_per_token(md, t, q.device)
             bt = md.block_tables[seq_of_tok]
             sl = md.seq_lens[seq_of_tok]
             o_lat = ops.mla_decode(qf, cache, bt.contiguous(), sl.contiguous(), t, n, self.scale, 1, topk_indices)
         else:
             o_lat = ops.mla_decode(qf, cache, md.block_tables, md.seq_lens, md.num_seqs, n, self.scale, md.q_len,
                                    topk_indices, max_seq_len=md.max_seq_len)
-        o_lat = o_lat.view(t, n, l).transpose(0, 1).reshape(n * t, l).contiguous()
-        o = ops.grouped_gemm(o_lat, self.w_uv, offs).view(n, t, self.v_dim).transpose(0, 1)
-        return o.reshape(t, n * self.v_dim).contiguous()
+        return self._unabsorb_o(o_lat, offs)
+
+
+class StaticSinkMLAAttention(MLAAttention):
+    """Latent attention with learned static sink tokens and an optional sliding window.
+
+    ``sink_len`` learned (latent | rope-key) rows are visible to every query of every sequence;
+    real keys are limited to the last ``sliding_window`` positions (0 = all).  Both prefill and
+    decode run in the latent space as two partial attentions over disjoint key sets, merged by
+    their log-sum-exp:
+
+    * the window: the sparse mode of the latent-cache kernel with per-token indices
+      ``pos - W + 1 .. pos`` (holes before the sequence start), so a long context costs W keys
+      per token and the cache needs no sink blocks;
+    * the sinks: one small GEMM of the absorbed queries against the ``sink_len`` x 576 table.
+
+    The sink rows go through the KV norm once after loading; their rope part is used as stored
+    (position-free).  Counterpart of the sink / sliding-window branches of the reference's MLA
+    backend (omni_npu/attention/backends/mla.py:495-560,724-760: two attention calls + LSE
+    update) and of ``StaticSinkMLAAttention`` / ``update_sink_kv``
+    (omni_npu/vllm_patches/patches/models/pangu_sink_swa_mla/patch_static_sink_attention.py:257-349,
+    patch_mla.py:18-78)."""
+
+    def __init__(self, cfg, layer_idx: int, device, prefix: str, quant_factory=None,
+                 sink_len: int = 0, sliding_window: int = 0) -> None:
+        super().__init__(cfg, layer_idx, device, prefix, quant_factory)
+        self.sink_len, self.window = int(sink_len), int(sliding_window or 0)
+        if self.sink_len:
+            self.param_sink_kv = nn.Parameter(torch.zeros(self.sink_len, self.kv_lora_rank + self.rope_dim,
+                                                          dtype=cfg.dtype, device=device), requires_grad=False)
+        self.sink_latent: Optional[torch.Tensor] = None     # [sink_len, 576] normed latent | rope key
+
+    def process_weights_after_loading(self) -> None:
+        super().process_weights_after_loading()
+        if self.sink_len:
+            raw = self.param_sink_kv.data
+            l = self.kv_lora_rank
+            self.sink_latent = torch.cat([self.kv_a_layernorm(raw[:, :l].contiguous()), raw[:, l:]], dim=-1)
+
+    def update_sink_kv(self, sink_k_pe: torch.Tensor, sink_compressed_kv: torch.Tensor) -> None:
+        """Install sink rows prepared by the caller (already normed / rotated as it wants them)."""
+        self.sink_latent = torch.cat([sink_compressed_kv, sink_k_pe], dim=-1).to(self.kv_b_proj.weight.device)
+        self.sink_len = self.sink_latent.shape[0]
+
+    def _prefill(self, q, q_pe, cache, md: AttentionMetadata) -> torch.Tensor:
+        return self._sink_window(q, q_pe, cache, md)
+
+    def _decode(self, q, q_pe, cache, md: AttentionMetadata, topk_indices) -> torch.Tensor:
+        if topk_indices is not None:
+            raise NotImplementedError("static sinks are not combined with indexer-selected keys")
+        return self._sink_window(q, q_pe, cache, md)
+
+    def _sink_window(self, q, q_pe, cache, md: AttentionMetadata) -> torch.Tensor:
+        t, n, l = q.shape[0], self.num_heads, self.kv_lora_rank
+        qf, offs = self._absorb_q(q, q_pe)
+        pos = md.positions.reshape(-1)[:t].to(torch.int32)
+        seq_of_tok = self._rows_per_token(md, t, q.device)
+        bt = md.block_tables[seq_of_tok].contiguous()
+        sl = (pos + 1).contiguous()                     # causal length of each token's own row
+        idx = None
+        if self.window:
+            w = self.window
+            idx = pos.unsqueeze(1) - (w - 1) + torch.arange(w, dtype=torch.int32, device=q.device).unsqueeze(0)
+            idx = torch.where(idx < 0, torch.full_like(idx, -1), idx).contiguous()
+        o_win, lse_win = ops.mla_decode(qf, cache, bt, sl, t, n, self.scale, 1, idx,
+                                        max_seq_len=md.max_seq_len, return_lse=True)
+        if not self.sink_len:
+            return self._unabsorb_o(o_win, offs)
+        if self.sink_latent is None:
+            self.process_weights_after_loading()
+        sink = self.sink_latent.to(qf.dtype)                                              # [S, 576]
+        sc = (qf.view(t * n, l + self.rope_dim) @ sink.t()).float() * self.scale          # [t*n, S]
+        lse_s = torch.logsumexp(sc, dim=-1).view(t, n)
+        o_s = (torch.softmax(sc, dim=-1).to(qf.dtype) @ sink[:, :l]).view(t, n, l)
+        o_lat, _ = ops.merge_attn_states(torch.stack([o_win.view(t, n, l), o_s]),
+                                         torch.stack([lse_win.view(t, n).float(), lse_s]))
+        return self._unabsorb_o(o_lat.reshape(t, n * l).to(qf.dtype), offs)

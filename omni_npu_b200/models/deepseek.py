@@ -16,7 +16,7 @@ from typing import Iterable, List, Optional, Tuple
 import torch
 from torch import nn
 
-from ..attention.mla import MLAAttention, MLABackend
+from ..attention.mla import MLAAttention, MLABackend, StaticSinkMLAAttention
 from ..config import EngineConfig, ModelConfig
 from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
 from ..layers.linear import Fp8BlockLinearMethod
@@ -24,7 +24,7 @@ from ..layers.mlp import FusedMLP
 from ..layers.moe import FusedMoE
 from ..layers.norm import RMSNorm, reduce_add_rms_norm
 from ..parallel import state as pstate
-from .utils import load_stacked_weights
+from .utils import IntermediateTensors, PPMissingLayer, build_pipeline_layers, load_stacked_weights
 
 _EXPERT_RE = re.compile(r"(.*)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$")
 
@@ -46,6 +46,11 @@ class DeepseekDecoderLayer(nn.Module):
         if cfg.use_sparse:
             from ..attention.dsa import SparseMLAAttention
             self.self_attn = SparseMLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf)
+        elif int((cfg.hf_config or {}).get("param_sink_number", 0)) or cfg.sliding_window:
+            # learned static sink tokens and / or a sliding window on the latent cache
+            self.self_attn = StaticSinkMLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf,
+                                                    sink_len=int((cfg.hf_config or {}).get("param_sink_number", 0)),
+                                                    sliding_window=cfg.sliding_window)
         else:
             self.self_attn = MLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
@@ -88,16 +93,41 @@ class DeepseekModel(nn.Module):
         super().__init__()
         cfg = engine.model
         layer_cls = layer_cls or DeepseekDecoderLayer
-        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
-        self.layers = nn.ModuleList([layer_cls(engine, i, device, f"model.layers.{i}")
-                                     for i in range(cfg.num_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        pp = pstate.get_pp_group()
+        self.pp_group = pp if pp.world_size > 1 else None
+        first = self.pp_group is None or pp.is_first_rank
+        last = self.pp_group is None or pp.is_last_rank
+        self.hidden_size = cfg.hidden_size
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device) \
+            if first else PPMissingLayer()
+        self.layers, self.start_layer, self.end_layer = build_pipeline_layers(
+            cfg.num_layers, lambda i: layer_cls(engine, i, device, f"model.layers.{i}"), self.pp_group)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device) if last else PPMissingLayer()
 
-    def forward(self, input_ids, positions, inputs_embeds=None, return_prenorm: bool = False):
-        hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device) -> IntermediateTensors:
+        return IntermediateTensors({k: torch.empty(num_tokens, self.hidden_size, dtype=dtype, device=device)
+                                    for k in ("hidden_states", "residual")})
+
+    def forward(self, input_ids, positions, inputs_embeds=None, return_prenorm: bool = False,
+                intermediate_tensors: Optional[IntermediateTensors] = None):
+        """With pipeline stages: the first stage embeds, later ones start from the received
+        (hidden, residual); a stage that is not the last returns ``IntermediateTensors``.  A
+        tensor-parallel reduction still pending at the boundary is done before the hand-over,
+        so the next stage always starts from a reduced ``hidden``."""
+        pp = self.pp_group
         residual, pending = None, False
-        for layer in self.layers:
+        if pp is None or pp.is_first_rank:
+            hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        else:
+            hidden, residual = intermediate_tensors["hidden_states"], intermediate_tensors["residual"]
+        for layer in self.layers[self.start_layer:self.end_layer]:
             hidden, residual, pending = layer(hidden, residual, pending)
+        if pp is not None and not pp.is_last_rank:
+            if pending:
+                hidden = pstate.get_tp_group().all_reduce(hidden)
+            if residual is None:
+                residual = torch.zeros_like(hidden)
+            return IntermediateTensors({"hidden_states": hidden, "residual": residual})
         if pending:
             hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, pstate.get_tp_group())
         else:
@@ -115,9 +145,11 @@ class DeepseekForCausalLM(nn.Module):
         self.engine_config = engine_config
         layer_cls = type(self).decoder_layer_cls or DeepseekDecoderLayer
         self.model = DeepseekModel(engine_config, device, layer_cls)
-        self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device)
+        pp = self.model.pp_group
+        self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device) \
+            if pp is None or pp.is_last_rank else PPMissingLayer()
         self.mtp = None
-        self.num_kv_layers = self.config.num_layers
+        self.num_kv_layers = self.model.end_layer - self.model.start_layer
         spec = engine_config.speculative
         if spec.method in ("mtp", "deepseek_mtp") and spec.num_speculative_tokens > 0:
             from .mtp import MultiTokenPredictor
@@ -126,8 +158,11 @@ class DeepseekForCausalLM(nn.Module):
                 lambda idx, prefix: layer_cls(engine_config, idx, device, prefix))
             self.num_kv_layers += self.mtp.num_mtp_layers
 
-    def forward(self, input_ids, positions, inputs_embeds=None):
-        return self.model(input_ids, positions, inputs_embeds)
+    def forward(self, input_ids, positions, inputs_embeds=None, intermediate_tensors=None):
+        return self.model(input_ids, positions, inputs_embeds, intermediate_tensors=intermediate_tensors)
+
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device):
+        return self.model.make_empty_intermediate_tensors(num_tokens, dtype, device)
 
     def mtp_forward(self, next_ids, positions, hidden):
         return self.mtp(self.model.embed_tokens(next_ids), hidden)
@@ -180,7 +215,10 @@ class DeepseekForCausalLM(nn.Module):
                              tensor))
                 continue
             prefix, eid, proj, kind = em.group(1), int(em.group(2)), em.group(3), em.group(4)
-            moe: FusedMoE = self.get_submodule(prefix + ".mlp")
+            try:
+                moe: FusedMoE = self.get_submodule(prefix + ".mlp")
+            except AttributeError:        # a layer of another pipeline stage
+                continue
             pname = ("w13" if proj != "down_proj" else "w2") + ("" if kind == "weight" else "_scale")
             if not hasattr(moe, pname):
                 continue

@@ -89,12 +89,14 @@ def iter_safetensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
 @torch.no_grad()
 def random_init_(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
     """Deterministic random initialisation (normal, std 0.02; norm weights 1).
-    Values are generated on the CPU per parameter so that a tensor-parallel
-    shard equals the matching slice of the unsharded tensor only when the
-    caller seeds per full tensor; for benchmarking each rank simply gets its
-    own stream."""
+    Each parameter's stream is seeded from ``seed`` and the parameter's NAME, so a
+    pipeline stage that holds a subset of the layers gets the same values for them
+    as a process that holds the whole model.  Tensor-parallel shards are drawn
+    per shard (a shard is not a slice of the unsharded draw)."""
+    import zlib
     g = torch.Generator(device="cpu")
-    for i, (name, p) in enumerate(sorted(model.named_parameters(), key=lambda kv: kv[0])):
+    for name, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
+        i = zlib.crc32(name.encode()) % 1000003
         g.manual_seed(seed * 1000003 + i)
         if "norm" in name and p.dim() == 1 and "bias" not in name:
             p.data.fill_(1.0)
@@ -165,3 +167,20 @@ def pp_layer_range(num_layers: int, pp_rank: int, pp_size: int) -> Tuple[int, in
             counts[order[i % pp_size]] += 1
     start = sum(counts[:pp_rank])
     return start, start + counts[pp_rank]
+
+
+def build_pipeline_layers(num_layers: int, make_layer, pp_group) -> Tuple[nn.ModuleList, int, int]:
+    """``ModuleList`` of ``num_layers`` entries in which only this stage's layers are real
+    (``make_layer(global_index)``), the rest ``PPMissingLayer``.  Layers are built with their
+    GLOBAL index (dense-vs-MoE pattern, window pattern, weight names); afterwards every
+    ``layer_idx`` attribute inside them, which indexes the per-stage list of KV caches, is
+    shifted to the position within the stage.  ``pp_group`` None = no pipeline."""
+    if pp_group is None or pp_group.world_size == 1:
+        return nn.ModuleList([make_layer(i) for i in range(num_layers)]), 0, num_layers
+    start, end = pp_layer_range(num_layers, pp_group.rank_in_group, pp_group.world_size)
+    layers = nn.ModuleList([make_layer(i) if start <= i < end else PPMissingLayer() for i in range(num_layers)])
+    for layer in layers[start:end]:
+        for m in layer.modules():
+            if isinstance(getattr(m, "layer_idx", None), int):
+                m.layer_idx -= start
+    return layers, start, end

@@ -98,6 +98,24 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_pp_deepseek(rank, world, port, workdir, device_kind):
+    """Randomly initialised tiny DeepSeek-style model (names seed the values, so every stage
+    draws what a whole-model process draws) over ``world`` pipeline stages."""
+    dev, state = setup(rank, world, port, device_kind)
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    spec = json.load(open(os.path.join(workdir, "spec.json")))
+    cfg = ModelConfig(dtype=torch.float32, **spec["model"])
+    llm = LLM(model=cfg, device=device_kind, pipeline_parallel_size=world, **spec["engine"])
+    outs = llm.generate(spec["prompts"], SamplingParams(max_tokens=spec["max_tokens"], ignore_eos=True))
+    json.dump({"tokens": [o.output_token_ids for o in outs],
+               "kv_layers": len(llm.engine.worker.model_runner.kv_caches)},
+              open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.get_world_group().barrier()
+    state.destroy_distributed()
+
+
 def task_symm(rank, world, port, workdir, device_kind):
     """Peer-memory collectives against NCCL results."""
     dev, state = setup(rank, world, port, "cuda")
@@ -467,7 +485,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "symm": task_symm}
+TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

@@ -4,6 +4,7 @@ import json
 import os
 import tempfile
 
+import pytest
 import torch
 
 import reference_llama as refm
@@ -100,6 +101,36 @@ def test_pipeline_times_tensor_parallel_with_uneven_stages():
     cfg = tiny_llama()
     part = f"1,{cfg.num_layers - 1}"
     _pipeline_case(world=4, pp=2, seed=8, partition=part)
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_pipeline_parallel_deepseek_matches_single_process(sparse, monkeypatch):
+    """MLA + routed experts (and the sparse-attention indexer with its third cache) over two
+    pipeline stages whose boundary follows a dense layer, against the same model in one process."""
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    model = dict(architecture="DeepseekV3ForCausalLM", model_type="deepseek_v3", hidden_size=128, num_layers=4,
+                 num_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=256, vocab_size=512,
+                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+                 num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
+                 first_k_dense=2, use_mla=True, q_lora_rank=48, kv_lora_rank=512, qk_nope_head_dim=32,
+                 qk_rope_head_dim=64, v_head_dim=32, scoring_func="sigmoid", norm_topk_prob=True)
+    if sparse:
+        model.update(architecture="DeepseekV32ForCausalLM", index_topk=12, index_n_heads=4, index_head_dim=128)
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 34, 5)]
+    monkeypatch.delenv("OMNI_B200_PP_LAYER_PARTITION", raising=False)
+    with tempfile.TemporaryDirectory() as d:
+        json.dump({"model": model, "engine": engine, "prompts": prompts, "max_tokens": 6},
+                  open(os.path.join(d, "spec.json"), "w"))
+        res = run_ranks("pp_deepseek", 2, d)
+    llm = LLM(model=ModelConfig(dtype=torch.float32, **model), device="cpu", **engine)
+    want = [o.output_token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    assert res[0]["tokens"] == want and res[1]["tokens"] == want
+    assert res[0]["kv_layers"] == 2 and res[1]["kv_layers"] == 2
 
 
 def test_decode_context_parallel_mla_two_ranks_gloo():
