@@ -19,6 +19,7 @@ from torch import nn
 
 from ..config import EngineConfig, ModelConfig
 from ..layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from ..layers.linear import ReducedShard, ReplicatedLinear
 from ..layers.mlp import FusedMLP
 from ..layers.moe import FusedMoE
 from ..layers.norm import RMSNorm, reduce_add_rms_norm
@@ -29,11 +30,61 @@ from .utils import load_stacked_weights
 _EXPERT_RE = re.compile(r"(.*)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$")
 
 
+class HeadToSequenceAttention(LlamaAttention):
+    """Attention whose output leaves the head-sharded layout by an all-to-all instead of a
+    reduction (Ulysses style), for steps on the token-sharded residual stream.
+
+    After attention every rank holds all tokens for ITS heads, ``[T, heads/tp * d]``.  The
+    row-parallel o_proj would turn that into partial sums of ``[T, hidden]`` and reduce-scatter
+    them (``T * hidden * (tp-1)/tp`` elements through each rank's links).  Here the rows are
+    exchanged instead: tokens scattered, heads gathered -> ``[T/tp, heads * d]``, and a
+    REPLICATED o_proj on those rows gives this rank's token shard complete, with
+    ``T * heads * d * (tp-1) / tp**2`` elements per rank on the wire, tp times fewer.  The price
+    is a full copy of the o_proj weight per rank; steps on the replicated stream (decode) keep
+    using the rank's column slice of it as an ordinary row-parallel projection.
+    (reference: ``prefill_enable_mla_alltoall`` and the replicated o_proj on the local
+    sequence shard, omni_npu/v0/models/qwen/qwen3_moe.py:164-169,238-252; the DP<->TP o_proj
+    linears omni_npu/v0/layers/linear.py:389-444)"""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__(cfg, layer_idx, device, prefix)
+        self.tp = pstate.get_tp_group()
+        width = cfg.num_heads * cfg.head_dim
+        if cfg.num_heads % self.tp.world_size:
+            raise ValueError("head-to-sequence all-to-all needs num_heads divisible by the tensor-parallel size")
+        self.o_proj_full = ReplicatedLinear(width, cfg.hidden_size, dtype=cfg.dtype, device=device,
+                                            prefix=f"{prefix}.o_proj_full", x_transform="NoOp", y_transform="NoOp")
+        per = width // self.tp.world_size
+        self._cols = slice(self.tp.rank_in_group * per, (self.tp.rank_in_group + 1) * per)
+
+    def process_weights_after_loading(self) -> None:
+        # one source of truth: the row-parallel shard is this rank's columns of the full weight
+        self.o_proj.weight.data.copy_(self.o_proj_full.weight.data[:, self._cols])
+
+    def forward(self, hidden, reduce: bool = True, fuse_norm=None, stream=None):
+        if stream is None or not stream.enabled:
+            return super().forward(hidden, reduce=reduce, fuse_norm=fuse_norm)
+        q, k, v = self.qkv_proj(hidden)
+        if self.qk_norm:
+            t = q.shape[0]
+            q = self.q_norm(q.reshape(-1, self.head_dim)).view(t, -1)
+            k = self.k_norm(k.reshape(-1, self.head_dim)).view(t, -1)
+        o = self.attn(q, k, v, self.rotary.cos_sin_cache)
+        if o.shape[0] != stream.padded:
+            o = torch.cat([o, o.new_zeros(stream.padded - o.shape[0], o.shape[1])], dim=0)
+        o = self.tp.comm.all_to_all(o, scatter_dim=0, gather_dim=-1)        # [T/tp, heads * d]
+        return ReducedShard(self.o_proj_full(o))
+
+
 class Qwen3MoeDecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str, engine: EngineConfig) -> None:
         super().__init__()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
-        self.self_attn = LlamaAttention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        # additional_config["attn_output_all_to_all"]: head <-> sequence exchange after attention
+        self.head_to_sequence = bool(engine.additional_config.get("attn_output_all_to_all", False)) \
+            and pstate.get_tp_group().world_size > 1
+        attn_cls = HeadToSequenceAttention if self.head_to_sequence else LlamaAttention
+        self.self_attn = attn_cls(cfg, layer_idx, device, f"{prefix}.self_attn")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
         self.is_moe = cfg.layer_is_moe(layer_idx)
         if self.is_moe:
@@ -72,8 +123,12 @@ class Qwen3MoeDecoderLayer(nn.Module):
         """Token-sharded residual stream (layers/flashcomm.py): attention between an
         all-gather and a reduce-scatter; the MoE block consumes the gathered rows and its
         (already complete) output is sliced back to this rank's tokens."""
-        hidden, residual = sp.block(self.input_layernorm, hidden, residual,
-                                    lambda full: self.self_attn(full, reduce=False))
+        if self.head_to_sequence:
+            hidden, residual = sp.block(self.input_layernorm, hidden, residual,
+                                        lambda full: self.self_attn(full, stream=sp))
+        else:
+            hidden, residual = sp.block(self.input_layernorm, hidden, residual,
+                                        lambda full: self.self_attn(full, reduce=False))
         if not self.is_moe:
             return sp.block(self.post_attention_layernorm, hidden, residual,
                             lambda full: self.mlp(full, reduce=False))
@@ -139,6 +194,9 @@ class Qwen3MoeForCausalLM(nn.Module):
             m = _EXPERT_RE.match(name)
             if m is None:
                 rest.append((name, tensor))
+                if name.endswith(".self_attn.o_proj.weight") and \
+                        name.replace(".o_proj.", ".o_proj_full.") in params:
+                    rest.append((name.replace(".o_proj.", ".o_proj_full."), tensor))
                 continue
             prefix, eid, proj, kind = m.group(1), int(m.group(2)), m.group(3), m.group(4)
             moe: FusedMoE = self.get_submodule(prefix + ".mlp")

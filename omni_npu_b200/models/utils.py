@@ -87,16 +87,21 @@ def iter_safetensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
 
 
 @torch.no_grad()
-def random_init_(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
+def random_init_(model: nn.Module, seed: int = 0, std: float = 0.02, by_name: Optional[bool] = None) -> None:
     """Deterministic random initialisation (normal, std 0.02; norm weights 1).
-    Each parameter's stream is seeded from ``seed`` and the parameter's NAME, so a
-    pipeline stage that holds a subset of the layers gets the same values for them
-    as a process that holds the whole model.  Tensor-parallel shards are drawn
-    per shard (a shard is not a slice of the unsharded draw)."""
+    Each parameter has its own stream, seeded from ``seed`` and the parameter's
+    index in name order, or (``by_name``; default: ``OMNI_B200_INIT_BY_NAME=1``;
+    always used for pipeline stages) from a checksum of its NAME, so that a stage
+    holding a subset of the layers draws the same values for them as a process
+    holding the whole model.  Tensor-parallel shards are drawn per shard (a shard
+    is not a slice of the unsharded draw)."""
     import zlib
+    if by_name is None:
+        by_name = os.environ.get("OMNI_B200_INIT_BY_NAME", "0") == "1"
     g = torch.Generator(device="cpu")
-    for name, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
-        i = zlib.crc32(name.encode()) % 1000003
+    for i, (name, p) in enumerate(sorted(model.named_parameters(), key=lambda kv: kv[0])):
+        if by_name:
+            i = zlib.crc32(name.encode()) % 1000003
         g.manual_seed(seed * 1000003 + i)
         if "norm" in name and p.dim() == 1 and "bias" not in name:
             p.data.fill_(1.0)

@@ -94,7 +94,7 @@ class ModelRunner:
             loaded = self.model.load_weights(iter_safetensors(cfg.model_path))
             logger.info("loaded %d tensors from %s", len(loaded), cfg.model_path)
         else:
-            random_init_(self.model, seed=cfg.seed)
+            random_init_(self.model, seed=cfg.seed, by_name=True if self.pp_group is not None else None)
         for m in self.model.modules():
             hook = getattr(m, "process_weights_after_loading", None)
             if callable(hook):

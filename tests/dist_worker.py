@@ -81,6 +81,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         kw["dtype"] = "float32"
     if os.path.exists(os.path.join(workdir, "sequence_parallel")):
         kw["sequence_parallel_residual"] = True
+    if os.path.exists(os.path.join(workdir, "additional_config.json")):
+        kw["additional_config"] = json.load(open(os.path.join(workdir, "additional_config.json")))
     if os.path.exists(os.path.join(workdir, "pipeline_parallel")):
         pp = int(open(os.path.join(workdir, "pipeline_parallel")).read())
         kw.update(pipeline_parallel_size=pp, tensor_parallel_size=world // pp)
@@ -90,7 +92,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         LlamaModel.auto_sequence_parallel = True
     llm = LLM(model=model_dir, **kw)
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
-    json.dump({"tokens": [o.output_token_ids for o in outs]},
+    kinds = sorted({type(m).__name__ for m in llm.engine.worker.get_model().modules() if "Attention" in type(m).__name__})
+    json.dump({"tokens": [o.output_token_ids for o in outs], "attention_modules": kinds},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":
         state.finish_process(llm.engine)

@@ -123,6 +123,7 @@ def test_pipeline_parallel_deepseek_matches_single_process(sparse, monkeypatch):
     g = torch.Generator().manual_seed(13)
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 34, 5)]
     monkeypatch.delenv("OMNI_B200_PP_LAYER_PARTITION", raising=False)
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")     # the one-process oracle draws by name like the stages
     with tempfile.TemporaryDirectory() as d:
         json.dump({"model": model, "engine": engine, "prompts": prompts, "max_tokens": 6},
                   open(os.path.join(d, "spec.json"), "w"))
