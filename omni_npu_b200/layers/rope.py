@@ -4,7 +4,8 @@ Every variant only differs in the inverse frequencies / magnitude scale it
 bakes into a ``[max_pos, rot_dim]`` fp32 table (cos | sin); applying the
 rotation is one kernel shared by all of them.  ``get_rope`` is the factory
 keyed on the HF ``rope_scaling`` dictionary, covering default, linear,
-dynamic NTK, llama3, YaRN, DeepSeek-YaRN, longrope and (interleaved) M-RoPE
+dynamic NTK (by factor or fixed alpha), llama3, mllama4, YaRN, DeepSeek-YaRN, longrope,
+xdrope (text positions) and (interleaved) M-RoPE
 (reference: omni_npu/v1/layers/rotary_embedding/__init__.py:26-292 and
 omni_npu/layers/rotary_embedding/*.py).
 """
@@ -121,12 +122,19 @@ def get_rope(head_dim: int, rot_dim: int, max_position: int, base: float, is_neo
     kind = rs.get("rope_type", rs.get("type", "default"))
     mrope = rs.get("mrope_section")
     inv, mscale, max_pos = None, 1.0, max_position
-    if kind in ("default", "mrope") or kind is None:
+    if kind in ("default", "mrope", "mllama4") or kind is None:
+        # mllama4 rotates interleaved pairs with the plain frequencies: the caller passes is_neox=False
         pass
     elif kind == "linear":
         inv = _linear_inv_freq(rot_dim, base, rs["factor"])
         max_pos = int(max_position * rs["factor"])
+    elif kind in ("dynamic", "xdrope") and "alpha" in rs:
+        # fixed-alpha NTK: base * alpha^(d / (d - 2)); xdrope adds per-axis sections, which coincide
+        # for text-only positions (all axes carry the same index), so one table serves it
+        inv = _base_inv_freq(rot_dim, base * float(rs["alpha"]) ** (rot_dim / (rot_dim - 2)))
     elif kind in ("dynamic", "ntk"):
+        if "factor" not in rs:
+            raise ValueError("dynamic rope scaling needs either 'alpha' or 'factor'")
         orig = rs.get("original_max_position_embeddings", max_position)
         max_pos = int(orig * rs["factor"]) if kind == "dynamic" else max_position
         inv = _ntk_inv_freq(rot_dim, base, rs["factor"], max_pos, orig)
@@ -140,7 +148,7 @@ def get_rope(head_dim: int, rot_dim: int, max_position: int, base: float, is_neo
                              rs.get("beta_slow", 1))
         mscale = yarn_get_mscale(rs["factor"]) * rs.get("attn_factor", 1.0)
         max_pos = int(orig * rs["factor"])
-    elif kind == "deepseek_yarn":
+    elif kind in ("deepseek_yarn", "deepseek_llama_scaling"):
         orig = rs.get("original_max_position_embeddings", max_position)
         inv = _yarn_inv_freq(rot_dim, base, rs["factor"], orig, rs.get("beta_fast", 32),
                              rs.get("beta_slow", 1))

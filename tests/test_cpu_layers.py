@@ -126,3 +126,23 @@ def test_norm_and_activation_layers_match_formulas():
     assert torch.allclose(ln(x), torch.nn.functional.layer_norm(x, (32,), ln.weight, ln.bias, 1e-6), atol=1e-5)
     g = torch.randn(3, 16)
     assert torch.allclose(SiluAndMul()(g), torch.nn.functional.silu(g[:, :8]) * g[:, 8:], atol=1e-6)
+
+
+def test_rope_factory_alpha_ntk_xdrope_and_aliases():
+    import math
+    from omni_npu_b200.layers.rope import get_rope
+    d, base, alpha = 64, 10000.0, 8.0
+    want = 1.0 / ((base * alpha ** (d / (d - 2))) ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    for kind, extra in (("dynamic", {}), ("xdrope", {"xdrope_section": [16, 16, 16, 16]})):
+        rope = get_rope(d, d, 256, base, True, {"rope_type": kind, "alpha": alpha, **extra})
+        cos, sin = rope.get_cos_sin(torch.tensor([7]))
+        assert torch.allclose(cos[0], torch.cos(7 * want), atol=1e-5)
+        assert torch.allclose(sin[0], torch.sin(7 * want), atol=1e-5)
+    plain = get_rope(d, d, 256, base, False, {"rope_type": "mllama4"})
+    assert torch.equal(plain.cos_sin_cache, get_rope(d, d, 256, base, False, None).cos_sin_cache)
+    ds = {"factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0, "mscale_all_dim": 1.0}
+    a = get_rope(d, d, 256, base, False, {"rope_type": "deepseek_yarn", **ds})
+    b = get_rope(d, d, 256, base, False, {"rope_type": "deepseek_llama_scaling", **ds})
+    assert torch.equal(a.cos_sin_cache, b.cos_sin_cache)
+    with pytest.raises(ValueError):
+        get_rope(d, d, 256, base, True, {"rope_type": "dynamic"})
