@@ -54,6 +54,11 @@ class LLMEngine:
         self.async_scheduling = bool(config.additional_config.get(
             "async_scheduling", _os.environ.get("OMNI_B200_ASYNC_SCHED", "1") != "0"))
         self._inflight = None
+        # data-parallel replicas (attention DP + experts sharded over DP x TP) step in lock-step
+        from ..parallel import state as pstate
+        dp = pstate.get_dp_group()
+        self.dp_group = dp if dp.world_size > 1 else None
+        self.dp_all_idle = False
 
     @property
     def device(self) -> torch.device:
@@ -80,7 +85,7 @@ class LLMEngine:
         host needs the token values between steps: no draft proposer, no KV connector, no draft head."""
         return (self.async_scheduling and self.proposer is None and self.scheduler.kv_connector is None
                 and self.worker.model_runner.mtp is None and getattr(self.worker, "ha_agent", None) is None
-                and self.worker.model_runner.pp_group is None)
+                and self.worker.model_runner.pp_group is None and self.dp_group is None)
 
     def _settle(self) -> List[RequestOutput]:
         """Read back the step in flight and fill its tokens in."""
@@ -116,7 +121,39 @@ class LLMEngine:
         done = self._settle()
         return done + self._run_scheduled(out)
 
+    def _step_data_parallel(self) -> List[RequestOutput]:
+        """One global step of a data-parallel deployment.  Every replica schedules its own
+        requests, but the expert-parallel exchanges inside the MoE layers span all replicas, so
+        each replica must run exactly one forward pass per global step: replicas agree (one
+        small host-side all-reduce) on whether anyone has work; a replica without work runs a
+        one-token dummy batch.  ``dp_all_idle`` tells the caller's loop when every replica is
+        done.  (reference: dummy batches on idle data-parallel ranks,
+        omni_npu/worker/npu_worker.py:213-214, and one engine process per DP rank in
+        examples/serve-pd-disaggregate.sh:195-238)"""
+        import torch.distributed as dist
+        busy = self.scheduler.has_unfinished()
+        flag = torch.tensor([int(busy)], dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.dp_group.cpu_group)
+        self.dp_all_idle = int(flag.item()) == 0
+        if self.dp_all_idle:
+            return []
+        out = self.scheduler.schedule() if busy else None
+        if out is None or out.kind == "idle":
+            if out is not None:
+                self.worker.model_runner.execute_model(out)      # retire rows, start KV loads
+            self.worker.execute_dummy_batch()
+            st = self.stats
+            st["steps"] += 1
+            st["dummy_steps"] = st.get("dummy_steps", 0) + 1
+            interval = self.config.parallel.eplb_step_interval
+            if interval > 0 and st["steps"] % interval == 0:
+                self.rebalance_experts()
+            return []
+        return self._run_scheduled(out)
+
     def step(self) -> List[RequestOutput]:
+        if self.dp_group is not None:
+            return self._step_data_parallel()
         if self._async_ok():
             return self._step_async()
         if self._inflight is not None:                  # the switch was turned off mid-flight
@@ -243,6 +280,13 @@ class LLM:
         for i, (p, sp) in enumerate(zip(prompts, sps)):
             order[self.engine.add_request(p, sp, arrival_time=now)] = i
         results: List[Optional[RequestOutput]] = [None] * len(prompts)
+        if self.engine.dp_group is not None:
+            # replicas finish at different times; keep stepping (dummy batches) until all are done
+            while True:
+                for o in self.engine.step():
+                    results[order[o.request_id]] = o
+                if self.engine.dp_all_idle:
+                    break
         while self.engine.has_unfinished_requests():
             for o in self.engine.step():
                 results[order[o.request_id]] = o

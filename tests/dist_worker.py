@@ -119,6 +119,25 @@ def task_pp_deepseek(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_dp_engine(rank, world, port, workdir, device_kind):
+    """One engine per data-parallel rank (experts sharded over all ranks); every rank serves its
+    own list of prompts, lists of different lengths."""
+    dev, state = setup(rank, world, port, device_kind)
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.engine.llm import LLM
+    prompts = json.load(open(os.path.join(workdir, "prompts.json")))[rank]
+    llm = LLM(model=os.path.join(workdir, "model"), device=device_kind, dtype="float32",
+              data_parallel_size=world, enable_expert_parallel=True, max_num_seqs=4,
+              max_num_batched_tokens=64, max_model_len=256, block_size=16, num_gpu_blocks=64)
+    moe = [m for m in llm.engine.worker.get_model().modules() if hasattr(m, "local_experts")]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    json.dump({"tokens": [o.output_token_ids for o in outs], "local_experts": moe[0].local_experts,
+               "dummy_steps": llm.engine.stats.get("dummy_steps", 0), "steps": llm.engine.stats["steps"]},
+              open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.get_world_group().barrier()
+    state.destroy_distributed()
+
+
 def task_symm(rank, world, port, workdir, device_kind):
     """Peer-memory collectives against NCCL results."""
     dev, state = setup(rank, world, port, "cuda")
@@ -488,7 +507,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

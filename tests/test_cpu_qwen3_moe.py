@@ -69,3 +69,24 @@ def test_token_sharded_stream_and_head_to_sequence_exchange_match_one_process():
     for kind, res in results.items():
         assert res[0]["tokens"] == want, kind
         assert res[1]["tokens"] == want, kind
+
+
+def test_data_parallel_replicas_with_shared_experts_step_in_lock_step():
+    """Two data-parallel replicas, experts sharded over both: the replica with less work keeps
+    the expert exchanges alive with dummy batches and every request decodes as in one process."""
+    g = torch.Generator().manual_seed(3)
+    per_rank = [[torch.randint(0, 256, (n,), generator=g).tolist() for n in (20, 70, 9)],
+                [torch.randint(0, 256, (5,), generator=g).tolist()]]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _checkpoint(os.path.join(d, "model"), seed=4)
+        json.dump(per_rank, open(os.path.join(d, "prompts.json"), "w"))
+        llm = LLM(model=os.path.join(d, "model"), device="cpu", dtype="float32", max_num_seqs=4,
+                  max_num_batched_tokens=64, max_model_len=256, block_size=16, num_gpu_blocks=64)
+        sp = SamplingParams(max_tokens=10, ignore_eos=True)
+        want = [[o.output_token_ids for o in llm.generate(p, sp)] for p in per_rank]
+        res = run_ranks("dp_engine", 2, d)
+    assert res[0]["tokens"] == want[0] and res[1]["tokens"] == want[1]
+    assert res[0]["local_experts"] == HF["num_experts"] // 2
+    assert res[0]["dummy_steps"] == 0 and res[1]["dummy_steps"] > 0
+    assert res[0]["steps"] == res[1]["steps"]
