@@ -25,7 +25,7 @@ from ..layers.moe import FusedMoE
 from ..layers.norm import RMSNorm, reduce_add_rms_norm
 from ..parallel import state as pstate
 from .llama import LlamaAttention
-from .utils import load_stacked_weights
+from .utils import IntermediateTensors, PPMissingLayer, build_pipeline_layers, load_stacked_weights
 
 _EXPERT_RE = re.compile(r"(.*)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$")
 
@@ -142,12 +142,48 @@ class Qwen3MoeModel(nn.Module):
         super().__init__()
         cfg = engine.model
         self.sequence_parallel = bool(engine.parallel.sequence_parallel_residual)
-        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device)
-        self.layers = nn.ModuleList([Qwen3MoeDecoderLayer(cfg, i, device, f"model.layers.{i}", engine)
-                                     for i in range(cfg.num_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
+        pp = pstate.get_pp_group()
+        self.pp_group = pp if pp.world_size > 1 else None
+        first = self.pp_group is None or pp.is_first_rank
+        last = self.pp_group is None or pp.is_last_rank
+        self.hidden_size = cfg.hidden_size
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device) \
+            if first else PPMissingLayer()
+        self.layers, self.start_layer, self.end_layer = build_pipeline_layers(
+            cfg.num_layers, lambda i: Qwen3MoeDecoderLayer(cfg, i, device, f"model.layers.{i}", engine),
+            self.pp_group)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device) if last else PPMissingLayer()
 
-    def forward(self, input_ids, positions, inputs_embeds=None) -> torch.Tensor:
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device) -> IntermediateTensors:
+        return IntermediateTensors({k: torch.empty(num_tokens, self.hidden_size, dtype=dtype, device=device)
+                                    for k in ("hidden_states", "residual")})
+
+    def _forward_stage(self, input_ids, inputs_embeds, intermediate_tensors):
+        """This rank's pipeline stage on the replicated stream; a reduction still pending at the
+        boundary is done before the hand-over."""
+        pp = self.pp_group
+        residual, pending = None, False
+        if pp.is_first_rank:
+            hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        else:
+            hidden, residual = intermediate_tensors["hidden_states"], intermediate_tensors["residual"]
+        for layer in self.layers[self.start_layer:self.end_layer]:
+            hidden, residual, pending = layer(hidden, residual, pending)
+        if not pp.is_last_rank:
+            if pending:
+                hidden = pstate.get_tp_group().all_reduce(hidden)
+            if residual is None:
+                residual = torch.zeros_like(hidden)
+            return IntermediateTensors({"hidden_states": hidden, "residual": residual})
+        if pending:
+            hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, pstate.get_tp_group())
+        else:
+            hidden, _ = self.norm(hidden, residual)
+        return hidden
+
+    def forward(self, input_ids, positions, inputs_embeds=None, intermediate_tensors=None):
+        if self.pp_group is not None:
+            return self._forward_stage(input_ids, inputs_embeds, intermediate_tensors)
         hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
         tp = pstate.get_tp_group()
         if self.sequence_parallel and tp.world_size > 1:
@@ -178,10 +214,16 @@ class Qwen3MoeForCausalLM(nn.Module):
         super().__init__()
         self.config = engine_config.model
         self.model = Qwen3MoeModel(engine_config, device)
-        self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device)
+        pp = self.model.pp_group
+        self.lm_head = ParallelLMHead(self.config.vocab_size, self.config.hidden_size, self.config.dtype, device) \
+            if pp is None or pp.is_last_rank else PPMissingLayer()
+        self.num_kv_layers = self.model.end_layer - self.model.start_layer
 
-    def forward(self, input_ids, positions, inputs_embeds=None):
-        return self.model(input_ids, positions, inputs_embeds)
+    def forward(self, input_ids, positions, inputs_embeds=None, intermediate_tensors=None):
+        return self.model(input_ids, positions, inputs_embeds, intermediate_tensors)
+
+    def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device):
+        return self.model.make_empty_intermediate_tensors(num_tokens, dtype, device)
 
     def compute_logits(self, hidden):
         return self.lm_head.compute_logits(hidden)
@@ -199,7 +241,10 @@ class Qwen3MoeForCausalLM(nn.Module):
                     rest.append((name.replace(".o_proj.", ".o_proj_full."), tensor))
                 continue
             prefix, eid, proj, kind = m.group(1), int(m.group(2)), m.group(3), m.group(4)
-            moe: FusedMoE = self.get_submodule(prefix + ".mlp")
+            try:
+                moe: FusedMoE = self.get_submodule(prefix + ".mlp")
+            except AttributeError:        # a layer of another pipeline stage
+                continue
             pname = {"gate_proj": "w13", "up_proj": "w13", "down_proj": "w2"}[proj]
             if kind != "weight":
                 pname += "_scale"

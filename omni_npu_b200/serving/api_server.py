@@ -61,11 +61,17 @@ class EngineLoop:
             self.waiters.pop(rid, None)
 
     def _run(self) -> None:
+        # data-parallel replicas step together even when this one is idle (its dummy batches keep
+        # the expert-parallel exchanges of the busy replicas going)
+        lock_step = getattr(self.engine, "dp_group", None) is not None
         while self.running:
-            if not self.engine.has_unfinished_requests():
+            if not lock_step and not self.engine.has_unfinished_requests():
                 self.wake.wait(0.05)
                 self.wake.clear()
                 continue
+            if lock_step and getattr(self.engine, "dp_all_idle", False):
+                self.wake.wait(0.002)
+                self.wake.clear()
             with self.lock:
                 outs = self.engine.step()
                 self.counters["steps"] += 1
@@ -244,6 +250,7 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--host", default="0.0.0.0")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--pipeline-parallel-size", type=int, default=1)
     ap.add_argument("--data-parallel-size", type=int, default=1)
     ap.add_argument("--enable-expert-parallel", action="store_true")
     ap.add_argument("--max-num-seqs", type=int, default=128)
@@ -275,6 +282,7 @@ def main(argv=None) -> None:
     from .parsers import get_reasoning_parser, get_tool_parser
     args = make_parser().parse_args(argv)
     kw = dict(tensor_parallel_size=args.tensor_parallel_size, data_parallel_size=args.data_parallel_size,
+              pipeline_parallel_size=args.pipeline_parallel_size,
               enable_expert_parallel=args.enable_expert_parallel, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
               block_size=args.block_size, gpu_memory_utilization=args.gpu_memory_utilization,

@@ -1,6 +1,6 @@
 """Qwen3-MoE from an HF-style checkpoint on CPU: one process, tensor parallel with the
-token-sharded residual stream, and the same with the head <-> sequence all-to-all after
-attention must all generate the same tokens."""
+token-sharded residual stream, the same with the head <-> sequence all-to-all after
+attention, and two pipeline stages must all generate the same tokens."""
 import json
 import os
 import tempfile
@@ -64,8 +64,13 @@ def test_token_sharded_stream_and_head_to_sequence_exchange_match_one_process():
         results["sp"] = run_ranks("tp_engine", 2, d)
         json.dump({"attn_output_all_to_all": True}, open(os.path.join(d, "additional_config.json"), "w"))
         results["a2a"] = run_ranks("tp_engine", 2, d)
+        os.remove(os.path.join(d, "additional_config.json"))
+        os.remove(os.path.join(d, "sequence_parallel"))
+        open(os.path.join(d, "pipeline_parallel"), "w").write("2")
+        results["pp"] = run_ranks("tp_engine", 2, d)
     assert "HeadToSequenceAttention" in results["a2a"][0]["attention_modules"]
     assert "HeadToSequenceAttention" not in results["sp"][0]["attention_modules"]
+    assert "HeadToSequenceAttention" not in results["pp"][0]["attention_modules"]
     for kind, res in results.items():
         assert res[0]["tokens"] == want, kind
         assert res[1]["tokens"] == want, kind
