@@ -498,9 +498,6 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                         scale, _pack_window(window, sink), splits, scratch, st.status)
 
 
-merge_attn_states = ref.merge_attn_states
-
-
 # -------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     if not logits.is_cuda:

@@ -221,17 +221,6 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return (out, lse) if return_lse else out
 
 
-def merge_attn_states(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor,
-                      lse2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """LSE-weighted merge of two partial attention results.  o [T,H,D], lse [T,H]."""
-    m = torch.maximum(lse1, lse2)
-    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
-    w1, w2 = torch.exp(lse1 - m), torch.exp(lse2 - m)
-    den = (w1 + w2).clamp_min(1e-30)
-    o = (o1.float() * (w1 / den).unsqueeze(-1) + o2.float() * (w2 / den).unsqueeze(-1)).to(o1.dtype)
-    return o, m + torch.log(den)
-
-
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     return logits.float().argmax(dim=-1).to(torch.int32)
 

@@ -178,3 +178,14 @@ def test_pp_layer_range_splits_evenly_and_honours_override(monkeypatch):
         pp_layer_range(8, 0, 2)
     x = torch.ones(2)
     assert PPMissingLayer()(x) is x and not list(PPMissingLayer().parameters())
+
+
+def test_public_ops_dispatch_through_the_ops_module_not_the_reference():
+    """Every op that has a CUDA kernel must be defined in ``ops`` itself (device dispatch), never
+    be a bare alias of its CPU reference: an alias would silently run tensor ops on the GPU."""
+    from omni_npu_b200 import ops
+    from omni_npu_b200.ops import ref
+    import types
+    aliased = [name for name in dir(ops)
+               if isinstance(getattr(ops, name), types.FunctionType) and getattr(ref, name, None) is getattr(ops, name)]
+    assert aliased == []
