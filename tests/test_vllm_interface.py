@@ -121,3 +121,19 @@ def test_thinking_budget_processor_follows_vllm_batch_updates():
     assert got[1].argmax() == 6 and torch.isfinite(got[0]).all()
     proc.update_state(BatchUpdate(batch_size=1, removed=[1], added=[], moved=[]))
     assert torch.isfinite(proc.apply(logits.clone())).all() and not proc.inner.state
+
+
+def test_padded_metadata_patch_applies_and_reverts():
+    """``unpadded`` keeps the padded metadata while the patch is applied and trims again after revert."""
+    pytest.importorskip("vllm")
+    from vllm.v1.attention.backends.utils import CommonAttentionMetadata
+    from omni_npu_b200.patches.common import backends_utils as bu
+    patch = bu.PaddedAttentionMetadataPatch
+    original = CommonAttentionMetadata.__dict__["unpadded"]
+    patch.apply()
+    try:
+        sentinel = object.__new__(CommonAttentionMetadata)
+        assert CommonAttentionMetadata.unpadded(sentinel, 3, 2) is sentinel
+    finally:
+        patch.revert()
+    assert CommonAttentionMetadata.__dict__["unpadded"] is original
