@@ -105,7 +105,7 @@ class LLMEngine:
         out = self.scheduler.schedule()
         if out.kind == "decode":
             runner = self.worker.model_runner
-            handle = runner.launch_decode(out, self._inflight[1] if self._inflight is not None else None)
+            handle = self.worker.launch_decode(out, self._inflight[1] if self._inflight is not None else None)
             self.scheduler.advance_pending(out)
             done = self._settle()                       # the previous step, while this one runs
             self._inflight = (out, handle)

@@ -115,18 +115,34 @@ class Worker:
             world.barrier()
 
     # ------------------------------------------------------------- running
-    @token_recover_wrapper
-    def execute_model(self, out: SchedulerOutput) -> List[int]:
+    def _profile_window_open(self, out: SchedulerOutput) -> None:
+        """Token-threshold profiling: a step that schedules exactly ``PROFILER_TOKEN_THRESHOLD``
+        tokens starts the profiler for ``PROFILER_STOP_STEP`` steps."""
         if self._profile_threshold and self.profiler is not None:
             if self._profile_steps_left == 0 and out.total_num_scheduled_tokens == self._profile_threshold:
                 self.profiler.start()
                 self._profile_steps_left = self._profile_stop_step
-        tokens = self.model_runner.execute_model(out)
+
+    def _profile_window_close(self) -> None:
         if self._profile_steps_left > 0:
             self._profile_steps_left -= 1
             if self._profile_steps_left == 0:
                 self.profiler.stop()
+
+    @token_recover_wrapper
+    def execute_model(self, out: SchedulerOutput) -> List[int]:
+        self._profile_window_open(out)
+        tokens = self.model_runner.execute_model(out)
+        self._profile_window_close()
         return tokens
+
+    def launch_decode(self, out: SchedulerOutput, prev: Optional[dict] = None) -> dict:
+        """Decode step launched ahead of its results (asynchronous scheduling): same profiling
+        window as ``execute_model``; the step counts when it is launched."""
+        self._profile_window_open(out)
+        handle = self.model_runner.launch_decode(out, prev)
+        self._profile_window_close()
+        return handle
 
     # ------------------------------------------------ token recovery hooks
     def enable_token_recovery(self, env=None) -> None:
