@@ -46,3 +46,82 @@ def support_graph_replay(cls=None, *, mode_attr: str = "cudagraph_mode"):
         return klass
 
     return wrap(cls) if cls is not None else wrap
+
+
+# ------------------------------------------------------------------ under vLLM
+def _vllm_step_has_prefill(ctx) -> bool:
+    """vLLM's forward context carries per-layer attention metadata (a dict) or a single object;
+    no metadata (profile run) counts as prefill."""
+    md = getattr(ctx, "attn_metadata", None)
+    if md is None:
+        return True
+    if isinstance(md, dict):
+        if not md:
+            return True
+        md = next(iter(md.values()))
+    return int(getattr(md, "num_prefills", 0) or 0) > 0
+
+
+def _wrap_compiled_call(original_call: Callable, get_ctx: Callable, full_mode) -> Callable:
+    @functools.wraps(original_call)
+    def call(self, *args, **kwargs):
+        ctx = get_ctx()
+        if _vllm_step_has_prefill(ctx) or getattr(ctx, "cudagraph_runtime_mode", None) != full_mode:
+            return self.forward(*args, **kwargs)                 # eager: never traced, never captured piecewise
+        out = original_call(self, *args, **kwargs)
+        # a compiled callable may hand back ([tensor],) instead of the tensor
+        if isinstance(out, (tuple, list)) and len(out) == 1:
+            inner = out[0]
+            if isinstance(inner, list) and len(inner) == 1 and hasattr(inner[0], "shape"):
+                inner = inner[0]
+            return inner
+        return out
+
+    call._omni_prefill_bypass = True
+    return call
+
+
+def patch_compile_decorators(dec_module=None, get_ctx: Optional[Callable] = None, full_mode=None) -> bool:
+    """Make every model class that vLLM prepares for compilation run its plain ``forward`` for
+    steps that contain prefill tokens or whose graph mode is not FULL: their MoE exchange and
+    variable shapes belong neither in a traced graph nor in a captured one, and on this platform
+    only whole decode steps are replayed.  Wraps ``vllm.compilation.decorators.
+    _support_torch_compile`` once (idempotent); returns whether a wrapper is installed.  The
+    arguments exist for tests.  (reference: omni_npu/compilation/decorators.py:49-101)"""
+    if dec_module is None:
+        try:
+            import vllm.compilation.decorators as dec_module
+            from vllm.config import CUDAGraphMode
+            from vllm.forward_context import get_forward_context as vllm_ctx
+        except Exception:
+            return False
+        get_ctx = get_ctx or vllm_ctx
+        full_mode = full_mode if full_mode is not None else CUDAGraphMode.FULL
+    original = getattr(dec_module, "_support_torch_compile", None)
+    if original is None:
+        return False
+    if getattr(original, "_omni_prefill_bypass", False):
+        return True
+
+    @functools.wraps(original)
+    def patched(cls, *args, **kwargs):
+        cls = original(cls, *args, **kwargs)
+        if not getattr(cls.__call__, "_omni_prefill_bypass", False):
+            cls.__call__ = _wrap_compiled_call(cls.__call__, get_ctx, full_mode)
+        return cls
+
+    patched._omni_prefill_bypass = True
+    patched._omni_original = original
+    dec_module._support_torch_compile = patched
+    return True
+
+
+def unpatch_compile_decorators(dec_module=None) -> None:
+    if dec_module is None:
+        try:
+            import vllm.compilation.decorators as dec_module
+        except Exception:
+            return
+    cur = getattr(dec_module, "_support_torch_compile", None)
+    if getattr(cur, "_omni_prefill_bypass", False):
+        dec_module._support_torch_compile = cur._omni_original

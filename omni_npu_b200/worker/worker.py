@@ -70,7 +70,14 @@ class Worker:
         self._init_profiler()
 
     def load_model(self) -> None:
-        self.model_runner.load_model()
+        if self.config.enable_sleep_mode and self.device.type == "cuda":
+            # weights live in the sleepable pool under their own tag: level-1 sleep copies them to
+            # pinned host memory and gives their device memory back, wake-up restores them in place
+            from .mem_pool import B200MemAllocator
+            with B200MemAllocator.get_instance().use_memory_pool(tag="weights"):
+                self.model_runner.load_model()
+        else:
+            self.model_runner.load_model()
 
     def get_model(self):
         return self.model_runner.get_model()
@@ -92,8 +99,8 @@ class Worker:
             self.model_runner.kv_connector = create_connector(self.config, role="worker",
                                                               device=self.device)
         if self.config.enable_sleep_mode and self.device.type == "cuda":
-            from .mem_pool import CudaMemAllocator
-            with CudaMemAllocator.get_instance().use_memory_pool(tag="kv_cache"):
+            from .mem_pool import B200MemAllocator
+            with B200MemAllocator.get_instance().use_memory_pool(tag="kv_cache"):
                 self.model_runner.initialize_kv_cache(num_blocks)
         else:
             self.model_runner.initialize_kv_cache(num_blocks)
@@ -195,13 +202,17 @@ class Worker:
             with_stack=bool(int(os.environ.get("VLLM_TORCH_PROFILER_WITH_STACK", "0"))),
             on_trace_ready=torch.profiler.tensorboard_trace_handler(trace_dir, use_gzip=True))
 
-    def sleep(self, level: int = 1) -> None:
-        from .mem_pool import CudaMemAllocator
-        CudaMemAllocator.get_instance().sleep(offload_tags=("weights",) if level == 1 else ())
+    def sleep(self, level: int = 1) -> int:
+        """Level 1: weights are kept in pinned host memory, the KV cache is discarded; level 2: both
+        are discarded.  Returns the device bytes released.
+        (reference: sleep-mode pool, omni_npu/worker/npu_mem_pool.py:109-284, wired in
+        omni_npu/worker/npu_worker.py:164-179)"""
+        from .mem_pool import B200MemAllocator
+        return B200MemAllocator.get_instance().sleep(offload_tags=("weights",) if level == 1 else ())
 
-    def wake_up(self, tags=None) -> None:
-        from .mem_pool import CudaMemAllocator
-        CudaMemAllocator.get_instance().wake_up(tags)
+    def wake_up(self, tags=None) -> int:
+        from .mem_pool import B200MemAllocator
+        return B200MemAllocator.get_instance().wake_up(tags)
 
     def shutdown(self) -> None:
         if self.model_runner is not None and self.model_runner.kv_connector is not None:

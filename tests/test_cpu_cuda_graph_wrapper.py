@@ -121,3 +121,57 @@ def test_outputs_are_held_weakly_and_attributes_pass_through(fake_cuda):
     del out
     gc.collect()
     assert w.entries[d].output_ref() is None
+
+
+def test_vllm_compile_decorator_patch_bypasses_prefill_and_non_full_modes():
+    import types
+
+    from omni_npu_b200.compilation import decorators as dec
+
+    log = []
+
+    def fake_support(cls):                 # stands in for vLLM's class preparation
+        def compiled_call(self, x):
+            log.append("compiled")
+            return ([x + 100],)
+        cls.__call__ = compiled_call
+        return cls
+
+    mod = types.SimpleNamespace(_support_torch_compile=fake_support)
+    ctx = types.SimpleNamespace(attn_metadata=None, cudagraph_runtime_mode="FULL")
+    assert dec.patch_compile_decorators(mod, lambda: ctx, "FULL")
+    assert dec.patch_compile_decorators(mod, lambda: ctx, "FULL")          # idempotent
+    assert mod._support_torch_compile._omni_original is fake_support
+
+    class Model:
+        def forward(self, x):
+            log.append("eager")
+            return x + 1
+
+    Model = mod._support_torch_compile(Model)
+    m = Model()
+    one = torch.tensor(1)
+    assert m(one) == 2 and log == ["eager"]                                # profile run: no metadata
+    ctx.attn_metadata = {"layer.0": types.SimpleNamespace(num_prefills=2)}
+    assert m(one) == 2 and log == ["eager", "eager"]                       # a prefill in the batch
+    ctx.attn_metadata = {"layer.0": types.SimpleNamespace(num_prefills=0)}
+    out = m(one)
+    assert torch.is_tensor(out) and out == 101 and log[-1] == "compiled"   # pure decode, FULL: graph path, unwrapped
+    ctx.cudagraph_runtime_mode = "PIECEWISE"
+    assert m(one) == 2 and log[-1] == "eager"
+    dec.unpatch_compile_decorators(mod)
+    assert mod._support_torch_compile is fake_support
+
+
+def test_vllm_compile_decorator_patch_installs_on_the_real_module():
+    pytest.importorskip("vllm")
+    import vllm.compilation.decorators as vdec
+
+    from omni_npu_b200.compilation import decorators as dec
+    before = vdec._support_torch_compile
+    try:
+        assert dec.patch_compile_decorators()
+        assert vdec._support_torch_compile._omni_original is before
+    finally:
+        dec.unpatch_compile_decorators()
+    assert vdec._support_torch_compile is before

@@ -119,3 +119,26 @@ def test_memory_budget_formula_with_a_faked_device(monkeypatch):
     monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (110 * spec.bytes_per_block, total))
     with pytest.raises(RuntimeError, match="not enough memory"):
         runner.determine_num_blocks()
+
+
+def test_sleep_and_wake_reach_the_pool_with_the_right_tags(monkeypatch):
+    from omni_npu_b200.worker import mem_pool
+
+    class _FakePool:
+        def __init__(self):
+            self.calls = []
+
+        def sleep(self, offload_tags=None):
+            self.calls.append(("sleep", tuple(offload_tags)))
+            return 123
+
+        def wake_up(self, tags=None):
+            self.calls.append(("wake", tags))
+            return 456
+
+    fake = _FakePool()
+    monkeypatch.setattr(mem_pool.B200MemAllocator, "get_instance", staticmethod(lambda: fake))
+    w = _llm().engine.worker
+    assert w.sleep(level=1) == 123 and w.sleep(level=2) == 123
+    assert w.wake_up(["weights"]) == 456 and w.wake_up() == 456
+    assert fake.calls == [("sleep", ("weights",)), ("sleep", ()), ("wake", ["weights"]), ("wake", None)]
