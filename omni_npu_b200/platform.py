@@ -113,23 +113,32 @@ class B200Platform(_Base):
         steps run eagerly, and register the KV connectors."""
         from . import ops
         ops.load_extension(required=True)
-        with contextlib.suppress(Exception):
+        # optional hooks: a failure is logged and does not keep the platform from loading
+        try:
             from .compilation.decorators import patch_compile_decorators
             patch_compile_decorators()
-        with contextlib.suppress(Exception):
+        except Exception as e:
+            logger.warning("compile-decorator patch not installed: %s", e)
+        try:
             from .kv_transfer.register import register_connectors
             register_connectors()
+        except Exception as e:
+            logger.warning("KV connectors not registered: %s", e)
 
     @classmethod
     def pre_register_and_update(cls, parser=None) -> None:
         """Runs before the engine config exists: registers the out-of-tree layer
         overrides and quantisation configs and extends the CLI."""
-        with contextlib.suppress(Exception):
+        try:
             from .layers import vllm_custom_ops  # noqa: F401  (@register_oot side effects)
+        except Exception as e:
+            logger.warning("out-of-tree custom ops not registered: %s", e)
         if parser is not None:
-            with contextlib.suppress(Exception):
+            try:
                 from .patches.common.engine_args import add_cli_args
                 add_cli_args(parser)
+            except Exception as e:
+                logger.warning("CLI arguments not added: %s", e)
 
     @classmethod
     def check_and_update_config(cls, vllm_config: Any) -> None:
