@@ -181,7 +181,7 @@ class LlamaModel(nn.Module):
             residual = None
         else:
             hidden, residual = intermediate_tensors["hidden_states"], intermediate_tensors["residual"]
-        for layer in self.layers[self.start_layer:self.end_layer]:
+        for layer in self._stage_layers():
             hidden, residual = layer(hidden, residual)
         if not pp.is_last_rank:
             if residual is None:        # a stage without layers passes the embeddings on
@@ -189,6 +189,15 @@ class LlamaModel(nn.Module):
             return IntermediateTensors({"hidden_states": hidden, "residual": residual})
         hidden, _ = reduce_add_rms_norm(self.norm, hidden, residual, tp)
         return hidden
+
+    def _stage_layers(self):
+        """This stage's decoder layers (all of them without pipeline parallelism), as a plain list
+        built once: slicing the ``ModuleList`` would construct a new module on every forward."""
+        cached = self.__dict__.get("_stage_layer_list")
+        if cached is None:
+            cached = list(self.layers)[self.start_layer:self.end_layer]
+            self.__dict__["_stage_layer_list"] = cached
+        return cached
 
     def make_empty_intermediate_tensors(self, num_tokens: int, dtype: torch.dtype, device) -> IntermediateTensors:
         h = self.hidden_size

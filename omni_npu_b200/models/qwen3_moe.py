@@ -154,6 +154,15 @@ class Qwen3MoeModel(nn.Module):
             self.pp_group)
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device) if last else PPMissingLayer()
 
+    def _stage_layers(self):
+        """This stage's decoder layers (all of them without pipeline parallelism), as a plain list
+        built once: slicing the ``ModuleList`` would construct a new module on every forward."""
+        cached = self.__dict__.get("_stage_layer_list")
+        if cached is None:
+            cached = list(self.layers)[self.start_layer:self.end_layer]
+            self.__dict__["_stage_layer_list"] = cached
+        return cached
+
     def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device) -> IntermediateTensors:
         return IntermediateTensors({k: torch.empty(num_tokens, self.hidden_size, dtype=dtype, device=device)
                                     for k in ("hidden_states", "residual")})
@@ -167,7 +176,7 @@ class Qwen3MoeModel(nn.Module):
             hidden = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
         else:
             hidden, residual = intermediate_tensors["hidden_states"], intermediate_tensors["residual"]
-        for layer in self.layers[self.start_layer:self.end_layer]:
+        for layer in self._stage_layers():
             hidden, residual, pending = layer(hidden, residual, pending)
         if not pp.is_last_rank:
             if pending:
