@@ -59,6 +59,12 @@ class B200AttentionMetadataBuilder(_Builder):
     # decode batches are replayed from CUDA graphs: lengths live in device tensors
     reorder_batch_threshold: ClassVar[int] = 1
 
+    def __init__(self, kv_cache_spec=None, layer_names=None, vllm_config=None, device=None) -> None:
+        # vLLM declares the base initialiser abstract: a builder that does not define its own
+        # cannot be instantiated
+        self.kv_cache_spec, self.layer_names = kv_cache_spec, layer_names
+        self.vllm_config, self.device = vllm_config, device
+
     def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False) -> B200AttentionMetadata:
         m = common_attn_metadata
         n_tok, n_req = int(m.num_actual_tokens), int(m.num_reqs)
