@@ -129,8 +129,9 @@ class P2PKVConnector:
 
     def request_finished(self, request, block_ids: List[int]) -> Tuple[Optional[float], Optional[Dict[str, Any]]]:
         """Returns (seconds to keep the blocks parked or None, kv_transfer_params or None)."""
-        from ..engine.request import RequestStatus
-        if not self.kt.is_producer or request.status != RequestStatus.FINISHED_LENGTH_CAPPED or not block_ids:
+        # compared by name: under vLLM the request carries vLLM's own status enum
+        status = getattr(request.status, "name", str(request.status))
+        if not self.kt.is_producer or status != "FINISHED_LENGTH_CAPPED" or not block_ids:
             return None, None
         with self._lock:
             self._finish_times[request.request_id] = time.monotonic()

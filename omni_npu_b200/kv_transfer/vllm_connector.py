@@ -25,6 +25,11 @@ else:
     class KVConnectorBase_V1:  # type: ignore[no-redef]
         def __init__(self, vllm_config=None, role=None, kv_cache_config=None) -> None:
             self._connector_metadata = None
+            self._role = role
+
+        @property
+        def role(self):
+            return self._role
 
     class KVConnectorMetadata:  # type: ignore[no-redef]
         pass
@@ -61,7 +66,8 @@ class B200KVConnector(KVConnectorBase_V1):
             super().__init__(vllm_config, role, kv_cache_config)
         except TypeError:                                 # older base: (vllm_config, role)
             super().__init__(vllm_config, role)
-        self.role = role
+        if not hasattr(self, "role"):                     # vLLM's base exposes ``role`` as a read-only property
+            self._role = role
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.impl = P2PKVConnector(engine_config_from_vllm(vllm_config),
                                    device if role == KVConnectorRole.WORKER else torch.device("cpu"))

@@ -213,3 +213,33 @@ def test_no_adapter_class_is_left_abstract():
         abstract += [f"{mn}.{n}: {sorted(c.__abstractmethods__)}" for n, c in vars(m).items()
                      if inspect.isclass(c) and c.__module__ == mn and inspect.isabstract(c)]
     assert abstract == []
+
+
+def test_vllm_connector_wrapper_with_vllm_request_status(monkeypatch):
+    """The wrapper builds from a vLLM-shaped config and hands out transfer parameters for a request
+    that carries vLLM's own ``RequestStatus`` enum (not this package's)."""
+    pytest.importorskip("vllm")
+    import types
+
+    from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorRole
+    from vllm.v1.request import RequestStatus as VllmStatus
+
+    from omni_npu_b200.kv_transfer.vllm_connector import B200ConnectorMetadata, B200KVConnector
+    kt = types.SimpleNamespace(kv_connector="P2PKVConnector", kv_role="kv_producer", kv_rank=0, kv_parallel_size=1,
+                               kv_ip="127.0.0.1", kv_port=25101, kv_connector_extra_config={"kv_port": 25101},
+                               is_kv_producer=True, is_kv_consumer=False, engine_id="e0")
+    vc = types.SimpleNamespace(kv_transfer_config=kt, cache_config=types.SimpleNamespace(block_size=16),
+                               parallel_config=types.SimpleNamespace(tensor_parallel_size=1), additional_config={})
+    c = B200KVConnector(vc, KVConnectorRole.SCHEDULER)
+    try:
+        assert c.role == KVConnectorRole.SCHEDULER
+        req = types.SimpleNamespace(request_id="r", status=VllmStatus.FINISHED_LENGTH_CAPPED, spec_token_ids=[],
+                                    num_prompt_tokens=20, kv_transfer_params=None)
+        keep, params = c.request_finished(req, [4, 5])
+        assert keep is True and params["remote_block_ids"] == [4, 5]
+        stopped = types.SimpleNamespace(request_id="s", status=VllmStatus.FINISHED_STOPPED, spec_token_ids=[])
+        assert c.request_finished(stopped, [6]) == (False, None)
+        assert isinstance(c.build_connector_meta(None), B200ConnectorMetadata)
+        assert c.get_num_new_matched_tokens(req, 0) == (0, False)
+    finally:
+        c.shutdown()
