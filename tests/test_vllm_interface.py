@@ -243,3 +243,58 @@ def test_vllm_connector_wrapper_with_vllm_request_status(monkeypatch):
         assert c.get_num_new_matched_tokens(req, 0) == (0, False)
     finally:
         c.shutdown()
+
+
+def test_model_adapter_translates_vllm_metadata_and_matches_the_inner_model(monkeypatch):
+    """A standalone model behind the vLLM-facing adapter: config taken from a vLLM-shaped object,
+    a profiling call without metadata, then a prefill whose metadata arrives through vLLM's forward
+    context; hidden states must equal the inner model run under this package's own context."""
+    pytest.importorskip("vllm")
+    import types
+
+    import vllm.forward_context as vfc
+
+    from omni_npu_b200.attention.gqa import GQABackend
+    from omni_npu_b200.attention.metadata import set_forward_context
+    from omni_npu_b200.attention.vllm_backends import B200AttentionMetadata
+    from omni_npu_b200.models.utils import random_init_
+    from omni_npu_b200.models.vllm_adapters import StandaloneModelAdapter, metadata_from_vllm
+    hf = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 64, "num_hidden_layers": 2,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128,
+          "vocab_size": 97, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 256,
+          "torch_dtype": "float32"}
+    vc = types.SimpleNamespace(
+        model_config=types.SimpleNamespace(hf_config=types.SimpleNamespace(**hf), dtype="float32", max_model_len=128),
+        cache_config=types.SimpleNamespace(block_size=16), parallel_config=types.SimpleNamespace(tensor_parallel_size=1),
+        scheduler_config=types.SimpleNamespace(max_num_seqs=4, max_num_batched_tokens=64), additional_config={})
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.float32)
+    try:
+        model = StandaloneModelAdapter(vllm_config=vc)
+    finally:
+        torch.set_default_dtype(prev)
+    assert model.engine_config.model.num_layers == 2 and model.engine_config.scheduler.max_model_len == 128
+    random_init_(model.inner, seed=2, std=0.1)
+    caches = [GQABackend.allocate_kv_cache(8, 16, 2, 16, torch.float32, torch.device("cpu")) for _ in range(2)]
+    model.bind_kv_caches(caches)
+    lens = [9, 5]
+    T = sum(lens)
+    ids = torch.randint(0, 97, (T,))
+    pos = torch.cat([torch.arange(n) for n in lens])
+    bt = torch.tensor([[1, 0], [2, 0]], dtype=torch.int32)
+    slots = torch.cat([bt[b, 0] * 16 + torch.arange(n) for b, n in enumerate(lens)]).to(torch.int32)
+    md = B200AttentionMetadata(num_actual_tokens=T, num_reqs=2, max_query_len=9, max_seq_len=9,
+                               query_start_loc=torch.tensor([0, 9, 14], dtype=torch.int32),
+                               seq_lens=torch.tensor(lens, dtype=torch.int32), block_table=bt, slot_mapping=slots,
+                               is_decode=False)
+    ctx = types.SimpleNamespace(attn_metadata=None)
+    monkeypatch.setattr(vfc, "get_forward_context", lambda: ctx)
+    assert float(model(ids, pos).abs().sum()) == 0            # profiling run: zeros of the hidden size
+    ctx.attn_metadata = {"model.layers.0.self_attn.attn": md}
+    got = model(ids, pos)
+    for k, v in caches:
+        k.zero_(), v.zero_()
+    with set_forward_context(metadata_from_vllm(md, pos), caches, model.engine_config):
+        want = model.inner(ids, pos.to(torch.int32))
+    torch.testing.assert_close(got, want)
+    assert model.compute_logits(got).shape == (T, 97)
