@@ -33,15 +33,30 @@ from ..logger import logger
 class EngineLoop:
     """Owns the engine; a background thread steps it while there is work."""
 
-    def __init__(self, llm) -> None:
+    def __init__(self, llm, follower: bool = False) -> None:
         self.llm = llm
         self.engine = llm.engine
+        # Ranks of one replica (tensor x pipeline parallel) run the same deterministic scheduler, so they
+        # must see the same requests in the same order between the same steps.  HTTP arrives at rank 0
+        # only: before every step it broadcasts what arrived since the last one (``_run_leader``), the
+        # other ranks apply it and step when told (``run_follower``).
+        from ..parallel import state as pstate
+        world = pstate.get_world_group()
+        self.group = world if world.world_size > 1 else None
+        if self.group is not None and getattr(self.engine, "dp_group", None) is not None:
+            raise NotImplementedError("the API server replicates requests inside ONE replica: start one server "
+                                      "per data-parallel rank with tensor_parallel_size * pipeline_parallel_size == 1, "
+                                      "or use data_parallel_size == 1")
+        self._new: List[tuple] = []
+        self._aborts: List[str] = []
         self.lock = threading.Lock()
         self.wake = threading.Event()
         self.waiters: Dict[str, Dict[str, Any]] = {}
         self.running = True
-        self.thread = threading.Thread(target=self._run, daemon=True)
-        self.thread.start()
+        self.thread = None
+        if not follower:
+            self.thread = threading.Thread(target=self._run if self.group is None else self._run_leader, daemon=True)
+            self.thread.start()
         self.counters = {"requests": 0, "finished": 0, "output_tokens": 0, "steps": 0}
 
     def submit(self, prompt_ids: List[int], sp: SamplingParams, kv_transfer_params=None) -> str:
@@ -49,15 +64,21 @@ class EngineLoop:
         slot = {"event": threading.Event(), "output": None, "seen": 0, "queue": [], "request": None}
         with self.lock:
             self.waiters[rid] = slot
-            self.engine.add_request(prompt_ids, sp, request_id=rid, kv_transfer_params=kv_transfer_params)
-            slot["request"] = self.engine.scheduler.requests[rid]
+            if self.group is None:
+                self.engine.add_request(prompt_ids, sp, request_id=rid, kv_transfer_params=kv_transfer_params)
+                slot["request"] = self.engine.scheduler.requests[rid]
+            else:                                   # added on every rank by the next broadcast
+                self._new.append((rid, list(prompt_ids), sp, kv_transfer_params))
             self.counters["requests"] += 1
         self.wake.set()
         return rid
 
     def abort(self, rid: str) -> None:
         with self.lock:
-            self.engine.abort_request(rid)
+            if self.group is None:
+                self.engine.abort_request(rid)
+            else:
+                self._aborts.append(rid)
             self.waiters.pop(rid, None)
 
     def _run(self) -> None:
@@ -73,27 +94,69 @@ class EngineLoop:
                 self.wake.wait(0.002)
                 self.wake.clear()
             with self.lock:
-                outs = self.engine.step()
-                self.counters["steps"] += 1
-                # streaming: hand over tokens produced since the last look
-                for rid, slot in self.waiters.items():
-                    req = slot["request"]
-                    if req is None:
-                        continue
-                    ids = req.output_token_ids
-                    ready = len(ids)
-                    while ready > 0 and ids[ready - 1] < 0:     # tokens of a step still in flight
-                        ready -= 1
-                    if ready > slot["seen"]:
-                        slot["queue"].extend(ids[slot["seen"]:ready])
-                        slot["seen"] = ready
-                for o in outs:
-                    slot = self.waiters.get(o.request_id)
-                    if slot is not None:
-                        slot["output"] = o
-                        slot["event"].set()
-                    self.counters["finished"] += 1
-                    self.counters["output_tokens"] += len(o.output_token_ids)
+                self._publish(self.engine.step())
+
+    def _publish(self, outs) -> None:
+        """After a step (lock held): hand new tokens to streaming waiters, finished outputs to all."""
+        self.counters["steps"] += 1
+        for rid, slot in self.waiters.items():
+            req = slot["request"]
+            if req is None:
+                continue
+            ids = req.output_token_ids
+            ready = len(ids)
+            while ready > 0 and ids[ready - 1] < 0:     # tokens of a step still in flight
+                ready -= 1
+            if ready > slot["seen"]:
+                slot["queue"].extend(ids[slot["seen"]:ready])
+                slot["seen"] = ready
+        for o in outs:
+            slot = self.waiters.get(o.request_id)
+            if slot is not None:
+                slot["output"] = o
+                slot["event"].set()
+            self.counters["finished"] += 1
+            self.counters["output_tokens"] += len(o.output_token_ids)
+
+    # ------------------------------------------------ more than one rank per replica
+    KEEPALIVE_S = 5.0        # idle leaders still broadcast, so followers never sit in a receive for long
+
+    def _apply(self, new, aborts) -> None:
+        for rid, prompt_ids, sp, kvp in new:
+            self.engine.add_request(prompt_ids, sp, request_id=rid, kv_transfer_params=kvp)
+            slot = self.waiters.get(rid)
+            if slot is not None:
+                slot["request"] = self.engine.scheduler.requests[rid]
+        for rid in aborts:
+            self.engine.abort_request(rid)
+
+    def _run_leader(self) -> None:
+        last = time.monotonic()
+        while self.running:
+            with self.lock:
+                new, aborts, self._new, self._aborts = self._new, self._aborts, [], []
+            busy = bool(new or aborts) or self.engine.has_unfinished_requests()
+            if not busy and time.monotonic() - last < self.KEEPALIVE_S:
+                self.wake.wait(0.05)
+                self.wake.clear()
+                continue
+            last = time.monotonic()
+            self.group.broadcast_object({"new": new, "aborts": aborts, "step": busy, "stop": False}, src=0)
+            with self.lock:
+                self._apply(new, aborts)
+                if busy:
+                    self._publish(self.engine.step())
+        self.group.broadcast_object({"new": [], "aborts": [], "step": False, "stop": True}, src=0)
+
+    def run_follower(self) -> None:
+        """Loop of every rank but the first: apply what rank 0 received, step when it steps."""
+        while True:
+            msg = self.group.broadcast_object(None, src=0)
+            if msg["stop"]:
+                return
+            self._apply(msg["new"], msg["aborts"])
+            if msg["step"]:
+                self.engine.step()
 
     def wait(self, rid: str, timeout: Optional[float] = None):
         slot = self.waiters[rid]
@@ -106,7 +169,8 @@ class EngineLoop:
     def shutdown(self) -> None:
         self.running = False
         self.wake.set()
-        self.thread.join(timeout=5)
+        if self.thread is not None:
+            self.thread.join(timeout=5)
 
 
 def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
@@ -291,6 +355,9 @@ def main(argv=None) -> None:
               speculative_config=args.speculative_config, additional_config=args.additional_config,
               load_format=args.load_format, seed=args.seed)
     llm = LLM(model=args.model, **kw)
+    if int(os.environ.get("RANK", "0")) != 0 and args.data_parallel_size == 1:
+        EngineLoop(llm, follower=True).run_follower()       # requests arrive through rank 0
+        return
     tokenizer = None
     tok_dir = args.tokenizer or (args.model if os.path.isdir(args.model) else None)
     if tok_dir:

@@ -138,6 +138,40 @@ def task_dp_engine(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_server_loop(rank, world, port, workdir, device_kind):
+    """The API server's engine loop under tensor parallelism: rank 0 receives the requests (as the
+    HTTP handlers would submit them, at different times) and replicates them; the other ranks follow."""
+    import time
+    dev, state = setup(rank, world, port, device_kind)
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.engine.llm import LLM
+    from omni_npu_b200.serving.api_server import EngineLoop
+    prompts = json.load(open(os.path.join(workdir, "prompts.json")))
+    llm = LLM(model=os.path.join(workdir, "model"), device=device_kind, dtype="float32", tensor_parallel_size=world,
+              max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, block_size=16, num_gpu_blocks=64)
+    result = {"tokens": None}
+    if rank == 0:
+        loop = EngineLoop(llm)
+        loop.KEEPALIVE_S = 0.2
+        sp = SamplingParams(max_tokens=12, ignore_eos=True)
+        rids = [loop.submit(prompts[0], sp)]
+        time.sleep(0.3)                                   # the second and third arrive while the first decodes
+        rids += [loop.submit(p, sp) for p in prompts[1:3]]
+        extra = loop.submit(prompts[0], SamplingParams(max_tokens=200, ignore_eos=True))
+        loop.abort(extra)                                 # an abort travels to the followers too
+        outs = [loop.wait(r, timeout=120) for r in rids]
+        time.sleep(0.5)                                   # a few idle keep-alive rounds
+        loop.shutdown()
+        result = {"tokens": [o.output_token_ids for o in outs], "steps": loop.counters["steps"]}
+    else:
+        EngineLoop(llm, follower=True).run_follower()
+        result = {"tokens": None, "free_blocks": llm.engine.scheduler.pool.num_free,
+                  "unfinished": llm.engine.has_unfinished_requests()}
+    json.dump(result, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.get_world_group().barrier()
+    state.destroy_distributed()
+
+
 def task_symm(rank, world, port, workdir, device_kind):
     """Peer-memory collectives against NCCL results."""
     dev, state = setup(rank, world, port, "cuda")
@@ -507,7 +541,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

@@ -64,6 +64,23 @@ def test_sequence_parallel_residual_stream_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
+def test_api_server_loop_replicates_requests_to_the_other_tensor_parallel_rank():
+    """Requests reach rank 0 only; its loop broadcasts them (and aborts) before each step and rank 1
+    follows step for step: tokens equal the plain PyTorch model, rank 1 ends idle with all blocks free."""
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=11)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 33, 9)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        res = run_ranks("server_loop", 2, d)
+    for p, toks in zip(prompts, res[0]["tokens"]):
+        assert toks == refm.greedy_generate(weights, cfg, p, 12)
+    assert res[1]["unfinished"] is False and res[1]["free_blocks"] == 64
+
+
 def _pipeline_case(world: int, pp: int, seed: int, partition=None):
     cfg = tiny_llama()
     weights = refm.make_weights(cfg, seed=seed)
