@@ -43,7 +43,11 @@ class EngineLoop:
         from ..parallel import state as pstate
         world = pstate.get_world_group()
         self.group = world if world.world_size > 1 else None
-        if self.group is not None and getattr(self.engine, "dp_group", None) is not None:
+        if getattr(self.engine, "dp_group", None) is not None:
+            # one server per data-parallel rank: nothing to replicate when the replica is a single rank
+            self.group = None
+        if self.group is None and getattr(self.engine, "dp_group", None) is not None and \
+                pstate.get_tp_group().world_size * pstate.get_pp_group().world_size > 1:
             raise NotImplementedError("the API server replicates requests inside ONE replica: start one server "
                                       "per data-parallel rank with tensor_parallel_size * pipeline_parallel_size == 1, "
                                       "or use data_parallel_size == 1")
@@ -358,6 +362,8 @@ def main(argv=None) -> None:
     if int(os.environ.get("RANK", "0")) != 0 and args.data_parallel_size == 1:
         EngineLoop(llm, follower=True).run_follower()       # requests arrive through rank 0
         return
+    if args.data_parallel_size > 1:
+        args.port += int(os.environ.get("RANK", "0"))      # one server per data-parallel rank: port + rank
     tokenizer = None
     tok_dir = args.tokenizer or (args.model if os.path.isdir(args.model) else None)
     if tok_dir:
