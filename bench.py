@@ -176,8 +176,12 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    ttfts, tpots = [], []
+
     def one_pass():
         outs = llm.generate(prompts, sp)
+        ttfts.extend(o.ttft for o in outs if o.ttft is not None)
+        tpots.extend(o.tpot for o in outs if o.tpot is not None)
         return sum(len(o.output_token_ids) for o in outs)
 
     for _ in range(args.warmup):
@@ -202,6 +206,8 @@ def run_ours(args) -> None:
         sampler.start()
     st0 = dict(llm.engine.stats)
     launches0 = ops.launch_count()
+    ttfts.clear()
+    tpots.clear()
     barrier()
     t0 = time.perf_counter()
     tokens = 0
@@ -236,7 +242,10 @@ def run_ours(args) -> None:
             "ms_per_step": round(device_ms / args.steps, 2),
             "higher_is_better": True,
             "scaling": "strong",
-            "vs_baseline": None,
+            "vs_baseline": _vs_stock(args, e2e),
+            "baseline": _stock_entry(args),
+            "ttft_p50_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
+            "tpot_p50_ms": round(statistics.median(tpots) * 1e3, 3) if tpots else None,
             "dtype": "bf16",
             "data": "synthetic uniform-random token ids; random-init weights (normal, std 0.02)",
             "impl": "ours",
@@ -265,14 +274,38 @@ def run_ours(args) -> None:
     _shutdown(llm, world)
 
 
+def _stock_entry(args):
+    """The measured stock-vLLM number for this model and GPU count (written by
+    baseline/run_stock_vllm.py on the same kind of box), or None."""
+    path = os.path.join(ROOT, "baseline", "stock_vllm_results.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+    except Exception:
+        return None
+    same = (args.num_requests, args.input_len, args.output_len, args.max_num_seqs) == (256, 1024, 256, 128)
+    ent = table.get(args.model, {}).get(str(args.gpus)) if same or args.model != "llama-3-8b" else None
+    return ent
+
+
+def _vs_stock(args, e2e_tok_s: float):
+    """Ours / stock vLLM, both end to end (wall clock around generate), same N."""
+    ent = _stock_entry(args)
+    if not ent or not ent.get("value"):
+        return None
+    return round(e2e_tok_s / float(ent["value"]), 3)
+
+
 def _shutdown(llm, world: int) -> None:
-    """Orderly teardown with a hard deadline: release peer-mapped memory, leave the
-    process groups, and end the process even if a library's finaliser blocks."""
+    """Orderly teardown, then a normal interpreter exit (exit hooks run).  A
+    watchdog ends the process only if a library's finaliser blocks for 30 s, and
+    says so."""
     import threading
 
     import torch.distributed as dist
 
     def _deadline():
+        print("shutdown watchdog fired after 30 s: forcing exit", file=sys.stderr)
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
@@ -292,7 +325,7 @@ def _shutdown(llm, world: int) -> None:
         print(f"shutdown: {type(e).__name__}: {e}", file=sys.stderr)
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+    # the watchdog stays armed through interpreter shutdown (daemon timer): a clean exit beats it
 
 
 def main() -> None:

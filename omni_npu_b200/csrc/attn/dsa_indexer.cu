@@ -33,6 +33,7 @@
 #include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 
 namespace b200 {
 
@@ -526,12 +527,14 @@ extern "C" int b200_dsa_indexer(const void* q, const float* w, const void* cache
   if (q_split > 64) q_split = 64;
   p.q_split = q_split;
   const size_t smem = 1024 + 2 * kIdxKeyBytes + 2 * (2 * static_cast<size_t>(N) * 128) + 2 * N * 4 + 12 * 8 + 16;
-  static size_t configured = 0;
-  if (smem > configured) {
+  if (smem > 227u * 1024u) return -23;
+  static DeviceOnce once;
+  int cur = 0;
+  if (once.needed(&cur)) {
     if (cudaFuncSetAttribute(dsa_indexer_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
+                             227 * 1024) != cudaSuccess)
       return -20;
-    configured = smem;
+    once.mark(cur);
   }
   CUtensorMap tk, tq;
   int r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cache,

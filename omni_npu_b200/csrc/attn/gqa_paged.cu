@@ -22,6 +22,7 @@
 #include "attn_common.cuh"
 #include "../common/pdl.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 
 namespace b200 {
 
@@ -933,12 +934,13 @@ template <int DQK, int DV>
 static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t stream) {
   using Cfg = PrefillCfg<DQK, DV>;
   auto kern = gqa_prefill_kernel<DQK, DV>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  int dev = 0;
+  if (once.needed(&dev)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
         cudaSuccess)
       return -20;
-    configured = true;
+    once.mark(dev);
   }
   dim3 grid((max_q_len + Cfg::BM - 1) / Cfg::BM, p.Hq, B);
   kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
@@ -949,12 +951,13 @@ template <int D, int NSTAGES, int MINB>
 static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = DecodeTmaCfg<D, NSTAGES>;
   auto kern = gqa_decode_tma_kernel<D, NSTAGES, MINB>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  int dev = 0;
+  if (once.needed(&dev)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
       return -20;
     cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    configured = true;
+    once.mark(dev);
   }
   const int box_rows = p.block_size < 64 ? p.block_size : 64;
   CUtensorMap tk, tv;
@@ -1009,12 +1012,13 @@ static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
   } else {
     using Cfg = DecodeCfg<D>;
     auto kern = gqa_decode_kernel<D>;
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce once;
+    int dev = 0;
+    if (once.needed(&dev)) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
           cudaSuccess)
         return -20;
-      configured = true;
+      once.mark(dev);
     }
     kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(p);
   }

@@ -20,6 +20,7 @@
 
 #include "attn_common.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 
 namespace b200 {
 
@@ -407,11 +408,12 @@ extern "C" int b200_mla_decode(const void* q, const void* cache, void* out, floa
   if (splits < 1) splits = 1;
   if (splits > 1 && scratch == nullptr) return -3;
   if ((block_size % 8) != 0 || !(block_size <= 64 ? (64 % block_size) == 0 : (block_size % 64) == 0)) return -4;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  int cur_dev = 0;
+  if (once.needed(&cur_dev)) {
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem) != cudaSuccess)
       return -20;
-    configured = true;
+    once.mark(cur_dev);
   }
   MlaParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);

@@ -28,6 +28,7 @@
 #include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 
 namespace b200 {
 
@@ -385,12 +386,14 @@ static int fb_launch_wg(const CUtensorMap& ta, const CUtensorMap& tw, const Fp8B
                         int max_ctas, cudaStream_t stream) {
   using Cfg = FbCfg<WG>;
   const size_t smem = Cfg::SMEM_BASE + (static_cast<size_t>(p.num_experts) + 2) * 4;
-  static size_t configured = 0;
-  if (smem > configured) {
+  if (smem > 227u * 1024u) return -23;
+  static DeviceOnce once;
+  int cur = 0;
+  if (once.needed(&cur)) {
     if (cudaFuncSetAttribute(gemm_fp8_block_kernel<WG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
+                             227 * 1024) != cudaSuccess)
       return -20;
-    configured = smem;
+    once.mark(cur);
   }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -29,6 +29,7 @@
 #include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 #include "../comm/ll_protocol.cuh"
 
 namespace b200 {
@@ -1153,11 +1154,12 @@ template <bool GROUPED, int KIND>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
                   size_t smem, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<GROUPED, KIND>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  int dev = 0;
+  if (once.needed(&dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return -20;
-    configured = true;
+    once.mark(dev);
   }
   const int cluster_x = p.cluster_split ? p.splits : 1;
   return launch_pdl(kern, dim3(grid, 1, 1), dim3(kThreads, 1, 1), smem, stream, cluster_x, ta, tw, p) == cudaSuccess

@@ -20,6 +20,7 @@
 
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "../common/device_once.h"
 
 namespace b200 {
 
@@ -409,8 +410,10 @@ template <bool FP8>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const PairParams& p, int max_ctas,
                        cudaStream_t stream) {
   auto kern = gemm_pair_kernel<FP8>;
-  static bool configured = false;
-  static int max_pairs = 0;
+  static DeviceOnce once;
+  static int max_pairs = 0;      // the same for every B200 of a machine
+  int dev = 0;
+  const bool configured = !once.needed(&dev);
   const size_t smem = pair_smem(p.BN, p.stages, p.ksub);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kPThreads, 1, 1);
@@ -433,7 +436,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const PairP
       n = sm_count() / 2;
     }
     max_pairs = n;
-    configured = true;
+    once.mark(dev);
   }
   long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
   int pairs = max_pairs;

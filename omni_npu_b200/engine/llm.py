@@ -68,13 +68,40 @@ class LLMEngine:
                     request_id: Optional[str] = None, kv_transfer_params=None,
                     arrival_time: Optional[float] = None) -> str:
         rid = request_id or f"req-{next(self._ids)}"
+        self.validate_sampling_params(sampling_params)
         req = Request(rid, prompt_token_ids, sampling_params, self.config.model.eos_token_id,
                       arrival_time, kv_transfer_params)
         self.scheduler.add_request(req)
         return rid
 
+    def validate_sampling_params(self, sp: Optional[SamplingParams]) -> None:
+        """Refuse (ValueError) what the sampler cannot honour rather than ignore it."""
+        if sp is None:
+            return
+        if sp.logprobs:
+            raise ValueError("logprobs are not supported by this engine")
+        runner = self.worker.model_runner
+        speculative = self.proposer is not None or runner.mtp is not None
+        if speculative and (sp.has_penalties or sp.thinking_token_budget is not None):
+            raise ValueError("penalties and thinking_token_budget are not supported together with "
+                             "speculative decoding")
+        if sp.thinking_token_budget is not None and not runner.thinking_processor.enabled:
+            raise ValueError("thinking_token_budget needs a reasoning config with think start / end "
+                             "token ids (additional_config['reasoning_config'], --reasoning-config)")
+
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
+
+    def fail_all_requests(self) -> List[RequestOutput]:
+        """Abort everything in flight (after a step raised): the requests end with
+        finish_reason "abort" and their blocks return to the pool."""
+        self._inflight = None
+        outs = []
+        for req in list(self.scheduler.running) + list(self.scheduler.waiting):
+            self.scheduler.abort_request(req.request_id)
+            self.worker.model_runner.input_batch.remove_request(req.request_id)
+            outs.append(RequestOutput.from_request(req))
+        return outs
 
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
@@ -83,9 +110,11 @@ class LLMEngine:
     def _async_ok(self) -> bool:
         """Decode steps may be launched before the previous step's tokens are read when nothing on the
         host needs the token values between steps: no draft proposer, no KV connector, no draft head."""
+        runner = self.worker.model_runner
         return (self.async_scheduling and self.proposer is None and self.scheduler.kv_connector is None
-                and self.worker.model_runner.mtp is None and getattr(self.worker, "ha_agent", None) is None
-                and self.worker.model_runner.pp_group is None and self.dp_group is None)
+                and runner.mtp is None and getattr(self.worker, "ha_agent", None) is None
+                and runner.pp_group is None and self.dp_group is None
+                and not any(runner.needs_host_logits(r) for r in self.scheduler.running))
 
     def _settle(self) -> List[RequestOutput]:
         """Read back the step in flight and fill its tokens in."""

@@ -58,12 +58,17 @@ class Scheduler:
         self._finished_since_last: List[str] = []
         self._step = 0
         self.spec_stats = {"drafted": 0, "accepted": 0}
+        self.kv_load_failures = 0
 
     # ------------------------------------------------------------------ intake
     def add_request(self, req: Request) -> None:
         if req.num_prompt_tokens >= self.cfg.max_model_len:
             raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len "
                              f"{self.cfg.max_model_len}")
+        usable = self.pool.num_blocks - self.pool.num_reserved
+        if self.pool.blocks_needed(req.num_prompt_tokens) > usable:
+            raise ValueError(f"prompt of {req.num_prompt_tokens} tokens does not fit the KV cache "
+                             f"({usable} blocks of {self.block_size} tokens)")
         self.requests[req.request_id] = req
         self.waiting.append(req)
 
@@ -150,7 +155,9 @@ class Scheduler:
         budget = self.cfg.max_num_batched_tokens
         # 1) unfinished prompt chunks of running requests, then new admissions
         prefill: List[ScheduledSeq] = []
-        for req in self.running:
+        for req in list(self.running):
+            if req not in self.running:            # evicted below to make room for an earlier request
+                continue
             remaining = req.num_tokens - req.num_computed_tokens
             if remaining > 1 or (remaining == 1 and not req.output_token_ids):
                 n = min(remaining, budget)
@@ -158,14 +165,51 @@ class Scheduler:
                     break
                 if not self.cfg.enable_chunked_prefill and n < remaining:
                     break
-                if not self._ensure_blocks(req, req.num_computed_tokens + n):
-                    break
+                # A half-computed prompt must never reach the decode branch (it would sample from
+                # an incomplete context).  When its next chunk finds no blocks, later-admitted
+                # requests are evicted for it; if it is itself the latest one, it goes back to the
+                # waiting queue and is recomputed when blocks are free again.
+                fits = self._ensure_blocks(req, req.num_computed_tokens + n)
+                while not fits:
+                    victim = self.running[-1]
+                    if victim is req:
+                        if len(self.running) == 1 and not prefill:
+                            raise RuntimeError("KV cache too small for a single sequence")
+                        self.preempt_for_recompute(req)
+                        out.preempted.append(req.request_id)
+                        break
+                    self.preempt_for_recompute(victim)
+                    out.preempted.append(victim.request_id)
+                    for s in prefill:
+                        if s.request is victim:
+                            budget += s.num_new_tokens
+                    prefill = [s for s in prefill if s.request is not victim]
+                    fits = self._ensure_blocks(req, req.num_computed_tokens + n)
+                if not fits:
+                    continue
                 prefill.append(ScheduledSeq(req, req.num_computed_tokens, n, n == remaining))
                 budget -= n
-        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+        # nothing is admitted in a step that had to evict: the evicted request sits at the head of
+        # the queue and would take the freed blocks straight back
+        while (self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
+               and not out.preempted):
             req = self.waiting[0]
             if req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
-                if self.kv_connector is not None and self.kv_connector.is_load_finished(req):
+                done = False
+                if self.kv_connector is not None:
+                    try:
+                        done = self.kv_connector.is_load_finished(req)
+                    except ConnectionError as e:
+                        # the producer is gone or the pull failed: compute the prompt here instead
+                        # (the blocks already allocated for the remote KV are simply filled locally)
+                        self.kv_load_failures += 1
+                        req.num_external_tokens = 0
+                        req.kv_transfer_params = None
+                        req.num_computed_tokens = 0
+                        done = True
+                        import logging
+                        logging.getLogger("omni_npu_b200").warning("%s: falling back to local prefill", e)
+                if done:
                     req.status = RequestStatus.WAITING
                 else:
                     # keep order simple: look at the next request instead
@@ -191,6 +235,10 @@ class Scheduler:
             n = min(remaining, budget)
             if n < remaining and not self.cfg.enable_chunked_prefill:
                 break
+            # admit only when the whole prompt would fit now: a prompt admitted chunk by chunk into
+            # a nearly full cache is evicted half-way and recomputed over and over
+            if not self.pool.can_allocate(self.pool.blocks_needed(req.num_tokens, len(req.block_ids))):
+                break
             if not self._ensure_blocks(req, req.num_computed_tokens + n):
                 break
             self.waiting.popleft()
@@ -210,6 +258,9 @@ class Scheduler:
         i = 0
         while i < len(self.running):
             req = self.running[i]
+            if req.num_tokens - req.num_computed_tokens > 1:
+                i += 1                 # prompt (or recompute) not finished: never sampled from here
+                continue
             # drafts must leave room for the bonus token inside max_model_len and the budget
             room = min(self.cfg.max_model_len - req.num_tokens - 1,
                        req.sampling_params.max_tokens - len(req.output_token_ids) - 1)

@@ -149,6 +149,11 @@ class P2PKVConnector:
         self._poll_events()
         with self._lock:
             if rid in self._failed:
+                # a per-request event: forget the load so the caller's fallback (local recompute)
+                # or a retry does not meet the same error again
+                self._failed.discard(rid)
+                self._pending_loads.pop(rid, None)
+                self._new_loads.pop(rid, None)
                 raise ConnectionError(f"KV load for request {rid} failed")
             if rid in self._loaded:
                 self._loaded.discard(rid)

@@ -64,6 +64,7 @@ class EngineLoop:
         self.counters = {"requests": 0, "finished": 0, "output_tokens": 0, "steps": 0}
 
     def submit(self, prompt_ids: List[int], sp: SamplingParams, kv_transfer_params=None) -> str:
+        self.engine.validate_sampling_params(sp)        # ValueError -> HTTP 400, before anything is queued
         rid = f"cmpl-{uuid.uuid4().hex}"
         slot = {"event": threading.Event(), "output": None, "seen": 0, "queue": [], "request": None}
         with self.lock:
@@ -98,7 +99,17 @@ class EngineLoop:
                 self.wake.wait(0.002)
                 self.wake.clear()
             with self.lock:
-                self._publish(self.engine.step())
+                self._publish(self._safe_step())
+
+    def _safe_step(self):
+        """One engine step.  An exception must not end the loop thread (every waiter would hang):
+        the requests in flight are failed with finish_reason "abort" and the loop goes on."""
+        try:
+            return self.engine.step()
+        except Exception:
+            logger.exception("engine step failed: aborting the requests in flight")
+            self.counters["failed_steps"] = self.counters.get("failed_steps", 0) + 1
+            return self.engine.fail_all_requests()
 
     def _publish(self, outs) -> None:
         """After a step (lock held): hand new tokens to streaming waiters, finished outputs to all."""
@@ -149,7 +160,7 @@ class EngineLoop:
             with self.lock:
                 self._apply(new, aborts)
                 if busy:
-                    self._publish(self.engine.step())
+                    self._publish(self._safe_step())
         self.group.broadcast_object({"new": [], "aborts": [], "step": False, "stop": True}, src=0)
 
     def run_follower(self) -> None:
@@ -160,7 +171,11 @@ class EngineLoop:
                 return
             self._apply(msg["new"], msg["aborts"])
             if msg["step"]:
-                self.engine.step()
+                try:
+                    self.engine.step()
+                except Exception:               # the leader fails the same step the same way
+                    logger.exception("engine step failed on a follower rank")
+                    self.engine.fail_all_requests()
 
     def wait(self, rid: str, timeout: Optional[float] = None):
         slot = self.waiters[rid]
@@ -187,7 +202,8 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           presence_penalty=float(body.get("presence_penalty") or 0.0),
                           frequency_penalty=float(body.get("frequency_penalty") or 0.0),
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
-                          thinking_token_budget=body.get("thinking_token_budget"))
+                          thinking_token_budget=body.get("thinking_token_budget"),
+                          logprobs=body.get("logprobs") or body.get("top_logprobs") or None)
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):
@@ -235,6 +251,12 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                  f"omni_b200_waiting_requests {len(llm.engine.scheduler.waiting)}"]
         return PlainTextResponse("\n".join(lines) + "\n")
 
+    def _submit(ids, body) -> str:
+        try:
+            return loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+
     async def _finish(rid: str):
         while True:
             out = await asyncio.to_thread(loop.wait, rid, 0.5)
@@ -262,7 +284,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
     @app.post("/v1/completions")
     async def completions(body: Dict[str, Any]):
         ids = encode(body.get("prompt"))
-        rid = loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+        rid = _submit(ids, body)
         created = int(time.time())
         if body.get("stream"):
             def chunk(toks, finish):
@@ -287,7 +309,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
             ids = msgs[-1]["content"]                      # token ids in the last message (no tokenizer)
         else:
             raise HTTPException(400, "chat needs a tokenizer with a chat template")
-        rid = loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+        rid = _submit(ids, body)
         out = await _finish(rid)
         text = decode(out.output_token_ids)
         message: Dict[str, Any] = {"role": "assistant", "content": text}
@@ -358,6 +380,8 @@ def main(argv=None) -> None:
               compilation_config=args.compilation_config, kv_transfer_config=args.kv_transfer_config,
               speculative_config=args.speculative_config, additional_config=args.additional_config,
               load_format=args.load_format, seed=args.seed)
+    if args.reasoning_config:
+        kw["additional_config"] = dict(kw["additional_config"] or {}, reasoning_config=args.reasoning_config)
     llm = LLM(model=args.model, **kw)
     if int(os.environ.get("RANK", "0")) != 0 and args.data_parallel_size == 1:
         EngineLoop(llm, follower=True).run_follower()       # requests arrive through rank 0
@@ -372,6 +396,12 @@ def main(argv=None) -> None:
             tokenizer = AutoTokenizer.from_pretrained(tok_dir)
         except Exception as e:
             logger.warning("no tokenizer loaded from %s (%s): token-id requests only", tok_dir, e)
+    if args.reasoning_config and tokenizer is not None:
+        # marker strings given instead of token ids: resolve them now that there is a tokenizer
+        proc = llm.engine.worker.model_runner.thinking_processor
+        if proc.cfg is not None and not proc.enabled:
+            proc.cfg.initialize_token_ids(tokenizer)
+            proc.__init__(proc.cfg, device=proc.device)
     rp = get_reasoning_parser(args.reasoning_parser)(tokenizer) if args.reasoning_parser and tokenizer else None
     tp = get_tool_parser(args.tool_call_parser)(tokenizer) if args.tool_call_parser and tokenizer else None
     app = build_app(llm, tokenizer, args.served_model_name or os.path.basename(str(args.model)), rp, tp)

@@ -56,6 +56,18 @@ class StepLayout:
         return lay
 
 
+def default_seed(request_id: str, base_seed: int = 0) -> int:
+    """Sampling seed of a request that gave none.  Tensor-parallel ranks are separate processes
+    and each samples on its own, so the value must not depend on the process: Python's ``hash``
+    of a string is salted per process, a CRC of the request id (mixed with the engine seed) is
+    the same everywhere."""
+    import zlib
+    data = request_id.encode("utf-8")
+    lo = zlib.crc32(data)
+    hi = zlib.crc32(data[::-1] + b"#", base_seed & 0xFFFFFFFF)
+    return ((hi << 32) | lo) & 0x7FFFFFFFFFFFFFFF
+
+
 class InputBatch:
     def __init__(self, max_num_seqs: int, max_model_len: int, block_size: int,
                  max_num_batched_tokens: int, device: torch.device) -> None:
@@ -72,6 +84,7 @@ class InputBatch:
         self.top_k = np.zeros(max_num_seqs, dtype=np.int32)
         self.top_p = np.ones(max_num_seqs, dtype=np.float32)
         self.seeds = np.zeros(max_num_seqs, dtype=np.int64)
+        self.base_seed = 0              # engine seed, mixed into the default per-request seeds
         cap_T = max(max_num_batched_tokens, max_num_seqs)
         self.capacity = StepLayout.make(cap_T, max_num_seqs, self.max_blocks)
         pin = device.type == "cuda"
@@ -95,8 +108,7 @@ class InputBatch:
             self.temperature[row] = sp.temperature
             self.top_k[row] = sp.top_k if sp.top_k and sp.top_k > 0 else 0
             self.top_p[row] = sp.top_p
-            seed = sp.seed if sp.seed is not None else hash(req.request_id) & 0x7FFFFFFFFFFFFFFF
-            self.seeds[row] = seed
+            self.seeds[row] = sp.seed if sp.seed is not None else default_seed(req.request_id, self.base_seed)
         self.sync_blocks(row, req)
         return row
 

@@ -57,6 +57,7 @@ class ModelRunner:
         sc = config.scheduler
         self.input_batch = InputBatch(sc.max_num_seqs, sc.max_model_len, config.cache.block_size,
                                       sc.max_num_batched_tokens, device)
+        self.input_batch.base_seed = int(config.seed or 0)
         self.sampler = Sampler(config, device)
         self.rejection_sampler = RejectionSampler(self.sampler)
         self.graphs: Dict[int, CUDAGraphRunner] = {}
@@ -64,6 +65,14 @@ class ModelRunner:
         pin = device.type == "cuda"
         self.sampled_host = torch.zeros(max(sc.max_num_seqs, 1), dtype=torch.int32, pin_memory=pin)
         self.sampled_host2 = torch.zeros(max(sc.max_num_seqs, 1), 2, dtype=torch.int32, pin_memory=pin)
+        # Penalties and the thinking-token budget work on each request's token history, which lives
+        # on the host: a step that needs them runs eagerly with ``_logits_fn`` set (never from a
+        # graph, never launched ahead of the previous step's tokens).
+        self._logits_fn = None
+        from ..sample.logits_processors import ThinkingTokenBudgetLogitsProcessor
+        from ..serving.reasoning_config import ReasoningConfig
+        rc = ReasoningConfig.from_cli(config.additional_config.get("reasoning_config"))
+        self.thinking_processor = ThinkingTokenBudgetLogitsProcessor(rc, sc.max_num_seqs, device)
         self.mtp = None                       # the model's multi-token-prediction head, if it drafts
         self.last_drafts: List[List[int]] = []
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
@@ -210,6 +219,8 @@ class ModelRunner:
             idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
             hidden = hidden_all.index_select(0, idx) if idx is not None else hidden_all[:num_samples]
             logits = self.model.compute_logits(hidden)
+            if self._logits_fn is not None:
+                logits = self._logits_fn(logits)
             sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
                                    views["top_p"][:num_samples], views["seeds"][:num_samples],
                                    self.step_counter)
@@ -250,6 +261,8 @@ class ModelRunner:
                 idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
                 hidden = out.index_select(0, idx) if idx is not None else out[:num_samples]
                 logits = self.model.compute_logits(hidden)
+                if self._logits_fn is not None:
+                    logits = self._logits_fn(logits)
                 sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
                                        views["top_p"][:num_samples], views["seeds"][:num_samples],
                                        self.step_counter).to(torch.int64)
@@ -283,6 +296,71 @@ class ModelRunner:
                 cols.append(draft.to(torch.int32).unsqueeze(1))
         return torch.cat(cols, dim=1)
 
+    @staticmethod
+    def needs_host_logits(req) -> bool:
+        """Whether sampling for this request needs its token history (penalties, thinking budget)."""
+        sp = req.sampling_params
+        return sp.has_penalties or sp.thinking_token_budget is not None
+
+    def _make_logits_fn(self, seqs):
+        """Logits adjustment for one step, or None when no scheduled sequence asks for any.
+        Row i of the logits belongs to ``seqs[i]``.  Penalties: occurrence counts of the generated
+        tokens and a mask of the prompt's tokens are built on the device from the token lists
+        (only for the rows that ask), then ``apply_penalties``
+        (reference: omni_npu/sample/sampler.py:115-158).  Thinking budget: the per-request state
+        machine forces the end-of-thinking marker once the budget is spent."""
+        from ..sample.sampler import apply_penalties
+        use_pen = self.config.use_penalty
+        pen_rows = [i for i, s in enumerate(seqs)
+                    if s.samples and use_pen and s.request.sampling_params.has_penalties]
+        tp = self.thinking_processor
+        think_rows = [i for i, s in enumerate(seqs) if s.samples and tp.enabled
+                      and s.request.sampling_params.thinking_token_budget is not None]
+        if not pen_rows and not think_rows:
+            return None
+        for i in think_rows:
+            r = seqs[i].request
+            if r.request_id not in tp.state:
+                tp.add_request(r.request_id, r.prompt_token_ids, r.sampling_params.thinking_token_budget)
+        dev = self.device
+
+        def fn(logits: torch.Tensor) -> torch.Tensor:
+            logits = logits.float()
+            V = logits.shape[-1]
+            if pen_rows:
+                rr, tt, pr, pt = [], [], [], []
+                for j, i in enumerate(pen_rows):
+                    r = seqs[i].request
+                    outs = [t for t in r.output_token_ids if 0 <= t < V]
+                    rr += [j] * len(outs)
+                    tt += outs
+                    ptoks = set(t for t in r.prompt_token_ids if 0 <= t < V)
+                    pr += [j] * len(ptoks)
+                    pt += list(ptoks)
+                counts = torch.zeros(len(pen_rows), V, dtype=torch.float32, device=dev)
+                if tt:
+                    counts.index_put_((torch.tensor(rr, device=dev), torch.tensor(tt, device=dev)),
+                                      torch.ones(len(tt), device=dev), accumulate=True)
+                pmask = torch.zeros(len(pen_rows), V, dtype=torch.bool, device=dev)
+                if pt:
+                    pmask[torch.tensor(pr, device=dev), torch.tensor(pt, device=dev)] = True
+                sps = [seqs[i].request.sampling_params for i in pen_rows]
+                idx = torch.tensor(pen_rows, device=dev)
+                sub = apply_penalties(
+                    logits.index_select(0, idx), pmask, counts,
+                    torch.tensor([sp.presence_penalty for sp in sps], dtype=torch.float32, device=dev),
+                    torch.tensor([sp.frequency_penalty for sp in sps], dtype=torch.float32, device=dev),
+                    torch.tensor([sp.repetition_penalty for sp in sps], dtype=torch.float32, device=dev))
+                logits = logits.index_copy(0, idx, sub)
+            if think_rows:
+                idx = torch.tensor(think_rows, device=dev)
+                sub = tp.apply(logits.index_select(0, idx).clone(),
+                               [seqs[i].request.request_id for i in think_rows],
+                               [seqs[i].request.output_token_ids for i in think_rows])
+                logits = logits.index_copy(0, idx, sub)
+            return logits
+        return fn
+
     def _pad_decode_size(self, n: int) -> Optional[int]:
         for s in self.capture_sizes:
             if s >= n:
@@ -296,6 +374,7 @@ class ModelRunner:
         ib = self.input_batch
         for rid in out.finished_req_ids:
             ib.remove_request(rid)
+            self.thinking_processor.remove_request(rid)
         for rid in out.preempted:
             ib.remove_request(rid)
         if self.kv_connector is not None and out.kv_connector_metadata is not None:
@@ -304,6 +383,13 @@ class ModelRunner:
             return []
         n = len(out.seqs)
         ev = None
+        self._logits_fn = self._make_logits_fn(out.seqs) if out.kind != "spec_decode" else None
+        try:
+            return self._execute_scheduled(out, ib, n, ev)
+        finally:
+            self._logits_fn = None
+
+    def _execute_scheduled(self, out: SchedulerOutput, ib, n: int, ev) -> List[int]:
         if out.kind == "spec_decode":
             T = out.num_tokens
             lay = ib.layout_for(T, n)
@@ -325,7 +411,7 @@ class ModelRunner:
             return [r[: r[-1]] for r in rows]
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
-            padded = self._pad_decode_size(n) if self.graphs else None
+            padded = self._pad_decode_size(n) if self.graphs and self._logits_fn is None else None
             S = padded or n
             lay = ib.layout_for(S, S)
             ib.stage_decode(lay, reqs)

@@ -197,3 +197,46 @@ def test_disaggregated_serving_through_the_host_pool(tmp_path, monkeypatch):
     finally:
         prefill.engine.shutdown()
         decode.engine.shutdown()
+
+
+def test_failed_kv_pull_falls_back_to_local_prefill():
+    """A pull that fails on the host (injected: the link manager raises) is a per-request event:
+    the decode instance computes that prompt itself, gives the same tokens, and keeps stepping."""
+    cfg = tiny_llama()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (36, 21)]
+    common = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=32, seed=1, additional_config={"async_pull_kv": False})
+    mono = LLM(model=cfg, **common)
+    want = [o.output_token_ids for o in mono.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    prefill = LLM(model=cfg, kv_transfer_config=dict(kv_connector="P2PKVConnector", kv_role="kv_producer",
+                                                      kv_port=0, kv_connector_extra_config={"kv_port": 24511}), **common)
+    decode = LLM(model=cfg, kv_transfer_config=dict(kv_connector="P2PKVConnector", kv_role="kv_consumer",
+                                                     kv_connector_extra_config={"kv_port": 24611}), **common)
+    decode.engine.worker.get_model().load_state_dict(prefill.engine.worker.get_model().state_dict())
+    try:
+        p_out = prefill.generate(prompts, SamplingParams(max_tokens=1, ignore_eos=True))
+        manager = decode.engine.worker.model_runner.kv_connector.manager
+        real_pull, calls = manager.pull_kv, {"n": 0}
+
+        def flaky_pull(*a, **kw):
+            calls["n"] += 1
+            if calls["n"] == 1:
+                raise ConnectionError("injected: producer unreachable")
+            return real_pull(*a, **kw)
+        manager.pull_kv = flaky_pull
+        order = {}
+        for i, (p, o) in enumerate(zip(prompts, p_out)):
+            order[decode.engine.add_request(p, SamplingParams(max_tokens=6, ignore_eos=True),
+                                            kv_transfer_params=o.kv_transfer_params)] = i
+        got, steps = [None] * 2, 0
+        while decode.engine.has_unfinished_requests() and steps < 200:
+            steps += 1
+            for o in decode.engine.step():
+                got[order[o.request_id]] = o.output_token_ids
+        assert got == want
+        assert decode.engine.scheduler.kv_load_failures == 1 and calls["n"] == 2
+        assert decode.engine.scheduler.pool.num_free == 32
+    finally:
+        prefill.engine.shutdown()
+        decode.engine.shutdown()

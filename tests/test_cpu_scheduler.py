@@ -114,3 +114,33 @@ def test_reserved_blocks_stay_out_of_the_free_list():
     s.add_request(_req("a", 16, max_tokens=1))
     o = s.schedule()
     assert o.kind == "prefill" and all(b >= 2 for b in s.requests["a"].block_ids)
+
+
+def test_half_computed_prompt_is_never_sampled_when_blocks_run_out():
+    """A chunked prompt whose next chunk finds no free blocks must not fall through to the decode
+    branch: no step may sample for it before its whole prompt is in the cache."""
+    s = Scheduler(SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
+                                  enable_chunked_prefill=True), CacheConfig(block_size=16), 10)
+    s.add_request(_req("B", 64, max_tokens=64))
+    o = s.schedule()
+    s.update_from_output(o, [7])                     # B: 4 blocks, decoding
+    s.add_request(_req("A", 128, max_tokens=8))
+    sampled_early = []
+    for _ in range(600):
+        o = s.schedule()
+        if o.kind == "idle":
+            break
+        for q in o.seqs:
+            r = q.request
+            if q.samples and q.start + q.num_new_tokens < r.num_tokens:
+                sampled_early.append((r.request_id, q.start, q.num_new_tokens))
+            if o.kind == "decode":
+                assert r.num_tokens - r.num_computed_tokens == 1, (r.request_id, q.start)
+        s.update_from_output(o, [5] * len(o.seqs))
+        if not s.has_unfinished():
+            break
+    assert not sampled_early
+    a, b = s.requests["A"], s.requests["B"]
+    assert a.is_finished and b.is_finished
+    assert len(a.output_token_ids) == 8 and len(b.output_token_ids) == 64
+    assert s.pool.num_free == 10
