@@ -148,6 +148,12 @@ class B200Platform(_Base):
         cc = getattr(vllm_config, "cache_config", None)
         if cc is not None and not getattr(cc, "block_size", None):
             cc.block_size = DEFAULT_BLOCK_SIZE
+        sc = getattr(vllm_config, "scheduler_config", None)
+        if sc is not None and getattr(sc, "async_scheduling", False):
+            # the worker returns each step's tokens itself; vLLM's placeholder-token protocol for
+            # steps scheduled ahead of their results is not implemented by it
+            with contextlib.suppress(Exception):
+                sc.async_scheduling = False
         comp = getattr(vllm_config, "compilation_config", None)
         if comp is not None:
             # fusion passes of the tracing compiler do not apply: the kernels are already fused
@@ -161,6 +167,11 @@ class B200Platform(_Base):
         vllm_config.b200_options = dict(ac)
         logger.info("B200 platform configured: worker=%s block_size=%s", WORKER_CLS,
                     getattr(cc, "block_size", None))
+
+    @classmethod
+    def update_block_size_for_backend(cls, vllm_config: Any) -> None:
+        """The worker sizes its own paged cache from ``cache_config.block_size`` when it is built;
+        the block size must not change afterwards."""
 
     @classmethod
     def get_attn_backend_cls(cls, selected_backend=None, attn_selector_config=None, num_heads=None,
@@ -213,3 +224,75 @@ class B200Platform(_Base):
     def verify_quantization(cls, quant: str) -> None:
         if quant and quant not in cls.supported_quantization:
             raise ValueError(f"{quant} quantization is not supported on the B200 platform")
+
+
+class B200CpuPlatform(B200Platform):
+    """The same plugin surface on a machine without a GPU: device ``cpu``, gloo process groups,
+    the fp32 reference ops instead of the CUDA kernels.  Selected with ``OMNI_B200_PLUGIN=cpu``;
+    meant for plumbing tests of the platform / worker / model runner under a vLLM engine."""
+    device_name: str = "cpu"
+    device_type: str = "cpu"
+    dispatch_key: str = "CPU"
+    dist_backend: str = "gloo"
+    device_control_env_var: str = "OMNI_B200_CPU_VISIBLE_DEVICES"
+
+    @classmethod
+    def set_device(cls, device: torch.device) -> None:
+        pass
+
+    @classmethod
+    def get_device_name(cls, device_id: int = 0) -> str:
+        return "cpu"
+
+    @classmethod
+    def get_device_capability(cls, device_id: int = 0):
+        return None
+
+    @classmethod
+    def get_device_total_memory(cls, device_id: int = 0) -> int:
+        import psutil
+        return psutil.virtual_memory().total
+
+    @classmethod
+    def device_count(cls) -> int:
+        return 1
+
+    @classmethod
+    def mem_get_info(cls, device: Optional[torch.device] = None) -> Tuple[int, int]:
+        import psutil
+        vm = psutil.virtual_memory()
+        return vm.available, vm.total
+
+    @classmethod
+    def get_current_memory_usage(cls, device: Optional[torch.device] = None) -> float:
+        return 0.0
+
+    @classmethod
+    def is_pin_memory_available(cls) -> bool:
+        return False
+
+    @classmethod
+    def manual_seed_all(cls, seed: int) -> None:
+        torch.manual_seed(seed)
+
+    def is_cuda_alike(self) -> bool:
+        return False
+
+    def is_sleep_mode_available(self) -> bool:
+        return False
+
+    @classmethod
+    def import_kernels(cls) -> None:
+        try:
+            from .kv_transfer.register import register_connectors
+            register_connectors()
+        except Exception as e:
+            logger.warning("KV connectors not registered: %s", e)
+
+    @classmethod
+    def use_custom_allreduce(cls) -> bool:
+        return False
+
+    @classmethod
+    def get_punica_wrapper(cls) -> str:
+        return "vllm.lora.punica_wrapper.punica_cpu.PunicaWrapperCPU"

@@ -1,123 +1,382 @@
-"""vLLM worker for B200.
+"""vLLM worker that runs this package's own model runner.
 
-A B200 is a CUDA device, so vLLM's own GPU worker and model runner already drive it; this
-class derives from them and adds what the platform plugin promises on top
-(omni_npu/worker/npu_worker.py:77-299 is the reference's counterpart, which has to replace
-far more because its device is not CUDA):
+``B200Worker`` derives from vLLM's ``WorkerBase`` only (not from vLLM's GPU worker and not
+from ``GPUModelRunner``): vLLM's engine core keeps its scheduler, KV block manager and
+executor, and every per-device step goes through this package's ``Worker`` /
+``ModelRunner`` (input batch with one pinned staging copy per step, full-step CUDA-graph
+decode, tcgen05 GEMMs, fused collectives, own sampler).  The counterpart in the reference is
+``NPUWorker`` + ``NPUModelRunner`` (omni_npu/worker/npu_worker.py:38-291,
+omni_npu/worker/npu_model_runner.py:68-623); the reference's runner subclasses
+``GPUModelRunner``, this one does not.
 
-* the device communicator, attention backends, custom ops, KV connector and patches are
-  installed by the platform / plugin entry points before the worker is built;
-* sleep mode routes model weights and KV cache through the VMM pool of
-  ``worker/mem_pool.py`` (physical memory released on ``sleep``, restored on ``wake_up``);
-* the best-practice deployment plan for the model is loaded after ``init_device`` and its
-  per-layer groups are created;
-* the profiler can be started by a token-count trigger (``VLLM_TORCH_PROFILER_DIR`` +
-  ``PROFILER_TOKEN_THRESHOLD`` / ``PROFILER_STOP_STEP``);
-* token recovery wraps ``execute_model`` when ``USE_HA=1``.
+What is translated per step:
+
+* vLLM ``SchedulerOutput`` -> ``engine.scheduler.SchedulerOutput``.  The worker keeps one
+  ``engine.request.Request`` per live request (tokens, block ids, sampling parameters) and
+  updates it from ``scheduled_new_reqs`` / ``scheduled_cached_reqs``.  A step whose sequences
+  all feed exactly one token that yields a sample is a *decode* step (CUDA graph); anything
+  else (prompt chunks, or prompt chunks mixed with decoding sequences, as vLLM's chunked
+  prefill produces) runs as a variable-length *prefill* step.
+* the runner's sampled tokens -> vLLM ``ModelRunnerOutput``.
+
+KV cache: ``get_kv_cache_spec`` describes one attention spec per layer so that vLLM's KV
+cache manager can size the cache; ``initialize_from_config`` takes the resulting block count
+and lets the runner allocate its own paged tensors.  Block 0 is vLLM's null block and is the
+only block the runner's dummy runs touch.
+
+Not supported under vLLM yet (refused with a clear error, never silently wrong): vLLM-side
+speculative decoding, structured-output bitmasks, LoRA, pooling, vLLM's asynchronous
+scheduling (switched off by the platform) and pipeline parallelism.
 """
 from __future__ import annotations
 
 import os
-from typing import Any, Optional
+from typing import Any, Dict, List, Optional
+
+import torch
 
 from .. import compat
-from ..ha.monitor import token_recover_wrapper
 from ..logger import logger
 
 if compat.vllm_available():
-    try:
-        from vllm.v1.worker.gpu_worker import Worker as _GPUWorker
-    except Exception:                                     # CPU-only environment without the CUDA worker
-        _GPUWorker = object
-else:
-    _GPUWorker = object
+    from vllm.v1.worker.worker_base import WorkerBase as _WorkerBase
+else:                                                     # importable without vLLM (docs, tests)
+    class _WorkerBase:                                    # type: ignore[no-redef]
+        def __init__(self, vllm_config, local_rank, rank, distributed_init_method, is_driver_worker=False):
+            self.vllm_config, self.local_rank, self.rank = vllm_config, local_rank, rank
+            self.distributed_init_method, self.is_driver_worker = distributed_init_method, is_driver_worker
 
 
-class B200Worker(_GPUWorker):  # type: ignore[misc, valid-type]
-    def __init__(self, *args: Any, **kwargs: Any) -> None:
-        super().__init__(*args, **kwargs)
+def engine_config_from_vllm(vllm_config, device_type: str):
+    """This package's ``EngineConfig`` for a vLLM ``VllmConfig``."""
+    from ..config import ModelConfig
+    from ..engine.llm import build_engine_config
+    mc_v = vllm_config.model_config
+    hf = mc_v.hf_config
+    d = hf.to_dict() if hasattr(hf, "to_dict") else dict(hf)
+    mc = ModelConfig.from_hf_dict(d, dtype=mc_v.dtype)
+    pc, sc, cc = vllm_config.parallel_config, vllm_config.scheduler_config, vllm_config.cache_config
+    if pc.pipeline_parallel_size > 1:
+        raise ValueError("pipeline parallelism under vLLM is not supported by the B200 worker; "
+                         "use the standalone engine (omni_npu_b200.serving.api_server)")
+    comp = vllm_config.compilation_config
+    sizes = list(getattr(comp, "cudagraph_capture_sizes", None) or [])
+    sizes = [s for s in sizes if s <= sc.max_num_seqs] or None
+    mode = str(getattr(getattr(comp, "cudagraph_mode", None), "name", "FULL_DECODE_ONLY"))
+    eager = bool(mc_v.enforce_eager) or mode == "NONE" or device_type != "cuda"
+    load_format = str(getattr(vllm_config.load_config, "load_format", "auto"))
+    path = mc_v.model if os.path.isdir(str(mc_v.model)) else None
+    ac = dict(getattr(vllm_config, "additional_config", None) or {})
+    cfg = build_engine_config(
+        mc, model_path=path, tensor_parallel_size=pc.tensor_parallel_size,
+        data_parallel_size=1, enable_expert_parallel=bool(pc.enable_expert_parallel),
+        max_num_seqs=sc.max_num_seqs, max_num_batched_tokens=sc.max_num_batched_tokens,
+        max_model_len=mc_v.max_model_len, block_size=cc.block_size,
+        gpu_memory_utilization=cc.gpu_memory_utilization, enforce_eager=eager,
+        compilation_config={"cudagraph_mode": "NONE" if eager else "FULL_DECODE_ONLY",
+                            "cudagraph_capture_sizes": sizes},
+        load_format="dummy" if load_format == "dummy" or path is None else "auto",
+        seed=int(mc_v.seed or 0), device=device_type,
+        enable_sleep_mode=bool(getattr(mc_v, "enable_sleep_mode", False)), additional_config=ac)
+    return cfg
+
+
+def sampling_params_from_vllm(sp):
+    """vLLM ``SamplingParams`` -> this package's.  Stop conditions stay with vLLM's scheduler,
+    which sees every sampled token; only what shapes the distribution is carried over."""
+    from ..engine.request import SamplingParams
+    if sp is None:
+        return SamplingParams(max_tokens=1 << 30, ignore_eos=True)
+    if getattr(sp, "logprobs", None) or getattr(sp, "prompt_logprobs", None):
+        raise ValueError("logprobs are not supported by the B200 worker")
+    top_k = int(getattr(sp, "top_k", 0) or 0)
+    return SamplingParams(
+        max_tokens=1 << 30, temperature=float(sp.temperature or 0.0), top_k=top_k if top_k > 0 else 0,
+        top_p=float(sp.top_p if sp.top_p is not None else 1.0), seed=sp.seed, ignore_eos=True,
+        presence_penalty=float(sp.presence_penalty or 0.0), frequency_penalty=float(sp.frequency_penalty or 0.0),
+        repetition_penalty=float(sp.repetition_penalty or 1.0),
+        thinking_token_budget=(getattr(sp, "extra_args", None) or {}).get("thinking_token_budget"))
+
+
+class StepTranslator:
+    """Per-request state of a worker and the translation of one scheduler step."""
+
+    def __init__(self) -> None:
+        self.requests: Dict[str, Any] = {}
+
+    def translate(self, so):
+        from ..engine.request import Request
+        from ..engine.scheduler import ScheduledSeq, SchedulerOutput
+        if getattr(so, "scheduled_spec_decode_tokens", None):
+            raise NotImplementedError("speculative decoding driven by vLLM's scheduler is not supported by "
+                                      "the B200 worker")
+        out = SchedulerOutput()
+        for rid in so.finished_req_ids:
+            if self.requests.pop(rid, None) is not None:
+                out.finished_req_ids.append(rid)
+        for rid in (getattr(so, "preempted_req_ids", None) or ()):
+            r = self.requests.get(rid)
+            if r is not None:
+                r.block_ids = []
+                r.num_computed_tokens = 0
+                out.preempted.append(rid)
+        for new in so.scheduled_new_reqs:
+            if new.pooling_params is not None:
+                raise NotImplementedError("pooling requests are not supported by the B200 worker")
+            if len(new.block_ids) != 1:
+                raise NotImplementedError("more than one KV cache group is not supported by the B200 worker")
+            toks = new.prompt_token_ids if new.prompt_token_ids is not None else new.prefill_token_ids
+            if toks is None:
+                raise NotImplementedError("prompt embeddings are not supported by the B200 worker")
+            req = Request(new.req_id, toks, sampling_params_from_vllm(new.sampling_params))
+            req.block_ids = list(new.block_ids[0])
+            req.num_computed_tokens = int(new.num_computed_tokens)
+            self.requests[new.req_id] = req
+        cached = so.scheduled_cached_reqs
+        for i, rid in enumerate(cached.req_ids):
+            req = self.requests[rid]
+            nb = cached.new_block_ids[i]
+            if rid in cached.resumed_req_ids:
+                req.block_ids = list(nb[0]) if nb is not None else []
+            elif nb is not None:
+                req.block_ids.extend(nb[0])
+            req.num_computed_tokens = int(cached.num_computed_tokens[i])
+            if cached.new_token_ids:                      # pipeline parallelism: tokens come from the scheduler
+                known = len(req.output_token_ids)
+                want = int(cached.num_output_tokens[i]) if cached.num_output_tokens else known
+                extra = cached.new_token_ids[i][-(want - known):] if want > known else []
+                req.output_token_ids.extend(int(t) for t in extra)
+        seqs: List[ScheduledSeq] = []
+        all_decode = True
+        order = [n.req_id for n in so.scheduled_new_reqs] + list(cached.req_ids)
+        for rid in order:
+            n = int(so.num_scheduled_tokens.get(rid, 0))
+            if n <= 0:
+                continue
+            req = self.requests[rid]
+            start = req.num_computed_tokens
+            samples = start + n >= req.num_tokens
+            seqs.append(ScheduledSeq(req, start, n, samples))
+            if not (n == 1 and samples and start > 0):
+                all_decode = False
+        out.seqs = seqs
+        out.num_tokens = sum(s.num_new_tokens for s in seqs)
+        out.kind = "idle" if not seqs else ("decode" if all_decode else "prefill")
+        return out
+
+    def commit(self, out, tokens: List[int]) -> List[List[int]]:
+        """Book the step's sampled tokens on the worker's request objects; returns vLLM's
+        ``sampled_token_ids`` (an empty list for a prompt chunk that does not end its prompt)."""
+        result: List[List[int]] = []
+        for seq, tok in zip(out.seqs, tokens):
+            req = seq.request
+            req.num_computed_tokens = seq.start + seq.num_new_tokens
+            if seq.samples:
+                req.output_token_ids.append(int(tok))
+                result.append([int(tok)])
+            else:
+                result.append([])
+        return result
+
+
+class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
+    def __init__(self, vllm_config, local_rank: int, rank: int, distributed_init_method: str,
+                 is_driver_worker: bool = False, **kwargs: Any) -> None:
+        super().__init__(vllm_config=vllm_config, local_rank=local_rank, rank=rank,
+                         distributed_init_method=distributed_init_method, is_driver_worker=is_driver_worker)
+        self.inner = None                      # this package's Worker
+        self.engine_config = None
+        self.translator = StepTranslator()
         self.ha_agent = None
-        self._profile_threshold = int(os.environ.get("PROFILER_TOKEN_THRESHOLD", "0"))
-        self._profile_stop_step = int(os.environ.get("PROFILER_STOP_STEP", "5"))
-        self._profile_steps_left = 0
+        self._kv_bytes_per_block = 0
+        self.steps = {"decode": 0, "prefill": 0}
 
     # ---------------------------------------------------------------- set-up
     def init_device(self) -> None:
-        super().init_device()
+        from vllm.platforms import current_platform
+        from .worker import Worker
+        device_type = "cuda" if current_platform.device_type == "cuda" and torch.cuda.is_available() else "cpu"
+        if device_type == "cuda":
+            os.environ.pop("NCCL_ASYNC_ERROR_HANDLING", None)
+            self.device = torch.device("cuda", self.local_rank)
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        # vLLM's own groups (executor message queues, process titles and any vLLM layer that
+        # asks for them) on the default process group; this package's groups are built on the
+        # same default group below
+        from vllm.v1.worker.gpu_worker import init_worker_distributed_environment
+        init_worker_distributed_environment(self.vllm_config, self.rank, self.distributed_init_method,
+                                            self.local_rank, current_platform.dist_backend)
+        self.engine_config = engine_config_from_vllm(self.vllm_config, device_type)
         try:
             from ..models import config_loader
             mc = self.vllm_config.model_config
             config_loader.load_model_extra_config(
-                mc.hf_config, enforce_eager=bool(getattr(mc, "enforce_eager", False)),
-                enable_chunked_prefill=bool(getattr(self.vllm_config.scheduler_config, "enable_chunked_prefill", False)),
-                enable_eplb=bool(getattr(self.vllm_config.parallel_config, "enable_eplb", False)),
+                mc.hf_config, enforce_eager=bool(mc.enforce_eager),
+                enable_chunked_prefill=bool(getattr(self.scheduler_config, "enable_chunked_prefill", True)),
+                enable_eplb=bool(getattr(self.parallel_config, "enable_eplb", False)),
                 additional_config=getattr(self.vllm_config, "additional_config", None))
             config_loader.apply_to_runtime()
         except Exception as e:                             # a missing plan is not fatal: defaults apply
-            logger.warning("deployment plan not applied: %s", e)
-        from ..ha.common import HAEnv
-        env = HAEnv.from_environ()
-        if env.use_ha:
-            from ..ha.monitor import HAWorkerAgent
-            self.ha_agent = HAWorkerAgent(env, getattr(self, "rank", 0), getattr(self, "local_rank", 0)).start()
+            logger.debug("deployment plan not applied: %s", e)
+        self.inner = Worker(self.engine_config, local_rank=self.local_rank, rank=self.rank,
+                            distributed_init_method=self.distributed_init_method,
+                            is_driver_worker=self.is_driver_worker)
+        self.inner.init_device()
+        self.model_runner = self.inner.model_runner
+        self.ha_agent = self.inner.ha_agent
+        logger.info("B200 worker rank %d on %s: own model runner (%s), tp=%d", self.rank, self.device,
+                    type(self.model_runner).__name__, self.engine_config.parallel.tensor_parallel_size)
+
+    def load_model(self, *, load_dummy_weights: bool = False) -> None:
+        if load_dummy_weights:
+            self.engine_config.load_format = "dummy"
+        self.inner.load_model()
+
+    def get_model(self):
+        return self.inner.get_model()
+
+    def get_supported_tasks(self):
+        return ("generate",)
+
+    def update_max_model_len(self, max_model_len: int) -> None:
+        self.model_config.max_model_len = max_model_len
+
+    # -------------------------------------------------------------- KV cache
+    def get_kv_cache_spec(self) -> Dict[str, Any]:
+        """One attention spec per layer, sized like the runner's own cache layout, so that vLLM's
+        block count times ``page_size_bytes`` is what the runner will allocate."""
+        from vllm.v1.kv_cache_interface import FullAttentionSpec, MLAAttentionSpec
+        spec = self.model_runner.get_kv_cache_spec()
+        mc = self.engine_config.model
+        self._kv_bytes_per_block = spec.bytes_per_block
+        per_layer = spec.bytes_per_block // spec.num_layers
+        esz = mc.dtype.itemsize
+        out: Dict[str, Any] = {}
+        for i in range(spec.num_layers):
+            name = f"model.layers.{i}.self_attn.attn"
+            if spec.kind == "gqa":
+                from ..parallel import state as pstate
+                hk = max(1, mc.num_kv_heads // pstate.tp_world_size())
+                s = FullAttentionSpec(block_size=spec.block_size, num_kv_heads=hk, head_size=mc.head_dim,
+                                      dtype=mc.dtype)
+            else:
+                width = per_layer // (spec.block_size * esz)      # latent + rope (+ index key) columns
+                s = MLAAttentionSpec(block_size=spec.block_size, num_kv_heads=1, head_size=width, dtype=mc.dtype)
+            if s.page_size_bytes != per_layer:
+                raise RuntimeError(f"KV spec of layer {i} is {s.page_size_bytes} bytes per block, the runner "
+                                   f"allocates {per_layer}")
+            out[name] = s
+        return out
+
+    def get_cache_block_size_bytes(self) -> int:
+        return self._kv_bytes_per_block or self.model_runner.get_kv_cache_spec().bytes_per_block
+
+    @torch.inference_mode()
+    def determine_available_memory(self) -> int:
+        """Bytes this rank can give to the KV cache: the requested share of the device minus what
+        is in use after loading and minus the activation peak of the largest prefill step."""
+        cc = self.cache_config
+        explicit = getattr(cc, "kv_cache_memory_bytes", None)
+        if explicit:
+            return int(explicit)
+        if self.device.type != "cuda":
+            spec = self.model_runner.get_kv_cache_spec()
+            want = self.engine_config.scheduler.max_num_seqs * self.engine_config.scheduler.max_model_len
+            return max(64, 2 * want // spec.block_size + 8) * spec.bytes_per_block
+        peak = self.model_runner.profile_run()
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * cc.gpu_memory_utilization) - (total - free) - peak
+        logger.info("KV cache budget %.2f GiB (activation peak %.2f GiB)", budget / 2**30, peak / 2**30)
+        if budget <= 0:
+            raise RuntimeError("no device memory left for the KV cache; lower max_num_batched_tokens or raise "
+                               "gpu_memory_utilization")
+        return budget
+
+    def initialize_from_config(self, kv_cache_config) -> None:
+        num_blocks = int(kv_cache_config.num_blocks)
+        self.cache_config.num_gpu_blocks = num_blocks
+        self.inner.initialize_from_config(num_blocks)
+        logger.info("KV cache: %d blocks of %d tokens", num_blocks, self.engine_config.cache.block_size)
+
+    def initialize_cache(self, num_gpu_blocks: int, num_cpu_blocks: int) -> None:
+        self.cache_config.num_gpu_blocks = num_gpu_blocks
+        self.cache_config.num_cpu_blocks = num_cpu_blocks
+
+    def compile_or_warm_up_model(self):
+        from vllm.v1.worker.worker_base import CompilationTimes
+        self.inner.compile_or_warm_up_model()
+        return CompilationTimes(language_model=float(self.model_runner.timings.get("capture_s", 0.0)), encoder=0.0)
+
+    # ---------------------------------------------------------------- running
+    @torch.inference_mode()
+    def execute_model(self, scheduler_output):
+        from vllm.v1.outputs import EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput
+        if getattr(scheduler_output, "has_structured_output_requests", False):
+            raise NotImplementedError("structured outputs are not supported by the B200 worker")
+        out = self.translator.translate(scheduler_output)
+        if out.kind == "idle":
+            self.inner.execute_model(out)                 # retire rows of finished requests
+            return EMPTY_MODEL_RUNNER_OUTPUT
+        tokens = self.inner.execute_model(out)
+        self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
+        sampled = self.translator.commit(out, tokens)
+        req_ids = [s.request.request_id for s in out.seqs]
+        return ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
+                                 sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
+                                 pooler_output=[])
+
+    def sample_tokens(self, grammar_output=None):
+        raise RuntimeError("execute_model of the B200 worker returns the step's output itself")
+
+    def take_draft_token_ids(self):
+        return None
+
+    def execute_dummy_batch(self) -> None:
+        self.inner.execute_dummy_batch()
+
+    def profile(self, is_start: bool = True, profile_prefix: Optional[str] = None) -> None:
+        self.inner.profile(is_start)
+
+    def check_health(self) -> None:
+        from .. import ops
+        if self.device is not None and self.device.type == "cuda":
+            ops.check_status(self.device)
+
+    # ------------------------------------------------------------------ LoRA
+    def add_lora(self, lora_request) -> bool:
+        raise NotImplementedError("LoRA is not supported by the B200 worker")
+
+    def remove_lora(self, lora_id: int) -> bool:
+        return False
+
+    def pin_lora(self, lora_id: int) -> bool:
+        return False
+
+    def list_loras(self) -> set:
+        return set()
 
     # -------------------------------------------------------------- sleep mode
     def sleep(self, level: int = 1) -> None:
-        from .mem_pool import B200MemAllocator
-        alloc = B200MemAllocator.get_instance()
-        released = alloc.sleep(offload_tags=("weights",) if level == 1 else ())
-        logger.info("sleep level %d: %.2f GiB released", level, released / 2**30)
+        self.inner.sleep(level)
 
     def wake_up(self, tags: Optional[list] = None) -> None:
-        from .mem_pool import B200MemAllocator
-        B200MemAllocator.get_instance().wake_up(tags)
-
-    def _maybe_pool(self, tag: str):
-        import contextlib
-        if getattr(self.vllm_config.model_config, "enable_sleep_mode", False):
-            from .mem_pool import B200MemAllocator
-            return B200MemAllocator.get_instance().use_memory_pool(tag=tag)
-        return contextlib.nullcontext()
-
-    def load_model(self, *args: Any, **kwargs: Any) -> None:
-        with self._maybe_pool("weights"):
-            super().load_model(*args, **kwargs)
-
-    def initialize_from_config(self, kv_cache_config) -> None:
-        with self._maybe_pool("kv_cache"):
-            super().initialize_from_config(kv_cache_config)
-
-    # ---------------------------------------------------------------- running
-    @token_recover_wrapper
-    def execute_model(self, scheduler_output, *args: Any, **kwargs: Any):
-        prof = getattr(self, "profiler", None)
-        if self._profile_threshold and prof is not None:
-            total = getattr(scheduler_output, "total_num_scheduled_tokens", 0)
-            if self._profile_steps_left == 0 and total == self._profile_threshold:
-                prof.start()
-                self._profile_steps_left = self._profile_stop_step
-        out = super().execute_model(scheduler_output, *args, **kwargs)
-        if self._profile_steps_left > 0:
-            self._profile_steps_left -= 1
-            if self._profile_steps_left == 0 and prof is not None:
-                prof.stop()
-        return out
+        self.inner.wake_up(tags)
 
     # token-recovery hooks (ha/monitor.py)
     def stop_device(self) -> None:
-        import torch
-
-        from ..parallel import state as pstate
-        try:
-            torch.cuda.synchronize()
-        except Exception as e:
-            logger.warning("synchronize during stop_device: %s", e)
-        pstate.abort_communicators()
+        self.inner.stop_device()
 
     def restart_device(self) -> None:
-        import torch
-        torch.cuda.empty_cache()
+        self.inner.restart_device()
 
     def reinit_process_group(self) -> None:
-        from ..parallel import state as pstate
-        pstate.reinit_communicators()
+        self.inner.reinit_process_group()
+
+    def shutdown(self) -> None:
+        if self.inner is not None:
+            try:
+                self.inner.shutdown()
+            except Exception as e:                         # pragma: no cover - best effort at exit
+                logger.warning("worker shutdown: %s", e)

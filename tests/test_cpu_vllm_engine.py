@@ -1,0 +1,74 @@
+"""The plugin under a real vLLM engine, without a GPU: vLLM's ``LLM`` (its scheduler, KV block
+manager and executor) drives this package's platform (CPU / gloo variant), worker and model
+runner.  Runs in a child process because vLLM resolves its platform once per process."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from omni_npu_b200 import compat
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.skipif(not compat.vllm_available(), reason="vLLM is not installed")
+
+
+def _child(*args: str, timeout: int = 900, model_dir: str = "") -> dict:
+    env = dict(os.environ)
+    env.pop("OMNI_B200_PLUGIN", None)
+    env.pop("OMNI_B200_TEST_MODEL_DIR", None)
+    if model_dir:
+        env["OMNI_B200_TEST_MODEL_DIR"] = model_dir
+    r = subprocess.run([sys.executable, str(ROOT / "tests" / "vllm_engine_child.py"), *args],
+                       capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert lines, f"child failed (rc={r.returncode}):\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}"
+    return json.loads(lines[-1][7:])
+
+
+def test_vllm_engine_runs_own_worker_and_runner_token_for_token():
+    res = _child("cpu")
+    assert res["platform"] == "B200CpuPlatform"
+    assert res["worker_cls"] == "omni_npu_b200.worker.vllm_worker.B200Worker" and res["worker"] == "B200Worker"
+    assert res["runner"] == "omni_npu_b200.worker.model_runner.ModelRunner"      # not vLLM's GPUModelRunner
+    assert res["async_scheduling"] is False
+    assert res["steps"]["prefill"] == 4 and res["steps"]["decode"] == 4 * 15
+    assert res["via_vllm"] == res["standalone"]
+    assert all(len(t) == 16 for t in res["via_vllm"])
+
+
+def test_vllm_engine_loads_a_safetensors_checkpoint_and_matches_plain_pytorch(tmp_path):
+    """The CPU plumbing configuration: tiny Llama, fp32, 4 prompts of 32 tokens, 16 greedy tokens,
+    through vLLM's engine and this package's platform / worker / runner, against a plain PyTorch
+    model reading the same checkpoint."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import reference_llama as refm
+    from safetensors.torch import save_file
+    from omni_npu_b200.config import tiny_llama
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=0)
+    save_file({k: v.contiguous() for k, v in weights.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": cfg.hidden_size,
+        "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_heads,
+        "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+        "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps,
+        "rope_theta": cfg.rope_theta, "max_position_embeddings": 2048, "torch_dtype": "float32",
+        "hidden_act": "silu", "tie_word_embeddings": False, "bos_token_id": 1, "eos_token_id": 2}))
+    res = _child("cpu", "1", "4", "64", model_dir=str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (32,), generator=g).tolist() for _ in range(4)]
+    want = [refm.greedy_generate(weights, cfg, p, 16) for p in prompts]
+    assert res["via_vllm"] == want
+    assert res["standalone"] == want
+
+
+def test_vllm_chunked_prefill_mixed_with_decode_gives_the_same_tokens():
+    # 4 running sequences and a 24-token budget: vLLM schedules prompt chunks together with
+    # decoding sequences; such steps run as variable-length prefill steps in the runner
+    res = _child("cpu", "1", "4", "24")
+    assert res["via_vllm"] == res["standalone"]
+    assert res["steps"]["prefill"] > 4
