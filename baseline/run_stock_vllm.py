@@ -29,7 +29,20 @@ import sys
 import tempfile
 import time
 
-os.environ["OMNI_B200_PLUGIN"] = "0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WITH_PLUGIN = "--with-plugin" in sys.argv
+if WITH_PLUGIN:
+    # the same vLLM entry point, but with this repository's platform plugin active: vLLM's engine
+    # core and scheduler drive this package's worker, model runner and kernels
+    sys.path.insert(0, ROOT)
+    from omni_npu_b200.plugin import write_entry_point_metadata
+    _meta = tempfile.mkdtemp(prefix="omni_b200_meta_")
+    write_entry_point_metadata(_meta)
+    sys.path.insert(0, _meta)
+    os.environ["PYTHONPATH"] = os.pathsep.join([ROOT, _meta, os.environ.get("PYTHONPATH", "")])
+    os.environ["OMNI_B200_PLUGIN"] = "1"
+else:
+    os.environ["OMNI_B200_PLUGIN"] = "0"
 os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
 os.environ.setdefault("VLLM_HOST_IP", "127.0.0.1")
@@ -81,6 +94,8 @@ def parse_args():
     ap.add_argument("--max-num-seqs", type=int, default=128)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--expert-parallel", action="store_true")
+    ap.add_argument("--with-plugin", action="store_true",
+                    help="activate this repository's vLLM platform plugin instead of vLLM's CUDA platform")
     ap.add_argument("--out", default=None, help="also write the JSON line to this file")
     return ap.parse_args()
 
@@ -140,7 +155,7 @@ def main() -> None:
         tpots += b
 
     out = {
-        "impl": "stock-vllm", "vllm_version": vllm.__version__, "torch": torch.__version__,
+        "impl": "vllm+omni_npu_b200-plugin" if WITH_PLUGIN else "stock-vllm", "vllm_version": vllm.__version__, "torch": torch.__version__,
         "metric": "output tok/s (whole box)", "value": round(tokens / wall, 1), "unit": "tok/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(wall * 1e3 / args.steps, 2),
@@ -152,6 +167,10 @@ def main() -> None:
                    "kv_block": args.block_size, "parallelism": f"tp{args.gpus}"
                    + ("+ep" if args.expert_parallel else ""), "note": note},
     }
+    if WITH_PLUGIN:
+        from vllm.platforms import current_platform
+        out["platform"] = type(current_platform).__name__
+        out["worker_cls"] = llm.llm_engine.vllm_config.parallel_config.worker_cls
     line = json.dumps(out)
     print(line, flush=True)
     if args.out:

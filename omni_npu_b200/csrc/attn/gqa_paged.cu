@@ -65,6 +65,8 @@ struct AttnParams {
   float* lse_part;            // [B, splits, 16]   (per kv head: index includes head)
   int* status;                // error word for bounded waits (may be null)
   int num_cache_blocks;       // blocks in the cache tensors (bounds the TMA view)
+  int* work_counter;          // persistent decode: [ticket, finished CTAs], zero at rest; null = strided items
+  int persistent;             // decode: 1 = persistent-CTA kernel when the problem allows it
 };
 
 template <int ROW_ELEMS, int ROWS, int THREADS>
@@ -892,6 +894,409 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   }
 }
 
+// ------------------------------------------------- decode, persistent CTAs
+// Same math and the same TMA-fed ring as gqa_decode_tma_kernel, but a CTA does not end with
+// its (sequence, kv head, split) item: the grid is sized to what is resident at once and every
+// CTA walks a list of items.  The producer warp runs ahead ACROSS items (its ring of K/V tiles,
+// the next item's query rows and block-table slice are in flight while the compute warps still
+// work on the current item), so the per-item prologue (query load, first-tile latency) and the
+// epilogue (merge of the four warps, output store) overlap with streaming, and no barrier or
+// stage is re-initialised between items.  Items are handed out through a device counter
+// (p.work_counter: ticket word + finished-CTA word, both zero at rest; the last CTA to finish
+// puts them back to zero, so graph replays need no host reset) or, without a counter, by
+// striding.  q_len rows x group heads <= 16 as in the other decode kernels.
+template <int D, int NSTAGES>
+struct DecodePersistCfg {
+  static constexpr int BN = 64;
+  static constexpr int STAGES = NSTAGES;
+  static constexpr int COMPUTE_THREADS = 128;
+  static constexpr int THREADS = 160;
+  static constexpr int HALVES = D / 64;
+  static constexpr int HALF_BYTES = BN * 128;
+  static constexpr int KV_BYTES = HALVES * HALF_BYTES;
+  static constexpr int BT_ENTRIES = 256;       // block-table slice of one item (per buffer)
+  static constexpr int META_INTS = 8;
+  // dynamic: 2 query buffers of rows x D bf16 and the merge buffer 4 x rows x (D + 4) fp32
+  static constexpr size_t smem(int rows) {
+    return 1024 + 2 * static_cast<size_t>(STAGES) * KV_BYTES + 2 * static_cast<size_t>(rows) * D * 2 +
+           4 * static_cast<size_t>(rows) * (D + 4) * 4 + 8 * static_cast<size_t>(rows) * 4 +
+           2 * BT_ENTRIES * 4 + 2 * META_INTS * 4 + (2 * STAGES + 4) * 8 + 64;
+  }
+};
+
+template <int D, int NSTAGES, int MINB>
+__global__ void __launch_bounds__(160, MINB)
+gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p,
+                          const int box_rows, const int total_items) {
+  using Cfg = DecodePersistCfg<D, NSTAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int G = p.Hq / p.Hk;
+  const int rows = G * p.q_len;
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
+  uint8_t* sQ = sV + Cfg::STAGES * Cfg::KV_BYTES;                       // [2][rows][D] bf16, linear
+  float* s_merge = reinterpret_cast<float*>(sQ + 2 * rows * D * 2);     // [4][rows][D + 4], then maxima and sums [2][4][rows]
+  int* s_bt = reinterpret_cast<int*>(s_merge + 4 * rows * (D + 4) + 8 * rows);   // [2][BT_ENTRIES]
+  int* s_meta = s_bt + 2 * Cfg::BT_ENTRIES;                             // [2][META_INTS]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_meta + 2 * Cfg::META_INTS);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* q_full = empty_bar + Cfg::STAGES;                           // [2]
+  uint64_t* q_empty = q_full + 2;                                       // [2]
+  int* s_abort = reinterpret_cast<int*>(q_empty + 2);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    mbar_init(&q_full[0], 1);
+    mbar_init(&q_full[1], 1);
+    mbar_init(&q_empty[0], 4);
+    mbar_init(&q_empty[1], 4);
+    *s_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  {
+    // rows of a partly filled tile that no copy ever wrote must hold finite values
+    uint4* z = reinterpret_cast<uint4*>(sK);
+    const int n16 = 2 * Cfg::STAGES * Cfg::KV_BYTES / 16;
+    for (int i = tid; i < n16; i += Cfg::THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  fence_proxy_async();
+  __syncthreads();
+  pdl_trigger();
+  pdl_wait();   // q, the cache rows of this step, lengths and block tables come from earlier kernels
+  volatile int* abort_flag = s_abort;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    int item = blockIdx.x;
+    uint32_t g = 0;            // tiles issued so far (ring position), identical in all lanes
+    for (int k = 0;; ++k) {
+      const int par = k & 1;
+      int next_item = item + static_cast<int>(gridDim.x);
+      if (p.work_counter != nullptr && lane == 0)
+        next_item = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
+      bool ok = true;
+      if (k >= 2 && lane == 0) ok = mbar_wait(&q_empty[par], static_cast<uint32_t>(((k >> 1) - 1) & 1));
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !*abort_flag;
+      if (!ok) {
+        if (lane == 0) {
+          if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      const bool valid = item < total_items;
+      int b = 0, kvh = 0, split = 0, kv_len = 0, t_begin = 0, n_tiles = 0, bt_first = 0, bt_last = 0;
+      const int* bt = p.block_tables;
+      if (valid) {
+        split = item % p.splits;
+        kvh = (item / p.splits) % p.Hk;
+        b = item / (p.splits * p.Hk);
+        kv_len = p.seq_lens[b];
+        bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+        const int n_tiles_all = (kv_len + Cfg::BN - 1) / Cfg::BN;
+        const int per = (n_tiles_all + p.splits - 1) / p.splits;
+        t_begin = split * per;
+        const int t_end = min(n_tiles_all, t_begin + per);
+        n_tiles = max(0, t_end - t_begin);
+        bt_first = (t_begin * Cfg::BN) / p.block_size;
+        bt_last = min(p.max_blocks, (min(kv_len, t_end * Cfg::BN) + p.block_size - 1) / p.block_size);
+      }
+      const bool bt_cached = (bt_last - bt_first) <= Cfg::BT_ENTRIES;
+      int* my_bt = s_bt + par * Cfg::BT_ENTRIES;
+      if (valid && bt_cached)
+        for (int i = bt_first + lane; i < bt_last; i += 32) my_bt[i - bt_first] = bt[i];
+      __syncwarp();
+      if (lane == 0) {
+        int* meta = s_meta + par * Cfg::META_INTS;
+        meta[0] = valid ? item : -1;
+        meta[1] = kv_len;
+        meta[2] = t_begin;
+        meta[3] = n_tiles;
+        if (!valid) {
+          mbar_arrive(&q_full[par]);
+        } else {
+          mbar_arrive_expect_tx(&q_full[par], static_cast<uint32_t>(rows * D * 2));
+          for (int qi = 0; qi < p.q_len; ++qi)
+            bulk_load_1d(sQ + (par * rows + qi * G) * D * 2,
+                         p.q + static_cast<long long>(b * p.q_len + qi) * p.q_stride +
+                             static_cast<long long>(kvh) * G * D,
+                         static_cast<uint32_t>(G * D * 2), &q_full[par]);
+          for (int it = 0; it < n_tiles; ++it, ++g) {
+            const int stage = static_cast<int>(g % Cfg::STAGES);
+            if (g >= Cfg::STAGES) {
+              const uint32_t parity = static_cast<uint32_t>(((g / Cfg::STAGES) - 1) & 1);
+              if (*abort_flag || !mbar_wait(&empty_bar[stage], parity)) {
+                if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
+                *abort_flag = 1;
+                break;
+              }
+            }
+            const int n0 = (t_begin + it) * Cfg::BN;
+            const int nvalid = min(Cfg::BN, kv_len - n0);
+            const int nboxes = (nvalid + box_rows - 1) / box_rows;
+            mbar_arrive_expect_tx(&full_bar[stage],
+                                  static_cast<uint32_t>(nboxes * box_rows * 128 * Cfg::HALVES * 2));
+            for (int j = 0; j < nboxes; ++j) {
+              const int key = n0 + j * box_rows;
+              const int bi = key / p.block_size;
+              const int blk = bt_cached ? my_bt[bi - bt_first] : bt[bi];
+              const int row = (blk * p.Hk + kvh) * p.block_size + key % p.block_size;
+#pragma unroll
+              for (int h = 0; h < Cfg::HALVES; ++h) {
+                const int dst = stage * Cfg::KV_BYTES + h * Cfg::HALF_BYTES + j * box_rows * 128;
+                tma_load_2d(sK + dst, &tm_k, &full_bar[stage], h * 64, row);
+                tma_load_2d(sV + dst, &tm_v, &full_bar[stage], h * 64, row);
+              }
+            }
+          }
+        }
+      }
+      g = __shfl_sync(0xffffffffu, g, 0);
+      if (!valid || *abort_flag) break;
+      item = __shfl_sync(0xffffffffu, next_item, 0);
+    }
+    if (lane == 0) {
+      if (*abort_flag) {
+        // bounded wait for the copies still in flight before the CTA retires
+        const uint32_t first = g > Cfg::STAGES ? g - Cfg::STAGES : 0;
+        for (uint32_t i = first; i < g; ++i)
+          mbar_wait(&full_bar[i % Cfg::STAGES], static_cast<uint32_t>((i / Cfg::STAGES) & 1));
+      }
+      if (p.work_counter != nullptr) {
+        // the last CTA to finish puts the ticket and finished-CTA words back to zero
+        __threadfence();
+        if (atomicAdd(p.work_counter + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+          p.work_counter[0] = 0;
+          p.work_counter[1] = 0;
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int r_a = lane >> 2;
+  uint32_t g = 0;
+  volatile int* s_dec = s_abort + 1;
+  float* m_buf = s_merge + 4 * rows * (D + 4);      // [4][rows] maxima, then [4][rows] sums
+  float* l_buf = m_buf + 4 * rows;
+  for (int k = 0;; ++k) {
+    const int par = k & 1;
+    bool ok = !*abort_flag && mbar_wait(&q_full[par], static_cast<uint32_t>((k >> 1) & 1));
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && lane == 0) {
+      if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+      *abort_flag = 1;
+    }
+    // The four compute warps leave the loop together or not at all: a warp that gave up on a wait
+    // must not exit while the others sit in a named barrier.  This barrier also frees the merge
+    // buffer of the previous item.
+    // The decision to leave is taken by one thread and read by all after the barrier (two slots:
+    // one per barrier of the loop body), so it is the same for every warp even when the flag
+    // changes while they cross the barrier.
+    if (tid == 0) s_dec[0] = *abort_flag;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (s_dec[0]) break;
+    const int* meta = s_meta + par * Cfg::META_INTS;
+    const int item = meta[0];
+    if (item < 0) break;
+    const int kv_len = meta[1], t_begin = meta[2], n_tiles = meta[3];
+    const int split = item % p.splits;
+    const int kvh = (item / p.splits) % p.Hk;
+    const int b = item / (p.splits * p.Hk);
+
+    // query fragments straight from the linear rows (rows beyond `rows` are zero)
+    uint32_t q_frag[D / 16][4];
+    {
+      const uint8_t* qb = sQ + par * rows * D * 2;
+      const int c0 = (lane & 3) * 2;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int col = ks * 16 + c0;
+        q_frag[ks][0] = r_a < rows ? *reinterpret_cast<const uint32_t*>(qb + (r_a * D + col) * 2) : 0u;
+        q_frag[ks][1] = r_a + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + ((r_a + 8) * D + col) * 2) : 0u;
+        q_frag[ks][2] = r_a < rows ? *reinterpret_cast<const uint32_t*>(qb + (r_a * D + col + 8) * 2) : 0u;
+        q_frag[ks][3] = r_a + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + ((r_a + 8) * D + col + 8) * 2) : 0u;
+      }
+    }
+    // the query buffer and the meta words of this parity may be rewritten from here on
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_empty[par]);
+
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+    float row_max[2] = {-INFINITY, -INFINITY};
+    float row_sum[2] = {0.f, 0.f};
+    int pos_r[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
+
+    for (int it = 0; it < n_tiles; ++it, ++g) {
+      const int stage = static_cast<int>(g % Cfg::STAGES);
+      bool okt = !*abort_flag && mbar_wait(&full_bar[stage], static_cast<uint32_t>((g / Cfg::STAGES) & 1));
+      okt = __all_sync(0xffffffffu, okt);
+      if (!okt) {
+        if (lane == 0) {
+          if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
+      const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
+      const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
+
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t kf[4];
+        const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int kchunk = ks * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
+        mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
+        mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
+      }
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
+          const int pos = pos_r[j >> 1];
+          bool keep = key <= pos && key < kv_len;
+          if (p.window > 0) keep = keep && (key > pos - p.window || key < p.sink);
+          const float v = keep ? s[i][j] * p.scale_log2 : -INFINITY;
+          s[i][j] = v;
+          tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+        }
+      }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float tm = quad_max(tile_max[r]);
+        const float new_max = fmaxf(row_max[r], tm);
+        corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+        row_max[r] = new_max;
+        row_sum[r] *= corr[r];
+      }
+      const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
+                              row_max[1] == -INFINITY ? 0.f : row_max[1]};
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float e = exp2f(s[i][j] - m_use[j >> 1]);
+          s[i][j] = e;
+          row_sum[j >> 1] += e;
+        }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= corr[0];
+        o_acc[i][1] *= corr[0];
+        o_acc[i][2] *= corr[1];
+        o_acc[i][3] *= corr[1];
+      }
+      uint32_t pa[4];
+      pa[0] = pack_bf16x2(s[0][0], s[0][1]);
+      pa[1] = pack_bf16x2(s[0][2], s[0][3]);
+      pa[2] = pack_bf16x2(s[1][0], s[1][1]);
+      pa[3] = pack_bf16x2(s[1][2], s[1][3]);
+#pragma unroll
+      for (int dt = 0; dt < D / 16; ++dt) {
+        uint32_t vf[4];
+        const int vrow = warp * 16 + (lane & 15);
+        const int vchunk = dt * 2 + (lane >> 4);
+        ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
+        mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
+        mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+
+    // ---- merge the four warps' partial results (rows < `rows` only) and store
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      row_sum[r] = quad_sum(row_sum[r]);
+      const int row = r_a + 8 * r;
+      if ((lane & 3) == 0 && row < rows) {
+        m_buf[warp * rows + row] = row_max[r];
+        l_buf[warp * rows + row] = row_sum[r];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + (lane & 3) * 2;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = r_a + 8 * r;
+        if (row < rows)
+          *reinterpret_cast<float2*>(s_merge + (static_cast<size_t>(warp) * rows + row) * (D + 4) + col) =
+              make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+      }
+    }
+    if (tid == 0) s_dec[1] = *abort_flag;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (s_dec[1]) break;
+    for (int idx = tid; idx < rows * (D / 4); idx += Cfg::COMPUTE_THREADS) {
+      const int row = idx / (D / 4);
+      const int c4 = (idx % (D / 4)) * 4;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, m_buf[w * rows + row]);
+      float l = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = m_buf[w * rows + row];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+        l += l_buf[w * rows + row] * f;
+        const float4 x =
+            *reinterpret_cast<const float4*>(s_merge + (static_cast<size_t>(w) * rows + row) * (D + 4) + c4);
+        acc.x += x.x * f;
+        acc.y += x.y * f;
+        acc.z += x.z * f;
+        acc.w += x.w * f;
+      }
+      const int qi = row / G, hh = kvh * G + row % G;
+      if (p.splits == 1) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint2 pk;
+        pk.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+        pk.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                                  static_cast<long long>(hh) * D + c4) = pk;
+        if (p.lse && c4 == 0)
+          p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+              l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+      } else {
+        const size_t pr = ((static_cast<size_t>(b) * p.Hk + kvh) * p.splits + split) * 16 + row;
+        *reinterpret_cast<float4*>(p.o_part + pr * D + c4) = acc;
+        if (c4 == 0) {
+          p.lse_part[pr * 2] = m;
+          p.lse_part[pr * 2 + 1] = l;
+        }
+      }
+    }
+  }
+}
+
 // Merge of split-KV partials: one warp per (sequence, kv head, row).
 template <int D>
 __global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnParams p, int B) {
@@ -982,8 +1387,64 @@ static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream
   return 0;
 }
 
+template <int D, int NSTAGES>
+static int launch_decode_persist(const AttnParams& p, int B, cudaStream_t stream) {
+  using Cfg = DecodePersistCfg<D, NSTAGES>;
+  auto kern = gqa_decode_persist_kernel<D, NSTAGES, 2>;
+  const int rows = (p.Hq / p.Hk) * p.q_len;
+  const size_t smem = Cfg::smem(rows);
+  static DeviceOnce once;
+  static int sms = 148;
+  int dev = 0;
+  if (once.needed(&dev)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(Cfg::smem(16))) != cudaSuccess)
+      return -20;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    once.mark(dev);
+  }
+  const int box_rows = p.block_size < 64 ? p.block_size : 64;
+  CUtensorMap tk, tv;
+  const uint64_t cache_rows = p.num_cache_blocks > 0
+                                  ? static_cast<uint64_t>(p.num_cache_blocks) * p.Hk * p.block_size
+                                  : (1ull << 31);
+  int r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.k_cache, cache_rows, D, D, box_rows, 64,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 2000;
+  r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.v_cache, cache_rows, D, D, box_rows, 64,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r - 3000;
+  const long long items = static_cast<long long>(B) * p.Hk * p.splits;
+  const int grid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);
+  if (launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), smem, stream, 1, tk, tv, p, box_rows,
+                 static_cast<int>(items)) != cudaSuccess)
+    return -21;
+  if (p.splits > 1) {
+    const long long warps = static_cast<long long>(B) * p.Hk * (p.Hq / p.Hk) * p.q_len;
+    gqa_decode_merge_kernel<D><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(p, B);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
+// Whether the persistent decode kernel can take this problem: TMA-compatible cache layout, at
+// most 16 query rows per kv head, and query rows that a bulk copy can fetch (16-byte aligned).
+static bool persist_ok(const AttnParams& p) {
+  const int rows = (p.Hq / p.Hk) * p.q_len;
+  const bool tma = (p.block_size % 8) == 0 && (p.block_size <= 64 ? (64 % p.block_size) == 0
+                                                                   : (p.block_size % 64) == 0) &&
+                   (reinterpret_cast<uintptr_t>(p.k_cache) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.v_cache) & 15) == 0;
+  return tma && rows <= 16 && (reinterpret_cast<uintptr_t>(p.q) & 15) == 0 && ((p.q_stride * 2) & 15) == 0;
+}
+
 template <int D>
 static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
+  if (p.persistent && persist_ok(p)) {
+    const int rows = (p.Hq / p.Hk) * p.q_len;
+    return rows <= 4 ? launch_decode_persist<D, 3>(p, B, stream) : launch_decode_persist<D, 2>(p, B, stream);
+  }
   const bool use_tma = (p.block_size % 8) == 0 && (p.block_size <= 64 ? (64 % p.block_size) == 0
                                                                        : (p.block_size % 64) == 0) &&
                        (reinterpret_cast<uintptr_t>(p.k_cache) & 15) == 0 &&
@@ -1076,12 +1537,32 @@ extern "C" size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits
   return static_cast<size_t>(B) * Hk * splits * 16 * (static_cast<size_t>(D) + 2) * sizeof(float);
 }
 
+// persistent != 0 selects the persistent-CTA kernel when the problem allows it (else the
+// one-CTA-per-item kernels run); work_counter: two ints, zero at rest, or null.
+extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                  float* lse, const int* block_tables, const int* seq_lens, int B,
+                                  int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
+                                  long long q_stride, long long out_stride, float scale, int window,
+                                  int splits, void* scratch, int num_cache_blocks, int* status,
+                                  int persistent, int* work_counter, cudaStream_t stream);
+
 extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                float* lse, const int* block_tables, const int* seq_lens, int B,
                                int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
                                long long q_stride, long long out_stride, float scale, int window,
                                int splits, void* scratch, int num_cache_blocks, int* status,
                                cudaStream_t stream) {
+  return b200_gqa_decode_ex(q, k_cache, v_cache, out, lse, block_tables, seq_lens, B, q_len, max_blocks,
+                            block_size, Hq, Hk, D, q_stride, out_stride, scale, window, splits, scratch,
+                            num_cache_blocks, status, 0, nullptr, stream);
+}
+
+extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                  float* lse, const int* block_tables, const int* seq_lens, int B,
+                                  int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
+                                  long long q_stride, long long out_stride, float scale, int window,
+                                  int splits, void* scratch, int num_cache_blocks, int* status,
+                                  int persistent, int* work_counter, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (Hq % Hk != 0 || (Hq / Hk) * q_len > 16 || q_len < 1) return -1;
   if (splits < 1) splits = 1;
@@ -1109,6 +1590,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.splits = splits;
   p.status = status;
   p.num_cache_blocks = num_cache_blocks;
+  p.persistent = persistent;
+  p.work_counter = work_counter;
   if (splits > 1) {
     p.o_part = static_cast<float*>(scratch);
     p.lse_part = p.o_part + static_cast<size_t>(B) * Hk * splits * 16 * D;

@@ -89,6 +89,11 @@ int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, voi
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
                     float scale, int window, int splits, void* scratch, int num_cache_blocks,
                     int* status, cudaStream_t stream);
+int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
+                       const int* block_tables, const int* seq_lens, int B, int q_len, int max_blocks,
+                       int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
+                       float scale, int window, int splits, void* scratch, int num_cache_blocks, int* status,
+                       int persistent, int* work_counter, cudaStream_t stream);
 int b200_kv_p2p_copy(const void* tensors, int num_tensors, const int* src_blocks, const int* dst_blocks,
                      int num_pairs, long long max_block_bytes, cudaStream_t stream);
 size_t b200_mla_decode_scratch_bytes(int total_tokens, int N, int splits);
@@ -671,7 +676,8 @@ int64_t gqa_decode_scratch_bytes(int64_t B, int64_t Hk, int64_t D, int64_t split
 Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& block_tables, const Tensor& seq_lens, int64_t num_seqs,
                   int64_t q_len, int64_t num_q_heads, double scale, int64_t window, int64_t splits,
-                  const c10::optional<Tensor>& scratch, const Tensor& status) {
+                  const c10::optional<Tensor>& scratch, const Tensor& status, bool persistent,
+                  const c10::optional<Tensor>& work_counter) {
   CHECK_CUDA_BF16(q);
   CHECK_CUDA_BF16(k_cache);
   CHECK_CUDA_BF16(v_cache);
@@ -691,11 +697,17 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                 "gqa_decode: scratch too small");
     sp = scratch->data_ptr();
   }
-  check(b200_gqa_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                        nullptr, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
-                        (int)num_seqs, (int)q_len, (int)block_tables.size(1), bs, Hq, Hk, D,
-                        q.stride(0), out.stride(0), (float)scale, (int)window, (int)splits, sp,
-                        (int)k_cache.size(0), status.data_ptr<int>(), cur_stream()),
+  int* wc = nullptr;
+  if (work_counter.has_value()) {
+    CHECK_I32((*work_counter));
+    TORCH_CHECK(work_counter->numel() >= 2, "gqa_decode: work_counter needs two ints");
+    wc = work_counter->data_ptr<int>();
+  }
+  check(b200_gqa_decode_ex(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                           nullptr, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
+                           (int)num_seqs, (int)q_len, (int)block_tables.size(1), bs, Hq, Hk, D,
+                           q.stride(0), out.stride(0), (float)scale, (int)window, (int)splits, sp,
+                           (int)k_cache.size(0), status.data_ptr<int>(), persistent ? 1 : 0, wc, cur_stream()),
         "gqa_decode");
   return out;
 }

@@ -111,6 +111,7 @@ class _DeviceState:
         self.gemm_ws = {}
         self.counters = {}
         self.attn_scratch = {}
+        self.work_counters = {}
         self.plans = {}
 
     def gemm_workspace(self, stream_id: int, nbytes: int, ncounters: int):
@@ -123,6 +124,16 @@ class _DeviceState:
             cnt = torch.zeros(max(ncounters, 65536), dtype=torch.int32, device=self.device)
             self.counters[stream_id] = cnt
         return ws, cnt
+
+    def work_counter(self, stream_id: int):
+        """Two zeroed ints per stream for kernels that hand out work items through a device
+        counter; the kernel that uses them puts them back to zero before it ends."""
+        wc = self.work_counters.get(stream_id)
+        if wc is None:
+            with torch.inference_mode(False):
+                wc = torch.zeros(2, dtype=torch.int32, device=self.device)
+            self.work_counters[stream_id] = wc
+        return wc
 
     def decode_scratch(self, stream_id: int, nbytes: int):
         sc = self.attn_scratch.get(stream_id)
@@ -473,21 +484,46 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_seq_len: int, sms: int =
     return max(1, min(want, cap, 16))
 
 
+def decode_splits_persistent(num_seqs: int, num_kv_heads: int, max_seq_len: int, sms: int = 148) -> int:
+    """Split-KV factor for the persistent decode kernel (two CTAs per SM walk the items
+    sequence x kv head x split): the smallest factor whose item count fills the resident CTAs to
+    within 7 % of a whole number of rounds, with at least 256 keys per split; when none gets that
+    close, the one that comes closest."""
+    slots = 2 * sms
+    base = max(1, num_seqs * num_kv_heads)
+    cap = max(1, min(16, max_seq_len // 256))
+    best, best_eff = 1, 0.0
+    for s in range(1, cap + 1):
+        per = base * s / slots
+        eff = per / max(1, -(-base * s // slots))
+        if eff >= 0.93:
+            return s
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best
+
+
+# OMNI_B200_DECODE_PERSISTENT=0 keeps the one-CTA-per-item decode kernels
+DECODE_PERSISTENT = os.environ.get("OMNI_B200_DECODE_PERSISTENT", "1") != "0"
+
+
 def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                block_tables: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, num_q_heads: int,
                scale: float, q_len: int = 1, window: int = 0, splits: int = 0,
-               max_seq_len: int = 0, sink: int = 0) -> torch.Tensor:
+               max_seq_len: int = 0, sink: int = 0, persistent: Optional[bool] = None) -> torch.Tensor:
     """Decode attention: q_len (usually 1) new tokens per sequence, sequences laid
-    out back to back in q."""
+    out back to back in q.  ``persistent`` (default: on) runs the persistent-CTA kernel, which
+    hands out (sequence, kv head, split) items through a device counter."""
     if not q.is_cuda:
         cu = torch.arange(0, (num_seqs + 1) * q_len, q_len, dtype=torch.int32, device=q.device)
         return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu,
                                    seq_lens[:num_seqs], num_q_heads, scale, True, window, False, sink)
     C = _C()
     hk, d = k_cache.shape[1], k_cache.shape[3]
+    persistent = DECODE_PERSISTENT if persistent is None else persistent
     if splits <= 0:
         bound = max_seq_len if max_seq_len > 0 else block_tables.shape[1] * k_cache.shape[2]
-        splits = decode_splits(num_seqs, hk, bound)
+        splits = (decode_splits_persistent if persistent else decode_splits)(num_seqs, hk, bound)
     scratch = None
     st = device_state(q.device)
     if splits > 1:
@@ -495,7 +531,8 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
     _count(2 if splits > 1 else 1)
     return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
-                        scale, _pack_window(window, sink), splits, scratch, st.status)
+                        scale, _pack_window(window, sink), splits, scratch, st.status, persistent,
+                        st.work_counter(torch.cuda.current_stream(q.device).cuda_stream) if persistent else None)
 
 
 # -------------------------------------------------------------------- sampling

@@ -92,6 +92,8 @@ class InputBatch:
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.capacity.total, dtype=torch.int32, device=device)
         self.h2d_bytes_last = 0
+        self._upload_event = None
+        self._upload_pending = False
 
     # ------------------------------------------------------------------ rows
     def add_request(self, req: Request) -> int:
@@ -159,9 +161,25 @@ class InputBatch:
         }
 
     def upload(self, lay: StepLayout) -> None:
-        """One H2D copy of the staged step (pinned host -> device)."""
+        """One H2D copy of the staged step (pinned host -> device).  The copy is asynchronous:
+        the staging buffer must not be rewritten until it has run (``wait_upload``)."""
         self.dev[: lay.total].copy_(self.host[: lay.total], non_blocking=True)
         self.h2d_bytes_last = lay.total * 4
+        if self.device.type == "cuda":
+            if self._upload_event is None:
+                self._upload_event = torch.cuda.Event()
+            self._upload_event.record()
+            self._upload_pending = True
+
+    def wait_upload(self) -> None:
+        """Block until the last ``upload`` has read the staging buffer.  Every ``stage_*`` call
+        starts with it: with a long queue ahead of the copy (for instance the zero-fill of a large
+        KV cache right before the warm-up steps) the host would otherwise overwrite the buffer
+        before the device has copied it, and the earlier step would run on the later step's
+        inputs."""
+        if self._upload_pending:
+            self._upload_event.synchronize()
+            self._upload_pending = False
 
     def _fill_sampling(self, lay: StepLayout, rows: np.ndarray, n: int) -> None:
         h = self.host_np
@@ -177,6 +195,7 @@ class InputBatch:
     def stage_decode(self, lay: StepLayout, reqs: Sequence[Request], q_len: int = 1) -> np.ndarray:
         """Stage a decode step for ``reqs`` (one new token each) padded to lay.S
         sequences.  Returns the row indices used."""
+        self.wait_upload()
         n = len(reqs)
         bs = self.block_size
         h = self.host_np
@@ -212,6 +231,7 @@ class InputBatch:
         """Stage a verification step: every sequence feeds its last token followed by its
         draft tokens (ScheduledSeq.spec_token_ids) at positions start .. start + k.
         Returns (rows, max_q_len)."""
+        self.wait_upload()
         h = self.host_np
         bs = self.block_size
         n = len(seqs)
@@ -252,6 +272,7 @@ class InputBatch:
     def stage_prefill(self, lay: StepLayout, seqs) -> Tuple[np.ndarray, int]:
         """Stage a prefill step.  ``seqs`` are ScheduledSeq (request, start,
         num_new_tokens).  Returns (rows, max_q_len)."""
+        self.wait_upload()
         h = self.host_np
         bs = self.block_size
         n = len(seqs)

@@ -473,14 +473,9 @@ class ModelRunner:
         padded = self._pad_decode_size(n) if self.graphs else None
         S = padded or n
         cuda = self.device.type == "cuda"
-        if cuda and getattr(self, "_upload_event", None) is not None:
-            self._upload_event.synchronize()          # the staging buffer is still being read by the last H2D copy
         lay = ib.layout_for(S, S)
-        ib.stage_decode(lay, reqs)
+        ib.stage_decode(lay, reqs)        # waits until the last H2D copy has read the staging buffer
         ib.upload(lay)
-        if cuda:
-            self._upload_event = torch.cuda.Event()
-            self._upload_event.record()
         views = ib.views(lay, ib.dev)
         if prev is not None:
             where = {id(r): i for i, r in enumerate(prev["reqs"])}
@@ -561,6 +556,7 @@ class ModelRunner:
             per = T // n_seq
             T = per * n_seq
             lay = ib.layout_for(T, n_seq)
+            ib.wait_upload()
             h = ib.host_np
             h[lay.ids: lay.ids + T] = 0
             pos = np.tile(np.arange(per, dtype=np.int32), n_seq)

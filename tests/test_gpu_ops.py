@@ -282,15 +282,35 @@ def test_gqa_prefill_window_and_mla_dims():
     _close(got, want, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("persistent", [True, False])
 @pytest.mark.parametrize("splits", [1, 2, 5])
-@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (4, 2, 64), (16, 1, 128)])
-def test_gqa_decode(splits, hq, hk, d):
+@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (4, 2, 64), (16, 1, 128), (16, 2, 128)])
+def test_gqa_decode(splits, hq, hk, d, persistent):
     seq_lens = [1, 17, 64, 65, 1000, 333]
     q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 6, hq, hk, d, 16, seed=7)
     want = ref.paged_attention(q, kc, vc, bt, cu, sl, hq, d ** -0.5, True, 0)
     got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 6, hq, d ** -0.5,
-                         splits=splits)
+                         splits=splits, persistent=persistent)
     _close(got, want, 2e-2, 2e-2)
+
+
+def test_gqa_decode_persistent_more_items_than_ctas_twice():
+    """More (sequence, kv head, split) items than resident CTAs: every CTA walks several items
+    handed out by the device counter; the counter is back at zero afterwards, so a second call
+    (as a graph replay would make it) gives the same result."""
+    torch.manual_seed(21)
+    seq_lens = [int(x) for x in torch.randint(1, 700, (96,))]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 96, 32, 8, 128, 16, seed=22)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 32, 128 ** -0.5, True, 0)
+    args = (q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 96, 32, 128 ** -0.5)
+    for splits in (1, 2):
+        for _ in range(2):
+            got = ops.gqa_decode(*args, splits=splits, persistent=True)
+            _close(got, want, 2e-2, 2e-2)
+    wc = ops.device_state(DEV).work_counter(torch.cuda.current_stream().cuda_stream)
+    assert wc.tolist() == [0, 0]
+    assert ops.decode_splits_persistent(128, 8, 1296) == 2 and ops.decode_splits_persistent(128, 4, 1296) == 4
+    assert ops.decode_splits_persistent(1, 8, 8192) > 8          # few items: split to fill the SMs
 
 
 def test_gqa_decode_multi_token():

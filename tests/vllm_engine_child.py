@@ -55,7 +55,7 @@ def main() -> None:
     llm = LLM(model=d, load_format=load_format, skip_tokenizer_init=True, dtype=cfg["torch_dtype"],
               max_model_len=256, max_num_seqs=seqs, max_num_batched_tokens=budget, block_size=16,
               enforce_eager=fp32, seed=0, enable_prefix_caching=False, tensor_parallel_size=tp,
-              gpu_memory_utilization=0.3)
+              gpu_memory_utilization=0.3, **({} if fp32 else {"kv_cache_memory_bytes": 1 << 30}))
     vcfg = llm.llm_engine.vllm_config
     outs = llm.generate([{"prompt_token_ids": p} for p in prompts],
                         SamplingParams(max_tokens=n_out, temperature=0.0, ignore_eos=True, detokenize=False),
