@@ -161,11 +161,14 @@ def bench_attn(args):
         bt = torch.arange(1, nblk, device="cuda", dtype=torch.int32).view(b, -1)
         sl = torch.full((b,), ctx, device="cuda", dtype=torch.int32)
         for splits in ((0,) if args.splits == 0 else (args.splits,)):
-            t = time_fn(lambda: ops.gqa_decode(q, kc, vc, bt, sl, b, hq, d ** -0.5, splits=splits,
-                                               max_seq_len=ctx), iters=args.iters)
             by = 2.0 * b * ctx * hk * d * 2
-            print(f"decode  B={b:4d} ctx={ctx:6d} splits={splits}: {t*1e3:8.1f} us  {by/t/1e6:7.0f} GB/s "
-                  f"frac {by/hbm/(t/1e3):.2f}")
+            for persistent in (True, False):
+                used = splits or (ops.decode_splits_persistent if persistent else ops.decode_splits)(b, hk, ctx)
+                t = time_fn(lambda: ops.gqa_decode(q, kc, vc, bt, sl, b, hq, d ** -0.5, splits=splits,
+                                                   max_seq_len=ctx, persistent=persistent), iters=args.iters)
+                kind = "persistent CTAs" if persistent else "one CTA per item"
+                print(f"decode  B={b:4d} ctx={ctx:6d} splits={used:2d} {kind}: {t*1e3:8.1f} us  "
+                      f"{by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
     for b, s in prefill_cases:
         nblk = b * (s // bs) + 1
         kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)

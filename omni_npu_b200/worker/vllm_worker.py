@@ -319,13 +319,42 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         if out.kind == "idle":
             self.inner.execute_model(out)                 # retire rows of finished requests
             return EMPTY_MODEL_RUNNER_OUTPUT
-        tokens = self.inner.execute_model(out)
-        self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
+        tokens = self._run(out)
         sampled = self.translator.commit(out, tokens)
         req_ids = [s.request.request_id for s in out.seqs]
         return ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
                                  sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
                                  pooler_output=[])
+
+    # a mixed step is split when it carries at least this many decoding sequences
+    MIXED_SPLIT_MIN_DECODES = int(os.environ.get("OMNI_B200_MIXED_SPLIT_MIN", "8"))
+
+    def _run(self, out) -> List[int]:
+        """Run one translated step.  vLLM's chunked prefill schedules prompt chunks together with
+        decoding sequences.  One-token rows are a poor fit for the variable-length prefill
+        attention (a 128-row query tile per sequence and head, the KV of a group read once per
+        query head), so a mixed step with enough decoding sequences runs as two launches: the
+        decoding sequences through the decode path (CUDA graph, split-KV attention), the prompt
+        chunks through the prefill path."""
+        from ..engine.scheduler import SchedulerOutput
+        if out.kind == "prefill":
+            dec = [i for i, s in enumerate(out.seqs) if s.num_new_tokens == 1 and s.samples and s.start > 0]
+            if self.MIXED_SPLIT_MIN_DECODES <= len(dec) < len(out.seqs):
+                pre = [i for i in range(len(out.seqs)) if i not in set(dec)]
+                first = SchedulerOutput(kind="decode", seqs=[out.seqs[i] for i in dec], num_tokens=len(dec),
+                                        preempted=out.preempted, finished_req_ids=out.finished_req_ids,
+                                        step_index=out.step_index)
+                second = SchedulerOutput(kind="prefill", seqs=[out.seqs[i] for i in pre],
+                                         num_tokens=sum(out.seqs[i].num_new_tokens for i in pre),
+                                         step_index=out.step_index)
+                tokens: List[int] = [0] * len(out.seqs)
+                for idx, part in ((dec, first), (pre, second)):
+                    for i, t in zip(idx, self.inner.execute_model(part)):
+                        tokens[i] = t
+                self.steps["mixed"] = self.steps.get("mixed", 0) + 1
+                return tokens
+        self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
+        return self.inner.execute_model(out)
 
     def sample_tokens(self, grammar_output=None):
         raise RuntimeError("execute_model of the B200 worker returns the step's output itself")

@@ -16,8 +16,9 @@ ROOT = Path(__file__).resolve().parent.parent
 pytestmark = pytest.mark.skipif(not compat.vllm_available(), reason="vLLM is not installed")
 
 
-def _child(*args: str, timeout: int = 900, model_dir: str = "") -> dict:
+def _child(*args: str, timeout: int = 900, model_dir: str = "", extra_env=None) -> dict:
     env = dict(os.environ)
+    env.update(extra_env or {})
     env.pop("OMNI_B200_PLUGIN", None)
     env.pop("OMNI_B200_TEST_MODEL_DIR", None)
     if model_dir:
@@ -72,3 +73,7 @@ def test_vllm_chunked_prefill_mixed_with_decode_gives_the_same_tokens():
     res = _child("cpu", "1", "4", "24")
     assert res["via_vllm"] == res["standalone"]
     assert res["steps"]["prefill"] > 4
+    # the same schedule with mixed steps split into a decode launch and a prefill launch
+    res = _child("cpu", "1", "4", "24", extra_env={"OMNI_B200_MIXED_SPLIT_MIN": "1"})
+    assert res["via_vllm"] == res["standalone"]
+    assert res["steps"].get("mixed", 0) > 0

@@ -307,7 +307,7 @@ def test_gqa_decode_persistent_more_items_than_ctas_twice():
         for _ in range(2):
             got = ops.gqa_decode(*args, splits=splits, persistent=True)
             _close(got, want, 2e-2, 2e-2)
-    wc = ops.device_state(DEV).work_counter(torch.cuda.current_stream().cuda_stream)
+    wc = ops.device_state(torch.device("cuda", 0)).work_counter(torch.cuda.current_stream().cuda_stream)
     assert wc.tolist() == [0, 0]
     assert ops.decode_splits_persistent(128, 8, 1296) == 2 and ops.decode_splits_persistent(128, 4, 1296) == 4
     assert ops.decode_splits_persistent(1, 8, 8192) > 8          # few items: split to fill the SMs
