@@ -201,6 +201,8 @@ def run_ours(args) -> None:
         one_pass()
         runner.drain_step_events()
 
+    runner.step_ms_by_kind.clear()
+    runner.step_count_by_kind.clear()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -261,6 +263,8 @@ def run_ours(args) -> None:
                              "(16 GB / N) and the KV cache, far above the 126 MB L2",
                 "engine_steps_per_pass": engine_steps // max(1, args.steps),
             },
+            "device_ms_by_step_kind": {k: round(v / args.steps, 1) for k, v in runner.step_ms_by_kind.items()},
+            "steps_by_kind": {k: v // args.steps for k, v in runner.step_count_by_kind.items()},
             "e2e": {
                 "value": round(e2e, 1), "unit": "tok/s",
                 "wall_ms_per_step": round(wall * 1e3 / args.steps, 2),

@@ -89,6 +89,11 @@ int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, voi
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
                     float scale, int window, int splits, void* scratch, int num_cache_blocks,
                     int* status, cudaStream_t stream);
+int b200_gqa_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
+                        const int* block_tables, const int* cu_q, const int* seq_lens, int B, int max_q_len,
+                        int max_blocks, int block_size, int Hq, int Hk, int Dqk, int Dv, long long q_stride,
+                        long long out_stride, float scale, int causal, int window, long long total_q_rows,
+                        int num_cache_blocks, int* status, cudaStream_t stream);
 int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                        const int* block_tables, const int* seq_lens, int B, int q_len, int max_blocks,
                        int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
@@ -644,7 +649,8 @@ std::tuple<Tensor, Tensor> gqa_prefill(const Tensor& q, const Tensor& k_cache, c
                                        const Tensor& block_tables, const Tensor& cu_q,
                                        const Tensor& seq_lens, int64_t num_seqs, int64_t max_q_len,
                                        int64_t num_q_heads, double scale, bool causal,
-                                       int64_t window, bool return_lse) {
+                                       int64_t window, bool return_lse, bool use_tcgen05,
+                                       const c10::optional<Tensor>& status) {
   CHECK_CUDA_BF16(q);
   CHECK_CUDA_BF16(k_cache);
   CHECK_CUDA_BF16(v_cache);
@@ -659,6 +665,17 @@ std::tuple<Tensor, Tensor> gqa_prefill(const Tensor& q, const Tensor& k_cache, c
   c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({T, (int64_t)Hq * Dv}, q.options());
   Tensor lse = return_lse ? torch::empty({T, Hq}, q.options().dtype(at::kFloat)) : Tensor();
+  if (use_tcgen05) {
+    // head size 128 without a sliding window: both products on tcgen05 with TMEM accumulators
+    const int rc = b200_gqa_prefill_tc(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        return_lse ? lse.data_ptr<float>() : nullptr, block_tables.data_ptr<int>(), cu_q.data_ptr<int>(),
+        seq_lens.data_ptr<int>(), (int)num_seqs, (int)max_q_len, (int)block_tables.size(1), bs, Hq, Hk, Dqk, Dv,
+        q.stride(0), out.stride(0), (float)scale, causal ? 1 : 0, (int)window, (long long)T, (int)k_cache.size(0),
+        status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream());
+    if (rc == 0) return {out, lse};
+    TORCH_CHECK(rc == 1, "omni_b200::gqa_prefill (tcgen05) failed with code ", rc);
+  }
   check(b200_gqa_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                          return_lse ? lse.data_ptr<float>() : nullptr, block_tables.data_ptr<int>(),
                          cu_q.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)num_seqs,

@@ -177,9 +177,13 @@ def bench_attn(args):
         bt = torch.arange(1, nblk, device="cuda", dtype=torch.int32).view(b, -1)
         sl = torch.full((b,), s, device="cuda", dtype=torch.int32)
         cu = torch.arange(0, (b + 1) * s, s, device="cuda", dtype=torch.int32)
-        t = time_fn(lambda: ops.gqa_prefill(q, kc, vc, bt, cu, sl, b, s, hq, d ** -0.5), iters=args.iters)
         fl = 4.0 * b * hq * s * s * d / 2
-        print(f"prefill B={b:3d} S={s:6d}: {t*1e3:9.1f} us  {fl/t/1e9:7.1f} TFLOP/s  frac {fl/flops_peak/(t/1e3):.2f}")
+        for tc in (True, False):
+            t = time_fn(lambda: ops.gqa_prefill(q, kc, vc, bt, cu, sl, b, s, hq, d ** -0.5, tcgen05=tc),
+                        iters=args.iters)
+            kind = "tcgen05 + TMEM" if tc else "mma.sync      "
+            print(f"prefill B={b:3d} S={s:6d} {kind}: {t*1e3:9.1f} us  {fl/t/1e9:7.1f} TFLOP/s  "
+                  f"frac {fl/flops_peak/(t/1e3):.2f}")
     ops.check_status()
 
 

@@ -147,8 +147,17 @@ class SymmetricMemory:
         return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0
                 and x.numel() > 0)
 
+    # Largest message the peer-memory all-reduce kernels take; larger ones go to NCCL.  Chosen by
+    # measurement, not by what fits the buffer: the push / one-shot kernels win for small messages
+    # (1 MiB on 2 GPUs: 23.7 us against NCCL's 25.8 us), the two-shot kernel loses for large ones
+    # (64 MiB on 2 GPUs: 424 us against 154 us; NCCL reduces inside the switch).
+    # OMNI_B200_SYMM_AR_MAX_BYTES overrides it.
+    ALL_REDUCE_MAX_BYTES = int(os.environ.get("OMNI_B200_SYMM_AR_MAX_BYTES", str(2 << 20)))
+
     def can_all_reduce(self, x: torch.Tensor) -> bool:
-        return self._ok(x) and x.numel() * 2 * (1 + 1.0 / self.world) + 64 <= self.half_bytes
+        nbytes = x.numel() * 2
+        return (self._ok(x) and nbytes <= self.ALL_REDUCE_MAX_BYTES
+                and nbytes * (1 + 1.0 / self.world) + 64 <= self.half_bytes)
 
     # --------------------------------------------------------------- collectives
     def _ll(self, x: torch.Tensor, out: torch.Tensor, residual, weight, h: int, eps: float) -> None:

@@ -83,7 +83,9 @@ class ModelRunner:
         self.timings: Dict[str, float] = {}
         # optional device-side timing of every step (CUDA events around the kernels)
         self.enable_step_events = False
-        self._step_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
+        self._step_events: List[Tuple[torch.cuda.Event, torch.cuda.Event, str]] = []
+        self.step_ms_by_kind: Dict[str, float] = {}      # device time per kind of step, filled by drain_step_events
+        self.step_count_by_kind: Dict[str, int] = {}
 
     # ------------------------------------------------------------------ model
     def load_model(self) -> None:
@@ -401,7 +403,7 @@ class ModelRunner:
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
             packed = self._forward_and_verify(views, md, out.seqs)
             self.step_counter += max_q
-            self._event_stop(ev)
+            self._event_stop(ev, "spec_decode")
             host = packed.cpu() if self.device.type != "cuda" else self._to_host(packed)
             self.d2h_bytes_last = packed.numel() * 4
             rows = host.tolist()
@@ -435,7 +437,7 @@ class ModelRunner:
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
             sampled = self._forward_and_sample(views, md, n)
         self.step_counter += 1
-        self._event_stop(ev)
+        self._event_stop(ev, out.kind)
         # D2H of the step's result (pinned), then the host learns the tokens
         if self.mtp is not None:
             host = self.sampled_host2[:n]
@@ -493,7 +495,7 @@ class ModelRunner:
             md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len, 1, n, n)
             sampled = self._forward_and_sample(views, md, S)
         self.step_counter += 1
-        self._event_stop(ev)
+        self._event_stop(ev, "decode")
         parity = getattr(self, "_launch_parity", 0)
         self._launch_parity = parity ^ 1
         if not hasattr(self, "_sampled_hosts"):
@@ -527,17 +529,22 @@ class ModelRunner:
         e0.record()
         return (e0, e1)
 
-    def _event_stop(self, ev) -> None:
+    def _event_stop(self, ev, kind: str = "prefill") -> None:
         if ev is not None:
             ev[1].record()
-            self._step_events.append(ev)
+            self._step_events.append((ev[0], ev[1], kind))
 
     def drain_step_events(self) -> float:
         """Sum (ms) of the device time of the steps recorded since the last call."""
         if not self._step_events:
             return 0.0
         torch.cuda.synchronize(self.device)
-        total = sum(a.elapsed_time(b) for a, b in self._step_events)
+        total = 0.0
+        for a, b, kind in self._step_events:
+            ms = a.elapsed_time(b)
+            total += ms
+            self.step_ms_by_kind[kind] = self.step_ms_by_kind.get(kind, 0.0) + ms
+            self.step_count_by_kind[kind] = self.step_count_by_kind.get(kind, 0) + 1
         self._step_events = []
         return total
 

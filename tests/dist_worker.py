@@ -14,9 +14,9 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import torch  # noqa: E402
 
 
-def setup(rank, world, port, device_kind):
+def setup(rank, world, port, device_kind, nccl_nvls="0"):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
-                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE=nccl_nvls)
     from omni_npu_b200.parallel import state
     if device_kind == "cuda":
         torch.cuda.set_device(rank)
@@ -306,6 +306,100 @@ def task_symm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_nvls(rank, world, port, workdir, device_kind):
+    """All-reduce through the switch (multimem) against NCCL: values, the fused residual + RMSNorm
+    tail, repeated calls (alternating halves), and a size sweep timed inside CUDA graphs against the
+    peer-store kernels and NCCL (NCCL left at its defaults, NVLS included, for the comparison)."""
+    dev, state = setup(rank, world, port, "cuda", nccl_nvls="1")
+    state.init_model_parallel(tp=world, device=dev)
+    import torch.distributed as dist
+    from omni_npu_b200 import ops
+    from omni_npu_b200.parallel.nvls import NvlsAllReduce
+    from omni_npu_b200.parallel.symm_mem import attach_symmetric_memory
+    g = state.get_tp_group()
+    res = {"max_err": {}, "us": {}}
+    try:
+        nv = NvlsAllReduce(g, dev, max_bytes=64 << 20)
+    except Exception as e:
+        res["unsupported"] = f"{type(e).__name__}: {e}"
+        json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+        state.destroy_distributed()
+        return
+    symm = attach_symmetric_memory(g, dev, half_bytes=96 << 20)
+    torch.manual_seed(200 + rank)
+    for name, shape, mode in (("one_tiny", (1, 4096), 1), ("one", (128, 4096), 1), ("one_odd", (7, 1032), 1),
+                              ("two", (128, 4096), 2), ("two_odd", (37, 1032), 2), ("two_large", (4096, 4096), 2),
+                              ("auto_large", (8192, 4096), 0), ("one_again", (128, 4096), 1)):
+        x = torch.randn(*shape, device=dev, dtype=torch.bfloat16)
+        want = x.float().clone()
+        dist.all_reduce(want, group=g.device_group)
+        for rep in range(3):
+            got = nv.all_reduce(x, mode=mode)
+        res["max_err"][name] = (got.float() - want).abs().max().item() / max(1.0, want.abs().max().item())
+    for name, rows, mode in (("fused_one", 96, 1), ("fused_two", 96, 2), ("fused_two_large", 2048, 2)):
+        x = torch.randn(rows, 4096, device=dev, dtype=torch.bfloat16)
+        resid = torch.randn(rows, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(4096, device=dev, dtype=torch.bfloat16)
+        dist.broadcast(resid, src=0, group=g.device_group)
+        dist.broadcast(w, src=0, group=g.device_group)
+        red = x.clone()
+        dist.all_reduce(red, group=g.device_group)
+        r_ref = resid.clone()
+        y_ref = ops.fused_add_rms_norm(red, r_ref, w, 1e-6)
+        r_got = resid.clone()
+        y_got = nv.all_reduce(x, r_got, w, 1e-6, mode=mode)
+        res["max_err"][name + "_out"] = (y_got.float() - y_ref.float()).abs().max().item()
+        res["max_err"][name + "_res"] = (r_got.float() - r_ref.float()).abs().max().item()
+
+    def graph_time(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(reps):
+                fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (3 * reps) * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g.device_group)     # max over ranks
+        return round(float(t), 1)
+
+    for rows in (1, 16, 128, 512, 2048, 8192):
+        x = torch.randn(rows, 4096, device=dev, dtype=torch.bfloat16)
+        nbytes = rows * 4096 * 2
+        reps = 20 if rows <= 512 else 5
+        row = {"nccl": graph_time(lambda: dist.all_reduce(x, group=g.device_group), reps)}
+        row["nvls_one_shot"] = graph_time(lambda: nv.all_reduce(x, mode=1), reps) if nbytes <= (8 << 20) else None
+        row["nvls_two_shot"] = graph_time(lambda: nv.all_reduce(x, mode=2), reps)
+        if nbytes <= symm.LL_SLOT_BYTES:
+            row["push"] = graph_time(lambda: symm.all_reduce(x, mode=3), reps)
+        row["peer_one_shot"] = graph_time(lambda: symm.all_reduce(x, mode=1), reps) if nbytes <= (8 << 20) else None
+        row["peer_two_shot"] = graph_time(lambda: symm.all_reduce(x, mode=2), reps)
+        res["us"][f"{nbytes >> 10}KiB"] = row
+    wn = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+    for rows in (16, 128):
+        x = torch.randn(rows, 4096, device=dev, dtype=torch.bfloat16)
+        rr = torch.zeros(rows, 4096, device=dev, dtype=torch.bfloat16)
+        res["us"][f"fused_norm_{rows}rows"] = {
+            "nvls_one_shot": graph_time(lambda: nv.all_reduce(x, rr, wn, 1e-6, mode=1), 20),
+            "push": graph_time(lambda: symm.all_reduce_add_rms_norm(x, rr, wn, 1e-6), 20)}
+    torch.cuda.synchronize()
+    ops.check_status()
+    g.barrier()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.destroy_distributed()
+
+
 def task_ep_moe(rank, world, port, workdir, device_kind):
     """Expert-parallel MoE layer (dispatch -> grouped GEMMs -> combine over peer memory, or the
     gloo all-to-all path on CPU) against the dense single-process computation."""
@@ -541,7 +635,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"nvls": task_nvls, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

@@ -256,6 +256,31 @@ def _paged_setup(seq_lens, q_lens, hq, hk, d, bs, dv=None, seed=0):
     return q, k_cache, v_cache, perm, cu, sl
 
 
+@pytest.mark.parametrize("tc", [True, False])
+@pytest.mark.parametrize("seq_lens,q_lens,hq,hk,bs,causal", [
+    ([130, 64, 517, 9], [130, 33, 200, 9], 8, 2, 16, True),        # with cached context, ragged tiles
+    ([1000, 1], [1000, 1], 4, 4, 16, True),                        # many key tiles, a one-row sequence
+    ([300, 257], [300, 129], 16, 2, 32, True),                     # 8 query heads per kv head, 32-token blocks
+    ([200, 77], [200, 40], 8, 2, 16, False),                       # not causal
+    ([640], [64], 8, 1, 64, True),                                 # short chunk over a long context, 64-token blocks
+])
+def test_gqa_prefill_tcgen05_matches_reference(seq_lens, q_lens, hq, hk, bs, causal, tc):
+    """Head size 128: the tcgen05 / TMEM kernel and the mma.sync kernel against the fp32 reference."""
+    d = 128
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, q_lens, hq, hk, d, bs, seed=31)
+    want, lse_want = ref.paged_attention(q, kc, vc, bt, cu, sl, hq, d ** -0.5, causal, 0, True)
+    got, lse = ops.gqa_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV), sl.to(DEV),
+                               len(seq_lens), max(q_lens), hq, d ** -0.5, causal, 0, True, tcgen05=tc)
+    _close(got, want, 2e-2, 2e-2)
+    _close(lse, lse_want, 2e-2, 1e-2)
+    # q as a column slice of a wider activation (the fused qkv projection's output)
+    wide = torch.randn(q.shape[0], q.shape[1] + 512, dtype=torch.bfloat16)
+    wide[:, : q.shape[1]] = q
+    got2 = ops.gqa_prefill(wide.to(DEV)[:, : q.shape[1]], kc.to(DEV), vc.to(DEV), bt.to(DEV), cu.to(DEV),
+                           sl.to(DEV), len(seq_lens), max(q_lens), hq, d ** -0.5, causal, tcgen05=tc)
+    _close(got2, want, 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("d,bs", [(128, 16), (64, 16), (128, 128)])
 def test_gqa_prefill(d, bs):
     seq_lens, q_lens = [130, 64, 517, 9], [130, 33, 200, 9]

@@ -24,6 +24,24 @@ def test_symmetric_memory_collectives_match_nccl():
           res[0]["us_symm_64MiB"], res[0]["us_nccl_64MiB"])
 
 
+def test_nvls_multimem_all_reduce_matches_nccl():
+    world = min(8, torch.cuda.device_count())
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("nvls", world, d, device="cuda", timeout=600)
+    if "unsupported" in res[0]:
+        pytest.skip("no NVLink multicast on this machine: " + res[0]["unsupported"])
+    for r in res:
+        for name, err in r["max_err"].items():
+            assert err <= (0.13 if "fused" in name else 0.02), (name, err)
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, f"nvls_all_reduce_{world}gpu.json"), "w") as f:
+            json.dump(res[0]["us"], f, indent=1)
+    print(f"all-reduce us on {world} GPUs (max over ranks, inside CUDA graphs):")
+    for size, row in res[0]["us"].items():
+        print(" ", size, row)
+
+
 def test_fused_all_gather_gemm_and_gemm_reduce_scatter():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("ag_gemm", 2, d, device="cuda", timeout=300)
