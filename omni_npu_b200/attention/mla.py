@@ -102,6 +102,9 @@ class MLAAttention(nn.Module):
         if rs.get("rope_type", rs.get("type")) in ("yarn", "deepseek_yarn") and rs.get("mscale_all_dim"):
             m = yarn_get_mscale(rs["factor"], rs["mscale_all_dim"])
             self.scale *= m * m
+        # decode context parallelism (the latent cache sharded by tokens over the tensor-parallel group)
+        # (set by the decoder layer from ParallelConfig.decode_context_parallel_size)
+        self.cp_group = None
         self.w_uk: Optional[torch.Tensor] = None    # [N, 512, 128]: rows = latent dims  (q_nope @ W_UK)
         self.w_uv: Optional[torch.Tensor] = None    # [N, 128, 512]: rows = v dims       (o_lat @ W_UV^T)
 
@@ -149,32 +152,51 @@ class MLAAttention(nn.Module):
         return self.o_proj(o, reduce=reduce)
 
     def _prefill(self, q, q_pe, cache, md: AttentionMetadata) -> torch.Tensor:
+        """Non-absorbed attention of this step's queries over every key of their sequences (cached
+        context included).  The latent blocks of the sequences are gathered block-wise, up-projected
+        with ``kv_b_proj`` and handed to the variable-length kernel as a temporary paged K / V whose
+        block table is the identity; lengths and block counts come from the host copy of the step
+        (no device-to-host read).  With decode context parallelism every rank gathers its token
+        shard of the same blocks, the shards are all-gathered, and (block, offset, rank) read in
+        that order IS the global token order, so the gathered tensor is the same paged latent with
+        ``block_size * world`` tokens per block
+        (reference: prefill omni_npu/attention/backends/mla.py:452-616, context gather under
+        context parallelism :317-375)."""
         t, n = q.shape[0], self.num_heads
         bs = cache.shape[1]
-        total_kv = int(md.extra.get("total_kv", 0)) or int(md.seq_lens[: md.num_seqs].sum().item())
-        slots, seq_id, pos = kv_slots_for_sequences(md, bs, total_kv)
-        lat = cache.view(-1, cache.shape[-1]).index_select(0, slots)              # [Tkv, 576]
-        kv = self.kv_b_proj(lat[:, : self.kv_lora_rank].contiguous()).view(total_kv, n, self.nope + self.v_dim)
-        k = torch.cat([kv[:, :, : self.nope],
-                       lat[:, self.kv_lora_rank:].unsqueeze(1).expand(total_kv, n, self.rope_dim)], dim=-1)
-        v = kv[:, :, self.nope:]
-        # temporary paged layout, one run of blocks per sequence
-        lens = md.seq_lens[: md.num_seqs].long()
-        nblk_per = (lens + bs - 1) // bs
-        blk_start = torch.cumsum(nblk_per, 0) - nblk_per
-        max_blocks = (md.max_seq_len + bs - 1) // bs
-        total_blocks = md.num_seqs * max_blocks
-        k_paged = torch.zeros(total_blocks, n, bs, self.qk_dim, dtype=q.dtype, device=q.device)
-        v_paged = torch.zeros(total_blocks, n, bs, self.v_dim, dtype=q.dtype, device=q.device)
-        tblk = seq_id * max_blocks + pos // bs
-        k_paged[tblk, :, pos % bs] = k
-        v_paged[tblk, :, pos % bs] = v
-        bt = (torch.arange(md.num_seqs, device=q.device).unsqueeze(1) * max_blocks +
-              torch.arange(max_blocks, device=q.device).unsqueeze(0)).to(torch.int32)
+        dev = q.device
+        lens_h = md.extra.get("seq_lens_host")
+        if lens_h is None:                   # a caller outside the model runner: one host read
+            lens_h = md.seq_lens[: md.num_seqs].tolist()
+        cp = self.cp_group
+        w = cp.world_size if cp is not None else 1
+        gbs = bs * w                                            # tokens per block id
+        nblk = [(int(l) + gbs - 1) // gbs for l in lens_h]
+        max_blocks = max(1, max(nblk))
+        total_blocks = sum(nblk)
+        seq_of_blk = [i for i, c in enumerate(nblk) for _ in range(c)]
+        j_of_blk = [j for c in nblk for j in range(c)]
+        starts, acc = [], 0
+        for c in nblk:
+            starts.append(acc)
+            acc += c
+        idx = torch.tensor([seq_of_blk, j_of_blk], dtype=torch.long).to(dev, non_blocking=True)
+        blk_ids = md.block_tables[idx[0], idx[1]].long()
+        lat = cache.index_select(0, blk_ids)                                     # [blocks, bs, 576]
+        if w > 1:
+            lat = cp.all_gather(lat.unsqueeze(2).contiguous(), dim=2)            # [blocks, bs, w, 576]
+            lat = lat.reshape(total_blocks, gbs, lat.shape[-1])
+        l = self.kv_lora_rank
+        kv = self.kv_b_proj(lat[..., :l].reshape(total_blocks * gbs, l).contiguous())
+        kv = kv.view(total_blocks, gbs, n, self.nope + self.v_dim)
+        k_pe = lat[..., l:].unsqueeze(2).expand(total_blocks, gbs, n, self.rope_dim)
+        k_paged = torch.cat([kv[..., : self.nope], k_pe], dim=-1).permute(0, 2, 1, 3).contiguous()
+        v_paged = kv[..., self.nope:].permute(0, 2, 1, 3).contiguous()
+        bt = torch.tensor([[s0 + min(j, max(c - 1, 0)) for j in range(max_blocks)] for s0, c in zip(starts, nblk)],
+                          dtype=torch.int32).to(dev, non_blocking=True)
         qf = torch.cat([q[:, :, : self.nope], q_pe], dim=-1).reshape(t, n * self.qk_dim)
-        out = ops.gqa_prefill(qf, k_paged, v_paged, bt, md.cu_q, md.seq_lens, md.num_seqs, md.max_q_len, n,
-                              self.scale, True, 0)
-        return out
+        return ops.gqa_prefill(qf, k_paged, v_paged, bt, md.cu_q, md.seq_lens, md.num_seqs, md.max_q_len, n,
+                               self.scale, True, 0)
 
     def _absorb_q(self, q, q_pe):
         """q_lat[h] = q_nope[h] @ W_UK[h] (heads act as the groups of a grouped GEMM); returns the
@@ -216,6 +238,14 @@ class MLAAttention(nn.Module):
             bt = md.block_tables[seq_of_tok]
             sl = md.seq_lens[seq_of_tok]
             o_lat = ops.mla_decode(qf, cache, bt.contiguous(), sl.contiguous(), t, n, self.scale, 1, topk_indices)
+        elif self.cp_group is not None:
+            # the cache holds this rank's token shard: attention of all heads over it, then the
+            # partial results are exchanged by head and merged by their log-sum-exp
+            if topk_indices is not None or md.q_len != 1:
+                raise NotImplementedError("decode context parallelism: plain one-token decode steps only")
+            from .dcp import dcp_mla_decode
+            o_lat = dcp_mla_decode(qf, cache, md.block_tables, md.seq_lens, md.num_seqs, n, self.scale,
+                                   self.cp_group)
         else:
             o_lat = ops.mla_decode(qf, cache, md.block_tables, md.seq_lens, md.num_seqs, n, self.scale, md.q_len,
                                    topk_indices, max_seq_len=md.max_seq_len)

@@ -41,7 +41,20 @@ class LLMEngine:
             from ..kv_transfer.connector import create_connector
             connector = create_connector(config, role="scheduler")
         reserved = getattr(self.worker.get_model(), "num_reserved_kv_blocks", 0)
-        self.scheduler = Scheduler(config.scheduler, config.cache, num_blocks, reserved, connector)
+        dcp = config.parallel.decode_context_parallel_size
+        if dcp > 1:
+            mc = config.model
+            if not mc.use_mla or mc.use_sparse:
+                raise ValueError("decode_context_parallel_size > 1 is supported for latent attention (MLA) "
+                                 "models without the sparse indexer")
+            if dcp != config.parallel.tensor_parallel_size:
+                raise ValueError("decode context parallelism shards the cache over the tensor-parallel group: "
+                                 "decode_context_parallel_size must equal tensor_parallel_size")
+            if connector is not None or (config.speculative.method and config.speculative.num_speculative_tokens):
+                raise ValueError("decode context parallelism is not combined with KV connectors or "
+                                 "speculative decoding")
+        self.scheduler = Scheduler(config.scheduler, config.cache, num_blocks, reserved, connector,
+                                   context_parallel_size=dcp)
         self._ids = itertools.count()
         self.stats = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "spec_decode_steps": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "output_tokens": 0}
@@ -336,6 +349,7 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                          pipeline_parallel_size=kw.pop("pipeline_parallel_size", 1),
                          data_parallel_size=kw.pop("data_parallel_size", 1),
                          enable_expert_parallel=kw.pop("enable_expert_parallel", False),
+                         decode_context_parallel_size=kw.pop("decode_context_parallel_size", 1),
                          sequence_parallel_residual=kw.pop("sequence_parallel_residual", False),
                          num_redundant_experts=kw.pop("num_redundant_experts", 0),
                          eplb_step_interval=kw.pop("eplb_step_interval", 0),

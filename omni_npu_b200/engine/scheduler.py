@@ -47,10 +47,12 @@ class SchedulerOutput:
 
 class Scheduler:
     def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
-                 num_reserved_blocks: int = 0, kv_connector=None) -> None:
+                 num_reserved_blocks: int = 0, kv_connector=None, context_parallel_size: int = 1) -> None:
         self.cfg = sched_cfg
-        self.block_size = cache_cfg.block_size
-        self.pool = BlockPool(num_blocks, cache_cfg.block_size, num_reserved_blocks)
+        # With decode context parallelism every rank stores 1 / world of a sequence's tokens
+        # (token p on rank p % world), so one block id covers block_size * world tokens.
+        self.block_size = cache_cfg.block_size * max(1, context_parallel_size)
+        self.pool = BlockPool(num_blocks, self.block_size, num_reserved_blocks)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.requests: Dict[str, Request] = {}

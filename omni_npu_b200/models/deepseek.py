@@ -53,6 +53,8 @@ class DeepseekDecoderLayer(nn.Module):
                                                     sliding_window=cfg.sliding_window)
         else:
             self.self_attn = MLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn", qf)
+        if engine.parallel.decode_context_parallel_size > 1 and pstate.get_tp_group().world_size > 1:
+            self.self_attn.cp_group = pstate.get_tp_group()
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype, device)
         self.is_moe = cfg.layer_is_moe(layer_idx)
         if self.is_moe:

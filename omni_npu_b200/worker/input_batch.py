@@ -70,10 +70,13 @@ def default_seed(request_id: str, base_seed: int = 0) -> int:
 
 class InputBatch:
     def __init__(self, max_num_seqs: int, max_model_len: int, block_size: int,
-                 max_num_batched_tokens: int, device: torch.device) -> None:
+                 max_num_batched_tokens: int, device: torch.device, cp_world: int = 1, cp_rank: int = 0) -> None:
         self.max_num_seqs = max_num_seqs
         self.block_size = block_size
-        self.max_blocks = (max_model_len + block_size - 1) // block_size
+        # decode context parallelism: token p of a sequence is stored on rank p % cp_world at local
+        # position p // cp_world; other ranks get slot -1 for it (the cache-write kernels skip those)
+        self.cp_world, self.cp_rank = max(1, cp_world), cp_rank
+        self.max_blocks = (max_model_len + block_size * self.cp_world - 1) // (block_size * self.cp_world)
         self.device = device
         self.num_rows = 0
         self.rows: List[Optional[Request]] = [None] * max_num_seqs
@@ -160,6 +163,16 @@ class InputBatch:
             "bt": buf[lay.bt: lay.bt + S * mb].view(S, mb),
         }
 
+    def _slots(self, row, pos: np.ndarray) -> np.ndarray:
+        """Cache slots of positions ``pos`` of the request(s) in ``row`` (an index or an index array
+        matching ``pos``)."""
+        bs = self.block_size
+        if self.cp_world == 1:
+            return self.block_table[row, pos // bs] * bs + pos % bs
+        lp = pos // self.cp_world
+        slot = self.block_table[row, lp // bs] * bs + lp % bs
+        return np.where(pos % self.cp_world == self.cp_rank, slot, -1).astype(np.int32)
+
     def upload(self, lay: StepLayout) -> None:
         """One H2D copy of the staged step (pinned host -> device).  The copy is asynchronous:
         the staging buffer must not be rewritten until it has run (``wait_upload``)."""
@@ -208,8 +221,7 @@ class InputBatch:
                            for r in reqs), dtype=np.int32, count=n)
         h[lay.ids: lay.ids + n] = ids
         h[lay.pos: lay.pos + n] = pos
-        blk = self.block_table[rows, pos // bs]
-        h[lay.slot: lay.slot + n] = blk * bs + pos % bs
+        h[lay.slot: lay.slot + n] = self._slots(rows, pos)
         h[lay.seq_lens: lay.seq_lens + n] = pos + 1
         if lay.S > n:
             # padded sequences: length 1 over block 0, results discarded
@@ -252,7 +264,7 @@ class InputBatch:
                 h[lay.ids + off + 1: lay.ids + off + q] = s.spec_token_ids
             p = np.arange(s.start, s.start + q, dtype=np.int32)
             h[lay.pos + off: lay.pos + off + q] = p
-            h[lay.slot + off: lay.slot + off + q] = self.block_table[row, p // bs] * bs + p % bs
+            h[lay.slot + off: lay.slot + off + q] = self._slots(row, p)
             h[lay.seq_lens + i] = s.start + q
             off += q
             cu[i + 1] = off
@@ -293,7 +305,7 @@ class InputBatch:
             h[lay.ids + off: lay.ids + off + q] = toks
             p = np.arange(s.start, s.start + q, dtype=np.int32)
             h[lay.pos + off: lay.pos + off + q] = p
-            h[lay.slot + off: lay.slot + off + q] = self.block_table[row, p // bs] * bs + p % bs
+            h[lay.slot + off: lay.slot + off + q] = self._slots(row, p)
             h[lay.seq_lens + i] = s.start + q
             # successors inside the chunk, then the token after it if the request already has it
             h[lay.next_ids + off: lay.next_ids + off + q - 1] = toks[1:]

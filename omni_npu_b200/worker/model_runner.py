@@ -55,8 +55,10 @@ class ModelRunner:
         self.kv_caches: List = []
         self.num_blocks = 0
         sc = config.scheduler
+        dcp = config.parallel.decode_context_parallel_size
         self.input_batch = InputBatch(sc.max_num_seqs, sc.max_model_len, config.cache.block_size,
-                                      sc.max_num_batched_tokens, device)
+                                      sc.max_num_batched_tokens, device, cp_world=dcp,
+                                      cp_rank=pstate.get_tp_group().rank_in_group if dcp > 1 else 0)
         self.input_batch.base_seed = int(config.seed or 0)
         self.sampler = Sampler(config, device)
         self.rejection_sampler = RejectionSampler(self.sampler)
@@ -435,6 +437,7 @@ class ModelRunner:
             views = ib.views(lay, ib.dev)
             max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
+            md.extra["seq_lens_host"] = [s.start + s.num_new_tokens for s in out.seqs]
             sampled = self._forward_and_sample(views, md, n)
         self.step_counter += 1
         self._event_stop(ev, out.kind)
@@ -577,11 +580,12 @@ class ModelRunner:
             h[lay.top_k: lay.top_k + n_seq] = 0
             h[lay.top_p: lay.top_p + n_seq] = np.float32(1.0).view(np.int32)
             bt = h[lay.bt: lay.bt + n_seq * lay.max_blocks].reshape(n_seq, lay.max_blocks)
-            nb = (per + bs - 1) // bs
+            nb = (per + bs * ib.cp_world - 1) // (bs * ib.cp_world)
             bt[:, :nb] = np.arange(nb, dtype=np.int32) % max(1, self.num_blocks)
             ib.upload(lay)
             views = ib.views(lay, ib.dev)
             md = self._metadata(lay, views, True, n_seq, T, per, per, 0, T, n_seq)
+            md.extra["seq_lens_host"] = [per] * n_seq
             self._forward_and_sample(views, md, n_seq)
         else:
             S = num_tokens

@@ -119,6 +119,28 @@ def task_pp_deepseek(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_dcp_engine(rank, world, port, workdir, device_kind):
+    """Tiny latent-attention model under tensor parallelism, with or without the KV cache sharded by
+    tokens over the same ranks (decode context parallelism); spec.json says which."""
+    dev, state = setup(rank, world, port, device_kind)
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    spec = json.load(open(os.path.join(workdir, "spec.json")))
+    cfg = ModelConfig(dtype=torch.float32 if device_kind == "cpu" else torch.bfloat16, **spec["model"])
+    llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world,
+              decode_context_parallel_size=world if spec["dcp"] else 1, **spec["engine"])
+    outs = llm.generate(spec["prompts"], SamplingParams(max_tokens=spec["max_tokens"], ignore_eos=True))
+    runner = llm.engine.worker.model_runner
+    json.dump({"tokens": [o.output_token_ids for o in outs], "max_blocks": runner.input_batch.max_blocks,
+               "free_blocks": llm.engine.scheduler.pool.num_free},
+              open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if device_kind == "cuda":
+        state.finish_process(llm.engine)
+    state.get_world_group().barrier()
+    state.destroy_distributed()
+
+
 def task_dp_engine(rank, world, port, workdir, device_kind):
     """One engine per data-parallel rank (experts sharded over all ranks); every rank serves its
     own list of prompts, lists of different lengths."""
@@ -635,7 +657,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"nvls": task_nvls, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"nvls": task_nvls, "dcp_engine": task_dcp_engine, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

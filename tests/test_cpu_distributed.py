@@ -163,3 +163,33 @@ def test_expert_parallel_moe_two_ranks_gloo():
         res = run_ranks("ep_moe", 2, d)
     for r in res:
         assert max(r["max_err"].values()) < 1e-4, r
+
+
+def test_decode_context_parallel_engine_matches_plain_tensor_parallel(monkeypatch):
+    """The latent KV cache sharded by tokens over the two tensor-parallel ranks (token p on rank
+    p % 2): cache writes skip foreign tokens, prefill gathers the shards of the context (a 70-token
+    prompt is chunked at 64, so the second chunk reads gathered context), decode merges the ranks'
+    partial attentions by their log-sum-exp.  Tokens equal the same deployment with a replicated
+    cache, and a block id covers twice the tokens."""
+    model = dict(architecture="DeepseekV2ForCausalLM", model_type="deepseek_v2", hidden_size=128, num_layers=3,
+                 num_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=256, vocab_size=512,
+                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+                 num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
+                 first_k_dense=1, use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=32,
+                 qk_rope_head_dim=64, v_head_dim=32)
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(17)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 70, 5)]
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")
+    res = {}
+    for dcp in (0, 1):
+        with tempfile.TemporaryDirectory() as d:
+            json.dump({"model": model, "engine": engine, "prompts": prompts, "max_tokens": 8, "dcp": dcp},
+                      open(os.path.join(d, "spec.json"), "w"))
+            res[dcp] = run_ranks("dcp_engine", 2, d)
+    assert res[1][0]["tokens"] == res[0][0]["tokens"]
+    assert res[1][0]["tokens"] == res[1][1]["tokens"]
+    assert all(len(t) == 8 for t in res[1][0]["tokens"])
+    assert res[1][0]["max_blocks"] * 2 == res[0][0]["max_blocks"]
+    assert res[1][0]["free_blocks"] == 64 and res[1][1]["free_blocks"] == 64
