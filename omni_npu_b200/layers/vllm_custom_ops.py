@@ -73,5 +73,79 @@ if compat.vllm_available():
                 return q2.view(query.shape), k2.view(key.shape)
 
         REGISTERED.append("RotaryEmbedding")
+
+        def _oot_variant(mod: str, name: str) -> None:
+            """The scaling variants (YaRN, DeepSeek-YaRN, linear, Llama-3) only change how the cos/sin
+            table is built; the rotation itself is the same fused kernel."""
+            try:
+                base = getattr(__import__(mod, fromlist=[name]), name)
+            except Exception:
+                return
+            if not issubclass(base, RotaryEmbedding):
+                return
+            cls = type("B200" + name, (base,), {"forward_oot": B200RotaryEmbedding.forward_oot,
+                                                "__doc__": f"{name} rotating with the fused kernel."})
+            base.register_oot(cls)
+            REGISTERED.append(name)
+
+        _rp = "vllm.model_executor.layers.rotary_embedding."
+        for _mod, _name in ((_rp + "deepseek_scaling_rope", "DeepseekScalingRotaryEmbedding"),
+                            (_rp + "linear_scaling_rope", "LinearScalingRotaryEmbedding"),
+                            (_rp + "llama3_rope", "Llama3RotaryEmbedding"),
+                            (_rp + "yarn_scaling_rope", "YaRNScalingRotaryEmbedding")):
+            _oot_variant(_mod, _name)
     except Exception:                                     # layout of the rotary module differs in this vLLM
+        pass
+
+    # ---- quantisation config: the name this platform's loaders answer to
+    try:
+        from vllm.model_executor.layers.quantization import register_quantization_config
+        from vllm.model_executor.layers.quantization.base_config import QuantizationConfig
+
+        from .quant_int8 import QUANT_NAME, CompressedTensorsConfig
+
+        @register_quantization_config(QUANT_NAME)
+        class B200CompressedTensorsQuantConfig(QuantizationConfig):
+            """vLLM-facing name of this package's compressed-tensors (W8A8 int8) support.  Checkpoints
+            whose HF ``quant_method`` is ``compressed-tensors`` select it automatically on this
+            platform (the reference does the same for its ``npu-compressed-tensors``:
+            omni_npu/layers/quantization/compressed_tensors/compressed_tensors.py:32-36,176-182).
+            The weights themselves are loaded by this package's own model classes
+            (``layers/quant_int8.py``); this class parses and carries the config."""
+
+            def __init__(self, inner: Optional[CompressedTensorsConfig] = None) -> None:
+                super().__init__()
+                self.inner = inner
+
+            def get_name(self) -> str:
+                return QUANT_NAME
+
+            @classmethod
+            def get_supported_act_dtypes(cls):
+                return [torch.bfloat16, torch.float16]
+
+            @classmethod
+            def get_min_capability(cls) -> int:
+                return 100
+
+            @classmethod
+            def get_config_filenames(cls):
+                return []
+
+            @classmethod
+            def from_config(cls, config):
+                return cls(CompressedTensorsConfig.from_config(config))
+
+            @classmethod
+            def override_quantization_method(cls, hf_quant_cfg, user_quant, *args, **kw):
+                method = (hf_quant_cfg or {}).get("quant_method")
+                if method == "compressed-tensors" and user_quant in (None, QUANT_NAME, "compressed-tensors"):
+                    return QUANT_NAME
+                return None
+
+            def get_quant_method(self, layer, prefix: str):
+                return None          # vLLM's own layers are not built under this platform's worker
+
+        REGISTERED.append("quantization:" + QUANT_NAME)
+    except Exception:
         pass

@@ -73,9 +73,14 @@ class DeepseekDecoderLayer(nn.Module):
                                 quant_method_factory=qf, prefix=f"{prefix}.mlp",
                                 fuse_swiglu=cfg.quant_method is None)
         self.tp_group = pstate.get_tp_group()
+        self.prefetcher = None            # set by the model's post_load when weight prefetch is on
+        self.next_attn = None
 
     def forward(self, hidden, residual, pending_reduce: bool):
         tp = self.tp_group
+        pf = self.prefetcher
+        if pf is not None:                # this layer's MLP / expert weights, while attention runs
+            pf.prefetch_moe(self.mlp) if self.is_moe else pf.prefetch_mlp(self.mlp)
         if residual is None:
             residual = hidden
             hidden = self.input_layernorm(hidden)
@@ -85,6 +90,8 @@ class DeepseekDecoderLayer(nn.Module):
             hidden, residual = self.input_layernorm(hidden, residual)
         hidden = self.self_attn(hidden, reduce=False)
         hidden, residual = reduce_add_rms_norm(self.post_attention_layernorm, hidden, residual, tp)
+        if pf is not None and self.next_attn is not None:      # the next layer's projections, while the MLP runs
+            pf.prefetch_attention(self.next_attn)
         if self.is_moe:
             return self.mlp(hidden), residual, False
         return self.mlp(hidden, reduce=False), residual, True
@@ -168,6 +175,29 @@ class DeepseekForCausalLM(nn.Module):
                 engine_config, device,
                 lambda idx, prefix: layer_cls(engine_config, idx, device, prefix))
             self.num_kv_layers += self.mtp.num_mtp_layers
+        self.prefetcher = None
+
+    def post_load(self) -> None:
+        """After the weights are in place: wire the L2 weight prefetcher into the decoder layers when
+        the deployment plan (or ``additional_config["weight_prefetch"]``) asks for it.  Each layer
+        then hints its own MLP / expert weights into L2 while its attention runs and the next
+        layer's attention projections while its MLP runs
+        (reference: ``prefetch_post_load`` and the per-layer hints,
+        omni_npu/v1/models/deepseek/deepseek_v3.py:165-218,398-428)."""
+        from ..layers.prefetch import Prefetcher
+        from .config_loader import model_extra_config
+        want = self.engine_config.additional_config.get("weight_prefetch")
+        plan = model_extra_config.kernels
+        if want is None:
+            want = model_extra_config.source is not None and plan.enable_prefetch
+        dev = next(self.parameters()).device
+        if not want or dev.type != "cuda":
+            return
+        self.prefetcher = Prefetcher.from_plan(dev, plan)
+        layers = self.model._stage_layers()
+        for i, layer in enumerate(layers):
+            layer.prefetcher = self.prefetcher
+            layer.next_attn = layers[i + 1].self_attn if i + 1 < len(layers) else None
 
     def forward(self, input_ids, positions, inputs_embeds=None, intermediate_tensors=None):
         return self.model(input_ids, positions, inputs_embeds, intermediate_tensors=intermediate_tensors)
