@@ -2,9 +2,9 @@
 //
 // The decode instance maps the prefill instance's KV-cache tensors (CUDA IPC) and
 // pulls the blocks of a request with ONE launch that covers every layer tensor:
-// CTA (pair p, tensor l) copies block src_block[p] of remote tensor l into block
-// dst_block[p] of local tensor l with 16-byte loads over NVLink (plain ld/st; the
-// destination is always this GPU's own memory).
+// block src_block[p] of remote tensor l goes into block dst_block[p] of local tensor l
+// with 16-byte loads over NVLink (plain ld/st; the destination is always this GPU's
+// own memory).
 //
 // Replaces llm_datadist's pull_blocks (omni_npu/connector/llmdatadist_manager_v1.py:303-349).
 
@@ -19,41 +19,60 @@ struct KvCopyTensor {
   long long block_bytes;
 };
 
+// Work items are (block pair, tensor, 32 KiB chunk), flattened; a fixed grid of CTAs strides over
+// them.  Every thread keeps eight 16-byte loads in flight (32 KiB per CTA): a pull over NVLink is
+// latency bound (a few microseconds per round trip), so bytes in flight, not CTA count, set the
+// bandwidth.
+static constexpr int kKvChunkBytes = 32 << 10;
+
 __global__ void __launch_bounds__(256)
 kv_p2p_copy_kernel(const KvCopyTensor* __restrict__ tensors, const int* __restrict__ src_blocks,
-                   const int* __restrict__ dst_blocks, int num_pairs) {
-  const int pair = blockIdx.x;
-  const KvCopyTensor t = tensors[blockIdx.y];
-  const long long nvec = t.block_bytes >> 4;
-  const uint4* src = reinterpret_cast<const uint4*>(t.src + static_cast<long long>(src_blocks[pair]) * t.block_bytes);
-  uint4* dst = reinterpret_cast<uint4*>(t.dst + static_cast<long long>(dst_blocks[pair]) * t.block_bytes);
-  // several chunks of a block may be assigned to different CTAs along z
-  const long long per = (nvec + gridDim.z - 1) / gridDim.z;
-  const long long b = per * blockIdx.z, e = min(nvec, b + per);
-  long long i = b + threadIdx.x;
-  for (; i + 3LL * blockDim.x < e; i += 4LL * blockDim.x) {
-    uint4 v[4];
+                   const int* __restrict__ dst_blocks, int num_pairs, int num_tensors, int chunks_per_block) {
+  const long long total = static_cast<long long>(num_pairs) * num_tensors * chunks_per_block;
+  for (long long item = blockIdx.x; item < total; item += gridDim.x) {
+    const int chunk = static_cast<int>(item % chunks_per_block);
+    const int ti = static_cast<int>((item / chunks_per_block) % num_tensors);
+    const int pair = static_cast<int>(item / (static_cast<long long>(chunks_per_block) * num_tensors));
+    const KvCopyTensor t = tensors[ti];
+    const long long b = static_cast<long long>(chunk) * kKvChunkBytes;
+    if (b >= t.block_bytes) continue;
+    const long long nvec = (min(t.block_bytes, b + kKvChunkBytes) - b) >> 4;
+    const uint4* src = reinterpret_cast<const uint4*>(t.src + static_cast<long long>(src_blocks[pair]) * t.block_bytes + b);
+    uint4* dst = reinterpret_cast<uint4*>(t.dst + static_cast<long long>(dst_blocks[pair]) * t.block_bytes + b);
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = __ldcv(src + i + u * blockDim.x);
+    for (int u = 0; u < 8; ++u) {
+      const long long i = threadIdx.x + u * 256LL;
+      if (i < nvec) v[u] = __ldcv(src + i);
+    }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) dst[i + u * blockDim.x] = v[u];
+    for (int u = 0; u < 8; ++u) {
+      const long long i = threadIdx.x + u * 256LL;
+      if (i < nvec) dst[i] = v[u];
+    }
   }
-  for (; i < e; i += blockDim.x) dst[i] = __ldcv(src + i);
 }
 
 }  // namespace b200
 
 // tensors: device array of num_tensors descriptors; src_blocks / dst_blocks: device int arrays.
+// Block sizes are multiples of 16 bytes.
 extern "C" int b200_kv_p2p_copy(const void* tensors, int num_tensors, const int* src_blocks,
                                 const int* dst_blocks, int num_pairs, long long max_block_bytes,
                                 cudaStream_t stream) {
   if (num_pairs <= 0 || num_tensors <= 0) return 0;
-  if (num_tensors > 65535) return -1;
-  int z = static_cast<int>((max_block_bytes + (64 << 10) - 1) / (64 << 10));   // ~64 KiB per CTA
-  if (z < 1) z = 1;
-  if (z > 16) z = 16;
-  dim3 grid(num_pairs, num_tensors, z);
+  if (num_tensors > 65535 || max_block_bytes <= 0) return -1;
+  const int chunks = static_cast<int>((max_block_bytes + b200::kKvChunkBytes - 1) / b200::kKvChunkBytes);
+  const long long total = static_cast<long long>(num_pairs) * num_tensors * chunks;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const long long cap = 8LL * sms;                       // 8 CTAs of 256 threads per SM
+  const int grid = static_cast<int>(total < cap ? total : cap);
   b200::kv_p2p_copy_kernel<<<grid, 256, 0, stream>>>(static_cast<const b200::KvCopyTensor*>(tensors),
-                                                     src_blocks, dst_blocks, num_pairs);
+                                                     src_blocks, dst_blocks, num_pairs, num_tensors, chunks);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

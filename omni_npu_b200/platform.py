@@ -149,9 +149,9 @@ class B200Platform(_Base):
         if cc is not None and not getattr(cc, "block_size", None):
             cc.block_size = DEFAULT_BLOCK_SIZE
         sc = getattr(vllm_config, "scheduler_config", None)
-        if sc is not None and getattr(sc, "async_scheduling", False):
-            # the worker returns each step's tokens itself; vLLM's placeholder-token protocol for
-            # steps scheduled ahead of their results is not implemented by it
+        if sc is not None and getattr(sc, "async_scheduling", False) \
+                and os.environ.get("OMNI_B200_VLLM_ASYNC", "1") == "0":
+            # OMNI_B200_VLLM_ASYNC=0: strictly alternating schedule / execute (debugging aid)
             with contextlib.suppress(Exception):
                 sc.async_scheduling = False
         comp = getattr(vllm_config, "compilation_config", None)

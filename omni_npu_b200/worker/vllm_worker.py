@@ -24,9 +24,13 @@ cache manager can size the cache; ``initialize_from_config`` takes the resulting
 and lets the runner allocate its own paged tensors.  Block 0 is vLLM's null block and is the
 only block the runner's dummy runs touch.
 
+vLLM's asynchronous scheduling is supported for plain decode steps: the step is launched without
+waiting for the previous step's tokens (they are fed forward on the device, the host books
+placeholders) and ``sample_tokens`` returns an ``AsyncModelRunnerOutput`` that the executor
+resolves later; any other kind of step first waits for the tokens in flight.
+
 Not supported under vLLM yet (refused with a clear error, never silently wrong): vLLM-side
-speculative decoding, structured-output bitmasks, LoRA, pooling, vLLM's asynchronous
-scheduling (switched off by the platform) and pipeline parallelism.
+speculative decoding, structured-output bitmasks, LoRA, pooling and pipeline parallelism.
 """
 from __future__ import annotations
 
@@ -164,6 +168,28 @@ class StepTranslator:
         out.kind = "idle" if not seqs else ("decode" if all_decode else "prefill")
         return out
 
+    def commit_pending(self, out) -> List[int]:
+        """Book a launched decode step whose tokens are not on the host yet: every sequence gets a
+        placeholder (-1) as its newest token.  Returns the placeholder positions for ``resolve``."""
+        pos = []
+        for seq in out.seqs:
+            req = seq.request
+            req.num_computed_tokens = seq.start + seq.num_new_tokens
+            req.output_token_ids.append(-1)
+            pos.append(len(req.output_token_ids) - 1)
+        return pos
+
+    @staticmethod
+    def resolve(out, pos: List[int], tokens: List[int]) -> List[List[int]]:
+        """Fill the placeholders of a launched step with the tokens that arrived."""
+        result: List[List[int]] = []
+        for seq, p, tok in zip(out.seqs, pos, tokens):
+            ids = seq.request.output_token_ids
+            if p < len(ids):
+                ids[p] = int(tok)
+            result.append([int(tok)])
+        return result
+
     def commit(self, out, tokens: List[int]) -> List[List[int]]:
         """Book the step's sampled tokens on the worker's request objects; returns vLLM's
         ``sampled_token_ids`` (an empty list for a prompt chunk that does not end its prompt)."""
@@ -179,6 +205,40 @@ class StepTranslator:
         return result
 
 
+class PendingDecodeOutput:
+    """Result of a decode step that was launched without waiting for its tokens (vLLM's
+    asynchronous scheduling).  ``get_output`` blocks until the device-to-host copy of the sampled
+    tokens has finished, fills the placeholders and builds vLLM's ``ModelRunnerOutput``; it may be
+    called from the executor's output thread."""
+
+    def __init__(self, worker: "B200Worker", out, handle: dict, pos: List[int]) -> None:
+        self.worker, self.out, self.handle, self.pos = worker, out, handle, pos
+        self._result = None
+
+    def tokens_on_host(self) -> None:
+        if self._result is None:
+            import threading
+            with self.worker._resolve_lock:
+                if self._result is None:
+                    tokens = self.worker.model_runner.collect_decode(self.handle)
+                    self._result = StepTranslator.resolve(self.out, self.pos, tokens)
+
+    def get_output(self):
+        from vllm.v1.outputs import ModelRunnerOutput
+        self.tokens_on_host()
+        req_ids = [s.request.request_id for s in self.out.seqs]
+        return ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
+                                 sampled_token_ids=self._result, logprobs=None, prompt_logprobs_dict={},
+                                 pooler_output=[])
+
+
+if compat.vllm_available():
+    from vllm.v1.outputs import AsyncModelRunnerOutput as _AsyncBase
+
+    class PendingDecodeOutput(PendingDecodeOutput, _AsyncBase):  # type: ignore[no-redef]
+        pass
+
+
 class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
     def __init__(self, vllm_config, local_rank: int, rank: int, distributed_init_method: str,
                  is_driver_worker: bool = False, **kwargs: Any) -> None:
@@ -190,6 +250,11 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         self.ha_agent = None
         self._kv_bytes_per_block = 0
         self.steps = {"decode": 0, "prefill": 0}
+        import threading
+        self._resolve_lock = threading.Lock()
+        self._inflight: Optional[PendingDecodeOutput] = None     # decode step launched ahead of its tokens
+        self._stashed = None                                     # output of execute_model, handed out by sample_tokens
+        self.async_scheduling = bool(getattr(vllm_config.scheduler_config, "async_scheduling", False))
 
     # ---------------------------------------------------------------- set-up
     def init_device(self) -> None:
@@ -319,12 +384,29 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         if out.kind == "idle":
             self.inner.execute_model(out)                 # retire rows of finished requests
             return EMPTY_MODEL_RUNNER_OUTPUT
+        runner = self.model_runner
+        if (self.async_scheduling and out.kind == "decode" and runner.mtp is None
+                and not any(runner.needs_host_logits(s.request) for s in out.seqs)):
+            # vLLM scheduled this step before the previous one's tokens were read: launch it without
+            # waiting; token values missing on the host are fed forward on the device
+            prev = self._inflight
+            handle = self.inner.launch_decode(out, prev.handle if prev is not None and prev._result is None else None)
+            pending = PendingDecodeOutput(self, out, handle, self.translator.commit_pending(out))
+            self._inflight = pending
+            self.steps["decode"] = self.steps.get("decode", 0) + 1
+            self.steps["launched_ahead"] = self.steps.get("launched_ahead", 0) + 1
+            self._stashed = pending
+            return None
+        if self._inflight is not None:
+            self._inflight.tokens_on_host()               # anything else stages token values on the host
+            self._inflight = None
         tokens = self._run(out)
         sampled = self.translator.commit(out, tokens)
         req_ids = [s.request.request_id for s in out.seqs]
-        return ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
-                                 sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
-                                 pooler_output=[])
+        self._stashed = ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
+                                          sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
+                                          pooler_output=[])
+        return None
 
     # a mixed step is split when it carries at least this many decoding sequences
     MIXED_SPLIT_MIN_DECODES = int(os.environ.get("OMNI_B200_MIXED_SPLIT_MIN", "8"))
@@ -357,7 +439,12 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         return self.inner.execute_model(out)
 
     def sample_tokens(self, grammar_output=None):
-        raise RuntimeError("execute_model of the B200 worker returns the step's output itself")
+        """Second half of vLLM's two-call step: the forward pass and the sampling both ran in
+        ``execute_model`` (structured-output bitmasks are refused there), this hands the result out."""
+        out, self._stashed = self._stashed, None
+        if out is None:
+            raise RuntimeError("sample_tokens called without a preceding execute_model")
+        return out
 
     def take_draft_token_ids(self):
         return None

@@ -496,18 +496,38 @@ def task_kv_pull(rank, world, port, workdir, device_kind):
             ok &= torch.equal(k[dst_blocks], rk[src_blocks]) and torch.equal(v[dst_blocks], rv[src_blocks])
             ok &= bool(k[1].abs().sum() == 0)
         res["byte_exact"] = bool(ok)
-        # bandwidth on a larger pull
-        n = 60
+        res["gbs_small"] = None
+    # bandwidth on a pull of serving size: 48 layers x (K, V) x 512 blocks of 4 kv heads x 16 tokens x 128
+    # = 96 tensors x 8 MiB = 768 MiB in the caches, 384 blocks pulled = 576 MiB over the link per pull
+    mgr2 = KVLinkManager(make_cluster_id("127.0.0.1", 30100 + rank, 1), 0, dev)
+    big = [(torch.zeros(512, 4, 16, 128, device=dev, dtype=torch.bfloat16),
+            torch.zeros(512, 4, 16, 128, device=dev, dtype=torch.bfloat16)) for _ in range(48)]
+    if rank == 0:
+        for k, v in big:
+            k.fill_(1.0), v.fill_(2.0)
+    exports2 = g.all_gather_object(mgr2.register_memory(big))
+    if rank == 1:
+        n = 384
+        blocks = list(range(n))
+        ev = mgr2.pull_kv(exports2[0].cluster_id, 0, blocks, blocks, refresh=lambda: exports2[0])
+        ev.synchronize()
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         t0.record()
-        for _ in range(10):
-            ev = mgr.pull_kv(exports[0].cluster_id, 0, list(range(n)), list(range(n)))
+        for _ in range(5):
+            ev = mgr2.pull_kv(exports2[0].cluster_id, 0, blocks, blocks)
         ev.synchronize()
         t1.record()
         torch.cuda.synchronize()
-        res["gbs"] = 10 * n * 8 * (2 * 16 * 128 * 2) / (t0.elapsed_time(t1) * 1e-3) / 1e9
+        nbytes = 5 * n * 96 * (4 * 16 * 128 * 2)
+        res["gbs"] = nbytes / (t0.elapsed_time(t1) * 1e-3) / 1e9
+        res["pull_mib"] = nbytes / 5 / 2**20
+        res["byte_exact"] = bool(res["byte_exact"] and float(big[7][0][383].float().mean()) == 1.0
+                                 and float(big[40][1][0].float().mean()) == 2.0
+                                 and float(big[3][0][384].float().abs().sum()) == 0.0)
+    g.barrier()
+    mgr2.close()
     json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     g.barrier()
     mgr.close()

@@ -35,7 +35,8 @@ def test_vllm_engine_runs_own_worker_and_runner_token_for_token():
     assert res["platform"] == "B200CpuPlatform"
     assert res["worker_cls"] == "omni_npu_b200.worker.vllm_worker.B200Worker" and res["worker"] == "B200Worker"
     assert res["runner"] == "omni_npu_b200.worker.model_runner.ModelRunner"      # not vLLM's GPUModelRunner
-    assert res["async_scheduling"] is False
+    assert res["async_scheduling"] is True            # vLLM schedules ahead; decode steps are launched ahead
+    assert res["steps"]["launched_ahead"] > 0
     assert res["steps"]["prefill"] == 4 and res["steps"]["decode"] == 4 * 15
     assert res["via_vllm"] == res["standalone"]
     assert all(len(t) == 16 for t in res["via_vllm"])

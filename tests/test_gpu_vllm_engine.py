@@ -15,7 +15,8 @@ def test_vllm_engine_on_gpu_runs_own_kernels_and_matches_standalone_engine():
     assert res["platform"] == "B200Platform"
     assert res["worker"] == "B200Worker"
     assert res["runner"] == "omni_npu_b200.worker.model_runner.ModelRunner"
-    assert res["async_scheduling"] is False
+    assert res["async_scheduling"] is True            # vLLM schedules ahead; decode steps are launched ahead
+    assert res["steps"]["launched_ahead"] > 0
     assert res["graphs"] > 0                       # decode steps replay this package's CUDA graphs
     assert res["launches"] > 100                   # kernels of this package's extension were launched
     assert res["steps"]["prefill"] == 4 and res["steps"]["decode"] == 4 * 15
