@@ -91,9 +91,25 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
         from omni_npu_b200.models.llama import LlamaModel
         LlamaModel.auto_sequence_parallel = True
     llm = LLM(model=model_dir, **kw)
+    # logits of the step that ends each prompt (captured through the runner's logits hook), for a
+    # tolerance comparison against another deployment of the same weights
+    first_logits = []
+    runner = llm.engine.worker.model_runner
+    real_hook = runner._make_logits_fn
+    if os.path.exists(os.path.join(workdir, "capture_logits")):
+        def hook(seqs):
+            def fn(logits):
+                rows = [i for i, q in enumerate(seqs) if q.samples and not q.request.output_token_ids]
+                for i in rows:
+                    first_logits.append((seqs[i].request.request_id, logits[i].float().cpu().tolist()))
+                return logits
+            return fn
+        runner._make_logits_fn = hook
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    runner._make_logits_fn = real_hook
     kinds = sorted({type(m).__name__ for m in llm.engine.worker.get_model().modules() if "Attention" in type(m).__name__})
-    json.dump({"tokens": [o.output_token_ids for o in outs], "attention_modules": kinds},
+    json.dump({"tokens": [o.output_token_ids for o in outs], "attention_modules": kinds,
+               "first_logits": [l for _, l in sorted(first_logits)]},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":
         state.finish_process(llm.engine)

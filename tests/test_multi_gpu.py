@@ -12,6 +12,39 @@ from dist_utils import run_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multi_gpu]
 
 
+def _first_logits(llm, prompts):
+    """Logits of the step that ends each prompt, in request order (one-GPU side of the comparison)."""
+    from omni_npu_b200 import SamplingParams
+    runner = llm.engine.worker.model_runner
+    got = []
+
+    def hook(seqs):
+        def fn(logits):
+            for i, q in enumerate(seqs):
+                if q.samples and not q.request.output_token_ids:
+                    got.append((q.request.request_id, logits[i].float().cpu()))
+            return logits
+        return fn
+    real = runner._make_logits_fn
+    runner._make_logits_fn = hook
+    try:
+        llm.generate(prompts, SamplingParams(max_tokens=1, ignore_eos=True))
+    finally:
+        runner._make_logits_fn = real
+    return [l for _, l in sorted(got, key=lambda t: t[0])]
+
+
+def _assert_first_logits_close(got_lists, want):
+    """bf16 partial sums are rounded differently on 1 and 2 GPUs: the logits agree within 3 % of the
+    logit range and point the same way (cosine)."""
+    assert len(got_lists) == len(want) and len(want) > 0
+    for a, b in zip(got_lists, want):
+        a = torch.tensor(a)
+        rel = (a - b).abs().max() / b.abs().max().clamp_min(1e-6)
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=0)
+        assert rel <= 3e-2 and cos >= 0.999, (float(rel), float(cos))
+
+
 def test_symmetric_memory_collectives_match_nccl():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("symm", 2, d, device="cuda", timeout=600)
@@ -83,14 +116,13 @@ def test_tensor_parallel_engine_two_gpus_matches_one_gpu():
         cfgj["torch_dtype"] = "bfloat16"
         json.dump(cfgj, open(os.path.join(d, "model", "config.json"), "w"))
         json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "capture_logits"), "w").close()
         res = run_ranks("tp_engine", 2, d, device="cuda", timeout=300)
         one = LLM(model=os.path.join(d, "model"), device="cuda", max_num_seqs=4, max_num_batched_tokens=64,
                   max_model_len=256, block_size=16, num_gpu_blocks=64)
-        want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+        want_logits = _first_logits(one, prompts)
     assert res[0]["tokens"] == res[1]["tokens"]
-    # bf16 partial sums differ in rounding between 1 and 2 GPUs: require the first tokens to agree
-    agree = sum(a[:2] == b[:2] for a, b in zip(res[0]["tokens"], want))
-    assert agree >= 2
+    _assert_first_logits_close(res[0]["first_logits"], want_logits)
 
 
 def test_tensor_parallel_prefill_on_token_sharded_stream_matches_one_gpu():
@@ -114,10 +146,10 @@ def test_tensor_parallel_prefill_on_token_sharded_stream_matches_one_gpu():
         json.dump(cfgj, open(os.path.join(d, "model", "config.json"), "w"))
         json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
         open(os.path.join(d, "long_prompts"), "w").close()
+        open(os.path.join(d, "capture_logits"), "w").close()
         res = run_ranks("tp_engine", 2, d, device="cuda", timeout=300)
         one = LLM(model=os.path.join(d, "model"), device="cuda", max_num_seqs=4, max_num_batched_tokens=256,
                   max_model_len=512, block_size=16, num_gpu_blocks=64)
-        want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+        want_logits = _first_logits(one, prompts)
     assert res[0]["tokens"] == res[1]["tokens"]
-    agree = sum(a[:2] == b[:2] for a, b in zip(res[0]["tokens"], want))
-    assert agree >= 1, (res[0]["tokens"], want)
+    _assert_first_logits_close(res[0]["first_logits"], want_logits)
