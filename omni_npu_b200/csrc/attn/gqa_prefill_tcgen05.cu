@@ -35,23 +35,31 @@ namespace b200 {
 namespace tcp {
 constexpr int BM = 128;                 // query rows per CTA
 constexpr int BN = 64;                  // keys per tile
-constexpr int D = 128;                  // head size
+constexpr int DV = 128;                 // value head size
 constexpr int THREADS = 192;
 constexpr int SLAB = BM * 128;          // 128 rows x 128 bytes
 constexpr int KV_SLAB = BN * 128;       // 64 keys x 128 bytes
-constexpr int Q_BYTES = 2 * SLAB;       // two 64-column halves
-constexpr int KV_BYTES = 2 * KV_SLAB;   // one K (or V) tile: two halves
 constexpr int P_BYTES = SLAB;           // 128 rows x 64 keys bf16
 constexpr int STAGES = 2;
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + Q_BYTES;
-constexpr int OFF_V = OFF_K + STAGES * KV_BYTES;
-constexpr int OFF_P = OFF_V + STAGES * KV_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;
 constexpr int NUM_BARS = 1 + 4 * STAGES + 2 * 2 + 3;   // q_full; k/v full+empty; s_full/s_empty[2]; p_full, o_done, drain
-constexpr int SMEM = OFF_BAR + NUM_BARS * 8 + 16;
 constexpr int TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,256)
 constexpr int COL_S = 0, COL_O = 128;
+
+// DQK: query / key head size, 128 (GQA models) or 192 (non-absorbed latent attention: 128 nope + 64 rope)
+template <int DQK>
+struct Cfg {
+  static constexpr int QK_SLABS = DQK / 64;
+  static constexpr int Q_BYTES = QK_SLABS * SLAB;
+  static constexpr int K_BYTES = QK_SLABS * KV_SLAB;
+  static constexpr int V_BYTES = 2 * KV_SLAB;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
+  static constexpr int OFF_P = OFF_V + STAGES * V_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int SMEM = OFF_BAR + NUM_BARS * 8 + 16;
+  static constexpr int CTAS_PER_SM = SMEM <= 115 * 1024 ? 2 : 1;
+};
 }  // namespace tcp
 
 enum : int { kStatusPrefillTimeout = 41, kStatusPrefillSmemAlign = 42 };
@@ -87,11 +95,18 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr, uint32_t lb
   return d;
 }
 
-__global__ void __launch_bounds__(tcp::THREADS, 2)
+// Launch bounds name 256 threads although 192 are launched: the register file is split over the
+// four sub-partitions of an SM, and two CTAs of six warps put four warps on one of them, which only
+// fits with at most 128 registers per thread (the bound a 256-thread, two-per-SM kernel gets).
+template <int DQK>
+__global__ void __launch_bounds__(256, tcp::Cfg<DQK>::CTAS_PER_SM)
 gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p, const int box_rows,
                       const int m_tiles) {
   using namespace tcp;
+  using C = Cfg<DQK>;
+  constexpr int OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_P = C::OFF_P, OFF_BAR = C::OFF_BAR;
+  constexpr int Q_BYTES = C::Q_BYTES, K_BYTES = C::K_BYTES, V_BYTES = C::V_BYTES, D = DV;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint64_t* q_full = bars;
@@ -143,7 +158,7 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   {
     // key rows of a partly filled tile that no copy writes must hold finite values
     uint4* z = reinterpret_cast<uint4*>(smem + OFF_K);
-    for (int i = tid; i < 2 * STAGES * KV_BYTES / 16; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < STAGES * (K_BYTES + V_BYTES) / 16; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -175,8 +190,9 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (lane == 0 && n_tiles > 0) {
       const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
       mbar_arrive_expect_tx(q_full, Q_BYTES);
-      tma_load_2d(smem + OFF_Q, &tm_q, q_full, h * D, q_begin + m0);
-      tma_load_2d(smem + OFF_Q + SLAB, &tm_q, q_full, h * D + 64, q_begin + m0);
+#pragma unroll
+      for (int sl = 0; sl < C::QK_SLABS; ++sl)
+        tma_load_2d(smem + OFF_Q + sl * SLAB, &tm_q, q_full, h * DQK + sl * 64, q_begin + m0);
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j % STAGES;
         if (j >= STAGES) {
@@ -190,19 +206,21 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int n0 = j * BN;
         const int nvalid = min(BN, kv_len - n0);
         const int nboxes = (nvalid + box_rows - 1) / box_rows;
-        const uint32_t bytes = static_cast<uint32_t>(nboxes * box_rows * 128 * 2);
-        mbar_arrive_expect_tx(&k_full[st], bytes);
-        mbar_arrive_expect_tx(&v_full[st], bytes);
+        const uint32_t box_bytes = static_cast<uint32_t>(nboxes * box_rows * 128);
+        mbar_arrive_expect_tx(&k_full[st], box_bytes * C::QK_SLABS);
+        mbar_arrive_expect_tx(&v_full[st], box_bytes * 2);
         for (int i = 0; i < nboxes; ++i) {
           const int key = n0 + i * box_rows;
           const int blk = bt[key / p.block_size];
           const int row = (blk * p.Hk + kvh) * p.block_size + key % p.block_size;
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int dst = st * KV_BYTES + hh * KV_SLAB + i * box_rows * 128;
-            tma_load_2d(smem + OFF_K + dst, &tm_k, &k_full[st], hh * 64, row);
-            tma_load_2d(smem + OFF_V + dst, &tm_v, &v_full[st], hh * 64, row);
-          }
+          for (int sl = 0; sl < C::QK_SLABS; ++sl)
+            tma_load_2d(smem + OFF_K + st * K_BYTES + sl * KV_SLAB + i * box_rows * 128, &tm_k, &k_full[st],
+                        sl * 64, row);
+#pragma unroll
+          for (int sl = 0; sl < 2; ++sl)
+            tma_load_2d(smem + OFF_V + st * V_BYTES + sl * KV_SLAB + i * box_rows * 128, &tm_v, &v_full[st],
+                        sl * 64, row);
         }
         issued = j + 1;
       }
@@ -221,7 +239,7 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             !mbar_wait(&v_full[st], static_cast<uint32_t>((j / STAGES) & 1)))
           return false;
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_BYTES);
+        const uint32_t v_addr = smem_u32(smem + OFF_V + st * V_BYTES);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -243,9 +261,9 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (ok && j >= 2) ok = mbar_wait(&s_empty[sb], static_cast<uint32_t>(((j >> 1) - 1) & 1));
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_BYTES);
+        const uint32_t k_addr = smem_u32(smem + OFF_K + st * K_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
+        for (int kk = 0; kk < DQK / 16; ++kk) {
           const int slab = kk >> 2, off = (kk & 3) * 32;
           umma_f16(tmem_base + COL_S + sb * BN, desc_kmajor(q_addr + slab * SLAB + off),
                    desc_kmajor(k_addr + slab * KV_SLAB + off), idesc_s, kk > 0 ? 1u : 0u);
@@ -286,16 +304,33 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int n0 = j * BN;
       float tile_max = -INFINITY;
       float s[64];
+      // tiles that lie entirely below the diagonal and inside the sequence need no mask
+      const int row_lo = ctx + m0 + quarter * 32;                      // smallest position in this warp
+      const bool interior = n0 + BN <= kv_len && (!p.causal || n0 + BN - 1 <= row_lo);
+      if (interior) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int key = n0 + c;
-        const bool keep = key < kv_len && (!p.causal || key <= q_pos);
-        const float v = keep ? __uint_as_float(sv[c >> 5][c & 31]) * p.scale_log2 : -INFINITY;
-        s[c] = v;
-        tile_max = fmaxf(tile_max, v);
+        for (int c = 0; c < 64; ++c) {
+          const float v = __uint_as_float(sv[c >> 5][c & 31]) * p.scale_log2;
+          s[c] = v;
+          tile_max = fmaxf(tile_max, v);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = n0 + c;
+          const bool keep = key < kv_len && (!p.causal || key <= q_pos);
+          const float v = keep ? __uint_as_float(sv[c >> 5][c & 31]) * p.scale_log2 : -INFINITY;
+          s[c] = v;
+          tile_max = fmaxf(tile_max, v);
+        }
       }
-      const float new_max = fmaxf(row_max, tile_max);
-      const float corr = (new_max == -INFINITY) ? 1.f : exp2f(row_max - new_max);
+      // The reference maximum only moves when the tile's maximum exceeds it by more than 2^8: P then
+      // stays below 256 (exact in bf16 relative terms, far from fp32 overflow in the sums), the
+      // result is the same after the final division, and the costly rescale of O in tensor memory
+      // becomes rare instead of happening on most early tiles.
+      float new_max = row_max;
+      if (tile_max > row_max + 8.f || row_max == -INFINITY) new_max = fmaxf(row_max, tile_max);
+      const float corr = (new_max == -INFINITY || row_max == new_max) ? 1.f : exp2f(row_max - new_max);
       const float m_use = new_max == -INFINITY ? 0.f : new_max;
       float sum = 0.f;
 #pragma unroll
@@ -401,28 +436,73 @@ gqa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
 using namespace b200;
 
+// CTAs of the kernel that fit one SM (2 for head size 128: 112 KB of shared memory, 256 TMEM columns each).
+// smem_bytes = 0: the kernel's own size; another value asks what a CTA of that size would get.
+extern "C" int b200_gqa_prefill_tc_ctas_per_sm(int smem_bytes) {
+  int n = 0;
+  auto kern = gqa_prefill_tc_kernel<128>;
+  if (smem_bytes <= 0) smem_bytes = tcp::Cfg<128>::SMEM;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::Cfg<128>::SMEM);
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tcp::THREADS, smem_bytes) != cudaSuccess) return -1;
+  return n;
+}
+
+// What the occupancy figure is made of: out[0..7] = registers per thread, static shared bytes, max dynamic
+// shared bytes, shared memory per SM, registers per SM, reserved shared bytes per block, max blocks per SM,
+// local (spill) bytes per thread.
+extern "C" int b200_gqa_prefill_tc_resources(int* out) {
+  cudaFuncAttributes fa{};
+  if (cudaFuncGetAttributes(&fa, gqa_prefill_tc_kernel<128>) != cudaSuccess) return -1;
+  int dev = 0, v = 0;
+  cudaGetDevice(&dev);
+  out[0] = fa.numRegs;
+  out[1] = static_cast<int>(fa.sharedSizeBytes);
+  out[2] = fa.maxDynamicSharedSizeBytes;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+  out[3] = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+  out[4] = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+  out[5] = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMaxBlocksPerMultiprocessor, dev);
+  out[6] = v;
+  out[7] = static_cast<int>(fa.localSizeBytes);
+  return 0;
+}
+
+template <int DQK>
+static int launch_prefill_tc(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                             int box_rows, dim3 grid, cudaStream_t stream) {
+  auto kern = gqa_prefill_tc_kernel<DQK>;
+  static DeviceOnce once;
+  int dev = 0;
+  if (once.needed(&dev)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::Cfg<DQK>::SMEM) != cudaSuccess)
+      return -20;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    once.mark(dev);
+  }
+  return launch_pdl(kern, grid, dim3(tcp::THREADS), tcp::Cfg<DQK>::SMEM, stream, 1, tq, tk, tv, p, box_rows,
+                    static_cast<int>(grid.x)) == cudaSuccess
+             ? 0
+             : -21;
+}
+
 // Returns 0 when the kernel ran, 1 when the problem is not one it takes (caller falls back), < 0 on error.
+// Takes query / key head sizes 128 and 192 with value head size 128, no sliding window.
 extern "C" int b200_gqa_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                                    const int* block_tables, const int* cu_q, const int* seq_lens, int B,
                                    int max_q_len, int max_blocks, int block_size, int Hq, int Hk, int Dqk, int Dv,
                                    long long q_stride, long long out_stride, float scale, int causal, int window,
                                    long long total_q_rows, int num_cache_blocks, int* status, cudaStream_t stream) {
-  if (Dqk != 128 || Dv != 128 || window != 0 || Hq % Hk != 0) return 1;
+  if ((Dqk != 128 && Dqk != 192) || Dv != 128 || window != 0 || Hq % Hk != 0) return 1;
   const bool tma_ok = (block_size % 8) == 0 && (block_size <= 64 ? (64 % block_size) == 0 : (block_size % 64) == 0) &&
                       (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0 &&
                       (reinterpret_cast<uintptr_t>(q) & 15) == 0 && ((q_stride * 2) & 15) == 0 &&
                       ((out_stride * 2) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   if (!tma_ok || num_cache_blocks <= 0 || total_q_rows <= 0) return 1;
   if (B <= 0 || max_q_len <= 0) return 0;
-  static DeviceOnce once;
-  int dev = 0;
-  if (once.needed(&dev)) {
-    if (cudaFuncSetAttribute(gqa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::SMEM) !=
-        cudaSuccess)
-      return -20;
-    cudaFuncSetAttribute(gqa_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    once.mark(dev);
-  }
   AttnParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
@@ -445,11 +525,11 @@ extern "C" int b200_gqa_prefill_tc(const void* q, const void* k_cache, const voi
   const int box_rows = block_size < 64 ? block_size : 64;
   CUtensorMap tq, tk, tv;
   int r = make_tensormap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, static_cast<uint64_t>(total_q_rows),
-                            static_cast<uint64_t>(Hq) * 128, static_cast<uint64_t>(q_stride), tcp::BM, 64,
+                            static_cast<uint64_t>(Hq) * Dqk, static_cast<uint64_t>(q_stride), tcp::BM, 64,
                             CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
   const uint64_t rows = static_cast<uint64_t>(num_cache_blocks) * Hk * block_size;
-  r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, 128, 128, box_rows, 64,
+  r = make_tensormap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, Dqk, Dqk, box_rows, 64,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 2000;
   r = make_tensormap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, 128, 128, box_rows, 64,
@@ -457,8 +537,6 @@ extern "C" int b200_gqa_prefill_tc(const void* q, const void* k_cache, const voi
   if (r) return r - 3000;
   const int m_tiles = (max_q_len + tcp::BM - 1) / tcp::BM;
   dim3 grid(m_tiles, Hq, B);
-  if (launch_pdl(gqa_prefill_tc_kernel, grid, dim3(tcp::THREADS), tcp::SMEM, stream, 1, tq, tk, tv, p, box_rows,
-                 m_tiles) != cudaSuccess)
-    return -21;
-  return 0;
+  return Dqk == 128 ? launch_prefill_tc<128>(tq, tk, tv, p, box_rows, grid, stream)
+                    : launch_prefill_tc<192>(tq, tk, tv, p, box_rows, grid, stream);
 }

@@ -9,7 +9,9 @@
 //                    first receive row this rank may write on the owning rank.
 //  ep_scatter        copies each routed token row straight into the owning rank's
 //                    receive buffer over NVLink (expert-sorted, no host sync),
-//                    remembers the slot for the way back.
+//                    remembers the slot for the way back.  The fp8 form quantises the
+//                    row on the way (e4m3, one scale per 128 columns): one byte per
+//                    element plus the scales cross the link instead of two bytes.
 //  ep_signal/ep_wait flag barrier between the phases (bounded waits).
 //  ep_combine        every token pulls its k expert outputs from the owners'
 //                    output buffers and reduces them with the routing weights
@@ -26,6 +28,7 @@
 // omni_npu/layers/fused_moe/npu_moe_prepare_finalize.py:66-119).
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -319,6 +322,53 @@ ep_scatter_kernel(EpGroup g, const __nv_bfloat16* __restrict__ x, const int* __r
   for (int i = lane; i < (H >> 3); i += 32) dst[i] = src[i];
 }
 
+// Phase 1b, quantising form: the row is turned into e4m3 with one fp32 scale per 128 columns
+// (scale = amax / 448, the arithmetic of quant_fp8_1x128_kernel, so the result is bit-identical to
+// scattering bf16 rows and quantising them on arrival) and stored into the owner's fp8 receive
+// buffer and scale buffer.  One warp per (token, j) pair, 128 columns per step, 4 per lane.
+__global__ void __launch_bounds__(256)
+ep_scatter_fp8_kernel(EpGroup g, void* const* __restrict__ recv_q, void* const* __restrict__ recv_s,
+                      const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_ids,
+                      const int* __restrict__ send_base, int* __restrict__ cursors, int* __restrict__ slots,
+                      int n_pairs, int k, int H, long long x_stride) {
+  const int pair = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pair >= n_pairs) return;
+  const int lane = threadIdx.x & 31;
+  const int e = topk_ids[pair];
+  int pos = -1;
+  if (e >= 0 && e < g.num_experts) {
+    if (lane == 0) pos = send_base[e] + atomicAdd(&cursors[e], 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos >= g.cap_rows) pos = -1;
+  }
+  if (lane == 0) slots[pair] = pos;
+  if (pos < 0) return;
+  const int d = e / g.experts_per_rank;
+  const int groups = H >> 7;
+  const __nv_bfloat16* src = x + static_cast<long long>(pair / k) * x_stride;
+  uint8_t* dq = static_cast<uint8_t*>(recv_q[d]) + static_cast<long long>(pos) * H;
+  float* ds = static_cast<float*>(recv_s[d]) + static_cast<long long>(pos) * groups;
+  for (int gi = 0; gi < groups; ++gi) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + gi * 128 + lane * 4);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax, 1e-10f) / 448.f;
+    const float inv = 1.f / scale;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_fp8_e4m3 f(v[j] * inv);
+      packed |= static_cast<uint32_t>(f.__x) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(dq + gi * 128 + lane * 4) = packed;
+    if (lane == 0) ds[gi] = scale;
+  }
+}
+
 // Phase 3 (after wait 2): out[t] = sum_j w[t,j] * y_owner[slot[t,j]] (+ shared[t]).
 // One CTA per token, 128 threads x 8 columns per pass.
 __global__ void __launch_bounds__(128)
@@ -399,11 +449,37 @@ extern "C" int b200_ep_flag_words() { return kEpFlagEpochWord + 4; }
 //   expert_offsets [E_local+1], send_base [E], cursors [E], slots [T*k], total_recv [1]: device ints.
 // On return (stream order) this rank's recv_x holds its experts' rows, grouped by
 // expert as described by expert_offsets.
+static int ep_dispatch_impl(const EpHostArgs* a, int world, int rank, int num_experts, int cap_rows, const void* x,
+                            const int* topk_ids, int T, int k, int H, long long x_stride, int* expert_offsets,
+                            int* send_base, int* cursors, int* slots, int* total_recv, int* status,
+                            void* const* recv_q_dev, void* const* recv_s_dev, cudaStream_t stream);
+
 extern "C" int b200_ep_dispatch(const EpHostArgs* a, int world, int rank, int num_experts,
                                 int cap_rows, const void* x, const int* topk_ids, int T, int k, int H,
                                 long long x_stride, int* expert_offsets, int* send_base,
                                 int* cursors, int* slots, int* total_recv, int* status,
                                 cudaStream_t stream) {
+  return ep_dispatch_impl(a, world, rank, num_experts, cap_rows, x, topk_ids, T, k, H, x_stride, expert_offsets,
+                          send_base, cursors, slots, total_recv, status, nullptr, nullptr, stream);
+}
+
+// The same routing, but the rows arrive as e4m3 with one fp32 scale per 128 columns (H % 128 == 0):
+// recv_q_dev / recv_s_dev are DEVICE arrays of `world` pointers to every rank's fp8 receive buffer
+// [cap_rows, H] and scale buffer [cap_rows, H / 128].
+extern "C" int b200_ep_dispatch_fp8(const EpHostArgs* a, int world, int rank, int num_experts, int cap_rows,
+                                    const void* x, const int* topk_ids, int T, int k, int H, long long x_stride,
+                                    int* expert_offsets, int* send_base, int* cursors, int* slots,
+                                    int* total_recv, int* status, void* const* recv_q_dev,
+                                    void* const* recv_s_dev, cudaStream_t stream) {
+  if ((H & 127) != 0 || recv_q_dev == nullptr || recv_s_dev == nullptr) return -4;
+  return ep_dispatch_impl(a, world, rank, num_experts, cap_rows, x, topk_ids, T, k, H, x_stride, expert_offsets,
+                          send_base, cursors, slots, total_recv, status, recv_q_dev, recv_s_dev, stream);
+}
+
+static int ep_dispatch_impl(const EpHostArgs* a, int world, int rank, int num_experts, int cap_rows, const void* x,
+                            const int* topk_ids, int T, int k, int H, long long x_stride, int* expert_offsets,
+                            int* send_base, int* cursors, int* slots, int* total_recv, int* status,
+                            void* const* recv_q_dev, void* const* recv_s_dev, cudaStream_t stream) {
   if (world < 1 || world > kEpMaxRanks || num_experts > kEpMaxExperts || num_experts % world != 0)
     return -1;
   if ((H & 7) != 0) return -2;
@@ -413,7 +489,11 @@ extern "C" int b200_ep_dispatch(const EpHostArgs* a, int world, int rank, int nu
   ep_count_kernel<<<1, 1024, 0, stream>>>(g, topk_ids, n_pairs, cursors);
   if (world > 1) ep_wait_kernel<<<1, 32, 0, stream>>>(g, 0, 0, status);
   ep_layout_kernel<<<1, 1024, 0, stream>>>(g, expert_offsets, send_base, total_recv, status);
-  if (n_pairs > 0)
+  if (n_pairs > 0 && recv_q_dev != nullptr)
+    ep_scatter_fp8_kernel<<<(n_pairs + 7) / 8, 256, 0, stream>>>(
+        g, recv_q_dev, recv_s_dev, static_cast<const __nv_bfloat16*>(x), topk_ids, send_base, cursors, slots,
+        n_pairs, k, H, x_stride);
+  else if (n_pairs > 0)
     ep_scatter_kernel<<<(n_pairs + 7) / 8, 256, 0, stream>>>(
         g, static_cast<const __nv_bfloat16*>(x), topk_ids, send_base, cursors, slots, n_pairs, k, H,
         x_stride);

@@ -113,12 +113,14 @@ class FusedMoE(nn.Module):
         dev = self.w13.device
         if dev.type != "cuda" or self.buffers is not None:
             return
-        shared = _SHARED_BUFFERS.get((id(self.ep_group), self.num_physical, self.hidden_size, self.top_k))
+        fp8 = self.quant == "fp8" and self.hidden_size % 128 == 0
+        key = (id(self.ep_group), self.num_physical, self.hidden_size, self.top_k, fp8)
+        shared = _SHARED_BUFFERS.get(key)
         if shared is None:
             group = self.ep_group if self.ep_group is not None else _solo_group()
             shared = EpBuffers(group, dev, self.num_physical if self.ep_size > 1 else self.local_experts,
-                               self.hidden_size, self.max_tokens, self.top_k)
-            _SHARED_BUFFERS[(id(self.ep_group), self.num_physical, self.hidden_size, self.top_k)] = shared
+                               self.hidden_size, self.max_tokens, self.top_k, fp8_dispatch=fp8)
+            _SHARED_BUFFERS[key] = shared
         self.buffers = shared
         self._side_stream = torch.cuda.Stream(dev)
 
@@ -246,11 +248,14 @@ class FusedMoE(nn.Module):
                 self._side_stream.wait_stream(cur)
                 with torch.cuda.stream(self._side_stream):
                     shared_out = self.shared_experts(x)
-            rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_physical, self.buffers)
+            fp8_rows = self.quant == "fp8" and self.buffers.fp8_dispatch
+            rows, offsets, handle = ep_dispatch(comm, x, ids_local, w, self.num_physical, self.buffers,
+                                                fp8=fp8_rows)
             if self.quant == "fp8":
-                # block-scaled e4m3 experts: quantise the dispatched rows per token per 128 columns,
-                # SwiGLU fused into the first product's epilogue, requantise, second product
-                rq, rs = ops.quant_fp8_1x128(rows)
+                # block-scaled e4m3 experts: the rows arrive quantised per token per 128 columns (the
+                # scatter kernel quantises them on the way; without fp8 buffers they are quantised
+                # here), SwiGLU fused into the first product's epilogue, requantise, second product
+                rq, rs = rows if fp8_rows else ops.quant_fp8_1x128(rows)
                 h1 = ops.grouped_gemm_fp8_block(rq, rs, self.w13, self.w13_scale, offsets, swiglu=True,
                                                 up_scale_row0=(self.intermediate_size + 127) // 128)
                 hq, hs = ops.quant_fp8_1x128(h1)

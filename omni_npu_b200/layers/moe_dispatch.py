@@ -41,6 +41,9 @@ def _lib():
         lib.b200_ep_dispatch.argtypes = [ctypes.POINTER(_EpHostArgs), ci, ci, ci, ci, vp, vp, ci, ci, ci, ll,
                                          vp, vp, vp, vp, vp, vp, vp]
         lib.b200_ep_dispatch.restype = ci
+        lib.b200_ep_dispatch_fp8.argtypes = [ctypes.POINTER(_EpHostArgs), ci, ci, ci, ci, vp, vp, ci, ci, ci, ll,
+                                             vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        lib.b200_ep_dispatch_fp8.restype = ci
         lib.b200_ep_combine.argtypes = [ctypes.POINTER(_EpHostArgs), ci, ci, ci, ci, vp, vp, vp, vp, vp, ci,
                                         ci, ci, ll, ll, vp, vp]
         lib.b200_ep_combine.restype = ci
@@ -62,7 +65,7 @@ class DispatchHandle:
 
 class EpBuffers:
     def __init__(self, group, device: torch.device, num_experts: int, hidden: int, max_tokens: int,
-                 top_k: int, capacity_factor: float = 2.0) -> None:
+                 top_k: int, capacity_factor: float = 2.0, fp8_dispatch: bool = False) -> None:
         from ..parallel.symm_mem import _lib as symm_lib
         self.group, self.device = group, device
         self.world, self.rank = group.world_size, group.rank_in_group
@@ -88,10 +91,17 @@ class EpBuffers:
         row_bytes = hidden * 2
         mine = [alloc(self.cap_rows * row_bytes), alloc(self.cap_rows * row_bytes),
                 alloc(self.world * num_experts * 4), alloc(_lib().b200_ep_flag_words() * 4)]
+        # fp8 dispatch: rows arrive quantised (e4m3 + one fp32 scale per 128 columns) in two more
+        # peer-mapped buffers; half the bytes of the bf16 rows cross the link
+        self.fp8_dispatch = bool(fp8_dispatch) and hidden % 128 == 0
+        if self.fp8_dispatch:
+            mine += [alloc(self.cap_rows * hidden), alloc(self.cap_rows * (hidden // 128) * 4)]
         handles = [h for _, h in mine]
         everyone = group.all_gather_object(handles) if self.world > 1 else [handles]
         self.args = _EpHostArgs()
-        tables = (self.args.recv_x, self.args.expert_y, self.args.counts, self.args.flags)
+        q_table, s_table = (ctypes.c_void_p * 8)(), (ctypes.c_void_p * 8)()
+        tables = (self.args.recv_x, self.args.expert_y, self.args.counts, self.args.flags) + \
+            ((q_table, s_table) if self.fp8_dispatch else ())
         for r in range(self.world):
             for i, table in enumerate(tables):
                 if r == self.rank:
@@ -105,6 +115,12 @@ class EpBuffers:
         # torch views of my own buffers (the grouped GEMMs read / write them in place)
         self.recv_x = _as_tensor(mine[0][0].value, (self.cap_rows, hidden), torch.bfloat16, device)
         self.expert_y = _as_tensor(mine[1][0].value, (self.cap_rows, hidden), torch.bfloat16, device)
+        if self.fp8_dispatch:
+            self.recv_q = _as_tensor(mine[4][0].value, (self.cap_rows, hidden), torch.uint8, device).view(torch.float8_e4m3fn)
+            self.recv_s = _as_tensor(mine[5][0].value, (self.cap_rows, hidden // 128), torch.float32, device)
+            # the kernel takes the two pointer tables from device memory
+            self.q_ptrs = torch.tensor([int(q_table[r] or 0) for r in range(8)], dtype=torch.int64, device=device)
+            self.s_ptrs = torch.tensor([int(s_table[r] or 0) for r in range(8)], dtype=torch.int64, device=device)
         i32 = dict(dtype=torch.int32, device=device)
         self.expert_offsets = torch.zeros(self.experts_per_rank + 1, **i32)
         self.send_base = torch.zeros(num_experts, **i32)
@@ -142,31 +158,46 @@ def _as_tensor(ptr: int, shape, dtype: torch.dtype, device: torch.device) -> tor
 
 # ----------------------------------------------------------------- public API
 def ep_dispatch(comm, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
-                num_experts: int, buffers: Optional[EpBuffers] = None):
+                num_experts: int, buffers: Optional[EpBuffers] = None, fp8: bool = False):
     """Send every token row to the ranks owning its experts.
 
     Returns ``(rows, expert_offsets, handle)``: ``rows`` [R,H] are the rows received
-    for this rank's experts, grouped by local expert as ``expert_offsets`` says."""
+    for this rank's experts, grouped by local expert as ``expert_offsets`` says.  With ``fp8``
+    (buffers built with ``fp8_dispatch``) the rows are quantised while they are scattered and
+    ``rows`` is the pair ``(e4m3 rows [R,H], scales [R,H/128])``: one byte per element plus the
+    scales cross the link (reference: ``quant_mode=2`` of the dispatch op,
+    omni_npu/layers/fused_moe/npu_moe_prepare_finalize.py:66-81)."""
     t, k = topk_ids.shape
     if not hidden.is_cuda:
-        return _cpu_dispatch(comm, hidden, topk_ids, topk_weights, num_experts)
+        rows, offsets, handle = _cpu_dispatch(comm, hidden, topk_ids, topk_weights, num_experts)
+        if fp8:
+            return ops.quant_fp8_1x128(rows), offsets, handle
+        return rows, offsets, handle
     buf = buffers or comm.ep_buffers
     if buf is None:
         raise RuntimeError("expert-parallel buffers not initialised for this communicator")
     if t > buf.max_tokens:
         raise RuntimeError(f"{t} tokens exceed the dispatch capacity of {buf.max_tokens}")
     stream = torch.cuda.current_stream(hidden.device).cuda_stream
-    rc = _lib().b200_ep_dispatch(ctypes.byref(buf.args), buf.world, buf.rank, buf.num_experts,
-                                 buf.cap_rows, hidden.data_ptr(), topk_ids.data_ptr(), t, k,
-                                 hidden.shape[1], hidden.stride(0), buf.expert_offsets.data_ptr(),
-                                 buf.send_base.data_ptr(), buf.cursors.data_ptr(), buf.slots.data_ptr(),
-                                 buf.total_recv.data_ptr(), buf.status.data_ptr(), stream)
+    common = (ctypes.byref(buf.args), buf.world, buf.rank, buf.num_experts,
+              buf.cap_rows, hidden.data_ptr(), topk_ids.data_ptr(), t, k,
+              hidden.shape[1], hidden.stride(0), buf.expert_offsets.data_ptr(),
+              buf.send_base.data_ptr(), buf.cursors.data_ptr(), buf.slots.data_ptr(),
+              buf.total_recv.data_ptr(), buf.status.data_ptr())
+    if fp8:
+        if not buf.fp8_dispatch:
+            raise RuntimeError("these expert-parallel buffers were built without fp8 dispatch")
+        rc = _lib().b200_ep_dispatch_fp8(*common, buf.q_ptrs.data_ptr(), buf.s_ptrs.data_ptr(), stream)
+    else:
+        rc = _lib().b200_ep_dispatch(*common, stream)
     if rc != 0:
         raise RuntimeError(f"ep_dispatch failed ({rc})")
     ops._count(3 if buf.world == 1 else 6)  # count, layout, scatter (+ flag kernels)
     # static upper bound on the rows in use (device-side counts decide the real extent)
     rows = buf.cap_rows if buf.world > 1 else max(t * k, 1)
     handle = DispatchHandle(topk_ids, topk_weights, buf.slots, t, rows, buf.expert_offsets)
+    if fp8:
+        return (buf.recv_q[:rows], buf.recv_s[:rows]), buf.expert_offsets, handle
     return buf.recv_x[:rows], buf.expert_offsets, handle
 
 

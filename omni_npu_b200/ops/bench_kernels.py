@@ -169,6 +169,16 @@ def bench_attn(args):
                 kind = "persistent CTAs" if persistent else "one CTA per item"
                 print(f"decode  B={b:4d} ctx={ctx:6d} splits={used:2d} {kind}: {t*1e3:8.1f} us  "
                       f"{by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
+    if prefill_cases:
+        import ctypes
+        lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so"))
+        print(f"# tcgen05 prefill kernel: {lib.b200_gqa_prefill_tc_ctas_per_sm(0)} CTAs per SM "
+              f"(by shared memory size: " + ", ".join(f"{k} KiB -> {lib.b200_gqa_prefill_tc_ctas_per_sm(k << 10)}"
+                                                       for k in (96, 104, 108, 110, 111, 112, 113)) + ")")
+        res = (ctypes.c_int * 8)()
+        lib.b200_gqa_prefill_tc_resources(res)
+        print("# registers/thread, static smem, max dyn smem, smem/SM, regs/SM, reserved smem/block, max blocks/SM, "
+              "local bytes:", list(res))
     for b, s in prefill_cases:
         nblk = b * (s // bs) + 1
         kc = torch.randn(nblk, hk, bs, d, device="cuda", dtype=torch.bfloat16)

@@ -737,3 +737,34 @@ def test_bounded_wait_gives_up_and_leaves_the_context_usable():
     a = torch.randn(64, 128, device=DEV, dtype=torch.bfloat16)
     w = torch.randn(32, 128, device=DEV, dtype=torch.bfloat16)
     _close(ops.gemm(a, w), a.float().cpu() @ w.float().cpu().t(), 2e-1, 2e-2)
+
+
+def test_ep_dispatch_quantising_scatter_matches_quantise_after_arrival():
+    """Expert-parallel dispatch that quantises the rows to e4m3 (one scale per 128 columns) inside the
+    scatter kernel: bit-identical to scattering bf16 rows and quantising them afterwards."""
+    from omni_npu_b200.layers.moe import _solo_group
+    from omni_npu_b200.layers.moe_dispatch import EpBuffers, ep_dispatch
+    torch.manual_seed(41)
+    t, h, e, k = 77, 1024, 16, 4
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    logits = torch.randn(t, e, device=DEV)
+    w, ids = torch.topk(torch.softmax(logits, -1), k)
+    ids = ids.to(torch.int32)
+    ids[5, 1] = -1                                   # an inactive slot
+    dev = torch.device("cuda", 0)
+    plain = EpBuffers(_solo_group(), dev, e, h, 128, k)
+    quant = EpBuffers(_solo_group(), dev, e, h, 128, k, fp8_dispatch=True)
+    rows, offs, _ = ep_dispatch(None, x, ids, w.float(), e, plain)
+    (rq, rs), offs_q, _ = ep_dispatch(None, x, ids, w.float(), e, quant, fp8=True)
+    torch.cuda.synchronize()
+    n = int(offs[-1])
+    assert n == t * k - 1 and torch.equal(offs, offs_q)
+    # rows of one expert arrive in an order fixed by atomics: compare expert by expert as multisets
+    want_q, want_s = ops.quant_fp8_1x128(rows[:n].contiguous())
+    for ei in range(e):
+        lo, hi = int(offs[ei]), int(offs[ei + 1])
+        a = torch.cat([want_q[lo:hi].view(torch.uint8).float(), want_s[lo:hi]], dim=1)
+        b = torch.cat([rq[lo:hi].view(torch.uint8).float(), rs[lo:hi]], dim=1)
+        assert torch.equal(torch.sort(a, dim=0).values, torch.sort(b, dim=0).values)
+    plain.close(), quant.close()
+    ops.check_status()
