@@ -88,16 +88,26 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--model", default="llama-3-8b", choices=sorted(ARCHS))
-    ap.add_argument("--num-requests", type=int, default=256)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--num-requests", type=int, default=None)
+    ap.add_argument("--input-len", type=int, default=None)
+    ap.add_argument("--output-len", type=int, default=None)
     ap.add_argument("--max-num-seqs", type=int, default=128)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--expert-parallel", action="store_true")
     ap.add_argument("--with-plugin", action="store_true",
                     help="activate this repository's vLLM platform plugin instead of vLLM's CUDA platform")
     ap.add_argument("--out", default=None, help="also write the JSON line to this file")
-    return ap.parse_args()
+    args = ap.parse_args()
+    n, i, o = WORKLOADS[args.model]
+    args.num_requests = args.num_requests or n
+    args.input_len = args.input_len or i
+    args.output_len = args.output_len or o
+    return args
+
+
+# requests, input tokens, output tokens of the named serving configurations
+WORKLOADS = {"llama-3-8b": (256, 1024, 256), "deepseek-v2-lite": (512, 2048, 512),
+             "qwen3-30b-a3b": (1024, 4096, 256)}
 
 
 def main() -> None:

@@ -42,16 +42,26 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama-3-8b")
-    ap.add_argument("--num-requests", type=int, default=256)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--num-requests", type=int, default=None)
+    ap.add_argument("--input-len", type=int, default=None)
+    ap.add_argument("--output-len", type=int, default=None)
     ap.add_argument("--max-num-seqs", type=int, default=128)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--no-fused-collectives", action="store_true")
     ap.add_argument("--profile", default=None,
                     help="write a per-kernel time table (torch profiler, one extra untimed pass) to this file")
-    return ap.parse_args()
+    args = ap.parse_args()
+    n, i, o = WORKLOADS.get(args.model, WORKLOADS["llama-3-8b"])
+    args.num_requests = args.num_requests or n
+    args.input_len = args.input_len or i
+    args.output_len = args.output_len or o
+    return args
+
+
+# requests, input tokens, output tokens of the named serving configurations
+WORKLOADS = {"llama-3-8b": (256, 1024, 256), "deepseek-v2-lite": (512, 2048, 512),
+             "qwen3-30b-a3b": (1024, 4096, 256), "deepseek-v3.2": (256, 8192, 1024)}
 
 
 # ------------------------------------------------------------------ reference
@@ -158,8 +168,10 @@ def run_ours(args) -> None:
 
     mc = PRESETS[args.model]()
     max_len = args.input_len + args.output_len + 16
+    moe = getattr(mc, "num_experts", 0) > 0
     cfg = build_engine_config(
-        mc, tensor_parallel_size=args.gpus, max_num_seqs=args.max_num_seqs,
+        mc, tensor_parallel_size=args.gpus, enable_expert_parallel=moe and args.gpus > 1,
+        max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=max_len,
         block_size=args.block_size, device="cuda", seed=0,
         additional_config={"fused_collectives": not args.no_fused_collectives})
@@ -257,7 +269,7 @@ def run_ours(args) -> None:
                 "requests": args.num_requests, "input_len": args.input_len,
                 "output_len": args.output_len, "global_batch": args.max_num_seqs,
                 "seq_len": args.input_len + args.output_len, "kv_block": args.block_size,
-                "parallelism": f"tp{args.gpus}",
+                "parallelism": (f"ep{args.gpus}+tp{args.gpus}" if moe and args.gpus > 1 else f"tp{args.gpus}"),
                 "step_definition": "one pass of the full workload through LLM.generate",
                 "l2_policy": "inputs larger than L2: every engine step streams the weights "
                              "(16 GB / N) and the KV cache, far above the 126 MB L2",
@@ -287,9 +299,9 @@ def _stock_entry(args):
             table = json.load(f)
     except Exception:
         return None
-    same = (args.num_requests, args.input_len, args.output_len, args.max_num_seqs) == (256, 1024, 256, 128)
-    ent = table.get(args.model, {}).get(str(args.gpus)) if same or args.model != "llama-3-8b" else None
-    return ent
+    same = (args.num_requests, args.input_len, args.output_len) == WORKLOADS.get(args.model) and \
+        args.max_num_seqs == 128
+    return table.get(args.model, {}).get(str(args.gpus)) if same else None
 
 
 def _vs_stock(args, e2e_tok_s: float):

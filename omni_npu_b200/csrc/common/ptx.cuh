@@ -156,6 +156,21 @@ __device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t cluster_addr) {
   return v;
 }
 
+__device__ __forceinline__ void st_shared_cluster_f4(uint32_t cluster_addr, uint32_t x, uint32_t y, uint32_t z,
+                                                     uint32_t w) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(x), "r"(y), "r"(z),
+               "r"(w)
+               : "memory");
+}
+
+// The two halves of the cluster-wide barrier, for code that has work to do between them.
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+
 // All threads of all CTAs of the cluster meet here.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

@@ -37,6 +37,21 @@ namespace b200 {
 static constexpr int kBM = 128;          // rows of A per tile (UMMA M)
 static constexpr int kRowBytes = 128;    // bytes of K per stage row (one swizzle span)
 static constexpr int kThreads = 192;
+
+// Build with -DB200_GEMM_TIMELINE to record, per CTA, the global timer at eight points of the
+// kernel (entry, set-up done, first slab landed, last MMA issued, accumulator complete, partial
+// tiles of all K slices staged, output stored, exit); read them back with b200_gemm_timeline().
+#ifdef B200_GEMM_TIMELINE
+__device__ unsigned long long g_timeline[1024 * 8];
+__device__ __forceinline__ void timeline_mark(int i) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (blockIdx.x < 1024) g_timeline[blockIdx.x * 8 + i] = t;
+}
+#define B200_TL(i) timeline_mark(i)
+#else
+#define B200_TL(i)
+#endif
 static constexpr int kMaxExperts = 512;
 static constexpr int kRsPitch = 144;                 // bytes per staged row (64 bf16 columns + padding)
 static constexpr int kRsWarpBytes = 32 * kRsPitch;   // staging of one epilogue warp
@@ -188,10 +203,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int w_stage_bytes = p.BN * kRowBytes;
   uint8_t* smem_a = smem;
   uint8_t* smem_w = smem + p.stages * a_stage_bytes;
-  // staging for the cluster reduction: [128 rows][BN + 4] fp32
+  // staging for the cluster reduction: [source rank][rows of my band][BN] fp32 (128 rows in all)
   float* red_buf = reinterpret_cast<float*>(smem_w + p.stages * w_stage_bytes);
-  const int red_stride = p.BN + 4;
-  const int red_bytes = p.cluster_split ? kBM * red_stride * 4 : (p.rs_world > 1 ? 4 * kRsWarpBytes : 0);
+  const int red_bytes = p.cluster_split ? kBM * p.BN * 4 : (p.rs_world > 1 ? 4 * kRsWarpBytes : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes + red_bytes);
   uint64_t* full_bar = bars;                    // [stages]
   uint64_t* empty_bar = bars + p.stages;        // [stages]
@@ -208,6 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    B200_TL(0);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -217,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(&tmem_empty[0], 4);
     mbar_init(&tmem_empty[1], 4);
     mbar_init(drain_bar, 1);
-    mbar_init(red_ready, static_cast<uint32_t>(p.splits));
+    mbar_init(red_ready, static_cast<uint32_t>(kBM));       // one arrival per pushed row (splits x rows of my band)
     mbar_init(red_done, static_cast<uint32_t>(p.splits));
     s_flags[0] = 0;
     s_flags[1] = 0;
@@ -251,8 +266,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     cta_rank = static_cast<int>(cluster_ctarank());
     t_first = blockIdx.x / p.splits;
     t_stride = gridDim.x / p.splits;
-    cluster_sync_all();  // peers' barriers are initialised before anyone signals them
+    // peers' barriers must be initialised before anyone signals them: arrive now, wait right
+    // before this thread's first remote access (or at the end of its role)
+    cluster_arrive_release();
   }
+  if (threadIdx.x == 0) B200_TL(1);
   const uint32_t tmem_base = *tmem_base_slot;
   if constexpr (GROUPED) {
     total_mn_tiles = s_tile_prefix[p.num_experts] * p.num_n_blocks;
@@ -383,6 +401,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    __syncwarp();
+    if (p.cluster_split) cluster_wait_acquire();
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
@@ -419,6 +439,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           tc_fence_after_sync();
+          if (k == tc.k_begin) B200_TL(2);
           uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage * p.ksub) * a_slab_lo;
           uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * p.ksub) * w_slab_lo;
           for (int j = 0; j < ns; ++j) {
@@ -444,9 +465,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    __syncwarp();
+    if (p.cluster_split) cluster_wait_acquire();
   } else {
     // ------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    bool cluster_met = false;      // this thread has completed the cluster barrier opened at set-up
     int acc = 0;
     uint32_t acc_phase = 0;
     int cursor = 0;
@@ -560,44 +584,89 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         break;
       }
       tc_fence_after_sync();
+      if (threadIdx.x == 64) B200_TL(4);
       const int row = tc.m0 + quarter * 32 + lane;
       const bool row_ok = row < tc.m_end;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * p.acc_stride);
       if (p.cluster_split) {
-        // ---- split-K inside a cluster: stage my K slice's partial tile in shared
-        // memory, then every CTA sums a band of rows over all peers (DSMEM reads).
+        // ---- split-K inside a cluster.  Rows of the tile are dealt out in bands of kBM / splits,
+        // band b to cluster rank b.  Every thread holds one row of this CTA's partial tile and
+        // PUSHES it into the owner's staging slot for this rank (remote shared-memory stores, then a
+        // release arrival on the owner's barrier); the owner sums the slots out of its own shared
+        // memory.  No CTA reads a peer's memory, so the only round trip is the arrival.
+        // Staging: [source rank][row of the band][BN] fp32, the 16-byte chunks of a row rotated by
+        // the row index so that the 32 rows a warp writes at once fall into different banks.
         bool okc = true;
+        const bool last_tile = t + t_stride >= total_mn_tiles;
         if (tile_iter > 0) okc = mbar_wait_cluster(red_done, static_cast<uint32_t>((tile_iter - 1) & 1));
-        float* my_row = red_buf + static_cast<size_t>(quarter * 32 + lane) * red_stride;
-        if (okc) {
-          for (int c = 0; c < p.BN; c += 16) {
-            uint32_t r[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
-                  "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-                  "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(t_row + static_cast<uint32_t>(c))
-                : "memory");
-            tmem_ld_wait();
-            uint4* dst = reinterpret_cast<uint4*>(my_row + c);
+        if (!cluster_met) {
+          cluster_wait_acquire();
+          cluster_met = true;
+        }
+        const int rows_per = kBM / p.splits;
+        const int nch = p.BN >> 2;
+        {
+          const int my_row = quarter * 32 + lane;
+          const int owner = my_row / rows_per;
+          const int rl = my_row - owner * rows_per;
+          const int rot = rl % nch;
+          const uint32_t row_addr = mapa_shared(
+              smem_u32(red_buf) + static_cast<uint32_t>((cta_rank * rows_per + rl) * p.BN) * 4u,
+              static_cast<uint32_t>(owner));
+          if (okc) {
+            // 32 columns per TMEM load; the load of the next 32 is in flight while these are stored
+            // (one warp per scheduler runs this: every dependent instruction costs its full latency)
+            auto ld_cols = [&](uint32_t (&r)[32], int c) {
+              if (c + 32 <= p.BN) {
+                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c), r);
+              } else {
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                      "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                      "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(t_row + static_cast<uint32_t>(c))
+                    : "memory");
+              }
+            };
+            auto st_cols = [&](const uint32_t (&r)[32], int c) {
+              int ch = (c >> 2) + rot;
+              ch -= ch >= nch ? nch : 0;
+              const int n4 = (p.BN - c) >= 32 ? 8 : 4;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+              for (int i = 0; i < 8; ++i) {
+                if (i < n4) {
+                  st_shared_cluster_f4(row_addr + static_cast<uint32_t>(ch) * 16u, r[4 * i], r[4 * i + 1],
+                                       r[4 * i + 2], r[4 * i + 3]);
+                  ch = ch + 1 == nch ? 0 : ch + 1;
+                }
+              }
+            };
+            uint32_t ra[32], rb[32];
+            ld_cols(ra, 0);
+            for (int c = 0; c < p.BN; c += 64) {
+              tmem_ld_wait();
+              if (c + 32 < p.BN) ld_cols(rb, c + 32);
+              st_cols(ra, c);
+              if (c + 32 < p.BN) {
+                tmem_ld_wait();
+                if (c + 64 < p.BN) ld_cols(ra, c + 64);
+                st_cols(rb, c + 32);
+              }
+            }
           }
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) {
-          const uint32_t a = smem_u32(red_ready);
-          for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+          // the arrival is a release at cluster scope: the owner's acquire sees this row
+          if (okc) mbar_arrive_cluster(mapa_shared(smem_u32(red_ready), static_cast<uint32_t>(owner)));
+          if (threadIdx.x == 64) B200_TL(3);
         }
         okc = okc && mbar_wait_cluster(red_ready, static_cast<uint32_t>(tile_iter & 1));
         {
@@ -619,26 +688,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           *abort_flag = 1;
           break;
         }
+        if (threadIdx.x == 64) B200_TL(5);
         {
-          const int rows_per = (kBM + p.splits - 1) / p.splits;
           const int r_begin = cta_rank * rows_per;
-          const int r_count = max(0, min(kBM, r_begin + rows_per) - r_begin);
-          const int c4n = p.BN >> 2;
           const int et = threadIdx.x - 64;
-          const uint32_t red_base = smem_u32(red_buf);
-          for (int idx = et; idx < r_count * c4n; idx += 128) {
-            const int rl = r_begin + idx / c4n;
-            const int c = (idx % c4n) * 4;
-            const uint32_t off = static_cast<uint32_t>((rl * red_stride + c) * 4);
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s2 = 0; s2 < p.splits; ++s2) {
-              const float4 x = ld_shared_cluster_f4(mapa_shared(red_base + off, s2));
-              sum.x += x.x;
-              sum.y += x.y;
-              sum.z += x.z;
-              sum.w += x.w;
+          // item = (row of the band, 16-byte chunk); a thread walks items et, et + 128, ... without
+          // dividing: 128 = row_step * nch + ch_step
+          const int row_step = 128 / nch, ch_step = 128 - row_step * nch;
+          int rl = et / nch;
+          int chl = et - rl * nch;
+          int rrot = rl % nch;
+          const int rot_step = row_step % nch;
+          const int slot_floats = rows_per * p.BN;
+          for (; rl < rows_per; ) {
+            int chp = chl + rrot;
+            chp -= chp >= nch ? nch : 0;
+            const int c = chl * 4;
+            const float* src = red_buf + rl * p.BN + chp * 4;
+            float4 x[8];
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2)
+              if (s2 < p.splits) x[s2] = *reinterpret_cast<const float4*>(src + s2 * slot_floats);
+            float4 sum = x[0];
+#pragma unroll
+            for (int s2 = 1; s2 < 8; ++s2) {
+              if (s2 < p.splits) {
+                sum.x += x[s2].x;
+                sum.y += x[s2].y;
+                sum.z += x[s2].z;
+                sum.w += x[s2].w;
+              }
             }
-            const int orow = tc.m0 + rl;
+            const int rl_now = rl;
+            // next item of this thread
+            chl += ch_step;
+            rl += row_step;
+            rrot += rot_step;
+            if (chl >= nch) {
+              chl -= nch;
+              ++rl;
+              ++rrot;
+            }
+            rrot -= rrot >= nch ? nch : 0;
+            rrot -= rrot >= nch ? nch : 0;
+            const int orow = tc.m0 + r_begin + rl_now;
             const int col = tc.n0 + c;
             if (orow >= tc.m_end || col >= p.N) continue;
             float v[4] = {sum.x, sum.y, sum.z, sum.w};
@@ -686,10 +779,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) {
-          const uint32_t a = smem_u32(red_done);
-          for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
+        if (threadIdx.x == 64) B200_TL(6);
+        if (!last_tile) {
+          // the slots may be overwritten once every owner has finished this tile; after the last
+          // tile nobody signals, so no CTA touches a peer that may already have retired
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            const uint32_t a = smem_u32(red_done);
+            for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
+          }
         }
         ++tile_iter;
         continue;
@@ -940,6 +1038,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     // foreign blocks this CTA has not delivered its share of yet (fewer tiles than sources, or an abort)
     while (ag_next < p.ag_world) ag_step();
+    if (p.cluster_split && !cluster_met) cluster_wait_acquire();
   }
 
   // ------------------------------------------------------------- teardown
@@ -1037,9 +1136,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   }
-  // No CTA of a cluster may retire while a peer can still read its staging
-  // buffer or signal its barriers.
-  if (p.cluster_split) cluster_sync_all();
+  // Split-K in a cluster: a CTA's last remote accesses are the pushes and arrivals of its final
+  // tile, and their targets cannot retire before those have landed (they wait for them), so CTAs
+  // leave without meeting again.  After an abort a peer may still push into this CTA: stay until
+  // every other CTA of the cluster has arrived here or has exited.
+  if (p.cluster_split && *abort_flag) cluster_sync_all();
+  if (threadIdx.x == 0) B200_TL(7);
   if (warp == 1) {
     if (*abort_flag && lane == 0) {
       // Give MMAs still in flight a bounded time to retire before TMEM goes away.
@@ -1069,7 +1171,7 @@ static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 static constexpr int kRsStageBytes = 4 * kRsWarpBytes;
 static size_t red_bytes_for(int BN, int cluster_split) {
   if (cluster_split == 2) return kRsStageBytes;
-  return cluster_split ? static_cast<size_t>(kBM) * (BN + 4) * 4 : 0;
+  return cluster_split ? static_cast<size_t>(kBM) * BN * 4 : 0;
 }
 
 static size_t smem_bytes_for(int BN, int stages, int num_experts, int cluster_split = 0) {
@@ -1212,6 +1314,7 @@ static bool plan_small_m(int M, int N, int K, int elem_bytes, bool allow_split, 
     const int clusters = m_blocks * n_blocks;
     const int max_sp = (allow_split && bn <= 128) ? 8 : 1;
     for (int sp = 1; sp <= max_sp; ++sp) {
+      if (kBM % sp != 0) continue;            // row bands of the cluster reduction: 1, 2, 4 or 8 K slices
       const int per = (k_iters + sp - 1) / sp;
       if (sp > 1 && (per < 4 || (sp - 1) * per >= k_iters)) continue;
       const int stages = stages_for(bn, sp > 1);
@@ -1241,6 +1344,12 @@ static bool plan_small_m(int M, int N, int K, int elem_bytes, bool allow_split, 
 // Chooses tile width / split-K for a problem.  out_cluster = 1 means the splits run
 // as one thread-block cluster (no workspace needed); otherwise split-K uses the
 // caller's fp32 workspace (bytes) and per-tile counters.
+#ifdef B200_GEMM_TIMELINE
+extern "C" int b200_gemm_timeline(unsigned long long* host, int ctas) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline, sizeof(unsigned long long) * 8 * ctas));
+}
+#endif
+
 extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, int force_bn,
                                int force_splits, int* out_bn, int* out_splits,
                                size_t* out_ws_bytes, int* out_counters, int* out_cluster) {
@@ -1254,7 +1363,7 @@ extern "C" void b200_gemm_plan(int M, int N, int K, int elem_bytes, int swiglu, 
   if (force_splits > 0) {
     pl.splits = force_splits;
     // a forced split count runs as a cluster when it can
-    pl.cluster = (force_splits > 1 && force_splits <= 8 && pl.BN <= 128 && !swiglu) ? 1 : 0;
+    pl.cluster = (force_splits > 1 && force_splits <= 8 && (kBM % force_splits) == 0 && pl.BN <= 128 && !swiglu) ? 1 : 0;
   }
   if (force_splits < 0) {  // negative: force the workspace (non-cluster) split-K with |splits|
     pl.splits = -force_splits;
@@ -1435,7 +1544,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   if (BN < 16 || BN > 256 || (BN % 16) != 0) return -10;
   if (swiglu && ((N % 16) != 0 || splits != 1)) return -11;
   if (splits <= 1) cluster_split = 0;
-  if (cluster_split && (splits > 8 || BN > 128)) return -14;
+  if (cluster_split && (splits > 8 || BN > 128 || (kBM % splits) != 0)) return -14;
   if (splits > 1 && !cluster_split && (workspace == nullptr || counters == nullptr)) return -12;
   GemmParams p{};
   p.M = M;

@@ -147,6 +147,160 @@ rope_cache_gqa_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
   }
 }
 
+// ---- the same operation with 16-byte accesses -----------------------------------------------
+// A token's work is cut into items of eight elements: rotary items of q (in place), rotary items
+// of k (stored into the cache), the k dims past rot_dim and all of v (copies).  A thread loads
+// two items before it stores either, so a decode step (one CTA per token, a few hundred items)
+// costs one round trip to memory instead of one per pair of elements.
+struct RopeItem {
+  uint4 a, b;
+  float4 c0, c1, s0, s1;
+  __nv_bfloat16* dst_a;
+  __nv_bfloat16* dst_b;
+  int kind;     // 0 nothing, 1 rotate (i, i + half), 2 rotate (2i, 2i + 1), 3 copy
+};
+
+struct RopeVecArgs {
+  __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  const float* cs;          // this token's cos | sin row
+  long long cache_row;      // (block * Hk) * block_size + offset, in rows of D; head h adds h * block_size
+  int Hq, Hk, D, rot_dim, half, neox, block_size;
+  int per_rot, nq, nk, nkp, nv;
+};
+
+__device__ __forceinline__ void rope_item_load(const RopeVecArgs& g, int idx, RopeItem& it) {
+  it.kind = 0;
+  const __nv_bfloat16* src;
+  __nv_bfloat16* dst;
+  int j;
+  if (idx < g.nq + g.nk) {
+    const bool is_q = idx < g.nq;
+    const int local = is_q ? idx : idx - g.nq;
+    const int head = local / g.per_rot;
+    j = local - head * g.per_rot;
+    if (is_q) {
+      dst = g.q + static_cast<long long>(head) * g.D;
+      src = dst;
+    } else {
+      src = g.k + static_cast<long long>(head) * g.D;
+      dst = g.k_cache + (g.cache_row + static_cast<long long>(head) * g.block_size) * g.D;
+    }
+    if (g.neox) {
+      it.kind = 1;
+      it.a = *reinterpret_cast<const uint4*>(src + 8 * j);
+      it.b = *reinterpret_cast<const uint4*>(src + g.half + 8 * j);
+      it.c0 = *reinterpret_cast<const float4*>(g.cs + 8 * j);
+      it.c1 = *reinterpret_cast<const float4*>(g.cs + 8 * j + 4);
+      it.s0 = *reinterpret_cast<const float4*>(g.cs + g.half + 8 * j);
+      it.s1 = *reinterpret_cast<const float4*>(g.cs + g.half + 8 * j + 4);
+      it.dst_a = dst + 8 * j;
+      it.dst_b = dst + g.half + 8 * j;
+    } else {
+      it.kind = 2;
+      it.a = *reinterpret_cast<const uint4*>(src + 8 * j);
+      it.c0 = *reinterpret_cast<const float4*>(g.cs + 4 * j);
+      it.s0 = *reinterpret_cast<const float4*>(g.cs + g.half + 4 * j);
+      it.dst_a = dst + 8 * j;
+    }
+    return;
+  }
+  idx -= g.nq + g.nk;
+  if (idx < g.nkp) {
+    const int per = (g.D - g.rot_dim) >> 3;
+    const int head = idx / per;
+    j = idx - head * per;
+    it.kind = 3;
+    it.a = *reinterpret_cast<const uint4*>(g.k + static_cast<long long>(head) * g.D + g.rot_dim + 8 * j);
+    it.dst_a = g.k_cache + (g.cache_row + static_cast<long long>(head) * g.block_size) * g.D + g.rot_dim + 8 * j;
+    return;
+  }
+  idx -= g.nkp;
+  if (idx < g.nv) {
+    const int per = g.D >> 3;
+    const int head = idx / per;
+    j = idx - head * per;
+    it.kind = 3;
+    it.a = *reinterpret_cast<const uint4*>(g.v + static_cast<long long>(head) * g.D + 8 * j);
+    it.dst_a = g.v_cache + (g.cache_row + static_cast<long long>(head) * g.block_size) * g.D + 8 * j;
+  }
+}
+
+__device__ __forceinline__ void rope_item_store(RopeItem& it) {
+  if (it.kind == 0) return;
+  if (it.kind == 3) {
+    *reinterpret_cast<uint4*>(it.dst_a) = it.a;
+    return;
+  }
+  __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&it.a);
+  if (it.kind == 1) {
+    __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&it.b);
+    const float c[8] = {it.c0.x, it.c0.y, it.c0.z, it.c0.w, it.c1.x, it.c1.y, it.c1.z, it.c1.w};
+    const float sn[8] = {it.s0.x, it.s0.y, it.s0.z, it.s0.w, it.s1.x, it.s1.y, it.s1.z, it.s1.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x0 = __bfloat1622float2(pa[e]);
+      const float2 x1 = __bfloat1622float2(pb[e]);
+      pa[e] = __floats2bfloat162_rn(x0.x * c[2 * e] - x1.x * sn[2 * e], x0.y * c[2 * e + 1] - x1.y * sn[2 * e + 1]);
+      pb[e] = __floats2bfloat162_rn(x1.x * c[2 * e] + x0.x * sn[2 * e], x1.y * c[2 * e + 1] + x0.y * sn[2 * e + 1]);
+    }
+    *reinterpret_cast<uint4*>(it.dst_a) = it.a;
+    *reinterpret_cast<uint4*>(it.dst_b) = it.b;
+    return;
+  }
+  const float c[4] = {it.c0.x, it.c0.y, it.c0.z, it.c0.w};
+  const float sn[4] = {it.s0.x, it.s0.y, it.s0.z, it.s0.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 x = __bfloat1622float2(pa[e]);
+    pa[e] = __floats2bfloat162_rn(x.x * c[e] - x.y * sn[e], x.y * c[e] + x.x * sn[e]);
+  }
+  *reinterpret_cast<uint4*>(it.dst_a) = it.a;
+}
+
+__global__ void __launch_bounds__(256)
+rope_cache_gqa_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                          const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ k_cache,
+                          __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
+                          const int* __restrict__ slot_mapping, const float* __restrict__ cos_sin,
+                          int Hq, int Hk, int D, int rot_dim, int neox, long long q_stride,
+                          long long k_stride, long long v_stride, int block_size) {
+  b200::pdl_trigger();
+  b200::pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = slot_mapping[t];
+  RopeVecArgs g;
+  g.q = q + t * q_stride;
+  g.k = k + t * k_stride;
+  g.v = v + t * v_stride;
+  g.k_cache = k_cache;
+  g.v_cache = v_cache;
+  g.cs = cos_sin + static_cast<long long>(pos) * rot_dim;
+  g.Hq = Hq, g.Hk = Hk, g.D = D, g.rot_dim = rot_dim, g.half = rot_dim >> 1, g.neox = neox;
+  g.block_size = block_size;
+  g.per_rot = neox ? (rot_dim >> 4) : (rot_dim >> 3);
+  g.nq = Hq * g.per_rot;
+  const bool store = slot >= 0;     // a padded token rotates q only
+  g.nk = store ? Hk * g.per_rot : 0;
+  g.nkp = store ? Hk * ((D - rot_dim) >> 3) : 0;
+  g.nv = store ? Hk * (D >> 3) : 0;
+  const long long blk = store ? slot / block_size : 0;
+  g.cache_row = blk * Hk * block_size + (store ? slot - blk * block_size : 0);
+  const int total = g.nq + g.nk + g.nkp + g.nv;
+  for (int idx = threadIdx.x; idx < total; idx += 2 * blockDim.x) {
+    RopeItem i0, i1;
+    rope_item_load(g, idx, i0);
+    i1.kind = 0;
+    if (idx + static_cast<int>(blockDim.x) < total) rope_item_load(g, idx + blockDim.x, i1);
+    rope_item_store(i0);
+    rope_item_store(i1);
+  }
+}
+
 // MLA: kv_c [T, L] (L = 512) is RMS-normalised with weight w; k_pe [T, R] (R = 64)
 // gets RoPE (gpt-j/interleaved or neox pairing); the row [norm(kv_c) | rope(k_pe)]
 // is written to cache[slot].  kv_c_out / k_pe_out (optional) receive the same
@@ -269,7 +423,10 @@ extern "C" int b200_rope_cache_gqa(void* q, const void* k, const void* v, void* 
                                    long long v_stride, int block_size, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((D & 7) != 0 || (rot_dim & 1) != 0 || rot_dim > D) return -1;
-  b200::launch_pdl(rope_cache_gqa_kernel, dim3(T), dim3(256), 0, stream, 1,
+  const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = (rot_dim & 15) == 0 && ((q_stride | k_stride | v_stride) & 7) == 0 && al16(q) && al16(k) &&
+                   al16(v) && al16(k_cache) && al16(v_cache) && al16(cos_sin);
+  b200::launch_pdl(vec ? rope_cache_gqa_vec_kernel : rope_cache_gqa_kernel, dim3(T), dim3(256), 0, stream, 1,
                    static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                    static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(k_cache),
                    static_cast<__nv_bfloat16*>(v_cache), positions, slot_mapping, cos_sin, Hq, Hk, D, rot_dim,

@@ -147,7 +147,7 @@ def bench_gemm(args):
 def bench_attn(args):
     hbm, flops_peak, src = peaks()
     print(f"# paged GQA attention, fractions of {src} peaks")
-    hq, hk, d, bs = args.hq, args.hk, 128, 16       # 32 / 8: Llama-3-8B on one GPU; 16 / 4, 8 / 2, 4 / 1: TP 2, 4, 8
+    hq, hk, d, bs = args.hq, args.hk, 128, args.block_size       # 32 / 8: Llama-3-8B on one GPU; 16 / 4, 8 / 2, 4 / 1: TP 2, 4, 8
     decode_cases = ((128, 1152), (128, 4096), (16, 8192), (1, 32768))
     prefill_cases = ((8, 1024), (2, 4096), (1, 8192))
     if args.b is not None:
@@ -306,6 +306,7 @@ def main():
     ap.add_argument("--hk", type=int, default=8, help="attn: KV heads")
     ap.add_argument("--b", type=int, help="attn: batch size of a single case")
     ap.add_argument("--ctx", type=int, default=1024, help="attn: context length of a single case")
+    ap.add_argument("--block-size", type=int, default=16, help="attn: tokens per cache block")
     ap.add_argument("--phase", default="both", choices=["both", "decode", "prefill"])
     args = ap.parse_args()
     ops.load_extension(required=True)
