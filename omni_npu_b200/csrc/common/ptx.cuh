@@ -225,6 +225,25 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
       : "memory");
 }
 
+// Untiled bulk copy shared -> global (bulk async group completion).  Both addresses 16-byte
+// aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+
+// Bulk copy from this CTA's shared memory into a peer CTA's (shared::cluster addresses for the
+// destination and its mbarrier, which receives the byte count on completion).
+__device__ __forceinline__ void bulk_push_cluster(uint32_t dst_cluster_addr, const void* smem_src, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          dst_cluster_addr),
+      "r"(smem_u32(smem_src)), "r"(bytes), "r"(bar_cluster_addr)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

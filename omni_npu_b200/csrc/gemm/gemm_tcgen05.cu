@@ -25,6 +25,7 @@
 // omni_npu/layers/fused_moe/npu_moe_permute_unpermute.py:108-149).
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "../common/pdl.cuh"
 #include "../common/ptx.cuh"
@@ -43,10 +44,14 @@ static constexpr int kThreads = 192;
 // tiles of all K slices staged, output stored, exit); read them back with b200_gemm_timeline().
 #ifdef B200_GEMM_TIMELINE
 __device__ unsigned long long g_timeline[1024 * 8];
+__device__ long long g_timeline_clk[1024 * 8];        // SM cycle counter at the same points
 __device__ __forceinline__ void timeline_mark(int i) {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  if (blockIdx.x < 1024) g_timeline[blockIdx.x * 8 + i] = t;
+  if (blockIdx.x < 1024) {
+    g_timeline[blockIdx.x * 8 + i] = t;
+    g_timeline_clk[blockIdx.x * 8 + i] = clock64();
+  }
 }
 #define B200_TL(i) timeline_mark(i)
 #else
@@ -203,7 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int w_stage_bytes = p.BN * kRowBytes;
   uint8_t* smem_a = smem;
   uint8_t* smem_w = smem + p.stages * a_stage_bytes;
-  // staging for the cluster reduction: [source rank][rows of my band][BN] fp32 (128 rows in all)
+  // receive area of the cluster reduction, or staging of the reduce-scatter push
   float* red_buf = reinterpret_cast<float*>(smem_w + p.stages * w_stage_bytes);
   const int red_bytes = p.cluster_split ? kBM * p.BN * 4 : (p.rs_world > 1 ? 4 * kRsWarpBytes : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_w + p.stages * w_stage_bytes + red_bytes);
@@ -213,7 +218,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tmem_empty = tmem_full + 2;         // [2]
   uint64_t* drain_bar = tmem_empty + 2;         // [1]
   uint64_t* red_ready = drain_bar + 1;          // [1] all K slices staged (cluster split-K)
-  uint64_t* red_done = red_ready + 1;           // [1] all peers finished reading my staging
+  uint64_t* red_done = red_ready + 1;           // [1] parked partial tile sent (cluster split-K): the ring is free again
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(red_done + 1);
   int* s_flags = reinterpret_cast<int*>(tmem_base_slot + 1);  // [0]=abort, [1]=is_last
   int* s_tile_prefix = s_flags + 2;                           // [num_experts + 1] (grouped)
@@ -232,11 +237,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(&tmem_empty[0], 4);
     mbar_init(&tmem_empty[1], 4);
     mbar_init(drain_bar, 1);
-    mbar_init(red_ready, static_cast<uint32_t>(kBM));       // one arrival per pushed row (splits x rows of my band)
-    mbar_init(red_done, static_cast<uint32_t>(p.splits));
+    mbar_init(red_ready, 1);      // armed below with the bytes of my band from every K slice
+    mbar_init(red_done, 1);
     s_flags[0] = 0;
     s_flags[1] = 0;
     fence_barrier_init();
+    if (p.cluster_split) mbar_arrive_expect_tx(red_ready, static_cast<uint32_t>(kBM * p.BN * 4));
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_w);
   }
@@ -270,7 +276,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // before this thread's first remote access (or at the end of its role)
     cluster_arrive_release();
   }
-  if (threadIdx.x == 0) B200_TL(1);
   const uint32_t tmem_base = *tmem_base_slot;
   if constexpr (GROUPED) {
     total_mn_tiles = s_tile_prefix[p.num_experts] * p.num_n_blocks;
@@ -439,7 +444,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           tc_fence_after_sync();
-          if (k == tc.k_begin) B200_TL(2);
           uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage * p.ksub) * a_slab_lo;
           uint32_t w_lo = w_lo0 + static_cast<uint32_t>(stage * p.ksub) * w_slab_lo;
           for (int j = 0; j < ns; ++j) {
@@ -590,31 +594,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * p.acc_stride);
       if (p.cluster_split) {
-        // ---- split-K inside a cluster.  Rows of the tile are dealt out in bands of kBM / splits,
-        // band b to cluster rank b.  Every thread holds one row of this CTA's partial tile and
-        // PUSHES it into the owner's staging slot for this rank (remote shared-memory stores, then a
-        // release arrival on the owner's barrier); the owner sums the slots out of its own shared
-        // memory.  No CTA reads a peer's memory, so the only round trip is the arrival.
-        // Staging: [source rank][row of the band][BN] fp32, the 16-byte chunks of a row rotated by
-        // the row index so that the 32 rows a warp writes at once fall into different banks.
+        // ---- split-K inside a cluster (one tile per CTA).  Rows of the tile are dealt out in bands
+        // of kBM / splits, band b to cluster rank b.  Every thread parks its row of the partial tile
+        // in shared memory (the operand ring is idle by now; 16-byte chunks XOR-swizzled against
+        // bank conflicts); one thread then sends each band with ONE bulk copy into its owner's
+        // receive area, completing on the owner's barrier, and the owner sums the slots of its band
+        // out of its own shared memory.  Measured on the way here: per-thread 16-byte stores of the
+        // rows (into a peer's shared memory or to an L2 workspace alike) took 3.6-3.8 us for a
+        // 64 KB tile, and a release arrival on each of four peers' barriers 0.3 us apiece.
+        // Receive area: [source rank][row of the band][BN] fp32, chunk c of row r at c ^ (r & swz).
         bool okc = true;
-        const bool last_tile = t + t_stride >= total_mn_tiles;
-        if (tile_iter > 0) okc = mbar_wait_cluster(red_done, static_cast<uint32_t>((tile_iter - 1) & 1));
         if (!cluster_met) {
           cluster_wait_acquire();
           cluster_met = true;
         }
         const int rows_per = kBM / p.splits;
         const int nch = p.BN >> 2;
+        const int swz = (nch & 7) == 0 ? 7 : 3;
+        float* park = reinterpret_cast<float*>(smem_a);     // [128 rows][BN] fp32 <= 64 KB <= two stages
         {
           const int my_row = quarter * 32 + lane;
-          const int owner = my_row / rows_per;
-          const int rl = my_row - owner * rows_per;
-          const int rot = rl % nch;
-          const uint32_t row_addr = mapa_shared(
-              smem_u32(red_buf) + static_cast<uint32_t>((cta_rank * rows_per + rl) * p.BN) * 4u,
-              static_cast<uint32_t>(owner));
-          if (okc) {
+          float4* park_row = reinterpret_cast<float4*>(park + my_row * p.BN);
+          const int rx = my_row & swz;
+          {
             // 32 columns per TMEM load; the load of the next 32 is in flight while these are stored
             // (one warp per scheduler runs this: every dependent instruction costs its full latency)
             auto ld_cols = [&](uint32_t (&r)[32], int c) {
@@ -632,16 +634,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             };
             auto st_cols = [&](const uint32_t (&r)[32], int c) {
-              int ch = (c >> 2) + rot;
-              ch -= ch >= nch ? nch : 0;
               const int n4 = (p.BN - c) >= 32 ? 8 : 4;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                if (i < n4) {
-                  st_shared_cluster_f4(row_addr + static_cast<uint32_t>(ch) * 16u, r[4 * i], r[4 * i + 1],
-                                       r[4 * i + 2], r[4 * i + 3]);
-                  ch = ch + 1 == nch ? 0 : ch + 1;
-                }
+                if (i < n4)
+                  park_row[((c >> 2) + i) ^ rx] =
+                      make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
               }
             };
             uint32_t ra[32], rb[32];
@@ -664,11 +663,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             acc = 0;
             acc_phase ^= 1;
           }
-          // the arrival is a release at cluster scope: the owner's acquire sees this row
-          if (okc) mbar_arrive_cluster(mapa_shared(smem_u32(red_ready), static_cast<uint32_t>(owner)));
-          if (threadIdx.x == 64) B200_TL(3);
+          fence_proxy_async();                              // the parked rows are read by bulk copies
+          if (threadIdx.x == 64) B200_TL(1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            const uint32_t band_bytes = static_cast<uint32_t>(rows_per * p.BN * 4);
+            const uint32_t recv = smem_u32(red_buf) + static_cast<uint32_t>(cta_rank) * band_bytes;
+            const uint32_t bar = smem_u32(red_ready);
+            for (int o = 0; o < p.splits; ++o)
+              bulk_push_cluster(mapa_shared(recv, static_cast<uint32_t>(o)),
+                                reinterpret_cast<const char*>(park) + static_cast<size_t>(o) * band_bytes, band_bytes,
+                                mapa_shared(bar, static_cast<uint32_t>(o)));
+            B200_TL(3);
+          }
         }
-        okc = okc && mbar_wait_cluster(red_ready, static_cast<uint32_t>(tile_iter & 1));
+        okc = okc && mbar_wait(red_ready, 0);      // all K slices of my band have landed
         {
           uint32_t all_ok;
           asm volatile(
@@ -692,48 +701,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         {
           const int r_begin = cta_rank * rows_per;
           const int et = threadIdx.x - 64;
-          // item = (row of the band, 16-byte chunk); a thread walks items et, et + 128, ... without
-          // dividing: 128 = row_step * nch + ch_step
-          const int row_step = 128 / nch, ch_step = 128 - row_step * nch;
-          int rl = et / nch;
-          int chl = et - rl * nch;
-          int rrot = rl % nch;
-          const int rot_step = row_step % nch;
-          const int slot_floats = rows_per * p.BN;
-          for (; rl < rows_per; ) {
-            int chp = chl + rrot;
-            chp -= chp >= nch ? nch : 0;
-            const int c = chl * 4;
-            const float* src = red_buf + rl * p.BN + chp * 4;
-            float4 x[8];
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2)
-              if (s2 < p.splits) x[s2] = *reinterpret_cast<const float4*>(src + s2 * slot_floats);
-            float4 sum = x[0];
-#pragma unroll
-            for (int s2 = 1; s2 < 8; ++s2) {
-              if (s2 < p.splits) {
-                sum.x += x[s2].x;
-                sum.y += x[s2].y;
-                sum.z += x[s2].z;
-                sum.w += x[s2].w;
-              }
-            }
-            const int rl_now = rl;
-            // next item of this thread
-            chl += ch_step;
-            rl += row_step;
-            rrot += rot_step;
-            if (chl >= nch) {
-              chl -= nch;
-              ++rl;
-              ++rrot;
-            }
-            rrot -= rrot >= nch ? nch : 0;
-            rrot -= rrot >= nch ? nch : 0;
+          // one reduced 16-byte chunk (4 columns of one row) to its destination
+          auto emit = [&](int rl_now, int c, float4 sum) {
             const int orow = tc.m0 + r_begin + rl_now;
             const int col = tc.n0 + c;
-            if (orow >= tc.m_end || col >= p.N) continue;
+            if (orow >= tc.m_end || col >= p.N) return;
             float v[4] = {sum.x, sum.y, sum.z, sum.w};
             const int ncols = min(4, p.N - col);
             if (p.ar_world > 1) {
@@ -755,7 +727,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(w0), "r"(w1) : "memory");
                 }
               }
-              continue;
+              return;
             }
             for (int i = 0; i < ncols; ++i) {
               if (p.bias) v[i] += __bfloat162float(p.bias[col + i]);
@@ -777,18 +749,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
               }
             }
-          }
+          };
+          // item = (row of the band, 16-byte chunk); a thread walks items et, et + 128, ... without
+          // dividing: 128 = row_step * nch + ch_step.  Consecutive threads read consecutive chunks.
+          const int row_step = 128 / nch, ch_step = 128 - row_step * nch;
+          const float4* band = reinterpret_cast<const float4*>(red_buf);
+          const int slot_vecs = rows_per * nch;
+          const int items = (rows_per * nch + 127 - et) / 128;      // items of this thread
+          auto advance = [&](int& r_, int& c_) {
+            c_ += ch_step;
+            r_ += row_step;
+            if (c_ >= nch) {
+              c_ -= nch;
+              ++r_;
+            }
+          };
+          auto sum_band = [&](auto sp_tag) {
+            constexpr int SP = decltype(sp_tag)::value;
+            int rl = et / nch;
+            int chl = et - rl * nch;
+            for (int i0 = 0; i0 < items; ++i0) {
+              const float4* src = band + rl * nch + (chl ^ ((r_begin + rl) & swz));
+              float4 x[SP];
+#pragma unroll
+              for (int s2 = 0; s2 < SP; ++s2) x[s2] = src[s2 * slot_vecs];
+              float4 sum = x[0];
+#pragma unroll
+              for (int s2 = 1; s2 < SP; ++s2) {
+                sum.x += x[s2].x;
+                sum.y += x[s2].y;
+                sum.z += x[s2].z;
+                sum.w += x[s2].w;
+              }
+              emit(rl, chl * 4, sum);
+              advance(rl, chl);
+            }
+          };
+          if (p.splits == 2) sum_band(std::integral_constant<int, 2>{});
+          else if (p.splits == 4) sum_band(std::integral_constant<int, 4>{});
+          else sum_band(std::integral_constant<int, 8>{});
         }
         if (threadIdx.x == 64) B200_TL(6);
-        if (!last_tile) {
-          // the slots may be overwritten once every owner has finished this tile; after the last
-          // tile nobody signals, so no CTA touches a peer that may already have retired
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64) {
-            const uint32_t a = smem_u32(red_done);
-            for (int s2 = 0; s2 < p.splits; ++s2) mbar_arrive_cluster(mapa_shared(a, s2));
-          }
-        }
         ++tile_iter;
         continue;
       }
@@ -1136,11 +1137,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   }
-  // Split-K in a cluster: a CTA's last remote accesses are the pushes and arrivals of its final
-  // tile, and their targets cannot retire before those have landed (they wait for them), so CTAs
-  // leave without meeting again.  After an abort a peer may still push into this CTA: stay until
-  // every other CTA of the cluster has arrived here or has exited.
-  if (p.cluster_split && *abort_flag) cluster_sync_all();
+  // Split-K in a cluster: the bulk copies out of this CTA's shared memory report completion to
+  // their destinations only, so no CTA leaves before every owner has its band (each arrives here
+  // after its sum; after an abort, peers either arrive or have exited).
+  if (p.cluster_split) cluster_sync_all();
   if (threadIdx.x == 0) B200_TL(7);
   if (warp == 1) {
     if (*abort_flag && lane == 0) {
@@ -1171,7 +1171,7 @@ static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 static constexpr int kRsStageBytes = 4 * kRsWarpBytes;
 static size_t red_bytes_for(int BN, int cluster_split) {
   if (cluster_split == 2) return kRsStageBytes;
-  return cluster_split ? static_cast<size_t>(kBM) * BN * 4 : 0;
+  return cluster_split ? static_cast<size_t>(kBM) * BN * 4 : 0;     // receive area of the cluster reduction
 }
 
 static size_t smem_bytes_for(int BN, int stages, int num_experts, int cluster_split = 0) {
@@ -1347,6 +1347,9 @@ static bool plan_small_m(int M, int N, int K, int elem_bytes, bool allow_split, 
 #ifdef B200_GEMM_TIMELINE
 extern "C" int b200_gemm_timeline(unsigned long long* host, int ctas) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline, sizeof(unsigned long long) * 8 * ctas));
+}
+extern "C" int b200_gemm_timeline_cycles(long long* host, int ctas) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline_clk, sizeof(long long) * 8 * ctas));
 }
 #endif
 
@@ -1546,6 +1549,7 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   if (splits <= 1) cluster_split = 0;
   if (cluster_split && (splits > 8 || BN > 128 || (kBM % splits) != 0)) return -14;
   if (splits > 1 && !cluster_split && (workspace == nullptr || counters == nullptr)) return -12;
+
   GemmParams p{};
   p.M = M;
   p.N = N;
@@ -1622,10 +1626,12 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   int grid;
   if (cluster_split) {
     const long long clusters = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
-    int cap = max_active_clusters(splits, smem);
-    if (cap <= 0) return -15;
-    if (max_ctas > 0 && max_ctas / splits < cap) cap = max_ctas / splits > 0 ? max_ctas / splits : 1;
-    grid = static_cast<int>(clusters < cap ? clusters : cap) * splits;
+    if (max_active_clusters(splits, smem) <= 0) return -15;
+    // one tile per CTA: the reduction's barriers and receive area are used once per launch, and
+    // clusters beyond what fits at once simply start as earlier ones retire (max_ctas is not
+    // honoured by this variant)
+    if (clusters * splits > 0x7fffffffLL) return -15;
+    grid = static_cast<int>(clusters) * splits;
   } else {
     const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks * splits;
     grid = sm_count();
