@@ -1321,7 +1321,10 @@ static bool plan_small_m(int M, int N, int K, int elem_bytes, bool allow_split, 
       const int cap = sp > 1 ? max_active_clusters(sp, smem_bytes_for(bn, stages, 0, 1)) : sm_count();
       if (cap <= 0) continue;
       const int waves = (clusters + cap - 1) / cap;
-      const double rows_a = M < kBM ? M : kBM;
+      // (the full 128-row slab is charged whatever M is: the plan, and with it the order in which
+      // a row's products are summed, must not depend on how many other rows share the launch:
+      // a decode step padded to a captured graph size gives the same numbers as the unpadded one)
+      const double rows_a = kBM;
       double t_cta = (rows_a + bn) * per * static_cast<double>(kRowBytes) / sm_ingest + 2.5e-6;
       if (sp > 1) t_cta += 1.5e-6;
       double t = waves * t_cta;

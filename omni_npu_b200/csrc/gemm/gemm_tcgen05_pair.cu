@@ -60,6 +60,13 @@ template <bool FP8>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                  const PairParams p) {
+  // The diagnostic modes (wrong results by design) exist only in builds with -DB200_GEMM_DIAG;
+  // otherwise `diag` is a constant zero and every branch on it is compiled out.
+#ifdef B200_GEMM_DIAG
+  const int diag = p.diag;
+#else
+  constexpr int diag = 0;
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -119,7 +126,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      const bool prof = (p.diag & 64) && blockIdx.x == 0;
+      const bool prof = (diag & 64) && blockIdx.x == 0;
       long long c_empty = 0, n_empty_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
         const int mb = static_cast<int>(t % p.num_m_blocks), nb = static_cast<int>(t / p.num_m_blocks);
@@ -128,11 +135,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int k = 0; k < p.k_iters; ++k) {
           const long long tp0 = prof ? clock64() : 0;
           if (prof && mbar_test(&empty_bar[stage], phase ^ 1)) ++n_empty_ready;
-          if ((p.diag & 4) && issued >= p.stages) {
+          if ((diag & 4) && issued >= p.stages) {
             ok = false;   // nobody waits for full barriers: the producer is done after the first fill
             break;
           }
-          if (!(p.diag & 8) && !mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          if (!(diag & 8) && !mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicCAS(p.status, 0, kStatusTimeoutEmptyBarrier);
             *abort_flag = 1;
             ok = false;
@@ -141,7 +148,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (prof) c_empty += clock64() - tp0;
           // the leader's barrier collects the bytes of both CTAs
           const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[stage]), 0);
-          if ((p.diag & 1) && issued >= p.stages) {
+          if ((diag & 1) && issued >= p.stages) {
             // diagnostics: hand the stage back without reloading it
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 0u);
             ++issued;
@@ -181,12 +188,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      const bool no_mma = (p.diag & 2) != 0;
+      const bool no_mma = (diag & 2) != 0;
       // low words of the shared-memory descriptors (start address >> 4) and their strides
       const uint32_t a_lo0 = (smem_u32(smem_a) & 0x3FFFF) >> 4, w_lo0 = (smem_u32(smem_w) & 0x3FFFF) >> 4;
       const uint32_t a_sub_lo = static_cast<uint32_t>(a_sub_bytes) >> 4, w_sub_lo = static_cast<uint32_t>(w_sub_bytes) >> 4;
       const uint32_t a_stage_lo = static_cast<uint32_t>(a_stage_bytes) >> 4, w_stage_lo = static_cast<uint32_t>(w_stage_bytes) >> 4;
-      const bool prof = (p.diag & 64) && blockIdx.x == 0;
+      const bool prof = (diag & 64) && blockIdx.x == 0;
       long long c_wait = 0, c_issue = 0, c_commit = 0, c_tmem = 0, n_wait = 0, n_ready = 0;
       for (long long t = t_first; ok && t < total_tiles; t += t_stride) {
         long long t0 = prof ? clock64() : 0;
@@ -204,7 +211,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ++n_wait;
             if (mbar_test(&full_bar[stage], phase)) ++n_ready;
           }
-          if (!(p.diag & 4) && !mbar_wait(&full_bar[stage], phase)) {
+          if (!(diag & 4) && !mbar_wait(&full_bar[stage], phase)) {
             atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
             *abort_flag = 1;
             ok = false;
@@ -235,7 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             t0 = t1;
           }
           // the stage is free in both CTAs once these MMAs retire
-          if (!(p.diag & 8)) tc_commit_pair_both(smem_u32(&empty_bar[stage]));
+          if (!(diag & 8)) tc_commit_pair_both(smem_u32(&empty_bar[stage]));
           if (prof) c_commit += clock64() - t0;
           if (++stage == p.stages) {
             stage = 0;
@@ -268,8 +275,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m0 = mb * 2 * kPBM + cta_rank * kPBM;
       const int n0 = nb * p.BN;
       bool ok = true;
-      if (!(p.diag & 16) || lane == 0) ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
-      if (p.diag & 16) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!(diag & 16) || lane == 0) ok = !*abort_flag && mbar_wait(&tmem_full[acc], acc_phase);
+      if (diag & 16) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       {
         uint32_t all_ok;
         asm volatile(
@@ -489,6 +496,8 @@ extern "C" int b200_gemm_pair(const void* A, const void* W, void* C, const void*
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.status = status;
+  p.diag = 0;
+#ifdef B200_GEMM_DIAG
   {
     static const int diag = [] {
       const char* e = getenv("OMNI_B200_GEMM_DIAG");
@@ -496,6 +505,7 @@ extern "C" int b200_gemm_pair(const void* A, const void* W, void* C, const void*
     }();
     p.diag = diag;
   }
+#endif
   CUtensorMap ta, tw;
   const CUtensorMapDataType dt = dtype_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int box_k = kPRowBytes / eb;

@@ -79,6 +79,93 @@ class RotaryEmbedding(nn.Module):
         return q, k
 
 
+class XDRotaryEmbedding(RotaryEmbedding):
+    """Rotary embedding whose frequency bands take their position from one of several axes
+    (``xdrope_section``: how many frequency indices each axis owns, e.g. four axes for
+    sequence / time / height / width).  ``positions`` is [axes, T]; a 1-D tensor means that all
+    axes carry the same index, which is the plain rotation.  The table is the fixed-alpha NTK one
+    the factory builds (reference: XDRotaryEmbedding selected by
+    omni_npu/v1/layers/rotary_embedding/__init__.py:168-187)."""
+
+    def __init__(self, *args, xdrope_section: Tuple[int, ...], **kw) -> None:
+        super().__init__(*args, **kw)
+        half = self.rot_dim // 2
+        if sum(xdrope_section) != half:
+            raise ValueError(f"xdrope_section {xdrope_section} must sum to rot_dim / 2 = {half}")
+        self.xdrope_section = tuple(int(x) for x in xdrope_section)
+        axis = torch.cat([torch.full((n,), a, dtype=torch.long) for a, n in enumerate(self.xdrope_section)])
+        self.register_buffer("axis_of_freq", axis, persistent=False)
+
+    def forward(self, positions: torch.Tensor, q: torch.Tensor, k: torch.Tensor):
+        if positions.dim() == 1:
+            return super().forward(positions, q, k)
+        if positions.shape[0] != len(self.xdrope_section):
+            raise ValueError(f"positions carry {positions.shape[0]} axes, the sections name {len(self.xdrope_section)}")
+        half = self.rot_dim // 2
+        # per token and frequency index: the position of the axis that owns the index
+        pos = positions.long()[self.axis_of_freq.to(positions.device)].t()           # [T, half]
+        idx = torch.arange(half, device=pos.device)
+        cos = self.cos_sin_cache[pos, idx].float()                                   # [T, half]
+        sin = self.cos_sin_cache[pos, half + idx].float()
+        for x in (q, k):
+            v = x.view(x.shape[0], -1, self.head_dim)
+            rot = v[..., : self.rot_dim].float()
+            c, s_ = cos[:, None, :], sin[:, None, :]
+            if self.is_neox:
+                x0, x1 = rot[..., :half], rot[..., half:]
+                out = torch.cat((x0 * c - x1 * s_, x1 * c + x0 * s_), dim=-1)
+            else:
+                x0, x1 = rot[..., 0::2], rot[..., 1::2]
+                out = torch.stack((x0 * c - x1 * s_, x1 * c + x0 * s_), dim=-1).flatten(-2)
+            v[..., : self.rot_dim] = out.to(x.dtype)
+        return q, k
+
+
+class DualChunkRotaryEmbedding(nn.Module):
+    """Rotations for dual-chunk attention (long contexts cut into chunks of ``chunk_size`` with a
+    local window of ``local_size``): keys are rotated by their position inside a chunk, and the
+    query is produced five times, for attention inside its chunk, to the chunk before it, to
+    earlier chunks, and the two "critical" variants used when chunks are selected.  All five are
+    the plain rotation at a remapped position, so one table serves them (reference: the
+    dual_chunk_attention_config branch of omni_npu/v1/layers/rotary_embedding/__init__.py:69-86).
+
+    ``forward`` returns ``(queries, key)`` with ``queries`` = the five variants concatenated along
+    the last dimension in the order (intra, successor, inter, successor-critical, inter-critical)."""
+
+    def __init__(self, head_dim: int, rot_dim: int, max_position: int, base: float, is_neox: bool,
+                 chunk_size: int, local_size: int, device=None) -> None:
+        super().__init__()
+        self.chunk_size, self.local_size = int(chunk_size), int(local_size)
+        self.chunk_len = self.chunk_size - self.local_size
+        if self.chunk_len <= 0:
+            raise ValueError("chunk_size must exceed local_size")
+        self.max_position = max_position
+        # largest remapped position: chunk_len - 1 + chunk_size (inter-critical)
+        self.rope = RotaryEmbedding(head_dim, rot_dim, self.chunk_size + self.chunk_len + 1, base, is_neox,
+                                    device=device)
+
+    def remap(self, positions: torch.Tensor):
+        """The six position tensors: key, then the five query variants."""
+        r = positions % self.chunk_len
+        succ = torch.clamp(r + self.chunk_len, max=self.chunk_size)
+        inter = torch.full_like(r, min(2 * self.chunk_len - 1, self.chunk_size))
+        return r, r, succ, inter, r + self.chunk_len, r + self.chunk_size
+
+    def forward(self, positions: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
+                offsets: Optional[torch.Tensor] = None):
+        if offsets is not None:
+            positions = positions + offsets
+        maps = self.remap(positions.to(torch.int32))
+        outs = []
+        none = q.new_zeros((q.shape[0], 0))
+        for i, pos in enumerate(maps[1:]):
+            qi = q.clone()
+            # the key is rotated together with the first query variant (same remapped position)
+            self.rope(pos.contiguous(), qi, k if i == 0 else none)
+            outs.append(qi)
+        return torch.cat(outs, dim=-1), k
+
+
 def _linear_inv_freq(rot_dim: int, base: float, factor: float) -> torch.Tensor:
     return _base_inv_freq(rot_dim, base) / factor
 
@@ -112,12 +199,20 @@ _ROPE_CACHE: Dict[Any, RotaryEmbedding] = {}
 
 
 def get_rope(head_dim: int, rot_dim: int, max_position: int, base: float, is_neox: bool = True,
-             rope_scaling: Optional[Dict[str, Any]] = None, device=None) -> RotaryEmbedding:
+             rope_scaling: Optional[Dict[str, Any]] = None, device=None,
+             dual_chunk_attention_config: Optional[Dict[str, Any]] = None) -> nn.Module:
+    dca = {k: v for k, v in (dual_chunk_attention_config or {}).items() if k in ("chunk_size", "local_size")}
     key = (head_dim, rot_dim, max_position, base, is_neox,
-           tuple(sorted((k, str(v)) for k, v in (rope_scaling or {}).items())), str(device))
+           tuple(sorted((k, str(v)) for k, v in (rope_scaling or {}).items())), str(device),
+           tuple(sorted(dca.items())))
     hit = _ROPE_CACHE.get(key)
     if hit is not None:
         return hit
+    if dual_chunk_attention_config is not None:
+        rope = DualChunkRotaryEmbedding(head_dim, rot_dim, max_position, base, is_neox,
+                                        dca.get("chunk_size", 8192), dca.get("local_size", 1024), device)
+        _ROPE_CACHE[key] = rope
+        return rope
     rs = dict(rope_scaling or {})
     kind = rs.get("rope_type", rs.get("type", "default"))
     mrope = rs.get("mrope_section")
@@ -166,8 +261,13 @@ def get_rope(head_dim: int, rot_dim: int, max_position: int, base: float, is_neo
     else:
         raise ValueError(f"unknown rope scaling type {kind!r}")
     max_pos = min(max_pos, 1 << 20)
-    rope = RotaryEmbedding(head_dim, rot_dim, max_pos, base, is_neox, inv, mscale,
-                           tuple(mrope) if mrope else None,
-                           bool(rs.get("mrope_interleaved", False)), device)
+    xd = rs.get("xdrope_section")
+    if xd:
+        rope = XDRotaryEmbedding(head_dim, rot_dim, max_pos, base, is_neox, inv, mscale, None, False, device,
+                                 xdrope_section=tuple(xd))
+    else:
+        rope = RotaryEmbedding(head_dim, rot_dim, max_pos, base, is_neox, inv, mscale,
+                               tuple(mrope) if mrope else None,
+                               bool(rs.get("mrope_interleaved", False)), device)
     _ROPE_CACHE[key] = rope
     return rope

@@ -133,7 +133,7 @@ def test_rope_factory_alpha_ntk_xdrope_and_aliases():
     from omni_npu_b200.layers.rope import get_rope
     d, base, alpha = 64, 10000.0, 8.0
     want = 1.0 / ((base * alpha ** (d / (d - 2))) ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
-    for kind, extra in (("dynamic", {}), ("xdrope", {"xdrope_section": [16, 16, 16, 16]})):
+    for kind, extra in (("dynamic", {}), ("xdrope", {"xdrope_section": [8, 8, 8, 8]})):
         rope = get_rope(d, d, 256, base, True, {"rope_type": kind, "alpha": alpha, **extra})
         cos, sin = rope.get_cos_sin(torch.tensor([7]))
         assert torch.allclose(cos[0], torch.cos(7 * want), atol=1e-5)
@@ -146,3 +146,46 @@ def test_rope_factory_alpha_ntk_xdrope_and_aliases():
     assert torch.equal(a.cos_sin_cache, b.cos_sin_cache)
     with pytest.raises(ValueError):
         get_rope(d, d, 256, base, True, {"rope_type": "dynamic"})
+
+
+def test_xdrope_takes_each_frequency_band_from_its_own_axis():
+    """Four position axes, sections (2, 2, 2, 2) of the 8 frequency indices: band b is rotated by
+    positions[b]; 1-D positions are the plain rotation."""
+    d, alpha, base = 16, 1000.0, 10000.0
+    rope = get_rope(d, d, 256, base, True, {"rope_type": "xdrope", "alpha": alpha, "xdrope_section": [2, 2, 2, 2]})
+    inv = 1.0 / ((base * alpha ** (d / (d - 2))) ** (torch.arange(0, d, 2).float() / d))
+    t = 6
+    pos = torch.stack([torch.arange(t) + 3 * a for a in range(4)]).to(torch.int32)      # [4, T]
+    q, k = torch.randn(t, 2 * d), torch.randn(t, d)
+    gq, gk = rope(pos, q.clone(), k.clone())
+    per_freq_pos = pos.long()[torch.tensor([0, 0, 1, 1, 2, 2, 3, 3])].t().float()       # [T, 8]
+    ang = per_freq_pos * inv
+    cos, sin = ang.cos(), ang.sin()
+
+    def rot(x):
+        a, b = x[:, : d // 2], x[:, d // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], 1)
+    assert torch.allclose(gq, torch.cat([rot(q[:, :d]), rot(q[:, d:])], 1), atol=1e-5)
+    assert torch.allclose(gk, rot(k), atol=1e-5)
+    flat = pos[0].contiguous()
+    g1, _ = rope(flat, q.clone(), k.clone())
+    g4, _ = rope(flat.expand(4, t).contiguous(), q.clone(), k.clone())
+    assert torch.allclose(g1, g4, atol=1e-6)
+
+
+def test_dual_chunk_rope_produces_the_five_query_views():
+    """Keys rotate by their offset inside a chunk; the query comes back five times at the remapped
+    positions (intra, successor, inter, successor-critical, inter-critical)."""
+    d, base, chunk, local = 16, 10000.0, 32, 8
+    rope = get_rope(d, d, 4096, base, True, None, None, {"chunk_size": chunk, "local_size": local})
+    clen = chunk - local
+    inv = 1.0 / (base ** (torch.arange(0, d, 2).float() / d))
+    pos = torch.tensor([0, 5, 23, 24, 47, 1000], dtype=torch.int32)
+    q, k = torch.randn(6, d), torch.randn(6, d)
+    qs, gk = rope(pos, q.clone(), k.clone())
+    assert qs.shape == (6, 5 * d)
+    r = pos.long() % clen
+    want_pos = [r, torch.clamp(r + clen, max=chunk), torch.full_like(r, min(2 * clen - 1, chunk)), r + clen, r + chunk]
+    for i, wp in enumerate(want_pos):
+        assert torch.allclose(qs[:, i * d:(i + 1) * d], _rot_ref(q, wp, inv, 1.0), atol=1e-5), i
+    assert torch.allclose(gk, _rot_ref(k, r, inv, 1.0), atol=1e-5)
