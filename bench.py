@@ -329,16 +329,39 @@ def _shutdown(llm, world: int) -> None:
     timer = threading.Timer(30.0, _deadline)
     timer.daemon = True
     timer.start()
+    t0 = time.perf_counter()
+    stage = "start"
+
+    def mark(name):
+        nonlocal stage
+        stage = name
+        if os.environ.get("OMNI_B200_BENCH_SHUTDOWN_TRACE"):
+            print(f"shutdown[{os.environ.get('RANK', '0')}] {time.perf_counter() - t0:6.2f}s {name}", file=sys.stderr,
+                  flush=True)
     try:
+        import gc
+
+        import torch
         if world > 1:
             dist.barrier()
+        mark("barrier done")
         from omni_npu_b200.parallel import state as pstate
+        runner = llm.engine.worker.model_runner
         llm.engine.shutdown()
+        # captured graphs hold the communicators' buffers and streams: let them go before the
+        # communicators are destroyed
+        if getattr(runner, "graphs", None):
+            runner.graphs.clear()
+        gc.collect()
+        torch.cuda.synchronize()
+        mark("engine down, graphs released")
         pstate.destroy_model_parallel()
+        mark("groups destroyed")
         if world > 1 and dist.is_initialized():
             dist.destroy_process_group()
+        mark("process group destroyed")
     except Exception as e:  # pragma: no cover - best effort
-        print(f"shutdown: {type(e).__name__}: {e}", file=sys.stderr)
+        print(f"shutdown after '{stage}': {type(e).__name__}: {e}", file=sys.stderr)
     sys.stdout.flush()
     sys.stderr.flush()
     # the watchdog stays armed through interpreter shutdown (daemon timer): a clean exit beats it

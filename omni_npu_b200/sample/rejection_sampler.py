@@ -144,3 +144,65 @@ def parse_output(tokens: torch.Tensor, counts: torch.Tensor) -> List[List[int]]:
     """[B, S+1] padded tokens + counts -> ragged python lists."""
     tl, cl = tokens.tolist(), counts.tolist()
     return [row[:n] for row, n in zip(tl, cl)]
+
+
+class SparseRejectionSampler:
+    """Accept / reject rule for a drafter that samples from the top-k of its own distribution.
+
+    The draft distribution of every position is kept sparse in a ``ProbCache`` (k token ids and
+    their renormalised probabilities, the distribution the draft token was actually drawn from).
+    Draft token x at a position is accepted with probability min(1, p(x) / q(x)); at the first
+    rejection a token is drawn from the recovered distribution max(p - q, 0) (q scattered from its
+    k entries), and when every draft is accepted the bonus token is drawn from the target
+    distribution of the last position.  The emitted tokens are then distributed exactly as the
+    target model's.  Rows whose draft distribution was never computed reject their drafts.
+    Everything stays on the device.  Same decision rule as ``SparseRejectionSampler`` of
+    omni_npu/v0/layers/sampler.py:952-1092."""
+
+    def __init__(self, prob_cache, penalty_cache=None) -> None:
+        self.prob_cache = prob_cache
+        self.penalty_cache = penalty_cache
+
+    def forward(self, target_probs: torch.Tensor, slots: torch.Tensor,
+                generator: Optional[torch.Generator] = None):
+        """``target_probs`` [B, n + 1, V]: the target distributions at the n draft positions and
+        the bonus position; ``slots`` [B]: rows of the prob cache.  Returns ``(tokens [B, n + 1]
+        with -1 after the last emitted token, num_emitted [B])``."""
+        pc = self.prob_cache
+        b, n1, v = target_probs.shape
+        n = n1 - 1
+        s = slots.long()
+        ids = pc.topk_ids[s, :n]                                   # [B, n, k]
+        q_all = pc.topk_probs[s, :n]
+        sel = pc.selected[s, :n].unsqueeze(-1)
+        draft = ids.gather(2, sel).squeeze(-1)                     # [B, n]
+        q = q_all.gather(2, sel).squeeze(-1)
+        p = target_probs[:, :n].gather(2, draft.unsqueeze(-1)).squeeze(-1)
+        u = torch.rand(p.shape, device=p.device, generator=generator)
+        ok = (u * q < p) & pc.computed[s].unsqueeze(1)             # u < p / q without dividing by zero
+        accepted = torch.cumprod(ok.to(torch.int32), dim=1).bool() # a rejection ends the run
+        num_acc = accepted.sum(dim=1)                              # [B] in 0..n
+        rows = torch.arange(b, device=p.device)
+        # distribution of the token emitted after the accepted run
+        p_next = target_probs[rows, num_acc]                       # [B, V]
+        rejected_here = num_acc < n
+        j = num_acc.clamp(max=max(n - 1, 0))
+        if n > 0:
+            q_dense = torch.zeros(b, v, dtype=p_next.dtype, device=p.device)
+            q_dense.scatter_(1, ids[rows, j], q_all[rows, j].to(p_next.dtype))
+            q_dense = q_dense * pc.computed[s].unsqueeze(1)        # no draft distribution: sample the target's
+            recovered = (p_next - q_dense).clamp_min(0)
+            total = recovered.sum(dim=1, keepdim=True)
+            recovered = torch.where(total > 0, recovered / total.clamp_min(1e-20), p_next)
+            p_next = torch.where(rejected_here.unsqueeze(1), recovered, p_next)
+        nxt = torch.multinomial(p_next.float(), 1, generator=generator).squeeze(1)
+        out = torch.full((b, n1), PLACEHOLDER_TOKEN_ID, dtype=torch.long, device=p.device)
+        if n > 0:
+            out[:, :n] = torch.where(accepted, draft, torch.full_like(draft, PLACEHOLDER_TOKEN_ID))
+        out[rows, num_acc] = nxt
+        if self.penalty_cache is not None:
+            for i in range(n1):
+                self.penalty_cache.record(s, out[:, i])
+        return out, num_acc + 1
+
+    __call__ = forward

@@ -306,6 +306,15 @@ class ModelRunner:
         sp = req.sampling_params
         return sp.has_penalties or sp.thinking_token_budget is not None
 
+    def _penalty_cache(self, vocab: int):
+        """The device-resident penalty state (created on first use: most workloads never ask)."""
+        pc = getattr(self, "_pen_cache", None)
+        if pc is None or pc.vocab_size != vocab:
+            from ..sample.sampler_cache import PenaltyCache
+            pc = PenaltyCache(max(8, 2 * self.config.scheduler.max_num_seqs), vocab, self.device)
+            self._pen_cache = pc
+        return pc
+
     def _make_logits_fn(self, seqs):
         """Logits adjustment for one step, or None when no scheduled sequence asks for any.
         Row i of the logits belongs to ``seqs[i]``.  Penalties: occurrence counts of the generated
@@ -332,26 +341,20 @@ class ModelRunner:
             logits = logits.float()
             V = logits.shape[-1]
             if pen_rows:
-                rr, tt, pr, pt = [], [], [], []
-                for j, i in enumerate(pen_rows):
+                # per-request prompt mask and occurrence counts live on the device from admission
+                # to completion; a step adds only the tokens generated since the last one
+                pc = self._penalty_cache(V)
+                rids = []
+                for i in pen_rows:
                     r = seqs[i].request
-                    outs = [t for t in r.output_token_ids if 0 <= t < V]
-                    rr += [j] * len(outs)
-                    tt += outs
-                    ptoks = set(t for t in r.prompt_token_ids if 0 <= t < V)
-                    pr += [j] * len(ptoks)
-                    pt += list(ptoks)
-                counts = torch.zeros(len(pen_rows), V, dtype=torch.float32, device=dev)
-                if tt:
-                    counts.index_put_((torch.tensor(rr, device=dev), torch.tensor(tt, device=dev)),
-                                      torch.ones(len(tt), device=dev), accumulate=True)
-                pmask = torch.zeros(len(pen_rows), V, dtype=torch.bool, device=dev)
-                if pt:
-                    pmask[torch.tensor(pr, device=dev), torch.tensor(pt, device=dev)] = True
+                    if not pc.has(r.request_id):
+                        pc.add_request(r.request_id, r.prompt_token_ids)
+                    pc.sync_from_history(r.request_id, r.output_token_ids)
+                    rids.append(r.request_id)
                 sps = [seqs[i].request.sampling_params for i in pen_rows]
                 idx = torch.tensor(pen_rows, device=dev)
-                sub = apply_penalties(
-                    logits.index_select(0, idx), pmask, counts,
+                sub = pc.apply(
+                    logits.index_select(0, idx), pc.slot_index(rids),
                     torch.tensor([sp.presence_penalty for sp in sps], dtype=torch.float32, device=dev),
                     torch.tensor([sp.frequency_penalty for sp in sps], dtype=torch.float32, device=dev),
                     torch.tensor([sp.repetition_penalty for sp in sps], dtype=torch.float32, device=dev))
@@ -379,6 +382,8 @@ class ModelRunner:
         for rid in out.finished_req_ids:
             ib.remove_request(rid)
             self.thinking_processor.remove_request(rid)
+            if getattr(self, "_pen_cache", None) is not None:
+                self._pen_cache.remove_request(rid)
         for rid in out.preempted:
             ib.remove_request(rid)
         if self.kv_connector is not None and out.kv_connector_metadata is not None:
@@ -471,6 +476,8 @@ class ModelRunner:
         ib = self.input_batch
         for rid in out.finished_req_ids:
             ib.remove_request(rid)
+            if getattr(self, "_pen_cache", None) is not None:
+                self._pen_cache.remove_request(rid)
         for rid in out.preempted:
             ib.remove_request(rid)
         n = len(out.seqs)

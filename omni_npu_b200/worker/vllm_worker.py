@@ -312,7 +312,7 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
     def get_kv_cache_spec(self) -> Dict[str, Any]:
         """One attention spec per layer, sized like the runner's own cache layout, so that vLLM's
         block count times ``page_size_bytes`` is what the runner will allocate."""
-        from vllm.v1.kv_cache_interface import FullAttentionSpec, MLAAttentionSpec
+        from vllm.v1.kv_cache_interface import FullAttentionSpec, MLAAttentionSpec, SinkFullAttentionSpec
         spec = self.model_runner.get_kv_cache_spec()
         mc = self.engine_config.model
         self._kv_bytes_per_block = spec.bytes_per_block
@@ -322,10 +322,21 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         for i in range(spec.num_layers):
             name = f"model.layers.{i}.self_attn.attn"
             if spec.kind == "gqa":
-                from ..parallel import state as pstate
-                hk = max(1, mc.num_kv_heads // pstate.tp_world_size())
-                s = FullAttentionSpec(block_size=spec.block_size, num_kv_heads=hk, head_size=mc.head_dim,
-                                      dtype=mc.dtype)
+                # per-block shapes of the runner's own caches: k [heads, block, D], v [heads, block, Dv]
+                hk, _, dk = spec.shapes["k"]
+                dv = spec.shapes["v"][-1]
+                # Static attention sinks: the model keeps its learned sink tokens in the blocks right
+                # after the null block; vLLM's sink manager takes exactly those out of its free
+                # queue (reference: SinkFullAttentionSpec and the manager that pops the sink blocks,
+                # omni_npu/vllm_patches/patches/models/pangu72b-vl/patch_kv_cache_interface.py:88-141,
+                # .../pangu_sink_swa_mla/patch_single_type_kv_cache_manager.py:26-62)
+                reserved = int(getattr(self.inner.get_model(), "num_reserved_kv_blocks", 0))
+                kw = dict(block_size=spec.block_size, num_kv_heads=int(hk), head_size=int(dk),
+                          head_size_v=int(dv), dtype=mc.dtype)
+                if reserved > 1:
+                    s = SinkFullAttentionSpec(sink_len=(reserved - 1) * spec.block_size, **kw)
+                else:
+                    s = FullAttentionSpec(**kw)
             else:
                 width = per_layer // (spec.block_size * esz)      # latent + rope (+ index key) columns
                 s = MLAAttentionSpec(block_size=spec.block_size, num_kv_heads=1, head_size=width, dtype=mc.dtype)

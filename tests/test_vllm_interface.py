@@ -298,3 +298,29 @@ def test_model_adapter_translates_vllm_metadata_and_matches_the_inner_model(monk
         want = model.inner(ids, pos.to(torch.int32))
     torch.testing.assert_close(got, want)
     assert model.compute_logits(got).shape == (T, 97)
+
+
+def test_worker_describes_sink_models_with_the_sink_spec():
+    """Static attention sinks under vLLM: the worker names the sink length so that vLLM's sink manager
+    takes the blocks after the null block out of circulation, and K / V head sizes may differ."""
+    pytest.importorskip("vllm")
+    import types
+
+    import torch
+    from vllm.v1.kv_cache_interface import FullAttentionSpec, SinkFullAttentionSpec
+
+    from omni_npu_b200.worker.model_runner import KVCacheSpec
+    from omni_npu_b200.worker.vllm_worker import B200Worker
+    bs, hk, dk, dv, layers = 16, 2, 192, 128, 3
+    per_layer = bs * hk * (dk + dv) * 2
+    w = B200Worker.__new__(B200Worker)
+    w.engine_config = types.SimpleNamespace(model=types.SimpleNamespace(dtype=torch.bfloat16, num_kv_heads=hk, head_dim=dk))
+    w.model_runner = types.SimpleNamespace(get_kv_cache_spec=lambda: KVCacheSpec(
+        "gqa", layers, bs, per_layer * layers, {"k": (hk, bs, dk), "v": (hk, bs, dv)}))
+    for reserved, cls, sink in ((1 + 128 // bs, SinkFullAttentionSpec, 128), (0, FullAttentionSpec, None)):
+        w.inner = types.SimpleNamespace(get_model=lambda r=reserved: types.SimpleNamespace(num_reserved_kv_blocks=r))
+        specs = w.get_kv_cache_spec()
+        assert len(specs) == layers
+        s = specs["model.layers.0.self_attn.attn"]
+        assert type(s) is cls and s.head_size == dk and s.head_size_v == dv and s.page_size_bytes == per_layer
+        assert getattr(s, "sink_len", None) == sink
