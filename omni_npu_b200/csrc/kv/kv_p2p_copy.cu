@@ -76,3 +76,8 @@ extern "C" int b200_kv_p2p_copy(const void* tensors, int num_tensors, const int*
                                                      src_blocks, dst_blocks, num_pairs, num_tensors, chunks);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// Reads (and thereby clears) the runtime's last-error state.  A runtime call made outside torch
+// that fails, e.g. pinning a mapping that cannot be pinned, leaves its code there, and the next
+// unrelated call that checks for errors would report it.
+extern "C" int b200_cuda_take_last_error() { return static_cast<int>(cudaGetLastError()); }

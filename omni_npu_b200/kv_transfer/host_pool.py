@@ -74,6 +74,14 @@ class HostKVPool:
             rc = torch.cuda.cudart().cudaHostRegister(self.buf.data_ptr(), total, 0)
             self.pinned = int(rc) == 0
             if not self.pinned:
+                # the runtime keeps the failure as its "last error": read it off, or the next
+                # unrelated CUDA call that checks for errors reports it
+                try:
+                    import ctypes
+                    from pathlib import Path
+                    ctypes.CDLL(str(Path(__file__).resolve().parent.parent / "_C.so")).b200_cuda_take_last_error()
+                except OSError:
+                    pass
                 logger.warning("KV pool %s: cudaHostRegister failed (%s); copies will be pageable", name, rc)
         self._free = list(range(self.num_slots - 1, -1, -1)) if create else []
         self._lock = threading.Lock()

@@ -431,6 +431,30 @@ def task_nvls(rank, world, port, workdir, device_kind):
         res["us"][f"fused_norm_{rows}rows"] = {
             "nvls_one_shot": graph_time(lambda: nv.all_reduce(x, rr, wn, 1e-6, mode=1), 20),
             "push": graph_time(lambda: symm.all_reduce_add_rms_norm(x, rr, wn, 1e-6), 20)}
+    # row-parallel decode projections of a Llama-3-8B layer at this world size, 128 tokens: the
+    # GEMM with the all-reduce + residual + RMSNorm pushed from its epilogue (one kernel, every rank
+    # sends its tile to every other rank), against the plain GEMM followed by the all-reduce + norm
+    # through the switch or by NCCL + the norm kernel
+    for label, k_full in (("o_proj", 4096), ("down_proj", 14336)):
+        k = k_full // world
+        x = torch.randn(128, k, device=dev, dtype=torch.bfloat16) * 0.1
+        ws = [torch.randn(4096, k, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(8)]
+        rr = torch.zeros(128, 4096, device=dev, dtype=torch.bfloat16)
+        it = [0]
+
+        def w_next():
+            it[0] += 1
+            return ws[it[0] % len(ws)]
+
+        def nccl_path():
+            y = ops.gemm(x, w_next())
+            dist.all_reduce(y, group=g.device_group)
+            return ops.fused_add_rms_norm(y, rr, wn, 1e-6)
+        row = {"gemm_then_nccl_then_norm": graph_time(nccl_path, 16),
+               "gemm_then_nvls_norm": graph_time(lambda: nv.all_reduce(ops.gemm(x, w_next()), rr, wn, 1e-6, mode=1), 16)}
+        if symm.can_fuse_gemm(x, ws[0]):
+            row["fused_gemm_push_norm"] = graph_time(lambda: symm.gemm_all_reduce(x, w_next(), None, rr, wn, 1e-6), 16)
+        res["us"][f"{label}_128x4096x{k}"] = row
     torch.cuda.synchronize()
     ops.check_status()
     g.barrier()

@@ -46,8 +46,13 @@ def test_sleep_releases_device_memory_and_wake_restores_the_weights():
 def test_disaggregated_serving_through_the_host_pool_on_the_gpu(tmp_path, monkeypatch):
     """Prefill instance copies the prompt KV into pinned host slots and frees its GPU blocks; the
     decode instance loads the slots into its own cache and generates what one instance generates."""
+    import os
+    import tempfile
+
     from omni_npu_b200.kv_transfer import host_pool
-    monkeypatch.setattr(host_pool, "POOL_DIR", str(tmp_path))
+    # shared memory, as in deployment (a mapping of a file on disk cannot be pinned)
+    shm = tempfile.mkdtemp(prefix="b200_pool_test_", dir="/dev/shm") if os.path.isdir("/dev/shm") else str(tmp_path)
+    monkeypatch.setattr(host_pool, "POOL_DIR", shm)
     cfg = ModelConfig(hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=64,
                       intermediate_size=1024, vocab_size=2048, rope_theta=10000.0,
                       max_position_embeddings=2048, dtype=torch.bfloat16)
@@ -86,3 +91,6 @@ def test_disaggregated_serving_through_the_host_pool_on_the_gpu(tmp_path, monkey
     finally:
         prefill.engine.shutdown()
         decode.engine.shutdown()
+        import shutil
+        if shm.startswith("/dev/shm/b200_pool_test_"):
+            shutil.rmtree(shm, ignore_errors=True)
