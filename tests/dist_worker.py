@@ -508,6 +508,84 @@ def task_ep_moe(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_ep_timing(rank, world, port, workdir, device_kind):
+    """Device time of the expert-parallel dispatch and combine alone (CUDA events around CUDA-graph
+    replays, max over ranks) for the row sizes of DeepSeek-V2-Lite and DeepSeek-V3.2, with the bytes
+    that cross NVLink per rank and the fraction of the measured peer-copy rate (770 GB/s per
+    direction) they amount to."""
+    dev, state = setup(rank, world, port, "cuda")
+    state.init_model_parallel(tp=world, device=dev)
+    import torch.distributed as dist
+    from omni_npu_b200 import ops
+    from omni_npu_b200.layers.moe_dispatch import EpBuffers, ep_combine, ep_dispatch
+    g = state.get_tp_group()
+    link = 770e9
+    res = {}
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(reps):
+                fn()
+        torch.cuda.synchronize()
+        g.barrier()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (3 * reps) * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g.device_group)
+        return float(t)
+
+    for label, E, K, H in (("v2lite", 64, 6, 2048), ("v32", 256, 8, 7168)):
+        for T in (128, 2048):
+            torch.manual_seed(11 + rank)
+            x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+            w, ids = torch.topk(torch.softmax(torch.randn(T, E, device=dev), -1), K)
+            ids = ids.to(torch.int32)
+            w = w.float()
+            row = {}
+            for fp8 in (False, True):
+                buf = EpBuffers(g, dev, E, H, T, K, fp8_dispatch=fp8)
+                out = [None]
+
+                def disp():
+                    out[0] = ep_dispatch(None, x, ids, w, E, buf, fp8=fp8)
+                t_d = timed(disp)
+                rows, offs, handle = out[0]
+                sent = T * K * (world - 1) / world                      # rows that leave this rank (uniform routing)
+                by = sent * (H + H // 128 * 4 if fp8 else H * 2)
+                key = "fp8" if fp8 else "bf16"
+                row[f"dispatch_{key}_us"] = round(t_d, 1)
+                row[f"dispatch_{key}_link_bytes"] = int(by)
+                row[f"dispatch_{key}_frac_of_link"] = round(by / link / (t_d * 1e-6), 3)
+                if not fp8:
+                    y = buf.expert_y
+                    y[: rows.shape[0]].copy_(rows)                       # combine reads the expert outputs in place
+                    t_c = timed(lambda: ep_combine(None, y[: rows.shape[0]], handle, None, buf))
+                    byc = sent * H * 2
+                    row["combine_us"] = round(t_c, 1)
+                    row["combine_link_bytes"] = int(byc)
+                    row["combine_frac_of_link"] = round(byc / link / (t_c * 1e-6), 3)
+                torch.cuda.synchronize()
+                g.barrier()
+                buf.close()
+            res[f"{label}_T{T}"] = row
+    ops.check_status()
+    g.barrier()
+    json.dump(res, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    state.finish_process()
+    state.destroy_distributed()
+
+
 def task_kv_pull(rank, world, port, workdir, device_kind):
     """Rank 0 owns a KV cache, rank 1 maps it through CUDA IPC and pulls blocks with the copy kernel."""
     dev, state = setup(rank, world, port, "cuda")
@@ -717,7 +795,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"nvls": task_nvls, "dcp_engine": task_dcp_engine, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"nvls": task_nvls, "ep_timing": task_ep_timing, "dcp_engine": task_dcp_engine, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

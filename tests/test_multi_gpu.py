@@ -91,11 +91,30 @@ def test_expert_parallel_moe_dispatch_combine_over_peer_memory():
         assert max(r["max_err"].values()) < 0.06, r
 
 
+def test_expert_parallel_dispatch_and_combine_device_times():
+    """Times only (the numerics are the test above): dispatch in bf16 and with the fp8 quantisation
+    fused in, and the combine, on every GPU of the box; written out for the profile notes."""
+    world = min(8, torch.cuda.device_count())
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("ep_timing", world, d, device="cuda", timeout=600)
+    for name, row in res[0].items():
+        assert row["dispatch_bf16_us"] > 0 and row["combine_us"] > 0, (name, row)
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, f"ep_dispatch_combine_{world}gpu.json"), "w") as f:
+            json.dump(res[0], f, indent=1)
+    print(f"EP dispatch / combine on {world} GPUs:", json.dumps(res[0], indent=1))
+
+
 def test_kv_blocks_pulled_gpu_to_gpu_are_byte_exact():
     with tempfile.TemporaryDirectory() as d:
         res = run_ranks("kv_pull", 2, d, device="cuda", timeout=300)
     assert res[1]["byte_exact"]
     print("kv pull GB/s:", res[1]["gbs"])
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "kv_pull_2gpu.json"), "w") as f:
+            json.dump({k: res[1].get(k) for k in ("gbs", "gbs_small", "byte_exact")}, f)
 
 
 def test_tensor_parallel_engine_two_gpus_matches_one_gpu():
