@@ -270,6 +270,9 @@ class SchedulerConfig:
     max_model_len: int = 8192
     enable_chunked_prefill: bool = True
     policy: str = "fcfs"
+    # cache slots kept allocated past the tokens a step feeds (a draft head that runs a chain of
+    # k steps writes its keys for k - 1 positions that are scheduled only in the next step)
+    num_lookahead_tokens: int = 0
 
 
 @dataclass

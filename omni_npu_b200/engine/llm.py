@@ -53,6 +53,8 @@ class LLMEngine:
             if connector is not None or (config.speculative.method and config.speculative.num_speculative_tokens):
                 raise ValueError("decode context parallelism is not combined with KV connectors or "
                                  "speculative decoding")
+        if config.speculative.method in ("mtp", "deepseek_mtp") and config.speculative.num_speculative_tokens > 1:
+            config.scheduler.num_lookahead_tokens = config.speculative.num_speculative_tokens - 1
         self.scheduler = Scheduler(config.scheduler, config.cache, num_blocks, reserved, connector,
                                    context_parallel_size=dcp)
         self._ids = itertools.count()

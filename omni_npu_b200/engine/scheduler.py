@@ -95,6 +95,10 @@ class Scheduler:
 
     # ---------------------------------------------------------------- blocks
     def _ensure_blocks(self, req: Request, total_tokens: int) -> bool:
+        look = getattr(self.cfg, "num_lookahead_tokens", 0)
+        if look:
+            # slots for a draft head's chain of extra steps (never past the longest sequence allowed)
+            total_tokens = max(total_tokens, min(total_tokens + look, self.cfg.max_model_len))
         need = self.pool.blocks_needed(total_tokens, len(req.block_ids))
         if need == 0:
             return True

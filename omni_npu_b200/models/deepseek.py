@@ -205,8 +205,8 @@ class DeepseekForCausalLM(nn.Module):
     def make_empty_intermediate_tensors(self, num_tokens: int, dtype, device):
         return self.model.make_empty_intermediate_tensors(num_tokens, dtype, device)
 
-    def mtp_forward(self, next_ids, positions, hidden):
-        return self.mtp(self.model.embed_tokens(next_ids), hidden)
+    def mtp_forward(self, next_ids, positions, hidden, spec_step: int = 0):
+        return self.mtp(self.model.embed_tokens(next_ids), hidden, spec_step)
 
     def mtp_logits(self, hidden):
         return (self.mtp.own_head or self.lm_head).compute_logits(hidden)

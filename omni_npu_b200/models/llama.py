@@ -241,9 +241,10 @@ class LlamaForCausalLM(nn.Module):
     def make_empty_intermediate_tensors(self, num_tokens: int, dtype: torch.dtype, device):
         return self.model.make_empty_intermediate_tensors(num_tokens, dtype, device)
 
-    def mtp_forward(self, next_ids: torch.Tensor, positions: torch.Tensor, hidden: torch.Tensor) -> torch.Tensor:
+    def mtp_forward(self, next_ids: torch.Tensor, positions: torch.Tensor, hidden: torch.Tensor,
+                    spec_step: int = 0) -> torch.Tensor:
         """Hidden states of the MTP head for (embedding of the next token, target hidden state)."""
-        return self.mtp(self.model.embed_tokens(next_ids), hidden)
+        return self.mtp(self.model.embed_tokens(next_ids), hidden, spec_step)
 
     def mtp_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         head = self.mtp.own_head or self.lm_head

@@ -66,7 +66,9 @@ class ModelRunner:
         self.capture_sizes: List[int] = []
         pin = device.type == "cuda"
         self.sampled_host = torch.zeros(max(sc.max_num_seqs, 1), dtype=torch.int32, pin_memory=pin)
-        self.sampled_host2 = torch.zeros(max(sc.max_num_seqs, 1), 2, dtype=torch.int32, pin_memory=pin)
+        # with a draft head: the sampled token and its k drafts per sequence
+        self.mtp_k = max(1, int(config.speculative.num_speculative_tokens or 1))
+        self.sampled_host2 = torch.zeros(max(sc.max_num_seqs, 1), 1 + self.mtp_k, dtype=torch.int32, pin_memory=pin)
         # Penalties and the thinking-token budget work on each request's token history, which lives
         # on the host: a step that needs them runs eagerly with ``_logits_fn`` set (never from a
         # graph, never launched ahead of the previous step's tokens).
@@ -214,8 +216,8 @@ class ModelRunner:
 
     def _forward_and_sample(self, views, md: AttentionMetadata, num_samples: int) -> torch.Tensor:
         """Model forward + LM head + sampling for the staged step (device side only).
-        Returns the sampled tokens [num_samples]; with an MTP head int32 [num_samples, 2]:
-        the sampled token and the draft for the token after it."""
+        Returns the sampled tokens [num_samples]; with an MTP head int32 [num_samples, 1 + k]:
+        the sampled token and the k drafts for the tokens after it."""
         if self.pp_group is not None:
             return self._forward_and_sample_pipeline(views, md, num_samples)
         with set_forward_context(md, self.kv_caches, self.config):
@@ -242,8 +244,38 @@ class ModelRunner:
                 nxt.clamp_(min=0)
             h = self.model.mtp_forward(nxt, views["pos"], hidden_all)
             h = h.index_select(0, idx) if idx is not None else h[:num_samples]
-            draft = ops.argmax(self.model.mtp_logits(h))
-        return torch.stack([tok, draft.to(torch.int32)], dim=1)
+            draft = ops.argmax(self.model.mtp_logits(h)).to(torch.int32)
+            drafts = [draft]
+            if self.mtp_k > 1:
+                pos = views["pos"]
+                last = pos.index_select(0, idx) if idx is not None else pos[:num_samples]
+                drafts += self._mtp_chain(h, draft, last, views["bt"][:num_samples], md)
+        return torch.stack([tok] + drafts, dim=1)
+
+    def _mtp_chain(self, h: torch.Tensor, draft: torch.Tensor, last_pos: torch.Tensor, bt: torch.Tensor,
+                   md: AttentionMetadata) -> List[torch.Tensor]:
+        """Draft tokens 2..k of a draft head that is run as a chain: step j feeds the token drafted
+        by step j - 1 and that step's hidden state at position ``last_pos + j`` (a one-token decode
+        step of the head's own cache layer; the scheduler keeps these slots allocated).  Everything
+        is computed on the device, so the chain is part of a captured decode step.  Same flow as the
+        draft loop of the reference's proposer (omni_npu/vllm_patches/patches/common/patch_eagle.py:417-560)."""
+        n = h.shape[0]
+        bs = self.config.cache.block_size
+        cu = torch.arange(n + 1, dtype=torch.int32, device=h.device)
+        out = []
+        for j in range(1, self.mtp_k):
+            pos = (last_pos + j).to(torch.int32)
+            blk_idx = (pos // bs).clamp(max=bt.shape[1] - 1).long().unsqueeze(1)
+            slot = (bt.gather(1, blk_idx).squeeze(1) * bs + pos % bs).to(torch.int32)
+            md_j = AttentionMetadata(is_prefill=False, num_seqs=n, num_tokens=n, max_q_len=1,
+                                     max_seq_len=md.max_seq_len + j, q_len=1, positions=pos, slot_mapping=slot,
+                                     block_tables=bt, seq_lens=pos + 1, cu_q=cu, num_actual_tokens=n,
+                                     num_actual_seqs=n)
+            with set_forward_context(md_j, self.kv_caches, self.config):
+                h = self.model.mtp_forward(draft.clamp_min(0), pos, h, spec_step=j)
+                draft = ops.argmax(self.model.mtp_logits(h)).to(torch.int32)
+            out.append(draft)
+        return out
 
     def _forward_and_sample_pipeline(self, views, md: AttentionMetadata, num_samples: int) -> torch.Tensor:
         """One step of this rank's pipeline stage.  Activations travel stage to stage with
@@ -279,8 +311,8 @@ class ModelRunner:
     def _forward_and_verify(self, views, md: AttentionMetadata, seqs) -> torch.Tensor:
         """Verification step of speculative decoding: logits at every fed position, target
         tokens sampled there, drafts accepted while they agree.  Returns int32
-        [n, max_k + 2 (+1)]: the settled tokens (-1 padded), their count and, with an MTP
-        head, the draft for the next step."""
+        [n, max_k + 2 (+k)]: the settled tokens (-1 padded), their count and, with an MTP
+        head, the k drafts for the next step."""
         n = len(seqs)
         with set_forward_context(md, self.kv_caches, self.config):
             hidden = self.model(views["ids"], views["pos"])
@@ -296,8 +328,12 @@ class ModelRunner:
                 nxt = toks.reshape(-1).index_select(0, views["next_ids"].long()).clamp_min(0)
                 h = self.model.mtp_forward(nxt, views["pos"], hidden)
                 rows = (views["cu_q"][:n] + counts - 1).long()
-                draft = ops.argmax(self.model.mtp_logits(h.index_select(0, rows)))
-                cols.append(draft.to(torch.int32).unsqueeze(1))
+                h_last = h.index_select(0, rows)
+                draft = ops.argmax(self.model.mtp_logits(h_last)).to(torch.int32)
+                cols.append(draft.unsqueeze(1))
+                if self.mtp_k > 1:
+                    last = views["pos"].index_select(0, rows)
+                    cols += [d.unsqueeze(1) for d in self._mtp_chain(h_last, draft, last, views["bt"][:n], md)]
         return torch.cat(cols, dim=1)
 
     @staticmethod
@@ -415,8 +451,9 @@ class ModelRunner:
             self.d2h_bytes_last = packed.numel() * 4
             rows = host.tolist()
             if self.mtp is not None:
-                self.last_drafts = [[r[-1]] for r in rows]
-                return [r[: r[-2]] for r in rows]
+                k = self.mtp_k
+                self.last_drafts = [r[-k:] for r in rows]
+                return [r[: r[-k - 1]] for r in rows]
             return [r[: r[-1]] for r in rows]
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
@@ -452,10 +489,10 @@ class ModelRunner:
             host.copy_(sampled[:n], non_blocking=True)
             if self.device.type == "cuda":
                 torch.cuda.current_stream(self.device).synchronize()
-            self.d2h_bytes_last = n * 8
+            self.d2h_bytes_last = n * 4 * (1 + self.mtp_k)
             pairs = host.tolist()
             tokens = [p[0] for p in pairs]
-            self.last_drafts = [[p[1]] if s.samples else [] for p, s in zip(pairs, out.seqs)]
+            self.last_drafts = [p[1:] if s.samples else [] for p, s in zip(pairs, out.seqs)]
         else:
             host = self.sampled_host[:n]
             host.copy_(sampled[:n], non_blocking=True)

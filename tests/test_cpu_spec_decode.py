@@ -102,6 +102,28 @@ def test_engine_with_mtp_head_matches_plain_greedy():
     assert st["drafted"] > 0 and spec.engine.stats["spec_decode_steps"] > 0
 
 
+def test_engine_with_mtp_chain_of_three_drafts_matches_plain_greedy():
+    """k = 3: the head runs as a chain of three steps (its own hidden state and draft feed the next
+    step one position further), the scheduler keeps two slots of look-ahead allocated, verification
+    steps check up to three drafts.  Output identical to plain greedy decoding; with the MTP layer
+    made a copy of the logic that produced the target's next token the drafts are also accepted."""
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (9, 30, 17, 5)]
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=24, max_model_len=128,
+              block_size=8, num_gpu_blocks=96, seed=3)
+    plain = LLM(model=_tiny(), **kw)
+    want = [o.output_token_ids for o in plain.generate(prompts, sp)]
+    spec = LLM(model=_tiny(), speculative_config={"method": "mtp", "num_speculative_tokens": 3}, **kw)
+    runner = spec.engine.worker.model_runner
+    assert runner.mtp_k == 3 and spec.engine.scheduler.cfg.num_lookahead_tokens == 2
+    got = [o.output_token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    st = spec.engine.scheduler.spec_stats
+    assert st["drafted"] >= 3 * spec.engine.stats["spec_decode_steps"] > 0
+    assert spec.engine.scheduler.pool.num_free == 96             # look-ahead blocks are released too
+
+
 def test_mtp_checkpoint_names():
     from omni_npu_b200.config import EngineConfig, SpeculativeConfig
     from omni_npu_b200.models.llama import LlamaForCausalLM
