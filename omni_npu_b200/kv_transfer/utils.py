@@ -80,3 +80,48 @@ class TPConvertor:
         """Blocks that actually hold tokens (the tail of the producer's list may be unused)."""
         n = (num_tokens + block_size - 1) // block_size
         return list(remote_block_ids[:n])
+
+
+# ------------------------------------------------------------------------------------------------
+# Token-interleaved caches (decode context parallelism): token p of a sequence lives on rank
+# p % world at local index p // world.  When the decode instance shards over more ranks than the
+# prefill instance (d_world = stride x p_world) a consumer rank needs every stride-th token of ONE
+# producer rank.  The reference pulls whole blocks at a block stride and then evens out the tail
+# block's tokens with an all-to-all among the consumer ranks (omni_npu/connector/utils.py:27-74,
+# 126-180); with per-token interleaving the same result is a strided gather out of the pulled
+# blocks, with no exchange between consumer ranks.
+@dataclass
+class DcpReshardPlan:
+    src_rank: int                 # producer rank this consumer rank pulls from
+    num_tokens: int               # tokens this consumer rank ends up holding
+    src_blocks: List[int]         # indices into the producer rank's block list that must be pulled
+    src_local: List[int]          # producer-local token index of each token, in consumer-local order
+
+
+def plan_dcp_reshard(num_tokens: int, p_world: int, d_world: int, d_rank: int, block_size: int) -> DcpReshardPlan:
+    """Which of the producer's tokens consumer rank ``d_rank`` takes, and from which blocks."""
+    if d_world % p_world != 0:
+        raise ValueError(f"consumer world {d_world} must be a multiple of the producer world {p_world}")
+    stride = d_world // p_world
+    a, b = divmod(d_rank, p_world)                       # token p = (k * stride + a) * p_world + b
+    n = max(0, -(-(num_tokens - d_rank) // d_world))     # tokens with p % d_world == d_rank
+    src_local = [k * stride + a for k in range(n)]
+    blocks = sorted({i // block_size for i in src_local})
+    return DcpReshardPlan(b, n, blocks, src_local)
+
+
+def apply_dcp_reshard(dst_cache, dst_block_ids: Sequence[int], pulled, plan: DcpReshardPlan, block_size: int) -> None:
+    """Move the planned tokens from ``pulled`` (the producer blocks named by ``plan.src_blocks``, in
+    that order, shape [len(src_blocks), block_size, ...]) into ``dst_cache`` ([num_blocks,
+    block_size, ...]) at this rank's blocks ``dst_block_ids``: consumer-local token k goes to block
+    ``dst_block_ids[k // block_size]``, offset ``k % block_size``."""
+    import torch
+    if plan.num_tokens == 0:
+        return
+    where = {blk: i for i, blk in enumerate(plan.src_blocks)}
+    dev = dst_cache.device
+    src_b = torch.tensor([where[i // block_size] for i in plan.src_local], dtype=torch.long, device=dev)
+    src_o = torch.tensor([i % block_size for i in plan.src_local], dtype=torch.long, device=dev)
+    k = torch.arange(plan.num_tokens, device=dev)
+    dst_b = torch.tensor(list(dst_block_ids), dtype=torch.long, device=dev)[k // block_size]
+    dst_cache[dst_b, k % block_size] = pulled[src_b, src_o]

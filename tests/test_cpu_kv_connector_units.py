@@ -98,3 +98,37 @@ def test_parked_blocks_return_on_ack_or_after_the_delay():
     assert pool.release_parked("req-a") and pool.num_free == free0 + 5      # the consumer's ack
     assert not pool.release_parked("req-a")                          # a second ack is harmless
     assert pool.num_parked == 0
+
+
+def test_token_interleaved_cache_resharded_to_a_wider_decode_group():
+    """Prefill on 2 ranks, decode on 4: every decode rank takes each second token of one prefill rank
+    out of the blocks it pulled and ends up with exactly its own tokens, in order."""
+    import torch
+
+    from omni_npu_b200.kv_transfer.utils import apply_dcp_reshard, plan_dcp_reshard
+    n, pw, dw, bs, width = 37, 2, 4, 4, 3
+    # producer caches: token p sits on rank p % pw at local index p // pw; its row carries p
+    prod = []
+    for r in range(pw):
+        local = [p for p in range(n) if p % pw == r]
+        nblk = -(-len(local) // bs)
+        c = torch.full((nblk, bs, width), -1.0)
+        for i, p in enumerate(local):
+            c[i // bs, i % bs] = float(p)
+        prod.append(c)
+    seen = []
+    for r in range(dw):
+        plan = plan_dcp_reshard(n, pw, dw, r, bs)
+        mine = [p for p in range(n) if p % dw == r]
+        assert plan.src_rank == r % pw and plan.num_tokens == len(mine)
+        pulled = prod[plan.src_rank][torch.tensor(plan.src_blocks, dtype=torch.long)]
+        ids = list(range(10, 10 + -(-len(mine) // bs)))              # this rank's block ids, arbitrary
+        cache = torch.full((32, bs, width), -1.0)
+        apply_dcp_reshard(cache, ids, pulled, plan, bs)
+        got = [cache[ids[k // bs], k % bs, 0].item() for k in range(len(mine))]
+        assert got == [float(p) for p in mine]
+        seen += mine
+    assert sorted(seen) == list(range(n))
+    # equal worlds: the identity
+    plan = plan_dcp_reshard(10, 2, 2, 1, 4)
+    assert plan.src_rank == 1 and plan.src_local == [0, 1, 2, 3, 4]
