@@ -567,6 +567,22 @@ __device__ __forceinline__ uint32_t kv_swz(int key, int chunk) {
   return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
 }
 
+// Build with -DB200_ATTN_TIMELINE to record, per CTA of the TMA decode kernel, the global timer at
+// six points (entry, set-up done, first tile landed, last tile consumed, merged and stored, and the
+// SM id); read back with b200_gqa_decode_timeline().
+#ifdef B200_ATTN_TIMELINE
+__device__ unsigned long long g_attn_timeline[4096 * 8];
+__device__ __forceinline__ void attn_mark(int i) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (cta < 4096) g_attn_timeline[cta * 8 + i] = t;
+}
+#define B200_ATL(i) attn_mark(i)
+#else
+#define B200_ATL(i)
+#endif
+
 // NSTAGES / MINB: three stages and two CTAs per SM, or two stages and three CTAs per SM (more
 // warps to hide the latency of the dependent ldmatrix -> mma -> softmax chains).
 template <int D, int NSTAGES, int MINB>
@@ -586,6 +602,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
   int* s_abort = reinterpret_cast<int*>(empty_bar + Cfg::STAGES);
 
+  if (threadIdx.x == 0) B200_ATL(0);
   pdl_trigger();
   pdl_wait();   // sequence lengths, block tables, q and the cache rows of this step come from earlier kernels
   const int b = blockIdx.x;
@@ -632,6 +649,15 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   fence_proxy_async();
   __syncthreads();
   volatile int* abort_flag = s_abort;
+  if (threadIdx.x == 0) {
+    B200_ATL(1);
+#ifdef B200_ATTN_TIMELINE
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < 4096) g_attn_timeline[cta * 8 + 5] = smid;
+#endif
+  }
 
   if (warp == 4) {
     // ------------------------------------------------------------ producer
@@ -724,6 +750,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       }
       break;
     }
+    if (it == 0 && threadIdx.x == 0) B200_ATL(2);
     const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
     const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
     const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
@@ -797,6 +824,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
     if (lane == 0) mbar_arrive(&empty_bar[stage]);
   }
   __syncthreads();   // every warp (and the producer) is past the main loop
+  if (threadIdx.x == 0) B200_ATL(3);
   if (*abort_flag) {
     __syncthreads();
     return;
@@ -864,6 +892,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       }
     }
   }
+  if (threadIdx.x == 0) B200_ATL(4);
 }
 
 // ------------------------------------------------- decode, persistent CTAs
@@ -1572,3 +1601,9 @@ extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void
   if (D == 64) return launch_decode<64>(p, B, stream);
   return -2;
 }
+
+#ifdef B200_ATTN_TIMELINE
+extern "C" int b200_gqa_decode_timeline(unsigned long long* host, int ctas) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, b200::g_attn_timeline, sizeof(unsigned long long) * 8 * ctas));
+}
+#endif

@@ -88,6 +88,59 @@ class B200Communicator:
             dist.reduce_scatter_tensor(out, xm, group=self.device_group)
         return out.movedim(0, dim)
 
+    # ---------------------------------------------------- asynchronous forms
+    # The collective is enqueued on this communicator's own stream behind what the caller's
+    # stream has done so far; the returned handle's ``wait()`` makes the caller's stream wait for
+    # it (no host blocking), so kernels launched in between overlap the transfer.  On CPU (gloo)
+    # the handle is the process group's work object.  Counterpart of ``all_reduce_async`` /
+    # ``all_gather_async`` / ``reduce_scatter_async`` (omni_npu/v0/distributed/communicator.py:125-159).
+    class _StreamHandle:
+        def __init__(self, event, keep):
+            self.event, self.keep = event, keep
+
+        def wait(self) -> None:
+            torch.cuda.current_stream().wait_event(self.event)
+            self.keep = None
+
+    class _DoneHandle:
+        def wait(self) -> None:
+            return None
+
+    def _comm_stream(self):
+        st = getattr(self, "_async_stream", None)
+        if st is None:
+            st = torch.cuda.Stream(device=self.device)
+            self._async_stream = st
+        return st
+
+    def _async(self, x: torch.Tensor, fn):
+        """Run ``fn()`` (a collective of this class) off the caller's stream; returns (result, handle)."""
+        if self.world_size == 1:
+            return fn(), self._DoneHandle()
+        if not x.is_cuda:
+            out = fn()                       # gloo: the blocking form, then an already-finished handle
+            return out, self._DoneHandle()
+        cur = torch.cuda.current_stream(x.device)
+        st = self._comm_stream()
+        st.wait_stream(cur)
+        with torch.cuda.stream(st):
+            out = fn()
+            ev = torch.cuda.Event()
+            ev.record(st)
+        x.record_stream(st)
+        if isinstance(out, torch.Tensor):
+            out.record_stream(cur)
+        return out, self._StreamHandle(ev, (x, out))
+
+    def all_reduce_async(self, x: torch.Tensor):
+        return self._async(x, lambda: self.all_reduce(x))
+
+    def all_gather_async(self, x: torch.Tensor, dim: int = 0):
+        return self._async(x, lambda: self.all_gather(x, dim))
+
+    def reduce_scatter_async(self, x: torch.Tensor, dim: int = 0):
+        return self._async(x, lambda: self.reduce_scatter(x, dim))
+
     def all_gatherv(self, x: Union[torch.Tensor, List[torch.Tensor]], dim: int = 0,
                     sizes: Optional[Sequence[int]] = None):
         """All-gather of tensors whose size along ``dim`` differs per rank."""

@@ -64,6 +64,15 @@ class GroupCoordinator:
     def reduce_scatter(self, x, dim=-1):
         return self.comm.reduce_scatter(x, dim)
 
+    def all_reduce_async(self, x):
+        return self.comm.all_reduce_async(x)
+
+    def all_gather_async(self, x, dim=0):
+        return self.comm.all_gather_async(x, dim)
+
+    def reduce_scatter_async(self, x, dim=0):
+        return self.comm.reduce_scatter_async(x, dim)
+
     def all_gatherv(self, x, dim=0, sizes=None):
         return self.comm.all_gatherv(x, dim, sizes)
 

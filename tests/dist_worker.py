@@ -60,6 +60,13 @@ def task_comm(rank, world, port, workdir, device_kind):
             g.send(torch.tensor([7.0, 8.0], device=dev), dst=1)
         elif rank == 1:
             res["recv"] = g.recv((2,), torch.float32, src=0).tolist()
+    # asynchronous forms: result + a handle to wait on before the result is used
+    y, h = g.all_reduce_async(torch.full((4, 6), float(rank + 1), device=dev))
+    z, h2 = g.all_gather_async(torch.full((2, 3), float(rank), device=dev), dim=0)
+    w, h3 = g.reduce_scatter_async(torch.arange(world * 2, dtype=torch.float32, device=dev).view(world * 2, 1).repeat(1, 2), dim=0)
+    for hh in (h, h2, h3):
+        hh.wait()
+    res["async"] = [y.flatten()[0].item(), z[:, 0].tolist(), w[:, 0].tolist()]
     res["bcast_obj"] = g.broadcast_object({"k": rank} if rank == 0 else None, src=0)
     lg = state.register_layer_group("self_attn.o_proj", world)
     res["layer_group"] = [lg.world_size, lg.rank_in_group]

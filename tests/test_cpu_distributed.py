@@ -28,6 +28,7 @@ def test_communicator_semantics_two_ranks():
     assert r1["recv"] == [7.0, 8.0]
     assert r0["swap"] == [11.0] * 3 and r1["swap"] == [10.0] * 3
     assert r1["bcast_obj"] == {"k": 0}
+    assert r0["async"] == [3.0, [0.0, 0.0, 1.0, 1.0], [0.0, 2.0]] and r1["async"][2] == [4.0, 6.0]
     assert r0["layer_group"] == [2, 0] and r1["layer_group"] == [2, 1]
 
 

@@ -197,3 +197,28 @@ def test_asynchronous_decode_scheduling_gives_the_same_tokens(eager):
         del llm
     assert outs[True] == outs[False]
     assert outs[True][4][1] == "stop" and len(outs[True][4][0]) <= 11
+
+
+def test_mtp_chain_of_three_drafts_under_cuda_graphs():
+    """A draft head run as a chain of three steps inside the step: the captured decode graphs
+    (target model + head + chain) give the tokens of the eager path, drafts are scheduled and
+    verified, and every block (the look-ahead ones included) goes back to the pool."""
+    cfg = _small_cfg()
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (48, 5, 130, 17)]
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    outs = {}
+    for eager in (False, True):
+        llm = LLM(model=cfg, device="cuda", max_num_seqs=4, max_num_batched_tokens=256, max_model_len=512,
+                  num_gpu_blocks=256, enforce_eager=eager, seed=3,
+                  speculative_config={"method": "mtp", "num_speculative_tokens": 3})
+        runner = llm.engine.worker.model_runner
+        assert runner.mtp is not None and runner.mtp_k == 3
+        outs[eager] = [o.output_token_ids for o in llm.generate(prompts, sp)]
+        assert all(len(t) == 20 for t in outs[eager])
+        st = llm.engine.scheduler.spec_stats
+        assert st["drafted"] >= 3 * llm.engine.stats["spec_decode_steps"] > 0
+        assert llm.engine.scheduler.pool.num_free == 256
+        ops.check_status()
+        del llm
+    assert outs[False] == outs[True]
