@@ -315,6 +315,16 @@ class LLM:
     def stop_profile(self) -> None:
         self.engine.worker.profile(False)
 
+    def sleep(self, level: int = 1) -> int:
+        """Give the device memory of the sleep-mode pool back (needs ``enable_sleep_mode=True``);
+        only between requests.  Returns the bytes released."""
+        if self.engine.has_unfinished_requests():
+            raise RuntimeError("sleep() while requests are running")
+        return self.engine.worker.sleep(level)
+
+    def wake_up(self, tags=None) -> int:
+        return self.engine.worker.wake_up(tags)
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  ) -> List[RequestOutput]:

@@ -238,6 +238,17 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
         llm.stop_profile()
         return {"status": "stopped"}
 
+    @app.post("/sleep")
+    async def sleep(level: int = 1):
+        try:
+            return {"status": "asleep", "released_bytes": llm.sleep(level)}
+        except RuntimeError as e:
+            return JSONResponse({"error": str(e)}, status_code=409)
+
+    @app.post("/wake_up")
+    async def wake_up():
+        return {"status": "awake", "mapped_bytes": llm.wake_up()}
+
     @app.get("/v1/models")
     def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
