@@ -290,9 +290,33 @@ def bench_indexer(args):
               f"(frac {fl/flops/(ms/1e3):.2f})  keys {by/ms/1e6:6.0f} GB/s (frac {by/hbm/(ms/1e3):.2f})")
 
 
+def bench_moe(args):
+    """Grouped (per-expert) GEMMs of the MoE layers at decode and prefill row counts, uniform routing."""
+    hbm, flops_peak, src = peaks()
+    print(f"# grouped expert GEMMs bf16, fractions of {src} peaks")
+    print(f"{'shape':34s} {'rows':>6s} {'E':>4s} {'N':>6s} {'K':>6s} {'us':>9s} {'GB/s':>7s} {'TFLOP/s':>8s} {'frac':>5s}")
+    cases = (("v2-lite w13 decode", 128 * 6, 64, 2 * 1408, 2048, True), ("v2-lite w2 decode", 128 * 6, 64, 2048, 1408, False),
+             ("qwen3-30b w13 decode", 128 * 8, 128, 2 * 768, 2048, True), ("qwen3-30b w2 decode", 128 * 8, 128, 2048, 768, False),
+             ("v2-lite w13 prefill", 8192 * 6, 64, 2 * 1408, 2048, True), ("qwen3-30b w13 prefill", 8192 * 8, 128, 2 * 768, 2048, True))
+    for label, rows, e, n, k, swiglu in cases:
+        torch.manual_seed(0)
+        ids = torch.randint(0, e, (rows,), device="cuda")
+        counts = torch.bincount(ids, minlength=e)
+        offs = torch.zeros(e + 1, dtype=torch.int32, device="cuda")
+        offs[1:] = torch.cumsum(counts, 0)
+        a = torch.randn(rows, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(e, n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+        t = time_fn(lambda: ops.grouped_gemm(a, w, offs, swiglu=swiglu), iters=args.iters)
+        by = 2.0 * (e * n * k + rows * k + rows * (n // 2 if swiglu else n))
+        fl = 2.0 * rows * n * k
+        frac = max(fl / flops_peak, by / hbm) / (t / 1e3)
+        print(f"{label:34s} {rows:6d} {e:4d} {n:6d} {k:6d} {t*1e3:9.1f} {by/t/1e6:7.0f} {fl/t/1e9:8.1f} {frac:5.2f}")
+    ops.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "indexer", "quant", "all"])
+    ap.add_argument("what", choices=["gemm", "attn", "norm", "sample", "indexer", "quant", "moe", "all"])
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
@@ -322,6 +346,8 @@ def main():
         bench_indexer(args)
     if args.what in ("quant", "all"):
         bench_quant(args)
+    if args.what in ("moe", "all"):
+        bench_moe(args)
 
 
 if __name__ == "__main__":
