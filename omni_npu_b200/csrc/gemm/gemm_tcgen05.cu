@@ -58,7 +58,6 @@ __device__ __forceinline__ void timeline_mark(int i) {
 #define B200_TL(i)
 #endif
 static constexpr int kMaxExperts = 512;
-static constexpr int kASmallRows = 32;               // rows of the short A box (multiple of the 8-row swizzle atom)
 static constexpr int kRsPitch = 144;                 // bytes per staged row (64 bf16 columns + padding)
 static constexpr int kRsWarpBytes = 32 * kRsPitch;   // staging of one epilogue warp
 
@@ -79,7 +78,6 @@ struct GemmParams {
   int swiglu;             // 1: C[:, n/2] = silu(acc[gate]) * acc[up], gate/up interleaved per 16 cols
   int num_experts;        // grouped: number of local experts (0 = dense)
   int cluster_split;      // 1: the `splits` CTAs of a cluster share one tile and reduce over DSMEM
-  int a_small_rows;       // > 0: tiles with at most this many valid rows load A through the short-box map
   void* C;
   const __nv_bfloat16* bias;       // [N] or null
   const __nv_bfloat16* residual;   // [M, ldc] or null
@@ -201,8 +199,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const int* s_ti
 template <bool GROUPED, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_w,
-                    const __grid_constant__ CUtensorMap tmap_a_small, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128B swizzle atoms.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -247,7 +244,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     fence_barrier_init();
     if (p.cluster_split) mbar_arrive_expect_tx(red_ready, static_cast<uint32_t>(kBM * p.BN * 4));
     tma_prefetch_desc(&tmap_a);
-    if (p.a_small_rows > 0) tma_prefetch_desc(&tmap_a_small);
     tma_prefetch_desc(&tmap_w);
   }
   int total_mn_tiles;
@@ -319,12 +315,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int c0 = 0;
         if (decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t_first, cta_rank, c0, tc)) {
           int g = 0;
-          const int a_bytes0 = (p.a_small_rows > 0 && tc.a_src < 0 && tc.m_end - tc.m0 <= p.a_small_rows)
-                                   ? p.a_small_rows * kRowBytes
-                                   : a_stage_bytes;
           for (int k = tc.k_begin; k < tc.k_end && g < groups; k += p.ksub, ++g) {
             const int ns = tc.k_end - k < p.ksub ? tc.k_end - k : p.ksub;
-            mbar_arrive_expect_tx(&full_bar[g], static_cast<uint32_t>(ns * (a_bytes0 + w_stage_bytes)));
+            mbar_arrive_expect_tx(&full_bar[g], static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
             for (int j = 0; j < ns; ++j)
               tma_load_2d(smem_w + (g * p.ksub + j) * w_stage_bytes, &tmap_w, &full_bar[g],
                           (k + j) * (kRowBytes / p.elem_bytes), tc.n0);
@@ -341,13 +334,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (long long t = t_first; ok && decode_tile<GROUPED>(p, s_tile_prefix, total_mn_tiles, t,
                                                                 cta_rank, cursor, tc);
            t += t_stride) {
-        // A tile with few valid rows (a decode step's share of one expert, a small batch) brings in
-        // only those rows: the full 128-row box would move as many bytes through the L2-to-SM fabric
-        // as the weight tile does.  The rows of the stage that no copy writes keep stale bytes; they
-        // feed accumulator rows that no epilogue stores.
-        const bool a_small = p.a_small_rows > 0 && tc.a_src < 0 && tc.m_end - tc.m0 <= p.a_small_rows;
-        const CUtensorMap* map_a = a_small ? &tmap_a_small : &tmap_a;
-        const int a_bytes = a_small ? p.a_small_rows * kRowBytes : a_stage_bytes;
+        const CUtensorMap* map_a = &tmap_a;
         const int a_row = tc.m0;
         if (tc.a_src >= 0 && !((ag_have >> tc.a_src) & 1u)) {
           // first tile of a foreign block: every CTA must have delivered its share of it
@@ -381,7 +368,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               break;
             }
             mbar_arrive_expect_tx(&full_bar[stage],
-                                  static_cast<uint32_t>(ns * (a_bytes + w_stage_bytes)));
+                                  static_cast<uint32_t>(ns * (a_stage_bytes + w_stage_bytes)));
           }
           for (int j = 0; j < ns; ++j) {
             const int slab = stage * p.ksub + j;
@@ -1266,8 +1253,8 @@ static int next_pow2_cols(int x) {
 }
 
 template <bool GROUPED, int KIND>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& ta_small, const GemmParams& p,
-                  int grid, size_t smem, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
+                  size_t smem, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<GROUPED, KIND>;
   static DeviceOnce once;
   int dev = 0;
@@ -1277,7 +1264,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMa
     once.mark(dev);
   }
   const int cluster_x = p.cluster_split ? p.splits : 1;
-  return launch_pdl(kern, dim3(grid, 1, 1), dim3(kThreads, 1, 1), smem, stream, cluster_x, ta, tw, ta_small, p) == cudaSuccess
+  return launch_pdl(kern, dim3(grid, 1, 1), dim3(kThreads, 1, 1), smem, stream, cluster_x, ta, tw, p) == cudaSuccess
              ? 0
              : (p.cluster_split ? -22 : -21);
 }
@@ -1638,12 +1625,6 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
   if (r) return r;
   r = make_tensormap_2d(&tw, dt, eb, W, N, K, ldw, BN, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
-  CUtensorMap ta_small = ta;
-  if (M <= kASmallRows && (ag == nullptr || ag->world <= 1)) {
-    r = make_tensormap_2d(&ta_small, dt, eb, A, M, K, lda, kASmallRows, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r) return r - 4000;
-    p.a_small_rows = kASmallRows;
-  }
   const size_t smem = smem_bytes_for(BN, p.stages, 0, smem_mode);
   int grid;
   if (cluster_split) {
@@ -1660,9 +1641,9 @@ static int gemm_impl(const void* A, const void* W, void* C, const void* bias, co
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (tiles < grid) grid = static_cast<int>(tiles);
   }
-  if (dtype_fp8 == 2) return launch<false, kKindI8>(ta, tw, ta_small, p, grid, smem, stream);
-  if (dtype_fp8) return launch<false, kKindFP8>(ta, tw, ta_small, p, grid, smem, stream);
-  return launch<false, kKindBF16>(ta, tw, ta_small, p, grid, smem, stream);
+  if (dtype_fp8 == 2) return launch<false, kKindI8>(ta, tw, p, grid, smem, stream);
+  if (dtype_fp8) return launch<false, kKindFP8>(ta, tw, p, grid, smem, stream);
+  return launch<false, kKindBF16>(ta, tw, p, grid, smem, stream);
 }
 
 // Grouped GEMM over E experts.  A [total_rows, K] holds each expert's rows
@@ -1709,14 +1690,9 @@ extern "C" int b200_grouped_gemm(const void* A, const void* W, void* C, const in
   r = make_tensormap_3d(&tw, dt, eb, W, num_experts, N, K, static_cast<uint64_t>(N) * K, K, BN,
                         box_k, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 1000;
-  // experts that received few rows (decode steps) load their A rows through a short box
-  CUtensorMap ta_small;
-  r = make_tensormap_2d(&ta_small, dt, eb, A, total_rows, K, lda, kASmallRows, box_k, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (r) return r - 4000;
-  p.a_small_rows = kASmallRows;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const size_t smem = smem_bytes_for(BN, stages, num_experts);
-  if (dtype_fp8) return launch<true, kKindFP8>(ta, tw, ta_small, p, grid, smem, stream);
-  return launch<true, kKindBF16>(ta, tw, ta_small, p, grid, smem, stream);
+  if (dtype_fp8) return launch<true, kKindFP8>(ta, tw, p, grid, smem, stream);
+  return launch<true, kKindBF16>(ta, tw, p, grid, smem, stream);
 }
