@@ -738,24 +738,26 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
 #pragma unroll
   for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
 
-  for (int it = 0; it < n_tiles; ++it) {
+  // The scores of tile it + 1 are issued before the softmax of tile it: the two chains are
+  // independent, so the ldmatrix -> mma latency of the one hides behind the arithmetic of the other
+  // (one warp per scheduler and CTA: a single dependent chain ran at a quarter of the issue rate).
+  auto wait_tile = [&](int it) -> bool {
     const int stage = it % Cfg::STAGES;
     bool ok = !*abort_flag &&
               mbar_wait(&full_bar[stage], static_cast<uint32_t>((it / Cfg::STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
-    if (!ok) {
-      if (lane == 0) {
-        if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
-        *abort_flag = 1;
-      }
-      break;
+    if (!ok && lane == 0) {
+      if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+      *abort_flag = 1;
     }
-    if (it == 0 && threadIdx.x == 0) B200_ATL(2);
-    const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
-    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
-    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
-
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    return ok;
+  };
+  auto scores = [&](int it, float (&s)[2][4]) {
+    const uint32_t kt = smem_u32(sK + (it % Cfg::STAGES) * Cfg::KV_BYTES);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t kf[4];
@@ -764,6 +766,22 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
       mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
       mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
+    }
+  };
+  float s[2][4], s_next[2][4];
+  bool have = n_tiles > 0 && wait_tile(0);
+  if (have) {
+    if (threadIdx.x == 0) B200_ATL(2);
+    scores(0, s);
+  }
+  for (int it = 0; have && it < n_tiles; ++it) {
+    const int stage = it % Cfg::STAGES;
+    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
+    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
+    bool have_next = false;
+    if (it + 1 < n_tiles) {
+      have_next = wait_tile(it + 1);
+      if (have_next) scores(it + 1, s_next);
     }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -780,11 +798,13 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       }
     }
     float corr[2];
+    bool moved = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const float tm = quad_max(tile_max[r]);
       const float new_max = fmaxf(row_max[r], tm);
       corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+      moved = moved || new_max != row_max[r];
       row_max[r] = new_max;
       row_sum[r] *= corr[r];
     }
@@ -798,12 +818,16 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         s[i][j] = e;
         row_sum[j >> 1] += e;
       }
+    // the accumulator is rescaled only when some row's running maximum moved (rare after the
+    // first tiles); the decision is taken by the whole warp
+    if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o_acc[i][0] *= corr[0];
-      o_acc[i][1] *= corr[0];
-      o_acc[i][2] *= corr[1];
-      o_acc[i][3] *= corr[1];
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= corr[0];
+        o_acc[i][1] *= corr[0];
+        o_acc[i][2] *= corr[1];
+        o_acc[i][3] *= corr[1];
+      }
     }
     uint32_t pa[4];
     pa[0] = pack_bf16x2(s[0][0], s[0][1]);
@@ -822,6 +846,13 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
     // This warp is done reading the stage.
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    if (it + 1 < n_tiles) {
+      have = have_next;
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = s_next[i][j];
+    }
   }
   __syncthreads();   // every warp (and the producer) is past the main loop
   if (threadIdx.x == 0) B200_ATL(3);

@@ -132,12 +132,16 @@ def task_pp_deepseek(rank, world, port, workdir, device_kind):
     from omni_npu_b200.config import ModelConfig
     from omni_npu_b200.engine.llm import LLM
     spec = json.load(open(os.path.join(workdir, "spec.json")))
-    cfg = ModelConfig(dtype=torch.float32, **spec["model"])
+    cfg = ModelConfig(dtype=torch.float32 if device_kind == "cpu" else torch.bfloat16, **spec["model"])
     llm = LLM(model=cfg, device=device_kind, pipeline_parallel_size=world, **spec["engine"])
     outs = llm.generate(spec["prompts"], SamplingParams(max_tokens=spec["max_tokens"], ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs],
                "kv_layers": len(llm.engine.worker.model_runner.kv_caches)},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if device_kind == "cuda":
+        from omni_npu_b200 import ops
+        ops.check_status()
+        state.finish_process(llm.engine)
     state.get_world_group().barrier()
     state.destroy_distributed()
 

@@ -172,3 +172,64 @@ def test_tensor_parallel_prefill_on_token_sharded_stream_matches_one_gpu():
         want_logits = _first_logits(one, prompts)
     assert res[0]["tokens"] == res[1]["tokens"]
     _assert_first_logits_close(res[0]["first_logits"], want_logits)
+
+
+_TINY_MLA_MOE = dict(architecture="DeepseekV3ForCausalLM", model_type="deepseek_v3", hidden_size=512, num_layers=3,
+                     num_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=1024, vocab_size=2048,
+                     rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048, rope_neox=False,
+                     num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, num_shared_experts=1,
+                     first_k_dense=1, use_mla=True, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+                     qk_rope_head_dim=64, v_head_dim=128, scoring_func="sigmoid", norm_topk_prob=True,
+                     n_group=4, topk_group=2, router_bias=True, routed_scaling_factor=2.5)
+
+
+def _nearly_same_tokens(a, b, exact_prefix=3, share=0.7):
+    """Two bf16 runs of a random-init model that differ in the order of a reduction: the first tokens
+    agree exactly; a later near-tie may send the greedy continuations apart."""
+    assert len(a) == len(b)
+    for x, y in zip(a, b):
+        assert len(x) == len(y) and x[:exact_prefix] == y[:exact_prefix], (x, y)
+        assert sum(p == q for p, q in zip(x, y)) >= share * len(x), (x, y)
+
+
+def test_decode_context_parallel_engine_two_gpus(monkeypatch):
+    """The latent cache sharded by tokens over two GPUs (token p on rank p % 2) against the same
+    tensor-parallel deployment with a replicated cache: prompts chunked at 64 tokens so that later
+    chunks read gathered context, decode merges the ranks' partial attentions by log-sum-exp."""
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(17)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (21, 70, 5)]
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")
+    res = {}
+    for dcp in (0, 1):
+        with tempfile.TemporaryDirectory() as d:
+            json.dump({"model": _TINY_MLA_MOE, "engine": engine, "prompts": prompts, "max_tokens": 8, "dcp": dcp},
+                      open(os.path.join(d, "spec.json"), "w"))
+            res[dcp] = run_ranks("dcp_engine", 2, d, device="cuda", timeout=600)
+    assert res[1][0]["tokens"] == res[1][1]["tokens"]
+    _nearly_same_tokens(res[1][0]["tokens"], res[0][0]["tokens"])
+    assert res[1][0]["max_blocks"] * 2 == res[0][0]["max_blocks"]
+    assert res[1][0]["free_blocks"] == 64 and res[1][1]["free_blocks"] == 64
+
+
+def test_pipeline_parallel_engine_two_gpus(monkeypatch):
+    """Two pipeline stages on two GPUs (activations sent stage to stage over NCCL, the last stage
+    samples and broadcasts) against the same model in one process on one GPU."""
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=128, max_model_len=256, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (21, 34, 5)]
+    monkeypatch.delenv("OMNI_B200_PP_LAYER_PARTITION", raising=False)
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")
+    with tempfile.TemporaryDirectory() as d:
+        json.dump({"model": _TINY_MLA_MOE, "engine": engine, "prompts": prompts, "max_tokens": 6},
+                  open(os.path.join(d, "spec.json"), "w"))
+        res = run_ranks("pp_deepseek", 2, d, device="cuda", timeout=600)
+    assert res[0]["tokens"] == res[1]["tokens"]
+    llm = LLM(model=ModelConfig(dtype=torch.bfloat16, **_TINY_MLA_MOE), device="cuda", enforce_eager=True, **engine)
+    want = [o.output_token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    _nearly_same_tokens(res[0]["tokens"], want)
