@@ -94,6 +94,35 @@ if compat.vllm_available():
                             (_rp + "llama3_rope", "Llama3RotaryEmbedding"),
                             (_rp + "yarn_scaling_rope", "YaRNScalingRotaryEmbedding")):
             _oot_variant(_mod, _name)
+
+        # multimodal rotary embedding: positions [3, T] (temporal, row, column), frequency bands taken
+        # from the axis that owns them (reference: MRotaryEmbedding override,
+        # omni_npu/v1/layers/rotary_embedding/mrope.py:17-206)
+        try:
+            from vllm.model_executor.layers.rotary_embedding.mrope import MRotaryEmbedding
+
+            def _mrope_forward_oot(self, positions: torch.Tensor, query: torch.Tensor,
+                                   key: Optional[torch.Tensor] = None, *args, **kw):
+                sec = getattr(self, "mrope_section", None)
+                if key is None or not _fast(query) or args or kw or (positions.dim() == 2 and (not sec or len(sec) != 3)):
+                    return self.forward_native(positions, query, key, *args, **kw)
+                cs = getattr(self, "_b200_cos_sin", None)
+                if cs is None or cs.device != query.device:
+                    cs = self.cos_sin_cache.to(device=query.device, dtype=torch.float32).contiguous()
+                    self._b200_cos_sin = cs
+                t = positions.shape[-1]
+                q2, k2 = query.reshape(t, -1), key.reshape(t, -1)
+                ops.rope_qk_(q2, k2, positions.to(torch.int32).contiguous(), cs, self.head_size, self.rotary_dim,
+                             bool(self.is_neox_style), tuple(int(x) for x in sec) if positions.dim() == 2 else None,
+                             bool(getattr(self, "mrope_interleaved", False)))
+                return q2.view(query.shape), k2.view(key.shape)
+
+            MRotaryEmbedding.register_oot(type("B200MRotaryEmbedding", (MRotaryEmbedding,),
+                                               {"forward_oot": _mrope_forward_oot,
+                                                "__doc__": "M-RoPE rotating with the fused kernel."}))
+            REGISTERED.append("MRotaryEmbedding")
+        except Exception:
+            pass
     except Exception:                                     # layout of the rotary module differs in this vLLM
         pass
 

@@ -768,3 +768,50 @@ def test_ep_dispatch_quantising_scatter_matches_quantise_after_arrival():
         assert torch.equal(torch.sort(a, dim=0).values, torch.sort(b, dim=0).values)
     plain.close(), quant.close()
     ops.check_status()
+
+
+@pytest.mark.parametrize("sink_len,window", [(4, 8), (0, 6), (3, 0)])
+def test_sink_window_latent_attention_cuda_matches_the_cpu_path(sink_len, window):
+    """Learned sink rows + sliding window on the latent cache, as composed on the GPU (sparse mode of
+    the latent-cache kernel with its log-sum-exp, the sink GEMM, the LSE merge kernel), against the
+    fp32 CPU path of the same module with the same weights."""
+    from omni_npu_b200.attention.metadata import AttentionMetadata, set_forward_context
+    from omni_npu_b200.attention.mla import MLABackend, StaticSinkMLAAttention
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.models.utils import random_init_
+    kw = dict(architecture="DeepseekV3ForCausalLM", model_type="deepseek_v3", hidden_size=512, num_layers=1,
+              num_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=1024, vocab_size=512,
+              rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+              use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64,
+              v_head_dim=128)
+    dev = torch.device("cuda", 0)
+    gpu = StaticSinkMLAAttention(ModelConfig(dtype=torch.bfloat16, **kw), 0, dev, "model.layers.0.self_attn",
+                                 sink_len=sink_len, sliding_window=window)
+    random_init_(gpu, seed=3, std=0.05)
+    if sink_len:
+        gpu.param_sink_kv.data.normal_(0, 0.5)
+    cpu = StaticSinkMLAAttention(ModelConfig(dtype=torch.float32, **kw), 0, torch.device("cpu"),
+                                 "model.layers.0.self_attn", sink_len=sink_len, sliding_window=window)
+    cpu.load_state_dict({k: v.float().cpu() for k, v in gpu.state_dict().items()})
+    gpu.process_weights_after_loading(), cpu.process_weights_after_loading()
+    bs, nblk, lens = 16, 8, [21, 13]
+    T = sum(lens)
+    torch.manual_seed(1)
+    hidden = (torch.randn(T, 512) * 0.5).to(torch.bfloat16)
+    pos = torch.cat([torch.arange(n) for n in lens]).to(torch.int32)
+    bt = torch.tensor([[1, 2, 0, 0], [3, 4, 0, 0]], dtype=torch.int32)
+    slots = torch.cat([bt[b, torch.arange(n) // bs] * bs + torch.arange(n) % bs for b, n in enumerate(lens)]).to(torch.int32)
+    cu = torch.tensor([0, lens[0], T], dtype=torch.int32)
+    outs = {}
+    for name, mod, d, dt in (("gpu", gpu, dev, torch.bfloat16), ("cpu", cpu, torch.device("cpu"), torch.float32)):
+        cache = MLABackend.allocate_kv_cache(nblk, bs, 512, 64, dt, d)
+        md = AttentionMetadata(is_prefill=True, num_seqs=2, num_tokens=T, max_q_len=max(lens), max_seq_len=max(lens),
+                               q_len=0, positions=pos.to(d), slot_mapping=slots.to(d), block_tables=bt.to(d),
+                               seq_lens=torch.tensor(lens, dtype=torch.int32, device=d), cu_q=cu.to(d),
+                               num_actual_tokens=T, num_actual_seqs=2)
+        with set_forward_context(md, [cache]):
+            outs[name] = mod(hidden.to(d, dt)).float().cpu()
+    got, want = outs["gpu"], outs["cpu"]
+    rel = (got - want).abs().max() / want.abs().max().clamp_min(1e-6)
+    assert rel <= 5e-2, float(rel)
+    ops.check_status()
