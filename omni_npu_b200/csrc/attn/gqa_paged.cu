@@ -738,26 +738,27 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
 #pragma unroll
   for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
 
-  // The scores of tile it + 1 are issued before the softmax of tile it: the two chains are
-  // independent, so the ldmatrix -> mma latency of the one hides behind the arithmetic of the other
-  // (one warp per scheduler and CTA: a single dependent chain ran at a quarter of the issue rate).
-  auto wait_tile = [&](int it) -> bool {
+  // (Issuing the scores of tile it + 1 before the softmax of tile it was tried: the warp then holds
+  // two stages of the ring at once, which leaves the producer one stage less to fill, and the kernel
+  // got slower, 161 us against 133 us on 128 sequences x 1152 keys x 8 kv heads.)
+  for (int it = 0; it < n_tiles; ++it) {
     const int stage = it % Cfg::STAGES;
     bool ok = !*abort_flag &&
               mbar_wait(&full_bar[stage], static_cast<uint32_t>((it / Cfg::STAGES) & 1));
     ok = __all_sync(0xffffffffu, ok);
-    if (!ok && lane == 0) {
-      if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
-      *abort_flag = 1;
+    if (!ok) {
+      if (lane == 0) {
+        if (!*abort_flag && p.status) atomicCAS(p.status, 0, kStatusTimeoutFullBarrier);
+        *abort_flag = 1;
+      }
+      break;
     }
-    return ok;
-  };
-  auto scores = [&](int it, float (&s)[2][4]) {
-    const uint32_t kt = smem_u32(sK + (it % Cfg::STAGES) * Cfg::KV_BYTES);
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    if (it == 0 && threadIdx.x == 0) B200_ATL(2);
+    const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
+    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
+    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t kf[4];
@@ -766,22 +767,6 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
       mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
       mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
-    }
-  };
-  float s[2][4], s_next[2][4];
-  bool have = n_tiles > 0 && wait_tile(0);
-  if (have) {
-    if (threadIdx.x == 0) B200_ATL(2);
-    scores(0, s);
-  }
-  for (int it = 0; have && it < n_tiles; ++it) {
-    const int stage = it % Cfg::STAGES;
-    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
-    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
-    bool have_next = false;
-    if (it + 1 < n_tiles) {
-      have_next = wait_tile(it + 1);
-      if (have_next) scores(it + 1, s_next);
     }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -846,13 +831,6 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
     // This warp is done reading the stage.
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[stage]);
-    if (it + 1 < n_tiles) {
-      have = have_next;
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) s[i][j] = s_next[i][j];
-    }
   }
   __syncthreads();   // every warp (and the producer) is past the main loop
   if (threadIdx.x == 0) B200_ATL(3);
@@ -937,6 +915,16 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
 // (p.work_counter: ticket word + finished-CTA word, both zero at rest; the last CTA to finish
 // puts them back to zero, so graph replays need no host reset) or, without a counter, by
 // striding.  q_len rows x group heads <= 16 as in the other decode kernels.
+//
+// Balanced mode (p.persistent == 2).  Whole items leave the last round of a grid part empty: 1024
+// items of 18 tiles on 444 resident CTAs take three rounds for 2.3 rounds of work.  Here the tiles
+// of all items, laid end to end (sequence, then kv head, then tile), are cut into gridDim.x equal
+// ranges, one per CTA.  A range covers whole items, which the CTA finishes and stores itself, and at
+// most two pieces of items that continue in a neighbour: the piece its range starts in and the piece
+// it ends in.  Pieces go to the fp32 scratch (slot 2 x CTA for the first segment of a CTA, 2 x CTA + 1
+// for a later one) and gqa_decode_merge_balanced_kernel, which derives the same cut from the
+// sequence lengths, joins them.  A sequence of length zero counts as one (fully masked) tile, so
+// that its output rows are written.
 template <int D, int NSTAGES>
 struct DecodePersistCfg {
   static constexpr int BN = 64;
@@ -948,13 +936,26 @@ struct DecodePersistCfg {
   static constexpr int KV_BYTES = HALVES * HALF_BYTES;
   static constexpr int BT_ENTRIES = 256;       // block-table slice of one item (per buffer)
   static constexpr int META_INTS = 8;
-  // dynamic: 2 query buffers of rows x D bf16 and the merge buffer 4 x rows x (D + 4) fp32
+  // dynamic: 2 query buffers of rows x D bf16 and two fold slots of rows x D fp32 (the four warps'
+  // results are joined 2, 3 -> 0, 1 and then 1 -> 0), their maxima and sums
   static constexpr size_t smem(int rows) {
     return 1024 + 2 * static_cast<size_t>(STAGES) * KV_BYTES + 2 * static_cast<size_t>(rows) * D * 2 +
-           4 * static_cast<size_t>(rows) * (D + 4) * 4 + 8 * static_cast<size_t>(rows) * 4 +
+           2 * static_cast<size_t>(rows) * D * 4 + 4 * static_cast<size_t>(rows) * 4 +
            2 * BT_ENTRIES * 4 + 2 * META_INTS * 4 + (2 * STAGES + 4) * 8 + 64;
   }
 };
+
+// Tiles that a sequence of kv_len keys counts for in the balanced cut (never zero).
+__device__ __forceinline__ int balanced_tiles(int kv_len) {
+  const int n = (kv_len + 63) >> 6;
+  return n > 0 ? n : 1;
+}
+// Tiles per CTA range: equal parts, at least two tiles (a piece of one tile costs more in set-up and
+// merge than it streams).
+__device__ __forceinline__ long long balanced_per(long long total_tiles, int ctas) {
+  const long long per = (total_tiles + ctas - 1) / ctas;
+  return per < 2 ? 2 : per;
+}
 
 template <int D, int NSTAGES, int MINB>
 __global__ void __launch_bounds__(160, MINB)
@@ -970,8 +971,8 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
   uint8_t* sQ = sV + Cfg::STAGES * Cfg::KV_BYTES;                       // [2][rows][D] bf16, linear
-  float* s_merge = reinterpret_cast<float*>(sQ + 2 * rows * D * 2);     // [4][rows][D + 4], then maxima and sums [2][4][rows]
-  int* s_bt = reinterpret_cast<int*>(s_merge + 4 * rows * (D + 4) + 8 * rows);   // [2][BT_ENTRIES]
+  float* s_fold = reinterpret_cast<float*>(sQ + 2 * rows * D * 2);      // [2][D / 8][rows][4] float2, then maxima [2][rows], sums [2][rows]
+  int* s_bt = reinterpret_cast<int*>(s_fold + 2 * rows * D + 4 * rows);  // [2][BT_ENTRIES]
   int* s_meta = s_bt + 2 * Cfg::BT_ENTRIES;                             // [2][META_INTS]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_meta + 2 * Cfg::META_INTS);
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
@@ -1014,6 +1015,47 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
     // ------------------------------------------------------------ producer
     int item = blockIdx.x;
     uint32_t g = 0;            // tiles issued so far (ring position), identical in all lanes
+    // balanced mode: position in the end-to-end tile sequence (all lanes hold the same values)
+    const bool balanced = p.persistent == 2;
+    const int n_seqs = total_items / p.Hk;
+    long long bx = 0, bx_end = 0;
+    int bal_b = 0, bal_kvh = 0, bal_t = 0, bal_nb = 1;
+    if (balanced) {
+      int total = 0;
+      for (int i = lane; i < n_seqs; i += 32) total += balanced_tiles(p.seq_lens[i]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+      const long long all_tiles = static_cast<long long>(total) * p.Hk;
+      const long long per = balanced_per(all_tiles, static_cast<int>(gridDim.x));
+      bx = static_cast<long long>(blockIdx.x) * per;
+      bx_end = bx + per < all_tiles ? bx + per : all_tiles;
+      if (bx < bx_end) {
+        // the sequence that tile bx belongs to: 32 sequences per pass, inclusive scan of their tiles
+        long long before = 0;      // tiles of the sequences ahead of the pass, times kv heads
+        for (int c0 = 0; c0 < n_seqs; c0 += 32) {
+          const int n = c0 + lane < n_seqs ? balanced_tiles(p.seq_lens[c0 + lane]) : 0;
+          int incl = n;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+          }
+          const unsigned past = __ballot_sync(0xffffffffu, before + static_cast<long long>(incl) * p.Hk > bx);
+          if (past != 0u) {
+            const int l = __ffs(static_cast<int>(past)) - 1;
+            const int incl_l = __shfl_sync(0xffffffffu, incl, l);
+            bal_nb = __shfl_sync(0xffffffffu, n, l);
+            bal_b = c0 + l;
+            before += static_cast<long long>(incl_l - bal_nb) * p.Hk;
+            break;
+          }
+          before += static_cast<long long>(__shfl_sync(0xffffffffu, incl, 31)) * p.Hk;
+        }
+        const int off = static_cast<int>(bx - before);      // < bal_nb * Hk
+        bal_kvh = off / bal_nb;
+        bal_t = off % bal_nb;
+      }
+    }
     for (int k = 0;; ++k) {
       const int par = k & 1;
       int next_item = item + static_cast<int>(gridDim.x);
@@ -1029,10 +1071,35 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
         break;
       }
-      const bool valid = item < total_items;
+      const bool valid = balanced ? bx < bx_end : item < total_items;
       int b = 0, kvh = 0, split = 0, kv_len = 0, t_begin = 0, n_tiles = 0, bt_first = 0, bt_last = 0;
+      int slot = -1;             // scratch slot of a partial result; -1: the output is final
       const int* bt = p.block_tables;
-      if (valid) {
+      if (valid && balanced) {
+        b = bal_b;
+        kvh = bal_kvh;
+        kv_len = p.seq_lens[b];
+        bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+        t_begin = bal_t;
+        const long long left = bx_end - bx;
+        n_tiles = bal_nb - bal_t < left ? bal_nb - bal_t : static_cast<int>(left);
+        const int t_end = t_begin + n_tiles;
+        if (t_begin != 0 || n_tiles != bal_nb) slot = 2 * static_cast<int>(blockIdx.x) + (k == 0 ? 0 : 1);
+        item = b * p.Hk + kvh;
+        bt_first = (t_begin * Cfg::BN) / p.block_size;
+        bt_last = min(p.max_blocks, (min(kv_len, t_end * Cfg::BN) + p.block_size - 1) / p.block_size);
+        // next segment
+        bx += n_tiles;
+        bal_t += n_tiles;
+        if (bal_t == bal_nb) {
+          bal_t = 0;
+          if (++bal_kvh == p.Hk) {
+            bal_kvh = 0;
+            ++bal_b;
+            bal_nb = bal_b < n_seqs ? balanced_tiles(p.seq_lens[bal_b]) : 1;
+          }
+        }
+      } else if (valid) {
         split = item % p.splits;
         kvh = (item / p.splits) % p.Hk;
         b = item / (p.splits * p.Hk);
@@ -1045,6 +1112,7 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
         n_tiles = max(0, t_end - t_begin);
         bt_first = (t_begin * Cfg::BN) / p.block_size;
         bt_last = min(p.max_blocks, (min(kv_len, t_end * Cfg::BN) + p.block_size - 1) / p.block_size);
+        if (p.splits > 1) slot = (b * p.Hk + kvh) * p.splits + split;
       }
       const bool bt_cached = (bt_last - bt_first) <= Cfg::BT_ENTRIES;
       int* my_bt = s_bt + par * Cfg::BT_ENTRIES;
@@ -1057,6 +1125,7 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
         meta[1] = kv_len;
         meta[2] = t_begin;
         meta[3] = n_tiles;
+        meta[4] = slot;
         if (!valid) {
           mbar_arrive(&q_full[par]);
         } else {
@@ -1123,8 +1192,8 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int r_a = lane >> 2;
   uint32_t g = 0;
   volatile int* s_dec = s_abort + 1;
-  float* m_buf = s_merge + 4 * rows * (D + 4);      // [4][rows] maxima, then [4][rows] sums
-  float* l_buf = m_buf + 4 * rows;
+  float* m_buf = s_fold + 2 * rows * D;             // [2][rows] maxima, then [2][rows] sums
+  float* l_buf = m_buf + 2 * rows;
   for (int k = 0;; ++k) {
     const int par = k & 1;
     bool ok = !*abort_flag && mbar_wait(&q_full[par], static_cast<uint32_t>((k >> 1) & 1));
@@ -1145,8 +1214,7 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int* meta = s_meta + par * Cfg::META_INTS;
     const int item = meta[0];
     if (item < 0) break;
-    const int kv_len = meta[1], t_begin = meta[2], n_tiles = meta[3];
-    const int split = item % p.splits;
+    const int kv_len = meta[1], t_begin = meta[2], n_tiles = meta[3], slot = meta[4];
     const int kvh = (item / p.splits) % p.Hk;
     const int b = item / (p.splits * p.Hk);
 
@@ -1262,67 +1330,86 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
 
-    // ---- merge the four warps' partial results (rows < `rows` only) and store
+    // ---- join the four warps' results (rows < `rows` only): warps 2 and 3 hand theirs to warps 0
+    // and 1, then warp 1 hands the sum to warp 0, which stores.  The same lane of every warp holds
+    // the same (row, column) positions, so a slot is indexed [column group][row][lane in quad].
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      row_sum[r] = quad_sum(row_sum[r]);
-      const int row = r_a + 8 * r;
-      if ((lane & 3) == 0 && row < rows) {
-        m_buf[warp * rows + row] = row_max[r];
-        l_buf[warp * rows + row] = row_sum[r];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      const int col = i * 8 + (lane & 3) * 2;
+    for (int r = 0; r < 2; ++r) row_sum[r] = quad_sum(row_sum[r]);
+    auto put = [&](int fs) {
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int row = r_a + 8 * r;
-        if (row < rows)
-          *reinterpret_cast<float2*>(s_merge + (static_cast<size_t>(warp) * rows + row) * (D + 4) + col) =
-              make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+        if (row < rows) {
+          if ((lane & 3) == 0) {
+            m_buf[fs * rows + row] = row_max[r];
+            l_buf[fs * rows + row] = row_sum[r];
+          }
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<float2*>(s_fold + (((fs * (D / 8) + i) * rows + row) * 4 + (lane & 3)) * 2) =
+                make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+        }
       }
-    }
+    };
+    auto take = [&](int fs) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = r_a + 8 * r;
+        if (row < rows) {
+          const float mo = m_buf[fs * rows + row];
+          const float m = fmaxf(row_max[r], mo);
+          const float fa = row_max[r] == -INFINITY ? 0.f : exp2f(row_max[r] - m);
+          const float fb = mo == -INFINITY ? 0.f : exp2f(mo - m);
+          row_sum[r] = row_sum[r] * fa + l_buf[fs * rows + row] * fb;
+          row_max[r] = m;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) {
+            const float2 x = *reinterpret_cast<const float2*>(
+                s_fold + (((fs * (D / 8) + i) * rows + row) * 4 + (lane & 3)) * 2);
+            o_acc[i][2 * r] = o_acc[i][2 * r] * fa + x.x * fb;
+            o_acc[i][2 * r + 1] = o_acc[i][2 * r + 1] * fa + x.y * fb;
+          }
+        }
+      }
+    };
+    if (warp >= 2) put(warp - 2);
     if (tid == 0) s_dec[1] = *abort_flag;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (s_dec[1]) break;
-    for (int idx = tid; idx < rows * (D / 4); idx += Cfg::COMPUTE_THREADS) {
-      const int row = idx / (D / 4);
-      const int c4 = (idx % (D / 4)) * 4;
-      float m = -INFINITY;
+    if (warp < 2) take(warp);
+    if (warp == 1) put(1);     // slot 1 was read by this warp alone
+    if (tid == 0) s_dec[2] = *abort_flag;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (s_dec[2]) break;
+    if (warp == 0) {
+      take(1);
 #pragma unroll
-      for (int w = 0; w < 4; ++w) m = fmaxf(m, m_buf[w * rows + row]);
-      float l = 0.f;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < 2; ++r) {
+        const int row = r_a + 8 * r;
+        if (row >= rows) continue;
+        const float m = row_max[r], l = row_sum[r];
+        const int qi = row / G, hh = kvh * G + row % G;
+        if (slot < 0) {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          __nv_bfloat16* dst = p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                               static_cast<long long>(hh) * D + (lane & 3) * 2;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = m_buf[w * rows + row];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-        l += l_buf[w * rows + row] * f;
-        const float4 x =
-            *reinterpret_cast<const float4*>(s_merge + (static_cast<size_t>(w) * rows + row) * (D + 4) + c4);
-        acc.x += x.x * f;
-        acc.y += x.y * f;
-        acc.z += x.z * f;
-        acc.w += x.w * f;
-      }
-      const int qi = row / G, hh = kvh * G + row % G;
-      if (p.splits == 1) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        uint2 pk;
-        pk.x = pack_bf16x2(acc.x * inv, acc.y * inv);
-        pk.y = pack_bf16x2(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
-                                  static_cast<long long>(hh) * D + c4) = pk;
-        if (p.lse && c4 == 0)
-          p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
-              l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
-      } else {
-        const size_t pr = ((static_cast<size_t>(b) * p.Hk + kvh) * p.splits + split) * 16 + row;
-        *reinterpret_cast<float4*>(p.o_part + pr * D + c4) = acc;
-        if (c4 == 0) {
-          p.lse_part[pr * 2] = m;
-          p.lse_part[pr * 2 + 1] = l;
+          for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<uint32_t*>(dst + i * 8) =
+                pack_bf16x2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv);
+          if (p.lse && (lane & 3) == 0)
+            p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+                l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+        } else {
+          const size_t pr = static_cast<size_t>(slot) * 16 + row;
+          float* dst = p.o_part + pr * D + (lane & 3) * 2;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+          if ((lane & 3) == 0) {
+            p.lse_part[pr * 2] = m;
+            p.lse_part[pr * 2 + 1] = l;
+          }
         }
       }
     }
@@ -1350,6 +1437,67 @@ __global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnParams 
   for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
   for (int s = 0; s < p.splits; ++s) {
     const size_t pr = (base + s) * 16 + row;
+    const float ms = p.lse_part[pr * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    l += p.lse_part[pr * 2 + 1] * f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] += p.o_part[pr * D + i * 32 + lane] * f;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const int qi = row / G, hh = kvh * G + row % G;
+  __nv_bfloat16* dst = p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                       static_cast<long long>(hh) * D;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) dst[i * 32 + lane] = __float2bfloat16(acc[i] * inv);
+  if (p.lse && lane == 0)
+    p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+        l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+}
+
+// Joins the pieces that the balanced persistent kernel left in the scratch: one warp per
+// (sequence, kv head, row).  The warp recomputes the cut (tiles ahead of its item, tiles per CTA
+// range), finds the CTAs that its item's tiles fell to, and returns at once when that is a single
+// CTA (which then stored the final output itself).
+template <int D>
+__global__ void __launch_bounds__(128) gqa_decode_merge_balanced_kernel(const AttnParams p, int B, int ctas) {
+  const int G = p.Hq / p.Hk;
+  const int rows = G * p.q_len;
+  const long long gw = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const long long total = static_cast<long long>(B) * p.Hk * rows;
+  if (gw >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int row = static_cast<int>(gw % rows);
+  const int kvh = static_cast<int>((gw / rows) % p.Hk);
+  const int b = static_cast<int>(gw / (static_cast<long long>(rows) * p.Hk));
+  int ahead = 0, all = 0;
+  for (int i = lane; i < B; i += 32) {
+    const int n = balanced_tiles(p.seq_lens[i]);
+    all += n;
+    if (i < b) ahead += n;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    all += __shfl_xor_sync(0xffffffffu, all, o);
+    ahead += __shfl_xor_sync(0xffffffffu, ahead, o);
+  }
+  const int nb = balanced_tiles(p.seq_lens[b]);
+  const long long per = balanced_per(static_cast<long long>(all) * p.Hk, ctas);
+  const long long x0 = static_cast<long long>(ahead) * p.Hk + static_cast<long long>(kvh) * nb;
+  const int c0 = static_cast<int>(x0 / per), c1 = static_cast<int>((x0 + nb - 1) / per);
+  if (c0 == c1) return;
+  // the piece in CTA c0 is that CTA's first segment only when the item starts its range
+  const int first_slot = 2 * c0 + (x0 == static_cast<long long>(c0) * per ? 0 : 1);
+  float m = -INFINITY;
+  for (int c = c0; c <= c1; ++c) {
+    const size_t pr = static_cast<size_t>(c == c0 ? first_slot : 2 * c) * 16 + row;
+    m = fmaxf(m, p.lse_part[pr * 2]);
+  }
+  float l = 0.f;
+  float acc[D / 32];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
+  for (int c = c0; c <= c1; ++c) {
+    const size_t pr = static_cast<size_t>(c == c0 ? first_slot : 2 * c) * 16 + row;
     const float ms = p.lse_part[pr * 2];
     const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
     l += p.lse_part[pr * 2 + 1] * f;
@@ -1419,10 +1567,25 @@ static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream
   return 0;
 }
 
-template <int D, int NSTAGES>
+// CTAs of the balanced persistent kernel: what is resident at once (three per SM when the shared
+// memory of a CTA allows it, else two).  The scratch holds two slots per CTA.
+static int balanced_ctas_per_sm(int D, int rows) {
+  return DecodePersistCfg<128, 2>::smem(rows) <= 75 * 1024 && D <= 128 ? 3 : 2;
+}
+static int device_sms() {
+  static const int sms = [] {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  return sms;
+}
+
+template <int D, int NSTAGES, int MINB>
 static int launch_decode_persist(const AttnParams& p, int B, cudaStream_t stream) {
   using Cfg = DecodePersistCfg<D, NSTAGES>;
-  auto kern = gqa_decode_persist_kernel<D, NSTAGES, 2>;
+  auto kern = gqa_decode_persist_kernel<D, NSTAGES, MINB>;
   const int rows = (p.Hq / p.Hk) * p.q_len;
   const size_t smem = Cfg::smem(rows);
   static DeviceOnce once;
@@ -1448,6 +1611,15 @@ static int launch_decode_persist(const AttnParams& p, int B, cudaStream_t stream
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r - 3000;
   const long long items = static_cast<long long>(B) * p.Hk * p.splits;
+  if (p.persistent == 2) {
+    const int grid = MINB * sms;
+    if (launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), smem, stream, 1, tk, tv, p, box_rows,
+                   static_cast<int>(items)) != cudaSuccess)
+      return -21;
+    const long long warps = static_cast<long long>(B) * p.Hk * rows;
+    gqa_decode_merge_balanced_kernel<D><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(p, B, grid);
+    return cudaGetLastError() != cudaSuccess ? -22 : 0;
+  }
   const int grid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);
   if (launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), smem, stream, 1, tk, tv, p, box_rows,
                  static_cast<int>(items)) != cudaSuccess)
@@ -1475,7 +1647,11 @@ template <int D>
 static int launch_decode(const AttnParams& p, int B, cudaStream_t stream) {
   if (p.persistent && persist_ok(p)) {
     const int rows = (p.Hq / p.Hk) * p.q_len;
-    return rows <= 4 ? launch_decode_persist<D, 3>(p, B, stream) : launch_decode_persist<D, 2>(p, B, stream);
+    if (p.persistent == 2) {
+      if (balanced_ctas_per_sm(D, rows) == 3) return launch_decode_persist<D, 2, 3>(p, B, stream);
+      return rows <= 8 ? launch_decode_persist<D, 3, 2>(p, B, stream) : launch_decode_persist<D, 2, 2>(p, B, stream);
+    }
+    return rows <= 4 ? launch_decode_persist<D, 3, 2>(p, B, stream) : launch_decode_persist<D, 2, 2>(p, B, stream);
   }
   const bool use_tma = (p.block_size % 8) == 0 && (p.block_size <= 64 ? (64 % p.block_size) == 0
                                                                        : (p.block_size % 64) == 0) &&
@@ -1569,8 +1745,17 @@ extern "C" size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits
   return static_cast<size_t>(B) * Hk * splits * 16 * (static_cast<size_t>(D) + 2) * sizeof(float);
 }
 
-// persistent != 0 selects the persistent-CTA kernel when the problem allows it (else the
-// one-CTA-per-item kernels run); work_counter: two ints, zero at rest, or null.
+// Scratch of the balanced persistent decode kernel: two slots of 16 rows per CTA.
+extern "C" size_t b200_gqa_decode_balanced_scratch_bytes(int D, int rows) {
+  const size_t slots = 2 * static_cast<size_t>(balanced_ctas_per_sm(D, rows)) * device_sms();
+  return slots * 16 * (static_cast<size_t>(D) + 2) * sizeof(float);
+}
+
+// persistent: 0 = one CTA per (sequence, kv head, split) item; 1 = persistent CTAs that take items
+// from a counter (work_counter: two ints, zero at rest, or null for striding); 2 = persistent CTAs
+// over a balanced cut of the tiles (splits is ignored, scratch of
+// b200_gqa_decode_balanced_scratch_bytes required).  1 and 2 fall back to 0 when the problem does
+// not fit the persistent kernel.
 extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
                                   float* lse, const int* block_tables, const int* seq_lens, int B,
                                   int q_len, int max_blocks, int block_size, int Hq, int Hk, int D,
@@ -1598,7 +1783,8 @@ extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void
   if (B <= 0) return 0;
   if (Hq % Hk != 0 || (Hq / Hk) * q_len > 16 || q_len < 1) return -1;
   if (splits < 1) splits = 1;
-  if (splits > 1 && scratch == nullptr) return -3;
+  if (persistent == 2) splits = 1;
+  if ((splits > 1 || persistent == 2) && scratch == nullptr) return -3;
   AttnParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
@@ -1627,6 +1813,15 @@ extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void
   if (splits > 1) {
     p.o_part = static_cast<float*>(scratch);
     p.lse_part = p.o_part + static_cast<size_t>(B) * Hk * splits * 16 * D;
+  }
+  if (persistent == 2) {
+    if (!persist_ok(p)) {
+      p.persistent = 0;       // one CTA per item, keys not split
+    } else {
+      const size_t slots = 2 * static_cast<size_t>(balanced_ctas_per_sm(D, (Hq / Hk) * q_len)) * device_sms();
+      p.o_part = static_cast<float*>(scratch);
+      p.lse_part = p.o_part + slots * 16 * D;
+    }
   }
   if (D == 128) return launch_decode<128>(p, B, stream);
   if (D == 64) return launch_decode<64>(p, B, stream);

@@ -84,6 +84,7 @@ int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, vo
                      long long q_stride, long long out_stride, float scale, int causal, int window,
                      cudaStream_t stream);
 size_t b200_gqa_decode_scratch_bytes(int B, int Hk, int D, int splits);
+size_t b200_gqa_decode_balanced_scratch_bytes(int D, int rows);
 int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                     const int* block_tables, const int* seq_lens, int B, int q_len, int max_blocks,
                     int block_size, int Hq, int Hk, int D, long long q_stride, long long out_stride,
@@ -693,7 +694,7 @@ int64_t gqa_decode_scratch_bytes(int64_t B, int64_t Hk, int64_t D, int64_t split
 Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                   const Tensor& block_tables, const Tensor& seq_lens, int64_t num_seqs,
                   int64_t q_len, int64_t num_q_heads, double scale, int64_t window, int64_t splits,
-                  const c10::optional<Tensor>& scratch, const Tensor& status, bool persistent,
+                  const c10::optional<Tensor>& scratch, const Tensor& status, int64_t persistent,
                   const c10::optional<Tensor>& work_counter) {
   CHECK_CUDA_BF16(q);
   CHECK_CUDA_BF16(k_cache);
@@ -707,7 +708,13 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({q.size(0), (int64_t)Hq * D}, q.options());
   void* sp = nullptr;
-  if (splits > 1) {
+  if (persistent == 2) {
+    TORCH_CHECK(scratch.has_value(), "gqa_decode: scratch required for the balanced kernel");
+    TORCH_CHECK((int64_t)scratch->nbytes() >=
+                    (int64_t)b200_gqa_decode_balanced_scratch_bytes(D, (int)((Hq / Hk) * q_len)),
+                "gqa_decode: scratch too small");
+    sp = scratch->data_ptr();
+  } else if (splits > 1) {
     TORCH_CHECK(scratch.has_value(), "gqa_decode: scratch required for splits > 1");
     TORCH_CHECK((int64_t)scratch->nbytes() >=
                     (int64_t)b200_gqa_decode_scratch_bytes((int)num_seqs, Hk, D, (int)splits),
@@ -724,7 +731,7 @@ Tensor gqa_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
                            nullptr, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
                            (int)num_seqs, (int)q_len, (int)block_tables.size(1), bs, Hq, Hk, D,
                            q.stride(0), out.stride(0), (float)scale, (int)window, (int)splits, sp,
-                           (int)k_cache.size(0), status.data_ptr<int>(), persistent ? 1 : 0, wc, cur_stream()),
+                           (int)k_cache.size(0), status.data_ptr<int>(), (int)persistent, wc, cur_stream()),
         "gqa_decode");
   return out;
 }
@@ -874,6 +881,9 @@ TORCH_LIBRARY(omni_b200, m) {
   m.def("gqa_cache_write", &gqa_cache_write);
   m.def("gqa_prefill", &gqa_prefill);
   m.def("gqa_decode_scratch_bytes", &gqa_decode_scratch_bytes);
+  m.def("gqa_decode_balanced_scratch_bytes", [](int64_t D, int64_t rows) {
+    return (int64_t)b200_gqa_decode_balanced_scratch_bytes((int)D, (int)rows);
+  });
   m.def("gqa_decode", &gqa_decode);
   m.def("kv_p2p_copy", &kv_p2p_copy);
   m.def("mla_decode_scratch_bytes", &mla_decode_scratch_bytes);
