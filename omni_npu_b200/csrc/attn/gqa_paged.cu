@@ -585,7 +585,160 @@ __device__ __forceinline__ void attn_mark(int i) {
 
 // NSTAGES / MINB: three stages and two CTAs per SM, or two stages and three CTAs per SM (more
 // warps to hide the latency of the dependent ldmatrix -> mma -> softmax chains).
-template <int D, int NSTAGES, int MINB>
+// One compute warp's share of a 64-key tile in the TMA-fed decode kernels: its 16 keys against the
+// query rows, online softmax, and the product with its 16 value rows.  kt / vt: shared-memory
+// addresses of the stage; n0: the warp's first key.  The accumulator is rescaled only when some
+// row's running maximum moved (rare after the first tiles); the decision is taken by the whole warp.
+//
+// NR = 2: up to sixteen query rows per kv head.  S = Q K^T with the queries as the 16 MMA rows;
+// lane 4 g + t holds rows g and g + 8.  o_acc[i][2 r + c]: row g + 8 r, column 8 i + 2 t + c.
+//
+// NR = 1: at most eight query rows per kv head (the single-token decode step of a model with a
+// group of 4 or 8, or two tokens of a group of 4).  Sixteen MMA rows would be half padding, so the
+// products are transposed: S^T = K Q^T (16 keys x 8 queries) and O^T = V^T P^T (head dims x 8
+// queries): half the MMAs, half the exponentials, half the accumulator and query registers.  Lane
+// 4 g + t holds queries 2 t and 2 t + 1.  o_acc[2 d + h][c]: head dim 16 d + g + 8 h, query 2 t + c.
+// P^T reaches the operand layout of the second product through two 8 x 8 transposes (movmatrix).
+// row_max / row_sum / pos_r are per row g + 8 r (NR = 2) or per query 2 t + c (NR = 1).
+template <int D, int NR>
+__device__ __forceinline__ void decode_warp_tile(uint32_t kt, uint32_t vt, int n0, int warp, int lane,
+                                                 const uint32_t (&q_frag)[D / 16][2 * NR],
+                                                 float (&o_acc)[D / 8][2 * NR], float (&row_max)[2],
+                                                 float (&row_sum)[2], const int (&pos_r)[2], int kv_len,
+                                                 float scale_log2, int window, int sink) {
+  if constexpr (NR == 2) {
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kf[4];
+      const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int kchunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
+      mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
+      mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
+        const int pos = pos_r[j >> 1];
+        bool keep = key <= pos && key < kv_len;
+        if (window > 0) keep = keep && (key > pos - window || key < sink);
+        const float v = keep ? s[i][j] * scale_log2 : -INFINITY;
+        s[i][j] = v;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+      }
+    }
+    float corr[2], m_use[2];
+    bool moved = false;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float tm = quad_max(tile_max[r]);
+      const float new_max = fmaxf(row_max[r], tm);
+      corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
+      moved = moved || new_max != row_max[r];
+      row_max[r] = new_max;
+      row_sum[r] *= corr[r];
+      m_use[r] = new_max == -INFINITY ? 0.f : new_max;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2f(s[i][j] - m_use[j >> 1]);
+        s[i][j] = e;
+        row_sum[j >> 1] += e;
+      }
+    if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o_acc[i][j] *= corr[j >> 1];
+    }
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(s[0][0], s[0][1]);
+    pa[1] = pack_bf16x2(s[0][2], s[0][3]);
+    pa[2] = pack_bf16x2(s[1][0], s[1][1]);
+    pa[3] = pack_bf16x2(s[1][2], s[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+      uint32_t vf[4];
+      const int vrow = warp * 16 + (lane & 15);
+      const int vchunk = dt * 2 + (lane >> 4);
+      ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
+      mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
+      mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
+    }
+  } else {
+    // S^T in two accumulators (even and odd 16-dim slices), so that the dependent chain is half as long
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kf[4];   // (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+      const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int kchunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
+      if (ks & 1)
+        mma_bf16_16816_regs(sb[0], sb[1], sb[2], sb[3], kf[0], kf[2], kf[1], kf[3], q_frag[ks][0], q_frag[ks][1]);
+      else
+        mma_bf16_16816_regs(sa[0], sa[1], sa[2], sa[3], kf[0], kf[2], kf[1], kf[3], q_frag[ks][0], q_frag[ks][1]);
+    }
+    // s[2 h + c]: key n0 + g + 8 h, query 2 t + c
+    float s[4];
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int key = n0 + (lane >> 2) + 8 * (j >> 1);
+      const int pos = pos_r[j & 1];
+      bool keep = key <= pos && key < kv_len;
+      if (window > 0) keep = keep && (key > pos - window || key < sink);
+      const float v = keep ? (sa[j] + sb[j]) * scale_log2 : -INFINITY;
+      s[j] = v;
+      tile_max[j & 1] = fmaxf(tile_max[j & 1], v);
+    }
+    float corr[2], m_use[2];
+    bool moved = false;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const float tm = col_max(tile_max[c]);
+      const float new_max = fmaxf(row_max[c], tm);
+      corr[c] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[c] - new_max);
+      moved = moved || new_max != row_max[c];
+      row_max[c] = new_max;
+      row_sum[c] *= corr[c];
+      m_use[c] = new_max == -INFINITY ? 0.f : new_max;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float e = exp2f(s[j] - m_use[j & 1]);
+      s[j] = e;
+      row_sum[j & 1] += e;
+    }
+    if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= corr[0];
+        o_acc[i][1] *= corr[1];
+      }
+    }
+    // P^T (16 keys x 8 queries) as the k16 x n8 operand: lane wants keys 2 t, 2 t + 1 (+ 8) of query g
+    const uint32_t pb0 = movmatrix_trans(pack_bf16x2(s[0], s[1]));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16x2(s[2], s[3]));
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+      uint32_t vf[4];   // transposed: (dims 0-7, keys 0-7), (dims 0-7, keys 8-15), (dims 8-15, keys 0-7), (dims 8-15, keys 8-15)
+      const int vrow = warp * 16 + (lane & 15);
+      const int vchunk = dt * 2 + (lane >> 4);
+      ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
+      mma_bf16_16816_regs(o_acc[2 * dt][0], o_acc[2 * dt][1], o_acc[2 * dt + 1][0], o_acc[2 * dt + 1][1], vf[0],
+                          vf[2], vf[1], vf[3], pb0, pb1);
+    }
+  }
+}
+
+template <int D, int NSTAGES, int MINB, int NR>
 __global__ void __launch_bounds__(160, MINB)
 gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p,
@@ -721,22 +874,34 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");
 
-  float o_acc[D / 8][4];
+  float o_acc[D / 8][2 * NR];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+    for (int j = 0; j < 2 * NR; ++j) o_acc[i][j] = 0.f;
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.f, 0.f};
-  uint32_t q_frag[D / 16][4];
+  uint32_t q_frag[D / 16][2 * NR];
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks)
-    ldmatrix_x4(q_frag[ks], smem_u32(sQ) + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t f[4];
+    ldmatrix_x4(f, smem_u32(sQ) + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+    if constexpr (NR == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q_frag[ks][j] = f[j];
+    } else {
+      q_frag[ks][0] = f[0];   // query lane / 4, dims 16 ks + 2 (lane % 4), + 1
+      q_frag[ks][1] = f[2];   // the same query, dims + 8
+    }
+  }
 
+  // the two rows this lane keeps statistics for: fragment rows g and g + 8 (NR = 2), queries
+  // 2 t and 2 t + 1 (NR = 1)
   const int r_a = lane >> 2;
+  const int row_of[2] = {NR == 2 ? r_a : (lane & 3) * 2, NR == 2 ? r_a + 8 : (lane & 3) * 2 + 1};
   int pos_r[2];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
+  for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + row_of[r] / G;
 
   // (Issuing the scores of tile it + 1 before the softmax of tile it was tried: the warp then holds
   // two stages of the ring at once, which leaves the producer one stage less to fill, and the kernel
@@ -754,80 +919,9 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
       break;
     }
     if (it == 0 && threadIdx.x == 0) B200_ATL(2);
-    const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
-    const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
-    const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
-
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      uint32_t kf[4];
-      const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-      const int kchunk = ks * 2 + ((lane >> 3) & 1);
-      ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
-      mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
-      mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
-    }
-    float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
-        const int pos = pos_r[j >> 1];
-        bool keep = key <= pos && key < kv_len;
-        if (p.window > 0) keep = keep && (key > pos - p.window || key < p.sink);
-        const float v = keep ? s[i][j] * p.scale_log2 : -INFINITY;
-        s[i][j] = v;
-        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
-      }
-    }
-    float corr[2];
-    bool moved = false;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const float tm = quad_max(tile_max[r]);
-      const float new_max = fmaxf(row_max[r], tm);
-      corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
-      moved = moved || new_max != row_max[r];
-      row_max[r] = new_max;
-      row_sum[r] *= corr[r];
-    }
-    const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
-                            row_max[1] == -INFINITY ? 0.f : row_max[1]};
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float e = exp2f(s[i][j] - m_use[j >> 1]);
-        s[i][j] = e;
-        row_sum[j >> 1] += e;
-      }
-    // the accumulator is rescaled only when some row's running maximum moved (rare after the
-    // first tiles); the decision is taken by the whole warp
-    if (__any_sync(0xffffffffu, moved)) {
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        o_acc[i][0] *= corr[0];
-        o_acc[i][1] *= corr[0];
-        o_acc[i][2] *= corr[1];
-        o_acc[i][3] *= corr[1];
-      }
-    }
-    uint32_t pa[4];
-    pa[0] = pack_bf16x2(s[0][0], s[0][1]);
-    pa[1] = pack_bf16x2(s[0][2], s[0][3]);
-    pa[2] = pack_bf16x2(s[1][0], s[1][1]);
-    pa[3] = pack_bf16x2(s[1][2], s[1][3]);
-#pragma unroll
-    for (int dt = 0; dt < D / 16; ++dt) {
-      uint32_t vf[4];
-      const int vrow = warp * 16 + (lane & 15);
-      const int vchunk = dt * 2 + (lane >> 4);
-      ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
-      mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
-      mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
-    }
+    decode_warp_tile<D, NR>(smem_u32(sK + stage * Cfg::KV_BYTES), smem_u32(sV + stage * Cfg::KV_BYTES),
+                            (t_begin + it) * Cfg::BN + warp * 16, warp, lane, q_frag, o_acc, row_max,
+                            row_sum, pos_r, kv_len, p.scale_log2, p.window, p.sink);
     // This warp is done reading the stage.
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -843,21 +937,39 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
   float* m_buf = reinterpret_cast<float*>(sK);
   float* l_buf = m_buf + 64;
   float* o_buf = l_buf + 64;
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    row_sum[r] = quad_sum(row_sum[r]);
-    if ((lane & 3) == 0) {
-      m_buf[warp * 16 + r_a + 8 * r] = row_max[r];
-      l_buf[warp * 16 + r_a + 8 * r] = row_sum[r];
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
-    const int col = i * 8 + (lane & 3) * 2;
+  if constexpr (NR == 2) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      float* dst = o_buf + (static_cast<size_t>(warp) * 16 + r_a + 8 * r) * (D + 4) + col;
-      *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+      row_sum[r] = quad_sum(row_sum[r]);
+      if ((lane & 3) == 0) {
+        m_buf[warp * 16 + r_a + 8 * r] = row_max[r];
+        l_buf[warp * 16 + r_a + 8 * r] = row_sum[r];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + (lane & 3) * 2;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float* dst = o_buf + (static_cast<size_t>(warp) * 16 + r_a + 8 * r) * (D + 4) + col;
+        *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      row_sum[c] = col_sum(row_sum[c]);
+      if (r_a == 0) {
+        m_buf[warp * 16 + row_of[c]] = row_max[c];
+        l_buf[warp * 16 + row_of[c]] = row_sum[c];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int dim = (i >> 1) * 16 + r_a + 8 * (i & 1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        o_buf[(static_cast<size_t>(warp) * 16 + row_of[c]) * (D + 4) + dim] = o_acc[i][c];
     }
   }
   __syncthreads();
@@ -940,7 +1052,7 @@ struct DecodePersistCfg {
   // results are joined 2, 3 -> 0, 1 and then 1 -> 0), their maxima and sums
   static constexpr size_t smem(int rows) {
     return 1024 + 2 * static_cast<size_t>(STAGES) * KV_BYTES + 2 * static_cast<size_t>(rows) * D * 2 +
-           2 * static_cast<size_t>(rows) * D * 4 + 4 * static_cast<size_t>(rows) * 4 +
+           2 * static_cast<size_t>((rows + 1) & ~1) * D * 4 + 4 * static_cast<size_t>(rows) * 4 +
            2 * BT_ENTRIES * 4 + 2 * META_INTS * 4 + (2 * STAGES + 4) * 8 + 64;
   }
 };
@@ -957,7 +1069,7 @@ __device__ __forceinline__ long long balanced_per(long long total_tiles, int cta
   return per < 2 ? 2 : per;
 }
 
-template <int D, int NSTAGES, int MINB>
+template <int D, int NSTAGES, int MINB, int NR>
 __global__ void __launch_bounds__(160, MINB)
 gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const AttnParams p,
@@ -972,7 +1084,7 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
   uint8_t* sQ = sV + Cfg::STAGES * Cfg::KV_BYTES;                       // [2][rows][D] bf16, linear
   float* s_fold = reinterpret_cast<float*>(sQ + 2 * rows * D * 2);      // [2][D / 8][rows][4] float2, then maxima [2][rows], sums [2][rows]
-  int* s_bt = reinterpret_cast<int*>(s_fold + 2 * rows * D + 4 * rows);  // [2][BT_ENTRIES]
+  int* s_bt = reinterpret_cast<int*>(s_fold + 2 * ((rows + 1) & ~1) * D + 4 * rows);  // [2][BT_ENTRIES]
   int* s_meta = s_bt + 2 * Cfg::BT_ENTRIES;                             // [2][META_INTS]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_meta + 2 * Cfg::META_INTS);
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
@@ -1192,7 +1304,7 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int r_a = lane >> 2;
   uint32_t g = 0;
   volatile int* s_dec = s_abort + 1;
-  float* m_buf = s_fold + 2 * rows * D;             // [2][rows] maxima, then [2][rows] sums
+  float* m_buf = s_fold + 2 * ((rows + 1) & ~1) * D;   // [2][rows] maxima, then [2][rows] sums
   float* l_buf = m_buf + 2 * rows;
   for (int k = 0;; ++k) {
     const int par = k & 1;
@@ -1218,34 +1330,41 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int kvh = (item / p.splits) % p.Hk;
     const int b = item / (p.splits * p.Hk);
 
-    // query fragments straight from the linear rows (rows beyond `rows` are zero)
-    uint32_t q_frag[D / 16][4];
+    // query fragments straight from the linear rows (rows beyond `rows` are zero).  NR = 2:
+    // {a0, a1, a2, a3} = (row, col), (row + 8, col), (row, col + 8), (row + 8, col + 8) with row =
+    // lane / 4; NR = 1: the operand of the transposed product, {(row, col), (row, col + 8)}.
+    uint32_t q_frag[D / 16][2 * NR];
     {
       const uint8_t* qb = sQ + par * rows * D * 2;
       const int c0 = (lane & 3) * 2;
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const int col = ks * 16 + c0;
-        q_frag[ks][0] = r_a < rows ? *reinterpret_cast<const uint32_t*>(qb + (r_a * D + col) * 2) : 0u;
-        q_frag[ks][1] = r_a + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + ((r_a + 8) * D + col) * 2) : 0u;
-        q_frag[ks][2] = r_a < rows ? *reinterpret_cast<const uint32_t*>(qb + (r_a * D + col + 8) * 2) : 0u;
-        q_frag[ks][3] = r_a + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + ((r_a + 8) * D + col + 8) * 2) : 0u;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          const int row = r_a + 8 * r;
+          q_frag[ks][r] = row < rows ? *reinterpret_cast<const uint32_t*>(qb + (row * D + col) * 2) : 0u;
+          q_frag[ks][NR + r] = row < rows ? *reinterpret_cast<const uint32_t*>(qb + (row * D + col + 8) * 2) : 0u;
+        }
       }
     }
     // the query buffer and the meta words of this parity may be rewritten from here on
     __syncwarp();
     if (lane == 0) mbar_arrive(&q_empty[par]);
 
-    float o_acc[D / 8][4];
+    float o_acc[D / 8][2 * NR];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+      for (int j = 0; j < 2 * NR; ++j) o_acc[i][j] = 0.f;
     float row_max[2] = {-INFINITY, -INFINITY};
     float row_sum[2] = {0.f, 0.f};
+    // the two rows this lane keeps statistics for: fragment rows g and g + 8 (NR = 2), queries
+    // 2 t and 2 t + 1 (NR = 1)
+    const int row_of[2] = {NR == 2 ? r_a : (lane & 3) * 2, NR == 2 ? r_a + 8 : (lane & 3) * 2 + 1};
     int pos_r[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + (r_a + 8 * r) / G;
+    for (int r = 0; r < 2; ++r) pos_r[r] = kv_len - p.q_len + row_of[r] / G;
 
     for (int it = 0; it < n_tiles; ++it, ++g) {
       const int stage = static_cast<int>(g % Cfg::STAGES);
@@ -1258,117 +1377,79 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
         break;
       }
-      const uint32_t kt = smem_u32(sK + stage * Cfg::KV_BYTES);
-      const uint32_t vt = smem_u32(sV + stage * Cfg::KV_BYTES);
-      const int n0 = (t_begin + it) * Cfg::BN + warp * 16;
-
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        uint32_t kf[4];
-        const int krow = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-        const int kchunk = ks * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(kf, kt + kv_swz<D>(krow, kchunk));
-        mma_bf16_16816(s[0], q_frag[ks], kf[0], kf[1]);
-        mma_bf16_16816(s[1], q_frag[ks], kf[2], kf[3]);
-      }
-      float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int key = n0 + i * 8 + (lane & 3) * 2 + (j & 1);
-          const int pos = pos_r[j >> 1];
-          bool keep = key <= pos && key < kv_len;
-          if (p.window > 0) keep = keep && (key > pos - p.window || key < p.sink);
-          const float v = keep ? s[i][j] * p.scale_log2 : -INFINITY;
-          s[i][j] = v;
-          tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
-        }
-      }
-      float corr[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const float tm = quad_max(tile_max[r]);
-        const float new_max = fmaxf(row_max[r], tm);
-        corr[r] = (new_max == -INFINITY) ? 1.f : exp2f(row_max[r] - new_max);
-        row_max[r] = new_max;
-        row_sum[r] *= corr[r];
-      }
-      const float m_use[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0],
-                              row_max[1] == -INFINITY ? 0.f : row_max[1]};
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float e = exp2f(s[i][j] - m_use[j >> 1]);
-          s[i][j] = e;
-          row_sum[j >> 1] += e;
-        }
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        o_acc[i][0] *= corr[0];
-        o_acc[i][1] *= corr[0];
-        o_acc[i][2] *= corr[1];
-        o_acc[i][3] *= corr[1];
-      }
-      uint32_t pa[4];
-      pa[0] = pack_bf16x2(s[0][0], s[0][1]);
-      pa[1] = pack_bf16x2(s[0][2], s[0][3]);
-      pa[2] = pack_bf16x2(s[1][0], s[1][1]);
-      pa[3] = pack_bf16x2(s[1][2], s[1][3]);
-#pragma unroll
-      for (int dt = 0; dt < D / 16; ++dt) {
-        uint32_t vf[4];
-        const int vrow = warp * 16 + (lane & 15);
-        const int vchunk = dt * 2 + (lane >> 4);
-        ldmatrix_x4_trans(vf, vt + kv_swz<D>(vrow, vchunk));
-        mma_bf16_16816(o_acc[2 * dt], pa, vf[0], vf[1]);
-        mma_bf16_16816(o_acc[2 * dt + 1], pa, vf[2], vf[3]);
-      }
+      decode_warp_tile<D, NR>(smem_u32(sK + stage * Cfg::KV_BYTES), smem_u32(sV + stage * Cfg::KV_BYTES),
+                              (t_begin + it) * Cfg::BN + warp * 16, warp, lane, q_frag, o_acc, row_max,
+                              row_sum, pos_r, kv_len, p.scale_log2, p.window, p.sink);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
 
     // ---- join the four warps' results (rows < `rows` only): warps 2 and 3 hand theirs to warps 0
     // and 1, then warp 1 hands the sum to warp 0, which stores.  The same lane of every warp holds
-    // the same (row, column) positions, so a slot is indexed [column group][row][lane in quad].
+    // the same positions of the output, so a slot is indexed by accumulator register and lane: as
+    // float2 [register pair i][row][lane % 4] (NR = 2: the pair of row g + 8 r) or
+    // [i][lane / 4][lane % 4 < tq] (NR = 1: the two queries of the lane, tq = ceil(rows / 2)).
+    const int tq = (rows + 1) >> 1;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) row_sum[r] = quad_sum(row_sum[r]);
+    for (int r = 0; r < 2; ++r) row_sum[r] = NR == 2 ? quad_sum(row_sum[r]) : col_sum(row_sum[r]);
+    const bool stat_lane = NR == 2 ? (lane & 3) == 0 : r_a == 0;      // writes the row's maximum and sum
+    const bool acc_lane = NR == 2 || (lane & 3) < tq;
+    auto fold_at = [&](int fs, int i, int r) -> float2* {
+      const int idx = NR == 2 ? ((fs * (D / 8) + i) * rows + row_of[r]) * 4 + (lane & 3)
+                              : ((fs * (D / 8) + i) * 8 + r_a) * tq + (lane & 3);
+      return reinterpret_cast<float2*>(s_fold) + idx;
+    };
     auto put = [&](int fs) {
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int row = r_a + 8 * r;
-        if (row < rows) {
-          if ((lane & 3) == 0) {
-            m_buf[fs * rows + row] = row_max[r];
-            l_buf[fs * rows + row] = row_sum[r];
-          }
-#pragma unroll
-          for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<float2*>(s_fold + (((fs * (D / 8) + i) * rows + row) * 4 + (lane & 3)) * 2) =
-                make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+      for (int r = 0; r < 2; ++r)
+        if (stat_lane && row_of[r] < rows) {
+          m_buf[fs * rows + row_of[r]] = row_max[r];
+          l_buf[fs * rows + row_of[r]] = row_sum[r];
         }
+      if constexpr (NR == 2) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+          if (row_of[r] < rows) {
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) *fold_at(fs, i, r) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+          }
+      } else if (acc_lane) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) *fold_at(fs, i, 0) = make_float2(o_acc[i][0], o_acc[i][1]);
       }
     };
     auto take = [&](int fs) {
+      float fa[2], fb[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int row = r_a + 8 * r;
-        if (row < rows) {
-          const float mo = m_buf[fs * rows + row];
+        fa[r] = 1.f;
+        fb[r] = 0.f;
+        if (row_of[r] < rows) {
+          const float mo = m_buf[fs * rows + row_of[r]];
           const float m = fmaxf(row_max[r], mo);
-          const float fa = row_max[r] == -INFINITY ? 0.f : exp2f(row_max[r] - m);
-          const float fb = mo == -INFINITY ? 0.f : exp2f(mo - m);
-          row_sum[r] = row_sum[r] * fa + l_buf[fs * rows + row] * fb;
+          fa[r] = row_max[r] == -INFINITY ? 0.f : exp2f(row_max[r] - m);
+          fb[r] = mo == -INFINITY ? 0.f : exp2f(mo - m);
+          row_sum[r] = row_sum[r] * fa[r] + l_buf[fs * rows + row_of[r]] * fb[r];
           row_max[r] = m;
+        }
+      }
+      if constexpr (NR == 2) {
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i) {
-            const float2 x = *reinterpret_cast<const float2*>(
-                s_fold + (((fs * (D / 8) + i) * rows + row) * 4 + (lane & 3)) * 2);
-            o_acc[i][2 * r] = o_acc[i][2 * r] * fa + x.x * fb;
-            o_acc[i][2 * r + 1] = o_acc[i][2 * r + 1] * fa + x.y * fb;
+        for (int r = 0; r < 2; ++r)
+          if (row_of[r] < rows) {
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+              const float2 x = *fold_at(fs, i, r);
+              o_acc[i][2 * r] = o_acc[i][2 * r] * fa[r] + x.x * fb[r];
+              o_acc[i][2 * r + 1] = o_acc[i][2 * r + 1] * fa[r] + x.y * fb[r];
+            }
           }
+      } else if (acc_lane) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          const float2 x = *fold_at(fs, i, 0);
+          o_acc[i][0] = o_acc[i][0] * fa[0] + x.x * fb[0];
+          o_acc[i][1] = o_acc[i][1] * fa[1] + x.y * fb[1];
         }
       }
     };
@@ -1385,28 +1466,41 @@ gqa_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_k,
       take(1);
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int row = r_a + 8 * r;
+        const int row = row_of[r];
         if (row >= rows) continue;
         const float m = row_max[r], l = row_sum[r];
         const int qi = row / G, hh = kvh * G + row % G;
-        if (slot < 0) {
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          __nv_bfloat16* dst = p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
-                               static_cast<long long>(hh) * D + (lane & 3) * 2;
+        const float inv = slot < 0 ? (l > 0.f ? 1.f / l : 0.f) : 1.f;
+        __nv_bfloat16* dst_o = p.out + static_cast<long long>(b * p.q_len + qi) * p.out_stride +
+                               static_cast<long long>(hh) * D;
+        float* dst_p = p.o_part + (static_cast<size_t>(slot < 0 ? 0 : slot) * 16 + row) * D;
+        if constexpr (NR == 2) {
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<uint32_t*>(dst + i * 8) =
-                pack_bf16x2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv);
-          if (p.lse && (lane & 3) == 0)
-            p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
-                l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+          for (int i = 0; i < D / 8; ++i) {
+            const int col = i * 8 + (lane & 3) * 2;
+            if (slot < 0)
+              *reinterpret_cast<uint32_t*>(dst_o + col) =
+                  pack_bf16x2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv);
+            else
+              *reinterpret_cast<float2*>(dst_p + col) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+          }
         } else {
-          const size_t pr = static_cast<size_t>(slot) * 16 + row;
-          float* dst = p.o_part + pr * D + (lane & 3) * 2;
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
-          if ((lane & 3) == 0) {
+          for (int i = 0; i < D / 8; ++i) {
+            const int dim = (i >> 1) * 16 + r_a + 8 * (i & 1);
+            if (slot < 0)
+              dst_o[dim] = __float2bfloat16(o_acc[i][r] * inv);
+            else
+              dst_p[dim] = o_acc[i][r];
+          }
+        }
+        if (stat_lane) {
+          if (slot < 0) {
+            if (p.lse)
+              p.lse[static_cast<long long>(b * p.q_len + qi) * p.Hq + hh] =
+                  l > 0.f ? (m + log2f(l)) / kLog2e : -INFINITY;
+          } else {
+            const size_t pr = static_cast<size_t>(slot) * 16 + row;
             p.lse_part[pr * 2] = m;
             p.lse_part[pr * 2 + 1] = l;
           }
@@ -1532,10 +1626,10 @@ static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
-template <int D, int NSTAGES, int MINB>
-static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+template <int D, int NSTAGES, int MINB, int NR>
+static int launch_decode_tma_rows(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = DecodeTmaCfg<D, NSTAGES>;
-  auto kern = gqa_decode_tma_kernel<D, NSTAGES, MINB>;
+  auto kern = gqa_decode_tma_kernel<D, NSTAGES, MINB, NR>;
   static DeviceOnce once;
   int dev = 0;
   if (once.needed(&dev)) {
@@ -1582,20 +1676,35 @@ static int device_sms() {
   return sms;
 }
 
+// At most eight query rows per kv head: the kernel variant that keeps half of every fragment.
+template <int D, int NSTAGES, int MINB>
+static int launch_decode_tma(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  return (p.Hq / p.Hk) * p.q_len <= 8 ? launch_decode_tma_rows<D, NSTAGES, MINB, 1>(p, grid, stream)
+                                      : launch_decode_tma_rows<D, NSTAGES, MINB, 2>(p, grid, stream);
+}
+
 template <int D, int NSTAGES, int MINB>
 static int launch_decode_persist(const AttnParams& p, int B, cudaStream_t stream) {
   using Cfg = DecodePersistCfg<D, NSTAGES>;
-  auto kern = gqa_decode_persist_kernel<D, NSTAGES, MINB>;
   const int rows = (p.Hq / p.Hk) * p.q_len;
+  // at most eight query rows per kv head: the variant that keeps half of every fragment
+  auto kern = rows <= 8 ? gqa_decode_persist_kernel<D, NSTAGES, MINB, 1> : gqa_decode_persist_kernel<D, NSTAGES, MINB, 2>;
   const size_t smem = Cfg::smem(rows);
   static DeviceOnce once;
   static int sms = 148;
   int dev = 0;
   if (once.needed(&dev)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gqa_decode_persist_kernel<D, NSTAGES, MINB, 1>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(Cfg::smem(8))) != cudaSuccess ||
+        cudaFuncSetAttribute(gqa_decode_persist_kernel<D, NSTAGES, MINB, 2>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::smem(16))) != cudaSuccess)
       return -20;
-    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gqa_decode_persist_kernel<D, NSTAGES, MINB, 1>,
+                         cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gqa_decode_persist_kernel<D, NSTAGES, MINB, 2>,
+                         cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     once.mark(dev);
   }

@@ -516,38 +516,80 @@ def decode_splits_persistent(num_seqs: int, num_kv_heads: int, max_seq_len: int,
     return best
 
 
-# OMNI_B200_DECODE_PERSISTENT=1 makes the persistent-CTA decode kernel the default.  Measured on the
-# serving shapes (128 sequences x 1152 keys, 8 kv heads) it is 2-5 % slower than one CTA per item
-# (130 us against 127 us), so it is opt-in.
-DECODE_PERSISTENT = os.environ.get("OMNI_B200_DECODE_PERSISTENT", "0") != "0"
+# Decode attention work distribution, OMNI_B200_DECODE_PERSISTENT = 0 | 1 | 2:
+#   0  one CTA per (sequence, kv head, split) item;
+#   1  persistent CTAs that take whole items from a device counter (measured 2-5 % slower than 0 on
+#      128 sequences x 1152 keys x 8 kv heads: 130 us against 127 us);
+#   2  persistent CTAs over a balanced cut of all key tiles: whole items leave the last round of the
+#      resident CTAs partly empty (1024 items on 444 CTAs: three rounds for 2.3 rounds of work), the
+#      balanced cut does not; pieces of items that cross a cut go through fp32 scratch and a merge
+#      kernel.  Measured 127.5 us on the same shapes (4 / 2 kv heads: 80.9 / 52.2 us against 69.7 /
+#      38.9 us for mode 0): the memory system is saturated with every resident CTA streaming, so the
+#      rounds saved do not shorten the call.
+DECODE_PERSISTENT = int(os.environ.get("OMNI_B200_DECODE_PERSISTENT", "0") or 0)
+
+
+def decode_balanced_plan(seq_lens, num_kv_heads: int, ctas: int, tile: int = 64):
+    """Host restatement of the balanced cut that ``gqa_decode_persist_kernel`` (mode 2) and its merge
+    kernel derive on the device, for tests and capacity checks.  Returns one list per CTA of
+    ``(sequence, kv head, first tile, tiles, scratch slot or -1)``."""
+    nb = [max(1, -(-int(n) // tile)) for n in seq_lens]
+    total = sum(nb) * num_kv_heads
+    per = max(2, -(-total // ctas))
+    starts, acc = [], 0
+    for n in nb:
+        starts.append(acc)
+        acc += n * num_kv_heads
+    plan = []
+    for c in range(ctas):
+        x, x_end = c * per, min(total, (c + 1) * per)
+        segs = []
+        while x < x_end:
+            b = max(i for i in range(len(nb)) if starts[i] <= x)
+            off = x - starts[b]
+            kvh, t = divmod(off, nb[b])
+            n = min(nb[b] - t, x_end - x)
+            whole = t == 0 and n == nb[b]
+            segs.append((b, kvh, t, n, -1 if whole else 2 * c + (0 if not segs else 1)))
+            x += n
+        plan.append(segs)
+    return plan
 
 
 def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                block_tables: torch.Tensor, seq_lens: torch.Tensor, num_seqs: int, num_q_heads: int,
                scale: float, q_len: int = 1, window: int = 0, splits: int = 0,
-               max_seq_len: int = 0, sink: int = 0, persistent: Optional[bool] = None) -> torch.Tensor:
+               max_seq_len: int = 0, sink: int = 0, persistent=None) -> torch.Tensor:
     """Decode attention: q_len (usually 1) new tokens per sequence, sequences laid
-    out back to back in q.  ``persistent`` (default: ``DECODE_PERSISTENT``) runs the persistent-CTA
-    kernel, which hands out (sequence, kv head, split) items through a device counter."""
+    out back to back in q.  ``persistent`` (default: ``DECODE_PERSISTENT``): 0 / False = one CTA per
+    item, 1 / True = persistent CTAs fed by a device counter, 2 = persistent CTAs over a balanced cut
+    of the key tiles (``splits`` is ignored)."""
     if not q.is_cuda:
         cu = torch.arange(0, (num_seqs + 1) * q_len, q_len, dtype=torch.int32, device=q.device)
         return ref.paged_attention(q, k_cache, v_cache, block_tables[:num_seqs], cu,
                                    seq_lens[:num_seqs], num_q_heads, scale, True, window, False, sink)
     C = _C()
     hk, d = k_cache.shape[1], k_cache.shape[3]
-    persistent = DECODE_PERSISTENT if persistent is None else persistent
+    persistent = int(DECODE_PERSISTENT if persistent is None else persistent)
+    st = device_state(q.device)
+    stream_id = torch.cuda.current_stream(q.device).cuda_stream
+    if persistent == 2:
+        nbytes = C.gqa_decode_balanced_scratch_bytes(d, (num_q_heads // hk) * q_len)
+        _count(2)
+        return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
+                            scale, _pack_window(window, sink), 1, st.decode_scratch(stream_id, nbytes),
+                            st.status, 2, None)
     if splits <= 0:
         bound = max_seq_len if max_seq_len > 0 else block_tables.shape[1] * k_cache.shape[2]
         splits = (decode_splits_persistent if persistent else decode_splits)(num_seqs, hk, bound)
     scratch = None
-    st = device_state(q.device)
     if splits > 1:
         nbytes = C.gqa_decode_scratch_bytes(num_seqs, hk, d, splits)
-        scratch = st.decode_scratch(torch.cuda.current_stream(q.device).cuda_stream, nbytes)
+        scratch = st.decode_scratch(stream_id, nbytes)
     _count(2 if splits > 1 else 1)
     return C.gqa_decode(q, k_cache, v_cache, block_tables, seq_lens, num_seqs, q_len, num_q_heads,
                         scale, _pack_window(window, sink), splits, scratch, st.status, persistent,
-                        st.work_counter(torch.cuda.current_stream(q.device).cuda_stream) if persistent else None)
+                        st.work_counter(stream_id) if persistent else None)
 
 
 # -------------------------------------------------------------------- sampling

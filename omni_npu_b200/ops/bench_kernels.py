@@ -160,13 +160,19 @@ def bench_attn(args):
         q = torch.randn(b, hq * d, device="cuda", dtype=torch.bfloat16)
         bt = torch.arange(1, nblk, device="cuda", dtype=torch.int32).view(b, -1)
         sl = torch.full((b,), ctx, device="cuda", dtype=torch.int32)
+        if args.ctx_spread > 0:      # lengths spread evenly over [ctx - spread, ctx]
+            sl = (ctx - torch.arange(b, device="cuda") * args.ctx_spread // max(1, b - 1)).to(torch.int32)
+            by_scale = float(sl.sum()) / (b * ctx)
+        else:
+            by_scale = 1.0
         for splits in ((0,) if args.splits == 0 else (args.splits,)):
-            by = 2.0 * b * ctx * hk * d * 2
-            for persistent in (True, False):
-                used = splits or (ops.decode_splits_persistent if persistent else ops.decode_splits)(b, hk, ctx)
+            by = 2.0 * b * ctx * hk * d * 2 * by_scale
+            for persistent in (2, 1, 0):
+                used = 1 if persistent == 2 else (
+                    splits or (ops.decode_splits_persistent if persistent else ops.decode_splits)(b, hk, ctx))
                 t = time_fn(lambda: ops.gqa_decode(q, kc, vc, bt, sl, b, hq, d ** -0.5, splits=splits,
                                                    max_seq_len=ctx, persistent=persistent), iters=args.iters)
-                kind = "persistent CTAs" if persistent else "one CTA per item"
+                kind = ("one CTA per item", "persistent CTAs", "balanced persistent CTAs")[persistent]
                 print(f"decode  B={b:4d} ctx={ctx:6d} splits={used:2d} {kind}: {t*1e3:8.1f} us  "
                       f"{by/t/1e6:7.0f} GB/s frac {by/hbm/(t/1e3):.2f}")
     if prefill_cases:
@@ -330,6 +336,7 @@ def main():
     ap.add_argument("--hk", type=int, default=8, help="attn: KV heads")
     ap.add_argument("--b", type=int, help="attn: batch size of a single case")
     ap.add_argument("--ctx", type=int, default=1024, help="attn: context length of a single case")
+    ap.add_argument("--ctx-spread", type=int, default=0, help="attn decode: lengths spread over [ctx - spread, ctx]")
     ap.add_argument("--block-size", type=int, default=16, help="attn: tokens per cache block")
     ap.add_argument("--phase", default="both", choices=["both", "decode", "prefill"])
     args = ap.parse_args()

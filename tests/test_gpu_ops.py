@@ -307,7 +307,7 @@ def test_gqa_prefill_window_and_mla_dims():
     _close(got, want, 2e-2, 2e-2)
 
 
-@pytest.mark.parametrize("persistent", [True, False])
+@pytest.mark.parametrize("persistent", [2, True, False])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (4, 2, 64), (16, 1, 128), (16, 2, 128)])
 def test_gqa_decode(splits, hq, hk, d, persistent):
@@ -336,6 +336,57 @@ def test_gqa_decode_persistent_more_items_than_ctas_twice():
     assert wc.tolist() == [0, 0]
     assert ops.decode_splits_persistent(128, 8, 1296) == 2 and ops.decode_splits_persistent(128, 4, 1296) == 4
     assert ops.decode_splits_persistent(1, 8, 8192) > 8          # few items: split to fill the SMs
+
+
+@pytest.mark.parametrize("n_seqs,hq,hk,hi", [(96, 32, 8, 700), (300, 8, 2, 150), (3, 16, 1, 5000), (40, 4, 4, 64)])
+def test_gqa_decode_balanced_cut(n_seqs, hq, hk, hi):
+    """Persistent CTAs over the balanced cut of the key tiles: ranges that hold several whole items,
+    items that spread over many CTAs, more CTAs than tiles; twice, as a graph replay would run it."""
+    torch.manual_seed(31)
+    seq_lens = [int(x) for x in torch.randint(1, hi, (n_seqs,))]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * n_seqs, hq, hk, 128, 16, seed=32)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, hq, 128 ** -0.5, True, 0)
+    args = (q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), n_seqs, hq, 128 ** -0.5)
+    for _ in range(2):
+        got = ops.gqa_decode(*args, persistent=2)
+        _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
+
+
+def test_gqa_decode_balanced_cut_multi_token_window_and_sink():
+    seq_lens = [40, 130, 7, 900]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [3] * 4, 8, 2, 128, 16, seed=33)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.09, True, 0)
+    got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 4, 8, 0.09, q_len=3,
+                         persistent=2)
+    _close(got, want, 2e-2, 2e-2)
+    seq_lens = [1, 17, 64, 65, 1000, 333]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 6, 8, 2, 128, 16, seed=13)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.1, True, 64, False, 32)
+    got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 6, 8, 0.1, window=64,
+                         sink=32, persistent=2)
+    _close(got, want, 2e-2, 2e-2)
+    # head size 64, sixteen query rows per kv head
+    seq_lens = [500, 3, 129]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [1] * 3, 16, 1, 64, 16, seed=34)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 16, 0.125, True, 0)
+    got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 3, 16, 0.125, persistent=2)
+    _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("persistent", [2, 1, 0])
+def test_gqa_decode_two_tokens_eight_rows(persistent):
+    """Two new tokens per sequence with a group of four: eight query rows per kv head, the
+    transposed-product path of the decode kernels, each query with its own causal limit."""
+    seq_lens = [40, 130, 7, 64, 2, 700]
+    q, kc, vc, bt, cu, sl = _paged_setup(seq_lens, [2] * 6, 8, 2, 128, 16, seed=35)
+    want = ref.paged_attention(q, kc, vc, bt, cu, sl, 8, 0.09, True, 0)
+    for splits in (1, 3):
+        got = ops.gqa_decode(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), 6, 8, 0.09, q_len=2,
+                             splits=splits, persistent=persistent)
+        _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
 
 
 def test_gqa_decode_multi_token():
