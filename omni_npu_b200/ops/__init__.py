@@ -170,6 +170,16 @@ def check_status(device: Optional[torch.device] = None) -> None:
 # ------------------------------------------------------------------------ GEMM
 # smallest M routed to the CTA-pair GEMM (0 = never); prefill-sized problems only
 PAIR_MIN_M = int(os.environ.get("OMNI_B200_GEMM_PAIR_MIN_M", "1024"))
+# Plain bf16 products (no bias, residual, SwiGLU, scales or fused collective) of a decode-sized batch
+# whose plan here is a cluster split-K: "library" hands them to cuBLAS, "own" keeps them on
+# gemm_tcgen05_kernel.  Measured at M = 128 inside a CUDA graph (us, own / cuBLAS): 4096 x 4096
+# 19.0 / 10.6, 6144 x 4096 20.2 / 12.6, 4096 x 14336 37.4 / 26.3: every CTA of the own kernel re-reads
+# the 128-row activation slab of its K slice and the K slices meet in a 3-4 us exchange, which a
+# library kernel that may share one activation load between the CTAs of a cluster does not pay.
+# Row counts below 64 stay on the own kernel (not measured against the library there, and its result
+# for a row does not depend on how many rows share the launch, which padded CUDA-graph steps rely on).
+SMALL_M_GEMM = os.environ.get("OMNI_B200_SMALL_M_GEMM", "library")
+SMALL_M_LIBRARY_ROWS = (64, 256)
 
 def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
@@ -201,6 +211,10 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         plan = C.gemm_plan(m, n, k, a.dtype.itemsize, swiglu, bn, 1 if swiglu else splits)
         st.plans[key] = plan
     pbn, psplits, ws_bytes, ncnt, cluster = plan
+    if (cluster and SMALL_M_GEMM == "library" and SMALL_M_LIBRARY_ROWS[0] <= m <= SMALL_M_LIBRARY_ROWS[1]
+            and bias is None and residual is None and not swiglu and bn == 0 and splits == 0
+            and a.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)):
+        return torch.nn.functional.linear(a, w)          # a library kernel: not counted as a launch of ours
     ws = cnt = None
     if psplits > 1 and not cluster:
         ws, cnt = st.gemm_workspace(torch.cuda.current_stream(a.device).cuda_stream, ws_bytes, ncnt)
