@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--no-fused-collectives", action="store_true")
+    ap.add_argument("--mixed-batches", action="store_true",
+                    help="decoding requests ride along in prefill steps (default: prompts first)")
     ap.add_argument("--profile", default=None,
                     help="write a per-kernel time table (torch profiler, one extra untimed pass) to this file")
     args = ap.parse_args()
@@ -173,7 +175,7 @@ def run_ours(args) -> None:
         mc, tensor_parallel_size=args.gpus, enable_expert_parallel=moe and args.gpus > 1,
         max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=max_len,
-        block_size=args.block_size, device="cuda", seed=0,
+        block_size=args.block_size, device="cuda", seed=0, enable_mixed_batches=args.mixed_batches,
         additional_config={"fused_collectives": not args.no_fused_collectives})
     llm = LLM(cfg)
     runner = llm.engine.worker.model_runner

@@ -72,6 +72,15 @@ class GQAAttention(torch.nn.Module):
                                 self.head_dim, self.rot_dim, self.neox)
         else:
             ops.gqa_cache_write(k, v, k_cache, v_cache, md.slot_mapping)
+        nd = md.extra.get("num_decode_seqs", 0) if md.is_prefill else 0
+        if nd:
+            # mixed batch: rows [0, nd) are the single new tokens of decoding sequences
+            o_dec = ops.gqa_decode(q[:nd], k_cache, v_cache, md.block_tables[:nd], md.seq_lens[:nd], nd,
+                                   self.num_heads, self.scale, 1, self.window, max_seq_len=md.max_seq_len)
+            o_pre = ops.gqa_prefill(q[nd:], k_cache, v_cache, md.block_tables[nd:], md.extra["cu_q_prefill"],
+                                    md.seq_lens[nd:], md.num_seqs - nd, md.extra["max_q_len_prefill"],
+                                    self.num_heads, self.scale, True, self.window)
+            return torch.cat([o_dec, o_pre], 0)
         if md.is_prefill:
             return ops.gqa_prefill(q, k_cache, v_cache, md.block_tables, md.cu_q, md.seq_lens,
                                    md.num_seqs, md.max_q_len, self.num_heads, self.scale, True,

@@ -146,6 +146,12 @@ class LLMEngine:
         return [RequestOutput.from_request(r) for r in finished]
 
     def _step_async(self) -> List[RequestOutput]:
+        early: List[RequestOutput] = []
+        if (self._inflight is not None and self.scheduler.cfg.enable_mixed_batches
+                and self.scheduler.prompt_work_waiting()):
+            # the next step may carry decoding requests beside prompt chunks: their newest tokens
+            # (and whether they have just finished) must be known before it is put together
+            early = self._settle()
         out = self.scheduler.schedule()
         if out.kind == "decode":
             runner = self.worker.model_runner
@@ -160,10 +166,10 @@ class LLMEngine:
             interval = self.config.parallel.eplb_step_interval
             if interval > 0 and st["steps"] % interval == 0:
                 self.rebalance_experts()                 # weight moves queue behind the step in flight
-            return done
+            return early + done
         # anything but a plain decode step needs the token values on the host first
         done = self._settle()
-        return done + self._run_scheduled(out)
+        return early + done + self._run_scheduled(out)
 
     def _step_data_parallel(self) -> List[RequestOutput]:
         """One global step of a data-parallel deployment.  Every replica schedules its own
@@ -369,7 +375,8 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
     sched = SchedulerConfig(max_num_seqs=kw.pop("max_num_seqs", 128),
                             max_num_batched_tokens=kw.pop("max_num_batched_tokens", 8192),
                             max_model_len=kw.pop("max_model_len", min(8192, model.max_position_embeddings)),
-                            enable_chunked_prefill=kw.pop("enable_chunked_prefill", True))
+                            enable_chunked_prefill=kw.pop("enable_chunked_prefill", True),
+                            enable_mixed_batches=kw.pop("enable_mixed_batches", False))
     comp = kw.pop("compilation_config", None)
     if isinstance(comp, dict):
         comp = CompilationConfig(cudagraph_mode=comp.get("cudagraph_mode", "FULL_DECODE_ONLY"),

@@ -34,6 +34,9 @@ class SchedulerOutput:
     kind: str = "idle"                      # "prefill" | "decode" | "spec_decode" | "idle"
     seqs: List[ScheduledSeq] = field(default_factory=list)
     num_tokens: int = 0
+    # mixed batches: the first num_decode_seqs entries of a "prefill" step are decoding requests
+    # that ride along with one token each
+    num_decode_seqs: int = 0
     preempted: List[str] = field(default_factory=list)
     finished_req_ids: List[str] = field(default_factory=list)
     kv_connector_metadata: Any = None
@@ -107,6 +110,15 @@ class Scheduler:
         req.block_ids.extend(self.pool.allocate(need))
         return True
 
+    def prompt_work_waiting(self) -> bool:
+        """Whether this step could hold prompt tokens: a running request with an unfinished prompt
+        (or recompute), or a waiting request and a free sequence slot."""
+        for req in self.running:
+            remaining = req.num_tokens - req.num_computed_tokens
+            if remaining > 1 or (remaining == 1 and not req.output_token_ids):
+                return True
+        return bool(self.waiting) and len(self.running) < self.cfg.max_num_seqs
+
     def _release(self, req: Request) -> None:
         delay = None
         if self.kv_connector is not None and req.status != RequestStatus.FINISHED_ABORTED:
@@ -159,6 +171,24 @@ class Scheduler:
                 self.pool.release_parked(rid)
 
         budget = self.cfg.max_num_batched_tokens
+        # 0) mixed batches: the decoding requests come first, one token each, when prompt work is
+        # waiting.  No eviction on their behalf: a rider that finds no block sits this step out.
+        riders: List[ScheduledSeq] = []
+        if self.cfg.enable_mixed_batches and self.prompt_work_waiting():
+            for req in self.running:
+                if budget <= 1:
+                    break
+                if req.num_tokens - req.num_computed_tokens != 1 or not req.output_token_ids:
+                    continue
+                if req.spec_token_ids:             # drafts are verified in decode steps only
+                    riders = []
+                    break
+                if not self._ensure_blocks(req, req.num_tokens):
+                    continue
+                riders.append(ScheduledSeq(req, req.num_computed_tokens, 1, True))
+                budget -= 1
+            if not riders:
+                budget = self.cfg.max_num_batched_tokens
         # 1) unfinished prompt chunks of running requests, then new admissions
         prefill: List[ScheduledSeq] = []
         for req in list(self.running):
@@ -253,9 +283,12 @@ class Scheduler:
             prefill.append(ScheduledSeq(req, req.num_computed_tokens, n, n == remaining))
             budget -= n
         if prefill:
+            # a rider whose request was evicted for a prompt chunk above is dropped
+            riders = [s for s in riders if s.request in self.running]
             out.kind = "prefill"
-            out.seqs = prefill
-            out.num_tokens = sum(s.num_new_tokens for s in prefill)
+            out.seqs = riders + prefill
+            out.num_decode_seqs = len(riders)
+            out.num_tokens = sum(s.num_new_tokens for s in out.seqs)
             self._finish_output(out)
             return out
 

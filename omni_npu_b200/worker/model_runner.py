@@ -480,6 +480,14 @@ class ModelRunner:
             max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
             md.extra["seq_lens_host"] = [s.start + s.num_new_tokens for s in out.seqs]
+            nd = getattr(out, "num_decode_seqs", 0)
+            if nd:
+                # mixed batch: the first nd sequences are decoding (one row each); attention layers
+                # that know about it run them through the decode kernel and the rest as a prefill
+                # whose query offsets start at zero
+                md.extra["num_decode_seqs"] = nd
+                md.extra["cu_q_prefill"] = views["cu_q"][nd: n + 1] - nd
+                md.extra["max_q_len_prefill"] = max(s.num_new_tokens for s in out.seqs[nd:])
             sampled = self._forward_and_sample(views, md, n)
         self.step_counter += 1
         self._event_stop(ev, out.kind)

@@ -222,3 +222,30 @@ def test_mtp_chain_of_three_drafts_under_cuda_graphs():
         ops.check_status()
         del llm
     assert outs[False] == outs[True]
+
+
+def test_mixed_batches_give_the_tokens_of_separate_steps():
+    """Decoding requests ride along in the prefill steps of later requests (their rows go through the
+    decode attention kernel, the prompt rows through the prefill kernel, one GEMM over all rows).  A
+    rider's row is multiplied inside a larger launch than in a decode step, so the logits agree to
+    rounding, not bit for bit: every request starts with the same tokens and most tokens agree."""
+    cfg = _small_cfg()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (48, 200, 130, 64, 170, 33, 90, 120)]
+    sps = [SamplingParams(max_tokens=m, ignore_eos=True) for m in (24, 6, 17, 12, 30, 9, 12, 24)]
+    outs, steps = {}, {}
+    for mixed in (False, True):
+        llm = LLM(model=cfg, device="cuda", max_num_seqs=3, max_num_batched_tokens=256, max_model_len=512,
+                  num_gpu_blocks=256, seed=3, enable_mixed_batches=mixed)
+        outs[mixed] = [o.output_token_ids for o in llm.generate(prompts, sps)]
+        steps[mixed] = llm.engine.stats["steps"]
+        ops.check_status()
+        assert llm.engine.scheduler.pool.num_free == 256
+        del llm
+    assert steps[True] < steps[False]
+    same = total = 0
+    for a, b in zip(outs[True], outs[False]):
+        assert len(a) == len(b) and a[:2] == b[:2]
+        same += sum(x == y for x, y in zip(a, b))
+        total += len(a)
+    assert same >= 0.6 * total
