@@ -130,6 +130,7 @@ class _State:
     pp: Optional[GroupCoordinator] = None
     dp: Optional[GroupCoordinator] = None
     ep: Optional[GroupCoordinator] = None
+    pcp: Optional[GroupCoordinator] = None
     local: Optional[GroupCoordinator] = None
     layer_groups: Optional[Dict[str, GroupCoordinator]] = None
     layer_transforms: Optional[Dict[str, tuple]] = None
@@ -164,15 +165,21 @@ def init_distributed(device: torch.device, backend: Optional[str] = None,
 
 
 def init_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, device: Optional[torch.device] = None,
-                        backend: Optional[str] = None) -> None:
+                        backend: Optional[str] = None, pcp: int = 1) -> None:
+    """Rank grid [dp, pp, pcp, tp], tp fastest.  ``pcp`` is the prefill-context-parallel dimension:
+    its ranks hold different tokens of the same prompts.  The expert-parallel group spans dp x pcp x
+    tp of one pipeline stage, so a MoE layer fed with a rank's own token shard needs nothing around
+    it: dispatch sends each shard's rows to the experts' owners and combine brings them back
+    (the reference all-gathers hidden states and router logits over the PCP group before its MoE and
+    reduce-scatters after it: omni_npu/vllm_patches/patches/models/pangu72b-vl/patch_fusedmoe.py:148-159,216-220)."""
     device = device or _S.device or torch.device("cpu")
     backend = backend or _S.backend or ("nccl" if device.type == "cuda" else "gloo")
     _S.device, _S.backend = device, backend
     world = dist.get_world_size() if dist.is_initialized() else 1
-    if world != tp * pp * dp:
-        raise ValueError(f"world size {world} != tp {tp} * pp {pp} * dp {dp}")
+    if world != tp * pp * dp * pcp:
+        raise ValueError(f"world size {world} != tp {tp} * pp {pp} * dp {dp} * pcp {pcp}")
     rank = dist.get_rank() if dist.is_initialized() else 0
-    grid = torch.arange(world).view(dp, pp, tp)
+    grid = torch.arange(world).view(dp, pp, pcp, tp)
 
     def make(name: str, lists: List[List[int]]) -> GroupCoordinator:
         mine = next(l for l in lists if rank in l)
@@ -180,9 +187,10 @@ def init_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, device: Optional[
 
     _S.world = make("world", [list(range(world))])
     _S.tp = make("tp", grid.reshape(-1, tp).tolist())
-    _S.pp = make("pp", grid.permute(0, 2, 1).reshape(-1, pp).tolist())
-    _S.dp = make("dp", grid.permute(1, 2, 0).reshape(-1, dp).tolist())
-    _S.ep = make("ep", grid.permute(1, 0, 2).reshape(pp, dp * tp).tolist())
+    _S.pp = make("pp", grid.permute(0, 2, 3, 1).reshape(-1, pp).tolist())
+    _S.dp = make("dp", grid.permute(1, 2, 3, 0).reshape(-1, dp).tolist())
+    _S.ep = make("ep", grid.permute(1, 0, 2, 3).reshape(pp, dp * pcp * tp).tolist())
+    _S.pcp = make("pcp", grid.permute(0, 1, 3, 2).reshape(-1, pcp).tolist())
     _S.local = _S.world
     _S.layer_groups = {}
     _S.layer_transforms = {}
@@ -221,6 +229,10 @@ def get_dp_group() -> GroupCoordinator:
 
 def get_ep_group() -> GroupCoordinator:
     return _get("ep")
+
+
+def get_pcp_group() -> GroupCoordinator:
+    return _get("pcp")
 
 
 def get_local_world_group() -> GroupCoordinator:
@@ -304,12 +316,12 @@ def get_layer_transforms(key: str) -> tuple:
 
 
 def destroy_model_parallel() -> None:
-    for g in (_S.tp, _S.pp, _S.dp, _S.ep, _S.world):
+    for g in (_S.tp, _S.pp, _S.dp, _S.ep, _S.pcp, _S.world):
         if g is not None:
             g.destroy()
     for g in (_S.layer_groups or {}).values():
         g.destroy()
-    _S.world = _S.tp = _S.pp = _S.dp = _S.ep = _S.local = None
+    _S.world = _S.tp = _S.pp = _S.dp = _S.ep = _S.pcp = _S.local = None
     _S.layer_groups = None
     _S.layer_transforms = None
     _S.initialized = False
@@ -322,7 +334,7 @@ def destroy_distributed() -> None:
 
 
 def _all_groups() -> List[GroupCoordinator]:
-    gs = [g for g in (_S.world, _S.tp, _S.pp, _S.dp, _S.ep, _S.local) if g is not None]
+    gs = [g for g in (_S.world, _S.tp, _S.pp, _S.dp, _S.ep, _S.pcp, _S.local) if g is not None]
     gs += list((_S.layer_groups or {}).values())
     seen, out = set(), []
     for g in gs:

@@ -519,6 +519,51 @@ def task_ep_moe(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
+def task_pcp_moe(rank, world, port, workdir, device_kind):
+    """Prefill context parallelism around a MoE layer: the ranks of the pcp group hold DIFFERENT
+    tokens, the expert-parallel group spans them, and each rank gets back the MoE output of its own
+    shard: dispatch and combine are the exchange, nothing is gathered around the layer."""
+    dev, state = setup(rank, world, port, device_kind)
+    state.init_model_parallel(tp=1, pcp=world, device=dev)
+    assert state.get_pcp_group().world_size == world and state.get_tp_group().world_size == 1
+    assert state.get_ep_group().world_size == world
+    from omni_npu_b200 import ops
+    from omni_npu_b200.layers.moe import FusedMoE, select_experts
+    from omni_npu_b200.ops import ref
+    dt = torch.bfloat16 if device_kind == "cuda" else torch.float32
+    E, K, H, I = 16, 4, 256, 128
+    g = torch.Generator().manual_seed(43)
+    full = dict(gate=torch.randn(E, H, generator=g) * 0.1, w13=torch.randn(E, 2 * I, H, generator=g) * 0.05,
+                w2=torch.randn(E, H, I, generator=g) * 0.05)
+    layer = FusedMoE(E, K, H, I, dtype=dt, device=dev, renormalize=True, max_tokens=512)
+    lo = layer.expert_start
+    layer.gate.weight.data.copy_(full["gate"])
+    layer.w13.data.copy_(full["w13"][lo:lo + layer.local_experts])
+    layer.w2.data.copy_(full["w2"][lo:lo + layer.local_experts])
+    errs = {}
+    for t in (64, 203):                                      # tokens of the whole prompt batch
+        x_all = (torch.randn(t, H, generator=g) * 0.5).to(dt)
+        per = (t + world - 1) // world
+        mine = x_all[rank * per: min(t, (rank + 1) * per)]   # this rank's shard (the last one is shorter)
+        xr = mine.float() if dt == torch.float32 else mine
+        logits = ref.gemm(xr.cpu(), full["gate"].to(dt), out_dtype=torch.float32)
+        w, ids = select_experts(logits, K, renormalize=True)
+        want = ref.moe_experts(xr.cpu(), full["w13"].to(dt), full["w2"].to(dt), ids, w).float()
+        got = layer(mine.to(dev))
+        assert got.shape == mine.shape
+        errs[str(t)] = (got.float().cpu() - want).abs().max().item()
+    if device_kind == "cuda":
+        torch.cuda.synchronize()
+        ops.check_status()
+    state.get_world_group().barrier()
+    json.dump({"max_err": errs}, open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if layer.buffers is not None:
+        layer.buffers.close()
+    if device_kind == "cuda":
+        state.finish_process()
+    state.destroy_distributed()
+
+
 def task_ep_timing(rank, world, port, workdir, device_kind):
     """Device time of the expert-parallel dispatch and combine alone (CUDA events around CUDA-graph
     replays, max over ranks) for the row sizes of DeepSeek-V2-Lite and DeepSeek-V3.2, with the bytes
@@ -806,7 +851,7 @@ def task_ag_gemm(rank, world, port, workdir, device_kind):
     state.destroy_distributed()
 
 
-TASKS = {"nvls": task_nvls, "ep_timing": task_ep_timing, "dcp_engine": task_dcp_engine, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
+TASKS = {"nvls": task_nvls, "ep_timing": task_ep_timing, "dcp_engine": task_dcp_engine, "ag_gemm": task_ag_gemm, "dcp_mla": task_dcp_mla, "ep_moe": task_ep_moe, "pcp_moe": task_pcp_moe, "kv_pull": task_kv_pull, "comm": task_comm, "tp_engine": task_tp_engine, "server_loop": task_server_loop, "dp_engine": task_dp_engine, "pp_deepseek": task_pp_deepseek, "symm": task_symm}
 
 if __name__ == "__main__":
     task, rank, world, port, workdir = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]

@@ -166,6 +166,28 @@ def test_expert_parallel_moe_two_ranks_gloo():
         assert max(r["max_err"].values()) < 1e-4, r
 
 
+def test_prefill_context_parallel_ranks_share_the_experts_two_ranks_gloo():
+    """The pcp dimension of the rank grid: two ranks hold different token shards, the expert-parallel
+    group spans them, every rank gets the MoE output of its own shard."""
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("pcp_moe", 2, d)
+    for r in res:
+        assert max(r["max_err"].values()) < 1e-4, r
+
+
+def test_rank_grid_with_a_prefill_context_parallel_dimension():
+    """Group membership on the [dp, pp, pcp, tp] grid, without processes: the lists that
+    init_model_parallel builds for 16 ranks as dp 2 x pp 2 x pcp 2 x tp 2."""
+    import torch
+    grid = torch.arange(16).view(2, 2, 2, 2)
+    tp = grid.reshape(-1, 2).tolist()
+    pcp = grid.permute(0, 1, 3, 2).reshape(-1, 2).tolist()
+    ep = grid.permute(1, 0, 2, 3).reshape(2, 8).tolist()
+    assert [0, 1] in tp and [2, 3] in tp
+    assert [0, 2] in pcp and [1, 3] in pcp and [4, 6] in pcp
+    assert ep[0] == [0, 1, 2, 3, 8, 9, 10, 11] and ep[1] == [4, 5, 6, 7, 12, 13, 14, 15]
+
+
 def test_decode_context_parallel_engine_matches_plain_tensor_parallel(monkeypatch):
     """The latent KV cache sharded by tokens over the two tensor-parallel ranks (token p on rank
     p % 2): cache writes skip foreign tokens, prefill gathers the shards of the context (a 70-token
