@@ -91,6 +91,15 @@ def test_expert_parallel_moe_dispatch_combine_over_peer_memory():
         assert max(r["max_err"].values()) < 0.06, r
 
 
+def test_prefill_context_parallel_token_shards_through_the_moe_layer():
+    """Two ranks of the pcp dimension hold different tokens; dispatch and combine over peer memory
+    return each rank the MoE output of its own shard."""
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks("pcp_moe", 2, d, device="cuda", timeout=300)
+    for r in res:
+        assert max(r["max_err"].values()) < 0.06, r
+
+
 def test_expert_parallel_dispatch_and_combine_device_times():
     """Times only (the numerics are the test above): dispatch in bf16 and with the fp8 quantisation
     fused in, and the combine, on every GPU of the box; written out for the profile notes."""
