@@ -29,8 +29,15 @@ waiting for the previous step's tokens (they are fed forward on the device, the 
 placeholders) and ``sample_tokens`` returns an ``AsyncModelRunnerOutput`` that the executor
 resolves later; any other kind of step first waits for the tokens in flight.
 
-Not supported under vLLM yet (refused with a clear error, never silently wrong): vLLM-side
-speculative decoding, structured-output bitmasks, LoRA, pooling and pipeline parallelism.
+Speculative decoding driven by vLLM's scheduler: the n-gram method.  The worker looks the drafts
+up on the host after every step and hands them to vLLM (``take_draft_token_ids``), vLLM schedules
+them, the worker verifies 1 + k rows per request in one pass and returns the accepted tokens plus
+the one that follows them (the reference patches vLLM's ``EagleProposer`` for graph-mode drafting:
+omni_npu/vllm_patches/patches/common/patch_eagle.py; the model-based drafters, the MTP head as a
+chain of k steps, run in the standalone engine here).
+
+Not supported under vLLM yet (refused with a clear error, never silently wrong): model-based
+speculative methods, structured-output bitmasks, LoRA, pooling and pipeline parallelism.
 """
 from __future__ import annotations
 
@@ -107,13 +114,15 @@ class StepTranslator:
 
     def __init__(self) -> None:
         self.requests: Dict[str, Any] = {}
+        self.allow_spec = False          # set by the worker when vLLM's speculative method is one it runs
 
     def translate(self, so):
         from ..engine.request import Request
         from ..engine.scheduler import ScheduledSeq, SchedulerOutput
-        if getattr(so, "scheduled_spec_decode_tokens", None):
-            raise NotImplementedError("speculative decoding driven by vLLM's scheduler is not supported by "
-                                      "the B200 worker")
+        spec = getattr(so, "scheduled_spec_decode_tokens", None) or {}
+        if spec and not self.allow_spec:
+            raise NotImplementedError("speculative decoding driven by vLLM's scheduler is supported for the "
+                                      "n-gram method only")
         out = SchedulerOutput()
         for rid in so.finished_req_ids:
             if self.requests.pop(rid, None) is not None:
@@ -152,6 +161,7 @@ class StepTranslator:
                 req.output_token_ids.extend(int(t) for t in extra)
         seqs: List[ScheduledSeq] = []
         all_decode = True
+        has_spec = False
         order = [n.req_id for n in so.scheduled_new_reqs] + list(cached.req_ids)
         for rid in order:
             n = int(so.num_scheduled_tokens.get(rid, 0))
@@ -159,6 +169,15 @@ class StepTranslator:
                 continue
             req = self.requests[rid]
             start = req.num_computed_tokens
+            drafts = [int(t) for t in spec.get(rid, ())]
+            if drafts:
+                # vLLM scheduled the newest token plus its drafts: n = 1 + drafts (fewer when the
+                # token budget cut them short)
+                drafts = drafts[: max(0, n - 1)]
+                n = 1 + len(drafts)
+                seqs.append(ScheduledSeq(req, start, n, True, drafts))
+                has_spec = True
+                continue
             samples = start + n >= req.num_tokens
             seqs.append(ScheduledSeq(req, start, n, samples))
             if not (n == 1 and samples and start > 0):
@@ -166,6 +185,8 @@ class StepTranslator:
         out.seqs = seqs
         out.num_tokens = sum(s.num_new_tokens for s in seqs)
         out.kind = "idle" if not seqs else ("decode" if all_decode else "prefill")
+        if has_spec:
+            out.kind = "spec_decode" if all_decode else "prefill+spec"
         return out
 
     def commit_pending(self, out) -> List[int]:
@@ -196,6 +217,13 @@ class StepTranslator:
         result: List[List[int]] = []
         for seq, tok in zip(out.seqs, tokens):
             req = seq.request
+            if isinstance(tok, (list, tuple)):
+                # a verification step: the accepted drafts and the token that follows them
+                toks = [int(t) for t in tok]
+                req.num_computed_tokens = seq.start + len(toks)
+                req.output_token_ids.extend(toks)
+                result.append(toks)
+                continue
             req.num_computed_tokens = seq.start + seq.num_new_tokens
             if seq.samples:
                 req.output_token_ids.append(int(tok))
@@ -255,6 +283,23 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         self._inflight: Optional[PendingDecodeOutput] = None     # decode step launched ahead of its tokens
         self._stashed = None                                     # output of execute_model, handed out by sample_tokens
         self.async_scheduling = bool(getattr(vllm_config.scheduler_config, "async_scheduling", False))
+        # speculative decoding driven by vLLM's scheduler: the n-gram method runs here (drafts are
+        # looked up on the host after every step and handed to vLLM through take_draft_token_ids;
+        # vLLM schedules them, this worker verifies them in one pass of 1 + k rows per request)
+        self.proposer = None
+        self._drafts = None
+        sc = getattr(vllm_config, "speculative_config", None)
+        if sc is not None:
+            method = str(getattr(sc, "method", "") or "")
+            if method != "ngram":
+                raise NotImplementedError(f"speculative method {method!r} under vLLM's scheduler is not supported by "
+                                          "the B200 worker (n-gram lookup is; the standalone engine also runs the "
+                                          "model's MTP head)")
+            from ..spec_decode.ngram_proposer import NgramProposer
+            self.proposer = NgramProposer(int(sc.num_speculative_tokens),
+                                          int(getattr(sc, "prompt_lookup_min", None) or 2),
+                                          int(getattr(sc, "prompt_lookup_max", None) or 4))
+            self.translator.allow_spec = True
 
     # ---------------------------------------------------------------- set-up
     def init_device(self) -> None:
@@ -396,7 +441,7 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
             self.inner.execute_model(out)                 # retire rows of finished requests
             return EMPTY_MODEL_RUNNER_OUTPUT
         runner = self.model_runner
-        if (self.async_scheduling and out.kind == "decode" and runner.mtp is None
+        if (self.async_scheduling and out.kind == "decode" and runner.mtp is None and self.proposer is None
                 and not any(runner.needs_host_logits(s.request) for s in out.seqs)):
             # vLLM scheduled this step before the previous one's tokens were read: launch it without
             # waiting; token values missing on the host are fed forward on the device
@@ -414,6 +459,10 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         tokens = self._run(out)
         sampled = self.translator.commit(out, tokens)
         req_ids = [s.request.request_id for s in out.seqs]
+        if self.proposer is not None:
+            # drafts for the next step of every request that got a token in this one
+            self._drafts = (req_ids, [self.proposer.propose_one(s.request.all_token_ids) if toks else []
+                                      for s, toks in zip(out.seqs, sampled)])
         self._stashed = ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
                                           sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
                                           pooler_output=[])
@@ -430,6 +479,26 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         decoding sequences through the decode path (CUDA graph, split-KV attention), the prompt
         chunks through the prefill path."""
         from ..engine.scheduler import SchedulerOutput
+        if out.kind == "prefill+spec":
+            # verification rows and prompt chunks in one vLLM step: two launches
+            ver = [i for i, s in enumerate(out.seqs) if s.spec_token_ids or (s.num_new_tokens == 1 and s.samples
+                                                                              and s.start > 0)]
+            pre = [i for i in range(len(out.seqs)) if i not in set(ver)]
+            first = SchedulerOutput(kind="spec_decode", seqs=[out.seqs[i] for i in ver],
+                                    num_tokens=sum(out.seqs[i].num_new_tokens for i in ver),
+                                    preempted=out.preempted, finished_req_ids=out.finished_req_ids,
+                                    step_index=out.step_index)
+            second = SchedulerOutput(kind="prefill", seqs=[out.seqs[i] for i in pre],
+                                     num_tokens=sum(out.seqs[i].num_new_tokens for i in pre),
+                                     step_index=out.step_index)
+            tokens = [0] * len(out.seqs)
+            for idx, part in ((ver, first), (pre, second)):
+                if idx:
+                    for i, t in zip(idx, self.inner.execute_model(part)):
+                        tokens[i] = t
+            self.steps["mixed"] = self.steps.get("mixed", 0) + 1
+            self.steps["spec_decode"] = self.steps.get("spec_decode", 0) + 1
+            return tokens
         if out.kind == "prefill":
             dec = [i for i, s in enumerate(out.seqs) if s.num_new_tokens == 1 and s.samples and s.start > 0]
             if self.MIXED_SPLIT_MIN_DECODES <= len(dec) < len(out.seqs):
@@ -458,7 +527,12 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         return out
 
     def take_draft_token_ids(self):
-        return None
+        """Drafts proposed after the last step, in vLLM's container (None without a proposer)."""
+        drafts, self._drafts = self._drafts, None
+        if drafts is None:
+            return None
+        from vllm.v1.outputs import DraftTokenIds
+        return DraftTokenIds(req_ids=list(drafts[0]), draft_token_ids=[list(d) for d in drafts[1]])
 
     def execute_dummy_batch(self) -> None:
         self.inner.execute_dummy_batch()

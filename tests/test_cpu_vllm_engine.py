@@ -78,3 +78,15 @@ def test_vllm_chunked_prefill_mixed_with_decode_gives_the_same_tokens():
     res = _child("cpu", "1", "4", "24", extra_env={"OMNI_B200_MIXED_SPLIT_MIN": "1"})
     assert res["via_vllm"] == res["standalone"]
     assert res["steps"].get("mixed", 0) > 0
+
+
+def test_vllm_driven_ngram_speculative_decoding_gives_greedy_tokens_in_fewer_steps():
+    """vLLM's scheduler hands out the drafts that this worker's n-gram look-up proposed
+    (``take_draft_token_ids``); the worker verifies 1 + k rows per request in one pass and returns
+    the accepted tokens.  Forty greedy tokens per request arrive in fewer than 39 decode steps and
+    equal plain greedy decoding of the standalone engine."""
+    res = _child("cpu", "1", "4", "64", "ngram")
+    assert res["via_vllm"] == res["standalone"]
+    assert all(len(t) == 40 for t in res["via_vllm"])
+    assert 0 < res["steps"]["spec_decode"] < 39 and res["steps"]["decode"] == 0
+    assert res["async_scheduling"] is False           # vLLM turns it off for n-gram drafts

@@ -18,6 +18,7 @@ def main() -> None:
     tp = int(sys.argv[2]) if len(sys.argv) > 2 else 1
     seqs = int(sys.argv[3]) if len(sys.argv) > 3 else 1
     budget = int(sys.argv[4]) if len(sys.argv) > 4 else 64
+    spec = sys.argv[5] if len(sys.argv) > 5 else ""          # "ngram": vLLM-driven n-gram speculative decoding
     os.environ["OMNI_B200_PLUGIN"] = "cpu" if mode == "cpu" else "1"
     if tp == 1:
         os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
@@ -47,6 +48,14 @@ def main() -> None:
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg["vocab_size"], (32,), generator=g).tolist() for _ in range(4)]
     n_out = 16
+    extra = {}
+    if spec == "ngram":
+        # prompts that repeat themselves, so that the look-up finds drafts, and enough new tokens
+        # for a tiny random model to fall into a loop of its own
+        prompts = [(p[:8] * 4) for p in prompts]
+        n_out = 40
+        extra["speculative_config"] = {"method": "ngram", "num_speculative_tokens": 3,
+                                       "prompt_lookup_max": 3, "prompt_lookup_min": 2}
 
     from vllm import LLM, SamplingParams
     from vllm.platforms import current_platform
@@ -55,7 +64,7 @@ def main() -> None:
     llm = LLM(model=d, load_format=load_format, skip_tokenizer_init=True, dtype=cfg["torch_dtype"],
               max_model_len=256, max_num_seqs=seqs, max_num_batched_tokens=budget, block_size=16,
               enforce_eager=fp32, seed=0, enable_prefix_caching=False, tensor_parallel_size=tp,
-              gpu_memory_utilization=0.3, **({} if fp32 else {"kv_cache_memory_bytes": 1 << 30}))
+              gpu_memory_utilization=0.3, **extra, **({} if fp32 else {"kv_cache_memory_bytes": 1 << 30}))
     vcfg = llm.llm_engine.vllm_config
     outs = llm.generate([{"prompt_token_ids": p} for p in prompts],
                         SamplingParams(max_tokens=n_out, temperature=0.0, ignore_eos=True, detokenize=False),
@@ -68,6 +77,7 @@ def main() -> None:
         info["worker"] = type(worker).__name__
         info["runner"] = type(worker.model_runner).__module__ + "." + type(worker.model_runner).__name__
         info["steps"] = dict(worker.steps)
+        info["num_vllm_steps"] = sum(v for k, v in worker.steps.items() if k in ("prefill", "decode", "spec_decode"))
         info["graphs"] = len(worker.model_runner.graphs)
         if mode != "cpu":
             from omni_npu_b200 import ops
