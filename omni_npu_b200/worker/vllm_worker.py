@@ -470,6 +470,18 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
 
     # a mixed step is split when it carries at least this many decoding sequences
     MIXED_SPLIT_MIN_DECODES = int(os.environ.get("OMNI_B200_MIXED_SPLIT_MIN", "8"))
+    # models whose attention layers take the decoding rows of a mixed step through the decode kernel
+    # (grouped-query attention) run such a step as ONE pass; 0 = always two launches
+    MIXED_ONE_PASS = os.environ.get("OMNI_B200_MIXED_ONE_PASS", "1") != "0"
+
+    def _gqa_only(self) -> bool:
+        if getattr(self, "_gqa_only_cached", None) is None:
+            from ..attention.gqa import GQAAttention
+            from ..attention.mla import MLAAttention
+            mods = list(self.get_model().modules())
+            other = any(isinstance(m, MLAAttention) or type(m).__name__ == "PanguSinkAttention" for m in mods)
+            self._gqa_only_cached = any(type(m) is GQAAttention for m in mods) and not other
+        return self._gqa_only_cached
 
     def _run(self, out) -> List[int]:
         """Run one translated step.  vLLM's chunked prefill schedules prompt chunks together with
@@ -501,6 +513,21 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
             return tokens
         if out.kind == "prefill":
             dec = [i for i, s in enumerate(out.seqs) if s.num_new_tokens == 1 and s.samples and s.start > 0]
+            if self.MIXED_ONE_PASS and 0 < len(dec) < len(out.seqs) and self._gqa_only():
+                # one forward pass over all rows: the decoding sequences first (their rows go through
+                # the decode attention kernel), the prompt chunks behind them; the GEMMs see one batch,
+                # so the weights stream once instead of once per launch
+                pre = [i for i in range(len(out.seqs)) if i not in set(dec)]
+                order = dec + pre
+                one = SchedulerOutput(kind="prefill", seqs=[out.seqs[i] for i in order], num_tokens=out.num_tokens,
+                                      preempted=out.preempted, finished_req_ids=out.finished_req_ids,
+                                      step_index=out.step_index, num_decode_seqs=len(dec))
+                tokens = [0] * len(out.seqs)
+                for i, t in zip(order, self.inner.execute_model(one)):
+                    tokens[i] = t
+                self.steps["mixed"] = self.steps.get("mixed", 0) + 1
+                self.steps["mixed_one_pass"] = self.steps.get("mixed_one_pass", 0) + 1
+                return tokens
             if self.MIXED_SPLIT_MIN_DECODES <= len(dec) < len(out.seqs):
                 pre = [i for i in range(len(out.seqs)) if i not in set(dec)]
                 first = SchedulerOutput(kind="decode", seqs=[out.seqs[i] for i in dec], num_tokens=len(dec),

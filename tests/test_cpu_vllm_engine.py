@@ -71,13 +71,18 @@ def test_vllm_engine_loads_a_safetensors_checkpoint_and_matches_plain_pytorch(tm
 def test_vllm_chunked_prefill_mixed_with_decode_gives_the_same_tokens():
     # 4 running sequences and a 24-token budget: vLLM schedules prompt chunks together with
     # decoding sequences; such steps run as variable-length prefill steps in the runner
+    # (a) as ONE pass: the decoding rows first, through the decode attention, one GEMM over all rows
     res = _child("cpu", "1", "4", "24")
     assert res["via_vllm"] == res["standalone"]
-    assert res["steps"]["prefill"] > 4
-    # the same schedule with mixed steps split into a decode launch and a prefill launch
-    res = _child("cpu", "1", "4", "24", extra_env={"OMNI_B200_MIXED_SPLIT_MIN": "1"})
+    assert res["steps"].get("mixed_one_pass", 0) > 0
+    # (b) as plain variable-length prefill steps
+    res = _child("cpu", "1", "4", "24", extra_env={"OMNI_B200_MIXED_ONE_PASS": "0"})
     assert res["via_vllm"] == res["standalone"]
-    assert res["steps"].get("mixed", 0) > 0
+    assert res["steps"]["prefill"] > 4 and res["steps"].get("mixed", 0) == 0
+    # (c) split into a decode launch and a prefill launch
+    res = _child("cpu", "1", "4", "24", extra_env={"OMNI_B200_MIXED_ONE_PASS": "0", "OMNI_B200_MIXED_SPLIT_MIN": "1"})
+    assert res["via_vllm"] == res["standalone"]
+    assert res["steps"].get("mixed", 0) > 0 and res["steps"].get("mixed_one_pass", 0) == 0
 
 
 def test_vllm_driven_ngram_speculative_decoding_gives_greedy_tokens_in_fewer_steps():
