@@ -372,5 +372,23 @@ def attach_symmetric_memory(group, device: torch.device, half_bytes: Optional[in
         logger.warning("symmetric-memory collectives support up to 8 ranks; using NCCL")
         return None
     hb = half_bytes or int(os.environ.get("OMNI_B200_SYMM_HALF_MB", "80")) << 20
-    group.comm.symm = SymmetricMemory(group, device, hb)
+    # A rank that cannot set its buffers up (no peer access, handle exchange refused) must not leave
+    # the others with peer-memory kernels that wait for it: the ranks agree on the outcome and fall
+    # back to NCCL together.
+    symm, err = None, None
+    try:
+        symm = SymmetricMemory(group, device, hb)
+    except Exception as e:                                # noqa: BLE001 - any set-up failure means NCCL
+        err = e
+    ok = torch.tensor([0 if symm is None else 1], dtype=torch.int32)
+    import torch.distributed as dist
+    if group.cpu_group is not None:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group.cpu_group)
+    if int(ok.item()) == 0:
+        if symm is not None:
+            symm.close()
+        logger.warning("symmetric-memory collectives unavailable on %d ranks (%s); using NCCL",
+                       group.world_size, err if err is not None else "another rank failed to set up")
+        return None
+    group.comm.symm = symm
     return group.comm.symm
