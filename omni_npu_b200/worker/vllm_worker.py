@@ -29,15 +29,16 @@ waiting for the previous step's tokens (they are fed forward on the device, the 
 placeholders) and ``sample_tokens`` returns an ``AsyncModelRunnerOutput`` that the executor
 resolves later; any other kind of step first waits for the tokens in flight.
 
-Speculative decoding driven by vLLM's scheduler: the n-gram method.  The worker looks the drafts
-up on the host after every step and hands them to vLLM (``take_draft_token_ids``), vLLM schedules
+Speculative decoding driven by vLLM's scheduler: the n-gram method and the model's own MTP head.
+The worker makes the drafts (a host look-up after every step, or the runner's MTP head running k
+times as a chain inside the step) and hands them to vLLM (``take_draft_token_ids``), vLLM schedules
 them, the worker verifies 1 + k rows per request in one pass and returns the accepted tokens plus
 the one that follows them (the reference patches vLLM's ``EagleProposer`` for graph-mode drafting:
-omni_npu/vllm_patches/patches/common/patch_eagle.py; the model-based drafters, the MTP head as a
-chain of k steps, run in the standalone engine here).
+omni_npu/vllm_patches/patches/common/patch_eagle.py).
 
-Not supported under vLLM yet (refused with a clear error, never silently wrong): model-based
-speculative methods, structured-output bitmasks, LoRA, pooling and pipeline parallelism.
+Not supported under vLLM yet (refused with a clear error, never silently wrong): separate draft
+models (Eagle heads, draft checkpoints), structured-output bitmasks, LoRA, pooling and pipeline
+parallelism.
 """
 from __future__ import annotations
 
@@ -56,6 +57,10 @@ else:                                                     # importable without v
         def __init__(self, vllm_config, local_rank, rank, distributed_init_method, is_driver_worker=False):
             self.vllm_config, self.local_rank, self.rank = vllm_config, local_rank, rank
             self.distributed_init_method, self.is_driver_worker = distributed_init_method, is_driver_worker
+
+
+# vLLM's names for drafting with the target model's own multi-token-prediction head
+MTP_METHODS = ("mtp", "deepseek_mtp")
 
 
 def engine_config_from_vllm(vllm_config, device_type: str):
@@ -78,6 +83,12 @@ def engine_config_from_vllm(vllm_config, device_type: str):
     load_format = str(getattr(vllm_config.load_config, "load_format", "auto"))
     path = mc_v.model if os.path.isdir(str(mc_v.model)) else None
     ac = dict(getattr(vllm_config, "additional_config", None) or {})
+    spec_kw = {}
+    vsc = getattr(vllm_config, "speculative_config", None)
+    if vsc is not None and str(getattr(vsc, "method", "")) in MTP_METHODS:
+        # the runner builds the model's MTP head and drafts with it inside its own steps
+        spec_kw["speculative_config"] = {"method": "deepseek_mtp",
+                                         "num_speculative_tokens": int(vsc.num_speculative_tokens)}
     cfg = build_engine_config(
         mc, model_path=path, tensor_parallel_size=pc.tensor_parallel_size,
         data_parallel_size=1, enable_expert_parallel=bool(pc.enable_expert_parallel),
@@ -88,7 +99,7 @@ def engine_config_from_vllm(vllm_config, device_type: str):
                             "cudagraph_capture_sizes": sizes},
         load_format="dummy" if load_format == "dummy" or path is None else "auto",
         seed=int(mc_v.seed or 0), device=device_type,
-        enable_sleep_mode=bool(getattr(mc_v, "enable_sleep_mode", False)), additional_config=ac)
+        enable_sleep_mode=bool(getattr(mc_v, "enable_sleep_mode", False)), additional_config=ac, **spec_kw)
     return cfg
 
 
@@ -288,17 +299,21 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         # vLLM schedules them, this worker verifies them in one pass of 1 + k rows per request)
         self.proposer = None
         self._drafts = None
+        self._step_drafts = None
         sc = getattr(vllm_config, "speculative_config", None)
+        self.mtp_drafts = False          # drafts come from the runner's MTP head (its chain of k steps)
         if sc is not None:
             method = str(getattr(sc, "method", "") or "")
-            if method != "ngram":
+            if method == "ngram":
+                from ..spec_decode.ngram_proposer import NgramProposer
+                self.proposer = NgramProposer(int(sc.num_speculative_tokens),
+                                              int(getattr(sc, "prompt_lookup_min", None) or 2),
+                                              int(getattr(sc, "prompt_lookup_max", None) or 4))
+            elif method in MTP_METHODS:
+                self.mtp_drafts = True
+            else:
                 raise NotImplementedError(f"speculative method {method!r} under vLLM's scheduler is not supported by "
-                                          "the B200 worker (n-gram lookup is; the standalone engine also runs the "
-                                          "model's MTP head)")
-            from ..spec_decode.ngram_proposer import NgramProposer
-            self.proposer = NgramProposer(int(sc.num_speculative_tokens),
-                                          int(getattr(sc, "prompt_lookup_min", None) or 2),
-                                          int(getattr(sc, "prompt_lookup_max", None) or 4))
+                                          "the B200 worker (n-gram look-up and the model's MTP head are)")
             self.translator.allow_spec = True
 
     # ---------------------------------------------------------------- set-up
@@ -463,6 +478,10 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
             # drafts for the next step of every request that got a token in this one
             self._drafts = (req_ids, [self.proposer.propose_one(s.request.all_token_ids) if toks else []
                                       for s, toks in zip(out.seqs, sampled)])
+        elif self.mtp_drafts:
+            # the MTP head ran inside the step (on the hidden states of the accepted positions)
+            got = self._step_drafts or [[] for _ in out.seqs]
+            self._drafts = (req_ids, [[int(t) for t in d] if toks else [] for d, toks in zip(got, sampled)])
         self._stashed = ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
                                           sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
                                           pooler_output=[])
@@ -491,6 +510,9 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         decoding sequences through the decode path (CUDA graph, split-KV attention), the prompt
         chunks through the prefill path."""
         from ..engine.scheduler import SchedulerOutput
+        self._step_drafts = None
+        if self.mtp_drafts:
+            return self._run_mtp(out)
         if out.kind == "prefill+spec":
             # verification rows and prompt chunks in one vLLM step: two launches
             ver = [i for i, s in enumerate(out.seqs) if s.spec_token_ids or (s.num_new_tokens == 1 and s.samples
@@ -544,6 +566,43 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
                 return tokens
         self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
         return self.inner.execute_model(out)
+
+    def _run_mtp(self, out) -> List[int]:
+        """A step of a deployment that drafts with the MTP head: verification rows (and decoding rows
+        without drafts) run as one verification pass, prompt chunks as a prefill pass; each pass leaves
+        the head's drafts for its sequences in ``runner.last_drafts``."""
+        from ..engine.scheduler import SchedulerOutput
+        runner = self.model_runner
+        n = len(out.seqs)
+        ver = [i for i, s in enumerate(out.seqs) if s.spec_token_ids]
+        rest = [i for i in range(n) if i not in set(ver)]
+        tokens: List[Any] = [0] * n
+        drafts: List[List[int]] = [[] for _ in range(n)]
+        parts = []
+        if ver:
+            parts.append((ver, SchedulerOutput(kind="spec_decode", seqs=[out.seqs[i] for i in ver],
+                                               num_tokens=sum(out.seqs[i].num_new_tokens for i in ver),
+                                               preempted=out.preempted, finished_req_ids=out.finished_req_ids,
+                                               step_index=out.step_index)))
+        if rest:
+            all_dec = all(out.seqs[i].num_new_tokens == 1 and out.seqs[i].samples and out.seqs[i].start > 0
+                          for i in rest)
+            parts.append((rest, SchedulerOutput(kind="decode" if all_dec else "prefill",
+                                                seqs=[out.seqs[i] for i in rest],
+                                                num_tokens=sum(out.seqs[i].num_new_tokens for i in rest),
+                                                preempted=[] if ver else out.preempted,
+                                                finished_req_ids=[] if ver else out.finished_req_ids,
+                                                step_index=out.step_index)))
+        for idx, part in parts:
+            got = self.inner.execute_model(part)
+            last = list(getattr(runner, "last_drafts", None) or [])
+            for j, i in enumerate(idx):
+                tokens[i] = got[j]
+                if j < len(last):
+                    drafts[i] = list(last[j])
+            self.steps[part.kind] = self.steps.get(part.kind, 0) + 1
+        self._step_drafts = drafts
+        return tokens
 
     def sample_tokens(self, grammar_output=None):
         """Second half of vLLM's two-call step: the forward pass and the sampling both ran in

@@ -95,3 +95,14 @@ def test_vllm_driven_ngram_speculative_decoding_gives_greedy_tokens_in_fewer_ste
     assert all(len(t) == 40 for t in res["via_vllm"])
     assert 0 < res["steps"]["spec_decode"] < 39 and res["steps"]["decode"] == 0
     assert res["async_scheduling"] is False           # vLLM turns it off for n-gram drafts
+
+
+def test_vllm_driven_drafting_with_the_models_mtp_head_gives_greedy_tokens():
+    """``speculative_config={"method": "mtp", "num_speculative_tokens": 2}`` under vLLM: the runner
+    builds the MTP head of a small DeepSeek-V3 shaped model and drafts two tokens per step as a chain,
+    vLLM schedules them, the worker verifies.  With random weights next to nothing is accepted; the
+    tokens must be those of plain greedy decoding."""
+    res = _child("cpu", "1", "4", "64", "mtp")
+    assert res["via_vllm"] == res["standalone"]
+    assert all(len(t) == 24 for t in res["via_vllm"])
+    assert res["steps"]["spec_decode"] > 0 and res["steps"]["decode"] == 0

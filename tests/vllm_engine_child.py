@@ -39,6 +39,19 @@ def main() -> None:
            "rope_theta": 10000.0, "max_position_embeddings": 2048, "hidden_act": "silu",
            "tie_word_embeddings": False, "torch_dtype": "float32" if fp32 else "bfloat16",
            "bos_token_id": 1, "eos_token_id": 2}
+    if spec == "mtp":
+        # a small DeepSeek-V3 shaped model (latent attention, routed + shared experts) with one
+        # multi-token-prediction layer: vLLM schedules the drafts that the runner's MTP head makes
+        cfg = {"architectures": ["DeepseekV3ForCausalLM"], "model_type": "deepseek_v3", "hidden_size": 128,
+               "intermediate_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 4,
+               "vocab_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512,
+               "hidden_act": "silu", "tie_word_embeddings": False, "torch_dtype": "float32" if fp32 else "bfloat16",
+               "bos_token_id": 1, "eos_token_id": 2, "n_routed_experts": 8, "num_experts_per_tok": 2,
+               "moe_intermediate_size": 64, "n_shared_experts": 1, "first_k_dense_replace": 1, "moe_layer_freq": 1,
+               "scoring_func": "sigmoid", "norm_topk_prob": True, "routed_scaling_factor": 1.0, "n_group": 1,
+               "topk_group": 1, "topk_method": "noaux_tc", "kv_lora_rank": 512, "q_lora_rank": None,
+               "qk_nope_head_dim": 32, "qk_rope_head_dim": 64, "v_head_dim": 32, "num_nextn_predict_layers": 1,
+               "attention_bias": False, "rope_scaling": None}
     d = os.environ.get("OMNI_B200_TEST_MODEL_DIR")     # a checkpoint directory (config + safetensors)
     load_format = "auto" if d else "dummy"
     if not d:
@@ -56,6 +69,9 @@ def main() -> None:
         n_out = 40
         extra["speculative_config"] = {"method": "ngram", "num_speculative_tokens": 3,
                                        "prompt_lookup_max": 3, "prompt_lookup_min": 2}
+    if spec == "mtp":
+        n_out = 24
+        extra["speculative_config"] = {"method": "mtp", "num_speculative_tokens": 2}
 
     from vllm import LLM, SamplingParams
     from vllm.platforms import current_platform
@@ -90,7 +106,8 @@ def main() -> None:
         own = OwnLLM(model=ModelConfig.from_hf_dict(cfg), device="cpu" if fp32 else "cuda", max_num_seqs=1,
                      max_num_batched_tokens=64, max_model_len=256, block_size=16, num_gpu_blocks=64, seed=0,
                      enforce_eager=fp32)
-        own.engine.worker.get_model().load_state_dict(state)
+        # the comparison engine decodes plainly: it has no draft head to load
+        own.engine.worker.get_model().load_state_dict({k: v for k, v in state.items() if not k.startswith("mtp.")})
         res = own.generate(prompts, SP(max_tokens=n_out, temperature=0.0, ignore_eos=True))
         info["standalone"] = [o.output_token_ids for o in res]
     info["via_vllm"] = via_vllm
