@@ -32,6 +32,21 @@ def test_vllm_engine_on_gpu_batched_requests_finish():
     assert [t[0] for t in res["via_vllm"]] == [t[0] for t in res["standalone"]]
 
 
+@pytest.mark.parametrize("method,n_out", [("ngram", 40), ("mtp", 24)])
+def test_vllm_driven_speculative_decoding_on_gpu(method, n_out):
+    """vLLM schedules the drafts that this worker makes (n-gram look-up, or the MTP head of a small
+    DeepSeek-V3 shaped model) and the worker verifies them with its own kernels.  Verification rows
+    and plain decode rows are rounded differently in bf16, so the tokens are compared as in the
+    batched test: the same first tokens, most tokens equal."""
+    res = _child("cuda", "1", "4", "64", method, timeout=1200)
+    assert res["worker"] == "B200Worker" and res["launches"] > 100
+    assert res["steps"].get("spec_decode", 0) > 0
+    assert all(len(t) == n_out for t in res["via_vllm"])
+    same = sum(x == y for a, b in zip(res["via_vllm"], res["standalone"]) for x, y in zip(a, b))
+    assert [t[0] for t in res["via_vllm"]] == [t[0] for t in res["standalone"]]
+    assert same >= 0.6 * n_out * len(res["via_vllm"])
+
+
 @pytest.mark.multi_gpu
 def test_vllm_engine_tensor_parallel_two_gpus():
     one = _child("cuda", timeout=1200)

@@ -52,6 +52,13 @@ def main() -> None:
                "topk_group": 1, "topk_method": "noaux_tc", "kv_lora_rank": 512, "q_lora_rank": None,
                "qk_nope_head_dim": 32, "qk_rope_head_dim": 64, "v_head_dim": 32, "num_nextn_predict_layers": 1,
                "attention_bias": False, "rope_scaling": None}
+        if not fp32:
+            # the sizes of the GPU end-to-end tests (head sizes 128 + 64 / 128 that the kernels take)
+            cfg.update({"hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 3,
+                        "num_attention_heads": 16, "num_key_value_heads": 16, "vocab_size": 2048,
+                        "n_routed_experts": 16, "num_experts_per_tok": 4, "moe_intermediate_size": 256,
+                        "n_group": 4, "topk_group": 2, "routed_scaling_factor": 2.5, "q_lora_rank": 256,
+                        "qk_nope_head_dim": 128, "v_head_dim": 128, "max_position_embeddings": 2048})
     d = os.environ.get("OMNI_B200_TEST_MODEL_DIR")     # a checkpoint directory (config + safetensors)
     load_format = "auto" if d else "dummy"
     if not d:
