@@ -181,6 +181,14 @@ PAIR_MIN_M = int(os.environ.get("OMNI_B200_GEMM_PAIR_MIN_M", "1024"))
 SMALL_M_GEMM = os.environ.get("OMNI_B200_SMALL_M_GEMM", "library")
 SMALL_M_LIBRARY_ROWS = (64, 256)
 
+def library_small_m(m: int, cluster_split_plan: bool, plain_bf16: bool) -> bool:
+    """Whether ``gemm`` hands a product to cuBLAS: only a plain bf16 product (nothing fused, no forced
+    tile or split), only when this package's plan for it is a cluster split-K, only for the row
+    counts the comparison was measured on, and only while ``OMNI_B200_SMALL_M_GEMM`` says so."""
+    return (SMALL_M_GEMM == "library" and plain_bf16 and cluster_split_plan
+            and SMALL_M_LIBRARY_ROWS[0] <= m <= SMALL_M_LIBRARY_ROWS[1])
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
          swiglu: bool = False, bn: int = 0, splits: int = 0, max_ctas: int = 0,
@@ -211,9 +219,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         plan = C.gemm_plan(m, n, k, a.dtype.itemsize, swiglu, bn, 1 if swiglu else splits)
         st.plans[key] = plan
     pbn, psplits, ws_bytes, ncnt, cluster = plan
-    if (cluster and SMALL_M_GEMM == "library" and SMALL_M_LIBRARY_ROWS[0] <= m <= SMALL_M_LIBRARY_ROWS[1]
-            and bias is None and residual is None and not swiglu and bn == 0 and splits == 0
-            and a.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)):
+    if library_small_m(m, bool(cluster), bias is None and residual is None and not swiglu and bn == 0
+                       and splits == 0 and a.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)):
         return torch.nn.functional.linear(a, w)          # a library kernel: not counted as a launch of ours
     ws = cnt = None
     if psplits > 1 and not cluster:

@@ -52,3 +52,14 @@ def test_balanced_plan_covers_every_tile_once_and_matches_the_merge(seed):
     for b in range(n_seqs):
         for kvh in range(hk):
             assert _merge_slots(seq_lens, hk, ctas, b, kvh) == written.get((b, kvh))
+
+
+def test_only_plain_decode_sized_cluster_split_products_go_to_the_library(monkeypatch):
+    assert ops.library_small_m(128, True, True)
+    assert ops.library_small_m(64, True, True) and ops.library_small_m(256, True, True)
+    assert not ops.library_small_m(32, True, True)        # small batches keep batch-invariant numerics
+    assert not ops.library_small_m(8192, True, True)      # prefill
+    assert not ops.library_small_m(128, False, True)      # gate_up, LM head: no cluster split-K plan
+    assert not ops.library_small_m(128, True, False)      # bias / residual / SwiGLU / scales / forced tiles
+    monkeypatch.setattr(ops, "SMALL_M_GEMM", "own")
+    assert not ops.library_small_m(128, True, True)
