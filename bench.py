@@ -276,6 +276,9 @@ def run_ours(args) -> None:
                 "l2_policy": "inputs larger than L2: every engine step streams the weights "
                              "(16 GB / N) and the KV cache, far above the 126 MB L2",
                 "engine_steps_per_pass": engine_steps // max(1, args.steps),
+                # which kernels ran the plain decode-sized projections (qkv, o, down): "library" = cuBLAS
+                # (not counted in gpu_launches), "own" = gemm_tcgen05_kernel; everything else is own code
+                "small_m_gemm": ops.SMALL_M_GEMM, "mixed_batches": bool(args.mixed_batches),
             },
             "device_ms_by_step_kind": {k: round(v / args.steps, 1) for k, v in runner.step_ms_by_kind.items()},
             "steps_by_kind": {k: v // args.steps for k, v in runner.step_count_by_kind.items()},
