@@ -67,6 +67,28 @@ class GQAAttention(torch.nn.Module):
         ctx = get_forward_context()
         md: AttentionMetadata = ctx.attn_metadata
         k_cache, v_cache = ctx.kv_caches[self.layer_idx]
+        pc = md.extra.get("pcp") if md.is_prefill else None
+        if pc is not None:
+            # prefill context parallelism: this rank holds the query rows of its token shard; the
+            # keys and values of the whole step are gathered, rotated with their own positions and
+            # written into the local cache, then the shard attends causally over the cache
+            t = q.shape[0]
+            pad = pc["pad"]
+
+            def gathered(x):
+                x = x.contiguous()
+                if t < pad:
+                    x = torch.cat([x, x.new_zeros(pad - t, x.shape[1])])
+                return pc["group"].all_gather(x, dim=0).index_select(0, pc["gather_idx"])
+
+            k_all, v_all = gathered(k), gathered(v)
+            if apply_rope and cos_sin is not None:
+                ops.rope_qk_(q, q.new_empty(t, 0), md.positions, cos_sin, self.head_dim, self.rot_dim, self.neox)
+                ops.rope_qk_(k_all, k_all.new_empty(k_all.shape[0], 0), pc["positions_all"], cos_sin, self.head_dim,
+                             self.rot_dim, self.neox)
+            ops.gqa_cache_write(k_all, v_all, k_cache, v_cache, pc["slot_all"])
+            return ops.gqa_prefill(q, k_cache, v_cache, md.block_tables, md.cu_q, md.seq_lens,
+                                   md.num_seqs, md.max_q_len, self.num_heads, self.scale, True, self.window)
         if apply_rope and cos_sin is not None and md.positions.dim() == 1:
             ops.rope_cache_gqa_(q, k, v, k_cache, v_cache, md.positions, md.slot_mapping, cos_sin,
                                 self.head_dim, self.rot_dim, self.neox)

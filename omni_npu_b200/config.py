@@ -248,6 +248,10 @@ class ParallelConfig:
     data_parallel_size: int = 1
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
+    # prefill context parallelism: the tokens of a prefill step are split over this many ranks (each
+    # with its own tensor-parallel group); every layer gathers the step's keys and values, so all
+    # ranks hold the whole KV cache and decode steps run replicated
+    prefill_context_parallel_size: int = 1
     # keep the residual stream sharded by tokens inside the tensor-parallel group
     # (reduce-scatter / all-gather around every block instead of all-reduce)
     sequence_parallel_residual: bool = False
@@ -260,7 +264,8 @@ class ParallelConfig:
 
     @property
     def world_size(self) -> int:
-        return self.tensor_parallel_size * self.pipeline_parallel_size * self.data_parallel_size
+        return (self.tensor_parallel_size * self.pipeline_parallel_size * self.data_parallel_size
+                * self.prefill_context_parallel_size)
 
 
 @dataclass
@@ -356,6 +361,17 @@ class EngineConfig:
             self.scheduler.max_model_len = self.model.max_position_embeddings
         if self.enforce_eager:
             self.compilation.cudagraph_mode = "NONE"
+        if self.parallel.prefill_context_parallel_size > 1:
+            if self.model.use_mla:
+                raise ValueError("prefill_context_parallel_size > 1 is supported for grouped-query attention "
+                                 "models (the latent-attention prefill does not gather the shards' keys)")
+            if (self.parallel.pipeline_parallel_size > 1 or self.parallel.data_parallel_size > 1
+                    or self.parallel.decode_context_parallel_size > 1 or self.parallel.sequence_parallel_residual):
+                raise ValueError("prefill context parallelism combines with tensor and expert parallelism only")
+            if self.speculative.method and self.speculative.num_speculative_tokens > 0:
+                raise ValueError("speculative decoding is not supported with prefill_context_parallel_size > 1")
+            if self.kv_transfer is not None:
+                raise ValueError("KV transfer connectors are not supported with prefill_context_parallel_size > 1")
         if self.parallel.pipeline_parallel_size > 1:
             # stages exchange (hidden, residual) with point-to-point sends; the draft paths would
             # need the last stage's hidden states on every stage

@@ -368,6 +368,7 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                          data_parallel_size=kw.pop("data_parallel_size", 1),
                          enable_expert_parallel=kw.pop("enable_expert_parallel", False),
                          decode_context_parallel_size=kw.pop("decode_context_parallel_size", 1),
+                         prefill_context_parallel_size=kw.pop("prefill_context_parallel_size", 1),
                          sequence_parallel_residual=kw.pop("sequence_parallel_residual", False),
                          num_redundant_experts=kw.pop("num_redundant_experts", 0),
                          eplb_step_interval=kw.pop("eplb_step_interval", 0),

@@ -84,6 +84,8 @@ class ModelRunner:
         self.kv_connector = None
         pp = pstate.get_pp_group()
         self.pp_group = pp if pp.world_size > 1 else None     # set: this rank runs one pipeline stage
+        pcp = pstate.get_pcp_group()
+        self.pcp_group = pcp if pcp.world_size > 1 else None  # set: prefill steps are split over these ranks
         self.timings: Dict[str, float] = {}
         # optional device-side timing of every step (CUDA events around the kernels)
         self.enable_step_events = False
@@ -251,6 +253,70 @@ class ModelRunner:
                 last = pos.index_select(0, idx) if idx is not None else pos[:num_samples]
                 drafts += self._mtp_chain(h, draft, last, views["bt"][:num_samples], md)
         return torch.stack([tok] + drafts, dim=1)
+
+    def _forward_and_sample_pcp(self, views, seqs, T: int, max_seq: int) -> torch.Tensor:
+        """A prefill step split over the ranks of the prefill-context-parallel group.  The step is
+        staged in full on every rank (all ranks run the same scheduler); this rank runs the model on
+        tokens [lo, hi) of the flat batch.  Each attention layer gathers the step's keys and values
+        from all ranks, writes ALL of them into the local cache and attends with its own query rows
+        (``attention/gqa.py``), so afterwards every rank holds the whole KV cache.  A sequence's
+        next token is sampled by the rank that owns its last row and shared with a max-reduction.
+        (vLLM's prefill context parallelism, which the reference's model patches assume around
+        their MoE block: omni_npu/vllm_patches/patches/models/pangu72b-vl/patch_fusedmoe.py:148-159.)"""
+        if self._logits_fn is not None or self.mtp is not None:
+            raise NotImplementedError("prefill context parallelism: logits processors and draft heads are not supported")
+        g = self.pcp_group
+        P, r = g.world_size, g.rank_in_group
+        dev = self.device
+        self.pcp_steps = getattr(self, "pcp_steps", 0) + 1
+        bounds = [j * T // P for j in range(P + 1)]           # every rank gets at least one token
+        lo, hi = bounds[r], bounds[r + 1]
+        sizes = [bounds[j + 1] - bounds[j] for j in range(P)]
+        pad = max(sizes)
+        # rows of the gathered [P * pad] tensor that hold real tokens, in flat-batch order
+        gather_idx = torch.tensor([j * pad + i for j in range(P) for i in range(sizes[j])], dtype=torch.long,
+                                  device=dev)
+        own_seq, own_q, own_len, cu = [], [], [], [0]
+        owner_of_last, off = [], 0
+        for i, s in enumerate(seqs):
+            cs, ce = off, off + s.num_new_tokens
+            a, b = max(cs, lo), min(ce, hi)
+            if b > a:
+                own_seq.append(i)
+                own_q.append(b - a)
+                own_len.append(s.start + (b - cs))            # keys up to this rank's last row of the sequence
+                cu.append(cu[-1] + (b - a))
+            owner_of_last.append(lo <= ce - 1 < hi)
+            off = ce
+        idx_seq = torch.tensor(own_seq, dtype=torch.long, device=dev)
+        md = AttentionMetadata(
+            is_prefill=True, num_seqs=len(own_seq), num_tokens=hi - lo, max_q_len=max(own_q),
+            max_seq_len=max_seq, q_len=0, positions=views["pos"][lo:hi], slot_mapping=views["slot"][lo:hi],
+            block_tables=views["bt"].index_select(0, idx_seq).contiguous(),
+            seq_lens=torch.tensor(own_len, dtype=torch.int32, device=dev),
+            cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), num_actual_tokens=hi - lo,
+            num_actual_seqs=len(own_seq))
+        md.extra["seq_lens_host"] = own_len
+        md.extra["pcp"] = {"group": g, "pad": pad, "gather_idx": gather_idx, "positions_all": views["pos"][:T],
+                           "slot_all": views["slot"][:T]}
+        n = len(seqs)
+        tokens = torch.full((n,), -1, dtype=torch.int32, device=dev)
+        with set_forward_context(md, self.kv_caches, self.config):
+            hidden = self.model(views["ids"][lo:hi], views["pos"][lo:hi])
+            mine = [i for i in range(n) if owner_of_last[i] and seqs[i].samples]
+            if mine:
+                sel = torch.tensor(mine, dtype=torch.long, device=dev)
+                rows = (views["logits_idx"][:n].long().index_select(0, sel) - lo)
+                logits = self.model.compute_logits(hidden.index_select(0, rows))
+                seeds = views["seeds"][:n].index_select(0, sel)
+                got = self.sampler(logits, views["temp"][:n].index_select(0, sel),
+                                   views["top_k"][:n].index_select(0, sel), views["top_p"][:n].index_select(0, sel),
+                                   seeds, self.step_counter)
+                tokens.index_copy_(0, sel, got.to(torch.int32))
+        # a token id is >= 0 and exactly one rank holds it: the maximum over the group is the token
+        import torch.distributed as dist
+        dist.all_reduce(tokens, op=dist.ReduceOp.MAX, group=g.device_group)
+        return tokens.clamp_(min=0)
 
     def _mtp_chain(self, h: torch.Tensor, draft: torch.Tensor, last_pos: torch.Tensor, bt: torch.Tensor,
                    md: AttentionMetadata) -> List[torch.Tensor]:
@@ -480,6 +546,16 @@ class ModelRunner:
             max_seq = max(s.start + s.num_new_tokens for s in out.seqs)
             md = self._metadata(lay, views, True, n, T, max_q, max_seq, 0, T, n)
             md.extra["seq_lens_host"] = [s.start + s.num_new_tokens for s in out.seqs]
+            if self.pcp_group is not None and T >= 2 * self.pcp_group.world_size:
+                sampled = self._forward_and_sample_pcp(views, out.seqs, T, max_seq)
+                self.step_counter += 1
+                self._event_stop(ev, out.kind)
+                host = self.sampled_host[:n]
+                host.copy_(sampled[:n], non_blocking=True)
+                if self.device.type == "cuda":
+                    torch.cuda.current_stream(self.device).synchronize()
+                self.d2h_bytes_last = n * 4
+                return host.tolist()
             nd = getattr(out, "num_decode_seqs", 0)
             if nd:
                 # mixed batch: the first nd sequences are decoding (one row each); attention layers

@@ -58,7 +58,8 @@ class Worker:
         if not pstate.model_parallel_is_initialized():
             pstate.init_distributed(self.device, init_method=self.distributed_init_method)
             pstate.init_model_parallel(pc.tensor_parallel_size, pc.pipeline_parallel_size,
-                                       pc.data_parallel_size, self.device)
+                                       pc.data_parallel_size, self.device,
+                                       pcp=pc.prefill_context_parallel_size)
             for key, spec in (pc.layer_parallel_config or {}).items():
                 if isinstance(spec, dict) and "tp_size_or_ranks" in spec:
                     pstate.register_layer_group(key, spec["tp_size_or_ranks"])

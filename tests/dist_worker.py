@@ -93,6 +93,9 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     if os.path.exists(os.path.join(workdir, "pipeline_parallel")):
         pp = int(open(os.path.join(workdir, "pipeline_parallel")).read())
         kw.update(pipeline_parallel_size=pp, tensor_parallel_size=world // pp)
+    if os.path.exists(os.path.join(workdir, "prefill_context_parallel")):
+        pcp = int(open(os.path.join(workdir, "prefill_context_parallel")).read() or world)
+        kw.update(prefill_context_parallel_size=pcp, tensor_parallel_size=world // pcp)
     if os.path.exists(os.path.join(workdir, "long_prompts")):
         kw.update(max_num_batched_tokens=256, max_model_len=512)
         from omni_npu_b200.models.llama import LlamaModel
@@ -116,6 +119,7 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     runner._make_logits_fn = real_hook
     kinds = sorted({type(m).__name__ for m in llm.engine.worker.get_model().modules() if "Attention" in type(m).__name__})
     json.dump({"tokens": [o.output_token_ids for o in outs], "attention_modules": kinds,
+               "pcp_steps": getattr(runner, "pcp_steps", 0),
                "first_logits": [l for _, l in sorted(first_logits)]},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":

@@ -65,6 +65,29 @@ def test_sequence_parallel_residual_stream_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
+@pytest.mark.parametrize("world,pcp", [(2, 2), (4, 2)])
+def test_prefill_context_parallel_engine_matches_plain_pytorch(world, pcp):
+    """Prefill steps split over two ranks by tokens (every layer gathers the step's keys and values,
+    each rank attends with its own query rows, the owner of a prompt's last row samples); decode
+    steps replicated.  Prompts are longer than the 64-token step budget, so later chunks attend
+    to keys that earlier steps gathered into the cache; tokens equal the plain PyTorch model."""
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=7)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (21, 70, 7, 50, 3)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "prefill_context_parallel"), "w").write(str(pcp))
+        res = run_ranks("tp_engine", world, d)             # world = pcp x tensor-parallel size
+    for p, toks in zip(prompts, res[0]["tokens"]):
+        assert toks == refm.greedy_generate(weights, cfg, p, 12)
+    for r in res[1:]:
+        assert r["tokens"] == res[0]["tokens"]
+        assert res[0]["pcp_steps"] >= 3 and r["pcp_steps"] == res[0]["pcp_steps"]
+
+
 def test_api_server_loop_replicates_requests_to_the_other_tensor_parallel_rank():
     """Requests reach rank 0 only; its loop broadcasts them (and aborts) before each step and rank 1
     follows step for step: tokens equal the plain PyTorch model, rank 1 ends idle with all blocks free."""

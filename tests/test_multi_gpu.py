@@ -153,6 +153,39 @@ def test_tensor_parallel_engine_two_gpus_matches_one_gpu():
     _assert_first_logits_close(res[0]["first_logits"], want_logits)
 
 
+def test_prefill_context_parallel_engine_two_gpus_matches_one_gpu():
+    """Prefill steps split by tokens over two GPUs (keys and values of the step gathered in every
+    layer, each GPU attends with its own query rows, the owner of a prompt's last row samples),
+    decode steps replicated; prompts longer than the 64-token step budget.  Compared with one GPU:
+    bf16 rounding differs between a 64-row and a 32-row launch, so the first tokens agree exactly
+    and most of the rest."""
+    import reference_llama as refm
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    from test_cpu_plumbing import _save
+    cfg = ModelConfig(hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=64,
+                      intermediate_size=1024, vocab_size=1024, rope_theta=10000.0, max_position_embeddings=2048)
+    weights = refm.make_weights(cfg, seed=6, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (21, 70, 7, 50, 3)]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _save(weights, cfg, os.path.join(d, "model"))
+        cfgj = json.load(open(os.path.join(d, "model", "config.json")))
+        cfgj["torch_dtype"] = "bfloat16"
+        json.dump(cfgj, open(os.path.join(d, "model", "config.json"), "w"))
+        json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
+        open(os.path.join(d, "prefill_context_parallel"), "w").write("2")
+        res = run_ranks("tp_engine", 2, d, device="cuda", timeout=300)
+        one = LLM(model=os.path.join(d, "model"), device="cuda", max_num_seqs=4, max_num_batched_tokens=64,
+                  max_model_len=256, block_size=16, num_gpu_blocks=64)
+        want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+    assert res[0]["tokens"] == res[1]["tokens"]
+    assert res[0]["pcp_steps"] >= 3
+    _nearly_same_tokens(res[0]["tokens"], want, exact_prefix=2, share=0.6)
+
+
 def test_tensor_parallel_prefill_on_token_sharded_stream_matches_one_gpu():
     """A prefill step of 256 tokens on 2 GPUs splits into whole tiles per rank, so the layers run on the
     token-sharded stream with the all-gather / reduce-scatter inside the GEMMs; tokens must match 1 GPU."""
