@@ -352,6 +352,8 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--tensor-parallel-size", type=int, default=1)
     ap.add_argument("--pipeline-parallel-size", type=int, default=1)
+    ap.add_argument("--prefill-context-parallel-size", type=int, default=1,
+                    help="split the tokens of prefill steps over this many ranks (grouped-query attention models)")
     ap.add_argument("--data-parallel-size", type=int, default=1)
     ap.add_argument("--enable-expert-parallel", action="store_true")
     ap.add_argument("--max-num-seqs", type=int, default=128)
@@ -386,6 +388,7 @@ def main(argv=None) -> None:
     args = make_parser().parse_args(argv)
     kw = dict(tensor_parallel_size=args.tensor_parallel_size, data_parallel_size=args.data_parallel_size,
               pipeline_parallel_size=args.pipeline_parallel_size,
+              prefill_context_parallel_size=args.prefill_context_parallel_size,
               enable_expert_parallel=args.enable_expert_parallel, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
               block_size=args.block_size, gpu_memory_utilization=args.gpu_memory_utilization,
