@@ -179,14 +179,20 @@ def task_dp_engine(rank, world, port, workdir, device_kind):
     from omni_npu_b200 import SamplingParams
     from omni_npu_b200.engine.llm import LLM
     prompts = json.load(open(os.path.join(workdir, "prompts.json")))[rank]
-    llm = LLM(model=os.path.join(workdir, "model"), device=device_kind, dtype="float32",
-              data_parallel_size=world, enable_expert_parallel=True, max_num_seqs=4,
-              max_num_batched_tokens=64, max_model_len=256, block_size=16, num_gpu_blocks=64)
+    kw = dict(dtype="float32") if device_kind == "cpu" else {}
+    llm = LLM(model=os.path.join(workdir, "model"), device=device_kind, data_parallel_size=world,
+              enable_expert_parallel=True, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
+              block_size=16, num_gpu_blocks=64, **kw)
     moe = [m for m in llm.engine.worker.get_model().modules() if hasattr(m, "local_experts")]
     outs = llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
     json.dump({"tokens": [o.output_token_ids for o in outs], "local_experts": moe[0].local_experts,
                "dummy_steps": llm.engine.stats.get("dummy_steps", 0), "steps": llm.engine.stats["steps"]},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
+    if device_kind == "cuda":
+        from omni_npu_b200 import ops
+        torch.cuda.synchronize()
+        ops.check_status()
+        state.finish_process(llm.engine)
     state.get_world_group().barrier()
     state.destroy_distributed()
 

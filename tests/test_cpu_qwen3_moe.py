@@ -18,8 +18,10 @@ HF = {"architectures": ["Qwen3MoeForCausalLM"], "model_type": "qwen3_moe", "hidd
       "moe_intermediate_size": 32, "norm_topk_prob": True}
 
 
-def _checkpoint(d: str, seed: int = 0) -> None:
+def _checkpoint(d: str, seed: int = 0, hf: dict = None) -> None:
+    """A random HF-style Qwen3-MoE checkpoint of the shape ``hf`` (default: the small CPU shape)."""
     from safetensors.torch import save_file
+    HF = hf or globals()["HF"]
     g = torch.Generator().manual_seed(seed)
 
     def r(*shape, std=0.05):
@@ -44,7 +46,8 @@ def _checkpoint(d: str, seed: int = 0) -> None:
             w[q + "gate_proj.weight"] = r(HF["moe_intermediate_size"], h, std=0.2)
             w[q + "up_proj.weight"] = r(HF["moe_intermediate_size"], h, std=0.2)
             w[q + "down_proj.weight"] = r(h, HF["moe_intermediate_size"], std=0.2)
-    save_file({k: t.contiguous() for k, t in w.items()}, os.path.join(d, "model.safetensors"))
+    dt = torch.bfloat16 if HF.get("torch_dtype") == "bfloat16" else torch.float32
+    save_file({k: t.to(dt).contiguous() for k, t in w.items()}, os.path.join(d, "model.safetensors"))
     json.dump(HF, open(os.path.join(d, "config.json"), "w"))
 
 

@@ -153,6 +153,38 @@ def test_tensor_parallel_engine_two_gpus_matches_one_gpu():
     _assert_first_logits_close(res[0]["first_logits"], want_logits)
 
 
+def test_data_parallel_replicas_share_the_experts_two_gpus():
+    """Two data-parallel replicas on two GPUs, the experts of a small Qwen3-MoE checkpoint sharded
+    over both (dispatch / combine over peer memory): each replica serves its own prompts, the one
+    with less work keeps the expert exchanges alive with dummy batches, and every request decodes
+    as on one GPU (bf16: the first tokens agree exactly, most of the rest)."""
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.engine.llm import LLM
+    from test_cpu_qwen3_moe import _checkpoint
+    hf = {"architectures": ["Qwen3MoeForCausalLM"], "model_type": "qwen3_moe", "hidden_size": 512,
+          "num_hidden_layers": 2, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128,
+          "intermediate_size": 1024, "vocab_size": 2048, "rms_norm_eps": 1e-6, "rope_theta": 10000.0,
+          "max_position_embeddings": 2048, "torch_dtype": "bfloat16", "num_experts": 16, "num_experts_per_tok": 4,
+          "moe_intermediate_size": 128, "norm_topk_prob": True}
+    g = torch.Generator().manual_seed(3)
+    per_rank = [[torch.randint(0, 2048, (n,), generator=g).tolist() for n in (20, 70, 9)],
+                [torch.randint(0, 2048, (5,), generator=g).tolist()]]
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "model"))
+        _checkpoint(os.path.join(d, "model"), seed=4, hf=hf)
+        json.dump(per_rank, open(os.path.join(d, "prompts.json"), "w"))
+        res = run_ranks("dp_engine", 2, d, device="cuda", timeout=300)
+        one = LLM(model=os.path.join(d, "model"), device="cuda", max_num_seqs=4, max_num_batched_tokens=64,
+                  max_model_len=256, block_size=16, num_gpu_blocks=64)
+        sp = SamplingParams(max_tokens=10, ignore_eos=True)
+        want = [[o.output_token_ids for o in one.generate(per_rank[r], sp)] for r in (0, 1)]
+    for r in (0, 1):
+        _nearly_same_tokens(res[r]["tokens"], want[r], exact_prefix=2, share=0.6)
+    assert res[0]["local_experts"] == 8
+    assert res[0]["dummy_steps"] == 0 and res[1]["dummy_steps"] > 0
+    assert res[0]["steps"] == res[1]["steps"]
+
+
 def test_prefill_context_parallel_engine_two_gpus_matches_one_gpu():
     """Prefill steps split by tokens over two GPUs (keys and values of the step gathered in every
     layer, each GPU attends with its own query rows, the owner of a prompt's last row samples),
