@@ -136,10 +136,24 @@ class MLAAttention(nn.Module):
         n = self.num_heads
         q = self._project_q(hidden).view(t, n, self.qk_dim)
         kv_a = self.kv_a_proj_with_mqa(hidden)
-        # fused: RMSNorm(c_kv), RoPE(k_pe), write [c_kv | k_pe] into the paged cache
-        ops.mla_kv_rmsnorm_rope_cache(kv_a[:, : self.kv_lora_rank], kv_a[:, self.kv_lora_rank:],
-                                      self.kv_a_layernorm.weight, cache, md.positions, md.slot_mapping,
-                                      self.rotary.cos_sin_cache, self.kv_a_layernorm.eps, False)
+        pc = md.extra.get("pcp") if md.is_prefill else None
+        if pc is not None:
+            # prefill context parallelism: this rank holds a token shard of the step; the compressed
+            # keys of the WHOLE step are gathered and written into the local cache with their own
+            # positions, so the prefill below (which reads every key from the cache) sees the tokens
+            # of the other shards that precede its query rows
+            x = kv_a.contiguous()
+            if t < pc["pad"]:
+                x = torch.cat([x, x.new_zeros(pc["pad"] - t, x.shape[1])])
+            kv_all = pc["group"].all_gather(x, dim=0).index_select(0, pc["gather_idx"])
+            ops.mla_kv_rmsnorm_rope_cache(kv_all[:, : self.kv_lora_rank], kv_all[:, self.kv_lora_rank:],
+                                          self.kv_a_layernorm.weight, cache, pc["positions_all"], pc["slot_all"],
+                                          self.rotary.cos_sin_cache, self.kv_a_layernorm.eps, False)
+        else:
+            # fused: RMSNorm(c_kv), RoPE(k_pe), write [c_kv | k_pe] into the paged cache
+            ops.mla_kv_rmsnorm_rope_cache(kv_a[:, : self.kv_lora_rank], kv_a[:, self.kv_lora_rank:],
+                                          self.kv_a_layernorm.weight, cache, md.positions, md.slot_mapping,
+                                          self.rotary.cos_sin_cache, self.kv_a_layernorm.eps, False)
         # RoPE on the rope part of q (k_pe is handled by the cache kernel)
         q_pe = q[:, :, self.nope:].reshape(t, n * self.rope_dim).contiguous()
         dummy_k = q_pe.new_empty(t, 0)

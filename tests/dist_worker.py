@@ -159,12 +159,18 @@ def task_dcp_engine(rank, world, port, workdir, device_kind):
     from omni_npu_b200.engine.llm import LLM
     spec = json.load(open(os.path.join(workdir, "spec.json")))
     cfg = ModelConfig(dtype=torch.float32 if device_kind == "cpu" else torch.bfloat16, **spec["model"])
-    llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world,
-              decode_context_parallel_size=world if spec["dcp"] else 1, **spec["engine"])
+    if spec.get("pcp"):
+        # prefill steps split by tokens over the ranks; experts replicated, so that the weights are
+        # those of a single process
+        llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world // spec["pcp"],
+                  prefill_context_parallel_size=spec["pcp"], enable_expert_parallel=False, **spec["engine"])
+    else:
+        llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world,
+                  decode_context_parallel_size=world if spec["dcp"] else 1, **spec["engine"])
     outs = llm.generate(spec["prompts"], SamplingParams(max_tokens=spec["max_tokens"], ignore_eos=True))
     runner = llm.engine.worker.model_runner
     json.dump({"tokens": [o.output_token_ids for o in outs], "max_blocks": runner.input_batch.max_blocks,
-               "free_blocks": llm.engine.scheduler.pool.num_free},
+               "free_blocks": llm.engine.scheduler.pool.num_free, "pcp_steps": getattr(runner, "pcp_steps", 0)},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":
         state.finish_process(llm.engine)

@@ -239,3 +239,31 @@ def test_decode_context_parallel_engine_matches_plain_tensor_parallel(monkeypatc
     assert all(len(t) == 8 for t in res[1][0]["tokens"])
     assert res[1][0]["max_blocks"] * 2 == res[0][0]["max_blocks"]
     assert res[1][0]["free_blocks"] == 64 and res[1][1]["free_blocks"] == 64
+
+
+def test_prefill_context_parallel_latent_attention_model_matches_one_process(monkeypatch):
+    """A small latent-attention (MLA) + MoE model with its prefill steps split by tokens over two
+    ranks: every layer gathers the step's compressed keys into the local cache, the prefill reads
+    all keys from there.  Tokens equal the single-process engine on the same weights."""
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    model = dict(architecture="DeepseekV2ForCausalLM", model_type="deepseek_v2", hidden_size=128, num_layers=3,
+                 num_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=256, vocab_size=512,
+                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+                 num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
+                 first_k_dense=1, use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=32,
+                 qk_rope_head_dim=64, v_head_dim=32)
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(19)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 70, 5)]
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")
+    with tempfile.TemporaryDirectory() as d:
+        json.dump({"model": model, "engine": engine, "prompts": prompts, "max_tokens": 8, "dcp": 0, "pcp": 2},
+                  open(os.path.join(d, "spec.json"), "w"))
+        res = run_ranks("dcp_engine", 2, d)
+    one = LLM(model=ModelConfig(dtype=torch.float32, **model), device="cpu", **engine)
+    want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+    assert res[0]["tokens"] == want and res[1]["tokens"] == want
+    assert res[0]["pcp_steps"] >= 2 and res[0]["free_blocks"] == 64
