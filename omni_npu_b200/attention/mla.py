@@ -159,7 +159,13 @@ class MLAAttention(nn.Module):
         dummy_k = q_pe.new_empty(t, 0)
         ops.rope_qk_(q_pe, dummy_k, md.positions, self.rotary.cos_sin_cache, self.rope_dim, self.rope_dim, False)
         q_pe = q_pe.view(t, n, self.rope_dim)
-        if md.is_prefill and topk_indices is None:
+        nd = md.extra.get("num_decode_seqs", 0) if md.is_prefill and topk_indices is None else 0
+        if nd and "md_decode" in md.extra:
+            # mixed batch: rows [0, nd) are the single new tokens of decoding sequences: they take the
+            # absorbed latent-space path, the prompt rows behind them the non-absorbed prefill
+            o = torch.cat([self._decode(q[:nd], q_pe[:nd], cache, md.extra["md_decode"], None),
+                           self._prefill(q[nd:], q_pe[nd:], cache, md.extra["md_prefill"])], 0)
+        elif md.is_prefill and topk_indices is None:
             o = self._prefill(q, q_pe, cache, md)
         else:
             o = self._decode(q, q_pe, cache, md, topk_indices)

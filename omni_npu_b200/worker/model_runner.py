@@ -564,6 +564,20 @@ class ModelRunner:
                 md.extra["num_decode_seqs"] = nd
                 md.extra["cu_q_prefill"] = views["cu_q"][nd: n + 1] - nd
                 md.extra["max_q_len_prefill"] = max(s.num_new_tokens for s in out.seqs[nd:])
+                # the two halves as metadata of their own, for attention layers that hand them to
+                # their decode and prefill paths unchanged (latent attention)
+                import dataclasses
+                lens = md.extra["seq_lens_host"]
+                md.extra["md_decode"] = dataclasses.replace(
+                    md, is_prefill=False, num_seqs=nd, num_tokens=nd, max_q_len=1, q_len=1,
+                    positions=views["pos"][:nd], slot_mapping=views["slot"][:nd], block_tables=views["bt"][:nd],
+                    seq_lens=views["seq_lens"][:nd], cu_q=views["cu_q"][: nd + 1], num_actual_tokens=nd,
+                    num_actual_seqs=nd, extra={"seq_lens_host": lens[:nd]})
+                md.extra["md_prefill"] = dataclasses.replace(
+                    md, num_seqs=n - nd, num_tokens=T - nd, max_q_len=md.extra["max_q_len_prefill"],
+                    positions=views["pos"][nd:T], slot_mapping=views["slot"][nd:T], block_tables=views["bt"][nd:n],
+                    seq_lens=views["seq_lens"][nd:n], cu_q=md.extra["cu_q_prefill"], num_actual_tokens=T - nd,
+                    num_actual_seqs=n - nd, extra={"seq_lens_host": lens[nd:]})
             sampled = self._forward_and_sample(views, md, n)
         self.step_counter += 1
         self._event_stop(ev, out.kind)

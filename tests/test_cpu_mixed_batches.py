@@ -71,3 +71,37 @@ def test_scheduler_puts_the_riders_first_and_charges_them_to_the_token_budget():
     sched.update_from_output(out, [13, 21])
     out = sched.schedule()
     assert out.kind == "decode" and out.num_decode_seqs == 0 and len(out.seqs) == 2
+
+
+def test_latent_attention_model_riders_take_the_absorbed_decode_path():
+    """Mixed batches of a small latent-attention (MLA) + MoE model: the riders' rows go through the
+    latent-space decode path, the prompt rows through the non-absorbed prefill; tokens equal the
+    engine with separate steps."""
+    from omni_npu_b200.attention.mla import MLAAttention
+    model = ModelConfig(architecture="DeepseekV2ForCausalLM", model_type="deepseek_v2", hidden_size=128, num_layers=3,
+                        num_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=256, vocab_size=512,
+                        rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+                        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
+                        first_k_dense=1, use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=32,
+                        qk_rope_head_dim=64, v_head_dim=32, dtype=torch.float32)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(1, 512, (n,), generator=g).tolist() for n in (5, 40, 9, 30, 3, 21)]
+    sps = [SamplingParams(max_tokens=m, ignore_eos=True) for m in (6, 9, 12, 3, 10, 2)]
+    outs, calls = {}, {}
+    for mixed in (False, True):
+        llm = LLM(model=model, device="cpu", max_num_seqs=3, max_num_batched_tokens=24, max_model_len=128,
+                  block_size=4, num_gpu_blocks=96, seed=3, enable_mixed_batches=mixed)
+        seen = []
+        real = MLAAttention._decode
+
+        def spy(self, q, q_pe, cache, md, topk, _seen=seen, _real=real):
+            _seen.append((md.is_prefill, q.shape[0]))
+            return _real(self, q, q_pe, cache, md, topk)
+        MLAAttention._decode = spy
+        try:
+            outs[mixed] = [o.output_token_ids for o in llm.generate(prompts, sps)]
+        finally:
+            MLAAttention._decode = real
+        calls[mixed] = llm.engine.stats["steps"]
+    assert outs[True] == outs[False]
+    assert calls[True] < calls[False]
