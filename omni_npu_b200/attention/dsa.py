@@ -87,7 +87,15 @@ class Indexer(nn.Module):
         ops.rope_qk_(q_pe, k_pe, md.positions, self.rotary.cos_sin_cache, self.rope_dim, self.rope_dim, True)
         q = torch.cat([q_pe.view(t, self.n_heads, self.rope_dim), q[:, :, self.rope_dim:]], dim=-1)
         k = torch.cat([k_pe, k[:, self.rope_dim:]], dim=-1).contiguous()
-        ops.paged_scatter_rows(index_cache, k, md.slot_mapping)
+        pc = md.extra.get("pcp") if md.is_prefill else None
+        if pc is not None:
+            # prefill context parallelism: the index keys of the whole step go into the local cache
+            if t < pc["pad"]:
+                k = torch.cat([k, k.new_zeros(pc["pad"] - t, k.shape[1])])
+            ops.paged_scatter_rows(index_cache, pc["group"].all_gather(k, dim=0).index_select(0, pc["gather_idx"]),
+                                   pc["slot_all"])
+        else:
+            ops.paged_scatter_rows(index_cache, k, md.slot_mapping)
         w = self.weights_proj(hidden).float() * (self.n_heads ** -0.5) * self.softmax_scale
         return self._topk(q, w, md, index_cache)
 

@@ -362,9 +362,6 @@ class EngineConfig:
         if self.enforce_eager:
             self.compilation.cudagraph_mode = "NONE"
         if self.parallel.prefill_context_parallel_size > 1:
-            if getattr(self.model, "use_sparse", False) or getattr(self.model, "index_topk", 0):
-                raise ValueError("prefill_context_parallel_size > 1 is not supported for sparse-attention models "
-                                 "(the index keys of the other shards are not gathered)")
             if (self.parallel.pipeline_parallel_size > 1 or self.parallel.data_parallel_size > 1
                     or self.parallel.decode_context_parallel_size > 1 or self.parallel.sequence_parallel_residual):
                 raise ValueError("prefill context parallelism combines with tensor and expert parallelism only")

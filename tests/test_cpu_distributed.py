@@ -241,7 +241,8 @@ def test_decode_context_parallel_engine_matches_plain_tensor_parallel(monkeypatc
     assert res[1][0]["free_blocks"] == 64 and res[1][1]["free_blocks"] == 64
 
 
-def test_prefill_context_parallel_latent_attention_model_matches_one_process(monkeypatch):
+@pytest.mark.parametrize("sparse", [False, True])
+def test_prefill_context_parallel_latent_attention_model_matches_one_process(monkeypatch, sparse):
     """A small latent-attention (MLA) + MoE model with its prefill steps split by tokens over two
     ranks: every layer gathers the step's compressed keys into the local cache, the prefill reads
     all keys from there.  Tokens equal the single-process engine on the same weights."""
@@ -254,6 +255,10 @@ def test_prefill_context_parallel_latent_attention_model_matches_one_process(mon
                  num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
                  first_k_dense=1, use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=32,
                  qk_rope_head_dim=64, v_head_dim=32)
+    if sparse:
+        # keys restricted to the indexer's top 16: the index keys of the step are gathered as well
+        model.update(architecture="DeepseekV32ForCausalLM", model_type="deepseek_v32", index_topk=16,
+                     index_n_heads=4, index_head_dim=64)
     engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
                   num_gpu_blocks=64, seed=5)
     g = torch.Generator().manual_seed(19)
@@ -265,5 +270,12 @@ def test_prefill_context_parallel_latent_attention_model_matches_one_process(mon
         res = run_ranks("dcp_engine", 2, d)
     one = LLM(model=ModelConfig(dtype=torch.float32, **model), device="cpu", **engine)
     want = [o.output_token_ids for o in one.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
-    assert res[0]["tokens"] == want and res[1]["tokens"] == want
+    assert res[0]["tokens"] == res[1]["tokens"]
+    if sparse:
+        # a 32-row and a 64-row product round a row's index key differently in the last bit, and a
+        # top-16 selection over near-equal scores can then differ: the tokens agree up to such a flip
+        for got, ref_toks in zip(res[0]["tokens"], want):
+            assert got[:4] == ref_toks[:4] and sum(a == b for a, b in zip(got, ref_toks)) >= 6
+    else:
+        assert res[0]["tokens"] == want
     assert res[0]["pcp_steps"] >= 2 and res[0]["free_blocks"] == 64
