@@ -46,6 +46,9 @@ class GQABackend:
 class GQAAttention(torch.nn.Module):
     """One layer's attention: RoPE + cache write + paged attention."""
 
+    # gathers the step's keys / values when the step is split over prefill-context-parallel ranks
+    supports_prefill_context_parallel = True
+
     def __init__(self, layer_idx: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  scale: float, rot_dim: int, neox: bool = True, sliding_window: int = 0,
                  head_dim_v: Optional[int] = None) -> None:

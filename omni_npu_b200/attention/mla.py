@@ -65,6 +65,9 @@ def kv_slots_for_sequences(md: AttentionMetadata, block_size: int, total_kv: int
 class MLAAttention(nn.Module):
     """Attention block of a DeepSeek-style layer: projections, cache write, attention, o_proj."""
 
+    # gathers the step's compressed keys when the step is split over prefill-context-parallel ranks
+    supports_prefill_context_parallel = True
+
     def __init__(self, cfg, layer_idx: int, device, prefix: str, quant_factory=None) -> None:
         super().__init__()
         self.layer_idx = layer_idx
@@ -291,6 +294,8 @@ class StaticSinkMLAAttention(MLAAttention):
     update) and of ``StaticSinkMLAAttention`` / ``update_sink_kv``
     (omni_npu/vllm_patches/patches/models/pangu_sink_swa_mla/patch_static_sink_attention.py:257-349,
     patch_mla.py:18-78)."""
+
+    supports_prefill_context_parallel = False     # the sink / window composition reads per-token rows it built itself
 
     def __init__(self, cfg, layer_idx: int, device, prefix: str, quant_factory=None,
                  sink_len: int = 0, sliding_window: int = 0) -> None:

@@ -265,6 +265,14 @@ class ModelRunner:
         their MoE block: omni_npu/vllm_patches/patches/models/pangu72b-vl/patch_fusedmoe.py:148-159.)"""
         if self._logits_fn is not None or self.mtp is not None:
             raise NotImplementedError("prefill context parallelism: logits processors and draft heads are not supported")
+        if getattr(self, "_pcp_checked", None) is None:
+            # every module that writes this step's keys into the cache must gather the other shards'
+            lacking = sorted({type(m).__name__ for m in self.model.modules()
+                              if hasattr(m, "layer_idx") and "Attention" in type(m).__name__
+                              and not getattr(m, "supports_prefill_context_parallel", False)})
+            if lacking:
+                raise NotImplementedError(f"prefill context parallelism is not supported by {', '.join(lacking)}")
+            self._pcp_checked = True
         g = self.pcp_group
         P, r = g.world_size, g.rank_in_group
         dev = self.device
