@@ -75,6 +75,13 @@ def engine_config_from_vllm(vllm_config, device_type: str):
     if pc.pipeline_parallel_size > 1:
         raise ValueError("pipeline parallelism under vLLM is not supported by the B200 worker; "
                          "use the standalone engine (omni_npu_b200.serving.api_server)")
+    if int(getattr(pc, "prefill_context_parallel_size", 1) or 1) > 1 or \
+            int(getattr(pc, "decode_context_parallel_size", 1) or 1) > 1:
+        # vLLM's block manager shards the cache of a context-parallel deployment by tokens; this
+        # package's prefill context parallelism keeps the whole cache on every rank and its decode
+        # context parallelism has its own block arithmetic (engine/scheduler.py)
+        raise ValueError("context parallelism under vLLM is not supported by the B200 worker; "
+                         "use the standalone engine (omni_npu_b200.serving.api_server)")
     comp = vllm_config.compilation_config
     sizes = list(getattr(comp, "cudagraph_capture_sizes", None) or [])
     sizes = [s for s in sizes if s <= sc.max_num_seqs] or None
