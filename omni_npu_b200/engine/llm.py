@@ -129,6 +129,7 @@ class LLMEngine:
         return (self.async_scheduling and self.proposer is None and self.scheduler.kv_connector is None
                 and runner.mtp is None and getattr(self.worker, "ha_agent", None) is None
                 and runner.pp_group is None and self.dp_group is None
+                and not (runner.pcp_group is not None and runner.pcp_decode_split)
                 and not any(runner.needs_host_logits(r) for r in self.scheduler.running))
 
     def _settle(self) -> List[RequestOutput]:

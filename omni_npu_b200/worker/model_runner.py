@@ -86,6 +86,11 @@ class ModelRunner:
         self.pp_group = pp if pp.world_size > 1 else None     # set: this rank runs one pipeline stage
         pcp = pstate.get_pcp_group()
         self.pcp_group = pcp if pcp.world_size > 1 else None  # set: prefill steps are split over these ranks
+        # decode steps of such a deployment: every rank decodes every sequence (default), or each
+        # sequence is decoded by one rank of the group (additional_config["pcp_decode_split"])
+        self.pcp_decode_split = bool((config.additional_config or {}).get("pcp_decode_split", False))
+        self._pcp_owner = {}
+        self.pcp_decode_rows = 0
         self.timings: Dict[str, float] = {}
         # optional device-side timing of every step (CUDA events around the kernels)
         self.enable_step_events = False
@@ -253,6 +258,62 @@ class ModelRunner:
                 last = pos.index_select(0, idx) if idx is not None else pos[:num_samples]
                 drafts += self._mtp_chain(h, draft, last, views["bt"][:num_samples], md)
         return torch.stack([tok] + drafts, dim=1)
+
+    def _decode_split_pcp(self, out: SchedulerOutput, ib, n: int) -> List[int]:
+        """A decode step of a prefill-context-parallel deployment with every sequence decoded by ONE
+        rank of the group.  After its prompt (whose keys every rank holds) a sequence gets an owner,
+        the least loaded rank at that moment (all ranks run the same scheduler on the same inputs, so
+        they agree without talking); only the owner attends to and stores the sequence's new keys.
+        Each rank runs one forward pass per step, a dummy batch when it owns nothing, so that
+        expert-parallel exchanges stay in step; the sampled tokens are gathered over the group."""
+        if self._logits_fn is not None:
+            raise NotImplementedError("prefill context parallelism: logits processors are not supported")
+        g = self.pcp_group
+        P, r = g.world_size, g.rank_in_group
+        rids = [s.request.request_id for s in out.seqs]
+        load = [0] * P
+        for rid in rids:
+            if rid in self._pcp_owner:
+                load[self._pcp_owner[rid]] += 1
+        for rid in rids:
+            if rid not in self._pcp_owner:
+                j = load.index(min(load))
+                self._pcp_owner[rid] = j
+                load[j] += 1
+        self._pcp_owner = {rid: self._pcp_owner[rid] for rid in rids}        # finished requests drop out
+        lists = [[i for i, rid in enumerate(rids) if self._pcp_owner[rid] == j] for j in range(P)]
+        mine, cap = lists[r], max(load)
+        ev = self._event_start()
+        buf = torch.full((cap,), -1, dtype=torch.int32, device=self.device)
+        if mine:
+            m = len(mine)
+            reqs = [out.seqs[i].request for i in mine]
+            padded = self._pad_decode_size(m) if self.graphs else None
+            S = padded or m
+            lay = ib.layout_for(S, S)
+            ib.stage_decode(lay, reqs)
+            ib.upload(lay)
+            if padded is not None:
+                sampled = self.graphs[padded].replay()
+            else:
+                views = ib.views(lay, ib.dev)
+                md = self._metadata(lay, views, False, S, S, 1, self.config.scheduler.max_model_len, 1, m, m)
+                sampled = self._forward_and_sample(views, md, S)
+            buf[:m] = sampled[:m].to(torch.int32)
+            self.pcp_decode_rows += m
+        else:
+            self._dummy_run(1, prefill=False)
+        got = g.all_gather(buf, dim=0).view(P, cap)
+        self.step_counter += 1
+        self._event_stop(ev, out.kind)
+        host = got.cpu() if self.device.type != "cuda" else self._to_host(got)
+        self.d2h_bytes_last = P * cap * 4
+        rows = host.tolist()
+        tokens = [0] * n
+        for j in range(P):
+            for k, i in enumerate(lists[j]):
+                tokens[i] = int(rows[j][k])
+        return tokens
 
     def _forward_and_sample_pcp(self, views, seqs, T: int, max_seq: int) -> torch.Tensor:
         """A prefill step split over the ranks of the prefill-context-parallel group.  The step is
@@ -529,6 +590,8 @@ class ModelRunner:
                 self.last_drafts = [r[-k:] for r in rows]
                 return [r[: r[-k - 1]] for r in rows]
             return [r[: r[-1]] for r in rows]
+        if out.kind == "decode" and self.pcp_group is not None and self.pcp_decode_split:
+            return self._decode_split_pcp(out, ib, n)
         if out.kind == "decode":
             reqs = [s.request for s in out.seqs]
             padded = self._pad_decode_size(n) if self.graphs and self._logits_fn is None else None

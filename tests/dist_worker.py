@@ -96,6 +96,8 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     if os.path.exists(os.path.join(workdir, "prefill_context_parallel")):
         pcp = int(open(os.path.join(workdir, "prefill_context_parallel")).read() or world)
         kw.update(prefill_context_parallel_size=pcp, tensor_parallel_size=world // pcp)
+        if os.path.exists(os.path.join(workdir, "pcp_decode_split")):
+            kw["additional_config"] = dict(kw.get("additional_config") or {}, pcp_decode_split=True)
     if os.path.exists(os.path.join(workdir, "long_prompts")):
         kw.update(max_num_batched_tokens=256, max_model_len=512)
         from omni_npu_b200.models.llama import LlamaModel
@@ -119,7 +121,7 @@ def task_tp_engine(rank, world, port, workdir, device_kind):
     runner._make_logits_fn = real_hook
     kinds = sorted({type(m).__name__ for m in llm.engine.worker.get_model().modules() if "Attention" in type(m).__name__})
     json.dump({"tokens": [o.output_token_ids for o in outs], "attention_modules": kinds,
-               "pcp_steps": getattr(runner, "pcp_steps", 0),
+               "pcp_steps": getattr(runner, "pcp_steps", 0), "pcp_decode_rows": getattr(runner, "pcp_decode_rows", 0),
                "first_logits": [l for _, l in sorted(first_logits)]},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":
@@ -163,14 +165,17 @@ def task_dcp_engine(rank, world, port, workdir, device_kind):
         # prefill steps split by tokens over the ranks; experts replicated, so that the weights are
         # those of a single process
         llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world // spec["pcp"],
-                  prefill_context_parallel_size=spec["pcp"], enable_expert_parallel=False, **spec["engine"])
+                  prefill_context_parallel_size=spec["pcp"], enable_expert_parallel=bool(spec.get("ep", False)),
+                  additional_config={"pcp_decode_split": bool(spec.get("pcp_decode_split", False))},
+                  **spec["engine"])
     else:
         llm = LLM(model=cfg, device=device_kind, tensor_parallel_size=world,
                   decode_context_parallel_size=world if spec["dcp"] else 1, **spec["engine"])
     outs = llm.generate(spec["prompts"], SamplingParams(max_tokens=spec["max_tokens"], ignore_eos=True))
     runner = llm.engine.worker.model_runner
     json.dump({"tokens": [o.output_token_ids for o in outs], "max_blocks": runner.input_batch.max_blocks,
-               "free_blocks": llm.engine.scheduler.pool.num_free, "pcp_steps": getattr(runner, "pcp_steps", 0)},
+               "free_blocks": llm.engine.scheduler.pool.num_free, "pcp_steps": getattr(runner, "pcp_steps", 0),
+               "pcp_decode_rows": getattr(runner, "pcp_decode_rows", 0)},
               open(os.path.join(workdir, f"result_{rank}.json"), "w"))
     if device_kind == "cuda":
         state.finish_process(llm.engine)

@@ -65,8 +65,8 @@ def test_sequence_parallel_residual_stream_matches_plain_pytorch():
     assert res[0]["tokens"] == res[1]["tokens"]
 
 
-@pytest.mark.parametrize("world,pcp", [(2, 2), (4, 2)])
-def test_prefill_context_parallel_engine_matches_plain_pytorch(world, pcp):
+@pytest.mark.parametrize("world,pcp,split", [(2, 2, False), (4, 2, False), (2, 2, True)])
+def test_prefill_context_parallel_engine_matches_plain_pytorch(world, pcp, split):
     """Prefill steps split over two ranks by tokens (every layer gathers the step's keys and values,
     each rank attends with its own query rows, the owner of a prompt's last row samples); decode
     steps replicated.  Prompts are longer than the 64-token step budget, so later chunks attend
@@ -80,12 +80,20 @@ def test_prefill_context_parallel_engine_matches_plain_pytorch(world, pcp):
         _save(weights, cfg, os.path.join(d, "model"))
         json.dump(prompts, open(os.path.join(d, "prompts.json"), "w"))
         open(os.path.join(d, "prefill_context_parallel"), "w").write(str(pcp))
+        if split:
+            # decode steps: every sequence decoded by ONE rank of the group, tokens gathered
+            open(os.path.join(d, "pcp_decode_split"), "w").close()
         res = run_ranks("tp_engine", world, d)             # world = pcp x tensor-parallel size
     for p, toks in zip(prompts, res[0]["tokens"]):
         assert toks == refm.greedy_generate(weights, cfg, p, 12)
     for r in res[1:]:
         assert r["tokens"] == res[0]["tokens"]
         assert res[0]["pcp_steps"] >= 3 and r["pcp_steps"] == res[0]["pcp_steps"]
+    if split:
+        rows = [r["pcp_decode_rows"] for r in res]
+        assert sum(rows) == 5 * 11 and all(0 < x < 5 * 11 for x in rows)     # 5 requests x 11 decode steps, shared out
+    else:
+        assert all(r["pcp_decode_rows"] == 0 for r in res)
 
 
 def test_api_server_loop_replicates_requests_to_the_other_tensor_parallel_rank():
@@ -279,3 +287,32 @@ def test_prefill_context_parallel_latent_attention_model_matches_one_process(mon
     else:
         assert res[0]["tokens"] == want
     assert res[0]["pcp_steps"] >= 2 and res[0]["free_blocks"] == 64
+
+
+def test_decode_split_over_the_prefill_context_parallel_ranks_with_sharded_experts(monkeypatch):
+    """A small MLA + MoE model, experts sharded over the two pcp ranks: with every sequence decoded
+    by one rank (a lone request leaves the other rank with dummy batches that keep the expert
+    exchanges in step) the tokens are those of the same deployment decoding replicated."""
+    model = dict(architecture="DeepseekV2ForCausalLM", model_type="deepseek_v2", hidden_size=128, num_layers=3,
+                 num_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=256, vocab_size=512,
+                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, rope_neox=False,
+                 num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, num_shared_experts=1,
+                 first_k_dense=1, use_mla=True, q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=32,
+                 qk_rope_head_dim=64, v_head_dim=32)
+    engine = dict(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=16,
+                  num_gpu_blocks=64, seed=5)
+    g = torch.Generator().manual_seed(23)
+    monkeypatch.setenv("OMNI_B200_INIT_BY_NAME", "1")
+    for lens in ((21, 70, 5), (33,)):
+        prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in lens]
+        res = {}
+        for split in (False, True):
+            with tempfile.TemporaryDirectory() as d:
+                json.dump({"model": model, "engine": engine, "prompts": prompts, "max_tokens": 8, "dcp": 0, "pcp": 2,
+                           "ep": True, "pcp_decode_split": split}, open(os.path.join(d, "spec.json"), "w"))
+                res[split] = run_ranks("dcp_engine", 2, d)
+        assert res[True][0]["tokens"] == res[False][0]["tokens"] == res[True][1]["tokens"]
+        rows = [r["pcp_decode_rows"] for r in res[True]]
+        assert sum(rows) == 7 * len(lens)                       # one owner per sequence and decode step
+        if len(lens) == 1:
+            assert sorted(rows) == [0, 7]                       # the other rank ran dummy batches only
