@@ -363,7 +363,8 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                           SchedulerConfig, SpeculativeConfig)
     cache = CacheConfig(block_size=kw.pop("block_size", 16),
                         gpu_memory_utilization=kw.pop("gpu_memory_utilization", 0.9),
-                        num_gpu_blocks=kw.pop("num_gpu_blocks", None))
+                        num_gpu_blocks=kw.pop("num_gpu_blocks", None),
+                        enable_prefix_caching=kw.pop("enable_prefix_caching", False))
     par = ParallelConfig(tensor_parallel_size=kw.pop("tensor_parallel_size", 1),
                          pipeline_parallel_size=kw.pop("pipeline_parallel_size", 1),
                          data_parallel_size=kw.pop("data_parallel_size", 1),

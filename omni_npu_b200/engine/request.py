@@ -51,7 +51,8 @@ class Request:
     __slots__ = ("request_id", "prompt_token_ids", "sampling_params", "output_token_ids", "status",
                  "block_ids", "num_computed_tokens", "arrival_time", "first_token_time",
                  "finish_time", "kv_transfer_params", "eos_token_id", "num_preemptions",
-                 "spec_token_ids", "client_index", "num_external_tokens")
+                 "spec_token_ids", "client_index", "num_external_tokens", "_block_hashes",
+                 "_registered_blocks")
 
     def __init__(self, request_id: str, prompt_token_ids: Sequence[int],
                  sampling_params: Optional[SamplingParams] = None,
@@ -73,6 +74,10 @@ class Request:
         self.spec_token_ids: List[int] = []
         self.client_index = 0
         self.num_external_tokens = 0
+        # prefix caching: content hashes of the full blocks hashed so far, and how many of this
+        # request's blocks are registered with the pool under their hash
+        self._block_hashes: Optional[List[bytes]] = None
+        self._registered_blocks = 0
 
     @property
     def num_prompt_tokens(self) -> int:

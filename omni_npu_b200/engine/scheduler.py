@@ -55,7 +55,12 @@ class Scheduler:
         # With decode context parallelism every rank stores 1 / world of a sequence's tokens
         # (token p on rank p % world), so one block id covers block_size * world tokens.
         self.block_size = cache_cfg.block_size * max(1, context_parallel_size)
-        self.pool = BlockPool(num_blocks, self.block_size, num_reserved_blocks)
+        # automatic prefix caching: full blocks are findable by the hash of their token prefix and
+        # shared between requests (not together with a KV connector, whose blocks are pulled by id)
+        self.pool = BlockPool(num_blocks, self.block_size, num_reserved_blocks,
+                              prefix_caching=bool(getattr(cache_cfg, "enable_prefix_caching", False))
+                              and kv_connector is None)
+        self.prefix_stats = {"requests": 0, "hit_tokens": 0}
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.requests: Dict[str, Request] = {}
@@ -110,6 +115,52 @@ class Scheduler:
         req.block_ids.extend(self.pool.allocate(need))
         return True
 
+    # ------------------------------------------------------------ prefix caching
+    def _attach_cached_prefix(self, req: Request) -> bool:
+        """Give a request that starts from nothing the cached blocks of its longest known prefix
+        (whole blocks, and never the whole sequence: the last token is always computed)."""
+        from .block_manager import chain_block_hashes
+        bs = self.block_size
+        usable = (req.num_tokens - 1) // bs
+        if usable <= 0:
+            return False
+        toks = req.all_token_ids
+        req._block_hashes = chain_block_hashes(toks, bs, getattr(req, "_block_hashes", None), upto_blocks=usable)
+        hit = self.pool.match_prefix(req._block_hashes[:usable])
+        self.prefix_stats["requests"] += 1
+        if not hit:
+            return False
+        self.pool.acquire(hit)
+        req.block_ids = list(hit)
+        req.num_computed_tokens = len(hit) * bs
+        req._registered_blocks = len(hit)
+        self.prefix_stats["hit_tokens"] += len(hit) * bs
+        return True
+
+    def _detach_cached_prefix(self, req: Request) -> None:
+        self.prefix_stats["hit_tokens"] -= len(req.block_ids) * self.block_size
+        self.pool.free(req.block_ids)
+        req.block_ids = []
+        req.num_computed_tokens = 0
+        req._registered_blocks = 0
+
+    def _register_full_blocks(self, req: Request) -> None:
+        """Make the blocks that this request has filled with settled tokens findable by content."""
+        if not self.pool.prefix_caching:
+            return
+        bs = self.block_size
+        nfull = min(req.num_computed_tokens, req.num_tokens) // bs
+        done = getattr(req, "_registered_blocks", 0)
+        if nfull <= done or nfull > len(req.block_ids):
+            return
+        from .block_manager import chain_block_hashes
+        hashes = chain_block_hashes(req.all_token_ids, bs, getattr(req, "_block_hashes", None), upto_blocks=nfull)
+        req._block_hashes = hashes
+        upto = min(len(hashes), nfull)
+        for i in range(done, upto):
+            self.pool.register(req.block_ids[i], hashes[i])
+        req._registered_blocks = max(done, upto)
+
     def prompt_work_waiting(self) -> bool:
         """Whether this step could hold prompt tokens: a running request with an unfinished prompt
         (or recompute), or a waiting request and a free sequence slot."""
@@ -141,6 +192,7 @@ class Scheduler:
             self.pool.free(victim.block_ids)
             victim.block_ids = []
             victim.num_computed_tokens = 0
+            victim._registered_blocks = 0
             victim.status = RequestStatus.PREEMPTED
             victim.num_preemptions += 1
             self.waiting.appendleft(victim)
@@ -155,6 +207,7 @@ class Scheduler:
         self.pool.free(req.block_ids)
         req.block_ids = []
         req.num_computed_tokens = 0
+        req._registered_blocks = 0
         req.spec_token_ids = []
         req.status = RequestStatus.PREEMPTED
         req.num_preemptions += 1
@@ -267,15 +320,17 @@ class Scheduler:
             if req.num_external_tokens and req.num_computed_tokens == 0:
                 # remote KV covers the prompt except (at least) its last token
                 req.num_computed_tokens = min(req.num_external_tokens, req.num_tokens - 1)
+            attached = (self.pool.prefix_caching and req.num_computed_tokens == 0 and not req.block_ids
+                        and self._attach_cached_prefix(req))
             remaining = req.num_tokens - req.num_computed_tokens
             n = min(remaining, budget)
-            if n < remaining and not self.cfg.enable_chunked_prefill:
-                break
             # admit only when the whole prompt would fit now: a prompt admitted chunk by chunk into
             # a nearly full cache is evicted half-way and recomputed over and over
-            if not self.pool.can_allocate(self.pool.blocks_needed(req.num_tokens, len(req.block_ids))):
-                break
-            if not self._ensure_blocks(req, req.num_computed_tokens + n):
+            if ((n < remaining and not self.cfg.enable_chunked_prefill)
+                    or not self.pool.can_allocate(self.pool.blocks_needed(req.num_tokens, len(req.block_ids)))
+                    or not self._ensure_blocks(req, req.num_computed_tokens + n)):
+                if attached:
+                    self._detach_cached_prefix(req)
                 break
             self.waiting.popleft()
             req.status = RequestStatus.RUNNING
@@ -337,6 +392,7 @@ class Scheduler:
             req = seq.request
             req.num_computed_tokens = seq.start + seq.num_new_tokens
             req.spec_token_ids = []
+            self._register_full_blocks(req)
             req.append_output(self.PENDING_TOKEN, now)
             out.pending_pos.append(len(req.output_token_ids) - 1)
             if len(req.output_token_ids) >= req.sampling_params.max_tokens or req.num_tokens >= self.cfg.max_model_len:
@@ -408,6 +464,7 @@ class Scheduler:
             else:
                 req.num_computed_tokens = seq.start + seq.num_new_tokens
             req.spec_token_ids = []
+            self._register_full_blocks(req)
             if not seq.samples:
                 continue
             done = False

@@ -363,6 +363,8 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
+    ap.add_argument("--enable-prefix-caching", action="store_true",
+                    help="reuse the KV blocks of a cached token prefix for new requests")
     ap.add_argument("--enable-mixed-batches", action="store_true",
                     help="decoding requests ride along in the prefill steps of other requests")
     ap.add_argument("--compilation-config", type=json.loads, default=None)
@@ -394,6 +396,7 @@ def main(argv=None) -> None:
               block_size=args.block_size, gpu_memory_utilization=args.gpu_memory_utilization,
               enforce_eager=args.enforce_eager, enable_chunked_prefill=args.enable_chunked_prefill,
               enable_mixed_batches=args.enable_mixed_batches,
+              enable_prefix_caching=args.enable_prefix_caching,
               compilation_config=args.compilation_config, kv_transfer_config=args.kv_transfer_config,
               speculative_config=args.speculative_config, additional_config=args.additional_config,
               load_format=args.load_format, seed=args.seed)
