@@ -93,13 +93,15 @@ class LLMEngine:
         """Refuse (ValueError) what the sampler cannot honour rather than ignore it."""
         if sp is None:
             return
-        if sp.logprobs:
-            raise ValueError("logprobs are not supported by this engine")
         runner = self.worker.model_runner
         speculative = self.proposer is not None or runner.mtp is not None
-        if speculative and (sp.has_penalties or sp.thinking_token_budget is not None):
-            raise ValueError("penalties and thinking_token_budget are not supported together with "
+        if speculative and (sp.has_penalties or sp.thinking_token_budget is not None or sp.logprobs):
+            raise ValueError("penalties, thinking_token_budget and logprobs are not supported together with "
                              "speculative decoding")
+        if sp.logprobs and (int(sp.logprobs) < 0 or int(sp.logprobs) > 20):
+            raise ValueError("logprobs must be between 0 and 20")
+        if sp.logprobs and (runner.pcp_group is not None or self.dp_group is not None):
+            raise ValueError("logprobs are not supported with prefill-context or data parallelism")
         if sp.thinking_token_budget is not None and not runner.thinking_processor.enabled:
             raise ValueError("thinking_token_budget needs a reasoning config with think start / end "
                              "token ids (additional_config['reasoning_config'], --reasoning-config)")
@@ -226,6 +228,8 @@ class LLMEngine:
             drafts = self._propose(out, tokens)
         before = sum(len(s.request.output_token_ids) for s in out.seqs)
         finished = self.scheduler.update_from_output(out, tokens, drafts=drafts)
+        for idx, entry in (getattr(self.worker.model_runner, "last_logprobs", None) or {}).items():
+            out.seqs[idx].request.logprobs.append(entry)
         st = self.stats
         st["steps"] += 1
         st[out.kind + "_steps"] += 1

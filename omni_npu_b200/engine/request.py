@@ -4,7 +4,7 @@ from __future__ import annotations
 import enum
 import time
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 
 @dataclass
@@ -52,7 +52,7 @@ class Request:
                  "block_ids", "num_computed_tokens", "arrival_time", "first_token_time",
                  "finish_time", "kv_transfer_params", "eos_token_id", "num_preemptions",
                  "spec_token_ids", "client_index", "num_external_tokens", "_block_hashes",
-                 "_registered_blocks")
+                 "_registered_blocks", "logprobs")
 
     def __init__(self, request_id: str, prompt_token_ids: Sequence[int],
                  sampling_params: Optional[SamplingParams] = None,
@@ -78,6 +78,9 @@ class Request:
         # request's blocks are registered with the pool under their hash
         self._block_hashes: Optional[List[bytes]] = None
         self._registered_blocks = 0
+        # one entry per output token when sampling_params.logprobs is set:
+        # (log-probability of the token, [(token id, log-probability), ...] of the most likely tokens)
+        self.logprobs: List[Tuple[float, List[Tuple[int, float]]]] = []
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -130,6 +133,7 @@ class RequestOutput:
     ttft: Optional[float] = None           # seconds from arrival to first token
     tpot: Optional[float] = None           # mean seconds per output token after the first
     kv_transfer_params: Optional[Dict[str, Any]] = None
+    logprobs: Optional[List[Tuple[float, List[Tuple[int, float]]]]] = None    # per output token, when asked for
 
     @classmethod
     def from_request(cls, r: Request) -> "RequestOutput":
@@ -145,4 +149,5 @@ class RequestOutput:
         if r.finish_time is not None and r.first_token_time is not None and len(r.output_token_ids) > 1:
             tpot = (r.finish_time - r.first_token_time) / (len(r.output_token_ids) - 1)
         return cls(r.request_id, list(r.prompt_token_ids), list(r.output_token_ids), r.is_finished,
-                   reason, ttft, tpot, r.kv_transfer_params)
+                   reason, ttft, tpot, r.kv_transfer_params,
+                   list(r.logprobs[: len(r.output_token_ids)]) if r.sampling_params.logprobs else None)

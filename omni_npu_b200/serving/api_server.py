@@ -192,6 +192,17 @@ class EngineLoop:
             self.thread.join(timeout=5)
 
 
+def _logprobs_from_body(body: Dict[str, Any]) -> Optional[int]:
+    """Completions: ``logprobs: n``.  Chat: ``logprobs: true`` with ``top_logprobs: n`` (n = 0: the
+    sampled token's log-probability only, asked for as 1 alternative here)."""
+    lp, top = body.get("logprobs"), body.get("top_logprobs")
+    if lp is True:
+        return max(1, int(top or 0))
+    if lp in (None, False) and not top:
+        return None
+    return max(1, int(top if top else lp))
+
+
 def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
     stop_ids = body.get("stop_token_ids") or ()
     return SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
@@ -203,7 +214,7 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           frequency_penalty=float(body.get("frequency_penalty") or 0.0),
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
                           thinking_token_budget=body.get("thinking_token_budget"),
-                          logprobs=body.get("logprobs") or body.get("top_logprobs") or None)
+                          logprobs=_logprobs_from_body(body))
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):
@@ -303,10 +314,17 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                         "choices": [{"index": 0, "text": decode(toks), "token_ids": toks, "finish_reason": finish}]}
             return StreamingResponse(_stream(rid, chunk), media_type="text/event-stream")
         out = await _finish(rid)
+        lp = None
+        if out.logprobs is not None:
+            # the completions form: parallel lists over the output tokens
+            lp = {"tokens": [decode([t]) if tokenizer is not None else str(t) for t in out.output_token_ids],
+                  "token_ids": out.output_token_ids, "token_logprobs": [e[0] for e in out.logprobs],
+                  "top_logprobs": [{(decode([i]) if tokenizer is not None else str(i)): v for i, v in e[1]}
+                                   for e in out.logprobs]}
         return JSONResponse({
             "id": rid, "object": "text_completion", "created": created, "model": model_name,
             "choices": [{"index": 0, "text": decode(out.output_token_ids), "token_ids": out.output_token_ids,
-                         "finish_reason": out.finish_reason or "stop"}],
+                         "logprobs": lp, "finish_reason": out.finish_reason or "stop"}],
             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
                       "total_tokens": len(ids) + len(out.output_token_ids)},
             "kv_transfer_params": out.kv_transfer_params})
@@ -336,7 +354,13 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                 message["content"] = info.content
         return JSONResponse({
             "id": rid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
-            "choices": [{"index": 0, "message": message, "finish_reason": out.finish_reason or "stop"}],
+            "choices": [{"index": 0, "message": message, "finish_reason": out.finish_reason or "stop",
+                         # the chat form: one entry per output token with its alternatives
+                         "logprobs": None if out.logprobs is None else {"content": [
+                             {"token": decode([t]) if tokenizer is not None else str(t), "token_id": t, "logprob": e[0],
+                              "top_logprobs": [{"token": decode([i]) if tokenizer is not None else str(i),
+                                                "token_id": i, "logprob": v} for i, v in e[1]]}
+                             for t, e in zip(out.output_token_ids, out.logprobs)]}}],
             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
                       "total_tokens": len(ids) + len(out.output_token_ids)}})
 

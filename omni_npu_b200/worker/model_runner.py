@@ -79,6 +79,8 @@ class ModelRunner:
         self.thinking_processor = ThinkingTokenBudgetLogitsProcessor(rc, sc.max_num_seqs, device)
         self.mtp = None                       # the model's multi-token-prediction head, if it drafts
         self.last_drafts: List[List[int]] = []
+        self.last_logprobs: Dict[int, Tuple[float, List[Tuple[int, float]]]] = {}   # of the last step, by index in its seqs
+        self._lp_capture = None
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
         self.d2h_bytes_last = 0
         self.kv_connector = None
@@ -475,7 +477,7 @@ class ModelRunner:
     def needs_host_logits(req) -> bool:
         """Whether sampling for this request needs its token history (penalties, thinking budget)."""
         sp = req.sampling_params
-        return sp.has_penalties or sp.thinking_token_budget is not None
+        return sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
 
     def _penalty_cache(self, vocab: int):
         """The device-resident penalty state (created on first use: most workloads never ask)."""
@@ -500,7 +502,11 @@ class ModelRunner:
         tp = self.thinking_processor
         think_rows = [i for i, s in enumerate(seqs) if s.samples and tp.enabled
                       and s.request.sampling_params.thinking_token_budget is not None]
-        if not pen_rows and not think_rows:
+        # log-probabilities: of the model's own distribution (before penalties, temperature and
+        # truncation), for the sampled token and the most likely tokens
+        lp_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.logprobs]
+        self._lp_capture = None
+        if not pen_rows and not think_rows and not lp_rows:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -511,6 +517,9 @@ class ModelRunner:
         def fn(logits: torch.Tensor) -> torch.Tensor:
             logits = logits.float()
             V = logits.shape[-1]
+            if lp_rows:
+                self._lp_capture = (lp_rows, torch.log_softmax(
+                    logits.index_select(0, torch.tensor(lp_rows, device=dev)), dim=-1))
             if pen_rows:
                 # per-request prompt mask and occurrence counts live on the device from admission
                 # to completion; a step adds only the tokens generated since the last one
@@ -539,6 +548,20 @@ class ModelRunner:
             return logits
         return fn
 
+    def _collect_logprobs(self, seqs, tokens) -> Dict[int, Tuple[float, List[Tuple[int, float]]]]:
+        """Log-probabilities of this step's sampled tokens for the sequences that asked:
+        {index in seqs: (log-probability of the token, [(token id, log-probability)] of the top k)}."""
+        cap, self._lp_capture = getattr(self, "_lp_capture", None), None
+        if cap is None:
+            return {}
+        rows, logp = cap
+        ks = [min(20, int(seqs[i].request.sampling_params.logprobs)) for i in rows]
+        top_v, top_i = logp.topk(max(ks), dim=-1)
+        tok = torch.tensor([int(tokens[i]) for i in rows], device=logp.device).unsqueeze(1)
+        picked = logp.gather(1, tok).squeeze(1)
+        top_v, top_i, picked = top_v.cpu().tolist(), top_i.cpu().tolist(), picked.cpu().tolist()
+        return {i: (picked[j], list(zip(top_i[j][: ks[j]], top_v[j][: ks[j]]))) for j, i in enumerate(rows)}
+
     def _pad_decode_size(self, n: int) -> Optional[int]:
         for s in self.capture_sizes:
             if s >= n:
@@ -563,6 +586,7 @@ class ModelRunner:
             return []
         n = len(out.seqs)
         ev = None
+        self.last_logprobs = {}
         self._logits_fn = self._make_logits_fn(out.seqs) if out.kind != "spec_decode" else None
         try:
             return self._execute_scheduled(out, ib, n, ev)
@@ -669,6 +693,7 @@ class ModelRunner:
                 torch.cuda.current_stream(self.device).synchronize()
             self.d2h_bytes_last = n * 4
             tokens = host.tolist()
+        self.last_logprobs = self._collect_logprobs(out.seqs, tokens)
         if self.kv_connector is not None:
             self.kv_connector.wait_for_save()
         return tokens

@@ -43,6 +43,29 @@ def test_completions_and_metrics(client):
     assert "omni_b200_requests_finished_total" in m and "omni_b200_output_tokens_total" in m
 
 
+def test_completions_and_chat_return_log_probabilities(client):
+    r = client.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 6, "ignore_eos": True, "logprobs": 2})
+    assert r.status_code == 200
+    ch = r.json()["choices"][0]
+    assert ch["token_ids"] == client.expected
+    lp = ch["logprobs"]
+    assert lp["token_ids"] == client.expected and len(lp["token_logprobs"]) == 6 and len(lp["top_logprobs"]) == 6
+    assert all(v <= 0 for v in lp["token_logprobs"]) and all(len(t) == 2 for t in lp["top_logprobs"])
+    # greedy: the sampled token is the first alternative
+    assert all(str(t) in top and abs(top[str(t)] - v) < 1e-6
+               for t, v, top in zip(lp["token_ids"], lp["token_logprobs"], lp["top_logprobs"]))
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [5, 6, 7, 8]}],
+                                                  "max_tokens": 3, "ignore_eos": True, "logprobs": True,
+                                                  "top_logprobs": 3})
+    assert r.status_code == 200
+    content = r.json()["choices"][0]["logprobs"]["content"]
+    assert len(content) == 3 and all(len(e["top_logprobs"]) == 3 and e["top_logprobs"][0]["token_id"] == e["token_id"]
+                                     for e in content)
+    # not asked for: the field is null
+    r = client.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 2, "ignore_eos": True})
+    assert r.json()["choices"][0]["logprobs"] is None
+
+
 def test_streaming_yields_all_tokens(client):
     with client.stream("POST", "/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 6, "ignore_eos": True,
                                                          "stream": True}) as r:

@@ -1,0 +1,57 @@
+"""Log-probabilities of the sampled tokens: the engine returns, per output token, the
+log-probability of the token under the model's own distribution and the most likely alternatives."""
+import math
+
+import pytest
+import torch
+
+from omni_npu_b200 import SamplingParams
+from omni_npu_b200.config import ModelConfig
+from omni_npu_b200.engine.llm import LLM
+
+
+def _cfg():
+    return ModelConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+                       vocab_size=97, rope_theta=10000.0, max_position_embeddings=512, dtype=torch.float32)
+
+
+def _llm(**kw):
+    return LLM(model=_cfg(), device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=4,
+               num_gpu_blocks=64, seed=3, **kw)
+
+
+def test_greedy_tokens_are_the_most_likely_ones_and_unchanged_by_asking():
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(1, 97, (n,), generator=g).tolist() for n in (5, 17, 9)]
+    plain = _llm().generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    sps = [SamplingParams(max_tokens=6, ignore_eos=True, logprobs=k) for k in (3, 1, 5)]
+    outs = _llm().generate(prompts, sps)
+    for o, p, sp in zip(outs, plain, sps):
+        assert o.output_token_ids == p.output_token_ids and p.logprobs is None
+        assert len(o.logprobs) == 6
+        for tok, (lp, top) in zip(o.output_token_ids, o.logprobs):
+            assert len(top) == sp.logprobs and lp <= 0.0
+            assert top[0][0] == tok and abs(top[0][1] - lp) < 1e-6          # greedy: the sampled token leads
+            assert all(a[1] >= b[1] for a, b in zip(top, top[1:]))
+            assert sum(math.exp(v) for _, v in top) <= 1.0 + 1e-5
+
+
+def test_mixed_batch_of_requests_with_and_without_logprobs_and_sampling():
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(1, 97, (n,), generator=g).tolist() for n in (8, 12)]
+    sps = [SamplingParams(max_tokens=5, ignore_eos=True),
+           SamplingParams(max_tokens=5, ignore_eos=True, temperature=0.8, seed=7, logprobs=2)]
+    outs = _llm().generate(prompts, sps)
+    assert outs[0].logprobs is None and len(outs[1].logprobs) == 5
+    for tok, (lp, top) in zip(outs[1].output_token_ids, outs[1].logprobs):
+        # a sampled token need not be the most likely one, but its log-probability is that of the
+        # model's distribution: never above the leader's
+        assert lp <= top[0][1] + 1e-6
+        if tok == top[0][0]:
+            assert abs(lp - top[0][1]) < 1e-6
+
+
+def test_logprobs_with_speculative_decoding_are_refused():
+    llm = _llm(speculative_config={"method": "ngram", "num_speculative_tokens": 2})
+    with pytest.raises(ValueError):
+        llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, logprobs=1))
