@@ -229,7 +229,7 @@ class LLMEngine:
         before = sum(len(s.request.output_token_ids) for s in out.seqs)
         finished = self.scheduler.update_from_output(out, tokens, drafts=drafts)
         for idx, entry in (getattr(self.worker.model_runner, "last_logprobs", None) or {}).items():
-            out.seqs[idx].request.logprobs.append(entry)
+            out.seqs[idx].request.logprobs.append(entry[:2])        # (log-probability, alternatives); the rank stays behind
         st = self.stats
         st["steps"] += 1
         st[out.kind + "_steps"] += 1

@@ -550,7 +550,8 @@ class ModelRunner:
 
     def _collect_logprobs(self, seqs, tokens) -> Dict[int, Tuple[float, List[Tuple[int, float]]]]:
         """Log-probabilities of this step's sampled tokens for the sequences that asked:
-        {index in seqs: (log-probability of the token, [(token id, log-probability)] of the top k)}."""
+        {index in seqs: (log-probability of the token, [(token id, log-probability)] of the top k,
+        rank of the token among all tokens)}."""
         cap, self._lp_capture = getattr(self, "_lp_capture", None), None
         if cap is None:
             return {}
@@ -559,8 +560,9 @@ class ModelRunner:
         top_v, top_i = logp.topk(max(ks), dim=-1)
         tok = torch.tensor([int(tokens[i]) for i in rows], device=logp.device).unsqueeze(1)
         picked = logp.gather(1, tok).squeeze(1)
+        rank = ((logp > picked.unsqueeze(1)).sum(dim=1) + 1).cpu().tolist()      # 1 = the most likely token
         top_v, top_i, picked = top_v.cpu().tolist(), top_i.cpu().tolist(), picked.cpu().tolist()
-        return {i: (picked[j], list(zip(top_i[j][: ks[j]], top_v[j][: ks[j]]))) for j, i in enumerate(rows)}
+        return {i: (picked[j], list(zip(top_i[j][: ks[j]], top_v[j][: ks[j]])), rank[j]) for j, i in enumerate(rows)}
 
     def _pad_decode_size(self, n: int) -> Optional[int]:
         for s in self.capture_sizes:

@@ -36,9 +36,12 @@ them, the worker verifies 1 + k rows per request in one pass and returns the acc
 the one that follows them (the reference patches vLLM's ``EagleProposer`` for graph-mode drafting:
 omni_npu/vllm_patches/patches/common/patch_eagle.py).
 
+Log-probabilities of sampled tokens (``SamplingParams.logprobs``) are computed by the runner from
+its own logits and handed back as vLLM's ``LogprobsLists``; such steps run as one eager launch.
+
 Not supported under vLLM yet (refused with a clear error, never silently wrong): separate draft
-models (Eagle heads, draft checkpoints), structured-output bitmasks, LoRA, pooling and pipeline
-parallelism.
+models (Eagle heads, draft checkpoints), prompt log-probabilities, structured-output bitmasks, LoRA,
+pooling, pipeline and context parallelism.
 """
 from __future__ import annotations
 
@@ -116,15 +119,39 @@ def sampling_params_from_vllm(sp):
     from ..engine.request import SamplingParams
     if sp is None:
         return SamplingParams(max_tokens=1 << 30, ignore_eos=True)
-    if getattr(sp, "logprobs", None) or getattr(sp, "prompt_logprobs", None):
-        raise ValueError("logprobs are not supported by the B200 worker")
+    if getattr(sp, "prompt_logprobs", None):
+        raise ValueError("prompt_logprobs are not supported by the B200 worker")
+    want_lp = getattr(sp, "logprobs", None)
     top_k = int(getattr(sp, "top_k", 0) or 0)
     return SamplingParams(
         max_tokens=1 << 30, temperature=float(sp.temperature or 0.0), top_k=top_k if top_k > 0 else 0,
         top_p=float(sp.top_p if sp.top_p is not None else 1.0), seed=sp.seed, ignore_eos=True,
         presence_penalty=float(sp.presence_penalty or 0.0), frequency_penalty=float(sp.frequency_penalty or 0.0),
         repetition_penalty=float(sp.repetition_penalty or 1.0),
-        thinking_token_budget=(getattr(sp, "extra_args", None) or {}).get("thinking_token_budget"))
+        thinking_token_budget=(getattr(sp, "extra_args", None) or {}).get("thinking_token_budget"),
+        # vLLM's 0 = the sampled token's log-probability only; the runner keeps at least one alternative
+        logprobs=None if want_lp is None else max(1, min(20, int(want_lp))))
+
+
+def logprobs_lists(seqs, sampled, last_logprobs):
+    """vLLM's ``LogprobsLists`` for one step: a row per request of the step, [sampled token, top k]
+    in the first k + 1 columns (rows of requests that did not ask, or got no token, are zeros)."""
+    import numpy as np
+    from vllm.v1.outputs import LogprobsLists
+    if not last_logprobs:
+        return None
+    k = max(len(e[1]) for e in last_logprobs.values())
+    n = len(seqs)
+    ids = np.zeros((n, k + 1), dtype=np.int64)
+    lps = np.full((n, k + 1), -np.inf, dtype=np.float32)
+    ranks = np.zeros((n,), dtype=np.int64)
+    for i, (lp, top, rank) in last_logprobs.items():
+        if not sampled[i]:
+            continue
+        ids[i, 0], lps[i, 0], ranks[i] = sampled[i][0], lp, rank
+        for j, (tid, v) in enumerate(top):
+            ids[i, 1 + j], lps[i, 1 + j] = tid, v
+    return LogprobsLists(ids, lps, ranks)
 
 
 class StepTranslator:
@@ -490,8 +517,9 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
             got = self._step_drafts or [[] for _ in out.seqs]
             self._drafts = (req_ids, [[int(t) for t in d] if toks else [] for d, toks in zip(got, sampled)])
         self._stashed = ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
-                                          sampled_token_ids=sampled, logprobs=None, prompt_logprobs_dict={},
-                                          pooler_output=[])
+                                          sampled_token_ids=sampled,
+                                          logprobs=logprobs_lists(out.seqs, sampled, runner.last_logprobs),
+                                          prompt_logprobs_dict={}, pooler_output=[])
         return None
 
     # a mixed step is split when it carries at least this many decoding sequences
@@ -518,6 +546,13 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         chunks through the prefill path."""
         from ..engine.scheduler import SchedulerOutput
         self._step_drafts = None
+        if any(s.request.sampling_params.logprobs for s in out.seqs):
+            if out.kind in ("spec_decode", "prefill+spec") or self.mtp_drafts:
+                raise NotImplementedError("logprobs together with speculative decoding are not supported by the "
+                                          "B200 worker")
+            # one launch, so that the step's log-probabilities line up with its sequences
+            self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
+            return self.inner.execute_model(out)
         if self.mtp_drafts:
             return self._run_mtp(out)
         if out.kind == "prefill+spec":

@@ -106,3 +106,14 @@ def test_vllm_driven_drafting_with_the_models_mtp_head_gives_greedy_tokens():
     assert res["via_vllm"] == res["standalone"]
     assert all(len(t) == 24 for t in res["via_vllm"])
     assert res["steps"]["spec_decode"] > 0 and res["steps"]["decode"] == 0
+
+
+def test_vllm_gets_log_probabilities_from_the_worker():
+    """``SamplingParams(logprobs=2)`` through vLLM: the worker fills vLLM's ``LogprobsLists`` (sampled
+    token, its rank, the top alternatives) from the runner's own logits; tokens are unchanged."""
+    res = _child("cpu", "1", "4", "64", "logprobs")
+    assert res["via_vllm"] == res["standalone"]
+    for toks, per_tok in zip(res["via_vllm"], res["logprobs"]):
+        assert len(per_tok) == len(toks) == 16
+        for t, (lp, rank, top_ids) in zip(toks, per_tok):
+            assert lp <= 0.0 and rank == 1 and top_ids[0] == t          # greedy: the sampled token leads

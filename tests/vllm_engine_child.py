@@ -76,6 +76,7 @@ def main() -> None:
         n_out = 40
         extra["speculative_config"] = {"method": "ngram", "num_speculative_tokens": 3,
                                        "prompt_lookup_max": 3, "prompt_lookup_min": 2}
+    want_logprobs = 2 if spec == "logprobs" else None
     if spec == "mtp":
         n_out = 24
         extra["speculative_config"] = {"method": "mtp", "num_speculative_tokens": 2}
@@ -90,9 +91,15 @@ def main() -> None:
               gpu_memory_utilization=0.3, **extra, **({} if fp32 else {"kv_cache_memory_bytes": 1 << 30}))
     vcfg = llm.llm_engine.vllm_config
     outs = llm.generate([{"prompt_token_ids": p} for p in prompts],
-                        SamplingParams(max_tokens=n_out, temperature=0.0, ignore_eos=True, detokenize=False),
+                        SamplingParams(max_tokens=n_out, temperature=0.0, ignore_eos=True, detokenize=False,
+                                       logprobs=want_logprobs),
                         use_tqdm=False)
     via_vllm = [list(o.outputs[0].token_ids) for o in outs]
+    lp_info = None
+    if want_logprobs:
+        # per request: for every output token (its log-probability, its rank, ids of the alternatives)
+        lp_info = [[(d[t].logprob, d[t].rank, sorted(d, key=lambda k: d[k].rank)[:want_logprobs])
+                    for t, d in zip(o.outputs[0].token_ids, o.outputs[0].logprobs)] for o in outs]
     info = {"platform": type(current_platform).__name__, "worker_cls": vcfg.parallel_config.worker_cls,
             "async_scheduling": bool(vcfg.scheduler_config.async_scheduling)}
     if tp == 1:
@@ -118,6 +125,7 @@ def main() -> None:
         res = own.generate(prompts, SP(max_tokens=n_out, temperature=0.0, ignore_eos=True))
         info["standalone"] = [o.output_token_ids for o in res]
     info["via_vllm"] = via_vllm
+    info["logprobs"] = lp_info
     print("RESULT " + json.dumps(info), flush=True)
 
 
