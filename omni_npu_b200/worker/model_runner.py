@@ -79,6 +79,7 @@ class ModelRunner:
         self.thinking_processor = ThinkingTokenBudgetLogitsProcessor(rc, sc.max_num_seqs, device)
         self.mtp = None                       # the model's multi-token-prediction head, if it drafts
         self.last_drafts: List[List[int]] = []
+        self.extra_logits_fn = None
         self.last_logprobs: Dict[int, Tuple[float, List[Tuple[int, float]]]] = {}   # of the last step, by index in its seqs
         self._lp_capture = None
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
@@ -506,7 +507,10 @@ class ModelRunner:
         # truncation), for the sampled token and the most likely tokens
         lp_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.logprobs]
         self._lp_capture = None
-        if not pen_rows and not think_rows and not lp_rows:
+        # a logits adjustment supplied for this one step by whoever drives the runner (the vLLM
+        # worker's grammar bitmask): applied last, to the rows of ``seqs`` in order
+        extra = getattr(self, "extra_logits_fn", None)
+        if not pen_rows and not think_rows and not lp_rows and extra is None:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -545,6 +549,8 @@ class ModelRunner:
                                [seqs[i].request.request_id for i in think_rows],
                                [seqs[i].request.output_token_ids for i in think_rows])
                 logits = logits.index_copy(0, idx, sub)
+            if extra is not None:
+                logits = extra(logits)
             return logits
         return fn
 

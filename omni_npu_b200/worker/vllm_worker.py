@@ -39,9 +39,13 @@ omni_npu/vllm_patches/patches/common/patch_eagle.py).
 Log-probabilities of sampled tokens (``SamplingParams.logprobs``) are computed by the runner from
 its own logits and handed back as vLLM's ``LogprobsLists``; such steps run as one eager launch.
 
+Structured outputs: vLLM hands the grammar's bitmask to ``sample_tokens``; a step with such requests
+is deferred to that call and runs there as one eager launch with the bitmask applied to the logits
+rows of the structured requests (``grammar_mask_fn``).
+
 Not supported under vLLM yet (refused with a clear error, never silently wrong): separate draft
-models (Eagle heads, draft checkpoints), prompt log-probabilities, structured-output bitmasks, LoRA,
-pooling, pipeline and context parallelism.
+models (Eagle heads, draft checkpoints), prompt log-probabilities, LoRA, pooling, pipeline and
+context parallelism; structured outputs or log-probabilities together with speculative decoding.
 """
 from __future__ import annotations
 
@@ -131,6 +135,30 @@ def sampling_params_from_vllm(sp):
         thinking_token_budget=(getattr(sp, "extra_args", None) or {}).get("thinking_token_budget"),
         # vLLM's 0 = the sampled token's log-probability only; the runner keeps at least one alternative
         logprobs=None if want_lp is None else max(1, min(20, int(want_lp))))
+
+
+def grammar_mask_fn(step_req_ids, structured_req_ids, bitmask):
+    """Logits adjustment for one step: row i of the logits belongs to ``step_req_ids[i]``; row j of
+    ``bitmask`` (int32 words, bit b of word w = token 32 w + b, set = allowed) to
+    ``structured_req_ids[j]``.  Tokens whose bit is clear get -inf; other rows are untouched."""
+    import numpy as np
+    row_of = {rid: i for i, rid in enumerate(step_req_ids)}
+    pairs = [(row_of[rid], j) for j, rid in enumerate(structured_req_ids) if rid in row_of]
+    words = np.ascontiguousarray(np.asarray(bitmask, dtype=np.int32))
+
+    def fn(logits: torch.Tensor) -> torch.Tensor:
+        if not pairs:
+            return logits
+        vocab = logits.shape[-1]
+        rows = torch.tensor([p[0] for p in pairs], dtype=torch.long, device=logits.device)
+        w = torch.from_numpy(words[[p[1] for p in pairs]]).to(logits.device)
+        bits = (w.unsqueeze(-1) >> torch.arange(32, device=logits.device, dtype=torch.int32)) & 1
+        allowed = bits.reshape(len(pairs), -1)[:, :vocab].bool()
+        if allowed.shape[1] < vocab:          # a bitmask narrower than the (padded) vocabulary: the tail is not allowed
+            allowed = torch.cat([allowed, allowed.new_zeros(len(pairs), vocab - allowed.shape[1])], dim=1)
+        sub = logits.index_select(0, rows).masked_fill(~allowed, float("-inf"))
+        return logits.index_copy(0, rows, sub)
+    return fn
 
 
 def logprobs_lists(seqs, sampled, last_logprobs):
@@ -327,6 +355,7 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
         self._resolve_lock = threading.Lock()
         self._inflight: Optional[PendingDecodeOutput] = None     # decode step launched ahead of its tokens
         self._stashed = None                                     # output of execute_model, handed out by sample_tokens
+        self._deferred = None                                    # a step that waits for its grammar bitmask
         self.async_scheduling = bool(getattr(vllm_config.scheduler_config, "async_scheduling", False))
         # speculative decoding driven by vLLM's scheduler: the n-gram method runs here (drafts are
         # looked up on the host after every step and handed to vLLM through take_draft_token_ids;
@@ -483,9 +512,16 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
     @torch.inference_mode()
     def execute_model(self, scheduler_output):
         from vllm.v1.outputs import EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput
-        if getattr(scheduler_output, "has_structured_output_requests", False):
-            raise NotImplementedError("structured outputs are not supported by the B200 worker")
         out = self.translator.translate(scheduler_output)
+        if getattr(scheduler_output, "has_structured_output_requests", False) and out.kind != "idle":
+            # the grammar bitmask of this step arrives with sample_tokens(): the whole step (forward
+            # pass and sampling are one launch sequence here) runs there, with the bitmask applied to
+            # the logits before sampling
+            if out.kind in ("spec_decode", "prefill+spec") or self.mtp_drafts:
+                raise NotImplementedError("structured outputs together with speculative decoding are not "
+                                          "supported by the B200 worker")
+            self._deferred = out
+            return None
         if out.kind == "idle":
             self.inner.execute_model(out)                 # retire rows of finished requests
             return EMPTY_MODEL_RUNNER_OUTPUT
@@ -649,10 +685,39 @@ class B200Worker(_WorkerBase):  # type: ignore[misc, valid-type]
     def sample_tokens(self, grammar_output=None):
         """Second half of vLLM's two-call step: the forward pass and the sampling both ran in
         ``execute_model`` (structured-output bitmasks are refused there), this hands the result out."""
+        if self._deferred is not None:
+            self._run_deferred(grammar_output)
         out, self._stashed = self._stashed, None
         if out is None:
             raise RuntimeError("sample_tokens called without a preceding execute_model")
         return out
+
+    def _run_deferred(self, grammar_output) -> None:
+        """A step with structured-output requests: run it now, with the grammar's bitmask (one row
+        of ceil(vocab / 32) int32 words per structured request, bit set = token allowed) applied to
+        the logits rows of those requests (reference: vLLM's ``apply_grammar_bitmask``)."""
+        from vllm.v1.outputs import ModelRunnerOutput
+        out, self._deferred = self._deferred, None
+        runner = self.model_runner
+        if self._inflight is not None:
+            self._inflight.tokens_on_host()
+            self._inflight = None
+        if grammar_output is not None and len(grammar_output.structured_output_request_ids):
+            runner.extra_logits_fn = grammar_mask_fn([s.request.request_id for s in out.seqs],
+                                                     list(grammar_output.structured_output_request_ids),
+                                                     grammar_output.grammar_bitmask)
+        try:
+            self.steps[out.kind] = self.steps.get(out.kind, 0) + 1
+            self.steps["structured"] = self.steps.get("structured", 0) + 1
+            tokens = self.inner.execute_model(out)          # one launch: logits rows line up with out.seqs
+        finally:
+            runner.extra_logits_fn = None
+        sampled = self.translator.commit(out, tokens)
+        req_ids = [s.request.request_id for s in out.seqs]
+        self._stashed = ModelRunnerOutput(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)},
+                                          sampled_token_ids=sampled,
+                                          logprobs=logprobs_lists(out.seqs, sampled, runner.last_logprobs),
+                                          prompt_logprobs_dict={}, pooler_output=[])
 
     def take_draft_token_ids(self):
         """Drafts proposed after the last step, in vLLM's container (None without a proposer)."""

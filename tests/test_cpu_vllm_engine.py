@@ -117,3 +117,20 @@ def test_vllm_gets_log_probabilities_from_the_worker():
         assert len(per_tok) == len(toks) == 16
         for t, (lp, rank, top_ids) in zip(toks, per_tok):
             assert lp <= 0.0 and rank == 1 and top_ids[0] == t          # greedy: the sampled token leads
+
+
+def test_structured_output_request_is_constrained_by_vllms_grammar_bitmask():
+    """A request with ``StructuredOutputsParams(choice=["red", "blue"])`` beside a free one: vLLM hands
+    the grammar's bitmask to ``sample_tokens``, the worker runs the step there and masks the logits
+    rows of the structured request, which therefore answers with one of the two words and stops."""
+    env = dict(os.environ)
+    env.pop("OMNI_B200_PLUGIN", None)
+    r = subprocess.run([sys.executable, str(ROOT / "tests" / "vllm_structured_child.py")], capture_output=True,
+                       text=True, timeout=900, env=env, cwd=str(ROOT))
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert lines, f"child failed (rc={r.returncode}):\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}"
+    res = json.loads(lines[-1][7:])
+    assert res["texts"][0].strip() in ("red", "blue")
+    assert res["ids"][0][-1] == 2 and len(res["ids"][0]) == 2          # the word, then end of sequence
+    assert len(res["ids"][1]) == 4                                     # the free request ran to its length cap
+    assert res["steps"]["structured"] >= 2

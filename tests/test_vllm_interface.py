@@ -324,3 +324,53 @@ def test_worker_describes_sink_models_with_the_sink_spec():
         s = specs["model.layers.0.self_attn.attn"]
         assert type(s) is cls and s.head_size == dk and s.head_size_v == dv and s.page_size_bytes == per_layer
         assert getattr(s, "sink_len", None) == sink
+
+
+def test_grammar_bitmask_masks_the_rows_of_structured_requests_only():
+    """The worker's bitmask application: one row of int32 words per structured request (bit set =
+    token allowed), in vLLM's order of structured request ids, applied to the logits rows of the
+    step in the step's own order."""
+    import numpy as np
+    import torch
+    from omni_npu_b200.worker.vllm_worker import grammar_mask_fn
+    vocab = 70                                            # three words, the last one partly used
+    logits = torch.arange(3 * vocab, dtype=torch.float32).view(3, vocab)
+    words = np.zeros((2, 3), dtype=np.uint32)
+    words[0, 0] = (1 << 5) | (1 << 31)                    # request "c": tokens 5 and 31 (the sign bit of the int32 word)
+    words[0, 2] = 1 << 3                                  # ... and token 67
+    words[1, 1] = 1 << 1                                  # request "a": token 33
+    words = words.view(np.int32)
+    fn = grammar_mask_fn(["a", "b", "c"], ["c", "a", "gone"], np.vstack([words, np.full((1, 3), -1, dtype=np.int32)]))
+    out = fn(logits.clone())
+    assert torch.equal(out[1], logits[1])                                 # "b" is not structured
+    assert torch.isfinite(out[0]).nonzero().flatten().tolist() == [33]    # "a" takes the second bitmask row
+    assert torch.isfinite(out[2]).nonzero().flatten().tolist() == [5, 31, 67]
+    assert out[2, 67] == logits[2, 67]
+
+
+def test_runner_applies_a_step_logits_adjustment_before_sampling():
+    """``ModelRunner.extra_logits_fn`` (what the vLLM worker installs for a structured-output step)
+    is applied to the step's logits rows: with every token but one masked, that token is sampled,
+    and the step runs eagerly."""
+    import torch
+    from omni_npu_b200 import SamplingParams
+    from omni_npu_b200.config import ModelConfig
+    from omni_npu_b200.engine.llm import LLM
+    cfg = ModelConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+                      vocab_size=97, rope_theta=10000.0, max_position_embeddings=512, dtype=torch.float32)
+    llm = LLM(model=cfg, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=4,
+              num_gpu_blocks=64, seed=3, additional_config={"async_scheduling": False})
+    runner = llm.engine.worker.model_runner
+
+    def only_token_42(logits):
+        masked = torch.full_like(logits, float("-inf"))
+        masked[:, 42] = logits[:, 42]
+        return masked
+    runner.extra_logits_fn = only_token_42
+    try:
+        outs = llm.generate([[1, 2, 3, 4, 5], [9, 8, 7]], SamplingParams(max_tokens=4, ignore_eos=True))
+    finally:
+        runner.extra_logits_fn = None
+    assert all(o.output_token_ids == [42] * 4 for o in outs)
+    free = llm.generate([[1, 2, 3, 4, 5]], SamplingParams(max_tokens=4, ignore_eos=True))
+    assert free[0].output_token_ids != [42] * 4
