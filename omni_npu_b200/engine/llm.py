@@ -98,6 +98,15 @@ class LLMEngine:
         if speculative and (sp.has_penalties or sp.thinking_token_budget is not None or sp.logprobs):
             raise ValueError("penalties, thinking_token_budget and logprobs are not supported together with "
                              "speculative decoding")
+        if sp.structured is not None:
+            if speculative:
+                raise ValueError("structured outputs are not supported together with speculative decoding")
+            if runner.structured is None:
+                raise ValueError("structured outputs need a tokenizer (LLM.enable_structured_outputs, or a server "
+                                 "started with a tokenizer directory)")
+            if runner.pcp_group is not None or self.dp_group is not None:
+                raise ValueError("structured outputs are not supported with prefill-context or data parallelism")
+            runner.structured.compile(sp.structured)         # a grammar that does not compile is refused here
         if sp.logprobs and (int(sp.logprobs) < 0 or int(sp.logprobs) > 20):
             raise ValueError("logprobs must be between 0 and 20")
         if sp.logprobs and (runner.pcp_group is not None or self.dp_group is not None):
@@ -238,6 +247,8 @@ class LLMEngine:
         st["output_tokens"] += sum(len(s.request.output_token_ids) for s in out.seqs) - before
         for r in finished:
             self.worker.model_runner.input_batch.remove_request(r.request_id)
+            if self.worker.model_runner.structured is not None:
+                self.worker.model_runner.structured.remove_request(r.request_id)
         interval = self.config.parallel.eplb_step_interval
         if interval > 0 and st["steps"] % interval == 0:
             self.rebalance_experts()
@@ -318,6 +329,11 @@ class LLM:
             config = build_engine_config(mc, model_path=path, **kw)
         self.config = config
         self.engine = LLMEngine(config)
+
+    def enable_structured_outputs(self, tokenizer) -> None:
+        """Give the engine the tokenizer that structured outputs (``SamplingParams.structured``) are
+        compiled against; call it on every rank."""
+        self.engine.worker.model_runner.enable_structured_outputs(tokenizer)
 
     def start_profile(self) -> None:
         """Start the worker's torch profiler (needs ``VLLM_TORCH_PROFILER_DIR`` at start-up)."""

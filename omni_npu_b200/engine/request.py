@@ -21,6 +21,9 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     thinking_token_budget: Optional[int] = None
     logprobs: Optional[int] = None
+    # structured output: {"choice": [...]} | {"json_schema": ...} | {"json_object": True} | {"regex": ...} |
+    # {"grammar": ebnf} (sample/structured.py); needs a tokenizer given to the engine
+    structured: Optional[Dict[str, Any]] = None
     extra_args: Dict[str, Any] = field(default_factory=dict)
 
     @property

@@ -192,6 +192,9 @@ class EngineLoop:
             self.thread.join(timeout=5)
 
 
+from ..sample.structured import structured_spec_from_body  # noqa: E402
+
+
 def _logprobs_from_body(body: Dict[str, Any]) -> Optional[int]:
     """Completions: ``logprobs: n``.  Chat: ``logprobs: true`` with ``top_logprobs: n`` (n = 0: the
     sampled token's log-probability only, asked for as 1 alternative here)."""
@@ -214,7 +217,7 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           frequency_penalty=float(body.get("frequency_penalty") or 0.0),
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
                           thinking_token_budget=body.get("thinking_token_budget"),
-                          logprobs=_logprobs_from_body(body))
+                          logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body))
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):
@@ -427,11 +430,6 @@ def main(argv=None) -> None:
     if args.reasoning_config:
         kw["additional_config"] = dict(kw["additional_config"] or {}, reasoning_config=args.reasoning_config)
     llm = LLM(model=args.model, **kw)
-    if int(os.environ.get("RANK", "0")) != 0 and args.data_parallel_size == 1:
-        EngineLoop(llm, follower=True).run_follower()       # requests arrive through rank 0
-        return
-    if args.data_parallel_size > 1:
-        args.port += int(os.environ.get("RANK", "0"))      # one server per data-parallel rank: port + rank
     tokenizer = None
     tok_dir = args.tokenizer or (args.model if os.path.isdir(args.model) else None)
     if tok_dir:
@@ -440,6 +438,16 @@ def main(argv=None) -> None:
             tokenizer = AutoTokenizer.from_pretrained(tok_dir)
         except Exception as e:
             logger.warning("no tokenizer loaded from %s (%s): token-id requests only", tok_dir, e)
+    if tokenizer is not None:
+        try:
+            llm.enable_structured_outputs(tokenizer)        # on every rank: each one masks its own logits
+        except Exception as e:
+            logger.warning("structured outputs are off (%s)", e)
+    if int(os.environ.get("RANK", "0")) != 0 and args.data_parallel_size == 1:
+        EngineLoop(llm, follower=True).run_follower()       # requests arrive through rank 0
+        return
+    if args.data_parallel_size > 1:
+        args.port += int(os.environ.get("RANK", "0"))      # one server per data-parallel rank: port + rank
     if args.reasoning_config and tokenizer is not None:
         # marker strings given instead of token ids: resolve them now that there is a tokenizer
         proc = llm.engine.worker.model_runner.thinking_processor

@@ -80,6 +80,7 @@ class ModelRunner:
         self.mtp = None                       # the model's multi-token-prediction head, if it drafts
         self.last_drafts: List[List[int]] = []
         self.extra_logits_fn = None
+        self.structured = None      # sample/structured.py manager, once a tokenizer is known
         self.last_logprobs: Dict[int, Tuple[float, List[Tuple[int, float]]]] = {}   # of the last step, by index in its seqs
         self._lp_capture = None
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
@@ -478,7 +479,13 @@ class ModelRunner:
     def needs_host_logits(req) -> bool:
         """Whether sampling for this request needs its token history (penalties, thinking budget)."""
         sp = req.sampling_params
-        return sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
+        return (sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
+                or sp.structured is not None)
+
+    def enable_structured_outputs(self, tokenizer) -> None:
+        """Structured outputs need the tokenizer's vocabulary (token id -> text)."""
+        from ..sample.structured import StructuredOutputManager
+        self.structured = StructuredOutputManager(tokenizer, self.config.model.vocab_size)
 
     def _penalty_cache(self, vocab: int):
         """The device-resident penalty state (created on first use: most workloads never ask)."""
@@ -510,7 +517,13 @@ class ModelRunner:
         # a logits adjustment supplied for this one step by whoever drives the runner (the vLLM
         # worker's grammar bitmask): applied last, to the rows of ``seqs`` in order
         extra = getattr(self, "extra_logits_fn", None)
-        if not pen_rows and not think_rows and not lp_rows and extra is None:
+        # structured outputs: the request's grammar says which tokens may come next
+        so = self.structured
+        so_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.structured is not None]
+        if so_rows and so is None:
+            raise RuntimeError("a request asks for structured output but the engine has no tokenizer "
+                               "(LLM.enable_structured_outputs)")
+        if not pen_rows and not think_rows and not lp_rows and not so_rows and extra is None:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -549,6 +562,16 @@ class ModelRunner:
                                [seqs[i].request.request_id for i in think_rows],
                                [seqs[i].request.output_token_ids for i in think_rows])
                 logits = logits.index_copy(0, idx, sub)
+            if so_rows:
+                rids = []
+                for i in so_rows:
+                    r = seqs[i].request
+                    if not so.has(r.request_id):
+                        so.add_request(r.request_id, r.sampling_params.structured)
+                    rids.append(r.request_id)
+                idx = torch.tensor(so_rows, device=dev)
+                sub = so.apply(logits.index_select(0, idx), rids, [seqs[i].request.output_token_ids for i in so_rows])
+                logits = logits.index_copy(0, idx, sub)
             if extra is not None:
                 logits = extra(logits)
             return logits
@@ -586,6 +609,8 @@ class ModelRunner:
             self.thinking_processor.remove_request(rid)
             if getattr(self, "_pen_cache", None) is not None:
                 self._pen_cache.remove_request(rid)
+            if self.structured is not None:
+                self.structured.remove_request(rid)
         for rid in out.preempted:
             ib.remove_request(rid)
         if self.kv_connector is not None and out.kv_connector_metadata is not None:

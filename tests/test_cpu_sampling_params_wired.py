@@ -1,6 +1,6 @@
 """Sampling parameters that need the token history are honoured or refused, never ignored:
 penalties and the thinking-token budget change the output of a tiny CPU engine exactly as a
-plain re-implementation predicts; logprobs are refused; default seeds do not depend on the
+plain re-implementation predicts; what cannot be honoured is refused; default seeds do not depend on the
 process; a failed step does not end the server's engine loop."""
 import subprocess
 import sys
@@ -95,10 +95,14 @@ def test_thinking_budget_forces_the_end_marker():
         _llm().generate([prompt], SamplingParams(max_tokens=4, thinking_token_budget=3))
 
 
-def test_logprobs_are_refused_not_ignored():
+def test_what_the_sampler_cannot_honour_is_refused_not_ignored():
     llm = _llm()
     with pytest.raises(ValueError, match="logprobs"):
-        llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, logprobs=5))
+        llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, logprobs=50))          # more than 20 alternatives
+    with pytest.raises(ValueError, match="tokenizer"):
+        llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, structured={"choice": ["a"]}))
+    out = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, ignore_eos=True, logprobs=5))[0]
+    assert len(out.logprobs) == 2 and len(out.logprobs[0][1]) == 5                    # ... and what it can is done
 
 
 def test_server_answers_400_and_survives_a_failing_step():
@@ -108,8 +112,10 @@ def test_server_answers_400_and_survives_a_failing_step():
     llm = _llm()
     app = build_app(llm, None, "tiny")
     with TestClient(app) as c:
-        r = c.post("/v1/completions", json={"prompt": [1, 2, 3], "max_tokens": 2, "logprobs": 3})
+        r = c.post("/v1/completions", json={"prompt": [1, 2, 3], "max_tokens": 2, "logprobs": 30})
         assert r.status_code == 400 and "logprobs" in r.text
+        r = c.post("/v1/completions", json={"prompt": [1, 2, 3], "max_tokens": 2, "guided_choice": ["a", "b"]})
+        assert r.status_code == 400 and "tokenizer" in r.text                  # this server has no tokenizer
         r = c.post("/v1/completions", json={"prompt": [1, 2, 3], "max_tokens": 4, "ignore_eos": True,
                                             "repetition_penalty": 1.3})
         assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 4

@@ -1,0 +1,106 @@
+"""Structured outputs of the standalone engine: a request restricted to a choice of strings, a JSON
+schema, a regular expression or a grammar only produces tokens its grammar allows, and ends when
+the grammar is complete."""
+import json
+
+import pytest
+import torch
+
+from omni_npu_b200 import SamplingParams
+from omni_npu_b200.config import ModelConfig
+from omni_npu_b200.engine.llm import LLM
+from omni_npu_b200.sample.structured import StructuredOutputManager, structured_spec_from_body
+
+pytest.importorskip("xgrammar")
+
+WORDS = ["yes", "no", "maybe", "the", "a", "cat", "dog", "is", "red", "blue", "{", "}", ":", ",", '"', "1", "2", "3",
+         "true", "false", "name", "age", "x", "q"]
+
+
+@pytest.fixture(scope="module")
+def tokenizer():
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    vocab = {"<unk>": 0, "<s>": 1, "</s>": 2}
+    for w in WORDS + [f"w{i}" for i in range(97 - 3 - len(WORDS))]:
+        vocab[w] = len(vocab)
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    return PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
+
+
+def _llm(tokenizer, **kw):
+    cfg = ModelConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+                      vocab_size=97, rope_theta=10000.0, max_position_embeddings=512, dtype=torch.float32)
+    cfg.eos_token_id = 2
+    llm = LLM(model=cfg, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128, block_size=4,
+              num_gpu_blocks=64, seed=3, **kw)
+    if tokenizer is not None:
+        llm.enable_structured_outputs(tokenizer)
+    return llm
+
+
+def test_choice_regex_and_free_requests_share_a_batch(tokenizer):
+    llm = _llm(tokenizer)
+    v = tokenizer.get_vocab()
+    prompts = [[5, 6, 7], [9, 8, 7, 6], [4, 4, 4]]
+    sps = [SamplingParams(max_tokens=8, structured={"choice": ["red", "blue"]}),
+           SamplingParams(max_tokens=8, temperature=0.9, seed=5, structured={"regex": "(yes|no)(yes|no)"}),
+           SamplingParams(max_tokens=5, ignore_eos=True)]
+    outs = llm.generate(prompts, sps)
+    # the word, then the end-of-sequence token (the only token a complete grammar allows)
+    assert outs[0].output_token_ids in ([v["red"], 2], [v["blue"], 2]) and outs[0].finish_reason == "stop"
+    two = outs[1].output_token_ids
+    assert len(two) == 3 and two[2] == 2 and all(t in (v["yes"], v["no"]) for t in two[:2])
+    assert len(outs[2].output_token_ids) == 5
+    free = _llm(None).generate(prompts[2:], sps[2:])
+    assert free[0].output_token_ids == outs[2].output_token_ids          # the free request is not disturbed
+    assert not llm.engine.worker.model_runner.structured._matchers       # matchers of finished requests are gone
+
+
+def test_a_grammar_the_vocabulary_cannot_continue_ends_the_request(tokenizer):
+    """"q" is a token and a prefix of the only allowed word, but no token spells the rest: after
+    "q" nothing is allowed, and the request ends instead of sampling from an empty row."""
+    llm = _llm(tokenizer)
+    v = tokenizer.get_vocab()
+    out = llm.generate([[5, 6, 7]], SamplingParams(max_tokens=6, structured={"regex": "qzz"}))[0]
+    assert out.output_token_ids == [v["q"], 2] and out.finish_reason == "stop"
+
+
+def test_json_schema_output_parses(tokenizer):
+    llm = _llm(tokenizer)
+    schema = {"type": "object", "properties": {"x": {"type": "boolean"}}, "required": ["x"], "additionalProperties": False}
+    out = llm.generate([[3, 4, 5]], SamplingParams(max_tokens=24, structured={"json_schema": schema}))[0]
+    assert out.finish_reason == "stop"
+    text = "".join(tokenizer.convert_ids_to_tokens(out.output_token_ids[:-1]))
+    assert json.loads(text) in ({"x": True}, {"x": False})
+
+
+def test_refusals_and_request_fields(tokenizer):
+    with pytest.raises(ValueError):
+        _llm(None).generate([[1, 2]], SamplingParams(max_tokens=2, structured={"choice": ["red"]}))
+    llm = _llm(tokenizer)
+    with pytest.raises(ValueError):
+        llm.generate([[1, 2]], SamplingParams(max_tokens=2, structured={"grammar": "root ::= ("}))
+    with pytest.raises(ValueError):
+        StructuredOutputManager.check_spec({"choice": []})
+    assert structured_spec_from_body({"guided_choice": ["a", "b"]}) == {"choice": ["a", "b"]}
+    assert structured_spec_from_body({"structured_outputs": {"regex": "a+"}}) == {"regex": "a+"}
+    assert structured_spec_from_body({"response_format": {"type": "json_object"}}) == {"json_object": True}
+    assert structured_spec_from_body({"response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "object"}}}}) \
+        == {"json_schema": {"type": "object"}}
+    assert structured_spec_from_body({"max_tokens": 3}) is None
+
+
+def test_api_server_routes_take_structured_output_fields(tokenizer):
+    from starlette.testclient import TestClient
+    from omni_npu_b200.serving.api_server import build_app
+    llm = _llm(tokenizer)
+    app = build_app(llm, tokenizer, "tiny")
+    with TestClient(app) as c:
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 8, "guided_choice": ["cat", "dog"]})
+        assert r.status_code == 200 and r.json()["choices"][0]["text"].replace("</s>", "").strip() in ("cat", "dog")
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 8,
+                                            "structured_outputs": {"grammar": "root ::= ("}})
+        assert r.status_code == 400                       # a grammar that does not compile is refused up front
+    app.state.engine_loop.shutdown()
