@@ -26,7 +26,7 @@ import time
 import uuid
 from typing import Any, Dict, List, Optional
 
-from ..engine.request import SamplingParams
+from ..engine.request import RequestOutput, SamplingParams
 from ..logger import logger
 
 
@@ -53,6 +53,7 @@ class EngineLoop:
                                       "or use data_parallel_size == 1")
         self._new: List[tuple] = []
         self._aborts: List[str] = []
+        self.tokenizer = None                 # set by build_app: stop strings are matched on decoded text
         self.lock = threading.Lock()
         self.wake = threading.Event()
         self.waiters: Dict[str, Dict[str, Any]] = {}
@@ -63,10 +64,16 @@ class EngineLoop:
             self.thread.start()
         self.counters = {"requests": 0, "finished": 0, "output_tokens": 0, "steps": 0}
 
-    def submit(self, prompt_ids: List[int], sp: SamplingParams, kv_transfer_params=None) -> str:
+    def submit(self, prompt_ids: List[int], sp: SamplingParams, kv_transfer_params=None,
+               stop: Optional[List[str]] = None) -> str:
+        """``stop``: strings that end the request when they appear in its decoded output (needs
+        ``self.tokenizer``); the answer's text is cut before the first of them."""
         self.engine.validate_sampling_params(sp)        # ValueError -> HTTP 400, before anything is queued
+        if stop and self.tokenizer is None:
+            raise ValueError("stop strings need a tokenizer (use stop_token_ids on a server without one)")
         rid = f"cmpl-{uuid.uuid4().hex}"
-        slot = {"event": threading.Event(), "output": None, "seen": 0, "queue": [], "request": None}
+        slot = {"event": threading.Event(), "output": None, "seen": 0, "queue": [], "request": None,
+                "stop": [s for s in (stop or []) if s], "text": None}
         with self.lock:
             self.waiters[rid] = slot
             if self.group is None:
@@ -101,6 +108,17 @@ class EngineLoop:
             with self.lock:
                 self._publish(self._safe_step())
 
+    def _find_stop(self, ids: List[int], seen: int, stops: List[str]):
+        """(tokens to keep, text before the stop string) when a stop string shows up in the decoded
+        output, else None.  Only prefixes that end in the newly arrived tokens are decoded."""
+        first = max(1, seen + 1)
+        for k in range(first, len(ids) + 1):
+            text = self.tokenizer.decode(ids[:k])
+            hits = [text.find(s) for s in stops if s in text]
+            if hits:
+                return k - 1, text[: min(hits)]
+        return None
+
     def _safe_step(self):
         """One engine step.  An exception must not end the loop thread (every waiter would hang):
         the requests in flight are failed with finish_reason "abort" and the loop goes on."""
@@ -123,11 +141,30 @@ class EngineLoop:
             while ready > 0 and ids[ready - 1] < 0:     # tokens of a step still in flight
                 ready -= 1
             if ready > slot["seen"]:
-                slot["queue"].extend(ids[slot["seen"]:ready])
+                new_ids = ids[slot["seen"]:ready]
+                if slot["stop"] and slot["output"] is None:
+                    cut = self._find_stop(ids[:ready], slot["seen"], slot["stop"])
+                    if cut is not None:
+                        keep, text = cut
+                        # the request ends here: answer now, drop what came after the stop string
+                        out = RequestOutput.from_request(req)
+                        out.output_token_ids = list(ids[:keep])
+                        out.finished, out.finish_reason = True, "stop"
+                        out.text = text                       # what the routes answer with instead of decoding
+                        slot["queue"].extend(ids[slot["seen"]:keep])
+                        slot["seen"] = ready
+                        slot["output"] = out
+                        slot["event"].set()
+                        if self.group is None:
+                            self.engine.abort_request(rid)
+                        else:
+                            self._aborts.append(rid)
+                        continue
+                slot["queue"].extend(new_ids)
                 slot["seen"] = ready
         for o in outs:
             slot = self.waiters.get(o.request_id)
-            if slot is not None:
+            if slot is not None and slot["output"] is None:
                 slot["output"] = o
                 slot["event"].set()
             self.counters["finished"] += 1
@@ -226,6 +263,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
 
     app = FastAPI()
     loop = EngineLoop(llm)
+    loop.tokenizer = tokenizer
     app.state.engine_loop = loop
 
     def encode(prompt) -> List[int]:
@@ -277,10 +315,17 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
         return PlainTextResponse("\n".join(lines) + "\n")
 
     def _submit(ids, body) -> str:
+        stop = body.get("stop")
+        stop = [stop] if isinstance(stop, str) else list(stop or [])
         try:
-            return loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"))
+            return loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"), stop=stop)
         except ValueError as e:
             raise HTTPException(400, str(e))
+
+    def _text(out) -> str:
+        """The answer's text: cut before a stop string when one ended the request."""
+        cut = getattr(out, "text", None)
+        return cut if cut is not None else decode(out.output_token_ids)
 
     async def _finish(rid: str):
         while True:
@@ -326,7 +371,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                                    for e in out.logprobs]}
         return JSONResponse({
             "id": rid, "object": "text_completion", "created": created, "model": model_name,
-            "choices": [{"index": 0, "text": decode(out.output_token_ids), "token_ids": out.output_token_ids,
+            "choices": [{"index": 0, "text": _text(out), "token_ids": out.output_token_ids,
                          "logprobs": lp, "finish_reason": out.finish_reason or "stop"}],
             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
                       "total_tokens": len(ids) + len(out.output_token_ids)},
@@ -343,7 +388,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
             raise HTTPException(400, "chat needs a tokenizer with a chat template")
         rid = _submit(ids, body)
         out = await _finish(rid)
-        text = decode(out.output_token_ids)
+        text = _text(out)
         message: Dict[str, Any] = {"role": "assistant", "content": text}
         if reasoning_parser is not None:
             reasoning, content = reasoning_parser.extract_reasoning(text)

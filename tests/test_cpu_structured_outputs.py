@@ -104,3 +104,34 @@ def test_api_server_routes_take_structured_output_fields(tokenizer):
                                             "structured_outputs": {"grammar": "root ::= ("}})
         assert r.status_code == 400                       # a grammar that does not compile is refused up front
     app.state.engine_loop.shutdown()
+
+
+def test_stop_strings_end_the_request_and_cut_the_text(tokenizer):
+    """``stop`` of the OpenAI routes: the decoded output is watched for the strings; the request is
+    aborted in the engine when one shows up and the answer's text ends before it."""
+    from starlette.testclient import TestClient
+    from omni_npu_b200.serving.api_server import build_app
+    llm = _llm(tokenizer)
+    app = build_app(llm, tokenizer, "tiny")
+    with TestClient(app) as c:
+        free = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 8, "ignore_eos": True}).json()
+        ids = free["choices"][0]["token_ids"]
+        words = tokenizer.convert_ids_to_tokens(ids)
+        stop_word = words[3]                                   # the fourth generated word ends the answer
+        first = words.index(stop_word)
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 8, "ignore_eos": True,
+                                            "stop": [stop_word, "never-there"]})
+        ch = r.json()["choices"][0]
+        assert r.status_code == 200 and ch["finish_reason"] == "stop"
+        assert ch["token_ids"] == ids[:first]
+        assert stop_word not in ch["text"].split() and ch["text"].strip() == tokenizer.decode(ids[:first]).strip()
+        # the engine is free again and serves the next request in full
+        again = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 8, "ignore_eos": True}).json()
+        assert again["choices"][0]["token_ids"] == ids
+        assert llm.engine.scheduler.pool.num_free == 64
+    app.state.engine_loop.shutdown()
+    # a server without a tokenizer refuses stop strings instead of ignoring them
+    app = build_app(_llm(None), None, "tiny")
+    with TestClient(app) as c:
+        assert c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 4, "stop": "x"}).status_code == 400
+    app.state.engine_loop.shutdown()
