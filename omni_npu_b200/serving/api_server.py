@@ -387,6 +387,20 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
         else:
             raise HTTPException(400, "chat needs a tokenizer with a chat template")
         rid = _submit(ids, body)
+        if body.get("stream"):
+            # chat.completion.chunk events: the role first, then the text of the new tokens as they
+            # arrive (reasoning / tool-call parsing needs the whole text and applies to the plain answer)
+            created = int(time.time())
+            state = {"first": True}
+
+            def chunk(toks, finish):
+                delta: Dict[str, Any] = {"content": decode(toks)} if toks else {}
+                if state["first"]:
+                    delta["role"] = "assistant"
+                    state["first"] = False
+                return {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model_name,
+                        "choices": [{"index": 0, "delta": delta, "token_ids": toks, "finish_reason": finish}]}
+            return StreamingResponse(_stream(rid, chunk), media_type="text/event-stream")
         out = await _finish(rid)
         text = _text(out)
         message: Dict[str, Any] = {"role": "assistant", "content": text}

@@ -83,6 +83,26 @@ def test_streaming_yields_all_tokens(client):
     assert done and toks == client.expected and finish
 
 
+def test_chat_streaming_yields_delta_chunks(client):
+    body = {"messages": [{"role": "user", "content": [5, 6, 7, 8]}], "max_tokens": 6, "ignore_eos": True, "stream": True}
+    with client.stream("POST", "/v1/chat/completions", json=body) as r:
+        toks, roles, finish, done = [], [], None, False
+        for line in r.iter_lines():
+            if not line.startswith("data: "):
+                continue
+            if line == "data: [DONE]":
+                done = True
+                break
+            ev = json.loads(line[6:])
+            assert ev["object"] == "chat.completion.chunk"
+            ch = ev["choices"][0]
+            toks += ch["token_ids"]
+            if "role" in ch["delta"]:
+                roles.append(ch["delta"]["role"])
+            finish = ch["finish_reason"] or finish
+    assert done and toks == client.expected and roles == ["assistant"] and finish == "length"
+
+
 def test_request_fields_and_cli():
     sp = sampling_from_body({"max_tokens": 9, "temperature": 0.7, "top_k": 5, "top_p": 0.9, "thinking_token_budget": 64,
                              "stop_token_ids": [2], "repetition_penalty": 1.1})
