@@ -351,9 +351,39 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                 yield "data: [DONE]\n\n"
                 return
 
+    def _n_choices(body) -> int:
+        n = int(body.get("n") or 1)
+        if n < 1 or n > 16:
+            raise HTTPException(400, "n must be between 1 and 16")
+        if n > 1 and body.get("stream"):
+            raise HTTPException(400, "streaming answers one choice (n = 1)")
+        return n
+
+    def _completion_choice(index: int, out) -> Dict[str, Any]:
+        lp = None
+        if out.logprobs is not None:
+            # the completions form: parallel lists over the output tokens
+            lp = {"tokens": [decode([t]) if tokenizer is not None else str(t) for t in out.output_token_ids],
+                  "token_ids": out.output_token_ids, "token_logprobs": [e[0] for e in out.logprobs],
+                  "top_logprobs": [{(decode([i]) if tokenizer is not None else str(i)): v for i, v in e[1]}
+                                   for e in out.logprobs]}
+        return {"index": index, "text": _text(out), "token_ids": out.output_token_ids, "logprobs": lp,
+                "finish_reason": out.finish_reason or "stop"}
+
     @app.post("/v1/completions")
     async def completions(body: Dict[str, Any]):
         ids = encode(body.get("prompt"))
+        n = _n_choices(body)
+        if n > 1:
+            # n independent requests (each draws from its own default seed, or from seed + index)
+            rids = [_submit(ids, dict(body, seed=body["seed"] + i) if body.get("seed") is not None else body)
+                    for i in range(n)]
+            outs = [await _finish(r) for r in rids]
+            done = sum(len(o.output_token_ids) for o in outs)
+            return JSONResponse({
+                "id": rids[0], "object": "text_completion", "created": int(time.time()), "model": model_name,
+                "choices": [_completion_choice(i, o) for i, o in enumerate(outs)],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": done, "total_tokens": len(ids) + done}})
         rid = _submit(ids, body)
         created = int(time.time())
         if body.get("stream"):
@@ -362,17 +392,9 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                         "choices": [{"index": 0, "text": decode(toks), "token_ids": toks, "finish_reason": finish}]}
             return StreamingResponse(_stream(rid, chunk), media_type="text/event-stream")
         out = await _finish(rid)
-        lp = None
-        if out.logprobs is not None:
-            # the completions form: parallel lists over the output tokens
-            lp = {"tokens": [decode([t]) if tokenizer is not None else str(t) for t in out.output_token_ids],
-                  "token_ids": out.output_token_ids, "token_logprobs": [e[0] for e in out.logprobs],
-                  "top_logprobs": [{(decode([i]) if tokenizer is not None else str(i)): v for i, v in e[1]}
-                                   for e in out.logprobs]}
         return JSONResponse({
             "id": rid, "object": "text_completion", "created": created, "model": model_name,
-            "choices": [{"index": 0, "text": _text(out), "token_ids": out.output_token_ids,
-                         "logprobs": lp, "finish_reason": out.finish_reason or "stop"}],
+            "choices": [_completion_choice(0, out)],
             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out.output_token_ids),
                       "total_tokens": len(ids) + len(out.output_token_ids)},
             "kv_transfer_params": out.kv_transfer_params})

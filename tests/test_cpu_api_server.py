@@ -103,6 +103,17 @@ def test_chat_streaming_yields_delta_chunks(client):
     assert done and toks == client.expected and roles == ["assistant"] and finish == "length"
 
 
+def test_n_choices_are_independent_samples(client):
+    body = {"prompt": [5, 6, 7, 8], "max_tokens": 6, "ignore_eos": True, "n": 3, "temperature": 1.0, "seed": 11}
+    r = client.post("/v1/completions", json=body)
+    assert r.status_code == 200
+    out = r.json()
+    assert [c["index"] for c in out["choices"]] == [0, 1, 2] and out["usage"]["completion_tokens"] == 18
+    assert len({tuple(c["token_ids"]) for c in out["choices"]}) > 1            # seeds 11, 12, 13 draw differently
+    assert client.post("/v1/completions", json=dict(body, stream=True)).status_code == 400
+    assert client.post("/v1/completions", json=dict(body, n=17)).status_code == 400
+
+
 def test_request_fields_and_cli():
     sp = sampling_from_body({"max_tokens": 9, "temperature": 0.7, "top_k": 5, "top_p": 0.9, "thinking_token_budget": 64,
                              "stop_token_ids": [2], "repetition_penalty": 1.1})
