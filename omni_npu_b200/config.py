@@ -277,7 +277,7 @@ class SchedulerConfig:
     # requests that are decoding take their next token inside the prefill steps of others (one row
     # each, counted against max_num_batched_tokens first) instead of waiting for the prompts to finish
     enable_mixed_batches: bool = False
-    policy: str = "fcfs"
+    policy: str = "fcfs"          # "fcfs" | "priority" (SamplingParams.priority: lower first, preempted last)
     # cache slots kept allocated past the tokens a step feeds (a draft head that runs a chain of
     # k steps writes its keys for k - 1 positions that are scheduled only in the next step)
     num_lookahead_tokens: int = 0

@@ -399,7 +399,8 @@ def build_engine_config(model: ModelConfig, model_path: Optional[str] = None, **
                             max_num_batched_tokens=kw.pop("max_num_batched_tokens", 8192),
                             max_model_len=kw.pop("max_model_len", min(8192, model.max_position_embeddings)),
                             enable_chunked_prefill=kw.pop("enable_chunked_prefill", True),
-                            enable_mixed_batches=kw.pop("enable_mixed_batches", False))
+                            enable_mixed_batches=kw.pop("enable_mixed_batches", False),
+                            policy=kw.pop("scheduling_policy", "fcfs"))
     comp = kw.pop("compilation_config", None)
     if isinstance(comp, dict):
         comp = CompilationConfig(cudagraph_mode=comp.get("cudagraph_mode", "FULL_DECODE_ONLY"),

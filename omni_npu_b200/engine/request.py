@@ -21,6 +21,9 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     thinking_token_budget: Optional[int] = None
     logprobs: Optional[int] = None
+    # scheduling priority under SchedulerConfig.policy == "priority": lower values are admitted first
+    # and preempted last (ties: earlier arrival first)
+    priority: int = 0
     # structured output: {"choice": [...]} | {"json_schema": ...} | {"json_object": True} | {"regex": ...} |
     # {"grammar": ebnf} (sample/structured.py); needs a tokenizer given to the engine
     structured: Optional[Dict[str, Any]] = None

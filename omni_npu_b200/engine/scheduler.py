@@ -80,7 +80,17 @@ class Scheduler:
             raise ValueError(f"prompt of {req.num_prompt_tokens} tokens does not fit the KV cache "
                              f"({usable} blocks of {self.block_size} tokens)")
         self.requests[req.request_id] = req
-        self.waiting.append(req)
+        if self.cfg.policy == "priority":
+            # keep the queue ordered by (priority, arrival): behind every request that is at least as urgent
+            key = (req.sampling_params.priority, req.arrival_time)
+            pos = len(self.waiting)
+            while pos > 0 and (self.waiting[pos - 1].sampling_params.priority,
+                               self.waiting[pos - 1].arrival_time) > key \
+                    and self.waiting[pos - 1].status != RequestStatus.PREEMPTED:
+                pos -= 1
+            self.waiting.insert(pos, req)
+        else:
+            self.waiting.append(req)
 
     def abort_request(self, request_id: str) -> None:
         req = self.requests.get(request_id)
@@ -184,8 +194,12 @@ class Scheduler:
         self._finished_since_last.append(req.request_id)
 
     def _preempt_one(self, protect: Request) -> Optional[Request]:
-        """Evict the most recently admitted running request (recompute later)."""
-        for victim in reversed(self.running):
+        """Evict the most recently admitted running request (recompute later); under the priority
+        policy the least urgent one (highest priority value, latest arrival)."""
+        order = list(reversed(self.running))
+        if self.cfg.policy == "priority":
+            order = sorted(self.running, key=lambda r: (r.sampling_params.priority, r.arrival_time), reverse=True)
+        for victim in order:
             if victim is protect:
                 continue
             self.running.remove(victim)

@@ -254,7 +254,8 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           frequency_penalty=float(body.get("frequency_penalty") or 0.0),
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
                           thinking_token_budget=body.get("thinking_token_budget"),
-                          logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body))
+                          logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body),
+                          priority=int(body.get("priority") or 0))
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):
@@ -471,6 +472,8 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
+    ap.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"],
+                    help="priority: requests carry a 'priority' field, lower values first")
     ap.add_argument("--enable-prefix-caching", action="store_true",
                     help="reuse the KV blocks of a cached token prefix for new requests")
     ap.add_argument("--enable-mixed-batches", action="store_true",
@@ -504,7 +507,7 @@ def main(argv=None) -> None:
               block_size=args.block_size, gpu_memory_utilization=args.gpu_memory_utilization,
               enforce_eager=args.enforce_eager, enable_chunked_prefill=args.enable_chunked_prefill,
               enable_mixed_batches=args.enable_mixed_batches,
-              enable_prefix_caching=args.enable_prefix_caching,
+              enable_prefix_caching=args.enable_prefix_caching, scheduling_policy=args.scheduling_policy,
               compilation_config=args.compilation_config, kv_transfer_config=args.kv_transfer_config,
               speculative_config=args.speculative_config, additional_config=args.additional_config,
               load_format=args.load_format, seed=args.seed)

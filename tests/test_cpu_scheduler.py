@@ -144,3 +144,26 @@ def test_half_computed_prompt_is_never_sampled_when_blocks_run_out():
     assert a.is_finished and b.is_finished
     assert len(a.output_token_ids) == 8 and len(b.output_token_ids) == 64
     assert s.pool.num_free == 10
+
+
+def test_priority_policy_orders_admission_and_picks_the_least_urgent_victim():
+    from omni_npu_b200.config import CacheConfig, SchedulerConfig
+    from omni_npu_b200.engine.request import Request, SamplingParams
+    from omni_npu_b200.engine.scheduler import Scheduler
+    sched = Scheduler(SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=64, policy="priority"),
+                      CacheConfig(block_size=4), num_blocks=64)
+    for rid, prio, t in (("late-urgent", 0, 3.0), ("early-relaxed", 5, 1.0), ("early-urgent", 0, 2.0), ("mid", 2, 2.5)):
+        sched.add_request(Request(rid, [1, 2, 3, 4, 5], SamplingParams(max_tokens=4, ignore_eos=True, priority=prio),
+                                  arrival_time=t))
+    assert [r.request_id for r in sched.waiting] == ["early-urgent", "late-urgent", "mid", "early-relaxed"]
+    out = sched.schedule()                                       # two sequence slots: the two urgent ones
+    assert [s.request.request_id for s in out.seqs] == ["early-urgent", "late-urgent"]
+    sched.update_from_output(out, [7, 7])
+    victim = sched._preempt_one(protect=None)
+    assert victim.request_id == "late-urgent"                    # same priority: the later arrival goes
+    # first come, first served ignores the field
+    fcfs = Scheduler(SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=64, max_model_len=64),
+                     CacheConfig(block_size=4), num_blocks=64)
+    for rid, prio in (("a", 9), ("b", 0)):
+        fcfs.add_request(Request(rid, [1, 2, 3], SamplingParams(max_tokens=2, priority=prio)))
+    assert [r.request_id for r in fcfs.waiting] == ["a", "b"]
