@@ -68,6 +68,7 @@ class Scheduler:
         self._finished_since_last: List[str] = []
         self._step = 0
         self.spec_stats = {"drafted": 0, "accepted": 0}
+        self.num_preemptions = 0          # over the life of the scheduler (finished requests leave ``requests``)
         self.kv_load_failures = 0
 
     # ------------------------------------------------------------------ intake
@@ -192,6 +193,7 @@ class Scheduler:
             self.pool.free(req.block_ids)
         req.block_ids = []
         self._finished_since_last.append(req.request_id)
+        self.requests.pop(req.request_id, None)      # a long-running server must not keep every request it ever saw
 
     def _preempt_one(self, protect: Request) -> Optional[Request]:
         """Evict the most recently admitted running request (recompute later); under the priority
@@ -209,6 +211,7 @@ class Scheduler:
             victim._registered_blocks = 0
             victim.status = RequestStatus.PREEMPTED
             victim.num_preemptions += 1
+            self.num_preemptions += 1
             self.waiting.appendleft(victim)
             return victim
         return None
@@ -225,6 +228,7 @@ class Scheduler:
         req.spec_token_ids = []
         req.status = RequestStatus.PREEMPTED
         req.num_preemptions += 1
+        self.num_preemptions += 1
         if req not in self.waiting:
             self.waiting.appendleft(req)
 

@@ -309,10 +309,22 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
     @app.get("/metrics")
     def metrics():
         c, e = loop.counters, llm.engine.stats
+        sch = llm.engine.scheduler
         lines = [f"omni_b200_requests_total {c['requests']}", f"omni_b200_requests_finished_total {c['finished']}",
                  f"omni_b200_output_tokens_total {c['output_tokens']}", f"omni_b200_engine_steps_total {e['steps']}",
-                 f"omni_b200_running_requests {len(llm.engine.scheduler.running)}",
-                 f"omni_b200_waiting_requests {len(llm.engine.scheduler.waiting)}"]
+                 f"omni_b200_prefill_steps_total {e.get('prefill_steps', 0)}",
+                 f"omni_b200_decode_steps_total {e.get('decode_steps', 0)}",
+                 f"omni_b200_spec_decode_steps_total {e.get('spec_decode_steps', 0)}",
+                 f"omni_b200_running_requests {len(sch.running)}",
+                 f"omni_b200_waiting_requests {len(sch.waiting)}",
+                 f"omni_b200_kv_cache_usage {sch.pool.usage:.6f}",
+                 f"omni_b200_kv_blocks_free {sch.pool.num_free}",
+                 f"omni_b200_preemptions_total {sch.num_preemptions}",
+                 f"omni_b200_prefix_cache_queries_total {sch.prefix_stats['requests']}",
+                 f"omni_b200_prefix_cache_hit_tokens_total {sch.prefix_stats['hit_tokens']}",
+                 f"omni_b200_spec_draft_tokens_total {sch.spec_stats['drafted']}",
+                 f"omni_b200_spec_accepted_tokens_total {sch.spec_stats['accepted']}",
+                 f"omni_b200_failed_steps_total {c.get('failed_steps', 0)}"]
         return PlainTextResponse("\n".join(lines) + "\n")
 
     def _submit(ids, body) -> str:

@@ -121,10 +121,12 @@ def test_half_computed_prompt_is_never_sampled_when_blocks_run_out():
     branch: no step may sample for it before its whole prompt is in the cache."""
     s = Scheduler(SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256,
                                   enable_chunked_prefill=True), CacheConfig(block_size=16), 10)
-    s.add_request(_req("B", 64, max_tokens=64))
+    b = _req("B", 64, max_tokens=64)
+    s.add_request(b)
     o = s.schedule()
     s.update_from_output(o, [7])                     # B: 4 blocks, decoding
-    s.add_request(_req("A", 128, max_tokens=8))
+    a = _req("A", 128, max_tokens=8)
+    s.add_request(a)
     sampled_early = []
     for _ in range(600):
         o = s.schedule()
@@ -140,8 +142,7 @@ def test_half_computed_prompt_is_never_sampled_when_blocks_run_out():
         if not s.has_unfinished():
             break
     assert not sampled_early
-    a, b = s.requests["A"], s.requests["B"]
-    assert a.is_finished and b.is_finished
+    assert a.is_finished and b.is_finished and not s.requests       # finished requests leave the scheduler's table
     assert len(a.output_token_ids) == 8 and len(b.output_token_ids) == 64
     assert s.pool.num_free == 10
 
