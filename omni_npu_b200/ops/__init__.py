@@ -627,7 +627,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            generator: Optional[torch.Generator] = None) -> torch.Tensor:
     """Temperature / top-k / top-p sampling; rows with temperature < 1e-5 are greedy."""
     if not logits.is_cuda:
-        return ref.sample(logits, temperature, top_k, top_p, generator)
+        return ref.sample(logits, temperature, top_k, top_p, generator, seeds, step_offset)
     _count(1)
     return _C().sample(logits, temperature, top_k, top_p, seeds, step_offset)
 

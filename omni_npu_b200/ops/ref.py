@@ -250,7 +250,11 @@ def apply_top_k_top_p(logits: torch.Tensor, top_k: Optional[torch.Tensor],
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
-           top_p: Optional[torch.Tensor], generator: Optional[torch.Generator] = None) -> torch.Tensor:
+           top_p: Optional[torch.Tensor], generator: Optional[torch.Generator] = None,
+           seeds: Optional[torch.Tensor] = None, step_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exponential-race sampling.  With ``seeds`` (int64 per row) every row draws from its own stream,
+    keyed by its seed and the step offset, as the CUDA kernel does (not the same numbers: the same
+    dependence on the seed)."""
     logits = logits.float()
     greedy = argmax(logits)
     if temperature is None:
@@ -258,7 +262,15 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
     t = temperature.clamp_min(1e-5).unsqueeze(1)
     masked = apply_top_k_top_p(logits / t, top_k, top_p)
     probs = masked.softmax(dim=-1)
-    e = torch.empty_like(probs).exponential_(1.0, generator=generator)
+    if seeds is not None:
+        off = int(step_offset.flatten()[0]) if step_offset is not None else 0
+        e = torch.empty_like(probs)
+        g = torch.Generator(device="cpu")
+        for i, sd in enumerate(seeds[: probs.shape[0]].tolist()):
+            g.manual_seed((int(sd) * 0x2545F4914F6CDD1D + off) & 0x7FFFFFFFFFFFFFFF)
+            e[i] = torch.empty(probs.shape[1]).exponential_(1.0, generator=g)
+    else:
+        e = torch.empty_like(probs).exponential_(1.0, generator=generator)
     tok = (probs / e).argmax(dim=-1).to(torch.int32)
     return torch.where(temperature < 1e-5, greedy, tok)
 

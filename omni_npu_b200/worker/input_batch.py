@@ -194,12 +194,22 @@ class InputBatch:
             self._upload_event.synchronize()
             self._upload_pending = False
 
-    def _fill_sampling(self, lay: StepLayout, rows: np.ndarray, n: int) -> None:
+    def _fill_sampling(self, lay: StepLayout, rows: np.ndarray, n: int, token_index=None) -> None:
+        """Sampling parameters of the step's rows.  The random stream of a row is keyed by the
+        request's seed mixed with the index of the token being sampled (``token_index``: output tokens
+        the request has so far), so a seeded request draws the same tokens whenever it runs and
+        whatever else the engine has done."""
         h = self.host_np
         h[lay.temp: lay.temp + n] = self.temperature[rows].view(np.int32)
         h[lay.top_k: lay.top_k + n] = self.top_k[rows]
         h[lay.top_p: lay.top_p + n] = self.top_p[rows].view(np.int32)
-        h[lay.seeds: lay.seeds + 2 * n] = self.seeds[rows].view(np.int32)
+        seeds = self.seeds[rows]
+        if token_index is not None and n:
+            idx = np.asarray(token_index, dtype=np.uint64) + np.uint64(1)
+            with np.errstate(over="ignore"):
+                seeds = ((seeds.astype(np.uint64) + idx * np.uint64(0x9E3779B97F4A7C15))
+                         & np.uint64(0x7FFFFFFFFFFFFFFF)).astype(np.int64)
+        h[lay.seeds: lay.seeds + 2 * n] = seeds.view(np.int32)
         if lay.S > n:
             h[lay.temp + n: lay.temp + lay.S] = 0
             h[lay.top_k + n: lay.top_k + lay.S] = 0
@@ -232,7 +242,7 @@ class InputBatch:
         h[lay.cu_q: lay.cu_q + lay.S + 1] = np.arange(lay.S + 1, dtype=np.int32) * q_len
         h[lay.logits_idx: lay.logits_idx + lay.S] = np.arange(lay.S, dtype=np.int32)
         h[lay.next_ids: lay.next_ids + lay.T] = -1
-        self._fill_sampling(lay, rows, n)
+        self._fill_sampling(lay, rows, n, [len(r.output_token_ids) for r in reqs])
         bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
         bt[:n] = self.block_table[rows]
         if lay.S > n:
@@ -269,7 +279,7 @@ class InputBatch:
             off += q
             cu[i + 1] = off
             h[lay.logits_idx + i] = off - 1
-        self._fill_sampling(lay, rows, n)
+        self._fill_sampling(lay, rows, n, [len(s.request.output_token_ids) for s in seqs])
         bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
         bt[:n] = self.block_table[rows]
         # successor of fed token j of sequence i = element (i, j) of the [n, max_q] matrix of
@@ -314,7 +324,7 @@ class InputBatch:
             off += q
             cu[i + 1] = off
             h[lay.logits_idx + i] = off - 1
-        self._fill_sampling(lay, rows, n)
+        self._fill_sampling(lay, rows, n, [len(s.request.output_token_ids) for s in seqs])
         bt = h[lay.bt: lay.bt + lay.S * lay.max_blocks].reshape(lay.S, lay.max_blocks)
         bt[:n] = self.block_table[rows]
         return rows, max_q

@@ -238,9 +238,9 @@ class ModelRunner:
             logits = self.model.compute_logits(hidden)
             if self._logits_fn is not None:
                 logits = self._logits_fn(logits)
+            # (no step offset: the staged seed of a row already carries the index of the token it samples)
             sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
-                                   views["top_p"][:num_samples], views["seeds"][:num_samples],
-                                   self.step_counter)
+                                   views["top_p"][:num_samples], views["seeds"][:num_samples], None)
             if self.mtp is None:
                 return sampled
             # successor of every fed token: known for prompt tokens, the fresh sample otherwise
@@ -384,7 +384,7 @@ class ModelRunner:
                 seeds = views["seeds"][:n].index_select(0, sel)
                 got = self.sampler(logits, views["temp"][:n].index_select(0, sel),
                                    views["top_k"][:n].index_select(0, sel), views["top_p"][:n].index_select(0, sel),
-                                   seeds, self.step_counter)
+                                   seeds, None)
                 tokens.index_copy_(0, sel, got.to(torch.int32))
         # a token id is >= 0 and exactly one rank holds it: the maximum over the group is the token
         import torch.distributed as dist
@@ -440,7 +440,7 @@ class ModelRunner:
                     logits = self._logits_fn(logits)
                 sampled = self.sampler(logits, views["temp"][:num_samples], views["top_k"][:num_samples],
                                        views["top_p"][:num_samples], views["seeds"][:num_samples],
-                                       self.step_counter).to(torch.int64)
+                                       None).to(torch.int64)
             else:
                 for _, t in sorted(out.items()):
                     pp.comm.send(t.contiguous(), dst=pp.rank_in_group + 1)

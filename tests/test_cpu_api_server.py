@@ -110,6 +110,12 @@ def test_n_choices_are_independent_samples(client):
     out = r.json()
     assert [c["index"] for c in out["choices"]] == [0, 1, 2] and out["usage"]["completion_tokens"] == 18
     assert len({tuple(c["token_ids"]) for c in out["choices"]}) > 1            # seeds 11, 12, 13 draw differently
+    # a seeded request draws the same tokens whenever it runs, whatever the engine did in between
+    client.post("/v1/completions", json={"prompt": [9, 9, 9], "max_tokens": 3, "temperature": 1.0})
+    again = client.post("/v1/completions", json=body).json()
+    assert [c["token_ids"] for c in again["choices"]] == [c["token_ids"] for c in out["choices"]]
+    alone = client.post("/v1/completions", json=dict(body, n=1, seed=12)).json()
+    assert alone["choices"][0]["token_ids"] == out["choices"][1]["token_ids"]
     assert client.post("/v1/completions", json=dict(body, stream=True)).status_code == 400
     assert client.post("/v1/completions", json=dict(body, n=17)).status_code == 400
 

@@ -48,7 +48,9 @@ def test_prefill_staging_positions_slots_and_next_tokens():
     assert v["seq_lens"][:2].tolist() == [7, 10] and v["cu_q"][:3].tolist() == [0, 7, 13]
     assert v["logits_idx"][:2].tolist() == [6, 12]
     assert v["next_ids"][:7].tolist() == list(range(11, 17)) + [-1]          # last prompt token: successor unknown
-    assert abs(float(v["temp"][0]) - 0.7) < 1e-6 and int(v["top_k"][0]) == 3 and int(v["seeds"][0]) == 11
+    assert abs(float(v["temp"][0]) - 0.7) < 1e-6 and int(v["top_k"][0]) == 3
+    # the staged seed: the request's seed (11) mixed with the index of the token being sampled (the first)
+    assert int(v["seeds"][0]) == (11 + 0x9E3779B97F4A7C15) & 0x7FFFFFFFFFFFFFFF
     assert float(v["top_p"][1]) == 1.0 and v["bt"][0, :2].tolist() == [5, 2] and v["bt"][1, :3].tolist() == [9, 1, 4]
 
 
