@@ -302,6 +302,35 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
     async def wake_up():
         return {"status": "awake", "mapped_bytes": llm.wake_up()}
 
+    @app.get("/ping")
+    def ping():
+        return PlainTextResponse("pong")
+
+    @app.get("/version")
+    def version():
+        from .. import __version__ as v
+        return {"version": v}
+
+    @app.post("/tokenize")
+    async def tokenize(body: Dict[str, Any]):
+        """Token ids of ``prompt`` (or of ``messages`` through the chat template)."""
+        if tokenizer is None:
+            raise HTTPException(400, "this server has no tokenizer")
+        if body.get("messages") is not None:
+            if not hasattr(tokenizer, "apply_chat_template"):
+                raise HTTPException(400, "the tokenizer has no chat template")
+            ids = tokenizer.apply_chat_template(body["messages"], tokenize=True,
+                                                add_generation_prompt=bool(body.get("add_generation_prompt", True)))
+        else:
+            ids = tokenizer.encode(body.get("prompt") or "")
+        return {"tokens": list(ids), "count": len(ids), "max_model_len": llm.config.scheduler.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(body: Dict[str, Any]):
+        if tokenizer is None:
+            raise HTTPException(400, "this server has no tokenizer")
+        return {"prompt": tokenizer.decode([int(t) for t in body.get("tokens") or []])}
+
     @app.get("/v1/models")
     def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model"}]}

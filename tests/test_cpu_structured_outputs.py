@@ -135,3 +135,19 @@ def test_stop_strings_end_the_request_and_cut_the_text(tokenizer):
     with TestClient(app) as c:
         assert c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 4, "stop": "x"}).status_code == 400
     app.state.engine_loop.shutdown()
+
+
+def test_tokenize_detokenize_and_version_routes(tokenizer):
+    from starlette.testclient import TestClient
+    from omni_npu_b200.serving.api_server import build_app
+    app = build_app(_llm(tokenizer), tokenizer, "tiny")
+    with TestClient(app) as c:
+        assert c.get("/ping").text == "pong" and "version" in c.get("/version").json()
+        t = c.post("/tokenize", json={"prompt": "the cat is red"}).json()
+        assert t["count"] == 4 and t["tokens"] == tokenizer.encode("the cat is red") and t["max_model_len"] == 128
+        assert c.post("/detokenize", json={"tokens": t["tokens"]}).json()["prompt"].split() == ["the", "cat", "is", "red"]
+    app.state.engine_loop.shutdown()
+    app = build_app(_llm(None), None, "tiny")
+    with TestClient(app) as c:
+        assert c.post("/tokenize", json={"prompt": "x"}).status_code == 400
+    app.state.engine_loop.shutdown()
