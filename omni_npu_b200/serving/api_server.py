@@ -28,6 +28,7 @@ from typing import Any, Dict, List, Optional
 
 from ..engine.request import RequestOutput, SamplingParams
 from ..logger import logger
+from ..sample.structured import structured_spec_from_body
 
 
 class EngineLoop:
@@ -227,9 +228,6 @@ class EngineLoop:
         self.wake.set()
         if self.thread is not None:
             self.thread.join(timeout=5)
-
-
-from ..sample.structured import structured_spec_from_body  # noqa: E402
 
 
 def _logprobs_from_body(body: Dict[str, Any]) -> Optional[int]:
