@@ -329,10 +329,27 @@ class LLM:
             config = build_engine_config(mc, model_path=path, **kw)
         self.config = config
         self.engine = LLMEngine(config)
+        self.tokenizer = None             # loaded on first use from the model directory (or set by the caller)
+
+    def get_tokenizer(self):
+        """The model directory's tokenizer (None when there is none): text prompts are encoded with
+        it, outputs get their ``text``, structured outputs are compiled against it."""
+        if self.tokenizer is None and self.config.model_path:
+            try:
+                from transformers import AutoTokenizer
+                self.tokenizer = AutoTokenizer.from_pretrained(self.config.model_path)
+            except Exception:                          # no tokenizer files beside the weights
+                return None
+            try:
+                self.enable_structured_outputs(self.tokenizer)
+            except Exception:                          # the grammar package is optional
+                pass
+        return self.tokenizer
 
     def enable_structured_outputs(self, tokenizer) -> None:
         """Give the engine the tokenizer that structured outputs (``SamplingParams.structured``) are
         compiled against; call it on every rank."""
+        self.tokenizer = self.tokenizer or tokenizer
         self.engine.worker.model_runner.enable_structured_outputs(tokenizer)
 
     def start_profile(self) -> None:
@@ -352,9 +369,17 @@ class LLM:
     def wake_up(self, tags=None) -> int:
         return self.engine.worker.wake_up(tags)
 
-    def generate(self, prompts: Sequence[Sequence[int]],
+    def generate(self, prompts: Sequence[Union[str, Sequence[int]]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  ) -> List[RequestOutput]:
+        """Run the prompts to completion.  A prompt is a list of token ids, or text when the model
+        directory has a tokenizer (the outputs then carry ``text`` as well)."""
+        tok = self.tokenizer
+        if any(isinstance(p, str) for p in prompts):
+            tok = self.get_tokenizer()
+            if tok is None:
+                raise ValueError("text prompts need a tokenizer in the model directory; pass token ids instead")
+            prompts = [tok.encode(p) if isinstance(p, str) else p for p in prompts]
         sps = sampling_params if isinstance(sampling_params, (list, tuple)) else [sampling_params] * len(prompts)
         order: Dict[str, int] = {}
         now = time.monotonic()
@@ -373,6 +398,10 @@ class LLM:
                 results[order[o.request_id]] = o
         if self.engine.device.type == "cuda":
             ops.check_status(self.engine.device)
+        if tok is not None:
+            for o in results:
+                if o is not None:
+                    o.text = tok.decode(o.output_token_ids)
         return results  # type: ignore[return-value]
 
 

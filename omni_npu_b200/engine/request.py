@@ -140,6 +140,7 @@ class RequestOutput:
     tpot: Optional[float] = None           # mean seconds per output token after the first
     kv_transfer_params: Optional[Dict[str, Any]] = None
     logprobs: Optional[List[Tuple[float, List[Tuple[int, float]]]]] = None    # per output token, when asked for
+    text: Optional[str] = None             # decoded output, when a tokenizer is at hand
 
     @classmethod
     def from_request(cls, r: Request) -> "RequestOutput":

@@ -151,3 +151,25 @@ def test_tokenize_detokenize_and_version_routes(tokenizer):
     with TestClient(app) as c:
         assert c.post("/tokenize", json={"prompt": "x"}).status_code == 400
     app.state.engine_loop.shutdown()
+
+
+def test_text_prompts_with_a_tokenizer_in_the_model_directory(tokenizer, tmp_path):
+    """``LLM(model=<directory>)`` finds the tokenizer beside the weights: text prompts are encoded,
+    outputs carry their text, structured outputs work without further set-up."""
+    import reference_llama as refm
+    from omni_npu_b200.config import tiny_llama
+    from test_cpu_plumbing import _save
+    cfg = tiny_llama()
+    weights = refm.make_weights(cfg, seed=0)
+    _save(weights, cfg, str(tmp_path))
+    tokenizer.save_pretrained(str(tmp_path))
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_num_seqs=4, max_num_batched_tokens=64,
+              max_model_len=128, block_size=16, num_gpu_blocks=32)
+    ids = tokenizer.encode("the cat is")
+    a, b = llm.generate(["the cat is", ids], SamplingParams(max_tokens=5, ignore_eos=True))
+    assert a.output_token_ids == b.output_token_ids == refm.greedy_generate(weights, cfg, ids, 5)
+    assert a.text == tokenizer.decode(a.output_token_ids)
+    c = llm.generate(["the cat is"], SamplingParams(max_tokens=4, structured={"choice": ["red", "blue"]}))[0]
+    assert c.text.replace("</s>", "").strip() in ("red", "blue")
+    with pytest.raises(ValueError):
+        _llm(None).generate(["text without a tokenizer"], SamplingParams(max_tokens=2))
