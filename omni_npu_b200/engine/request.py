@@ -21,6 +21,10 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     thinking_token_budget: Optional[int] = None
     logprobs: Optional[int] = None
+    # added to the logits of the named tokens before sampling ({token id: bias}, as in the OpenAI API)
+    logit_bias: Optional[Dict[int, float]] = None
+    # the end-of-sequence and stop tokens cannot be sampled before this many output tokens
+    min_tokens: int = 0
     # scheduling priority under SchedulerConfig.policy == "priority": lower values are admitted first
     # and preempted last (ties: earlier arrival first)
     priority: int = 0

@@ -253,7 +253,8 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
                           thinking_token_budget=body.get("thinking_token_budget"),
                           logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body),
-                          priority=int(body.get("priority") or 0))
+                          priority=int(body.get("priority") or 0), min_tokens=int(body.get("min_tokens") or 0),
+                          logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None)
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=None, tool_parser=None):

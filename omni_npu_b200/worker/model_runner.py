@@ -480,7 +480,8 @@ class ModelRunner:
         """Whether sampling for this request needs its token history (penalties, thinking budget)."""
         sp = req.sampling_params
         return (sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
-                or sp.structured is not None)
+                or sp.structured is not None or bool(sp.logit_bias)
+                or (sp.min_tokens > 0 and len(req.output_token_ids) < sp.min_tokens))
 
     def enable_structured_outputs(self, tokenizer) -> None:
         """Structured outputs need the tokenizer's vocabulary (token id -> text)."""
@@ -523,7 +524,12 @@ class ModelRunner:
         if so_rows and so is None:
             raise RuntimeError("a request asks for structured output but the engine has no tokenizer "
                                "(LLM.enable_structured_outputs)")
-        if not pen_rows and not think_rows and not lp_rows and not so_rows and extra is None:
+        # logit bias, and end tokens held back until min_tokens outputs exist
+        bias_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.logit_bias]
+        min_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.min_tokens > 0
+                    and len(s.request.output_token_ids) < s.request.sampling_params.min_tokens]
+        if not pen_rows and not think_rows and not lp_rows and not so_rows and not bias_rows and not min_rows \
+                and extra is None:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -562,6 +568,19 @@ class ModelRunner:
                                [seqs[i].request.request_id for i in think_rows],
                                [seqs[i].request.output_token_ids for i in think_rows])
                 logits = logits.index_copy(0, idx, sub)
+            for i in bias_rows:
+                lb = seqs[i].request.sampling_params.logit_bias
+                ids = torch.tensor([int(t) for t in lb if 0 <= int(t) < V], dtype=torch.long, device=dev)
+                vals = torch.tensor([float(v) for t, v in lb.items() if 0 <= int(t) < V], dtype=torch.float32, device=dev)
+                logits[i, ids] += vals
+            for i in min_rows:
+                r = seqs[i].request
+                ends = set(r.sampling_params.stop_token_ids or ())
+                if r.eos_token_id is not None and not r.sampling_params.ignore_eos:
+                    ends.add(r.eos_token_id)
+                ends = [t for t in ends if 0 <= t < V]
+                if ends:
+                    logits[i, torch.tensor(ends, dtype=torch.long, device=dev)] = float("-inf")
             if so_rows:
                 rids = []
                 for i in so_rows:

@@ -134,7 +134,12 @@ def sampling_params_from_vllm(sp):
         repetition_penalty=float(sp.repetition_penalty or 1.0),
         thinking_token_budget=(getattr(sp, "extra_args", None) or {}).get("thinking_token_budget"),
         # vLLM's 0 = the sampled token's log-probability only; the runner keeps at least one alternative
-        logprobs=None if want_lp is None else max(1, min(20, int(want_lp))))
+        logprobs=None if want_lp is None else max(1, min(20, int(want_lp))),
+        # vLLM's own sampler (and with it its logits processors) is not on this worker's path: the
+        # bias and the minimum length are applied by the runner's logits hook instead
+        logit_bias={int(k): float(v) for k, v in (getattr(sp, "logit_bias", None) or {}).items()} or None,
+        min_tokens=int(getattr(sp, "min_tokens", 0) or 0),
+        stop_token_ids=tuple(int(t) for t in (getattr(sp, "all_stop_token_ids", None) or ())))
 
 
 def grammar_mask_fn(step_req_ids, structured_req_ids, bitmask):

@@ -55,3 +55,18 @@ def test_logprobs_with_speculative_decoding_are_refused():
     llm = _llm(speculative_config={"method": "ngram", "num_speculative_tokens": 2})
     with pytest.raises(ValueError):
         llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2, logprobs=1))
+
+
+def test_logit_bias_and_min_tokens_shape_what_is_sampled():
+    prompts = [[5, 6, 7, 8]]
+    free = _llm().generate(prompts, SamplingParams(max_tokens=4, ignore_eos=True))[0].output_token_ids
+    # a large bias makes a token win; a large negative one bans the token greedy decoding would pick
+    forced = _llm().generate(prompts, SamplingParams(max_tokens=4, ignore_eos=True, logit_bias={42: 100.0}))[0]
+    assert forced.output_token_ids == [42] * 4
+    banned = _llm().generate(prompts, SamplingParams(max_tokens=4, ignore_eos=True, logit_bias={free[0]: -100.0}))[0]
+    assert banned.output_token_ids[0] != free[0]
+    # stop token = the first free token: without min_tokens the request ends at once, with it only later
+    stops = SamplingParams(max_tokens=6, stop_token_ids=(free[0],))
+    assert _llm().generate(prompts, stops)[0].output_token_ids == [free[0]]
+    held = _llm().generate(prompts, SamplingParams(max_tokens=6, stop_token_ids=(free[0],), min_tokens=3))[0]
+    assert len(held.output_token_ids) >= 3 and free[0] not in held.output_token_ids[:3]
