@@ -125,6 +125,10 @@ def sampling_params_from_vllm(sp):
         return SamplingParams(max_tokens=1 << 30, ignore_eos=True)
     if getattr(sp, "prompt_logprobs", None):
         raise ValueError("prompt_logprobs are not supported by the B200 worker")
+    # parameters that vLLM's own sampler would honour through logits processors this worker does not run
+    for name in ("min_p", "bad_words", "allowed_token_ids", "logits_processors"):
+        if getattr(sp, name, None):
+            raise ValueError(f"sampling parameter {name} is not supported by the B200 worker")
     want_lp = getattr(sp, "logprobs", None)
     top_k = int(getattr(sp, "top_k", 0) or 0)
     return SamplingParams(
