@@ -13,7 +13,7 @@ with the same package; under vLLM this package's worker applies vLLM's bitmask i
 from __future__ import annotations
 
 import json
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, Optional, Sequence
 
 import torch
 
