@@ -25,6 +25,10 @@ class SamplingParams:
     logit_bias: Optional[Dict[int, float]] = None
     # the end-of-sequence and stop tokens cannot be sampled before this many output tokens
     min_tokens: int = 0
+    # tokens whose probability (after temperature) is below min_p x the largest one cannot be sampled
+    min_p: float = 0.0
+    # when given, only these tokens can be sampled
+    allowed_token_ids: Optional[Sequence[int]] = None
     # scheduling priority under SchedulerConfig.policy == "priority": lower values are admitted first
     # and preempted last (ties: earlier arrival first)
     priority: int = 0

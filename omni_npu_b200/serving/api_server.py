@@ -254,6 +254,7 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           thinking_token_budget=body.get("thinking_token_budget"),
                           logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body),
                           priority=int(body.get("priority") or 0), min_tokens=int(body.get("min_tokens") or 0),
+                          min_p=float(body.get("min_p") or 0.0), allowed_token_ids=body.get("allowed_token_ids") or None,
                           logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None)
 
 

@@ -480,7 +480,7 @@ class ModelRunner:
         """Whether sampling for this request needs its token history (penalties, thinking budget)."""
         sp = req.sampling_params
         return (sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
-                or sp.structured is not None or bool(sp.logit_bias)
+                or sp.structured is not None or bool(sp.logit_bias) or sp.min_p > 0 or bool(sp.allowed_token_ids)
                 or (sp.min_tokens > 0 and len(req.output_token_ids) < sp.min_tokens))
 
     def enable_structured_outputs(self, tokenizer) -> None:
@@ -528,8 +528,10 @@ class ModelRunner:
         bias_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.logit_bias]
         min_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.min_tokens > 0
                     and len(s.request.output_token_ids) < s.request.sampling_params.min_tokens]
+        allow_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.allowed_token_ids]
+        minp_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.min_p > 0]
         if not pen_rows and not think_rows and not lp_rows and not so_rows and not bias_rows and not min_rows \
-                and extra is None:
+                and not allow_rows and not minp_rows and extra is None:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -581,6 +583,16 @@ class ModelRunner:
                 ends = [t for t in ends if 0 <= t < V]
                 if ends:
                     logits[i, torch.tensor(ends, dtype=torch.long, device=dev)] = float("-inf")
+            for i in allow_rows:
+                ok = torch.tensor([int(t) for t in seqs[i].request.sampling_params.allowed_token_ids if 0 <= int(t) < V],
+                                  dtype=torch.long, device=dev)
+                keep = torch.zeros(V, dtype=torch.bool, device=dev)
+                keep[ok] = True
+                logits[i] = logits[i].masked_fill(~keep, float("-inf"))
+            for i in minp_rows:
+                sp = seqs[i].request.sampling_params
+                p = torch.softmax(logits[i] / max(float(sp.temperature), 1e-5), dim=-1)
+                logits[i] = logits[i].masked_fill(p < sp.min_p * p.max(), float("-inf"))
             if so_rows:
                 rids = []
                 for i in so_rows:

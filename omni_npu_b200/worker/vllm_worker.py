@@ -126,7 +126,7 @@ def sampling_params_from_vllm(sp):
     if getattr(sp, "prompt_logprobs", None):
         raise ValueError("prompt_logprobs are not supported by the B200 worker")
     # parameters that vLLM's own sampler would honour through logits processors this worker does not run
-    for name in ("min_p", "bad_words", "allowed_token_ids", "logits_processors"):
+    for name in ("bad_words", "logits_processors"):
         if getattr(sp, name, None):
             raise ValueError(f"sampling parameter {name} is not supported by the B200 worker")
     want_lp = getattr(sp, "logprobs", None)
@@ -142,7 +142,8 @@ def sampling_params_from_vllm(sp):
         # vLLM's own sampler (and with it its logits processors) is not on this worker's path: the
         # bias and the minimum length are applied by the runner's logits hook instead
         logit_bias={int(k): float(v) for k, v in (getattr(sp, "logit_bias", None) or {}).items()} or None,
-        min_tokens=int(getattr(sp, "min_tokens", 0) or 0),
+        min_tokens=int(getattr(sp, "min_tokens", 0) or 0), min_p=float(getattr(sp, "min_p", 0.0) or 0.0),
+        allowed_token_ids=list(getattr(sp, "allowed_token_ids", None) or ()) or None,
         stop_token_ids=tuple(int(t) for t in (getattr(sp, "all_stop_token_ids", None) or ())))
 
 

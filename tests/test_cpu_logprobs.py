@@ -70,3 +70,14 @@ def test_logit_bias_and_min_tokens_shape_what_is_sampled():
     assert _llm().generate(prompts, stops)[0].output_token_ids == [free[0]]
     held = _llm().generate(prompts, SamplingParams(max_tokens=6, stop_token_ids=(free[0],), min_tokens=3))[0]
     assert len(held.output_token_ids) >= 3 and free[0] not in held.output_token_ids[:3]
+
+
+def test_allowed_token_ids_and_min_p_restrict_the_candidates():
+    prompts = [[5, 6, 7, 8]]
+    only = _llm().generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True, temperature=1.0, seed=1,
+                                                    allowed_token_ids=[10, 11, 12]))[0]
+    assert set(only.output_token_ids) <= {10, 11, 12}
+    # min_p = 1: only the most likely token survives, so sampling at any temperature is greedy decoding
+    greedy = _llm().generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))[0].output_token_ids
+    hot = _llm().generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True, temperature=5.0, seed=3, min_p=1.0))[0]
+    assert hot.output_token_ids == greedy
