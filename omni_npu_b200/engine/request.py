@@ -29,6 +29,9 @@ class SamplingParams:
     min_p: float = 0.0
     # when given, only these tokens can be sampled
     allowed_token_ids: Optional[Sequence[int]] = None
+    # token sequences that must not appear in the output: once the output ends with all but the last
+    # token of one of them, that last token cannot be sampled
+    bad_words_token_ids: Optional[Sequence[Sequence[int]]] = None
     # scheduling priority under SchedulerConfig.policy == "priority": lower values are admitted first
     # and preempted last (ties: earlier arrival first)
     priority: int = 0

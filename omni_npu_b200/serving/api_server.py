@@ -241,7 +241,23 @@ def _logprobs_from_body(body: Dict[str, Any]) -> Optional[int]:
     return max(1, int(top if top else lp))
 
 
-def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
+def bad_words_token_ids(words, tokenizer) -> Optional[list]:
+    """Token sequences of the words a request bans: each word as it is written at the start of a text
+    and as it is written after a space (most vocabularies spell the two differently)."""
+    if not words:
+        return None
+    if tokenizer is None:
+        raise ValueError("bad_words needs a tokenizer; this server has none")
+    seqs = []
+    for w in words:
+        for text in (w.lstrip(), " " + w.lstrip()):
+            ids = [int(t) for t in tokenizer.encode(text, add_special_tokens=False)]
+            if ids and ids not in seqs:
+                seqs.append(ids)
+    return seqs or None
+
+
+def sampling_from_body(body: Dict[str, Any], tokenizer=None) -> SamplingParams:
     stop_ids = body.get("stop_token_ids") or ()
     return SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
                           temperature=float(body.get("temperature", 1.0 if body.get("top_p") else 0.0) or 0.0),
@@ -255,6 +271,7 @@ def sampling_from_body(body: Dict[str, Any]) -> SamplingParams:
                           logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body),
                           priority=int(body.get("priority") or 0), min_tokens=int(body.get("min_tokens") or 0),
                           min_p=float(body.get("min_p") or 0.0), allowed_token_ids=body.get("allowed_token_ids") or None,
+                          bad_words_token_ids=bad_words_token_ids(body.get("bad_words"), tokenizer),
                           logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None)
 
 
@@ -360,7 +377,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
         stop = body.get("stop")
         stop = [stop] if isinstance(stop, str) else list(stop or [])
         try:
-            return loop.submit(ids, sampling_from_body(body), body.get("kv_transfer_params"), stop=stop)
+            return loop.submit(ids, sampling_from_body(body, tokenizer), body.get("kv_transfer_params"), stop=stop)
         except ValueError as e:
             raise HTTPException(400, str(e))
 

@@ -480,7 +480,8 @@ class ModelRunner:
         """Whether sampling for this request needs its token history (penalties, thinking budget)."""
         sp = req.sampling_params
         return (sp.has_penalties or sp.thinking_token_budget is not None or bool(sp.logprobs)
-                or sp.structured is not None or bool(sp.logit_bias) or sp.min_p > 0 or bool(sp.allowed_token_ids)
+                or sp.structured is not None or bool(sp.logit_bias) or sp.min_p > 0
+                or bool(sp.allowed_token_ids) or bool(sp.bad_words_token_ids)
                 or (sp.min_tokens > 0 and len(req.output_token_ids) < sp.min_tokens))
 
     def enable_structured_outputs(self, tokenizer) -> None:
@@ -529,9 +530,10 @@ class ModelRunner:
         min_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.min_tokens > 0
                     and len(s.request.output_token_ids) < s.request.sampling_params.min_tokens]
         allow_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.allowed_token_ids]
+        bad_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.bad_words_token_ids]
         minp_rows = [i for i, s in enumerate(seqs) if s.samples and s.request.sampling_params.min_p > 0]
         if not pen_rows and not think_rows and not lp_rows and not so_rows and not bias_rows and not min_rows \
-                and not allow_rows and not minp_rows and extra is None:
+                and not allow_rows and not minp_rows and not bad_rows and extra is None:
             return None
         for i in think_rows:
             r = seqs[i].request
@@ -589,6 +591,14 @@ class ModelRunner:
                 keep = torch.zeros(V, dtype=torch.bool, device=dev)
                 keep[ok] = True
                 logits[i] = logits[i].masked_fill(~keep, float("-inf"))
+            for i in bad_rows:
+                out_ids = list(seqs[i].request.output_token_ids)
+                banned = [int(w[-1]) for w in seqs[i].request.sampling_params.bad_words_token_ids
+                          if len(w) and 0 <= int(w[-1]) < V
+                          and (len(w) == 1 or (len(out_ids) >= len(w) - 1
+                                               and out_ids[len(out_ids) - len(w) + 1:] == [int(t) for t in w[:-1]]))]
+                if banned:
+                    logits[i, torch.tensor(banned, dtype=torch.long, device=dev)] = float("-inf")
             for i in minp_rows:
                 sp = seqs[i].request.sampling_params
                 p = torch.softmax(logits[i] / max(float(sp.temperature), 1e-5), dim=-1)

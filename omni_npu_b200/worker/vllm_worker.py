@@ -126,9 +126,12 @@ def sampling_params_from_vllm(sp):
     if getattr(sp, "prompt_logprobs", None):
         raise ValueError("prompt_logprobs are not supported by the B200 worker")
     # parameters that vLLM's own sampler would honour through logits processors this worker does not run
-    for name in ("bad_words", "logits_processors"):
-        if getattr(sp, name, None):
-            raise ValueError(f"sampling parameter {name} is not supported by the B200 worker")
+    if getattr(sp, "logits_processors", None):
+        raise ValueError("sampling parameter logits_processors is not supported by the B200 worker")
+    # vLLM tokenizes the banned words when it takes the request in; without that list they cannot be honoured
+    bad = getattr(sp, "bad_words_token_ids", None)
+    if getattr(sp, "bad_words", None) and not bad:
+        raise ValueError("sampling parameter bad_words reached the B200 worker without its token ids")
     want_lp = getattr(sp, "logprobs", None)
     top_k = int(getattr(sp, "top_k", 0) or 0)
     return SamplingParams(
@@ -144,6 +147,7 @@ def sampling_params_from_vllm(sp):
         logit_bias={int(k): float(v) for k, v in (getattr(sp, "logit_bias", None) or {}).items()} or None,
         min_tokens=int(getattr(sp, "min_tokens", 0) or 0), min_p=float(getattr(sp, "min_p", 0.0) or 0.0),
         allowed_token_ids=list(getattr(sp, "allowed_token_ids", None) or ()) or None,
+        bad_words_token_ids=[list(w) for w in bad] if bad else None,
         stop_token_ids=tuple(int(t) for t in (getattr(sp, "all_stop_token_ids", None) or ())))
 
 

@@ -81,3 +81,32 @@ def test_allowed_token_ids_and_min_p_restrict_the_candidates():
     greedy = _llm().generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))[0].output_token_ids
     hot = _llm().generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True, temperature=5.0, seed=3, min_p=1.0))[0]
     assert hot.output_token_ids == greedy
+
+
+def test_bad_words_ban_a_token_only_after_its_prefix():
+    prompts = [[5, 6, 7, 8]]
+    free = _llm().generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))[0].output_token_ids
+    # a one-token word is banned everywhere
+    one = _llm().generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True, bad_words_token_ids=[[free[0]]]))[0]
+    assert free[0] not in one.output_token_ids
+    # a two-token word: its first token may come, the second not right after it
+    two = _llm().generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True,
+                                                  bad_words_token_ids=[[free[1], free[2]]]))[0].output_token_ids
+    assert two[:2] == free[:2] and two[2] != free[2]
+    # a word whose prefix never appears changes nothing
+    same = _llm().generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True,
+                                                   bad_words_token_ids=[[96, free[0]]]))[0].output_token_ids
+    assert same == free
+
+
+def test_server_turns_bad_words_into_token_sequences():
+    from omni_npu_b200.serving.api_server import bad_words_token_ids, sampling_from_body
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [100 + len(text)] if text.startswith(" ") else [len(text)]
+    assert bad_words_token_ids(["abc", " de"], Tok()) == [[3], [104], [2], [103]]
+    assert sampling_from_body({"bad_words": ["abc"]}, Tok()).bad_words_token_ids == [[3], [104]]
+    assert sampling_from_body({}, None).bad_words_token_ids is None
+    with pytest.raises(ValueError, match="tokenizer"):
+        sampling_from_body({"bad_words": ["abc"]}, None)
