@@ -111,6 +111,13 @@ class LLMEngine:
             raise ValueError("logprobs must be between 0 and 20")
         if sp.logprobs and (runner.pcp_group is not None or self.dp_group is not None):
             raise ValueError("logprobs are not supported with prefill-context or data parallelism")
+        if sp.prompt_logprobs is not None:
+            if not 0 <= int(sp.prompt_logprobs) <= 20:
+                raise ValueError("prompt_logprobs must be between 0 and 20")
+            if speculative or runner.pcp_group is not None or runner.pp_group is not None or self.dp_group is not None \
+                    or runner.kv_connector is not None:
+                raise ValueError("prompt_logprobs are not supported with speculative decoding, KV connectors, "
+                                 "pipeline, prefill-context or data parallelism")
         if sp.thinking_token_budget is not None and not runner.thinking_processor.enabled:
             raise ValueError("thinking_token_budget needs a reasoning config with think start / end "
                              "token ids (additional_config['reasoning_config'], --reasoning-config)")
@@ -239,6 +246,8 @@ class LLMEngine:
         finished = self.scheduler.update_from_output(out, tokens, drafts=drafts)
         for idx, entry in (getattr(self.worker.model_runner, "last_logprobs", None) or {}).items():
             out.seqs[idx].request.logprobs.append(entry[:2])        # (log-probability, alternatives); the rank stays behind
+        for idx, (first, entries) in (getattr(self.worker.model_runner, "last_prompt_logprobs", None) or {}).items():
+            out.seqs[idx].request.prompt_logprobs[first: first + len(entries)] = entries
         st = self.stats
         st["steps"] += 1
         st[out.kind + "_steps"] += 1

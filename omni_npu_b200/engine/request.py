@@ -21,6 +21,9 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     thinking_token_budget: Optional[int] = None
     logprobs: Optional[int] = None
+    # log-probabilities of the prompt's own tokens (each given the tokens before it) with this many
+    # most likely alternatives; 0 asks for the prompt tokens' values alone
+    prompt_logprobs: Optional[int] = None
     # added to the logits of the named tokens before sampling ({token id: bias}, as in the OpenAI API)
     logit_bias: Optional[Dict[int, float]] = None
     # the end-of-sequence and stop tokens cannot be sampled before this many output tokens
@@ -69,7 +72,7 @@ class Request:
                  "block_ids", "num_computed_tokens", "arrival_time", "first_token_time",
                  "finish_time", "kv_transfer_params", "eos_token_id", "num_preemptions",
                  "spec_token_ids", "client_index", "num_external_tokens", "_block_hashes",
-                 "_registered_blocks", "logprobs")
+                 "_registered_blocks", "logprobs", "prompt_logprobs")
 
     def __init__(self, request_id: str, prompt_token_ids: Sequence[int],
                  sampling_params: Optional[SamplingParams] = None,
@@ -98,6 +101,10 @@ class Request:
         # one entry per output token when sampling_params.logprobs is set:
         # (log-probability of the token, [(token id, log-probability), ...] of the most likely tokens)
         self.logprobs: List[Tuple[float, List[Tuple[int, float]]]] = []
+        # one entry per prompt token when sampling_params.prompt_logprobs is set (None for the first
+        # token, which has nothing before it), same shape as an entry of ``logprobs``
+        self.prompt_logprobs: Optional[List[Optional[Tuple[float, List[Tuple[int, float]]]]]] = (
+            [None] * len(self.prompt_token_ids) if self.sampling_params.prompt_logprobs is not None else None)
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -152,6 +159,7 @@ class RequestOutput:
     kv_transfer_params: Optional[Dict[str, Any]] = None
     logprobs: Optional[List[Tuple[float, List[Tuple[int, float]]]]] = None    # per output token, when asked for
     text: Optional[str] = None             # decoded output, when a tokenizer is at hand
+    prompt_logprobs: Optional[List[Optional[Tuple[float, List[Tuple[int, float]]]]]] = None   # per prompt token
 
     @classmethod
     def from_request(cls, r: Request) -> "RequestOutput":
@@ -168,4 +176,5 @@ class RequestOutput:
             tpot = (r.finish_time - r.first_token_time) / (len(r.output_token_ids) - 1)
         return cls(r.request_id, list(r.prompt_token_ids), list(r.output_token_ids), r.is_finished,
                    reason, ttft, tpot, r.kv_transfer_params,
-                   list(r.logprobs[: len(r.output_token_ids)]) if r.sampling_params.logprobs else None)
+                   list(r.logprobs[: len(r.output_token_ids)]) if r.sampling_params.logprobs else None,
+                   prompt_logprobs=list(r.prompt_logprobs) if r.prompt_logprobs is not None else None)

@@ -133,7 +133,8 @@ class Scheduler:
         from .block_manager import chain_block_hashes
         bs = self.block_size
         usable = (req.num_tokens - 1) // bs
-        if usable <= 0:
+        # a request that wants the log-probabilities of its prompt has to run every prompt row
+        if usable <= 0 or req.sampling_params.prompt_logprobs is not None:
             return False
         toks = req.all_token_ids
         req._block_hashes = chain_block_hashes(toks, bs, getattr(req, "_block_hashes", None), upto_blocks=usable)

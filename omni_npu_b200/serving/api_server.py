@@ -268,7 +268,9 @@ def sampling_from_body(body: Dict[str, Any], tokenizer=None) -> SamplingParams:
                           frequency_penalty=float(body.get("frequency_penalty") or 0.0),
                           repetition_penalty=float(body.get("repetition_penalty") or 1.0),
                           thinking_token_budget=body.get("thinking_token_budget"),
-                          logprobs=_logprobs_from_body(body), structured=structured_spec_from_body(body),
+                          logprobs=_logprobs_from_body(body),
+                          prompt_logprobs=(int(body["prompt_logprobs"]) if body.get("prompt_logprobs") is not None else None),
+                          structured=structured_spec_from_body(body),
                           priority=int(body.get("priority") or 0), min_tokens=int(body.get("min_tokens") or 0),
                           min_p=float(body.get("min_p") or 0.0), allowed_token_ids=body.get("allowed_token_ids") or None,
                           bad_words_token_ids=bad_words_token_ids(body.get("bad_words"), tokenizer),
@@ -426,7 +428,14 @@ def build_app(llm, tokenizer=None, model_name: str = "model", reasoning_parser=N
                   "token_ids": out.output_token_ids, "token_logprobs": [e[0] for e in out.logprobs],
                   "top_logprobs": [{(decode([i]) if tokenizer is not None else str(i)): v for i, v in e[1]}
                                    for e in out.logprobs]}
-        return {"index": index, "text": _text(out), "token_ids": out.output_token_ids, "logprobs": lp,
+        if out.prompt_logprobs is not None:
+            # one entry per prompt token: null for the first, else {token: log-probability} of the token and its alternatives
+            name = (lambda i: decode([i])) if tokenizer is not None else str
+            extra = {"prompt_logprobs": [None if e is None else {name(t): e[0], **{name(i): v for i, v in e[1]}}
+                                         for t, e in zip(out.prompt_token_ids, out.prompt_logprobs)]}
+        else:
+            extra = {}
+        return {**extra, "index": index, "text": _text(out), "token_ids": out.output_token_ids, "logprobs": lp,
                 "finish_reason": out.finish_reason or "stop"}
 
     @app.post("/v1/completions")

@@ -83,6 +83,11 @@ class ModelRunner:
         self.structured = None      # sample/structured.py manager, once a tokenizer is known
         self.last_logprobs: Dict[int, Tuple[float, List[Tuple[int, float]]]] = {}   # of the last step, by index in its seqs
         self._lp_capture = None
+        # log-probabilities of prompt tokens: the plan of the step in flight, what it captured on the
+        # device, and the result by index in the step's seqs: (position of the first entry, entries)
+        self._plp_plan = None
+        self._plp_capture = None
+        self.last_prompt_logprobs: Dict[int, Tuple[int, list]] = {}
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=device)
         self.d2h_bytes_last = 0
         self.kv_connector = None
@@ -236,6 +241,8 @@ class ModelRunner:
             idx = views["logits_idx"][:num_samples].long() if md.is_prefill else None
             hidden = hidden_all.index_select(0, idx) if idx is not None else hidden_all[:num_samples]
             logits = self.model.compute_logits(hidden)
+            if self._plp_plan:
+                self._capture_prompt_logprobs(hidden_all)
             if self._logits_fn is not None:
                 logits = self._logits_fn(logits)
             # (no step offset: the staged seed of a row already carries the index of the token it samples)
@@ -618,6 +625,47 @@ class ModelRunner:
             return logits
         return fn
 
+    def _plan_prompt_logprobs(self, out: SchedulerOutput):
+        """Rows of a prefill step whose next prompt token is known and asked about:
+        [(index in seqs, first row, rows, position of the first predicted token, k)].  A step's rows
+        are its sequences' new tokens in order; row j of a sequence fed from ``start`` predicts the
+        prompt token at ``start + j + 1``."""
+        plan, row = [], 0
+        for i, q in enumerate(out.seqs):
+            k = q.request.sampling_params.prompt_logprobs
+            if k is not None:
+                rows = min(q.num_new_tokens, q.request.num_prompt_tokens - 1 - q.start)
+                if rows > 0:
+                    plan.append((i, row, rows, q.start + 1, int(k)))
+            row += q.num_new_tokens
+        return plan or None
+
+    def _capture_prompt_logprobs(self, hidden_all: torch.Tensor) -> None:
+        """Log-probabilities of the planned prompt tokens and their most likely alternatives, kept on
+        the device until the step's tokens are read (LM head on at most 1024 rows at a time)."""
+        cap = []
+        for i, row, rows, first, k, targets in self._plp_plan:
+            lps, tops = [], []
+            for a in range(0, rows, 1024):
+                b = min(rows, a + 1024)
+                lsm = torch.log_softmax(self.model.compute_logits(hidden_all[row + a: row + b]).float(), dim=-1)
+                lps.append(lsm.gather(1, targets[a:b].unsqueeze(1)).squeeze(1))
+                if k > 0:
+                    tops.append(lsm.topk(k, dim=-1))
+            cap.append((i, first, torch.cat(lps), torch.cat([t.values for t in tops]) if tops else None,
+                        torch.cat([t.indices for t in tops]) if tops else None))
+        self._plp_capture = cap
+
+    def _collect_prompt_logprobs(self) -> Dict[int, Tuple[int, list]]:
+        cap, self._plp_capture = self._plp_capture, None
+        res = {}
+        for i, first, lp, vals, ids in cap or ():
+            lp = lp.tolist()
+            vals = vals.tolist() if vals is not None else [[]] * len(lp)
+            ids = ids.tolist() if ids is not None else [[]] * len(lp)
+            res[i] = (first, [(lp[j], list(zip(ids[j], vals[j]))) for j in range(len(lp))])
+        return res
+
     def _collect_logprobs(self, seqs, tokens) -> Dict[int, Tuple[float, List[Tuple[int, float]]]]:
         """Log-probabilities of this step's sampled tokens for the sequences that asked:
         {index in seqs: (log-probability of the token, [(token id, log-probability)] of the top k,
@@ -662,10 +710,18 @@ class ModelRunner:
         ev = None
         self.last_logprobs = {}
         self._logits_fn = self._make_logits_fn(out.seqs) if out.kind != "spec_decode" else None
+        self.last_prompt_logprobs = {}
+        if out.kind == "prefill" and any(q.request.sampling_params.prompt_logprobs is not None for q in out.seqs):
+            plan = self._plan_prompt_logprobs(out) or []
+            self._plp_plan = [p + (torch.tensor(out.seqs[p[0]].request.prompt_token_ids[p[3]: p[3] + p[2]],
+                                                dtype=torch.long, device=self.device),) for p in plan]
         try:
-            return self._execute_scheduled(out, ib, n, ev)
+            tokens = self._execute_scheduled(out, ib, n, ev)
+            self.last_prompt_logprobs = self._collect_prompt_logprobs()
+            return tokens
         finally:
             self._logits_fn = None
+            self._plp_plan = self._plp_capture = None
 
     def _execute_scheduled(self, out: SchedulerOutput, ib, n: int, ev) -> List[int]:
         if out.kind == "spec_decode":

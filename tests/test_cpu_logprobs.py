@@ -110,3 +110,52 @@ def test_server_turns_bad_words_into_token_sequences():
     assert sampling_from_body({}, None).bad_words_token_ids is None
     with pytest.raises(ValueError, match="tokenizer"):
         sampling_from_body({"bad_words": ["abc"]}, None)
+
+
+def test_prompt_logprobs_match_a_plain_forward_pass_across_chunks():
+    prompt = list(range(3, 3 + 23))
+    # a token budget of 8 splits the prompt into three chunks
+    llm = LLM(model=_cfg(), device="cpu", max_num_seqs=4, max_num_batched_tokens=8, max_model_len=128, block_size=4,
+              num_gpu_blocks=64, seed=3, enable_prefix_caching=True)
+    out = llm.generate([prompt, [7, 8, 9]], [SamplingParams(max_tokens=2, ignore_eos=True, prompt_logprobs=3),
+                                             SamplingParams(max_tokens=2, ignore_eos=True)])
+    plp = out[0].prompt_logprobs
+    assert out[1].prompt_logprobs is None and len(plp) == len(prompt) and plp[0] is None
+    model = llm.engine.worker.model_runner.model
+    # the oracle: one unchunked pass of the same engine over the prompt, reading every row's logits
+    one = LLM(model=_cfg(), device="cpu", max_num_seqs=1, max_num_batched_tokens=64, max_model_len=128, block_size=4,
+              num_gpu_blocks=64, seed=3)
+    one.engine.worker.model_runner.model.load_state_dict(model.state_dict())
+    ref = one.generate([prompt], SamplingParams(max_tokens=1, ignore_eos=True, prompt_logprobs=0))[0].prompt_logprobs
+    for j in range(1, len(prompt)):
+        lp, top = plp[j]
+        assert lp == pytest.approx(ref[j][0], abs=1e-4) and ref[j][1] == []
+        assert len(top) == 3 and top[0][1] >= top[1][1] >= top[2][1] and lp <= top[0][1] + 1e-6
+    # an independent path: force prompt[j] as the first generated token after prompt[:j] and read its log-probability
+    for j in (1, 9, 22):
+        forced = one.generate([prompt[:j]], SamplingParams(max_tokens=1, ignore_eos=True, logprobs=1,
+                                                           allowed_token_ids=[prompt[j]]))[0]
+        assert forced.output_token_ids == [prompt[j]]
+        assert forced.logprobs[0][0] == pytest.approx(plp[j][0], abs=1e-4)
+    # asking again hits no cached prefix (such requests always run their whole prompt) and gives the same values
+    again = llm.generate([prompt], SamplingParams(max_tokens=1, ignore_eos=True, prompt_logprobs=0))[0].prompt_logprobs
+    assert [e[0] for e in again[1:]] == pytest.approx([e[0] for e in plp[1:]], abs=1e-5)
+    with pytest.raises(ValueError, match="prompt_logprobs"):
+        llm.generate([prompt], SamplingParams(max_tokens=1, prompt_logprobs=21))
+
+
+def test_server_returns_prompt_logprobs():
+    from starlette.testclient import TestClient
+
+    from omni_npu_b200.serving.api_server import build_app
+    app = build_app(_llm(), None, "tiny")
+    with TestClient(app) as c:
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 2, "ignore_eos": True, "prompt_logprobs": 2})
+        assert r.status_code == 200, r.text
+        plp = r.json()["choices"][0]["prompt_logprobs"]
+        assert plp[0] is None and len(plp) == 4
+        assert all("%d" % t in e and 2 <= len(e) <= 3 and max(e.values()) <= 0.0 for t, e in zip([6, 7, 8], plp[1:]))
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 2, "ignore_eos": True})
+        assert "prompt_logprobs" not in r.json()["choices"][0]
+        assert c.post("/v1/completions", json={"prompt": [5, 6], "max_tokens": 1, "prompt_logprobs": 50}).status_code == 400
+    app.state.engine_loop.shutdown()
