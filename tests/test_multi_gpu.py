@@ -66,7 +66,7 @@ def test_nvls_multimem_all_reduce_matches_nccl():
     for r in res:
         for name, err in r["max_err"].items():
             assert err <= (0.13 if "fused" in name else 0.02), (name, err)
-    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    out = os.environ.get("OMNI_B200_TEST_RESULTS_DIR", "")
     if os.path.isdir(out):
         with open(os.path.join(out, f"nvls_all_reduce_{world}gpu.json"), "w") as f:
             json.dump(res[0]["us"], f, indent=1)
@@ -108,7 +108,7 @@ def test_expert_parallel_dispatch_and_combine_device_times():
         res = run_ranks("ep_timing", world, d, device="cuda", timeout=600)
     for name, row in res[0].items():
         assert row["dispatch_bf16_us"] > 0 and row["combine_us"] > 0, (name, row)
-    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    out = os.environ.get("OMNI_B200_TEST_RESULTS_DIR", "")
     if os.path.isdir(out):
         with open(os.path.join(out, f"ep_dispatch_combine_{world}gpu.json"), "w") as f:
             json.dump(res[0], f, indent=1)
@@ -120,7 +120,7 @@ def test_kv_blocks_pulled_gpu_to_gpu_are_byte_exact():
         res = run_ranks("kv_pull", 2, d, device="cuda", timeout=300)
     assert res[1]["byte_exact"]
     print("kv pull GB/s:", res[1]["gbs"])
-    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "gpurun_out")
+    out = os.environ.get("OMNI_B200_TEST_RESULTS_DIR", "")
     if os.path.isdir(out):
         with open(os.path.join(out, "kv_pull_2gpu.json"), "w") as f:
             json.dump({k: res[1].get(k) for k in ("gbs", "gbs_small", "byte_exact")}, f)
